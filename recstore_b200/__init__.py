@@ -1,0 +1,17 @@
+"""recstore_b200: a Blackwell-native (sm_100a) embedding parameter server and
+recommendation / knowledge-graph training framework with the capabilities of RecStore.
+
+Sub-packages
+------------
+``ops``       native kernels (tcgen05 GEMM, fused embedding forward/backward, interaction, losses)
+``parallel``  in-box NVLink transport: peer windows, flags, all-reduce, sharding policies
+``models``    DLRM (dot / DCNv2), SimpleDLRM, knowledge-graph embedding models
+``utils``     synthetic data, timers, logging
+``baseline``  PyTorch + NCCL restatements of the reference algorithms (oracle and measured baseline)
+
+The native library is built in-tree (``python -m recstore_b200.build``) and bound with ctypes.
+"""
+__version__ = "0.1.0"
+
+from . import _lib  # noqa: F401
+from ._lib import RecStoreError, DeviceStatusError  # noqa: F401

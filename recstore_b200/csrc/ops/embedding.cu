@@ -1,0 +1,380 @@
+// Fused embedding forward and backward for model-parallel embedding shards on sm_100a.
+//
+// Forward (rs_emb_forward): for every (local table, sample) bag it resolves the ids to rows of
+// the shard (direct index or hash-table probe), sum-pools the rows (optional per-sample
+// weights) and stores the pooled vector STRAIGHT INTO THE DESTINATION RANK'S BUFFER through a
+// peer pointer: destination rank = sample / B_local, address = dst[rank] + (sample % B_local) *
+// row_stride + dst_col[table].  With peer windows mapped over NVLink this is the table-wise
+// all-to-all of the reference (nn.EmbeddingBag per table, src/executable/dlrm/dlrm_model.py:
+// 255-314, followed by all_to_all_single, extend_distributed.py:389-426) done by the gather
+// kernel itself, with no pack/unpack and no collective call.  It also replaces the plain
+// gather kernels uva_cache_query / UVAQueryKernel / LookupKernel
+// (src/framework/pytorch/recstore_pytorch.cu:12-37, src/storage/gpu_cache/gpu_cache_nohash.cu:
+// 2-12, static_hash_table.cu:223-268).
+//
+// Backward (rs_emb_backward): consumes per-bag gradients (as pushed by the peers into this
+// rank's gradient window), segment-reduces duplicate rows inside each 256-occurrence group
+// with a shared-memory hash + linked lists, and applies SGD or row-wise Adagrad in place with
+// one vector atomic per (group, distinct row).  Semantics follow the reference optimizers
+// (src/python/pytorch/recstore/DistOpt.py:511-557): state[row] += sum over occurrences of
+// mean(g^2); W[row] -= lr * sum over occurrences of g / (sqrt(state[row]) + eps), with the
+// state read after all occurrences of the step were accumulated (hence two passes).
+//
+// No kernel here traps: out-of-range ids set RS_DEV_OOB_ROW in the status word and are skipped.
+#include <cuda_bf16.h>
+#include "common/rs_common.h"
+#include "kv/hash_table.cuh"
+
+namespace {
+
+struct EmbFwdArgs {
+  const float* weight;
+  const long long* table_base;   // [T] first row of each local table inside `weight`
+  const long long* table_rows;   // [T] number of rows of each local table
+  const long long* indices;      // [nnz]
+  const long long* offsets;      // [T*B + 1] or null when hotness is fixed per table
+  const int* hotness;            // [T] used when offsets == null
+  const long long* hot_base;     // [T] start of table t's ids inside `indices` when offsets == null
+  const float* psw;              // optional per-sample weights [nnz]
+  int T, B, D, B_local;
+  void* const* dst;              // [world] destination base pointers
+  long long dst_row_stride;      // elements
+  const int* dst_col;            // [T] element offset of the table's feature inside a destination row
+  int out_bf16;
+  long long* row_idx;            // optional [nnz]: resolved row per id (-1 if invalid)
+  int* occ2bag;                  // optional [nnz]
+  int use_hash;
+  rs::HashTableView ht;
+  unsigned long long* status;
+};
+
+constexpr int kMaxChunks = 4;  // D <= 512
+
+__global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
+  const int warps_per_block = blockDim.x >> 5;
+  const long long bag = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const long long nbags = static_cast<long long>(a.T) * a.B;
+  if (bag >= nbags) return;
+  const int t = static_cast<int>(bag / a.B);
+  const int b = static_cast<int>(bag % a.B);
+  long long beg, end;
+  if (a.offsets) {
+    beg = a.offsets[bag];
+    end = a.offsets[bag + 1];
+  } else {
+    const int h = a.hotness[t];
+    beg = a.hot_base[t] + static_cast<long long>(b) * h;
+    end = beg + h;
+  }
+  const long long base = a.table_base[t];
+  const long long nrows = a.table_rows[t];
+  const int nvec = a.D >> 2;  // float4 per row
+  float4 acc[kMaxChunks];
+#pragma unroll
+  for (int c = 0; c < kMaxChunks; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  for (long long i0 = beg; i0 < end; i0 += 32) {
+    const int n = static_cast<int>(min(32ll, end - i0));
+    long long my_row = -1;
+    float my_w = 1.f;
+    if (lane < n) {
+      const long long id = a.indices[i0 + lane];
+      if (a.use_hash) {
+        const int r = rs::ht_find(a.ht, static_cast<unsigned long long>(id));
+        my_row = r;  // absent key -> -1 -> contributes zeros
+      } else if (id >= 0 && id < nrows) {
+        my_row = base + id;
+      } else if (a.status) {
+        atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
+      }
+      if (a.psw) my_w = a.psw[i0 + lane];
+      if (a.row_idx) a.row_idx[i0 + lane] = my_row;
+      if (a.occ2bag) a.occ2bag[i0 + lane] = static_cast<int>(bag);
+    }
+    int j = 0;
+    for (; j + 4 <= n; j += 4) {
+      long long r[4];
+      float w[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        r[u] = __shfl_sync(0xffffffffu, my_row, j + u);
+        w[u] = __shfl_sync(0xffffffffu, my_w, j + u);
+      }
+#pragma unroll
+      for (int c = 0; c < kMaxChunks; ++c) {
+        const int v = lane + c * 32;
+        if (v < nvec) {
+          float4 x[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            x[u] = r[u] >= 0 ? __ldg(reinterpret_cast<const float4*>(a.weight + r[u] * a.D) + v)
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            acc[c].x += w[u] * x[u].x; acc[c].y += w[u] * x[u].y;
+            acc[c].z += w[u] * x[u].z; acc[c].w += w[u] * x[u].w;
+          }
+        }
+      }
+    }
+    for (; j < n; ++j) {
+      const long long r = __shfl_sync(0xffffffffu, my_row, j);
+      const float w = __shfl_sync(0xffffffffu, my_w, j);
+      if (r < 0) continue;
+#pragma unroll
+      for (int c = 0; c < kMaxChunks; ++c) {
+        const int v = lane + c * 32;
+        if (v < nvec) {
+          const float4 x = __ldg(reinterpret_cast<const float4*>(a.weight + r * a.D) + v);
+          acc[c].x += w * x.x; acc[c].y += w * x.y; acc[c].z += w * x.z; acc[c].w += w * x.w;
+        }
+      }
+    }
+  }
+
+  const int dst_rank = b / a.B_local;
+  const long long off = static_cast<long long>(b - dst_rank * a.B_local) * a.dst_row_stride + a.dst_col[t];
+#pragma unroll
+  for (int c = 0; c < kMaxChunks; ++c) {
+    const int v = lane + c * 32;
+    if (v < nvec) {
+      if (a.out_bf16) {
+        __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(a.dst[dst_rank]) + off;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc[c].x, acc[c].y);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(acc[c].z, acc[c].w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        *(reinterpret_cast<uint2*>(d) + v) = o;
+      } else {
+        float* d = reinterpret_cast<float*>(a.dst[dst_rank]) + off;
+        *(reinterpret_cast<float4*>(d) + v) = acc[c];
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ backward
+struct EmbBwdArgs {
+  float* weight;
+  float* state;                  // [rows] row-wise Adagrad accumulator (null for SGD)
+  const long long* row_idx;      // [nnz] resolved rows (-1 = skip)
+  const int* occ2bag;            // [nnz] or null (bag == occurrence)
+  long long nnz;
+  const void* grad;              // per-bag gradients
+  const int* grad_col;           // [T] element offset of the table's slice inside a gradient row, or null
+  long long grad_row_stride;     // elements between samples
+  int B, D, grad_bf16;
+  const float* psw;
+  float lr, eps;
+  int optimizer;                 // 0 = SGD, 1 = row-wise Adagrad
+  int pass;                      // Adagrad: 1 = accumulate state, 2 = apply; SGD: ignored
+  long long total_rows;
+  unsigned long long* status;
+};
+
+constexpr int kGroup = 256;
+constexpr int kSlots = 512;
+
+__global__ void __launch_bounds__(kGroup) emb_bwd_kernel(const EmbBwdArgs a) {
+  __shared__ long long s_key[kSlots];
+  __shared__ int s_head[kSlots];
+  __shared__ int s_next[kGroup];
+  __shared__ int s_leader_slot[kGroup];
+  __shared__ int s_nleaders;
+
+  const int tid = threadIdx.x;
+  const long long g0 = static_cast<long long>(blockIdx.x) * kGroup;
+  for (int s = tid; s < kSlots; s += kGroup) {
+    s_key[s] = -1;
+    s_head[s] = -1;
+  }
+  if (tid == 0) s_nleaders = 0;
+  __syncthreads();
+
+  long long row = -1;
+  if (g0 + tid < a.nnz) {
+    row = a.row_idx[g0 + tid];
+    if (row >= a.total_rows) {
+      if (a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
+      row = -1;
+    }
+  }
+  if (row >= 0) {
+    unsigned s = static_cast<unsigned>(rs::ht_hash(static_cast<unsigned long long>(row))) & (kSlots - 1);
+    for (int p = 0; p < kSlots; ++p) {
+      const long long prev = static_cast<long long>(atomicCAS(reinterpret_cast<unsigned long long*>(&s_key[s]),
+                                                               static_cast<unsigned long long>(-1ll),
+                                                               static_cast<unsigned long long>(row)));
+      if (prev == -1) {  // first occurrence of this row in the group: becomes a leader slot
+        const int k = atomicAdd(&s_nleaders, 1);
+        s_leader_slot[k] = static_cast<int>(s);
+      }
+      if (prev == -1 || prev == row) {
+        s_next[tid] = atomicExch(&s_head[s], tid);
+        break;
+      }
+      s = (s + 1) & (kSlots - 1);
+    }
+  }
+  __syncthreads();
+
+  const int warp = tid >> 5, lane = tid & 31;
+  const int nvec = a.D >> 2;
+  const int nleaders = s_nleaders;
+  const float inv_d = 1.f / static_cast<float>(a.D);
+  for (int k = warp; k < nleaders; k += kGroup / 32) {
+    const int slot = s_leader_slot[k];
+    const long long r = s_key[slot];
+    float4 acc[kMaxChunks];
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float sq = 0.f;
+    for (int j = s_head[slot]; j >= 0; j = s_next[j]) {
+      const long long occ = g0 + j;
+      const long long bag = a.occ2bag ? a.occ2bag[occ] : occ;
+      const int t = static_cast<int>(bag / a.B);
+      const long long b = bag % a.B;
+      const long long goff = b * a.grad_row_stride + (a.grad_col ? a.grad_col[t] : 0);
+      const float w = a.psw ? a.psw[occ] : 1.f;
+#pragma unroll
+      for (int c = 0; c < kMaxChunks; ++c) {
+        const int v = lane + c * 32;
+        if (v < nvec) {
+          float4 g;
+          if (a.grad_bf16) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.grad) + goff) + v);
+            const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+            const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+            const float2 flo = __bfloat1622float2(lo), fhi = __bfloat1622float2(hi);
+            g = make_float4(flo.x, flo.y, fhi.x, fhi.y);
+          } else {
+            g = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.grad) + goff) + v);
+          }
+          g.x *= w; g.y *= w; g.z *= w; g.w *= w;
+          acc[c].x += g.x; acc[c].y += g.y; acc[c].z += g.z; acc[c].w += g.w;
+          sq += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
+        }
+      }
+    }
+    if (a.optimizer == 1 && a.pass == 1) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if (lane == 0) atomicAdd(&a.state[r], sq * inv_d);
+      continue;
+    }
+    float scale = -a.lr;
+    if (a.optimizer == 1) {
+      const float st = __ldcv(&a.state[r]);
+      scale = -a.lr / (sqrtf(st) + a.eps);
+    }
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int v = lane + c * 32;
+      if (v < nvec) {
+        float4 u = make_float4(scale * acc[c].x, scale * acc[c].y, scale * acc[c].z, scale * acc[c].w);
+        atomicAdd(reinterpret_cast<float4*>(a.weight + r * a.D) + v, u);
+      }
+    }
+  }
+}
+
+// Plain row gather / scatter used by the PS get / put verbs: out[i] = W[rows[i]] (zeros when rows[i] < 0).
+__global__ void rows_gather_kernel(const float* __restrict__ w, const long long* __restrict__ rows, long long n, int D,
+                                   float* __restrict__ out) {
+  const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= n) return;
+  const int lane = threadIdx.x & 31;
+  const long long r = rows[i];
+  for (int v = lane; v < (D >> 2); v += 32) {
+    const float4 x = r >= 0 ? __ldg(reinterpret_cast<const float4*>(w + r * D) + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    *(reinterpret_cast<float4*>(out + i * D) + v) = x;
+  }
+}
+__global__ void rows_scatter_kernel(float* __restrict__ w, const long long* __restrict__ rows, long long n, int D,
+                                    const float* __restrict__ in) {
+  const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= n) return;
+  const int lane = threadIdx.x & 31;
+  const long long r = rows[i];
+  if (r < 0) return;
+  for (int v = lane; v < (D >> 2); v += 32)
+    *(reinterpret_cast<float4*>(w + r * D) + v) = __ldg(reinterpret_cast<const float4*>(in + i * D) + v);
+}
+
+}  // namespace
+
+RS_API int rs_emb_forward(const float* weight, const long long* table_base, const long long* table_rows,
+                          const long long* indices, const long long* offsets, const int* hotness,
+                          const long long* hot_base, const float* psw, int T, int B, int D, int B_local,
+                          void* const* dst, long long dst_row_stride, const int* dst_col, int out_bf16,
+                          long long* row_idx, int* occ2bag, const rs::HashTableView* ht,
+                          unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(weight && table_base && table_rows && indices && dst && dst_col, "rs_emb_forward: null argument");
+  RS_REQUIRE(offsets || (hotness && hot_base), "rs_emb_forward: need offsets or fixed hotness");
+  RS_REQUIRE(D % 4 == 0 && D > 0 && D <= 128 * kMaxChunks, "rs_emb_forward: D=%d must be a multiple of 4, <= 512", D);
+  RS_REQUIRE(T >= 0 && B >= 0 && B_local > 0, "rs_emb_forward: bad sizes");
+  if (T == 0 || B == 0) return RS_OK;
+  EmbFwdArgs a;
+  a.weight = weight; a.table_base = table_base; a.table_rows = table_rows; a.indices = indices;
+  a.offsets = offsets; a.hotness = hotness; a.hot_base = hot_base; a.psw = psw;
+  a.T = T; a.B = B; a.D = D; a.B_local = B_local; a.dst = dst; a.dst_row_stride = dst_row_stride;
+  a.dst_col = dst_col; a.out_bf16 = out_bf16; a.row_idx = row_idx; a.occ2bag = occ2bag;
+  a.use_hash = ht != nullptr;
+  if (ht) a.ht = *ht; else memset(&a.ht, 0, sizeof(a.ht));
+  a.status = status;
+  const long long nbags = static_cast<long long>(T) * B;
+  const int wpb = 8;
+  const long long grid = (nbags + wpb - 1) / wpb;
+  RS_REQUIRE(grid < (1ll << 31), "rs_emb_forward: too many bags");
+  emb_fwd_kernel<<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+// optimizer: 0 SGD (one launch), 1 row-wise Adagrad (two launches: state pass, apply pass).
+RS_API int rs_emb_backward(float* weight, float* state, long long total_rows, const long long* row_idx,
+                           const int* occ2bag, long long nnz, const void* grad, const int* grad_col,
+                           long long grad_row_stride, int B, int D, int grad_bf16, const float* psw, float lr,
+                           float eps, int optimizer, unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(weight && row_idx && grad, "rs_emb_backward: null argument");
+  RS_REQUIRE(optimizer == 0 || (optimizer == 1 && state), "rs_emb_backward: row-wise Adagrad needs a state tensor");
+  RS_REQUIRE(D % 4 == 0 && D > 0 && D <= 128 * kMaxChunks, "rs_emb_backward: D=%d must be a multiple of 4, <= 512", D);
+  RS_REQUIRE(B > 0, "rs_emb_backward: B must be positive");
+  if (nnz == 0) return RS_OK;
+  EmbBwdArgs a;
+  a.weight = weight; a.state = state; a.row_idx = row_idx; a.occ2bag = occ2bag; a.nnz = nnz; a.grad = grad;
+  a.grad_col = grad_col; a.grad_row_stride = grad_row_stride; a.B = B; a.D = D; a.grad_bf16 = grad_bf16;
+  a.psw = psw; a.lr = lr; a.eps = eps; a.optimizer = optimizer; a.total_rows = total_rows; a.status = status;
+  const long long grid = (nnz + kGroup - 1) / kGroup;
+  RS_REQUIRE(grid < (1ll << 31), "rs_emb_backward: too many occurrences");
+  if (optimizer == 1) {
+    a.pass = 1;
+    emb_bwd_kernel<<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
+    RS_LAUNCH_CHECK();
+    a.pass = 2;
+  } else {
+    a.pass = 0;
+  }
+  emb_bwd_kernel<<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+RS_API int rs_rows_gather(const float* weight, const long long* rows, long long n, int D, float* out,
+                          cudaStream_t stream) {
+  RS_REQUIRE(weight && rows && out && D % 4 == 0, "rs_rows_gather: bad argument");
+  if (n == 0) return RS_OK;
+  rows_gather_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(weight, rows, n, D, out);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+RS_API int rs_rows_scatter(float* weight, const long long* rows, long long n, int D, const float* in,
+                           cudaStream_t stream) {
+  RS_REQUIRE(weight && rows && in && D % 4 == 0, "rs_rows_scatter: bad argument");
+  if (n == 0) return RS_OK;
+  rows_scatter_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(weight, rows, n, D, in);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}

@@ -1,0 +1,456 @@
+// bf16 GEMM for sm_100a: tcgen05.mma with the accumulator in TMEM, operands staged in
+// shared memory by TMA (per-CTA loads only), persistent warp-specialised CTAs.
+//
+// It replaces the cuBLAS calls behind nn.Linear forward / dgrad / wgrad of the
+// reference's MLP stacks (src/executable/dlrm/dlrm_model.py:72-110,
+// model_zoo/dlrm.py:132-141, 407-425) and the two skinny GEMMs of the low-rank
+// DCNv2 cross layer (model_zoo/dlrm.py:261-286).
+//
+// Two operand layouts:
+//   mode 0 ("TN"):  D[M,N] = A[M,K] . B[N,K]^T   A and B row-major, K contiguous
+//                   (forward: A = activations, B = W;  dgrad: A = dY, B = W^T)
+//   mode 1 ("NT"):  D[M,N] = A[K,M]^T . B[K,N]   A and B row-major, reduction over rows
+//                   (wgrad: A = dY[batch,N_out], B = X[batch,K_in]); split over the
+//                   reduction with fp32 atomic accumulation into D.
+// Epilogues (fused into the TMEM read-back):
+//   0  D = acc (+ bias[n])                       bf16 store
+//   1  D = relu(acc + bias[n])                   bf16 store
+//   2  D = acc * (aux[m,n] > 0)                  bf16 store (ReLU backward)
+//   3  D += acc                                  fp32 atomic add (split reduction)
+//   4  D = acc (+ bias[n])                       fp32 store
+//   5  D = x0[m,n] * (acc + bias[n]) + aux[m,n]  bf16 store (DCNv2 cross update)
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs,
+// warps 2..5 read the accumulator back (one TMEM lane quadrant each).  Two
+// accumulators are kept in TMEM so that the epilogue of tile i overlaps the main
+// loop of tile i+1.  Every mbarrier wait is bounded; on give-up the kernel sets
+// RS_DEV_WAIT_TIMEOUT in the status word, frees TMEM and returns.
+#include <cuda_bf16.h>
+#include <mutex>
+#include <unordered_map>
+#include "common/ptx.cuh"
+#include "common/rs_common.h"
+
+namespace {
+using namespace rs::ptx;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+constexpr uint32_t kABytes = BM * BK * 2;  // 16 KiB per stage
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmArgs {
+  int M, N, K;          // logical problem (see modes above); K = reduction length
+  int bn;               // tile width in N (multiple of 32, <= 256)
+  int stages;
+  int tiles_m, tiles_n;
+  int splits;           // reduction splits (mode 1 / epilogue 3), else 1
+  int kblocks;          // ceil(K / 64)
+  int epi;
+  int ldd, ldaux, ldx0;
+  void* D;
+  const float* bias;
+  const __nv_bfloat16* aux;
+  const __nv_bfloat16* x0;
+  unsigned long long* status;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int stages = g.stages;
+  const uint32_t b_bytes = static_cast<uint32_t>(g.bn) * BK * 2;
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + static_cast<size_t>(stages) * kABytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sB + static_cast<size_t>(stages) * b_bytes);
+  uint64_t* empty = full + stages;
+  uint64_t* tfull = empty + stages;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles = g.tiles_m * g.tiles_n;
+  const int items = tiles * g.splits;
+  const int kb_per_split = (g.kblocks + g.splits - 1) / g.splits;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int last_stage = -1;
+      uint32_t last_phase = 0;
+      for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
+        const int tile = it % tiles;
+        const int split = it / tiles;
+        const int m0 = (tile / g.tiles_n) * BM;
+        const int n0 = (tile % g.tiles_n) * g.bn;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(g.kblocks, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&full[stage], kABytes + b_bytes);
+          uint8_t* a_dst = sA + static_cast<size_t>(stage) * kABytes;
+          uint8_t* b_dst = sB + static_cast<size_t>(stage) * b_bytes;
+          if (MODE == 0) {
+            tma_load_2d(a_dst, &tma_a, &full[stage], kb * BK, m0);
+            tma_load_2d(b_dst, &tma_b, &full[stage], kb * BK, n0);
+          } else {
+            for (int h = 0; h < BM / 64; ++h) tma_load_2d(a_dst + h * 8192, &tma_a, &full[stage], m0 + h * 64, kb * BK);
+            for (int h = 0; h < g.bn / 64; ++h) tma_load_2d(b_dst + h * 8192, &tma_b, &full[stage], n0 + h * 64, kb * BK);
+          }
+          last_stage = stage;
+          last_phase = phase;
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && last_stage >= 0) {
+        // Leaving early: let the copies already in flight land before the CTA's shared memory goes away.
+        mbar_wait(&full[last_stage], last_phase, nullptr, 1u << 16);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, static_cast<uint32_t>(g.bn), MODE, MODE);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
+        const int split = it / tiles;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(g.kblocks, kb0 + kb_per_split);
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * g.bn);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(sA + static_cast<size_t>(stage) * kABytes);
+          const uint32_t b_addr = smem_u32(sB + static_cast<size_t>(stage) * b_bytes);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            uint64_t ad, bd;
+            if (MODE == 0) {
+              // K-major, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart; a K step of 16
+              // elements moves the start address by 32 B inside the swizzled row.
+              ad = make_smem_desc(a_addr + k * 32, 16, 1024, 2);
+              bd = make_smem_desc(b_addr + k * 32, 16, 1024, 2);
+            } else {
+              // MN-major, 128-byte swizzle: each TMA box holds 64 reduction rows x 64 columns; 8-row
+              // groups are 1024 B apart (SBO), the next 64 columns start one box (8 KiB) later (LBO).
+              ad = make_smem_desc(a_addr + k * 2048, 8192, 1024, 2);
+              bd = make_smem_desc(b_addr + k * 2048, 8192, 1024, 2);
+            }
+            umma_f16(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
+      const int tile = it % tiles;
+      const int m0 = (tile / g.tiles_n) * BM;
+      const int n0 = (tile % g.tiles_n) * g.bn;
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < g.M;
+      for (int c = 0; c < g.bn / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= g.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * g.bn + c * 32), r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (g.epi == 3) {
+          if (row_ok) {
+            float* d = reinterpret_cast<float*>(g.D) + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col0 + j < g.N) atomicAdd(reinterpret_cast<float4*>(d + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+            }
+          }
+          continue;
+        }
+        if (g.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            if (col0 + j < g.N) {
+              const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col0 + j));
+              v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+            }
+          }
+        }
+        if (g.epi == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+        } else if (g.epi == 2 && row_ok) {
+          const __nv_bfloat16* a = g.aux + static_cast<size_t>(row) * g.ldaux + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < g.N) {
+              const uint4 m = __ldg(reinterpret_cast<const uint4*>(a + j));
+              const __nv_bfloat16* mb = reinterpret_cast<const __nv_bfloat16*>(&m);
+#pragma unroll
+              for (int t = 0; t < 8; ++t) v[j + t] = (__bfloat162float(mb[t]) > 0.f) ? v[j + t] : 0.f;
+            }
+          }
+        } else if (g.epi == 5 && row_ok) {
+          const __nv_bfloat16* a = g.aux + static_cast<size_t>(row) * g.ldaux + col0;
+          const __nv_bfloat16* x = g.x0 + static_cast<size_t>(row) * g.ldx0 + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < g.N) {
+              const uint4 ma = __ldg(reinterpret_cast<const uint4*>(a + j));
+              const uint4 mx = __ldg(reinterpret_cast<const uint4*>(x + j));
+              const __nv_bfloat16* pa = reinterpret_cast<const __nv_bfloat16*>(&ma);
+              const __nv_bfloat16* px = reinterpret_cast<const __nv_bfloat16*>(&mx);
+#pragma unroll
+              for (int t = 0; t < 8; ++t) v[j + t] = __bfloat162float(px[t]) * v[j + t] + __bfloat162float(pa[t]);
+            }
+          }
+        }
+        if (row_ok) {
+          if (g.epi == 4) {
+            float* d = reinterpret_cast<float*>(g.D) + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              if (col0 + j < g.N) *reinterpret_cast<float4*>(d + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(g.D) + static_cast<size_t>(row) * g.ldd + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < g.N) {
+                uint4 o;
+                o.x = pack_bf16(v[j], v[j + 1]);
+                o.y = pack_bf16(v[j + 2], v[j + 3]);
+                o.z = pack_bf16(v[j + 4], v[j + 5]);
+                o.w = pack_bf16(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(d + j) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag && g.status) atomicOr(g.status, (unsigned long long)RS_DEV_WAIT_TIMEOUT);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* p; uint64_t rows, cols, ld; uint32_t box_r, box_c;
+  bool operator==(const MapKey& o) const {
+    return p == o.p && rows == o.rows && cols == o.cols && ld == o.ld && box_r == o.box_r && box_c == o.box_c;
+  }
+};
+struct MapHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.p);
+    h = h * 1000003u ^ k.rows; h = h * 1000003u ^ k.cols; h = h * 1000003u ^ k.ld;
+    h = h * 1000003u ^ k.box_r; h = h * 1000003u ^ k.box_c;
+    return h;
+  }
+};
+
+// 2-D bf16 row-major tensor [rows, cols] with leading dimension ld (elements); box = box_r x box_c,
+// 128-byte swizzle, zero fill outside the tensor.
+int make_map_bf16(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_r,
+                  uint32_t box_c) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+  MapKey key{ptr, rows, cols, ld, box_r, box_c};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return RS_OK; }
+  }
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return rs::set_error(RS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15))
+    return rs::set_error(RS_ERR_INVALID, "TMA operand must be 16-byte aligned with a 16-byte multiple row pitch");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_c, box_r};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return rs::set_error(RS_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  std::lock_guard<std::mutex> lk(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = *out;
+  return RS_OK;
+}
+
+int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+}  // namespace
+
+// D = epilogue(A x B) as described at the top of the file.  All leading dimensions in elements.
+// bn / splits: 0 selects automatically.  `status` is a device word that receives RsDevErr bits.
+RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias, const void* aux, const void* x0,
+                        int M, int N, int K, int lda, int ldb, int ldd, int ldaux, int ldx0, int mode, int epi,
+                        int bn, int splits, unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(A && B && D, "rs_gemm_bf16: null operand");
+  RS_REQUIRE(M > 0 && N > 0 && K > 0, "rs_gemm_bf16: empty problem %d %d %d", M, N, K);
+  RS_REQUIRE(mode == 0 || mode == 1, "rs_gemm_bf16: mode must be 0 or 1");
+  RS_REQUIRE(epi >= 0 && epi <= 5, "rs_gemm_bf16: unknown epilogue %d", epi);
+  RS_REQUIRE(N % 32 == 0, "rs_gemm_bf16: N (%d) must be a multiple of 32", N);
+  RS_REQUIRE(mode == 0 || (M % 64 == 0 && N % 64 == 0), "rs_gemm_bf16: mode 1 needs M, N multiples of 64");
+  RS_REQUIRE(epi != 2 || aux, "rs_gemm_bf16: epilogue 2 needs aux");
+  RS_REQUIRE(epi != 5 || (aux && x0), "rs_gemm_bf16: epilogue 5 needs aux and x0");
+  const bool f32_out = (epi == 3 || epi == 4);
+  RS_REQUIRE((ldd * (f32_out ? 4 : 2)) % 16 == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0,
+             "rs_gemm_bf16: D must be 16-byte aligned with a 16-byte multiple pitch");
+  if (bn == 0) {
+    if (N % 256 == 0) bn = 256;
+    else if (N % 128 == 0) bn = 128;
+    else if (N % 64 == 0) bn = 64;
+    else bn = (mode == 0) ? 32 : 64;
+    if (N < bn) bn = N;
+  }
+  RS_REQUIRE(bn % 32 == 0 && bn <= 256 && bn >= 32, "rs_gemm_bf16: bad tile width %d", bn);
+  RS_REQUIRE(mode == 0 || bn % 64 == 0, "rs_gemm_bf16: mode 1 needs a tile width multiple of 64");
+
+  GemmArgs g;
+  g.M = M; g.N = N; g.K = K; g.bn = bn;
+  g.tiles_m = (M + BM - 1) / BM;
+  g.tiles_n = (N + bn - 1) / bn;
+  g.kblocks = (K + BK - 1) / BK;
+  const int sms = num_sms();
+  if (epi == 3) {
+    if (splits == 0) {
+      const int tiles = g.tiles_m * g.tiles_n;
+      splits = (sms + tiles - 1) / tiles;
+      if (splits > g.kblocks) splits = g.kblocks;
+      if (splits < 1) splits = 1;
+    }
+  } else {
+    splits = 1;
+  }
+  // Make every split non-empty.
+  {
+    const int per = (g.kblocks + splits - 1) / splits;
+    splits = (g.kblocks + per - 1) / per;
+  }
+  g.splits = splits;
+  const uint32_t stage_bytes = kABytes + static_cast<uint32_t>(bn) * BK * 2;
+  int stages = static_cast<int>((200u * 1024u) / stage_bytes);
+  if (stages > 8) stages = 8;
+  if (stages < 2) stages = 2;
+  g.stages = stages;
+  g.epi = epi; g.ldd = ldd; g.ldaux = ldaux; g.ldx0 = ldx0;
+  g.D = D; g.bias = bias;
+  g.aux = reinterpret_cast<const __nv_bfloat16*>(aux);
+  g.x0 = reinterpret_cast<const __nv_bfloat16*>(x0);
+  g.status = status;
+
+  CUtensorMap ma, mb;
+  int rc;
+  if (mode == 0) {
+    if ((rc = make_map_bf16(&ma, A, M, K, lda, BM, BK)) != RS_OK) return rc;
+    if ((rc = make_map_bf16(&mb, B, N, K, ldb, bn, BK)) != RS_OK) return rc;
+  } else {
+    if ((rc = make_map_bf16(&ma, A, K, M, lda, BK, 64)) != RS_OK) return rc;
+    if ((rc = make_map_bf16(&mb, B, K, N, ldb, BK, 64)) != RS_OK) return rc;
+  }
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024 + 256;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[mode]) {
+    if (mode == 0) RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    else RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_set[mode] = true;
+  }
+  const int items = g.tiles_m * g.tiles_n * g.splits;
+  const int grid = items < sms ? items : sms;
+  if (mode == 0) gemm_tcgen05_kernel<0><<<grid, kThreads, smem, stream>>>(ma, mb, g);
+  else gemm_tcgen05_kernel<1><<<grid, kThreads, smem, stream>>>(ma, mb, g);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}

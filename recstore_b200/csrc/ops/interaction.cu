@@ -1,0 +1,252 @@
+// DLRM pairwise-dot feature interaction, forward and backward, one warp per sample.
+//
+// Forward: T = [x; e_1 .. e_{F-1}] (F x D, bf16, read in place from the buffer that the embedding
+// all-to-all and the bottom MLP wrote), Z = T.T^T on tensor cores, output row =
+// [x (D values), Z[i][j] for i > j in row-major order (1,0),(2,0),(2,1),...], zero padded to
+// `out_ld`.  This is interact_features of the reference (src/executable/dlrm/dlrm_model.py:
+// 316-340: bmm + strictly-lower-triangle gather + cat) in one pass over the data.
+//
+// Backward: dT = (dZ + dZ^T).T with dT[0] += dOut[0:D]; row 0 goes to the bottom-MLP gradient,
+// rows 1.. are stored STRAIGHT INTO THE OWNING RANK'S GRADIENT WINDOW through peer pointers
+// (the backward all-to-all of extend_distributed.py:444-486 done by the producing kernel).
+//
+// The per-sample products are 32x32x128 / 32x128x32, far below one tcgen05 tile, and the op is
+// bound by the bytes of T; warp-level mma.m16n8k16 keeps it at memory speed.
+#include <cuda_bf16.h>
+#include "common/rs_common.h"
+
+namespace {
+
+constexpr int kMaxF = 32;
+constexpr int kMaxD = 128;
+constexpr int kLd = kMaxD + 8;       // padded smem row (elements): 272 B, conflict-free ldmatrix
+constexpr int kWarps = 4;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Loads the F x D tile of one sample into padded shared memory, zero-filling rows F..31.
+__device__ __forceinline__ void load_tile(__nv_bfloat16* sT, const __nv_bfloat16* src, int F, int D, int lane) {
+  const int vec_per_row = D >> 3;  // uint4 = 8 bf16
+  const int total = 32 * vec_per_row;
+  for (int i = lane; i < total; i += 32) {
+    const int r = i / vec_per_row, v = i % vec_per_row;
+    uint4 x = make_uint4(0, 0, 0, 0);
+    if (r < F) x = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * D) + v);
+    *reinterpret_cast<uint4*>(sT + r * kLd + v * 8) = x;
+  }
+}
+
+__global__ void __launch_bounds__(kWarps * 32) interaction_fwd_kernel(const __nv_bfloat16* __restrict__ T, int B, int F,
+                                                                      int D, __nv_bfloat16* __restrict__ out, int out_ld) {
+  __shared__ __align__(16) __nv_bfloat16 sT[kWarps][32 * kLd];
+  __shared__ __align__(16) __nv_bfloat16 sO[kWarps][kMaxD + kMaxF * (kMaxF - 1) / 2 + 8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x * kWarps + warp;
+  if (b >= B) return;
+  __nv_bfloat16* t = sT[warp];
+  load_tile(t, T + static_cast<size_t>(b) * F * D, F, D, lane);
+  __syncwarp();
+
+  // acc[mt][nt]: rows mt*16.., cols nt*8..; only tiles that touch the strict lower triangle.
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
+
+  const int ksteps = D >> 4;
+  for (int ks = 0; ks < ksteps; ++ks) {
+    const int k0 = ks * 16;
+    uint32_t a0[4], a1[4], b01[4], b23[4];
+    ldmatrix_x4(a0, t + ((lane & 7) + ((lane >> 3) & 1) * 8) * kLd + k0 + (lane >> 4) * 8);
+    ldmatrix_x4(a1, t + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kLd + k0 + (lane >> 4) * 8);
+    // B fragments from the same tile viewed as [n][k]: n-tiles {0,1} and {2,3}.
+    ldmatrix_x4(b01, t + ((lane & 7) + (lane >> 4) * 8) * kLd + k0 + ((lane >> 3) & 1) * 8);
+    ldmatrix_x4(b23, t + (16 + (lane & 7) + (lane >> 4) * 8) * kLd + k0 + ((lane >> 3) & 1) * 8);
+    mma_bf16(acc[0][0], a0, b01[0], b01[1]);
+    mma_bf16(acc[0][1], a0, b01[2], b01[3]);
+    mma_bf16(acc[1][0], a1, b01[0], b01[1]);
+    mma_bf16(acc[1][1], a1, b01[2], b01[3]);
+    mma_bf16(acc[1][2], a1, b23[0], b23[1]);
+    mma_bf16(acc[1][3], a1, b23[2], b23[3]);
+  }
+
+  __nv_bfloat16* o = sO[warp];
+  for (int d = lane; d < D; d += 32) o[d] = t[d];  // row 0 = dense features
+  const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      if (mt == 0 && nt >= 2) continue;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = mt * 16 + g + (e >> 1) * 8;
+        const int j = nt * 8 + q * 2 + (e & 1);
+        if (i < F && j < i) o[D + i * (i - 1) / 2 + j] = __float2bfloat16(acc[mt][nt][e]);
+      }
+    }
+  __syncwarp();
+  const int nvalid = D + F * (F - 1) / 2;
+  __nv_bfloat16* dst = out + static_cast<size_t>(b) * out_ld;
+  // out_ld is a multiple of 8: 16-byte stores, zero fill past nvalid.
+  for (int v = lane; v < (out_ld >> 3); v += 32) {
+    uint4 x;
+    __nv_bfloat16* xe = reinterpret_cast<__nv_bfloat16*>(&x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int idx = v * 8 + e;
+      xe[e] = idx < nvalid ? o[idx] : __float2bfloat16(0.f);
+    }
+    *(reinterpret_cast<uint4*>(dst) + v) = x;
+  }
+}
+
+struct InterBwdArgs {
+  const __nv_bfloat16* T;     // [B, F, D]
+  const __nv_bfloat16* dout;  // [B, dout_ld]
+  int B, F, D, dout_ld;
+  __nv_bfloat16* dx;          // [B, dx_ld] gradient of feature 0 (bottom MLP output)
+  int dx_ld;
+  void* const* gdst;          // [world] gradient windows of the owning ranks
+  const int* owner;           // [F-1] owning rank of each embedding feature
+  const int* gcol;            // [F-1] element offset inside the owner's gradient row
+  long long grow_stride;      // elements per sample row in a gradient window
+  long long sample_base;      // this rank's first global sample index (rank * B_local)
+  int relu_mask_dx;           // feature 0 is a ReLU output: zero dx where it is not positive
+};
+
+__global__ void __launch_bounds__(kWarps * 32) interaction_bwd_kernel(const InterBwdArgs a) {
+  __shared__ __align__(16) __nv_bfloat16 sT[kWarps][32 * kLd];
+  __shared__ __align__(16) __nv_bfloat16 sS[kWarps][32 * 40];  // symmetric dZ, padded rows of 40
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x * kWarps + warp;
+  if (b >= a.B) return;
+  const int F = a.F, D = a.D;
+  __nv_bfloat16* t = sT[warp];
+  __nv_bfloat16* s = sS[warp];
+  load_tile(t, a.T + static_cast<size_t>(b) * F * D, F, D, lane);
+  const __nv_bfloat16* dout = a.dout + static_cast<size_t>(b) * a.dout_ld;
+  for (int i = lane; i < 32 * 40; i += 32) s[i] = __float2bfloat16(0.f);
+  __syncwarp();
+  const int npairs = F * (F - 1) / 2;
+  for (int p = lane; p < npairs; p += 32) {
+    // invert p = i(i-1)/2 + j
+    int i = static_cast<int>((1.f + sqrtf(1.f + 8.f * p)) * 0.5f);
+    while (i * (i - 1) / 2 > p) --i;
+    while ((i + 1) * i / 2 <= p) ++i;
+    const int j = p - i * (i - 1) / 2;
+    const __nv_bfloat16 v = dout[D + p];
+    s[i * 40 + j] = v;
+    s[j * 40 + i] = v;
+  }
+  __syncwarp();
+
+  // dT[32 x D] = S[32 x 32] . T[32 x D]; two k-steps; loop over n in halves of 64 to bound registers.
+  uint32_t sa[2][2][4];  // [mt][ks]
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks)
+      ldmatrix_x4(sa[mt][ks], s + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 40 + ks * 16 + (lane >> 4) * 8);
+
+  const int g = lane >> 2, q = lane & 3;
+  for (int n0 = 0; n0 < D; n0 += 64) {
+    float acc[2][8][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {  // pairs of n-tiles
+        if (n0 + np * 16 >= D) continue;
+        uint32_t bb[4];
+        ldmatrix_x4_trans(bb, t + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kLd + n0 + np * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma_bf16(acc[mt][np * 2], sa[mt][ks], bb[0], bb[1]);
+          mma_bf16(acc[mt][np * 2 + 1], sa[mt][ks], bb[2], bb[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int col = n0 + nt * 8 + q * 2;
+        if (col >= D) continue;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int i = mt * 16 + g + h * 8;
+          if (i >= F) continue;
+          float v0 = acc[mt][nt][h * 2], v1 = acc[mt][nt][h * 2 + 1];
+          __nv_bfloat16* dst;
+          if (i == 0) {
+            v0 += __bfloat162float(dout[col]);
+            v1 += __bfloat162float(dout[col + 1]);
+            if (a.relu_mask_dx) {
+              if (!(__bfloat162float(t[col]) > 0.f)) v0 = 0.f;
+              if (!(__bfloat162float(t[col + 1]) > 0.f)) v1 = 0.f;
+            }
+            dst = a.dx + static_cast<size_t>(b) * a.dx_ld + col;
+          } else {
+            const int f = i - 1;
+            dst = reinterpret_cast<__nv_bfloat16*>(a.gdst[a.owner[f]]) + (a.sample_base + b) * a.grow_stride + a.gcol[f] + col;
+          }
+          *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
+        }
+      }
+  }
+}
+
+}  // namespace
+
+RS_API int rs_interaction_forward(const void* T, int B, int F, int D, void* out, int out_ld, cudaStream_t stream) {
+  RS_REQUIRE(T && out, "rs_interaction_forward: null argument");
+  RS_REQUIRE(F >= 1 && F <= kMaxF && D % 16 == 0 && D >= 16 && D <= kMaxD, "rs_interaction_forward: F=%d D=%d unsupported", F, D);
+  RS_REQUIRE(out_ld % 8 == 0 && out_ld >= D + F * (F - 1) / 2, "rs_interaction_forward: out_ld=%d too small or unaligned", out_ld);
+  if (B == 0) return RS_OK;
+  interaction_fwd_kernel<<<(B + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(T), B, F, D, reinterpret_cast<__nv_bfloat16*>(out), out_ld);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+RS_API int rs_interaction_backward(const void* T, const void* dout, int B, int F, int D, int dout_ld, void* dx,
+                                   int dx_ld, void* const* gdst, const int* owner, const int* gcol,
+                                   long long grow_stride, long long sample_base, int relu_mask_dx,
+                                   cudaStream_t stream) {
+  RS_REQUIRE(T && dout && dx && gdst && owner && gcol, "rs_interaction_backward: null argument");
+  RS_REQUIRE(F >= 1 && F <= kMaxF && D % 16 == 0 && D >= 16 && D <= kMaxD, "rs_interaction_backward: F=%d D=%d unsupported", F, D);
+  if (B == 0) return RS_OK;
+  InterBwdArgs a;
+  a.T = reinterpret_cast<const __nv_bfloat16*>(T);
+  a.dout = reinterpret_cast<const __nv_bfloat16*>(dout);
+  a.B = B; a.F = F; a.D = D; a.dout_ld = dout_ld;
+  a.dx = reinterpret_cast<__nv_bfloat16*>(dx); a.dx_ld = dx_ld;
+  a.gdst = gdst; a.owner = owner; a.gcol = gcol; a.grow_stride = grow_stride; a.sample_base = sample_base;
+  a.relu_mask_dx = relu_mask_dx;
+  interaction_bwd_kernel<<<(B + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(a);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}

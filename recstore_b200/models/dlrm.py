@@ -1,0 +1,476 @@
+"""DLRM (dot interaction) training / inference engine on the native sm_100a kernels.
+
+Model: the Facebook DLRM as forked by the reference (``DLRM_Net``,
+src/executable/dlrm/dlrm_model.py:72-110 MLPs, :255-314 embedding bags, :316-351 dot
+interaction, :364-423 distributed forward): bottom MLP on the dense features, one sum-pooled
+embedding bag per table, pairwise dot interaction, top MLP, sigmoid + BCE.
+
+Parallelisation (one process per GPU): embedding tables are placed table-wise on the ranks
+(model parallel), the MLPs are replicated (data parallel).  The "butterfly" all-to-all of the
+reference is not a collective here: the embedding gather kernel stores each pooled row straight
+into the destination rank's interaction buffer over NVLink, the interaction backward kernel
+stores each embedding gradient straight into the owning rank's gradient window, and flag
+channels order the steps.  The dense gradient all-reduce is a two-shot push kernel followed by
+the SGD kernels (``parallel.peer``).  There is no autograd graph: the backward pass is written
+out as a fixed sequence of kernel launches, captured once into a CUDA graph and replayed.
+
+Inputs are double buffered: ``submit`` enqueues the host-to-device copies of the next batch on a
+copy stream while the previous step still computes.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import _lib
+from ..ops import functional as F_
+from ..parallel.peer import PeerContext
+
+CH_FWD, CH_BWD, CH_GRADS, CH_REDUCED, CH_MISC = 0, 1, 2, 3, 4
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+@dataclass
+class DLRMConfig:
+    table_rows: Sequence[int]
+    batch: int                                   # global batch size
+    emb_dim: int = 128
+    hotness: Optional[Sequence[int]] = None      # ids per bag for every table (default 1)
+    num_dense: int = 13
+    bottom_mlp: Sequence[int] = (512, 256, 128)  # output widths; the last equals emb_dim
+    top_mlp: Sequence[int] = (1024, 1024, 512, 256, 1)
+    emb_lr: float = 0.01
+    emb_eps: float = 1e-10
+    emb_optimizer: str = "rowwise_adagrad"       # or "sgd"
+    mlp_lr: float = 0.01
+    seed: int = 0
+    use_cuda_graph: bool = True
+    emb_init: str = "uniform"                    # U(+-sqrt(1/n)) as in the reference, or "normal"
+
+    def __post_init__(self):
+        if self.hotness is None:
+            self.hotness = [1] * len(self.table_rows)
+        assert len(self.hotness) == len(self.table_rows)
+        assert self.bottom_mlp[-1] == self.emb_dim, "bottom MLP must end at the embedding width"
+        assert self.top_mlp[-1] == 1, "top MLP ends in one logit"
+
+
+class _Layer:
+    """One Linear(K -> N): fp32 master slices of the flat buffers plus bf16 copies W and W^T."""
+
+    def __init__(self, N: int, K: int, Kp: int):
+        self.N, self.K, self.Kp = N, K, Kp
+        self.w = self.b = self.gw = self.gb = self.rw = self.rb = None
+        self.wb = self.wt = None
+
+
+@dataclass
+class PinnedBatch:
+    """One rank's share of a global batch in pinned host memory."""
+    dense: torch.Tensor     # [B_local, num_dense] fp32
+    ids: torch.Tensor       # [nnz_local] int64: for each local table, B * hotness ids, sample-major
+    labels: torch.Tensor    # [B_local] fp32
+
+    @property
+    def nbytes(self) -> int:
+        return self.dense.numel() * 4 + self.ids.numel() * 8 + self.labels.numel() * 4
+
+
+class StepHandle:
+    """Result of an asynchronously submitted step."""
+
+    def __init__(self, engine: "DLRM", slot: int, event: torch.cuda.Event):
+        self._e, self._slot, self._ev = engine, slot, event
+
+    def result(self) -> float:
+        """Waits for the step and returns this rank's share of the mean BCE loss (sum over ranks = loss)."""
+        self._ev.synchronize()
+        return float(self._e._loss_host[self._slot].item())
+
+
+class DLRM:
+    def __init__(self, cfg: DLRMConfig, ctx: Optional[PeerContext] = None):
+        if not torch.cuda.is_available():
+            raise _lib.RecStoreError(_lib.ERR_STATE, "models.DLRM needs a CUDA device (sm_100a)")
+        _lib.lib()
+        self.cfg = cfg
+        self.ctx = ctx if ctx is not None else PeerContext(0, 1)
+        self.rank, self.world = self.ctx.rank, self.ctx.world
+        dev = self.dev = self.ctx.device
+        assert cfg.batch % self.world == 0
+        self.B = cfg.batch
+        self.Bl = cfg.batch // self.world
+        self.T = len(cfg.table_rows)
+        self.D = cfg.emb_dim
+        self.F = self.T + 1
+        assert self.F <= 32, "dot interaction kernel handles up to 31 embedding features"
+        # ---- table placement: round robin by table index
+        self.owner = [t % self.world for t in range(self.T)]
+        self.local_tables = [t for t in range(self.T) if self.owner[t] == self.rank]
+        self.Tl = len(self.local_tables)
+        self.Tmax = max(sum(1 for t in range(self.T) if self.owner[t] == r) for r in range(self.world))
+        local_idx = {}
+        cnt = [0] * self.world
+        for t in range(self.T):
+            local_idx[t] = cnt[self.owner[t]]
+            cnt[self.owner[t]] += 1
+        self.local_idx = local_idx
+
+        g = torch.Generator(device="cpu").manual_seed(cfg.seed)
+        i32 = dict(dtype=torch.int32, device=dev)
+        i64 = dict(dtype=torch.int64, device=dev)
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+
+        # ---- embedding shard
+        rows = [cfg.table_rows[t] for t in self.local_tables]
+        base = [0]
+        for r in rows:
+            base.append(base[-1] + r)
+        self.total_rows = base[-1]
+        self.table_base = torch.tensor(base[:-1] or [0], **i64)
+        self.table_rows = torch.tensor(rows or [0], **i64)
+        self.weight = torch.empty(max(self.total_rows, 1), self.D, **f32)
+        gg = torch.Generator(device=dev).manual_seed(cfg.seed * 1000 + 17)
+        for j, t in enumerate(self.local_tables):
+            n = cfg.table_rows[t]
+            gt = torch.Generator(device=dev).manual_seed(cfg.seed * 1000 + t)
+            w = self.weight[base[j]:base[j + 1]]
+            if cfg.emb_init == "uniform":
+                w.uniform_(-math.sqrt(1.0 / n), math.sqrt(1.0 / n), generator=gt)
+            else:
+                w.normal_(0.0, 0.01, generator=gt)
+        del gg
+        self.state = torch.zeros(max(self.total_rows, 1), **f32)
+        hot = [cfg.hotness[t] for t in self.local_tables]
+        hb = [0]
+        for h in hot:
+            hb.append(hb[-1] + self.B * h)
+        self.nnz = hb[-1]
+        self.hotness = torch.tensor(hot or [1], **i32)
+        self.hot_base = torch.tensor(hb[:-1] or [0], **i64)
+        self.dst_col = torch.tensor([(1 + t) * self.D for t in self.local_tables] or [0], **i32)
+        self.grad_col = torch.tensor([j * self.D for j in range(self.Tl)] or [0], **i32)
+        self.row_idx = torch.empty(max(self.nnz, 1), **i64)
+        self.occ2bag = torch.empty(max(self.nnz, 1), **i32)
+        self.owner_dev = torch.tensor(self.owner, **i32)
+        self.gcol_dev = torch.tensor([local_idx[t] * self.D for t in range(self.T)], **i32)
+
+        # ---- peer windows
+        self.grow_stride = self.Tmax * self.D
+        self.Twin = self.ctx.alloc("dlrm_T", self.Bl * self.F * self.D * 2)
+        self.Gwin = self.ctx.alloc("dlrm_G", self.B * self.grow_stride * 2)
+        self.Tbuf = self.Twin.view(torch.bfloat16, (self.Bl, self.F * self.D))
+
+        # ---- dense parameters (flat fp32 master / grad / reduced buffers)
+        self.Kin0 = _round_up(cfg.num_dense, 64)
+        self.n_inter = self.D + self.F * (self.F - 1) // 2
+        self.Kz = _round_up(self.n_inter, 64)
+        dims_b = [(cfg.num_dense, self.Kin0)] + [(n, n) for n in cfg.bottom_mlp[:-1]]
+        self.bot: List[_Layer] = [_Layer(n, k, kp) for (k, kp), n in zip(dims_b, cfg.bottom_mlp)]
+        dims_t = [(self.n_inter, self.Kz)] + [(n, n) for n in cfg.top_mlp[:-2]]
+        self.top: List[_Layer] = [_Layer(n, k, kp) for (k, kp), n in zip(dims_t, cfg.top_mlp[:-1])]
+        self.head_K = cfg.top_mlp[-2]
+        layers = self.bot + self.top
+        off = 0
+        w_off = []
+        for L in layers:
+            w_off.append(off)
+            off += L.N * L.Kp
+        self.n_w = off
+        b_off = []
+        for L in layers:
+            b_off.append(off)
+            off += _round_up(L.N, 4)
+        head_w_off = off
+        off += _round_up(self.head_K, 4)
+        head_b_off = off
+        off += 4
+        self.n_params = off
+        self.tail_off, self.tail_n = self.n_w, off - self.n_w
+        self.master = torch.zeros(self.n_params, **f32)
+        self.Gflat = self.ctx.alloc("dlrm_dense_grad", self.n_params * 4)
+        self.grads = self.Gflat.view(torch.float32, (self.n_params,))
+        if self.world > 1:
+            self.Rflat = self.ctx.alloc("dlrm_dense_reduced", self.n_params * 4)
+            self.reduced = self.Rflat.view(torch.float32, (self.n_params,))
+        else:
+            self.reduced = self.grads
+        for L, wo, bo in zip(layers, w_off, b_off):
+            L.w = self.master[wo:wo + L.N * L.Kp].view(L.N, L.Kp)
+            L.b = self.master[bo:bo + L.N]
+            L.gw = self.grads[wo:wo + L.N * L.Kp].view(L.N, L.Kp)
+            L.gb = self.grads[bo:bo + L.N]
+            L.rw = self.reduced[wo:wo + L.N * L.Kp].view(L.N, L.Kp)
+            L.wb = torch.zeros(L.N, L.Kp, **bf)
+            L.wt = torch.zeros(L.Kp, L.N, **bf)
+            w0 = torch.randn(L.N, L.K, generator=g) * math.sqrt(2.0 / (L.N + L.K))
+            b0 = torch.randn(L.N, generator=g) * math.sqrt(1.0 / L.N)
+            L.w[:, :L.K].copy_(w0)
+            L.b.copy_(b0)
+        self.head_w = self.master[head_w_off:head_w_off + self.head_K]
+        self.head_b = self.master[head_b_off:head_b_off + 1]
+        self.g_head_w = self.grads[head_w_off:head_w_off + self.head_K]
+        self.g_head_b = self.grads[head_b_off:head_b_off + 1]
+        self.head_w.copy_(torch.randn(self.head_K, generator=g) * math.sqrt(2.0 / (1 + self.head_K)))
+        self.head_b.copy_(torch.randn(1, generator=g))
+        self._refresh_bf16()
+
+        # ---- activations and their gradients
+        Bl = self.Bl
+        self.x0p = torch.zeros(Bl, self.Kin0, **bf)
+        self.act_b = [torch.empty(Bl, L.N, **bf) for L in self.bot[:-1]]          # h1, h2 (h3 lives in Tbuf)
+        self.z = torch.empty(Bl, self.Kz, **bf)
+        self.act_t = [torch.empty(Bl, L.N, **bf) for L in self.top]               # t1..t4
+        self.d_act_t = [torch.empty(Bl, L.N, **bf) for L in self.top]
+        self.d_z = torch.empty(Bl, self.Kz, **bf)
+        self.d_act_b = [torch.empty(Bl, L.N, **bf) for L in self.bot]             # d_h1, d_h2, d_h3
+        self.prob = torch.empty(Bl, **f32)
+
+        # ---- double-buffered inputs, loss
+        self.in_dense = [torch.empty(Bl, cfg.num_dense, **f32) for _ in range(2)]
+        self.in_ids = [torch.empty(max(self.nnz, 1), **i64) for _ in range(2)]
+        self.in_labels = [torch.empty(Bl, **f32) for _ in range(2)]
+        self._loss_dev = [torch.zeros(1, **f32) for _ in range(2)]
+        self._loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self.copy_stream = torch.cuda.Stream(device=dev)
+        self.compute_stream = torch.cuda.Stream(device=dev)
+        self._copied = [torch.cuda.Event() for _ in range(2)]
+        self._consumed = [torch.cuda.Event() for _ in range(2)]
+        self._done = [torch.cuda.Event() for _ in range(2)]
+        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._step_no = 0
+        self.launches_per_step = 0
+        self._warm_native()
+        torch.cuda.synchronize(dev)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=self.ctx.group)
+
+    # ------------------------------------------------------------------ helpers
+    def _warm_native(self):
+        """Runs both GEMM variants once on scratch data so that one-time function attributes are set
+        before any stream capture (the model state is untouched)."""
+        a = torch.zeros(128, 64, dtype=torch.bfloat16, device=self.dev)
+        o = torch.zeros(128, 128, dtype=torch.bfloat16, device=self.dev)
+        o32 = torch.zeros(64, 64, dtype=torch.float32, device=self.dev)
+        F_.gemm_bf16(a, a, o, mode=0, epi=F_.EPI_NONE, status=self.ctx.status)
+        F_.gemm_bf16(a, a, o32, mode=1, epi=F_.EPI_ATOMIC_F32, status=self.ctx.status)
+
+    def _refresh_bf16(self):
+        for L in self.bot + self.top:
+            L.wb.copy_(L.w)
+            L.wt.copy_(L.w.t())
+
+    def make_pinned_batch(self, dense: torch.Tensor, ids: Sequence[torch.Tensor], labels: torch.Tensor) -> PinnedBatch:
+        """Cuts this rank's share out of a GLOBAL batch (dense [B,nd], per-table ids [B*hot], labels [B])."""
+        lo, hi = self.rank * self.Bl, (self.rank + 1) * self.Bl
+        d = dense[lo:hi].contiguous().pin_memory()
+        l = labels[lo:hi].contiguous().pin_memory()
+        if self.local_tables:
+            i = torch.cat([ids[t].reshape(-1) for t in self.local_tables]).to(torch.int64).pin_memory()
+        else:
+            i = torch.zeros(1, dtype=torch.int64).pin_memory()
+        assert i.numel() == max(self.nnz, 1)
+        return PinnedBatch(d, i, l)
+
+    def _count(self, n=1):
+        self.launches_per_step += n
+
+    # ------------------------------------------------------------------ the step as a launch sequence
+    def _forward(self, slot: int):
+        c, st = self.cfg, self.ctx.status
+        F_.pad_cast_bf16(self.in_dense[slot], self.x0p); self._count()
+        if self.Tl:
+            F_.emb_forward(self.weight, self.table_base, self.table_rows, self.in_ids[slot], hotness=self.hotness,
+                           hot_base=self.hot_base, T=self.Tl, B=self.B, D=self.D, B_local=self.Bl,
+                           dst_table=self.Twin.table, dst_row_stride=self.F * self.D, dst_col=self.dst_col,
+                           out_bf16=True, row_idx=self.row_idx, occ2bag=self.occ2bag, status=st)
+            self._count()
+        if self.world > 1:
+            self.ctx.signal(CH_FWD); self._count()
+        x = self.x0p
+        for i, L in enumerate(self.bot):
+            out = self.act_b[i] if i < len(self.bot) - 1 else self.Tbuf[:, :self.D]
+            F_.gemm_bf16(x, L.wb, out, mode=0, epi=F_.EPI_RELU, bias=L.b, status=st, n=L.N); self._count()
+            x = out
+        if self.world > 1:
+            self.ctx.wait(CH_FWD); self._count()
+        F_.interaction_forward(self.Tbuf, self.Bl, self.F, self.D, self.z); self._count()
+        x = self.z
+        for i, L in enumerate(self.top):
+            F_.gemm_bf16(x, L.wb, self.act_t[i], mode=0, epi=F_.EPI_RELU, bias=L.b, status=st); self._count()
+            x = self.act_t[i]
+        return x
+
+    def _run_step(self, slot: int):
+        c, st = self.cfg, self.ctx.status
+        self.launches_per_step = 0
+        x = self._forward(slot)
+        self._loss_dev[slot].zero_(); self._count()
+        F_.head_bce(x, self.head_w, self.head_b, self.in_labels[slot], 1.0 / self.B, prob=self.prob,
+                    loss_sum=self._loss_dev[slot], dx=self.d_act_t[-1], dw=self.g_head_w, db=self.g_head_b)
+        self._count()
+        # ---- top MLP backward
+        for i in range(len(self.top) - 1, -1, -1):
+            L = self.top[i]
+            dy = self.d_act_t[i]
+            xin = self.act_t[i - 1] if i > 0 else self.z
+            F_.colsum_bf16(dy, L.gb); self._count()
+            F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
+            if i > 0:
+                F_.gemm_bf16(dy, L.wt, self.d_act_t[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
+            else:
+                F_.gemm_bf16(dy, L.wt, self.d_z, mode=0, epi=F_.EPI_NONE, status=st)
+            self._count()
+        # ---- interaction backward: dense part stays, embedding gradients go to their owners
+        F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
+                                self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
+                                relu_mask_dx=True)
+        self._count()
+        if self.world > 1:
+            self.ctx.signal(CH_BWD); self._count()
+        # ---- bottom MLP backward
+        for i in range(len(self.bot) - 1, -1, -1):
+            L = self.bot[i]
+            dy = self.d_act_b[i]
+            xin = self.act_b[i - 1] if i > 0 else self.x0p
+            F_.colsum_bf16(dy, L.gb); self._count()
+            F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
+            if i > 0:
+                F_.gemm_bf16(dy, L.wt, self.d_act_b[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
+                self._count()
+        if self.world > 1:
+            self.ctx.wait(CH_BWD); self._count()
+        # ---- sparse optimizer on the owned rows
+        if self.Tl:
+            F_.emb_backward(self.weight, self.state, self.row_idx, self.occ2bag, self.nnz, self.Gwin.local,
+                            grad_col=self.grad_col, grad_row_stride=self.grow_stride, B=self.B, D=self.D,
+                            grad_bf16=True, lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st)
+            self._count(2 if c.emb_optimizer == "rowwise_adagrad" else 1)
+        # ---- dense gradients: all-reduce + SGD
+        if self.world > 1:
+            self.ctx.signal(CH_GRADS); self.ctx.wait(CH_GRADS)
+            F_.allreduce_push(self.Gflat.table, self.Rflat.table, self.world, self.rank, self.n_params)
+            self.ctx.signal(CH_REDUCED); self.ctx.wait(CH_REDUCED)
+            self._count(5)
+        solo = self.world == 1
+        for L in self.bot + self.top:
+            F_.dense_sgd(L.w, L.rw, c.mlp_lr, L.wb, L.wt, zero_grad=solo); self._count()
+        F_.vec_sgd(self.master[self.tail_off:], self.reduced[self.tail_off:], c.mlp_lr, zero_grad=solo); self._count()
+        if not solo:
+            self.grads.zero_(); self._count()
+
+    # ------------------------------------------------------------------ public API
+    def submit(self, batch: PinnedBatch) -> StepHandle:
+        """Enqueues H2D copies of ``batch`` and one training step; returns immediately."""
+        slot = self._step_no & 1
+        self._step_no += 1
+        cs, ms = self.copy_stream, self.compute_stream
+        with torch.cuda.stream(cs):
+            cs.wait_event(self._consumed[slot])       # previous user of this slot has finished
+            self.in_dense[slot].copy_(batch.dense, non_blocking=True)
+            self.in_ids[slot].copy_(batch.ids, non_blocking=True)
+            self.in_labels[slot].copy_(batch.labels, non_blocking=True)
+            self._copied[slot].record(cs)
+        with torch.cuda.stream(ms):
+            ms.wait_event(self._copied[slot])
+            if self.cfg.use_cuda_graph:
+                g = self._graphs.get(slot)
+                if g is None:
+                    g = self._capture(slot)
+                g.replay()
+            else:
+                self._run_step(slot)
+            self._consumed[slot].record(ms)
+            self._loss_host[slot].copy_(self._loss_dev[slot], non_blocking=True)
+            self._done[slot].record(ms)
+        return StepHandle(self, slot, self._done[slot])
+
+    def train_step(self, batch: PinnedBatch) -> float:
+        return self.submit(batch).result()
+
+    def time_steps_on_device(self, steps: int) -> float:
+        """Runs ``steps`` training steps on the batches already resident in the two input slots and
+        returns the elapsed milliseconds measured with CUDA events on the compute stream."""
+        ms = self.compute_stream
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(self.dev)
+        with torch.cuda.stream(ms):
+            if self.cfg.use_cuda_graph:
+                for slot in (0, 1):
+                    if slot not in self._graphs:
+                        self._capture(slot)
+            e0.record(ms)
+            for i in range(steps):
+                slot = i & 1
+                if self.cfg.use_cuda_graph:
+                    self._graphs[slot].replay()
+                else:
+                    self._run_step(slot)
+            e1.record(ms)
+        e1.synchronize()
+        return e0.elapsed_time(e1)
+
+    def _capture(self, slot: int) -> torch.cuda.CUDAGraph:
+        torch.cuda.current_stream().synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=torch.cuda.current_stream(), capture_error_mode="relaxed"):
+            self._run_step(slot)
+        self._graphs[slot] = g
+        return g
+
+    @torch.no_grad()
+    def predict(self, batch: PinnedBatch) -> torch.Tensor:
+        """Click probabilities of this rank's samples (inference, no parameter update)."""
+        with torch.cuda.stream(self.compute_stream):
+            self.in_dense[0].copy_(batch.dense, non_blocking=True)
+            self.in_ids[0].copy_(batch.ids, non_blocking=True)
+            x = self._forward(0)
+            F_.head_bce(x, self.head_w, self.head_b, None, 1.0 / self.B, prob=self.prob)
+            if self.world > 1:
+                self.ctx.barrier(CH_MISC)  # nobody may overwrite the interaction buffer before all have read it
+            out = self.prob.clone()
+        self.compute_stream.synchronize()
+        return out
+
+    def check(self):
+        self.ctx.check_status()
+
+    # ------------------------------------------------------------------ state access (tests, checkpoints)
+    def dense_state(self) -> Dict[str, torch.Tensor]:
+        out = {}
+        for name, Ls in (("bot", self.bot), ("top", self.top)):
+            for i, L in enumerate(Ls):
+                out[f"{name}.{i}.weight"] = L.w[:, :L.K].clone()
+                out[f"{name}.{i}.bias"] = L.b.clone()
+        out["head.weight"] = self.head_w.clone()
+        out["head.bias"] = self.head_b.clone()
+        return out
+
+    def load_dense_state(self, sd: Dict[str, torch.Tensor]) -> None:
+        for name, Ls in (("bot", self.bot), ("top", self.top)):
+            for i, L in enumerate(Ls):
+                L.w.zero_()
+                L.w[:, :L.K].copy_(sd[f"{name}.{i}.weight"])
+                L.b.copy_(sd[f"{name}.{i}.bias"])
+        self.head_w.copy_(sd["head.weight"].reshape(-1))
+        self.head_b.copy_(sd["head.bias"].reshape(-1))
+        self._refresh_bf16()
+
+    def table_weight(self, t: int) -> torch.Tensor:
+        """View of table ``t`` if this rank owns it."""
+        j = self.local_tables.index(t)
+        b0 = int(self.table_base[j].item())
+        return self.weight[b0:b0 + self.cfg.table_rows[t]]
+
+    def table_state(self, t: int) -> torch.Tensor:
+        j = self.local_tables.index(t)
+        b0 = int(self.table_base[j].item())
+        return self.state[b0:b0 + self.cfg.table_rows[t]]

@@ -1,0 +1,138 @@
+"""Functional wrappers of the native sm_100a kernels (thin: shape checks + pointer passing).
+
+Each function launches on the current CUDA stream and allocates nothing unless it says so, so
+all of them can be captured in a CUDA graph.  ``status`` is a 1-element int64 device tensor
+that receives device-side error bits (see ``_lib.decode_status``).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .._lib import call, ptr, stream_ptr
+
+EPI_NONE, EPI_RELU, EPI_RELU_MASK, EPI_ATOMIC_F32, EPI_F32, EPI_CROSS = range(6)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.RecStoreError(_lib.ERR_INVALID, "native GPU op called with a CPU tensor")
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, mode: int = 0, epi: int = EPI_NONE,
+              bias: Optional[torch.Tensor] = None, aux: Optional[torch.Tensor] = None,
+              x0: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, bn: int = 0,
+              splits: int = 0, n: Optional[int] = None, k: Optional[int] = None) -> torch.Tensor:
+    """tcgen05 GEMM.
+
+    mode 0: ``out[M,N] = epi(a[M,K] @ b[N,K].T)``; mode 1: ``out[M,N] (+)= a[K,M].T @ b[K,N]``
+    (``out`` fp32, epi ``EPI_ATOMIC_F32``).  Operands are 2-D bf16 with unit inner stride; the
+    leading dimensions are taken from ``stride(0)`` so column slices of wider buffers work.
+    """
+    _need_cuda(a, b, out)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1
+    if mode == 0:
+        M, K = a.shape
+        N = b.shape[0]
+        assert b.shape[1] == K, (a.shape, b.shape)
+    else:
+        K, M = a.shape
+        N = b.shape[1]
+        assert b.shape[0] == K, (a.shape, b.shape)
+    if n is not None:
+        N = n
+    if k is not None:
+        K = k
+    assert out.shape[0] >= M and out.shape[1] >= N
+    call("rs_gemm_bf16", ptr(a), ptr(b), ptr(out), ptr(bias), ptr(aux), ptr(x0), M, N, K, a.stride(0), b.stride(0),
+         out.stride(0), aux.stride(0) if aux is not None else 0, x0.stride(0) if x0 is not None else 0, mode, epi,
+         bn, splits, ptr(status), stream_ptr())
+    return out
+
+
+def emb_forward(weight, table_base, table_rows, indices, *, offsets=None, hotness=None, hot_base=None,
+                per_sample_weights=None, T: int, B: int, D: int, B_local: int, dst_table, dst_row_stride: int,
+                dst_col, out_bf16: bool = True, row_idx=None, occ2bag=None, ht=None, status=None) -> None:
+    """Pooled gather of every (table, sample) bag, stored through ``dst_table[sample // B_local]``."""
+    _need_cuda(weight, indices)
+    import ctypes as C
+    call("rs_emb_forward", ptr(weight), ptr(table_base), ptr(table_rows), ptr(indices), ptr(offsets), ptr(hotness),
+         ptr(hot_base), ptr(per_sample_weights), T, B, D, B_local, ptr(dst_table), dst_row_stride, ptr(dst_col),
+         1 if out_bf16 else 0, ptr(row_idx), ptr(occ2bag), C.byref(ht) if ht is not None else None, ptr(status),
+         stream_ptr())
+
+
+def emb_backward(weight, state, row_idx, occ2bag, nnz: int, grad, *, grad_col=None, grad_row_stride: int, B: int,
+                 D: int, grad_bf16: bool = True, per_sample_weights=None, lr: float, eps: float = 1e-10,
+                 optimizer: str = "rowwise_adagrad", status=None) -> None:
+    """Segment-reduces duplicate rows and applies SGD / row-wise Adagrad in place."""
+    _need_cuda(weight, row_idx, grad)
+    opt = {"sgd": 0, "rowwise_adagrad": 1}[optimizer]
+    call("rs_emb_backward", ptr(weight), ptr(state), weight.shape[0], ptr(row_idx), ptr(occ2bag), nnz, ptr(grad),
+         ptr(grad_col), grad_row_stride, B, D, 1 if grad_bf16 else 0, ptr(per_sample_weights), lr, eps, opt,
+         ptr(status), stream_ptr())
+
+
+def rows_gather(weight, rows, out) -> torch.Tensor:
+    call("rs_rows_gather", ptr(weight), ptr(rows), rows.numel(), weight.shape[1], ptr(out), stream_ptr())
+    return out
+
+
+def rows_scatter(weight, rows, values) -> None:
+    call("rs_rows_scatter", ptr(weight), ptr(rows), rows.numel(), weight.shape[1], ptr(values), stream_ptr())
+
+
+def interaction_forward(T, B: int, F: int, D: int, out) -> torch.Tensor:
+    """``out[b] = [T[b,0,:], lower_triangle(T[b] @ T[b].T)]`` zero padded to ``out.stride(0)``."""
+    _need_cuda(T, out)
+    call("rs_interaction_forward", ptr(T), B, F, D, ptr(out), out.stride(0), stream_ptr())
+    return out
+
+
+def interaction_backward(T, dout, B: int, F: int, D: int, dx, gdst_table, owner, gcol, grow_stride: int,
+                         sample_base: int, relu_mask_dx: bool = True) -> None:
+    _need_cuda(T, dout, dx)
+    call("rs_interaction_backward", ptr(T), ptr(dout), B, F, D, dout.stride(0), ptr(dx), dx.stride(0),
+         ptr(gdst_table), ptr(owner), ptr(gcol), grow_stride, sample_base, 1 if relu_mask_dx else 0, stream_ptr())
+
+
+def head_bce(x, w, bias, labels, inv_batch: float, *, prob=None, loss_sum=None, dx=None, dw=None, db=None) -> None:
+    """Final 1-output linear layer + sigmoid + BCE and all its gradients in one kernel."""
+    _need_cuda(x, w)
+    M, K = x.shape
+    call("rs_head_bce", ptr(x), x.stride(0), M, K, ptr(w), ptr(bias), ptr(labels), inv_batch, ptr(prob),
+         ptr(loss_sum), ptr(dx), dx.stride(0) if dx is not None else 0, ptr(dw), ptr(db), stream_ptr())
+
+
+def colsum_bf16(dy, db) -> None:
+    M, N = dy.shape
+    call("rs_colsum_bf16", ptr(dy), dy.stride(0), M, N, ptr(db), stream_ptr())
+
+
+def dense_sgd(w, g, lr: float, wb=None, wt=None, zero_grad: bool = True) -> None:
+    N, K = w.shape
+    call("rs_dense_sgd", ptr(w), ptr(g), N, K, lr, ptr(wb), wb.stride(0) if wb is not None else 0, ptr(wt),
+         wt.stride(0) if wt is not None else 0, 1 if zero_grad else 0, stream_ptr())
+
+
+def vec_sgd(w, g, lr: float, zero_grad: bool = True) -> None:
+    call("rs_vec_sgd", ptr(w), ptr(g), w.numel(), lr, 1 if zero_grad else 0, stream_ptr())
+
+
+def pad_cast_bf16(x, out) -> torch.Tensor:
+    M, K = x.shape
+    call("rs_pad_cast_bf16", ptr(x), M, K, x.stride(0), ptr(out), out.stride(0), stream_ptr())
+    return out
+
+
+def mse_fwd_bwd(pred, target, loss_sum, dpred=None) -> None:
+    n = pred.numel()
+    call("rs_mse_fwd_bwd", ptr(pred), ptr(target), n, 1.0 / n, ptr(loss_sum), ptr(dpred), stream_ptr())
+
+
+def allreduce_push(grads_table, reduced_table, world: int, rank: int, n: int, scale: float = 1.0) -> None:
+    call("rs_allreduce_push", ptr(grads_table), ptr(reduced_table), world, rank, n, scale, stream_ptr())

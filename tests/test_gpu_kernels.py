@@ -1,0 +1,308 @@
+"""Numerics of every native kernel against a plain PyTorch fp32 reference of the same op (GPU only)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from recstore_b200 import _lib
+    _lib.lib()
+    return torch.device("cuda:0")
+
+
+def _status(dev):
+    return torch.zeros(1, dtype=torch.int64, device=dev)
+
+
+def _rel_err(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+# ---------------------------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (1000, 512, 256), (4096, 1024, 1024),
+                                   (8192, 128, 256), (512, 64, 64), (300, 96, 192), (2048, 3456, 512)])
+def test_gemm_tn_plain(dev, M, N, K):
+    from recstore_b200.ops import functional as F_
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    b = torch.randn(N, K, device=dev, generator=g).bfloat16()
+    out = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+    st = _status(dev)
+    F_.gemm_bf16(a, b, out, mode=0, epi=F_.EPI_NONE, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    ref = a.float() @ b.float().t()
+    assert _rel_err(out, ref) < 1e-2
+    # exactness pattern: catches swizzle / descriptor mistakes that a norm could hide
+    assert (out.float() - ref).abs().max().item() < 0.05 * ref.abs().max().item() + 0.5
+
+
+def test_gemm_tn_epilogues(dev):
+    from recstore_b200.ops import functional as F_
+    M, N, K = 1024, 512, 256
+    g = torch.Generator(device=dev).manual_seed(1)
+    a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    b = (torch.randn(N, K, device=dev, generator=g) / math.sqrt(K)).bfloat16()
+    bias = torch.randn(N, device=dev, generator=g)
+    ref = a.float() @ b.float().t()
+    st = _status(dev)
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    F_.gemm_bf16(a, b, out, epi=F_.EPI_RELU, bias=bias, status=st)
+    assert _rel_err(out, torch.relu(ref + bias)) < 1e-2
+    aux = torch.randn(M, N, device=dev, generator=g).bfloat16()
+    F_.gemm_bf16(a, b, out, epi=F_.EPI_RELU_MASK, aux=aux, status=st)
+    assert _rel_err(out, ref * (aux.float() > 0)) < 1e-2
+    o32 = torch.empty(M, N, device=dev)
+    F_.gemm_bf16(a, b, o32, epi=F_.EPI_F32, bias=bias, status=st)
+    assert _rel_err(o32, ref + bias) < 1e-3
+    x0 = torch.randn(M, N, device=dev, generator=g).bfloat16()
+    F_.gemm_bf16(a, b, out, epi=F_.EPI_CROSS, bias=bias, aux=aux, x0=x0, status=st)
+    assert _rel_err(out, x0.float() * (ref + bias) + aux.float()) < 1e-2
+    # strided output (column slice of a wider buffer) and explicit tile widths
+    wide = torch.zeros(M, 4 * N, device=dev, dtype=torch.bfloat16)
+    for bn in (64, 128, 256):
+        F_.gemm_bf16(a, b, wide[:, N:2 * N], epi=F_.EPI_NONE, status=st, bn=bn)
+        assert _rel_err(wide[:, N:2 * N], ref) < 1e-2
+        assert wide[:, :N].abs().sum().item() == 0 and wide[:, 2 * N:].abs().sum().item() == 0
+    torch.cuda.synchronize()
+    assert st.item() == 0
+
+
+@pytest.mark.parametrize("R,M,N", [(256, 128, 64), (4096, 256, 512), (8192, 1024, 1024), (1000, 128, 256), (65536, 512, 64)])
+def test_gemm_nt_wgrad(dev, R, M, N):
+    from recstore_b200.ops import functional as F_
+    g = torch.Generator(device=dev).manual_seed(R + M)
+    a = (torch.randn(R, M, device=dev, generator=g) / math.sqrt(R)).bfloat16()
+    b = torch.randn(R, N, device=dev, generator=g).bfloat16()
+    out = torch.zeros(M, N, device=dev)
+    st = _status(dev)
+    F_.gemm_bf16(a, b, out, mode=1, epi=F_.EPI_ATOMIC_F32, status=st)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    ref = a.float().t() @ b.float()
+    assert _rel_err(out, ref) < 2e-3
+    # accumulates on a second call
+    F_.gemm_bf16(a, b, out, mode=1, epi=F_.EPI_ATOMIC_F32, status=st, splits=3)
+    assert _rel_err(out, 2 * ref) < 2e-3
+
+
+# ---------------------------------------------------------------------------------------------- embedding
+def _emb_setup(dev, T, B, D, rows, hot, seed=0):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    base = [0]
+    for r in rows:
+        base.append(base[-1] + r)
+    weight = torch.randn(base[-1], D, device=dev, generator=g)
+    ids = [torch.randint(0, rows[t], (B * hot[t],), device=dev, generator=g) for t in range(T)]
+    # force many duplicates
+    for t in range(T):
+        ids[t][::3] = 0
+        ids[t][1::7] = min(rows[t] - 1, 5)
+    return weight, base, ids
+
+
+@pytest.mark.parametrize("D,hot", [(128, [1, 1, 1]), (128, [3, 1, 40]), (32, [2, 2, 2]), (400, [1, 5, 1])])
+def test_embedding_forward_backward(dev, D, hot):
+    from recstore_b200.ops import functional as F_
+    T, B = 3, 777
+    rows = [50, 1000, 33]
+    weight, base, ids = _emb_setup(dev, T, B, D, rows, hot)
+    w0 = weight.clone()
+    i64 = dict(dtype=torch.int64, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    table_base = torch.tensor(base[:-1], **i64)
+    table_rows = torch.tensor(rows, **i64)
+    hb = [0]
+    for h in hot:
+        hb.append(hb[-1] + B * h)
+    nnz = hb[-1]
+    indices = torch.cat(ids)
+    out = torch.zeros(B, T * D, device=dev, dtype=torch.float32)
+    dst_table = torch.tensor([out.data_ptr()], **i64)
+    dst_col = torch.tensor([t * D for t in range(T)], **i32)
+    row_idx = torch.empty(nnz, **i64)
+    occ2bag = torch.empty(nnz, **i32)
+    st = _status(dev)
+    F_.emb_forward(weight, table_base, table_rows, indices, hotness=torch.tensor(hot, **i32),
+                   hot_base=torch.tensor(hb[:-1], **i64), T=T, B=B, D=D, B_local=B, dst_table=dst_table,
+                   dst_row_stride=T * D, dst_col=dst_col, out_bf16=False, row_idx=row_idx, occ2bag=occ2bag, status=st)
+    ref = torch.cat([weight[base[t]:base[t + 1]][ids[t].view(B, hot[t])].sum(1) for t in range(T)], 1)
+    torch.cuda.synchronize()
+    assert st.item() == 0
+    assert torch.allclose(out, ref, atol=1e-4, rtol=1e-5)
+    # bf16 output variant
+    outb = torch.zeros(B, T * D, device=dev, dtype=torch.bfloat16)
+    F_.emb_forward(weight, table_base, table_rows, indices, hotness=torch.tensor(hot, **i32),
+                   hot_base=torch.tensor(hb[:-1], **i64), T=T, B=B, D=D, B_local=B,
+                   dst_table=torch.tensor([outb.data_ptr()], **i64), dst_row_stride=T * D, dst_col=dst_col,
+                   out_bf16=True, status=st)
+    assert _rel_err(outb, ref) < 5e-3
+
+    # ---- backward: row-wise Adagrad and SGD against the reference semantics
+    from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update, sgd_update
+    grad = torch.randn(B, T * D, device=dev)
+    grad_col = dst_col
+    for opt in ("rowwise_adagrad", "sgd"):
+        weight.copy_(w0)
+        state = torch.zeros(weight.shape[0], device=dev)
+        wr, sr = w0.clone(), torch.zeros(weight.shape[0], device=dev)
+        for step in range(2):
+            F_.emb_backward(weight, state, row_idx, occ2bag, nnz, grad, grad_col=grad_col, grad_row_stride=T * D,
+                            B=B, D=D, grad_bf16=False, lr=0.05, eps=1e-8, optimizer=opt, status=st)
+            for t in range(T):
+                g_t = grad[:, t * D:(t + 1) * D].repeat_interleave(hot[t], 0)
+                idx = ids[t] + base[t]
+                if opt == "sgd":
+                    sgd_update(wr, idx, g_t, 0.05)
+                else:
+                    rowwise_adagrad_update(wr, sr, idx, g_t, 0.05, 1e-8)
+        torch.cuda.synchronize()
+        assert st.item() == 0
+        assert torch.allclose(weight, wr, atol=2e-3, rtol=2e-3), (opt, (weight - wr).abs().max())
+        if opt != "sgd":
+            assert torch.allclose(state, sr, atol=1e-3, rtol=1e-3)
+
+
+def test_embedding_oob_id_sets_status(dev):
+    from recstore_b200.ops import functional as F_
+    D, B = 16, 8
+    weight = torch.ones(10, D, device=dev)
+    i64 = dict(dtype=torch.int64, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    ids = torch.tensor([0, 1, 2, 99, 4, 5, 6, 7], **i64)
+    out = torch.zeros(B, D, device=dev)
+    st = _status(dev)
+    F_.emb_forward(weight, torch.tensor([0], **i64), torch.tensor([10], **i64), ids, hotness=torch.tensor([1], **i32),
+                   hot_base=torch.tensor([0], **i64), T=1, B=B, D=D, B_local=B,
+                   dst_table=torch.tensor([out.data_ptr()], **i64), dst_row_stride=D,
+                   dst_col=torch.tensor([0], **i32), out_bf16=False, status=st)
+    torch.cuda.synchronize()
+    assert st.item() & 1  # RS_DEV_OOB_ROW, and the kernel did not fault
+    assert out[3].abs().sum().item() == 0 and out[2].sum().item() == D
+
+
+# ---------------------------------------------------------------------------------------------- interaction
+@pytest.mark.parametrize("F,D", [(27, 128), (9, 64), (32, 128), (2, 16)])
+def test_interaction(dev, F, D):
+    from recstore_b200.ops import functional as F_
+    B = 301
+    g = torch.Generator(device=dev).manual_seed(F * D)
+    T = (torch.randn(B, F, D, device=dev, generator=g) * 0.5).bfloat16()
+    n_inter = D + F * (F - 1) // 2
+    ld = (n_inter + 63) // 64 * 64
+    out = torch.full((B, ld), 7.0, device=dev, dtype=torch.bfloat16)
+    F_.interaction_forward(T, B, F, D, out)
+    Tf = T.float().requires_grad_(True)
+    Z = torch.bmm(Tf, Tf.transpose(1, 2))
+    li, lj = torch.tril_indices(F, F, offset=-1)
+    ref = torch.cat([Tf[:, 0], Z[:, li, lj]], 1)
+    torch.cuda.synchronize()
+    assert _rel_err(out[:, :n_inter], ref) < 1e-2
+    assert out[:, n_inter:].abs().sum().item() == 0
+
+    dout = torch.zeros(B, ld, device=dev, dtype=torch.bfloat16)
+    dout[:, :n_inter] = (torch.randn(B, n_inter, device=dev, generator=g) * 0.1).bfloat16()
+    ref.backward(dout[:, :n_inter].float())
+    gref = Tf.grad                                   # [B, F, D]
+    dx = torch.zeros(B, D, device=dev, dtype=torch.bfloat16)
+    Gw = torch.zeros(B, (F - 1) * D + 8, device=dev, dtype=torch.bfloat16)
+    i32 = dict(dtype=torch.int32, device=dev)
+    F_.interaction_backward(T, dout, B, F, D, dx, torch.tensor([Gw.data_ptr()], dtype=torch.int64, device=dev),
+                            torch.zeros(max(F - 1, 1), **i32), torch.tensor([f * D for f in range(max(F - 1, 1))], **i32),
+                            Gw.stride(0), 0, relu_mask_dx=False)
+    torch.cuda.synchronize()
+    assert _rel_err(dx, gref[:, 0]) < 2e-2
+    if F > 1:
+        assert _rel_err(Gw[:, :(F - 1) * D].view(B, F - 1, D), gref[:, 1:]) < 2e-2
+    # with the ReLU mask of feature 0
+    F_.interaction_backward(T, dout, B, F, D, dx, torch.tensor([Gw.data_ptr()], dtype=torch.int64, device=dev),
+                            torch.zeros(max(F - 1, 1), **i32), torch.tensor([f * D for f in range(max(F - 1, 1))], **i32),
+                            Gw.stride(0), 0, relu_mask_dx=True)
+    assert _rel_err(dx, gref[:, 0] * (T[:, 0].float() > 0)) < 2e-2
+
+
+# ---------------------------------------------------------------------------------------------- head / small dense ops
+def test_head_bce_and_small_ops(dev):
+    from recstore_b200.ops import functional as F_
+    M, K, Bglob = 1000, 256, 4000
+    g = torch.Generator(device=dev).manual_seed(3)
+    x = torch.relu(torch.randn(M, K, device=dev, generator=g)).bfloat16()
+    w = (torch.randn(K, device=dev, generator=g) * 0.1).requires_grad_(True)
+    b = torch.randn(1, device=dev, generator=g).requires_grad_(True)
+    y = (torch.rand(M, device=dev, generator=g) < 0.25).float()
+    xf = x.float().requires_grad_(True)
+    logit = xf @ w + b
+    loss = torch.nn.functional.binary_cross_entropy_with_logits(logit, y, reduction="sum") / Bglob
+    loss.backward()
+    prob = torch.empty(M, device=dev)
+    ls = torch.zeros(1, device=dev)
+    dx = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+    dw = torch.zeros(K, device=dev)
+    db = torch.zeros(1, device=dev)
+    F_.head_bce(x, w.detach(), b.detach(), y, 1.0 / Bglob, prob=prob, loss_sum=ls, dx=dx, dw=dw, db=db)
+    torch.cuda.synchronize()
+    assert abs(ls.item() - loss.item()) < 1e-4 * max(1.0, abs(loss.item()))
+    assert torch.allclose(prob, torch.sigmoid(logit.detach()), atol=1e-4)
+    assert _rel_err(dw, w.grad) < 1e-3 and _rel_err(db, b.grad) < 1e-3
+    assert _rel_err(dx, xf.grad * (x.float() > 0)) < 1e-2
+
+    dy = torch.randn(777, 300, device=dev, generator=g).bfloat16()
+    cs = torch.zeros(300, device=dev)
+    F_.colsum_bf16(dy, cs)
+    assert torch.allclose(cs, dy.float().sum(0), atol=1e-2, rtol=1e-3)
+
+    W = torch.randn(70, 100, device=dev, generator=g)
+    G = torch.randn(70, 100, device=dev, generator=g)
+    Wr = W - 0.1 * G
+    wb = torch.empty(70, 100, device=dev, dtype=torch.bfloat16)
+    wt = torch.empty(100, 70, device=dev, dtype=torch.bfloat16)
+    F_.dense_sgd(W, G, 0.1, wb, wt, zero_grad=True)
+    assert torch.allclose(W, Wr) and G.abs().sum().item() == 0
+    assert torch.equal(wb, Wr.bfloat16()) and torch.equal(wt, Wr.t().bfloat16())
+
+    xin = torch.randn(50, 13, device=dev, generator=g)
+    xo = torch.full((50, 64), 3.0, device=dev, dtype=torch.bfloat16)
+    F_.pad_cast_bf16(xin, xo)
+    assert torch.equal(xo[:, :13], xin.bfloat16()) and xo[:, 13:].abs().sum().item() == 0
+
+
+# ---------------------------------------------------------------------------------------------- whole DLRM step
+@pytest.mark.parametrize("graph", [False, True])
+def test_dlrm_step_matches_torch_oracle(dev, graph):
+    from recstore_b200.models.dlrm import DLRM, DLRMConfig
+    from recstore_b200.baseline.dlrm_torch import TorchDLRM
+    from recstore_b200.utils.data import DLRMBatchSource
+    rows = [1000, 37, 5000, 12, 300, 20000]
+    hot = [1, 2, 1, 3, 1, 1]
+    B = 512
+    cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=0.05, mlp_lr=0.05, seed=5, use_cuda_graph=graph)
+    eng = DLRM(cfg)
+    ora = TorchDLRM(rows, B, hotness=hot, emb_lr=0.05, mlp_lr=0.05, device=dev, seed=5)
+    # identical initial state
+    with torch.no_grad():
+        sd = eng.dense_state()
+        for k, v in sd.items():
+            ora.params[k].copy_(v.view_as(ora.params[k]))
+        for t in range(len(rows)):
+            ora.tables[t].copy_(eng.table_weight(t))
+    src = DLRMBatchSource(rows, hot, B, alpha=1.2, seed=9)
+    losses = []
+    for step in range(3):
+        b = src.next()
+        l_ref = ora.train_step(b.dense, b.ids, b.labels).item()
+        l = eng.train_step(eng.make_pinned_batch(b.dense, b.ids, b.labels))
+        losses.append((l, l_ref))
+    eng.check()
+    for l, l_ref in losses:
+        assert abs(l - l_ref) < 2e-2 * max(1.0, abs(l_ref)), losses
+    sd = eng.dense_state()
+    for k, v in sd.items():
+        ref = ora.params[k].detach().view_as(v)
+        assert _rel_err(v, ref) < 3e-2, k
+    for t in range(len(rows)):
+        assert _rel_err(eng.table_weight(t), ora.tables[t]) < 3e-2, t
+        assert _rel_err(eng.table_state(t), ora.states[t]) < 6e-2, t
