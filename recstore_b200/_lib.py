@@ -63,12 +63,12 @@ _SIGNATURES = {
     "rs_gemm_bf16": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp]),
     # ops/embedding.cu
     "rs_emb_forward": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i64, vp, i32, vp, vp, vp, vp, vp]),
-    "rs_emb_backward": (i32, [vp, vp, i64, vp, vp, i64, vp, vp, i64, i32, i32, i32, vp, f32, f32, i32, vp, vp]),
+    "rs_emb_backward": (i32, [vp, vp, i64, vp, vp, i64, vp, vp, i64, vp, i32, i32, i32, i32, vp, f32, f32, i32, vp, vp]),
     "rs_rows_gather": (i32, [vp, vp, i64, i32, vp, vp]),
     "rs_rows_scatter": (i32, [vp, vp, i64, i32, vp, vp]),
     # ops/interaction.cu
     "rs_interaction_forward": (i32, [vp, i32, i32, i32, vp, i32, vp]),
-    "rs_interaction_backward": (i32, [vp, vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, i64, i64, i32, vp]),
+    "rs_interaction_backward": (i32, [vp, vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, i64, i64, i32, vp, i32, vp]),
     # ops/dense.cu
     "rs_head_bce": (i32, [vp, i32, i32, i32, vp, vp, vp, f32, vp, vp, vp, i32, vp, vp, vp]),
     "rs_colsum_bf16": (i32, [vp, i32, i32, i32, vp, vp]),

@@ -50,93 +50,12 @@ struct EmbFwdArgs {
 
 constexpr int kMaxChunks = 4;  // D <= 512
 
-__global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
-  const int warps_per_block = blockDim.x >> 5;
-  const long long bag = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  const long long nbags = static_cast<long long>(a.T) * a.B;
-  if (bag >= nbags) return;
-  const int t = static_cast<int>(bag / a.B);
-  const int b = static_cast<int>(bag % a.B);
-  long long beg, end;
-  if (a.offsets) {
-    beg = a.offsets[bag];
-    end = a.offsets[bag + 1];
-  } else {
-    const int h = a.hotness[t];
-    beg = a.hot_base[t] + static_cast<long long>(b) * h;
-    end = beg + h;
-  }
-  const long long base = a.table_base[t];
-  const long long nrows = a.table_rows[t];
-  const int nvec = a.D >> 2;  // float4 per row
-  float4 acc[kMaxChunks];
-#pragma unroll
-  for (int c = 0; c < kMaxChunks; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-
-  for (long long i0 = beg; i0 < end; i0 += 32) {
-    const int n = static_cast<int>(min(32ll, end - i0));
-    long long my_row = -1;
-    float my_w = 1.f;
-    if (lane < n) {
-      const long long id = a.indices[i0 + lane];
-      if (a.use_hash) {
-        const int r = rs::ht_find(a.ht, static_cast<unsigned long long>(id));
-        my_row = r;  // absent key -> -1 -> contributes zeros
-      } else if (id >= 0 && id < nrows) {
-        my_row = base + id;
-      } else if (a.status) {
-        atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
-      }
-      if (a.psw) my_w = a.psw[i0 + lane];
-      if (a.row_idx) a.row_idx[i0 + lane] = my_row;
-      if (a.occ2bag) a.occ2bag[i0 + lane] = static_cast<int>(bag);
-    }
-    int j = 0;
-    for (; j + 4 <= n; j += 4) {
-      long long r[4];
-      float w[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        r[u] = __shfl_sync(0xffffffffu, my_row, j + u);
-        w[u] = __shfl_sync(0xffffffffu, my_w, j + u);
-      }
-#pragma unroll
-      for (int c = 0; c < kMaxChunks; ++c) {
-        const int v = lane + c * 32;
-        if (v < nvec) {
-          float4 x[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            x[u] = r[u] >= 0 ? __ldg(reinterpret_cast<const float4*>(a.weight + r[u] * a.D) + v)
-                             : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            acc[c].x += w[u] * x[u].x; acc[c].y += w[u] * x[u].y;
-            acc[c].z += w[u] * x[u].z; acc[c].w += w[u] * x[u].w;
-          }
-        }
-      }
-    }
-    for (; j < n; ++j) {
-      const long long r = __shfl_sync(0xffffffffu, my_row, j);
-      const float w = __shfl_sync(0xffffffffu, my_w, j);
-      if (r < 0) continue;
-#pragma unroll
-      for (int c = 0; c < kMaxChunks; ++c) {
-        const int v = lane + c * 32;
-        if (v < nvec) {
-          const float4 x = __ldg(reinterpret_cast<const float4*>(a.weight + r * a.D) + v);
-          acc[c].x += w * x.x; acc[c].y += w * x.y; acc[c].z += w * x.z; acc[c].w += w * x.w;
-        }
-      }
-    }
-  }
-
+template <int NC>
+__device__ __forceinline__ void store_pooled(const EmbFwdArgs& a, int t, int b, const float4 (&acc)[NC], int lane, int nvec) {
   const int dst_rank = b / a.B_local;
   const long long off = static_cast<long long>(b - dst_rank * a.B_local) * a.dst_row_stride + a.dst_col[t];
 #pragma unroll
-  for (int c = 0; c < kMaxChunks; ++c) {
+  for (int c = 0; c < NC; ++c) {
     const int v = lane + c * 32;
     if (v < nvec) {
       if (a.out_bf16) {
@@ -155,6 +74,117 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
   }
 }
 
+// One warp per block of 32 consecutive bags of one table.  Lane i first resolves the metadata of
+// bag i (id range, and for single-id bags the row itself) with coalesced loads; the rows are then
+// fetched 8 bags at a time so that every warp keeps 8 independent 512-byte reads in flight.
+template <int NC>
+__global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
+  const int warps_per_block = blockDim.x >> 5;
+  const long long blk = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int blocks_per_table = (a.B + 31) >> 5;
+  if (blk >= static_cast<long long>(a.T) * blocks_per_table) return;
+  const int t = static_cast<int>(blk / blocks_per_table);
+  const int b0 = static_cast<int>(blk % blocks_per_table) << 5;
+  const int nb = min(32, a.B - b0);
+  const long long base = a.table_base[t];
+  const long long nrows = a.table_rows[t];
+  const int nvec = a.D >> 2;
+
+  long long beg = 0, end = 0;
+  if (lane < nb) {
+    const long long bag = static_cast<long long>(t) * a.B + b0 + lane;
+    if (a.offsets) {
+      beg = a.offsets[bag];
+      end = a.offsets[bag + 1];
+    } else {
+      const int h = a.hotness[t];
+      beg = a.hot_base[t] + static_cast<long long>(b0 + lane) * h;
+      end = beg + h;
+    }
+  }
+  const bool single = __all_sync(0xffffffffu, lane >= nb || end - beg == 1);
+  if (single && a.psw == nullptr) {
+    long long my_row = -1;
+    if (lane < nb) {
+      const long long id = a.indices[beg];
+      if (a.use_hash) my_row = rs::ht_find(a.ht, static_cast<unsigned long long>(id));
+      else if (id >= 0 && id < nrows) my_row = base + id;
+      else if (a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
+      if (a.row_idx) a.row_idx[beg] = my_row;
+      if (a.occ2bag) a.occ2bag[beg] = static_cast<int>(static_cast<long long>(t) * a.B + b0 + lane);
+    }
+    for (int j0 = 0; j0 < nb; j0 += 8) {
+      float4 x[8][NC];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const long long r = __shfl_sync(0xffffffffu, my_row, (j0 + u) & 31);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          const int v = lane + c * 32;
+          x[u][c] = (j0 + u < nb && r >= 0 && v < nvec) ? __ldg(reinterpret_cast<const float4*>(a.weight + r * a.D) + v)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (j0 + u < nb) store_pooled<NC>(a, t, b0 + j0 + u, x[u], lane, nvec);
+    }
+    return;
+  }
+
+  // General path: pooled bags (several ids, optional per-sample weights).
+  for (int j = 0; j < nb; ++j) {
+    const long long jb = __shfl_sync(0xffffffffu, beg, j);
+    const long long je = __shfl_sync(0xffffffffu, end, j);
+    const long long bag = static_cast<long long>(t) * a.B + b0 + j;
+    float4 acc[NC];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (long long i0 = jb; i0 < je; i0 += 32) {
+      const int n = static_cast<int>(min(32ll, je - i0));
+      long long my_row = -1;
+      float my_w = 1.f;
+      if (lane < n) {
+        const long long id = a.indices[i0 + lane];
+        if (a.use_hash) my_row = rs::ht_find(a.ht, static_cast<unsigned long long>(id));
+        else if (id >= 0 && id < nrows) my_row = base + id;
+        else if (a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
+        if (a.psw) my_w = a.psw[i0 + lane];
+        if (a.row_idx) a.row_idx[i0 + lane] = my_row;
+        if (a.occ2bag) a.occ2bag[i0 + lane] = static_cast<int>(bag);
+      }
+      for (int k0 = 0; k0 < n; k0 += 4) {
+        long long r[4];
+        float w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          r[u] = __shfl_sync(0xffffffffu, my_row, (k0 + u) & 31);
+          w[u] = __shfl_sync(0xffffffffu, my_w, (k0 + u) & 31);
+          if (k0 + u >= n) r[u] = -1;
+        }
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          const int v = lane + c * 32;
+          if (v < nvec) {
+            float4 x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              x[u] = r[u] >= 0 ? __ldg(reinterpret_cast<const float4*>(a.weight + r[u] * a.D) + v)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              acc[c].x += w[u] * x[u].x; acc[c].y += w[u] * x[u].y;
+              acc[c].z += w[u] * x[u].z; acc[c].w += w[u] * x[u].w;
+            }
+          }
+        }
+      }
+    }
+    store_pooled<NC>(a, t, b0 + j, acc, lane, nvec);
+  }
+}
+
 // ------------------------------------------------------------------ backward
 struct EmbBwdArgs {
   float* weight;
@@ -165,11 +195,12 @@ struct EmbBwdArgs {
   const void* grad;              // per-bag gradients
   const int* grad_col;           // [T] element offset of the table's slice inside a gradient row, or null
   long long grad_row_stride;     // elements between samples
+  const float* gnorm;            // optional [B, gnorm_stride]: sum of squares of each bag gradient
+  int gnorm_stride;
   int B, D, grad_bf16;
   const float* psw;
   float lr, eps;
   int optimizer;                 // 0 = SGD, 1 = row-wise Adagrad
-  int pass;                      // Adagrad: 1 = accumulate state, 2 = apply; SGD: ignored
   long long total_rows;
   unsigned long long* status;
 };
@@ -177,10 +208,74 @@ struct EmbBwdArgs {
 constexpr int kGroup = 256;
 constexpr int kSlots = 512;
 
-__global__ void __launch_bounds__(kGroup) emb_bwd_kernel(const EmbBwdArgs a) {
+template <int NC>
+__device__ __forceinline__ void load_grad(const EmbBwdArgs& a, long long goff, int lane, int nvec, float4 (&g)[NC]) {
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int v = lane + c * 32;
+    if (v < nvec) {
+      if (a.grad_bf16) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.grad) + goff) + v);
+        const float2 flo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 fhi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        g[c] = make_float4(flo.x, flo.y, fhi.x, fhi.y);
+      } else {
+        g[c] = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.grad) + goff) + v);
+      }
+    } else {
+      g[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+}
+
+// Pass 1 of row-wise Adagrad: state[row] += w^2 * |g_bag|^2 / D for every occurrence.
+// With precomputed bag norms this is one thread per occurrence; otherwise one warp per occurrence.
+template <int NC>
+__global__ void __launch_bounds__(256) emb_state_kernel(const EmbBwdArgs a) {
+  const float inv_d = 1.f / static_cast<float>(a.D);
+  if (a.gnorm) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= a.nnz) return;
+    const long long row = a.row_idx[i];
+    if (row < 0 || row >= a.total_rows) return;
+    const long long bag = a.occ2bag ? a.occ2bag[i] : i;
+    const int t = static_cast<int>(bag / a.B);
+    const long long b = bag % a.B;
+    const float w = a.psw ? a.psw[i] : 1.f;
+    atomicAdd(&a.state[row], w * w * a.gnorm[b * a.gnorm_stride + t] * inv_d);
+    return;
+  }
+  const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= a.nnz) return;
+  const int lane = threadIdx.x & 31;
+  const long long row = a.row_idx[i];
+  if (row < 0 || row >= a.total_rows) return;
+  const long long bag = a.occ2bag ? a.occ2bag[i] : i;
+  const int t = static_cast<int>(bag / a.B);
+  const long long b = bag % a.B;
+  const long long goff = b * a.grad_row_stride + (a.grad_col ? a.grad_col[t] : 0);
+  const float w = a.psw ? a.psw[i] : 1.f;
+  float4 g[NC];
+  load_grad<NC>(a, goff, lane, a.D >> 2, g);
+  float sq = 0.f;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) sq += g[c].x * g[c].x + g[c].y * g[c].y + g[c].z * g[c].z + g[c].w * g[c].w;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  if (lane == 0) atomicAdd(&a.state[row], w * w * sq * inv_d);
+}
+
+// Apply pass: one CTA per group of 256 occurrences.  Threads first resolve their occurrence
+// (row, gradient offset, weight) into shared memory and chain equal rows into linked lists through
+// a shared-memory hash; then each warp takes distinct rows in turn, sums the gradients of the
+// chain (4 loads in flight) and issues ONE vector atomic per row and group.
+template <int NC>
+__global__ void __launch_bounds__(kGroup) emb_apply_kernel(const EmbBwdArgs a) {
   __shared__ long long s_key[kSlots];
   __shared__ int s_head[kSlots];
   __shared__ int s_next[kGroup];
+  __shared__ long long s_goff[kGroup];
+  __shared__ float s_w[kGroup];
   __shared__ int s_leader_slot[kGroup];
   __shared__ int s_nleaders;
 
@@ -195,11 +290,17 @@ __global__ void __launch_bounds__(kGroup) emb_bwd_kernel(const EmbBwdArgs a) {
 
   long long row = -1;
   if (g0 + tid < a.nnz) {
-    row = a.row_idx[g0 + tid];
+    const long long occ = g0 + tid;
+    row = a.row_idx[occ];
     if (row >= a.total_rows) {
       if (a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
       row = -1;
     }
+    const long long bag = a.occ2bag ? a.occ2bag[occ] : occ;
+    const int t = static_cast<int>(bag / a.B);
+    const long long b = bag % a.B;
+    s_goff[tid] = b * a.grad_row_stride + (a.grad_col ? a.grad_col[t] : 0);
+    s_w[tid] = a.psw ? a.psw[occ] : 1.f;
   }
   if (row >= 0) {
     unsigned s = static_cast<unsigned>(rs::ht_hash(static_cast<unsigned long long>(row))) & (kSlots - 1);
@@ -223,54 +324,40 @@ __global__ void __launch_bounds__(kGroup) emb_bwd_kernel(const EmbBwdArgs a) {
   const int warp = tid >> 5, lane = tid & 31;
   const int nvec = a.D >> 2;
   const int nleaders = s_nleaders;
-  const float inv_d = 1.f / static_cast<float>(a.D);
   for (int k = warp; k < nleaders; k += kGroup / 32) {
     const int slot = s_leader_slot[k];
     const long long r = s_key[slot];
-    float4 acc[kMaxChunks];
+    float4 acc[NC];
 #pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float sq = 0.f;
-    for (int j = s_head[slot]; j >= 0; j = s_next[j]) {
-      const long long occ = g0 + j;
-      const long long bag = a.occ2bag ? a.occ2bag[occ] : occ;
-      const int t = static_cast<int>(bag / a.B);
-      const long long b = bag % a.B;
-      const long long goff = b * a.grad_row_stride + (a.grad_col ? a.grad_col[t] : 0);
-      const float w = a.psw ? a.psw[occ] : 1.f;
+    for (int c = 0; c < NC; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int j = s_head[slot];
+    while (j >= 0) {
+      int jj[4];
+      float4 g[4][NC];
 #pragma unroll
-      for (int c = 0; c < kMaxChunks; ++c) {
-        const int v = lane + c * 32;
-        if (v < nvec) {
-          float4 g;
-          if (a.grad_bf16) {
-            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.grad) + goff) + v);
-            const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-            const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-            const float2 flo = __bfloat1622float2(lo), fhi = __bfloat1622float2(hi);
-            g = make_float4(flo.x, flo.y, fhi.x, fhi.y);
-          } else {
-            g = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.grad) + goff) + v);
+      for (int u = 0; u < 4; ++u) {
+        jj[u] = j;
+        if (j >= 0) {
+          load_grad<NC>(a, s_goff[j], lane, nvec, g[u]);
+          j = s_next[j];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (jj[u] >= 0) {
+          const float w = s_w[jj[u]];
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            acc[c].x += w * g[u][c].x; acc[c].y += w * g[u][c].y;
+            acc[c].z += w * g[u][c].z; acc[c].w += w * g[u][c].w;
           }
-          g.x *= w; g.y *= w; g.z *= w; g.w *= w;
-          acc[c].x += g.x; acc[c].y += g.y; acc[c].z += g.z; acc[c].w += g.w;
-          sq += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
         }
       }
     }
-    if (a.optimizer == 1 && a.pass == 1) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-      if (lane == 0) atomicAdd(&a.state[r], sq * inv_d);
-      continue;
-    }
     float scale = -a.lr;
-    if (a.optimizer == 1) {
-      const float st = __ldcv(&a.state[r]);
-      scale = -a.lr / (sqrtf(st) + a.eps);
-    }
+    if (a.optimizer == 1) scale = -a.lr / (sqrtf(__ldcv(&a.state[r])) + a.eps);
 #pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
+    for (int c = 0; c < NC; ++c) {
       const int v = lane + c * 32;
       if (v < nvec) {
         float4 u = make_float4(scale * acc[c].x, scale * acc[c].y, scale * acc[c].z, scale * acc[c].w);
@@ -324,20 +411,25 @@ RS_API int rs_emb_forward(const float* weight, const long long* table_base, cons
   a.use_hash = ht != nullptr;
   if (ht) a.ht = *ht; else memset(&a.ht, 0, sizeof(a.ht));
   a.status = status;
-  const long long nbags = static_cast<long long>(T) * B;
+  const long long nblocks = static_cast<long long>(T) * ((B + 31) / 32);
   const int wpb = 8;
-  const long long grid = (nbags + wpb - 1) / wpb;
+  const long long grid = (nblocks + wpb - 1) / wpb;
   RS_REQUIRE(grid < (1ll << 31), "rs_emb_forward: too many bags");
-  emb_fwd_kernel<<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
+  if (D <= 128) emb_fwd_kernel<1><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
+  else if (D <= 256) emb_fwd_kernel<2><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
+  else emb_fwd_kernel<4><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
 
 // optimizer: 0 SGD (one launch), 1 row-wise Adagrad (two launches: state pass, apply pass).
+// gnorm (optional): precomputed sum of squares of every bag gradient, [B, gnorm_stride] fp32 indexed
+// [sample, local table]; saves the state pass a full read of the gradients.
 RS_API int rs_emb_backward(float* weight, float* state, long long total_rows, const long long* row_idx,
                            const int* occ2bag, long long nnz, const void* grad, const int* grad_col,
-                           long long grad_row_stride, int B, int D, int grad_bf16, const float* psw, float lr,
-                           float eps, int optimizer, unsigned long long* status, cudaStream_t stream) {
+                           long long grad_row_stride, const float* gnorm, int gnorm_stride, int B, int D,
+                           int grad_bf16, const float* psw, float lr, float eps, int optimizer,
+                           unsigned long long* status, cudaStream_t stream) {
   RS_REQUIRE(weight && row_idx && grad, "rs_emb_backward: null argument");
   RS_REQUIRE(optimizer == 0 || (optimizer == 1 && state), "rs_emb_backward: row-wise Adagrad needs a state tensor");
   RS_REQUIRE(D % 4 == 0 && D > 0 && D <= 128 * kMaxChunks, "rs_emb_backward: D=%d must be a multiple of 4, <= 512", D);
@@ -345,19 +437,23 @@ RS_API int rs_emb_backward(float* weight, float* state, long long total_rows, co
   if (nnz == 0) return RS_OK;
   EmbBwdArgs a;
   a.weight = weight; a.state = state; a.row_idx = row_idx; a.occ2bag = occ2bag; a.nnz = nnz; a.grad = grad;
-  a.grad_col = grad_col; a.grad_row_stride = grad_row_stride; a.B = B; a.D = D; a.grad_bf16 = grad_bf16;
+  a.grad_col = grad_col; a.grad_row_stride = grad_row_stride; a.gnorm = gnorm; a.gnorm_stride = gnorm_stride;
+  a.B = B; a.D = D; a.grad_bf16 = grad_bf16;
   a.psw = psw; a.lr = lr; a.eps = eps; a.optimizer = optimizer; a.total_rows = total_rows; a.status = status;
   const long long grid = (nnz + kGroup - 1) / kGroup;
   RS_REQUIRE(grid < (1ll << 31), "rs_emb_backward: too many occurrences");
+  const int nc = D <= 128 ? 1 : (D <= 256 ? 2 : 4);
   if (optimizer == 1) {
-    a.pass = 1;
-    emb_bwd_kernel<<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
+    const long long g1 = gnorm ? (nnz + 255) / 256 : (nnz + 7) / 8;
+    RS_REQUIRE(g1 < (1ll << 31), "rs_emb_backward: too many occurrences");
+    if (nc == 1) emb_state_kernel<1><<<static_cast<unsigned>(g1), 256, 0, stream>>>(a);
+    else if (nc == 2) emb_state_kernel<2><<<static_cast<unsigned>(g1), 256, 0, stream>>>(a);
+    else emb_state_kernel<4><<<static_cast<unsigned>(g1), 256, 0, stream>>>(a);
     RS_LAUNCH_CHECK();
-    a.pass = 2;
-  } else {
-    a.pass = 0;
   }
-  emb_bwd_kernel<<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
+  if (nc == 1) emb_apply_kernel<1><<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
+  else if (nc == 2) emb_apply_kernel<2><<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
+  else emb_apply_kernel<4><<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

@@ -130,20 +130,27 @@ struct InterBwdArgs {
   long long grow_stride;      // elements per sample row in a gradient window
   long long sample_base;      // this rank's first global sample index (rank * B_local)
   int relu_mask_dx;           // feature 0 is a ReLU output: zero dx where it is not positive
+  float* const* ndst;         // optional [world]: per-owner [B_global, nstride] sum of squares of each pushed row
+  int nstride;
 };
 
-__global__ void __launch_bounds__(kWarps * 32) interaction_bwd_kernel(const InterBwdArgs a) {
-  __shared__ __align__(16) __nv_bfloat16 sT[kWarps][32 * kLd];
-  __shared__ __align__(16) __nv_bfloat16 sS[kWarps][32 * 40];  // symmetric dZ, padded rows of 40
+constexpr int kWarpsBwd = 3;  // 15.9 KB of shared memory per warp: 3 warps stay under the 48 KB static limit
+constexpr int kOutLd = 72;    // staging row: 64 columns + 8 pad (144 B, 16-byte aligned, conflict-free)
+
+__global__ void __launch_bounds__(kWarpsBwd * 32) interaction_bwd_kernel(const InterBwdArgs a) {
+  __shared__ __align__(16) __nv_bfloat16 sT[kWarpsBwd][32 * kLd];
+  __shared__ __align__(16) __nv_bfloat16 sS[kWarpsBwd][32 * 40];  // symmetric dZ, padded rows of 40
+  __shared__ __align__(16) __nv_bfloat16 sO[kWarpsBwd][32 * kOutLd];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x * kWarps + warp;
+  const int b = blockIdx.x * kWarpsBwd + warp;
   if (b >= a.B) return;
   const int F = a.F, D = a.D;
   __nv_bfloat16* t = sT[warp];
   __nv_bfloat16* s = sS[warp];
+  __nv_bfloat16* o = sO[warp];
   load_tile(t, a.T + static_cast<size_t>(b) * F * D, F, D, lane);
   const __nv_bfloat16* dout = a.dout + static_cast<size_t>(b) * a.dout_ld;
-  for (int i = lane; i < 32 * 40; i += 32) s[i] = __float2bfloat16(0.f);
+  for (int i = lane; i < 32 * 40 / 8; i += 32) reinterpret_cast<uint4*>(s)[i] = make_uint4(0, 0, 0, 0);
   __syncwarp();
   const int npairs = F * (F - 1) / 2;
   for (int p = lane; p < npairs; p += 32) {
@@ -158,7 +165,7 @@ __global__ void __launch_bounds__(kWarps * 32) interaction_bwd_kernel(const Inte
   }
   __syncwarp();
 
-  // dT[32 x D] = S[32 x 32] . T[32 x D]; two k-steps; loop over n in halves of 64 to bound registers.
+  // dT[32 x D] = S[32 x 32] . T[32 x D]; two k-steps; n in halves of 64 columns.
   uint32_t sa[2][2][4];  // [mt][ks]
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
@@ -167,6 +174,11 @@ __global__ void __launch_bounds__(kWarps * 32) interaction_bwd_kernel(const Inte
       ldmatrix_x4(sa[mt][ks], s + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 40 + ks * 16 + (lane >> 4) * 8);
 
   const int g = lane >> 2, q = lane & 3;
+  const int orow = lane >> 3, ochunk = lane & 7;  // coalesced store phase: 4 rows x 8 chunks of 16 B
+  float rownorm[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) rownorm[i] = 0.f;
+
   for (int n0 = 0; n0 < D; n0 += 64) {
     float acc[2][8][4];
 #pragma unroll
@@ -189,33 +201,69 @@ __global__ void __launch_bounds__(kWarps * 32) interaction_bwd_kernel(const Inte
         }
       }
     }
+    // fragments -> staging tile (bf16)
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        const int col = n0 + nt * 8 + q * 2;
-        if (col >= D) continue;
+        const int cl = nt * 8 + q * 2;  // column inside the half
+        const int col = n0 + cl;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int i = mt * 16 + g + h * 8;
-          if (i >= F) continue;
           float v0 = acc[mt][nt][h * 2], v1 = acc[mt][nt][h * 2 + 1];
-          __nv_bfloat16* dst;
-          if (i == 0) {
+          if (i == 0 && col < D) {
             v0 += __bfloat162float(dout[col]);
             v1 += __bfloat162float(dout[col + 1]);
             if (a.relu_mask_dx) {
               if (!(__bfloat162float(t[col]) > 0.f)) v0 = 0.f;
               if (!(__bfloat162float(t[col + 1]) > 0.f)) v1 = 0.f;
             }
-            dst = a.dx + static_cast<size_t>(b) * a.dx_ld + col;
-          } else {
-            const int f = i - 1;
-            dst = reinterpret_cast<__nv_bfloat16*>(a.gdst[a.owner[f]]) + (a.sample_base + b) * a.grow_stride + a.gcol[f] + col;
           }
-          *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
+          *reinterpret_cast<__nv_bfloat162*>(o + i * kOutLd + cl) = __floats2bfloat162_rn(v0, v1);
         }
       }
+    __syncwarp();
+    // staging tile -> global, 16 bytes per lane, 4 rows per instruction
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int i = it * 4 + orow;
+      const int col = n0 + ochunk * 8;
+      if (i < F && col < D) {
+        const uint4 v = *reinterpret_cast<const uint4*>(o + i * kOutLd + ochunk * 8);
+        const __nv_bfloat16* ve = reinterpret_cast<const __nv_bfloat16*>(&v);
+        float sq = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float f = __bfloat162float(ve[e]);
+          sq += f * f;
+        }
+        rownorm[it] += sq;
+        __nv_bfloat16* dst;
+        if (i == 0) {
+          dst = a.dx + static_cast<size_t>(b) * a.dx_ld + col;
+        } else {
+          const int f = i - 1;
+          dst = reinterpret_cast<__nv_bfloat16*>(a.gdst[a.owner[f]]) + (a.sample_base + b) * a.grow_stride + a.gcol[f] + col;
+        }
+        *reinterpret_cast<uint4*>(dst) = v;
+      }
+    }
+    __syncwarp();
+  }
+  if (a.ndst) {
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      float sq = rownorm[it];
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+      const int i = it * 4 + orow;
+      if (ochunk == 0 && i >= 1 && i < F) {
+        const int f = i - 1;
+        a.ndst[a.owner[f]][(a.sample_base + b) * a.nstride + a.gcol[f] / D] = sq;
+      }
+    }
   }
 }
 
@@ -235,7 +283,7 @@ RS_API int rs_interaction_forward(const void* T, int B, int F, int D, void* out,
 RS_API int rs_interaction_backward(const void* T, const void* dout, int B, int F, int D, int dout_ld, void* dx,
                                    int dx_ld, void* const* gdst, const int* owner, const int* gcol,
                                    long long grow_stride, long long sample_base, int relu_mask_dx,
-                                   cudaStream_t stream) {
+                                   void* const* ndst, int nstride, cudaStream_t stream) {
   RS_REQUIRE(T && dout && dx && gdst && owner && gcol, "rs_interaction_backward: null argument");
   RS_REQUIRE(F >= 1 && F <= kMaxF && D % 16 == 0 && D >= 16 && D <= kMaxD, "rs_interaction_backward: F=%d D=%d unsupported", F, D);
   if (B == 0) return RS_OK;
@@ -246,7 +294,8 @@ RS_API int rs_interaction_backward(const void* T, const void* dout, int B, int F
   a.dx = reinterpret_cast<__nv_bfloat16*>(dx); a.dx_ld = dx_ld;
   a.gdst = gdst; a.owner = owner; a.gcol = gcol; a.grow_stride = grow_stride; a.sample_base = sample_base;
   a.relu_mask_dx = relu_mask_dx;
-  interaction_bwd_kernel<<<(B + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(a);
+  a.ndst = reinterpret_cast<float* const*>(ndst); a.nstride = nstride;
+  interaction_bwd_kernel<<<(B + kWarpsBwd - 1) / kWarpsBwd, kWarpsBwd * 32, 0, stream>>>(a);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

@@ -1,0 +1,212 @@
+// Named timers and counters with mean / P50 / P99 over a sliding sample window, an ASCII report
+// and an optional background report thread.  Same role as xmh::Timer / PerfCounter / Reporter of
+// the reference (src/base/timer.h:292-629) and its pybind module (src/base/pybind_timer.cc:9-22).
+//
+// Design: one registry keyed by name; each entry keeps a fixed ring of the most recent samples
+// (sharded by thread to keep recording contention-free) plus cumulative count / sum.  Recording
+// is wait-free on the hot path (atomic index increment into the thread's shard).
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <cstdio>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "common/rs_common.h"
+
+namespace {
+
+constexpr int kShards = 16;
+constexpr int kRing = 1024;
+
+struct Series {
+  std::string name;
+  bool is_time;  // nanoseconds (timers) or plain values (counters)
+  struct Shard {
+    std::atomic<uint64_t> n{0};
+    double ring[kRing];
+  };
+  Shard shards[kShards];
+  std::atomic<uint64_t> count{0};
+  std::atomic<double> sum{0.0};
+  std::atomic<double> last{0.0};
+
+  void record(double v) {
+    static thread_local int shard = static_cast<int>(std::hash<std::thread::id>()(std::this_thread::get_id()) % kShards);
+    Shard& s = shards[shard];
+    const uint64_t i = s.n.fetch_add(1, std::memory_order_relaxed);
+    s.ring[i % kRing] = v;
+    count.fetch_add(1, std::memory_order_relaxed);
+    double old = sum.load(std::memory_order_relaxed);
+    while (!sum.compare_exchange_weak(old, old + v, std::memory_order_relaxed)) {}
+    last.store(v, std::memory_order_relaxed);
+  }
+  void snapshot(std::vector<double>* out) const {
+    out->clear();
+    for (const Shard& s : shards) {
+      const uint64_t n = std::min<uint64_t>(s.n.load(), kRing);
+      for (uint64_t i = 0; i < n; ++i) out->push_back(s.ring[i]);
+    }
+  }
+};
+
+struct Registry {
+  std::mutex mu;
+  std::map<std::string, std::unique_ptr<Series>> series;
+  std::thread reporter;
+  std::mutex rmu;
+  std::condition_variable rcv;
+  bool stop = false;
+  bool running = false;
+
+  Series* get(const char* name, bool is_time) {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = series.find(name);
+    if (it == series.end()) {
+      auto s = std::make_unique<Series>();
+      s->name = name;
+      s->is_time = is_time;
+      it = series.emplace(name, std::move(s)).first;
+    }
+    return it->second.get();
+  }
+
+  std::string report() {
+    std::vector<Series*> all;
+    {
+      std::lock_guard<std::mutex> lk(mu);
+      for (auto& kv : series) all.push_back(kv.second.get());
+    }
+    std::string out;
+    char line[256];
+    snprintf(line, sizeof(line), "+%s+\n", std::string(94, '-').c_str());
+    out += line;
+    snprintf(line, sizeof(line), "| %-34s | %10s | %10s | %10s | %10s | %5s |\n", "name", "count", "mean", "P50", "P99", "unit");
+    out += line;
+    std::vector<double> v;
+    for (Series* s : all) {
+      s->snapshot(&v);
+      double p50 = 0, p99 = 0;
+      if (!v.empty()) {
+        std::sort(v.begin(), v.end());
+        p50 = v[v.size() / 2];
+        p99 = v[std::min(v.size() - 1, static_cast<size_t>(v.size() * 0.99))];
+      }
+      const uint64_t c = s->count.load();
+      double mean = c ? s->sum.load() / c : 0.0;
+      const char* unit = "";
+      if (s->is_time) {
+        unit = "us";
+        mean /= 1e3; p50 /= 1e3; p99 /= 1e3;
+      }
+      snprintf(line, sizeof(line), "| %-34.34s | %10llu | %10.3f | %10.3f | %10.3f | %5s |\n", s->name.c_str(),
+               static_cast<unsigned long long>(c), mean, p50, p99, unit);
+      out += line;
+    }
+    snprintf(line, sizeof(line), "+%s+\n", std::string(94, '-').c_str());
+    out += line;
+    return out;
+  }
+};
+
+Registry& reg() {
+  static Registry* r = new Registry();  // leaked on purpose: threads may record during exit
+  return *r;
+}
+
+uint64_t now_ns() {
+  return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+}  // namespace
+
+RS_API unsigned long long rs_now_ns() { return now_ns(); }
+RS_API void* rs_timer_get(const char* name) { return reg().get(name, true); }
+RS_API void* rs_counter_get(const char* name) { return reg().get(name, false); }
+RS_API void rs_series_record(void* series, double v) {
+  if (series) static_cast<Series*>(series)->record(v);
+}
+RS_API void rs_timer_record_ns(const char* name, double ns) { reg().get(name, true)->record(ns); }
+RS_API void rs_counter_record(const char* name, double v) { reg().get(name, false)->record(v); }
+
+// mean, p50, p99, last, count of one series (times in nanoseconds); returns RS_ERR_NOTFOUND if unknown.
+RS_API int rs_series_stats(const char* name, double* out5) {
+  Registry& r = reg();
+  Series* s = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(r.mu);
+    auto it = r.series.find(name);
+    if (it != r.series.end()) s = it->second.get();
+  }
+  if (!s) return rs::set_error(RS_ERR_NOTFOUND, "no timer or counter named %s", name);
+  std::vector<double> v;
+  s->snapshot(&v);
+  std::sort(v.begin(), v.end());
+  const uint64_t c = s->count.load();
+  out5[0] = c ? s->sum.load() / c : 0.0;
+  out5[1] = v.empty() ? 0.0 : v[v.size() / 2];
+  out5[2] = v.empty() ? 0.0 : v[std::min(v.size() - 1, static_cast<size_t>(v.size() * 0.99))];
+  out5[3] = s->last.load();
+  out5[4] = static_cast<double>(c);
+  return RS_OK;
+}
+
+// Writes the report table into buf (truncated to cap-1 bytes); returns the full length.
+RS_API int rs_report(char* buf, int cap) {
+  const std::string s = reg().report();
+  if (buf && cap > 0) {
+    const int n = std::min<int>(cap - 1, static_cast<int>(s.size()));
+    memcpy(buf, s.data(), n);
+    buf[n] = 0;
+  }
+  return static_cast<int>(s.size());
+}
+
+RS_API int rs_report_thread_start(int period_ms) {
+  Registry& r = reg();
+  std::lock_guard<std::mutex> lk(r.rmu);
+  if (r.running) return RS_OK;
+  r.stop = false;
+  r.running = true;
+  r.reporter = std::thread([&r, period_ms] {
+    std::unique_lock<std::mutex> lk(r.rmu);
+    while (!r.stop) {
+      if (r.rcv.wait_for(lk, std::chrono::milliseconds(period_ms), [&] { return r.stop; })) break;
+      lk.unlock();
+      const std::string s = r.report();
+      fputs(s.c_str(), stderr);
+      lk.lock();
+    }
+  });
+  return RS_OK;
+}
+RS_API int rs_report_thread_stop() {
+  Registry& r = reg();
+  {
+    std::lock_guard<std::mutex> lk(r.rmu);
+    if (!r.running) return RS_OK;
+    r.stop = true;
+  }
+  r.rcv.notify_all();
+  r.reporter.join();
+  std::lock_guard<std::mutex> lk(r.rmu);
+  r.running = false;
+  return RS_OK;
+}
+// Resets every series to empty (handles returned by rs_timer_get stay valid).
+RS_API void rs_timers_clear() {
+  Registry& r = reg();
+  std::lock_guard<std::mutex> lk(r.mu);
+  for (auto& kv : r.series) {
+    Series* s = kv.second.get();
+    for (auto& sh : s->shards) sh.n.store(0);
+    s->count.store(0);
+    s->sum.store(0.0);
+    s->last.store(0.0);
+  }
+}

@@ -165,7 +165,11 @@ class DLRM:
         # ---- peer windows
         self.grow_stride = self.Tmax * self.D
         self.Twin = self.ctx.alloc("dlrm_T", self.Bl * self.F * self.D * 2)
-        self.Gwin = self.ctx.alloc("dlrm_G", self.B * self.grow_stride * 2)
+        # gradient window: [B, Tmax*D] bf16 rows pushed by the peers, then [B, Tmax] fp32 squared norms
+        self.gn_off = _round_up(self.B * self.grow_stride * 2, 256)
+        self.Gwin = self.ctx.alloc("dlrm_G", self.gn_off + self.B * self.Tmax * 4)
+        self.gnorm = self.Gwin.view(torch.float32, (self.B, self.Tmax), byte_offset=self.gn_off)
+        self.ndst_table = torch.tensor([p + self.gn_off for p in self.Gwin.ptrs], dtype=torch.int64, device=dev)
         self.Tbuf = self.Twin.view(torch.bfloat16, (self.Bl, self.F * self.D))
 
         # ---- dense parameters (flat fp32 master / grad / reduced buffers)
@@ -332,7 +336,7 @@ class DLRM:
         # ---- interaction backward: dense part stays, embedding gradients go to their owners
         F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
                                 self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
-                                relu_mask_dx=True)
+                                relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax)
         self._count()
         if self.world > 1:
             self.ctx.signal(CH_BWD); self._count()
@@ -352,7 +356,8 @@ class DLRM:
         if self.Tl:
             F_.emb_backward(self.weight, self.state, self.row_idx, self.occ2bag, self.nnz, self.Gwin.local,
                             grad_col=self.grad_col, grad_row_stride=self.grow_stride, B=self.B, D=self.D,
-                            grad_bf16=True, lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st)
+                            grad_bf16=True, lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st,
+                            gnorm=self.gnorm, gnorm_stride=self.Tmax)
             self._count(2 if c.emb_optimizer == "rowwise_adagrad" else 1)
         # ---- dense gradients: all-reduce + SGD
         if self.world > 1:

@@ -68,12 +68,16 @@ def emb_forward(weight, table_base, table_rows, indices, *, offsets=None, hotnes
 
 def emb_backward(weight, state, row_idx, occ2bag, nnz: int, grad, *, grad_col=None, grad_row_stride: int, B: int,
                  D: int, grad_bf16: bool = True, per_sample_weights=None, lr: float, eps: float = 1e-10,
-                 optimizer: str = "rowwise_adagrad", status=None) -> None:
-    """Segment-reduces duplicate rows and applies SGD / row-wise Adagrad in place."""
+                 optimizer: str = "rowwise_adagrad", status=None, gnorm=None, gnorm_stride: int = 0) -> None:
+    """Segment-reduces duplicate rows and applies SGD / row-wise Adagrad in place.
+
+    ``gnorm`` (optional, fp32 ``[B, gnorm_stride]``): sum of squares of every bag gradient, indexed
+    ``[sample, local table]``, as produced by :func:`interaction_backward`."""
     _need_cuda(weight, row_idx, grad)
     opt = {"sgd": 0, "rowwise_adagrad": 1}[optimizer]
     call("rs_emb_backward", ptr(weight), ptr(state), weight.shape[0], ptr(row_idx), ptr(occ2bag), nnz, ptr(grad),
-         ptr(grad_col), grad_row_stride, B, D, 1 if grad_bf16 else 0, ptr(per_sample_weights), lr, eps, opt,
+         ptr(grad_col), grad_row_stride, ptr(gnorm), gnorm_stride, B, D, 1 if grad_bf16 else 0,
+         ptr(per_sample_weights), lr, eps, opt,
          ptr(status), stream_ptr())
 
 
@@ -94,10 +98,15 @@ def interaction_forward(T, B: int, F: int, D: int, out) -> torch.Tensor:
 
 
 def interaction_backward(T, dout, B: int, F: int, D: int, dx, gdst_table, owner, gcol, grow_stride: int,
-                         sample_base: int, relu_mask_dx: bool = True) -> None:
+                         sample_base: int, relu_mask_dx: bool = True, ndst_table=None, nstride: int = 0) -> None:
+    """Backward of :func:`interaction_forward`.  Row 0 of dT goes to ``dx``; row f>=1 of sample b is stored
+    at ``gdst_table[owner[f-1]] + (sample_base + b) * grow_stride + gcol[f-1]`` (bf16).  With
+    ``ndst_table`` the sum of squares of each stored row also goes to
+    ``ndst_table[owner[f-1]][(sample_base + b) * nstride + gcol[f-1] // D]`` (fp32)."""
     _need_cuda(T, dout, dx)
     call("rs_interaction_backward", ptr(T), ptr(dout), B, F, D, dout.stride(0), ptr(dx), dx.stride(0),
-         ptr(gdst_table), ptr(owner), ptr(gcol), grow_stride, sample_base, 1 if relu_mask_dx else 0, stream_ptr())
+         ptr(gdst_table), ptr(owner), ptr(gcol), grow_stride, sample_base, 1 if relu_mask_dx else 0,
+         ptr(ndst_table), nstride, stream_ptr())
 
 
 def head_bce(x, w, bias, labels, inv_batch: float, *, prob=None, loss_sum=None, dx=None, dw=None, db=None) -> None:

@@ -150,9 +150,11 @@ def test_embedding_forward_backward(dev, D, hot):
         weight.copy_(w0)
         state = torch.zeros(weight.shape[0], device=dev)
         wr, sr = w0.clone(), torch.zeros(weight.shape[0], device=dev)
+        gnorm = grad.view(B, T, D).pow(2).sum(-1).contiguous()
         for step in range(2):
             F_.emb_backward(weight, state, row_idx, occ2bag, nnz, grad, grad_col=grad_col, grad_row_stride=T * D,
-                            B=B, D=D, grad_bf16=False, lr=0.05, eps=1e-8, optimizer=opt, status=st)
+                            B=B, D=D, grad_bf16=False, lr=0.05, eps=1e-8, optimizer=opt, status=st,
+                            gnorm=gnorm if step == 1 else None, gnorm_stride=T)
             for t in range(T):
                 g_t = grad[:, t * D:(t + 1) * D].repeat_interleave(hot[t], 0)
                 idx = ids[t] + base[t]
@@ -211,13 +213,17 @@ def test_interaction(dev, F, D):
     dx = torch.zeros(B, D, device=dev, dtype=torch.bfloat16)
     Gw = torch.zeros(B, (F - 1) * D + 8, device=dev, dtype=torch.bfloat16)
     i32 = dict(dtype=torch.int32, device=dev)
+    nrm = torch.zeros(B, max(F - 1, 1), device=dev)
     F_.interaction_backward(T, dout, B, F, D, dx, torch.tensor([Gw.data_ptr()], dtype=torch.int64, device=dev),
                             torch.zeros(max(F - 1, 1), **i32), torch.tensor([f * D for f in range(max(F - 1, 1))], **i32),
-                            Gw.stride(0), 0, relu_mask_dx=False)
+                            Gw.stride(0), 0, relu_mask_dx=False,
+                            ndst_table=torch.tensor([nrm.data_ptr()], dtype=torch.int64, device=dev), nstride=max(F - 1, 1))
     torch.cuda.synchronize()
     assert _rel_err(dx, gref[:, 0]) < 2e-2
     if F > 1:
-        assert _rel_err(Gw[:, :(F - 1) * D].view(B, F - 1, D), gref[:, 1:]) < 2e-2
+        got = Gw[:, :(F - 1) * D].view(B, F - 1, D)
+        assert _rel_err(got, gref[:, 1:]) < 2e-2
+        assert torch.allclose(nrm, got.float().pow(2).sum(-1), rtol=1e-4, atol=1e-12)
     # with the ReLU mask of feature 0
     F_.interaction_backward(T, dout, B, F, D, dx, torch.tensor([Gw.data_ptr()], dtype=torch.int64, device=dev),
                             torch.zeros(max(F - 1, 1), **i32), torch.tensor([f * D for f in range(max(F - 1, 1))], **i32),
@@ -329,3 +335,21 @@ def test_dlrm_step_matches_torch_oracle(dev, graph):
     for l, l_ref in losses:
         assert abs(l - l_ref) < 3e-2 * max(1.0, abs(l_ref)), losses
     assert losses[-1][0] < losses[0][0]
+
+
+def test_bounded_wait_times_out_without_hanging(dev):
+    """A flag wait that nothing satisfies returns after its time limit with an error status; the CUDA
+    context stays usable (no trap, no hang)."""
+    from recstore_b200 import _lib
+    from recstore_b200.parallel.peer import PeerContext
+    ctx = PeerContext(0, 1, device=dev, wait_timeout_s=0.1)
+    ctx.barrier()
+    torch.cuda.synchronize()
+    ctx.check_status()
+    ctx.wait(3)                 # nothing signals channel 3
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.DeviceStatusError) as e:
+        ctx.check_status()
+    assert "wait_timeout" in str(e.value)
+    assert torch.ones(8, device=dev).sum().item() == 8
+    ctx.check_status()          # status was reset

@@ -1,0 +1,133 @@
+"""Multi-GPU tests (one process per GPU, NCCL bootstrap, NVLink peer windows).  Skipped with < 2 GPUs."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _ngpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _init(rank, world, port):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    import torch.distributed as dist
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    return dist
+
+
+def _dlrm_worker(rank, world, port, graph, out):
+    dist = _init(rank, world, port)
+    try:
+        from recstore_b200.models.dlrm import DLRM, DLRMConfig
+        from recstore_b200.parallel.peer import PeerContext
+        from recstore_b200.utils.data import DLRMBatchSource
+        rows = [1000, 37, 5000, 12, 300, 20000, 64]
+        hot = [1, 2, 1, 3, 1, 1, 1]
+        B = 512
+        cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=0.05, mlp_lr=0.05, seed=5, use_cuda_graph=graph)
+        ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"))
+        eng = DLRM(cfg, ctx)
+        solo = DLRM(cfg) if rank == 0 else None          # same seeds -> identical initial state
+        src = DLRMBatchSource(rows, hot, B, alpha=1.2, seed=9)
+        for step in range(4):
+            b = src.next()
+            l = eng.train_step(eng.make_pinned_batch(b.dense, b.ids, b.labels))
+            lt = torch.tensor([l], device="cuda", dtype=torch.float64)
+            dist.all_reduce(lt)
+            if rank == 0:
+                ls = solo.train_step(solo.make_pinned_batch(b.dense, b.ids, b.labels))
+                assert abs(lt.item() - ls) < 2e-3 * max(1.0, abs(ls)), (step, lt.item(), ls)
+        eng.check()
+        # tables: every rank sends its tables to rank 0 for comparison with the single-GPU run
+        for t in range(len(rows)):
+            if eng.owner[t] == rank and rank != 0:
+                dist.send(eng.table_weight(t).contiguous(), dst=0)
+            if rank == 0:
+                if eng.owner[t] == 0:
+                    w = eng.table_weight(t)
+                else:
+                    w = torch.empty(rows[t], cfg.emb_dim, device="cuda")
+                    dist.recv(w, src=eng.owner[t])
+                ref = solo.table_weight(t)
+                err = ((w - ref).norm() / ref.norm()).item()
+                assert err < 5e-2, (t, err)
+        if rank == 0:
+            sd, sr = eng.dense_state(), solo.dense_state()
+            for k in sd:
+                err = ((sd[k] - sr[k]).norm() / (sr[k].norm() + 1e-12)).item()
+                assert err < 1e-3, (k, err)
+        # inference path agrees between the sharded and the single-GPU engine
+        b = src.next()
+        p = eng.predict(eng.make_pinned_batch(b.dense, b.ids, b.labels))
+        if rank == 0:
+            ps = solo.predict(solo.make_pinned_batch(b.dense, b.ids, b.labels))
+            assert (p - ps[:p.numel()]).abs().max().item() < 5e-2
+        dist.barrier()
+        out[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_dlrm_two_ranks_match_single(graph):
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    world = min(_ngpus(), 4) if _ngpus() in (2, 4) else 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_dlrm_worker, args=(world, _free_port(), graph, out), nprocs=world, join=True)
+    assert all(out.get(r) == "ok" for r in range(world)), dict(out)
+
+
+def _timeout_worker(rank, world, port, out):
+    """A wait whose signal never comes must return an error status, not hang, and leave the context usable."""
+    dist = _init(rank, world, port)
+    try:
+        from recstore_b200.parallel.peer import PeerContext
+        from recstore_b200 import _lib
+        ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"), wait_timeout_s=0.2)
+        ctx.barrier()                       # a normal round works
+        torch.cuda.synchronize()
+        ctx.check_status()
+        if rank == 0:
+            ctx.wait(5)                     # nobody signals channel 5
+            torch.cuda.synchronize()
+            try:
+                ctx.check_status()
+                out[rank] = "no error raised"
+            except _lib.DeviceStatusError as e:
+                assert "wait_timeout" in str(e)
+                x = torch.ones(4, device="cuda") * 2   # context still usable
+                assert x.sum().item() == 8
+                out[rank] = "ok"
+        else:
+            out[rank] = "ok"
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_bounded_wait_reports_timeout():
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_timeout_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert all(out.get(r) == "ok" for r in range(2)), dict(out)
