@@ -425,6 +425,7 @@ class KVEngineChunkHash final : public BaseKV {
     Chunk* chunks = nullptr;
     uint64_t nchunks = 0;
     size_t map_bytes = 0;
+    uint64_t max_probe = 0;   // largest distance from its home chunk at which any key was ever placed
   };
   struct Meta {          // first 4 KiB of every dict file
     uint64_t magic;
@@ -505,6 +506,7 @@ class KVEngineChunkHash final : public BaseKV {
             break;
           }
         if (p != 0 && s.chunks[home].overflow < 255) ++s.chunks[home].overflow;
+        if (p > s.max_probe) s.max_probe = p;
         size_.fetch_add(1, std::memory_order_relaxed);
         return true;
       }
@@ -600,6 +602,7 @@ class KVEngineChunkHash final : public BaseKV {
     std::vector<bool> live(slab_.high_water(), false);
     uint64_t total = 0;
     for (Shard& s : shards_) {
+      s.max_probe = 0;
       for (uint64_t c = 0; c < s.nchunks; ++c) s.chunks[c].overflow = 0;
       for (uint64_t c = 0; c < s.nchunks; ++c) {
         Chunk& ch = s.chunks[c];
@@ -616,6 +619,7 @@ class KVEngineChunkHash final : public BaseKV {
           ++used;
           const uint64_t home = (h >> 8) % s.nchunks;
           if (home != c && s.chunks[home].overflow < 255) ++s.chunks[home].overflow;
+          s.max_probe = std::max<uint64_t>(s.max_probe, (c + s.nchunks - home) % s.nchunks);
         }
         ch.used = static_cast<uint8_t>(used);
         total += used;
@@ -661,7 +665,10 @@ class KVEngineChunkHash final : public BaseKV {
     return true;
   }
   void ClearLocked() {
-    for (Shard& s : shards_) memset(s.chunks, 0, s.nchunks * sizeof(Chunk));
+    for (Shard& s : shards_) {
+      memset(s.chunks, 0, s.nchunks * sizeof(Chunk));
+      s.max_probe = 0;
+    }
     slab_.reset();
     size_.store(0);
   }
@@ -678,14 +685,10 @@ class KVEngineChunkHash final : public BaseKV {
         if (ch.keys[i] == key) { *chunk = ci; *slot = i; return true; }
         m &= m - 1;
       }
-      // Nothing of this home chunk lives further down unless its overflow counter says so.
+      // Nothing of this home chunk lives further down unless its overflow counter says so, and
+      // never further than the longest displacement any insert has used.
       if (p == 0 && ch.overflow == 0) return false;
-      if (p != 0 && ch.used < kSlots && s.chunks[home].overflow != 255) {
-        // a non-full chunk on the path ends the run of chunks that can hold overflowed keys only if
-        // no erase happened in between; erases keep tombstone-free semantics by never compacting, so
-        // keep scanning up to the bound below.
-      }
-      if (p >= 64 && s.chunks[home].overflow != 255) return false;
+      if (p >= s.max_probe) return false;
     }
     return false;
   }

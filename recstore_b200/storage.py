@@ -1,0 +1,145 @@
+"""Host KV engines behind the ``BaseKV`` interface (native, see ``csrc/runtime/kv_engine.h``).
+
+``BaseKV(engine, config)`` with ``config = {"path", "capacity", "value_size", ...}`` mirrors
+``base::Factory<BaseKV, const BaseKVConfig&>::NewInstance`` of the reference
+(src/storage/kv_engine/base_kv.h:14-56, engine_map.h:129).  Values are float32 vectors of
+``value_size // 4`` elements.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+from typing import List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import cstr, i32, i64, u64, vp
+
+_lib.register_signatures({
+    "rs_kv_create": (i32, [cstr, cstr, C.POINTER(vp)]),
+    "rs_kv_destroy": (i32, [vp]),
+    "rs_kv_value_size": (i32, [vp]),
+    "rs_kv_put": (i32, [vp, u64, vp]),
+    "rs_kv_get": (i32, [vp, u64, vp, C.POINTER(i32)]),
+    "rs_kv_erase": (i32, [vp, u64, C.POINTER(i32)]),
+    "rs_kv_batch_get": (i32, [vp, vp, i64, vp, vp]),
+    "rs_kv_batch_put": (i32, [vp, vp, i64, vp, C.POINTER(i64)]),
+    "rs_kv_bulk_load": (i32, [vp, u64]),
+    "rs_kv_clear": (i32, [vp]),
+    "rs_kv_size": (u64, [vp]),
+    "rs_kv_flush": (i32, [vp]),
+    "rs_kv_keys": (i64, [vp, vp, i64]),
+    "rs_kv_debug_info": (i32, [vp, C.c_char_p, i32]),
+    "rs_kv_check_consistency": (i32, [vp, C.POINTER(i32)]),
+    "rs_kv_migrate_hot": (i32, [vp, vp, i64, C.POINTER(i64)]),
+    "rs_kv_recovery_state": (i32, [vp, C.POINTER(i32), C.POINTER(i32)]),
+    "rs_kv_list_engines": (i32, [C.c_char_p, i32]),
+})
+
+
+def list_engines() -> List[str]:
+    l = _lib.lib()
+    n = l.rs_kv_list_engines(None, 0)
+    buf = C.create_string_buffer(n + 1)
+    l.rs_kv_list_engines(buf, n + 1)
+    return [x for x in buf.value.decode().split("\n") if x]
+
+
+class BaseKV:
+    def __init__(self, engine: str = "KVEngineMap", config: Optional[dict] = None):
+        self._l = _lib.lib()
+        cfg = dict(config or {})
+        h = vp()
+        _lib.call("rs_kv_create", engine.encode(), json.dumps(cfg).encode(), C.byref(h))
+        self._h = h.value
+        self.engine = engine
+        self.value_size = self._l.rs_kv_value_size(self._h)
+        self.dim = self.value_size // 4
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._l.rs_kv_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _keys(keys) -> torch.Tensor:
+        return torch.as_tensor(keys, dtype=torch.int64).contiguous()
+
+    def Put(self, key: int, value) -> None:
+        v = torch.as_tensor(value, dtype=torch.float32).contiguous()
+        assert v.numel() == self.dim
+        _lib.call("rs_kv_put", self._h, int(key), v.data_ptr())
+
+    def Get(self, key: int) -> Optional[torch.Tensor]:
+        out = torch.empty(self.dim, dtype=torch.float32)
+        found = i32()
+        _lib.call("rs_kv_get", self._h, int(key), out.data_ptr(), C.byref(found))
+        return out if found.value else None
+
+    def Erase(self, key: int) -> bool:
+        e = i32()
+        _lib.call("rs_kv_erase", self._h, int(key), C.byref(e))
+        return bool(e.value)
+
+    def BatchGet(self, keys) -> Tuple[torch.Tensor, torch.Tensor]:
+        """-> (values [n, dim] with zero rows for absent keys, found [n] bool)."""
+        k = self._keys(keys)
+        out = torch.empty(k.numel(), self.dim, dtype=torch.float32)
+        found = torch.empty(k.numel(), dtype=torch.uint8)
+        _lib.call("rs_kv_batch_get", self._h, k.data_ptr(), k.numel(), out.data_ptr(), found.data_ptr())
+        return out, found.bool()
+
+    def BatchPut(self, keys, values) -> None:
+        k = self._keys(keys)
+        v = torch.as_tensor(values, dtype=torch.float32).contiguous()
+        assert v.shape == (k.numel(), self.dim)
+        stored = i64()
+        _lib.call("rs_kv_batch_put", self._h, k.data_ptr(), k.numel(), v.data_ptr(), C.byref(stored))
+
+    def BulkLoad(self, n: int) -> None:
+        _lib.call("rs_kv_bulk_load", self._h, int(n))
+
+    def clear(self) -> None:
+        _lib.call("rs_kv_clear", self._h)
+
+    def Flush(self) -> None:
+        _lib.call("rs_kv_flush", self._h)
+
+    def __len__(self) -> int:
+        return int(self._l.rs_kv_size(self._h))
+
+    def keys(self) -> torch.Tensor:
+        n = len(self)
+        out = torch.empty(max(n, 1), dtype=torch.int64)
+        m = self._l.rs_kv_keys(self._h, out.data_ptr(), n)
+        return out[:m]
+
+    def DebugInfo(self) -> str:
+        n = self._l.rs_kv_debug_info(self._h, None, 0)
+        buf = C.create_string_buffer(n + 1)
+        self._l.rs_kv_debug_info(self._h, buf, n + 1)
+        return buf.value.decode()
+
+    def check_consistency(self) -> bool:
+        ok = i32()
+        _lib.call("rs_kv_check_consistency", self._h, C.byref(ok))
+        return bool(ok.value)
+
+    def migrate_hot(self, keys) -> int:
+        k = self._keys(keys)
+        moved = i64()
+        _lib.call("rs_kv_migrate_hot", self._h, k.data_ptr(), k.numel(), C.byref(moved))
+        return int(moved.value)
+
+    def recovery_state(self) -> Tuple[bool, bool]:
+        r, c = i32(), i32()
+        _lib.call("rs_kv_recovery_state", self._h, C.byref(r), C.byref(c))
+        return bool(r.value), bool(c.value)

@@ -1,0 +1,151 @@
+"""Named timers / counters (native registry with mean, P50, P99 and an ASCII report) plus CUDA-event
+timing and NVTX ranges.
+
+``Timer`` / ``PerfCounter`` / ``Reporter`` mirror the reference's ``timer_module``
+(src/base/pybind_timer.cc:9-22) and its Python wrappers ``Timer``, ``GPUTimer``, ``PerfCounter``,
+``xmh_nvtx_range`` (src/python/pytorch/recstore/utils.py:107-180).  ``DeviceTimer`` measures a region
+with CUDA events on the launching stream (what the benchmarks report), never by host clock.
+"""
+from __future__ import annotations
+
+import contextlib
+import ctypes as C
+
+import torch
+
+from .. import _lib
+from .._lib import cstr, f64, i32, u64, vp
+
+_lib.register_signatures({
+    "rs_now_ns": (u64, []),
+    "rs_timer_get": (vp, [cstr]),
+    "rs_counter_get": (vp, [cstr]),
+    "rs_series_record": (None, [vp, f64]),
+    "rs_timer_record_ns": (None, [cstr, f64]),
+    "rs_counter_record": (None, [cstr, f64]),
+    "rs_series_stats": (i32, [cstr, C.POINTER(f64)]),
+    "rs_report": (i32, [C.c_char_p, i32]),
+    "rs_report_thread_start": (i32, [i32]),
+    "rs_report_thread_stop": (i32, []),
+    "rs_timers_clear": (None, []),
+})
+
+
+class Timer:
+    """``t = Timer("Forward"); t.Start(); ...; t.End()``; every ``sampling``-th interval is recorded."""
+
+    def __init__(self, name: str, sampling: int = 1):
+        self._l = _lib.lib()
+        self.name = name
+        self._h = self._l.rs_timer_get(name.encode())
+        self._sampling = max(1, int(sampling))
+        self._n = 0
+        self._t0 = 0
+
+    def Start(self):
+        self._t0 = self._l.rs_now_ns()
+
+    def End(self):
+        self._n += 1
+        if self._n % self._sampling == 0:
+            self._l.rs_series_record(self._h, float(self._l.rs_now_ns() - self._t0))
+
+    start, stop = Start, End
+
+    def __enter__(self):
+        self.Start()
+        return self
+
+    def __exit__(self, *a):
+        self.End()
+
+    @staticmethod
+    def ManualRecordNs(name: str, ns: float):
+        _lib.lib().rs_timer_record_ns(name.encode(), float(ns))
+
+
+class GPUTimer(Timer):
+    """Host timer around a device region: synchronises before reading the clock, opens an NVTX range."""
+
+    def Start(self):
+        if torch.cuda.is_available():
+            torch.cuda.nvtx.range_push(self.name)
+            torch.cuda.synchronize()
+        super().Start()
+
+    def End(self):
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+            torch.cuda.nvtx.range_pop()
+        super().End()
+
+    start, stop = Start, End
+
+
+class DeviceTimer:
+    """Device-side time of a region (CUDA events on the current stream), recorded under ``name`` in ns."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self._e0 = torch.cuda.Event(enable_timing=True)
+        self._e1 = torch.cuda.Event(enable_timing=True)
+
+    def __enter__(self):
+        self._e0.record()
+        return self
+
+    def __exit__(self, *a):
+        self._e1.record()
+
+    def elapsed_ms(self) -> float:
+        self._e1.synchronize()
+        ms = self._e0.elapsed_time(self._e1)
+        Timer.ManualRecordNs(self.name, ms * 1e6)
+        return ms
+
+
+class PerfCounter:
+    @staticmethod
+    def Record(name: str, value: float):
+        _lib.lib().rs_counter_record(name.encode(), float(value))
+
+
+class Reporter:
+    @staticmethod
+    def StartReportThread(period_ms: int = 5000):
+        _lib.call("rs_report_thread_start", int(period_ms))
+
+    @staticmethod
+    def StopReportThread():
+        _lib.call("rs_report_thread_stop")
+
+    @staticmethod
+    def Report() -> str:
+        l = _lib.lib()
+        n = l.rs_report(None, 0)
+        buf = C.create_string_buffer(n + 1)
+        l.rs_report(buf, n + 1)
+        return buf.value.decode()
+
+    @staticmethod
+    def Clear():
+        _lib.lib().rs_timers_clear()
+
+
+def stats(name: str) -> dict:
+    """{'mean','p50','p99','last','count'} of a timer (ns) or counter."""
+    out = (f64 * 5)()
+    _lib.call("rs_series_stats", name.encode(), out)
+    return {"mean": out[0], "p50": out[1], "p99": out[2], "last": out[3], "count": int(out[4])}
+
+
+@contextlib.contextmanager
+def nvtx_range(msg: str, enabled: bool = True):
+    if enabled and torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(msg)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield

@@ -1,0 +1,234 @@
+"""Host runtime (no GPU): shared tensors, barrier, timers, Zipf, KV engines, DistTensor / optimizers."""
+import math
+import os
+import multiprocessing as mp
+
+import numpy as np
+import pytest
+import torch
+
+
+@pytest.fixture(autouse=True)
+def _ns():
+    from recstore_b200 import ipc, kvstore
+    ipc.set_namespace(f"pytest{os.getpid()}")
+    ipc.IPCTensorFactory.ClearIPCMemory()
+    kvstore.kvreset()
+    yield
+    ipc.IPCTensorFactory.ClearIPCMemory()
+    ipc.MultiProcessBarrierFactory.ClearIPCMemory()
+    kvstore.kvreset()
+
+
+def _child_mutate(ns, q):
+    from recstore_b200 import ipc
+    ipc.set_namespace(ns)
+    t = ipc.IPCTensorFactory.FindIPCTensorFromName("shared_a")
+    t[1] = 7.0
+    s = ipc.IPCTensorFactory.GetSlicedIPCTensorFromName("ring")
+    s.Copy_(torch.arange(5, dtype=torch.int64))
+    b = ipc.MultiProcessBarrierFactory.Create("b0", 2)
+    b.Wait()
+    q.put(("ok", ipc.IPCTensorFactory.ListIPCTensors()))
+
+
+def test_ipc_tensor_shared_between_processes():
+    from recstore_b200 import ipc
+    ns = f"pytest{os.getpid()}"
+    t = ipc.IPCTensorFactory.NewIPCTensor("shared_a", (4, 3), torch.float32)
+    assert t is not None and t.abs().sum() == 0
+    assert ipc.IPCTensorFactory.NewIPCTensor("shared_a", (4, 3), torch.float32) is None   # name taken
+    ring = ipc.IPCTensorFactory.NewSlicedIPCTensor("ring", (16,), torch.int64)
+    assert len(ring) == 0
+    b = ipc.MultiProcessBarrierFactory.Create("b0", 2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_child_mutate, args=(ns, q))
+    p.start()
+    b.Wait()
+    msg, names = q.get(timeout=60)
+    p.join(60)
+    assert msg == "ok" and set(names) >= {"shared_a", "ring"}
+    assert torch.equal(t[1], torch.full((3,), 7.0))
+    assert torch.equal(ring.GetSlicedTensor(), torch.arange(5))
+    assert ipc.IPCTensorFactory.ClearIPCMemory() >= 2
+
+
+def test_barrier_timeout_is_an_error_not_a_hang():
+    from recstore_b200 import ipc, _lib
+    b = ipc.MultiProcessBarrierFactory.Create("lonely", 2, timeout_ms=100)
+    with pytest.raises(_lib.RecStoreError) as e:
+        b.Wait()                       # the second party never arrives
+    assert e.value.code == _lib.ERR_TIMEOUT
+
+
+def test_timers_and_counters():
+    from recstore_b200.utils import timer as T
+    T.Reporter.Clear()
+    t = T.Timer("unit:sleep")
+    for _ in range(5):
+        with t:
+            pass
+    T.Timer.ManualRecordNs("unit:manual", 2_000_000)
+    T.PerfCounter.Record("unit:hit_ratio", 0.75)
+    s = T.stats("unit:manual")
+    assert s["count"] == 1 and abs(s["mean"] - 2e6) < 1
+    assert T.stats("unit:sleep")["count"] == 5
+    rep = T.Reporter.Report()
+    assert "unit:hit_ratio" in rep and "P99" in rep
+    T.Reporter.StartReportThread(10_000)
+    T.Reporter.StopReportThread()
+
+
+def test_zipf_native_matches_python_and_is_skewed():
+    import ctypes as C
+    from recstore_b200 import _lib
+    from recstore_b200.utils.data import zipf_from_uniform
+    _lib.register_signatures({"rs_zipf_from_uniform": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_double]),
+                              "rs_zipf_fill": (C.c_int, [C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_double, C.c_ulonglong, C.c_int])})
+    rng = np.random.default_rng(0)
+    for alpha in (0.9, 1.0, 1.2, 1.3):
+        u = rng.random(20000)
+        ref = zipf_from_uniform(u, 1_000_000, alpha)
+        out = np.empty(20000, dtype=np.int64)
+        _lib.call("rs_zipf_from_uniform", u.ctypes.data, out.ctypes.data, 20000, 1_000_000, alpha)
+        assert (out == ref).mean() > 0.9999          # libm vs numpy pow may differ in the last ulp
+        assert ref.min() >= 0 and ref.max() < 1_000_000
+    ids = np.empty(100000, dtype=np.int64)
+    _lib.call("rs_zipf_fill", ids.ctypes.data, 100000, 1000, 1.2, 7, 1)
+    assert ids.min() >= 1 and ids.max() <= 1000
+    assert (ids == 1).mean() > 0.1                    # heavy head
+
+
+@pytest.mark.parametrize("engine", ["KVEngineMap", "KVEngineExtendibleHash", "KVEngineChunkHash"])
+def test_kv_engine_put_get_mirror(engine):
+    """Random put / get / erase against a Python dict mirror (the reference's client consistency test,
+    src/grpc_ps/python_client/python_client_test.py:9-44, applied to every engine)."""
+    from recstore_b200.storage import BaseKV, list_engines
+    assert engine in list_engines()
+    kv = BaseKV(engine, {"capacity": 50000, "value_size": 32})
+    rng = np.random.default_rng(1)
+    mirror = {}
+    for rnd in range(30):
+        keys = rng.integers(0, 20000, size=500)
+        vals = torch.from_numpy(rng.standard_normal((500, 8)).astype(np.float32))
+        kv.BatchPut(keys, vals)
+        for k, v in zip(keys.tolist(), vals):
+            mirror[k] = v
+        q = rng.integers(0, 25000, size=400)
+        got, found = kv.BatchGet(q)
+        for i, k in enumerate(q.tolist()):
+            if k in mirror:
+                assert found[i] and torch.equal(got[i], mirror[k])
+            else:
+                assert not found[i] and got[i].abs().sum() == 0
+        for k in rng.integers(0, 20000, size=50).tolist():
+            assert kv.Erase(k) == (k in mirror)
+            mirror.pop(k, None)
+        assert len(kv) == len(mirror)
+    assert set(kv.keys().tolist()) == set(mirror.keys())
+    if engine == "KVEngineExtendibleHash":
+        assert kv.check_consistency()
+    kv.clear()
+    assert len(kv) == 0 and kv.Get(int(next(iter(mirror)))) is None
+    kv.BulkLoad(1000)                                  # key -> [key] * dim
+    got, found = kv.BatchGet(torch.arange(1000))
+    assert found.all() and torch.equal(got[:, 0], torch.arange(1000, dtype=torch.float32))
+    assert "size=1000" in kv.DebugInfo()
+
+
+def test_chunkhash_crash_recovery_and_hot_migration(tmp_path):
+    from recstore_b200.storage import BaseKV
+    cfg = {"capacity": 20000, "value_size": 16, "path": str(tmp_path / "kv"), "num_shards": 4}
+    kv = BaseKV("KVEngineChunkHash", cfg)
+    keys = torch.arange(0, 12000)
+    kv.BatchPut(keys, keys.float().unsqueeze(1).repeat(1, 4))
+    for k in range(0, 12000, 7):
+        kv.Erase(k)
+    n_live = len(kv)
+    moved = kv.migrate_hot(keys[:2000])
+    assert moved >= 0
+    # "crash": drop the handle without Flush -> files stay marked dirty; reopen must rebuild the index
+    kv._l.rs_kv_destroy  # noqa: B018  (destructor flushes; emulate a crash by reopening while still open)
+    kv2 = BaseKV("KVEngineChunkHash", cfg)
+    recovered, clean = kv2.recovery_state()
+    assert recovered and not clean
+    assert len(kv2) == n_live
+    got, found = kv2.BatchGet(keys)
+    exp = torch.ones(12000, dtype=torch.bool)
+    exp[::7] = False
+    assert torch.equal(found, exp)
+    assert torch.equal(got[found][:, 0], keys[found].float())
+    kv2.BatchPut(torch.arange(0, 12000, 7), torch.zeros(len(range(0, 12000, 7)), 4))   # free list was rebuilt
+    assert len(kv2) == 12000
+    kv2.close()
+    kv.close()
+    kv3 = BaseKV("KVEngineChunkHash", cfg)
+    assert kv3.recovery_state() == (True, True) and len(kv3) == 12000
+
+
+def test_dist_tensor_embedding_and_optimizers(tmp_path):
+    import recstore_b200 as rs
+    from recstore_b200.dist_tensor import DistTensor, DistEmbedding
+    from recstore_b200 import dist_opt
+    rs.kvinit()
+    a = DistTensor((10, 3), torch.float32, name="a", persistent=True)
+    a[1] = torch.tensor([1.0, 2.0, 3.0])
+    assert torch.equal(a[torch.tensor([1])], torch.tensor([[1.0, 2.0, 3.0]]))
+    assert len(a) == 10 and a.shape == (10, 3) and a.name == "a"
+
+    def init(t, shape, dtype):
+        t.copy_(torch.arange(shape[0], dtype=dtype).unsqueeze(1).expand(shape))   # row i == i
+    emb = DistEmbedding(50, 4, name="emb", init_func=init)
+    idx = torch.tensor([3, 3, 7, 9, 3])
+    # --- SparseSGD: mean over duplicates
+    opt = dist_opt.SparseSGD([emb], lr=0.5)
+    e = emb(idx)
+    (e * torch.arange(5.0).unsqueeze(1)).sum().backward()
+    opt.step(); opt.zero_grad()
+    w = emb.weight
+    assert torch.allclose(w[3], torch.full((4,), 3 - 0.5 * (0 + 1 + 4) / 3))
+    assert torch.allclose(w[7], torch.full((4,), 7 - 0.5 * 2)) and torch.allclose(w[9], torch.full((4,), 9 - 0.5 * 3))
+    # --- row-wise Adagrad: reference semantics against a hand-written loop
+    emb2 = DistEmbedding(50, 4, name="emb2", init_func=init)
+    opt2 = dist_opt.SparseRowWiseAdaGrad([emb2], lr=0.1, eps=1e-10)
+    w_ref = emb2.weight.clone(); s_ref = torch.zeros(50)
+    for step in range(3):
+        e = emb2(idx)
+        g = torch.randn(5, 4, generator=torch.Generator().manual_seed(step))
+        e.backward(g)
+        opt2.step(); opt2.zero_grad()
+        for i, k in enumerate(idx.tolist()):
+            s_ref[k] += g[i].pow(2).mean()
+        for i, k in enumerate(idx.tolist()):
+            w_ref[k] -= 0.1 * g[i] / (s_ref[k].sqrt() + 1e-10)
+    assert torch.allclose(emb2.weight, w_ref, atol=1e-5)
+    # --- element-wise Adagrad runs (disabled upstream)
+    emb3 = DistEmbedding(20, 4, name="emb3", init_func=init)
+    opt3 = dist_opt.SparseAdagrad([emb3], lr=0.1)
+    e = emb3(torch.tensor([1, 1, 2])); e.sum().backward(); opt3.step(); opt3.zero_grad()
+    assert torch.allclose(emb3.weight[1], torch.full((4,), 1 - 0.1 * 1 / (1 + 1e-10)))
+    # --- checkpoint round trip in the per-rank file format
+    f = str(tmp_path / "opt.ckpt")
+    opt2.save(f)
+    assert os.path.exists(f + "_0")
+    sd = torch.load(f + "_0", weights_only=False)
+    assert set(sd) == {"params", "emb_states"} and sd["params"]["world_size"] == 1 and "_lr" in sd["params"]
+    name = "emb2_SparseRowWiseAdaGrad_sum"
+    assert torch.equal(sd["emb_states"]["emb2"]["states"][name], s_ref[sd["emb_states"]["emb2"]["ids"]].to(torch.float32)) or \
+        torch.allclose(sd["emb_states"]["emb2"]["states"][name], s_ref[sd["emb_states"]["emb2"]["ids"]], atol=1e-6)
+    opt2._state["emb2"].get_shm_tensor().zero_()
+    opt2.load(f)
+    assert torch.allclose(opt2._state["emb2"].get_shm_tensor(), s_ref, atol=1e-6)
+    # scale-in: a 2-rank checkpoint loaded by 1 rank picks up both files
+    sd0 = opt2.local_state_dict(); sd1 = opt2.local_state_dict()
+    ids = torch.arange(50)
+    sd0["params"]["world_size"] = 2; sd1["params"]["world_size"] = 2
+    sd0["emb_states"]["emb2"] = {"ids": ids[0::2], "states": {name: torch.full((25,), 5.0)}}
+    sd1["emb_states"]["emb2"] = {"ids": ids[1::2], "states": {name: torch.full((25,), 9.0)}}
+    torch.save(sd0, f + "2_0"); torch.save(sd1, f + "2_1")
+    opt2.load(f + "2")
+    st = opt2._state["emb2"].get_shm_tensor()
+    assert torch.equal(st[0::2], torch.full((25,), 5.0)) and torch.equal(st[1::2], torch.full((25,), 9.0))
+    with pytest.warns(UserWarning):
+        opt2.load(str(tmp_path / "missing"))
