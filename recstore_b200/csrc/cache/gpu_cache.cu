@@ -1,0 +1,310 @@
+// Set-associative LRU embedding cache in HBM with the Query / Replace / Update / Dump contract of the
+// cache the reference vendors from HugeCTR (src/storage/gpu_cache/nv_gpu_cache.cu:392-531 get_kernel,
+// 700-852 insert_replace_kernel, 970-1074 update_kernel, 1155-1226 dump_kernel; API
+// gpu_cache_api.hpp:27-50; torch wrapper src/framework/pytorch/recstore_gpu_cache.h:31-106).
+//
+// Layout: `nsets` sets of 32 slots; a warp probes a set with one 256-byte coalesced load (one key per
+// lane) and a ballot.  Differences from the reference kernel shape (1 key per warp, 2 keys per
+// 64-thread block, a per-set mutex even on reads):
+//   * each warp walks a strided list of keys and keeps the next key's set line in flight while it
+//     copies the current row, so many keys are in flight per SM;
+//   * the hit path takes no lock: it only reads keys / values and stamps the slot's counter with a
+//     relaxed store (a stale stamp only makes LRU slightly approximate);
+//   * Replace / Update take a per-set lock with a BOUNDED spin; on give-up the key is skipped and
+//     RS_DEV_WAIT_TIMEOUT is recorded.
+// Semantics kept: Query writes hit rows in place, leaves miss rows untouched, appends (position,
+// key) of every miss in arbitrary order with a device-side count, bumps the global clock; Replace
+// inserts into an empty slot or evicts the smallest stamp and refreshes the stamp when the key is
+// already cached; Update overwrites values of cached keys only; Dump enumerates the keys of a set range.
+#include "common/rs_common.h"
+#include "kv/hash_table.cuh"
+
+namespace {
+using rs::ht_hash;
+
+constexpr unsigned long long kEmptyKey = 0xFFFFFFFFFFFFFFFFull;
+constexpr int kWays = 32;
+
+struct CacheView {
+  unsigned long long* keys;   // [nsets * 32]
+  unsigned* stamps;           // [nsets * 32]
+  float* values;              // [nsets * 32, dim]
+  int* locks;                 // [nsets]
+  unsigned* clock;            // global LRU clock
+  unsigned long long nsets;
+  int dim;
+};
+
+__device__ __forceinline__ void copy_row(float* __restrict__ dst, const float* __restrict__ src, int dim, int lane) {
+  for (int v = lane; v < (dim >> 2); v += 32) reinterpret_cast<float4*>(dst)[v] = reinterpret_cast<const float4*>(src)[v];
+}
+
+__global__ void cache_init_kernel(CacheView c) {
+  const unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < c.nsets * kWays) {
+    c.keys[i] = kEmptyKey;
+    c.stamps[i] = 0;
+  }
+  if (i < c.nsets) c.locks[i] = 0;
+  if (i == 0) *c.clock = 0;
+}
+
+__global__ void cache_tick_kernel(unsigned* clock, int* miss_count) {
+  atomicAdd(clock, 1u);
+  if (miss_count) *miss_count = 0;
+}
+
+__global__ void __launch_bounds__(256) cache_query_kernel(CacheView c, const long long* __restrict__ keys, long long n,
+                                                          float* __restrict__ out, long long* __restrict__ miss_index,
+                                                          long long* __restrict__ miss_keys, int* __restrict__ miss_count) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const unsigned now = *c.clock;
+  long long i = warp;
+  if (i >= n) return;
+  unsigned long long key = static_cast<unsigned long long>(keys[i]);
+  unsigned long long set = ht_hash(key) % c.nsets;
+  unsigned long long line = c.keys[set * kWays + lane];
+  while (i < n) {
+    const long long ni = i + nwarps;
+    unsigned long long nkey = 0, nset = 0, nline = 0;
+    if (ni < n) {  // next key's set line in flight while this row is copied
+      nkey = static_cast<unsigned long long>(keys[ni]);
+      nset = ht_hash(nkey) % c.nsets;
+      nline = c.keys[nset * kWays + lane];
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, line == key && key != kEmptyKey);
+    if (hit) {
+      const int way = __ffs(hit) - 1;
+      const unsigned long long slot = set * kWays + way;
+      if (lane == 0) c.stamps[slot] = now;
+      copy_row(out + i * c.dim, c.values + slot * c.dim, c.dim, lane);
+    } else if (lane == 0) {
+      const int pos = atomicAdd(miss_count, 1);
+      miss_index[pos] = i;
+      miss_keys[pos] = static_cast<long long>(key);
+    }
+    i = ni; key = nkey; set = nset; line = nline;
+  }
+}
+
+__device__ __forceinline__ bool lock_set(int* lock, int lane) {
+  int ok = 0;
+  if (lane == 0) {
+    for (int spin = 0; spin < (1 << 20); ++spin) {
+      if (atomicCAS(lock, 0, 1) == 0) { ok = 1; break; }
+      __nanosleep(32);
+    }
+    __threadfence();
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+__device__ __forceinline__ void unlock_set(int* lock, int lane) {
+  __syncwarp();
+  if (lane == 0) {
+    __threadfence();
+    atomicExch(lock, 0);
+  }
+}
+
+// mode 0: Replace (insert or evict LRU, refresh stamp when present); mode 1: Update (present keys only).
+__global__ void __launch_bounds__(256) cache_write_kernel(CacheView c, const long long* __restrict__ keys, long long n,
+                                                          const float* __restrict__ values, int mode,
+                                                          unsigned long long* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const unsigned now = *c.clock;
+  for (long long i = warp; i < n; i += nwarps) {
+    const unsigned long long key = static_cast<unsigned long long>(keys[i]);
+    if (key == kEmptyKey) continue;
+    const unsigned long long set = ht_hash(key) % c.nsets;
+    if (!lock_set(&c.locks[set], lane)) {
+      if (lane == 0 && status) atomicOr(status, (unsigned long long)RS_DEV_WAIT_TIMEOUT);
+      continue;
+    }
+    const unsigned long long line = *reinterpret_cast<volatile unsigned long long*>(&c.keys[set * kWays + lane]);
+    const unsigned hit = __ballot_sync(0xffffffffu, line == key);
+    int way = -1;
+    bool write_value = false;
+    if (hit) {
+      way = __ffs(hit) - 1;
+      write_value = (mode == 1);          // Replace of a cached key only refreshes its stamp
+    } else if (mode == 0) {
+      const unsigned empty = __ballot_sync(0xffffffffu, line == kEmptyKey);
+      if (empty) {
+        way = __ffs(empty) - 1;
+      } else {                             // evict the least recently stamped slot
+        unsigned st = *reinterpret_cast<volatile unsigned*>(&c.stamps[set * kWays + lane]);
+        unsigned long long best = (static_cast<unsigned long long>(st) << 5) | lane;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+          best = other < best ? other : best;
+        }
+        way = static_cast<int>(best & 31);
+      }
+      write_value = true;
+    }
+    if (way >= 0) {
+      const unsigned long long slot = set * kWays + way;
+      if (write_value) copy_row(c.values + slot * c.dim, values + i * c.dim, c.dim, lane);
+      if (lane == 0) {
+        if (!hit) c.keys[slot] = key;
+        if (mode == 0) c.stamps[slot] = now;
+      }
+    }
+    unlock_set(&c.locks[set], lane);
+  }
+}
+
+__global__ void cache_dump_kernel(CacheView c, unsigned long long set_begin, unsigned long long set_end,
+                                  long long* __restrict__ keys_out, unsigned long long* count) {
+  const unsigned long long i = set_begin * kWays + static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= set_end * kWays) return;
+  const unsigned long long k = c.keys[i];
+  if (k == kEmptyKey) return;
+  keys_out[atomicAdd(count, 1ull)] = static_cast<long long>(k);
+}
+
+struct CacheOwned {
+  CacheView v;
+};
+}  // namespace
+
+// num_items is rounded up to a multiple of 32; dim must be a multiple of 4.
+RS_API int rs_cache_create(unsigned long long num_items, int dim, void** handle) {
+  RS_REQUIRE(handle && num_items > 0 && dim > 0 && dim % 4 == 0, "rs_cache_create: bad argument (dim %% 4 == 0)");
+  CacheOwned* h = new CacheOwned();
+  CacheView& v = h->v;
+  v.nsets = (num_items + kWays - 1) / kWays;
+  v.dim = dim;
+  const unsigned long long slots = v.nsets * kWays;
+  RS_CUDA(cudaMalloc(&v.keys, slots * sizeof(unsigned long long)));
+  RS_CUDA(cudaMalloc(&v.stamps, slots * sizeof(unsigned)));
+  RS_CUDA(cudaMalloc(&v.values, slots * static_cast<size_t>(dim) * sizeof(float)));
+  RS_CUDA(cudaMalloc(&v.locks, v.nsets * sizeof(int)));
+  RS_CUDA(cudaMalloc(&v.clock, sizeof(unsigned)));
+  cache_init_kernel<<<static_cast<unsigned>((slots + 255) / 256), 256>>>(v);
+  RS_LAUNCH_CHECK();
+  RS_CUDA(cudaDeviceSynchronize());
+  *handle = h;
+  return RS_OK;
+}
+RS_API int rs_cache_destroy(void* handle) {
+  if (!handle) return RS_OK;
+  CacheOwned* h = static_cast<CacheOwned*>(handle);
+  cudaFree(h->v.keys); cudaFree(h->v.stamps); cudaFree(h->v.values); cudaFree(h->v.locks); cudaFree(h->v.clock);
+  delete h;
+  return RS_OK;
+}
+RS_API unsigned long long rs_cache_capacity(void* handle) { return static_cast<CacheOwned*>(handle)->v.nsets * kWays; }
+RS_API unsigned long long rs_cache_num_sets(void* handle) { return static_cast<CacheOwned*>(handle)->v.nsets; }
+
+// out: [n, dim] (hit rows written, miss rows untouched); miss_index / miss_keys: [n]; miss_count: device int.
+RS_API int rs_cache_query(void* handle, const long long* keys, long long n, float* out, long long* miss_index,
+                          long long* miss_keys, int* miss_count, cudaStream_t stream) {
+  RS_REQUIRE(handle && keys && out && miss_index && miss_keys && miss_count, "rs_cache_query: null argument");
+  CacheView& v = static_cast<CacheOwned*>(handle)->v;
+  cache_tick_kernel<<<1, 1, 0, stream>>>(v.clock, miss_count);
+  RS_LAUNCH_CHECK();
+  if (n == 0) return RS_OK;
+  long long warps = (n + 3) / 4;  // >= 4 keys per warp when there are enough keys
+  if (warps > 148 * 32) warps = 148 * 32;
+  cache_query_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(v, keys, n, out, miss_index, miss_keys, miss_count);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+RS_API int rs_cache_replace(void* handle, const long long* keys, long long n, const float* values,
+                            unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(handle && keys && values, "rs_cache_replace: null argument");
+  if (n == 0) return RS_OK;
+  CacheView& v = static_cast<CacheOwned*>(handle)->v;
+  long long warps = n < 148 * 32 ? n : 148 * 32;
+  cache_write_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(v, keys, n, values, 0, status);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+RS_API int rs_cache_update(void* handle, const long long* keys, long long n, const float* values,
+                           unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(handle && keys && values, "rs_cache_update: null argument");
+  if (n == 0) return RS_OK;
+  CacheView& v = static_cast<CacheOwned*>(handle)->v;
+  long long warps = n < 148 * 32 ? n : 148 * 32;
+  cache_write_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(v, keys, n, values, 1, status);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+// keys_out must hold (set_end - set_begin) * 32 entries; count: device counter, zeroed here.
+RS_API int rs_cache_dump(void* handle, unsigned long long set_begin, unsigned long long set_end, long long* keys_out,
+                         unsigned long long* count, cudaStream_t stream) {
+  RS_REQUIRE(handle && keys_out && count, "rs_cache_dump: null argument");
+  CacheView& v = static_cast<CacheOwned*>(handle)->v;
+  RS_REQUIRE(set_begin <= set_end && set_end <= v.nsets, "rs_cache_dump: set range [%llu, %llu) outside [0, %llu)",
+             set_begin, set_end, v.nsets);
+  RS_CUDA(cudaMemsetAsync(count, 0, sizeof(unsigned long long), stream));
+  const unsigned long long slots = (set_end - set_begin) * kWays;
+  if (slots == 0) return RS_OK;
+  cache_dump_kernel<<<static_cast<unsigned>((slots + 255) / 256), 256, 0, stream>>>(v, set_begin, set_end, keys_out, count);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+// out[missing_index[i]] = retrieved[i]  (the reference's merge_op, src/framework/pytorch/merge.cu:6-18)
+namespace {
+__global__ void merge_rows_kernel(float* __restrict__ out, const float* __restrict__ retrieved,
+                                  const long long* __restrict__ missing_index, long long n, int dim) {
+  const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= n) return;
+  const int lane = threadIdx.x & 31;
+  const long long d = missing_index[i];
+  if ((dim & 3) == 0) {
+    for (int v = lane; v < (dim >> 2); v += 32)
+      reinterpret_cast<float4*>(out + d * dim)[v] = reinterpret_cast<const float4*>(retrieved + i * dim)[v];
+  } else {
+    for (int v = lane; v < dim; v += 32) out[d * dim + v] = retrieved[i * dim + v];
+  }
+}
+// dst[i] = key in [start, end) ? hbm[key - start] : host_table[key]   (uva_cache_query_op,
+// src/framework/pytorch/recstore_pytorch.cu:12-37); host_table is device-accessible host memory.
+__global__ void range_cache_query_kernel(float* __restrict__ dst, const long long* __restrict__ ids, long long n, int dim,
+                                         const float* __restrict__ hbm, const float* __restrict__ host_table, long long start,
+                                         long long end, long long host_rows, unsigned long long* status) {
+  const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= n) return;
+  const int lane = threadIdx.x & 31;
+  const long long k = ids[i];
+  const float* src;
+  if (k >= start && k < end) src = hbm + (k - start) * dim;
+  else if (k >= 0 && k < host_rows) src = host_table + k * dim;
+  else {
+    if (lane == 0 && status) atomicOr(status, (unsigned long long)RS_DEV_OOB_ROW);
+    return;
+  }
+  if ((dim & 3) == 0) {
+    for (int v = lane; v < (dim >> 2); v += 32) reinterpret_cast<float4*>(dst + i * dim)[v] = reinterpret_cast<const float4*>(src)[v];
+  } else {
+    for (int v = lane; v < dim; v += 32) dst[i * dim + v] = src[v];
+  }
+}
+}  // namespace
+
+RS_API int rs_merge_rows(float* out, const float* retrieved, const long long* missing_index, long long n, int dim,
+                         cudaStream_t stream) {
+  RS_REQUIRE(out && retrieved && missing_index, "rs_merge_rows: null argument");
+  if (n == 0) return RS_OK;
+  merge_rows_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(out, retrieved, missing_index, n, dim);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+RS_API int rs_range_cache_query(float* dst, const long long* ids, long long n, int dim, const float* hbm,
+                                const float* host_table, long long start, long long end, long long host_rows,
+                                unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(dst && ids && hbm && host_table, "rs_range_cache_query: null argument");
+  if (n == 0) return RS_OK;
+  range_cache_query_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(dst, ids, n, dim, hbm, host_table, start,
+                                                                                   end, host_rows, status);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}

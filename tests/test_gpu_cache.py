@@ -1,0 +1,118 @@
+"""GPU hash table, set-associative cache, unique, merge / range-cache ops against CPU mirrors."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from recstore_b200 import _lib
+    _lib.lib()
+    return torch.device("cuda:0")
+
+
+def test_hash_table_insert_lookup_erase_dump(dev):
+    from recstore_b200.cache import GpuHashTable
+    g = torch.Generator().manual_seed(0)
+    ht = GpuHashTable(capacity=1 << 16, max_rows=30000, device=dev)
+    keys = torch.randint(0, 1 << 40, (20000,), generator=g)
+    keys = torch.cat([keys, keys[:5000]])                      # duplicates inside one launch
+    rows = ht.insert(keys).cpu()
+    uniq = torch.unique(keys)
+    assert (rows >= 0).all() and rows.max() < 30000
+    m = {}
+    for k, r in zip(keys.tolist(), rows.tolist()):
+        assert m.setdefault(k, r) == r                          # same key -> same row
+    assert len(set(m.values())) == len(m) == uniq.numel()       # distinct keys -> distinct rows
+    live, size, bad = ht.check()
+    assert live == size == uniq.numel() and bad == 0
+    q = torch.cat([keys[:100], torch.arange(1 << 41, (1 << 41) + 50)])
+    got = ht.lookup(q).cpu()
+    assert torch.equal(got[:100], rows[:100]) and (got[100:] == -1).all()
+    gone = uniq[::3]
+    ht.erase(gone)
+    assert (ht.lookup(gone).cpu() == -1).all()
+    live, size, bad = ht.check()
+    assert live == size == uniq.numel() - gone.numel() and bad == 0
+    r2 = ht.insert(gone[:100]).cpu()                            # freed rows are reused
+    assert (r2 >= 0).all() and r2.max() < 30000
+    dk, dr = ht.dump()
+    assert set(dk.cpu().tolist()) == (set(uniq.tolist()) - set(gone.tolist())) | set(gone[:100].tolist())
+    assert ht.status.item() == 0
+    # row store exhaustion is reported, not fatal
+    small = GpuHashTable(capacity=1024, max_rows=10, device=dev)
+    r = small.insert(torch.arange(100)).cpu()
+    assert (r >= 0).sum().item() == 10 and small.status.item() != 0
+    ht.clear()
+    assert ht.check()[0] == 0
+
+
+def test_unique_keys(dev):
+    from recstore_b200.cache import unique_keys
+    g = torch.Generator().manual_seed(1)
+    keys = torch.randint(0, 5000, (100000,), generator=g).to(dev)
+    st = torch.zeros(1, dtype=torch.int64, device=dev)
+    u, inv = unique_keys(keys, st)
+    assert st.item() == 0
+    assert torch.equal(torch.sort(u).values, torch.unique(keys))
+    assert torch.equal(u[inv], keys)
+
+
+def test_gpu_cache_query_replace_update_dump(dev):
+    from recstore_b200.cache import GpuCache, merge_op
+    D = 32
+    cache = GpuCache(4096, D, device=dev)
+    table = torch.arange(100000, dtype=torch.float32, device=dev).unsqueeze(1).repeat(1, D)   # row i == i
+    g = torch.Generator().manual_seed(2)
+    mirror = set()
+    for it in range(20):
+        keys = torch.randint(0, 3000, (2000,), generator=g).to(dev)
+        vals = torch.full((2000, D), -1.0, device=dev)
+        res = cache.Query(keys, vals)
+        hit = torch.ones(2000, dtype=torch.bool, device=dev)
+        hit[res.missing_index] = False
+        assert torch.equal(vals[hit][:, 0], keys[hit].float())                 # hits carry the right rows
+        assert (vals[~hit] == -1).all()                                         # misses untouched
+        assert torch.equal(torch.sort(res.missing_keys).values, torch.sort(keys[~hit]).values)
+        for k in keys[hit].unique().tolist():
+            assert k in mirror
+        fetched = table[res.missing_keys]
+        merge_op(vals, fetched, res.missing_index)
+        assert torch.equal(vals[:, 0], keys.float())
+        cache.Replace(res.missing_keys, fetched)
+        mirror |= set(res.missing_keys.tolist())
+    dumped = set(cache.Dump().tolist())
+    assert dumped <= mirror and len(dumped) >= min(len(mirror), 2000)
+    # everything fits (3000 keys < 4096 slots, ~23 per 32-way set on average): the hit rate is high now
+    keys = torch.arange(3000, device=dev)
+    res = cache.Query(keys)
+    assert res.missing_keys.numel() < 300
+    # Update overwrites cached rows only
+    cache.Update(torch.tensor([1, 2, 999999], device=dev), torch.full((3, D), 5.0, device=dev))
+    res = cache.Query(torch.tensor([1, 2, 999999], device=dev))
+    assert 999999 in res.missing_keys.tolist()
+    hitmask = torch.ones(3, dtype=torch.bool); hitmask[res.missing_index.cpu()] = False
+    assert (res.values.cpu()[hitmask] == 5.0).all()
+    assert cache.status.item() == 0
+    # LRU: a set that overflows evicts the least recently used key
+    c2 = GpuCache(32, 4, device=dev)                                           # one set
+    c2.Replace(torch.arange(32, device=dev), torch.zeros(32, 4, device=dev))
+    c2.Query(torch.arange(1, 32, device=dev))                                  # touch all but key 0
+    c2.Replace(torch.tensor([100], device=dev), torch.ones(1, 4, device=dev))
+    assert 0 not in c2.Dump().tolist() and 100 in c2.Dump().tolist()
+
+
+def test_range_cache_query(dev):
+    from recstore_b200.cache import uva_cache_query_op
+    D = 12                                                   # not a multiple of 4: scalar path
+    host = torch.arange(1000, dtype=torch.float32).unsqueeze(1).repeat(1, D).pin_memory()
+    start, end = 100, 300
+    hbm = (host[start:end] + 0.5).to(dev)                    # cached copy is distinguishable
+    ids = torch.tensor([0, 100, 299, 300, 999, 150], device=dev)
+    out = torch.zeros(6, D, device=dev)
+    st = torch.zeros(1, dtype=torch.int64, device=dev)
+    uva_cache_query_op(out, ids, hbm, host, start, end, st)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:, 0].cpu(), torch.tensor([0, 100.5, 299.5, 300, 999, 150.5]))
+    assert st.item() == 0
