@@ -105,7 +105,10 @@ __global__ void unique_kernel(const long long* keys, long long n, unsigned long 
     }
     if (cur == k) {
       int u = __ldcv(&slots_idx[s]);
-      for (int spin = 0; u < 0 && spin < (1 << 16); ++spin) u = __ldcv(&slots_idx[s]);
+      for (int spin = 0; u < 0 && spin < (1 << 18); ++spin) {
+        __nanosleep(spin < 64 ? 20 : 200);
+        u = __ldcv(&slots_idx[s]);
+      }
       if (u < 0 && status) atomicOr(status, (unsigned long long)RS_DEV_WAIT_TIMEOUT);
       if (inverse) inverse[i] = u;
       return;

@@ -40,15 +40,24 @@ __host__ __device__ __forceinline__ unsigned long long ht_hash(unsigned long lon
   return k;
 }
 
+// Waits (bounded, with back-off so that a publisher in the same warp can make progress) until the
+// row of a claimed slot has been published.
+__device__ __forceinline__ int ht_wait_row(const int* p) {
+  int r = __ldcv(p);
+  for (int spin = 0; r == kHtRowPending && spin < (1 << 18); ++spin) {
+    __nanosleep(spin < 64 ? 20 : 200);
+    r = __ldcv(p);
+  }
+  return r == kHtRowPending ? -1 : r;
+}
+
 // Returns the row of `key`, or -1 when absent.
 __device__ __forceinline__ int ht_find(const HashTableView& t, unsigned long long key) {
   unsigned long long s = ht_hash(key) & t.mask;
   for (int p = 0; p < kHtMaxProbe; ++p) {
     const unsigned long long k = __ldcv(&t.keys[s]);
     if (k == key) {
-      int r = __ldcv(&t.rows[s]);
-      for (int spin = 0; r == kHtRowPending && spin < 4096; ++spin) r = __ldcv(&t.rows[s]);
-      return r == kHtRowPending ? -1 : r;
+      return ht_wait_row(&t.rows[s]);
     }
     if (k == kHtEmpty) return -1;
     s = (s + 1) & t.mask;
@@ -96,9 +105,7 @@ __device__ __forceinline__ int ht_insert(const HashTableView& t, unsigned long l
       k = prev;  // somebody claimed it first: fall through and compare
     }
     if (k == key) {
-      int r = __ldcv(&t.rows[s]);
-      for (int spin = 0; r == kHtRowPending && spin < 4096; ++spin) r = __ldcv(&t.rows[s]);
-      return r == kHtRowPending ? -1 : r;
+      return ht_wait_row(&t.rows[s]);
     }
     s = (s + 1) & t.mask;
   }

@@ -39,6 +39,7 @@ constexpr int BK = 64;
 constexpr int kThreads = 192;
 constexpr uint32_t kABytes = BM * BK * 2;  // 16 KiB per stage
 constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kStageBytes = 4 * 2 * 4096;  // per epilogue warp: output tile + aux tile, 32 rows x 128 B each
 
 struct GemmArgs {
   int M, N, K;          // logical problem (see modes above); K = reduction length
@@ -71,7 +72,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const uint32_t b_bytes = static_cast<uint32_t>(g.bn) * BK * 2;
   uint8_t* sA = smem;
   uint8_t* sB = smem + static_cast<size_t>(stages) * kABytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(sB + static_cast<size_t>(stages) * b_bytes);
+  uint8_t* sStage = sB + static_cast<size_t>(stages) * b_bytes;   // 4 epilogue warps x 2 x 4 KiB
+  uint64_t* full = reinterpret_cast<uint64_t*>(sStage + kStageBytes);
   uint64_t* empty = full + stages;
   uint64_t* tfull = empty + stages;
   uint64_t* tempty = tfull + 2;
@@ -202,6 +204,85 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < g.M;
+      if (g.epi <= 2 && (g.bn & 63) == 0) {
+        // bf16 output staged through shared memory: every thread owns one row of the accumulator, but
+        // global memory is touched row-contiguously (4 rows x 128 B per warp instruction) for both the
+        // output store and the ReLU-mask load.  16-byte chunks are XOR-swizzled by (row & 7).
+        uint8_t* so = sStage + (warp - 2) * 8192;
+        uint8_t* sa = so + 4096;
+        const int lrow = lane >> 3, lchunk = lane & 7;
+        for (int c = 0; c < g.bn / 64; ++c) {
+          const int col0 = n0 + c * 64;
+          if (col0 >= g.N) break;
+          if (g.epi == 2) {
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = it * 4 + lrow;
+              const int grow = m0 + q * 32 + r;
+              uint4 m = make_uint4(0, 0, 0, 0);
+              if (grow < g.M && col0 + lchunk * 8 < g.N)
+                m = __ldg(reinterpret_cast<const uint4*>(g.aux + static_cast<size_t>(grow) * g.ldaux + col0) + lchunk);
+              *reinterpret_cast<uint4*>(sa + r * 128 + ((lchunk ^ (r & 7)) << 4)) = m;
+            }
+            __syncwarp();
+          }
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * g.bn + c * 64 + half * 32), r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            const int cb = col0 + half * 32;
+            if (g.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                if (cb + j < g.N) {
+                  const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + cb + j));
+                  v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+                }
+              }
+            }
+            if (g.epi == 1) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const int chunk = half * 4 + (j >> 3);
+              if (g.epi == 2) {
+                const uint4 m = *reinterpret_cast<const uint4*>(sa + lane * 128 + ((chunk ^ (lane & 7)) << 4));
+                const __nv_bfloat16* mb = reinterpret_cast<const __nv_bfloat16*>(&m);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) v[j + t] = (__bfloat162float(mb[t]) > 0.f) ? v[j + t] : 0.f;
+              }
+              uint4 o;
+              o.x = pack_bf16(v[j], v[j + 1]);
+              o.y = pack_bf16(v[j + 2], v[j + 3]);
+              o.z = pack_bf16(v[j + 4], v[j + 5]);
+              o.w = pack_bf16(v[j + 6], v[j + 7]);
+              *reinterpret_cast<uint4*>(so + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = o;
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + lrow;
+            const int grow = m0 + q * 32 + r;
+            if (grow < g.M && col0 + lchunk * 8 < g.N) {
+              const uint4 o = *reinterpret_cast<const uint4*>(so + r * 128 + ((lchunk ^ (r & 7)) << 4));
+              *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.D) + static_cast<size_t>(grow) * g.ldd + col0) + lchunk) = o;
+            }
+          }
+          __syncwarp();
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&tempty[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+        continue;
+      }
       for (int c = 0; c < g.bn / 32; ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= g.N) break;  // uniform across the warp
@@ -421,7 +502,7 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   }
   g.splits = splits;
   const uint32_t stage_bytes = kABytes + static_cast<uint32_t>(bn) * BK * 2;
-  int stages = static_cast<int>((200u * 1024u) / stage_bytes);
+  int stages = static_cast<int>((227u * 1024u - kStageBytes - 2048u) / stage_bytes);
   if (stages > 8) stages = 8;
   if (stages < 2) stages = 2;
   g.stages = stages;
@@ -440,7 +521,7 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
     if ((rc = make_map_bf16(&ma, A, K, M, lda, BK, 64)) != RS_OK) return rc;
     if ((rc = make_map_bf16(&mb, B, K, N, ldb, BK, 64)) != RS_OK) return rc;
   }
-  const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024 + 256;
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + kStageBytes + 1024 + 256;
   static bool attr_set[2] = {false, false};
   if (!attr_set[mode]) {
     if (mode == 0) RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
