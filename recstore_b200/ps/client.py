@@ -1,0 +1,338 @@
+"""Parameter-server front end.
+
+* ``ParameterServer``: one shard ("CachePS": KV engine + Put/Get/Update/LoadFakeData/Clear +
+  checkpoints) that can be used in-process or served on a loopback port.
+* ``ParameterClient(host, port, shard)``: the client API of the reference
+  (src/grpc_ps/grpc_ps_client.h:33-77): ``GetParameter``, ``PutParameter``, ``ClearPS``,
+  ``LoadFakeData``, ``LoadCkpt`` (+ ``SaveCkpt`` and ``UpdateParameter``, the gradient verb).  Requests
+  are cut into sub-requests of ``MAX_PARAMETER_BATCH`` keys that are pipelined on the connection.
+  A missing key yields a zero row, not an error.
+* ``PythonParameterClient(host, port, shard, emb_dim)``: the torch-facing variant
+  (src/grpc_ps/grpc_ps_client_pytorch.cpp:5-73) returning ``Tensor[n, dim]``.
+* Asynchronous form of ``BaseParameterClient`` (src/rdma_ps/base_client.h:6-47):
+  ``GetParameterAsync -> rpc_id``, ``QueryRPCFinished``, ``WaitRPCFinish``, ``RevokeRPCResource``,
+  ``GetReceiveBuffer``.
+* ``AllShardsParameterClient``: partitions keys with ``ShardManager.KeyPartition`` (hash(key) %
+  servers, src/ps_common/shard_manager.h:5-9) and fans out (src/rdma_ps/allshards_ps_client.h:46-95).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+from concurrent.futures import Future, ThreadPoolExecutor
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import _lib
+from .._lib import cstr, i32, i64, u64, vp
+
+_lib.register_signatures({
+    "rs_wire_packed_size": (i64, [i64, i32]),
+    "rs_wire_pack": (i32, [vp, i64, i32, vp, vp, vp, i64, C.POINTER(i64)]),
+    "rs_wire_count": (i32, [vp, i64]),
+    "rs_wire_unpack": (i32, [vp, i64, i32, vp, vp, vp]),
+    "rs_ps_create": (i32, [cstr, cstr, C.POINTER(vp)]),
+    "rs_ps_destroy": (i32, [vp]),
+    "rs_ps_dim": (i32, [vp]),
+    "rs_ps_size": (u64, [vp]),
+    "rs_ps_put": (i32, [vp, vp, i64, vp]),
+    "rs_ps_get": (i32, [vp, vp, i64, vp, vp]),
+    "rs_ps_update": (i32, [vp, vp, i64, vp, C.POINTER(i64)]),
+    "rs_ps_load_fake": (i32, [vp, u64]),
+    "rs_ps_clear": (i32, [vp]),
+    "rs_ps_save": (i32, [vp, cstr]),
+    "rs_ps_load": (i32, [vp, cstr]),
+    "rs_ps_server_start": (i32, [vp, i32, C.POINTER(vp), C.POINTER(i32)]),
+    "rs_ps_server_stop": (i32, [vp]),
+    "rs_ps_client_connect": (i32, [cstr, i32, C.POINTER(vp)]),
+    "rs_ps_client_close": (i32, [vp]),
+    "rs_ps_client_get": (i32, [vp, vp, i64, i32, vp, vp, i32]),
+    "rs_ps_client_put": (i32, [vp, vp, i64, i32, vp, i32]),
+    "rs_ps_client_update": (i32, [vp, vp, i64, i32, vp, i32, C.POINTER(u64)]),
+    "rs_ps_client_command": (i32, [vp, i32, vp, i64, C.POINTER(u64)]),
+})
+
+MAX_PARAMETER_BATCH = 2000
+OP_CLEAR, OP_FAKE, OP_SAVE, OP_LOAD, OP_STATS = 4, 5, 6, 7, 8
+
+
+def _keys(keys) -> torch.Tensor:
+    return torch.as_tensor(keys, dtype=torch.int64).contiguous()
+
+
+def pack_records(keys, values: torch.Tensor, dims: Optional[Sequence[int]] = None) -> bytes:
+    """[int32 n][int32 end_offset[n]]{u64 key; int32 dim; float emb[dim]} x n"""
+    _lib.lib()
+    k = _keys(keys)
+    v = torch.as_tensor(values, dtype=torch.float32).contiguous()
+    n, dim = v.shape
+    cap = _lib.lib().rs_wire_packed_size(n, dim)
+    buf = C.create_string_buffer(cap)
+    d = torch.as_tensor(dims, dtype=torch.int32).contiguous() if dims is not None else None
+    w = i64()
+    _lib.call("rs_wire_pack", k.data_ptr(), n, dim, v.data_ptr(), d.data_ptr() if d is not None else None, buf, cap, C.byref(w))
+    return buf.raw[: w.value]
+
+
+def unpack_records(buf: bytes, dim: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """-> (keys [n], dims [n], values [n, dim]; records of another dim give zero rows)."""
+    _lib.lib()
+    n = _lib.lib().rs_wire_count(buf, len(buf))
+    if n < 0:
+        raise _lib.RecStoreError(_lib.ERR_INVALID, "malformed record buffer")
+    k = torch.empty(n, dtype=torch.int64)
+    d = torch.empty(n, dtype=torch.int32)
+    v = torch.empty(n, dim, dtype=torch.float32)
+    _lib.call("rs_wire_unpack", buf, len(buf), dim, k.data_ptr(), d.data_ptr(), v.data_ptr())
+    return k, d, v
+
+
+class ShardManager:
+    @staticmethod
+    def KeyPartition(keys, num_shards: int) -> torch.Tensor:
+        """Owner shard of every key: a 64-bit mix of the key modulo the shard count."""
+        k = _keys(keys).numpy().astype(np.uint64)
+        with np.errstate(over="ignore"):
+            k ^= k >> np.uint64(33); k *= np.uint64(0xff51afd7ed558ccd)
+            k ^= k >> np.uint64(33); k *= np.uint64(0xc4ceb9fe1a85ec53)
+            k ^= k >> np.uint64(33)
+        return torch.from_numpy((k % np.uint64(num_shards)).astype(np.int64))
+
+
+class ParameterServer:
+    """One PS shard.  ``config``: ``dim`` (floats per key), ``capacity``, ``engine``-specific keys, and the
+    server-side optimizer: ``optimizer`` ("rowwise_adagrad" | "sgd"), ``lr``, ``eps``."""
+
+    def __init__(self, engine: str = "KVEngineMap", config: Optional[dict] = None):
+        self._l = _lib.lib()
+        cfg = {"dim": 32, "capacity": 1 << 20}
+        cfg.update(config or {})
+        h = vp()
+        _lib.call("rs_ps_create", engine.encode(), json.dumps(cfg).encode(), C.byref(h))
+        self._h = h.value
+        self.dim = self._l.rs_ps_dim(self._h)
+        self._server = None
+        self.port = None
+
+    # in-process verbs -------------------------------------------------
+    def PutParameter(self, keys, values) -> None:
+        k = _keys(keys); v = torch.as_tensor(values, dtype=torch.float32).contiguous()
+        assert v.shape == (k.numel(), self.dim)
+        _lib.call("rs_ps_put", self._h, k.data_ptr(), k.numel(), v.data_ptr())
+
+    def GetParameter(self, keys) -> torch.Tensor:
+        k = _keys(keys)
+        out = torch.empty(k.numel(), self.dim)
+        _lib.call("rs_ps_get", self._h, k.data_ptr(), k.numel(), out.data_ptr(), None)
+        return out
+
+    def UpdateParameter(self, keys, grads) -> int:
+        k = _keys(keys); g = torch.as_tensor(grads, dtype=torch.float32).contiguous()
+        a = i64()
+        _lib.call("rs_ps_update", self._h, k.data_ptr(), k.numel(), g.data_ptr(), C.byref(a))
+        return int(a.value)
+
+    def LoadFakeData(self, n: int) -> None:
+        _lib.call("rs_ps_load_fake", self._h, int(n))
+
+    def ClearPS(self) -> None:
+        _lib.call("rs_ps_clear", self._h)
+
+    def SaveCkpt(self, path: str) -> None:
+        _lib.call("rs_ps_save", self._h, path.encode())
+
+    def LoadCkpt(self, path: str) -> None:
+        _lib.call("rs_ps_load", self._h, path.encode())
+
+    def __len__(self):
+        return int(self._l.rs_ps_size(self._h))
+
+    # serving ----------------------------------------------------------
+    def serve(self, port: int = 0) -> int:
+        """Starts the loopback server; returns the bound port (``port=0`` picks a free one)."""
+        s, p = vp(), i32()
+        _lib.call("rs_ps_server_start", self._h, int(port), C.byref(s), C.byref(p))
+        self._server, self.port = s.value, p.value
+        return self.port
+
+    def stop(self) -> None:
+        if self._server:
+            self._l.rs_ps_server_stop(self._server)
+            self._server = None
+
+    def close(self) -> None:
+        self.stop()
+        if self._h:
+            self._l.rs_ps_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ParameterClient:
+    def __init__(self, host: str, port: int, shard: int = 0, emb_dim: int = 32):
+        self._l = _lib.lib()
+        h = vp()
+        _lib.call("rs_ps_client_connect", host.encode(), int(port), C.byref(h))
+        self._h = h.value
+        self._shard = shard
+        self.dim = emb_dim
+        self._pool: Optional[ThreadPoolExecutor] = None
+        self._rpcs: Dict[int, Tuple[Future, torch.Tensor]] = {}
+        self._next_rpc = 0
+
+    def shard(self) -> int:
+        return self._shard
+
+    def GetParameter(self, keys, perf: bool = True) -> torch.Tensor:
+        k = _keys(keys)
+        out = torch.empty(k.numel(), self.dim)
+        _lib.call("rs_ps_client_get", self._h, k.data_ptr(), k.numel(), self.dim, out.data_ptr(), None, MAX_PARAMETER_BATCH)
+        return out
+
+    def GetParameterWithMask(self, keys) -> Tuple[torch.Tensor, torch.Tensor]:
+        k = _keys(keys)
+        out = torch.empty(k.numel(), self.dim)
+        found = torch.empty(k.numel(), dtype=torch.uint8)
+        _lib.call("rs_ps_client_get", self._h, k.data_ptr(), k.numel(), self.dim, out.data_ptr(), found.data_ptr(), MAX_PARAMETER_BATCH)
+        return out, found.bool()
+
+    def PutParameter(self, keys, values) -> bool:
+        k = _keys(keys); v = torch.as_tensor(values, dtype=torch.float32).contiguous()
+        assert v.shape == (k.numel(), self.dim)
+        _lib.call("rs_ps_client_put", self._h, k.data_ptr(), k.numel(), self.dim, v.data_ptr(), MAX_PARAMETER_BATCH)
+        return True
+
+    def UpdateParameter(self, keys, grads) -> int:
+        k = _keys(keys); g = torch.as_tensor(grads, dtype=torch.float32).contiguous()
+        a = u64()
+        _lib.call("rs_ps_client_update", self._h, k.data_ptr(), k.numel(), self.dim, g.data_ptr(), MAX_PARAMETER_BATCH, C.byref(a))
+        return int(a.value)
+
+    def _cmd(self, op: int, payload: bytes = b"") -> Tuple[int, int, int]:
+        r = (u64 * 3)()
+        _lib.call("rs_ps_client_command", self._h, op, payload, len(payload), r)
+        return int(r[0]), int(r[1]), int(r[2])
+
+    def ClearPS(self) -> bool:
+        self._cmd(OP_CLEAR)
+        return True
+
+    def LoadFakeData(self, n: int) -> bool:
+        self._cmd(OP_FAKE, int(n).to_bytes(8, "little"))
+        return True
+
+    def LoadCkpt(self, model_config_path=None, emb_file_path=None) -> bool:
+        """Loads a checkpoint written by ``SaveCkpt``; ``emb_file_path`` may be a path or a list of paths."""
+        paths = emb_file_path if isinstance(emb_file_path, (list, tuple)) else [emb_file_path or model_config_path]
+        for p in paths:
+            rc = self._cmd(OP_LOAD, str(p).encode())[0]
+            if rc != 0:
+                raise _lib.RecStoreError(_lib.ERR_IO, f"server could not load {p}")
+        return True
+
+    def SaveCkpt(self, path: str) -> bool:
+        if self._cmd(OP_SAVE, str(path).encode())[0] != 0:
+            raise _lib.RecStoreError(_lib.ERR_IO, f"server could not write {path}")
+        return True
+
+    def Stats(self) -> dict:
+        s = self._cmd(OP_STATS)
+        return {"keys_stored": s[0], "requests": s[1], "keys_served": s[2]}
+
+    # asynchronous form ------------------------------------------------------------------
+    def InitThread(self, n: int = 1) -> None:
+        self._pool = ThreadPoolExecutor(max_workers=max(1, n))
+
+    def GetParameterAsync(self, keys) -> int:
+        if self._pool is None:
+            self.InitThread()
+        k = _keys(keys)
+        out = torch.empty(k.numel(), self.dim)
+        fut = self._pool.submit(lambda: _lib.call("rs_ps_client_get", self._h, k.data_ptr(), k.numel(), self.dim,
+                                                  out.data_ptr(), None, MAX_PARAMETER_BATCH))
+        rid = self._next_rpc
+        self._next_rpc += 1
+        self._rpcs[rid] = (fut, out)
+        return rid
+
+    def QueryRPCFinished(self, rpc_id: int) -> bool:
+        return self._rpcs[rpc_id][0].done()
+
+    def WaitRPCFinish(self, rpc_id: int) -> None:
+        self._rpcs[rpc_id][0].result()
+
+    def GetReceiveBuffer(self, rpc_id: int) -> torch.Tensor:
+        return self._rpcs[rpc_id][1]
+
+    def RevokeRPCResource(self, rpc_id: int) -> None:
+        self._rpcs.pop(rpc_id, None)
+
+    def close(self) -> None:
+        if self._pool is not None:
+            self._pool.shutdown(wait=True)
+            self._pool = None
+        if self._h:
+            self._l.rs_ps_client_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class PythonParameterClient(ParameterClient):
+    """``PythonParameterClient(host, port, shard, emb_dim)``: argument order of the torch custom class."""
+
+    def __init__(self, host: str, port: int, shard: int, emb_dim: int):
+        super().__init__(host, port, shard, emb_dim)
+
+
+class AllShardsParameterClient:
+    """Fans a request out to every shard's client and reassembles the rows in request order."""
+
+    def __init__(self, clients: List[ParameterClient]):
+        self.clients = clients
+        self.dim = clients[0].dim
+        self._pool = ThreadPoolExecutor(max_workers=len(clients))
+
+    def _split(self, keys):
+        k = _keys(keys)
+        owner = ShardManager.KeyPartition(k, len(self.clients))
+        return k, [torch.nonzero(owner == s).flatten() for s in range(len(self.clients))]
+
+    def GetParameter(self, keys) -> torch.Tensor:
+        k, parts = self._split(keys)
+        out = torch.empty(k.numel(), self.dim)
+        futs = [self._pool.submit(c.GetParameter, k[p]) if p.numel() else None for c, p in zip(self.clients, parts)]
+        for f, p in zip(futs, parts):
+            if f is not None:
+                out[p] = f.result()
+        return out
+
+    def PutParameter(self, keys, values) -> bool:
+        k, parts = self._split(keys)
+        v = torch.as_tensor(values, dtype=torch.float32)
+        futs = [self._pool.submit(c.PutParameter, k[p], v[p]) for c, p in zip(self.clients, parts) if p.numel()]
+        for f in futs:
+            f.result()
+        return True
+
+    def UpdateParameter(self, keys, grads) -> int:
+        k, parts = self._split(keys)
+        g = torch.as_tensor(grads, dtype=torch.float32)
+        futs = [self._pool.submit(c.UpdateParameter, k[p], g[p]) for c, p in zip(self.clients, parts) if p.numel()]
+        return sum(f.result() for f in futs)
+
+    def ClearPS(self) -> bool:
+        for c in self.clients:
+            c.ClearPS()
+        return True

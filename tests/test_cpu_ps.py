@@ -1,0 +1,112 @@
+"""Parameter server on the CPU: record format, put/get/update semantics, loopback clients, sharding."""
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+
+def test_record_format_layout_and_roundtrip():
+    from recstore_b200.ps import pack_records, unpack_records
+    keys = torch.tensor([7, 1 << 40, 3])
+    vals = torch.arange(12, dtype=torch.float32).view(3, 4)
+    buf = pack_records(keys, vals, dims=[4, 0, 4])            # middle record "missing"
+    n, = struct.unpack_from("<i", buf, 0)
+    ends = struct.unpack_from("<3i", buf, 4)
+    assert n == 3 and ends == (16 + 12 + 16, 16 + 28 + 12, 16 + 28 + 12 + 28) and len(buf) == ends[-1]
+    k0, d0 = struct.unpack_from("<Qi", buf, 16)
+    assert (k0, d0) == (7, 4) and struct.unpack_from("<4f", buf, 28) == (0.0, 1.0, 2.0, 3.0)
+    k, d, v = unpack_records(buf, 4)
+    assert k.tolist() == keys.tolist() and d.tolist() == [4, 0, 4]
+    assert torch.equal(v[0], vals[0]) and v[1].abs().sum() == 0 and torch.equal(v[2], vals[2])
+    with pytest.raises(Exception):
+        unpack_records(buf[:20], 4)
+
+
+@pytest.mark.parametrize("engine", ["KVEngineMap", "KVEngineChunkHash"])
+def test_ps_client_server_mirror(engine, tmp_path):
+    """clear -> get(empty) -> put -> get(equal) -> update -> checkpoint -> clear -> get(empty) -> load, plus the
+    10-round random put/get mirror of the reference's python client test."""
+    from recstore_b200.ps import ParameterServer, ParameterClient
+    dim = 8
+    srv = ParameterServer(engine, {"dim": dim, "capacity": 100000, "optimizer": "rowwise_adagrad", "lr": 0.1, "eps": 1e-10})
+    port = srv.serve(0)
+    cli = ParameterClient("127.0.0.1", port, 0, dim)
+    cli.ClearPS()
+    keys = torch.arange(5000)
+    out, found = cli.GetParameterWithMask(keys)
+    assert not found.any() and out.abs().sum() == 0                     # missing key -> zero row, no error
+    rng = np.random.default_rng(0)
+    mirror = torch.zeros(20000, dim)
+    present = torch.zeros(20000, dtype=torch.bool)
+    for _ in range(10):
+        k = torch.from_numpy(rng.choice(20000, size=4500, replace=False))   # > 2 sub-requests of 2000 keys
+        v = torch.from_numpy(rng.standard_normal((4500, dim)).astype(np.float32))
+        cli.PutParameter(k, v)
+        mirror[k] = v; present[k] = True
+        q = torch.from_numpy(rng.integers(0, 20000, size=5000))
+        got = cli.GetParameter(q)
+        assert torch.equal(got, mirror[q] * present[q].unsqueeze(1))
+    # gradient verb with duplicates: row-wise Adagrad, post-step state for every occurrence
+    k = torch.tensor([5, 5, 9])
+    cli.PutParameter(torch.tensor([5, 9]), torch.ones(2, dim))
+    g = torch.tensor([[1.0] * dim, [3.0] * dim, [2.0] * dim])
+    assert cli.UpdateParameter(k, g) == 3
+    s5, s9 = 1.0 + 9.0, 4.0
+    exp5 = 1 - 0.1 * (1 + 3) / (s5 ** 0.5 + 1e-10)
+    exp9 = 1 - 0.1 * 2 / (s9 ** 0.5 + 1e-10)
+    got = cli.GetParameter(torch.tensor([5, 9]))
+    assert torch.allclose(got[0], torch.full((dim,), exp5), atol=1e-6) and torch.allclose(got[1], torch.full((dim,), exp9), atol=1e-6)
+    mirror[5] = got[0]; mirror[9] = got[1]; present[5] = True; present[9] = True
+    # async window
+    rid = cli.GetParameterAsync(torch.arange(3000))
+    cli.WaitRPCFinish(rid)
+    assert cli.QueryRPCFinished(rid)
+    assert torch.equal(cli.GetReceiveBuffer(rid), (mirror * present.unsqueeze(1))[:3000])
+    cli.RevokeRPCResource(rid)
+    # checkpoint round trip through the server
+    ck = str(tmp_path / "ps.ckpt")
+    cli.SaveCkpt(ck)
+    n_before = cli.Stats()["keys_stored"]
+    cli.ClearPS()
+    assert cli.Stats()["keys_stored"] == 0 and cli.GetParameter(torch.tensor([5])).abs().sum() == 0
+    cli.LoadCkpt(None, [ck])
+    assert cli.Stats()["keys_stored"] == n_before
+    assert torch.equal(cli.GetParameter(torch.arange(20000)), mirror * present.unsqueeze(1))
+    # the optimizer state came back too: one more update continues from s5
+    cli.UpdateParameter(torch.tensor([5]), torch.full((1, dim), 2.0))
+    assert torch.allclose(cli.GetParameter(torch.tensor([5]))[0], torch.full((dim,), exp5 - 0.1 * 2 / ((s5 + 4) ** 0.5)), atol=1e-6)
+    with pytest.raises(Exception):
+        cli.LoadCkpt(None, [str(tmp_path / "missing.ckpt")])
+    cli.LoadFakeData(100)
+    assert torch.equal(cli.GetParameter(torch.tensor([42]))[0], torch.full((dim,), 42.0))
+    cli.close(); srv.close()
+
+
+def test_all_shards_client():
+    from recstore_b200.ps import ParameterServer, ParameterClient, AllShardsParameterClient, ShardManager
+    dim = 4
+    servers = [ParameterServer("KVEngineExtendibleHash", {"dim": dim, "capacity": 50000, "optimizer": "sgd", "lr": 1.0}) for _ in range(2)]
+    clients = [ParameterClient("127.0.0.1", s.serve(0), i, dim) for i, s in enumerate(servers)]
+    allc = AllShardsParameterClient(clients)
+    keys = torch.arange(10000)
+    vals = keys.float().unsqueeze(1).repeat(1, dim)
+    allc.PutParameter(keys, vals)
+    owner = ShardManager.KeyPartition(keys, 2)
+    assert len(servers[0]) == int((owner == 0).sum()) and len(servers[1]) == int((owner == 1).sum())
+    assert abs(len(servers[0]) - 5000) < 400                           # the hash spreads keys
+    perm = torch.randperm(10000)
+    assert torch.equal(allc.GetParameter(perm), vals[perm])
+    assert allc.UpdateParameter(torch.tensor([1, 2, 3]), torch.ones(3, dim)) == 3
+    assert torch.equal(allc.GetParameter(torch.tensor([1, 2, 3])), vals[1:4] - 1)
+    for c in clients:
+        c.close()
+    for s in servers:
+        s.close()
+
+
+def test_client_connect_failure_is_an_error():
+    from recstore_b200.ps import ParameterClient
+    from recstore_b200 import _lib
+    with pytest.raises(_lib.RecStoreError):
+        ParameterClient("127.0.0.1", 1, 0, 4)
