@@ -1,0 +1,461 @@
+// Lookahead cache controller: deferred ("lazy") application of sparse updates to the big host table,
+// ordered by the next step in which each id will be read.
+//
+// Contract kept from the reference's KGCacheController (src/framework/pytorch/kg_controller.h:36-116,
+// grad_base.h:146-507, grad_async_v1.h:181-593, grad_async_v2.h:11-322): a key read at step s
+// observes every update produced by steps < s (BlockToStepN), while updates of ids that nobody
+// will read soon may lag behind in a priority queue.  The samplers publish the ids of the next L
+// batches (lookahead); an id with pending writes has priority = its earliest future read step,
+// +infinity when no read is registered.
+//
+// What is different: no polling "detect" thread and no shared-memory mailboxes inside the
+// controller -- the sampler calls PublishReads directly and the trainer passes (keys, grads) of the
+// step; the queue is a bucket array over steps (O(1) insert / move, like ParallelPq,
+// parallel_pq.h:164-446) sharded by id so that ranks upsert in parallel; background flusher threads
+// drain the lowest bucket first and BlockToStepN helps draining instead of spinning.  Rows cached in
+// HBM are updated by the owning GPU's kernel; here "cache" rows are the caller-registered per-rank
+// cache tensors (used on the CPU path and by the tests).
+//
+// Also here: the binary-heap priority queue with an index map and an invariant checker
+// (src/base/pq.h:11-224) used as the oracle in tests.
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <climits>
+#include <condition_variable>
+#include <cstring>
+#include <mutex>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include "common/rs_common.h"
+#include "runtime/base.h"
+#include "runtime/json_lite.h"
+
+namespace rs {
+
+// ============================================================== heap PQ with index map
+class IndexedHeap {
+ public:
+  // push or change the priority of `id`
+  void upsert(int64_t id, int64_t prio) {
+    auto it = pos_.find(id);
+    if (it == pos_.end()) {
+      heap_.push_back({prio, id});
+      pos_[id] = heap_.size() - 1;
+      up(heap_.size() - 1);
+    } else {
+      const size_t i = it->second;
+      const int64_t old = heap_[i].prio;
+      heap_[i].prio = prio;
+      if (prio < old) up(i); else down(i);
+    }
+  }
+  bool erase(int64_t id) {
+    auto it = pos_.find(id);
+    if (it == pos_.end()) return false;
+    const size_t i = it->second;
+    swap_nodes(i, heap_.size() - 1);
+    pos_.erase(heap_.back().id);
+    heap_.pop_back();
+    if (i < heap_.size()) { up(i); down(i); }
+    return true;
+  }
+  bool top(int64_t* id, int64_t* prio) const {
+    if (heap_.empty()) return false;
+    *id = heap_[0].id; *prio = heap_[0].prio;
+    return true;
+  }
+  bool pop(int64_t* id, int64_t* prio) {
+    if (!top(id, prio)) return false;
+    erase(*id);
+    return true;
+  }
+  size_t size() const { return heap_.size(); }
+  bool check() const {
+    if (pos_.size() != heap_.size()) return false;
+    for (size_t i = 0; i < heap_.size(); ++i) {
+      if (i && heap_[(i - 1) / 2].prio > heap_[i].prio) return false;
+      auto it = pos_.find(heap_[i].id);
+      if (it == pos_.end() || it->second != i) return false;
+    }
+    return true;
+  }
+
+ private:
+  struct Node { int64_t prio, id; };
+  void swap_nodes(size_t a, size_t b) {
+    if (a == b) return;
+    std::swap(heap_[a], heap_[b]);
+    pos_[heap_[a].id] = a;
+    pos_[heap_[b].id] = b;
+  }
+  void up(size_t i) {
+    while (i && heap_[(i - 1) / 2].prio > heap_[i].prio) { swap_nodes(i, (i - 1) / 2); i = (i - 1) / 2; }
+  }
+  void down(size_t i) {
+    for (;;) {
+      size_t l = 2 * i + 1, r = l + 1, m = i;
+      if (l < heap_.size() && heap_[l].prio < heap_[m].prio) m = l;
+      if (r < heap_.size() && heap_[r].prio < heap_[m].prio) m = r;
+      if (m == i) return;
+      swap_nodes(i, m);
+      i = m;
+    }
+  }
+  std::vector<Node> heap_;
+  std::unordered_map<int64_t, size_t> pos_;
+};
+
+// ============================================================== controller
+constexpr int64_t kInf = INT64_MAX;
+constexpr int kHorizon = 1024;  // steps of lookahead the bucket array can hold (reference: kMaxPriority = 1000)
+
+struct Elem {
+  std::vector<int64_t> reads;    // future read steps, ascending, may hold duplicates (several ranks)
+  std::vector<float> pending;    // accumulated -clr * sum of grads not yet applied (empty = none)
+  int64_t prio = kInf;           // bucket it currently sits in (kInf = infinity bucket / not queued)
+  bool queued = false;
+};
+
+class Controller {
+ public:
+  explicit Controller(const std::string& json) {
+    JsonLite j(json);
+    ranks_ = static_cast<int>(j.i64("num_gpus", 1));
+    L_ = std::min<int>(static_cast<int>(j.i64("L", 10)), kHorizon - 2);
+    clr_ = static_cast<float>(j.num("clr", 0.01));
+    dim_ = static_cast<int>(j.i64("dim", j.i64("emb_dim", 32)));
+    capacity_ = j.i64("full_emb_capacity", 0);
+    const double ratio = j.num("cache_ratio", 0.0);
+    cache_size_ = static_cast<int64_t>(capacity_ * ratio);
+    const std::string mode = j.str("backwardMode", "CppAsyncV2");
+    async_ = mode != "CppSync" && mode != "PySync";
+    nthreads_ = static_cast<int>(j.i64("nr_background_threads", 2));
+    nshards_ = std::max(1, static_cast<int>(j.i64("kUpdatePqWorkerNum", 16)));
+    shards_ = std::vector<Shard>(nshards_);
+    for (auto& s : shards_) s.buckets.resize(kHorizon);
+    caches_.assign(ranks_, nullptr);
+    inputs_.assign(ranks_, Input{});
+  }
+  ~Controller() { StopThreads(); }
+
+  void RegisterTable(float* table, int64_t rows) {
+    table_ = table;
+    rows_ = rows;
+    if (capacity_ == 0) capacity_ = rows;
+    row_locks_.resize(static_cast<size_t>(rows));
+  }
+  void RegisterCache(int rank, float* cache) { caches_[rank] = cache; }
+  void Start() {
+    if (!async_ || running_) return;
+    running_ = true;
+    for (int t = 0; t < nthreads_; ++t) flushers_.emplace_back([this] { FlushLoop(); });
+  }
+  void StopThreads() {
+    if (!running_.exchange(false)) return;
+    for (auto& t : flushers_) t.join();
+    flushers_.clear();
+  }
+  // Flush everything that is still pending (end of training / before a checkpoint).
+  void Drain() {
+    for (int s = 0; s < nshards_; ++s)
+      while (FlushOne(s, kInf, true)) {}
+  }
+
+  // The sampler tells that `rank` will read `ids` at `step` (step > current step).
+  void PublishReads(int rank, int64_t step, const int64_t* ids, int64_t n) {
+    (void)rank;
+    if (!async_) return;
+    for (int64_t i = 0; i < n; ++i) {
+      const int64_t id = ids[i];
+      if (InCache(id)) continue;
+      Shard& sh = shard_of(id);
+      std::lock_guard<SpinLock> lk(sh.mu);
+      Elem& e = sh.elems[id];
+      e.reads.insert(std::upper_bound(e.reads.begin(), e.reads.end(), step), step);
+      Requeue(sh, id, e);
+    }
+    max_published_.store(std::max<int64_t>(max_published_.load(), step));
+  }
+  void SetStepInput(int rank, const int64_t* keys, int64_t n, const float* grads) { inputs_[rank] = Input{keys, n, grads}; }
+
+  // Consumes the registered (keys, grads) of every rank for `step`: cached rows are updated in the
+  // owning rank's cache, the rest goes to the host table now (sync) or to the queue (async).
+  void ProcessOneStep(int64_t step) {
+    auto body = [&](size_t rb, size_t re, int) {
+      for (size_t r = rb; r < re; ++r) {
+        const Input& in = inputs_[r];
+        for (int64_t i = 0; i < in.n; ++i) {
+          const int64_t id = in.keys[i];
+          if (id < 0 || id >= rows_) continue;
+          const float* g = in.grads + i * dim_;
+          const int owner = CacheOwner(id);
+          if (owner >= 0) {
+            // Cached rows are authoritative in the owner's cache.  A registered (host-visible) cache is
+            // updated here; an HBM cache is updated by the owning GPU's kernel, nothing to do on the host.
+            if (caches_[owner]) {
+              float* row = caches_[owner] + (id - owner * cache_size_) * dim_;
+              BitRow br = row_lock(id);
+            std::lock_guard<BitRow> lk(br);
+              for (int d = 0; d < dim_; ++d) row[d] -= clr_ * g[d];
+            }
+            continue;
+          }
+          if (!async_) {
+            BitRow br = row_lock(id);
+            std::lock_guard<BitRow> lk(br);
+            float* row = table_ + id * dim_;
+            for (int d = 0; d < dim_; ++d) row[d] -= clr_ * g[d];
+            continue;
+          }
+          Shard& sh = shard_of(id);
+          std::lock_guard<SpinLock> lk(sh.mu);
+          Elem& e = sh.elems[id];
+          // this step's read of the id is over
+          auto it = std::lower_bound(e.reads.begin(), e.reads.end(), step);
+          if (it != e.reads.end() && *it == step) e.reads.erase(it);
+          if (e.pending.empty()) e.pending.assign(dim_, 0.f);
+          for (int d = 0; d < dim_; ++d) e.pending[d] -= clr_ * g[d];
+          Requeue(sh, id, e);
+        }
+      }
+    };
+    if (ranks_ > 1) ThreadPool::global().parallel_for(ranks_, body);
+    else body(0, ranks_, 0);
+    // reads registered for this step by ranks that produced no gradient for the id are dropped lazily in Requeue
+    cur_step_.store(step);
+  }
+
+  // Returns once no id that is read at a step <= `step` has an unapplied update (helps flushing).
+  // false = timed out.
+  bool BlockToStepN(int64_t step, int timeout_ms) {
+    if (!async_) return true;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+      bool busy = false;
+      for (int s = 0; s < nshards_; ++s) {
+        while (FlushOne(s, step, false)) busy = true;
+      }
+      if (!busy && MinPriority() > step && inflight_.load() == 0) return true;
+      if (timeout_ms >= 0 &&
+          std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > timeout_ms)
+        return false;
+    }
+  }
+  int64_t MinPriority() {
+    int64_t m = kInf;
+    for (auto& sh : shards_) {
+      std::lock_guard<SpinLock> lk(sh.mu);
+      for (int64_t p = sh.min_hint; p < sh.min_hint + kHorizon; ++p) {
+        if (!sh.buckets[p % kHorizon].empty()) { m = std::min(m, p); break; }
+        if (p >= sh.max_prio) break;
+      }
+    }
+    return m;
+  }
+  int64_t PendingCount() {
+    int64_t n = 0;
+    for (auto& sh : shards_) {
+      std::lock_guard<SpinLock> lk(sh.mu);
+      for (auto& kv : sh.elems) n += kv.second.pending.empty() ? 0 : 1;
+    }
+    return n;
+  }
+  std::string PrintPq() {
+    std::string s = "pq: min=" + (MinPriority() == kInf ? std::string("inf") : std::to_string(MinPriority())) +
+                    " pending=" + std::to_string(PendingCount()) + " flushed=" + std::to_string(flushed_.load());
+    return s;
+  }
+  int dim() const { return dim_; }
+  bool async() const { return async_; }
+
+ private:
+  struct Input { const int64_t* keys = nullptr; int64_t n = 0; const float* grads = nullptr; };
+  struct Shard {
+    SpinLock mu;
+    std::unordered_map<int64_t, Elem> elems;
+    std::vector<std::vector<int64_t>> buckets;  // ids per step bucket (lazy deletion: entry valid iff elem.prio matches)
+    std::vector<int64_t> inf_bucket;
+    int64_t min_hint = 0, max_prio = 0;
+  };
+  struct BitRow {
+    BitLockTable* t; size_t i;
+    void lock() { t->lock(i); }
+    void unlock() { t->unlock(i); }
+  };
+  BitRow row_lock(int64_t id) { return BitRow{&row_locks_, static_cast<size_t>(id)}; }
+  Shard& shard_of(int64_t id) { return shards_[hash64(static_cast<uint64_t>(id)) % nshards_]; }
+  bool InCache(int64_t id) const { return cache_size_ > 0 && id < cache_size_ * ranks_; }
+  int CacheOwner(int64_t id) const { return InCache(id) ? static_cast<int>(id / cache_size_) : -1; }
+
+  // sh.mu held.  Recomputes the priority of `id` and moves it to the right bucket.
+  void Requeue(Shard& sh, int64_t id, Elem& e) {
+    const int64_t cur = cur_step_.load();
+    while (!e.reads.empty() && e.reads.front() <= cur) e.reads.erase(e.reads.begin());  // stale reads
+    int64_t prio = kInf;
+    if (!e.pending.empty()) prio = e.reads.empty() ? kInf : e.reads.front();
+    if (e.pending.empty()) {
+      e.queued = false;
+      e.prio = kInf;
+      if (e.reads.empty()) sh.elems.erase(id);
+      return;
+    }
+    if (e.queued && e.prio == prio) return;
+    e.prio = prio;
+    e.queued = true;
+    if (prio == kInf) {
+      sh.inf_bucket.push_back(id);
+    } else {
+      sh.buckets[prio % kHorizon].push_back(id);
+      sh.min_hint = std::min(sh.min_hint, prio);
+      sh.max_prio = std::max(sh.max_prio, prio);
+    }
+  }
+  // Applies the pending update of one id of shard s whose priority is <= limit (or anything, when
+  // `any`, including the infinity bucket).  Returns false when nothing qualified.
+  bool FlushOne(int s, int64_t limit, bool any) {
+    Shard& sh = shards_[s];
+    int64_t id = -1;
+    std::vector<float> upd;
+    {
+      std::lock_guard<SpinLock> lk(sh.mu);
+      const int64_t hi = std::min<int64_t>(any ? sh.max_prio : limit, sh.max_prio);
+      for (int64_t p = sh.min_hint; p <= hi && id < 0; ++p) {
+        auto& b = sh.buckets[p % kHorizon];
+        while (!b.empty()) {
+          const int64_t cand = b.back();
+          b.pop_back();
+          auto it = sh.elems.find(cand);
+          if (it == sh.elems.end() || !it->second.queued || it->second.prio != p) continue;  // moved meanwhile
+          id = cand;
+          break;
+        }
+        if (id < 0 && b.empty() && p == sh.min_hint && sh.min_hint < sh.max_prio) ++sh.min_hint;
+      }
+      if (id < 0 && any) {
+        while (!sh.inf_bucket.empty()) {
+          const int64_t cand = sh.inf_bucket.back();
+          sh.inf_bucket.pop_back();
+          auto it = sh.elems.find(cand);
+          if (it == sh.elems.end() || !it->second.queued || it->second.prio != kInf) continue;
+          id = cand;
+          break;
+        }
+      }
+      if (id < 0) return false;
+      Elem& e = sh.elems[id];
+      upd.swap(e.pending);
+      e.queued = false;
+      e.prio = kInf;
+      if (e.reads.empty()) sh.elems.erase(id);
+      inflight_.fetch_add(1);
+    }
+    {
+      BitRow br = row_lock(id);
+            std::lock_guard<BitRow> lk(br);
+      float* row = table_ + id * dim_;
+      for (int d = 0; d < dim_; ++d) row[d] += upd[d];
+    }
+    flushed_.fetch_add(1, std::memory_order_relaxed);
+    inflight_.fetch_sub(1);
+    return true;
+  }
+  void FlushLoop() {
+    int s = 0;
+    while (running_) {
+      bool any = false;
+      for (int k = 0; k < nshards_ && running_; ++k) {
+        s = (s + 1) % nshards_;
+        // background threads stay within the lookahead window first, then take idle (infinity) work
+        if (FlushOne(s, cur_step_.load() + L_ + 1, false)) any = true;
+      }
+      if (!any) {
+        for (int k = 0; k < nshards_ && running_; ++k)
+          if (FlushOne(k, kInf, true)) { any = true; break; }
+      }
+      if (!any) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+  }
+
+  int ranks_ = 1, L_ = 10, dim_ = 32, nthreads_ = 2, nshards_ = 16;
+  float clr_ = 0.01f;
+  int64_t capacity_ = 0, cache_size_ = 0, rows_ = 0;
+  bool async_ = true;
+  float* table_ = nullptr;
+  std::vector<float*> caches_;
+  std::vector<Input> inputs_;
+  std::vector<Shard> shards_;
+  BitLockTable row_locks_;
+  std::atomic<int64_t> cur_step_{-1}, max_published_{-1}, flushed_{0};
+  std::atomic<int> inflight_{0};
+  std::atomic<bool> running_{false};
+  std::vector<std::thread> flushers_;
+};
+
+}  // namespace rs
+
+// ================================================================ C ABI
+using rs::Controller;
+using rs::IndexedHeap;
+
+RS_API void* rs_heap_create() { return new IndexedHeap(); }
+RS_API void rs_heap_destroy(void* h) { delete static_cast<IndexedHeap*>(h); }
+RS_API void rs_heap_upsert(void* h, long long id, long long prio) { static_cast<IndexedHeap*>(h)->upsert(id, prio); }
+RS_API int rs_heap_erase(void* h, long long id) { return static_cast<IndexedHeap*>(h)->erase(id) ? 1 : 0; }
+RS_API int rs_heap_pop(void* h, long long* id, long long* prio) {
+  int64_t i, p;
+  if (!static_cast<IndexedHeap*>(h)->pop(&i, &p)) return 0;
+  *id = i; *prio = p;
+  return 1;
+}
+RS_API int rs_heap_top(void* h, long long* id, long long* prio) {
+  int64_t i, p;
+  if (!static_cast<IndexedHeap*>(h)->top(&i, &p)) return 0;
+  *id = i; *prio = p;
+  return 1;
+}
+RS_API long long rs_heap_size(void* h) { return static_cast<long long>(static_cast<IndexedHeap*>(h)->size()); }
+RS_API int rs_heap_check(void* h) { return static_cast<IndexedHeap*>(h)->check() ? 1 : 0; }
+
+RS_API int rs_ctrl_create(const char* json, void** out) {
+  RS_REQUIRE(json && out, "rs_ctrl_create: null argument");
+  *out = new Controller(json);
+  return RS_OK;
+}
+RS_API int rs_ctrl_destroy(void* c) { delete static_cast<Controller*>(c); return RS_OK; }
+RS_API int rs_ctrl_register_table(void* c, float* table, long long rows) {
+  RS_REQUIRE(c && table && rows > 0, "rs_ctrl_register_table: bad argument");
+  static_cast<Controller*>(c)->RegisterTable(table, rows);
+  return RS_OK;
+}
+RS_API int rs_ctrl_register_cache(void* c, int rank, float* cache) { static_cast<Controller*>(c)->RegisterCache(rank, cache); return RS_OK; }
+RS_API int rs_ctrl_start(void* c) { static_cast<Controller*>(c)->Start(); return RS_OK; }
+RS_API int rs_ctrl_stop(void* c) { static_cast<Controller*>(c)->StopThreads(); return RS_OK; }
+RS_API int rs_ctrl_drain(void* c) { static_cast<Controller*>(c)->Drain(); return RS_OK; }
+RS_API int rs_ctrl_publish_reads(void* c, int rank, long long step, const long long* ids, long long n) {
+  static_cast<Controller*>(c)->PublishReads(rank, step, reinterpret_cast<const int64_t*>(ids), n);
+  return RS_OK;
+}
+RS_API int rs_ctrl_set_step_input(void* c, int rank, const long long* keys, long long n, const float* grads) {
+  static_cast<Controller*>(c)->SetStepInput(rank, reinterpret_cast<const int64_t*>(keys), n, grads);
+  return RS_OK;
+}
+RS_API int rs_ctrl_process_one_step(void* c, long long step) { static_cast<Controller*>(c)->ProcessOneStep(step); return RS_OK; }
+RS_API int rs_ctrl_block_to_step(void* c, long long step, int timeout_ms) {
+  return static_cast<Controller*>(c)->BlockToStepN(step, timeout_ms)
+             ? RS_OK
+             : rs::set_error(RS_ERR_TIMEOUT, "BlockToStepN(%lld) timed out after %d ms", step, timeout_ms);
+}
+RS_API long long rs_ctrl_pending(void* c) { return static_cast<Controller*>(c)->PendingCount(); }
+RS_API long long rs_ctrl_min_priority(void* c) { return static_cast<Controller*>(c)->MinPriority(); }
+RS_API int rs_ctrl_print_pq(void* c, char* buf, int cap) {
+  const std::string s = static_cast<Controller*>(c)->PrintPq();
+  if (buf && cap > 0) {
+    const int n = std::min<int>(cap - 1, static_cast<int>(s.size()));
+    memcpy(buf, s.data(), n);
+    buf[n] = 0;
+  }
+  return static_cast<int>(s.size());
+}
