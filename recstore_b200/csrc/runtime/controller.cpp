@@ -170,7 +170,7 @@ class Controller {
     if (!async_) return;
     for (int64_t i = 0; i < n; ++i) {
       const int64_t id = ids[i];
-      if (InCache(id)) continue;
+      if (id < 0 || id >= rows_) continue;
       Shard& sh = shard_of(id);
       std::lock_guard<SpinLock> lk(sh.mu);
       Elem& e = sh.elems[id];
@@ -192,16 +192,14 @@ class Controller {
           if (id < 0 || id >= rows_) continue;
           const float* g = in.grads + i * dim_;
           const int owner = CacheOwner(id);
-          if (owner >= 0) {
-            // Cached rows are authoritative in the owner's cache.  A registered (host-visible) cache is
-            // updated here; an HBM cache is updated by the owning GPU's kernel, nothing to do on the host.
-            if (caches_[owner]) {
-              float* row = caches_[owner] + (id - owner * cache_size_) * dim_;
-              BitRow br = row_lock(id);
-            std::lock_guard<BitRow> lk(br);
-              for (int d = 0; d < dim_; ++d) row[d] -= clr_ * g[d];
-            }
-            continue;
+          if (owner >= 0 && caches_[owner]) {
+            // A registered (host-visible) cache replica is updated here; an HBM replica is updated by the
+            // owning GPU's kernel.  The host table receives every update as well (grad_base.h:440-461, 509-565),
+            // so it stays a complete copy that any rank may read.
+            float* row = caches_[owner] + (id - owner * cache_size_) * dim_;
+            BitRow cr = row_lock(id);
+            std::lock_guard<BitRow> clk(cr);
+            for (int d = 0; d < dim_; ++d) row[d] -= clr_ * g[d];
           }
           if (!async_) {
             BitRow br = row_lock(id);
