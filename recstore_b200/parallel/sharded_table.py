@@ -1,0 +1,148 @@
+"""Row-sharded embedding table over the GPUs of one box (cyclic placement: owner(id) = id % world).
+
+``lookup(ids)`` returns the rows of arbitrary global ids on the calling rank; ``update(grads)`` sends
+the gradients of the last lookup back to the owners, which segment-reduce duplicates and apply SGD
+or row-wise Adagrad in place.  Keys, rows and gradients move with peer stores into NVLink-mapped
+windows (``csrc/comm/shard_exchange.cu``), ordered by flag channels; nothing is staged through the
+host and no collective is called.  Duplicate ids are folded before they travel
+(``unique_keys`` + ``segment_sum``), which matters for Zipf / power-law id streams.
+
+This is the storage behind the knowledge-graph entity table (86 M x 400 spread over 8 x HBM) and the
+parameter-server micro-benchmark, and the native counterpart of the reference's
+``KnownShardedCachedEmbedding`` exchange (src/python/pytorch/recstore/cache/sharded_cache.py:181-345).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .._lib import HashTableView, i32, i64, vp, f32, ptr, stream_ptr
+from ..ops import functional as F_
+from .peer import PeerContext
+
+_lib.register_signatures({
+    "rs_shard_push_keys": (i32, [vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp, vp]),
+    "rs_shard_gather_push_rows": (i32, [vp, i64, vp, vp, vp, vp, i32, i32, i32, i64, C.POINTER(HashTableView), vp, vp]),
+    "rs_shard_unbucket_rows": (i32, [vp, vp, i64, i32, vp, i32, vp]),
+    "rs_shard_push_grads": (i32, [vp, vp, i64, i32, i32, i64, vp, vp]),
+    "rs_segment_sum": (i32, [vp, vp, i64, i32, vp, vp]),
+    "rs_expand_rows": (i32, [vp, vp, i64, i32, vp, vp]),
+    "rs_unique_keys": (i32, [vp, i64, vp, vp, _lib.u64, vp, vp, vp, vp, vp]),
+})
+
+CH_KEYS, CH_ROWS, CH_GRADS = 8, 9, 10
+
+
+class ShardedEmbeddingTable:
+    def __init__(self, ctx: PeerContext, name: str, num_rows: int, dim: int, max_keys: int, *, lr: float = 0.01,
+                 eps: float = 1e-10, optimizer: str = "rowwise_adagrad", dedup: bool = True, init: str = "uniform",
+                 init_scale: Optional[float] = None, seed: int = 0):
+        assert dim % 4 == 0
+        self.ctx, self.name, self.N, self.D = ctx, name, int(num_rows), int(dim)
+        self.rank, self.world = ctx.rank, ctx.world
+        self.cap = int(max_keys)
+        self.lr, self.eps, self.optimizer, self.dedup = lr, eps, optimizer, dedup
+        dev = self.dev = ctx.device
+        self.local_rows = (self.N + self.world - 1) // self.world
+        self.weight = torch.empty(self.local_rows, self.D, device=dev)
+        g = torch.Generator(device=dev).manual_seed(seed * 131 + self.rank)
+        if init == "uniform":
+            b = init_scale if init_scale is not None else math.sqrt(1.0 / self.N)
+            self.weight.uniform_(-b, b, generator=g)
+        elif init == "zeros":
+            self.weight.zero_()
+        elif init == "row_index":                          # row of global id i holds the value i (tests)
+            ids = torch.arange(self.local_rows, device=dev, dtype=torch.float32) * self.world + self.rank
+            self.weight.copy_(ids.unsqueeze(1).expand(-1, self.D))
+        else:
+            raise ValueError(init)
+        self.state = torch.zeros(self.local_rows, device=dev) if optimizer == "rowwise_adagrad" else None
+        W, cap, D = self.world, self.cap, self.D
+        self.key_win = ctx.alloc(f"{name}.keys", W * cap * 8)
+        self.count_win = ctx.alloc(f"{name}.counts", W * 4)
+        self.row_win = ctx.alloc(f"{name}.rows", W * cap * D * 4)
+        self.grad_win = ctx.alloc(f"{name}.grads", W * cap * D * 4)
+        self.rowidx = torch.full((W * cap,), -1, dtype=torch.int64, device=dev)
+        self._counts = torch.zeros(W, dtype=torch.int32, device=dev)
+        self._cursor = torch.zeros(W, dtype=torch.int32, device=dev)
+        n = W * cap
+        self._slot = torch.empty(n, dtype=torch.int64, device=dev)
+        nslots = 2
+        while nslots < 2 * n:
+            nslots <<= 1
+        self._nslots = nslots
+        self._sk = torch.empty(nslots, dtype=torch.int64, device=dev)
+        self._si = torch.empty(nslots, dtype=torch.int32, device=dev)
+        self._uniq = torch.empty(n, dtype=torch.int64, device=dev)
+        self._inv = torch.empty(n, dtype=torch.int32, device=dev)
+        self._ucount = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._urows = torch.empty(n, D, device=dev)
+        self._ugrad = torch.empty(n, D, device=dev)
+        self._n = 0
+        self.launches = 0
+
+    # ------------------------------------------------------------------ forward
+    def lookup(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Rows of ``ids`` ([n] int64 on this device, n <= world * max_keys and at most ``max_keys`` per owner)."""
+        ids = ids.contiguous()
+        n = ids.numel()
+        assert n <= self.world * self.cap
+        st, sp = self.ctx.status, stream_ptr()
+        self._n = n
+        self.launches = 0
+        if self.dedup:
+            self._uniq[:n].fill_(-1)
+            _lib.call("rs_unique_keys", ptr(ids), n, ptr(self._sk), ptr(self._si), self._nslots, ptr(self._uniq), ptr(self._inv),
+                      ptr(self._ucount), ptr(st), sp)
+            keys = self._uniq
+            self.launches += 3
+        else:
+            keys = ids
+        _lib.call("rs_shard_push_keys", ptr(keys), n, self.world, self.rank, self.cap, ptr(self._counts), ptr(self._cursor),
+                  ptr(self.key_win.table), ptr(self.count_win.table), ptr(self._slot), ptr(st), sp)
+        self.ctx.signal(CH_KEYS); self.ctx.wait(CH_KEYS)
+        _lib.call("rs_shard_gather_push_rows", ptr(self.weight), self.local_rows, self.key_win.local_ptr, self.count_win.local_ptr,
+                  ptr(self.row_win.table), ptr(self.rowidx), self.world, self.rank, self.D, self.cap, None, ptr(st), sp)
+        self.ctx.signal(CH_ROWS); self.ctx.wait(CH_ROWS)
+        if out is None:
+            out = torch.empty(n, self.D, device=self.dev)
+        if self.dedup:
+            _lib.call("rs_shard_unbucket_rows", self.row_win.local_ptr, ptr(self._slot), n, self.D, ptr(self._urows), 0, sp)
+            _lib.call("rs_expand_rows", ptr(self._urows), ptr(self._inv), n, self.D, ptr(out), sp)
+            self.launches += 1
+        else:
+            _lib.call("rs_shard_unbucket_rows", self.row_win.local_ptr, ptr(self._slot), n, self.D, ptr(out), 0, sp)
+        self.launches += 9
+        return out
+
+    # ------------------------------------------------------------------ backward
+    def update(self, grads: torch.Tensor) -> None:
+        """Applies the optimizer to the rows of the LAST lookup; ``grads`` [n, D] fp32, one row per looked-up id."""
+        n = self._n
+        assert grads.shape == (n, self.D) and grads.dtype == torch.float32
+        grads = grads.contiguous()
+        st, sp = self.ctx.status, stream_ptr()
+        if self.dedup:
+            self._ugrad[:n].zero_()
+            _lib.call("rs_segment_sum", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), sp)
+            src = self._ugrad
+        else:
+            src = grads
+        _lib.call("rs_shard_push_grads", ptr(src), ptr(self._slot), n, self.D, self.rank, self.cap, ptr(self.grad_win.table), sp)
+        self.ctx.signal(CH_GRADS); self.ctx.wait(CH_GRADS)
+        nnz = self.world * self.cap
+        F_.emb_backward(self.weight, self.state, self.rowidx, None, nnz, self.grad_win.view(torch.float32, (nnz, self.D)),
+                        grad_row_stride=self.D, B=nnz, D=self.D, grad_bf16=False, lr=self.lr, eps=self.eps,
+                        optimizer=self.optimizer, status=st)
+        self.launches += 7
+
+    # ------------------------------------------------------------------ whole-table access (tests, checkpoints)
+    def local_global_ids(self) -> torch.Tensor:
+        return torch.arange(self.local_rows, device=self.dev) * self.world + self.rank
+
+    def nvlink_bytes_per_lookup(self, n_unique_remote: int) -> int:
+        return n_unique_remote * (8 + self.D * 4)

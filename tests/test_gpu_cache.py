@@ -116,3 +116,30 @@ def test_range_cache_query(dev):
     torch.cuda.synchronize()
     assert torch.equal(out[:, 0].cpu(), torch.tensor([0, 100.5, 299.5, 300, 999, 150.5]))
     assert st.item() == 0
+
+
+def test_sharded_table_single_gpu(dev):
+    """The row-sharded table degenerates to a local gather / update on one GPU (same kernels, local windows)."""
+    from recstore_b200.parallel.peer import PeerContext
+    from recstore_b200.parallel.sharded_table import ShardedEmbeddingTable
+    from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update, sgd_update
+    ctx = PeerContext(0, 1, device=dev)
+    N, D, n = 2000, 16, 4096
+    for opt in ("rowwise_adagrad", "sgd"):
+        tab = ShardedEmbeddingTable(ctx, f"solo_{opt}", N, D, max_keys=n, lr=0.1, eps=1e-8, optimizer=opt, init="row_index")
+        W = torch.arange(N, device=dev, dtype=torch.float32).unsqueeze(1).repeat(1, D)
+        S = torch.zeros(N, device=dev)
+        g = torch.Generator(device=dev).manual_seed(3)
+        for step in range(3):
+            ids = torch.randint(0, N, (n,), device=dev, generator=g)
+            rows = tab.lookup(ids)
+            assert torch.allclose(rows, W[ids], atol=1e-4)
+            grads = torch.randn(n, D, device=dev, generator=g)
+            tab.update(grads)
+            if opt == "sgd":
+                sgd_update(W, ids, grads, 0.1)
+            else:
+                rowwise_adagrad_update(W, S, ids, grads, 0.1, 1e-8)
+        torch.cuda.synchronize()
+        ctx.check_status()
+        assert torch.allclose(tab.weight, W, atol=2e-3, rtol=2e-3)

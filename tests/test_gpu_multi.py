@@ -131,3 +131,52 @@ def test_bounded_wait_reports_timeout():
     out = mgr.dict()
     mp.spawn(_timeout_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     assert all(out.get(r) == "ok" for r in range(2)), dict(out)
+
+
+def _sharded_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    try:
+        from recstore_b200.parallel.peer import PeerContext
+        from recstore_b200.parallel.sharded_table import ShardedEmbeddingTable
+        from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
+        ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"))
+        N, D, n = 5000, 32, 3000
+        for dedup in (True, False):
+            tab = ShardedEmbeddingTable(ctx, f"t{int(dedup)}", N, D, max_keys=n, lr=0.1, eps=1e-8, dedup=dedup, init="row_index")
+            # oracle: full table replicated on every rank
+            W = torch.arange(N, device="cuda", dtype=torch.float32).unsqueeze(1).repeat(1, D)
+            S = torch.zeros(N, device="cuda")
+            g = torch.Generator(device="cuda").manual_seed(7 + rank)
+            for step in range(3):
+                ids = torch.randint(0, N, (n,), device="cuda", generator=g)
+                ids[::5] = 3                                            # hot key, owned by rank 3 % world
+                rows = tab.lookup(ids)
+                assert torch.allclose(rows, W[ids], atol=1e-4), (rank, dedup, step)
+                grads = torch.randn(n, D, device="cuda", generator=g)
+                tab.update(grads)
+                # every rank's (ids, grads) reach the oracle on every rank
+                all_ids = [torch.empty_like(ids) for _ in range(world)]
+                all_g = [torch.empty_like(grads) for _ in range(world)]
+                dist.all_gather(all_ids, ids); dist.all_gather(all_g, grads)
+                rowwise_adagrad_update(W, S, torch.cat(all_ids), torch.cat(all_g), 0.1, 1e-8)
+            torch.cuda.synchronize()
+            ctx.check_status()
+            mine = tab.local_global_ids()
+            mine = mine[mine < N]
+            assert torch.allclose(tab.weight[: mine.numel()], W[mine], atol=2e-3, rtol=2e-3), (rank, dedup)
+            assert torch.allclose(tab.state[: mine.numel()], S[mine], atol=1e-2, rtol=2e-3), (rank, dedup)
+        dist.barrier()
+        out[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_table_lookup_update_matches_replicated_oracle():
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    world = 4 if _ngpus() >= 4 else 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_sharded_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert all(out.get(r) == "ok" for r in range(world)), dict(out)
