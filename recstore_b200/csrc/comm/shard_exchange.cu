@@ -133,7 +133,8 @@ __global__ void __launch_bounds__(256) unbucket_rows_kernel(const float* __restr
 // grad_win[owner][me * cap + p] = grad[i]
 __global__ void __launch_bounds__(256) push_grads_kernel(const float* __restrict__ grad, const long long* __restrict__ slot,
                                                          long long n, int D, int me, long long cap,
-                                                         float* const* __restrict__ grad_win) {
+                                                         float* const* __restrict__ grad_win, const float* __restrict__ norm,
+                                                         float* const* __restrict__ norm_win) {
   const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (i >= n) return;
   const int lane = threadIdx.x & 31;
@@ -143,18 +144,30 @@ __global__ void __launch_bounds__(256) push_grads_kernel(const float* __restrict
   const long long p = s % cap;
   float* dst = grad_win[d] + (static_cast<long long>(me) * cap + p) * D;
   for (int v = lane; v < (D >> 2); v += 32) reinterpret_cast<float4*>(dst)[v] = __ldg(reinterpret_cast<const float4*>(grad + i * D) + v);
+  if (norm && lane == 0) norm_win[d][static_cast<long long>(me) * cap + p] = norm[i];
 }
 
-// ugrad[inverse[i]] += grad[i]   (segment-sum of duplicate keys before the exchange; ugrad zeroed by the caller)
+// ugrad[inverse[i]] += grad[i], unorm[inverse[i]] += |grad[i]|^2   (segment-sum of duplicate keys before the
+// exchange; both outputs zeroed by the caller).  The separate sum of squares keeps row-wise Adagrad exact:
+// its state needs the sum over occurrences of mean(g^2), not the square of the summed gradient.
 __global__ void __launch_bounds__(256) segment_sum_kernel(const float* __restrict__ grad, const int* __restrict__ inverse,
-                                                          long long n, int D, float* __restrict__ ugrad) {
+                                                          long long n, int D, float* __restrict__ ugrad, float* __restrict__ unorm) {
   const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (i >= n) return;
   const int lane = threadIdx.x & 31;
   const int u = inverse[i];
   if (u < 0) return;
-  for (int v = lane; v < (D >> 2); v += 32)
-    atomicAdd(reinterpret_cast<float4*>(ugrad + static_cast<long long>(u) * D) + v, __ldg(reinterpret_cast<const float4*>(grad + i * D) + v));
+  float sq = 0.f;
+  for (int v = lane; v < (D >> 2); v += 32) {
+    const float4 g = __ldg(reinterpret_cast<const float4*>(grad + i * D) + v);
+    sq += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
+    atomicAdd(reinterpret_cast<float4*>(ugrad + static_cast<long long>(u) * D) + v, g);
+  }
+  if (unorm) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if (lane == 0) atomicAdd(&unorm[u], sq);
+  }
 }
 
 // out[i] = src[inverse[i]]
@@ -215,19 +228,22 @@ RS_API int rs_shard_unbucket_rows(const float* row_win, const long long* slot, l
   return RS_OK;
 }
 
+// norm / norm_win (optional): per-row sum of squares delivered next to the gradients ([world, cap] fp32 windows).
 RS_API int rs_shard_push_grads(const float* grad, const long long* slot, long long n, int D, int me, long long cap,
-                               void* const* grad_win, cudaStream_t stream) {
+                               void* const* grad_win, const float* norm, void* const* norm_win, cudaStream_t stream) {
   RS_REQUIRE(grad && slot && grad_win && D % 4 == 0, "rs_shard_push_grads: bad argument");
   if (n == 0) return RS_OK;
-  push_grads_kernel<<<warps_grid(n), 256, 0, stream>>>(grad, slot, n, D, me, cap, reinterpret_cast<float* const*>(grad_win));
+  push_grads_kernel<<<warps_grid(n), 256, 0, stream>>>(grad, slot, n, D, me, cap, reinterpret_cast<float* const*>(grad_win), norm,
+                                                       reinterpret_cast<float* const*>(norm_win));
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
 
-RS_API int rs_segment_sum(const float* grad, const int* inverse, long long n, int D, float* ugrad, cudaStream_t stream) {
+RS_API int rs_segment_sum(const float* grad, const int* inverse, long long n, int D, float* ugrad, float* unorm,
+                          cudaStream_t stream) {
   RS_REQUIRE(grad && inverse && ugrad && D % 4 == 0, "rs_segment_sum: bad argument");
   if (n == 0) return RS_OK;
-  segment_sum_kernel<<<warps_grid(n), 256, 0, stream>>>(grad, inverse, n, D, ugrad);
+  segment_sum_kernel<<<warps_grid(n), 256, 0, stream>>>(grad, inverse, n, D, ugrad, unorm);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

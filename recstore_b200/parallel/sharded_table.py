@@ -28,8 +28,8 @@ _lib.register_signatures({
     "rs_shard_push_keys": (i32, [vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp, vp]),
     "rs_shard_gather_push_rows": (i32, [vp, i64, vp, vp, vp, vp, i32, i32, i32, i64, C.POINTER(HashTableView), vp, vp]),
     "rs_shard_unbucket_rows": (i32, [vp, vp, i64, i32, vp, i32, vp]),
-    "rs_shard_push_grads": (i32, [vp, vp, i64, i32, i32, i64, vp, vp]),
-    "rs_segment_sum": (i32, [vp, vp, i64, i32, vp, vp]),
+    "rs_shard_push_grads": (i32, [vp, vp, i64, i32, i32, i64, vp, vp, vp, vp]),
+    "rs_segment_sum": (i32, [vp, vp, i64, i32, vp, vp, vp]),
     "rs_expand_rows": (i32, [vp, vp, i64, i32, vp, vp]),
     "rs_unique_keys": (i32, [vp, i64, vp, vp, _lib.u64, vp, vp, vp, vp, vp]),
 })
@@ -66,6 +66,8 @@ class ShardedEmbeddingTable:
         self.count_win = ctx.alloc(f"{name}.counts", W * 4)
         self.row_win = ctx.alloc(f"{name}.rows", W * cap * D * 4)
         self.grad_win = ctx.alloc(f"{name}.grads", W * cap * D * 4)
+        self.norm_win = ctx.alloc(f"{name}.norms", W * cap * 4)
+        self._unorm = torch.empty(W * cap, device=dev)
         self.rowidx = torch.full((W * cap,), -1, dtype=torch.int64, device=dev)
         self._counts = torch.zeros(W, dtype=torch.int32, device=dev)
         self._cursor = torch.zeros(W, dtype=torch.int32, device=dev)
@@ -126,18 +128,22 @@ class ShardedEmbeddingTable:
         assert grads.shape == (n, self.D) and grads.dtype == torch.float32
         grads = grads.contiguous()
         st, sp = self.ctx.status, stream_ptr()
+        gnorm = None
         if self.dedup:
             self._ugrad[:n].zero_()
-            _lib.call("rs_segment_sum", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), sp)
-            src = self._ugrad
+            self._unorm[:n].zero_()
+            _lib.call("rs_segment_sum", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), sp)
+            _lib.call("rs_shard_push_grads", ptr(self._ugrad), ptr(self._slot), n, self.D, self.rank, self.cap,
+                      ptr(self.grad_win.table), ptr(self._unorm), ptr(self.norm_win.table), sp)
+            gnorm = self.norm_win.view(torch.float32, (self.world * self.cap,))
         else:
-            src = grads
-        _lib.call("rs_shard_push_grads", ptr(src), ptr(self._slot), n, self.D, self.rank, self.cap, ptr(self.grad_win.table), sp)
+            _lib.call("rs_shard_push_grads", ptr(grads), ptr(self._slot), n, self.D, self.rank, self.cap,
+                      ptr(self.grad_win.table), None, None, sp)
         self.ctx.signal(CH_GRADS); self.ctx.wait(CH_GRADS)
         nnz = self.world * self.cap
         F_.emb_backward(self.weight, self.state, self.rowidx, None, nnz, self.grad_win.view(torch.float32, (nnz, self.D)),
                         grad_row_stride=self.D, B=nnz, D=self.D, grad_bf16=False, lr=self.lr, eps=self.eps,
-                        optimizer=self.optimizer, status=st)
+                        optimizer=self.optimizer, status=st, gnorm=gnorm, gnorm_stride=1)
         self.launches += 7
 
     # ------------------------------------------------------------------ whole-table access (tests, checkpoints)
