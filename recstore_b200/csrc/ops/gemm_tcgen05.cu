@@ -12,6 +12,8 @@
 //   mode 1 ("NT"):  D[M,N] = A[K,M]^T . B[K,N]   A and B row-major, reduction over rows
 //                   (wgrad: A = dY[batch,N_out], B = X[batch,K_in]); split over the
 //                   reduction with fp32 atomic accumulation into D.
+//   mode 2 ("NN"):  D[M,N] = A[M,K]   . B[K,N]   A K-major as in mode 0, B row-major [K,N] as in
+//                   mode 1 (e.g. W[bs, negs] . Neg[negs, dim] in the KG gradient)
 // Epilogues (fused into the TMEM read-back):
 //   0  D = acc (+ bias[n])                       bf16 store
 //   1  D = relu(acc + bias[n])                   bf16 store
@@ -129,11 +131,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           mbar_expect_tx(&full[stage], kABytes + b_bytes);
           uint8_t* a_dst = sA + static_cast<size_t>(stage) * kABytes;
           uint8_t* b_dst = sB + static_cast<size_t>(stage) * b_bytes;
-          if (MODE == 0) {
+          if (MODE != 1) {
             tma_load_2d(a_dst, &tma_a, &full[stage], kb * BK, m0);
-            tma_load_2d(b_dst, &tma_b, &full[stage], kb * BK, n0);
           } else {
             for (int h = 0; h < BM / 64; ++h) tma_load_2d(a_dst + h * 8192, &tma_a, &full[stage], m0 + h * 64, kb * BK);
+          }
+          if (MODE == 0) {
+            tma_load_2d(b_dst, &tma_b, &full[stage], kb * BK, n0);
+          } else {
             for (int h = 0; h < g.bn / 64; ++h) tma_load_2d(b_dst + h * 8192, &tma_b, &full[stage], n0 + h * 64, kb * BK);
           }
           last_stage = stage;
@@ -148,7 +153,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(BM, static_cast<uint32_t>(g.bn), MODE, MODE);
+      const uint32_t idesc = make_idesc_bf16(BM, static_cast<uint32_t>(g.bn), MODE == 1 ? 1u : 0u, MODE != 0 ? 1u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -169,17 +174,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             uint64_t ad, bd;
-            if (MODE == 0) {
-              // K-major, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart; a K step of 16
-              // elements moves the start address by 32 B inside the swizzled row.
-              ad = make_smem_desc(a_addr + k * 32, 16, 1024, 2);
-              bd = make_smem_desc(b_addr + k * 32, 16, 1024, 2);
-            } else {
-              // MN-major, 128-byte swizzle: each TMA box holds 64 reduction rows x 64 columns; 8-row
-              // groups are 1024 B apart (SBO), the next 64 columns start one box (8 KiB) later (LBO).
-              ad = make_smem_desc(a_addr + k * 2048, 8192, 1024, 2);
-              bd = make_smem_desc(b_addr + k * 2048, 8192, 1024, 2);
-            }
+            // K-major, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart; a K step of 16
+            // elements moves the start address by 32 B inside the swizzled row.
+            // MN-major, 128-byte swizzle: each TMA box holds 64 reduction rows x 64 columns; 8-row
+            // groups are 1024 B apart (SBO), the next 64 columns start one box (8 KiB) later (LBO).
+            if (MODE != 1) ad = make_smem_desc(a_addr + k * 32, 16, 1024, 2);
+            else ad = make_smem_desc(a_addr + k * 2048, 8192, 1024, 2);
+            if (MODE == 0) bd = make_smem_desc(b_addr + k * 32, 16, 1024, 2);
+            else bd = make_smem_desc(b_addr + k * 2048, 8192, 1024, 2);
             umma_f16(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
@@ -460,10 +462,10 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
                         int bn, int splits, unsigned long long* status, cudaStream_t stream) {
   RS_REQUIRE(A && B && D, "rs_gemm_bf16: null operand");
   RS_REQUIRE(M > 0 && N > 0 && K > 0, "rs_gemm_bf16: empty problem %d %d %d", M, N, K);
-  RS_REQUIRE(mode == 0 || mode == 1, "rs_gemm_bf16: mode must be 0 or 1");
+  RS_REQUIRE(mode >= 0 && mode <= 2, "rs_gemm_bf16: mode must be 0, 1 or 2");
   RS_REQUIRE(epi >= 0 && epi <= 5, "rs_gemm_bf16: unknown epilogue %d", epi);
-  RS_REQUIRE(N % 32 == 0, "rs_gemm_bf16: N (%d) must be a multiple of 32", N);
-  RS_REQUIRE(mode == 0 || (M % 64 == 0 && N % 64 == 0), "rs_gemm_bf16: mode 1 needs M, N multiples of 64");
+  RS_REQUIRE(N % 8 == 0, "rs_gemm_bf16: N (%d) must be a multiple of 8", N);
+  RS_REQUIRE(mode != 1 || M % 8 == 0, "rs_gemm_bf16: mode 1 needs M to be a multiple of 8");
   RS_REQUIRE(epi != 2 || aux, "rs_gemm_bf16: epilogue 2 needs aux");
   RS_REQUIRE(epi != 5 || (aux && x0), "rs_gemm_bf16: epilogue 5 needs aux and x0");
   const bool f32_out = (epi == 3 || epi == 4);
@@ -473,11 +475,11 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
     if (N % 256 == 0) bn = 256;
     else if (N % 128 == 0) bn = 128;
     else if (N % 64 == 0) bn = 64;
-    else bn = (mode == 0) ? 32 : 64;
-    if (N < bn) bn = N;
+    else bn = (mode == 0 && N % 32 == 0) ? 32 : 64;
+    if (mode == 0 && N < bn && N % 32 == 0) bn = N;
   }
   RS_REQUIRE(bn % 32 == 0 && bn <= 256 && bn >= 32, "rs_gemm_bf16: bad tile width %d", bn);
-  RS_REQUIRE(mode == 0 || bn % 64 == 0, "rs_gemm_bf16: mode 1 needs a tile width multiple of 64");
+  RS_REQUIRE(mode == 0 || bn % 64 == 0, "rs_gemm_bf16: modes 1 and 2 need a tile width multiple of 64");
 
   GemmArgs g;
   g.M = M; g.N = N; g.K = K; g.bn = bn;
@@ -514,24 +516,23 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
 
   CUtensorMap ma, mb;
   int rc;
-  if (mode == 0) {
-    if ((rc = make_map_bf16(&ma, A, M, K, lda, BM, BK)) != RS_OK) return rc;
-    if ((rc = make_map_bf16(&mb, B, N, K, ldb, bn, BK)) != RS_OK) return rc;
-  } else {
-    if ((rc = make_map_bf16(&ma, A, K, M, lda, BK, 64)) != RS_OK) return rc;
-    if ((rc = make_map_bf16(&mb, B, K, N, ldb, BK, 64)) != RS_OK) return rc;
-  }
+  if (mode != 1) { if ((rc = make_map_bf16(&ma, A, M, K, lda, BM, BK)) != RS_OK) return rc; }
+  else { if ((rc = make_map_bf16(&ma, A, K, M, lda, BK, 64)) != RS_OK) return rc; }
+  if (mode == 0) { if ((rc = make_map_bf16(&mb, B, N, K, ldb, bn, BK)) != RS_OK) return rc; }
+  else { if ((rc = make_map_bf16(&mb, B, K, N, ldb, BK, 64)) != RS_OK) return rc; }
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + kStageBytes + 1024 + 256;
-  static bool attr_set[2] = {false, false};
+  static bool attr_set[3] = {false, false, false};
   if (!attr_set[mode]) {
     if (mode == 0) RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    else RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    else if (mode == 1) RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    else RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set[mode] = true;
   }
   const int items = g.tiles_m * g.tiles_n * g.splits;
   const int grid = items < sms ? items : sms;
   if (mode == 0) gemm_tcgen05_kernel<0><<<grid, kThreads, smem, stream>>>(ma, mb, g);
-  else gemm_tcgen05_kernel<1><<<grid, kThreads, smem, stream>>>(ma, mb, g);
+  else if (mode == 1) gemm_tcgen05_kernel<1><<<grid, kThreads, smem, stream>>>(ma, mb, g);
+  else gemm_tcgen05_kernel<2><<<grid, kThreads, smem, stream>>>(ma, mb, g);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

@@ -1,0 +1,221 @@
+"""Knowledge-graph embedding training (TransE-L2, DistMult) on row-sharded HBM entity / relation tables.
+
+Model, negative sampling and loss follow the reference's patched DGL-KE
+(src/kg/kg/dgl-ke/python/dglke/models/general_models.py:568-631, score_fun.py, loss.py:69-99,
+sampler.py:703-818): a batch of ``batch`` positives per GPU is cut into chunks of ``neg_chunk_size``, each
+chunk shares ``neg_sample_size`` uniformly drawn negative entities, corrupt-head and corrupt-tail
+batches alternate, the loss is the log-sigmoid loss, and embeddings are trained with row-wise sparse
+Adagrad (tensor_models.py:366-436).  Init is ``U(+-(gamma + 2) / dim)`` (general_models.py:223-224).
+
+What is different: the entity table (86 M x 400 fp32 = 138 GB in the headline config) does not live in
+host memory behind a cache; it is spread cyclically over the GPUs' HBM
+(``parallel.sharded_table.ShardedEmbeddingTable``), rows and gradients move by peer stores, and the
+scoring is three element-wise kernels around tcgen05 GEMMs (``csrc/ops/kge.cu``).
+
+Checkpoints keep the reference layout (tensor_models.py:452-476, general_models.py:316-346):
+``{dataset}_{model}_entity.npy``, ``{dataset}_{model}_relation.npy`` and ``config.json``.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import asdict, dataclass
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .. import _lib
+from .._lib import f32, i32, ptr, stream_ptr, vp
+from ..ops import functional as F_
+from ..parallel.peer import PeerContext
+from ..parallel.sharded_table import ShardedEmbeddingTable
+
+_lib.register_signatures({
+    "rs_kge_stage": (i32, [i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
+                           vp, vp, vp, vp, vp, vp, vp]),
+})
+
+MODELS = {"TransE": 0, "TransE_l2": 0, "DistMult": 1}
+
+
+@dataclass
+class KGEConfig:
+    n_entities: int
+    n_relations: int
+    dim: int = 400
+    model: str = "TransE_l2"
+    gamma: float = 10.0
+    batch: int = 1024                 # positives per GPU and step
+    neg_sample_size: int = 256
+    neg_chunk_size: int = 256
+    lr: float = 0.1
+    eps: float = 1e-10
+    seed: int = 0
+    dataset: str = "synthetic"
+
+
+class KGEModel:
+    def __init__(self, cfg: KGEConfig, ctx: Optional[PeerContext] = None):
+        if cfg.model not in MODELS:
+            raise ValueError(f"unsupported model {cfg.model!r}; available: {sorted(MODELS)}")
+        assert cfg.batch % cfg.neg_chunk_size == 0, "the batch is cut into whole chunks (reference rounds it up, utils.py:27-33)"
+        assert cfg.dim % 4 == 0
+        self.cfg = cfg
+        self.ctx = ctx if ctx is not None else PeerContext(0, 1)
+        dev = self.dev = self.ctx.device
+        self.bs, self.cs, self.ns, self.D = cfg.batch, cfg.neg_chunk_size, cfg.neg_sample_size, cfg.dim
+        self.C = self.bs // self.cs
+        self.nneg = self.C * self.ns
+        self.Dp = (self.D + 63) // 64 * 64
+        self.model_id = MODELS[cfg.model]
+        scale = (cfg.gamma + 2.0) / cfg.dim
+        n_ids = 2 * self.bs + self.nneg
+        self.entity = ShardedEmbeddingTable(self.ctx, "kge_entity", cfg.n_entities, self.D, max_keys=n_ids, lr=cfg.lr, eps=cfg.eps,
+                                            init="uniform", init_scale=scale, seed=cfg.seed)
+        self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations, self.D, max_keys=self.bs, lr=cfg.lr,
+                                              eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 1)
+        f = dict(dtype=torch.float32, device=dev)
+        b = dict(dtype=torch.bfloat16, device=dev)
+        self.ent_rows = torch.empty(n_ids, self.D, **f)
+        self.rel_rows = torch.empty(self.bs, self.D, **f)
+        self.ent_grad = torch.empty(n_ids, self.D, **f)
+        self.rel_grad = torch.empty(self.bs, self.D, **f)
+        self.A = torch.zeros(self.bs, self.Dp, **b)
+        self.Bn = torch.zeros(self.nneg, self.Dp, **b)
+        self.a2 = torch.empty(self.bs, **f)
+        self.b2 = torch.empty(self.nneg, **f)
+        self.S = torch.empty(self.bs, self.nneg, **f)
+        self.W = torch.empty(self.bs, self.nneg, **b)
+        self.rowsum = torch.empty(self.bs, **f)
+        self.colsum = torch.empty(self.nneg, **f)
+        self.GA = torch.empty(self.bs, self.Dp, **f)
+        self.GB = torch.empty(self.nneg, self.Dp, **f)
+        self.loss = torch.zeros(2, **f)
+        self.pos_score = torch.empty(self.bs, **f)
+        self.neg_score = torch.empty(self.bs, self.ns, **f)
+        self.ids = torch.empty(n_ids, dtype=torch.int64, device=dev)
+        self.step_no = 0
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------ kernels
+    def _stage(self, stage: int, corrupt_head: bool, want_scores: bool):
+        bs = self.bs
+        h, t, neg = self.ent_rows[:bs], self.ent_rows[bs:2 * bs], self.ent_rows[2 * bs:]
+        gh, gt, gneg = self.ent_grad[:bs], self.ent_grad[bs:2 * bs], self.ent_grad[2 * bs:]
+        _lib.call("rs_kge_stage", stage, ptr(h), ptr(self.rel_rows), ptr(t), ptr(neg), bs, self.cs, self.ns, self.D, self.Dp,
+                  self.model_id, 1 if corrupt_head else 0, self.cfg.gamma, ptr(self.A), ptr(self.Bn), ptr(self.a2), ptr(self.b2),
+                  ptr(self.loss), ptr(gh), ptr(self.rel_grad), ptr(gt), ptr(gneg), ptr(self.S), ptr(self.W), ptr(self.rowsum),
+                  ptr(self.colsum), ptr(self.GA), ptr(self.GB), ptr(self.pos_score) if want_scores else None,
+                  ptr(self.neg_score) if want_scores else None, stream_ptr())
+
+    def _forward(self, corrupt_head: bool, want_scores: bool):
+        st = self.ctx.status
+        self.loss.zero_(); self.rowsum.zero_(); self.colsum.zero_()
+        self._stage(0, corrupt_head, want_scores)
+        F_.gemm_bf16(self.A, self.Bn, self.S, mode=0, epi=F_.EPI_F32, status=st)
+        self._stage(1, corrupt_head, want_scores)
+
+    def _fetch(self, h_ids, r_ids, t_ids, neg_ids):
+        bs = self.bs
+        self.ids[:bs].copy_(h_ids); self.ids[bs:2 * bs].copy_(t_ids); self.ids[2 * bs:].copy_(neg_ids)
+        self.entity.lookup(self.ids, out=self.ent_rows)
+        self.relation.lookup(r_ids.contiguous(), out=self.rel_rows)
+
+    def train_step(self, h_ids: torch.Tensor, r_ids: torch.Tensor, t_ids: torch.Tensor, neg_ids: torch.Tensor,
+                   corrupt_head: Optional[bool] = None) -> torch.Tensor:
+        """One step on device id tensors (``neg_ids``: ``[batch / chunk * neg_sample_size]`` entity ids); returns the
+        loss as a 0-d device tensor (no host synchronisation)."""
+        if corrupt_head is None:
+            corrupt_head = bool(self.step_no & 1)            # head / tail corruption alternate
+        self.step_no += 1
+        st = self.ctx.status
+        self._fetch(h_ids, r_ids, t_ids, neg_ids)
+        self._forward(corrupt_head, False)
+        F_.gemm_bf16(self.W, self.Bn, self.GA, mode=2, epi=F_.EPI_F32, status=st)
+        F_.gemm_bf16(self.W, self.A, self.GB, mode=1, epi=F_.EPI_F32, status=st)
+        self._stage(2, corrupt_head, False)
+        self.entity.update(self.ent_grad)
+        self.relation.update(self.rel_grad)
+        self.launches_per_step = 6 + 3 + self.entity.launches + self.relation.launches
+        return self.loss.sum()
+
+    @torch.no_grad()
+    def score_batch(self, h_ids, r_ids, t_ids, neg_ids, corrupt_head: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Scores of the positives ``[batch]`` and of every (positive, chunk negative) pair ``[batch, neg_sample_size]``."""
+        self._fetch(h_ids, r_ids, t_ids, neg_ids)
+        self._forward(corrupt_head, True)
+        return self.pos_score.clone(), self.neg_score.clone()
+
+    @torch.no_grad()
+    def evaluate(self, h_ids, r_ids, t_ids, generator: Optional[torch.Generator] = None) -> Dict[str, float]:
+        """Link-prediction metrics of one batch of test triples against sampled negatives, both corruptions
+        (rank of the positive among its chunk's negatives; general_models.py:464-513): MRR, MR, HITS@1/3/10."""
+        ranks = []
+        for corrupt_head in (False, True):
+            neg = torch.randint(0, self.cfg.n_entities, (self.nneg,), device=self.dev, generator=generator)
+            pos, negs = self.score_batch(h_ids, r_ids, t_ids, neg, corrupt_head)
+            ranks.append(1 + (negs >= pos.unsqueeze(1)).sum(1))
+        r = torch.cat(ranks).float()
+        return {"MRR": (1.0 / r).mean().item(), "MR": r.mean().item(), "HITS@1": (r <= 1).float().mean().item(),
+                "HITS@3": (r <= 3).float().mean().item(), "HITS@10": (r <= 10).float().mean().item()}
+
+    # ------------------------------------------------------------------ checkpoints
+    def _gather_table(self, tab: ShardedEmbeddingTable) -> Optional[np.ndarray]:
+        """Full table on rank 0 (host), ``None`` elsewhere.  Meant for tables that fit in host memory."""
+        world, rank = self.ctx.world, self.ctx.rank
+        local = tab.weight.cpu()
+        if world == 1:
+            return local[: tab.N].numpy()
+        import torch.distributed as dist
+        parts = [None] * world if rank == 0 else None
+        dist.gather_object(local, parts, dst=0, group=self.ctx.group)
+        if rank != 0:
+            return None
+        full = torch.empty(tab.local_rows * world, tab.D)
+        for r, p in enumerate(parts):
+            full[r::world] = p
+        return full[: tab.N].numpy()
+
+    def save(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        ent = self._gather_table(self.entity)
+        rel = self._gather_table(self.relation)
+        if self.ctx.rank == 0:
+            c = self.cfg
+            np.save(os.path.join(path, f"{c.dataset}_{c.model}_entity.npy"), ent)
+            np.save(os.path.join(path, f"{c.dataset}_{c.model}_relation.npy"), rel)
+            conf = asdict(c)
+            conf.update({"emp_file": f"{c.dataset}_{c.model}_entity.npy", "rmap_file": f"{c.dataset}_{c.model}_relation.npy",
+                         "hidden_dim": c.dim, "model_name": c.model})
+            with open(os.path.join(path, "config.json"), "w") as f:
+                json.dump(conf, f, indent=2)
+
+    def load(self, path: str) -> None:
+        c = self.cfg
+        for tab, kind in ((self.entity, "entity"), (self.relation, "relation")):
+            full = torch.from_numpy(np.load(os.path.join(path, f"{c.dataset}_{c.model}_{kind}.npy")))
+            mine = full[self.ctx.rank::self.ctx.world]
+            tab.weight[: mine.shape[0]].copy_(mine)
+
+
+class KGSampler:
+    """Synthetic triples with power-law entity degrees; every ``next()`` yields device id tensors of one step."""
+
+    def __init__(self, cfg: KGEConfig, n_triples: int, alpha: float = 1.3, device="cuda", rank: int = 0, seed: int = 0):
+        from ..utils.data import powerlaw_triples
+        h, r, t = powerlaw_triples(n_triples, cfg.n_entities, cfg.n_relations, alpha, seed * 97 + rank)
+        self.h, self.r, self.t = (torch.from_numpy(x).to(device) for x in (h, r, t))
+        self.cfg, self.dev, self.n = cfg, device, n_triples
+        self.gen = torch.Generator(device=device).manual_seed(seed * 31 + rank)
+        self.nneg = cfg.batch // cfg.neg_chunk_size * cfg.neg_sample_size
+        self.step = 0
+
+    def __next__(self):
+        idx = torch.randint(0, self.n, (self.cfg.batch,), device=self.dev, generator=self.gen)
+        neg = torch.randint(0, self.cfg.n_entities, (self.nneg,), device=self.dev, generator=self.gen)
+        self.step += 1
+        return self.h[idx], self.r[idx], self.t[idx], neg
+
+    def __iter__(self):
+        return self
