@@ -232,3 +232,23 @@ def test_dist_tensor_embedding_and_optimizers(tmp_path):
     assert torch.equal(st[0::2], torch.full((25,), 5.0)) and torch.equal(st[1::2], torch.full((25,), 9.0))
     with pytest.warns(UserWarning):
         opt2.load(str(tmp_path / "missing"))
+
+
+def test_renumbering_narrow_and_zipf_filler():
+    from recstore_b200 import torch_op
+    d = torch.empty(20, dtype=torch.int64)
+    hot = [torch.tensor([5, 7, 19]), torch.tensor([0, 3])]
+    torch_op.construct_renumbering_dict_op(d, 2, hot)
+    assert d[[5, 7, 19]].tolist() == [0, 1, 2] and d[[0, 3]].tolist() == [3, 4]
+    cold = [i for i in range(20) if i not in (5, 7, 19, 0, 3)]
+    assert d[cold].tolist() == list(range(5, 20))                    # cold ids keep their relative order
+    assert sorted(d.tolist()) == list(range(20))                     # a permutation
+    with pytest.raises(Exception):
+        torch_op.construct_renumbering_dict_op(d, 2, [torch.tensor([1]), torch.tensor([1])])
+    buf = torch.zeros(1000, 100)
+    v = torch_op.NarrowShapeTensor_op(buf, (7, 3), torch.int64)
+    v.fill_(5)
+    assert v.shape == (7, 3) and v.data_ptr() == buf.data_ptr()
+    t = torch.empty(10000, dtype=torch.int64)
+    torch_op.ZipfianTorchFiller(1000, 0.99).fillArrayTorch(t)
+    assert t.min() >= 1 and t.max() <= 1000 and (t <= 10).float().mean() > 0.2
