@@ -4,8 +4,10 @@
 // API parity: insert/lookup of the reference's StaticHashTable (src/storage/gpu_cache/
 // static_hash_table.cu:117-144, 223-268), extended with erase, dump (checkpoint enumeration) and an
 // invariant checker for the tests (count of live slots == size, every key finds itself).
+#include <mutex>
 #include "common/rs_common.h"
 #include "kv/hash_table.cuh"
+#include "kv/unique_noalloc.h"
 
 namespace {
 using namespace rs;
@@ -237,6 +239,55 @@ RS_API int rs_unique_keys(const long long* keys, long long n, void* slots_key, v
   if (n == 0) return RS_OK;
   unique_kernel<<<grid_for(n), 256, 0, stream>>>(keys, n, static_cast<unsigned long long*>(slots_key),
                                                  static_cast<int*>(slots_idx), nslots - 1, unique_out, inverse, count, status);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+// ------------------------------------------------------------------ allocation-free unique
+// Scratch of rs_unique_keys_noalloc (see kv/unique_noalloc.h): 2 * MAX_KEYS slots, 8-byte keys first,
+// then 4-byte indices.  In host code the NAME of this array is only a handle for the runtime, not a
+// device address; the address every kernel gets comes from cudaGetSymbolAddress below.
+namespace {
+constexpr unsigned long long kNoAllocSlots = 2ull * RS_UNIQUE_NOALLOC_MAX_KEYS;
+static __device__ __align__(256) unsigned char g_unique_noalloc_scratch[kNoAllocSlots * (sizeof(unsigned long long) + sizeof(int))];
+
+constexpr int kMaxDevices = 64;
+void* g_noalloc_addr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+}  // namespace
+
+RS_API int rs_unique_keys_noalloc(const long long* keys, long long n, long long* unique_out, int* inverse, int* count,
+                                  unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(unique_out && count && (keys || n == 0), "rs_unique_keys_noalloc: null argument");
+  RS_REQUIRE(n >= 0, "rs_unique_keys_noalloc: negative key count");
+  if (n > RS_UNIQUE_NOALLOC_MAX_KEYS)
+    return rs::set_error(RS_ERR_CAPACITY,
+                         "rs_unique_keys_noalloc: %lld keys exceed the built-in scratch (at most %d keys per call); "
+                         "split the batch or use rs_unique_keys with caller-provided scratch",
+                         n, RS_UNIQUE_NOALLOC_MAX_KEYS);
+  int dev = 0;
+  RS_CUDA(cudaGetDevice(&dev));
+  RS_REQUIRE(dev >= 0 && dev < kMaxDevices, "rs_unique_keys_noalloc: device index %d not supported", dev);
+  void* base = nullptr;
+  {
+    // One-time set-up per device, with that device current: resolve the device address of the array.
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (g_noalloc_addr[dev] == nullptr) {
+      void* p = nullptr;
+      RS_CUDA(cudaGetSymbolAddress(&p, g_unique_noalloc_scratch));
+      g_noalloc_addr[dev] = p;
+    }
+    base = g_noalloc_addr[dev];
+  }
+  unsigned long long nslots = 2;
+  while (nslots < 2ull * static_cast<unsigned long long>(n)) nslots <<= 1;   // <= kNoAllocSlots by the check above
+  unsigned long long* slots_key = static_cast<unsigned long long*>(base);
+  int* slots_idx = reinterpret_cast<int*>(static_cast<unsigned char*>(base) + kNoAllocSlots * sizeof(unsigned long long));
+  // The array still holds the previous call's keys: clear the slots this call will use (and the counter).
+  unique_clear_kernel<<<grid_for(nslots), 256, 0, stream>>>(slots_key, slots_idx, nslots, count);
+  RS_LAUNCH_CHECK();
+  if (n == 0) return RS_OK;
+  unique_kernel<<<grid_for(n), 256, 0, stream>>>(keys, n, slots_key, slots_idx, nslots - 1, unique_out, inverse, count, status);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
