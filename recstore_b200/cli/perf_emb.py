@@ -1,0 +1,166 @@
+"""Embedding micro-benchmark / differential test driver.
+
+Flags follow the reference's ``perf_emb.py`` (src/executable/perf_emb.py:83-134) and ``test_emb.py``
+(:160-301): ``--num_workers --num_embs --emb_dim --L --batch_size --cache_ratio --log_interval --run_steps
+--emb_choice --backwardMode --backgrad_init --kForwardItersPerStep --nr_background_threads --distribution
+--zipf_alpha``, plus ``--device cpu|cuda`` and ``--diff_test`` (compare every step against a replicated
+``nn.Embedding``, the reference's ``DIFF_TEST`` switch, perf_emb.py:43-44, 373-387).
+
+    python -m recstore_b200.cli.perf_emb --num_workers 2 --device cpu --run_steps 50 --diff_test
+
+Each worker is one process (spawned here); on ``cuda`` worker r uses GPU r.  The loop per step is the
+reference's: sample ids (publishing the lookahead window) -> forward -> loss = weighted sum -> backward ->
+after_backward (cache update, controller step, BlockToStepN).  Prints ``Successfully xmh`` at the end, the
+completion marker the reference's experiment harness greps for (src/kg/scripts/exp_config.py:119-139).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import socket
+import time
+
+
+def parse_args(argv=None):
+    p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    p.add_argument("--num_workers", type=int, default=2)
+    p.add_argument("--num_embs", type=int, default=100_000)
+    p.add_argument("--emb_dim", type=int, default=32)
+    p.add_argument("--L", type=int, default=10)
+    p.add_argument("--with_perf", action="store_true")
+    p.add_argument("--batch_size", type=int, default=5000)
+    p.add_argument("--cache_ratio", type=float, default=0.1)
+    p.add_argument("--log_interval", type=int, default=50)
+    p.add_argument("--run_steps", type=int, default=500)
+    p.add_argument("--emb_choice", default="KnownLocalCachedEmbedding")
+    p.add_argument("--backwardMode", choices=["CppSync", "CppAsync", "CppAsyncV2", "PySync"], default="CppAsyncV2")
+    p.add_argument("--backgrad_init", choices=["cpu", "gpu", "both"], default="both")
+    p.add_argument("--kForwardItersPerStep", type=int, default=1)
+    p.add_argument("--nr_background_threads", type=int, default=4)
+    p.add_argument("--distribution", choices=["uniform", "zipf"], default="zipf")
+    p.add_argument("--zipf_alpha", type=float, default=0.99)
+    p.add_argument("--device", choices=["cpu", "cuda"], default="cpu")
+    p.add_argument("--clr", type=float, default=0.1)
+    p.add_argument("--diff_test", action="store_true")
+    p.add_argument("--max_seconds", type=float, default=90.0)
+    return p.parse_args(argv)
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
+    return p
+
+
+def routine(rank: int, args, port: int, ns: str, out=None):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    if args.device == "cuda":
+        torch.cuda.set_device(rank)
+    dist.init_process_group("nccl" if args.device == "cuda" else "gloo", rank=rank, world_size=args.num_workers)
+    import recstore_b200 as rs
+    from recstore_b200 import ipc
+    from recstore_b200.cache import CacheEmbFactory
+    from recstore_b200.controller import KGCacheControllerWrapperBase, BasePerfSampler, ZipfPerfSampler
+    from recstore_b200.utils import comm
+    from recstore_b200.utils.timer import Timer, Reporter
+    ipc.set_namespace(ns)
+    if rank == 0:
+        KGCacheControllerWrapperBase.BeforeDDPInit()
+    dist.barrier()
+    rs.kvinit()
+    dev = torch.device(f"cuda:{rank}") if args.device == "cuda" else torch.device("cpu")
+    N, D = args.num_embs, args.emb_dim
+
+    def init(t, shape, dtype):
+        t.copy_((torch.arange(shape[0], dtype=dtype) % 1000).unsqueeze(1).expand(shape) * 1e-3)
+    if rank == 0:
+        emb = rs.DistEmbedding(N, D, name="full_emb", init_func=init)
+    dist.barrier()
+    if rank != 0:
+        emb = rs.DistEmbedding(N, D, name="full_emb", init_func=init)
+    cfg = json.dumps({"num_gpus": args.num_workers, "L": args.L, "clr": args.clr, "dim": D, "backwardMode": args.backwardMode,
+                      "nr_background_threads": args.nr_background_threads, "full_emb_capacity": N, "cache_ratio": args.cache_ratio,
+                      "kForwardItersPerStep": args.kForwardItersPerStep})
+    ctrl = KGCacheControllerWrapperBase.FactoryNew("RecStore", cfg, rank, args.num_workers)
+    ctrl.init(emb.get_shm_tensor() if rank == 0 else None)
+    abs_emb = CacheEmbFactory.New(args.emb_choice, emb, {"cache_ratio": args.cache_ratio, "backwardMode": args.backwardMode,
+                                                           "clr": args.clr, "controller": ctrl,
+                                                           "kForwardItersPerStep": args.kForwardItersPerStep,
+                                                           "backgrad_init": args.backgrad_init}, device=dev)
+    golden = gopt = None
+    if args.diff_test:
+        golden = CacheEmbFactory.New("TorchNativeStdEmbDDP", emb, device=dev)
+        gopt = torch.optim.SGD(golden.std_emb.parameters(), lr=args.clr)
+    Smp = ZipfPerfSampler if args.distribution == "zipf" else BasePerfSampler
+    kw = {"alpha": args.zipf_alpha} if args.distribution == "zipf" else {}
+    sampler = Smp(rank, args.L, args.batch_size, N, args.backwardMode, None, seed=1, **kw)
+
+    def publish(step, ids):
+        allids = comm.gather_variable_shape_tensor(ids, 0)
+        if rank == 0 and ctrl.controller is not None:
+            for r, t in enumerate(allids):
+                ctrl.controller.PublishReads(r, step, t)
+    future = [sampler.gen_next_sample() for _ in range(args.L)]
+    for s, ids in enumerate(future):
+        publish(s, ids)
+    t_step = Timer("OneStep")
+    t0 = time.time()
+    worst = 0.0
+    steps_done = 0
+    for step in range(args.run_steps):
+        with t_step:
+            nxt = sampler.gen_next_sample()
+            publish(step + args.L, nxt)
+            future.append(nxt)
+            ids = future.pop(0).to(dev)
+            for _ in range(args.kForwardItersPerStep):
+                out_emb = abs_emb.forward(ids)
+                loss = out_emb.sum() * (rank + 1)
+                loss.backward()
+                if golden is not None:
+                    ref = golden.forward(ids)
+                    worst = max(worst, (out_emb.detach() - ref.detach()).abs().max().item())
+                    gopt.zero_grad()
+                    (ref.sum() * (rank + 1)).backward()
+                    gopt.step()
+            abs_emb.after_backward()
+        steps_done += 1
+        if rank == 0 and (step + 1) % args.log_interval == 0:
+            el = time.time() - t0
+            print(f"step {step + 1}: {el / (step + 1) * 1e3:.2f} ms/step, "
+                  f"{args.batch_size * args.num_workers * (step + 1) / el / 1e6:.3f} Mkeys/s", flush=True)
+        stop = torch.tensor([1 if time.time() - t0 > args.max_seconds else 0])
+        if args.device == "cuda":
+            stop = stop.to(dev)
+        dist.all_reduce(stop)
+        if int(stop.item()) > 0:
+            break
+    ctrl.GraceFullyStopThreads()
+    dist.barrier()
+    if rank == 0:
+        if args.with_perf:
+            print(Reporter.Report())
+        if args.diff_test:
+            print(f"diff_test: worst |cached - golden| = {worst:.3e}")
+        print("Successfully xmh", flush=True)
+    if out is not None:
+        out[rank] = (steps_done, worst)
+    dist.destroy_process_group()
+
+
+def main(argv=None):
+    args = parse_args(argv)
+    import torch.multiprocessing as mp
+    port, ns = _free_port(), f"perf_emb_{os.getpid()}"
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(routine, args=(args, port, ns, out), nprocs=args.num_workers, join=True)
+    if args.diff_test:
+        assert all(v[1] < 1e-3 for v in out.values()), dict(out)
+    return dict(out)
+
+
+if __name__ == "__main__":
+    main()
