@@ -38,10 +38,12 @@ using namespace rs::ptx;
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;               // two warps per TMEM lane quadrant: one scheduler alone cannot hide the epilogue's latencies
+constexpr int kThreads = 64 + kEpiWarps * 32;
 constexpr uint32_t kABytes = BM * BK * 2;  // 16 KiB per stage
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kStageBytes = 4 * 2 * 4096;  // per epilogue warp: output tile + aux tile, 32 rows x 128 B each
+constexpr uint32_t kWarpStage = 2 * 4096 + 256;          // per epilogue warp: output tile + aux tile (32 rows x 128 B each) + 64 bias values
+constexpr uint32_t kStageBytes = kEpiWarps * kWarpStage;
 
 struct GemmArgs {
   int M, N, K;          // logical problem (see modes above); K = reduction length
@@ -92,7 +94,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 128);
+      mbar_init(&tempty[a], kEpiWarps * 32);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -194,7 +196,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       }
     }
   } else {
-    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const int q = warp & 3;            // TMEM lane quadrant this warp may read
+    const int part = (warp - 2) >> 2;  // which half of the column groups this warp of the quadrant's pair takes
+    constexpr int kParts = kEpiWarps / 4;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -210,40 +214,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         // bf16 output staged through shared memory: every thread owns one row of the accumulator, but
         // global memory is touched row-contiguously (4 rows x 128 B per warp instruction) for both the
         // output store and the ReLU-mask load.  16-byte chunks are XOR-swizzled by (row & 7).
-        uint8_t* so = sStage + (warp - 2) * 8192;
+        uint8_t* so = sStage + (warp - 2) * kWarpStage;
         uint8_t* sa = so + 4096;
+        float* sbias = reinterpret_cast<float*>(so + 8192);
         const int lrow = lane >> 3, lchunk = lane & 7;
-        for (int c = 0; c < g.bn / 64; ++c) {
+        for (int c = part; c < g.bn / 64; c += kParts) {
           const int col0 = n0 + c * 64;
           if (col0 >= g.N) break;
+          // Both 32-column halves of the accumulator are requested first; the global loads this group
+          // needs (bias, ReLU mask) are issued while they are in flight.
+          uint32_t r0[32], r1[32];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * g.bn + c * 64);
+          tmem_ld_32x32(taddr, r0);
+          tmem_ld_32x32(taddr + 32, r1);
+          float2 bv = make_float2(0.f, 0.f);
+          if (g.bias != nullptr && col0 + lane * 2 < g.N) bv = __ldg(reinterpret_cast<const float2*>(g.bias + col0) + lane);
           if (g.epi == 2) {
+            uint4 m[8];
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
               const int r = it * 4 + lrow;
               const int grow = m0 + q * 32 + r;
-              uint4 m = make_uint4(0, 0, 0, 0);
+              m[it] = make_uint4(0, 0, 0, 0);
               if (grow < g.M && col0 + lchunk * 8 < g.N)
-                m = __ldg(reinterpret_cast<const uint4*>(g.aux + static_cast<size_t>(grow) * g.ldaux + col0) + lchunk);
-              *reinterpret_cast<uint4*>(sa + r * 128 + ((lchunk ^ (r & 7)) << 4)) = m;
+                m[it] = __ldg(reinterpret_cast<const uint4*>(g.aux + static_cast<size_t>(grow) * g.ldaux + col0) + lchunk);
             }
-            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = it * 4 + lrow;
+              *reinterpret_cast<uint4*>(sa + r * 128 + ((lchunk ^ (r & 7)) << 4)) = m[it];
+            }
           }
+          reinterpret_cast<float2*>(sbias)[lane] = bv;
+          __syncwarp();
+          tmem_ld_wait();
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            uint32_t r[32];
-            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * g.bn + c * 64 + half * 32), r);
-            tmem_ld_wait();
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            const int cb = col0 + half * 32;
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(half == 0 ? r0[j] : r1[j]);
             if (g.bias != nullptr) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
-                if (cb + j < g.N) {
-                  const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + cb + j));
-                  v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
-                }
+                const float4 b = *reinterpret_cast<const float4*>(sbias + half * 32 + j);   // same address in every lane: broadcast
+                v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
               }
             }
             if (g.epi == 1) {
@@ -268,14 +282,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
           }
           __syncwarp();
+          uint4 o[8];
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + lrow;
+            o[it] = *reinterpret_cast<const uint4*>(so + r * 128 + ((lchunk ^ (r & 7)) << 4));
+          }
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int r = it * 4 + lrow;
             const int grow = m0 + q * 32 + r;
-            if (grow < g.M && col0 + lchunk * 8 < g.N) {
-              const uint4 o = *reinterpret_cast<const uint4*>(so + r * 128 + ((lchunk ^ (r & 7)) << 4));
-              *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.D) + static_cast<size_t>(grow) * g.ldd + col0) + lchunk) = o;
-            }
+            if (grow < g.M && col0 + lchunk * 8 < g.N)
+              *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.D) + static_cast<size_t>(grow) * g.ldd + col0) + lchunk) = o[it];
           }
           __syncwarp();
         }
@@ -285,7 +303,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         if (acc == 0) acc_phase ^= 1u;
         continue;
       }
-      for (int c = 0; c < g.bn / 32; ++c) {
+      for (int c = part; c < g.bn / 32; c += kParts) {
         const int col0 = n0 + c * 32;
         if (col0 >= g.N) break;  // uniform across the warp
         uint32_t r[32];
