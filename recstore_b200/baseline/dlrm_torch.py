@@ -43,7 +43,7 @@ class TorchDLRM:
                  num_dense: int = 13, bottom_mlp=(512, 256, 128), top_mlp=(1024, 1024, 512, 256, 1),
                  emb_lr: float = 0.01, emb_eps: float = 1e-10, emb_optimizer: str = "rowwise_adagrad",
                  mlp_lr: float = 0.01, device="cpu", rank: int = 0, world: int = 1, autocast_bf16: bool = False,
-                 seed: int = 0, group=None):
+                 seed: int = 0, group=None, interaction: str = "dot", dcn_layers: int = 3, dcn_rank: int = 512):
         self.table_rows = list(table_rows)
         self.T = len(self.table_rows)
         self.D = emb_dim
@@ -65,7 +65,8 @@ class TorchDLRM:
             self.states[t] = torch.zeros(n, device=self.device)
         g = torch.Generator(device="cpu").manual_seed(seed)
         self.params: Dict[str, torch.Tensor] = {}
-        n_inter = emb_dim + (self.T + 1) * self.T // 2
+        self.interaction = interaction
+        n_inter = (self.T + 1) * emb_dim if interaction == "dcn" else emb_dim + (self.T + 1) * self.T // 2
         kb = [num_dense] + list(bottom_mlp[:-1])
         for i, (k, n) in enumerate(zip(kb, bottom_mlp)):
             self.params[f"bot.{i}.weight"] = (torch.randn(n, k, generator=g) * math.sqrt(2.0 / (n + k))).to(self.device)
@@ -74,6 +75,13 @@ class TorchDLRM:
         for i, (k, n) in enumerate(zip(kt, top_mlp[:-1])):
             self.params[f"top.{i}.weight"] = (torch.randn(n, k, generator=g) * math.sqrt(2.0 / (n + k))).to(self.device)
             self.params[f"top.{i}.bias"] = (torch.randn(n, generator=g) * math.sqrt(1.0 / n)).to(self.device)
+        self.n_cross = dcn_layers if interaction == "dcn" else 0
+        for l in range(self.n_cross):
+            # low-rank cross layer of DCNv2 (torchrec LowRankCrossNet as used by model_zoo/dlrm.py:261-286)
+            self.params[f"crossV.{l}.weight"] = (torch.randn(dcn_rank, n_inter, generator=g) * math.sqrt(2.0 / (dcn_rank + n_inter))).to(self.device)
+            self.params[f"crossV.{l}.bias"] = torch.zeros(dcn_rank, device=self.device)       # unused, kept for a uniform layout
+            self.params[f"crossW.{l}.weight"] = (torch.randn(n_inter, dcn_rank, generator=g) * math.sqrt(2.0 / (dcn_rank + n_inter))).to(self.device)
+            self.params[f"crossW.{l}.bias"] = torch.zeros(n_inter, device=self.device)
         hk = top_mlp[-2]
         self.params["head.weight"] = (torch.randn(hk, generator=g) * math.sqrt(2.0 / (1 + hk))).to(self.device)
         self.params["head.bias"] = torch.randn(1, generator=g).to(self.device)
@@ -132,8 +140,16 @@ class TorchDLRM:
         with torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast):
             x = self._mlp(dense_local, "bot", self.n_bot)
             Tm = torch.cat([x.unsqueeze(1), emb.to(x.dtype)], 1)                 # [Bl, F, D]
-            Z = torch.bmm(Tm, Tm.transpose(1, 2))
-            z = torch.cat([x, Z[:, self.li, self.lj]], 1)
+            if self.interaction == "dcn":
+                x0 = Tm.reshape(Tm.shape[0], -1)
+                z = x0
+                for l in range(self.n_cross):
+                    tl = F.linear(z, self.params[f"crossV.{l}.weight"].to(z.dtype))
+                    u = F.linear(tl, self.params[f"crossW.{l}.weight"].to(z.dtype), self.params[f"crossW.{l}.bias"].to(z.dtype))
+                    z = x0 * u + z
+            else:
+                Z = torch.bmm(Tm, Tm.transpose(1, 2))
+                z = torch.cat([x, Z[:, self.li, self.lj]], 1)
             y = self._mlp(z, "top", self.n_top)
             logit = F.linear(y, self.params["head.weight"].to(y.dtype).unsqueeze(0), self.params["head.bias"].to(y.dtype))
         return logit.float().squeeze(1)
@@ -163,6 +179,9 @@ class TorchDLRM:
                 else:
                     sgd_update(self.tables[t], idx, g, self.emb_lr)
             if self.world > 1:
+                for p in self.params.values():
+                    if p.grad is None:
+                        p.grad = torch.zeros_like(p)
                 flat = torch.cat([p.grad.reshape(-1) for p in self.params.values()])
                 dist.all_reduce(flat, group=self.group)
                 o = 0
@@ -170,7 +189,8 @@ class TorchDLRM:
                     p.grad.copy_(flat[o:o + p.numel()].view_as(p))
                     o += p.numel()
             for p in self.params.values():
-                p.add_(p.grad, alpha=-self.mlp_lr)
+                if p.grad is not None:
+                    p.add_(p.grad, alpha=-self.mlp_lr)
         return loss.detach()
 
     @torch.no_grad()

@@ -178,6 +178,110 @@ __global__ void mse_kernel(const __nv_bfloat16* __restrict__ pred, const float* 
   if ((threadIdx.x & 31) == 0 && l != 0.f) atomicAdd(loss_sum, l);
 }
 
+// ---------------------------------------------------------------- DCNv2 low-rank cross layer, element-wise parts
+// x_next = x0 * u + x_l                      (u = W_l (V_l x_l) + b_l comes from the GEMMs)
+__global__ void __launch_bounds__(256) cross_fwd_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ u,
+                                                        const __nv_bfloat16* __restrict__ xl, __nv_bfloat16* __restrict__ out,
+                                                        long long n8) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(x0) + i), b = __ldg(reinterpret_cast<const uint4*>(u) + i),
+              c = __ldg(reinterpret_cast<const uint4*>(xl) + i);
+  const __nv_bfloat16* pa = reinterpret_cast<const __nv_bfloat16*>(&a);
+  const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&b);
+  const __nv_bfloat16* pc = reinterpret_cast<const __nv_bfloat16*>(&c);
+  uint4 o;
+  __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) po[e] = __float2bfloat16(__bfloat162float(pa[e]) * __bfloat162float(pb[e]) + __bfloat162float(pc[e]));
+  reinterpret_cast<uint4*>(out)[i] = o;
+}
+// dU = dX * x0 ; dx0_acc (+)= dX * u
+__global__ void __launch_bounds__(256) cross_bwd_kernel(const __nv_bfloat16* __restrict__ dx, const __nv_bfloat16* __restrict__ x0,
+                                                        const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ du,
+                                                        float* __restrict__ dx0_acc, long long n8, int accumulate) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(dx) + i), b = __ldg(reinterpret_cast<const uint4*>(x0) + i),
+              c = __ldg(reinterpret_cast<const uint4*>(u) + i);
+  const __nv_bfloat16* pa = reinterpret_cast<const __nv_bfloat16*>(&a);
+  const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&b);
+  const __nv_bfloat16* pc = reinterpret_cast<const __nv_bfloat16*>(&c);
+  uint4 o;
+  __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(&o);
+  float acc[8];
+  if (accumulate) {
+    const float4 p0 = reinterpret_cast<const float4*>(dx0_acc)[2 * i], p1 = reinterpret_cast<const float4*>(dx0_acc)[2 * i + 1];
+    acc[0] = p0.x; acc[1] = p0.y; acc[2] = p0.z; acc[3] = p0.w; acc[4] = p1.x; acc[5] = p1.y; acc[6] = p1.z; acc[7] = p1.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float d = __bfloat162float(pa[e]);
+    po[e] = __float2bfloat16(d * __bfloat162float(pb[e]));
+    acc[e] += d * __bfloat162float(pc[e]);
+  }
+  reinterpret_cast<uint4*>(du)[i] = o;
+  reinterpret_cast<float4*>(dx0_acc)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  reinterpret_cast<float4*>(dx0_acc)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
+// Gradient of the concatenated feature matrix T[B, F, D] (acc fp32 optional + dxb bf16): feature 0 goes to the
+// bottom-MLP gradient (with the ReLU mask of T[:,0]), features 1.. go STRAIGHT INTO THE OWNING RANK'S gradient
+// window through peer pointers, with their squared norms (same contract as the dot-interaction backward).
+struct PushArgs {
+  const float* acc; const __nv_bfloat16* dxb; const __nv_bfloat16* T;
+  int B, F, D;
+  __nv_bfloat16* dx; int dx_ld;
+  void* const* gdst; const int* owner; const int* gcol; long long grow_stride, sample_base;
+  int relu_mask_dx;
+  float* const* ndst; int nstride;
+};
+__global__ void __launch_bounds__(256) push_feature_grads_kernel(const PushArgs a) {
+  const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= static_cast<long long>(a.B) * a.F) return;
+  const int b = static_cast<int>(w / a.F), f = static_cast<int>(w % a.F);
+  const long long base = w * a.D;
+  float sq = 0.f;
+  for (int d = lane * 4; d < a.D; d += 128) {
+    float v[4];
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(a.dxb + base + d));
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+    if (a.acc) {
+      const float4 p = __ldg(reinterpret_cast<const float4*>(a.acc + base + d));
+      v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+    }
+    __nv_bfloat16* dst;
+    if (f == 0) {
+      if (a.relu_mask_dx) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (!(__bfloat162float(a.T[base + d + e]) > 0.f)) v[e] = 0.f;
+      }
+      dst = a.dx + static_cast<long long>(b) * a.dx_ld + d;
+    } else {
+      dst = reinterpret_cast<__nv_bfloat16*>(a.gdst[a.owner[f - 1]]) + (a.sample_base + b) * a.grow_stride + a.gcol[f - 1] + d;
+    }
+    __nv_bfloat162 o0 = __floats2bfloat162_rn(v[0], v[1]), o1 = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&o0);
+    o.y = *reinterpret_cast<uint32_t*>(&o1);
+    *reinterpret_cast<uint2*>(dst) = o;
+    const float2 r0 = __bfloat1622float2(o0), r1 = __bfloat1622float2(o1);
+    sq += r0.x * r0.x + r0.y * r0.y + r1.x * r1.x + r1.y * r1.y;
+  }
+  if (a.ndst && f > 0) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if (lane == 0) a.ndst[a.owner[f - 1]][(a.sample_base + b) * a.nstride + a.gcol[f - 1] / a.D] = sq;
+  }
+}
+
 }  // namespace
 
 // labels == nullptr: inference, only `prob` is written.
@@ -240,6 +344,41 @@ RS_API int rs_mse_fwd_bwd(const void* pred, const float* target, int n, float in
   if (n == 0) return RS_OK;
   mse_kernel<<<(n + 255) / 256, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(pred), target, n, inv_n,
                                                   loss_sum, reinterpret_cast<__nv_bfloat16*>(dpred));
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+RS_API int rs_cross_fwd(const void* x0, const void* u, const void* xl, void* out, long long n, cudaStream_t stream) {
+  RS_REQUIRE(x0 && u && xl && out && n % 8 == 0, "rs_cross_fwd: bad argument (n must be a multiple of 8)");
+  if (n == 0) return RS_OK;
+  cross_fwd_kernel<<<static_cast<unsigned>((n / 8 + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x0), reinterpret_cast<const __nv_bfloat16*>(u),
+      reinterpret_cast<const __nv_bfloat16*>(xl), reinterpret_cast<__nv_bfloat16*>(out), n / 8);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+RS_API int rs_cross_bwd(const void* dx, const void* x0, const void* u, void* du, float* dx0_acc, long long n, int accumulate,
+                        cudaStream_t stream) {
+  RS_REQUIRE(dx && x0 && u && du && dx0_acc && n % 8 == 0, "rs_cross_bwd: bad argument (n must be a multiple of 8)");
+  if (n == 0) return RS_OK;
+  cross_bwd_kernel<<<static_cast<unsigned>((n / 8 + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dx), reinterpret_cast<const __nv_bfloat16*>(x0),
+      reinterpret_cast<const __nv_bfloat16*>(u), reinterpret_cast<__nv_bfloat16*>(du), dx0_acc, n / 8, accumulate);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+RS_API int rs_push_feature_grads(const float* acc, const void* dxb, const void* T, int B, int F, int D, void* dx, int dx_ld,
+                                 void* const* gdst, const int* owner, const int* gcol, long long grow_stride,
+                                 long long sample_base, int relu_mask_dx, void* const* ndst, int nstride, cudaStream_t stream) {
+  RS_REQUIRE(dxb && T && dx && gdst && owner && gcol && D % 4 == 0, "rs_push_feature_grads: bad argument");
+  if (B == 0) return RS_OK;
+  PushArgs a;
+  a.acc = acc; a.dxb = reinterpret_cast<const __nv_bfloat16*>(dxb); a.T = reinterpret_cast<const __nv_bfloat16*>(T);
+  a.B = B; a.F = F; a.D = D; a.dx = reinterpret_cast<__nv_bfloat16*>(dx); a.dx_ld = dx_ld; a.gdst = gdst; a.owner = owner;
+  a.gcol = gcol; a.grow_stride = grow_stride; a.sample_base = sample_base; a.relu_mask_dx = relu_mask_dx;
+  a.ndst = reinterpret_cast<float* const*>(ndst); a.nstride = nstride;
+  const long long warps = static_cast<long long>(B) * F;
+  push_feature_grads_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(a);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

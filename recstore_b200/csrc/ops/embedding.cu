@@ -234,15 +234,40 @@ template <int NC>
 __global__ void __launch_bounds__(256) emb_state_kernel(const EmbBwdArgs a) {
   const float inv_d = 1.f / static_cast<float>(a.D);
   if (a.gnorm) {
+    // One thread per occurrence; equal rows of the block are combined in a shared-memory hash first, so a hot
+    // row costs one global atomic per block instead of one per occurrence.
+    __shared__ long long s_key[kSlots];
+    __shared__ float s_val[kSlots];
+    for (int s = threadIdx.x; s < kSlots; s += blockDim.x) {
+      s_key[s] = -1;
+      s_val[s] = 0.f;
+    }
+    __syncthreads();
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= a.nnz) return;
-    const long long row = a.row_idx[i];
-    if (row < 0 || row >= a.total_rows) return;
-    const long long bag = a.occ2bag ? a.occ2bag[i] : i;
-    const int t = static_cast<int>(bag / a.B);
-    const long long b = bag % a.B;
-    const float w = a.psw ? a.psw[i] : 1.f;
-    atomicAdd(&a.state[row], w * w * a.gnorm[b * a.gnorm_stride + t] * inv_d);
+    if (i < a.nnz) {
+      const long long row = a.row_idx[i];
+      if (row >= 0 && row < a.total_rows) {
+        const long long bag = a.occ2bag ? a.occ2bag[i] : i;
+        const int t = static_cast<int>(bag / a.B);
+        const long long b = bag % a.B;
+        const float w = a.psw ? a.psw[i] : 1.f;
+        const float v = w * w * a.gnorm[b * a.gnorm_stride + t] * inv_d;
+        unsigned s = static_cast<unsigned>(rs::ht_hash(static_cast<unsigned long long>(row))) & (kSlots - 1);
+        for (int p = 0; p < kSlots; ++p) {
+          const long long prev = static_cast<long long>(atomicCAS(reinterpret_cast<unsigned long long*>(&s_key[s]),
+                                                                   static_cast<unsigned long long>(-1ll),
+                                                                   static_cast<unsigned long long>(row)));
+          if (prev == -1 || prev == row) {
+            atomicAdd(&s_val[s], v);
+            break;
+          }
+          s = (s + 1) & (kSlots - 1);
+        }
+      }
+    }
+    __syncthreads();
+    for (int s = threadIdx.x; s < kSlots; s += blockDim.x)
+      if (s_key[s] >= 0) atomicAdd(&a.state[s_key[s]], s_val[s]);
     return;
   }
   const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);

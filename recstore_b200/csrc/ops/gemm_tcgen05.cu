@@ -21,6 +21,7 @@
 //   3  D += acc                                  fp32 atomic add (split reduction)
 //   4  D = acc (+ bias[n])                       fp32 store
 //   5  D = x0[m,n] * (acc + bias[n]) + aux[m,n]  bf16 store (DCNv2 cross update)
+//   6  D = acc + aux[m,n]                        bf16 store (residual add)
 //
 // CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs,
 // warps 2..5 read the accumulator back (one TMEM lane quadrant each).  Two
@@ -345,6 +346,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
               for (int t = 0; t < 8; ++t) v[j + t] = (__bfloat162float(mb[t]) > 0.f) ? v[j + t] : 0.f;
             }
           }
+        } else if (g.epi == 6 && row_ok) {
+          const __nv_bfloat16* a = g.aux + static_cast<size_t>(row) * g.ldaux + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < g.N) {
+              const uint4 ma = __ldg(reinterpret_cast<const uint4*>(a + j));
+              const __nv_bfloat16* pa = reinterpret_cast<const __nv_bfloat16*>(&ma);
+#pragma unroll
+              for (int t = 0; t < 8; ++t) v[j + t] += __bfloat162float(pa[t]);
+            }
+          }
         } else if (g.epi == 5 && row_ok) {
           const __nv_bfloat16* a = g.aux + static_cast<size_t>(row) * g.ldaux + col0;
           const __nv_bfloat16* x = g.x0 + static_cast<size_t>(row) * g.ldx0 + col0;
@@ -481,10 +493,10 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   RS_REQUIRE(A && B && D, "rs_gemm_bf16: null operand");
   RS_REQUIRE(M > 0 && N > 0 && K > 0, "rs_gemm_bf16: empty problem %d %d %d", M, N, K);
   RS_REQUIRE(mode >= 0 && mode <= 2, "rs_gemm_bf16: mode must be 0, 1 or 2");
-  RS_REQUIRE(epi >= 0 && epi <= 5, "rs_gemm_bf16: unknown epilogue %d", epi);
+  RS_REQUIRE(epi >= 0 && epi <= 6, "rs_gemm_bf16: unknown epilogue %d", epi);
   RS_REQUIRE(N % 8 == 0, "rs_gemm_bf16: N (%d) must be a multiple of 8", N);
   RS_REQUIRE(mode != 1 || M % 8 == 0, "rs_gemm_bf16: mode 1 needs M to be a multiple of 8");
-  RS_REQUIRE(epi != 2 || aux, "rs_gemm_bf16: epilogue 2 needs aux");
+  RS_REQUIRE((epi != 2 && epi != 6) || aux, "rs_gemm_bf16: epilogues 2 and 6 need aux");
   RS_REQUIRE(epi != 5 || (aux && x0), "rs_gemm_bf16: epilogue 5 needs aux and x0");
   const bool f32_out = (epi == 3 || epi == 4);
   RS_REQUIRE((ldd * (f32_out ? 4 : 2)) % 16 == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0,

@@ -105,15 +105,12 @@ __global__ void __launch_bounds__(kWarps * 32) interaction_fwd_kernel(const __nv
   __syncwarp();
   const int nvalid = D + F * (F - 1) / 2;
   __nv_bfloat16* dst = out + static_cast<size_t>(b) * out_ld;
-  // out_ld is a multiple of 8: 16-byte stores, zero fill past nvalid.
+  // zero the padding inside the last 16-byte group, then copy whole groups; groups past nvalid are zeros
+  for (int idx = nvalid + lane; idx < ((nvalid + 7) & ~7); idx += 32) o[idx] = __float2bfloat16(0.f);
+  __syncwarp();
+  const int nfull = (nvalid + 7) >> 3;
   for (int v = lane; v < (out_ld >> 3); v += 32) {
-    uint4 x;
-    __nv_bfloat16* xe = reinterpret_cast<__nv_bfloat16*>(&x);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int idx = v * 8 + e;
-      xe[e] = idx < nvalid ? o[idx] : __float2bfloat16(0.f);
-    }
+    const uint4 x = v < nfull ? *reinterpret_cast<const uint4*>(o + v * 8) : make_uint4(0, 0, 0, 0);
     *(reinterpret_cast<uint4*>(dst) + v) = x;
   }
 }
@@ -134,134 +131,167 @@ struct InterBwdArgs {
   int nstride;
 };
 
-constexpr int kWarpsBwd = 3;  // 15.9 KB of shared memory per warp: 3 warps stay under the 48 KB static limit
+constexpr int kWarpsBwd = 6;  // 17 KB of shared memory per warp: two CTAs (12 warps) per SM
 constexpr int kOutLd = 72;    // staging row: 64 columns + 8 pad (144 B, 16-byte aligned, conflict-free)
+constexpr int kDoutMax = kMaxD + kMaxF * (kMaxF - 1) / 2 + 16;
+// per-warp shared memory of the backward kernel (bytes): T tile, symmetric dZ, output staging, dOut row
+constexpr int kBwdWarpBytes = 32 * kLd * 2 + 32 * 40 * 2 + 32 * kOutLd * 2 + kDoutMax * 2;
 
+__device__ __forceinline__ void stmatrix_x4(void* p, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Persistent warps: every warp walks samples b = first, first + stride, ...  Everything that does not depend on
+// the sample (pair -> (i, j) table, destination pointers of the rows a lane stores) is set up once.
 __global__ void __launch_bounds__(kWarpsBwd * 32) interaction_bwd_kernel(const InterBwdArgs a) {
-  __shared__ __align__(16) __nv_bfloat16 sT[kWarpsBwd][32 * kLd];
-  __shared__ __align__(16) __nv_bfloat16 sS[kWarpsBwd][32 * 40];  // symmetric dZ, padded rows of 40
-  __shared__ __align__(16) __nv_bfloat16 sO[kWarpsBwd][32 * kOutLd];
+  extern __shared__ __align__(16) unsigned char smem_bwd[];
+  __shared__ unsigned short s_ij[kMaxF * (kMaxF - 1) / 2];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x * kWarpsBwd + warp;
-  if (b >= a.B) return;
   const int F = a.F, D = a.D;
-  __nv_bfloat16* t = sT[warp];
-  __nv_bfloat16* s = sS[warp];
-  __nv_bfloat16* o = sO[warp];
-  load_tile(t, a.T + static_cast<size_t>(b) * F * D, F, D, lane);
-  const __nv_bfloat16* dout = a.dout + static_cast<size_t>(b) * a.dout_ld;
-  for (int i = lane; i < 32 * 40 / 8; i += 32) reinterpret_cast<uint4*>(s)[i] = make_uint4(0, 0, 0, 0);
-  __syncwarp();
   const int npairs = F * (F - 1) / 2;
-  for (int p = lane; p < npairs; p += 32) {
-    // invert p = i(i-1)/2 + j
+  for (int p = threadIdx.x; p < npairs; p += blockDim.x) {
     int i = static_cast<int>((1.f + sqrtf(1.f + 8.f * p)) * 0.5f);
     while (i * (i - 1) / 2 > p) --i;
     while ((i + 1) * i / 2 <= p) ++i;
-    const int j = p - i * (i - 1) / 2;
-    const __nv_bfloat16 v = dout[D + p];
-    s[i * 40 + j] = v;
-    s[j * 40 + i] = v;
+    s_ij[p] = static_cast<unsigned short>((i << 8) | (p - i * (i - 1) / 2));
   }
-  __syncwarp();
-
-  // dT[32 x D] = S[32 x 32] . T[32 x D]; two k-steps; n in halves of 64 columns.
-  uint32_t sa[2][2][4];  // [mt][ks]
-#pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-    for (int ks = 0; ks < 2; ++ks)
-      ldmatrix_x4(sa[mt][ks], s + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 40 + ks * 16 + (lane >> 4) * 8);
+  unsigned char* base = smem_bwd + warp * kBwdWarpBytes;
+  __nv_bfloat16* t = reinterpret_cast<__nv_bfloat16*>(base);
+  __nv_bfloat16* s = t + 32 * kLd;
+  __nv_bfloat16* o = s + 32 * 40;
+  __nv_bfloat16* sd = o + 32 * kOutLd;
+  for (int i = lane; i < 32 * 40 / 8; i += 32) reinterpret_cast<uint4*>(s)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
 
   const int g = lane >> 2, q = lane & 3;
-  const int orow = lane >> 3, ochunk = lane & 7;  // coalesced store phase: 4 rows x 8 chunks of 16 B
-  float rownorm[8];
+  const int orow = lane >> 3, ochunk = lane & 7;  // store phase: 4 rows x 8 chunks of 16 B per instruction
+  // destination of the rows this lane stores (row i = it * 4 + orow), without the per-sample offset
+  __nv_bfloat16* dst_base[8];
+  float* nrm_base[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) rownorm[i] = 0.f;
-
-  for (int n0 = 0; n0 < D; n0 += 64) {
-    float acc[2][8][4];
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
-#pragma unroll
-      for (int np = 0; np < 4; ++np) {  // pairs of n-tiles
-        if (n0 + np * 16 >= D) continue;
-        uint32_t bb[4];
-        ldmatrix_x4_trans(bb, t + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kLd + n0 + np * 16 + (lane >> 4) * 8);
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-          mma_bf16(acc[mt][np * 2], sa[mt][ks], bb[0], bb[1]);
-          mma_bf16(acc[mt][np * 2 + 1], sa[mt][ks], bb[2], bb[3]);
-        }
-      }
+  for (int it = 0; it < 8; ++it) {
+    const int i = it * 4 + orow;
+    dst_base[it] = nullptr;
+    nrm_base[it] = nullptr;
+    if (i == 0) {
+      dst_base[it] = a.dx + ochunk * 8;
+    } else if (i < F) {
+      const int f = i - 1;
+      dst_base[it] = reinterpret_cast<__nv_bfloat16*>(a.gdst[a.owner[f]]) + a.sample_base * a.grow_stride + a.gcol[f] + ochunk * 8;
+      if (a.ndst) nrm_base[it] = a.ndst[a.owner[f]] + a.sample_base * a.nstride + a.gcol[f] / D;
     }
-    // fragments -> staging tile (bf16)
+  }
+  const int dvec = (a.dout_ld * 2) >> 4;  // uint4 per dOut row
+
+  for (int b = blockIdx.x * kWarpsBwd + warp; b < a.B; b += gridDim.x * kWarpsBwd) {
+    load_tile(t, a.T + static_cast<size_t>(b) * F * D, F, D, lane);
+    const __nv_bfloat16* dout = a.dout + static_cast<size_t>(b) * a.dout_ld;
+    for (int v = lane; v < dvec; v += 32) reinterpret_cast<uint4*>(sd)[v] = __ldg(reinterpret_cast<const uint4*>(dout) + v);
+    __syncwarp();
+    for (int p = lane; p < npairs; p += 32) {
+      const int ij = s_ij[p];
+      const int i = ij >> 8, j = ij & 255;
+      const __nv_bfloat16 v = sd[D + p];
+      s[i * 40 + j] = v;
+      s[j * 40 + i] = v;
+    }
+    __syncwarp();
+
+    uint32_t sa[2][2][4];  // [mt][ks]
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int cl = nt * 8 + q * 2;  // column inside the half
-        const int col = n0 + cl;
+      for (int ks = 0; ks < 2; ++ks)
+        ldmatrix_x4(sa[mt][ks], s + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 40 + ks * 16 + (lane >> 4) * 8);
+
+    float rownorm[8];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int i = mt * 16 + g + h * 8;
-          float v0 = acc[mt][nt][h * 2], v1 = acc[mt][nt][h * 2 + 1];
-          if (i == 0 && col < D) {
-            v0 += __bfloat162float(dout[col]);
-            v1 += __bfloat162float(dout[col + 1]);
+    for (int i = 0; i < 8; ++i) rownorm[i] = 0.f;
+
+    for (int n0 = 0; n0 < D; n0 += 64) {
+      float acc[2][8][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          if (n0 + np * 16 >= D) continue;
+          uint32_t bb[4];
+          ldmatrix_x4_trans(bb, t + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kLd + n0 + np * 16 + (lane >> 4) * 8);
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            mma_bf16(acc[mt][np * 2], sa[mt][ks], bb[0], bb[1]);
+            mma_bf16(acc[mt][np * 2 + 1], sa[mt][ks], bb[2], bb[3]);
+          }
+        }
+      }
+      // row 0 (feature 0): + dOut[0:D], ReLU mask.  Row 0 lives in lanes with g == 0, m-tile 0, elements 0 and 1.
+      if (g == 0) {
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          const int col = n0 + nt * 8 + q * 2;
+          if (col < D) {
+            float v0 = acc[0][nt][0] + __bfloat162float(sd[col]);
+            float v1 = acc[0][nt][1] + __bfloat162float(sd[col + 1]);
             if (a.relu_mask_dx) {
               if (!(__bfloat162float(t[col]) > 0.f)) v0 = 0.f;
               if (!(__bfloat162float(t[col + 1]) > 0.f)) v1 = 0.f;
             }
+            acc[0][nt][0] = v0;
+            acc[0][nt][1] = v1;
           }
-          *reinterpret_cast<__nv_bfloat162*>(o + i * kOutLd + cl) = __floats2bfloat162_rn(v0, v1);
         }
       }
-    __syncwarp();
-    // staging tile -> global, 16 bytes per lane, 4 rows per instruction
+      // fragments -> staging tile: one stmatrix.x4 per (m-tile, pair of n-tiles)
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int i = it * 4 + orow;
-      const int col = n0 + ochunk * 8;
-      if (i < F && col < D) {
-        const uint4 v = *reinterpret_cast<const uint4*>(o + i * kOutLd + ochunk * 8);
-        const __nv_bfloat16* ve = reinterpret_cast<const __nv_bfloat16*>(&v);
-        float sq = 0.f;
+      for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float f = __bfloat162float(ve[e]);
-          sq += f * f;
+        for (int np = 0; np < 4; ++np) {
+          __nv_bfloat16* dstm = o + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kOutLd + (np * 2 + (lane >> 4)) * 8;
+          stmatrix_x4(dstm, pack2(acc[mt][np * 2][0], acc[mt][np * 2][1]), pack2(acc[mt][np * 2][2], acc[mt][np * 2][3]),
+                      pack2(acc[mt][np * 2 + 1][0], acc[mt][np * 2 + 1][1]), pack2(acc[mt][np * 2 + 1][2], acc[mt][np * 2 + 1][3]));
         }
-        rownorm[it] += sq;
-        __nv_bfloat16* dst;
-        if (i == 0) {
-          dst = a.dx + static_cast<size_t>(b) * a.dx_ld + col;
-        } else {
-          const int f = i - 1;
-          dst = reinterpret_cast<__nv_bfloat16*>(a.gdst[a.owner[f]]) + (a.sample_base + b) * a.grow_stride + a.gcol[f] + col;
+      __syncwarp();
+      // staging tile -> global, 16 bytes per lane, 4 rows per instruction
+      if (n0 + ochunk * 8 < D) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          if (dst_base[it] == nullptr) continue;
+          const int i = it * 4 + orow;
+          const uint4 v = *reinterpret_cast<const uint4*>(o + i * kOutLd + ochunk * 8);
+          const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&v);
+          float sq = 0.f;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f2 = __bfloat1622float2(vp[e]);
+            sq += f2.x * f2.x + f2.y * f2.y;
+          }
+          rownorm[it] += sq;
+          const long long off = (i == 0) ? static_cast<long long>(b) * a.dx_ld : static_cast<long long>(b) * a.grow_stride;
+          *reinterpret_cast<uint4*>(dst_base[it] + off + n0) = v;
         }
-        *reinterpret_cast<uint4*>(dst) = v;
       }
+      __syncwarp();
     }
-    __syncwarp();
-  }
-  if (a.ndst) {
+    if (a.ndst) {
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      float sq = rownorm[it];
-      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
-      sq += __shfl_xor_sync(0xffffffffu, sq, 4);
-      const int i = it * 4 + orow;
-      if (ochunk == 0 && i >= 1 && i < F) {
-        const int f = i - 1;
-        a.ndst[a.owner[f]][(a.sample_base + b) * a.nstride + a.gcol[f] / D] = sq;
+      for (int it = 0; it < 8; ++it) {
+        float sq = rownorm[it];
+        sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+        if (ochunk == 0 && nrm_base[it] != nullptr) nrm_base[it][static_cast<long long>(b) * a.nstride] = sq;
       }
     }
   }
@@ -295,7 +325,16 @@ RS_API int rs_interaction_backward(const void* T, const void* dout, int B, int F
   a.gdst = gdst; a.owner = owner; a.gcol = gcol; a.grow_stride = grow_stride; a.sample_base = sample_base;
   a.relu_mask_dx = relu_mask_dx;
   a.ndst = reinterpret_cast<float* const*>(ndst); a.nstride = nstride;
-  interaction_bwd_kernel<<<(B + kWarpsBwd - 1) / kWarpsBwd, kWarpsBwd * 32, 0, stream>>>(a);
+  RS_REQUIRE(dout_ld % 8 == 0 && dout_ld <= kDoutMax, "rs_interaction_backward: dout_ld=%d must be a multiple of 8, <= %d", dout_ld, kDoutMax);
+  const size_t smem = static_cast<size_t>(kWarpsBwd) * kBwdWarpBytes;
+  static bool attr_done = false;
+  if (!attr_done) {
+    RS_CUDA(cudaFuncSetAttribute(interaction_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    attr_done = true;
+  }
+  int grid = (B + kWarpsBwd - 1) / kWarpsBwd;
+  if (grid > 148 * 4) grid = 148 * 4;   // persistent: warps loop over the samples
+  interaction_bwd_kernel<<<grid, kWarpsBwd * 32, smem, stream>>>(a);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

@@ -52,6 +52,9 @@ class DLRMConfig:
     seed: int = 0
     use_cuda_graph: bool = True
     emb_init: str = "uniform"                    # U(+-sqrt(1/n)) as in the reference, or "normal"
+    interaction: str = "dot"                     # "dot" (DLRM) or "dcn" (DLRM-DCNv2: low-rank cross network)
+    dcn_layers: int = 3
+    dcn_rank: int = 512
 
     def __post_init__(self):
         if self.hotness is None:
@@ -109,7 +112,9 @@ class DLRM:
         self.T = len(cfg.table_rows)
         self.D = cfg.emb_dim
         self.F = self.T + 1
-        assert self.F <= 32, "dot interaction kernel handles up to 31 embedding features"
+        self.dcn = cfg.interaction == "dcn"
+        assert cfg.interaction in ("dot", "dcn")
+        assert self.dcn or self.F <= 32, "dot interaction kernel handles up to 31 embedding features"
         # ---- table placement: round robin by table index
         self.owner = [t % self.world for t in range(self.T)]
         self.local_tables = [t for t in range(self.T) if self.owner[t] == self.rank]
@@ -174,14 +179,24 @@ class DLRM:
 
         # ---- dense parameters (flat fp32 master / grad / reduced buffers)
         self.Kin0 = _round_up(cfg.num_dense, 64)
-        self.n_inter = self.D + self.F * (self.F - 1) // 2
+        self.n_inter = self.F * self.D if self.dcn else self.D + self.F * (self.F - 1) // 2
         self.Kz = _round_up(self.n_inter, 64)
+        assert not self.dcn or self.Kz == self.n_inter, "DCN needs (1 + tables) * dim to be a multiple of 64"
         dims_b = [(cfg.num_dense, self.Kin0)] + [(n, n) for n in cfg.bottom_mlp[:-1]]
         self.bot: List[_Layer] = [_Layer(n, k, kp) for (k, kp), n in zip(dims_b, cfg.bottom_mlp)]
         dims_t = [(self.n_inter, self.Kz)] + [(n, n) for n in cfg.top_mlp[:-2]]
         self.top: List[_Layer] = [_Layer(n, k, kp) for (k, kp), n in zip(dims_t, cfg.top_mlp[:-1])]
         self.head_K = cfg.top_mlp[-2]
-        layers = self.bot + self.top
+        # DCNv2 low-rank cross layers: x_{l+1} = x0 * (W_l (V_l x_l) + b_l) + x_l, V_l [rank, in], W_l [in, rank]
+        self.crossV: List[_Layer] = []
+        self.crossW: List[_Layer] = []
+        if self.dcn:
+            r = cfg.dcn_rank
+            assert r % 64 == 0
+            self.crossV = [_Layer(r, self.n_inter, self.n_inter) for _ in range(cfg.dcn_layers)]
+            self.crossW = [_Layer(self.n_inter, r, r) for _ in range(cfg.dcn_layers)]
+        layers = self.bot + self.top + self.crossV + self.crossW
+        self.layers = layers
         off = 0
         w_off = []
         for L in layers:
@@ -216,6 +231,10 @@ class DLRM:
             L.wt = torch.zeros(L.Kp, L.N, **bf)
             w0 = torch.randn(L.N, L.K, generator=g) * math.sqrt(2.0 / (L.N + L.K))
             b0 = torch.randn(L.N, generator=g) * math.sqrt(1.0 / L.N)
+            if L in self.crossV:
+                b0.zero_()                       # V has no bias
+            if L in self.crossW:
+                b0.zero_()                       # cross bias starts at zero (torchrec LowRankCrossNet)
             L.w[:, :L.K].copy_(w0)
             L.b.copy_(b0)
         self.head_w = self.master[head_w_off:head_w_off + self.head_K]
@@ -235,6 +254,15 @@ class DLRM:
         self.d_act_t = [torch.empty(Bl, L.N, **bf) for L in self.top]
         self.d_z = torch.empty(Bl, self.Kz, **bf)
         self.d_act_b = [torch.empty(Bl, L.N, **bf) for L in self.bot]             # d_h1, d_h2, d_h3
+        if self.dcn:
+            nl, r = cfg.dcn_layers, cfg.dcn_rank
+            self.cx = [self.Tbuf] + [torch.empty(Bl, self.n_inter, **bf) for _ in range(nl - 1)] + [self.z]   # x_0 .. x_L
+            self.ct = [torch.empty(Bl, r, **bf) for _ in range(nl)]                    # V_l x_l
+            self.cu = [torch.empty(Bl, self.n_inter, **bf) for _ in range(nl)]         # W_l t_l + b_l
+            self.c_du = torch.empty(Bl, self.n_inter, **bf)
+            self.c_dt = torch.empty(Bl, r, **bf)
+            self.c_dx = [self.d_z, torch.empty(Bl, self.n_inter, **bf)]                # ping-pong dX_l
+            self.c_dx0 = torch.empty(Bl, self.n_inter, **f32)
         self.prob = torch.empty(Bl, **f32)
 
         # ---- double-buffered inputs, loss
@@ -268,7 +296,7 @@ class DLRM:
         F_.gemm_bf16(a, a, o32, mode=1, epi=F_.EPI_ATOMIC_F32, status=self.ctx.status)
 
     def _refresh_bf16(self):
-        for L in self.bot + self.top:
+        for L in self.layers:
             L.wb.copy_(L.w)
             L.wt.copy_(L.w.t())
 
@@ -306,7 +334,15 @@ class DLRM:
             x = out
         if self.world > 1:
             self.ctx.wait(CH_FWD); self._count()
-        F_.interaction_forward(self.Tbuf, self.Bl, self.F, self.D, self.z); self._count()
+        if self.dcn:
+            for l in range(len(self.crossV)):
+                V, W = self.crossV[l], self.crossW[l]
+                F_.gemm_bf16(self.cx[l], V.wb, self.ct[l], mode=0, epi=F_.EPI_NONE, status=st)
+                F_.gemm_bf16(self.ct[l], W.wb, self.cu[l], mode=0, epi=F_.EPI_NONE, bias=W.b, status=st)
+                F_.cross_fwd(self.Tbuf, self.cu[l], self.cx[l], self.cx[l + 1])
+                self._count(3)
+        else:
+            F_.interaction_forward(self.Tbuf, self.Bl, self.F, self.D, self.z); self._count()
         x = self.z
         for i, L in enumerate(self.top):
             F_.gemm_bf16(x, L.wb, self.act_t[i], mode=0, epi=F_.EPI_RELU, bias=L.b, status=st); self._count()
@@ -334,9 +370,26 @@ class DLRM:
                 F_.gemm_bf16(dy, L.wt, self.d_z, mode=0, epi=F_.EPI_NONE, status=st)
             self._count()
         # ---- interaction backward: dense part stays, embedding gradients go to their owners
-        F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
-                                self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
-                                relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax)
+        if self.dcn:
+            dx = self.c_dx[0]                                     # dX_L from the over-arch
+            for l in range(len(self.crossV) - 1, -1, -1):
+                V, W = self.crossV[l], self.crossW[l]
+                nxt = self.c_dx[(len(self.crossV) - l) & 1]
+                F_.cross_bwd(dx, self.Tbuf, self.cu[l], self.c_du, self.c_dx0, accumulate=(l != len(self.crossV) - 1))
+                F_.colsum_bf16(self.c_du, W.gb)
+                F_.gemm_bf16(self.c_du, self.ct[l], W.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st)
+                F_.gemm_bf16(self.c_du, W.wt, self.c_dt, mode=0, epi=F_.EPI_NONE, status=st)
+                F_.gemm_bf16(self.c_dt, self.cx[l], V.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st)
+                F_.gemm_bf16(self.c_dt, V.wt, nxt, mode=0, epi=F_.EPI_ADD, aux=dx, status=st)
+                dx = nxt
+                self._count(6)
+            F_.push_feature_grads(self.c_dx0, dx, self.Tbuf, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
+                                  self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl, relu_mask_dx=True,
+                                  ndst_table=self.ndst_table, nstride=self.Tmax)
+        else:
+            F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
+                                    self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
+                                    relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax)
         self._count()
         if self.world > 1:
             self.ctx.signal(CH_BWD); self._count()
@@ -366,7 +419,7 @@ class DLRM:
             self.ctx.signal(CH_REDUCED); self.ctx.wait(CH_REDUCED)
             self._count(5)
         solo = self.world == 1
-        for L in self.bot + self.top:
+        for L in self.layers:
             F_.dense_sgd(L.w, L.rw, c.mlp_lr, L.wb, L.wt, zero_grad=solo); self._count()
         F_.vec_sgd(self.master[self.tail_off:], self.reduced[self.tail_off:], c.mlp_lr, zero_grad=solo); self._count()
         if not solo:
@@ -451,7 +504,7 @@ class DLRM:
     # ------------------------------------------------------------------ state access (tests, checkpoints)
     def dense_state(self) -> Dict[str, torch.Tensor]:
         out = {}
-        for name, Ls in (("bot", self.bot), ("top", self.top)):
+        for name, Ls in (("bot", self.bot), ("top", self.top), ("crossV", self.crossV), ("crossW", self.crossW)):
             for i, L in enumerate(Ls):
                 out[f"{name}.{i}.weight"] = L.w[:, :L.K].clone()
                 out[f"{name}.{i}.bias"] = L.b.clone()
@@ -460,7 +513,7 @@ class DLRM:
         return out
 
     def load_dense_state(self, sd: Dict[str, torch.Tensor]) -> None:
-        for name, Ls in (("bot", self.bot), ("top", self.top)):
+        for name, Ls in (("bot", self.bot), ("top", self.top), ("crossV", self.crossV), ("crossW", self.crossW)):
             for i, L in enumerate(Ls):
                 L.w.zero_()
                 L.w[:, :L.K].copy_(sd[f"{name}.{i}.weight"])

@@ -13,7 +13,7 @@ import torch
 from .. import _lib
 from .._lib import call, ptr, stream_ptr
 
-EPI_NONE, EPI_RELU, EPI_RELU_MASK, EPI_ATOMIC_F32, EPI_F32, EPI_CROSS = range(6)
+EPI_NONE, EPI_RELU, EPI_RELU_MASK, EPI_ATOMIC_F32, EPI_F32, EPI_CROSS, EPI_ADD = range(7)
 
 
 def _need_cuda(*ts):
@@ -145,3 +145,21 @@ def mse_fwd_bwd(pred, target, loss_sum, dpred=None) -> None:
 
 def allreduce_push(grads_table, reduced_table, world: int, rank: int, n: int, scale: float = 1.0) -> None:
     call("rs_allreduce_push", ptr(grads_table), ptr(reduced_table), world, rank, n, scale, stream_ptr())
+
+
+def cross_fwd(x0, u, xl, out) -> None:
+    """DCNv2 cross update ``out = x0 * u + xl`` (bf16, element-wise)."""
+    call("rs_cross_fwd", ptr(x0), ptr(u), ptr(xl), ptr(out), out.numel(), stream_ptr())
+
+
+def cross_bwd(dx, x0, u, du, dx0_acc, accumulate: bool) -> None:
+    """``du = dx * x0`` (bf16) and ``dx0_acc (+)= dx * u`` (fp32)."""
+    call("rs_cross_bwd", ptr(dx), ptr(x0), ptr(u), ptr(du), ptr(dx0_acc), dx.numel(), 1 if accumulate else 0, stream_ptr())
+
+
+def push_feature_grads(acc, dxb, T, B: int, F: int, D: int, dx, gdst_table, owner, gcol, grow_stride: int, sample_base: int,
+                       relu_mask_dx: bool = True, ndst_table=None, nstride: int = 0) -> None:
+    """Splits the gradient of the feature matrix ``[B, F, D]`` (``acc`` fp32, optional, plus ``dxb`` bf16): feature 0 to
+    ``dx``, features 1.. through the owners' peer pointers, with squared norms (see :func:`interaction_backward`)."""
+    call("rs_push_feature_grads", ptr(acc), ptr(dxb), ptr(T), B, F, D, ptr(dx), dx.stride(0), ptr(gdst_table), ptr(owner),
+         ptr(gcol), grow_stride, sample_base, 1 if relu_mask_dx else 0, ptr(ndst_table), nstride, stream_ptr())

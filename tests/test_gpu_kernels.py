@@ -353,3 +353,51 @@ def test_bounded_wait_times_out_without_hanging(dev):
     assert "wait_timeout" in str(e.value)
     assert torch.ones(8, device=dev).sum().item() == 8
     ctx.check_status()          # status was reset
+
+
+def test_dcn_step_matches_torch_oracle(dev):
+    """DLRM-DCNv2 (low-rank cross network instead of the dot interaction) against the fp32 oracle."""
+    from recstore_b200.models.dlrm import DLRM, DLRMConfig
+    from recstore_b200.baseline.dlrm_torch import TorchDLRM, rowwise_adagrad_update
+    from recstore_b200.utils.data import DLRMBatchSource
+    rows = [1000, 37, 5000, 12, 300, 20000, 64]
+    hot = [1, 2, 1, 3, 1, 1, 5]
+    B, D = 512, 64
+    kw = dict(emb_dim=D, bottom_mlp=(128, D), top_mlp=(256, 128, 1))
+    cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=0.05, mlp_lr=0.02, seed=5, use_cuda_graph=True,
+                     interaction="dcn", dcn_layers=3, dcn_rank=64, **kw)
+    eng = DLRM(cfg)
+    ora = TorchDLRM(rows, B, hotness=hot, emb_lr=0.05, mlp_lr=0.02, device=dev, seed=5, interaction="dcn", dcn_layers=3,
+                    dcn_rank=64, **kw)
+    with torch.no_grad():
+        for k, v in eng.dense_state().items():
+            ora.params[k].copy_(v.view_as(ora.params[k]))
+        for t in range(len(rows)):
+            ora.tables[t].copy_(eng.table_weight(t))
+    src = DLRMBatchSource(rows, hot, B, alpha=1.2, seed=9)
+    dense0 = {k: v.clone() for k, v in eng.dense_state().items()}
+    losses = []
+    for step in range(10):
+        b = src.next()
+        W0 = [eng.table_weight(t).clone() for t in range(len(rows))]
+        S0 = [eng.table_state(t).clone() for t in range(len(rows))]
+        l_ref = ora.train_step(b.dense, b.ids, b.labels).item()
+        l = eng.train_step(eng.make_pinned_batch(b.dense, b.ids, b.labels))
+        losses.append((l, l_ref))
+        G = eng.Gwin.view(torch.bfloat16, (B, eng.grow_stride)).view(B, eng.Tmax, eng.D).float()
+        for t in range(len(rows)):
+            idx = b.ids[t].to(dev).view(-1)
+            g = G[:, t].repeat_interleave(hot[t], 0) if hot[t] > 1 else G[:, t]
+            rowwise_adagrad_update(W0[t], S0[t], idx, g, 0.05, 1e-10)
+            assert _rel_err(eng.table_weight(t), W0[t]) < 2e-3, (step, t)
+        if step == 0:
+            assert abs(l - l_ref) < 3e-3 * max(1.0, abs(l_ref)), (l, l_ref)
+            sd = eng.dense_state()
+            for k, v in sd.items():
+                d_ref = ora.params[k].detach().view_as(v) - dense0[k]
+                if d_ref.abs().sum() == 0:
+                    continue
+                assert _rel_err(v - dense0[k], d_ref) < 0.2, (k, _rel_err(v - dense0[k], d_ref))
+    eng.check()
+    for l, l_ref in losses:
+        assert abs(l - l_ref) < 4e-2 * max(1.0, abs(l_ref)), losses
