@@ -43,7 +43,7 @@ constexpr int kEpiWarps = 8;               // two warps per TMEM lane quadrant: 
 constexpr int kThreads = 64 + kEpiWarps * 32;
 constexpr uint32_t kABytes = BM * BK * 2;  // 16 KiB per stage
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kWarpStage = 2 * 4096 + 256;          // per epilogue warp: output tile + aux tile (32 rows x 128 B each) + 64 bias values
+constexpr uint32_t kWarpStage = 4096 + 256;              // per epilogue warp: output tile (32 rows x 128 B) + 64 bias values
 constexpr uint32_t kStageBytes = kEpiWarps * kWarpStage;
 
 struct GemmArgs {
@@ -59,6 +59,7 @@ struct GemmArgs {
   const float* bias;
   const __nv_bfloat16* aux;
   const __nv_bfloat16* x0;
+  float* colsum;        // optional: colsum[n] += sum over rows of the bf16 output (bias gradient of the consumer)
   unsigned long long* status;
 };
 
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_raw;   // the kernel has no static shared memory: the dynamic window starts 1024-byte aligned (checked below)
   const int stages = g.stages;
   const uint32_t b_bytes = static_cast<uint32_t>(g.bn) * BK * 2;
   uint8_t* sA = smem;
@@ -88,6 +89,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  if ((smem_u32(smem_raw) & 1023u) != 0u) {   // swizzled TMA tiles need 1024-byte aligned bases
+    if (threadIdx.x == 0 && g.status) atomicOr(g.status, (unsigned long long)RS_DEV_BAD_ARG);
+    return;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full[s], 1);
@@ -216,8 +221,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         // global memory is touched row-contiguously (4 rows x 128 B per warp instruction) for both the
         // output store and the ReLU-mask load.  16-byte chunks are XOR-swizzled by (row & 7).
         uint8_t* so = sStage + (warp - 2) * kWarpStage;
-        uint8_t* sa = so + 4096;
-        float* sbias = reinterpret_cast<float*>(so + 8192);
+        float* sbias = reinterpret_cast<float*>(so + 4096);
         const int lrow = lane >> 3, lchunk = lane & 7;
         for (int c = part; c < g.bn / 64; c += kParts) {
           const int col0 = n0 + c * 64;
@@ -230,20 +234,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           tmem_ld_32x32(taddr + 32, r1);
           float2 bv = make_float2(0.f, 0.f);
           if (g.bias != nullptr && col0 + lane * 2 < g.N) bv = __ldg(reinterpret_cast<const float2*>(g.bias + col0) + lane);
+          const bool col_ok = col0 + lchunk * 8 < g.N;
+          uint4 m[8];   // ReLU mask source, row-contiguous like the store phase: rows it*4+lrow, 16-byte chunk lchunk
           if (g.epi == 2) {
-            uint4 m[8];
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
-              const int r = it * 4 + lrow;
-              const int grow = m0 + q * 32 + r;
+              const int grow = m0 + q * 32 + it * 4 + lrow;
               m[it] = make_uint4(0, 0, 0, 0);
-              if (grow < g.M && col0 + lchunk * 8 < g.N)
+              if (grow < g.M && col_ok)
                 m[it] = __ldg(reinterpret_cast<const uint4*>(g.aux + static_cast<size_t>(grow) * g.ldaux + col0) + lchunk);
-            }
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-              const int r = it * 4 + lrow;
-              *reinterpret_cast<uint4*>(sa + r * 128 + ((lchunk ^ (r & 7)) << 4)) = m[it];
             }
           }
           reinterpret_cast<float2*>(sbias)[lane] = bv;
@@ -268,12 +267,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               const int chunk = half * 4 + (j >> 3);
-              if (g.epi == 2) {
-                const uint4 m = *reinterpret_cast<const uint4*>(sa + lane * 128 + ((chunk ^ (lane & 7)) << 4));
-                const __nv_bfloat16* mb = reinterpret_cast<const __nv_bfloat16*>(&m);
-#pragma unroll
-                for (int t = 0; t < 8; ++t) v[j + t] = (__bfloat162float(mb[t]) > 0.f) ? v[j + t] : 0.f;
-              }
               uint4 o;
               o.x = pack_bf16(v[j], v[j + 1]);
               o.y = pack_bf16(v[j + 2], v[j + 3]);
@@ -283,18 +276,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
           }
           __syncwarp();
-          uint4 o[8];
+          float csum[8];
 #pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int r = it * 4 + lrow;
-            o[it] = *reinterpret_cast<const uint4*>(so + r * 128 + ((lchunk ^ (r & 7)) << 4));
-          }
+          for (int e = 0; e < 8; ++e) csum[e] = 0.f;
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int r = it * 4 + lrow;
             const int grow = m0 + q * 32 + r;
-            if (grow < g.M && col0 + lchunk * 8 < g.N)
-              *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.D) + static_cast<size_t>(grow) * g.ldd + col0) + lchunk) = o[it];
+            uint4 o = *reinterpret_cast<const uint4*>(so + r * 128 + ((lchunk ^ (r & 7)) << 4));
+            if (g.epi == 2) {   // ReLU backward: zero where the forward activation was not positive
+              __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&o);
+              const __nv_bfloat16* me = reinterpret_cast<const __nv_bfloat16*>(&m[it]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (!(__bfloat162float(me[e]) > 0.f)) oe[e] = __float2bfloat16(0.f);
+            }
+            if (grow < g.M && col_ok) {
+              *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.D) + static_cast<size_t>(grow) * g.ldd + col0) + lchunk) = o;
+              if (g.colsum != nullptr) {
+                const __nv_bfloat16* oe = reinterpret_cast<const __nv_bfloat16*>(&o);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) csum[e] += __bfloat162float(oe[e]);
+              }
+            }
+          }
+          if (g.colsum != nullptr) {   // rows of this warp are spread over lanes l, l+8, l+16, l+24
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              csum[e] += __shfl_xor_sync(0xffffffffu, csum[e], 8);
+              csum[e] += __shfl_xor_sync(0xffffffffu, csum[e], 16);
+            }
+            if (lrow == 0 && col_ok) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) atomicAdd(g.colsum + col0 + lchunk * 8 + e, csum[e]);
+            }
           }
           __syncwarp();
         }
@@ -489,7 +504,7 @@ int num_sms() {
 // bn / splits: 0 selects automatically.  `status` is a device word that receives RsDevErr bits.
 RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias, const void* aux, const void* x0,
                         int M, int N, int K, int lda, int ldb, int ldd, int ldaux, int ldx0, int mode, int epi,
-                        int bn, int splits, unsigned long long* status, cudaStream_t stream) {
+                        int bn, int splits, float* colsum, unsigned long long* status, cudaStream_t stream) {
   RS_REQUIRE(A && B && D, "rs_gemm_bf16: null operand");
   RS_REQUIRE(M > 0 && N > 0 && K > 0, "rs_gemm_bf16: empty problem %d %d %d", M, N, K);
   RS_REQUIRE(mode >= 0 && mode <= 2, "rs_gemm_bf16: mode must be 0, 1 or 2");
@@ -534,7 +549,7 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   }
   g.splits = splits;
   const uint32_t stage_bytes = kABytes + static_cast<uint32_t>(bn) * BK * 2;
-  int stages = static_cast<int>((227u * 1024u - kStageBytes - 2048u) / stage_bytes);
+  int stages = static_cast<int>((227u * 1024u - kStageBytes - 256u) / stage_bytes);
   if (stages > 8) stages = 8;
   if (stages < 2) stages = 2;
   g.stages = stages;
@@ -543,6 +558,8 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   g.aux = reinterpret_cast<const __nv_bfloat16*>(aux);
   g.x0 = reinterpret_cast<const __nv_bfloat16*>(x0);
   g.status = status;
+  g.colsum = colsum;
+  RS_REQUIRE(colsum == nullptr || (epi <= 2 && bn % 64 == 0), "rs_gemm_bf16: colsum needs a bf16 epilogue (0, 1, 2) and a tile width multiple of 64");
 
   CUtensorMap ma, mb;
   int rc;
@@ -550,7 +567,7 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   else { if ((rc = make_map_bf16(&ma, A, K, M, lda, BK, 64)) != RS_OK) return rc; }
   if (mode == 0) { if ((rc = make_map_bf16(&mb, B, N, K, ldb, bn, BK)) != RS_OK) return rc; }
   else { if ((rc = make_map_bf16(&mb, B, K, N, ldb, BK, 64)) != RS_OK) return rc; }
-  const size_t smem = static_cast<size_t>(stages) * stage_bytes + kStageBytes + 1024 + 256;
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes + kStageBytes + 256;
   static bool attr_set[3] = {false, false, false};
   if (!attr_set[mode]) {
     if (mode == 0) RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));

@@ -362,10 +362,12 @@ class DLRM:
             L = self.top[i]
             dy = self.d_act_t[i]
             xin = self.act_t[i - 1] if i > 0 else self.z
-            F_.colsum_bf16(dy, L.gb); self._count()
+            if i == len(self.top) - 1:
+                F_.colsum_bf16(dy, L.gb); self._count()       # the other bias gradients come out of the dgrad epilogues
             F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
             if i > 0:
-                F_.gemm_bf16(dy, L.wt, self.d_act_t[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
+                F_.gemm_bf16(dy, L.wt, self.d_act_t[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st,
+                             colsum=self.top[i - 1].gb)
             else:
                 F_.gemm_bf16(dy, L.wt, self.d_z, mode=0, epi=F_.EPI_NONE, status=st)
             self._count()
@@ -398,10 +400,12 @@ class DLRM:
             L = self.bot[i]
             dy = self.d_act_b[i]
             xin = self.act_b[i - 1] if i > 0 else self.x0p
-            F_.colsum_bf16(dy, L.gb); self._count()
+            if i == len(self.bot) - 1:
+                F_.colsum_bf16(dy, L.gb); self._count()
             F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
             if i > 0:
-                F_.gemm_bf16(dy, L.wt, self.d_act_b[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
+                F_.gemm_bf16(dy, L.wt, self.d_act_b[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st,
+                             colsum=self.bot[i - 1].gb)
                 self._count()
         if self.world > 1:
             self.ctx.wait(CH_BWD); self._count()
