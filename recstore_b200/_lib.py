@@ -120,10 +120,13 @@ def lib():
     with _lock:
         if _lib is not None:
             return _lib
-        if not _LIB_PATH.exists() or os.environ.get("RECSTORE_B200_REBUILD"):
-            from . import build as _build
-            _build.build()
-        l = C.CDLL(str(_LIB_PATH), mode=C.RTLD_GLOBAL)
+        path = os.environ.get("RECSTORE_B200_LIB")   # an alternative build of the same ABI (A/B timing of kernels)
+        if path is None:
+            if not _LIB_PATH.exists() or os.environ.get("RECSTORE_B200_REBUILD"):
+                from . import build as _build
+                _build.build()
+            path = str(_LIB_PATH)
+        l = C.CDLL(path, mode=C.RTLD_GLOBAL)
         _apply(l, _SIGNATURES)
         _lib = l
     return _lib

@@ -151,6 +151,7 @@ def main():
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--epi", type=int, default=F_.EPI_RELU)
     ap.add_argument("--batch", type=int, default=65536)
+    ap.add_argument("--alpha", type=float, default=1.2, help="Zipf exponent of the embedding ids (0 = uniform)")
     ap.add_argument("--small", action="store_true", help="a few hundred MB on the device: suited to an ncu capture")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
@@ -168,7 +169,7 @@ def main():
         for (m, n) in [(1024, 1024), (1024, 512), (256, 512)]:
             bench_gemm(tm, dev, m, n, B, 1)
     if a.kernel in ("all", "embedding"):
-        bench_embedding(tm, dev, B, 26 if not a.small else 8, 128, 1_000_000)
+        bench_embedding(tm, dev, B, 26 if not a.small else 8, 128, 1_000_000, alpha=a.alpha)
     if a.kernel in ("all", "interaction"):
         bench_interaction(tm, dev, B, 27, 128)
 

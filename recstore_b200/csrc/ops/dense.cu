@@ -108,14 +108,60 @@ __global__ void __launch_bounds__(256) head_bce_kernel(const __nv_bfloat16* __re
   }
 }
 
-// db[n] += sum over rows of dY[m, n]; block handles 128 rows x 256 columns.
+// db[n] += sum over rows of dY[m, n].  A block covers 256 columns (32 lanes x 8 columns, 16-byte loads) and
+// kColsumRows rows (8 row-lanes, 4 loads in flight each); partial sums meet in shared memory, one atomic per column.
+constexpr int kColsumRows = 128;
 __global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __restrict__ dY, int ld, int M, int N,
                                                      float* __restrict__ db) {
+  __shared__ float s_part[8][256];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int n0 = blockIdx.x * 256 + tx * 8;
+  const int m0 = blockIdx.y * kColsumRows;
+  const int m1 = min(M, m0 + kColsumRows);
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  if (n0 < N) {
+    for (int m = m0 + ty; m < m1; m += 32) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int mm = m + u * 8;
+        v[u] = mm < m1 ? __ldg(reinterpret_cast<const uint4*>(dY + static_cast<size_t>(mm) * ld + n0)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(p[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) s_part[ty][tx * 8 + e] = acc[e];
+  __syncthreads();
+  const int c = threadIdx.x;
+  const int n = blockIdx.x * 256 + c;
+  if (n < N) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) s += s_part[r][c];
+    atomicAdd(&db[n], s);
+  }
+}
+
+// Same sums for shapes the 16-byte loads cannot take (odd widths, unaligned views): one column per thread.
+__global__ void __launch_bounds__(256) colsum_scalar_kernel(const __nv_bfloat16* __restrict__ dY, int ld, int M, int N,
+                                                            float* __restrict__ db) {
   const int n = blockIdx.x * 256 + threadIdx.x;
-  const int m0 = blockIdx.y * 128;
   if (n >= N) return;
+  const int m0 = blockIdx.y * kColsumRows;
+  const int m1 = min(M, m0 + kColsumRows);
   float s = 0.f;
-  const int m1 = min(M, m0 + 128);
   for (int m = m0; m < m1; ++m) s += __bfloat162float(dY[static_cast<size_t>(m) * ld + n]);
   atomicAdd(&db[n], s);
 }
@@ -303,7 +349,12 @@ RS_API int rs_head_bce(const void* X, int ldx, int M, int K, const float* w, con
 RS_API int rs_colsum_bf16(const void* dY, int ld, int M, int N, float* db, cudaStream_t stream) {
   RS_REQUIRE(dY && db, "rs_colsum_bf16: null argument");
   if (M == 0 || N == 0) return RS_OK;
-  dim3 grid((N + 255) / 256, (M + 127) / 128);
+  dim3 grid((N + 255) / 256, (M + kColsumRows - 1) / kColsumRows);
+  if (N % 8 != 0 || ld % 8 != 0 || (reinterpret_cast<uintptr_t>(dY) & 15) != 0) {
+    colsum_scalar_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dY), ld, M, N, db);
+    RS_LAUNCH_CHECK();
+    return RS_OK;
+  }
   colsum_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dY), ld, M, N, db);
   RS_LAUNCH_CHECK();
   return RS_OK;
