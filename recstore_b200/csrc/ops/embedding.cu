@@ -290,30 +290,57 @@ __global__ void __launch_bounds__(256) emb_state_kernel(const EmbBwdArgs a) {
   if (lane == 0) atomicAdd(&a.state[row], w * w * sq * inv_d);
 }
 
-// Apply pass: one CTA per group of 256 occurrences.  Threads first resolve their occurrence
-// (row, gradient offset, weight) into shared memory and chain equal rows into linked lists through
-// a shared-memory hash; then each warp takes distinct rows in turn, sums the gradients of the
-// chain (4 loads in flight) and issues ONE vector atomic per row and group.
-template <int NC>
+// Apply pass: one CTA per group of 256 occurrences.  The group is counting-sorted by row in shared memory (hash
+// slot -> count -> exclusive scan -> position), so equal rows sit next to each other.  Every warp then owns 32
+// consecutive sorted positions, whatever the skew of the ids: it streams their gradients with kApplyInFlight
+// loads (and the matching Adagrad states) in flight, sums runs of equal rows in registers and issues one vector
+// atomic per run.  A row that straddles warps or groups simply receives several atomics.
+constexpr int kApplyInFlight = 8;
+
+// Raw (unconverted) gradient chunk: the loads of a batch are issued back to back with no branch and no use of
+// their results in between, so all of them are in flight together; conversion happens when they are consumed.
+template <bool BF16> struct RawGrad;
+template <> struct RawGrad<true> {
+  uint2 v;
+  __device__ __forceinline__ void load(const void* base, long long goff, int vec) {
+    v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + goff) + vec);
+  }
+  __device__ __forceinline__ float4 get() const {
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+  }
+};
+template <> struct RawGrad<false> {
+  float4 v;
+  __device__ __forceinline__ void load(const void* base, long long goff, int vec) {
+    v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + goff) + vec);
+  }
+  __device__ __forceinline__ float4 get() const { return v; }
+};
+
+template <int NC, bool BF16>
 __global__ void __launch_bounds__(kGroup) emb_apply_kernel(const EmbBwdArgs a) {
   __shared__ long long s_key[kSlots];
-  __shared__ int s_head[kSlots];
-  __shared__ int s_next[kGroup];
-  __shared__ long long s_goff[kGroup];
-  __shared__ float s_w[kGroup];
-  __shared__ int s_leader_slot[kGroup];
-  __shared__ int s_nleaders;
+  __shared__ int s_cnt[kSlots];        // occurrences per slot, then exclusive offsets
+  __shared__ long long s_goff[kGroup];  // sorted: gradient offset
+  __shared__ long long s_row[kGroup];   // sorted: row
+  __shared__ float s_w[kGroup];         // sorted: per-sample weight
+  __shared__ int s_warp_sum[kGroup / 32];
+  __shared__ int s_total;
 
   const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
   const long long g0 = static_cast<long long>(blockIdx.x) * kGroup;
   for (int s = tid; s < kSlots; s += kGroup) {
     s_key[s] = -1;
-    s_head[s] = -1;
+    s_cnt[s] = 0;
   }
-  if (tid == 0) s_nleaders = 0;
   __syncthreads();
 
-  long long row = -1;
+  long long row = -1, goff = 0;
+  float w = 1.f;
+  int slot = -1, rank = 0;
   if (g0 + tid < a.nnz) {
     const long long occ = g0 + tid;
     row = a.row_idx[occ];
@@ -324,8 +351,8 @@ __global__ void __launch_bounds__(kGroup) emb_apply_kernel(const EmbBwdArgs a) {
     const long long bag = a.occ2bag ? a.occ2bag[occ] : occ;
     const int t = static_cast<int>(bag / a.B);
     const long long b = bag % a.B;
-    s_goff[tid] = b * a.grad_row_stride + (a.grad_col ? a.grad_col[t] : 0);
-    s_w[tid] = a.psw ? a.psw[occ] : 1.f;
+    goff = b * a.grad_row_stride + (a.grad_col ? a.grad_col[t] : 0);
+    if (a.psw) w = a.psw[occ];
   }
   if (row >= 0) {
     unsigned s = static_cast<unsigned>(rs::ht_hash(static_cast<unsigned long long>(row))) & (kSlots - 1);
@@ -333,63 +360,99 @@ __global__ void __launch_bounds__(kGroup) emb_apply_kernel(const EmbBwdArgs a) {
       const long long prev = static_cast<long long>(atomicCAS(reinterpret_cast<unsigned long long*>(&s_key[s]),
                                                                static_cast<unsigned long long>(-1ll),
                                                                static_cast<unsigned long long>(row)));
-      if (prev == -1) {  // first occurrence of this row in the group: becomes a leader slot
-        const int k = atomicAdd(&s_nleaders, 1);
-        s_leader_slot[k] = static_cast<int>(s);
-      }
       if (prev == -1 || prev == row) {
-        s_next[tid] = atomicExch(&s_head[s], tid);
+        slot = static_cast<int>(s);
+        rank = atomicAdd(&s_cnt[s], 1);
         break;
       }
       s = (s + 1) & (kSlots - 1);
     }
   }
   __syncthreads();
-
-  const int warp = tid >> 5, lane = tid & 31;
-  const int nvec = a.D >> 2;
-  const int nleaders = s_nleaders;
-  for (int k = warp; k < nleaders; k += kGroup / 32) {
-    const int slot = s_leader_slot[k];
-    const long long r = s_key[slot];
-    float4 acc[NC];
+  // exclusive scan of the 512 slot counts: two slots per thread, warp shuffles, then the warp totals
+  {
+    const int c0 = s_cnt[2 * tid], c1 = s_cnt[2 * tid + 1];
+    int incl = c0 + c1;
 #pragma unroll
-    for (int c = 0; c < NC; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-    int j = s_head[slot];
-    while (j >= 0) {
-      int jj[4];
-      float4 g[4][NC];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        jj[u] = j;
-        if (j >= 0) {
-          load_grad<NC>(a, s_goff[j], lane, nvec, g[u]);
-          j = s_next[j];
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (jj[u] >= 0) {
-          const float w = s_w[jj[u]];
-#pragma unroll
-          for (int c = 0; c < NC; ++c) {
-            acc[c].x += w * g[u][c].x; acc[c].y += w * g[u][c].y;
-            acc[c].z += w * g[u][c].z; acc[c].w += w * g[u][c].w;
-          }
-        }
-      }
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
     }
+    if (lane == 31) s_warp_sum[warp] = incl;
+    __syncthreads();
+    int base = 0;
+#pragma unroll
+    for (int q = 0; q < kGroup / 32; ++q) base += q < warp ? s_warp_sum[q] : 0;
+    const int excl = base + incl - (c0 + c1);
+    s_cnt[2 * tid] = excl;
+    s_cnt[2 * tid + 1] = excl + c0;
+    if (tid == kGroup - 1) s_total = base + incl;
+  }
+  __syncthreads();
+  if (slot >= 0) {
+    const int pos = s_cnt[slot] + rank;
+    s_goff[pos] = goff;
+    s_row[pos] = row;
+    s_w[pos] = w;
+  }
+  __syncthreads();
+
+  const int total = s_total;
+  const int nvec = a.D >> 2;
+  const int p_end = min(total, warp * 32 + 32);
+  long long cur = -1;
+  float cur_state = 0.f;
+  float4 acc[NC];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  auto flush = [&]() {
+    if (cur < 0) return;
     float scale = -a.lr;
-    if (a.optimizer == 1) scale = -a.lr / (sqrtf(__ldcv(&a.state[r])) + a.eps);
+    if (a.optimizer == 1) scale = -a.lr / (sqrtf(cur_state) + a.eps);
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
       const int v = lane + c * 32;
       if (v < nvec) {
         float4 u = make_float4(scale * acc[c].x, scale * acc[c].y, scale * acc[c].z, scale * acc[c].w);
-        atomicAdd(reinterpret_cast<float4*>(a.weight + r * a.D) + v, u);
+        atomicAdd(reinterpret_cast<float4*>(a.weight + cur * a.D) + v, u);
+      }
+      acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+
+  constexpr int U = NC == 1 ? kApplyInFlight : (NC == 2 ? 4 : 2);
+  for (int p0 = warp * 32; p0 < p_end; p0 += U) {
+    RawGrad<BF16> g[U][NC];
+    float st[U];
+    long long r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int p = min(p0 + u, p_end - 1);   // past the end: re-read the last valid position, ignored below
+      r[u] = s_row[p];
+      const long long go = s_goff[p];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) g[u][c].load(a.grad, go, min(lane + c * 32, nvec - 1));
+      st[u] = a.optimizer == 1 ? __ldcv(&a.state[r[u]]) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (p0 + u >= p_end) break;
+      if (r[u] != cur) {
+        flush();
+        cur = r[u];
+        cur_state = st[u];
+      }
+      const float wu = s_w[p0 + u];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const float4 x = g[u][c].get();
+        acc[c].x += wu * x.x; acc[c].y += wu * x.y;
+        acc[c].z += wu * x.z; acc[c].w += wu * x.w;
       }
     }
   }
+  flush();
 }
 
 // Plain row gather / scatter used by the PS get / put verbs: out[i] = W[rows[i]] (zeros when rows[i] < 0).
@@ -476,9 +539,16 @@ RS_API int rs_emb_backward(float* weight, float* state, long long total_rows, co
     else emb_state_kernel<4><<<static_cast<unsigned>(g1), 256, 0, stream>>>(a);
     RS_LAUNCH_CHECK();
   }
-  if (nc == 1) emb_apply_kernel<1><<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
-  else if (nc == 2) emb_apply_kernel<2><<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
-  else emb_apply_kernel<4><<<static_cast<unsigned>(grid), kGroup, 0, stream>>>(a);
+  const unsigned g = static_cast<unsigned>(grid);
+  if (grad_bf16) {
+    if (nc == 1) emb_apply_kernel<1, true><<<g, kGroup, 0, stream>>>(a);
+    else if (nc == 2) emb_apply_kernel<2, true><<<g, kGroup, 0, stream>>>(a);
+    else emb_apply_kernel<4, true><<<g, kGroup, 0, stream>>>(a);
+  } else {
+    if (nc == 1) emb_apply_kernel<1, false><<<g, kGroup, 0, stream>>>(a);
+    else if (nc == 2) emb_apply_kernel<2, false><<<g, kGroup, 0, stream>>>(a);
+    else emb_apply_kernel<4, false><<<g, kGroup, 0, stream>>>(a);
+  }
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
