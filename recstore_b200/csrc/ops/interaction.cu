@@ -38,15 +38,27 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Loads the F x D tile of one sample into padded shared memory, zero-filling rows F..31.
-__device__ __forceinline__ void load_tile(__nv_bfloat16* sT, const __nv_bfloat16* src, int F, int D, int lane) {
-  const int vec_per_row = D >> 3;  // uint4 = 8 bf16
-  const int total = 32 * vec_per_row;
+// Asynchronous 16-byte global -> shared copies: no registers held, so a lane keeps all of its copies of a tile in
+// flight at once (a register-staged loop with a run-time trip count issues them one after the other).
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Zero-fills rows F..31 of a padded tile (they never change afterwards).
+__device__ __forceinline__ void zero_tail_rows(__nv_bfloat16* sT, int F, int D, int lane) {
+  const int vec_per_row = D >> 3;
+  for (int i = F * vec_per_row + lane; i < 32 * vec_per_row; i += 32)
+    *reinterpret_cast<uint4*>(sT + (i / vec_per_row) * kLd + (i % vec_per_row) * 8) = make_uint4(0, 0, 0, 0);
+}
+// Starts the copy of the F x D tile of one sample into padded shared memory (rows 0..F-1); the caller waits.
+__device__ __forceinline__ void load_tile_async(__nv_bfloat16* sT, const __nv_bfloat16* src, int F, int D, int lane) {
+  const int vec_per_row = D >> 3;  // 16 bytes = 8 bf16
+  const int total = F * vec_per_row;
   for (int i = lane; i < total; i += 32) {
     const int r = i / vec_per_row, v = i % vec_per_row;
-    uint4 x = make_uint4(0, 0, 0, 0);
-    if (r < F) x = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * D) + v);
-    *reinterpret_cast<uint4*>(sT + r * kLd + v * 8) = x;
+    cp_async16(sT + r * kLd + v * 8, src + static_cast<size_t>(r) * D + v * 8);
   }
 }
 
@@ -58,7 +70,9 @@ __global__ void __launch_bounds__(kWarps * 32) interaction_fwd_kernel(const __nv
   const int b = blockIdx.x * kWarps + warp;
   if (b >= B) return;
   __nv_bfloat16* t = sT[warp];
-  load_tile(t, T + static_cast<size_t>(b) * F * D, F, D, lane);
+  load_tile_async(t, T + static_cast<size_t>(b) * F * D, F, D, lane);
+  zero_tail_rows(t, F, D, lane);
+  cp_async_wait_all();
   __syncwarp();
 
   // acc[mt][nt]: rows mt*16.., cols nt*8..; only tiles that touch the strict lower triangle.
@@ -167,6 +181,7 @@ __global__ void __launch_bounds__(kWarpsBwd * 32) interaction_bwd_kernel(const I
   __nv_bfloat16* o = s + 32 * 40;
   __nv_bfloat16* sd = o + 32 * kOutLd;
   for (int i = lane; i < 32 * 40 / 8; i += 32) reinterpret_cast<uint4*>(s)[i] = make_uint4(0, 0, 0, 0);
+  zero_tail_rows(t, F, D, lane);
   __syncthreads();
 
   const int g = lane >> 2, q = lane & 3;
@@ -190,9 +205,10 @@ __global__ void __launch_bounds__(kWarpsBwd * 32) interaction_bwd_kernel(const I
   const int dvec = (a.dout_ld * 2) >> 4;  // uint4 per dOut row
 
   for (int b = blockIdx.x * kWarpsBwd + warp; b < a.B; b += gridDim.x * kWarpsBwd) {
-    load_tile(t, a.T + static_cast<size_t>(b) * F * D, F, D, lane);
+    load_tile_async(t, a.T + static_cast<size_t>(b) * F * D, F, D, lane);
     const __nv_bfloat16* dout = a.dout + static_cast<size_t>(b) * a.dout_ld;
-    for (int v = lane; v < dvec; v += 32) reinterpret_cast<uint4*>(sd)[v] = __ldg(reinterpret_cast<const uint4*>(dout) + v);
+    for (int v = lane; v < dvec; v += 32) cp_async16(sd + v * 8, dout + v * 8);
+    cp_async_wait_all();
     __syncwarp();
     for (int p = lane; p < npairs; p += 32) {
       const int ij = s_ij[p];
