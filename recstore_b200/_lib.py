@@ -60,7 +60,7 @@ _SIGNATURES = {
     "rs_last_error": (cstr, []),
     "rs_abi_version": (i32, []),
     # ops/gemm_tcgen05.cu
-    "rs_gemm_bf16": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]),
+    "rs_gemm_bf16": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp]),
     # ops/embedding.cu
     "rs_emb_forward": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i64, vp, i32, vp, vp, vp, vp, vp]),
     "rs_emb_backward": (i32, [vp, vp, i64, vp, vp, i64, vp, vp, i64, vp, i32, i32, i32, i32, vp, f32, f32, i32, vp, vp]),

@@ -111,6 +111,26 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Named barriers for a subset of the CTA's warps (id 1..15; id 0 is __syncthreads).  `count` = participating threads.
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+// Barrier that also returns the AND of every participant's predicate.
+__device__ __forceinline__ bool bar_red_and(uint32_t id, uint32_t count, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %3, 0;\n"
+      "bar.red.and.pred p, %1, %2, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(id), "r"(count), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out != 0;
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 // Allocation is a warp-wide (.sync.aligned) operation; ncols is a power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {

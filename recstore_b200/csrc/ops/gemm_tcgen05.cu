@@ -23,8 +23,11 @@
 //   5  D = x0[m,n] * (acc + bias[n]) + aux[m,n]  bf16 store (DCNv2 cross update)
 //   6  D = acc + aux[m,n]                        bf16 store (residual add)
 //
-// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs,
-// warps 2..5 read the accumulator back (one TMEM lane quadrant each).  Two
+// CTA = 10 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs,
+// warps 2..9 read the accumulator back: two groups of four warps (one warp per TMEM
+// lane quadrant in each group) take alternate 64-column chunks of a tile, convert
+// them in registers, stage them in 128-byte-swizzled shared memory and hand them to
+// a TMA store, so no thread issues global stores for the bf16 epilogues.  Two
 // accumulators are kept in TMEM so that the epilogue of tile i overlaps the main
 // loop of tile i+1.  Every mbarrier wait is bounded; on give-up the kernel sets
 // RS_DEV_WAIT_TIMEOUT in the status word, frees TMEM and returns.
@@ -43,8 +46,12 @@ constexpr int kEpiWarps = 8;               // two warps per TMEM lane quadrant: 
 constexpr int kThreads = 64 + kEpiWarps * 32;
 constexpr uint32_t kABytes = BM * BK * 2;  // 16 KiB per stage
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kWarpStage = 4096 + 256;              // per epilogue warp: output tile (32 rows x 128 B) + 64 bias values
-constexpr uint32_t kStageBytes = kEpiWarps * kWarpStage;
+constexpr int kEpiGroups = kEpiWarps / 4;
+constexpr uint32_t kChunkBytes = BM * 128;               // staging of one 128-row x 64-column bf16 chunk (one TMA store box)
+constexpr uint32_t kBiasBytes = 256 * 4;                 // bias slice of one tile
+constexpr uint32_t kStageBytes = kEpiGroups * (kChunkBytes + kBiasBytes);
+constexpr uint32_t kWarpStage = kStageBytes / kEpiWarps;   // ReLU-backward epilogue: 32 rows x 128 B + 64 bias values per warp
+static_assert(kWarpStage >= 4096 + 256 && kWarpStage % 16 == 0, "per-warp staging slice");
 
 struct GemmArgs {
   int M, N, K;          // logical problem (see modes above); K = reduction length
@@ -59,7 +66,7 @@ struct GemmArgs {
   const float* bias;
   const __nv_bfloat16* aux;
   const __nv_bfloat16* x0;
-  float* colsum;        // optional: colsum[n] += sum over rows of the bf16 output (bias gradient of the consumer)
+  int tma_out;          // bf16 epilogue through shared memory and a TMA store (tile width multiple of 64)
   unsigned long long* status;
 };
 
@@ -71,14 +78,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                    const GemmArgs g) {
+                    const __grid_constant__ CUtensorMap tma_d, const GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw;   // the kernel has no static shared memory: the dynamic window starts 1024-byte aligned (checked below)
   const int stages = g.stages;
   const uint32_t b_bytes = static_cast<uint32_t>(g.bn) * BK * 2;
   uint8_t* sA = smem;
   uint8_t* sB = smem + static_cast<size_t>(stages) * kABytes;
-  uint8_t* sStage = sB + static_cast<size_t>(stages) * b_bytes;   // 4 epilogue warps x 2 x 4 KiB
+  uint8_t* sStage = sB + static_cast<size_t>(stages) * b_bytes;   // per epilogue group: one chunk; then the bias slices
   uint64_t* full = reinterpret_cast<uint64_t*>(sStage + kStageBytes);
   uint64_t* empty = full + stages;
   uint64_t* tfull = empty + stages;
@@ -106,6 +113,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     mbar_fence_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (g.tma_out) tma_prefetch_desc(&tma_d);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -203,11 +211,148 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
   } else {
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
-    const int part = (warp - 2) >> 2;  // which half of the column groups this warp of the quadrant's pair takes
-    constexpr int kParts = kEpiWarps / 4;
+    const int part = (warp - 2) >> 2;  // epilogue group of this warp
+    constexpr int kParts = kEpiGroups;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    if (g.tma_out && g.epi != 2) {
+      uint8_t* so = sStage + part * kChunkBytes;
+      float* sbias = reinterpret_cast<float*>(sStage + kEpiGroups * kChunkBytes + part * kBiasBytes);
+      const int gtid = ((warp - 2) & 3) * 32 + lane;   // 0..127 inside the group
+      const bool leader = gtid == 0;
+      const uint32_t bar_id = 1u + static_cast<uint32_t>(part);
+      const int srow = q * 32 + lane;                  // row of the tile (= TMEM lane) this thread converts
+      uint8_t* srow_ptr = so + srow * 128;
+      const uint32_t sw = static_cast<uint32_t>(srow & 7);
+      const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
+      const int nchunks = g.bn / 64;
+      for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int tile = it % tiles;
+        const int m0 = (tile / g.tiles_n) * BM;
+        const int n0 = (tile % g.tiles_n) * g.bn;
+        // The tile's bias slice is requested before the accumulator is ready, so its latency hides behind the wait.
+        float2 bv = make_float2(0.f, 0.f);
+        if (g.bias != nullptr && n0 + gtid * 2 < g.N && gtid * 2 < g.bn) bv = __ldg(reinterpret_cast<const float2*>(g.bias + n0) + gtid);
+        const bool mine = mbar_wait(&tfull[acc], acc_phase, abort_flag);
+        reinterpret_cast<float2*>(sbias)[gtid] = bv;
+        // One verdict for the whole group (a thread that gave up must not leave the others at a barrier); the same
+        // barrier publishes the bias slice.
+        ok = bar_red_and(bar_id, 128, mine);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const int row = m0 + srow;
+        const bool row_ok = row < g.M;
+        bool released = false;
+        for (int c = part; c < nchunks; c += kParts) {
+          const int col0 = n0 + c * 64;
+          if (col0 >= g.N) break;
+          uint32_t r[64];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * g.bn + c * 64);
+          tmem_ld_32x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+          tmem_ld_32x32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          // Operands from global memory (ReLU mask source, residual, x0) are fetched row-contiguously, four rows
+          // of 128 bytes per warp instruction, while the accumulator is on its way.  They reach the thread that
+          // owns the row through this warp's 32 rows of the staging buffer, in the layout a TMA load would give.
+          const bool use_aux = g.epi == 2 || g.epi >= 5;
+          const int lrow = lane >> 3, lchunk = lane & 7;
+          uint4 ax[8], xx[8];
+          if (use_aux) {
+            const bool col_in = col0 + lchunk * 8 < g.N;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int grow = m0 + q * 32 + j * 4 + lrow;
+              const bool in = col_in && grow < g.M;
+              const size_t r_eff = in ? static_cast<size_t>(grow) : 0;
+              ax[j] = __ldg(reinterpret_cast<const uint4*>(g.aux + r_eff * g.ldaux + (in ? col0 + lchunk * 8 : 0)));
+              if (g.epi == 5) xx[j] = __ldg(reinterpret_cast<const uint4*>(g.x0 + r_eff * g.ldx0 + (in ? col0 + lchunk * 8 : 0)));
+            }
+          }
+          if (leader) tma_store_wait_read<0>();   // the previous chunk's store has finished reading the staging
+          named_bar_sync(bar_id, 128);
+          if (use_aux) {
+            uint8_t* wbase = so + (q * 32) * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int rr = j * 4 + lrow;
+              *reinterpret_cast<uint4*>(wbase + rr * 128 + ((static_cast<uint32_t>(lchunk) ^ (rr & 7)) << 4)) = ax[j];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ax[j] = *reinterpret_cast<const uint4*>(srow_ptr + ((static_cast<uint32_t>(j) ^ sw) << 4));
+            if (g.epi == 5) {   // second operand: same route, after the first has been read back
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int rr = j * 4 + lrow;
+                *reinterpret_cast<uint4*>(wbase + rr * 128 + ((static_cast<uint32_t>(lchunk) ^ (rr & 7)) << 4)) = xx[j];
+              }
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) xx[j] = *reinterpret_cast<const uint4*>(srow_ptr + ((static_cast<uint32_t>(j) ^ sw) << 4));
+            }
+            __syncwarp();   // every lane has its row before anyone overwrites the staging with results
+          }
+          tmem_ld_wait();
+          if (c + kParts >= nchunks || col0 + kParts * 64 >= g.N) {   // last chunk of this thread in the tile
+            tc_fence_before_sync();
+            mbar_arrive(&tempty[acc]);
+            released = true;
+          }
+          uint32_t pk[32];
+          const float* sb = sbias + c * 64;
+#pragma unroll
+          for (int j = 0; j < 64; j += 4) {
+            float v0 = __uint_as_float(r[j]), v1 = __uint_as_float(r[j + 1]);
+            float v2 = __uint_as_float(r[j + 2]), v3 = __uint_as_float(r[j + 3]);
+            if (g.bias != nullptr) {
+              const float4 b = *reinterpret_cast<const float4*>(sb + j);   // same address in every lane: broadcast
+              v0 += b.x; v1 += b.y; v2 += b.z; v3 += b.w;
+            }
+            if (g.epi >= 5) {
+              const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ax[j >> 3]) + ((j & 4) >> 1);
+              const float2 a0 = __bfloat1622float2(pa[0]), a1 = __bfloat1622float2(pa[1]);
+              if (g.epi == 5) {
+                const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&xx[j >> 3]) + ((j & 4) >> 1);
+                const float2 x0v = __bfloat1622float2(px[0]), x1v = __bfloat1622float2(px[1]);
+                v0 = x0v.x * v0 + a0.x; v1 = x0v.y * v1 + a0.y;
+                v2 = x1v.x * v2 + a1.x; v3 = x1v.y * v3 + a1.y;
+              } else {
+                v0 += a0.x; v1 += a0.y; v2 += a1.x; v3 += a1.y;
+              }
+            }
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1), p1 = __floats2bfloat162_rn(v2, v3);
+            if (g.epi == 1) {          // max commutes with the rounding, so ReLU runs on packed pairs
+              p0 = __hmax2(p0, zero2);
+              p1 = __hmax2(p1, zero2);
+            } else if (g.epi == 2) {   // ReLU backward: multiply by (forward activation > 0) as 1.0 / 0.0
+              const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ax[j >> 3]) + ((j & 4) >> 1);
+              p0 = __hmul2(p0, __hgt2(pa[0], zero2));
+              p1 = __hmul2(p1, __hgt2(pa[1], zero2));
+            }
+            pk[j >> 1] = *reinterpret_cast<uint32_t*>(&p0);
+            pk[(j >> 1) + 1] = *reinterpret_cast<uint32_t*>(&p1);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(srow_ptr + ((static_cast<uint32_t>(j) ^ sw) << 4)) =
+                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          fence_proxy_async_smem();
+          named_bar_sync(bar_id, 128);
+          if (leader) {
+            tma_store_2d(&tma_d, so, col0, m0);   // rows >= M and columns >= N are clipped by the tensor map
+            tma_store_commit();
+          }
+        }
+        if (!released) {
+          tc_fence_before_sync();
+          mbar_arrive(&tempty[acc]);
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (leader) tma_store_wait<0>();   // shared memory must outlive the stores that read it
+    } else
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int tile = it % tiles;
       const int m0 = (tile / g.tiles_n) * BM;
@@ -216,11 +361,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < g.M;
-      if (g.epi <= 2 && (g.bn & 63) == 0) {
+      if (g.epi == 2 && (g.bn & 63) == 0) {
         // bf16 output staged through shared memory: every thread owns one row of the accumulator, but
         // global memory is touched row-contiguously (4 rows x 128 B per warp instruction) for both the
         // output store and the ReLU-mask load.  16-byte chunks are XOR-swizzled by (row & 7).
-        uint8_t* so = sStage + (warp - 2) * kWarpStage;
+        uint8_t* so = sStage + (warp - 2) * kWarpStage;   // per-warp slices of the same staging region
         float* sbias = reinterpret_cast<float*>(so + 4096);
         const int lrow = lane >> 3, lchunk = lane & 7;
         for (int c = part; c < g.bn / 64; c += kParts) {
@@ -276,39 +421,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
           }
           __syncwarp();
-          float csum[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) csum[e] = 0.f;
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int r = it * 4 + lrow;
             const int grow = m0 + q * 32 + r;
             uint4 o = *reinterpret_cast<const uint4*>(so + r * 128 + ((lchunk ^ (r & 7)) << 4));
             if (g.epi == 2) {   // ReLU backward: zero where the forward activation was not positive
-              __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&o);
-              const __nv_bfloat16* me = reinterpret_cast<const __nv_bfloat16*>(&m[it]);
+              __nv_bfloat162* oe = reinterpret_cast<__nv_bfloat162*>(&o);
+              const __nv_bfloat162* me = reinterpret_cast<const __nv_bfloat162*>(&m[it]);
+              const __nv_bfloat162 z2 = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
-              for (int e = 0; e < 8; ++e)
-                if (!(__bfloat162float(me[e]) > 0.f)) oe[e] = __float2bfloat16(0.f);
+              for (int e = 0; e < 4; ++e) oe[e] = __hmul2(oe[e], __hgt2(me[e], z2));   // (activation > 0) as 1.0 / 0.0
             }
             if (grow < g.M && col_ok) {
               *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(g.D) + static_cast<size_t>(grow) * g.ldd + col0) + lchunk) = o;
-              if (g.colsum != nullptr) {
-                const __nv_bfloat16* oe = reinterpret_cast<const __nv_bfloat16*>(&o);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) csum[e] += __bfloat162float(oe[e]);
-              }
-            }
-          }
-          if (g.colsum != nullptr) {   // rows of this warp are spread over lanes l, l+8, l+16, l+24
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              csum[e] += __shfl_xor_sync(0xffffffffu, csum[e], 8);
-              csum[e] += __shfl_xor_sync(0xffffffffu, csum[e], 16);
-            }
-            if (lrow == 0 && col_ok) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) atomicAdd(g.colsum + col0 + lchunk * 8 + e, csum[e]);
             }
           }
           __syncwarp();
@@ -504,7 +630,7 @@ int num_sms() {
 // bn / splits: 0 selects automatically.  `status` is a device word that receives RsDevErr bits.
 RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias, const void* aux, const void* x0,
                         int M, int N, int K, int lda, int ldb, int ldd, int ldaux, int ldx0, int mode, int epi,
-                        int bn, int splits, float* colsum, unsigned long long* status, cudaStream_t stream) {
+                        int bn, int splits, unsigned long long* status, cudaStream_t stream) {
   RS_REQUIRE(A && B && D, "rs_gemm_bf16: null operand");
   RS_REQUIRE(M > 0 && N > 0 && K > 0, "rs_gemm_bf16: empty problem %d %d %d", M, N, K);
   RS_REQUIRE(mode >= 0 && mode <= 2, "rs_gemm_bf16: mode must be 0, 1 or 2");
@@ -558,15 +684,16 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   g.aux = reinterpret_cast<const __nv_bfloat16*>(aux);
   g.x0 = reinterpret_cast<const __nv_bfloat16*>(x0);
   g.status = status;
-  g.colsum = colsum;
-  RS_REQUIRE(colsum == nullptr || (epi <= 2 && bn % 64 == 0), "rs_gemm_bf16: colsum needs a bf16 epilogue (0, 1, 2) and a tile width multiple of 64");
+  g.tma_out = (!f32_out && bn % 64 == 0) ? 1 : 0;
 
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, md;
   int rc;
   if (mode != 1) { if ((rc = make_map_bf16(&ma, A, M, K, lda, BM, BK)) != RS_OK) return rc; }
   else { if ((rc = make_map_bf16(&ma, A, K, M, lda, BK, 64)) != RS_OK) return rc; }
   if (mode == 0) { if ((rc = make_map_bf16(&mb, B, N, K, ldb, bn, BK)) != RS_OK) return rc; }
   else { if ((rc = make_map_bf16(&mb, B, K, N, ldb, BK, 64)) != RS_OK) return rc; }
+  if (g.tma_out) { if ((rc = make_map_bf16(&md, D, M, N, ldd, BM, 64)) != RS_OK) return rc; }
+  else md = ma;   // unused by the kernel
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + kStageBytes + 256;
   static bool attr_set[3] = {false, false, false};
   if (!attr_set[mode]) {
@@ -577,9 +704,9 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   }
   const int items = g.tiles_m * g.tiles_n * g.splits;
   const int grid = items < sms ? items : sms;
-  if (mode == 0) gemm_tcgen05_kernel<0><<<grid, kThreads, smem, stream>>>(ma, mb, g);
-  else if (mode == 1) gemm_tcgen05_kernel<1><<<grid, kThreads, smem, stream>>>(ma, mb, g);
-  else gemm_tcgen05_kernel<2><<<grid, kThreads, smem, stream>>>(ma, mb, g);
+  if (mode == 0) gemm_tcgen05_kernel<0><<<grid, kThreads, smem, stream>>>(ma, mb, md, g);
+  else if (mode == 1) gemm_tcgen05_kernel<1><<<grid, kThreads, smem, stream>>>(ma, mb, md, g);
+  else gemm_tcgen05_kernel<2><<<grid, kThreads, smem, stream>>>(ma, mb, md, g);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

@@ -113,10 +113,6 @@ class DLRM:
         self.D = cfg.emb_dim
         self.F = self.T + 1
         import os
-        # Bias gradients can come out of the dgrad epilogues (GEMM `colsum`), but every CTA then adds into the same N
-        # addresses and the atomics serialise: measured 2.95 ms/step against 2.38 ms with the separate column-sum
-        # kernel on the benchmark config, so the fusion stays off unless asked for.
-        self.fuse_colsum = os.environ.get("RECSTORE_FUSE_COLSUM", "0") == "1"
         self.dcn = cfg.interaction == "dcn"
         assert cfg.interaction in ("dot", "dcn")
         assert self.dcn or self.F <= 32, "dot interaction kernel handles up to 31 embedding features"
@@ -367,12 +363,12 @@ class DLRM:
             L = self.top[i]
             dy = self.d_act_t[i]
             xin = self.act_t[i - 1] if i > 0 else self.z
-            if i == len(self.top) - 1 or not self.fuse_colsum:
-                F_.colsum_bf16(dy, L.gb); self._count()       # the other bias gradients come out of the dgrad epilogues
+            # Bias gradient as a pass of its own: summing columns inside the dgrad epilogue was measured slower
+            # (every CTA adds into the same N addresses) than this bandwidth-bound kernel.
+            F_.colsum_bf16(dy, L.gb); self._count()
             F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
             if i > 0:
-                F_.gemm_bf16(dy, L.wt, self.d_act_t[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st,
-                             colsum=self.top[i - 1].gb if self.fuse_colsum else None)
+                F_.gemm_bf16(dy, L.wt, self.d_act_t[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
             else:
                 F_.gemm_bf16(dy, L.wt, self.d_z, mode=0, epi=F_.EPI_NONE, status=st)
             self._count()
@@ -405,12 +401,10 @@ class DLRM:
             L = self.bot[i]
             dy = self.d_act_b[i]
             xin = self.act_b[i - 1] if i > 0 else self.x0p
-            if i == len(self.bot) - 1 or not self.fuse_colsum:
-                F_.colsum_bf16(dy, L.gb); self._count()
+            F_.colsum_bf16(dy, L.gb); self._count()
             F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
             if i > 0:
-                F_.gemm_bf16(dy, L.wt, self.d_act_b[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st,
-                             colsum=self.bot[i - 1].gb if self.fuse_colsum else None)
+                F_.gemm_bf16(dy, L.wt, self.d_act_b[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
                 self._count()
         if self.world > 1:
             self.ctx.wait(CH_BWD); self._count()

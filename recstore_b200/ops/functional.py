@@ -25,15 +25,12 @@ def _need_cuda(*ts):
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, mode: int = 0, epi: int = EPI_NONE,
               bias: Optional[torch.Tensor] = None, aux: Optional[torch.Tensor] = None,
               x0: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, bn: int = 0,
-              splits: int = 0, n: Optional[int] = None, k: Optional[int] = None,
-              colsum: Optional[torch.Tensor] = None) -> torch.Tensor:
+              splits: int = 0, n: Optional[int] = None, k: Optional[int] = None) -> torch.Tensor:
     """tcgen05 GEMM.
 
     mode 0: ``out[M,N] = epi(a[M,K] @ b[N,K].T)``; mode 1: ``out[M,N] (+)= a[K,M].T @ b[K,N]``
     (``out`` fp32, epi ``EPI_ATOMIC_F32``).  Operands are 2-D bf16 with unit inner stride; the
     leading dimensions are taken from ``stride(0)`` so column slices of wider buffers work.
-    ``colsum`` (fp32 ``[N]``, bf16 epilogues only): receives ``+= out.sum(0)``, i.e. the bias gradient of the
-    layer whose pre-activation gradient ``out`` is, for free in the epilogue.
     """
     _need_cuda(a, b, out)
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
@@ -53,7 +50,7 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, mode: int 
     assert out.shape[0] >= M and out.shape[1] >= N
     call("rs_gemm_bf16", ptr(a), ptr(b), ptr(out), ptr(bias), ptr(aux), ptr(x0), M, N, K, a.stride(0), b.stride(0),
          out.stride(0), aux.stride(0) if aux is not None else 0, x0.stride(0) if x0 is not None else 0, mode, epi,
-         bn, splits, ptr(colsum), ptr(status), stream_ptr())
+         bn, splits, ptr(status), stream_ptr())
     return out
 
 
