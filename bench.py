@@ -130,7 +130,7 @@ def run_native(args):
     rows = table_rows(args.seed)
     ctx = PeerContext(rank, world, device=torch.device(f"cuda:{local}"))
     cfg = DLRMConfig(table_rows=rows, batch=BATCH, emb_dim=DIM, emb_lr=0.01, mlp_lr=0.01, seed=args.seed,
-                     use_cuda_graph=not args.no_graph)
+                     use_cuda_graph=not args.no_graph, trace_phases=args.trace_phases)
     eng = DLRM(cfg, ctx)
     src = DLRMBatchSource(rows, [1] * TABLES, BATCH, alpha=ALPHA, seed=args.seed + 1)
     nb = 4
@@ -165,6 +165,16 @@ def run_native(args):
     torch.cuda.synchronize()
     ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3, world)
     eng.check()
+    if args.trace_phases:   # per-rank phase timeline of the last step (stamps cost one tiny launch each)
+        ph = eng.phase_times()
+        allph = [ph]
+        if world > 1:
+            import torch.distributed as dist
+            allph = [None] * world
+            dist.all_gather_object(allph, ph)
+        if rank == 0:
+            for k in ph:
+                print(f"[phases] {k:42s} " + " ".join(f"{p[k]:8.1f}" for p in allph) + "  us per rank", file=sys.stderr)
     h2d = batches[0].nbytes
     if rank == 0:
         out = {
@@ -264,6 +274,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference", "torch_baseline"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--trace-phases", action="store_true",
+                    help="stamp the GPU timer at phase boundaries of the step and print the timeline of every rank to stderr")
     args = ap.parse_args()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     if args.impl == "reference":

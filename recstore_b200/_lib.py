@@ -68,12 +68,13 @@ _SIGNATURES = {
     "rs_rows_scatter": (i32, [vp, vp, i64, i32, vp, vp]),
     # ops/interaction.cu
     "rs_interaction_forward": (i32, [vp, i32, i32, i32, vp, i32, vp]),
-    "rs_interaction_backward": (i32, [vp, vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, i64, i64, i32, vp, i32, vp]),
+    "rs_interaction_backward": (i32, [vp, vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, i64, i64, i32, vp, i32, i32, vp]),
     # ops/dense.cu
     "rs_head_bce": (i32, [vp, i32, i32, i32, vp, vp, vp, f32, vp, vp, vp, i32, vp, vp, vp]),
     "rs_colsum_bf16": (i32, [vp, i32, i32, i32, vp, vp]),
     "rs_dense_sgd": (i32, [vp, vp, i32, i32, f32, vp, i32, vp, i32, i32, vp]),
     "rs_vec_sgd": (i32, [vp, vp, i32, f32, i32, vp]),
+    "rs_dense_sgd_multi": (i32, [vp, vp, i32, i32, vp, vp, i32, f32, i32, vp]),
     "rs_pad_cast_bf16": (i32, [vp, i32, i32, i32, vp, i32, vp]),
     "rs_mse_fwd_bwd": (i32, [vp, vp, i32, f32, vp, vp, vp]),
     "rs_cross_fwd": (i32, [vp, vp, vp, vp, i64, vp]),
@@ -90,6 +91,7 @@ _SIGNATURES = {
     "rs_peer_wait": (i32, [vp, i32, i32, vp, u64, vp, vp]),
     "rs_allreduce_push": (i32, [vp, vp, i32, i32, i64, f32, vp]),
     "rs_memset_async": (i32, [vp, i32, sz, vp]),
+    "rs_stamp_time": (i32, [vp, vp]),
     "rs_read_status": (i32, [vp, C.POINTER(u64), i32]),
 }
 

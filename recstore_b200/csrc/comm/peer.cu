@@ -164,6 +164,22 @@ RS_API int rs_allreduce_push(const void* const* grads_of, void* const* reduced_o
   return RS_OK;
 }
 
+// One-thread kernel that stores the GPU's nanosecond timer: a time stamp that orders with the kernels around it on
+// the stream (and inside a captured graph), for phase-level timelines without a profiler.
+namespace {
+__global__ void stamp_kernel(unsigned long long* slot) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *slot = t;
+}
+}  // namespace
+RS_API int rs_stamp_time(unsigned long long* slot, cudaStream_t stream) {
+  RS_REQUIRE(slot != nullptr, "rs_stamp_time: null slot");
+  stamp_kernel<<<1, 1, 0, stream>>>(slot);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
 // Generic device helpers the Python layer needs without going through torch.
 RS_API int rs_memset_async(void* p, int value, size_t bytes, cudaStream_t stream) {
   RS_CUDA(cudaMemsetAsync(p, value, bytes, stream));

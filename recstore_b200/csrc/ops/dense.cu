@@ -194,6 +194,55 @@ __global__ void __launch_bounds__(256) dense_sgd_kernel(float* __restrict__ W, f
   }
 }
 
+// All layers of a model in one launch.  desc holds 8 int64 per layer: W, g, Wb, Wt (addresses), N, K, ldw, ldt;
+// tile_prefix[l] = first 32x32 tile of layer l; blocks past the last tile update the flat tail (biases, head).
+__global__ void __launch_bounds__(256) dense_sgd_multi_kernel(const long long* __restrict__ desc, const int* __restrict__ tile_prefix,
+                                                              int n_layers, float* __restrict__ tail_w, float* __restrict__ tail_g,
+                                                              int tail_n, float lr, int zero_grad) {
+  __shared__ float tile[32][33];
+  const int total = tile_prefix[n_layers];
+  int b = blockIdx.x;
+  if (b >= total) {
+    const int i = (b - total) * 256 + threadIdx.x;
+    if (i < tail_n) {
+      tail_w[i] -= lr * tail_g[i];
+      if (zero_grad) tail_g[i] = 0.f;
+    }
+    return;
+  }
+  int l = 0;
+  while (l + 1 < n_layers && tile_prefix[l + 1] <= b) ++l;
+  b -= tile_prefix[l];
+  const long long* d = desc + l * 8;
+  float* W = reinterpret_cast<float*>(d[0]);
+  float* g = reinterpret_cast<float*>(d[1]);
+  __nv_bfloat16* Wb = reinterpret_cast<__nv_bfloat16*>(d[2]);
+  __nv_bfloat16* Wt = reinterpret_cast<__nv_bfloat16*>(d[3]);
+  const int N = static_cast<int>(d[4]), K = static_cast<int>(d[5]), ldw = static_cast<int>(d[6]), ldt = static_cast<int>(d[7]);
+  const int tiles_k = (K + 31) / 32;
+  const int k0 = (b % tiles_k) * 32, n0 = (b / tiles_k) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int j = ty; j < 32; j += 8) {
+    const int n = n0 + j, k = k0 + tx;
+    float v = 0.f;
+    if (n < N && k < K) {
+      const size_t idx = static_cast<size_t>(n) * K + k;
+      v = W[idx] - lr * g[idx];
+      W[idx] = v;
+      if (zero_grad) g[idx] = 0.f;
+      if (Wb) Wb[static_cast<size_t>(n) * ldw + k] = __float2bfloat16(v);
+    }
+    tile[j][tx] = v;
+  }
+  __syncthreads();
+  if (Wt) {
+    for (int j = ty; j < 32; j += 8) {
+      const int k = k0 + j, n = n0 + tx;
+      if (n < N && k < K) Wt[static_cast<size_t>(k) * ldt + n] = __float2bfloat16(tile[tx][j]);
+    }
+  }
+}
+
 __global__ void vec_sgd_kernel(float* __restrict__ w, float* __restrict__ g, int n, float lr, int zero_grad) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
@@ -367,6 +416,18 @@ RS_API int rs_dense_sgd(float* W, float* g, int N, int K, float lr, void* Wb, in
   dim3 grid((K + 31) / 32, (N + 31) / 32);
   dense_sgd_kernel<<<grid, 256, 0, stream>>>(W, g, N, K, lr, reinterpret_cast<__nv_bfloat16*>(Wb), ldw,
                                              reinterpret_cast<__nv_bfloat16*>(Wt), ldt, zero_grad);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+// SGD step of every dense layer plus the flat tail in one launch (see dense_sgd_multi_kernel for the descriptor).
+RS_API int rs_dense_sgd_multi(const long long* desc, const int* tile_prefix, int n_layers, int total_tiles, float* tail_w,
+                              float* tail_g, int tail_n, float lr, int zero_grad, cudaStream_t stream) {
+  RS_REQUIRE(desc && tile_prefix && n_layers > 0 && total_tiles >= 0, "rs_dense_sgd_multi: bad argument");
+  RS_REQUIRE(tail_n == 0 || (tail_w && tail_g), "rs_dense_sgd_multi: tail pointers missing");
+  const int blocks = total_tiles + (tail_n + 255) / 256;
+  if (blocks == 0) return RS_OK;
+  dense_sgd_multi_kernel<<<blocks, 256, 0, stream>>>(desc, tile_prefix, n_layers, tail_w, tail_g, tail_n, lr, zero_grad);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

@@ -143,6 +143,7 @@ struct InterBwdArgs {
   int relu_mask_dx;           // feature 0 is a ReLU output: zero dx where it is not positive
   float* const* ndst;         // optional [world]: per-owner [B_global, nstride] sum of squares of each pushed row
   int nstride;
+  int rows;                   // 0 = every row; 1 = only feature 0 (dx); 2 = only the embedding rows (pushed to their owners)
 };
 
 constexpr int kWarpsBwd = 6;  // 17 KB of shared memory per warp: two CTAs (12 warps) per SM
@@ -195,8 +196,8 @@ __global__ void __launch_bounds__(kWarpsBwd * 32) interaction_bwd_kernel(const I
     dst_base[it] = nullptr;
     nrm_base[it] = nullptr;
     if (i == 0) {
-      dst_base[it] = a.dx + ochunk * 8;
-    } else if (i < F) {
+      if (a.rows != 2) dst_base[it] = a.dx + ochunk * 8;
+    } else if (i < F && a.rows != 1) {
       const int f = i - 1;
       dst_base[it] = reinterpret_cast<__nv_bfloat16*>(a.gdst[a.owner[f]]) + a.sample_base * a.grow_stride + a.gcol[f] + ochunk * 8;
       if (a.ndst) nrm_base[it] = a.ndst[a.owner[f]] + a.sample_base * a.nstride + a.gcol[f] / D;
@@ -329,8 +330,9 @@ RS_API int rs_interaction_forward(const void* T, int B, int F, int D, void* out,
 RS_API int rs_interaction_backward(const void* T, const void* dout, int B, int F, int D, int dout_ld, void* dx,
                                    int dx_ld, void* const* gdst, const int* owner, const int* gcol,
                                    long long grow_stride, long long sample_base, int relu_mask_dx,
-                                   void* const* ndst, int nstride, cudaStream_t stream) {
+                                   void* const* ndst, int nstride, int rows, cudaStream_t stream) {
   RS_REQUIRE(T && dout && dx && gdst && owner && gcol, "rs_interaction_backward: null argument");
+  RS_REQUIRE(rows >= 0 && rows <= 2, "rs_interaction_backward: rows must be 0 (all), 1 (feature 0) or 2 (embedding rows)");
   RS_REQUIRE(F >= 1 && F <= kMaxF && D % 16 == 0 && D >= 16 && D <= kMaxD, "rs_interaction_backward: F=%d D=%d unsupported", F, D);
   if (B == 0) return RS_OK;
   InterBwdArgs a;
@@ -340,7 +342,7 @@ RS_API int rs_interaction_backward(const void* T, const void* dout, int B, int F
   a.dx = reinterpret_cast<__nv_bfloat16*>(dx); a.dx_ld = dx_ld;
   a.gdst = gdst; a.owner = owner; a.gcol = gcol; a.grow_stride = grow_stride; a.sample_base = sample_base;
   a.relu_mask_dx = relu_mask_dx;
-  a.ndst = reinterpret_cast<float* const*>(ndst); a.nstride = nstride;
+  a.ndst = reinterpret_cast<float* const*>(ndst); a.nstride = nstride; a.rows = rows;
   RS_REQUIRE(dout_ld % 8 == 0 && dout_ld <= kDoutMax, "rs_interaction_backward: dout_ld=%d must be a multiple of 8, <= %d", dout_ld, kDoutMax);
   const size_t smem = static_cast<size_t>(kWarpsBwd) * kBwdWarpBytes;
   static bool attr_done = false;

@@ -26,6 +26,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import _lib
+from .._lib import call, stream_ptr
 from ..ops import functional as F_
 from ..parallel.peer import PeerContext
 
@@ -55,6 +56,7 @@ class DLRMConfig:
     interaction: str = "dot"                     # "dot" (DLRM) or "dcn" (DLRM-DCNv2: low-rank cross network)
     dcn_layers: int = 3
     dcn_rank: int = 512
+    trace_phases: bool = False                   # stamp the GPU timer at phase boundaries (see DLRM.phase_times)
 
     def __post_init__(self):
         if self.hotness is None:
@@ -245,6 +247,14 @@ class DLRM:
         self.head_w.copy_(torch.randn(self.head_K, generator=g) * math.sqrt(2.0 / (1 + self.head_K)))
         self.head_b.copy_(torch.randn(1, generator=g))
         self._refresh_bf16()
+        # descriptor of the one-launch SGD step over all layers (8 int64 per layer) and its tile prefix
+        desc, prefix = [], [0]
+        for L in layers:
+            desc += [L.w.data_ptr(), L.rw.data_ptr(), L.wb.data_ptr(), L.wt.data_ptr(), L.N, L.Kp, L.wb.stride(0), L.wt.stride(0)]
+            prefix.append(prefix[-1] + ((L.Kp + 31) // 32) * ((L.N + 31) // 32))
+        self._sgd_desc = torch.tensor(desc, dtype=torch.int64, device=dev)
+        self._sgd_prefix = torch.tensor(prefix, dtype=torch.int32, device=dev)
+        self._sgd_tiles = prefix[-1]
 
         # ---- activations and their gradients
         Bl = self.Bl
@@ -280,6 +290,10 @@ class DLRM:
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._step_no = 0
         self.launches_per_step = 0
+        self.s_wgrad = torch.cuda.Stream(device=dev)   # weight/bias gradients, then the dense all-reduce and SGD
+        self.s_comm = torch.cuda.Stream(device=dev)    # embedding lookup / gradient push: the NVLink-bound kernels
+        self._phase_names: List[str] = []
+        self._phase_buf = torch.zeros(64, dtype=torch.int64, device=dev)
         self._warm_native()
         torch.cuda.synchronize(dev)
         if self.world > 1:
@@ -316,25 +330,52 @@ class DLRM:
     def _count(self, n=1):
         self.launches_per_step += n
 
+    def _stamp(self, name: str):
+        """Phase boundary: with ``trace_phases`` a one-thread kernel stores the GPU timer here (also inside the graph)."""
+        if not self.cfg.trace_phases:
+            return
+        if name not in self._phase_names:
+            self._phase_names.append(name)
+        call("rs_stamp_time", self._phase_buf.data_ptr() + 8 * self._phase_names.index(name), stream_ptr())
+        self._count()
+
+    def phase_times(self) -> Dict[str, float]:
+        """Microseconds spent between consecutive phase stamps of the last completed step on this rank."""
+        assert self.cfg.trace_phases, "construct the engine with trace_phases=True"
+        torch.cuda.synchronize(self.dev)
+        t = self._phase_buf[:len(self._phase_names)].cpu().tolist()
+        return {f"{a}->{b}": (t[i + 1] - t[i]) / 1e3
+                for i, (a, b) in enumerate(zip(self._phase_names[:-1], self._phase_names[1:]))}
+
     # ------------------------------------------------------------------ the step as a launch sequence
     def _forward(self, slot: int):
         c, st = self.cfg, self.ctx.status
+        self._stamp("start")
         F_.pad_cast_bf16(self.in_dense[slot], self.x0p); self._count()
-        if self.Tl:
-            F_.emb_forward(self.weight, self.table_base, self.table_rows, self.in_ids[slot], hotness=self.hotness,
-                           hot_base=self.hot_base, T=self.Tl, B=self.B, D=self.D, B_local=self.Bl,
-                           dst_table=self.Twin.table, dst_row_stride=self.F * self.D, dst_col=self.dst_col,
-                           out_bf16=True, row_idx=self.row_idx, occ2bag=self.occ2bag, status=st)
-            self._count()
-        if self.world > 1:
-            self.ctx.signal(CH_FWD); self._count()
+        main = torch.cuda.current_stream(self.dev)
+        overlap = self.world > 1
+        if overlap:   # the lookup and its all-to-all (peer stores) run beside the bottom MLP
+            self.s_comm.wait_stream(main)
+        with torch.cuda.stream(self.s_comm if overlap else main):
+            if self.Tl:
+                F_.emb_forward(self.weight, self.table_base, self.table_rows, self.in_ids[slot], hotness=self.hotness,
+                               hot_base=self.hot_base, T=self.Tl, B=self.B, D=self.D, B_local=self.Bl,
+                               dst_table=self.Twin.table, dst_row_stride=self.F * self.D, dst_col=self.dst_col,
+                               out_bf16=True, row_idx=self.row_idx, occ2bag=self.occ2bag, status=st)
+                self._count()
+            if self.world > 1:
+                self.ctx.signal(CH_FWD); self._count()
+        self._stamp("emb_fwd_done")
         x = self.x0p
         for i, L in enumerate(self.bot):
             out = self.act_b[i] if i < len(self.bot) - 1 else self.Tbuf[:, :self.D]
             F_.gemm_bf16(x, L.wb, out, mode=0, epi=F_.EPI_RELU, bias=L.b, status=st, n=L.N); self._count()
             x = out
+        self._stamp("bot_fwd_done")
         if self.world > 1:
+            main.wait_stream(self.s_comm)
             self.ctx.wait(CH_FWD); self._count()
+        self._stamp("a2a_fwd_arrived")
         if self.dcn:
             for l in range(len(self.crossV)):
                 V, W = self.crossV[l], self.crossW[l]
@@ -344,6 +385,7 @@ class DLRM:
                 self._count(3)
         else:
             F_.interaction_forward(self.Tbuf, self.Bl, self.F, self.D, self.z); self._count()
+        self._stamp("interaction_fwd_done")
         x = self.z
         for i, L in enumerate(self.top):
             F_.gemm_bf16(x, L.wb, self.act_t[i], mode=0, epi=F_.EPI_RELU, bias=L.b, status=st); self._count()
@@ -354,26 +396,35 @@ class DLRM:
         c, st = self.cfg, self.ctx.status
         self.launches_per_step = 0
         x = self._forward(slot)
+        self._stamp("top_fwd_done")
         self._loss_dev[slot].zero_(); self._count()
         F_.head_bce(x, self.head_w, self.head_b, self.in_labels[slot], 1.0 / self.B, prob=self.prob,
                     loss_sum=self._loss_dev[slot], dx=self.d_act_t[-1], dw=self.g_head_w, db=self.g_head_b)
         self._count()
-        # ---- top MLP backward
+        self._stamp("head_done")
+        main = torch.cuda.current_stream(self.dev)
+        side = self.s_wgrad
+        # ---- top MLP backward.  The dgrad chain is the critical path; bias and weight gradients of a layer only need
+        # that layer's dY, so they run beside it on a second stream and fill the gaps and tails of the chain.
         for i in range(len(self.top) - 1, -1, -1):
             L = self.top[i]
             dy = self.d_act_t[i]
             xin = self.act_t[i - 1] if i > 0 else self.z
-            # Bias gradient as a pass of its own: summing columns inside the dgrad epilogue was measured slower
-            # (every CTA adds into the same N addresses) than this bandwidth-bound kernel.
-            F_.colsum_bf16(dy, L.gb); self._count()
-            F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                # Bias gradient as a pass of its own: summing columns inside the dgrad epilogue was measured slower
+                # (every CTA adds into the same N addresses) than this bandwidth-bound kernel.
+                F_.colsum_bf16(dy, L.gb); self._count()
+                F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
             if i > 0:
                 F_.gemm_bf16(dy, L.wt, self.d_act_t[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
             else:
                 F_.gemm_bf16(dy, L.wt, self.d_z, mode=0, epi=F_.EPI_NONE, status=st)
             self._count()
+        self._stamp("top_bwd_done")
         # ---- interaction backward: dense part stays, embedding gradients go to their owners
         if self.dcn:
+            main.wait_stream(side)                                # the scratch buffers below are shared with nothing on `side`
             dx = self.c_dx[0]                                     # dX_L from the over-arch
             for l in range(len(self.crossV) - 1, -1, -1):
                 V, W = self.crossV[l], self.crossW[l]
@@ -389,44 +440,70 @@ class DLRM:
             F_.push_feature_grads(self.c_dx0, dx, self.Tbuf, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
                                   self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl, relu_mask_dx=True,
                                   ndst_table=self.ndst_table, nstride=self.Tmax)
+            self._count()
+            if self.world > 1:
+                self.ctx.signal(CH_BWD); self._count()
+        elif self.world > 1:
+            # The gradient all-to-all (peer stores from the kernel) is bound by NVLink, not by the SMs: a first pass
+            # produces only the bottom MLP's input gradient, then the pass that pushes the embedding gradients runs
+            # on the communication stream beside the bottom MLP's backward.
+            F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
+                                    self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
+                                    relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax, rows=1)
+            self.s_comm.wait_stream(main)
+            with torch.cuda.stream(self.s_comm):
+                F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
+                                        self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
+                                        relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax, rows=2)
+                self.ctx.signal(CH_BWD)
+            self._count(3)
         else:
             F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
                                     self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
                                     relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax)
-        self._count()
-        if self.world > 1:
-            self.ctx.signal(CH_BWD); self._count()
+            self._count()
+        self._stamp("interaction_bwd_done")
         # ---- bottom MLP backward
         for i in range(len(self.bot) - 1, -1, -1):
             L = self.bot[i]
             dy = self.d_act_b[i]
             xin = self.act_b[i - 1] if i > 0 else self.x0p
-            F_.colsum_bf16(dy, L.gb); self._count()
-            F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                F_.colsum_bf16(dy, L.gb); self._count()
+                F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
             if i > 0:
                 F_.gemm_bf16(dy, L.wt, self.d_act_b[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
                 self._count()
-        if self.world > 1:
-            self.ctx.wait(CH_BWD); self._count()
+        self._stamp("bot_bwd_done")
+        # ---- dense gradients (complete once `side` has drained): all-reduce + SGD, beside the sparse optimizer
+        solo = self.world == 1
+        with torch.cuda.stream(side):
+            if not solo:
+                self.ctx.signal(CH_GRADS); self.ctx.wait(CH_GRADS)
+                F_.allreduce_push(self.Gflat.table, self.Rflat.table, self.world, self.rank, self.n_params)
+                self.ctx.signal(CH_REDUCED); self.ctx.wait(CH_REDUCED)
+                self._count(5)
+            call("rs_dense_sgd_multi", self._sgd_desc.data_ptr(), self._sgd_prefix.data_ptr(), len(self.layers), self._sgd_tiles,
+                 self.master[self.tail_off:].data_ptr(), self.reduced[self.tail_off:].data_ptr(), self.tail_n, c.mlp_lr,
+                 1 if solo else 0, stream_ptr())
+            self._count()
+            if not solo:
+                self.grads.zero_(); self._count()
         # ---- sparse optimizer on the owned rows
+        if self.world > 1:
+            main.wait_stream(self.s_comm)
+            self.ctx.wait(CH_BWD); self._count()
+        self._stamp("a2a_bwd_arrived")
         if self.Tl:
             F_.emb_backward(self.weight, self.state, self.row_idx, self.occ2bag, self.nnz, self.Gwin.local,
                             grad_col=self.grad_col, grad_row_stride=self.grow_stride, B=self.B, D=self.D,
                             grad_bf16=True, lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st,
                             gnorm=self.gnorm, gnorm_stride=self.Tmax)
             self._count(2 if c.emb_optimizer == "rowwise_adagrad" else 1)
-        # ---- dense gradients: all-reduce + SGD
-        if self.world > 1:
-            self.ctx.signal(CH_GRADS); self.ctx.wait(CH_GRADS)
-            F_.allreduce_push(self.Gflat.table, self.Rflat.table, self.world, self.rank, self.n_params)
-            self.ctx.signal(CH_REDUCED); self.ctx.wait(CH_REDUCED)
-            self._count(5)
-        solo = self.world == 1
-        for L in self.layers:
-            F_.dense_sgd(L.w, L.rw, c.mlp_lr, L.wb, L.wt, zero_grad=solo); self._count()
-        F_.vec_sgd(self.master[self.tail_off:], self.reduced[self.tail_off:], c.mlp_lr, zero_grad=solo); self._count()
-        if not solo:
-            self.grads.zero_(); self._count()
+        self._stamp("emb_bwd_done")
+        main.wait_stream(side)
+        self._stamp("sgd_done")
 
     # ------------------------------------------------------------------ public API
     def submit(self, batch: PinnedBatch) -> StepHandle:

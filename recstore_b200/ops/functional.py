@@ -98,15 +98,17 @@ def interaction_forward(T, B: int, F: int, D: int, out) -> torch.Tensor:
 
 
 def interaction_backward(T, dout, B: int, F: int, D: int, dx, gdst_table, owner, gcol, grow_stride: int,
-                         sample_base: int, relu_mask_dx: bool = True, ndst_table=None, nstride: int = 0) -> None:
-    """Backward of :func:`interaction_forward`.  Row 0 of dT goes to ``dx``; row f>=1 of sample b is stored
+                         sample_base: int, relu_mask_dx: bool = True, ndst_table=None, nstride: int = 0,
+                         rows: int = 0) -> None:
+    """Backward of :func:`interaction_forward`.  ``rows``: 0 = everything, 1 = only ``dx`` (so that the bottom MLP can
+    start its backward early), 2 = only the embedding rows.  Row 0 of dT goes to ``dx``; row f>=1 of sample b is stored
     at ``gdst_table[owner[f-1]] + (sample_base + b) * grow_stride + gcol[f-1]`` (bf16).  With
     ``ndst_table`` the sum of squares of each stored row also goes to
     ``ndst_table[owner[f-1]][(sample_base + b) * nstride + gcol[f-1] // D]`` (fp32)."""
     _need_cuda(T, dout, dx)
     call("rs_interaction_backward", ptr(T), ptr(dout), B, F, D, dout.stride(0), ptr(dx), dx.stride(0),
          ptr(gdst_table), ptr(owner), ptr(gcol), grow_stride, sample_base, 1 if relu_mask_dx else 0,
-         ptr(ndst_table), nstride, stream_ptr())
+         ptr(ndst_table), nstride, rows, stream_ptr())
 
 
 def head_bce(x, w, bias, labels, inv_batch: float, *, prob=None, loss_sum=None, dx=None, dw=None, db=None) -> None:
