@@ -1,0 +1,102 @@
+"""Parameter-server client benchmark: closed loop with a window of requests in flight, or open loop (Poisson).
+
+    python -m recstore_b200.bench.ps_client --threads 4 --window 4 --batch 500 --alpha 0.99 --seconds 3
+    python -m recstore_b200.bench.ps_client --poisson-rate 2000 --seconds 3
+
+Starts an in-process server shard on a loopback port unless ``--host/--port`` point at a running one.  Prints the
+throughput once per second and a JSON summary, like the reference's closed-loop client benchmark
+(src/benchmark/benchmark_client_common.h:16-292: async window, zipf or dataset keys, per-second print).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import threading
+import time
+
+import numpy as np
+import torch
+
+from ..ps import ParameterClient, ParameterServer
+from ..ps.load_generator import DatasetReplay, PoissonLoadGenerator, zipf_key_source
+
+
+def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, seconds, dataset=None, quiet=False):
+    done = [0] * threads
+    stop = threading.Event()
+
+    def worker(t):
+        c = ParameterClient(host, port, 0, dim)
+        c.InitThread(window)
+        src = iter(DatasetReplay(dataset)) if dataset else zipf_key_source(key_space, batch, alpha, seed=t + 1)
+        inflight = []
+        while not stop.is_set():
+            while len(inflight) < window:
+                k = next(src)
+                inflight.append((c.GetParameterAsync(k), k.numel()))
+            rid, n = inflight.pop(0)
+            c.WaitRPCFinish(rid)
+            c.RevokeRPCResource(rid)
+            done[t] += n
+        for rid, _ in inflight:
+            c.WaitRPCFinish(rid)
+        c.close()
+
+    ths = [threading.Thread(target=worker, args=(t,)) for t in range(threads)]
+    t0 = time.perf_counter()
+    for th in ths:
+        th.start()
+    last, last_t = 0, t0
+    per_sec = []
+    while time.perf_counter() - t0 < seconds:
+        time.sleep(min(1.0, max(0.05, seconds - (time.perf_counter() - t0))))
+        now, tot = time.perf_counter(), sum(done)
+        rate = (tot - last) / (now - last_t)
+        per_sec.append(rate)
+        if not quiet:
+            print(f"[ps_client] {rate / 1e6:8.3f} M keys/s", flush=True)
+        last, last_t = tot, now
+    stop.set()
+    for th in ths:
+        th.join()
+    el = time.perf_counter() - t0
+    return {"mode": "closed", "threads": threads, "window": window, "batch": batch, "keys_per_s": sum(done) / el,
+            "per_second": per_sec, "seconds": el}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--host", default=None)
+    ap.add_argument("--port", type=int, default=0)
+    ap.add_argument("--dim", type=int, default=32)
+    ap.add_argument("--threads", type=int, default=2)
+    ap.add_argument("--window", type=int, default=4, help="requests in flight per thread")
+    ap.add_argument("--batch", type=int, default=500)
+    ap.add_argument("--alpha", type=float, default=0.99)
+    ap.add_argument("--key-space", type=int, default=1_000_000)
+    ap.add_argument("--seconds", type=float, default=3.0)
+    ap.add_argument("--dataset", default=None, help="replay key batches from this file instead of Zipf keys")
+    ap.add_argument("--poisson-rate", type=float, default=0.0, help="open loop: requests per second (0 = closed loop)")
+    ap.add_argument("--engine", default="KVEngineMap")
+    a = ap.parse_args(argv)
+    srv = None
+    host, port = a.host, a.port
+    if host is None:
+        srv = ParameterServer(a.engine, {"capacity": int(a.key_space * 1.5), "dim": a.dim})
+        srv.LoadFakeData(a.key_space)
+        host, port = "127.0.0.1", srv.serve(0)
+    try:
+        if a.poisson_rate > 0:
+            src = iter(DatasetReplay(a.dataset)) if a.dataset else zipf_key_source(a.key_space, a.batch, a.alpha)
+            gen = PoissonLoadGenerator(lambda: ParameterClient(host, port, 0, a.dim), src, a.poisson_rate, senders=a.threads)
+            out = {"mode": "poisson", "rate": a.poisson_rate, **gen.run(a.seconds).summary()}
+        else:
+            out = closed_loop(host, port, a.dim, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset)
+        print(json.dumps(out), flush=True)
+    finally:
+        if srv is not None:
+            srv.close()
+
+
+if __name__ == "__main__":
+    main()

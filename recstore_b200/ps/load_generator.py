@@ -1,0 +1,125 @@
+"""Open-loop load generation for a parameter server: Poisson arrivals, Zipf or replayed keys.
+
+``PoissonLoadGenerator`` issues ``GetParameter`` requests at exponentially distributed intervals of a given rate from
+a pool of sender threads and records each request's latency (queueing included), as the reference's load generator
+does against its PS (src/grpc_ps/python_client/loadGenerator.py:16-79).  ``DatasetReplay`` iterates key batches of a
+recorded trace: a text file with one request per line (ids separated by spaces or commas), or a ``.npy`` pair of ids
+and offsets (src/grpc_ps/python_client/dataset.py:5-29).
+"""
+from __future__ import annotations
+
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import dataclass, field
+from typing import Callable, Iterator, List, Optional
+
+import numpy as np
+import torch
+
+from ..utils.data import zipf_ids
+
+
+class DatasetReplay:
+    def __init__(self, path: str, offsets_path: Optional[str] = None, loop: bool = True):
+        self.loop = loop
+        if path.endswith(".npy"):
+            ids = np.load(path).astype(np.int64).reshape(-1)
+            if offsets_path:
+                off = np.load(offsets_path).astype(np.int64).reshape(-1)
+                if off[-1] != ids.size:
+                    off = np.concatenate([off, [ids.size]])
+            else:
+                off = np.arange(0, ids.size + 1, 26 if ids.size % 26 == 0 else 1)
+            self.batches = [ids[off[i]:off[i + 1]] for i in range(off.size - 1)]
+        else:
+            self.batches = []
+            with open(path) as f:
+                for line in f:
+                    toks = line.replace(",", " ").split()
+                    if toks:
+                        self.batches.append(np.array([int(t) for t in toks], dtype=np.int64))
+        if not self.batches:
+            raise ValueError(f"no requests in {path}")
+
+    def __len__(self):
+        return len(self.batches)
+
+    def __iter__(self) -> Iterator[torch.Tensor]:
+        while True:
+            for b in self.batches:
+                yield torch.from_numpy(b)
+            if not self.loop:
+                return
+
+
+def zipf_key_source(key_space: int, batch: int, alpha: float, seed: int = 0) -> Iterator[torch.Tensor]:
+    rng = np.random.default_rng(seed)
+    while True:
+        yield torch.from_numpy(zipf_ids(batch, key_space, alpha, rng))
+
+
+@dataclass
+class LoadReport:
+    sent: int = 0
+    completed: int = 0
+    keys: int = 0
+    seconds: float = 0.0
+    latencies_ms: List[float] = field(default_factory=list)
+
+    def summary(self) -> dict:
+        lat = np.array(self.latencies_ms) if self.latencies_ms else np.zeros(1)
+        return {"sent": self.sent, "completed": self.completed, "offered_rps": self.sent / max(self.seconds, 1e-9),
+                "achieved_rps": self.completed / max(self.seconds, 1e-9), "keys_per_s": self.keys / max(self.seconds, 1e-9),
+                "lat_ms_mean": float(lat.mean()), "lat_ms_p50": float(np.percentile(lat, 50)),
+                "lat_ms_p99": float(np.percentile(lat, 99)), "lat_ms_max": float(lat.max())}
+
+
+class PoissonLoadGenerator:
+    """``run(seconds)`` sends requests with exponential inter-arrival times of mean ``1 / rate`` (requests / s)."""
+
+    def __init__(self, make_client: Callable[[], object], keys: Iterator[torch.Tensor], rate: float, senders: int = 4,
+                 seed: int = 0):
+        self.make_client, self.keys, self.rate, self.senders = make_client, keys, float(rate), senders
+        self.rng = np.random.default_rng(seed)
+        self._local = threading.local()
+        self._clients: List[object] = []
+        self._lock = threading.Lock()
+
+    def _client(self):
+        c = getattr(self._local, "c", None)
+        if c is None:
+            c = self._local.c = self.make_client()
+            with self._lock:
+                self._clients.append(c)
+        return c
+
+    def _one(self, k: torch.Tensor, t_arrival: float, rep: LoadReport):
+        self._client().GetParameter(k)
+        dt = (time.perf_counter() - t_arrival) * 1e3
+        with self._lock:
+            rep.completed += 1
+            rep.keys += k.numel()
+            rep.latencies_ms.append(dt)
+
+    def run(self, seconds: float) -> LoadReport:
+        rep = LoadReport()
+        t0 = time.perf_counter()
+        nxt = t0
+        with ThreadPoolExecutor(max_workers=self.senders) as pool:
+            while True:
+                nxt += self.rng.exponential(1.0 / self.rate)
+                if nxt - t0 > seconds:
+                    break
+                d = nxt - time.perf_counter()
+                if d > 0:
+                    time.sleep(d)
+                pool.submit(self._one, next(self.keys), nxt, rep)   # latency counts from the scheduled arrival
+                rep.sent += 1
+        rep.seconds = time.perf_counter() - t0
+        for c in self._clients:
+            close = getattr(c, "close", None)
+            if close:
+                close()
+        self._clients = []
+        return rep

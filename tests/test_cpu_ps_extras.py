@@ -1,0 +1,93 @@
+"""Bags over PS rows, load generation, dataset replay and the native engine benchmark (CPU only)."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from recstore_b200.ps import ParameterClient, ParameterServer
+from recstore_b200.ps.embedding_bag import PSEmbeddingBagModule, pool_rows
+from recstore_b200.ps.load_generator import DatasetReplay, PoissonLoadGenerator, zipf_key_source
+
+
+@pytest.mark.parametrize("mode", ["sum", "mean", "max"])
+@pytest.mark.parametrize("padding_idx", [None, 3])
+def test_pool_rows_matches_torch_embedding_bag(mode, padding_idx):
+    g = torch.Generator().manual_seed(0)
+    N, D = 20, 8
+    w = torch.randn(N, D, generator=g)
+    idx = torch.randint(0, N, (37,), generator=g)
+    idx[::5] = 3
+    offsets = torch.tensor([0, 4, 4, 9, 20, 30])            # one empty bag
+    psw = torch.rand(37, generator=g) if mode == "sum" else None
+    ref_mod = torch.nn.EmbeddingBag(N, D, mode=mode, padding_idx=padding_idx)
+    with torch.no_grad():
+        ref_mod.weight.copy_(w)
+    ref = ref_mod(idx, offsets, per_sample_weights=psw)
+    rows = w[idx].clone().requires_grad_(True)
+    out = pool_rows(rows, idx, offsets, mode, psw, padding_idx)
+    assert torch.allclose(out, ref, atol=1e-6)
+    # gradients w.r.t. the table agree once row gradients are scattered back
+    ref.sum().backward()
+    out.sum().backward()
+    gt = torch.zeros(N, D).index_add(0, idx, rows.grad)
+    assert torch.allclose(gt, ref_mod.weight.grad, atol=1e-6)
+
+
+def test_pool_rows_matrix_and_last_offset():
+    w = torch.arange(40, dtype=torch.float32).view(10, 4)
+    idx2 = torch.tensor([[1, 2, 3], [4, 5, 6]])
+    out = pool_rows(w[idx2.reshape(-1)], idx2, None, "sum")
+    assert torch.equal(out, w[idx2].sum(1))
+    idx = torch.tensor([0, 1, 2, 3, 4])
+    out = pool_rows(w[idx], idx, torch.tensor([0, 2, 5]), "mean", include_last_offset=True)
+    assert torch.allclose(out, torch.stack([w[:2].mean(0), w[2:5].mean(0)]))
+
+
+def test_ps_bag_module_updates_rows_on_server():
+    srv = ParameterServer("KVEngineMap", {"capacity": 1000, "dim": 4, "optimizer": "sgd", "lr": 0.5})
+    port = srv.serve(0)
+    c = ParameterClient("127.0.0.1", port, 0, 4)
+    try:
+        keys = torch.arange(10)
+        c.PutParameter(keys + 100, torch.ones(10, 4))
+        bag = PSEmbeddingBagModule(c, 10, 4, mode="sum", padding_idx=0, key_offset=100)
+        out = bag(torch.tensor([0, 1, 2, 2]), torch.tensor([0, 2]))
+        assert torch.allclose(out, torch.tensor([[1.0] * 4, [2.0] * 4]))
+        out.sum().backward()
+        assert bag.step() == 3                                 # the padding row is neither read into the sum nor updated
+        after = c.GetParameter(keys + 100)
+        assert torch.allclose(after[0], torch.ones(4)) and not torch.allclose(after[2], torch.ones(4))
+    finally:
+        c.close()
+        srv.close()
+
+
+def test_dataset_replay_and_poisson_generator(tmp_path):
+    p = tmp_path / "trace.txt"
+    p.write_text("1 2 3\n4,5\n\n6\n")
+    rep = DatasetReplay(str(p), loop=False)
+    assert [b.tolist() for b in rep] == [[1, 2, 3], [4, 5], [6]]
+    np.save(tmp_path / "ids.npy", np.arange(12))
+    np.save(tmp_path / "off.npy", np.array([0, 5, 12]))
+    rep = DatasetReplay(str(tmp_path / "ids.npy"), str(tmp_path / "off.npy"), loop=False)
+    assert [b.numel() for b in rep] == [5, 7]
+    srv = ParameterServer("KVEngineMap", {"capacity": 5000, "dim": 8})
+    srv.LoadFakeData(2000)
+    port = srv.serve(0)
+    try:
+        gen = PoissonLoadGenerator(lambda: ParameterClient("127.0.0.1", port, 0, 8), zipf_key_source(2000, 16, 0.9), rate=400,
+                                   senders=2, seed=1)
+        s = gen.run(0.5).summary()
+        assert s["completed"] == s["sent"] > 50 and s["lat_ms_p99"] >= s["lat_ms_p50"] > 0
+    finally:
+        srv.close()
+
+
+def test_native_engine_benchmark_and_zipf_check():
+    from recstore_b200.bench.kv_engine import run_engine, zipf_check
+    r = run_engine("KVEngineMap", threads=2, seconds=0.2, batch=32, alpha=0.9, read_ratio=0.8, key_space=5000)
+    assert r["get_mkvs"] > 0 and r["put_mkvs"] > 0 and 0.99 <= r["hit_ratio"] <= 1.0
+    z = zipf_check(100000, 1.2, n=200000, top=10)
+    assert abs(z["mass"] - z["expected"]) < 0.01
+    json.dumps(r)
