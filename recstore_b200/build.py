@@ -47,10 +47,27 @@ def _cuda_home() -> Path:
     return Path("/usr/local/cuda")
 
 
+PRELOAD_DIR = CSRC / "preload"          # LD_PRELOAD shims: one small library each, never part of the main one
+UVM_SHIM_PATH = PKG_DIR / "lib" / "librecstore_uvm_intercept.so"
+
+
 def _sources():
-    cu = sorted(CSRC.rglob("*.cu"))
-    cpp = sorted(CSRC.rglob("*.cpp"))
+    cu = sorted(p for p in CSRC.rglob("*.cu") if PRELOAD_DIR not in p.parents)
+    cpp = sorted(p for p in CSRC.rglob("*.cpp") if PRELOAD_DIR not in p.parents)
     return cu, cpp
+
+
+def build_preload_shims(verbose: bool = False) -> Path:
+    """Builds the cudaMalloc -> cudaMallocManaged interposer (no CUDA needed at build time)."""
+    src = PRELOAD_DIR / "uvm_intercept.cpp"
+    UVM_SHIM_PATH.parent.mkdir(parents=True, exist_ok=True)
+    if not UVM_SHIM_PATH.exists() or UVM_SHIM_PATH.stat().st_mtime < src.stat().st_mtime:
+        rc, out = _run([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+                        str(src), "-o", str(UVM_SHIM_PATH), "-ldl"], verbose)
+        if rc != 0:
+            print(out, file=sys.stderr)
+            raise RuntimeError("building the UVM interposer failed")
+    return UVM_SHIM_PATH
 
 
 def _headers_digest() -> str:
@@ -150,6 +167,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False, job
         if rc != 0:
             print(out, file=sys.stderr)
             raise RuntimeError("link failed")
+    build_preload_shims(verbose)
     return LIB_PATH
 
 
