@@ -1,0 +1,39 @@
+"""Command-line drivers end to end on CPU (gloo, two worker processes each)."""
+import numpy as np
+import pytest
+
+
+def test_perf_emb_differential_two_workers():
+    from recstore_b200.cli import perf_emb
+    out = perf_emb.main(["--num_workers", "2", "--device", "cpu", "--run_steps", "12", "--num_embs", "5000", "--emb_dim", "8",
+                         "--batch_size", "200", "--L", "4", "--diff_test", "--log_interval", "100"])
+    if out is not None:
+        for r, v in dict(out).items():
+            assert v[0] == 12 and v[1] < 1e-4, (r, v)
+
+
+@pytest.mark.parametrize("mode", ["CppSync", "CppAsyncV2"])
+def test_perf_rec_model_matches_golden(mode):
+    from recstore_b200.cli import perf_rec_model
+    out = perf_rec_model.main(["--num_workers", "2", "--device", "cpu", "--run_steps", "10", "--dataset", "avazu", "--num_embs", "8000",
+                               "--emb_dim", "8", "--batch_size", "64", "--L", "3", "--diff_test", "--backwardMode", mode,
+                               "--with_nn", "16,1", "--log_interval", "100"])
+    assert len(out) == 2
+    for r, (steps, worst, loss) in out.items():
+        assert steps == 10 and worst < 1e-4 and np.isfinite(loss), (r, steps, worst, loss)
+
+
+def test_rec_dataset_loader_reads_files_and_synthesises(tmp_path):
+    from recstore_b200.utils.rec_dataset import RecDatasetLoader
+    ids = np.random.default_rng(0).integers(0, 5, size=(50, 21))
+    np.save(tmp_path / "avazu.npy", ids)
+    np.save(tmp_path / "avazu_offsets.npy", np.arange(0, 22) * 5)
+    l0 = RecDatasetLoader("avazu", 8, root=str(tmp_path), rank=0, world=2)
+    l1 = RecDatasetLoader("avazu", 8, root=str(tmp_path), rank=1, world=2)
+    b0, b1 = l0.next_batch(), l1.next_batch()
+    assert b0.shape == (8, 21) and l0.num_embeddings == 105
+    assert (b0.numpy() == ids[0:8] + np.arange(21) * 5).all() and (b1.numpy() == ids[8:16] + np.arange(21) * 5).all()
+    s = RecDatasetLoader("criteo", 16, synthetic_total=10000)
+    b = s.next_batch()
+    assert b.shape == (16, 26) and s.synthetic and int(b.max()) < s.num_embeddings
+    assert (b.numpy() >= s.offsets[:-1]).all() and (b.numpy() < s.offsets[1:]).all()
