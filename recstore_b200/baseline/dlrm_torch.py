@@ -66,6 +66,8 @@ class TorchDLRM:
         g = torch.Generator(device="cpu").manual_seed(seed)
         self.params: Dict[str, torch.Tensor] = {}
         self.interaction = interaction
+        self._num_dense, self._bottom_mlp, self._top_mlp = num_dense, list(bottom_mlp), list(top_mlp)
+        self._dcn_layers, self._dcn_rank = dcn_layers, dcn_rank
         n_inter = (self.T + 1) * emb_dim if interaction == "dcn" else emb_dim + (self.T + 1) * self.T // 2
         kb = [num_dense] + list(bottom_mlp[:-1])
         for i, (k, n) in enumerate(zip(kb, bottom_mlp)):
@@ -155,6 +157,26 @@ class TorchDLRM:
         return logit.float().squeeze(1)
 
     # -------------------------------------------------------------- one training step
+    # ---- state access shared with the GPU engine (checkpoints move between the two)
+    def describe(self) -> dict:
+        return {"table_rows": list(self.table_rows), "emb_dim": self.D, "hotness": list(self.hotness),
+                "num_dense": self._num_dense, "bottom_mlp": list(self._bottom_mlp), "top_mlp": list(self._top_mlp),
+                "interaction": self.interaction, "dcn_layers": self._dcn_layers, "dcn_rank": self._dcn_rank}
+
+    def dense_state(self) -> Dict[str, torch.Tensor]:
+        return {k: v.detach().clone() for k, v in self.params.items()}
+
+    def load_dense_state(self, sd: Dict[str, torch.Tensor]) -> None:
+        with torch.no_grad():
+            for k, v in self.params.items():
+                v.copy_(sd[k].view_as(v))
+
+    def table_weight(self, t: int) -> torch.Tensor:
+        return self.tables[t]
+
+    def table_state(self, t: int) -> torch.Tensor:
+        return self.states[t]
+
     def train_step(self, dense: torch.Tensor, ids: Sequence[torch.Tensor], labels: torch.Tensor) -> torch.Tensor:
         """``dense`` [B, nd], ``ids`` per table [B*hot], ``labels`` [B]: the GLOBAL batch."""
         lo, hi = self.rank * self.Bl, (self.rank + 1) * self.Bl

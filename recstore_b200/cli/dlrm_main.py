@@ -1,0 +1,196 @@
+"""DLRM training driver with the flag names of the reference's ``dlrm_model.py``.
+
+    python -m recstore_b200.cli.dlrm_main --arch-sparse-feature-size 64 --arch-embedding-size 1000-2000-500 \
+        --arch-mlp-bot 13-128-64 --arch-mlp-top 128-64-1 --mini-batch-size 2048 --num-batches 100 --use-gpu
+
+Recognised flags (src/executable/dlrm/dlrm_model.py:618-760): ``--arch-sparse-feature-size --arch-embedding-size
+--arch-mlp-bot --arch-mlp-top --arch-interaction-op dot|dcn --mini-batch-size --nepochs --num-batches
+--learning-rate --num-indices-per-lookup --num-indices-per-lookup-fixed --data-generation random|synthetic
+--numpy-rand-seed --print-freq --test-freq --test-mini-batch-size --save-model --load-model --use-gpu``, plus
+``--emb-learning-rate --emb-optimizer --zipf-alpha --dcn-layers --dcn-rank``.  The first number of
+``--arch-mlp-bot`` is the count of dense features, its last must equal the sparse feature size; the first number of
+``--arch-mlp-top`` is the interaction width and is checked, as the reference does (:914-951).
+
+With ``--use-gpu`` the native engine runs (one process per GPU under ``torch.distributed.run``); without it the
+PyTorch restatement runs on the CPU, same data, same checkpoints.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+
+
+def dash_ints(s: str):
+    return [int(x) for x in s.split("-") if x != ""]
+
+
+def parse_args(argv=None):
+    p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    p.add_argument("--arch-sparse-feature-size", type=int, default=16)
+    p.add_argument("--arch-embedding-size", type=dash_ints, default=[4, 3, 2])
+    p.add_argument("--arch-mlp-bot", type=dash_ints, default=[4, 16])
+    p.add_argument("--arch-mlp-top", type=dash_ints, default=None, help="default: <interaction width>-64-1")
+    p.add_argument("--arch-interaction-op", choices=["dot", "dcn"], default="dot")
+    p.add_argument("--dcn-layers", type=int, default=3)
+    p.add_argument("--dcn-rank", type=int, default=64)
+    p.add_argument("--mini-batch-size", type=int, default=128)
+    p.add_argument("--nepochs", type=int, default=1)
+    p.add_argument("--num-batches", type=int, default=50)
+    p.add_argument("--learning-rate", type=float, default=0.01)
+    p.add_argument("--emb-learning-rate", type=float, default=None)
+    p.add_argument("--emb-optimizer", choices=["rowwise_adagrad", "sgd"], default="rowwise_adagrad")
+    p.add_argument("--num-indices-per-lookup", type=int, default=1)
+    p.add_argument("--num-indices-per-lookup-fixed", action="store_true", default=True)
+    p.add_argument("--data-generation", choices=["random", "synthetic"], default="random",
+                   help="random: uniform ids; synthetic: Zipf ids (--zipf-alpha)")
+    p.add_argument("--zipf-alpha", type=float, default=1.2)
+    p.add_argument("--numpy-rand-seed", type=int, default=123)
+    p.add_argument("--print-freq", type=int, default=10)
+    p.add_argument("--test-freq", type=int, default=0)
+    p.add_argument("--test-mini-batch-size", type=int, default=0)
+    p.add_argument("--save-model", default="")
+    p.add_argument("--load-model", default="")
+    p.add_argument("--use-gpu", action="store_true")
+    return p.parse_args(argv)
+
+
+def interaction_width(args) -> int:
+    T, D = len(args.arch_embedding_size), args.arch_sparse_feature_size
+    return (T + 1) * D if args.arch_interaction_op == "dcn" else D + (T + 1) * T // 2
+
+
+def validate(args):
+    D = args.arch_sparse_feature_size
+    if args.arch_mlp_bot[-1] != D:
+        sys.exit(f"ERROR: arch-sparse-feature-size {D} does not match last dim of bottom mlp {args.arch_mlp_bot[-1]}")
+    w = interaction_width(args)
+    if args.arch_mlp_top is None:
+        args.arch_mlp_top = [w, 64, 1]
+    if args.arch_mlp_top[0] != w:
+        sys.exit(f"ERROR: # of feature interactions {w} does not match first dimension of top mlp {args.arch_mlp_top[0]}")
+    if args.arch_mlp_top[-1] != 1:
+        sys.exit("ERROR: the top mlp must end in one output")
+
+
+class _CpuModel:
+    """Adapter giving the PyTorch restatement the engine's train_step / predict signature."""
+
+    def __init__(self, m):
+        self.m = m
+        self.rank, self.world = m.rank, m.world
+
+    def train_step(self, b):
+        return float(self.m.train_step(b.dense, b.ids, b.labels))
+
+    def predict(self, b):
+        return self.m.predict(b.dense, b.ids)
+
+    def save(self, path, step):
+        from recstore_b200.models.checkpoint import save_checkpoint
+        save_checkpoint(self.m, path, step)
+
+    def load(self, path):
+        from recstore_b200.models.checkpoint import load_checkpoint
+        return load_checkpoint(self.m, path)
+
+
+class _GpuModel:
+    def __init__(self, eng):
+        self.e = eng
+        self.rank, self.world = eng.rank, eng.world
+
+    def _pin(self, b):
+        return self.e.make_pinned_batch(b.dense, b.ids, b.labels)
+
+    def train_step(self, b):
+        return self.e.train_step(self._pin(b))
+
+    def predict(self, b):
+        return self.e.predict(self._pin(b)).float().cpu()
+
+    def save(self, path, step):
+        self.e.save_checkpoint(path, step)
+
+    def load(self, path):
+        return self.e.load_checkpoint(path)
+
+
+def run(args) -> dict:
+    validate(args)
+    from recstore_b200.utils.data import DLRMBatchSource
+    rows, D = args.arch_embedding_size, args.arch_sparse_feature_size
+    hot = [args.num_indices_per_lookup] * len(rows)
+    nd = args.arch_mlp_bot[0]
+    kw = dict(emb_dim=D, hotness=hot, num_dense=nd, bottom_mlp=tuple(args.arch_mlp_bot[1:]), top_mlp=tuple(args.arch_mlp_top[1:]),
+              emb_lr=args.emb_learning_rate if args.emb_learning_rate is not None else args.learning_rate,
+              emb_optimizer=args.emb_optimizer, mlp_lr=args.learning_rate, seed=args.numpy_rand_seed,
+              interaction=args.arch_interaction_op, dcn_layers=args.dcn_layers, dcn_rank=args.dcn_rank)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if args.use_gpu:
+        from recstore_b200.models.dlrm import DLRM, DLRMConfig
+        from recstore_b200.parallel.peer import PeerContext
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        if world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        ctx = PeerContext(rank, world, device=torch.device(f"cuda:{local}"))
+        model = _GpuModel(DLRM(DLRMConfig(table_rows=rows, batch=args.mini_batch_size, **kw), ctx))
+    else:
+        from recstore_b200.baseline.dlrm_torch import TorchDLRM
+        model = _CpuModel(TorchDLRM(rows, args.mini_batch_size, device="cpu", rank=0, world=1, **kw))
+    alpha = args.zipf_alpha if args.data_generation == "synthetic" else 0.0
+    src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 1)
+    test_src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 2)
+    step0 = 0
+    if args.load_model:
+        step0 = int(model.load(args.load_model).get("step", 0))
+        if rank == 0:
+            print(f"Loaded checkpoint {args.load_model} (step {step0})", flush=True)
+    losses, t0, done = [], time.time(), 0
+    test_acc = None
+    for ep in range(args.nepochs):
+        for j in range(args.num_batches):
+            b = src.next()
+            loss = model.train_step(b)
+            losses.append(loss)
+            done += 1
+            if rank == 0 and args.print_freq and done % args.print_freq == 0:
+                el = (time.time() - t0) / done * 1e3
+                print(f"Finished training it {j + 1}/{args.num_batches} of epoch {ep}, {el:.2f} ms/it, "
+                      f"loss {np.mean(losses[-args.print_freq:]):.6f}", flush=True)
+            if args.test_freq and done % args.test_freq == 0:
+                tb = test_src.next()
+                lo, hi = (model.rank * (args.mini_batch_size // model.world), (model.rank + 1) * (args.mini_batch_size // model.world))
+                p = model.predict(tb).reshape(-1)
+                test_acc = float(((p > 0.5).float() == tb.labels[lo:hi]).float().mean())
+                if rank == 0:
+                    print(f"Testing at - {done}: accuracy {test_acc * 100:.3f} % (rank 0 share)", flush=True)
+    if args.save_model:
+        model.save(args.save_model, step0 + done)
+        if rank == 0:
+            print(f"Saved checkpoint {args.save_model}", flush=True)
+    out = {"steps": done, "first_loss": losses[0] if losses else None, "last_loss": losses[-1] if losses else None,
+           "mean_last_10": float(np.mean(losses[-10:])) if losses else None, "test_accuracy": test_acc}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if args.use_gpu and world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    return out
+
+
+def main(argv=None):
+    return run(parse_args(argv))
+
+
+if __name__ == "__main__":
+    main()

@@ -602,6 +602,24 @@ class DLRM:
         self.head_b.copy_(sd["head.bias"].reshape(-1))
         self._refresh_bf16()
 
+    def describe(self) -> dict:
+        """Shape of the model, as stored beside a checkpoint."""
+        c = self.cfg
+        return {"table_rows": list(c.table_rows), "emb_dim": c.emb_dim, "hotness": list(c.hotness), "num_dense": c.num_dense,
+                "bottom_mlp": list(c.bottom_mlp), "top_mlp": list(c.top_mlp), "interaction": c.interaction,
+                "dcn_layers": c.dcn_layers, "dcn_rank": c.dcn_rank}
+
+    def save_checkpoint(self, path: str, step: int = 0) -> None:
+        from .checkpoint import save_checkpoint
+        torch.cuda.synchronize(self.dev)
+        save_checkpoint(self, path, step)
+
+    def load_checkpoint(self, path: str) -> dict:
+        from .checkpoint import load_checkpoint
+        meta = load_checkpoint(self, path)
+        torch.cuda.synchronize(self.dev)
+        return meta
+
     def table_weight(self, t: int) -> torch.Tensor:
         """View of table ``t`` if this rank owns it."""
         j = self.local_tables.index(t)

@@ -37,3 +37,41 @@ def test_rec_dataset_loader_reads_files_and_synthesises(tmp_path):
     b = s.next_batch()
     assert b.shape == (16, 26) and s.synthetic and int(b.max()) < s.num_embeddings
     assert (b.numpy() >= s.offsets[:-1]).all() and (b.numpy() < s.offsets[1:]).all()
+
+
+def test_dlrm_main_trains_saves_and_resumes(tmp_path):
+    import torch
+    from recstore_b200.cli import dlrm_main
+    ck = str(tmp_path / "ck")
+    common = ["--arch-sparse-feature-size", "8", "--arch-embedding-size", "50-20-300", "--arch-mlp-bot", "5-16-8",
+              "--arch-mlp-top", "14-16-1", "--mini-batch-size", "64", "--print-freq", "0", "--data-generation", "synthetic"]
+    a = dlrm_main.main(common + ["--num-batches", "40", "--save-model", ck])
+    assert a["steps"] == 40 and a["mean_last_10"] < a["first_loss"]
+    b = dlrm_main.main(common + ["--num-batches", "5", "--load-model", ck, "--test-freq", "5"])
+    assert abs(b["first_loss"] - a["mean_last_10"]) < 0.2 and b["test_accuracy"] is not None
+    # wrong architecture is refused
+    with pytest.raises((ValueError, SystemExit)):
+        dlrm_main.main(["--arch-sparse-feature-size", "8", "--arch-embedding-size", "50-20", "--arch-mlp-bot", "5-16-8",
+                        "--mini-batch-size", "64", "--num-batches", "1", "--load-model", ck, "--print-freq", "0"])
+    with pytest.raises(SystemExit):
+        dlrm_main.main(["--arch-sparse-feature-size", "8", "--arch-mlp-bot", "5-16-4", "--num-batches", "1"])
+
+
+def test_checkpoint_roundtrip_preserves_predictions(tmp_path):
+    import torch
+    from recstore_b200.baseline.dlrm_torch import TorchDLRM
+    from recstore_b200.models.checkpoint import load_checkpoint, save_checkpoint
+    from recstore_b200.utils.data import DLRMBatchSource
+    rows = [30, 200, 17]
+    kw = dict(emb_dim=8, bottom_mlp=(16, 8), top_mlp=(16, 1), num_dense=4, seed=1)
+    m = TorchDLRM(rows, 32, **kw)
+    src = DLRMBatchSource(rows, [1, 1, 1], 32, num_dense=4, seed=2)
+    for _ in range(5):
+        b = src.next()
+        m.train_step(b.dense, b.ids, b.labels)
+    save_checkpoint(m, str(tmp_path / "c"), step=5)
+    m2 = TorchDLRM(rows, 32, **dict(kw, seed=99))
+    meta = load_checkpoint(m2, str(tmp_path / "c"))
+    b = src.next()
+    assert meta["step"] == 5 and torch.allclose(m.predict(b.dense, b.ids), m2.predict(b.dense, b.ids))
+    assert torch.equal(m.states[1], m2.states[1])

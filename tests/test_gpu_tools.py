@@ -36,3 +36,29 @@ def test_device_pool_tensors_are_usable_by_kernels():
     del b, c
     gc.collect()
     p.close()
+
+
+def test_engine_checkpoint_loads_into_pytorch_restatement_and_back(tmp_path):
+    from recstore_b200.baseline.dlrm_torch import TorchDLRM
+    from recstore_b200.models.checkpoint import load_checkpoint
+    from recstore_b200.models.dlrm import DLRM, DLRMConfig
+    from recstore_b200.utils.data import DLRMBatchSource
+    rows, B, D = [500, 37, 2000], 256, 64
+    kw = dict(emb_dim=D, bottom_mlp=(128, D), top_mlp=(128, 64, 1))
+    eng = DLRM(DLRMConfig(table_rows=rows, batch=B, seed=3, **kw))
+    src = DLRMBatchSource(rows, [1, 1, 1], B, seed=4)
+    for _ in range(4):
+        b = src.next()
+        eng.train_step(eng.make_pinned_batch(b.dense, b.ids, b.labels))
+    eng.save_checkpoint(str(tmp_path / "ck"), step=4)
+    ora = TorchDLRM(rows, B, device="cuda:0", seed=77, **kw)
+    meta = load_checkpoint(ora, str(tmp_path / "ck"))
+    assert meta["step"] == 4 and meta["table_rows"] == rows
+    b = src.next()
+    p_eng = eng.predict(eng.make_pinned_batch(b.dense, b.ids, b.labels)).float().view(-1)
+    p_ora = ora.predict(b.dense, b.ids).float().view(-1).to(p_eng.device)
+    assert (p_eng - p_ora).abs().max().item() < 2e-2          # bf16 MLPs against fp32
+    eng2 = DLRM(DLRMConfig(table_rows=rows, batch=B, seed=99, **kw))
+    eng2.load_checkpoint(str(tmp_path / "ck"))
+    p2 = eng2.predict(eng2.make_pinned_batch(b.dense, b.ids, b.labels)).float().view(-1)
+    assert torch.equal(p_eng, p2)
