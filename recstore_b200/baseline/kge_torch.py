@@ -1,0 +1,163 @@
+"""Knowledge-graph embedding models in plain PyTorch: every score function, chunked negatives, trainer.
+
+This is the oracle for the native KG kernels and the CPU path of the KG driver.  Score functions and their
+chunked-negative forms follow the reference's DGL-KE (src/kg/kg/dgl-ke/python/dglke/models/pytorch/score_fun.py:
+TransE l1/l2 :40-108, TransR :110-220, DistMult :222-286, ComplEx :288-368, RESCAL :370-438, RotatE :440-538,
+SimplE :540-641); loss = log-sigmoid (loss.py:69-99); embeddings trained with row-wise sparse Adagrad
+(tensor_models.py:366-436); init U(+-(gamma + 2) / dim) (general_models.py:223-224).
+
+Layouts: ComplEx and RotatE entities are ``[re | im]`` halves; RotatE relations are ``dim / 2`` phases scaled by
+``pi / emb_init``; SimplE entities are ``[head role | tail role]`` and relations ``[r | r_inv]``; TransR / RESCAL
+relations carry a ``dim x rel_dim`` (``dim x dim``) matrix in a second table.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+MODEL_NAMES = ("TransE", "TransE_l1", "TransE_l2", "TransR", "DistMult", "ComplEx", "RESCAL", "RotatE", "SimplE")
+
+
+def relation_dim(model: str, dim: int) -> int:
+    return dim // 2 if model == "RotatE" else dim
+
+
+def projection_dim(model: str, dim: int, rel_dim: Optional[int] = None) -> int:
+    """Floats per relation in the second (matrix) table; 0 if the model has none."""
+    if model == "TransR":
+        return dim * (rel_dim or dim)
+    if model == "RESCAL":
+        return dim * dim
+    return 0
+
+
+def _rotate_rel(r: torch.Tensor, emb_init: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    phase = r / (emb_init / math.pi)
+    return torch.cos(phase), torch.sin(phase)
+
+
+def edge_score(model: str, h: torch.Tensor, r: torch.Tensor, t: torch.Tensor, gamma: float, proj: Optional[torch.Tensor] = None,
+               emb_init: float = 1.0) -> torch.Tensor:
+    """Score of aligned triples: ``h, t`` ``[n, dim]``, ``r`` ``[n, rel_dim]`` -> ``[n]``."""
+    if model in ("TransE", "TransE_l2"):
+        return gamma - torch.sqrt(((h + r - t) ** 2).sum(-1).clamp_min(1e-30))
+    if model == "TransE_l1":
+        return gamma - (h + r - t).abs().sum(-1)
+    if model == "DistMult":
+        return (h * r * t).sum(-1)
+    if model == "ComplEx":
+        hr, hi = h.chunk(2, -1); tr, ti = t.chunk(2, -1); rr, ri = r.chunk(2, -1)
+        return (hr * tr * rr + hi * ti * rr + hr * ti * ri - hi * tr * ri).sum(-1)
+    if model == "RotatE":
+        hr, hi = h.chunk(2, -1); tr, ti = t.chunk(2, -1)
+        c, s = _rotate_rel(r, emb_init)
+        dr, di = hr * c - hi * s - tr, hr * s + hi * c - ti
+        return gamma - torch.sqrt(dr * dr + di * di).sum(-1)
+    if model == "SimplE":
+        h_i, h_j = h.chunk(2, -1); t_i, t_j = t.chunk(2, -1); rel, rinv = r.chunk(2, -1)
+        return (((h_i * rel * t_j).sum(-1) + (t_i * rinv * h_j).sum(-1)) / 2).clamp(-20, 20)
+    if model == "TransR":
+        d = h.shape[-1]
+        M = proj.view(h.shape[0], d, -1)
+        hp, tp = torch.einsum("nd,ndk->nk", h, M), torch.einsum("nd,ndk->nk", t, M)
+        return gamma - (hp + r - tp).abs().sum(-1)
+    if model == "RESCAL":
+        d = h.shape[-1]
+        M = proj.view(h.shape[0], d, d)
+        return (h * torch.einsum("nij,nj->ni", M, t)).sum(-1)
+    raise ValueError(model)
+
+
+def chunk_neg_score(model: str, h, r, t, neg, corrupt_head: bool, chunk: int, gamma: float, proj=None, emb_init: float = 1.0):
+    """Scores of every positive against the ``ns`` negatives shared by its chunk: ``h, r, t`` ``[bs, .]``, ``neg``
+    ``[bs / chunk * ns, dim]`` -> ``[bs, ns]``.  Written as the per-pair definition (broadcast), which is what the
+    bmm forms of the reference compute."""
+    bs, d = h.shape
+    C = bs // chunk
+    ns = neg.shape[0] // C
+    n = neg.view(C, 1, ns, d).expand(C, chunk, ns, d).reshape(bs * ns, d)
+    rep = lambda x: None if x is None else x.unsqueeze(1).expand(bs, ns, x.shape[-1]).reshape(bs * ns, -1)
+    hh, tt = (n, rep(t)) if corrupt_head else (rep(h), n)
+    return edge_score(model, hh, rep(r), tt, gamma, rep(proj), emb_init).view(bs, ns)
+
+
+def logsigmoid_loss(pos: torch.Tensor, neg: torch.Tensor) -> torch.Tensor:
+    return (-F.logsigmoid(pos).mean() - F.logsigmoid(-neg).mean()) / 2
+
+
+def rowwise_adagrad_(weight: torch.Tensor, state: torch.Tensor, ids: torch.Tensor, grad: torch.Tensor, lr: float, eps: float = 1e-10):
+    """state[u] += mean_d((sum of the row's gradients / count)^2); w[u] -= lr * g / (sqrt(state[u]) + eps), with the
+    duplicate gradients of a row averaged as the reference's sparse Adagrad does (tensor_models.py:380-415)."""
+    u, inv, cnt = torch.unique(ids, return_inverse=True, return_counts=True)
+    g = torch.zeros(u.numel(), grad.shape[1], dtype=grad.dtype, device=grad.device).index_add_(0, inv, grad)
+    g = g / cnt.unsqueeze(1).to(g.dtype)
+    state[u] += (g * g).mean(1)
+    weight[u] -= lr * g / (state[u].sqrt().unsqueeze(1) + eps)
+
+
+class TorchKGE:
+    """Dense entity / relation tables on one device, trained like the reference's stock path."""
+
+    def __init__(self, n_entities: int, n_relations: int, dim: int, model: str = "TransE_l2", gamma: float = 12.0,
+                 lr: float = 0.1, device="cpu", seed: int = 0, rel_dim: Optional[int] = None, neg_chunk_size: int = 0):
+        assert model in MODEL_NAMES, model
+        self.model, self.dim, self.gamma, self.lr, self.device = model, dim, gamma, lr, torch.device(device)
+        self.emb_init = (gamma + 2.0) / dim
+        g = torch.Generator().manual_seed(seed)
+        u = lambda n, d: ((torch.rand(n, d, generator=g) * 2 - 1) * self.emb_init).to(self.device)
+        self.rel_dim = relation_dim(model, rel_dim or dim)
+        self.entity, self.relation = u(n_entities, dim), u(n_relations, self.rel_dim)
+        pd = projection_dim(model, dim, rel_dim)
+        self.proj = u(n_relations, pd) if pd else None
+        self.state: Dict[str, torch.Tensor] = {"entity": torch.zeros(n_entities, device=self.device),
+                                               "relation": torch.zeros(n_relations, device=self.device)}
+        if self.proj is not None:
+            self.state["proj"] = torch.zeros(n_relations, device=self.device)
+        self.step_no = 0
+
+    def _rows(self, h_ids, r_ids, t_ids, neg_ids):
+        rows = [self.entity[h_ids].clone().requires_grad_(True), self.relation[r_ids].clone().requires_grad_(True),
+                self.entity[t_ids].clone().requires_grad_(True), self.entity[neg_ids].clone().requires_grad_(True)]
+        p = self.proj[r_ids].clone().requires_grad_(True) if self.proj is not None else None
+        return rows, p
+
+    def scores(self, h_ids, r_ids, t_ids, neg_ids, corrupt_head: bool, chunk: int):
+        (h, r, t, n), p = self._rows(h_ids, r_ids, t_ids, neg_ids)
+        pos = edge_score(self.model, h, r, t, self.gamma, p, self.emb_init)
+        neg = chunk_neg_score(self.model, h, r, t, n, corrupt_head, chunk, self.gamma, p, self.emb_init)
+        return pos, neg, (h, r, t, n, p)
+
+    def train_step(self, h_ids, r_ids, t_ids, neg_ids, chunk: int, corrupt_head: Optional[bool] = None) -> float:
+        if corrupt_head is None:
+            corrupt_head = bool(self.step_no & 1)
+        self.step_no += 1
+        pos, neg, (h, r, t, n, p) = self.scores(h_ids, r_ids, t_ids, neg_ids, corrupt_head, chunk)
+        loss = logsigmoid_loss(pos, neg)
+        loss.backward()
+        with torch.no_grad():
+            ids = torch.cat([h_ids, t_ids, neg_ids])
+            rowwise_adagrad_(self.entity, self.state["entity"], ids, torch.cat([h.grad, t.grad, n.grad]), self.lr)
+            if r.grad is not None:      # RESCAL scores with the relation matrix only
+                rowwise_adagrad_(self.relation, self.state["relation"], r_ids, r.grad, self.lr)
+            if p is not None:
+                rowwise_adagrad_(self.proj, self.state["proj"], r_ids, p.grad, self.lr)
+        return loss.item()
+
+    @torch.no_grad()
+    def evaluate(self, h_ids, r_ids, t_ids, n_neg: int = 256, generator: Optional[torch.Generator] = None) -> Dict[str, float]:
+        """Rank of each positive among ``n_neg`` sampled corruptions of its head and of its tail."""
+        bs = h_ids.numel()
+        ranks = []
+        for corrupt_head in (False, True):
+            neg_ids = torch.randint(0, self.entity.shape[0], (n_neg,), generator=generator).to(self.device)
+            p = self.proj[r_ids] if self.proj is not None else None
+            pos = edge_score(self.model, self.entity[h_ids], self.relation[r_ids], self.entity[t_ids], self.gamma, p, self.emb_init)
+            neg = chunk_neg_score(self.model, self.entity[h_ids], self.relation[r_ids], self.entity[t_ids], self.entity[neg_ids],
+                                  corrupt_head, bs, self.gamma, p, self.emb_init)
+            ranks.append(1 + (neg >= pos.unsqueeze(1)).sum(1))
+        r = torch.cat(ranks).float()
+        return {"MRR": (1.0 / r).mean().item(), "MR": r.mean().item(), "HITS@1": (r <= 1).float().mean().item(),
+                "HITS@3": (r <= 3).float().mean().item(), "HITS@10": (r <= 10).float().mean().item()}

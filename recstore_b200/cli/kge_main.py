@@ -1,0 +1,203 @@
+"""Knowledge-graph embedding training driver (the counterpart of the reference's ``dgl-ke-main.py``).
+
+    python -m recstore_b200.cli.kge_main --model_name TransE_l2 --dataset synthetic --n_entities 100000 --n_triples 2000000 \
+        --hidden_dim 400 --gamma 10 --batch_size 1024 --neg_sample_size 256 --max_step 1000 --num_proc 2 --device cuda --test
+
+Pipeline (src/executable/kg/dgl-ke-main.py:168-552): load or synthesise the dataset -> partition the training triples
+over the workers (``--rel_part`` balanced, ``--soft_rel_part``, else random) -> per-worker chunked negative samplers ->
+optional pre-sampling of ``--presample_steps`` steps, hot sets of ``--cache_ratio`` x entities per worker, renumbering so
+that each worker's hot entities are contiguous -> one training process per worker -> save -> sampled-negative test
+(MRR / MR / HITS@k).
+
+Engines: on ``--device cuda`` TransE_l2 / DistMult run on the native path (entity and relation tables row-sharded over
+the GPUs' HBM, tcgen05 scoring); every other score function, and ``--device cpu``, runs the PyTorch implementation on
+tables shared between the worker processes (lock-free updates, as the reference's stock path does).  Prints
+``Successfully xmh`` when done.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import socket
+import time
+
+import numpy as np
+import torch
+
+NATIVE_MODELS = ("TransE", "TransE_l2", "DistMult")
+
+
+def parse_args(argv=None):
+    from recstore_b200.baseline.kge_torch import MODEL_NAMES
+    p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    p.add_argument("--model_name", default="TransE_l2", choices=MODEL_NAMES)
+    p.add_argument("--dataset", default="synthetic")
+    p.add_argument("--data_path", default=None)
+    p.add_argument("--data_files", nargs="+", default=None)
+    p.add_argument("--format", default="raw_udd_hrt")
+    p.add_argument("--n_entities", type=int, default=20000)
+    p.add_argument("--n_relations", type=int, default=50)
+    p.add_argument("--n_triples", type=int, default=200000)
+    p.add_argument("--hidden_dim", type=int, default=64)
+    p.add_argument("--gamma", type=float, default=12.0)
+    p.add_argument("--lr", type=float, default=0.1)
+    p.add_argument("--batch_size", type=int, default=256)
+    p.add_argument("--neg_sample_size", type=int, default=64)
+    p.add_argument("--neg_chunk_size", type=int, default=None)
+    p.add_argument("--max_step", type=int, default=200)
+    p.add_argument("--log_interval", type=int, default=100)
+    p.add_argument("--num_proc", type=int, default=1)
+    p.add_argument("--device", choices=["cpu", "cuda"], default="cpu")
+    p.add_argument("--rel_part", action="store_true")
+    p.add_argument("--soft_rel_part", action="store_true")
+    p.add_argument("--cache_ratio", type=float, default=0.0)
+    p.add_argument("--presample_steps", type=int, default=0)
+    p.add_argument("--test", action="store_true")
+    p.add_argument("--batch_size_eval", type=int, default=256)
+    p.add_argument("--neg_sample_size_eval", type=int, default=256)
+    p.add_argument("--save_path", default=None)
+    p.add_argument("--seed", type=int, default=0)
+    a = p.parse_args(argv)
+    if a.neg_chunk_size is None:
+        a.neg_chunk_size = min(a.neg_sample_size, a.batch_size)
+    a.batch_size = -(-a.batch_size // a.neg_chunk_size) * a.neg_chunk_size      # whole chunks, like the reference (utils.py:27-33)
+    return a
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
+    return p
+
+
+def prepare(args):
+    """Dataset -> partitions (-> renumbering).  Returns (dataset, parts, info)."""
+    from recstore_b200.utils import kg_data as K
+    if args.dataset == "synthetic" or args.data_path is None:
+        ds = K.KGDataset.synthetic(args.n_entities, args.n_relations, args.n_triples, seed=args.seed)
+    else:
+        ds = K.KGDataset.load(args.data_path, args.data_files or ["train.tsv"], args.format, name=args.dataset)
+    W = args.num_proc
+    info = {"n_entities": ds.n_entities, "n_relations": ds.n_relations, "n_train": int(ds.train[0].size)}
+    if args.rel_part:
+        parts, cross = K.balanced_relation_partition(ds.train[1], W, args.seed)
+        info["cross_relations"] = int(cross.sum())
+    elif args.soft_rel_part:
+        parts, cross = K.soft_relation_partition(ds.train[1], W, seed=args.seed)
+        info["cross_relations"] = int(cross.sum())
+    else:
+        parts = K.random_partition(ds.train[0].size, W, args.seed)
+    if args.cache_ratio > 0 and args.presample_steps > 0:
+        cache = max(1, int(ds.n_entities * args.cache_ratio / W))
+        smp = [K.ChunkedNegativeSampler(tuple(x[p] for x in ds.train), ds.n_entities, args.batch_size, args.neg_sample_size,
+                                        args.neg_chunk_size, seed=args.seed * 100 + r) for r, p in enumerate(parts)]
+        counts = K.presample(smp, ds.n_entities, args.presample_steps)
+        hot = K.hot_sets(counts, cache)
+        covered = sum(int(c[h].sum()) for c, h in zip(counts, hot)) / max(1, sum(int(c.sum()) for c in counts))
+        ds, _ = K.renumber_graph(ds, hot, cache)
+        info.update({"cache_rows_per_worker": cache, "presampled_hit_ratio": covered})
+    return ds, parts, info
+
+
+def worker(rank: int, args, ds, parts, port: int, shared, out):
+    from recstore_b200.utils.kg_data import ChunkedNegativeSampler
+    W = args.num_proc
+    dev = torch.device(f"cuda:{rank}") if args.device == "cuda" else torch.device("cpu")
+    native = args.device == "cuda" and args.model_name in NATIVE_MODELS
+    if args.device == "cpu" and W > 1:
+        torch.set_num_threads(max(1, (os.cpu_count() or W) // W))       # the workers share the host's cores
+    if W > 1 or native:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+        if args.device == "cuda":
+            torch.cuda.set_device(rank)
+        dist.init_process_group("nccl" if args.device == "cuda" else "gloo", rank=rank, world_size=W)
+    mine = tuple(x[parts[rank]] for x in ds.train)
+    smp = ChunkedNegativeSampler(mine, ds.n_entities, args.batch_size, args.neg_sample_size, args.neg_chunk_size,
+                                 seed=args.seed * 100 + rank, device=dev)
+    if native:
+        from recstore_b200.models.kge import KGEConfig, KGEModel
+        from recstore_b200.parallel.peer import PeerContext
+        ctx = PeerContext(rank, W, device=dev)
+        model = KGEModel(KGEConfig(ds.n_entities, ds.n_relations, dim=args.hidden_dim, model=args.model_name, gamma=args.gamma,
+                                   batch=args.batch_size, neg_sample_size=args.neg_sample_size, neg_chunk_size=args.neg_chunk_size,
+                                   lr=args.lr, seed=args.seed, dataset=ds.name), ctx)
+        step_fn = lambda h, r, t, n, ch: model.train_step(h, r, t, n, ch)
+    else:
+        from recstore_b200.baseline.kge_torch import TorchKGE
+        model = TorchKGE(ds.n_entities, ds.n_relations, args.hidden_dim, args.model_name, args.gamma, args.lr, device=dev, seed=args.seed)
+        if shared is not None:           # one table for all CPU workers
+            model.entity, model.relation, model.proj, model.state = shared["entity"], shared["relation"], shared.get("proj"), shared["state"]
+        step_fn = lambda h, r, t, n, ch: model.train_step(h, r, t, n, args.neg_chunk_size, ch)
+    t0 = time.time()
+    losses = []
+    for step in range(args.max_step):
+        h, r, t, n, ch = next(smp)
+        losses.append(step_fn(h, r, t, n, ch))
+        if rank == 0 and (step + 1) % args.log_interval == 0:
+            recent = [float(x) for x in losses[-args.log_interval:]]
+            print(f"[{rank}] step {step + 1}: loss {np.mean(recent):.5f}, {(time.time() - t0) / (step + 1) * 1e3:.2f} ms/step", flush=True)
+    if args.device == "cuda":
+        torch.cuda.synchronize()
+    el = time.time() - t0
+    res = {"steps": args.max_step, "first_loss": float(losses[0]), "last_loss": float(np.mean([float(x) for x in losses[-10:]])),
+           "triples_per_s": args.batch_size * args.max_step / el}
+    if W > 1 or native:
+        import torch.distributed as dist
+        dist.barrier()
+    if args.test and ds.test is not None:
+        th, tr, tt = (torch.as_tensor(x[: args.batch_size_eval * 4]).to(dev) for x in ds.test)
+        g = torch.Generator(device=dev if native else "cpu").manual_seed(5)
+        if native:
+            ms = []
+            for s in range(0, th.numel() - args.batch_size + 1, args.batch_size):
+                ms.append(model.evaluate(th[s:s + args.batch_size], tr[s:s + args.batch_size], tt[s:s + args.batch_size], g))
+            res["test"] = {k: float(np.mean([m[k] for m in ms])) for k in ms[0]} if ms else None
+        elif rank == 0:
+            res["test"] = model.evaluate(th, tr, tt, args.neg_sample_size_eval, g)
+    if args.save_path:
+        if native:
+            model.save(args.save_path)
+        elif rank == 0:
+            os.makedirs(args.save_path, exist_ok=True)
+            np.save(os.path.join(args.save_path, f"{ds.name}_{args.model_name}_entity.npy"), model.entity.cpu().numpy())
+            np.save(os.path.join(args.save_path, f"{ds.name}_{args.model_name}_relation.npy"), model.relation.cpu().numpy())
+            with open(os.path.join(args.save_path, "config.json"), "w") as f:
+                json.dump({"dataset": ds.name, "model_name": args.model_name, "hidden_dim": args.hidden_dim, "gamma": args.gamma,
+                           "emp_file": f"{ds.name}_{args.model_name}_entity.npy", "rmap_file": f"{ds.name}_{args.model_name}_relation.npy"}, f, indent=2)
+    if out is not None:
+        out[rank] = res
+    if W > 1 or native:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main(argv=None):
+    args = parse_args(argv)
+    ds, parts, info = prepare(args)
+    print(json.dumps({"prepared": info}), flush=True)
+    shared = None
+    native = args.device == "cuda" and args.model_name in NATIVE_MODELS
+    if not native and args.num_proc > 1 and args.device == "cpu":
+        from recstore_b200.baseline.kge_torch import TorchKGE
+        m = TorchKGE(ds.n_entities, ds.n_relations, args.hidden_dim, args.model_name, args.gamma, args.lr, seed=args.seed)
+        shared = {"entity": m.entity.share_memory_(), "relation": m.relation.share_memory_(),
+                  "state": {k: v.share_memory_() for k, v in m.state.items()}}
+        if m.proj is not None:
+            shared["proj"] = m.proj.share_memory_()
+    if args.num_proc == 1 and not native:
+        out = {}
+        worker(0, args, ds, parts, 0, shared, out)
+    else:
+        import torch.multiprocessing as mp
+        out = mp.Manager().dict()
+        mp.spawn(worker, args=(args, ds, parts, _free_port(), shared, out), nprocs=args.num_proc, join=True)
+        out = dict(out)
+    print(json.dumps({"result": out.get(0)}), flush=True)
+    print("Successfully xmh", flush=True)
+    return dict(out), info
+
+
+if __name__ == "__main__":
+    main()

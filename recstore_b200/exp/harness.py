@@ -49,7 +49,7 @@ def expand_grid(grid: Dict[str, Sequence], fixed: Optional[dict] = None, exclude
 
 def run_dir_name(index: int, cfg: dict, varying: Sequence[str]) -> str:
     parts = [f"{k}={cfg[k]}" for k in varying]
-    name = f"run_{index:03d}" + ("_" + "_".join(parts) if parts else "")
+    name = "run" + ("_" + "_".join(parts) if parts else f"_{index:03d}")   # named by its options: stable across re-runs
     return "".join(c if c.isalnum() or c in "=_.-" else "-" for c in name)[:200]
 
 

@@ -1,0 +1,250 @@
+"""Knowledge-graph datasets, triple partitioning, pre-sampling and hot-id renumbering.
+
+* ``KGDataset``: user-defined datasets in the reference's ``raw_udd_{hrt|htr|...}`` form (tab separated triples of
+  names, dictionaries built on the fly and written as ``entities.tsv`` / ``relations.tsv``) or ``udd_*`` (triples of
+  integer ids plus the two dictionary files), and synthetic power-law graphs for boxes without data
+  (src/kg/kg/dgl-ke/python/dglke/dataloader/KGDataset.py: ``KGDatasetUDDRaw`` / ``KGDatasetUDD``).
+* Partitioning of the training triples over the workers: ``random_partition``, ``balanced_relation_partition`` (every
+  relation on as few workers as its size allows, equal shares) and ``soft_relation_partition`` (large relations spread,
+  small ones pinned) -- sampler.py:45-313 of the reference.  (Its METIS edge-cut partition needs the METIS library;
+  the relation-based partitions are the ones kept.)
+* ``presample``: run the sampler ahead for some steps and count how often each entity is touched per worker
+  (sampler.py:512-600) -> per-worker hot sets.
+* ``renumber_graph``: give the hot entities of worker r the ids ``[start_r, start_r + len_r)`` and everything else the
+  ids after them, rewrite the triples (sampler.py:600-634; the dictionary is built by the native
+  ``construct_renumbering_dict_op``).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+
+@dataclass
+class KGDataset:
+    name: str
+    n_entities: int
+    n_relations: int
+    train: Tuple[np.ndarray, np.ndarray, np.ndarray]          # (head, rel, tail) int64
+    valid: Optional[Tuple[np.ndarray, np.ndarray, np.ndarray]] = None
+    test: Optional[Tuple[np.ndarray, np.ndarray, np.ndarray]] = None
+    entity2id: Optional[Dict[str, int]] = None
+    relation2id: Optional[Dict[str, int]] = None
+
+    @staticmethod
+    def synthetic(n_entities: int, n_relations: int, n_triples: int, alpha: float = 1.3, seed: int = 0, test_frac: float = 0.02):
+        from .data import powerlaw_triples
+        h, r, t = powerlaw_triples(n_triples, n_entities, n_relations, alpha, seed)
+        n_test = max(1, int(n_triples * test_frac))
+        cut = lambda a, b: (h[a:b], r[a:b], t[a:b])
+        return KGDataset("synthetic", n_entities, n_relations, cut(2 * n_test, n_triples), cut(0, n_test), cut(n_test, 2 * n_test))
+
+    @staticmethod
+    def load(path: str, files: Sequence[str], fmt: str = "raw_udd_hrt", name: Optional[str] = None, delimiter: str = "\t"):
+        """``files``: train [valid test] for ``raw_udd_*``; entities, relations, train [valid test] for ``udd_*``."""
+        raw = fmt.startswith("raw_udd_")
+        order = fmt.split("_")[-1]
+        assert sorted(order) == ["h", "r", "t"], f"bad format {fmt}"
+        col = {c: i for i, c in enumerate(order)}
+        files = list(files)
+        if raw:
+            e2i: Dict[str, int] = {}
+            r2i: Dict[str, int] = {}
+            tfiles = files
+        else:
+            e2i = _read_dict(os.path.join(path, files[0]), delimiter)
+            r2i = _read_dict(os.path.join(path, files[1]), delimiter)
+            tfiles = files[2:]
+        assert 1 <= len(tfiles) <= 3, "expected train [valid test]"
+        splits = []
+        for fn in tfiles:
+            hs, rs, ts = [], [], []
+            with open(os.path.join(path, fn)) as f:
+                for ln, line in enumerate(f):
+                    p = line.rstrip("\n").split(delimiter)
+                    if len(p) < 3:
+                        if line.strip():
+                            raise ValueError(f"{fn}:{ln + 1}: expected 3 columns")
+                        continue
+                    hn, rn, tn = p[col["h"]], p[col["r"]], p[col["t"]]
+                    if raw:
+                        hs.append(e2i.setdefault(hn, len(e2i))); ts.append(e2i.setdefault(tn, len(e2i)))
+                        rs.append(r2i.setdefault(rn, len(r2i)))
+                    else:
+                        hs.append(int(hn)); rs.append(int(rn)); ts.append(int(tn))
+            splits.append((np.array(hs, dtype=np.int64), np.array(rs, dtype=np.int64), np.array(ts, dtype=np.int64)))
+        if raw:   # the dictionaries the run used, as the reference writes them beside the data
+            _write_dict(os.path.join(path, "entities.tsv"), e2i, delimiter)
+            _write_dict(os.path.join(path, "relations.tsv"), r2i, delimiter)
+        ne, nr = (len(e2i), len(r2i))
+        for h, r, t in splits:
+            if h.size and (max(h.max(), t.max()) >= ne or r.max() >= nr):
+                raise ValueError("triple id outside the dictionaries")
+        return KGDataset(name or os.path.basename(os.path.normpath(path)), ne, nr, splits[0], splits[1] if len(splits) > 1 else None,
+                         splits[2] if len(splits) > 2 else None, e2i, r2i)
+
+
+def _read_dict(path: str, delimiter: str) -> Dict[str, int]:
+    d = {}
+    with open(path) as f:
+        for line in f:
+            p = line.rstrip("\n").split(delimiter)
+            if len(p) >= 2:
+                d[p[1]] = int(p[0])
+    return d
+
+
+def _write_dict(path: str, d: Dict[str, int], delimiter: str) -> None:
+    with open(path, "w") as f:
+        for k, v in sorted(d.items(), key=lambda kv: kv[1]):
+            f.write(f"{v}{delimiter}{k}\n")
+
+
+# ------------------------------------------------------------------------------------------------ partitioning
+def random_partition(n_triples: int, n_parts: int, seed: int = 0) -> List[np.ndarray]:
+    perm = np.random.default_rng(seed).permutation(n_triples)
+    return [np.sort(p) for p in np.array_split(perm, n_parts)]
+
+
+def balanced_relation_partition(rel: np.ndarray, n_parts: int, seed: int = 0) -> Tuple[List[np.ndarray], np.ndarray]:
+    """Equal-sized parts with every relation on as few parts as possible.  Relations are placed largest first on the
+    emptiest part; a relation that does not fit is cut.  Returns the parts and ``cross[r]`` (relation spans parts)."""
+    n = rel.size
+    cap = -(-n // n_parts)
+    cnt = np.bincount(rel)
+    order = np.argsort(-cnt, kind="stable")
+    fill = np.zeros(n_parts, dtype=np.int64)
+    take: List[List[Tuple[int, int]]] = [[] for _ in range(n_parts)]     # (relation, how many) per part
+    cross = np.zeros(cnt.size, dtype=bool)
+    for r in order:
+        left = int(cnt[r])
+        first = True
+        while left > 0:
+            p = int(np.argmin(fill))
+            room = cap - int(fill[p])
+            k = min(left, room) if room > 0 else left
+            take[p].append((int(r), k)); fill[p] += k; left -= k
+            if not first or left > 0:
+                cross[r] = True
+            first = False
+    rng = np.random.default_rng(seed)
+    by_rel = {int(r): rng.permutation(np.nonzero(rel == r)[0]) for r in np.nonzero(cnt)[0]}
+    cur = {r: 0 for r in by_rel}
+    parts = []
+    for p in range(n_parts):
+        idx = []
+        for r, k in take[p]:
+            idx.append(by_rel[r][cur[r]:cur[r] + k]); cur[r] += k
+        parts.append(np.sort(np.concatenate(idx)) if idx else np.zeros(0, dtype=np.int64))
+    return parts, cross
+
+
+def soft_relation_partition(rel: np.ndarray, n_parts: int, threshold: float = 0.05, seed: int = 0) -> Tuple[List[np.ndarray], np.ndarray]:
+    """Relations with more than ``threshold`` of the triples are spread evenly over all parts; the others go whole to
+    the emptiest part."""
+    n = rel.size
+    cnt = np.bincount(rel)
+    rng = np.random.default_rng(seed)
+    fill = np.zeros(n_parts, dtype=np.int64)
+    buckets: List[List[np.ndarray]] = [[] for _ in range(n_parts)]
+    cross = np.zeros(cnt.size, dtype=bool)
+    for r in np.argsort(-cnt, kind="stable"):
+        if cnt[r] == 0:
+            continue
+        idx = rng.permutation(np.nonzero(rel == r)[0])
+        if cnt[r] > threshold * n and n_parts > 1:
+            cross[r] = True
+            for p, piece in enumerate(np.array_split(idx, n_parts)):
+                buckets[p].append(piece); fill[p] += piece.size
+        else:
+            p = int(np.argmin(fill))
+            buckets[p].append(idx); fill[p] += idx.size
+    return [np.sort(np.concatenate(b)) if b else np.zeros(0, dtype=np.int64) for b in buckets], cross
+
+
+# ------------------------------------------------------------------------------------------------ sampling
+class ChunkedNegativeSampler:
+    """Positive batches from one worker's triples plus ``batch / chunk * neg_sample_size`` uniform negative entities;
+    head / tail corruption alternates (sampler.py:703-818 of the reference)."""
+
+    def __init__(self, triples, n_entities: int, batch: int, neg_sample_size: int, neg_chunk_size: int, seed: int = 0, device="cpu"):
+        self.h, self.r, self.t = (torch.as_tensor(x, dtype=torch.int64, device=device) for x in triples)
+        assert batch % neg_chunk_size == 0
+        self.n, self.ne, self.batch = self.h.numel(), n_entities, batch
+        self.nneg = batch // neg_chunk_size * neg_sample_size
+        self.chunk = neg_chunk_size
+        self.gen = torch.Generator(device=device).manual_seed(seed)
+        self.dev = device
+        self.step = 0
+
+    def __next__(self):
+        idx = torch.randint(0, self.n, (self.batch,), generator=self.gen, device=self.dev)
+        neg = torch.randint(0, self.ne, (self.nneg,), generator=self.gen, device=self.dev)
+        corrupt_head = bool(self.step & 1)
+        self.step += 1
+        return self.h[idx], self.r[idx], self.t[idx], neg, corrupt_head
+
+    def __iter__(self):
+        return self
+
+
+def presample(samplers: Sequence[ChunkedNegativeSampler], n_entities: int, steps: int) -> List[torch.Tensor]:
+    """Access counts ``[n_entities]`` per worker over ``steps`` sampled batches (positives and negatives).  The
+    samplers are advanced; build fresh ones (same seeds) for training if the streams must match."""
+    out = []
+    for s in samplers:
+        c = torch.zeros(n_entities, dtype=torch.int64)
+        for _ in range(steps):
+            h, _, t, neg, _ = next(s)
+            ids = torch.cat([h, t, neg]).cpu()
+            c += torch.bincount(ids, minlength=n_entities)
+        out.append(c)
+    return out
+
+
+def hot_sets(counts: Sequence[torch.Tensor], cache_size: int) -> List[torch.Tensor]:
+    """Disjoint per-worker hot sets: every entity goes to the worker that touches it most; each keeps its top
+    ``cache_size`` by count."""
+    C = torch.stack(list(counts))                     # [W, N]
+    owner = C.argmax(0)
+    best = C.max(0).values
+    out = []
+    for w in range(C.shape[0]):
+        mine = torch.nonzero((owner == w) & (best > 0)).view(-1)
+        if mine.numel() > cache_size:
+            top = torch.topk(best[mine], cache_size).indices
+            mine = mine[top]
+        out.append(mine.sort().values)
+    return out
+
+
+def renumber_graph(ds: KGDataset, hot: Sequence[torch.Tensor], cache_size: int) -> Tuple[KGDataset, torch.Tensor]:
+    """New ids: hot set of worker r -> ``[r * cache_size, r * cache_size + len)``, the rest after them in old order.
+    Returns the rewritten dataset and ``new_id[old_id]``."""
+    from ..torch_op import construct_renumbering_dict_op
+    W = len(hot)
+    padded = []
+    used = torch.zeros(ds.n_entities, dtype=torch.bool)
+    for hs in hot:
+        assert hs.numel() <= cache_size
+        used[hs] = True
+        padded.append(hs)
+    # pad every hot set to cache_size with cold ids so that worker r's range starts at r * cache_size
+    cold = torch.nonzero(~used).view(-1)
+    need = [cache_size - p.numel() for p in padded]
+    assert sum(need) <= cold.numel(), "cache_size * workers exceeds the number of entities"
+    o = 0
+    full = []
+    for p, k in zip(padded, need):
+        full.append(torch.cat([p, cold[o:o + k]]))
+        o += k
+    d = torch.full((ds.n_entities,), -1, dtype=torch.int64)
+    construct_renumbering_dict_op(d, W, full)
+    m = d.numpy()
+    f = lambda tr: None if tr is None else (m[tr[0]], tr[1], m[tr[2]])
+    e2i = {k: int(m[v]) for k, v in ds.entity2id.items()} if ds.entity2id else None
+    return KGDataset(ds.name, ds.n_entities, ds.n_relations, f(ds.train), f(ds.valid), f(ds.test), e2i, ds.relation2id), d

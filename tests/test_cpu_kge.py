@@ -1,0 +1,136 @@
+"""KG score functions against per-edge loops, datasets from fake files, partitions, pre-sampling, the driver (CPU)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from recstore_b200.baseline.kge_torch import MODEL_NAMES, TorchKGE, chunk_neg_score, edge_score, projection_dim, relation_dim
+from recstore_b200.utils import kg_data as K
+
+
+def _naive(model, h, r, t, gamma, proj, emb_init):
+    """One triple, scalar loops over the definition."""
+    d = h.numel()
+    if model in ("TransE", "TransE_l2"):
+        return gamma - math.sqrt(sum((h[i] + r[i] - t[i]) ** 2 for i in range(d)))
+    if model == "TransE_l1":
+        return gamma - sum(abs(h[i] + r[i] - t[i]) for i in range(d))
+    if model == "DistMult":
+        return sum(h[i] * r[i] * t[i] for i in range(d))
+    k = d // 2
+    if model == "ComplEx":
+        s = 0.0
+        for i in range(k):
+            a = complex(h[i], h[i + k]) * complex(r[i], r[i + k]) * complex(t[i], t[i + k]).conjugate()
+            s += a.real
+        return s
+    if model == "RotatE":
+        s = 0.0
+        for i in range(k):
+            ph = r[i] / (emb_init / math.pi)
+            z = complex(h[i], h[i + k]) * complex(math.cos(ph), math.sin(ph)) - complex(t[i], t[i + k])
+            s += abs(z)
+        return gamma - s
+    if model == "SimplE":
+        s = sum(h[i] * r[i] * t[i + k] for i in range(k)) + sum(t[i] * r[i + k] * h[i + k] for i in range(k))
+        return max(-20.0, min(20.0, s / 2))
+    M = proj.view(d, -1)
+    if model == "TransR":
+        hp, tp = h @ M, t @ M
+        return gamma - sum(abs(hp[i] + r[i] - tp[i]) for i in range(M.shape[1]))
+    if model == "RESCAL":
+        return float(h @ (M @ t))
+    raise AssertionError(model)
+
+
+@pytest.mark.parametrize("model", MODEL_NAMES)
+def test_scores_match_per_edge_definition(model):
+    g = torch.Generator().manual_seed(3)
+    d, bs, chunk, ns, gamma, init = 8, 6, 3, 4, 5.0, 0.7
+    rd = relation_dim(model, d)
+    h, t = torch.randn(bs, d, generator=g, dtype=torch.float64), torch.randn(bs, d, generator=g, dtype=torch.float64)
+    r = torch.randn(bs, rd, generator=g, dtype=torch.float64)
+    pd = projection_dim(model, d)
+    proj = torch.randn(bs, pd, generator=g, dtype=torch.float64) if pd else None
+    neg = torch.randn(bs // chunk * ns, d, generator=g, dtype=torch.float64)
+    pos = edge_score(model, h, r, t, gamma, proj, init)
+    for i in range(bs):
+        assert abs(pos[i].item() - _naive(model, h[i], r[i], t[i], gamma, None if proj is None else proj[i], init)) < 1e-9
+    for corrupt_head in (False, True):
+        sc = chunk_neg_score(model, h, r, t, neg, corrupt_head, chunk, gamma, proj, init)
+        assert sc.shape == (bs, ns)
+        for i in range(bs):
+            for j in range(ns):
+                n = neg[(i // chunk) * ns + j]
+                hh, tt = (n, t[i]) if corrupt_head else (h[i], n)
+                assert abs(sc[i, j].item() - _naive(model, hh, r[i], tt, gamma, None if proj is None else proj[i], init)) < 1e-9
+
+
+@pytest.mark.parametrize("model", ["TransE_l1", "ComplEx", "RotatE"])
+def test_trainer_learns_a_small_graph(model):
+    g = torch.Generator().manual_seed(0)
+    k = TorchKGE(150, 5, 16, model, gamma=6.0, lr=0.1, seed=1)
+    h = torch.randint(0, 150, (48,), generator=g); r = torch.randint(0, 5, (48,), generator=g); t = (h * 5 + r) % 150
+    first = last = None
+    for s in range(150):
+        last = k.train_step(h, r, t, torch.randint(0, 150, (3 * 8,), generator=g), chunk=16)
+        first = first if first is not None else last
+    assert last < 0.5 * first and k.evaluate(h, r, t, 64, g)["MRR"] > 0.5
+
+
+def test_dataset_from_fake_files(tmp_path):
+    (tmp_path / "train.tsv").write_text("a\tlikes\tb\nb\tlikes\tc\nc\thates\ta\n")
+    (tmp_path / "valid.tsv").write_text("a\thates\tc\n")
+    ds = K.KGDataset.load(str(tmp_path), ["train.tsv", "valid.tsv"], "raw_udd_hrt")
+    assert (ds.n_entities, ds.n_relations) == (3, 2) and ds.train[0].tolist() == [0, 1, 2] and ds.train[2].tolist() == [1, 2, 0]
+    assert ds.valid[1].tolist() == [1] and ds.test is None
+    assert (tmp_path / "entities.tsv").read_text().splitlines() == ["0\ta", "1\tb", "2\tc"]
+    # the same triples with columns in another order, then the id form with the dictionaries written above
+    (tmp_path / "ids.tsv").write_text("0\t1\t2\n")
+    d2 = K.KGDataset.load(str(tmp_path), ["entities.tsv", "relations.tsv", "ids.tsv"], "udd_hrt")
+    assert d2.n_entities == 3 and d2.train[1].tolist() == [1]
+    (tmp_path / "bad.tsv").write_text("0\t9\t2\n")
+    with pytest.raises(ValueError):
+        K.KGDataset.load(str(tmp_path), ["entities.tsv", "relations.tsv", "bad.tsv"], "udd_hrt")
+    (tmp_path / "t2.tsv").write_text("a\tb\tlikes\n")           # (this load rewrites the dictionary files)
+    assert K.KGDataset.load(str(tmp_path), ["t2.tsv"], "raw_udd_htr").train[1].tolist() == [0]
+
+
+def test_partitions_cover_every_triple_once():
+    ds = K.KGDataset.synthetic(500, 9, 6000, seed=1)
+    rel = ds.train[1]
+    for parts, cross in (K.balanced_relation_partition(rel, 4), K.soft_relation_partition(rel, 4, threshold=0.2)):
+        allidx = np.concatenate(parts)
+        assert np.array_equal(np.sort(allidx), np.arange(rel.size))
+        for r in range(9):
+            on = sum(1 for p in parts if (rel[p] == r).any())
+            assert (on > 1) == bool(cross[r]) or (rel == r).sum() == 0
+    bal, _ = K.balanced_relation_partition(rel, 4)
+    assert max(p.size for p in bal) - min(p.size for p in bal) <= 1
+    assert sum(p.size for p in K.random_partition(rel.size, 3)) == rel.size
+
+
+def test_presample_hot_sets_and_renumbering():
+    ds = K.KGDataset.synthetic(400, 4, 5000, seed=2)
+    parts = K.random_partition(ds.train[0].size, 2)
+    smp = [K.ChunkedNegativeSampler(tuple(x[p] for x in ds.train), 400, 32, 8, 8, seed=i) for i, p in enumerate(parts)]
+    counts = K.presample(smp, 400, 10)
+    assert all(int(c.sum()) == 10 * (32 * 2 + 32) for c in counts)
+    hot = K.hot_sets(counts, 40)
+    assert all(h.numel() <= 40 for h in hot) and not set(hot[0].tolist()) & set(hot[1].tolist())
+    ds2, d = K.renumber_graph(ds, hot, 40)
+    assert sorted(d.tolist()) == list(range(400))                      # a permutation
+    for w, hs in enumerate(hot):
+        assert ((d[hs] >= w * 40) & (d[hs] < (w + 1) * 40)).all()      # worker w's hot ids are its contiguous range
+    assert np.array_equal(ds2.train[0], d.numpy()[ds.train[0]]) and np.array_equal(ds2.train[1], ds.train[1])
+
+
+def test_driver_runs_on_cpu(tmp_path):
+    from recstore_b200.cli import kge_main
+    out, info = kge_main.main(["--model_name", "DistMult", "--max_step", "30", "--n_entities", "500", "--n_triples", "5000", "--hidden_dim", "16",
+                               "--batch_size", "64", "--neg_sample_size", "16", "--soft_rel_part", "--cache_ratio", "0.2",
+                               "--presample_steps", "5", "--test", "--save_path", str(tmp_path / "o"), "--log_interval", "1000"])
+    r = out[0]
+    assert r["steps"] == 30 and r["last_loss"] < r["first_loss"] and 0 < r["test"]["MRR"] <= 1
+    assert info["presampled_hit_ratio"] > 0.1 and (tmp_path / "o" / "config.json").exists()
