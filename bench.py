@@ -40,6 +40,16 @@ def table_rows(seed: int = 0):
     return loguniform_table_rows(TABLES, 10, 10_000_000, 34_000_000, seed)
 
 
+# Second workload (not the headline): DLRM-DCNv2, multi-hot, ~200 M rows, largest table 40 M rows, low-rank (512) cross
+# network of 3 layers, top MLP 1024-1024-512-256-1, ids Zipf(1.1); tables are placed table-wise on the GPUs.
+DCN_HOTNESS = [3, 2, 1, 2, 6, 1, 1, 1, 1, 7, 3, 8, 1, 6, 9, 5, 1, 1, 1, 12, 100, 27, 10, 3, 1, 1]
+
+
+def dcn_table_rows(seed: int = 0):
+    from recstore_b200.utils.data import loguniform_table_rows
+    return loguniform_table_rows(TABLES, 10, 40_000_000, 200_000_000, seed, pin_largest=40_000_000)
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -127,12 +137,15 @@ def run_native(args):
     from recstore_b200.parallel.peer import PeerContext
     from recstore_b200.utils.data import DLRMBatchSource
     rank, world, local = dist_setup(args.gpus)
-    rows = table_rows(args.seed)
+    dcn = args.workload == "dcnv2"
+    rows = dcn_table_rows(args.seed) if dcn else table_rows(args.seed)
+    hot = DCN_HOTNESS if dcn else [1] * TABLES
     ctx = PeerContext(rank, world, device=torch.device(f"cuda:{local}"))
-    cfg = DLRMConfig(table_rows=rows, batch=BATCH, emb_dim=DIM, emb_lr=0.01, mlp_lr=0.01, seed=args.seed,
-                     use_cuda_graph=not args.no_graph, trace_phases=args.trace_phases)
+    extra = dict(interaction="dcn", dcn_layers=3, dcn_rank=512, hotness=hot, top_mlp=(1024, 1024, 512, 256, 1)) if dcn else {}
+    cfg = DLRMConfig(table_rows=rows, batch=BATCH, emb_dim=DIM, emb_lr=0.01, mlp_lr=0.01 if not dcn else 0.001, seed=args.seed,
+                     use_cuda_graph=not args.no_graph, trace_phases=args.trace_phases, **extra)
     eng = DLRM(cfg, ctx)
-    src = DLRMBatchSource(rows, [1] * TABLES, BATCH, alpha=ALPHA, seed=args.seed + 1)
+    src = DLRMBatchSource(rows, hot, BATCH, alpha=1.1 if dcn else ALPHA, seed=args.seed + 1)
     nb = 4
     batches = []
     for _ in range(nb):
@@ -178,11 +191,13 @@ def run_native(args):
     h2d = batches[0].nbytes
     if rank == 0:
         out = {
-            "metric": METRIC, "value": BATCH * args.steps / (ms_dev * 1e-3), "unit": "samples/s",
+            "metric": METRIC if not dcn else "dlrm_dcnv2_train_samples_per_s", "value": BATCH * args.steps / (ms_dev * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (Zipf 1.2 ids, random-init weights)", "impl": "native",
-            "config": {"model": "DLRM dot, 26 tables x dim 128, ~34M rows, bot 13-512-256-128, top 479-1024-1024-512-256-1",
+            "data": f"synthetic (Zipf {1.1 if dcn else 1.2} ids, random-init weights)", "impl": "native",
+            "config": {"model": "DLRM dot, 26 tables x dim 128, ~34M rows, bot 13-512-256-128, top 479-1024-1024-512-256-1" if not dcn else
+                       "DLRM-DCNv2 multi-hot (sum of hotness 214), 26 tables x dim 128, ~200M rows (largest 40M), bot 13-512-256-128, "
+                       "3-layer rank-512 cross network, top 3456-1024-1024-512-256-1",
                        "global_batch": BATCH, "seq_len": None,
                        "parallelism": f"table-wise MP embeddings x{world} + DP MLP x{world}",
                        "l2": "working set per step (>=450 MB of windows + ~17 GB of tables) exceeds the 126 MB L2",
@@ -274,6 +289,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference", "torch_baseline"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--workload", default="dlrm", choices=["dlrm", "dcnv2"],
+                    help="dlrm: the headline config; dcnv2: the multi-hot DLRM-DCNv2 config (native arm only)")
     ap.add_argument("--trace-phases", action="store_true",
                     help="stamp the GPU timer at phase boundaries of the step and print the timeline of every rank to stderr")
     args = ap.parse_args()
