@@ -46,8 +46,16 @@ DCN_HOTNESS = [3, 2, 1, 2, 6, 1, 1, 1, 1, 7, 3, 8, 1, 6, 9, 5, 1, 1, 1, 12, 100,
 
 
 def dcn_table_rows(seed: int = 0):
+    """Row counts drawn as for the headline config, then handed out so that tables with more ids per sample are the
+    larger ones (as in click logs: the long multi-hot features are the high-cardinality ones).  With U(+-sqrt(1/n))
+    rows, a 100-hot sum over a 75-row table would start at magnitude ~10 and the cubic cross network overflows bf16."""
     from recstore_b200.utils.data import loguniform_table_rows
-    return loguniform_table_rows(TABLES, 10, 40_000_000, 200_000_000, seed, pin_largest=40_000_000)
+    rows = sorted(loguniform_table_rows(TABLES, 10, 40_000_000, 200_000_000, seed, pin_largest=40_000_000), reverse=True)
+    order = sorted(range(TABLES), key=lambda t: -DCN_HOTNESS[t])
+    out = [0] * TABLES
+    for k, t in enumerate(order):
+        out[t] = rows[k]
+    return out
 
 
 class ClockSampler:
@@ -142,7 +150,9 @@ def run_native(args):
     hot = DCN_HOTNESS if dcn else [1] * TABLES
     ctx = PeerContext(rank, world, device=torch.device(f"cuda:{local}"))
     extra = dict(interaction="dcn", dcn_layers=3, dcn_rank=512, hotness=hot, top_mlp=(1024, 1024, 512, 256, 1)) if dcn else {}
-    cfg = DLRMConfig(table_rows=rows, batch=BATCH, emb_dim=DIM, emb_lr=0.01, mlp_lr=0.01 if not dcn else 0.001, seed=args.seed,
+    # dcnv2: with sum-of-squares row-wise Adagrad a row that occurs n times in a batch moves by ~lr * sqrt(n); the
+    # 100-hot Zipf feature repeats its hottest rows ~10^5 times per batch, so the embedding step is kept small.
+    cfg = DLRMConfig(table_rows=rows, batch=BATCH, emb_dim=DIM, emb_lr=0.01 if not dcn else 1e-4, mlp_lr=0.01 if not dcn else 0.001, seed=args.seed,
                      use_cuda_graph=not args.no_graph, trace_phases=args.trace_phases, **extra)
     eng = DLRM(cfg, ctx)
     src = DLRMBatchSource(rows, hot, BATCH, alpha=1.1 if dcn else ALPHA, seed=args.seed + 1)
