@@ -143,3 +143,36 @@ def test_sharded_table_single_gpu(dev):
         torch.cuda.synchronize()
         ctx.check_status()
         assert torch.allclose(tab.weight, W, atol=2e-3, rtol=2e-3)
+
+
+def test_tiered_table_lookup_and_adagrad_on_both_tiers():
+    from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
+    from recstore_b200.cache.tiered_table import TieredEmbeddingTable
+    dev = torch.device("cuda:0")
+    N, D = 5000, 32
+    t = TieredEmbeddingTable(N, D, hbm_ratio=0.1, max_keys=4096, lr=0.05, device=dev, init="row_index")
+    assert t.hot_rows == 500 and t.cold.is_pinned()
+    g = torch.Generator(device=dev).manual_seed(0)
+    ids = torch.randint(0, N, (3000,), device=dev, generator=g)
+    ids[::4] = 7            # hot duplicate
+    ids[1::9] = 4321        # cold duplicate
+    out = t.lookup(ids)
+    assert torch.equal(out[:, 0].cpu(), ids.float().cpu()) and torch.equal(out[:, -1].cpu(), ids.float().cpu())
+    hs = t.hit_stats()
+    assert hs["hbm_rows"] + hs["host_rows"] == torch.unique(ids).numel() and 0 < hs["hit_ratio"] < 1
+    # two optimizer steps against the reference semantics on a dense copy of the table
+    W = torch.arange(N, dtype=torch.float32, device=dev).unsqueeze(1).expand(-1, D).contiguous()
+    S = torch.zeros(N, device=dev)
+    for step in range(2):
+        ids = torch.randint(0, N, (3000,), device=dev, generator=g)
+        ids[::5] = 11
+        ids[2::7] = 4000
+        grads = torch.randn(3000, D, device=dev, generator=g)
+        t.lookup(ids)
+        t.update(grads)
+        rowwise_adagrad_update(W, S, ids, grads, 0.05, 1e-10)
+    torch.cuda.synchronize()
+    full = torch.cat([t.hot.cpu(), t.cold])
+    assert torch.allclose(full, W.cpu(), atol=1e-4, rtol=1e-5)
+    assert torch.allclose(torch.cat([t.hot_state.cpu(), t.cold_state]), S.cpu(), atol=1e-5, rtol=1e-5)
+    assert t.status.item() == 0
