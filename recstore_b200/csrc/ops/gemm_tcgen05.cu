@@ -59,6 +59,7 @@ struct GemmArgs {
   int stages;
   int tiles_m, tiles_n;
   int splits;           // reduction splits (mode 1 / epilogue 3), else 1
+  int units_per_cta;    // > 0: balanced decomposition of epilogue 3 (see WorkIter), else 0
   int kblocks;          // ceil(K / 64)
   int epi;
   int ldd, ldaux, ldx0;
@@ -74,6 +75,45 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+
+// Work of one CTA as a sequence of (tile, k-block range) segments; the three roles of a CTA walk identical copies.
+//   units_per_cta == 0: items (tile, split) handed out round-robin (it = cta, cta + grid, ...)
+//   units_per_cta  > 0: the tiles x k-blocks units are cut into equal contiguous ranges, one per CTA, so every CTA
+//                       does the same number of k-blocks whatever tiles x splits would have divided the SMs into;
+//                       a range that crosses a tile boundary yields two segments (fp32 atomic epilogue only).
+struct WorkIter {
+  int it, items, stride, tiles, kb_per_split, kblocks;
+  long long u, uend;
+  bool balanced;
+  __device__ WorkIter(const GemmArgs& g, int cta, int grid) {
+    tiles = g.tiles_m * g.tiles_n;
+    kblocks = g.kblocks;
+    balanced = g.units_per_cta > 0;
+    it = cta; stride = grid; items = tiles * g.splits;
+    kb_per_split = (g.kblocks + g.splits - 1) / g.splits;
+    u = static_cast<long long>(cta) * g.units_per_cta;
+    uend = u + g.units_per_cta;
+    const long long total = static_cast<long long>(tiles) * kblocks;
+    if (uend > total) uend = total;
+  }
+  __device__ bool next(int& tile, int& kb0, int& kb1) {
+    if (!balanced) {
+      if (it >= items) return false;
+      tile = it % tiles;
+      kb0 = (it / tiles) * kb_per_split;
+      kb1 = min(kblocks, kb0 + kb_per_split);
+      it += stride;
+      return true;
+    }
+    if (u >= uend) return false;
+    tile = static_cast<int>(u / kblocks);
+    kb0 = static_cast<int>(u % kblocks);
+    const long long room = uend - u;
+    kb1 = static_cast<int>(min(static_cast<long long>(kblocks), kb0 + room));
+    u += kb1 - kb0;
+    return true;
+  }
+};
 
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -124,10 +164,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles = g.tiles_m * g.tiles_n;
-  const int items = tiles * g.splits;
-  const int kb_per_split = (g.kblocks + g.splits - 1) / g.splits;
-
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
@@ -135,13 +171,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       bool ok = true;
       int last_stage = -1;
       uint32_t last_phase = 0;
-      for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
-        const int tile = it % tiles;
-        const int split = it / tiles;
+      WorkIter w(g, blockIdx.x, gridDim.x);
+      int tile, kb0, kb1;
+      while (ok && w.next(tile, kb0, kb1)) {
         const int m0 = (tile / g.tiles_n) * BM;
         const int n0 = (tile % g.tiles_n) * g.bn;
-        const int kb0 = split * kb_per_split;
-        const int kb1 = min(g.kblocks, kb0 + kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&full[stage], kABytes + b_bytes);
@@ -175,10 +209,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
-        const int split = it / tiles;
-        const int kb0 = split * kb_per_split;
-        const int kb1 = min(g.kblocks, kb0 + kb_per_split);
+      WorkIter w(g, blockIdx.x, gridDim.x);
+      int tile, kb0, kb1;
+      while (ok && w.next(tile, kb0, kb1)) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * g.bn);
@@ -227,8 +260,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const uint32_t sw = static_cast<uint32_t>(srow & 7);
       const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
       const int nchunks = g.bn / 64;
-      for (int it = blockIdx.x; it < items; it += gridDim.x) {
-        const int tile = it % tiles;
+      WorkIter w(g, blockIdx.x, gridDim.x);
+      int tile, kb0, kb1;
+      while (w.next(tile, kb0, kb1)) {
         const int m0 = (tile / g.tiles_n) * BM;
         const int n0 = (tile % g.tiles_n) * g.bn;
         // The tile's bias slice is requested before the accumulator is ready, so its latency hides behind the wait.
@@ -352,9 +386,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         if (acc == 0) acc_phase ^= 1u;
       }
       if (leader) tma_store_wait<0>();   // shared memory must outlive the stores that read it
-    } else
-    for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
-      const int tile = it % tiles;
+    } else {
+    WorkIter w(g, blockIdx.x, gridDim.x);
+    int tile, kb0, kb1;
+    while (ok && w.next(tile, kb0, kb1)) {
       const int m0 = (tile / g.tiles_n) * BM;
       const int n0 = (tile % g.tiles_n) * g.bn;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
@@ -540,6 +575,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    }
   }
 
   tc_fence_before_sync();
@@ -658,10 +694,23 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   g.tiles_n = (N + bn - 1) / bn;
   g.kblocks = (K + BK - 1) / BK;
   const int sms = num_sms();
+  g.units_per_cta = 0;
+  int grid_override = 0;
   if (epi == 3) {
-    if (splits == 0) {
-      const int tiles = g.tiles_m * g.tiles_n;
-      splits = (sms + tiles - 1) / tiles;
+    const int tiles = g.tiles_m * g.tiles_n;
+    if (splits < 0) {
+      // On request: cut tiles x k-blocks into one equal contiguous range per SM.  Perfectly balanced, but CTAs that
+      // run together then read different reduction rows and nothing is shared through L2: measured 253 us against
+      // 166 us for the 1024 x 1024 x 65536 weight gradient, so it is not the default.
+      const long long total = static_cast<long long>(tiles) * g.kblocks;
+      const int ctas = static_cast<int>(total < sms ? total : sms);
+      g.units_per_cta = static_cast<int>((total + ctas - 1) / ctas);
+      grid_override = static_cast<int>((total + g.units_per_cta - 1) / g.units_per_cta);
+      splits = 1;
+    } else if (splits == 0) {
+      // One wave: as many splits as fit on the SMs (rounding up instead gives e.g. 160 items on 148 SMs, which take
+      // the time of two waves).  Items of one split run together and share their reduction rows through L2.
+      splits = tiles >= sms ? 1 : sms / tiles;
       if (splits > g.kblocks) splits = g.kblocks;
       if (splits < 1) splits = 1;
     }
@@ -703,7 +752,7 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
     attr_set[mode] = true;
   }
   const int items = g.tiles_m * g.tiles_n * g.splits;
-  const int grid = items < sms ? items : sms;
+  const int grid = grid_override > 0 ? grid_override : (items < sms ? items : sms);
   if (mode == 0) gemm_tcgen05_kernel<0><<<grid, kThreads, smem, stream>>>(ma, mb, md, g);
   else if (mode == 1) gemm_tcgen05_kernel<1><<<grid, kThreads, smem, stream>>>(ma, mb, md, g);
   else gemm_tcgen05_kernel<2><<<grid, kThreads, smem, stream>>>(ma, mb, md, g);
