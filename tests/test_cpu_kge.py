@@ -134,3 +134,32 @@ def test_driver_runs_on_cpu(tmp_path):
     r = out[0]
     assert r["steps"] == 30 and r["last_loss"] < r["first_loss"] and 0 < r["test"]["MRR"] <= 1
     assert info["presampled_hit_ratio"] > 0.1 and (tmp_path / "o" / "config.json").exists()
+
+
+def test_score_infer_modes_and_emb_similarity(tmp_path):
+    from recstore_b200.models.kge_infer import EmbSimInfer, ScoreInfer
+    g = torch.Generator().manual_seed(0)
+    ent, rel = torch.randn(12, 8, generator=g), torch.randn(3, 8, generator=g)
+    inf = ScoreInfer("DistMult", ent, rel)
+    (h, r, t, s), = inf.topk(head=[0, 1], rel=[0, 2], tail=None, k=5, exec_mode="all")
+    full = torch.stack([(ent[a] * rel[b] * ent[c]).sum() for a in (0, 1) for b in (0, 2) for c in range(12)])
+    assert torch.allclose(s, torch.topk(full, 5).values, atol=1e-6)
+    assert torch.allclose(s, (ent[h] * rel[r] * ent[t]).sum(1), atol=1e-6) and bool((s[:-1] >= s[1:]).all())
+    per_head = inf.topk(head=[3, 4, 5], rel=[1], tail=[0, 1, 2, 3], k=2, exec_mode="batch_head")
+    assert len(per_head) == 3 and all(x[0].unique().numel() == 1 for x in per_head)
+    (h, r, t, s), = inf.topk([1, 2], [0, 1], [3, 4], k=10, exec_mode="triplet_wise")
+    assert s.numel() == 2
+    # checkpoints of the trainers load directly
+    import json
+    import numpy as np
+    np.save(tmp_path / "d_DistMult_entity.npy", ent.numpy()); np.save(tmp_path / "d_DistMult_relation.npy", rel.numpy())
+    (tmp_path / "config.json").write_text(json.dumps({"model_name": "DistMult", "gamma": 5.0, "emp_file": "d_DistMult_entity.npy",
+                                                       "rmap_file": "d_DistMult_relation.npy"}))
+    assert torch.equal(ScoreInfer.load(str(tmp_path)).entity, ent)
+    sim = EmbSimInfer(ent, "cosine")
+    (l, rr, v), = sim.topk(left=[0, 1, 2], right=None, k=3)
+    assert torch.allclose(v, torch.ones(3), atol=1e-6) and torch.equal(l.sort().values, rr.sort().values)    # each id matches itself
+    lists = EmbSimInfer(ent, "l2").topk(left=[5], right=[1, 5, 7], k=2, bcast=True)
+    assert lists[0][1][0].item() == 5 and abs(lists[0][2][0].item()) < 1e-6
+    for fn in ("l1", "dot", "ext_jaccard"):
+        assert EmbSimInfer(ent, fn).topk([0, 1], [2, 3], k=1, pair_ws=True)[0][2].numel() == 1

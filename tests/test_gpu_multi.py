@@ -180,3 +180,18 @@ def test_sharded_table_lookup_update_matches_replicated_oracle():
     out = mgr.dict()
     mp.spawn(_sharded_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert all(out.get(r) == "ok" for r in range(world)), dict(out)
+
+
+def test_kge_driver_two_gpus_native_path():
+    """TransE-L2 on entity / relation tables sharded over two GPUs, through the training driver."""
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    from recstore_b200.cli import kge_main
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    out, info = kge_main.main(["--device", "cuda", "--num_proc", "2", "--model_name", "TransE_l2", "--max_step", "120",
+                               "--n_entities", "20000", "--n_triples", "200000", "--hidden_dim", "128", "--gamma", "10",
+                               "--batch_size", "512", "--neg_sample_size", "128", "--rel_part", "--test", "--log_interval", "1000"])
+    assert len(out) == 2
+    for r in (0, 1):
+        assert out[r]["last_loss"] < 0.6 * out[r]["first_loss"], out[r]
+        assert out[r]["test"]["MRR"] > 0.2, out[r]
