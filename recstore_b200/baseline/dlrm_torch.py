@@ -43,7 +43,8 @@ class TorchDLRM:
                  num_dense: int = 13, bottom_mlp=(512, 256, 128), top_mlp=(1024, 1024, 512, 256, 1),
                  emb_lr: float = 0.01, emb_eps: float = 1e-10, emb_optimizer: str = "rowwise_adagrad",
                  mlp_lr: float = 0.01, device="cpu", rank: int = 0, world: int = 1, autocast_bf16: bool = False,
-                 seed: int = 0, group=None, interaction: str = "dot", dcn_layers: int = 3, dcn_rank: int = 512):
+                 seed: int = 0, group=None, interaction: str = "dot", dcn_layers: int = 3, dcn_rank: int = 512,
+                 projection_sizes: Sequence[int] = (4, 4)):
         self.table_rows = list(table_rows)
         self.T = len(self.table_rows)
         self.D = emb_dim
@@ -68,7 +69,11 @@ class TorchDLRM:
         self.interaction = interaction
         self._num_dense, self._bottom_mlp, self._top_mlp = num_dense, list(bottom_mlp), list(top_mlp)
         self._dcn_layers, self._dcn_rank = dcn_layers, dcn_rank
+        assert interaction in ("dot", "dcn", "projection")
+        self.I1, self.I2 = projection_sizes
         n_inter = (self.T + 1) * emb_dim if interaction == "dcn" else emb_dim + (self.T + 1) * self.T // 2
+        if interaction == "projection":          # DLRM_Projection: two learned projections of the features, then their product
+            n_inter = emb_dim + self.I1 * self.I2
         kb = [num_dense] + list(bottom_mlp[:-1])
         for i, (k, n) in enumerate(zip(kb, bottom_mlp)):
             self.params[f"bot.{i}.weight"] = (torch.randn(n, k, generator=g) * math.sqrt(2.0 / (n + k))).to(self.device)
@@ -84,6 +89,12 @@ class TorchDLRM:
             self.params[f"crossV.{l}.bias"] = torch.zeros(dcn_rank, device=self.device)       # unused, kept for a uniform layout
             self.params[f"crossW.{l}.weight"] = (torch.randn(n_inter, dcn_rank, generator=g) * math.sqrt(2.0 / (dcn_rank + n_inter))).to(self.device)
             self.params[f"crossW.{l}.bias"] = torch.zeros(n_inter, device=self.device)
+        if interaction == "projection":
+            # InteractionProjectionArch of the reference (model_zoo/dlrm.py:289-404): Linear((F*D) -> I*D) branches
+            fd = (self.T + 1) * emb_dim
+            for name, I in (("proj1", self.I1), ("proj2", self.I2)):
+                self.params[f"{name}.0.weight"] = (torch.randn(I * emb_dim, fd, generator=g) * math.sqrt(2.0 / (I * emb_dim + fd))).to(self.device)
+                self.params[f"{name}.0.bias"] = torch.zeros(I * emb_dim, device=self.device)
         hk = top_mlp[-2]
         self.params["head.weight"] = (torch.randn(hk, generator=g) * math.sqrt(2.0 / (1 + hk))).to(self.device)
         self.params["head.bias"] = torch.randn(1, generator=g).to(self.device)
@@ -149,6 +160,12 @@ class TorchDLRM:
                     tl = F.linear(z, self.params[f"crossV.{l}.weight"].to(z.dtype))
                     u = F.linear(tl, self.params[f"crossW.{l}.weight"].to(z.dtype), self.params[f"crossW.{l}.bias"].to(z.dtype))
                     z = x0 * u + z
+            elif self.interaction == "projection":
+                flat = Tm.reshape(Tm.shape[0], -1)
+                b1 = F.relu(F.linear(flat, self.params["proj1.0.weight"].to(flat.dtype), self.params["proj1.0.bias"].to(flat.dtype)))
+                b2 = F.relu(F.linear(flat, self.params["proj2.0.weight"].to(flat.dtype), self.params["proj2.0.bias"].to(flat.dtype)))
+                inter = torch.bmm(b1.view(-1, self.I1, self.D), b2.view(-1, self.I2, self.D).transpose(1, 2))   # [B, I1, I2]
+                z = torch.cat([x, inter.reshape(inter.shape[0], -1)], 1)
             else:
                 Z = torch.bmm(Tm, Tm.transpose(1, 2))
                 z = torch.cat([x, Z[:, self.li, self.lj]], 1)
@@ -161,7 +178,8 @@ class TorchDLRM:
     def describe(self) -> dict:
         return {"table_rows": list(self.table_rows), "emb_dim": self.D, "hotness": list(self.hotness),
                 "num_dense": self._num_dense, "bottom_mlp": list(self._bottom_mlp), "top_mlp": list(self._top_mlp),
-                "interaction": self.interaction, "dcn_layers": self._dcn_layers, "dcn_rank": self._dcn_rank}
+                "interaction": self.interaction, "dcn_layers": self._dcn_layers, "dcn_rank": self._dcn_rank,
+                "projection_sizes": [self.I1, self.I2]}
 
     def dense_state(self) -> Dict[str, torch.Tensor]:
         return {k: v.detach().clone() for k, v in self.params.items()}

@@ -36,7 +36,9 @@ def parse_args(argv=None):
     p.add_argument("--arch-embedding-size", type=dash_ints, default=[4, 3, 2])
     p.add_argument("--arch-mlp-bot", type=dash_ints, default=[4, 16])
     p.add_argument("--arch-mlp-top", type=dash_ints, default=None, help="default: <interaction width>-64-1")
-    p.add_argument("--arch-interaction-op", choices=["dot", "dcn"], default="dot")
+    p.add_argument("--arch-interaction-op", choices=["dot", "dcn", "projection"], default="dot",
+                   help="dot: DLRM; dcn: low-rank DCNv2 cross network; projection: DLRM_Projection (PyTorch path only)")
+    p.add_argument("--interaction-branch-sizes", type=dash_ints, default=[4, 4], help="I1-I2 of the projection interaction")
     p.add_argument("--dcn-layers", type=int, default=3)
     p.add_argument("--dcn-rank", type=int, default=64)
     p.add_argument("--mini-batch-size", type=int, default=128)
@@ -62,6 +64,8 @@ def parse_args(argv=None):
 
 def interaction_width(args) -> int:
     T, D = len(args.arch_embedding_size), args.arch_sparse_feature_size
+    if args.arch_interaction_op == "projection":
+        return D + args.interaction_branch_sizes[0] * args.interaction_branch_sizes[1]
     return (T + 1) * D if args.arch_interaction_op == "dcn" else D + (T + 1) * T // 2
 
 
@@ -134,6 +138,8 @@ def run(args) -> dict:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if args.use_gpu:
+        if args.arch_interaction_op == "projection":
+            sys.exit("ERROR: the projection interaction runs on the PyTorch path only (drop --use-gpu)")
         from recstore_b200.models.dlrm import DLRM, DLRMConfig
         from recstore_b200.parallel.peer import PeerContext
         local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -145,7 +151,8 @@ def run(args) -> dict:
         model = _GpuModel(DLRM(DLRMConfig(table_rows=rows, batch=args.mini_batch_size, **kw), ctx))
     else:
         from recstore_b200.baseline.dlrm_torch import TorchDLRM
-        model = _CpuModel(TorchDLRM(rows, args.mini_batch_size, device="cpu", rank=0, world=1, **kw))
+        model = _CpuModel(TorchDLRM(rows, args.mini_batch_size, device="cpu", rank=0, world=1,
+                                    projection_sizes=tuple(args.interaction_branch_sizes), **kw))
     alpha = args.zipf_alpha if args.data_generation == "synthetic" else 0.0
     src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 1)
     test_src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 2)

@@ -91,3 +91,40 @@ def test_native_engine_benchmark_and_zipf_check():
     z = zipf_check(100000, 1.2, n=200000, top=10)
     assert abs(z["mass"] - z["expected"]) < 0.01
     json.dumps(r)
+
+
+def _po_member(gid, port, q):
+    import torch
+    from recstore_b200.ps import AllShardsParameterClient, ParameterClient, ParameterServer
+    from recstore_b200.ps.postoffice import Postoffice
+    po = Postoffice(num_servers=2, num_clients=1, global_id=gid, store_port=port, timeout_s=30)
+    if po.is_server:
+        srv = ParameterServer("KVEngineMap", {"dim": 4, "capacity": 1000})
+        po.publish_server("127.0.0.1", srv.serve(0))
+        po.barrier("ready"); po.barrier("done")
+        q.put(("server", po.server_id, len(srv)))
+        srv.close()
+    else:
+        po.barrier("ready")
+        cl = AllShardsParameterClient([ParameterClient(h, p, i, 4) for i, (h, p) in enumerate(po.all_servers())])
+        keys = torch.arange(40)
+        cl.PutParameter(keys, keys.float().unsqueeze(1).expand(-1, 4).contiguous())
+        ok = torch.equal(cl.GetParameter(keys)[:, 0], keys.float())
+        po.barrier("done")
+        q.put(("client", po.client_id, ok))
+
+
+def test_postoffice_roles_rendezvous_and_barrier():
+    import multiprocessing as mp
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_po_member, args=(g, port, q)) for g in range(3)]
+    for p in ps:
+        p.start()
+    got = sorted(q.get(timeout=60) for _ in range(3))
+    for p in ps:
+        p.join(30)
+    assert got[0] == ("client", 0, True)
+    assert got[1][0] == got[2][0] == "server" and got[1][2] + got[2][2] == 40 and min(got[1][2], got[2][2]) > 0
