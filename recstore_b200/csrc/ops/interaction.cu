@@ -56,76 +56,90 @@ __device__ __forceinline__ void zero_tail_rows(__nv_bfloat16* sT, int F, int D, 
 __device__ __forceinline__ void load_tile_async(__nv_bfloat16* sT, const __nv_bfloat16* src, int F, int D, int lane) {
   const int vec_per_row = D >> 3;  // 16 bytes = 8 bf16
   const int total = F * vec_per_row;
+  if (vec_per_row == 16) {         // D = 128: shifts instead of a division by a run-time value in every iteration
+    for (int i = lane; i < total; i += 32) cp_async16(sT + (i >> 4) * kLd + (i & 15) * 8, src + static_cast<size_t>(i) * 8);
+    return;
+  }
   for (int i = lane; i < total; i += 32) {
     const int r = i / vec_per_row, v = i % vec_per_row;
     cp_async16(sT + r * kLd + v * 8, src + static_cast<size_t>(r) * D + v * 8);
   }
 }
 
+// Persistent warps: every warp walks samples b = first, first + stride, ...; the positions of this lane's
+// accumulator elements inside the output row (strict lower triangle, row-major) are worked out once.
 __global__ void __launch_bounds__(kWarps * 32) interaction_fwd_kernel(const __nv_bfloat16* __restrict__ T, int B, int F,
                                                                       int D, __nv_bfloat16* __restrict__ out, int out_ld) {
   __shared__ __align__(16) __nv_bfloat16 sT[kWarps][32 * kLd];
   __shared__ __align__(16) __nv_bfloat16 sO[kWarps][kMaxD + kMaxF * (kMaxF - 1) / 2 + 8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x * kWarps + warp;
-  if (b >= B) return;
   __nv_bfloat16* t = sT[warp];
-  load_tile_async(t, T + static_cast<size_t>(b) * F * D, F, D, lane);
-  zero_tail_rows(t, F, D, lane);
-  cp_async_wait_all();
-  __syncwarp();
-
-  // acc[mt][nt]: rows mt*16.., cols nt*8..; only tiles that touch the strict lower triangle.
-  float acc[2][4][4];
-#pragma unroll
-  for (int i = 0; i < 2; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
-
-  const int ksteps = D >> 4;
-  for (int ks = 0; ks < ksteps; ++ks) {
-    const int k0 = ks * 16;
-    uint32_t a0[4], a1[4], b01[4], b23[4];
-    ldmatrix_x4(a0, t + ((lane & 7) + ((lane >> 3) & 1) * 8) * kLd + k0 + (lane >> 4) * 8);
-    ldmatrix_x4(a1, t + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kLd + k0 + (lane >> 4) * 8);
-    // B fragments from the same tile viewed as [n][k]: n-tiles {0,1} and {2,3}.
-    ldmatrix_x4(b01, t + ((lane & 7) + (lane >> 4) * 8) * kLd + k0 + ((lane >> 3) & 1) * 8);
-    ldmatrix_x4(b23, t + (16 + (lane & 7) + (lane >> 4) * 8) * kLd + k0 + ((lane >> 3) & 1) * 8);
-    mma_bf16(acc[0][0], a0, b01[0], b01[1]);
-    mma_bf16(acc[0][1], a0, b01[2], b01[3]);
-    mma_bf16(acc[1][0], a1, b01[0], b01[1]);
-    mma_bf16(acc[1][1], a1, b01[2], b01[3]);
-    mma_bf16(acc[1][2], a1, b23[0], b23[1]);
-    mma_bf16(acc[1][3], a1, b23[2], b23[3]);
-  }
-
   __nv_bfloat16* o = sO[warp];
-  for (int d = lane; d < D; d += 32) o[d] = t[d];  // row 0 = dense features
+  zero_tail_rows(t, F, D, lane);
   const int g = lane >> 2, q = lane & 3;
+  // offset of acc[mt][nt][e] in the staging row, or -1 outside the strict lower triangle / past F
+  short off[2][4][4];
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-      if (mt == 0 && nt >= 2) continue;
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = mt * 16 + g + (e >> 1) * 8;
         const int j = nt * 8 + q * 2 + (e & 1);
-        if (i < F && j < i) o[D + i * (i - 1) / 2 + j] = __float2bfloat16(acc[mt][nt][e]);
+        off[mt][nt][e] = (i < F && j < i) ? static_cast<short>(D + i * (i - 1) / 2 + j) : static_cast<short>(-1);
       }
-    }
-  __syncwarp();
   const int nvalid = D + F * (F - 1) / 2;
-  __nv_bfloat16* dst = out + static_cast<size_t>(b) * out_ld;
-  // zero the padding inside the last 16-byte group, then copy whole groups; groups past nvalid are zeros
-  for (int idx = nvalid + lane; idx < ((nvalid + 7) & ~7); idx += 32) o[idx] = __float2bfloat16(0.f);
-  __syncwarp();
   const int nfull = (nvalid + 7) >> 3;
-  for (int v = lane; v < (out_ld >> 3); v += 32) {
-    const uint4 x = v < nfull ? *reinterpret_cast<const uint4*>(o + v * 8) : make_uint4(0, 0, 0, 0);
-    *(reinterpret_cast<uint4*>(dst) + v) = x;
+  const int ksteps = D >> 4;
+  for (int b = blockIdx.x * kWarps + warp; b < B; b += gridDim.x * kWarps) {
+    load_tile_async(t, T + static_cast<size_t>(b) * F * D, F, D, lane);
+    cp_async_wait_all();
+    __syncwarp();
+
+    // acc[mt][nt]: rows mt*16.., cols nt*8..; only tiles that touch the strict lower triangle.
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
+    for (int ks = 0; ks < ksteps; ++ks) {
+      const int k0 = ks * 16;
+      uint32_t a0[4], a1[4], b01[4], b23[4];
+      ldmatrix_x4(a0, t + ((lane & 7) + ((lane >> 3) & 1) * 8) * kLd + k0 + (lane >> 4) * 8);
+      ldmatrix_x4(a1, t + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kLd + k0 + (lane >> 4) * 8);
+      // B fragments from the same tile viewed as [n][k]: n-tiles {0,1} and {2,3}.
+      ldmatrix_x4(b01, t + ((lane & 7) + (lane >> 4) * 8) * kLd + k0 + ((lane >> 3) & 1) * 8);
+      ldmatrix_x4(b23, t + (16 + (lane & 7) + (lane >> 4) * 8) * kLd + k0 + ((lane >> 3) & 1) * 8);
+      mma_bf16(acc[0][0], a0, b01[0], b01[1]);
+      mma_bf16(acc[0][1], a0, b01[2], b01[3]);
+      mma_bf16(acc[1][0], a1, b01[0], b01[1]);
+      mma_bf16(acc[1][1], a1, b01[2], b01[3]);
+      mma_bf16(acc[1][2], a1, b23[0], b23[1]);
+      mma_bf16(acc[1][3], a1, b23[2], b23[3]);
+    }
+
+    for (int d = lane * 8; d < D; d += 256) *reinterpret_cast<uint4*>(o + d) = *reinterpret_cast<const uint4*>(t + d);  // row 0 = dense features
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        if (mt == 0 && nt >= 2) continue;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (off[mt][nt][e] >= 0) o[off[mt][nt][e]] = __float2bfloat16(acc[mt][nt][e]);
+      }
+    // zero the padding inside the last 16-byte group, then copy whole groups; groups past nvalid are zeros
+    for (int idx = nvalid + lane; idx < ((nvalid + 7) & ~7); idx += 32) o[idx] = __float2bfloat16(0.f);
+    __syncwarp();
+    __nv_bfloat16* dst = out + static_cast<size_t>(b) * out_ld;
+    for (int v = lane; v < (out_ld >> 3); v += 32) {
+      const uint4 x = v < nfull ? *reinterpret_cast<const uint4*>(o + v * 8) : make_uint4(0, 0, 0, 0);
+      *(reinterpret_cast<uint4*>(dst) + v) = x;
+    }
+    __syncwarp();   // the next sample's copies overwrite t and o
   }
 }
 
@@ -321,7 +335,9 @@ RS_API int rs_interaction_forward(const void* T, int B, int F, int D, void* out,
   RS_REQUIRE(F >= 1 && F <= kMaxF && D % 16 == 0 && D >= 16 && D <= kMaxD, "rs_interaction_forward: F=%d D=%d unsupported", F, D);
   RS_REQUIRE(out_ld % 8 == 0 && out_ld >= D + F * (F - 1) / 2, "rs_interaction_forward: out_ld=%d too small or unaligned", out_ld);
   if (B == 0) return RS_OK;
-  interaction_fwd_kernel<<<(B + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(
+  int grid = (B + kWarps - 1) / kWarps;
+  if (grid > 148 * 5) grid = 148 * 5;   // persistent: 5 CTAs of 4 warps fit one SM's shared memory
+  interaction_fwd_kernel<<<grid, kWarps * 32, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(T), B, F, D, reinterpret_cast<__nv_bfloat16*>(out), out_ld);
   RS_LAUNCH_CHECK();
   return RS_OK;
