@@ -1,6 +1,6 @@
 """PyTorch (+NCCL, +cuBLAS) restatement of the reference's distributed DLRM step.
 
-This is the measured same-box BASELINE and the numerical oracle, not the product path: it
+This is the measured same-box baseline and the numerical oracle, not the product path: it
 follows the reference algorithm with stock PyTorch ops only --
 ``nn.EmbeddingBag(mode="sum")`` per local table over the full batch, ``all_to_all_single`` of
 the pooled rows (src/executable/dlrm/dlrm_model.py:364-405, extend_distributed.py:389-486),

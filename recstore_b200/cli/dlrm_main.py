@@ -59,6 +59,8 @@ def parse_args(argv=None):
     p.add_argument("--save-model", default="")
     p.add_argument("--load-model", default="")
     p.add_argument("--use-gpu", action="store_true")
+    p.add_argument("--optimizer", default="sgd", choices=["sgd"], help="dense optimizer (the embeddings use --emb-optimizer)")
+    p.add_argument("--dist-backend", default="nccl", choices=["nccl"], help="bootstrap backend; the data plane is NVLink peer memory")
     return p.parse_args(argv)
 
 

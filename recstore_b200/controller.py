@@ -228,6 +228,49 @@ class ZipfPerfSampler(BasePerfSampler):
         return zipf_ids_torch(self.n, self.capacity, self.alpha, self.gen)
 
 
+class GraphCachedSampler:
+    """Lookahead wrapper of a knowledge-graph sampler: keeps the next ``L`` batches, and publishes the entity ids a
+    batch will touch (``cat(head, tail, negatives)``) when it enters the window, so that pending host-tier updates of
+    those rows are flushed before the step that reads them.  ``sampler`` yields ``(h, r, t, neg, corrupt_head)`` (e.g.
+    ``utils.kg_data.ChunkedNegativeSampler``).  Counterpart of the reference's wrapper around the DGL sampler
+    (src/python/pytorch/recstore/controller_process.py:160-242)."""
+
+    def __init__(self, sampler, rank: int, L: int, backmode: str = "CppAsyncV2", controller: Optional[KGCacheController] = None):
+        self.sampler, self.rank, self.L = sampler, rank, L
+        self.ring = CircleBuffer(L, rank, controller if backmode in ("CppAsync", "CppAsyncV2") else None)
+        self._batches: List = []
+
+    @staticmethod
+    def entity_ids(batch) -> torch.Tensor:
+        h, _, t, neg = batch[0], batch[1], batch[2], batch[3]
+        return torch.cat([h.reshape(-1), t.reshape(-1), neg.reshape(-1)]).cpu()
+
+    def _push(self) -> None:
+        b = next(self.sampler)
+        self._batches.append(b)
+        self.ring.push(self.entity_ids(b))
+
+    def Prefill(self) -> None:
+        for _ in range(self.L):
+            self._push()
+
+    def __next__(self):
+        self._push()
+        self.ring.pop()
+        return self._batches.pop(0)
+
+    def __iter__(self):
+        return self
+
+    @staticmethod
+    def BatchCreateCachedSamplers(L: int, samplers, backmode: str = "CppAsyncV2", controller: Optional[KGCacheController] = None):
+        """One cached sampler per rank-local sampler, all prefilled (rank = position in the list)."""
+        out = [GraphCachedSampler(s, r, L, backmode, controller) for r, s in enumerate(samplers)]
+        for c in out:
+            c.Prefill()
+        return out
+
+
 class KGCacheControllerWrapperBase:
     @staticmethod
     def BeforeDDPInit() -> None:

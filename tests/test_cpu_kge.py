@@ -163,3 +163,22 @@ def test_score_infer_modes_and_emb_similarity(tmp_path):
     assert lists[0][1][0].item() == 5 and abs(lists[0][2][0].item()) < 1e-6
     for fn in ("l1", "dot", "ext_jaccard"):
         assert EmbSimInfer(ent, fn).topk([0, 1], [2, 3], k=1, pair_ws=True)[0][2].numel() == 1
+
+
+def test_graph_cached_sampler_keeps_a_window_and_publishes_entity_ids():
+    from recstore_b200.controller import GraphCachedSampler
+    ds = K.KGDataset.synthetic(300, 4, 3000, seed=3)
+    published = []
+
+    class FakeController:
+        def PublishReads(self, rank, step, ids):
+            published.append((rank, step, ids.clone()))
+    mk = lambda seed: K.ChunkedNegativeSampler(ds.train, 300, 16, 8, 8, seed=seed)
+    cached = GraphCachedSampler.BatchCreateCachedSamplers(3, [mk(0), mk(1)], "CppAsyncV2", FakeController())
+    assert len(published) == 6 and [p[1] for p in published if p[0] == 0] == [0, 1, 2]
+    plain = mk(0)
+    for step in range(4):
+        got, want = next(cached[0]), next(plain)
+        assert all(torch.equal(a, b) for a, b in zip(got[:4], want[:4])) and got[4] == want[4]     # same stream, L steps later
+    mine = [p for p in published if p[0] == 0]
+    assert [p[1] for p in mine] == list(range(7)) and mine[0][2].numel() == 16 * 2 + 16
