@@ -20,10 +20,38 @@ import torch
 from ..utils.data import zipf_ids
 
 
+def write_binary_trace(path: str, requests, dim: int = 32) -> None:
+    """Writes key batches as the reference's binary trace: ``int32 nreq``, then per request ``int32 nkeys`` followed by
+    ``nkeys`` records of ``{uint64 key, int32 dim}`` (src/benchmark/parse_dataset.h:19-148)."""
+    with open(path, "wb") as f:
+        f.write(np.int32(len(requests)).tobytes())
+        for keys in requests:
+            k = np.asarray(keys, dtype=np.uint64)
+            f.write(np.int32(k.size).tobytes())
+            rec = np.zeros(k.size, dtype=np.dtype([("key", "<u8"), ("dim", "<i4")]))
+            rec["key"], rec["dim"] = k, dim
+            f.write(rec.tobytes())
+
+
+def read_binary_trace(path: str) -> List[np.ndarray]:
+    raw = np.fromfile(path, dtype=np.uint8)
+    nreq = int(raw[:4].view("<i4")[0])
+    o, out = 4, []
+    rec = np.dtype([("key", "<u8"), ("dim", "<i4")])
+    for _ in range(nreq):
+        n = int(raw[o:o + 4].view("<i4")[0]); o += 4
+        out.append(raw[o:o + n * rec.itemsize].view(rec)["key"].astype(np.int64)); o += n * rec.itemsize
+    if o != raw.size:
+        raise ValueError(f"{path}: {raw.size - o} trailing bytes after {nreq} requests")
+    return out
+
+
 class DatasetReplay:
     def __init__(self, path: str, offsets_path: Optional[str] = None, loop: bool = True):
         self.loop = loop
-        if path.endswith(".npy"):
+        if path.endswith(".bin"):
+            self.batches = read_binary_trace(path)
+        elif path.endswith(".npy"):
             ids = np.load(path).astype(np.int64).reshape(-1)
             if offsets_path:
                 off = np.load(offsets_path).astype(np.int64).reshape(-1)

@@ -128,3 +128,18 @@ def test_postoffice_roles_rendezvous_and_barrier():
         p.join(30)
     assert got[0] == ("client", 0, True)
     assert got[1][0] == got[2][0] == "server" and got[1][2] + got[2][2] == 40 and min(got[1][2], got[2][2]) > 0
+
+
+def test_binary_trace_roundtrip(tmp_path):
+    from recstore_b200.ps.load_generator import read_binary_trace, write_binary_trace
+    reqs = [[1, 2, 3], [], [2 ** 40 + 5]]
+    p = str(tmp_path / "t.bin")
+    write_binary_trace(p, reqs, dim=32)
+    assert [r.tolist() for r in read_binary_trace(p)] == reqs
+    assert (tmp_path / "t.bin").stat().st_size == 4 + 3 * 4 + 4 * 12
+    rep = DatasetReplay(p, loop=False)
+    assert [b.tolist() for b in rep] == reqs
+    with open(p, "ab") as f:
+        f.write(b"xx")
+    with pytest.raises(ValueError):
+        read_binary_trace(p)
