@@ -75,3 +75,34 @@ def test_checkpoint_roundtrip_preserves_predictions(tmp_path):
     b = src.next()
     assert meta["step"] == 5 and torch.allclose(m.predict(b.dense, b.ids), m2.predict(b.dense, b.ids))
     assert torch.equal(m.states[1], m2.states[1])
+
+
+def test_criteo_parser_random_dataset_and_trace_tools(tmp_path):
+    import torch
+    from recstore_b200.utils.dlrm_data import CriteoDataset, RandomDataset, criteo_preprocess, trace_generate, trace_profile
+    rng = np.random.default_rng(0)
+    lines = []
+    for i in range(200):
+        ints = [str(int(x)) if rng.random() > 0.1 else "" for x in rng.integers(0, 50, 13)]
+        cats = ["%08x" % int(x) if rng.random() > 0.05 else "" for x in rng.integers(0, 7, 26)]
+        lines.append("\t".join([str(int(rng.random() < 0.3))] + ints + cats) + "\n")
+    lines.append("garbage line\n")
+    d = criteo_preprocess(lines, str(tmp_path / "c.npz"))
+    assert d["y"].shape == (200,) and d["X_cat"].shape == (200, 26) and int(d["counts"].max()) <= 8
+    assert (d["X_cat"].max(0) < d["counts"]).all()
+    ds = CriteoDataset(str(tmp_path / "c.npz"), batch=32)
+    b = next(iter(ds))
+    assert b.dense.shape == (32, 13) and len(b.ids) == 26 and b.ids[3].shape == (32,) and len(ds) == 5 and len(ds.table_rows) == 26
+    assert torch.all(b.dense >= 0)
+    rb = next(iter(RandomDataset([10, 1000], 4, 16, 2, num_indices_per_lookup=5, fixed=False, alpha=1.1, seed=1)))
+    assert rb.offsets[0][0] == 0 and rb.ids[1].numel() >= 16 and int(rb.ids[0].max()) < 10
+    trace = np.array([1, 2, 1, 3, 2, 1, 4, 1, 2, 3] * 30)
+    uniq, dist, p = trace_profile(trace)
+    assert uniq == [1, 2, 3, 4] and abs(p.sum() - 1) < 1e-12 and dist[0] == 0
+    syn = trace_generate(uniq, dist, p, 3000, seed=2)
+    _, d2, p2 = trace_profile(syn)
+    common = {int(a): b for a, b in zip(dist, p)}
+    for a, b in zip(d2, p2):
+        if int(a) in common and common[int(a)] > 0.1:
+            assert abs(b - common[int(a)]) < 0.05          # the reuse distribution is reproduced
+    assert set(syn.tolist()) <= {1, 2, 3, 4}
