@@ -353,8 +353,8 @@ class DLRM:
         self._stamp("start")
         F_.pad_cast_bf16(self.in_dense[slot], self.x0p); self._count()
         main = torch.cuda.current_stream(self.dev)
-        overlap = self.world > 1
-        if overlap:   # the lookup and its all-to-all (peer stores) run beside the bottom MLP
+        overlap = True   # the lookup (bound by HBM, and by NVLink when multi-GPU) runs beside the bottom MLP (bound by the tensor pipe)
+        if overlap:
             self.s_comm.wait_stream(main)
         with torch.cuda.stream(self.s_comm if overlap else main):
             if self.Tl:
@@ -372,8 +372,8 @@ class DLRM:
             F_.gemm_bf16(x, L.wb, out, mode=0, epi=F_.EPI_RELU, bias=L.b, status=st, n=L.N); self._count()
             x = out
         self._stamp("bot_fwd_done")
+        main.wait_stream(self.s_comm)
         if self.world > 1:
-            main.wait_stream(self.s_comm)
             self.ctx.wait(CH_FWD); self._count()
         self._stamp("a2a_fwd_arrived")
         if self.dcn:
@@ -462,6 +462,18 @@ class DLRM:
                                     self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
                                     relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax)
             self._count()
+        # ---- sparse optimizer on the owned rows: bound by HBM (and by the peers' pushes), so it runs on the
+        # communication stream beside the bottom MLP's backward, the dense all-reduce and the SGD step
+        self.s_comm.wait_stream(main)
+        with torch.cuda.stream(self.s_comm):
+            if self.world > 1:
+                self.ctx.wait(CH_BWD); self._count()
+            if self.Tl:
+                F_.emb_backward(self.weight, self.state, self.row_idx, self.occ2bag, self.nnz, self.Gwin.local,
+                                grad_col=self.grad_col, grad_row_stride=self.grow_stride, B=self.B, D=self.D,
+                                grad_bf16=True, lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st,
+                                gnorm=self.gnorm, gnorm_stride=self.Tmax)
+                self._count(2 if c.emb_optimizer == "rowwise_adagrad" else 1)
         self._stamp("interaction_bwd_done")
         # ---- bottom MLP backward
         for i in range(len(self.bot) - 1, -1, -1):
@@ -490,17 +502,7 @@ class DLRM:
             self._count()
             if not solo:
                 self.grads.zero_(); self._count()
-        # ---- sparse optimizer on the owned rows
-        if self.world > 1:
-            main.wait_stream(self.s_comm)
-            self.ctx.wait(CH_BWD); self._count()
-        self._stamp("a2a_bwd_arrived")
-        if self.Tl:
-            F_.emb_backward(self.weight, self.state, self.row_idx, self.occ2bag, self.nnz, self.Gwin.local,
-                            grad_col=self.grad_col, grad_row_stride=self.grow_stride, B=self.B, D=self.D,
-                            grad_bf16=True, lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st,
-                            gnorm=self.gnorm, gnorm_stride=self.Tmax)
-            self._count(2 if c.emb_optimizer == "rowwise_adagrad" else 1)
+        main.wait_stream(self.s_comm)
         self._stamp("emb_bwd_done")
         main.wait_stream(side)
         self._stamp("sgd_done")
