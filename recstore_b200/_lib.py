@@ -68,6 +68,7 @@ _SIGNATURES = {
     "rs_rows_scatter": (i32, [vp, vp, i64, i32, vp, vp]),
     # ops/interaction.cu
     "rs_interaction_forward": (i32, [vp, i32, i32, i32, vp, i32, vp]),
+    "rs_interaction_dx": (i32, [vp, vp, i32, i32, i32, i32, vp, i32, i32, vp]),
     "rs_interaction_backward": (i32, [vp, vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, i64, i64, i32, vp, i32, i32, vp]),
     # ops/dense.cu
     "rs_head_bce": (i32, [vp, i32, i32, i32, vp, vp, vp, f32, vp, vp, vp, i32, vp, vp, vp]),

@@ -328,7 +328,71 @@ __global__ void __launch_bounds__(kWarpsBwd * 32) interaction_bwd_kernel(const I
   }
 }
 
+// Gradient of feature 0 only (the bottom MLP's output): dx = dOut[0:D] + sum_{j>=1} dZ[j][0] * T[j], ReLU-masked.
+// One warp per sample, every row load independent: a matrix-vector product at memory speed, so that the bottom
+// MLP's backward can start while the full backward (which pushes the embedding gradients) is still running.
+__global__ void __launch_bounds__(256, 2) interaction_dx_kernel(const __nv_bfloat16* __restrict__ T, const __nv_bfloat16* __restrict__ dout,
+                                                             int B, int F, int D, int dout_ld, __nv_bfloat16* __restrict__ dx,
+                                                             int dx_ld, int relu_mask) {
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b >= B) return;
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat16* t = T + static_cast<size_t>(b) * F * D;
+  const __nv_bfloat16* go = dout + static_cast<size_t>(b) * dout_ld;
+  // lane j (1 <= j < F) fetches its coefficient dZ[j][0]; they are broadcast by shuffles below
+  float coef = 0.f;
+  if (lane >= 1 && lane < F) coef = __bfloat162float(go[D + lane * (lane - 1) / 2]);
+  for (int c0 = lane * 4; c0 < D; c0 += 128) {
+    float acc[4];
+    const uint2 g0 = *reinterpret_cast<const uint2*>(go + c0);
+    const uint2 x0 = *reinterpret_cast<const uint2*>(t + c0);
+    {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g0.x));
+      const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g0.y));
+      acc[0] = a.x; acc[1] = a.y; acc[2] = c.x; acc[3] = c.y;
+    }
+    uint2 rows[kMaxF];
+#pragma unroll
+    for (int j = 1; j < kMaxF; ++j)
+      if (j < F) rows[j] = __ldg(reinterpret_cast<const uint2*>(t + static_cast<size_t>(j) * D + c0));
+#pragma unroll
+    for (int j = 1; j < kMaxF; ++j) {
+      const float w = __shfl_sync(0xffffffffu, coef, j);
+      if (j < F) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rows[j].x));
+        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rows[j].y));
+        acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * c.x; acc[3] += w * c.y;
+      }
+    }
+    if (relu_mask) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x0.x));
+      const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x0.y));
+      if (!(a.x > 0.f)) acc[0] = 0.f;
+      if (!(a.y > 0.f)) acc[1] = 0.f;
+      if (!(c.x > 0.f)) acc[2] = 0.f;
+      if (!(c.y > 0.f)) acc[3] = 0.f;
+    }
+    uint2 o;
+    o.x = pack2(acc[0], acc[1]);
+    o.y = pack2(acc[2], acc[3]);
+    *reinterpret_cast<uint2*>(dx + static_cast<size_t>(b) * dx_ld + c0) = o;
+  }
+}
+
 }  // namespace
+
+RS_API int rs_interaction_dx(const void* T, const void* dout, int B, int F, int D, int dout_ld, void* dx, int dx_ld,
+                             int relu_mask_dx, cudaStream_t stream) {
+  RS_REQUIRE(T && dout && dx, "rs_interaction_dx: null argument");
+  RS_REQUIRE(F >= 1 && F <= kMaxF && D % 16 == 0 && D >= 16 && D <= kMaxD, "rs_interaction_dx: F=%d D=%d unsupported", F, D);
+  RS_REQUIRE(dout_ld % 4 == 0 && dx_ld % 4 == 0, "rs_interaction_dx: leading dimensions must be multiples of 4");
+  if (B == 0) return RS_OK;
+  interaction_dx_kernel<<<(B + 7) / 8, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(T),
+                                                         reinterpret_cast<const __nv_bfloat16*>(dout), B, F, D, dout_ld,
+                                                         reinterpret_cast<__nv_bfloat16*>(dx), dx_ld, relu_mask_dx);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
 
 RS_API int rs_interaction_forward(const void* T, int B, int F, int D, void* out, int out_ld, cudaStream_t stream) {
   RS_REQUIRE(T && out, "rs_interaction_forward: null argument");

@@ -445,11 +445,9 @@ class DLRM:
                 self.ctx.signal(CH_BWD); self._count()
         elif self.world > 1:
             # The gradient all-to-all (peer stores from the kernel) is bound by NVLink, not by the SMs: a first pass
-            # produces only the bottom MLP's input gradient, then the pass that pushes the embedding gradients runs
+            # produces only the bottom MLP's input gradient (a matrix-vector product per sample), then the pass that pushes the embedding gradients runs
             # on the communication stream beside the bottom MLP's backward.
-            F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
-                                    self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
-                                    relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax, rows=1)
+            F_.interaction_dx(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], relu_mask_dx=True)
             self.s_comm.wait_stream(main)
             with torch.cuda.stream(self.s_comm):
                 F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,

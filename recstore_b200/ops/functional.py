@@ -111,6 +111,14 @@ def interaction_backward(T, dout, B: int, F: int, D: int, dx, gdst_table, owner,
          ptr(ndst_table), nstride, rows, stream_ptr())
 
 
+def interaction_dx(T, dout, B: int, F: int, D: int, dx, relu_mask_dx: bool = True) -> None:
+    """Only the gradient of feature 0 of :func:`interaction_forward` (a matrix-vector product per sample); the rest of
+    the backward can then run beside whatever consumes ``dx``."""
+    _need_cuda(T, dout, dx)
+    call("rs_interaction_dx", ptr(T), ptr(dout), B, F, D, dout.stride(0), ptr(dx), dx.stride(0), 1 if relu_mask_dx else 0,
+         stream_ptr())
+
+
 def head_bce(x, w, bias, labels, inv_batch: float, *, prob=None, loss_sum=None, dx=None, dw=None, db=None) -> None:
     """Final 1-output linear layer + sigmoid + BCE and all its gradients in one kernel."""
     _need_cuda(x, w)

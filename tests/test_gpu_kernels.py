@@ -229,6 +229,20 @@ def test_interaction(dev, F, D):
                             torch.zeros(max(F - 1, 1), **i32), torch.tensor([f * D for f in range(max(F - 1, 1))], **i32),
                             Gw.stride(0), 0, relu_mask_dx=True)
     assert _rel_err(dx, gref[:, 0] * (T[:, 0].float() > 0)) < 2e-2
+    # the stand-alone dx pass (what lets the bottom MLP's backward start early) and the push-only pass
+    dx2 = torch.zeros_like(dx)
+    F_.interaction_dx(T, dout, B, F, D, dx2, relu_mask_dx=True)
+    assert _rel_err(dx2, gref[:, 0] * (T[:, 0].float() > 0)) < 2e-2
+    F_.interaction_dx(T, dout, B, F, D, dx2, relu_mask_dx=False)
+    assert _rel_err(dx2, gref[:, 0]) < 2e-2
+    if F > 1:
+        Gw.zero_()
+        dx3 = torch.full_like(dx, 7.0)
+        F_.interaction_backward(T, dout, B, F, D, dx3, torch.tensor([Gw.data_ptr()], dtype=torch.int64, device=dev),
+                                torch.zeros(F - 1, **i32), torch.tensor([f * D for f in range(F - 1)], **i32),
+                                Gw.stride(0), 0, relu_mask_dx=True, rows=2)
+        torch.cuda.synchronize()
+        assert bool((dx3 == 7.0).all()) and _rel_err(Gw[:, :(F - 1) * D].view(B, F - 1, D), gref[:, 1:]) < 2e-2
 
 
 # ---------------------------------------------------------------------------------------------- head / small dense ops
