@@ -32,6 +32,7 @@
 // loop of tile i+1.  Every mbarrier wait is bounded; on give-up the kernel sets
 // RS_DEV_WAIT_TIMEOUT in the status word, frees TMEM and returns.
 #include <cuda_bf16.h>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 #include "common/ptx.cuh"
@@ -115,14 +116,22 @@ struct WorkIter {
   }
 };
 
-template <int MODE>
+// CG = 1: one CTA per 128 x bn tile.  CG = 2: a pair of CTAs (cluster of 2) per 256 x bn tile: CTA `rank` holds
+// rows [rank * 128, +128) of A and rows [rank * bn / 2, + bn / 2) of B, the leader (rank 0) issues cta_group::2 MMAs
+// that read both CTAs' shared memory, and each CTA reads back its own 128 accumulator rows.  The pair halves the
+// B-operand traffic per CTA (48 KB -> 32 KB per k-block), which is what bounds the single-CTA main loop.
+template <int MODE, int CG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ CUtensorMap tma_d, const GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw;   // the kernel has no static shared memory: the dynamic window starts 1024-byte aligned (checked below)
   const int stages = g.stages;
-  const uint32_t b_bytes = static_cast<uint32_t>(g.bn) * BK * 2;
+  const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
+  const bool leader_cta = rank == 0;
+  const int bn_cta = g.bn / CG;                          // rows of the B tile this CTA loads
+  const uint32_t b_bytes = static_cast<uint32_t>(bn_cta) * BK * 2;
+  const int cta_id = blockIdx.x / CG, n_ctas = gridDim.x / CG;   // work is handed out per CTA (CG = 1) or per pair
   uint8_t* sA = smem;
   uint8_t* sB = smem + static_cast<size_t>(stages) * kABytes;
   uint8_t* sStage = sB + static_cast<size_t>(stages) * b_bytes;   // per epilogue group: one chunk; then the bias slices
@@ -147,7 +156,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], kEpiWarps * 32);
+      mbar_init(&tempty[a], kEpiWarps * 32 * CG);   // the leader's barrier collects both CTAs' epilogue threads
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -156,13 +165,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if (g.tma_out) tma_prefetch_desc(&tma_d);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if (CG == 2) { tmem_alloc_pair(tmem_slot, kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (CG == 2) cluster_sync_all();   // the peer's barriers are initialised before anything is signalled across CTAs
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Releasing an accumulator: an arrival on the leader's tempty barrier (local for CG = 1).
+  auto release_acc = [&](int a) {
+    if (CG == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[a]), 0));
+    else mbar_arrive(&tempty[a]);
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -171,25 +186,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       bool ok = true;
       int last_stage = -1;
       uint32_t last_phase = 0;
-      WorkIter w(g, blockIdx.x, gridDim.x);
+      WorkIter w(g, cta_id, n_ctas);
       int tile, kb0, kb1;
       while (ok && w.next(tile, kb0, kb1)) {
-        const int m0 = (tile / g.tiles_n) * BM;
-        const int n0 = (tile % g.tiles_n) * g.bn;
+        const int m0 = (tile / g.tiles_n) * (BM * CG) + static_cast<int>(rank) * BM;
+        const int n0 = (tile % g.tiles_n) * g.bn + static_cast<int>(rank) * bn_cta;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&full[stage], kABytes + b_bytes);
           uint8_t* a_dst = sA + static_cast<size_t>(stage) * kABytes;
           uint8_t* b_dst = sB + static_cast<size_t>(stage) * b_bytes;
-          if (MODE != 1) {
-            tma_load_2d(a_dst, &tma_a, &full[stage], kb * BK, m0);
+          if (CG == 1) {
+            mbar_expect_tx(&full[stage], kABytes + b_bytes);
+            if (MODE != 1) {
+              tma_load_2d(a_dst, &tma_a, &full[stage], kb * BK, m0);
+            } else {
+              for (int h = 0; h < BM / 64; ++h) tma_load_2d(a_dst + h * 8192, &tma_a, &full[stage], m0 + h * 64, kb * BK);
+            }
+            if (MODE == 0) {
+              tma_load_2d(b_dst, &tma_b, &full[stage], kb * BK, n0);
+            } else {
+              for (int h = 0; h < bn_cta / 64; ++h) tma_load_2d(b_dst + h * 8192, &tma_b, &full[stage], n0 + h * 64, kb * BK);
+            }
           } else {
-            for (int h = 0; h < BM / 64; ++h) tma_load_2d(a_dst + h * 8192, &tma_a, &full[stage], m0 + h * 64, kb * BK);
-          }
-          if (MODE == 0) {
-            tma_load_2d(b_dst, &tma_b, &full[stage], kb * BK, n0);
-          } else {
-            for (int h = 0; h < g.bn / 64; ++h) tma_load_2d(b_dst + h * 8192, &tma_b, &full[stage], n0 + h * 64, kb * BK);
+            // Both CTAs' copies are counted on the leader's barrier; only the leader announces the bytes (of both).
+            if (leader_cta) mbar_expect_tx(&full[stage], 2u * (kABytes + b_bytes));
+            const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
+            if (MODE != 1) {
+              tma_load_2d_pair(a_dst, &tma_a, bar, kb * BK, m0);
+            } else {
+              for (int h = 0; h < BM / 64; ++h) tma_load_2d_pair(a_dst + h * 8192, &tma_a, bar, m0 + h * 64, kb * BK);
+            }
+            if (MODE == 0) {
+              tma_load_2d_pair(b_dst, &tma_b, bar, kb * BK, n0);
+            } else {
+              for (int h = 0; h < bn_cta / 64; ++h) tma_load_2d_pair(b_dst + h * 8192, &tma_b, bar, n0 + h * 64, kb * BK);
+            }
           }
           last_stage = stage;
           last_phase = phase;
@@ -197,19 +228,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
       }
       if (!ok && last_stage >= 0) {
-        // Leaving early: let the copies already in flight land before the CTA's shared memory goes away.
-        mbar_wait(&full[last_stage], last_phase, nullptr, 1u << 16);
+        // Leaving early: let the copies already in flight land before the CTA's shared memory goes away.  (The peer
+        // of a pair cannot see the leader's barrier complete; it just gives its copies time.)
+        if (CG == 1 || leader_cta) mbar_wait(&full[last_stage], last_phase, nullptr, 1u << 16);
+        else for (int i = 0; i < 64; ++i) __nanosleep(1000);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(BM, static_cast<uint32_t>(g.bn), MODE == 1 ? 1u : 0u, MODE != 0 ? 1u : 0u);
+    if (lane == 0 && leader_cta) {
+      const uint32_t idesc = make_idesc_bf16(BM * CG, static_cast<uint32_t>(g.bn), MODE == 1 ? 1u : 0u, MODE != 0 ? 1u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      WorkIter w(g, blockIdx.x, gridDim.x);
+      WorkIter w(g, cta_id, n_ctas);
       int tile, kb0, kb1;
       while (ok && w.next(tile, kb0, kb1)) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -231,13 +264,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             else ad = make_smem_desc(a_addr + k * 2048, 8192, 1024, 2);
             if (MODE == 0) bd = make_smem_desc(b_addr + k * 32, 16, 1024, 2);
             else bd = make_smem_desc(b_addr + k * 2048, 8192, 1024, 2);
-            umma_f16(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (CG == 2) umma_f16_pair(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else umma_f16(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&empty[stage]);
+          if (CG == 2) umma_commit_pair(&empty[stage], 3);   // frees the stage in both CTAs
+          else umma_commit(&empty[stage]);
           if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(&tfull[acc]);
+        if (CG == 2) umma_commit_pair(&tfull[acc], 3);     // each CTA's epilogue waits on its own barrier
+        else umma_commit(&tfull[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -260,10 +296,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const uint32_t sw = static_cast<uint32_t>(srow & 7);
       const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
       const int nchunks = g.bn / 64;
-      WorkIter w(g, blockIdx.x, gridDim.x);
+      WorkIter w(g, cta_id, n_ctas);
       int tile, kb0, kb1;
       while (w.next(tile, kb0, kb1)) {
-        const int m0 = (tile / g.tiles_n) * BM;
+        const int m0 = (tile / g.tiles_n) * (BM * CG) + static_cast<int>(rank) * BM;
         const int n0 = (tile % g.tiles_n) * g.bn;
         // The tile's bias slice is requested before the accumulator is ready, so its latency hides behind the wait.
         float2 bv = make_float2(0.f, 0.f);
@@ -330,7 +366,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           tmem_ld_wait();
           if (c + kParts >= nchunks || col0 + kParts * 64 >= g.N) {   // last chunk of this thread in the tile
             tc_fence_before_sync();
-            mbar_arrive(&tempty[acc]);
+            release_acc(acc);
             released = true;
           }
           uint32_t pk[32];
@@ -380,17 +416,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         if (!released) {
           tc_fence_before_sync();
-          mbar_arrive(&tempty[acc]);
+          release_acc(acc);
         }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
       if (leader) tma_store_wait<0>();   // shared memory must outlive the stores that read it
     } else {
-    WorkIter w(g, blockIdx.x, gridDim.x);
+    WorkIter w(g, cta_id, n_ctas);
     int tile, kb0, kb1;
     while (ok && w.next(tile, kb0, kb1)) {
-      const int m0 = (tile / g.tiles_n) * BM;
+      const int m0 = (tile / g.tiles_n) * (BM * CG) + static_cast<int>(rank) * BM;
       const int n0 = (tile % g.tiles_n) * g.bn;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
@@ -475,7 +511,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           __syncwarp();
         }
         tc_fence_before_sync();
-        mbar_arrive(&tempty[acc]);
+        release_acc(acc);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
         continue;
@@ -571,7 +607,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
       }
       tc_fence_before_sync();
-      mbar_arrive(&tempty[acc]);
+      release_acc(acc);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -580,9 +616,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
   tc_fence_before_sync();
   __syncthreads();
+  if (CG == 2) cluster_sync_all();   // the leader's MMAs read the peer's shared memory until the very end
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (CG == 2) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag && g.status) atomicOr(g.status, (unsigned long long)RS_DEV_WAIT_TIMEOUT);
 }
@@ -688,12 +726,19 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   RS_REQUIRE(bn % 32 == 0 && bn <= 256 && bn >= 32, "rs_gemm_bf16: bad tile width %d", bn);
   RS_REQUIRE(mode == 0 || bn % 64 == 0, "rs_gemm_bf16: modes 1 and 2 need a tile width multiple of 64");
 
+  // CTA pairs (cta_group::2) when the problem has at least one 256-row tile and the B tile splits into two
+  // 64-column-aligned halves.  RECSTORE_GEMM_CTA_PAIRS=0 keeps every GEMM on single CTAs.
+  static const bool pairs_allowed = [] {
+    const char* e = getenv("RECSTORE_GEMM_CTA_PAIRS");
+    return !(e && e[0] == '0');
+  }();
+  const int cg = (pairs_allowed && M >= 2 * BM && bn % 128 == 0 && num_sms() % 2 == 0) ? 2 : 1;
   GemmArgs g;
   g.M = M; g.N = N; g.K = K; g.bn = bn;
-  g.tiles_m = (M + BM - 1) / BM;
+  g.tiles_m = (M + BM * cg - 1) / (BM * cg);
   g.tiles_n = (N + bn - 1) / bn;
   g.kblocks = (K + BK - 1) / BK;
-  const int sms = num_sms();
+  const int sms = num_sms() / cg;   // schedulable units: CTAs or CTA pairs
   g.units_per_cta = 0;
   int grid_override = 0;
   if (epi == 3) {
@@ -723,7 +768,7 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
     splits = (g.kblocks + per - 1) / per;
   }
   g.splits = splits;
-  const uint32_t stage_bytes = kABytes + static_cast<uint32_t>(bn) * BK * 2;
+  const uint32_t stage_bytes = kABytes + static_cast<uint32_t>(bn / cg) * BK * 2;
   int stages = static_cast<int>((227u * 1024u - kStageBytes - 256u) / stage_bytes);
   if (stages > 8) stages = 8;
   if (stages < 2) stages = 2;
@@ -739,23 +784,35 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   int rc;
   if (mode != 1) { if ((rc = make_map_bf16(&ma, A, M, K, lda, BM, BK)) != RS_OK) return rc; }
   else { if ((rc = make_map_bf16(&ma, A, K, M, lda, BK, 64)) != RS_OK) return rc; }
-  if (mode == 0) { if ((rc = make_map_bf16(&mb, B, N, K, ldb, bn, BK)) != RS_OK) return rc; }
+  if (mode == 0) { if ((rc = make_map_bf16(&mb, B, N, K, ldb, bn / cg, BK)) != RS_OK) return rc; }
   else { if ((rc = make_map_bf16(&mb, B, K, N, ldb, BK, 64)) != RS_OK) return rc; }
   if (g.tma_out) { if ((rc = make_map_bf16(&md, D, M, N, ldd, BM, 64)) != RS_OK) return rc; }
   else md = ma;   // unused by the kernel
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + kStageBytes + 256;
-  static bool attr_set[3] = {false, false, false};
-  if (!attr_set[mode]) {
-    if (mode == 0) RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    else if (mode == 1) RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    else RS_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set[mode] = true;
+  using Kern = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmArgs);
+  static const Kern kernels[2][3] = {{gemm_tcgen05_kernel<0, 1>, gemm_tcgen05_kernel<1, 1>, gemm_tcgen05_kernel<2, 1>},
+                                     {gemm_tcgen05_kernel<0, 2>, gemm_tcgen05_kernel<1, 2>, gemm_tcgen05_kernel<2, 2>}};
+  static bool attr_set[2][3] = {{false, false, false}, {false, false, false}};
+  const Kern kern = kernels[cg - 1][mode];
+  if (!attr_set[cg - 1][mode]) {
+    RS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_set[cg - 1][mode] = true;
   }
   const int items = g.tiles_m * g.tiles_n * g.splits;
-  const int grid = grid_override > 0 ? grid_override : (items < sms ? items : sms);
-  if (mode == 0) gemm_tcgen05_kernel<0><<<grid, kThreads, smem, stream>>>(ma, mb, md, g);
-  else if (mode == 1) gemm_tcgen05_kernel<1><<<grid, kThreads, smem, stream>>>(ma, mb, md, g);
-  else gemm_tcgen05_kernel<2><<<grid, kThreads, smem, stream>>>(ma, mb, md, g);
+  const int units = grid_override > 0 ? grid_override : (items < sms ? items : sms);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(units * cg));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(cg);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cg == 2 ? 1 : 0;
+  RS_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, md, g));
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
