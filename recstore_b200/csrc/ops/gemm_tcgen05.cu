@@ -83,14 +83,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 //                       does the same number of k-blocks whatever tiles x splits would have divided the SMs into;
 //                       a range that crosses a tile boundary yields two segments (fp32 atomic epilogue only).
 struct WorkIter {
-  int it, items, stride, tiles, kb_per_split, kblocks;
+  int cur_tile, cur_split, splits, stride, tiles, kb_per_split, kblocks;
   long long u, uend;
   bool balanced;
   __device__ WorkIter(const GemmArgs& g, int cta, int grid) {
     tiles = g.tiles_m * g.tiles_n;
     kblocks = g.kblocks;
     balanced = g.units_per_cta > 0;
-    it = cta; stride = grid; items = tiles * g.splits;
+    stride = grid; splits = g.splits;
+    cur_tile = cta % tiles; cur_split = cta / tiles;       // the only divisions: next() is on the MMA thread's path
     kb_per_split = (g.kblocks + g.splits - 1) / g.splits;
     u = static_cast<long long>(cta) * g.units_per_cta;
     uend = u + g.units_per_cta;
@@ -99,11 +100,12 @@ struct WorkIter {
   }
   __device__ bool next(int& tile, int& kb0, int& kb1) {
     if (!balanced) {
-      if (it >= items) return false;
-      tile = it % tiles;
-      kb0 = (it / tiles) * kb_per_split;
+      if (cur_split >= splits) return false;
+      tile = cur_tile;
+      kb0 = cur_split * kb_per_split;
       kb1 = min(kblocks, kb0 + kb_per_split);
-      it += stride;
+      cur_tile += stride;                                   // item index advances by the grid size
+      while (cur_tile >= tiles) { cur_tile -= tiles; ++cur_split; }
       return true;
     }
     if (u >= uend) return false;
@@ -311,8 +313,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         ok = bar_red_and(bar_id, 128, mine);
         if (!ok) break;
         tc_fence_after_sync();
-        const int row = m0 + srow;
-        const bool row_ok = row < g.M;
         bool released = false;
         for (int c = part; c < nchunks; c += kParts) {
           const int col0 = n0 + c * 64;
