@@ -39,6 +39,8 @@ def main(argv=None):
     ap.add_argument("--alphas", type=float, nargs="+", default=[0.9, 1.1, 1.3])
     ap.add_argument("--batches", type=int, nargs="+", default=[4096, 32768, 262144])
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--sharded-tiered", action="store_true",
+                    help="with --sharded / several ranks: every shard keeps only --hbm-ratio of its rows in HBM, the rest in pinned host memory")
     ap.add_argument("--sharded", action="store_true", help="all-HBM table sharded over the ranks instead of the tiered table")
     a = ap.parse_args(argv)
     from recstore_b200.utils.data import zipf_ids_torch
@@ -53,7 +55,8 @@ def main(argv=None):
         from recstore_b200.parallel.peer import PeerContext
         from recstore_b200.parallel.sharded_table import ShardedEmbeddingTable
         ctx = PeerContext(rank, world, device=dev)
-        tab = ShardedEmbeddingTable(ctx, "psbench", a.rows, a.dim, max_keys=maxb, lr=0.01)
+        tab = ShardedEmbeddingTable(ctx, "psbench", a.rows, a.dim, max_keys=maxb, lr=0.01,
+                                    hbm_ratio=a.hbm_ratio if a.sharded_tiered else 1.0)
     else:
         from recstore_b200.cache.tiered_table import TieredEmbeddingTable
         tab = TieredEmbeddingTable(a.rows, a.dim, a.hbm_ratio, max_keys=maxb, lr=0.01, device=dev)
@@ -83,7 +86,7 @@ def main(argv=None):
                 remote = uniq * (world - 1) / world
                 rec.update({"ms": round(ms, 4), "mkeys_per_s_total": round(B * world / ms / 1e3, 2),
                             "nvlink_gbs_per_gpu": round(2 * tab.nvlink_bytes_per_lookup(int(remote)) / ms / 1e6, 2),
-                            "mode": f"sharded x{world}"})
+                            "mode": f"sharded x{world}" + (f" tiered hbm_ratio={a.hbm_ratio}" if a.sharded_tiered else "")})
             elif a.sharded:
                 rec["mode"] = "sharded x1"
             else:

@@ -69,7 +69,9 @@ __global__ void push_counts_kernel(int* counts, int* cursor, int world, int me, 
 }
 
 struct GatherArgs {
-  const float* weight;              // local shard [local_rows, D]
+  const float* weight;              // local shard [local_rows, D] (or its first hot_rows rows)
+  const float* cold_weight;         // rows [hot_rows, local_rows) in device-visible host memory, or null
+  long long hot_rows;
   long long local_rows;
   const long long* key_win;         // my key window   [world, cap]
   const int* count_win;             // my count window [world]
@@ -104,7 +106,11 @@ __global__ void __launch_bounds__(256) gather_push_rows_kernel(const GatherArgs 
   if (lane == 0) a.rowidx[w] = r;
   float* dst = a.row_win[s] + (static_cast<long long>(a.me) * a.cap + p) * a.D;
   for (int v = lane; v < (a.D >> 2); v += 32) {
-    const float4 x = r >= 0 ? __ldg(reinterpret_cast<const float4*>(a.weight + r * a.D) + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r >= 0) {
+      if (r < a.hot_rows) x = __ldg(reinterpret_cast<const float4*>(a.weight + r * a.D) + v);
+      else x = __ldcv(reinterpret_cast<const float4*>(a.cold_weight + (r - a.hot_rows) * a.D) + v);   // host tier, read in place
+    }
     reinterpret_cast<float4*>(dst)[v] = x;
   }
 }
@@ -204,12 +210,34 @@ RS_API int rs_shard_push_keys(const long long* keys, long long n, int world, int
   return RS_OK;
 }
 
+namespace {
+int launch_gather(const float* weight, const float* cold_weight, long long hot_rows, long long local_rows, const long long* key_win,
+                  const int* count_win, void* const* row_win, long long* rowidx, int world, int me, int D, long long cap,
+                  const rs::HashTableView* ht, unsigned long long* status, cudaStream_t stream);
+}  // namespace
+
 RS_API int rs_shard_gather_push_rows(const float* weight, long long local_rows, const long long* key_win, const int* count_win,
                                      void* const* row_win, long long* rowidx, int world, int me, int D, long long cap,
                                      const rs::HashTableView* ht, unsigned long long* status, cudaStream_t stream) {
-  RS_REQUIRE(weight && key_win && count_win && row_win && rowidx && D % 4 == 0, "rs_shard_gather_push_rows: bad argument");
+  return launch_gather(weight, nullptr, local_rows, local_rows, key_win, count_win, row_win, rowidx, world, me, D, cap, ht, status, stream);
+}
+
+// Same with a two-tier shard: rows [0, hot_rows) at `weight` (HBM), rows [hot_rows, local_rows) at `cold_weight`
+// (pinned host memory, device-visible).
+RS_API int rs_shard_gather_push_rows_tiered(const float* weight, const float* cold_weight, long long hot_rows, long long local_rows,
+                                            const long long* key_win, const int* count_win, void* const* row_win, long long* rowidx,
+                                            int world, int me, int D, long long cap, unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(hot_rows >= 0 && hot_rows <= local_rows && (hot_rows == local_rows || cold_weight), "rs_shard_gather_push_rows_tiered: bad tiers");
+  return launch_gather(weight, cold_weight, hot_rows, local_rows, key_win, count_win, row_win, rowidx, world, me, D, cap, nullptr, status, stream);
+}
+
+namespace {
+int launch_gather(const float* weight, const float* cold_weight, long long hot_rows, long long local_rows, const long long* key_win,
+                  const int* count_win, void* const* row_win, long long* rowidx, int world, int me, int D, long long cap,
+                  const rs::HashTableView* ht, unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE((weight || hot_rows == 0) && key_win && count_win && row_win && rowidx && D % 4 == 0, "rs_shard_gather_push_rows: bad argument");
   GatherArgs a;
-  a.weight = weight; a.local_rows = local_rows; a.key_win = key_win; a.count_win = count_win;
+  a.weight = weight; a.cold_weight = cold_weight; a.hot_rows = hot_rows; a.local_rows = local_rows; a.key_win = key_win; a.count_win = count_win;
   a.row_win = reinterpret_cast<float* const*>(row_win); a.rowidx = rowidx; a.world = world; a.me = me; a.D = D; a.cap = cap;
   a.use_hash = ht != nullptr;
   if (ht) a.ht = *ht; else memset(&a.ht, 0, sizeof(a.ht));
@@ -218,6 +246,7 @@ RS_API int rs_shard_gather_push_rows(const float* weight, long long local_rows, 
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
+}  // namespace
 
 RS_API int rs_shard_unbucket_rows(const float* row_win, const long long* slot, long long n, int D, void* out, int out_bf16,
                                   cudaStream_t stream) {

@@ -27,6 +27,8 @@ from .peer import PeerContext
 _lib.register_signatures({
     "rs_shard_push_keys": (i32, [vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp, vp]),
     "rs_shard_gather_push_rows": (i32, [vp, i64, vp, vp, vp, vp, i32, i32, i32, i64, C.POINTER(HashTableView), vp, vp]),
+    "rs_shard_gather_push_rows_tiered": (i32, [vp, vp, i64, i64, vp, vp, vp, vp, i32, i32, i32, i64, vp, vp]),
+    "rs_tiered_apply": (i32, [vp, vp, vp, vp, i64, i64, vp, i64, i32, vp, vp, f32, f32, i32, vp]),
     "rs_shard_unbucket_rows": (i32, [vp, vp, i64, i32, vp, i32, vp]),
     "rs_shard_push_grads": (i32, [vp, vp, i64, i32, i32, i64, vp, vp, vp, vp]),
     "rs_segment_sum": (i32, [vp, vp, i64, i32, vp, vp, vp]),
@@ -40,7 +42,7 @@ CH_KEYS, CH_ROWS, CH_GRADS = 8, 9, 10
 class ShardedEmbeddingTable:
     def __init__(self, ctx: PeerContext, name: str, num_rows: int, dim: int, max_keys: int, *, lr: float = 0.01,
                  eps: float = 1e-10, optimizer: str = "rowwise_adagrad", dedup: bool = True, init: str = "uniform",
-                 init_scale: Optional[float] = None, seed: int = 0):
+                 init_scale: Optional[float] = None, seed: int = 0, hbm_ratio: float = 1.0):
         assert dim % 4 == 0
         self.ctx, self.name, self.N, self.D = ctx, name, int(num_rows), int(dim)
         self.rank, self.world = ctx.rank, ctx.world
@@ -48,19 +50,34 @@ class ShardedEmbeddingTable:
         self.lr, self.eps, self.optimizer, self.dedup = lr, eps, optimizer, dedup
         dev = self.dev = ctx.device
         self.local_rows = (self.N + self.world - 1) // self.world
-        self.weight = torch.empty(self.local_rows, self.D, device=dev)
+        # Two tiers per shard when hbm_ratio < 1: local rows [0, hot_rows) in HBM, the rest in pinned host memory that
+        # the kernels address in place.  Local row = id // world, so with ids in popularity order the hot ids of every
+        # shard are its first rows.
+        self.hot_rows = self.local_rows if hbm_ratio >= 1.0 else max(1, int(math.ceil(self.local_rows * hbm_ratio)))
+        self.tiered = self.hot_rows < self.local_rows
+        self.cold = torch.empty(self.local_rows - self.hot_rows, self.D, pin_memory=True) if self.tiered else None
+        self.weight = torch.empty(self.hot_rows, self.D, device=dev)
         g = torch.Generator(device=dev).manual_seed(seed * 131 + self.rank)
         if init == "uniform":
             b = init_scale if init_scale is not None else math.sqrt(1.0 / self.N)
             self.weight.uniform_(-b, b, generator=g)
+            if self.tiered:
+                self.cold.uniform_(-b, b, generator=torch.Generator().manual_seed(seed * 131 + self.rank + 7))
         elif init == "zeros":
             self.weight.zero_()
+            if self.tiered:
+                self.cold.zero_()
         elif init == "row_index":                          # row of global id i holds the value i (tests)
-            ids = torch.arange(self.local_rows, device=dev, dtype=torch.float32) * self.world + self.rank
-            self.weight.copy_(ids.unsqueeze(1).expand(-1, self.D))
+            ids = torch.arange(self.local_rows, dtype=torch.float32) * self.world + self.rank
+            full = ids.unsqueeze(1).expand(-1, self.D)
+            self.weight.copy_(full[:self.hot_rows])
+            if self.tiered:
+                self.cold.copy_(full[self.hot_rows:])
         else:
             raise ValueError(init)
-        self.state = torch.zeros(self.local_rows, device=dev) if optimizer == "rowwise_adagrad" else None
+        adagrad = optimizer == "rowwise_adagrad"
+        self.state = torch.zeros(self.hot_rows, device=dev) if adagrad else None
+        self.cold_state = torch.zeros(self.local_rows - self.hot_rows, pin_memory=True) if adagrad and self.tiered else None
         W, cap, D = self.world, self.cap, self.D
         self.key_win = ctx.alloc(f"{name}.keys", W * cap * 8)
         self.count_win = ctx.alloc(f"{name}.counts", W * 4)
@@ -107,8 +124,13 @@ class ShardedEmbeddingTable:
         _lib.call("rs_shard_push_keys", ptr(keys), n, self.world, self.rank, self.cap, ptr(self._counts), ptr(self._cursor),
                   ptr(self.key_win.table), ptr(self.count_win.table), ptr(self._slot), ptr(st), sp)
         self.ctx.signal(CH_KEYS); self.ctx.wait(CH_KEYS)
-        _lib.call("rs_shard_gather_push_rows", ptr(self.weight), self.local_rows, self.key_win.local_ptr, self.count_win.local_ptr,
-                  ptr(self.row_win.table), ptr(self.rowidx), self.world, self.rank, self.D, self.cap, None, ptr(st), sp)
+        if self.tiered:
+            _lib.call("rs_shard_gather_push_rows_tiered", ptr(self.weight), ptr(self.cold), self.hot_rows, self.local_rows,
+                      self.key_win.local_ptr, self.count_win.local_ptr, ptr(self.row_win.table), ptr(self.rowidx), self.world,
+                      self.rank, self.D, self.cap, ptr(st), sp)
+        else:
+            _lib.call("rs_shard_gather_push_rows", ptr(self.weight), self.local_rows, self.key_win.local_ptr, self.count_win.local_ptr,
+                      ptr(self.row_win.table), ptr(self.rowidx), self.world, self.rank, self.D, self.cap, None, ptr(st), sp)
         self.ctx.signal(CH_ROWS); self.ctx.wait(CH_ROWS)
         if out is None:
             out = torch.empty(n, self.D, device=self.dev)
@@ -141,10 +163,50 @@ class ShardedEmbeddingTable:
                       ptr(self.grad_win.table), None, None, sp)
         self.ctx.signal(CH_GRADS); self.ctx.wait(CH_GRADS)
         nnz = self.world * self.cap
+        if self.tiered:
+            self._apply_tiered(nnz, gnorm, st, sp)
+            self.launches += 10
+            return
         F_.emb_backward(self.weight, self.state, self.rowidx, None, nnz, self.grad_win.view(torch.float32, (nnz, self.D)),
                         grad_row_stride=self.D, B=nnz, D=self.D, grad_bf16=False, lr=self.lr, eps=self.eps,
                         optimizer=self.optimizer, status=st, gnorm=gnorm, gnorm_stride=1)
         self.launches += 7
+
+    def _apply_tiered(self, nnz: int, gnorm, st, sp) -> None:
+        """Owner side of the tiered update: the received (row, gradient) pairs still hold duplicates across source ranks,
+        so they are folded once more here (unique + segment sum); every distinct row is then updated by exactly one
+        warp with plain loads and stores, which is what makes the host tier safe (no atomics over PCIe)."""
+        if not hasattr(self, "_own_uniq"):
+            n, dev = nnz, self.dev
+            ns = 2
+            while ns < 2 * n:
+                ns <<= 1
+            self._own_ns = ns
+            self._own_sk = torch.empty(ns, dtype=torch.int64, device=dev)
+            self._own_si = torch.empty(ns, dtype=torch.int32, device=dev)
+            self._own_uniq = torch.empty(n, dtype=torch.int64, device=dev)
+            self._own_inv = torch.empty(n, dtype=torch.int32, device=dev)
+            self._own_cnt = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._own_grad = torch.empty(n, self.D, device=dev)
+            self._own_norm = torch.empty(n, device=dev)
+            self._own_nbuf = torch.empty(n, device=dev)
+        rows = torch.where(self.rowidx < 0, torch.full_like(self.rowidx, self.local_rows), self.rowidx)   # empty slots -> a row past the shard (skipped)
+        grads = self.grad_win.view(torch.float32, (nnz, self.D))
+        self._own_uniq.fill_(-1)
+        _lib.call("rs_unique_keys", ptr(rows), nnz, ptr(self._own_sk), ptr(self._own_si), self._own_ns, ptr(self._own_uniq),
+                  ptr(self._own_inv), ptr(self._own_cnt), ptr(st), sp)
+        self._own_grad.zero_()
+        self._own_norm.zero_()
+        self._own_nbuf.zero_()
+        _lib.call("rs_segment_sum", ptr(grads), ptr(self._own_inv), nnz, self.D, ptr(self._own_grad), ptr(self._own_nbuf), sp)
+        if gnorm is not None:      # per-key squared norms travelled with the gradients: add them up per distinct row
+            self._own_norm.index_add_(0, self._own_inv.long().clamp_min(0), gnorm.view(-1)[:nnz] * (self.rowidx >= 0))
+            norm = self._own_norm
+        else:
+            norm = self._own_nbuf  # segment_sum's own sum of squares (rows were not folded at the source)
+        _lib.call("rs_tiered_apply", ptr(self.weight), ptr(self.state), ptr(self.cold), ptr(self.cold_state), self.hot_rows,
+                  self.local_rows, ptr(self._own_uniq), nnz, self.D, ptr(self._own_grad), ptr(norm), self.lr, self.eps,
+                  1 if self.optimizer == "rowwise_adagrad" else 0, sp)
 
     # ------------------------------------------------------------------ whole-table access (tests, checkpoints)
     def local_global_ids(self) -> torch.Tensor:

@@ -141,8 +141,9 @@ def _sharded_worker(rank, world, port, out):
         from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
         ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"))
         N, D, n = 5000, 32, 3000
-        for dedup in (True, False):
-            tab = ShardedEmbeddingTable(ctx, f"t{int(dedup)}", N, D, max_keys=n, lr=0.1, eps=1e-8, dedup=dedup, init="row_index")
+        for dedup, ratio in ((True, 1.0), (False, 1.0), (True, 0.2), (False, 0.2)):   # ratio < 1: host tier behind the HBM rows
+            tab = ShardedEmbeddingTable(ctx, f"t{int(dedup)}{int(ratio * 10)}", N, D, max_keys=n, lr=0.1, eps=1e-8, dedup=dedup,
+                                        init="row_index", hbm_ratio=ratio)
             # oracle: full table replicated on every rank
             W = torch.arange(N, device="cuda", dtype=torch.float32).unsqueeze(1).repeat(1, D)
             S = torch.zeros(N, device="cuda")
@@ -163,8 +164,10 @@ def _sharded_worker(rank, world, port, out):
             ctx.check_status()
             mine = tab.local_global_ids()
             mine = mine[mine < N]
-            assert torch.allclose(tab.weight[: mine.numel()], W[mine], atol=2e-3, rtol=2e-3), (rank, dedup)
-            assert torch.allclose(tab.state[: mine.numel()], S[mine], atol=1e-2, rtol=2e-3), (rank, dedup)
+            w_all = torch.cat([tab.weight.cpu(), tab.cold]) if tab.tiered else tab.weight.cpu()
+            s_all = torch.cat([tab.state.cpu(), tab.cold_state]) if tab.tiered else tab.state.cpu()
+            assert torch.allclose(w_all[: mine.numel()], W[mine].cpu(), atol=2e-3, rtol=2e-3), (rank, dedup, ratio)
+            assert torch.allclose(s_all[: mine.numel()], S[mine].cpu(), atol=1e-2, rtol=2e-3), (rank, dedup, ratio)
         dist.barrier()
         out[rank] = "ok"
     finally:
