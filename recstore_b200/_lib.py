@@ -75,7 +75,7 @@ _SIGNATURES = {
     "rs_colsum_bf16": (i32, [vp, i32, i32, i32, vp, vp]),
     "rs_dense_sgd": (i32, [vp, vp, i32, i32, f32, vp, i32, vp, i32, i32, vp]),
     "rs_vec_sgd": (i32, [vp, vp, i32, f32, i32, vp]),
-    "rs_dense_sgd_multi": (i32, [vp, vp, i32, i32, vp, vp, i32, f32, i32, vp]),
+    "rs_dense_sgd_multi": (i32, [vp, vp, i32, i32, vp, vp, i32, f32, i32, i64, i32, vp]),
     "rs_pad_cast_bf16": (i32, [vp, i32, i32, i32, vp, i32, vp]),
     "rs_mse_fwd_bwd": (i32, [vp, vp, i32, f32, vp, vp, vp]),
     "rs_cross_fwd": (i32, [vp, vp, vp, vp, i64, vp]),
@@ -90,6 +90,7 @@ _SIGNATURES = {
     "rs_ipc_close": (i32, [vp]),
     "rs_peer_signal": (i32, [vp, i32, i32, i32, vp, vp]),
     "rs_peer_wait": (i32, [vp, i32, i32, vp, u64, vp, vp]),
+    "rs_peer_sync": (i32, [vp, vp, i32, i32, i32, vp, vp, u64, vp, vp]),
     "rs_allreduce_push": (i32, [vp, vp, i32, i32, i64, f32, vp]),
     "rs_memset_async": (i32, [vp, i32, sz, vp]),
     "rs_stamp_time": (i32, [vp, vp]),

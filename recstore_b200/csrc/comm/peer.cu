@@ -69,6 +69,36 @@ __global__ void wait_kernel(const uint32_t* my_flags, int world, int channel, ui
   }
 }
 
+// Signal then wait on one channel in ONE launch (a barrier of the ranks): lane d publishes this rank's new epoch to
+// rank d, then waits for rank d's flag to reach this rank's new wait epoch.  Same bounds as wait_kernel.
+__global__ void sync_kernel(uint32_t* const* flags_of, const uint32_t* my_flags, int world, int me, int channel,
+                            uint32_t* sig_counters, uint32_t* wait_counters, unsigned long long timeout_ns,
+                            unsigned long long* status) {
+  const int d = threadIdx.x;
+  uint32_t se = 0, we = 0;
+  if (d == 0) { se = ++sig_counters[channel]; we = ++wait_counters[channel]; }
+  se = __shfl_sync(0xffffffffu, se, 0);
+  we = __shfl_sync(0xffffffffu, we, 0);
+  if (d >= world) return;
+  __threadfence_system();
+  st_release_sys(flags_of[d] + channel * world + me, se);
+  const uint32_t* f = my_flags + channel * world + d;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (true) {
+    const uint32_t v = ld_acquire_sys(f);
+    if (static_cast<int32_t>(v - we) >= 0) break;
+    if ((++spins & 63u) == 0u) {
+      if (globaltimer_ns() - t0 > timeout_ns) {
+        if (status) atomicOr(status, (unsigned long long)RS_DEV_WAIT_TIMEOUT | (static_cast<unsigned long long>(d) << 32) |
+                                         (static_cast<unsigned long long>(channel) << 48));
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
 // grads_of[p]: peer p's gradient buffer; reduced_of[p]: peer p's output buffer; n elements (fp32),
 // slice boundaries in float4 units.
 __global__ void __launch_bounds__(512) allreduce_push_kernel(const float* const* grads_of, float* const* reduced_of,
@@ -143,6 +173,15 @@ RS_API int rs_peer_wait(const void* my_flags, int world, int channel, unsigned* 
                         unsigned long long timeout_ns, unsigned long long* status, cudaStream_t stream) {
   RS_REQUIRE(my_flags && wait_counters && world >= 1 && world <= 32, "rs_peer_wait: bad argument");
   wait_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint32_t*>(my_flags), world, channel, wait_counters, timeout_ns, status);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+RS_API int rs_peer_sync(void* const* flags_of, const void* my_flags, int world, int me, int channel, unsigned* sig_counters,
+                        unsigned* wait_counters, unsigned long long timeout_ns, unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(flags_of && my_flags && sig_counters && wait_counters && world >= 1 && world <= 32, "rs_peer_sync: bad argument");
+  sync_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<uint32_t* const*>(flags_of), reinterpret_cast<const uint32_t*>(my_flags), world,
+                                    me, channel, sig_counters, wait_counters, timeout_ns, status);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

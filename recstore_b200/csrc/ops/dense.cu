@@ -196,9 +196,13 @@ __global__ void __launch_bounds__(256) dense_sgd_kernel(float* __restrict__ W, f
 
 // All layers of a model in one launch.  desc holds 8 int64 per layer: W, g, Wb, Wt (addresses), N, K, ldw, ldt;
 // tile_prefix[l] = first 32x32 tile of layer l; blocks past the last tile update the flat tail (biases, head).
+// `zero_shift` (elements, may be 0 with zero_base == nullptr): when the gradients that are read are a reduced copy, the
+// rank's own accumulation buffer holds the same layout at zero_base + (g - g_base); it is cleared here as well so
+// that no separate memset launch is needed.
 __global__ void __launch_bounds__(256) dense_sgd_multi_kernel(const long long* __restrict__ desc, const int* __restrict__ tile_prefix,
                                                               int n_layers, float* __restrict__ tail_w, float* __restrict__ tail_g,
-                                                              int tail_n, float lr, int zero_grad) {
+                                                              int tail_n, float lr, int zero_grad, long long zero_delta,
+                                                              int zero_other) {
   __shared__ float tile[32][33];
   const int total = tile_prefix[n_layers];
   int b = blockIdx.x;
@@ -207,6 +211,7 @@ __global__ void __launch_bounds__(256) dense_sgd_multi_kernel(const long long* _
     if (i < tail_n) {
       tail_w[i] -= lr * tail_g[i];
       if (zero_grad) tail_g[i] = 0.f;
+      if (zero_other) *(tail_g + i + zero_delta) = 0.f;
     }
     return;
   }
@@ -230,6 +235,7 @@ __global__ void __launch_bounds__(256) dense_sgd_multi_kernel(const long long* _
       v = W[idx] - lr * g[idx];
       W[idx] = v;
       if (zero_grad) g[idx] = 0.f;
+      if (zero_other) *(g + idx + zero_delta) = 0.f;
       if (Wb) Wb[static_cast<size_t>(n) * ldw + k] = __float2bfloat16(v);
     }
     tile[j][tx] = v;
@@ -421,13 +427,17 @@ RS_API int rs_dense_sgd(float* W, float* g, int N, int K, float lr, void* Wb, in
 }
 
 // SGD step of every dense layer plus the flat tail in one launch (see dense_sgd_multi_kernel for the descriptor).
+// zero_other != 0: a second buffer with the layout of the gradient buffer that is read (e.g. the rank's own accumulation
+// buffer when the step reads an all-reduced copy) lies `zero_delta` elements away from it and is cleared as well.
 RS_API int rs_dense_sgd_multi(const long long* desc, const int* tile_prefix, int n_layers, int total_tiles, float* tail_w,
-                              float* tail_g, int tail_n, float lr, int zero_grad, cudaStream_t stream) {
+                              float* tail_g, int tail_n, float lr, int zero_grad, long long zero_delta, int zero_other,
+                              cudaStream_t stream) {
   RS_REQUIRE(desc && tile_prefix && n_layers > 0 && total_tiles >= 0, "rs_dense_sgd_multi: bad argument");
   RS_REQUIRE(tail_n == 0 || (tail_w && tail_g), "rs_dense_sgd_multi: tail pointers missing");
   const int blocks = total_tiles + (tail_n + 255) / 256;
   if (blocks == 0) return RS_OK;
-  dense_sgd_multi_kernel<<<blocks, 256, 0, stream>>>(desc, tile_prefix, n_layers, tail_w, tail_g, tail_n, lr, zero_grad);
+  dense_sgd_multi_kernel<<<blocks, 256, 0, stream>>>(desc, tile_prefix, n_layers, tail_w, tail_g, tail_n, lr, zero_grad, zero_delta,
+                                                     zero_other);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

@@ -292,6 +292,7 @@ class DLRM:
         self.launches_per_step = 0
         self.s_wgrad = torch.cuda.Stream(device=dev)   # weight/bias gradients, then the dense all-reduce and SGD
         self.s_comm = torch.cuda.Stream(device=dev)    # embedding lookup / gradient push: the NVLink-bound kernels
+        self.s_col = torch.cuda.Stream(device=dev)     # bias gradients (column sums): bandwidth-bound, beside the wgrad GEMMs
         self._phase_names: List[str] = []
         self._phase_buf = torch.zeros(64, dtype=torch.int64, device=dev)
         self._warm_native()
@@ -411,10 +412,12 @@ class DLRM:
             dy = self.d_act_t[i]
             xin = self.act_t[i - 1] if i > 0 else self.z
             side.wait_stream(main)
-            with torch.cuda.stream(side):
+            self.s_col.wait_stream(main)
+            with torch.cuda.stream(self.s_col):
                 # Bias gradient as a pass of its own: summing columns inside the dgrad epilogue was measured slower
                 # (every CTA adds into the same N addresses) than this bandwidth-bound kernel.
                 F_.colsum_bf16(dy, L.gb); self._count()
+            with torch.cuda.stream(side):
                 F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
             if i > 0:
                 F_.gemm_bf16(dy, L.wt, self.d_act_t[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
@@ -479,8 +482,10 @@ class DLRM:
             dy = self.d_act_b[i]
             xin = self.act_b[i - 1] if i > 0 else self.x0p
             side.wait_stream(main)
-            with torch.cuda.stream(side):
+            self.s_col.wait_stream(main)
+            with torch.cuda.stream(self.s_col):
                 F_.colsum_bf16(dy, L.gb); self._count()
+            with torch.cuda.stream(side):
                 F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
             if i > 0:
                 F_.gemm_bf16(dy, L.wt, self.d_act_b[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
@@ -488,18 +493,20 @@ class DLRM:
         self._stamp("bot_bwd_done")
         # ---- dense gradients (complete once `side` has drained): all-reduce + SGD, beside the sparse optimizer
         solo = self.world == 1
+        side.wait_stream(self.s_col)                               # bias gradients are part of the flat buffer
         with torch.cuda.stream(side):
             if not solo:
-                self.ctx.signal(CH_GRADS); self.ctx.wait(CH_GRADS)
+                self.ctx.sync(CH_GRADS)                            # every rank's gradients are complete
                 F_.allreduce_push(self.Gflat.table, self.Rflat.table, self.world, self.rank, self.n_params)
-                self.ctx.signal(CH_REDUCED); self.ctx.wait(CH_REDUCED)
-                self._count(5)
+                self.ctx.sync(CH_REDUCED)                          # every rank's slice has landed here
+                self._count(3)
+            # SGD on the reduced gradients; it also clears this rank's own accumulation buffer (same layout,
+            # `delta` elements away), so no memset launch follows
+            delta = 0 if solo else (self.grads.data_ptr() - self.reduced.data_ptr()) // 4
             call("rs_dense_sgd_multi", self._sgd_desc.data_ptr(), self._sgd_prefix.data_ptr(), len(self.layers), self._sgd_tiles,
                  self.master[self.tail_off:].data_ptr(), self.reduced[self.tail_off:].data_ptr(), self.tail_n, c.mlp_lr,
-                 1 if solo else 0, stream_ptr())
+                 1 if solo else 0, delta, 0 if solo else 1, stream_ptr())
             self._count()
-            if not solo:
-                self.grads.zero_(); self._count()
         main.wait_stream(self.s_comm)
         self._stamp("emb_bwd_done")
         main.wait_stream(side)

@@ -148,9 +148,14 @@ class PeerContext:
                   self._counters.data_ptr() + 4 * self.NUM_CHANNELS, self.wait_timeout_ns,
                   self.status.data_ptr(), _lib.stream_ptr(stream))
 
+    def sync(self, channel: int, stream=None) -> None:
+        """``signal`` + ``wait`` on one channel in a single launch (a barrier of the ranks on that channel)."""
+        _lib.call("rs_peer_sync", self._flags.table.data_ptr(), self._flags.local_ptr, self.world, self.rank, channel,
+                  self._counters.data_ptr(), self._counters.data_ptr() + 4 * self.NUM_CHANNELS, self.wait_timeout_ns,
+                  self.status.data_ptr(), _lib.stream_ptr(stream))
+
     def barrier(self, channel: int = NUM_CHANNELS - 1, stream=None) -> None:
-        self.signal(channel, stream)
-        self.wait(channel, stream)
+        self.sync(channel, stream)
 
     # ------------------------------------------------------------------ status
     def check_status(self, reset: bool = True) -> None:
