@@ -292,6 +292,7 @@ class DLRM:
         self.launches_per_step = 0
         self.s_wgrad = torch.cuda.Stream(device=dev)   # weight/bias gradients, then the dense all-reduce and SGD
         self.s_comm = torch.cuda.Stream(device=dev)    # embedding lookup / gradient push: the NVLink-bound kernels
+        self.s_wgrad2 = torch.cuda.Stream(device=dev)  # weight gradients of the bottom MLP
         self.s_col = torch.cuda.Stream(device=dev)     # bias gradients (column sums): bandwidth-bound, beside the wgrad GEMMs
         self._phase_names: List[str] = []
         self._phase_buf = torch.zeros(64, dtype=torch.int64, device=dev)
@@ -481,11 +482,11 @@ class DLRM:
             L = self.bot[i]
             dy = self.d_act_b[i]
             xin = self.act_b[i - 1] if i > 0 else self.x0p
-            side.wait_stream(main)
+            self.s_wgrad2.wait_stream(main)                       # bottom-MLP weight gradients do not queue behind the top MLP's
             self.s_col.wait_stream(main)
             with torch.cuda.stream(self.s_col):
                 F_.colsum_bf16(dy, L.gb); self._count()
-            with torch.cuda.stream(side):
+            with torch.cuda.stream(self.s_wgrad2):
                 F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st); self._count()
             if i > 0:
                 F_.gemm_bf16(dy, L.wt, self.d_act_b[i - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
@@ -494,6 +495,7 @@ class DLRM:
         # ---- dense gradients (complete once `side` has drained): all-reduce + SGD, beside the sparse optimizer
         solo = self.world == 1
         side.wait_stream(self.s_col)                               # bias gradients are part of the flat buffer
+        side.wait_stream(self.s_wgrad2)
         with torch.cuda.stream(side):
             if not solo:
                 self.ctx.sync(CH_GRADS)                            # every rank's gradients are complete
