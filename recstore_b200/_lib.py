@@ -91,7 +91,7 @@ _SIGNATURES = {
     "rs_peer_signal": (i32, [vp, i32, i32, i32, vp, vp]),
     "rs_peer_wait": (i32, [vp, i32, i32, vp, u64, vp, vp]),
     "rs_peer_sync": (i32, [vp, vp, i32, i32, i32, vp, vp, u64, vp, vp]),
-    "rs_allreduce_push": (i32, [vp, vp, i32, i32, i64, f32, vp]),
+    "rs_allreduce_push": (i32, [vp, vp, i32, i32, i64, i64, f32, vp]),
     "rs_memset_async": (i32, [vp, i32, sz, vp]),
     "rs_stamp_time": (i32, [vp, vp]),
     "rs_read_status": (i32, [vp, C.POINTER(u64), i32]),

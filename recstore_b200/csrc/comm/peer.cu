@@ -102,10 +102,10 @@ __global__ void sync_kernel(uint32_t* const* flags_of, const uint32_t* my_flags,
 // grads_of[p]: peer p's gradient buffer; reduced_of[p]: peer p's output buffer; n elements (fp32),
 // slice boundaries in float4 units.
 __global__ void __launch_bounds__(512) allreduce_push_kernel(const float* const* grads_of, float* const* reduced_of,
-                                                             int world, int me, long long n4, float scale) {
+                                                             int world, int me, long long off4, long long n4, float scale) {
   const long long per = (n4 + world - 1) / world;
-  const long long beg = per * me;
-  const long long end = min(n4, beg + per);
+  const long long beg = off4 + per * me;
+  const long long end = off4 + min(n4, per * (me + 1));
   for (long long i = beg + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < end;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -188,9 +188,10 @@ RS_API int rs_peer_sync(void* const* flags_of, const void* my_flags, int world, 
 
 // n must be a multiple of 4; buffers 16-byte aligned.  The caller brackets this with signal/wait
 // pairs: peers' gradients complete before, reduced buffers complete after.
-RS_API int rs_allreduce_push(const void* const* grads_of, void* const* reduced_of, int world, int me, long long n,
+// Reduces elements [off, off + n) of the flat buffers (a bucket); off and n multiples of 4.
+RS_API int rs_allreduce_push(const void* const* grads_of, void* const* reduced_of, int world, int me, long long off, long long n,
                              float scale, cudaStream_t stream) {
-  RS_REQUIRE(grads_of && reduced_of && n % 4 == 0, "rs_allreduce_push: bad argument (n must be a multiple of 4)");
+  RS_REQUIRE(grads_of && reduced_of && n % 4 == 0 && off % 4 == 0 && off >= 0, "rs_allreduce_push: bad argument (off and n must be multiples of 4)");
   if (n == 0) return RS_OK;
   const long long n4 = n / 4;
   const long long per = (n4 + world - 1) / world;
@@ -198,7 +199,7 @@ RS_API int rs_allreduce_push(const void* const* grads_of, void* const* reduced_o
   if (grid > 296) grid = 296;
   if (grid < 1) grid = 1;
   allreduce_push_kernel<<<grid, 512, 0, stream>>>(reinterpret_cast<const float* const*>(grads_of),
-                                                  reinterpret_cast<float* const*>(reduced_of), world, me, n4, scale);
+                                                  reinterpret_cast<float* const*>(reduced_of), world, me, off / 4, n4, scale);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

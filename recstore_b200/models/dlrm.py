@@ -30,7 +30,7 @@ from .._lib import call, stream_ptr
 from ..ops import functional as F_
 from ..parallel.peer import PeerContext
 
-CH_FWD, CH_BWD, CH_GRADS, CH_REDUCED, CH_MISC = 0, 1, 2, 3, 4
+CH_FWD, CH_BWD, CH_GRADS, CH_REDUCED, CH_MISC, CH_GRADS_TOP = 0, 1, 2, 3, 4, 5
 
 
 def _round_up(x: int, m: int) -> int:
@@ -206,6 +206,7 @@ class DLRM:
             w_off.append(off)
             off += L.N * L.Kp
         self.n_w = off
+        self.top_w_off = w_off[len(self.bot)]              # weights of the top MLP (and cross layers) start here
         b_off = []
         for L in layers:
             b_off.append(off)
@@ -425,6 +426,16 @@ class DLRM:
             else:
                 F_.gemm_bf16(dy, L.wt, self.d_z, mode=0, epi=F_.EPI_NONE, status=st)
             self._count()
+        # First all-reduce bucket: the top MLP's weight gradients (most of the dense parameters) are complete once the
+        # wgrad stream has drained, long before the bottom MLP's; reducing them now hides the transfer behind the rest
+        # of the backward.  (With the cross network its layers' gradients come later, so everything goes at the end.)
+        early_bucket = self.world > 1 and not self.dcn
+        if early_bucket:
+            with torch.cuda.stream(side):
+                self.ctx.sync(CH_GRADS_TOP)
+                F_.allreduce_push(self.Gflat.table, self.Rflat.table, self.world, self.rank, self.n_w - self.top_w_off,
+                                  offset=self.top_w_off)
+                self._count(2)
         self._stamp("top_bwd_done")
         # ---- interaction backward: dense part stays, embedding gradients go to their owners
         if self.dcn:
@@ -499,8 +510,13 @@ class DLRM:
         with torch.cuda.stream(side):
             if not solo:
                 self.ctx.sync(CH_GRADS)                            # every rank's gradients are complete
-                F_.allreduce_push(self.Gflat.table, self.Rflat.table, self.world, self.rank, self.n_params)
-                self.ctx.sync(CH_REDUCED)                          # every rank's slice has landed here
+                if early_bucket:                                   # what is left: bottom-MLP weights, then biases + head
+                    F_.allreduce_push(self.Gflat.table, self.Rflat.table, self.world, self.rank, self.top_w_off)
+                    F_.allreduce_push(self.Gflat.table, self.Rflat.table, self.world, self.rank, self.tail_n, offset=self.n_w)
+                    self._count()
+                else:
+                    F_.allreduce_push(self.Gflat.table, self.Rflat.table, self.world, self.rank, self.n_params)
+                self.ctx.sync(CH_REDUCED)                          # every rank's slices have landed here
                 self._count(3)
             # SGD on the reduced gradients; it also clears this rank's own accumulation buffer (same layout,
             # `delta` elements away), so no memset launch follows

@@ -153,8 +153,9 @@ def mse_fwd_bwd(pred, target, loss_sum, dpred=None) -> None:
     call("rs_mse_fwd_bwd", ptr(pred), ptr(target), n, 1.0 / n, ptr(loss_sum), ptr(dpred), stream_ptr())
 
 
-def allreduce_push(grads_table, reduced_table, world: int, rank: int, n: int, scale: float = 1.0) -> None:
-    call("rs_allreduce_push", ptr(grads_table), ptr(reduced_table), world, rank, n, scale, stream_ptr())
+def allreduce_push(grads_table, reduced_table, world: int, rank: int, n: int, scale: float = 1.0, offset: int = 0) -> None:
+    """Two-shot all-reduce over peer memory of elements ``[offset, offset + n)`` of the flat buffers (multiples of 4)."""
+    call("rs_allreduce_push", ptr(grads_table), ptr(reduced_table), world, rank, offset, n, scale, stream_ptr())
 
 
 def cross_fwd(x0, u, xl, out) -> None:
