@@ -39,6 +39,7 @@ def main(argv=None):
     ap.add_argument("--alphas", type=float, nargs="+", default=[0.9, 1.1, 1.3])
     ap.add_argument("--batches", type=int, nargs="+", default=[4096, 32768, 262144])
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--prefetch", action="store_true", help="tiered table: stage the next batch's rows one step ahead (lookahead prefetch)")
     ap.add_argument("--sharded-tiered", action="store_true",
                     help="with --sharded / several ranks: every shard keeps only --hbm-ratio of its rows in HBM, the rest in pinned host memory")
     ap.add_argument("--sharded", action="store_true", help="all-HBM table sharded over the ranks instead of the tiered table")
@@ -71,6 +72,8 @@ def main(argv=None):
                 ids = pool[it[0] & 3]
                 it[0] += 1
                 tab.lookup(ids)
+                if a.prefetch and hasattr(tab, "prefetch"):
+                    tab.prefetch(pool[it[0] & 3])        # next step's rows are staged while this step updates
                 tab.update(grads)
             if hasattr(tab, "hit_stats"):
                 tab.hit_stats()

@@ -6,6 +6,12 @@ host tensor that the kernels address directly.  ``lookup(ids)`` folds duplicate 
 from its tier and expands; ``update(grads)`` segment-sums the gradients of the last lookup and applies SGD or
 row-wise Adagrad on both tiers in one kernel.  ``hit_stats()`` reports how many distinct rows came from HBM.
 
+**Lookahead prefetch.**  ``prefetch(next_ids)`` runs the duplicate folding and the gather of the NEXT step's rows on a
+side stream while the current step is still computing (the host-tier reads are the slow part; BagPipe-style lookahead
+hides them); ``update()`` of the current step then re-reads, from the staged rows, exactly those that it has just
+changed (membership in its own folding hash), so the staged copy is what a fresh gather would return; the next
+``lookup(next_ids)`` only expands the staged rows.
+
 This is the storage of the PS / cache micro-benchmark (HBM cache of 10 % over a host-DRAM tier) and the native
 counterpart of the reference's known-range cache over a UVA-mapped host table
 (src/python/pytorch/recstore/cache/local_cache.py:357-467, src/framework/pytorch/recstore_pytorch.cu:12-64).
@@ -23,6 +29,7 @@ from .._lib import f32, i32, i64, ptr, stream_ptr, u64, vp
 _lib.register_signatures({
     "rs_tiered_gather": (i32, [vp, vp, i64, i64, vp, i64, i32, vp, vp, vp, vp]),
     "rs_tiered_apply": (i32, [vp, vp, vp, vp, i64, i64, vp, i64, i32, vp, vp, f32, f32, i32, vp]),
+    "rs_tiered_refresh": (i32, [vp, vp, i64, i64, vp, i64, i32, vp, vp, u64, vp, vp]),
     "rs_unique_keys": (i32, [vp, i64, vp, vp, u64, vp, vp, vp, vp, vp]),
     "rs_segment_sum": (i32, [vp, vp, i64, i32, vp, vp, vp]),
     "rs_expand_rows": (i32, [vp, vp, i64, i32, vp, vp]),
@@ -61,46 +68,93 @@ class TieredEmbeddingTable:
         while nslots < 2 * n:
             nslots <<= 1
         self._nslots = nslots
-        self._sk = torch.empty(nslots, dtype=torch.int64, device=dev)
-        self._si = torch.empty(nslots, dtype=torch.int32, device=dev)
-        self._uniq = torch.empty(n, dtype=torch.int64, device=dev)
-        self._inv = torch.empty(n, dtype=torch.int32, device=dev)
-        self._ucount = torch.zeros(1, dtype=torch.int32, device=dev)
-        self._urows = torch.empty(n, self.D, device=dev)
+
+        class _Scratch:
+            pass
+        self._sc = []
+        for _ in range(2):          # two sets: the step whose update is pending, and the step prefetched behind it
+            sc = _Scratch()
+            sc.sk = torch.empty(nslots, dtype=torch.int64, device=dev)
+            sc.si = torch.empty(nslots, dtype=torch.int32, device=dev)
+            sc.uniq = torch.empty(n, dtype=torch.int64, device=dev)
+            sc.inv = torch.empty(n, dtype=torch.int32, device=dev)
+            sc.ucount = torch.zeros(1, dtype=torch.int32, device=dev)
+            sc.urows = torch.empty(n, self.D, device=dev)
+            sc.n, sc.ids, sc.ev = 0, None, torch.cuda.Event()
+            self._sc.append(sc)
+        self._cur = 0                # scratch of the last lookup (its update may still come)
+        self._pf: Optional[int] = None
+        self.s_pf = torch.cuda.Stream(device=dev)
         self._ugrad = torch.empty(n, self.D, device=dev)
         self._unorm = torch.empty(n, device=dev)
-        self._counters = torch.zeros(2, dtype=torch.int64, device=dev)
+        self._counters = torch.zeros(3, dtype=torch.int64, device=dev)     # HBM rows, host rows, staged rows read again
         self.status = status if status is not None else torch.zeros(1, dtype=torch.int64, device=dev)
-        self._n = 0
+        self.prefetched_lookups = 0
 
     # ------------------------------------------------------------------
+    def _fold_and_gather(self, sc, ids: torch.Tensor, sp) -> None:
+        n = ids.numel()
+        sc.n = n
+        sc.uniq[:n].fill_(-1)
+        _lib.call("rs_unique_keys", ptr(ids), n, ptr(sc.sk), ptr(sc.si), self._nslots, ptr(sc.uniq), ptr(sc.inv),
+                  ptr(sc.ucount), ptr(self.status), sp)
+        _lib.call("rs_tiered_gather", ptr(self.hot), ptr(self.cold), self.hot_rows, self.N, ptr(sc.uniq), n, self.D,
+                  ptr(sc.urows), ptr(self._counters), ptr(self.status), sp)
+
+    def prefetch(self, next_ids: torch.Tensor) -> None:
+        """Stages the rows of the NEXT lookup on a side stream.  Pass the same tensor object to ``lookup`` afterwards;
+        at most one ``update`` (of the current step) may lie in between."""
+        next_ids = next_ids.contiguous()
+        assert next_ids.numel() <= self.cap and next_ids.is_cuda and next_ids.dtype == torch.int64
+        j = 1 - self._cur
+        sc = self._sc[j]
+        self.s_pf.wait_stream(torch.cuda.current_stream(self.dev))     # the ids exist; earlier users of this scratch are done
+        with torch.cuda.stream(self.s_pf):
+            self._fold_and_gather(sc, next_ids, stream_ptr())
+            sc.ev.record()
+        sc.ids = next_ids
+        self._pf = j
+
     def lookup(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        ids = ids.contiguous()
         n = ids.numel()
         assert n <= self.cap and ids.is_cuda and ids.dtype == torch.int64
         sp = stream_ptr()
-        self._n = n
-        self._uniq[:n].fill_(-1)
-        _lib.call("rs_unique_keys", ptr(ids), n, ptr(self._sk), ptr(self._si), self._nslots, ptr(self._uniq), ptr(self._inv),
-                  ptr(self._ucount), ptr(self.status), sp)
-        _lib.call("rs_tiered_gather", ptr(self.hot), ptr(self.cold), self.hot_rows, self.N, ptr(self._uniq), n, self.D,
-                  ptr(self._urows), ptr(self._counters), ptr(self.status), sp)
+        if self._pf is not None and self._sc[self._pf].ids is ids:
+            sc = self._sc[self._pf]
+            torch.cuda.current_stream(self.dev).wait_event(sc.ev)      # staged (and refreshed, which ran on this stream)
+            self._cur, self._pf = self._pf, None
+            self.prefetched_lookups += 1
+        else:
+            ids = ids.contiguous()
+            self._pf = None                                            # a pending prefetch was for other ids: drop it
+            sc = self._sc[self._cur]
+            self._fold_and_gather(sc, ids, sp)
+        sc.ids = None
         if out is None:
             out = torch.empty(n, self.D, device=self.dev)
-        _lib.call("rs_expand_rows", ptr(self._urows), ptr(self._inv), n, self.D, ptr(out), sp)
+        _lib.call("rs_expand_rows", ptr(sc.urows), ptr(sc.inv), n, self.D, ptr(out), sp)
         return out
 
     def update(self, grads: torch.Tensor) -> None:
         """Optimizer step on the rows of the LAST lookup; ``grads`` [n, D] fp32, one row per looked-up id."""
-        n = self._n
+        sc = self._sc[self._cur]
+        n = sc.n
         assert grads.shape == (n, self.D) and grads.dtype == torch.float32 and grads.is_cuda
         sp = stream_ptr()
         self._ugrad[:n].zero_()
         self._unorm[:n].zero_()
-        _lib.call("rs_segment_sum", ptr(grads.contiguous()), ptr(self._inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), sp)
+        _lib.call("rs_segment_sum", ptr(grads.contiguous()), ptr(sc.inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), sp)
         _lib.call("rs_tiered_apply", ptr(self.hot), ptr(self.hot_state), ptr(self.cold), ptr(self.cold_state), self.hot_rows, self.N,
-                  ptr(self._uniq), n, self.D, ptr(self._ugrad), ptr(self._unorm), self.lr, self.eps,
+                  ptr(sc.uniq), n, self.D, ptr(self._ugrad), ptr(self._unorm), self.lr, self.eps,
                   1 if self.optimizer == "rowwise_adagrad" else 0, sp)
+        if self._pf is not None:
+            # Rows staged for the next step that this update has just changed (or that were read while it ran) are
+            # read again, after the gather and after the apply: the staged copy equals a fresh gather.
+            pf = self._sc[self._pf]
+            torch.cuda.current_stream(self.dev).wait_event(pf.ev)
+            _lib.call("rs_tiered_refresh", ptr(self.hot), ptr(self.cold), self.hot_rows, self.N, ptr(pf.uniq), pf.n, self.D,
+                      ptr(pf.urows), ptr(sc.sk), self._nslots, ptr(self._counters), sp)
+            pf.ev.record()
 
     def hit_stats(self, reset: bool = True) -> dict:
         """Distinct rows served from HBM / from the host tier since the last reset (synchronises)."""
@@ -108,7 +162,8 @@ class TieredEmbeddingTable:
         if reset:
             self._counters.zero_()
         tot = max(1, c[0] + c[1])
-        return {"hbm_rows": c[0], "host_rows": c[1], "hit_ratio": c[0] / tot}
+        return {"hbm_rows": c[0], "host_rows": c[1], "hit_ratio": c[0] / tot, "staged_rows_refreshed": c[2],
+                "prefetched_lookups": self.prefetched_lookups}
 
     def row(self, i: int) -> torch.Tensor:
         torch.cuda.synchronize(self.dev)

@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 
 #include "common/rs_common.h"
+#include "kv/hash_table.cuh"
 
 namespace {
 
@@ -76,6 +77,32 @@ __global__ void __launch_bounds__(256) tiered_apply_kernel(const TieredArgs a, c
   }
 }
 
+// Lookahead refresh: `rows` are the distinct rows that were gathered AHEAD of time for the next step into `staged`;
+// those among them that the step in between has just updated (members of its duplicate-folding hash) are read again.
+__global__ void __launch_bounds__(256) tiered_refresh_kernel(const TieredArgs a, float* __restrict__ staged,
+                                                             const unsigned long long* __restrict__ updated_keys,
+                                                             unsigned long long mask, unsigned long long* __restrict__ counters) {
+  const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= a.n) return;
+  const int lane = threadIdx.x & 31;
+  const long long r = a.rows[i];
+  if (r < 0 || r >= a.total_rows) return;
+  bool hit = false;
+  unsigned long long s = rs::ht_hash(static_cast<unsigned long long>(r)) & mask;
+  for (int p = 0; p < rs::kHtMaxProbe; ++p) {          // warp-uniform probe of the open-addressing set
+    const unsigned long long k = __ldg(&updated_keys[s]);
+    if (k == rs::kHtEmpty) break;
+    if (k == static_cast<unsigned long long>(r)) { hit = true; break; }
+    s = (s + 1) & mask;
+  }
+  if (!hit) return;
+  const bool hot = r < a.hot_rows;
+  const float4* src = reinterpret_cast<const float4*>(hot ? a.hot_w + r * a.D : a.cold_w + (r - a.hot_rows) * a.D);
+  float4* o = reinterpret_cast<float4*>(staged + i * a.D);
+  for (int v = lane; v < (a.D >> 2); v += 32) o[v] = __ldcv(src + v);
+  if (lane == 0 && counters) atomicAdd(&counters[2], 1ull);
+}
+
 int fill(TieredArgs& a, float* hot_w, float* hot_s, float* cold_w, float* cold_s, long long hot_rows, long long total_rows,
          const long long* rows, long long n, int D) {
   RS_REQUIRE(rows && D > 0 && D % 4 == 0 && hot_rows >= 0 && hot_rows <= total_rows, "tiered table: bad sizes");
@@ -115,6 +142,22 @@ RS_API int rs_tiered_apply(float* hot_w, float* hot_s, float* cold_w, float* col
   if (rc != RS_OK) return rc;
   if (n == 0) return RS_OK;
   tiered_apply_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(a, grad, sqnorm, lr, eps, optimizer);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+// staged [n, D]: rows gathered ahead for `rows` (distinct); updated_keys: the key slots of the hash that folded the
+// duplicates of the step that ran in between (nslots a power of two).  counters[2] += rows read again.
+RS_API int rs_tiered_refresh(const float* hot_w, const float* cold_w, long long hot_rows, long long total_rows,
+                             const long long* rows, long long n, int D, float* staged, const void* updated_keys,
+                             unsigned long long nslots, unsigned long long* counters, cudaStream_t stream) {
+  RS_REQUIRE(staged && updated_keys && nslots >= 2 && (nslots & (nslots - 1)) == 0, "rs_tiered_refresh: bad argument");
+  TieredArgs a;
+  int rc = fill(a, const_cast<float*>(hot_w), nullptr, const_cast<float*>(cold_w), nullptr, hot_rows, total_rows, rows, n, D);
+  if (rc != RS_OK) return rc;
+  if (n == 0) return RS_OK;
+  tiered_refresh_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(
+      a, staged, static_cast<const unsigned long long*>(updated_keys), nslots - 1, counters);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

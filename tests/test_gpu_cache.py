@@ -176,3 +176,37 @@ def test_tiered_table_lookup_and_adagrad_on_both_tiers():
     assert torch.allclose(full, W.cpu(), atol=1e-4, rtol=1e-5)
     assert torch.allclose(torch.cat([t.hot_state.cpu(), t.cold_state]), S.cpu(), atol=1e-5, rtol=1e-5)
     assert t.status.item() == 0
+
+
+def test_tiered_table_lookahead_prefetch_is_exact():
+    """The same id / gradient stream with and without staging the next batch one step ahead: identical rows out,
+    identical tables at the end (the rows a step updates are re-read into the staged copy)."""
+    from recstore_b200.cache.tiered_table import TieredEmbeddingTable
+    dev = torch.device("cuda:0")
+    N, D, n = 4000, 32, 2500
+    mk = lambda: TieredEmbeddingTable(N, D, hbm_ratio=0.15, max_keys=4096, lr=0.05, device=dev, init="row_index")
+    plain, ahead = mk(), mk()
+    g = torch.Generator(device=dev).manual_seed(1)
+    batches = []
+    for _ in range(6):
+        ids = torch.randint(0, N, (n,), device=dev, generator=g)
+        ids[::6] = 5                  # hot duplicate shared by consecutive steps
+        ids[1::11] = 3900             # cold duplicate shared by consecutive steps
+        batches.append((ids, torch.randn(n, D, device=dev, generator=g)))
+    outs_plain, outs_ahead = [], []
+    for ids, gr in batches:
+        outs_plain.append(plain.lookup(ids).clone())
+        plain.update(gr)
+    for i, (ids, gr) in enumerate(batches):
+        outs_ahead.append(ahead.lookup(ids).clone())
+        if i + 1 < len(batches):
+            ahead.prefetch(batches[i + 1][0])
+        ahead.update(gr)
+    torch.cuda.synchronize()
+    for a, b in zip(outs_plain, outs_ahead):
+        assert torch.equal(a, b)
+    assert torch.equal(plain.hot, ahead.hot) and torch.equal(plain.cold, ahead.cold)
+    assert torch.equal(plain.cold_state, ahead.cold_state)
+    st = ahead.hit_stats()
+    assert st["prefetched_lookups"] == len(batches) - 1 and st["staged_rows_refreshed"] > 0
+    assert ahead.status.item() == 0
