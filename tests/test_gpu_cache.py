@@ -203,10 +203,13 @@ def test_tiered_table_lookahead_prefetch_is_exact():
             ahead.prefetch(batches[i + 1][0])
         ahead.update(gr)
     torch.cuda.synchronize()
-    for a, b in zip(outs_plain, outs_ahead):
-        assert torch.equal(a, b)
-    assert torch.equal(plain.hot, ahead.hot) and torch.equal(plain.cold, ahead.cold)
-    assert torch.equal(plain.cold_state, ahead.cold_state)
+    # (duplicate gradients are summed with atomics, so two runs agree to rounding, not bit for bit; a stale staged row
+    # would be off by a whole optimizer step, ~1e-2 here)
+    close = lambda x, y: torch.allclose(x, y, rtol=1e-5, atol=1e-5)
+    for i, (a, b) in enumerate(zip(outs_plain, outs_ahead)):
+        assert close(a, b), (i, (a - b).abs().max().item())
+    assert close(plain.hot, ahead.hot) and close(plain.cold, ahead.cold)
+    assert close(plain.cold_state, ahead.cold_state)
     st = ahead.hit_stats()
     assert st["prefetched_lookups"] == len(batches) - 1 and st["staged_rows_refreshed"] > 0
     assert ahead.status.item() == 0
