@@ -58,6 +58,7 @@ def parse_args(argv=None):
     p.add_argument("--neg_sample_size_eval", type=int, default=256)
     p.add_argument("--save_path", default=None)
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--no_graph", action="store_true", help="native path: launch the step eagerly instead of replaying a CUDA graph")
     a = p.parse_args(argv)
     if a.neg_chunk_size is None:
         a.neg_chunk_size = min(a.neg_sample_size, a.batch_size)
@@ -121,7 +122,7 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
         ctx = PeerContext(rank, W, device=dev)
         model = KGEModel(KGEConfig(ds.n_entities, ds.n_relations, dim=args.hidden_dim, model=args.model_name, gamma=args.gamma,
                                    batch=args.batch_size, neg_sample_size=args.neg_sample_size, neg_chunk_size=args.neg_chunk_size,
-                                   lr=args.lr, seed=args.seed, dataset=ds.name), ctx)
+                                   lr=args.lr, seed=args.seed, dataset=ds.name, use_cuda_graph=not args.no_graph), ctx)
         step_fn = lambda h, r, t, n, ch: model.train_step(h, r, t, n, ch)
     else:
         from recstore_b200.baseline.kge_torch import TorchKGE
