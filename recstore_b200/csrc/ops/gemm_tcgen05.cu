@@ -716,23 +716,39 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   const bool f32_out = (epi == 3 || epi == 4);
   RS_REQUIRE((ldd * (f32_out ? 4 : 2)) % 16 == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0,
              "rs_gemm_bf16: D must be 16-byte aligned with a 16-byte multiple pitch");
-  if (bn == 0) {
-    if (N % 256 == 0) bn = 256;
-    else if (N % 128 == 0) bn = 128;
-    else if (N % 64 == 0) bn = 64;
-    else bn = (mode == 0 && N % 32 == 0) ? 32 : 64;
-    if (mode == 0 && N < bn && N % 32 == 0) bn = N;
-  }
-  RS_REQUIRE(bn % 32 == 0 && bn <= 256 && bn >= 32, "rs_gemm_bf16: bad tile width %d", bn);
-  RS_REQUIRE(mode == 0 || bn % 64 == 0, "rs_gemm_bf16: modes 1 and 2 need a tile width multiple of 64");
-
-  // CTA pairs (cta_group::2) when the problem has at least one 256-row tile and the B tile splits into two
-  // 64-column-aligned halves.  RECSTORE_GEMM_CTA_PAIRS=0 keeps every GEMM on single CTAs.
-  static const bool pairs_allowed = [] {
+  static const bool pairs_allowed = [] {                 // RECSTORE_GEMM_CTA_PAIRS=0 keeps every GEMM on single CTAs
     const char* e = getenv("RECSTORE_GEMM_CTA_PAIRS");
     return !(e && e[0] == '0');
   }();
-  const int cg = (pairs_allowed && M >= 2 * BM && bn % 128 == 0 && num_sms() % 2 == 0) ? 2 : 1;
+  const bool pairs_possible = pairs_allowed && M >= 2 * BM && num_sms() % 2 == 0;
+  int cg = 0;
+  if (bn == 0) {
+    // Tile width and CTA pairing are chosen together.  A large problem takes the largest tile (best operand reuse);
+    // a problem with fewer tiles than SMs takes a smaller one so that the machine is filled (M = 8192, N = 256 as
+    // 256-wide pair tiles would occupy 64 of 148 SMs).  Estimated time = waves x tile width x a reuse penalty.
+    double best = 0.0;
+    int cand[4], nc = 0;
+    for (int w = 256; w >= 64; w >>= 1)
+      if (N % w == 0) cand[nc++] = w;                                  // whole tiles only
+    if (mode == 0 && N % 32 == 0 && N % 64 != 0) cand[nc++] = 32;
+    for (int ci = 0; ci < nc; ++ci) {
+      const int w = cand[ci];
+      for (int c = 2; c >= 1; --c) {
+        if (c == 2 && (!pairs_possible || w % 128 != 0)) continue;
+        const long long tiles = static_cast<long long>((M + BM * c - 1) / (BM * c)) * (N / w);
+        const long long units = num_sms() / c;
+        const double penalty = (c == 2 ? 0.9 : 1.0) * (w == 256 ? 1.0 : w == 128 ? 1.15 : w == 64 ? 1.4 : 1.8);
+        // The split-reduction GEMM (weight gradients) fills the machine with splits whatever the tile: largest tile wins.
+        const double est = epi == 3 ? penalty : static_cast<double>((tiles + units - 1) / units) * w * penalty;
+        if (cg == 0 || est < best) { best = est; bn = w; cg = c; }
+      }
+    }
+    if (cg == 0) { bn = 64; cg = 1; }                                    // ragged N: 64-wide tiles, the last one partial
+  }
+  RS_REQUIRE(bn % 32 == 0 && bn <= 256 && bn >= 32, "rs_gemm_bf16: bad tile width %d", bn);
+  RS_REQUIRE(mode == 0 || bn % 64 == 0, "rs_gemm_bf16: modes 1 and 2 need a tile width multiple of 64");
+  // CTA pairs (cta_group::2) need at least one 256-row tile and a B tile that splits into two 64-column-aligned halves.
+  if (cg == 0) cg = (pairs_possible && bn % 128 == 0) ? 2 : 1;
   GemmArgs g;
   g.M = M; g.N = N; g.K = K; g.bn = bn;
   g.tiles_m = (M + BM * cg - 1) / (BM * cg);
