@@ -467,6 +467,22 @@ __global__ void rows_gather_kernel(const float* __restrict__ w, const long long*
     *(reinterpret_cast<float4*>(out + i * D) + v) = x;
   }
 }
+// Same gather with the row range checked: rows >= total_rows give zeros and set RS_DEV_OOB_ROW in the status word.
+__global__ void rows_gather_checked_kernel(const float* __restrict__ w, long long total_rows, const long long* __restrict__ rows,
+                                           long long n, int D, float* __restrict__ out, unsigned long long* status) {
+  const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= n) return;
+  const int lane = threadIdx.x & 31;
+  long long r = rows[i];
+  if (r >= total_rows) {
+    if (lane == 0 && status) atomicOr(status, (unsigned long long)RS_DEV_OOB_ROW);
+    r = -1;
+  }
+  for (int v = lane; v < (D >> 2); v += 32) {
+    const float4 x = r >= 0 ? __ldg(reinterpret_cast<const float4*>(w + r * D) + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    *(reinterpret_cast<float4*>(out + i * D) + v) = x;
+  }
+}
 __global__ void rows_scatter_kernel(float* __restrict__ w, const long long* __restrict__ rows, long long n, int D,
                                     const float* __restrict__ in) {
   const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -561,6 +577,15 @@ RS_API int rs_rows_gather(const float* weight, const long long* rows, long long 
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
+RS_API int rs_rows_gather_checked(const float* weight, long long total_rows, const long long* rows, long long n, int D, float* out,
+                                  unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(weight && rows && out && D % 4 == 0 && total_rows >= 0, "rs_rows_gather_checked: bad argument");
+  if (n == 0) return RS_OK;
+  rows_gather_checked_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(weight, total_rows, rows, n, D, out, status);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
 RS_API int rs_rows_scatter(float* weight, const long long* rows, long long n, int D, const float* in,
                            cudaStream_t stream) {
   RS_REQUIRE(weight && rows && in && D % 4 == 0, "rs_rows_scatter: bad argument");

@@ -102,6 +102,7 @@ class KGEModel:
         self._g_ids = (torch.zeros(self.bs, dtype=torch.int64, device=dev), torch.zeros(self.bs, dtype=torch.int64, device=dev),
                        torch.zeros(self.bs, dtype=torch.int64, device=dev), torch.zeros(self.nneg, dtype=torch.int64, device=dev))
         self._g_loss = torch.zeros((), **f)
+        self._cap_stream: Optional[torch.cuda.Stream] = None
 
     # ------------------------------------------------------------------ kernels
     def _stage(self, stage: int, corrupt_head: bool, want_scores: bool):
@@ -143,7 +144,13 @@ class KGEModel:
             self._g_loss.copy_(self._step(*self._g_ids, corrupt_head))   # eager once (this step's update): one-time set-up happens here
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=torch.cuda.current_stream(), capture_error_mode="relaxed"):
+            cur = torch.cuda.current_stream()
+            if cur == torch.cuda.default_stream():           # capture needs a non-default stream; replay runs on any
+                if self._cap_stream is None:
+                    self._cap_stream = torch.cuda.Stream()
+                self._cap_stream.wait_stream(cur)
+                cur = self._cap_stream
+            with torch.cuda.graph(g, stream=cur, capture_error_mode="relaxed"):
                 self._g_loss.copy_(self._step(*self._g_ids, corrupt_head))
             self._graphs[corrupt_head] = g
             return self._g_loss.clone()                       # the eager pass above already did this step's update

@@ -29,6 +29,7 @@ _lib.register_signatures({
     "rs_shard_gather_push_rows": (i32, [vp, i64, vp, vp, vp, vp, i32, i32, i32, i64, C.POINTER(HashTableView), vp, vp]),
     "rs_shard_gather_push_rows_tiered": (i32, [vp, vp, i64, i64, vp, vp, vp, vp, i32, i32, i32, i64, vp, vp]),
     "rs_tiered_apply": (i32, [vp, vp, vp, vp, i64, i64, vp, i64, i32, vp, vp, f32, f32, i32, vp]),
+    "rs_rows_gather_checked": (i32, [vp, i64, vp, i64, i32, vp, vp, vp]),
     "rs_shard_unbucket_rows": (i32, [vp, vp, i64, i32, vp, i32, vp]),
     "rs_shard_push_grads": (i32, [vp, vp, i64, i32, i32, i64, vp, vp, vp, vp]),
     "rs_segment_sum": (i32, [vp, vp, i64, i32, vp, vp, vp]),
@@ -121,6 +122,18 @@ class ShardedEmbeddingTable:
             self.launches += 3
         else:
             keys = ids
+        if self.world == 1 and not self.tiered:
+            # One rank: every row is local (local row = id), so nothing is bucketed or exchanged.
+            src_keys = keys[:n]
+            if out is None:
+                out = torch.empty(n, self.D, device=self.dev)
+            dst = self._urows if self.dedup else out
+            _lib.call("rs_rows_gather_checked", ptr(self.weight), self.N, ptr(src_keys), n, self.D, ptr(dst), ptr(st), sp)
+            if self.dedup:
+                _lib.call("rs_expand_rows", ptr(self._urows), ptr(self._inv), n, self.D, ptr(out), sp)
+            self._local_rows = src_keys
+            self.launches += 2
+            return out
         _lib.call("rs_shard_push_keys", ptr(keys), n, self.world, self.rank, self.cap, ptr(self._counts), ptr(self._cursor),
                   ptr(self.key_win.table), ptr(self.count_win.table), ptr(self._slot), ptr(st), sp)
         self.ctx.signal(CH_KEYS); self.ctx.wait(CH_KEYS)
@@ -150,6 +163,18 @@ class ShardedEmbeddingTable:
         assert grads.shape == (n, self.D) and grads.dtype == torch.float32
         grads = grads.contiguous()
         st, sp = self.ctx.status, stream_ptr()
+        if self.world == 1 and not self.tiered:
+            if self.dedup:
+                self._ugrad[:n].zero_()
+                self._unorm[:n].zero_()
+                _lib.call("rs_segment_sum", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), sp)
+                g, gn = self._ugrad, self._unorm
+            else:
+                g, gn = grads, None
+            F_.emb_backward(self.weight, self.state, self._local_rows, None, n, g, grad_row_stride=self.D, B=n, D=self.D,
+                            grad_bf16=False, lr=self.lr, eps=self.eps, optimizer=self.optimizer, status=st, gnorm=gn, gnorm_stride=1)
+            self.launches += 5
+            return
         gnorm = None
         if self.dedup:
             self._ugrad[:n].zero_()
