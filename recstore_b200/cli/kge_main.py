@@ -9,8 +9,9 @@ optional pre-sampling of ``--presample_steps`` steps, hot sets of ``--cache_rati
 that each worker's hot entities are contiguous -> one training process per worker -> save -> sampled-negative test
 (MRR / MR / HITS@k).
 
-Engines: on ``--device cuda`` TransE_l2 / DistMult run on the native path (entity and relation tables row-sharded over
-the GPUs' HBM, tcgen05 scoring); every other score function, and ``--device cpu``, runs the PyTorch implementation on
+Engines: on ``--device cuda`` TransE (L1 / L2), DistMult, ComplEx, SimplE and RotatE run on the native path (entity and
+relation tables row-sharded over the GPUs' HBM; tcgen05 scoring where the negative scores are cross products, fp32 pair
+kernels for the L1 / modulus distances); TransR and RESCAL, and ``--device cpu``, run the PyTorch implementation on
 tables shared between the worker processes (lock-free updates, as the reference's stock path does).  Prints
 ``Successfully xmh`` when done.
 """
@@ -25,7 +26,7 @@ import time
 import numpy as np
 import torch
 
-NATIVE_MODELS = ("TransE", "TransE_l2", "DistMult")
+NATIVE_MODELS = ("TransE", "TransE_l1", "TransE_l2", "DistMult", "ComplEx", "SimplE", "RotatE")
 
 
 def parse_args(argv=None):

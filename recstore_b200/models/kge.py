@@ -1,4 +1,4 @@
-"""Knowledge-graph embedding training (TransE-L2, DistMult) on row-sharded HBM entity / relation tables.
+"""Knowledge-graph embedding training (TransE L2 / L1, DistMult, ComplEx, SimplE, RotatE) on row-sharded HBM tables.
 
 Model, negative sampling and loss follow the reference's patched DGL-KE
 (src/kg/kg/dgl-ke/python/dglke/models/general_models.py:568-631, score_fun.py, loss.py:69-99,
@@ -10,7 +10,9 @@ Adagrad (tensor_models.py:366-436).  Init is ``U(+-(gamma + 2) / dim)`` (general
 What is different: the entity table (86 M x 400 fp32 = 138 GB in the headline config) does not live in
 host memory behind a cache; it is spread cyclically over the GPUs' HBM
 (``parallel.sharded_table.ShardedEmbeddingTable``), rows and gradients move by peer stores, and the
-scoring is three element-wise kernels around tcgen05 GEMMs (``csrc/ops/kge.cu``).
+scoring is three element-wise kernels around tcgen05 GEMMs for the models whose negative scores are cross
+products (TransE-L2, DistMult, ComplEx, SimplE) and three pair-walking fp32 kernels for TransE-L1 and RotatE
+(``csrc/ops/kge.cu``).  TransR and RESCAL (a matrix per relation) run on the PyTorch path only.
 
 Checkpoints keep the reference layout (tensor_models.py:452-476, general_models.py:316-346):
 ``{dataset}_{model}_entity.npy``, ``{dataset}_{model}_relation.npy`` and ``config.json``.
@@ -32,11 +34,12 @@ from ..parallel.peer import PeerContext
 from ..parallel.sharded_table import ShardedEmbeddingTable
 
 _lib.register_signatures({
-    "rs_kge_stage": (i32, [i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
-                           vp, vp, vp, vp, vp, vp, vp]),
+    "rs_kge_stage": (i32, [i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp,
+                           vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
 })
 
-MODELS = {"TransE": 0, "TransE_l2": 0, "DistMult": 1}
+MODELS = {"TransE": 0, "TransE_l2": 0, "DistMult": 1, "ComplEx": 2, "SimplE": 3, "TransE_l1": 4, "RotatE": 5}
+PAIRWISE = (4, 5)                     # no cross-product form: scored pair by pair in fp32
 
 
 @dataclass
@@ -70,18 +73,22 @@ class KGEModel:
         self.nneg = self.C * self.ns
         self.Dp = (self.D + 63) // 64 * 64
         self.model_id = MODELS[cfg.model]
-        scale = (cfg.gamma + 2.0) / cfg.dim
+        self.pairwise = self.model_id in PAIRWISE
+        self.Dr = self.D // 2 if cfg.model == "RotatE" else self.D      # RotatE relations are phases
+        if self.pairwise:
+            assert self.cs % 8 == 0 and self.ns % 8 == 0, "TransE_l1 / RotatE: chunk and negative counts are multiples of 8"
+        scale = self.emb_init = (cfg.gamma + 2.0) / cfg.dim
         n_ids = 2 * self.bs + self.nneg
         self.entity = ShardedEmbeddingTable(self.ctx, "kge_entity", cfg.n_entities, self.D, max_keys=n_ids, lr=cfg.lr, eps=cfg.eps,
                                             init="uniform", init_scale=scale, seed=cfg.seed)
-        self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations, self.D, max_keys=self.bs, lr=cfg.lr,
+        self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations, self.Dr, max_keys=self.bs, lr=cfg.lr,
                                               eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 1)
         f = dict(dtype=torch.float32, device=dev)
         b = dict(dtype=torch.bfloat16, device=dev)
         self.ent_rows = torch.empty(n_ids, self.D, **f)
-        self.rel_rows = torch.empty(self.bs, self.D, **f)
+        self.rel_rows = torch.empty(self.bs, self.Dr, **f)
         self.ent_grad = torch.empty(n_ids, self.D, **f)
-        self.rel_grad = torch.empty(self.bs, self.D, **f)
+        self.rel_grad = torch.empty(self.bs, self.Dr, **f)
         self.A = torch.zeros(self.bs, self.Dp, **b)
         self.Bn = torch.zeros(self.nneg, self.Dp, **b)
         self.a2 = torch.empty(self.bs, **f)
@@ -110,7 +117,7 @@ class KGEModel:
         h, t, neg = self.ent_rows[:bs], self.ent_rows[bs:2 * bs], self.ent_rows[2 * bs:]
         gh, gt, gneg = self.ent_grad[:bs], self.ent_grad[bs:2 * bs], self.ent_grad[2 * bs:]
         _lib.call("rs_kge_stage", stage, ptr(h), ptr(self.rel_rows), ptr(t), ptr(neg), bs, self.cs, self.ns, self.D, self.Dp,
-                  self.model_id, 1 if corrupt_head else 0, self.cfg.gamma, ptr(self.A), ptr(self.Bn), ptr(self.a2), ptr(self.b2),
+                  self.Dr, self.model_id, 1 if corrupt_head else 0, self.cfg.gamma, self.emb_init, ptr(self.A), ptr(self.Bn), ptr(self.a2), ptr(self.b2),
                   ptr(self.loss), ptr(gh), ptr(self.rel_grad), ptr(gt), ptr(gneg), ptr(self.S), ptr(self.W), ptr(self.rowsum),
                   ptr(self.colsum), ptr(self.GA), ptr(self.GB), ptr(self.pos_score) if want_scores else None,
                   ptr(self.neg_score) if want_scores else None, stream_ptr())
@@ -119,7 +126,8 @@ class KGEModel:
         st = self.ctx.status
         self.loss.zero_(); self.rowsum.zero_(); self.colsum.zero_()
         self._stage(0, corrupt_head, want_scores)
-        F_.gemm_bf16(self.A, self.Bn, self.S, mode=0, epi=F_.EPI_F32, status=st)
+        if not self.pairwise:
+            F_.gemm_bf16(self.A, self.Bn, self.S, mode=0, epi=F_.EPI_F32, status=st)
         self._stage(1, corrupt_head, want_scores)
 
     def _fetch(self, h_ids, r_ids, t_ids, neg_ids):
@@ -161,12 +169,13 @@ class KGEModel:
         st = self.ctx.status
         self._fetch(h_ids, r_ids, t_ids, neg_ids)
         self._forward(corrupt_head, False)
-        F_.gemm_bf16(self.W, self.Bn, self.GA, mode=2, epi=F_.EPI_F32, status=st)
-        F_.gemm_bf16(self.W, self.A, self.GB, mode=1, epi=F_.EPI_F32, status=st)
+        if not self.pairwise:
+            F_.gemm_bf16(self.W, self.Bn, self.GA, mode=2, epi=F_.EPI_F32, status=st)
+            F_.gemm_bf16(self.W, self.A, self.GB, mode=1, epi=F_.EPI_F32, status=st)
         self._stage(2, corrupt_head, False)
         self.entity.update(self.ent_grad)
         self.relation.update(self.rel_grad)
-        self.launches_per_step = 6 + 3 + self.entity.launches + self.relation.launches
+        self.launches_per_step = (7 if self.pairwise else 9) + self.entity.launches + self.relation.launches
         return self.loss.sum()
 
     @torch.no_grad()

@@ -5,29 +5,22 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _ref_loss(model, gamma, h, r, t, neg, cs, ns, corrupt_head):
-    bs, D = h.shape
-    C = bs // cs
-    if model == "DistMult":
-        pos = (h * r * t).sum(-1)
-        a = (t * r) if corrupt_head else (h * r)
-        negs = torch.bmm(a.view(C, cs, D), neg.view(C, ns, D).transpose(1, 2))
-    else:
-        pos = gamma - (h + r - t).norm(dim=-1)
-        a = (t - r) if corrupt_head else (h + r)
-        negs = gamma - torch.cdist(a.view(C, cs, D), neg.view(C, ns, D))
-    ls = torch.nn.functional.logsigmoid
-    return ((-ls(pos)).mean() + (-ls(-negs)).mean()) / 2, pos, negs.reshape(bs, ns)
+def _ref_loss(model, gamma, h, r, t, neg, cs, ns, corrupt_head, emb_init):
+    """Per-pair definition of every score function (the oracle of the PyTorch path)."""
+    from recstore_b200.baseline.kge_torch import chunk_neg_score, edge_score, logsigmoid_loss
+    pos = edge_score(model, h, r, t, gamma, None, emb_init)
+    negs = chunk_neg_score(model, h, r, t, neg, corrupt_head, cs, gamma, None, emb_init)
+    return logsigmoid_loss(pos, negs), pos, negs
 
 
-@pytest.mark.parametrize("model", ["TransE_l2", "DistMult"])
+@pytest.mark.parametrize("model", ["TransE_l2", "DistMult", "ComplEx", "SimplE", "TransE_l1", "RotatE"])
 @pytest.mark.parametrize("corrupt_head", [False, True])
 def test_kge_step_matches_autograd(model, corrupt_head):
     from recstore_b200.models.kge import KGEConfig, KGEModel
     from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
     dev = torch.device("cuda:0")
-    cfg = KGEConfig(n_entities=3000, n_relations=40, dim=400 if model == "TransE_l2" else 64, model=model, gamma=10.0, batch=512,
-                    neg_sample_size=128, neg_chunk_size=128, lr=0.1, seed=3)
+    cfg = KGEConfig(n_entities=3000, n_relations=40, dim=400 if model in ("TransE_l2", "RotatE") else 64, model=model,
+                    gamma=10.0, batch=512, neg_sample_size=128, neg_chunk_size=128, lr=0.1, seed=3)
     m = KGEModel(cfg)
     bs, ns, cs, D = cfg.batch, cfg.neg_sample_size, cfg.neg_chunk_size, cfg.dim
     g = torch.Generator(device=dev).manual_seed(1)
@@ -41,7 +34,7 @@ def test_kge_step_matches_autograd(model, corrupt_head):
         ni = torch.randint(0, cfg.n_entities, (bs // cs * ns,), device=dev, generator=g)
         h = E[hi].clone().requires_grad_(True); t = E[ti].clone().requires_grad_(True)
         r = R[ri].clone().requires_grad_(True); n = E[ni].clone().requires_grad_(True)
-        loss_ref, pos_ref, neg_ref = _ref_loss(model, cfg.gamma, h, r, t, n, cs, ns, corrupt_head)
+        loss_ref, pos_ref, neg_ref = _ref_loss(model, cfg.gamma, h, r, t, n, cs, ns, corrupt_head, m.emb_init)
         loss_ref.backward()
         pos, negs = m.score_batch(hi, ri, ti, ni, corrupt_head)
         assert torch.allclose(pos, pos_ref, atol=2e-3, rtol=1e-3)
