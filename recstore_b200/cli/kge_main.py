@@ -4,7 +4,7 @@
         --hidden_dim 400 --gamma 10 --batch_size 1024 --neg_sample_size 256 --max_step 1000 --num_proc 2 --device cuda --test
 
 Pipeline (src/executable/kg/dgl-ke-main.py:168-552): load or synthesise the dataset -> partition the training triples
-over the workers (``--rel_part`` balanced, ``--soft_rel_part``, else random) -> per-worker chunked negative samplers ->
+over the workers (``--rel_part`` balanced, ``--soft_rel_part``, ``--graph_part`` edge-cut, else random) -> per-worker chunked negative samplers ->
 optional pre-sampling of ``--presample_steps`` steps, hot sets of ``--cache_ratio`` x entities per worker, renumbering so
 that each worker's hot entities are contiguous -> one training process per worker -> save -> sampled-negative test
 (MRR / MR / HITS@k).
@@ -52,6 +52,7 @@ def parse_args(argv=None):
     p.add_argument("--device", choices=["cpu", "cuda"], default="cpu")
     p.add_argument("--rel_part", action="store_true")
     p.add_argument("--soft_rel_part", action="store_true")
+    p.add_argument("--graph_part", action="store_true", help="balanced edge-cut partition of the entity graph (the METIS role)")
     p.add_argument("--cache_ratio", type=float, default=0.0)
     p.add_argument("--presample_steps", type=int, default=0)
     p.add_argument("--test", action="store_true")
@@ -87,6 +88,9 @@ def prepare(args):
     elif args.soft_rel_part:
         parts, cross = K.soft_relation_partition(ds.train[1], W, seed=args.seed)
         info["cross_relations"] = int(cross.sum())
+    elif args.graph_part:
+        parts, _, st = K.graph_partition(ds.train[0], ds.train[2], ds.n_entities, W, seed=args.seed)
+        info["edge_cut"] = st["edge_cut"]
     else:
         parts = K.random_partition(ds.train[0].size, W, args.seed)
     if args.cache_ratio > 0 and args.presample_steps > 0:

@@ -6,8 +6,9 @@
   (src/kg/kg/dgl-ke/python/dglke/dataloader/KGDataset.py: ``KGDatasetUDDRaw`` / ``KGDatasetUDD``).
 * Partitioning of the training triples over the workers: ``random_partition``, ``balanced_relation_partition`` (every
   relation on as few workers as its size allows, equal shares) and ``soft_relation_partition`` (large relations spread,
-  small ones pinned) -- sampler.py:45-313 of the reference.  (Its METIS edge-cut partition needs the METIS library;
-  the relation-based partitions are the ones kept.)
+  small ones pinned) -- sampler.py:45-313 of the reference -- and ``graph_partition``: a balanced edge-cut partition of
+  the entity graph (the role METIS plays in sampler.py:408-429) by the native multilevel partitioner
+  (``csrc/runtime/graph_partition.cpp``); a triple goes to the part of its tail.
 * ``presample``: run the sampler ahead for some steps and count how often each entity is touched per worker
   (sampler.py:512-600) -> per-worker hot sets.
 * ``renumber_graph``: give the hot entities of worker r the ids ``[start_r, start_r + len_r)`` and everything else the
@@ -164,6 +165,32 @@ def soft_relation_partition(rel: np.ndarray, n_parts: int, threshold: float = 0.
             p = int(np.argmin(fill))
             buckets[p].append(idx); fill[p] += idx.size
     return [np.sort(np.concatenate(b)) if b else np.zeros(0, dtype=np.int64) for b in buckets], cross
+
+
+def graph_partition(head: np.ndarray, tail: np.ndarray, n_entities: int, n_parts: int, imbalance: float = 0.03, seed: int = 0,
+                    refine_sweeps: int = 8, balance: str = "triples") -> Tuple[List[np.ndarray], np.ndarray, Dict[str, float]]:
+    """Balanced edge-cut partition of the entities (multilevel: heavy-edge matching, greedy growing, boundary
+    refinement).  ``balance="triples"`` weighs an entity by the triples it brings to its part (1 + its count as a tail),
+    so that the workers get equal shares of the training set; ``"nodes"`` gives equal entity counts.  Returns the triple
+    indices per part (a triple belongs to the part of its tail), the part of every entity, and ``{"edge_cut": fraction
+    of triples whose ends lie in different parts, "max_part": heaviest part / ideal weight, "levels": ...}``."""
+    import ctypes as C
+    from .. import _lib
+    from .._lib import i32, i64, u64, vp, f64
+    _lib.register_signatures({"rs_graph_partition": (i32, [i64, i64, vp, vp, vp, i32, f64, u64, i32, vp, vp])})
+    assert balance in ("triples", "nodes")
+    h = np.ascontiguousarray(head, dtype=np.int64)
+    t = np.ascontiguousarray(tail, dtype=np.int64)
+    part = np.empty(n_entities, dtype=np.int32)
+    stats = np.zeros(4, dtype=np.int64)
+    nw = (1 + np.bincount(t, minlength=n_entities)).astype(np.int64) if balance == "triples" else None
+    _lib.call("rs_graph_partition", int(n_entities), int(h.size), h.ctypes.data, t.ctypes.data,
+              nw.ctypes.data if nw is not None else None, int(n_parts), float(imbalance),
+              int(seed), int(refine_sweeps), part.ctypes.data, stats.ctypes.data)
+    owner = part[t]
+    parts = [np.nonzero(owner == p)[0].astype(np.int64) for p in range(n_parts)]
+    return parts, part, {"edge_cut": float(stats[0]) / max(1, h.size), "max_part": float(stats[1]) * n_parts / max(1, int(stats[3])),
+                         "levels": int(stats[2])}
 
 
 # ------------------------------------------------------------------------------------------------ sampling
