@@ -80,7 +80,9 @@ _SIGNATURES = {
     "rs_mse_fwd_bwd": (i32, [vp, vp, i32, f32, vp, vp, vp]),
     "rs_cross_fwd": (i32, [vp, vp, vp, vp, i64, vp]),
     "rs_cross_bwd": (i32, [vp, vp, vp, vp, vp, i64, i32, vp]),
-    "rs_push_feature_grads": (i32, [vp, vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, i64, i64, i32, vp, i32, vp]),
+    "rs_push_feature_grads": (i32, [vp, vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, i64, i64, i32, vp, i32, vp, i32, vp]),
+    "rs_proj_inter_fwd": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp]),
+    "rs_proj_inter_bwd": (i32, [vp, i32, i32, vp, vp, i32, i32, i32, i32, vp, vp, vp]),
     # comm/peer.cu
     "rs_device_count": (i32, [C.POINTER(i32)]),
     "rs_peer_alloc": (i32, [sz, C.POINTER(vp)]),

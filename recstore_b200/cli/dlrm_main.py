@@ -4,7 +4,7 @@
         --arch-mlp-bot 13-128-64 --arch-mlp-top 128-64-1 --mini-batch-size 2048 --num-batches 100 --use-gpu
 
 Recognised flags (src/executable/dlrm/dlrm_model.py:618-760): ``--arch-sparse-feature-size --arch-embedding-size
---arch-mlp-bot --arch-mlp-top --arch-interaction-op dot|dcn --mini-batch-size --nepochs --num-batches
+--arch-mlp-bot --arch-mlp-top --arch-interaction-op dot|dcn|projection --mini-batch-size --nepochs --num-batches
 --learning-rate --num-indices-per-lookup --num-indices-per-lookup-fixed --data-generation random|synthetic
 --numpy-rand-seed --print-freq --test-freq --test-mini-batch-size --save-model --load-model --use-gpu``, plus
 ``--emb-learning-rate --emb-optimizer --zipf-alpha --dcn-layers --dcn-rank``.  The first number of
@@ -140,8 +140,6 @@ def run(args) -> dict:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if args.use_gpu:
-        if args.arch_interaction_op == "projection":
-            sys.exit("ERROR: the projection interaction runs on the PyTorch path only (drop --use-gpu)")
         from recstore_b200.models.dlrm import DLRM, DLRMConfig
         from recstore_b200.parallel.peer import PeerContext
         local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -150,7 +148,8 @@ def run(args) -> dict:
             import torch.distributed as dist
             dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
         ctx = PeerContext(rank, world, device=torch.device(f"cuda:{local}"))
-        model = _GpuModel(DLRM(DLRMConfig(table_rows=rows, batch=args.mini_batch_size, **kw), ctx))
+        model = _GpuModel(DLRM(DLRMConfig(table_rows=rows, batch=args.mini_batch_size,
+                                          projection_sizes=tuple(args.interaction_branch_sizes), **kw), ctx))
     else:
         from recstore_b200.baseline.dlrm_torch import TorchDLRM
         model = _CpuModel(TorchDLRM(rows, args.mini_batch_size, device="cpu", rank=0, world=1,

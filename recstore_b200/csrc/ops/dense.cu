@@ -339,6 +339,7 @@ struct PushArgs {
   void* const* gdst; const int* owner; const int* gcol; long long grow_stride, sample_base;
   int relu_mask_dx;
   float* const* ndst; int nstride;
+  const __nv_bfloat16* extra; int extra_ld;   // optional [B, >= D]: added to feature 0 only (a direct path of the dense feature)
 };
 __global__ void __launch_bounds__(256) push_feature_grads_kernel(const PushArgs a) {
   const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -359,6 +360,12 @@ __global__ void __launch_bounds__(256) push_feature_grads_kernel(const PushArgs 
     }
     __nv_bfloat16* dst;
     if (f == 0) {
+      if (a.extra) {
+        const uint2 er = __ldg(reinterpret_cast<const uint2*>(a.extra + static_cast<long long>(b) * a.extra_ld + d));
+        const float2 e0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&er.x));
+        const float2 e1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&er.y));
+        v[0] += e0.x; v[1] += e0.y; v[2] += e1.x; v[3] += e1.y;
+      }
       if (a.relu_mask_dx) {
 #pragma unroll
         for (int e = 0; e < 4; ++e)
@@ -491,14 +498,17 @@ RS_API int rs_cross_bwd(const void* dx, const void* x0, const void* u, void* du,
 }
 RS_API int rs_push_feature_grads(const float* acc, const void* dxb, const void* T, int B, int F, int D, void* dx, int dx_ld,
                                  void* const* gdst, const int* owner, const int* gcol, long long grow_stride,
-                                 long long sample_base, int relu_mask_dx, void* const* ndst, int nstride, cudaStream_t stream) {
+                                 long long sample_base, int relu_mask_dx, void* const* ndst, int nstride, const void* extra,
+                                 int extra_ld, cudaStream_t stream) {
   RS_REQUIRE(dxb && T && dx && gdst && owner && gcol && D % 4 == 0, "rs_push_feature_grads: bad argument");
+  RS_REQUIRE(!extra || (extra_ld % 4 == 0 && extra_ld >= D), "rs_push_feature_grads: bad extra gradient");
   if (B == 0) return RS_OK;
   PushArgs a;
   a.acc = acc; a.dxb = reinterpret_cast<const __nv_bfloat16*>(dxb); a.T = reinterpret_cast<const __nv_bfloat16*>(T);
   a.B = B; a.F = F; a.D = D; a.dx = reinterpret_cast<__nv_bfloat16*>(dx); a.dx_ld = dx_ld; a.gdst = gdst; a.owner = owner;
   a.gcol = gcol; a.grow_stride = grow_stride; a.sample_base = sample_base; a.relu_mask_dx = relu_mask_dx;
   a.ndst = reinterpret_cast<float* const*>(ndst); a.nstride = nstride;
+  a.extra = reinterpret_cast<const __nv_bfloat16*>(extra); a.extra_ld = extra_ld;
   const long long warps = static_cast<long long>(B) * F;
   push_feature_grads_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(a);
   RS_LAUNCH_CHECK();

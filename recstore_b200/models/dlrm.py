@@ -21,7 +21,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -53,7 +53,8 @@ class DLRMConfig:
     seed: int = 0
     use_cuda_graph: bool = True
     emb_init: str = "uniform"                    # U(+-sqrt(1/n)) as in the reference, or "normal"
-    interaction: str = "dot"                     # "dot" (DLRM) or "dcn" (DLRM-DCNv2: low-rank cross network)
+    interaction: str = "dot"                     # "dot" (DLRM), "dcn" (DLRM-DCNv2: low-rank cross network) or "projection"
+    projection_sizes: Tuple[int, int] = (4, 4)   # DLRM_Projection: rows of the two projected branches
     dcn_layers: int = 3
     dcn_rank: int = 512
     trace_phases: bool = False                   # stamp the GPU timer at phase boundaries (see DLRM.phase_times)
@@ -116,8 +117,9 @@ class DLRM:
         self.F = self.T + 1
         import os
         self.dcn = cfg.interaction == "dcn"
-        assert cfg.interaction in ("dot", "dcn")
-        assert self.dcn or self.F <= 32, "dot interaction kernel handles up to 31 embedding features"
+        self.proj = cfg.interaction == "projection"
+        assert cfg.interaction in ("dot", "dcn", "projection")
+        assert self.dcn or self.proj or self.F <= 32, "dot interaction kernel handles up to 31 embedding features"
         # ---- table placement: round robin by table index
         self.owner = [t % self.world for t in range(self.T)]
         self.local_tables = [t for t in range(self.T) if self.owner[t] == self.rank]
@@ -183,6 +185,11 @@ class DLRM:
         # ---- dense parameters (flat fp32 master / grad / reduced buffers)
         self.Kin0 = _round_up(cfg.num_dense, 64)
         self.n_inter = self.F * self.D if self.dcn else self.D + self.F * (self.F - 1) // 2
+        if self.proj:
+            self.I1, self.I2 = cfg.projection_sizes
+            assert 1 <= self.I1 <= 8 and 1 <= self.I2 <= 8, "projection branches have 1..8 rows"
+            assert (self.F * self.D) % 64 == 0, "projection needs (1 + tables) * dim to be a multiple of 64"
+            self.n_inter = self.D + self.I1 * self.I2
         self.Kz = _round_up(self.n_inter, 64)
         assert not self.dcn or self.Kz == self.n_inter, "DCN needs (1 + tables) * dim to be a multiple of 64"
         dims_b = [(cfg.num_dense, self.Kin0)] + [(n, n) for n in cfg.bottom_mlp[:-1]]
@@ -198,7 +205,12 @@ class DLRM:
             assert r % 64 == 0
             self.crossV = [_Layer(r, self.n_inter, self.n_inter) for _ in range(cfg.dcn_layers)]
             self.crossW = [_Layer(self.n_inter, r, r) for _ in range(cfg.dcn_layers)]
-        layers = self.bot + self.top + self.crossV + self.crossW
+        # DLRM_Projection: two linear branches over the flattened features, [I * D, F * D] each
+        self.projL: List[_Layer] = []
+        if self.proj:
+            fd = self.F * self.D
+            self.projL = [_Layer(self.I1 * self.D, fd, fd), _Layer(self.I2 * self.D, fd, fd)]
+        layers = self.bot + self.top + self.crossV + self.crossW + self.projL
         self.layers = layers
         off = 0
         w_off = []
@@ -237,8 +249,8 @@ class DLRM:
             b0 = torch.randn(L.N, generator=g) * math.sqrt(1.0 / L.N)
             if L in self.crossV:
                 b0.zero_()                       # V has no bias
-            if L in self.crossW:
-                b0.zero_()                       # cross bias starts at zero (torchrec LowRankCrossNet)
+            if L in self.crossW or L in self.projL:
+                b0.zero_()                       # cross / projection biases start at zero
             L.w[:, :L.K].copy_(w0)
             L.b.copy_(b0)
         self.head_w = self.master[head_w_off:head_w_off + self.head_K]
@@ -275,6 +287,10 @@ class DLRM:
             self.c_dt = torch.empty(Bl, r, **bf)
             self.c_dx = [self.d_z, torch.empty(Bl, self.n_inter, **bf)]                # ping-pong dX_l
             self.c_dx0 = torch.empty(Bl, self.n_inter, **f32)
+        if self.proj:
+            self.pb = [torch.empty(Bl, L.N, **bf) for L in self.projL]                 # relu(X P^T + c)
+            self.pdb = [torch.empty(Bl, L.N, **bf) for L in self.projL]
+            self.p_dx = [torch.empty(Bl, self.F * self.D, **bf) for _ in range(2)]
         self.prob = torch.empty(Bl, **f32)
 
         # ---- double-buffered inputs, loss
@@ -386,6 +402,11 @@ class DLRM:
                 F_.gemm_bf16(self.ct[l], W.wb, self.cu[l], mode=0, epi=F_.EPI_NONE, bias=W.b, status=st)
                 F_.cross_fwd(self.Tbuf, self.cu[l], self.cx[l], self.cx[l + 1])
                 self._count(3)
+        elif self.proj:
+            for L, out in zip(self.projL, self.pb):
+                F_.gemm_bf16(self.Tbuf, L.wb, out, mode=0, epi=F_.EPI_RELU, bias=L.b, status=st)
+            F_.proj_inter_forward(self.Tbuf, self.pb[0], self.pb[1], self.I1, self.I2, self.D, self.z)
+            self._count(3)
         else:
             F_.interaction_forward(self.Tbuf, self.Bl, self.F, self.D, self.z); self._count()
         self._stamp("interaction_fwd_done")
@@ -429,7 +450,7 @@ class DLRM:
         # First all-reduce bucket: the top MLP's weight gradients (most of the dense parameters) are complete once the
         # wgrad stream has drained, long before the bottom MLP's; reducing them now hides the transfer behind the rest
         # of the backward.  (With the cross network its layers' gradients come later, so everything goes at the end.)
-        early_bucket = self.world > 1 and not self.dcn
+        early_bucket = self.world > 1 and not self.dcn and not self.proj
         if early_bucket:
             with torch.cuda.stream(side):
                 self.ctx.sync(CH_GRADS_TOP)
@@ -456,6 +477,24 @@ class DLRM:
                                   self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl, relu_mask_dx=True,
                                   ndst_table=self.ndst_table, nstride=self.Tmax)
             self._count()
+            if self.world > 1:
+                self.ctx.signal(CH_BWD); self._count()
+        elif self.proj:
+            F_.proj_inter_backward(self.d_z, self.pb[0], self.pb[1], self.I1, self.I2, self.D, self.pdb[0], self.pdb[1])
+            side.wait_stream(main)
+            self.s_col.wait_stream(main)
+            for L, dy in zip(self.projL, self.pdb):
+                with torch.cuda.stream(self.s_col):
+                    F_.colsum_bf16(dy, L.gb)
+                with torch.cuda.stream(side):
+                    F_.gemm_bf16(dy, self.Tbuf, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st)
+            F_.gemm_bf16(self.pdb[0], self.projL[0].wt, self.p_dx[0], mode=0, epi=F_.EPI_NONE, status=st)
+            F_.gemm_bf16(self.pdb[1], self.projL[1].wt, self.p_dx[1], mode=0, epi=F_.EPI_ADD, aux=self.p_dx[0], status=st)
+            # features: both branches' input gradients; the dense feature also feeds the over-arch directly
+            F_.push_feature_grads(None, self.p_dx[1], self.Tbuf, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
+                                  self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl, relu_mask_dx=True,
+                                  ndst_table=self.ndst_table, nstride=self.Tmax, dense_extra=self.d_z)
+            self._count(8)
             if self.world > 1:
                 self.ctx.signal(CH_BWD); self._count()
         elif self.world > 1:
@@ -607,9 +646,14 @@ class DLRM:
         self.ctx.check_status()
 
     # ------------------------------------------------------------------ state access (tests, checkpoints)
+    def _named_layers(self):
+        """Parameter-name prefixes shared with the PyTorch implementation (``baseline/dlrm_torch.py``)."""
+        return (("bot", self.bot), ("top", self.top), ("crossV", self.crossV), ("crossW", self.crossW),
+                ("proj1", self.projL[:1]), ("proj2", self.projL[1:]))
+
     def dense_state(self) -> Dict[str, torch.Tensor]:
         out = {}
-        for name, Ls in (("bot", self.bot), ("top", self.top), ("crossV", self.crossV), ("crossW", self.crossW)):
+        for name, Ls in self._named_layers():
             for i, L in enumerate(Ls):
                 out[f"{name}.{i}.weight"] = L.w[:, :L.K].clone()
                 out[f"{name}.{i}.bias"] = L.b.clone()
@@ -618,7 +662,7 @@ class DLRM:
         return out
 
     def load_dense_state(self, sd: Dict[str, torch.Tensor]) -> None:
-        for name, Ls in (("bot", self.bot), ("top", self.top), ("crossV", self.crossV), ("crossW", self.crossW)):
+        for name, Ls in self._named_layers():
             for i, L in enumerate(Ls):
                 L.w.zero_()
                 L.w[:, :L.K].copy_(sd[f"{name}.{i}.weight"])
@@ -632,7 +676,7 @@ class DLRM:
         c = self.cfg
         return {"table_rows": list(c.table_rows), "emb_dim": c.emb_dim, "hotness": list(c.hotness), "num_dense": c.num_dense,
                 "bottom_mlp": list(c.bottom_mlp), "top_mlp": list(c.top_mlp), "interaction": c.interaction,
-                "dcn_layers": c.dcn_layers, "dcn_rank": c.dcn_rank}
+                "dcn_layers": c.dcn_layers, "dcn_rank": c.dcn_rank, "projection_sizes": list(c.projection_sizes)}
 
     def save_checkpoint(self, path: str, step: int = 0) -> None:
         from .checkpoint import save_checkpoint

@@ -169,8 +169,23 @@ def cross_bwd(dx, x0, u, du, dx0_acc, accumulate: bool) -> None:
 
 
 def push_feature_grads(acc, dxb, T, B: int, F: int, D: int, dx, gdst_table, owner, gcol, grow_stride: int, sample_base: int,
-                       relu_mask_dx: bool = True, ndst_table=None, nstride: int = 0) -> None:
+                       relu_mask_dx: bool = True, ndst_table=None, nstride: int = 0, dense_extra=None) -> None:
     """Splits the gradient of the feature matrix ``[B, F, D]`` (``acc`` fp32, optional, plus ``dxb`` bf16): feature 0 to
-    ``dx``, features 1.. through the owners' peer pointers, with squared norms (see :func:`interaction_backward`)."""
+    ``dx``, features 1.. through the owners' peer pointers, with squared norms (see :func:`interaction_backward`).
+    ``dense_extra`` (bf16 ``[B, >= D]``, optional) is added to feature 0: the gradient of a direct path of the dense
+    feature into the over-arch."""
     call("rs_push_feature_grads", ptr(acc), ptr(dxb), ptr(T), B, F, D, ptr(dx), dx.stride(0), ptr(gdst_table), ptr(owner),
-         ptr(gcol), grow_stride, sample_base, 1 if relu_mask_dx else 0, ptr(ndst_table), nstride, stream_ptr())
+         ptr(gcol), grow_stride, sample_base, 1 if relu_mask_dx else 0, ptr(ndst_table), nstride, ptr(dense_extra),
+         dense_extra.stride(0) if dense_extra is not None else 0, stream_ptr())
+
+
+def proj_inter_forward(T, b1, b2, I1: int, I2: int, D: int, z) -> None:
+    """``z[b] = [T[b, :D] | b1[b].view(I1, D) @ b2[b].view(I2, D).T | 0]`` (bf16; DLRM_Projection, model_zoo/dlrm.py:289-404)."""
+    call("rs_proj_inter_fwd", ptr(T), T.stride(0), ptr(b1), ptr(b2), T.shape[0], I1, I2, D, ptr(z), z.stride(0), z.shape[1],
+         stream_ptr())
+
+
+def proj_inter_backward(dz, b1, b2, I1: int, I2: int, D: int, db1, db2) -> None:
+    """Gradients of the two (post-ReLU) branches from ``dz[:, D:D + I1 * I2]``, ReLU masks applied."""
+    call("rs_proj_inter_bwd", ptr(dz), dz.stride(0), dz.shape[1], ptr(b1), ptr(b2), dz.shape[0], I1, I2, D, ptr(db1), ptr(db2),
+         stream_ptr())

@@ -369,8 +369,10 @@ def test_bounded_wait_times_out_without_hanging(dev):
     ctx.check_status()          # status was reset
 
 
-def test_dcn_step_matches_torch_oracle(dev):
-    """DLRM-DCNv2 (low-rank cross network instead of the dot interaction) against the fp32 oracle."""
+@pytest.mark.parametrize("kind", ["dcn", "projection"])
+def test_dcn_step_matches_torch_oracle(dev, kind):
+    """DLRM-DCNv2 (low-rank cross network) and DLRM_Projection (product of two learned projections) instead of the dot
+    interaction, against the fp32 oracle."""
     from recstore_b200.models.dlrm import DLRM, DLRMConfig
     from recstore_b200.baseline.dlrm_torch import TorchDLRM, rowwise_adagrad_update
     from recstore_b200.utils.data import DLRMBatchSource
@@ -379,10 +381,10 @@ def test_dcn_step_matches_torch_oracle(dev):
     B, D = 512, 64
     kw = dict(emb_dim=D, bottom_mlp=(128, D), top_mlp=(256, 128, 1))
     cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=0.05, mlp_lr=0.002, seed=5, use_cuda_graph=True,
-                     interaction="dcn", dcn_layers=3, dcn_rank=64, **kw)
+                     interaction=kind, dcn_layers=3, dcn_rank=64, projection_sizes=(4, 3), **kw)
     eng = DLRM(cfg)
-    ora = TorchDLRM(rows, B, hotness=hot, emb_lr=0.05, mlp_lr=0.002, device=dev, seed=5, interaction="dcn", dcn_layers=3,
-                    dcn_rank=64, **kw)
+    ora = TorchDLRM(rows, B, hotness=hot, emb_lr=0.05, mlp_lr=0.002, device=dev, seed=5, interaction=kind, dcn_layers=3,
+                    dcn_rank=64, projection_sizes=(4, 3), **kw)
     with torch.no_grad():
         for k, v in eng.dense_state().items():
             ora.params[k].copy_(v.view_as(ora.params[k]))

@@ -30,7 +30,7 @@ def _init(rank, world, port):
     return dist
 
 
-def _dlrm_worker(rank, world, port, graph, out):
+def _dlrm_worker(rank, world, port, graph, out, kind="dot"):
     dist = _init(rank, world, port)
     try:
         from recstore_b200.models.dlrm import DLRM, DLRMConfig
@@ -39,7 +39,8 @@ def _dlrm_worker(rank, world, port, graph, out):
         rows = [1000, 37, 5000, 12, 300, 20000, 64]
         hot = [1, 2, 1, 3, 1, 1, 1]
         B = 512
-        cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=0.05, mlp_lr=0.05, seed=5, use_cuda_graph=graph)
+        cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=0.05, mlp_lr=0.05 if kind == "dot" else 0.002, seed=5,
+                         use_cuda_graph=graph, interaction=kind, dcn_layers=2, dcn_rank=64, projection_sizes=(3, 4))
         ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"))
         eng = DLRM(cfg, ctx)
         solo = DLRM(cfg) if rank == 0 else None          # same seeds -> identical initial state
@@ -93,6 +94,18 @@ def test_dlrm_two_ranks_match_single(graph):
     out = mgr.dict()
     mp.spawn(_dlrm_worker, args=(world, _free_port(), graph, out), nprocs=world, join=True)
     assert all(out.get(r) == "ok" for r in range(world)), dict(out)
+
+
+@pytest.mark.parametrize("kind", ["dcn", "projection"])
+def test_dlrm_two_ranks_match_single_other_interactions(kind):
+    """The cross-network and projection interactions: sharded run == single-GPU run (losses, tables, dense weights)."""
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_dlrm_worker, args=(2, _free_port(), True, out, kind), nprocs=2, join=True)
+    assert all(out.get(r) == "ok" for r in range(2)), dict(out)
 
 
 def _timeout_worker(rank, world, port, out):
