@@ -168,6 +168,8 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
             os.makedirs(args.save_path, exist_ok=True)
             np.save(os.path.join(args.save_path, f"{ds.name}_{args.model_name}_entity.npy"), model.entity.cpu().numpy())
             np.save(os.path.join(args.save_path, f"{ds.name}_{args.model_name}_relation.npy"), model.relation.cpu().numpy())
+            if getattr(model, "proj", None) is not None:      # TransR / RESCAL: the per-relation matrices (tensor_models.py:452-476)
+                np.save(os.path.join(args.save_path, f"{ds.name}_{args.model_name}projection.npy"), model.proj.cpu().numpy())
             with open(os.path.join(args.save_path, "config.json"), "w") as f:
                 json.dump({"dataset": ds.name, "model_name": args.model_name, "hidden_dim": args.hidden_dim, "gamma": args.gamma,
                            "emp_file": f"{ds.name}_{args.model_name}_entity.npy", "rmap_file": f"{ds.name}_{args.model_name}_relation.npy"}, f, indent=2)

@@ -136,6 +136,19 @@ def test_driver_runs_on_cpu(tmp_path):
     assert info["presampled_hit_ratio"] > 0.1 and (tmp_path / "o" / "config.json").exists()
 
 
+def test_driver_graph_partition_and_transr_checkpoint(tmp_path):
+    """Edge-cut partition in the driver, and the TransR checkpoint with its per-relation projection file."""
+    import numpy as np
+    from recstore_b200.cli import kge_main
+    out, info = kge_main.main(["--model_name", "TransR", "--max_step", "5", "--n_entities", "300", "--n_relations", "6", "--n_triples", "3000",
+                               "--hidden_dim", "8", "--batch_size", "32", "--neg_sample_size", "8", "--num_proc", "2", "--graph_part",
+                               "--save_path", str(tmp_path / "o"), "--log_interval", "1000"])
+    assert 0.0 <= info["edge_cut"] <= 1.0 and out[0]["steps"] == 5
+    proj = np.load(tmp_path / "o" / "synthetic_TransRprojection.npy")
+    assert proj.shape == (6, 64)
+    assert np.load(tmp_path / "o" / "synthetic_TransR_entity.npy").shape == (300, 8)
+
+
 def test_score_infer_modes_and_emb_similarity(tmp_path):
     from recstore_b200.models.kge_infer import EmbSimInfer, ScoreInfer
     g = torch.Generator().manual_seed(0)
