@@ -22,9 +22,13 @@ from ..baseline.kge_torch import edge_score
 
 
 class ScoreInfer:
-    def __init__(self, model_name: str, entity: torch.Tensor, relation: torch.Tensor, gamma: float = 12.0, device="cpu"):
+    def __init__(self, model_name: str, entity: torch.Tensor, relation: torch.Tensor, gamma: float = 12.0, device="cpu",
+                 projection: Optional[torch.Tensor] = None):
         self.model, self.gamma, self.dev = model_name, gamma, torch.device(device)
         self.entity, self.relation = entity.to(self.dev), relation.to(self.dev)
+        # TransR / RESCAL: one matrix per relation, stored flat (tensor_models.py:188-199 reads the same file)
+        self.projection = projection.to(self.dev) if projection is not None else None
+        assert self.projection is not None or model_name not in ("TransR", "RESCAL"), f"{model_name} needs its projection matrices"
         self.emb_init = (gamma + 2.0) / entity.shape[1]
 
     @staticmethod
@@ -33,10 +37,14 @@ class ScoreInfer:
             c = json.load(f)
         ent = torch.from_numpy(np.load(os.path.join(path, c["emp_file"])))
         rel = torch.from_numpy(np.load(os.path.join(path, c["rmap_file"])))
-        return ScoreInfer(c.get("model_name", c.get("model")), ent, rel, float(c.get("gamma", 12.0)), device)
+        name = c.get("model_name", c.get("model"))
+        pfile = os.path.join(path, c["emp_file"].replace("_entity.npy", "projection.npy"))
+        proj = torch.from_numpy(np.load(pfile)) if os.path.exists(pfile) else None
+        return ScoreInfer(name, ent, rel, float(c.get("gamma", 12.0)), device, projection=proj)
 
     def _score(self, h, r, t) -> torch.Tensor:
-        return edge_score(self.model, self.entity[h], self.relation[r], self.entity[t], self.gamma, None, self.emb_init)
+        proj = self.projection[r] if self.projection is not None else None
+        return edge_score(self.model, self.entity[h], self.relation[r], self.entity[t], self.gamma, proj, self.emb_init)
 
     def topk(self, head=None, rel=None, tail=None, k: int = 10, exec_mode: str = "all") -> List[Tuple[torch.Tensor, ...]]:
         """Each result is ``(head_ids, rel_ids, tail_ids, scores)`` sorted by decreasing score.  ``None`` = all ids."""

@@ -147,6 +147,15 @@ def test_driver_graph_partition_and_transr_checkpoint(tmp_path):
     proj = np.load(tmp_path / "o" / "synthetic_TransRprojection.npy")
     assert proj.shape == (6, 64)
     assert np.load(tmp_path / "o" / "synthetic_TransR_entity.npy").shape == (300, 8)
+    # the inference loader reads the projection file too and scores with it
+    import torch
+    from recstore_b200.baseline.kge_torch import edge_score
+    from recstore_b200.models.kge_infer import ScoreInfer
+    inf = ScoreInfer.load(str(tmp_path / "o"))
+    assert inf.projection is not None and inf.projection.shape == (6, 64)
+    h, r, t = torch.tensor([1, 2]), torch.tensor([0, 5]), torch.tensor([7, 9])
+    want = edge_score("TransR", inf.entity[h], inf.relation[r], inf.entity[t], inf.gamma, inf.projection[r], inf.emb_init)
+    assert torch.allclose(inf._score(h, r, t), want)
 
 
 def test_score_infer_modes_and_emb_similarity(tmp_path):
