@@ -44,7 +44,7 @@ class TorchDLRM:
                  emb_lr: float = 0.01, emb_eps: float = 1e-10, emb_optimizer: str = "rowwise_adagrad",
                  mlp_lr: float = 0.01, device="cpu", rank: int = 0, world: int = 1, autocast_bf16: bool = False,
                  seed: int = 0, group=None, interaction: str = "dot", dcn_layers: int = 3, dcn_rank: int = 512,
-                 projection_sizes: Sequence[int] = (4, 4)):
+                 projection_sizes: Sequence[int] = (4, 4), projection_hidden: Sequence[Sequence[int]] = ((), ())):
         self.table_rows = list(table_rows)
         self.T = len(self.table_rows)
         self.D = emb_dim
@@ -71,6 +71,7 @@ class TorchDLRM:
         self._dcn_layers, self._dcn_rank = dcn_layers, dcn_rank
         assert interaction in ("dot", "dcn", "projection")
         self.I1, self.I2 = projection_sizes
+        self.proj_hidden = (tuple(projection_hidden[0]), tuple(projection_hidden[1]))    # hidden widths of the two branch MLPs
         n_inter = (self.T + 1) * emb_dim if interaction == "dcn" else emb_dim + (self.T + 1) * self.T // 2
         if interaction == "projection":          # DLRM_Projection: two learned projections of the features, then their product
             n_inter = emb_dim + self.I1 * self.I2
@@ -92,9 +93,11 @@ class TorchDLRM:
         if interaction == "projection":
             # InteractionProjectionArch of the reference (model_zoo/dlrm.py:289-404): Linear((F*D) -> I*D) branches
             fd = (self.T + 1) * emb_dim
-            for name, I in (("proj1", self.I1), ("proj2", self.I2)):
-                self.params[f"{name}.0.weight"] = (torch.randn(I * emb_dim, fd, generator=g) * math.sqrt(2.0 / (I * emb_dim + fd))).to(self.device)
-                self.params[f"{name}.0.bias"] = torch.zeros(I * emb_dim, device=self.device)
+            for name, I, hid in (("proj1", self.I1, self.proj_hidden[0]), ("proj2", self.I2, self.proj_hidden[1])):
+                widths = [fd] + list(hid) + [I * emb_dim]
+                for li, (k, n) in enumerate(zip(widths[:-1], widths[1:])):
+                    self.params[f"{name}.{li}.weight"] = (torch.randn(n, k, generator=g) * math.sqrt(2.0 / (n + k))).to(self.device)
+                    self.params[f"{name}.{li}.bias"] = torch.zeros(n, device=self.device)
         hk = top_mlp[-2]
         self.params["head.weight"] = (torch.randn(hk, generator=g) * math.sqrt(2.0 / (1 + hk))).to(self.device)
         self.params["head.bias"] = torch.randn(1, generator=g).to(self.device)
@@ -162,8 +165,8 @@ class TorchDLRM:
                     z = x0 * u + z
             elif self.interaction == "projection":
                 flat = Tm.reshape(Tm.shape[0], -1)
-                b1 = F.relu(F.linear(flat, self.params["proj1.0.weight"].to(flat.dtype), self.params["proj1.0.bias"].to(flat.dtype)))
-                b2 = F.relu(F.linear(flat, self.params["proj2.0.weight"].to(flat.dtype), self.params["proj2.0.bias"].to(flat.dtype)))
+                b1 = self._mlp(flat, "proj1", len(self.proj_hidden[0]) + 1)       # ReLU after every layer of a branch
+                b2 = self._mlp(flat, "proj2", len(self.proj_hidden[1]) + 1)
                 inter = torch.bmm(b1.view(-1, self.I1, self.D), b2.view(-1, self.I2, self.D).transpose(1, 2))   # [B, I1, I2]
                 z = torch.cat([x, inter.reshape(inter.shape[0], -1)], 1)
             else:
@@ -179,7 +182,7 @@ class TorchDLRM:
         return {"table_rows": list(self.table_rows), "emb_dim": self.D, "hotness": list(self.hotness),
                 "num_dense": self._num_dense, "bottom_mlp": list(self._bottom_mlp), "top_mlp": list(self._top_mlp),
                 "interaction": self.interaction, "dcn_layers": self._dcn_layers, "dcn_rank": self._dcn_rank,
-                "projection_sizes": [self.I1, self.I2]}
+                "projection_sizes": [self.I1, self.I2], "projection_hidden": [list(h) for h in self.proj_hidden]}
 
     def dense_state(self) -> Dict[str, torch.Tensor]:
         return {k: v.detach().clone() for k, v in self.params.items()}

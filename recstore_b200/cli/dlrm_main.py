@@ -37,8 +37,10 @@ def parse_args(argv=None):
     p.add_argument("--arch-mlp-bot", type=dash_ints, default=[4, 16])
     p.add_argument("--arch-mlp-top", type=dash_ints, default=None, help="default: <interaction width>-64-1")
     p.add_argument("--arch-interaction-op", choices=["dot", "dcn", "projection"], default="dot",
-                   help="dot: DLRM; dcn: low-rank DCNv2 cross network; projection: DLRM_Projection (PyTorch path only)")
+                   help="dot: DLRM; dcn: low-rank DCNv2 cross network; projection: DLRM_Projection")
     p.add_argument("--interaction-branch-sizes", type=dash_ints, default=[4, 4], help="I1-I2 of the projection interaction")
+    p.add_argument("--interaction-branch1-hidden", type=dash_ints, default=[], help="hidden widths of branch 1's MLP, e.g. 512-256")
+    p.add_argument("--interaction-branch2-hidden", type=dash_ints, default=[], help="hidden widths of branch 2's MLP")
     p.add_argument("--dcn-layers", type=int, default=3)
     p.add_argument("--dcn-rank", type=int, default=64)
     p.add_argument("--mini-batch-size", type=int, default=128)
@@ -149,11 +151,15 @@ def run(args) -> dict:
             dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
         ctx = PeerContext(rank, world, device=torch.device(f"cuda:{local}"))
         model = _GpuModel(DLRM(DLRMConfig(table_rows=rows, batch=args.mini_batch_size,
-                                          projection_sizes=tuple(args.interaction_branch_sizes), **kw), ctx))
+                                          projection_sizes=tuple(args.interaction_branch_sizes),
+                                          projection_hidden=(tuple(args.interaction_branch1_hidden),
+                                                             tuple(args.interaction_branch2_hidden)), **kw), ctx))
     else:
         from recstore_b200.baseline.dlrm_torch import TorchDLRM
         model = _CpuModel(TorchDLRM(rows, args.mini_batch_size, device="cpu", rank=0, world=1,
-                                    projection_sizes=tuple(args.interaction_branch_sizes), **kw))
+                                    projection_sizes=tuple(args.interaction_branch_sizes),
+                                    projection_hidden=(tuple(args.interaction_branch1_hidden),
+                                                       tuple(args.interaction_branch2_hidden)), **kw))
     alpha = args.zipf_alpha if args.data_generation == "synthetic" else 0.0
     src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 1)
     test_src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 2)

@@ -55,6 +55,7 @@ class DLRMConfig:
     emb_init: str = "uniform"                    # U(+-sqrt(1/n)) as in the reference, or "normal"
     interaction: str = "dot"                     # "dot" (DLRM), "dcn" (DLRM-DCNv2: low-rank cross network) or "projection"
     projection_sizes: Tuple[int, int] = (4, 4)   # DLRM_Projection: rows of the two projected branches
+    projection_hidden: Tuple[Sequence[int], Sequence[int]] = ((), ())   # hidden widths of the two branch MLPs (multiples of 64)
     dcn_layers: int = 3
     dcn_rank: int = 512
     trace_phases: bool = False                   # stamp the GPU timer at phase boundaries (see DLRM.phase_times)
@@ -205,11 +206,14 @@ class DLRM:
             assert r % 64 == 0
             self.crossV = [_Layer(r, self.n_inter, self.n_inter) for _ in range(cfg.dcn_layers)]
             self.crossW = [_Layer(self.n_inter, r, r) for _ in range(cfg.dcn_layers)]
-        # DLRM_Projection: two linear branches over the flattened features, [I * D, F * D] each
-        self.projL: List[_Layer] = []
+        # DLRM_Projection: two branch MLPs over the flattened features, F * D -> hidden... -> I * D, ReLU after every layer
+        self.projB: List[List[_Layer]] = [[], []]
         if self.proj:
-            fd = self.F * self.D
-            self.projL = [_Layer(self.I1 * self.D, fd, fd), _Layer(self.I2 * self.D, fd, fd)]
+            for b, (I, hid) in enumerate(zip((self.I1, self.I2), cfg.projection_hidden)):
+                widths = [self.F * self.D] + list(hid) + [I * self.D]
+                assert all(w % 64 == 0 for w in widths[:-1]), "projection branch widths are multiples of 64"
+                self.projB[b] = [_Layer(n, k, k) for k, n in zip(widths[:-1], widths[1:])]
+        self.projL: List[_Layer] = self.projB[0] + self.projB[1]
         layers = self.bot + self.top + self.crossV + self.crossW + self.projL
         self.layers = layers
         off = 0
@@ -288,8 +292,8 @@ class DLRM:
             self.c_dx = [self.d_z, torch.empty(Bl, self.n_inter, **bf)]                # ping-pong dX_l
             self.c_dx0 = torch.empty(Bl, self.n_inter, **f32)
         if self.proj:
-            self.pb = [torch.empty(Bl, L.N, **bf) for L in self.projL]                 # relu(X P^T + c)
-            self.pdb = [torch.empty(Bl, L.N, **bf) for L in self.projL]
+            self.pb = [[torch.empty(Bl, L.N, **bf) for L in Ls] for Ls in self.projB]   # activations of the branch layers
+            self.pdb = [[torch.empty(Bl, L.N, **bf) for L in Ls] for Ls in self.projB]  # and their gradients
             self.p_dx = [torch.empty(Bl, self.F * self.D, **bf) for _ in range(2)]
         self.prob = torch.empty(Bl, **f32)
 
@@ -403,10 +407,13 @@ class DLRM:
                 F_.cross_fwd(self.Tbuf, self.cu[l], self.cx[l], self.cx[l + 1])
                 self._count(3)
         elif self.proj:
-            for L, out in zip(self.projL, self.pb):
-                F_.gemm_bf16(self.Tbuf, L.wb, out, mode=0, epi=F_.EPI_RELU, bias=L.b, status=st)
-            F_.proj_inter_forward(self.Tbuf, self.pb[0], self.pb[1], self.I1, self.I2, self.D, self.z)
-            self._count(3)
+            for Ls, outs in zip(self.projB, self.pb):
+                x = self.Tbuf
+                for L, out in zip(Ls, outs):
+                    F_.gemm_bf16(x, L.wb, out, mode=0, epi=F_.EPI_RELU, bias=L.b, status=st); self._count()
+                    x = out
+            F_.proj_inter_forward(self.Tbuf, self.pb[0][-1], self.pb[1][-1], self.I1, self.I2, self.D, self.z)
+            self._count()
         else:
             F_.interaction_forward(self.Tbuf, self.Bl, self.F, self.D, self.z); self._count()
         self._stamp("interaction_fwd_done")
@@ -480,21 +487,31 @@ class DLRM:
             if self.world > 1:
                 self.ctx.signal(CH_BWD); self._count()
         elif self.proj:
-            F_.proj_inter_backward(self.d_z, self.pb[0], self.pb[1], self.I1, self.I2, self.D, self.pdb[0], self.pdb[1])
-            side.wait_stream(main)
-            self.s_col.wait_stream(main)
-            for L, dy in zip(self.projL, self.pdb):
-                with torch.cuda.stream(self.s_col):
-                    F_.colsum_bf16(dy, L.gb)
-                with torch.cuda.stream(side):
-                    F_.gemm_bf16(dy, self.Tbuf, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st)
-            F_.gemm_bf16(self.pdb[0], self.projL[0].wt, self.p_dx[0], mode=0, epi=F_.EPI_NONE, status=st)
-            F_.gemm_bf16(self.pdb[1], self.projL[1].wt, self.p_dx[1], mode=0, epi=F_.EPI_ADD, aux=self.p_dx[0], status=st)
+            F_.proj_inter_backward(self.d_z, self.pb[0][-1], self.pb[1][-1], self.I1, self.I2, self.D,
+                                   self.pdb[0][-1], self.pdb[1][-1])
+            self._count()
+            for b, Ls in enumerate(self.projB):
+                for li in range(len(Ls) - 1, -1, -1):
+                    L, dy = Ls[li], self.pdb[b][li]
+                    xin = self.pb[b][li - 1] if li > 0 else self.Tbuf
+                    side.wait_stream(main)
+                    self.s_col.wait_stream(main)
+                    with torch.cuda.stream(self.s_col):
+                        F_.colsum_bf16(dy, L.gb)
+                    with torch.cuda.stream(side):
+                        F_.gemm_bf16(dy, xin, L.gw, mode=1, epi=F_.EPI_ATOMIC_F32, status=st)
+                    if li > 0:
+                        F_.gemm_bf16(dy, L.wt, self.pdb[b][li - 1], mode=0, epi=F_.EPI_RELU_MASK, aux=xin, status=st)
+                    elif b == 0:
+                        F_.gemm_bf16(dy, L.wt, self.p_dx[0], mode=0, epi=F_.EPI_NONE, status=st)
+                    else:
+                        F_.gemm_bf16(dy, L.wt, self.p_dx[1], mode=0, epi=F_.EPI_ADD, aux=self.p_dx[0], status=st)
+                    self._count(3)
             # features: both branches' input gradients; the dense feature also feeds the over-arch directly
             F_.push_feature_grads(None, self.p_dx[1], self.Tbuf, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
                                   self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl, relu_mask_dx=True,
                                   ndst_table=self.ndst_table, nstride=self.Tmax, dense_extra=self.d_z)
-            self._count(8)
+            self._count()
             if self.world > 1:
                 self.ctx.signal(CH_BWD); self._count()
         elif self.world > 1:
@@ -649,7 +666,7 @@ class DLRM:
     def _named_layers(self):
         """Parameter-name prefixes shared with the PyTorch implementation (``baseline/dlrm_torch.py``)."""
         return (("bot", self.bot), ("top", self.top), ("crossV", self.crossV), ("crossW", self.crossW),
-                ("proj1", self.projL[:1]), ("proj2", self.projL[1:]))
+                ("proj1", self.projB[0]), ("proj2", self.projB[1]))
 
     def dense_state(self) -> Dict[str, torch.Tensor]:
         out = {}
@@ -676,7 +693,8 @@ class DLRM:
         c = self.cfg
         return {"table_rows": list(c.table_rows), "emb_dim": c.emb_dim, "hotness": list(c.hotness), "num_dense": c.num_dense,
                 "bottom_mlp": list(c.bottom_mlp), "top_mlp": list(c.top_mlp), "interaction": c.interaction,
-                "dcn_layers": c.dcn_layers, "dcn_rank": c.dcn_rank, "projection_sizes": list(c.projection_sizes)}
+                "dcn_layers": c.dcn_layers, "dcn_rank": c.dcn_rank, "projection_sizes": list(c.projection_sizes),
+                "projection_hidden": [list(h) for h in c.projection_hidden]}
 
     def save_checkpoint(self, path: str, step: int = 0) -> None:
         from .checkpoint import save_checkpoint

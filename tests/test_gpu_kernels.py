@@ -369,7 +369,7 @@ def test_bounded_wait_times_out_without_hanging(dev):
     ctx.check_status()          # status was reset
 
 
-@pytest.mark.parametrize("kind", ["dcn", "projection"])
+@pytest.mark.parametrize("kind", ["dcn", "projection", "projection_mlp"])
 def test_dcn_step_matches_torch_oracle(dev, kind):
     """DLRM-DCNv2 (low-rank cross network) and DLRM_Projection (product of two learned projections) instead of the dot
     interaction, against the fp32 oracle."""
@@ -380,6 +380,9 @@ def test_dcn_step_matches_torch_oracle(dev, kind):
     hot = [1, 2, 1, 3, 1, 1, 5]
     B, D = 512, 64
     kw = dict(emb_dim=D, bottom_mlp=(128, D), top_mlp=(256, 128, 1))
+    if kind == "projection_mlp":                 # branch MLPs of different depth
+        kind = "projection"
+        kw["projection_hidden"] = ((128,), (192, 64))
     cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=0.05, mlp_lr=0.002, seed=5, use_cuda_graph=True,
                      interaction=kind, dcn_layers=3, dcn_rank=64, projection_sizes=(4, 3), **kw)
     eng = DLRM(cfg)
