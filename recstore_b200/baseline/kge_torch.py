@@ -88,6 +88,39 @@ def logsigmoid_loss(pos: torch.Tensor, neg: torch.Tensor) -> torch.Tensor:
     return (-F.logsigmoid(pos).mean() - F.logsigmoid(-neg).mean()) / 2
 
 
+LOSS_GENRES = ("Logsigmoid", "Logistic", "Hinge", "BCE")
+
+
+def kg_loss(pos: torch.Tensor, neg: torch.Tensor, genre: str = "Logsigmoid", margin: float = 1.0, adversarial: bool = False,
+            temperature: float = 1.0, edge_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Loss over positive scores ``[bs]`` and negative scores ``[bs, ns]`` (loss.py:10-99 of the reference): a criterion
+    applied with label +1 to positives and -1 (0 for BCE) to negatives, negatives averaged per positive -- or weighted by
+    ``softmax(neg * temperature)`` (self-adversarial sampling, weights not differentiated) -- then
+    ``(mean(pos part) + mean(neg part)) / 2``.  ``edge_weight`` ``[bs]`` scales both parts per positive."""
+    if genre == "Logsigmoid":
+        crit = lambda x, y: -F.logsigmoid(y * x)
+        neg_label = -1.0
+    elif genre == "Logistic":
+        crit = lambda x, y: F.softplus(-y * x)
+        neg_label = -1.0
+    elif genre == "Hinge":
+        crit = lambda x, y: (margin - y * x).clamp_min(0)
+        neg_label = -1.0
+    elif genre == "BCE":
+        crit = lambda x, y: -(y * F.logsigmoid(x) + (1 - y) * F.logsigmoid(-x))     # log(1 - sigmoid(x)) = logsigmoid(-x)
+        neg_label = 0.0
+    else:
+        raise ValueError(f"loss genre {genre!r} is not supported; one of {LOSS_GENRES}")
+    pl, nl = crit(pos, 1.0), crit(neg, neg_label)
+    if edge_weight is not None:
+        pl, nl = pl * edge_weight, nl * edge_weight.view(-1, 1)
+    if adversarial:
+        nl = (torch.softmax(neg * temperature, dim=-1).detach() * nl).sum(-1)
+    else:
+        nl = nl.mean(-1)
+    return (pl.mean() + nl.mean()) / 2
+
+
 def rowwise_adagrad_(weight: torch.Tensor, state: torch.Tensor, ids: torch.Tensor, grad: torch.Tensor, lr: float, eps: float = 1e-10):
     """state[u] += mean_d((sum of the row's gradients / count)^2); w[u] -= lr * g / (sqrt(state[u]) + eps), with the
     duplicate gradients of a row averaged as the reference's sparse Adagrad does (tensor_models.py:380-415)."""
@@ -102,8 +135,13 @@ class TorchKGE:
     """Dense entity / relation tables on one device, trained like the reference's stock path."""
 
     def __init__(self, n_entities: int, n_relations: int, dim: int, model: str = "TransE_l2", gamma: float = 12.0,
-                 lr: float = 0.1, device="cpu", seed: int = 0, rel_dim: Optional[int] = None, neg_chunk_size: int = 0):
+                 lr: float = 0.1, device="cpu", seed: int = 0, rel_dim: Optional[int] = None, neg_chunk_size: int = 0,
+                 loss_genre: str = "Logsigmoid", margin: float = 1.0, neg_adversarial_sampling: bool = False,
+                 adversarial_temperature: float = 1.0, regularization_coef: float = 0.0, regularization_norm: int = 3):
         assert model in MODEL_NAMES, model
+        assert loss_genre in LOSS_GENRES, loss_genre
+        self.loss_cfg = dict(genre=loss_genre, margin=margin, adversarial=neg_adversarial_sampling, temperature=adversarial_temperature)
+        self.reg_coef, self.reg_norm = regularization_coef, regularization_norm
         self.model, self.dim, self.gamma, self.lr, self.device = model, dim, gamma, lr, torch.device(device)
         self.emb_init = (gamma + 2.0) / dim
         g = torch.Generator().manual_seed(seed)
@@ -130,12 +168,15 @@ class TorchKGE:
         neg = chunk_neg_score(self.model, h, r, t, n, corrupt_head, chunk, self.gamma, p, self.emb_init)
         return pos, neg, (h, r, t, n, p)
 
-    def train_step(self, h_ids, r_ids, t_ids, neg_ids, chunk: int, corrupt_head: Optional[bool] = None) -> float:
+    def train_step(self, h_ids, r_ids, t_ids, neg_ids, chunk: int, corrupt_head: Optional[bool] = None,
+                   edge_weight: Optional[torch.Tensor] = None) -> float:
         if corrupt_head is None:
             corrupt_head = bool(self.step_no & 1)
         self.step_no += 1
         pos, neg, (h, r, t, n, p) = self.scores(h_ids, r_ids, t_ids, neg_ids, corrupt_head, chunk)
-        loss = logsigmoid_loss(pos, neg)
+        loss = kg_loss(pos, neg, edge_weight=edge_weight, **self.loss_cfg)
+        if self.reg_coef > 0.0 and self.reg_norm > 0:          # on the rows of this batch (general_models.py:623-629)
+            loss = loss + self.reg_coef * (torch.cat([h, t, n]).norm(p=self.reg_norm) + r.norm(p=self.reg_norm))
         loss.backward()
         with torch.no_grad():
             ids = torch.cat([h_ids, t_ids, neg_ids])

@@ -14,6 +14,12 @@ relation tables row-sharded over the GPUs' HBM; tcgen05 scoring where the negati
 kernels for the L1 / modulus distances); TransR and RESCAL, and ``--device cpu``, run the PyTorch implementation on
 tables shared between the worker processes (lock-free updates, as the reference's stock path does).  Prints
 ``Successfully xmh`` when done.
+
+The command line mirrors the reference's (utils.py:199-304, dgl-ke-main.py:84-152).  Loss options (``--loss_genre``,
+``-adv``, ``-rc``), degree-based negatives and edge importance run on the PyTorch tables; ``--mix_cpu_gpu`` keeps only the
+``--cache_ratio`` share of every entity shard in HBM and the rest in pinned host memory that the kernels address in
+place; ``--gpu`` / ``--nr_gpus`` select the CUDA path with one worker per GPU; ``--valid --eval_interval N`` scores the
+validation split during training; ``--force_sync_interval N`` puts a barrier between the workers every N steps.
 """
 from __future__ import annotations
 
@@ -61,11 +67,66 @@ def parse_args(argv=None):
     p.add_argument("--save_path", default=None)
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--no_graph", action="store_true", help="native path: launch the step eagerly instead of replaying a CUDA graph")
+    # ---- the rest of the reference's surface (utils.py:199-304 CommonArgParser, dgl-ke-main.py:84-152)
+    p.add_argument("--delimiter", default="\t", help="field separator of the triple files")
+    p.add_argument("--double_ent", action="store_true", help="entity embeddings are 2 x hidden_dim wide (RotatE, ComplEx)")
+    p.add_argument("--double_rel", action="store_true", help="relation embeddings are 2 x hidden_dim wide (ComplEx)")
+    p.add_argument("--loss_genre", "-lg", default="Logsigmoid", choices=["Hinge", "Logistic", "Logsigmoid", "BCE"])
+    p.add_argument("--margin", "-m", type=float, default=1.0, help="margin of the hinge loss")
+    p.add_argument("--pairwise", "-pw", action="store_true", help="pairwise loss (closed in the reference: loss.py asserts)")
+    p.add_argument("--neg_adversarial_sampling", "-adv", action="store_true")
+    p.add_argument("--adversarial_temperature", "-a", type=float, default=1.0)
+    p.add_argument("--regularization_coef", "-rc", type=float, default=0.0)
+    p.add_argument("--regularization_norm", "-rn", type=int, default=3)
+    p.add_argument("--neg_deg_sample", action="store_true", help="draw negatives proportionally to entity degree")
+    p.add_argument("--neg_deg_sample_eval", action="store_true")
+    p.add_argument("--valid", action="store_true", help="evaluate on the validation split every --eval_interval steps")
+    p.add_argument("--eval_interval", type=int, default=10000)
+    p.add_argument("--eval_percent", type=float, default=1.0, help="share of the evaluation split that is scored")
+    p.add_argument("--no_eval_filter", action="store_true", help="accepted: evaluation here ranks against sampled negatives, unfiltered")
+    p.add_argument("--no_save_emb", action="store_true")
+    p.add_argument("--num_thread", type=int, default=0, help="host threads per worker (0: share the cores evenly)")
+    p.add_argument("--force_sync_interval", type=int, default=-1, help="barrier between the workers every N steps")
+    p.add_argument("--shuffle", action="store_true", help="accepted: batches are drawn uniformly at random already")
+    p.add_argument("--has_edge_importance", action="store_true", help="a fourth column of the triple files weighs each triple")
+    p.add_argument("--gpu", type=int, nargs="+", default=None, help="GPU ids: selects --device cuda and one worker per GPU")
+    p.add_argument("--nr_gpus", type=int, default=None)
+    p.add_argument("--mix_cpu_gpu", action="store_true", help="keep only the hot share (--cache_ratio) of the entity table in HBM")
+    p.add_argument("--async_update", action="store_true", help="accepted: the native step already overlaps the sparse update")
+    p.add_argument("--use_my_emb", type=lambda v: str(v).lower() in ("1", "true", "yes"), default=True,
+                   help="RecStore embedding path (here: the native sharded tables); false = the PyTorch tables")
+    p.add_argument("--cached_emb_type", default="KnownShardedCachedEmbedding")
+    p.add_argument("--backwardMode", default="CppAsyncV2", choices=["PySync", "CppSync", "CppAsync", "CppAsyncV2"])
+    p.add_argument("--L", type=int, default=10, help="lookahead window of the cached sampler, in steps")
+    p.add_argument("--nr_background_threads", type=int, default=4)
+    p.add_argument("--update_cache_use_omp", type=int, default=1)
+    p.add_argument("--update_pq_use_omp", type=int, default=1)
     a = p.parse_args(argv)
+    if a.pairwise:
+        p.error("--pairwise is closed in the reference (its loss generator asserts) and is not offered here")
+    if a.gpu is not None or a.nr_gpus is not None:
+        a.device = "cuda"
+        a.num_proc = a.nr_gpus if a.nr_gpus is not None else len(a.gpu)
+    if a.double_rel and not a.double_ent:
+        p.error("--double_rel without --double_ent: entity and relation widths must match for every model but RotatE")
+    a.dim = a.hidden_dim * (2 if a.double_ent else 1)          # width of an entity row
     if a.neg_chunk_size is None:
         a.neg_chunk_size = min(a.neg_sample_size, a.batch_size)
     a.batch_size = -(-a.batch_size // a.neg_chunk_size) * a.neg_chunk_size      # whole chunks, like the reference (utils.py:27-33)
     return a
+
+
+def _native(args) -> bool:
+    """The sharded-HBM engine takes the default loss only; every other combination runs on the PyTorch tables."""
+    plain = (args.loss_genre == "Logsigmoid" and not args.neg_adversarial_sampling and args.regularization_coef == 0.0
+             and not args.neg_deg_sample and not args.has_edge_importance)
+    return args.device == "cuda" and args.use_my_emb and plain and args.model_name in NATIVE_MODELS
+
+
+def _loss_kwargs(args) -> dict:
+    return dict(loss_genre=args.loss_genre, margin=args.margin, neg_adversarial_sampling=args.neg_adversarial_sampling,
+                adversarial_temperature=args.adversarial_temperature, regularization_coef=args.regularization_coef,
+                regularization_norm=args.regularization_norm)
 
 
 def _free_port():
@@ -79,7 +140,8 @@ def prepare(args):
     if args.dataset == "synthetic" or args.data_path is None:
         ds = K.KGDataset.synthetic(args.n_entities, args.n_relations, args.n_triples, seed=args.seed)
     else:
-        ds = K.KGDataset.load(args.data_path, args.data_files or ["train.tsv"], args.format, name=args.dataset)
+        ds = K.KGDataset.load(args.data_path, args.data_files or ["train.tsv"], args.format, name=args.dataset,
+                              delimiter=args.delimiter, has_edge_importance=args.has_edge_importance)
     W = args.num_proc
     info = {"n_entities": ds.n_entities, "n_relations": ds.n_relations, "n_train": int(ds.train[0].size)}
     if args.rel_part:
@@ -109,8 +171,10 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
     from recstore_b200.utils.kg_data import ChunkedNegativeSampler
     W = args.num_proc
     dev = torch.device(f"cuda:{rank}") if args.device == "cuda" else torch.device("cpu")
-    native = args.device == "cuda" and args.model_name in NATIVE_MODELS
-    if args.device == "cpu" and W > 1:
+    native = _native(args)
+    if args.num_thread > 0:
+        torch.set_num_threads(args.num_thread)
+    elif args.device == "cpu" and W > 1:
         torch.set_num_threads(max(1, (os.cpu_count() or W) // W))       # the workers share the host's cores
     if W > 1 or native:
         import torch.distributed as dist
@@ -119,27 +183,55 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
             torch.cuda.set_device(rank)
         dist.init_process_group("nccl" if args.device == "cuda" else "gloo", rank=rank, world_size=W)
     mine = tuple(x[parts[rank]] for x in ds.train)
+    w_mine = ds.train_weight[parts[rank]] if (args.has_edge_importance and ds.train_weight is not None) else None
     smp = ChunkedNegativeSampler(mine, ds.n_entities, args.batch_size, args.neg_sample_size, args.neg_chunk_size,
-                                 seed=args.seed * 100 + rank, device=dev)
+                                 seed=args.seed * 100 + rank, device=dev, neg_deg_sample=args.neg_deg_sample, weight=w_mine)
     if native:
         from recstore_b200.models.kge import KGEConfig, KGEModel
         from recstore_b200.parallel.peer import PeerContext
         ctx = PeerContext(rank, W, device=dev)
-        model = KGEModel(KGEConfig(ds.n_entities, ds.n_relations, dim=args.hidden_dim, model=args.model_name, gamma=args.gamma,
+        hbm = (args.cache_ratio if args.cache_ratio > 0 else 0.25) if args.mix_cpu_gpu else 1.0
+        model = KGEModel(KGEConfig(ds.n_entities, ds.n_relations, dim=args.dim, model=args.model_name, gamma=args.gamma,
                                    batch=args.batch_size, neg_sample_size=args.neg_sample_size, neg_chunk_size=args.neg_chunk_size,
-                                   lr=args.lr, seed=args.seed, dataset=ds.name, use_cuda_graph=not args.no_graph), ctx)
+                                   lr=args.lr, seed=args.seed, dataset=ds.name, use_cuda_graph=not args.no_graph,
+                                   entity_hbm_ratio=hbm), ctx)
         step_fn = lambda h, r, t, n, ch: model.train_step(h, r, t, n, ch)
     else:
         from recstore_b200.baseline.kge_torch import TorchKGE
-        model = TorchKGE(ds.n_entities, ds.n_relations, args.hidden_dim, args.model_name, args.gamma, args.lr, device=dev, seed=args.seed)
+        model = TorchKGE(ds.n_entities, ds.n_relations, args.dim, args.model_name, args.gamma, args.lr, device=dev, seed=args.seed,
+                         **_loss_kwargs(args))
         if shared is not None:           # one table for all CPU workers
             model.entity, model.relation, model.proj, model.state = shared["entity"], shared["relation"], shared.get("proj"), shared["state"]
-        step_fn = lambda h, r, t, n, ch: model.train_step(h, r, t, n, args.neg_chunk_size, ch)
+        step_fn = lambda h, r, t, n, ch: model.train_step(h, r, t, n, args.neg_chunk_size, ch, edge_weight=smp.last_weight)
+    def run_eval(split, percent: float = 1.0):
+        """Sampled-negative ranking metrics of (a share of) a split; native: every rank scores, else rank 0 only."""
+        n_eval = max(args.batch_size, int(min(split[0].size, args.batch_size_eval * 4) * percent))
+        th, tr, tt = (torch.as_tensor(x[:n_eval]).to(dev) for x in split)
+        g = torch.Generator(device=dev if native else "cpu").manual_seed(5)
+        if native:
+            ms = []
+            for s0 in range(0, th.numel() - args.batch_size + 1, args.batch_size):
+                ms.append(model.evaluate(th[s0:s0 + args.batch_size], tr[s0:s0 + args.batch_size], tt[s0:s0 + args.batch_size], g))
+            return {k: float(np.mean([m[k] for m in ms])) for k in ms[0]} if ms else None
+        if rank == 0:
+            return model.evaluate(th, tr, tt, args.neg_sample_size_eval, g)
+        return None
+
     t0 = time.time()
     losses = []
+    valid_log = []
     for step in range(args.max_step):
         h, r, t, n, ch = next(smp)
         losses.append(step_fn(h, r, t, n, ch))
+        if args.force_sync_interval > 0 and W > 1 and (step + 1) % args.force_sync_interval == 0:
+            import torch.distributed as dist
+            dist.barrier()                   # keeps the workers within one interval of each other (train_pytorch.py:292-294)
+        if args.valid and (step + 1) % args.eval_interval == 0 and (ds.valid is not None or ds.test is not None):
+            m = run_eval(ds.valid if ds.valid is not None else ds.test, args.eval_percent)
+            if m is not None:
+                valid_log.append({"step": step + 1, **m})
+                if rank == 0:
+                    print(f"[{rank}] valid @ {step + 1}: " + ", ".join(f"{k} {v:.4f}" for k, v in m.items()), flush=True)
         if rank == 0 and (step + 1) % args.log_interval == 0:
             recent = [float(x) for x in losses[-args.log_interval:]]
             print(f"[{rank}] step {step + 1}: loss {np.mean(recent):.5f}, {(time.time() - t0) / (step + 1) * 1e3:.2f} ms/step", flush=True)
@@ -151,17 +243,11 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
     if W > 1 or native:
         import torch.distributed as dist
         dist.barrier()
+    if valid_log:
+        res["valid"] = valid_log
     if args.test and ds.test is not None:
-        th, tr, tt = (torch.as_tensor(x[: args.batch_size_eval * 4]).to(dev) for x in ds.test)
-        g = torch.Generator(device=dev if native else "cpu").manual_seed(5)
-        if native:
-            ms = []
-            for s in range(0, th.numel() - args.batch_size + 1, args.batch_size):
-                ms.append(model.evaluate(th[s:s + args.batch_size], tr[s:s + args.batch_size], tt[s:s + args.batch_size], g))
-            res["test"] = {k: float(np.mean([m[k] for m in ms])) for k in ms[0]} if ms else None
-        elif rank == 0:
-            res["test"] = model.evaluate(th, tr, tt, args.neg_sample_size_eval, g)
-    if args.save_path:
+        res["test"] = run_eval(ds.test)
+    if args.save_path and not args.no_save_emb:
         if native:
             model.save(args.save_path)
         elif rank == 0:
@@ -171,7 +257,7 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
             if getattr(model, "proj", None) is not None:      # TransR / RESCAL: the per-relation matrices (tensor_models.py:452-476)
                 np.save(os.path.join(args.save_path, f"{ds.name}_{args.model_name}projection.npy"), model.proj.cpu().numpy())
             with open(os.path.join(args.save_path, "config.json"), "w") as f:
-                json.dump({"dataset": ds.name, "model_name": args.model_name, "hidden_dim": args.hidden_dim, "gamma": args.gamma,
+                json.dump({"dataset": ds.name, "model_name": args.model_name, "hidden_dim": args.dim, "gamma": args.gamma,
                            "emp_file": f"{ds.name}_{args.model_name}_entity.npy", "rmap_file": f"{ds.name}_{args.model_name}_relation.npy"}, f, indent=2)
     if out is not None:
         out[rank] = res
@@ -186,10 +272,10 @@ def main(argv=None):
     ds, parts, info = prepare(args)
     print(json.dumps({"prepared": info}), flush=True)
     shared = None
-    native = args.device == "cuda" and args.model_name in NATIVE_MODELS
+    native = _native(args)
     if not native and args.num_proc > 1 and args.device == "cpu":
         from recstore_b200.baseline.kge_torch import TorchKGE
-        m = TorchKGE(ds.n_entities, ds.n_relations, args.hidden_dim, args.model_name, args.gamma, args.lr, seed=args.seed)
+        m = TorchKGE(ds.n_entities, ds.n_relations, args.dim, args.model_name, args.gamma, args.lr, seed=args.seed)
         shared = {"entity": m.entity.share_memory_(), "relation": m.relation.share_memory_(),
                   "state": {k: v.share_memory_() for k, v in m.state.items()}}
         if m.proj is not None:

@@ -56,6 +56,7 @@ class KGEConfig:
     eps: float = 1e-10
     seed: int = 0
     dataset: str = "synthetic"
+    entity_hbm_ratio: float = 1.0     # < 1: that share of every entity shard stays in HBM (low ids), the rest in pinned host memory
     use_cuda_graph: bool = False      # capture the step (one graph per corruption side) and replay it: ~40 launches per step
 
 
@@ -80,7 +81,7 @@ class KGEModel:
         scale = self.emb_init = (cfg.gamma + 2.0) / cfg.dim
         n_ids = 2 * self.bs + self.nneg
         self.entity = ShardedEmbeddingTable(self.ctx, "kge_entity", cfg.n_entities, self.D, max_keys=n_ids, lr=cfg.lr, eps=cfg.eps,
-                                            init="uniform", init_scale=scale, seed=cfg.seed)
+                                            init="uniform", init_scale=scale, seed=cfg.seed, hbm_ratio=cfg.entity_hbm_ratio)
         self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations, self.Dr, max_keys=self.bs, lr=cfg.lr,
                                               eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 1)
         f = dict(dtype=torch.float32, device=dev)
@@ -203,6 +204,8 @@ class KGEModel:
         """Full table on rank 0 (host), ``None`` elsewhere.  Meant for tables that fit in host memory."""
         world, rank = self.ctx.world, self.ctx.rank
         local = tab.weight.cpu()
+        if tab.tiered:                       # hot rows in HBM, then the host tier
+            local = torch.cat([local, tab.cold])
         if world == 1:
             return local[: tab.N].numpy()
         import torch.distributed as dist
@@ -234,7 +237,10 @@ class KGEModel:
         for tab, kind in ((self.entity, "entity"), (self.relation, "relation")):
             full = torch.from_numpy(np.load(os.path.join(path, f"{c.dataset}_{c.model}_{kind}.npy")))
             mine = full[self.ctx.rank::self.ctx.world]
-            tab.weight[: mine.shape[0]].copy_(mine)
+            hot = min(mine.shape[0], tab.weight.shape[0])
+            tab.weight[:hot].copy_(mine[:hot])
+            if tab.tiered and mine.shape[0] > hot:
+                tab.cold[: mine.shape[0] - hot].copy_(mine[hot:])
 
 
 class KGSampler:

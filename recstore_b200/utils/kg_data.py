@@ -35,6 +35,7 @@ class KGDataset:
     test: Optional[Tuple[np.ndarray, np.ndarray, np.ndarray]] = None
     entity2id: Optional[Dict[str, int]] = None
     relation2id: Optional[Dict[str, int]] = None
+    train_weight: Optional[np.ndarray] = None                 # importance of every training triple (a fourth column), float32
 
     @staticmethod
     def synthetic(n_entities: int, n_relations: int, n_triples: int, alpha: float = 1.3, seed: int = 0, test_frac: float = 0.02):
@@ -45,8 +46,11 @@ class KGDataset:
         return KGDataset("synthetic", n_entities, n_relations, cut(2 * n_test, n_triples), cut(0, n_test), cut(n_test, 2 * n_test))
 
     @staticmethod
-    def load(path: str, files: Sequence[str], fmt: str = "raw_udd_hrt", name: Optional[str] = None, delimiter: str = "\t"):
-        """``files``: train [valid test] for ``raw_udd_*``; entities, relations, train [valid test] for ``udd_*``."""
+    def load(path: str, files: Sequence[str], fmt: str = "raw_udd_hrt", name: Optional[str] = None, delimiter: str = "\t",
+             has_edge_importance: bool = False):
+        """``files``: train [valid test] for ``raw_udd_*``; entities, relations, train [valid test] for ``udd_*``.
+        With ``has_edge_importance`` the training file has a fourth column, the weight of the triple in the loss
+        (KGDataset.py of the reference: ``has_importance``)."""
         raw = fmt.startswith("raw_udd_")
         order = fmt.split("_")[-1]
         assert sorted(order) == ["h", "r", "t"], f"bad format {fmt}"
@@ -62,7 +66,8 @@ class KGDataset:
             tfiles = files[2:]
         assert 1 <= len(tfiles) <= 3, "expected train [valid test]"
         splits = []
-        for fn in tfiles:
+        weights: List[float] = []
+        for fi, fn in enumerate(tfiles):
             hs, rs, ts = [], [], []
             with open(os.path.join(path, fn)) as f:
                 for ln, line in enumerate(f):
@@ -72,6 +77,10 @@ class KGDataset:
                             raise ValueError(f"{fn}:{ln + 1}: expected 3 columns")
                         continue
                     hn, rn, tn = p[col["h"]], p[col["r"]], p[col["t"]]
+                    if has_edge_importance and fi == 0:
+                        if len(p) < 4:
+                            raise ValueError(f"{fn}:{ln + 1}: expected a fourth column with the triple's importance")
+                        weights.append(float(p[3]))
                     if raw:
                         hs.append(e2i.setdefault(hn, len(e2i))); ts.append(e2i.setdefault(tn, len(e2i)))
                         rs.append(r2i.setdefault(rn, len(r2i)))
@@ -86,7 +95,8 @@ class KGDataset:
             if h.size and (max(h.max(), t.max()) >= ne or r.max() >= nr):
                 raise ValueError("triple id outside the dictionaries")
         return KGDataset(name or os.path.basename(os.path.normpath(path)), ne, nr, splits[0], splits[1] if len(splits) > 1 else None,
-                         splits[2] if len(splits) > 2 else None, e2i, r2i)
+                         splits[2] if len(splits) > 2 else None, e2i, r2i,
+                         np.array(weights, dtype=np.float32) if has_edge_importance else None)
 
 
 def _read_dict(path: str, delimiter: str) -> Dict[str, int]:
@@ -196,10 +206,19 @@ def graph_partition(head: np.ndarray, tail: np.ndarray, n_entities: int, n_parts
 # ------------------------------------------------------------------------------------------------ sampling
 class ChunkedNegativeSampler:
     """Positive batches from one worker's triples plus ``batch / chunk * neg_sample_size`` uniform negative entities;
-    head / tail corruption alternates (sampler.py:703-818 of the reference)."""
+    head / tail corruption alternates (sampler.py:703-818 of the reference).  ``neg_deg_sample`` draws the negatives in
+    proportion to ``1 + degree`` over this worker's triples instead of uniformly; ``weight`` (one float per triple)
+    makes ``last_weight`` hold the importance of the batch's positives after every ``next()``."""
 
-    def __init__(self, triples, n_entities: int, batch: int, neg_sample_size: int, neg_chunk_size: int, seed: int = 0, device="cpu"):
+    def __init__(self, triples, n_entities: int, batch: int, neg_sample_size: int, neg_chunk_size: int, seed: int = 0, device="cpu",
+                 neg_deg_sample: bool = False, weight=None):
         self.h, self.r, self.t = (torch.as_tensor(x, dtype=torch.int64, device=device) for x in triples)
+        self.weight = torch.as_tensor(weight, dtype=torch.float32, device=device) if weight is not None else None
+        self.last_weight: Optional[torch.Tensor] = None
+        self.neg_prob = None
+        if neg_deg_sample:
+            deg = torch.bincount(torch.cat([self.h, self.t]), minlength=n_entities).float() + 1.0
+            self.neg_prob = deg / deg.sum()
         assert batch % neg_chunk_size == 0
         self.n, self.ne, self.batch = self.h.numel(), n_entities, batch
         self.nneg = batch // neg_chunk_size * neg_sample_size
@@ -210,7 +229,12 @@ class ChunkedNegativeSampler:
 
     def __next__(self):
         idx = torch.randint(0, self.n, (self.batch,), generator=self.gen, device=self.dev)
-        neg = torch.randint(0, self.ne, (self.nneg,), generator=self.gen, device=self.dev)
+        if self.neg_prob is None:
+            neg = torch.randint(0, self.ne, (self.nneg,), generator=self.gen, device=self.dev)
+        else:
+            neg = torch.multinomial(self.neg_prob, self.nneg, replacement=True, generator=self.gen)
+        if self.weight is not None:
+            self.last_weight = self.weight[idx]
         corrupt_head = bool(self.step & 1)
         self.step += 1
         return self.h[idx], self.r[idx], self.t[idx], neg, corrupt_head
@@ -274,4 +298,5 @@ def renumber_graph(ds: KGDataset, hot: Sequence[torch.Tensor], cache_size: int) 
     m = d.numpy()
     f = lambda tr: None if tr is None else (m[tr[0]], tr[1], m[tr[2]])
     e2i = {k: int(m[v]) for k, v in ds.entity2id.items()} if ds.entity2id else None
-    return KGDataset(ds.name, ds.n_entities, ds.n_relations, f(ds.train), f(ds.valid), f(ds.test), e2i, ds.relation2id), d
+    return KGDataset(ds.name, ds.n_entities, ds.n_relations, f(ds.train), f(ds.valid), f(ds.test), e2i, ds.relation2id,
+                     ds.train_weight), d

@@ -239,3 +239,56 @@ def test_graph_partition_recovers_planted_blocks_and_balances():
     import pytest
     with pytest.raises(Exception):
         K.graph_partition(np.array([0, n]), np.array([1, 2]), n, 2)
+
+
+def test_loss_genres_match_their_definitions():
+    """Criteria of the reference's loss generator (loss.py:10-99): label +1 for positives, -1 (0 for BCE) for negatives,
+    negatives averaged or self-adversarially weighted, the two parts averaged."""
+    import torch
+    import torch.nn.functional as F
+    from recstore_b200.baseline.kge_torch import kg_loss, logsigmoid_loss
+    g = torch.Generator().manual_seed(0)
+    pos, neg = torch.randn(16, generator=g) * 3, torch.randn(16, 7, generator=g) * 3
+    assert torch.allclose(kg_loss(pos, neg), logsigmoid_loss(pos, neg))
+    assert torch.allclose(kg_loss(pos, neg, "Logistic"), (F.softplus(-pos).mean() + F.softplus(neg).mean(-1).mean()) / 2)
+    want = ((2.0 - pos).clamp_min(0).mean() + (2.0 + neg).clamp_min(0).mean(-1).mean()) / 2
+    assert torch.allclose(kg_loss(pos, neg, "Hinge", margin=2.0), want)
+    bce = (-torch.log(torch.sigmoid(pos)).mean() - torch.log(1 - torch.sigmoid(neg)).mean(-1).mean()) / 2
+    assert torch.allclose(kg_loss(pos, neg, "BCE"), bce, atol=1e-5)
+    w = torch.softmax(neg * 0.5, -1)
+    adv = (-F.logsigmoid(pos).mean() + (w * -F.logsigmoid(-neg)).sum(-1).mean()) / 2
+    assert torch.allclose(kg_loss(pos, neg, adversarial=True, temperature=0.5), adv)
+    ew = torch.rand(16, generator=g)
+    wl = ((-F.logsigmoid(pos) * ew).mean() + (-F.logsigmoid(-neg) * ew[:, None]).mean(-1).mean()) / 2
+    assert torch.allclose(kg_loss(pos, neg, edge_weight=ew), wl)
+    # the adversarial weights carry no gradient
+    n2 = neg.clone().requires_grad_(True)
+    kg_loss(pos, n2, adversarial=True).backward()
+    direct = torch.autograd.grad((torch.softmax(neg, -1) * -F.logsigmoid(-n2)).sum(-1).mean() / 2, n2)[0]
+    assert torch.allclose(n2.grad, direct)
+
+
+def test_driver_reference_flags(tmp_path):
+    """The rest of the reference's command line: loss options, degree-based negatives, validation during training,
+    worker barriers, edge importance from a fourth column, --no_save_emb."""
+    import numpy as np
+    from recstore_b200.cli import kge_main
+    rng = np.random.default_rng(0)
+    with open(tmp_path / "train.tsv", "w") as f:
+        for _ in range(600):
+            f.write(f"e{rng.integers(0, 50)}|r{rng.integers(0, 4)}|e{rng.integers(0, 50)}|{rng.random():.3f}\n")
+    out, info = kge_main.main(["--model_name", "ComplEx", "--dataset", "toy", "--data_path", str(tmp_path), "--data_files", "train.tsv",
+                               "--format", "raw_udd_hrt", "--delimiter", "|", "--has_edge_importance", "--hidden_dim", "8", "--double_ent",
+                               "--double_rel", "--batch_size", "32", "--neg_sample_size", "8", "--max_step", "12", "-lg", "Hinge",
+                               "-m", "2.0", "-adv", "-a", "0.5", "-rc", "1e-6", "-rn", "3", "--neg_deg_sample", "--num_proc", "2",
+                               "--force_sync_interval", "4", "--num_thread", "1", "--save_path", str(tmp_path / "o"), "--no_save_emb",
+                               "--log_interval", "1000"])
+    assert out[0]["steps"] == 12 and np.isfinite(out[0]["last_loss"]) and info["n_entities"] <= 50
+    assert not (tmp_path / "o").exists()
+    out, _ = kge_main.main(["--model_name", "DistMult", "--max_step", "20", "--n_entities", "300", "--n_triples", "3000", "--hidden_dim", "8",
+                            "--batch_size", "32", "--neg_sample_size", "8", "--valid", "--eval_interval", "10", "--eval_percent", "0.5",
+                            "--log_interval", "1000"])
+    assert [v["step"] for v in out[0]["valid"]] == [10, 20] and 0 < out[0]["valid"][-1]["MRR"] <= 1
+    import pytest
+    with pytest.raises(SystemExit):
+        kge_main.main(["--pairwise"])
