@@ -53,6 +53,7 @@ class TorchDLRM:
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device)
         self.emb_lr, self.emb_eps, self.emb_optimizer, self.mlp_lr = emb_lr, emb_eps, emb_optimizer, mlp_lr
+        self.loss_function, self.loss_weights = "bce", (1.0, 1.0)     # "bce" | "mse" | "wbce"; set by the driver
         self.autocast = autocast_bf16
         self.owner = [t % world for t in range(self.T)]
         self.local_tables = [t for t in range(self.T) if self.owner[t] == rank]
@@ -209,7 +210,14 @@ class TorchDLRM:
         for p in self.params.values():
             p.grad = None
         logit = self.forward_logits(dense[lo:hi].to(self.device), emb)
-        loss = F.binary_cross_entropy_with_logits(logit, labels[lo:hi].to(self.device), reduction="sum") / self.B
+        y = labels[lo:hi].to(self.device)
+        if self.loss_function == "bce":
+            loss = F.binary_cross_entropy_with_logits(logit, y, reduction="sum") / self.B
+        elif self.loss_function == "mse":                    # on the click probability (dlrm_model.py: loss_fn = MSELoss on sigmoid output)
+            loss = ((torch.sigmoid(logit) - y) ** 2).sum() / self.B
+        else:                                                # "wbce": per-class weights w[0] for label 0, w[1] for label 1
+            w = self.loss_weights[1] * y + self.loss_weights[0] * (1 - y)
+            loss = (w * F.binary_cross_entropy_with_logits(logit, y, reduction="none")).sum() / self.B
         loss.backward()
         with torch.no_grad():
             gemb = self._a2a_bwd(emb.grad)                                           # [B, Tl, D]

@@ -7,7 +7,12 @@ Recognised flags (src/executable/dlrm/dlrm_model.py:618-760): ``--arch-sparse-fe
 --arch-mlp-bot --arch-mlp-top --arch-interaction-op dot|dcn|projection --mini-batch-size --nepochs --num-batches
 --learning-rate --num-indices-per-lookup --num-indices-per-lookup-fixed --data-generation random|synthetic
 --numpy-rand-seed --print-freq --test-freq --test-mini-batch-size --save-model --load-model --use-gpu``, plus
-``--emb-learning-rate --emb-optimizer --zipf-alpha --dcn-layers --dcn-rank``.  The first number of
+``--emb-learning-rate --emb-optimizer --zipf-alpha --dcn-layers --dcn-rank``; further ``--inference-only --data-size
+--max-ind-range --rand-data-dist/-min/-max/-mu/-sigma --round-targets --loss-function bce|mse|wbce --loss-weights
+--loss-threshold --lr-num-warmup-steps --lr-decay-start-step --lr-num-decay-steps --mlperf-acc-threshold
+--enable-profiling --print-time``.  Flags of features this engine does not have (QR / mixed-dimension embeddings,
+quantisation, ONNX export, ``--arch-interaction-itself``, ``--weighted-pooling``) are recognised and refused with a
+message; loader / logging flags of the Criteo pipeline are accepted and have no effect on generated data.  The first number of
 ``--arch-mlp-bot`` is the count of dense features, its last must equal the sparse feature size; the first number of
 ``--arch-mlp-top`` is the interaction width and is checked, as the reference does (:914-951).
 
@@ -63,7 +68,83 @@ def parse_args(argv=None):
     p.add_argument("--use-gpu", action="store_true")
     p.add_argument("--optimizer", default="sgd", choices=["sgd"], help="dense optimizer (the embeddings use --emb-optimizer)")
     p.add_argument("--dist-backend", default="nccl", choices=["nccl"], help="bootstrap backend; the data plane is NVLink peer memory")
-    return p.parse_args(argv)
+    # ---- more of the reference's surface (dlrm_model.py:618-760)
+    p.add_argument("--activation-function", default="relu", choices=["relu"], help="MLP activation (the fused epilogues implement ReLU)")
+    p.add_argument("--arch-interaction-itself", action="store_true", help="not offered: the interaction kernels take the strict lower triangle")
+    p.add_argument("--loss-function", default="bce", choices=["bce", "mse", "wbce"], help="mse / wbce run on the PyTorch path")
+    p.add_argument("--loss-weights", type=lambda v: [float(x) for x in v.split("-")], default=[1.0, 1.0], help="wbce: weight of label 0 - label 1")
+    p.add_argument("--loss-threshold", type=float, default=0.0, help="clamp predictions to [t, 1 - t] when reporting")
+    p.add_argument("--round-targets", action="store_true", help="round the labels to 0 / 1")
+    p.add_argument("--data-size", type=int, default=0, help="samples per epoch when --num-batches is 0")
+    p.add_argument("--rand-data-dist", default="uniform", choices=["uniform", "gaussian"], help="random ids: uniform or clipped gaussian")
+    p.add_argument("--rand-data-min", type=float, default=0.0)
+    p.add_argument("--rand-data-max", type=float, default=1.0)
+    p.add_argument("--rand-data-mu", type=float, default=-1.0)
+    p.add_argument("--rand-data-sigma", type=float, default=1.0)
+    p.add_argument("--max-ind-range", type=int, default=-1, help="cap every table at this many rows")
+    p.add_argument("--inference-only", action="store_true")
+    p.add_argument("--lr-num-warmup-steps", type=int, default=0)
+    p.add_argument("--lr-decay-start-step", type=int, default=0)
+    p.add_argument("--lr-num-decay-steps", type=int, default=0)
+    p.add_argument("--print-time", action="store_true")
+    p.add_argument("--print-wall-time", action="store_true")
+    p.add_argument("--print-precision", type=int, default=5)
+    p.add_argument("--debug-mode", action="store_true")
+    p.add_argument("--local_rank", type=int, default=-1, help="set by launchers; LOCAL_RANK of the environment wins")
+    p.add_argument("--num-workers", type=int, default=0, help="accepted: batches are generated in-process")
+    p.add_argument("--test-num-workers", type=int, default=-1)
+    p.add_argument("--sync-dense-params", type=lambda v: str(v).lower() in ("1", "true", "yes"), default=True,
+                   help="accepted: the dense replicas are always kept identical by the all-reduce")
+    p.add_argument("--weighted-pooling", default=None, choices=[None, "fixed", "learned"], help="not offered: bags are summed")
+    p.add_argument("--enable-profiling", action="store_true", help="stamp the GPU timer at the phase boundaries and print the timeline")
+    p.add_argument("--tensor-board-filename", default="run_kaggle_pt")
+    p.add_argument("--data-set", default="kaggle", help="accepted; data here is generated (--data-generation)")
+    for name in ("--raw-data-file", "--processed-data-file", "--data-trace-file"):
+        p.add_argument(name, default="")
+    for name in ("--data-randomize",):
+        p.add_argument(name, default="total")
+    p.add_argument("--data-sub-sample-rate", type=float, default=0.0)
+    for name in ("--memory-map", "--data-trace-enable-padding", "--dataset-multiprocessing", "--mlperf-logging", "--mlperf-bin-loader",
+                 "--mlperf-bin-shuffle", "--plot-compute-graph", "--save-onnx", "--qr-flag", "--md-flag", "--md-round-dims"):
+        p.add_argument(name, action="store_true")
+    p.add_argument("--mlperf-acc-threshold", type=float, default=0.0, help="stop once the test accuracy reaches this")
+    p.add_argument("--mlperf-auc-threshold", type=float, default=0.0)
+    p.add_argument("--mlperf-grad-accum-iter", type=int, default=1)
+    p.add_argument("--qr-threshold", type=int, default=200)
+    p.add_argument("--qr-operation", default="mult")
+    p.add_argument("--qr-collisions", type=int, default=4)
+    p.add_argument("--md-threshold", type=int, default=200)
+    p.add_argument("--md-temperature", type=float, default=0.3)
+    p.add_argument("--quantize-mlp-with-bit", type=int, default=32)
+    p.add_argument("--quantize-emb-with-bit", type=int, default=32)
+    a = p.parse_args(argv)
+    closed = [n for n, on in (("--arch-interaction-itself", a.arch_interaction_itself), ("--weighted-pooling", a.weighted_pooling),
+                              ("--qr-flag", a.qr_flag), ("--md-flag", a.md_flag), ("--save-onnx", a.save_onnx),
+                              ("--plot-compute-graph", a.plot_compute_graph), ("--mlperf-bin-loader", a.mlperf_bin_loader),
+                              ("--quantize-mlp-with-bit", a.quantize_mlp_with_bit != 32),
+                              ("--quantize-emb-with-bit", a.quantize_emb_with_bit != 32),
+                              ("--mlperf-grad-accum-iter", a.mlperf_grad_accum_iter != 1)) if on]
+    if closed:
+        p.error("not offered by this engine: " + ", ".join(closed))
+    if a.max_ind_range > 0:
+        a.arch_embedding_size = [min(n, a.max_ind_range) for n in a.arch_embedding_size]
+    if a.num_batches <= 0 and a.data_size > 0:
+        a.num_batches = -(-a.data_size // a.mini_batch_size)
+    return a
+
+
+def lr_at(step: int, base: float, warmup: int, decay_start: int, decay_steps: int) -> float:
+    """Learning-rate policy of the reference's driver (dlrm_model.py LRPolicyScheduler): linear warm-up over ``warmup``
+    steps, constant, then a quadratic decay from ``decay_start`` over ``decay_steps`` steps down to a floor of 1e-7."""
+    step += 1
+    if step < warmup:
+        return base * step / warmup
+    end = decay_start + decay_steps
+    if decay_steps > 0 and step >= decay_start:
+        if step >= end:
+            return 1e-7
+        return max(1e-7, base * ((end - step) / decay_steps) ** 2)
+    return base
 
 
 def interaction_width(args) -> int:
@@ -99,6 +180,9 @@ class _CpuModel:
     def predict(self, b):
         return self.m.predict(b.dense, b.ids)
 
+    def set_lr(self, lr):
+        self.m.mlp_lr = lr
+
     def save(self, path, step):
         from recstore_b200.models.checkpoint import save_checkpoint
         save_checkpoint(self.m, path, step)
@@ -122,6 +206,9 @@ class _GpuModel:
     def predict(self, b):
         return self.e.predict(self._pin(b)).float().cpu()
 
+    def set_lr(self, lr):
+        self.e.cfg.mlp_lr = lr                    # read at every launch of the (eager) step
+
     def save(self, path, step):
         self.e.save_checkpoint(path, step)
 
@@ -141,7 +228,14 @@ def run(args) -> dict:
               interaction=args.arch_interaction_op, dcn_layers=args.dcn_layers, dcn_rank=args.dcn_rank)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
+    scheduled = args.lr_num_warmup_steps > 0 or args.lr_num_decay_steps > 0
+    if args.use_gpu and args.loss_function != "bce":
+        sys.exit(f"ERROR: --loss-function {args.loss_function} runs on the PyTorch path only (drop --use-gpu)")
     if args.use_gpu:
+        if scheduled:
+            kw["use_cuda_graph"] = False          # the learning rate is a launch argument: a replayed graph would freeze it
+        if args.enable_profiling:
+            kw["trace_phases"] = True
         from recstore_b200.models.dlrm import DLRM, DLRMConfig
         from recstore_b200.parallel.peer import PeerContext
         local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -160,9 +254,12 @@ def run(args) -> dict:
                                     projection_sizes=tuple(args.interaction_branch_sizes),
                                     projection_hidden=(tuple(args.interaction_branch1_hidden),
                                                        tuple(args.interaction_branch2_hidden)), **kw))
+        model.m.loss_function, model.m.loss_weights = args.loss_function, tuple(args.loss_weights)
     alpha = args.zipf_alpha if args.data_generation == "synthetic" else 0.0
-    src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 1)
-    test_src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 2)
+    gauss = ((args.rand_data_mu, args.rand_data_sigma, args.rand_data_min, args.rand_data_max)
+             if args.data_generation == "random" and args.rand_data_dist == "gaussian" else None)
+    src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 1, gaussian=gauss)
+    test_src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 2, gaussian=gauss)
     step0 = 0
     if args.load_model:
         step0 = int(model.load(args.load_model).get("step", 0))
@@ -170,9 +267,34 @@ def run(args) -> dict:
             print(f"Loaded checkpoint {args.load_model} (step {step0})", flush=True)
     losses, t0, done = [], time.time(), 0
     test_acc = None
+
+    def test_once():
+        tb = test_src.next()
+        lo, hi = (model.rank * (args.mini_batch_size // model.world), (model.rank + 1) * (args.mini_batch_size // model.world))
+        p = model.predict(tb).reshape(-1)
+        if args.loss_threshold > 0:
+            p = p.clamp(args.loss_threshold, 1.0 - args.loss_threshold)
+        return float(((p > 0.5).float() == tb.labels[lo:hi]).float().mean())
+
+    if args.inference_only:
+        accs = [test_once() for _ in range(max(1, args.num_batches))]
+        out = {"steps": 0, "inference_batches": len(accs), "test_accuracy": float(np.mean(accs)),
+               "ms_per_batch": (time.time() - t0) / len(accs) * 1e3}
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        _teardown(args, world)
+        return out
+    stop = False
     for ep in range(args.nepochs):
+        if stop:
+            break
         for j in range(args.num_batches):
             b = src.next()
+            if args.round_targets:
+                b.labels.round_()
+            if scheduled:
+                model.set_lr(lr_at(step0 + done, args.learning_rate, args.lr_num_warmup_steps, args.lr_decay_start_step,
+                                   args.lr_num_decay_steps))
             loss = model.train_step(b)
             losses.append(loss)
             done += 1
@@ -181,25 +303,33 @@ def run(args) -> dict:
                 print(f"Finished training it {j + 1}/{args.num_batches} of epoch {ep}, {el:.2f} ms/it, "
                       f"loss {np.mean(losses[-args.print_freq:]):.6f}", flush=True)
             if args.test_freq and done % args.test_freq == 0:
-                tb = test_src.next()
-                lo, hi = (model.rank * (args.mini_batch_size // model.world), (model.rank + 1) * (args.mini_batch_size // model.world))
-                p = model.predict(tb).reshape(-1)
-                test_acc = float(((p > 0.5).float() == tb.labels[lo:hi]).float().mean())
+                test_acc = test_once()
                 if rank == 0:
                     print(f"Testing at - {done}: accuracy {test_acc * 100:.3f} % (rank 0 share)", flush=True)
+                if args.mlperf_acc_threshold > 0 and test_acc >= args.mlperf_acc_threshold and world == 1:
+                    stop = True                   # the reference's early exit once the accuracy target is met
+                    break
     if args.save_model:
         model.save(args.save_model, step0 + done)
         if rank == 0:
             print(f"Saved checkpoint {args.save_model}", flush=True)
     out = {"steps": done, "first_loss": losses[0] if losses else None, "last_loss": losses[-1] if losses else None,
            "mean_last_10": float(np.mean(losses[-10:])) if losses else None, "test_accuracy": test_acc}
+    if args.print_time or args.print_wall_time:
+        out["ms_per_iteration"] = (time.time() - t0) / max(1, done) * 1e3
+    if args.enable_profiling and args.use_gpu:
+        out["phases_us"] = {k: round(v, 1) for k, v in model.e.phase_times().items()}
     if rank == 0:
         print(json.dumps(out), flush=True)
+    _teardown(args, world)
+    return out
+
+
+def _teardown(args, world):
     if args.use_gpu and world > 1:
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
-    return out
 
 
 def main(argv=None):

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
-from typing import List, Optional, Sequence
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -90,10 +90,13 @@ class DLRMBatch:
 
 
 class DLRMBatchSource:
-    """Generates global batches on the CPU; every rank constructs the same stream from the seed."""
+    """Generates global batches on the CPU; every rank constructs the same stream from the seed.  Ids are Zipf
+    (``alpha``; 0 = uniform) or, with ``gaussian=(mu, sigma, lo, hi)``, a normal draw clipped to ``[lo, hi]`` and scaled
+    to the table (the ``--rand-data-dist gaussian`` generator of the reference's driver, dlrm_data_pytorch.py)."""
 
     def __init__(self, table_rows: Sequence[int], hotness: Sequence[int], batch: int, num_dense: int = 13,
-                 alpha: float = 1.2, seed: int = 0):
+                 alpha: float = 1.2, seed: int = 0, gaussian: Optional[Tuple[float, float, float, float]] = None):
+        self.gaussian = gaussian
         self.table_rows = list(table_rows)
         self.hotness = list(hotness)
         self.batch = batch
@@ -105,5 +108,13 @@ class DLRMBatchSource:
         B = self.batch
         dense = np.log1p(self.rng.exponential(1.0, size=(B, self.num_dense))).astype(np.float32)
         labels = (self.rng.random(B) < 0.25).astype(np.float32)
-        ids = [torch.from_numpy(zipf_ids(B * h, n, self.alpha, self.rng)) for n, h in zip(self.table_rows, self.hotness)]
+        if self.gaussian is not None:
+            mu, sigma, lo, hi = self.gaussian
+            mu = (lo + hi) / 2.0 if mu == -1 else mu
+            ids = []
+            for n, h in zip(self.table_rows, self.hotness):
+                r = np.clip(self.rng.normal(mu, sigma, size=B * h), lo, hi)
+                ids.append(torch.from_numpy(np.minimum((n * (r - lo) / (hi - lo)).astype(np.int64), n - 1)))
+        else:
+            ids = [torch.from_numpy(zipf_ids(B * h, n, self.alpha, self.rng)) for n, h in zip(self.table_rows, self.hotness)]
         return DLRMBatch(torch.from_numpy(dense), ids, torch.from_numpy(labels))

@@ -106,3 +106,27 @@ def test_criteo_parser_random_dataset_and_trace_tools(tmp_path):
         if int(a) in common and common[int(a)] > 0.1:
             assert abs(b - common[int(a)]) < 0.05          # the reuse distribution is reproduced
     assert set(syn.tolist()) <= {1, 2, 3, 4}
+
+
+def test_dlrm_driver_reference_flags():
+    """Learning-rate policy, alternative losses, gaussian ids, inference-only and refused flags of the DLRM driver."""
+    import pytest
+    from recstore_b200.cli import dlrm_main
+    lr = [dlrm_main.lr_at(s, 1.0, 4, 8, 4) for s in range(14)]
+    assert lr[:4] == [0.25, 0.5, 0.75, 1.0] and lr[6] == 1.0                  # warm-up, then constant
+    assert lr[7] == 1.0 and abs(lr[8] - (3 / 4) ** 2) < 1e-12 and lr[10] == (1 / 4) ** 2 and lr[11] == 1e-7 and lr[13] == 1e-7
+    base = ["--arch-embedding-size", "50-30-20", "--arch-sparse-feature-size", "8", "--arch-mlp-bot", "4-16-8", "--mini-batch-size", "64",
+            "--print-freq", "0"]
+    out = dlrm_main.main(base + ["--num-batches", "0", "--data-size", "640", "--loss-function", "wbce", "--loss-weights", "0.5-2.0",
+                                 "--lr-num-warmup-steps", "3", "--lr-decay-start-step", "6", "--lr-num-decay-steps", "4",
+                                 "--rand-data-dist", "gaussian", "--rand-data-sigma", "0.2", "--round-targets", "--print-time",
+                                 "--max-ind-range", "40"])
+    assert out["steps"] == 10 and out["last_loss"] == out["last_loss"] and out["ms_per_iteration"] > 0
+    out = dlrm_main.main(base + ["--num-batches", "5", "--loss-function", "mse"])
+    assert 0 < out["last_loss"] < 1
+    out = dlrm_main.main(base + ["--num-batches", "3", "--inference-only", "--loss-threshold", "0.01"])
+    assert out["steps"] == 0 and out["inference_batches"] == 3 and 0 <= out["test_accuracy"] <= 1
+    with pytest.raises(SystemExit):
+        dlrm_main.main(base + ["--qr-flag"])
+    with pytest.raises(SystemExit):
+        dlrm_main.main(base + ["--quantize-emb-with-bit", "8"])
