@@ -316,6 +316,7 @@ class DLRM:
         self.s_wgrad2 = torch.cuda.Stream(device=dev)  # weight gradients of the bottom MLP
         self.s_col = torch.cuda.Stream(device=dev)     # bias gradients (column sums): bandwidth-bound, beside the wgrad GEMMs
         self._phase_names: List[str] = []
+        self._no_stamp = False
         self._phase_buf = torch.zeros(64, dtype=torch.int64, device=dev)
         self._warm_native()
         torch.cuda.synchronize(dev)
@@ -355,7 +356,7 @@ class DLRM:
 
     def _stamp(self, name: str):
         """Phase boundary: with ``trace_phases`` a one-thread kernel stores the GPU timer here (also inside the graph)."""
-        if not self.cfg.trace_phases:
+        if not self.cfg.trace_phases or self._no_stamp:
             return
         if name not in self._phase_names:
             self._phase_names.append(name)
@@ -651,7 +652,11 @@ class DLRM:
         with torch.cuda.stream(self.compute_stream):
             self.in_dense[0].copy_(batch.dense, non_blocking=True)
             self.in_ids[0].copy_(batch.ids, non_blocking=True)
-            x = self._forward(0)
+            self._no_stamp = True          # the phase stamps describe the last training step, not an inference pass
+            try:
+                x = self._forward(0)
+            finally:
+                self._no_stamp = False
             F_.head_bce(x, self.head_w, self.head_b, None, 1.0 / self.B, prob=self.prob)
             if self.world > 1:
                 self.ctx.barrier(CH_MISC)  # nobody may overwrite the interaction buffer before all have read it
