@@ -48,13 +48,48 @@ def _cuda_home() -> Path:
 
 
 PRELOAD_DIR = CSRC / "preload"          # LD_PRELOAD shims: one small library each, never part of the main one
+STRESS_DIR = CSRC / "stress"            # stand-alone drivers (their own main), built on demand with a sanitizer
 UVM_SHIM_PATH = PKG_DIR / "lib" / "librecstore_uvm_intercept.so"
 
 
 def _sources():
-    cu = sorted(p for p in CSRC.rglob("*.cu") if PRELOAD_DIR not in p.parents)
-    cpp = sorted(p for p in CSRC.rglob("*.cpp") if PRELOAD_DIR not in p.parents)
+    skip = (PRELOAD_DIR, STRESS_DIR)
+    cu = sorted(p for p in CSRC.rglob("*.cu") if not any(d in p.parents for d in skip))
+    cpp = sorted(p for p in CSRC.rglob("*.cpp") if not any(d in p.parents for d in skip))
     return cu, cpp
+
+
+def build_host_stress(sanitize: str = "thread", out_dir: Path | None = None, verbose: bool = False) -> Path:
+    """Builds ``csrc/stress/host_stress.cpp`` together with the host runtime (``csrc/runtime``, ``csrc/common``: no
+    CUDA kernels) into one executable under ``-fsanitize=<sanitize>`` ("thread", "address" or "" for none).  The CUDA
+    runtime is linked for the symbols the allocator files name; the driver never calls into it."""
+    cuda = _cuda_home()
+    cxx = os.environ.get("CXX", "g++")
+    if sanitize:                     # not every toolchain ships the sanitizer runtimes: take the first compiler that has this one
+        rt = {"thread": "libtsan.so", "address": "libasan.so", "undefined": "libubsan.so"}.get(sanitize)
+        for cand in dict.fromkeys([cxx, "g++", "/usr/bin/g++"]):
+            if shutil.which(cand) is None:
+                continue
+            found = subprocess.run([cand, "-print-file-name=" + (rt or "libc.so")], stdout=subprocess.PIPE, text=True).stdout.strip()
+            if rt is None or os.path.isabs(found):
+                cxx = cand
+                break
+        else:
+            raise RuntimeError(f"no compiler with the {sanitize} sanitizer runtime was found")
+    out_dir = Path(out_dir) if out_dir is not None else PKG_DIR / "lib"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    exe = out_dir / ("host_stress_" + (sanitize or "plain"))
+    srcs = sorted((CSRC / "runtime").glob("*.cpp")) + sorted((CSRC / "common").glob("*.cpp")) + [STRESS_DIR / "host_stress.cpp"]
+    cmd = [cxx, "-O1", "-g", "-std=c++17", "-pthread", "-fno-omit-frame-pointer", "-I", str(CSRC), "-I", str(cuda / "include")]
+    if sanitize:
+        cmd += ["-fsanitize=" + sanitize]
+    cmd += [str(s) for s in srcs] + ["-o", str(exe), "-L", str(cuda / "lib64"), "-lcudart", "-lrt", "-ldl",
+                                     "-Wl,-rpath," + str(cuda / "lib64")]
+    rc, out = _run(cmd, verbose)
+    if rc != 0:
+        print(out, file=sys.stderr)
+        raise RuntimeError("building the host stress driver failed")
+    return exe
 
 
 def build_preload_shims(verbose: bool = False) -> Path:

@@ -1,0 +1,233 @@
+// Multi-threaded stress driver of the host runtime, meant to be built with -fsanitize=thread (or address) and run
+// without Python: every component that owns threads or is called from several threads is driven through its C entry
+// points, with the same invariants the Python tests check.
+//
+//   1. KV engines: N threads of mixed batch gets / puts on Zipf keys (rs_kv_benchmark), then the engine's own
+//      consistency check.
+//   2. Parameter server: a loopback server and several client threads putting, getting and updating overlapping keys.
+//   3. Lookahead controller: "ranks" as threads sharing one controller (the layout of the reference's
+//      VirtualEnvironment test, src/framework_test), background flush threads on, the read-your-updates contract
+//      checked at every step against a synchronous oracle.
+//
+// Exit code 0 and a final "host_stress: ok" line mean that no invariant broke; a sanitizer report makes the process
+// exit non-zero by itself (TSAN_OPTIONS=halt_on_error=1 exitcode=66 is set by the test that runs it).
+#include <atomic>
+#include <cmath>
+#include <condition_variable>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+extern "C" {
+int rs_kv_create(const char* engine, const char* json_config, void** out);
+int rs_kv_destroy(void* h);
+int rs_kv_check_consistency(void* h, int* ok);
+unsigned long long rs_kv_size(void* h);
+int rs_kv_benchmark(void* handle, int threads, double seconds, int batch, double zipf_alpha, double read_ratio,
+                    unsigned long long key_space, unsigned long long seed, double* out);
+int rs_ps_create(const char* engine, const char* json, void** out);
+int rs_ps_destroy(void* ps);
+int rs_ps_server_start(void* ps, int port, void** server_out, int* port_out);
+int rs_ps_server_stop(void* server);
+int rs_ps_client_connect(const char* host, int port, void** out);
+int rs_ps_client_close(void* c);
+int rs_ps_client_get(void* c, const unsigned long long* keys, long long n, int dim, float* out, unsigned char* found, int max_per_req);
+int rs_ps_client_put(void* c, const unsigned long long* keys, long long n, int dim, const float* values, int max_per_req);
+int rs_ctrl_create(const char* json, void** out);
+int rs_ctrl_destroy(void* c);
+int rs_ctrl_register_table(void* c, float* table, long long rows);
+int rs_ctrl_register_cache(void* c, int rank, float* cache);
+int rs_ctrl_start(void* c);
+int rs_ctrl_stop(void* c);
+int rs_ctrl_drain(void* c);
+int rs_ctrl_publish_reads(void* c, int rank, long long step, const long long* ids, long long n);
+int rs_ctrl_set_step_input(void* c, int rank, const long long* keys, long long n, const float* grads);
+int rs_ctrl_process_one_step(void* c, long long step);
+int rs_ctrl_block_to_step(void* c, long long step, int timeout_ms);
+long long rs_ctrl_pending(void* c);
+const char* rs_last_error();
+}
+
+namespace {
+
+int g_failures = 0;
+std::mutex g_fail_mu;
+
+void fail(const char* what, const std::string& detail = "") {
+  std::lock_guard<std::mutex> l(g_fail_mu);
+  ++g_failures;
+  std::fprintf(stderr, "host_stress: FAIL %s %s (%s)\n", what, detail.c_str(), rs_last_error());
+}
+#define EXPECT_OK(call) do { if ((call) != 0) fail(#call); } while (0)
+
+// Reusable barrier for the rank threads (std::barrier is C++20).
+class Barrier {
+ public:
+  explicit Barrier(int n) : n_(n) {}
+  void wait() {
+    std::unique_lock<std::mutex> l(mu_);
+    const long gen = gen_;
+    if (++count_ == n_) { count_ = 0; ++gen_; cv_.notify_all(); return; }
+    cv_.wait(l, [&] { return gen_ != gen; });
+  }
+ private:
+  std::mutex mu_;
+  std::condition_variable cv_;
+  int n_, count_ = 0;
+  long gen_ = 0;
+};
+
+struct Lcg {
+  unsigned long long s;
+  explicit Lcg(unsigned long long seed) : s(seed * 6364136223846793005ull + 1442695040888963407ull) {}
+  unsigned long long next() { s = s * 6364136223846793005ull + 1442695040888963407ull; return s >> 17; }
+};
+
+void stress_kv(const char* engine, const char* json) {
+  void* kv = nullptr;
+  if (rs_kv_create(engine, json, &kv) != 0) { fail("rs_kv_create", engine); return; }
+  double out[8];
+  EXPECT_OK(rs_kv_benchmark(kv, 6, 0.3, 64, 0.99, 0.5, 20000, 7, out));
+  int ok = 1;
+  if (rs_kv_check_consistency(kv, &ok) == 0 && !ok) fail("kv consistency", engine);   // non-zero: the engine has no checker
+  std::printf("host_stress: kv %-12s get %.2f Mkv/s put %.2f Mkv/s size %llu\n", engine, out[0], out[1], rs_kv_size(kv));
+  EXPECT_OK(rs_kv_destroy(kv));
+}
+
+void stress_ps() {
+  constexpr int kDim = 8, kClients = 4, kRounds = 60, kKeys = 48;
+  void* ps = nullptr;
+  void* server = nullptr;
+  int port = 0;
+  if (rs_ps_create("KVEngineMap", "{\"capacity\": 65536, \"dim\": 8}", &ps) != 0) { fail("rs_ps_create"); return; }
+  if (rs_ps_server_start(ps, 0, &server, &port) != 0) { fail("rs_ps_server_start"); rs_ps_destroy(ps); return; }
+  std::vector<std::thread> ts;
+  for (int c = 0; c < kClients; ++c) {
+    ts.emplace_back([&, c] {
+      void* cl = nullptr;
+      if (rs_ps_client_connect("127.0.0.1", port, &cl) != 0) { fail("rs_ps_client_connect"); return; }
+      Lcg rng(100 + c);
+      std::vector<unsigned long long> keys(kKeys);
+      std::vector<float> vals(kKeys * kDim), got(kKeys * kDim);
+      std::vector<unsigned char> found(kKeys);
+      for (int r = 0; r < kRounds; ++r) {
+        // own keys (exact read-back) interleaved with keys every client writes (same value from everybody)
+        for (int i = 0; i < kKeys; ++i) {
+          const bool shared = (i & 1) != 0;
+          keys[i] = shared ? 1000000ull + rng.next() % 64 : static_cast<unsigned long long>(c) * 10000 + rng.next() % 512;
+          for (int d = 0; d < kDim; ++d) vals[i * kDim + d] = shared ? static_cast<float>(keys[i] % 97) : static_cast<float>(keys[i] + d);
+        }
+        EXPECT_OK(rs_ps_client_put(cl, keys.data(), kKeys, kDim, vals.data(), 16));
+        EXPECT_OK(rs_ps_client_get(cl, keys.data(), kKeys, kDim, got.data(), found.data(), 16));
+        for (int i = 0; i < kKeys; ++i) {
+          if (!found[i] || std::memcmp(&got[i * kDim], &vals[i * kDim], kDim * sizeof(float)) != 0) {
+            fail("ps read-back", "client " + std::to_string(c) + " round " + std::to_string(r));
+            break;
+          }
+        }
+      }
+      EXPECT_OK(rs_ps_client_close(cl));
+    });
+  }
+  for (auto& t : ts) t.join();
+  EXPECT_OK(rs_ps_server_stop(server));
+  EXPECT_OK(rs_ps_destroy(ps));
+  std::printf("host_stress: ps %d clients x %d rounds\n", kClients, kRounds);
+}
+
+void stress_controller(const char* mode) {
+  constexpr int kRanks = 4, kRows = 2000, kDim = 8, kL = 5, kSteps = 30, kPer = 64;
+  const float clr = 0.5f;
+  const int cache_rows = kRows / 20;
+  char json[512];
+  std::snprintf(json, sizeof(json),
+                "{\"num_gpus\": %d, \"L\": %d, \"clr\": %f, \"dim\": %d, \"backwardMode\": \"%s\", \"nr_background_threads\": 2, "
+                "\"full_emb_capacity\": %d, \"cache_ratio\": 0.05}", kRanks, kL, clr, kDim, mode, kRows);
+  void* ctrl = nullptr;
+  if (rs_ctrl_create(json, &ctrl) != 0) { fail("rs_ctrl_create", mode); return; }
+  std::vector<float> table(static_cast<size_t>(kRows) * kDim, 0.f), oracle(table);
+  std::vector<std::vector<float>> caches(kRanks, std::vector<float>(static_cast<size_t>(cache_rows) * kDim, 0.f));
+  EXPECT_OK(rs_ctrl_register_table(ctrl, table.data(), kRows));
+  for (int r = 0; r < kRanks; ++r) EXPECT_OK(rs_ctrl_register_cache(ctrl, r, caches[r].data()));
+  EXPECT_OK(rs_ctrl_start(ctrl));
+  const bool async = std::strncmp(mode, "CppAsync", 8) == 0;
+  // batches[r][s]: ids rank r reads at step s, drawn up front; reads are published kL steps ahead
+  std::vector<std::vector<std::vector<long long>>> batches(kRanks);
+  for (int r = 0; r < kRanks; ++r) {
+    Lcg rng(3000 + r);
+    batches[r].resize(kSteps + kL);
+    for (auto& b : batches[r]) { b.resize(kPer); for (auto& id : b) id = static_cast<long long>(rng.next() % kRows); }
+    if (async) for (int s = 0; s < kL; ++s) EXPECT_OK(rs_ctrl_publish_reads(ctrl, r, s, batches[r][s].data(), kPer));
+  }
+  Barrier bar(kRanks);
+  std::vector<std::vector<float>> grads(kRanks, std::vector<float>(static_cast<size_t>(kPer) * kDim));
+  std::atomic<int> mismatches{0};
+  std::vector<std::thread> ts;
+  for (int r = 0; r < kRanks; ++r) {
+    ts.emplace_back([&, r] {
+      for (int step = 0; step < kSteps; ++step) {
+        if (async) EXPECT_OK(rs_ctrl_publish_reads(ctrl, r, step + kL, batches[r][step + kL].data(), kPer));
+        const auto& ids = batches[r][step];
+        for (int i = 0; i < kPer; ++i) {                      // read through the cache placement: first rows live in the caches
+          const long long id = ids[i];
+          const float* row = id < static_cast<long long>(cache_rows) * kRanks
+                                 ? &caches[id / cache_rows][static_cast<size_t>(id % cache_rows) * kDim]
+                                 : &table[static_cast<size_t>(id) * kDim];
+          for (int d = 0; d < kDim; ++d)
+            if (std::fabs(row[d] - oracle[static_cast<size_t>(id) * kDim + d]) > 1e-4f) { mismatches.fetch_add(1); break; }
+        }
+        const float g = static_cast<float>(r + 1) * static_cast<float>(1 + step % 3);
+        std::fill(grads[r].begin(), grads[r].end(), g);
+        EXPECT_OK(rs_ctrl_set_step_input(ctrl, r, ids.data(), kPer, grads[r].data()));
+        bar.wait();
+        if (r == 0) {
+          EXPECT_OK(rs_ctrl_process_one_step(ctrl, step));
+          for (int rr = 0; rr < kRanks; ++rr)                 // synchronous oracle
+            for (int i = 0; i < kPer; ++i)
+              for (int d = 0; d < kDim; ++d)
+                oracle[static_cast<size_t>(batches[rr][step][i]) * kDim + d] -= clr * grads[rr][static_cast<size_t>(i) * kDim + d];
+          EXPECT_OK(rs_ctrl_block_to_step(ctrl, step + 1, 60000));
+        }
+        bar.wait();
+      }
+    });
+  }
+  for (auto& t : ts) t.join();
+  EXPECT_OK(rs_ctrl_drain(ctrl));
+  EXPECT_OK(rs_ctrl_stop(ctrl));
+  if (rs_ctrl_pending(ctrl) != 0) fail("controller pending after drain", mode);
+  if (mismatches.load() != 0) fail("controller read-your-updates", std::string(mode) + ": " + std::to_string(mismatches.load()) + " stale reads");
+  for (int id = 0; id < kRows; ++id) {
+    const float* row = id < cache_rows * kRanks ? &caches[id / cache_rows][static_cast<size_t>(id % cache_rows) * kDim]
+                                                : &table[static_cast<size_t>(id) * kDim];
+    if (std::fabs(row[0] - oracle[static_cast<size_t>(id) * kDim]) > 1e-3f) { fail("controller final table", mode); break; }
+  }
+  EXPECT_OK(rs_ctrl_destroy(ctrl));
+  std::printf("host_stress: controller %s, %d ranks x %d steps\n", mode, kRanks, kSteps);
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  const std::string only = argc > 1 ? argv[1] : "all";
+  if (only == "all" || only == "kv") {
+    stress_kv("KVEngineMap", "{\"capacity\": 65536, \"value_size\": 32}");
+    stress_kv("KVEngineExtendibleHash", "{\"capacity\": 65536, \"value_size\": 32}");
+    stress_kv("KVEngineChunkHash", "{\"capacity\": 65536, \"value_size\": 32}");
+  }
+  if (only == "all" || only == "ps") stress_ps();
+  if (only == "all" || only == "controller") {
+    stress_controller("CppSync");
+    stress_controller("CppAsyncV2");
+  }
+  if (g_failures) {
+    std::fprintf(stderr, "host_stress: %d failure(s)\n", g_failures);
+    return 1;
+  }
+  std::printf("host_stress: ok\n");
+  return 0;
+}

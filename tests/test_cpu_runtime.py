@@ -252,3 +252,22 @@ def test_renumbering_narrow_and_zipf_filler():
     t = torch.empty(10000, dtype=torch.int64)
     torch_op.ZipfianTorchFiller(1000, 0.99).fillArrayTorch(t)
     assert t.min() >= 1 and t.max() <= 1000 and (t <= 10).float().mean() > 0.2
+
+
+def test_host_runtime_under_thread_sanitizer(tmp_path):
+    """The host runtime (KV engines, parameter server + clients, lookahead controller with its background threads) built
+    with -fsanitize=thread and driven from several threads by the stand-alone stress driver: no data race report, no
+    broken invariant."""
+    import os
+    import subprocess
+    import pytest
+    from recstore_b200.build import build_host_stress
+    try:
+        exe = build_host_stress("thread", out_dir=tmp_path)
+    except RuntimeError as e:
+        if "sanitizer runtime" in str(e):
+            pytest.skip(str(e))
+        raise
+    env = dict(os.environ, TSAN_OPTIONS="halt_on_error=1 exitcode=66 report_signal_unsafe=0")
+    p = subprocess.run([str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
+    assert p.returncode == 0 and "host_stress: ok" in p.stdout and "ThreadSanitizer" not in p.stdout, p.stdout[-3000:]
