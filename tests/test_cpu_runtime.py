@@ -254,20 +254,22 @@ def test_renumbering_narrow_and_zipf_filler():
     assert t.min() >= 1 and t.max() <= 1000 and (t <= 10).float().mean() > 0.2
 
 
-def test_host_runtime_under_thread_sanitizer(tmp_path):
+@pytest.mark.parametrize("sanitizer", ["thread", "address"])
+def test_host_runtime_under_thread_sanitizer(tmp_path, sanitizer):
     """The host runtime (KV engines, parameter server + clients, lookahead controller with its background threads) built
-    with -fsanitize=thread and driven from several threads by the stand-alone stress driver: no data race report, no
-    broken invariant."""
+    with -fsanitize=thread / address (+ leak check) and driven from several threads by the stand-alone stress driver: no
+    sanitizer report, no broken invariant."""
     import os
     import subprocess
     import pytest
     from recstore_b200.build import build_host_stress
     try:
-        exe = build_host_stress("thread", out_dir=tmp_path)
+        exe = build_host_stress(sanitizer, out_dir=tmp_path)
     except RuntimeError as e:
         if "sanitizer runtime" in str(e):
             pytest.skip(str(e))
         raise
-    env = dict(os.environ, TSAN_OPTIONS="halt_on_error=1 exitcode=66 report_signal_unsafe=0")
+    env = dict(os.environ, TSAN_OPTIONS="halt_on_error=1 exitcode=66 report_signal_unsafe=0",
+               ASAN_OPTIONS="detect_leaks=1 exitcode=67")
     p = subprocess.run([str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
-    assert p.returncode == 0 and "host_stress: ok" in p.stdout and "ThreadSanitizer" not in p.stdout, p.stdout[-3000:]
+    assert p.returncode == 0 and "host_stress: ok" in p.stdout and "Sanitizer" not in p.stdout, p.stdout[-3000:]
