@@ -29,7 +29,7 @@ struct Series {
   bool is_time;  // nanoseconds (timers) or plain values (counters)
   struct Shard {
     std::atomic<uint64_t> n{0};
-    double ring[kRing];
+    std::atomic<double> ring[kRing];   // written by recorders (threads may share a shard), read by the reporter: relaxed atomics
   };
   Shard shards[kShards];
   std::atomic<uint64_t> count{0};
@@ -40,7 +40,7 @@ struct Series {
     static thread_local int shard = static_cast<int>(std::hash<std::thread::id>()(std::this_thread::get_id()) % kShards);
     Shard& s = shards[shard];
     const uint64_t i = s.n.fetch_add(1, std::memory_order_relaxed);
-    s.ring[i % kRing] = v;
+    s.ring[i % kRing].store(v, std::memory_order_relaxed);
     count.fetch_add(1, std::memory_order_relaxed);
     double old = sum.load(std::memory_order_relaxed);
     while (!sum.compare_exchange_weak(old, old + v, std::memory_order_relaxed)) {}
@@ -50,7 +50,7 @@ struct Series {
     out->clear();
     for (const Shard& s : shards) {
       const uint64_t n = std::min<uint64_t>(s.n.load(), kRing);
-      for (uint64_t i = 0; i < n; ++i) out->push_back(s.ring[i]);
+      for (uint64_t i = 0; i < n; ++i) out->push_back(s.ring[i].load(std::memory_order_relaxed));
     }
   }
 };

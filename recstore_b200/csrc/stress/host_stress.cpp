@@ -5,7 +5,9 @@
 //   1. KV engines: N threads of mixed batch gets / puts on Zipf keys (rs_kv_benchmark), then the engine's own
 //      consistency check.
 //   2. Parameter server: a loopback server and several client threads putting, getting and updating overlapping keys.
-//   3. Lookahead controller: "ranks" as threads sharing one controller (the layout of the reference's
+//   3. Allocators (pool / binning / fixed length on pageable host memory), the timer registry with its report thread,
+//      and the shared-memory barrier, each hit from several threads.
+//   4. Lookahead controller: "ranks" as threads sharing one controller (the layout of the reference's
 //      VirtualEnvironment test, src/framework_test), background flush threads on, the read-your-updates contract
 //      checked at every step against a synchronous oracle.
 //
@@ -49,6 +51,22 @@ int rs_ctrl_set_step_input(void* c, int rank, const long long* keys, long long n
 int rs_ctrl_process_one_step(void* c, long long step);
 int rs_ctrl_block_to_step(void* c, long long step, int timeout_ms);
 long long rs_ctrl_pending(void* c);
+int rs_devpool_create(int kind, int backing, size_t initial_bytes, size_t max_bytes, size_t param, void** out);
+int rs_devpool_destroy(void* h);
+int rs_devpool_alloc(void* h, size_t bytes, void** out);
+int rs_devpool_free(void* h, void* p);
+int rs_devpool_stats(void* h, unsigned long long* out6);
+void rs_timer_record_ns(const char* name, double ns);
+void rs_counter_record(const char* name, double v);
+int rs_series_stats(const char* name, double* out5);
+int rs_report_thread_start(int period_ms);
+int rs_report_thread_stop();
+void rs_timers_clear();
+int rs_shm_set_namespace(const char* ns);
+int rs_barrier_create(const char* name, int parties, void** out_handle);
+int rs_barrier_wait(void* handle, int timeout_ms);
+int rs_barrier_close(void* handle);
+int rs_barrier_unlink(const char* name);
 const char* rs_last_error();
 }
 
@@ -139,6 +157,85 @@ void stress_ps() {
   std::printf("host_stress: ps %d clients x %d rounds\n", kClients, kRounds);
 }
 
+// Every thread allocates blocks of random sizes, fills each with its own tag, checks the tags before freeing: an
+// allocator that hands one byte to two owners, or corrupts its free lists under contention, shows up as a wrong tag.
+void stress_allocator(int kind, const char* name) {
+  constexpr int kThreads = 6, kRounds = 400, kLive = 24;
+  void* pool = nullptr;
+  if (rs_devpool_create(kind, 2, size_t{1} << 20, size_t{256} << 20, kind == 2 ? 4096 : (size_t{1} << 16), &pool) != 0) {
+    fail("rs_devpool_create", name);
+    return;
+  }
+  std::atomic<int> bad{0};
+  std::vector<std::thread> ts;
+  for (int t = 0; t < kThreads; ++t) {
+    ts.emplace_back([&, t] {
+      Lcg rng(500 + t);
+      struct Block { unsigned char* p; size_t n; unsigned char tag; };
+      std::vector<Block> live;
+      for (int r = 0; r < kRounds; ++r) {
+        if (live.size() < static_cast<size_t>(kLive) && (rng.next() & 3) != 0) {
+          const size_t n = kind == 2 ? 4096 : 16 + rng.next() % 30000;
+          void* p = nullptr;
+          if (rs_devpool_alloc(pool, n, &p) != 0 || p == nullptr) { bad.fetch_add(1); continue; }
+          const unsigned char tag = static_cast<unsigned char>(1 + (t * 37 + r) % 250);
+          std::memset(p, tag, n);
+          live.push_back({static_cast<unsigned char*>(p), n, tag});
+        } else if (!live.empty()) {
+          const size_t i = rng.next() % live.size();
+          const Block b = live[i];
+          if (b.p[0] != b.tag || b.p[b.n / 2] != b.tag || b.p[b.n - 1] != b.tag) bad.fetch_add(1);
+          if (rs_devpool_free(pool, b.p) != 0) bad.fetch_add(1);
+          live[i] = live.back();
+          live.pop_back();
+        }
+      }
+      for (const Block& b : live) {
+        if (b.p[0] != b.tag || b.p[b.n - 1] != b.tag) bad.fetch_add(1);
+        if (rs_devpool_free(pool, b.p) != 0) bad.fetch_add(1);
+      }
+    });
+  }
+  for (auto& t : ts) t.join();
+  unsigned long long st[6] = {0, 0, 0, 0, 0, 0};
+  EXPECT_OK(rs_devpool_stats(pool, st));
+  if (bad.load() != 0) fail("allocator blocks", std::string(name) + ": " + std::to_string(bad.load()) + " bad blocks");
+  EXPECT_OK(rs_devpool_destroy(pool));
+  std::printf("host_stress: allocator %s, %d threads x %d rounds\n", name, kThreads, kRounds);
+}
+
+void stress_timers_and_barrier() {
+  constexpr int kThreads = 4, kRounds = 200;
+  rs_timers_clear();
+  EXPECT_OK(rs_report_thread_start(5));
+  char ns[64];
+  std::snprintf(ns, sizeof(ns), "rs_stress_%d", static_cast<int>(std::rand()));
+  EXPECT_OK(rs_shm_set_namespace(ns));
+  std::vector<void*> handles(kThreads, nullptr);
+  for (int t = 0; t < kThreads; ++t) EXPECT_OK(rs_barrier_create("stress_barrier", kThreads, &handles[t]));
+  std::atomic<int> arrived{0}, out_of_step{0};
+  std::vector<std::thread> ts;
+  for (int t = 0; t < kThreads; ++t) {
+    ts.emplace_back([&, t] {
+      for (int r = 0; r < kRounds; ++r) {
+        rs_timer_record_ns("stress.timer", 100.0 + r);
+        rs_counter_record(t & 1 ? "stress.odd" : "stress.even", 1.0);
+        arrived.fetch_add(1);
+        if (rs_barrier_wait(handles[t], 20000) != 0) { fail("rs_barrier_wait"); return; }
+        if (arrived.load() < (r + 1) * kThreads) out_of_step.fetch_add(1);     // nobody leaves before everybody arrived
+      }
+    });
+  }
+  for (auto& t : ts) t.join();
+  EXPECT_OK(rs_report_thread_stop());
+  double st[5] = {0, 0, 0, 0, 0};
+  EXPECT_OK(rs_series_stats("stress.timer", st));
+  if (out_of_step.load() != 0) fail("barrier released early");
+  for (int t = 0; t < kThreads; ++t) EXPECT_OK(rs_barrier_close(handles[t]));
+  EXPECT_OK(rs_barrier_unlink("stress_barrier"));
+  std::printf("host_stress: timers + barrier, %d threads x %d rounds\n", kThreads, kRounds);
+}
+
 void stress_controller(const char* mode) {
   constexpr int kRanks = 4, kRows = 2000, kDim = 8, kL = 5, kSteps = 30, kPer = 64;
   const float clr = 0.5f;
@@ -220,6 +317,12 @@ int main(int argc, char** argv) {
     stress_kv("KVEngineChunkHash", "{\"capacity\": 65536, \"value_size\": 32}");
   }
   if (only == "all" || only == "ps") stress_ps();
+  if (only == "all" || only == "alloc") {
+    stress_allocator(0, "pool");
+    stress_allocator(1, "binning");
+    stress_allocator(2, "fixed");
+  }
+  if (only == "all" || only == "misc") stress_timers_and_barrier();
   if (only == "all" || only == "controller") {
     stress_controller("CppSync");
     stress_controller("CppAsyncV2");
