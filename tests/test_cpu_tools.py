@@ -85,3 +85,14 @@ def test_uvm_interposer_exports_and_falls_back_without_cuda():
     out = (C.c_ulonglong * 3)()
     lib.rs_uvm_intercept_stats(out)
     assert out[0] >= 1
+
+
+def test_uvm_baseline_trainer_runs_under_the_interposer():
+    """The unified-memory baseline re-executes itself with the shim preloaded; on a host without a GPU the shim is
+    loaded (its statistics symbol resolves) and simply sees no device allocation."""
+    from recstore_b200.baseline import uvm_trainer
+    r = uvm_trainer.main(["--vocab_size", "2000", "--embed_size", "8", "--batch_size", "128", "--sample_number", "4", "--device", "cpu"])
+    assert r["uvm"] is True and r["intercepted"]["cudaMalloc_calls"] == 0 and r["ms_per_step"] > 0
+    r = uvm_trainer.main(["--vocab_size", "2000", "--embed_size", "8", "--batch_size", "128", "--sample_number", "4", "--device", "cpu",
+                          "--no_uvm"])
+    assert r["uvm"] is False and r["intercepted"] is None

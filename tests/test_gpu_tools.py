@@ -62,3 +62,15 @@ def test_engine_checkpoint_loads_into_pytorch_restatement_and_back(tmp_path):
     eng2.load_checkpoint(str(tmp_path / "ck"))
     p2 = eng2.predict(eng2.make_pinned_batch(b.dense, b.ids, b.labels)).float().view(-1)
     assert torch.equal(p_eng, p2)
+
+
+def test_uvm_baseline_trainer_allocates_managed_memory():
+    """Under the interposer the trainer's device allocations (the embedding table among them) become managed memory and
+    training still runs; without it nothing is redirected."""
+    from recstore_b200.baseline import uvm_trainer
+    args = ["--vocab_size", "200000", "--embed_size", "32", "--batch_size", "4096", "--sample_number", "5"]
+    r = uvm_trainer.main(args)
+    assert r["device"].startswith("cuda") and r["uvm"] is True
+    assert r["intercepted"]["made_managed"] > 0 and r["intercepted"]["bytes"] >= 200000 * 32 * 4
+    r0 = uvm_trainer.main(args + ["--no_uvm"])
+    assert r0["uvm"] is False and abs(r0["first_loss"] - r["first_loss"]) < 1e-3 * max(1.0, abs(r["first_loss"]))
