@@ -46,6 +46,60 @@ def read_binary_trace(path: str) -> List[np.ndarray]:
     return out
 
 
+VALID_TRACE_DIMS = (4, 8, 16, 32, 64)
+
+
+def _read_trace_records(path: str):
+    """Requests of a binary trace as structured arrays with ``key`` and ``dim`` fields."""
+    raw = np.fromfile(path, dtype=np.uint8)
+    nreq = int(raw[:4].view("<i4")[0])
+    rec = np.dtype([("key", "<u8"), ("dim", "<i4")])
+    o, out = 4, []
+    for _ in range(nreq):
+        n = int(raw[o:o + 4].view("<i4")[0]); o += 4
+        out.append(raw[o:o + n * rec.itemsize].view(rec).copy()); o += n * rec.itemsize
+    if o != raw.size:
+        raise ValueError(f"{path}: {raw.size - o} trailing bytes after {nreq} requests")
+    return out
+
+
+def renumber_trace(in_path: str, out_path: str) -> int:
+    """Rewrites a binary trace with dense keys ``0..n_unique-1`` in order of first appearance and returns ``n_unique``;
+    every record's dim must be one of 4, 8, 16, 32, 64 (the reference's tool: src/benchmark/dataset_renumbering.cc:24-80)."""
+    reqs = _read_trace_records(in_path)
+    if not reqs:
+        write_binary_trace(out_path, [])
+        return 0
+    allrec = np.concatenate(reqs)
+    bad = ~np.isin(allrec["dim"], VALID_TRACE_DIMS)
+    if bad.any():
+        raise ValueError(f"{in_path}: record {int(np.nonzero(bad)[0][0])} has dim {int(allrec['dim'][bad][0])}, expected one of {VALID_TRACE_DIMS}")
+    uniq, first, inv = np.unique(allrec["key"], return_index=True, return_inverse=True)
+    rank = np.empty(uniq.size, dtype=np.uint64)
+    rank[np.argsort(first, kind="stable")] = np.arange(uniq.size, dtype=np.uint64)      # order of first appearance
+    new = rank[inv]
+    with open(out_path, "wb") as f:
+        f.write(np.int32(len(reqs)).tobytes())
+        o = 0
+        for r in reqs:
+            f.write(np.int32(r.size).tobytes())
+            out = r.copy()
+            out["key"] = new[o:o + r.size]
+            o += r.size
+            f.write(out.tobytes())
+    return int(uniq.size)
+
+
+def trace_wordcount(path: str):
+    """Keys of a binary trace with how often each is requested, most frequent first (dataset_wordcount.cc of the reference)."""
+    reqs = _read_trace_records(path)
+    if not reqs:
+        return np.zeros(0, dtype=np.int64), np.zeros(0, dtype=np.int64)
+    keys, counts = np.unique(np.concatenate(reqs)["key"], return_counts=True)
+    order = np.argsort(-counts, kind="stable")
+    return keys[order].astype(np.int64), counts[order].astype(np.int64)
+
+
 class DatasetReplay:
     def __init__(self, path: str, offsets_path: Optional[str] = None, loop: bool = True):
         self.loop = loop
@@ -151,3 +205,23 @@ class PoissonLoadGenerator:
                 close()
         self._clients = []
         return rep
+
+
+def _main(argv=None):
+    """``python -m recstore_b200.ps.load_generator renumber IN OUT`` / ``wordcount IN [TOP]``."""
+    import argparse
+    import json
+    p = argparse.ArgumentParser(description="binary PS trace tools")
+    sub = p.add_subparsers(dest="cmd", required=True)
+    r = sub.add_parser("renumber"); r.add_argument("src"); r.add_argument("dst")
+    w = sub.add_parser("wordcount"); w.add_argument("src"); w.add_argument("top", nargs="?", type=int, default=20)
+    a = p.parse_args(argv)
+    if a.cmd == "renumber":
+        print(json.dumps({"unique_keys": renumber_trace(a.src, a.dst)}))
+    else:
+        k, c = trace_wordcount(a.src)
+        print(json.dumps({"unique_keys": int(k.size), "requests_keys": int(c.sum()), "top": [[int(x), int(y)] for x, y in zip(k[:a.top], c[:a.top])]}))
+
+
+if __name__ == "__main__":
+    _main()

@@ -48,6 +48,17 @@ def criteo_preprocess(lines: Iterable[str], out_path: Optional[str] = None, max_
     return out
 
 
+def create_mini_dataset(src_npz: str, dst_npz: str, n_samples: int = 100_000) -> int:
+    """Truncates a preprocessed ``.npz`` to its first ``n_samples`` samples and re-counts the categories that remain
+    (the role of the reference's create_mini_dataset.py, which cuts its id / offset / label arrays to 100 k samples)."""
+    d = np.load(src_npz)
+    n = min(int(n_samples), int(d["y"].shape[0]))
+    xc = d["X_cat"][:n]
+    counts = np.array([int(xc[:, j].max()) + 1 if n else 0 for j in range(xc.shape[1])], dtype=np.int64)
+    np.savez_compressed(dst_npz, y=d["y"][:n], X_int=d["X_int"][:n], X_cat=xc, counts=counts)
+    return n
+
+
 class CriteoDataset:
     """Batches of a preprocessed ``.npz`` in the engine's input form (global batch, ids per table)."""
 

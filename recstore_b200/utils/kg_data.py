@@ -203,6 +203,36 @@ def graph_partition(head: np.ndarray, tail: np.ndarray, n_entities: int, n_parts
                          "levels": int(stats[2])}
 
 
+def write_partition_files(out_dir: str, ds: "KGDataset", parts: Sequence[np.ndarray], node_part: Optional[np.ndarray] = None) -> List[str]:
+    """One directory per part (``part_<i>``) for a multi-machine run, as the reference's partition tool lays them out
+    (partition.py:35-160): ``train.txt`` with the part's triples as ``head<TAB>rel<TAB>tail`` in GLOBAL ids,
+    ``local_to_global.txt`` (line i = global id of the part's i-th entity: those the part owns first, then the remote
+    ends of its triples), ``partition_book.txt`` (owner part of every local entity) and ``meta.json``."""
+    import json
+    h, r, t = ds.train
+    if node_part is None:                                     # no node partition given: an entity belongs to the part with most of its triples
+        votes = np.zeros((len(parts), ds.n_entities), dtype=np.int64)
+        for p, idx in enumerate(parts):
+            np.add.at(votes[p], h[idx], 1); np.add.at(votes[p], t[idx], 1)
+        node_part = votes.argmax(0).astype(np.int32)
+    dirs = []
+    for p, idx in enumerate(parts):
+        d = os.path.join(out_dir, f"part_{p}")
+        os.makedirs(d, exist_ok=True)
+        ends = np.unique(np.concatenate([h[idx], t[idx]])) if idx.size else np.zeros(0, dtype=np.int64)
+        own = np.nonzero(node_part == p)[0]
+        halo = ends[node_part[ends] != p]
+        l2g = np.concatenate([own, halo]).astype(np.int64)
+        np.savetxt(os.path.join(d, "train.txt"), np.stack([h[idx], r[idx], t[idx]], 1), fmt="%d", delimiter="\t")
+        np.savetxt(os.path.join(d, "local_to_global.txt"), l2g, fmt="%d")
+        np.savetxt(os.path.join(d, "partition_book.txt"), node_part[l2g], fmt="%d")
+        with open(os.path.join(d, "meta.json"), "w") as f:
+            json.dump({"part": p, "n_parts": len(parts), "n_triples": int(idx.size), "n_owned_entities": int(own.size),
+                       "n_halo_entities": int(halo.size), "n_entities": ds.n_entities, "n_relations": ds.n_relations}, f)
+        dirs.append(d)
+    return dirs
+
+
 # ------------------------------------------------------------------------------------------------ sampling
 class ChunkedNegativeSampler:
     """Positive batches from one worker's triples plus ``batch / chunk * neg_sample_size`` uniform negative entities;

@@ -292,3 +292,28 @@ def test_driver_reference_flags(tmp_path):
     import pytest
     with pytest.raises(SystemExit):
         kge_main.main(["--pairwise"])
+
+
+def test_partition_files_for_multi_machine_runs(tmp_path):
+    """Per-part directories: triples in global ids, owned entities first in the local-to-global map, halo entities after."""
+    import json
+    import numpy as np
+    from recstore_b200.utils import kg_data as K
+    ds = K.KGDataset.synthetic(300, 6, 3000, seed=2)
+    parts, node, _ = K.graph_partition(ds.train[0], ds.train[2], 300, 3, seed=1)
+    dirs = K.write_partition_files(str(tmp_path), ds, parts, node)
+    seen = 0
+    for p, d in enumerate(dirs):
+        tri = np.loadtxt(f"{d}/train.txt", dtype=np.int64, ndmin=2)
+        l2g = np.loadtxt(f"{d}/local_to_global.txt", dtype=np.int64, ndmin=1)
+        book = np.loadtxt(f"{d}/partition_book.txt", dtype=np.int64, ndmin=1)
+        meta = json.load(open(f"{d}/meta.json"))
+        assert tri.shape == (parts[p].size, 3) and np.array_equal(tri[:, 0], ds.train[0][parts[p]])
+        assert np.all(node[tri[:, 2]] == p)                                   # a triple lives with its tail
+        assert np.all(book[: meta["n_owned_entities"]] == p) and np.all(book[meta["n_owned_entities"]:] != p)
+        assert np.isin(np.unique(tri[:, [0, 2]]), l2g).all() and np.unique(l2g).size == l2g.size
+        seen += tri.shape[0]
+    assert seen == ds.train[0].size
+    # without a node partition the owner is the part holding most of the entity's triples
+    rp = K.random_partition(ds.train[0].size, 2, 0)
+    assert len(K.write_partition_files(str(tmp_path / "r"), ds, rp)) == 2

@@ -143,3 +143,23 @@ def test_binary_trace_roundtrip(tmp_path):
         f.write(b"xx")
     with pytest.raises(ValueError):
         read_binary_trace(p)
+
+
+def test_binary_trace_renumber_and_wordcount(tmp_path):
+    """Trace tools of the PS benchmark: dense renumbering in order of first appearance (with the dim check) and key
+    frequencies."""
+    import numpy as np
+    import pytest
+    from recstore_b200.ps import load_generator as L
+    src, dst = str(tmp_path / "a.bin"), str(tmp_path / "b.bin")
+    reqs = [[50, 7, 50], [9, 7], [10 ** 12]]
+    L.write_binary_trace(src, reqs, dim=32)
+    assert L.renumber_trace(src, dst) == 4
+    assert [x.tolist() for x in L.read_binary_trace(dst)] == [[0, 1, 0], [2, 1], [3]]
+    keys, counts = L.trace_wordcount(src)
+    assert dict(zip(keys.tolist(), counts.tolist())) == {50: 2, 7: 2, 9: 1, 10 ** 12: 1} and counts.tolist() == sorted(counts.tolist(), reverse=True)
+    L.write_binary_trace(src, reqs, dim=12)
+    with pytest.raises(ValueError):
+        L.renumber_trace(src, dst)
+    replay = L.DatasetReplay(dst, loop=False)
+    assert sum(1 for _ in replay) == 3

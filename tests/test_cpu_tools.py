@@ -96,3 +96,18 @@ def test_uvm_baseline_trainer_runs_under_the_interposer():
     r = uvm_trainer.main(["--vocab_size", "2000", "--embed_size", "8", "--batch_size", "128", "--sample_number", "4", "--device", "cpu",
                           "--no_uvm"])
     assert r["uvm"] is False and r["intercepted"] is None
+
+
+def test_create_mini_dataset_truncates_and_recounts(tmp_path):
+    import numpy as np
+    from recstore_b200.utils import dlrm_data as Dd
+    rng = np.random.default_rng(0)
+    lines = ["\t".join([str(rng.integers(0, 2))] + [str(rng.integers(0, 9)) for _ in range(Dd.NUM_INT)] +
+                       [format(int(rng.integers(0, 40)), "x") for _ in range(Dd.NUM_CAT)]) for _ in range(60)]
+    full = Dd.criteo_preprocess(lines, str(tmp_path / "full.npz"))
+    assert Dd.create_mini_dataset(str(tmp_path / "full.npz"), str(tmp_path / "mini.npz"), 25) == 25
+    mini = np.load(tmp_path / "mini.npz")
+    assert mini["y"].shape == (25,) and np.array_equal(mini["X_cat"], full["X_cat"][:25])
+    assert np.all(mini["counts"] <= full["counts"]) and np.all(mini["counts"] == mini["X_cat"].max(0) + 1)
+    ds = Dd.CriteoDataset(str(tmp_path / "mini.npz"), batch=5, test_frac=0.2)
+    assert len(ds) == 4 and len(next(iter(ds)).ids) == Dd.NUM_CAT
