@@ -101,6 +101,9 @@ def parse_args(argv=None):
     p.add_argument("--nr_background_threads", type=int, default=4)
     p.add_argument("--update_cache_use_omp", type=int, default=1)
     p.add_argument("--update_pq_use_omp", type=int, default=1)
+    p.add_argument("--determinism_dir", default=os.environ.get("RECSTORE_DETERMINISM_DIR"),
+                   help="record the sampled batches of the first --determinism_steps steps there; later runs must reproduce them")
+    p.add_argument("--determinism_steps", type=int, default=20)
     a = p.parse_args(argv)
     if a.pairwise:
         p.error("--pairwise is closed in the reference (its loss generator asserts) and is not offered here")
@@ -220,8 +223,12 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
     t0 = time.time()
     losses = []
     valid_log = []
+    from recstore_b200.utils.determinism import RunRecorder
+    recorder = RunRecorder(args.determinism_dir)
     for step in range(args.max_step):
         h, r, t, n, ch = next(smp)
+        if step < args.determinism_steps:
+            recorder.diff_presampling(h, r, t, n, rank, step, ch)
         losses.append(step_fn(h, r, t, n, ch))
         if args.force_sync_interval > 0 and W > 1 and (step + 1) % args.force_sync_interval == 0:
             import torch.distributed as dist

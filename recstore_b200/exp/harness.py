@@ -61,6 +61,24 @@ def log_succeeded(path: str, marker: str = MARKER) -> bool:
         return False
 
 
+def clean_unsuccessful(root: str, marker: str = MARKER, dry: bool = False) -> List[str]:
+    """Removes the run directories under ``root`` whose log lacks the success marker, so that the next sweep runs them
+    again from a clean directory (the reference's clean_unsuccess_log.py); returns the directories concerned.  Only
+    directories that look like runs of this harness (a ``config.json`` beside the log) are touched."""
+    import shutil
+    gone = []
+    for name in sorted(os.listdir(root)) if os.path.isdir(root) else []:
+        d = os.path.join(root, name)
+        if not (os.path.isdir(d) and os.path.exists(os.path.join(d, "config.json"))):
+            continue
+        if log_succeeded(os.path.join(d, "log"), marker):
+            continue
+        gone.append(d)
+        if not dry:
+            shutil.rmtree(d)
+    return gone
+
+
 @contextlib.contextmanager
 def box_lock(path: str, timeout_s: float = 0.0, poll_s: float = 1.0) -> Iterator[None]:
     """Exclusive advisory lock on ``path``; waits up to ``timeout_s`` (0 = fail at once if it is taken)."""
@@ -158,6 +176,7 @@ def main(argv=None):
     ap.add_argument("--spec", required=True, help="JSON file: name, command, grid, fixed, exclude, log_root, timeout_s")
     ap.add_argument("--rerun", action="store_true", help="run configurations again even if their log has the marker")
     ap.add_argument("--dry", action="store_true", help="only create the run directories and print the commands")
+    ap.add_argument("--clean", action="store_true", help="remove the run directories without the success marker, then exit")
     ap.add_argument("--lock", default=None, help="lock file shared by every sweep on this box")
     ap.add_argument("--lock-timeout", type=float, default=0.0)
     a = ap.parse_args(argv)
@@ -165,6 +184,10 @@ def main(argv=None):
         spec = json.load(f)
     exp = Experiment(spec["name"], spec["command"], spec.get("grid", {}), spec.get("fixed"), spec.get("exclude"),
                      spec.get("log_root", "runs"), spec.get("timeout_s", 3600.0), spec.get("marker", MARKER), spec.get("env"))
+    if a.clean:
+        for d in clean_unsuccessful(exp.root, exp.marker, dry=a.dry):
+            print(("would remove " if a.dry else "removed ") + d)
+        sys.exit(0)
     ctx = box_lock(a.lock, a.lock_timeout) if a.lock else contextlib.nullcontext()
     with ctx:
         res = exp.run(rerun=a.rerun, dry=a.dry)

@@ -46,3 +46,39 @@ def test_box_lock_is_exclusive(tmp_path):
                 pass
     with box_lock(p):
         pass
+
+
+def test_clean_unsuccessful_removes_only_failed_runs(tmp_path):
+    import json
+    from recstore_b200.exp import harness as H
+    for name, text, cfg in (("run_a=1", "all good\n" + H.MARKER + "\n", True), ("run_a=2", "crashed\n", True), ("notes", "x", False)):
+        d = tmp_path / name
+        d.mkdir()
+        (d / "log").write_text(text)
+        if cfg:
+            (d / "config.json").write_text(json.dumps({}))
+    assert [p.split("/")[-1] for p in H.clean_unsuccessful(str(tmp_path), dry=True)] == ["run_a=2"] and (tmp_path / "run_a=2").exists()
+    assert len(H.clean_unsuccessful(str(tmp_path))) == 1
+    assert (tmp_path / "run_a=1").exists() and not (tmp_path / "run_a=2").exists() and (tmp_path / "notes").exists()
+
+
+def test_determinism_recorder_and_driver_flag(tmp_path):
+    """First run records, an identical run passes, a run with another seed is caught."""
+    import pytest
+    import torch
+    from recstore_b200.utils.determinism import DeterminismError, RunRecorder
+    rec = RunRecorder(str(tmp_path / "d"))
+    rec.diff_objs(torch.arange(5), "x"); rec.diff_objs({"a": 1}, "cfg")
+    rec2 = RunRecorder(str(tmp_path / "d"))
+    rec2.diff_objs(torch.arange(5), "x"); rec2.diff_objs({"a": 1}, "cfg")
+    assert rec.recorded == 2 and rec2.compared == 2
+    with pytest.raises(DeterminismError):
+        rec2.diff_objs(torch.arange(5) + 1, "x")
+    RunRecorder(None).diff_objs(torch.zeros(1), "ignored")
+    from recstore_b200.cli import kge_main
+    base = ["--max_step", "6", "--n_entities", "200", "--n_triples", "2000", "--hidden_dim", "8", "--batch_size", "32",
+            "--neg_sample_size", "8", "--log_interval", "1000", "--determinism_dir", str(tmp_path / "kg")]
+    kge_main.main(base)
+    kge_main.main(base)
+    with pytest.raises(DeterminismError):
+        kge_main.main(base + ["--seed", "7"])
