@@ -133,6 +133,25 @@ def parse_args(argv=None):
     return a
 
 
+def _trace_id_fn(args):
+    """Ids with the stack-distance profile of a recorded access trace (``--data-generation synthetic --data-trace-file F``,
+    the trace-driven generator of the reference's dlrm_data_pytorch.py:774-1286): the file holds integers separated by
+    commas or white space; every table replays a synthetic trace of that profile, folded into its row count."""
+    import re
+    from recstore_b200.utils.dlrm_data import trace_generate, trace_profile
+    with open(args.data_trace_file) as f:
+        trace = [int(x) for x in re.split(r"[,\s]+", f.read().strip()) if x]
+    if not trace:
+        sys.exit(f"ERROR: {args.data_trace_file} holds no ids")
+    uniq, dist, prob = trace_profile(trace)
+    calls = [0]
+
+    def fn(n_ids, n_rows, table):
+        calls[0] += 1
+        return trace_generate(uniq, dist, prob, n_ids, seed=args.numpy_rand_seed * 7919 + calls[0]) % n_rows
+    return fn
+
+
 def lr_at(step: int, base: float, warmup: int, decay_start: int, decay_steps: int) -> float:
     """Learning-rate policy of the reference's driver (dlrm_model.py LRPolicyScheduler): linear warm-up over ``warmup``
     steps, constant, then a quadratic decay from ``decay_start`` over ``decay_steps`` steps down to a floor of 1e-7."""
@@ -258,8 +277,11 @@ def run(args) -> dict:
     alpha = args.zipf_alpha if args.data_generation == "synthetic" else 0.0
     gauss = ((args.rand_data_mu, args.rand_data_sigma, args.rand_data_min, args.rand_data_max)
              if args.data_generation == "random" and args.rand_data_dist == "gaussian" else None)
-    src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 1, gaussian=gauss)
-    test_src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 2, gaussian=gauss)
+    id_fn = _trace_id_fn(args) if (args.data_generation == "synthetic" and args.data_trace_file) else None
+    src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 1, gaussian=gauss,
+                          id_fn=id_fn)
+    test_src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 2, gaussian=gauss,
+                               id_fn=id_fn)
     step0 = 0
     if args.load_model:
         step0 = int(model.load(args.load_model).get("step", 0))

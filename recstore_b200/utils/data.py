@@ -95,8 +95,10 @@ class DLRMBatchSource:
     to the table (the ``--rand-data-dist gaussian`` generator of the reference's driver, dlrm_data_pytorch.py)."""
 
     def __init__(self, table_rows: Sequence[int], hotness: Sequence[int], batch: int, num_dense: int = 13,
-                 alpha: float = 1.2, seed: int = 0, gaussian: Optional[Tuple[float, float, float, float]] = None):
+                 alpha: float = 1.2, seed: int = 0, gaussian: Optional[Tuple[float, float, float, float]] = None,
+                 id_fn=None):
         self.gaussian = gaussian
+        self.id_fn = id_fn                   # optional ``id_fn(n_ids, n_rows, table_index) -> int64 array``: overrides the generators
         self.table_rows = list(table_rows)
         self.hotness = list(hotness)
         self.batch = batch
@@ -108,7 +110,10 @@ class DLRMBatchSource:
         B = self.batch
         dense = np.log1p(self.rng.exponential(1.0, size=(B, self.num_dense))).astype(np.float32)
         labels = (self.rng.random(B) < 0.25).astype(np.float32)
-        if self.gaussian is not None:
+        if self.id_fn is not None:
+            ids = [torch.from_numpy(np.ascontiguousarray(self.id_fn(B * h, n, t), dtype=np.int64))
+                   for t, (n, h) in enumerate(zip(self.table_rows, self.hotness))]
+        elif self.gaussian is not None:
             mu, sigma, lo, hi = self.gaussian
             mu = (lo + hi) / 2.0 if mu == -1 else mu
             ids = []

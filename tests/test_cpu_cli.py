@@ -126,6 +126,12 @@ def test_dlrm_driver_reference_flags():
     assert 0 < out["last_loss"] < 1
     out = dlrm_main.main(base + ["--num-batches", "3", "--inference-only", "--loss-threshold", "0.01"])
     assert out["steps"] == 0 and out["inference_batches"] == 3 and 0 <= out["test_accuracy"] <= 1
+    import numpy as np, os, tempfile
+    tf = os.path.join(tempfile.mkdtemp(), "trace.txt")
+    with open(tf, "w") as f:
+        f.write(", ".join(str(int(x)) for x in np.random.default_rng(0).zipf(1.5, 400) % 40))
+    out = dlrm_main.main(base + ["--num-batches", "3", "--data-generation", "synthetic", "--data-trace-file", tf])
+    assert out["steps"] == 3 and out["last_loss"] == out["last_loss"]
     with pytest.raises(SystemExit):
         dlrm_main.main(base + ["--qr-flag"])
     with pytest.raises(SystemExit):
