@@ -317,3 +317,21 @@ def test_partition_files_for_multi_machine_runs(tmp_path):
     # without a node partition the owner is the part holding most of the entity's triples
     rp = K.random_partition(ds.train[0].size, 2, 0)
     assert len(K.write_partition_files(str(tmp_path / "r"), ds, rp)) == 2
+
+
+def test_distributed_trainer_against_ps_shards(tmp_path):
+    """KVStore mode: two server shards with server-side row-wise Adagrad, two trainer processes on an edge-cut
+    partition; the loss falls, every entity / relation key lives on exactly one shard, the checkpoint has the usual
+    files."""
+    import numpy as np
+    from recstore_b200.cli import kge_dist
+    out = kge_dist.main(["--model_name", "TransE_l2", "--num_servers", "2", "--num_clients", "2", "--max_step", "40", "--n_entities", "1500",
+                         "--n_relations", "10", "--n_triples", "15000", "--hidden_dim", "16", "--batch_size", "64", "--neg_sample_size", "16",
+                         "--gamma", "6", "--graph_part", "--test", "--save_path", str(tmp_path / "ck"), "--partition_dir", str(tmp_path / "parts")])
+    assert sum(out["server_keys"]) == 1500 + 10 and min(out["server_keys"]) > 500
+    for w in out["workers"]:
+        assert w["last_loss"] < w["first_loss"]
+    assert 0 < out["test"]["MRR"] <= 1 and 0 <= out["prepared"]["edge_cut"] <= 1
+    assert np.load(tmp_path / "ck" / "synthetic_TransE_l2_entity.npy").shape == (1500, 16)
+    assert np.load(tmp_path / "ck" / "synthetic_TransE_l2_relation.npy").shape == (10, 16)
+    assert (tmp_path / "parts" / "part_1" / "train.txt").exists()
