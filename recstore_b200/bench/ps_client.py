@@ -2,6 +2,7 @@
 
     python -m recstore_b200.bench.ps_client --threads 4 --window 4 --batch 500 --alpha 0.99 --seconds 3
     python -m recstore_b200.bench.ps_client --poisson-rate 2000 --seconds 3
+    python -m recstore_b200.bench.ps_client --processes 8 --threads 2 --seconds 3
 
 Starts an in-process server shard on a loopback port unless ``--host/--port`` point at a running one.  Prints the
 throughput once per second and a JSON summary, like the reference's closed-loop client benchmark
@@ -64,6 +65,29 @@ def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, secon
             "per_second": per_sec, "seconds": el}
 
 
+def _process_entry(args, q):
+    q.put(closed_loop(*args, quiet=True))
+
+
+def multi_process(host, port, dim, processes, threads, window, batch, alpha, key_space, seconds, dataset=None):
+    """``processes`` load-generator processes (each with ``threads`` closed-loop senders) against one server: the Python
+    interpreter of a single process is the limit long before the server is, as the reference's multi_client.py (8
+    processes) works around (src/grpc_ps/python_client/multi_client.py)."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_process_entry, args=((host, port, dim, threads, window, batch, alpha, key_space, seconds, dataset), q))
+          for _ in range(processes)]
+    for p in ps:
+        p.start()
+    res = [q.get(timeout=seconds + 120) for _ in ps]
+    for p in ps:
+        p.join(30)
+    return {"mode": "closed", "processes": processes, "threads": threads, "window": window, "batch": batch,
+            "keys_per_s": sum(r["keys_per_s"] for r in res), "per_process": [r["keys_per_s"] for r in res],
+            "seconds": max(r["seconds"] for r in res)}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--host", default=None)
@@ -78,6 +102,7 @@ def main(argv=None):
     ap.add_argument("--dataset", default=None, help="replay key batches from this file instead of Zipf keys")
     ap.add_argument("--poisson-rate", type=float, default=0.0, help="open loop: requests per second (0 = closed loop)")
     ap.add_argument("--engine", default="KVEngineMap")
+    ap.add_argument("--processes", type=int, default=1, help="closed loop: load-generator processes, each with --threads senders")
     a = ap.parse_args(argv)
     srv = None
     host, port = a.host, a.port
@@ -90,6 +115,8 @@ def main(argv=None):
             src = iter(DatasetReplay(a.dataset)) if a.dataset else zipf_key_source(a.key_space, a.batch, a.alpha)
             gen = PoissonLoadGenerator(lambda: ParameterClient(host, port, 0, a.dim), src, a.poisson_rate, senders=a.threads)
             out = {"mode": "poisson", "rate": a.poisson_rate, **gen.run(a.seconds).summary()}
+        elif a.processes > 1:
+            out = multi_process(host, port, a.dim, a.processes, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset)
         else:
             out = closed_loop(host, port, a.dim, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset)
         print(json.dumps(out), flush=True)

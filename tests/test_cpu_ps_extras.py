@@ -163,3 +163,12 @@ def test_binary_trace_renumber_and_wordcount(tmp_path):
         L.renumber_trace(src, dst)
     replay = L.DatasetReplay(dst, loop=False)
     assert sum(1 for _ in replay) == 3
+
+
+def test_ps_client_benchmark_with_several_processes(capsys):
+    """Closed-loop load from two generator processes against one in-process server shard."""
+    import json
+    from recstore_b200.bench import ps_client
+    ps_client.main(["--processes", "2", "--threads", "1", "--seconds", "0.6", "--key-space", "20000", "--batch", "200"])
+    out = json.loads([ln for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")][-1])
+    assert out["processes"] == 2 and len(out["per_process"]) == 2 and out["keys_per_s"] > 0
