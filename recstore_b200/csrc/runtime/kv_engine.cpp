@@ -5,6 +5,7 @@
 #include <cstring>
 #include <mutex>
 #include <shared_mutex>
+#include <thread>
 #include <unordered_map>
 
 #include <emmintrin.h>
@@ -238,15 +239,51 @@ class KVEngineMap final : public BaseKV {
 };
 
 // ============================================================== KVEngineExtendibleHash
+// Reader-writer lock for a structure that is read by every operation and written rarely (the directory): a reader
+// takes only the stripe its thread hashes to, so readers on different cores do not share a cache line; the writer
+// takes every stripe.
+class StripedSharedMutex {
+  static constexpr int kStripes = 64;
+  struct alignas(64) Stripe { std::shared_mutex mu; };
+
+ public:
+  void lock_shared() { s_[slot()].mu.lock_shared(); }
+  void unlock_shared() { s_[slot()].mu.unlock_shared(); }
+  void lock() { for (auto& st : s_) st.mu.lock(); }
+  void unlock() { for (int i = kStripes - 1; i >= 0; --i) s_[i].mu.unlock(); }
+
+ private:
+  static int slot() {
+    static thread_local const int v = static_cast<int>(std::hash<std::thread::id>()(std::this_thread::get_id()) % kStripes);
+    return v;
+  }
+  Stripe s_[kStripes];
+};
+
 class KVEngineExtendibleHash final : public BaseKV {
   static constexpr int kSegCap = 128;
   struct Segment {
     SpinLock mu;
     int local_depth = 0;
     int count = 0;
+    alignas(16) uint8_t tags[kSegCap];   // one hash byte per slot: a lookup compares 16 tags at a time and reads a key only on a tag match
     uint64_t keys[kSegCap];
     uint32_t idx[kSegCap];
   };
+  static uint8_t tag_of(uint64_t h) { return static_cast<uint8_t>(h >> 56); }   // the directory uses the low bits
+  // slot of `key` in the segment, or -1
+  static int find(const Segment* s, uint64_t key, uint8_t tag) {
+    const __m128i want = _mm_set1_epi8(static_cast<char>(tag));
+    for (int base = 0; base < s->count; base += 16) {
+      unsigned m = static_cast<unsigned>(_mm_movemask_epi8(_mm_cmpeq_epi8(_mm_load_si128(reinterpret_cast<const __m128i*>(s->tags + base)), want)));
+      while (m) {
+        const int i = base + __builtin_ctz(m);
+        if (i < s->count && s->keys[i] == key) return i;
+        m &= m - 1;
+      }
+    }
+    return -1;
+  }
 
  public:
   explicit KVEngineExtendibleHash(const KVConfig& c) : BaseKV(c) {
@@ -259,33 +296,32 @@ class KVEngineExtendibleHash final : public BaseKV {
 
   bool Get(uint64_t key, void* out) override {
     const uint64_t h = hash64(key);
-    std::shared_lock<std::shared_mutex> dl(dir_mu_);
+    std::shared_lock<StripedSharedMutex> dl(dir_mu_);
     Segment* s = dir_[h & (dir_.size() - 1)];
     std::lock_guard<SpinLock> lk(s->mu);
-    for (int i = 0; i < s->count; ++i)
-      if (s->keys[i] == key) {
-        memcpy(out, slab_.at(s->idx[i]), cfg_.value_size);
-        return true;
-      }
-    return false;
+    const int i = find(s, key, tag_of(h));
+    if (i < 0) return false;
+    memcpy(out, slab_.at(s->idx[i]), cfg_.value_size);
+    return true;
   }
   bool Put(uint64_t key, const void* value) override {
     const uint64_t h = hash64(key);
     for (int attempt = 0; attempt < 64; ++attempt) {
       {
-        std::shared_lock<std::shared_mutex> dl(dir_mu_);
+        std::shared_lock<StripedSharedMutex> dl(dir_mu_);
         Segment* s = dir_[h & (dir_.size() - 1)];
         std::lock_guard<SpinLock> lk(s->mu);
-        for (int i = 0; i < s->count; ++i)
-          if (s->keys[i] == key) {
-            memcpy(slab_.at(s->idx[i]), value, cfg_.value_size);
-            return true;
-          }
+        const int at = find(s, key, tag_of(h));
+        if (at >= 0) {
+          memcpy(slab_.at(s->idx[at]), value, cfg_.value_size);
+          return true;
+        }
         if (s->count < kSegCap) {
           const uint32_t v = slab_.alloc();
           if (v == UINT32_MAX) return false;
           memcpy(slab_.at(v), value, cfg_.value_size);
           s->keys[s->count] = key;
+          s->tags[s->count] = tag_of(h);
           s->idx[s->count] = v;
           ++s->count;
           size_.fetch_add(1, std::memory_order_relaxed);
@@ -298,22 +334,21 @@ class KVEngineExtendibleHash final : public BaseKV {
   }
   bool Erase(uint64_t key) override {
     const uint64_t h = hash64(key);
-    std::shared_lock<std::shared_mutex> dl(dir_mu_);
+    std::shared_lock<StripedSharedMutex> dl(dir_mu_);
     Segment* s = dir_[h & (dir_.size() - 1)];
     std::lock_guard<SpinLock> lk(s->mu);
-    for (int i = 0; i < s->count; ++i)
-      if (s->keys[i] == key) {
-        slab_.release(s->idx[i]);
-        s->keys[i] = s->keys[s->count - 1];
-        s->idx[i] = s->idx[s->count - 1];
-        --s->count;
-        size_.fetch_sub(1, std::memory_order_relaxed);
-        return true;
-      }
-    return false;
+    const int i = find(s, key, tag_of(h));
+    if (i < 0) return false;
+    slab_.release(s->idx[i]);
+    s->keys[i] = s->keys[s->count - 1];
+    s->tags[i] = s->tags[s->count - 1];
+    s->idx[i] = s->idx[s->count - 1];
+    --s->count;
+    size_.fetch_sub(1, std::memory_order_relaxed);
+    return true;
   }
   void Clear() override {
-    std::unique_lock<std::shared_mutex> dl(dir_mu_);
+    std::unique_lock<StripedSharedMutex> dl(dir_mu_);
     free_segments();
     reset_dir();
     slab_.reset();
@@ -321,12 +356,12 @@ class KVEngineExtendibleHash final : public BaseKV {
   }
   uint64_t Size() const override { return size_.load(); }
   std::string DebugInfo() const override {
-    std::shared_lock<std::shared_mutex> dl(dir_mu_);
+    std::shared_lock<StripedSharedMutex> dl(dir_mu_);
     return "KVEngineExtendibleHash size=" + std::to_string(Size()) + " global_depth=" + std::to_string(global_depth_) +
            " segments=" + std::to_string(segments_.size());
   }
   size_t Keys(uint64_t* out, size_t cap) const override {
-    std::shared_lock<std::shared_mutex> dl(dir_mu_);
+    std::shared_lock<StripedSharedMutex> dl(dir_mu_);
     size_t n = 0;
     for (Segment* s : segments_) {
       std::lock_guard<SpinLock> lk(s->mu);
@@ -337,7 +372,7 @@ class KVEngineExtendibleHash final : public BaseKV {
   // Invariant checker used by the tests: every key sits in the segment its hash selects, local
   // depths are consistent with the directory, the counts add up.
   bool CheckConsistency() const {
-    std::shared_lock<std::shared_mutex> dl(dir_mu_);
+    std::shared_lock<StripedSharedMutex> dl(dir_mu_);
     uint64_t total = 0;
     for (size_t d = 0; d < dir_.size(); ++d) {
       Segment* s = dir_[d];
@@ -346,6 +381,7 @@ class KVEngineExtendibleHash final : public BaseKV {
       for (int i = 0; i < s->count; ++i) {
         const uint64_t h = hash64(s->keys[i]);
         if ((h & lmask) != (d & lmask)) return false;
+        if (s->tags[i] != tag_of(h)) return false;
       }
     }
     for (Segment* s : segments_) total += s->count;
@@ -369,7 +405,7 @@ class KVEngineExtendibleHash final : public BaseKV {
     dir_.clear();
   }
   void split(uint64_t h) {
-    std::unique_lock<std::shared_mutex> dl(dir_mu_);
+    std::unique_lock<StripedSharedMutex> dl(dir_mu_);
     Segment* s = dir_[h & (dir_.size() - 1)];
     if (s->count < kSegCap) return;  // somebody else split it meanwhile
     if (s->local_depth == global_depth_) {
@@ -387,10 +423,12 @@ class KVEngineExtendibleHash final : public BaseKV {
     for (int i = 0; i < s->count; ++i) {
       if (hash64(s->keys[i]) & bit) {
         n->keys[n->count] = s->keys[i];
+        n->tags[n->count] = s->tags[i];
         n->idx[n->count] = s->idx[i];
         ++n->count;
       } else {
         s->keys[keep] = s->keys[i];
+        s->tags[keep] = s->tags[i];
         s->idx[keep] = s->idx[i];
         ++keep;
       }
@@ -401,7 +439,7 @@ class KVEngineExtendibleHash final : public BaseKV {
       if (d & bit) dir_[d] = n;
   }
 
-  mutable std::shared_mutex dir_mu_;
+  mutable StripedSharedMutex dir_mu_;
   std::vector<Segment*> dir_;
   std::vector<Segment*> segments_;
   int global_depth_ = 0;
