@@ -202,3 +202,51 @@ class TorchKGE:
         r = torch.cat(ranks).float()
         return {"MRR": (1.0 / r).mean().item(), "MR": r.mean().item(), "HITS@1": (r <= 1).float().mean().item(),
                 "HITS@3": (r <= 3).float().mean().item(), "HITS@10": (r <= 10).float().mean().item()}
+
+    @torch.no_grad()
+    def evaluate_full(self, h_ids, r_ids, t_ids, known: Optional[Dict[str, Dict[tuple, torch.Tensor]]] = None,
+                      batch: int = 64) -> Dict[str, float]:
+        """Ranks every test triple against ALL entities as corrupted tails and as corrupted heads (the reference's full
+        evaluation, ``neg_sample_size_eval = -1``).  ``known`` = :func:`known_triple_index` of every true triple turns on
+        the filtered setting: other true answers are taken out of the candidate list (the default of the reference;
+        ``--no_eval_filter`` switches it off)."""
+        n_ent = self.entity.shape[0]
+        allent = self.entity
+        ranks = []
+        for lo in range(0, h_ids.numel(), batch):
+            h, r, t = h_ids[lo:lo + batch], r_ids[lo:lo + batch], t_ids[lo:lo + batch]
+            bs = h.numel()
+            p = self.proj[r] if self.proj is not None else None
+            he, re, te = self.entity[h], self.relation[r], self.entity[t]
+            pos = edge_score(self.model, he, re, te, self.gamma, p, self.emb_init)
+            for corrupt_head in (False, True):
+                sc = chunk_neg_score(self.model, he, re, te, allent, corrupt_head, bs, self.gamma, p, self.emb_init)   # [bs, n_ent]
+                if known is not None:
+                    table = known["heads" if corrupt_head else "tails"]
+                    for i in range(bs):
+                        key = (int(r[i]), int(t[i])) if corrupt_head else (int(h[i]), int(r[i]))
+                        others = table.get(key)
+                        if others is not None:
+                            sc[i, others.to(sc.device)] = float("-inf")
+                truth = h if corrupt_head else t
+                sc[torch.arange(bs), truth] = float("-inf")              # the positive itself is compared through `pos`
+                ranks.append(1 + (sc > pos.unsqueeze(1)).sum(1))
+        r_ = torch.cat(ranks).float()
+        return {"MRR": (1.0 / r_).mean().item(), "MR": r_.mean().item(), "HITS@1": (r_ <= 1).float().mean().item(),
+                "HITS@3": (r_ <= 3).float().mean().item(), "HITS@10": (r_ <= 10).float().mean().item(), "candidates": n_ent}
+
+
+def known_triple_index(*splits) -> Dict[str, Dict[tuple, torch.Tensor]]:
+    """``{"tails": {(h, r): tensor of true tails}, "heads": {(r, t): tensor of true heads}}`` over the given
+    ``(head, rel, tail)`` splits (train, valid, test): the filter of the filtered ranking metrics."""
+    tails: Dict[tuple, list] = {}
+    heads: Dict[tuple, list] = {}
+    for sp in splits:
+        if sp is None:
+            continue
+        h, r, t = (torch.as_tensor(x).tolist() for x in sp)
+        for a, b, c in zip(h, r, t):
+            tails.setdefault((a, b), []).append(c)
+            heads.setdefault((b, c), []).append(a)
+    return {"tails": {k: torch.tensor(sorted(set(v)), dtype=torch.int64) for k, v in tails.items()},
+            "heads": {k: torch.tensor(sorted(set(v)), dtype=torch.int64) for k, v in heads.items()}}

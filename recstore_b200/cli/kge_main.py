@@ -63,7 +63,7 @@ def parse_args(argv=None):
     p.add_argument("--presample_steps", type=int, default=0)
     p.add_argument("--test", action="store_true")
     p.add_argument("--batch_size_eval", type=int, default=256)
-    p.add_argument("--neg_sample_size_eval", type=int, default=256)
+    p.add_argument("--neg_sample_size_eval", type=int, default=256, help="-1: rank against all entities (filtered unless --no_eval_filter)")
     p.add_argument("--save_path", default=None)
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--no_graph", action="store_true", help="native path: launch the step eagerly instead of replaying a CUDA graph")
@@ -83,7 +83,7 @@ def parse_args(argv=None):
     p.add_argument("--valid", action="store_true", help="evaluate on the validation split every --eval_interval steps")
     p.add_argument("--eval_interval", type=int, default=10000)
     p.add_argument("--eval_percent", type=float, default=1.0, help="share of the evaluation split that is scored")
-    p.add_argument("--no_eval_filter", action="store_true", help="accepted: evaluation here ranks against sampled negatives, unfiltered")
+    p.add_argument("--no_eval_filter", action="store_true", help="full ranking (--neg_sample_size_eval -1) without removing other true triples")
     p.add_argument("--no_save_emb", action="store_true")
     p.add_argument("--num_thread", type=int, default=0, help="host threads per worker (0: share the cores evenly)")
     p.add_argument("--force_sync_interval", type=int, default=-1, help="barrier between the workers every N steps")
@@ -211,6 +211,17 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
         n_eval = max(args.batch_size, int(min(split[0].size, args.batch_size_eval * 4) * percent))
         th, tr, tt = (torch.as_tensor(x[:n_eval]).to(dev) for x in split)
         g = torch.Generator(device=dev if native else "cpu").manual_seed(5)
+        if args.neg_sample_size_eval < 0:           # rank against every entity, filtered unless --no_eval_filter
+            from recstore_b200.baseline.kge_torch import TorchKGE, known_triple_index
+            known = None if args.no_eval_filter else known_triple_index(ds.train, ds.valid, ds.test)
+            if native:                               # the sharded tables come to rank 0 (collective), scored there on the host
+                ent, rel = model._gather_table(model.entity), model._gather_table(model.relation)
+                if rank != 0:
+                    return None
+                scorer = TorchKGE(2, 2, args.dim, args.model_name, args.gamma, args.lr)
+                scorer.entity, scorer.relation = torch.from_numpy(ent), torch.from_numpy(rel)
+                return scorer.evaluate_full(th.cpu(), tr.cpu(), tt.cpu(), known)
+            return model.evaluate_full(th, tr, tt, known) if rank == 0 else None
         if native:
             ms = []
             for s0 in range(0, th.numel() - args.batch_size + 1, args.batch_size):

@@ -335,3 +335,34 @@ def test_distributed_trainer_against_ps_shards(tmp_path):
     assert np.load(tmp_path / "ck" / "synthetic_TransE_l2_entity.npy").shape == (1500, 16)
     assert np.load(tmp_path / "ck" / "synthetic_TransE_l2_relation.npy").shape == (10, 16)
     assert (tmp_path / "parts" / "part_1" / "train.txt").exists()
+
+
+def test_full_filtered_ranking_matches_brute_force_and_driver_flag():
+    import torch
+    from recstore_b200.baseline.kge_torch import TorchKGE, edge_score, known_triple_index
+    m = TorchKGE(40, 3, 8, "TransE_l2", gamma=6, seed=1)
+    h, r, t = torch.tensor([1, 2, 3, 1]), torch.tensor([0, 1, 2, 0]), torch.tensor([4, 5, 6, 9])
+    raw = m.evaluate_full(h, r, t)
+    known = known_triple_index((h, r, t))
+    filt = m.evaluate_full(h, r, t, known)
+    E, R = m.entity, m.relation
+    pos = edge_score("TransE_l2", E[h], R[r], E[t], 6)
+    ranks_raw, ranks_f = [], []
+    for i in range(4):
+        for side in ("tail", "head"):
+            if side == "tail":
+                sc = edge_score("TransE_l2", E[h[i]].expand(40, -1), R[r[i]].expand(40, -1), E, 6)
+                truth, others = int(t[i]), [int(t[j]) for j in range(4) if int(h[j]) == int(h[i]) and int(r[j]) == int(r[i])]
+            else:
+                sc = edge_score("TransE_l2", E, R[r[i]].expand(40, -1), E[t[i]].expand(40, -1), 6)
+                truth, others = int(h[i]), [int(h[j]) for j in range(4) if int(t[j]) == int(t[i]) and int(r[j]) == int(r[i])]
+            sc = sc.clone(); sc[truth] = float("-inf")
+            ranks_raw.append(1 + int((sc > pos[i]).sum()))
+            sc[others] = float("-inf")
+            ranks_f.append(1 + int((sc > pos[i]).sum()))
+    assert abs(raw["MRR"] - sum(1 / x for x in ranks_raw) / 8) < 1e-6
+    assert abs(filt["MRR"] - sum(1 / x for x in ranks_f) / 8) < 1e-6 and filt["MRR"] >= raw["MRR"]
+    from recstore_b200.cli import kge_main
+    out, _ = kge_main.main(["--model_name", "DistMult", "--max_step", "30", "--n_entities", "300", "--n_triples", "3000", "--hidden_dim", "8",
+                            "--batch_size", "32", "--neg_sample_size", "8", "--test", "--neg_sample_size_eval", "-1", "--log_interval", "1000"])
+    assert out[0]["test"]["candidates"] == 300 and 0 < out[0]["test"]["MRR"] <= 1
