@@ -28,6 +28,9 @@ extern "C" {
 int rs_kv_create(const char* engine, const char* json_config, void** out);
 int rs_kv_destroy(void* h);
 int rs_kv_check_consistency(void* h, int* ok);
+int rs_kv_put(void* h, unsigned long long key, const void* value);
+int rs_kv_get(void* h, unsigned long long key, void* out, int* found);
+int rs_kv_erase(void* h, unsigned long long key, int* erased);
 unsigned long long rs_kv_size(void* h);
 int rs_kv_benchmark(void* handle, int threads, double seconds, int batch, double zipf_alpha, double read_ratio,
                     unsigned long long key_space, unsigned long long seed, double* out);
@@ -110,6 +113,32 @@ void stress_kv(const char* engine, const char* json) {
   if (rs_kv_create(engine, json, &kv) != 0) { fail("rs_kv_create", engine); return; }
   double out[8];
   EXPECT_OK(rs_kv_benchmark(kv, 6, 0.3, 64, 0.99, 0.5, 20000, 7, out));
+  // put / get / erase cycles: every thread owns the keys congruent to its index, so each read-back is exact while the
+  // threads still collide in the engine's buckets, segments and locks
+  {
+    constexpr int kThreads = 6, kRounds = 3000;
+    std::atomic<int> bad{0};
+    std::vector<std::thread> ts;
+    for (int t = 0; t < kThreads; ++t) {
+      ts.emplace_back([&, t] {
+        Lcg rng(900 + t);
+        float val[8], got[8];
+        for (int r = 0; r < kRounds; ++r) {
+          const unsigned long long key = 5000000ull + (rng.next() % 4096) * kThreads + t;
+          for (int d = 0; d < 8; ++d) val[d] = static_cast<float>(key % 1000 + d + r);
+          int found = 0, erased = 0;
+          if (rs_kv_put(kv, key, val) != 0) { bad.fetch_add(1); continue; }
+          if (rs_kv_get(kv, key, got, &found) != 0 || !found || std::memcmp(got, val, sizeof(val)) != 0) bad.fetch_add(1);
+          if ((r & 3) == 0) {
+            if (rs_kv_erase(kv, key, &erased) != 0 || !erased) bad.fetch_add(1);
+            if (rs_kv_get(kv, key, got, &found) != 0 || found) bad.fetch_add(1);
+          }
+        }
+      });
+    }
+    for (auto& t : ts) t.join();
+    if (bad.load() != 0) fail("kv put/get/erase cycles", std::string(engine) + ": " + std::to_string(bad.load()) + " wrong answers");
+  }
   int ok = 1;
   if (rs_kv_check_consistency(kv, &ok) == 0 && !ok) fail("kv consistency", engine);   // non-zero: the engine has no checker
   std::printf("host_stress: kv %-12s get %.2f Mkv/s put %.2f Mkv/s size %llu\n", engine, out[0], out[1], rs_kv_size(kv));
