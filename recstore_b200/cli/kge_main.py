@@ -154,8 +154,11 @@ def prepare(args):
         parts, cross = K.soft_relation_partition(ds.train[1], W, seed=args.seed)
         info["cross_relations"] = int(cross.sum())
     elif args.graph_part:
-        parts, _, st = K.graph_partition(ds.train[0], ds.train[2], ds.n_entities, W, seed=args.seed)
+        parts, node_part, st = K.graph_partition(ds.train[0], ds.train[2], ds.n_entities, W, seed=args.seed)
         info["edge_cut"] = st["edge_cut"]
+        if args.device == "cuda" and W > 1:      # the sharded tables place row id on GPU id % W: make that the entity's part
+            ds, new_id = K.renumber_by_partition(ds, node_part, W)
+            info["entities_on_their_workers_gpu"] = float(np.mean(new_id % W == node_part))
     else:
         parts = K.random_partition(ds.train[0].size, W, args.seed)
     if args.cache_ratio > 0 and args.presample_steps > 0:

@@ -203,6 +203,35 @@ def graph_partition(head: np.ndarray, tail: np.ndarray, n_entities: int, n_parts
                          "levels": int(stats[2])}
 
 
+def renumber_by_partition(ds: "KGDataset", node_part: np.ndarray, n_parts: int) -> Tuple["KGDataset", np.ndarray]:
+    """New entity ids such that ``new_id % n_parts`` is the entity's part wherever the part sizes allow: a table that is
+    sharded cyclically over ``n_parts`` GPUs (row ``id`` on GPU ``id % n_parts``) then keeps every part's entities on
+    the GPU of the worker that trains the part, and only the cut edges and the negatives cross NVLink.  Parts larger
+    than ``ceil(n / n_parts)`` spill their last entities into the free ids of smaller parts.  Returns the rewritten
+    dataset and ``new_id[old_id]``."""
+    n = ds.n_entities
+    new_id = np.full(n, -1, dtype=np.int64)
+    slots = [np.arange(p, n, n_parts, dtype=np.int64) for p in range(n_parts)]       # ids with residue p
+    spill: List[np.ndarray] = []
+    free: List[np.ndarray] = []
+    for p in range(n_parts):
+        mine = np.nonzero(node_part == p)[0]
+        k = min(mine.size, slots[p].size)
+        new_id[mine[:k]] = slots[p][:k]
+        if mine.size > k:
+            spill.append(mine[k:])
+        elif slots[p].size > k:
+            free.append(slots[p][k:])
+    if spill:
+        sp, fr = np.concatenate(spill), np.concatenate(free)
+        assert sp.size == fr.size
+        new_id[sp] = fr
+    assert (new_id >= 0).all()
+    f = lambda tr: None if tr is None else (new_id[tr[0]], tr[1], new_id[tr[2]])
+    e2i = {k: int(new_id[v]) for k, v in ds.entity2id.items()} if ds.entity2id else None
+    return KGDataset(ds.name, n, ds.n_relations, f(ds.train), f(ds.valid), f(ds.test), e2i, ds.relation2id, ds.train_weight), new_id
+
+
 def write_partition_files(out_dir: str, ds: "KGDataset", parts: Sequence[np.ndarray], node_part: Optional[np.ndarray] = None) -> List[str]:
     """One directory per part (``part_<i>``) for a multi-machine run, as the reference's partition tool lays them out
     (partition.py:35-160): ``train.txt`` with the part's triples as ``head<TAB>rel<TAB>tail`` in GLOBAL ids,

@@ -366,3 +366,21 @@ def test_full_filtered_ranking_matches_brute_force_and_driver_flag():
     out, _ = kge_main.main(["--model_name", "DistMult", "--max_step", "30", "--n_entities", "300", "--n_triples", "3000", "--hidden_dim", "8",
                             "--batch_size", "32", "--neg_sample_size", "8", "--test", "--neg_sample_size_eval", "-1", "--log_interval", "1000"])
     assert out[0]["test"]["candidates"] == 300 and 0 < out[0]["test"]["MRR"] <= 1
+
+
+def test_renumber_by_partition_aligns_ids_with_cyclic_sharding():
+    import numpy as np
+    from recstore_b200.utils import kg_data as K
+    ds = K.KGDataset.synthetic(1001, 5, 8000, seed=4)
+    parts, node, _ = K.graph_partition(ds.train[0], ds.train[2], 1001, 4, seed=2, balance="nodes")
+    ds2, new_id = K.renumber_by_partition(ds, node, 4)
+    assert np.array_equal(np.sort(new_id), np.arange(1001))                       # a permutation
+    assert np.mean(new_id % 4 == node) > 0.95                                     # all but the spill of oversized parts
+    assert np.array_equal(ds2.train[0], new_id[ds.train[0]]) and np.array_equal(ds2.train[1], ds.train[1])
+    assert np.array_equal(ds2.test[2], new_id[ds.test[2]])
+    # triples of part p now mostly name entities with id % 4 == p
+    local = np.mean([(np.mean(ds2.train[2][idx] % 4 == p)) for p, idx in enumerate(parts)])
+    assert local > 0.9
+    skew = np.zeros(1001, dtype=np.int32); skew[:700] = 0; skew[700:] = 1          # one oversized part spills
+    _, nid = K.renumber_by_partition(ds, skew, 2)
+    assert np.array_equal(np.sort(nid), np.arange(1001)) and np.mean(nid[700:] % 2 == 1) == 1.0
