@@ -152,6 +152,23 @@ def _trace_id_fn(args):
     return fn
 
 
+def roc_auc(scores: torch.Tensor, labels: torch.Tensor) -> float:
+    """Area under the ROC curve from ranks (ties get their average rank); NaN if only one class is present."""
+    s, y = scores.double().reshape(-1), labels.double().reshape(-1)
+    n_pos, n_neg = float(y.sum()), float((1 - y).sum())
+    if n_pos == 0 or n_neg == 0:
+        return float("nan")
+    order = torch.argsort(s)
+    ss = s[order]
+    ranks = torch.empty_like(ss)
+    ranks[:] = torch.arange(1, ss.numel() + 1, dtype=torch.double)
+    uniq, inv, cnt = torch.unique_consecutive(ss, return_inverse=True, return_counts=True)      # average rank inside ties
+    ends = torch.cumsum(cnt, 0).double()
+    ranks = (ends - (cnt.double() - 1) / 2)[inv]
+    r_pos = ranks[y[order] > 0.5].sum()
+    return float((r_pos - n_pos * (n_pos + 1) / 2) / (n_pos * n_neg))
+
+
 def lr_at(step: int, base: float, warmup: int, decay_start: int, decay_steps: int) -> float:
     """Learning-rate policy of the reference's driver (dlrm_model.py LRPolicyScheduler): linear warm-up over ``warmup``
     steps, constant, then a quadratic decay from ``decay_start`` over ``decay_steps`` steps down to a floor of 1e-7."""
@@ -290,12 +307,15 @@ def run(args) -> dict:
     losses, t0, done = [], time.time(), 0
     test_acc = None
 
+    last_auc = [float("nan")]
+
     def test_once():
         tb = test_src.next()
         lo, hi = (model.rank * (args.mini_batch_size // model.world), (model.rank + 1) * (args.mini_batch_size // model.world))
         p = model.predict(tb).reshape(-1)
         if args.loss_threshold > 0:
             p = p.clamp(args.loss_threshold, 1.0 - args.loss_threshold)
+        last_auc[0] = roc_auc(p, tb.labels[lo:hi])
         return float(((p > 0.5).float() == tb.labels[lo:hi]).float().mean())
 
     if args.inference_only:
@@ -328,7 +348,8 @@ def run(args) -> dict:
                 test_acc = test_once()
                 if rank == 0:
                     print(f"Testing at - {done}: accuracy {test_acc * 100:.3f} % (rank 0 share)", flush=True)
-                if args.mlperf_acc_threshold > 0 and test_acc >= args.mlperf_acc_threshold and world == 1:
+                reached_auc = args.mlperf_auc_threshold > 0 and last_auc[0] >= args.mlperf_auc_threshold
+                if (reached_auc or (args.mlperf_acc_threshold > 0 and test_acc >= args.mlperf_acc_threshold)) and world == 1:
                     stop = True                   # the reference's early exit once the accuracy target is met
                     break
     if args.save_model:
@@ -336,7 +357,8 @@ def run(args) -> dict:
         if rank == 0:
             print(f"Saved checkpoint {args.save_model}", flush=True)
     out = {"steps": done, "first_loss": losses[0] if losses else None, "last_loss": losses[-1] if losses else None,
-           "mean_last_10": float(np.mean(losses[-10:])) if losses else None, "test_accuracy": test_acc}
+           "mean_last_10": float(np.mean(losses[-10:])) if losses else None, "test_accuracy": test_acc,
+           "test_auc": None if last_auc[0] != last_auc[0] else last_auc[0]}
     if args.print_time or args.print_wall_time:
         out["ms_per_iteration"] = (time.time() - t0) / max(1, done) * 1e3
     if args.enable_profiling and args.use_gpu:

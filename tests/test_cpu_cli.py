@@ -124,6 +124,13 @@ def test_dlrm_driver_reference_flags():
     assert out["steps"] == 10 and out["last_loss"] == out["last_loss"] and out["ms_per_iteration"] > 0
     out = dlrm_main.main(base + ["--num-batches", "5", "--loss-function", "mse"])
     assert 0 < out["last_loss"] < 1
+    import torch
+    g = torch.Generator().manual_seed(0)
+    sc, yy = torch.randint(0, 10, (300,), generator=g).float(), (torch.rand(300, generator=g) < 0.4).float()
+    pairs = (sc[yy > 0.5][:, None] > sc[yy < 0.5][None, :]).double() + 0.5 * (sc[yy > 0.5][:, None] == sc[yy < 0.5][None, :]).double()
+    assert abs(dlrm_main.roc_auc(sc, yy) - pairs.mean().item()) < 1e-9             # AUC = P(score of a positive > score of a negative)
+    out = dlrm_main.main(base + ["--num-batches", "6", "--test-freq", "3"])
+    assert 0.0 <= out["test_auc"] <= 1.0
     out = dlrm_main.main(base + ["--num-batches", "3", "--inference-only", "--loss-threshold", "0.01"])
     assert out["steps"] == 0 and out["inference_batches"] == 3 and 0 <= out["test_accuracy"] <= 1
     import numpy as np, os, tempfile
