@@ -457,7 +457,9 @@ RS_API long long rs_wire_packed_size(long long n, int dim) { return 4 + 4 * n + 
 // Packs n records of a common dim (dims may be overridden per item by `dims`, 0 = missing).
 RS_API int rs_wire_pack(const unsigned long long* keys, long long n, int dim, const float* values, const int* dims, void* out,
                         long long cap, long long* written) {
-  RS_REQUIRE(keys && out && written, "rs_wire_pack: null argument");
+  RS_REQUIRE(n >= 0 && (n == 0 || (keys && (values || dim == 0))) && out && written, "rs_wire_pack: null argument");
+  if (dims)
+    for (long long i = 0; i < n; ++i) RS_REQUIRE(dims[i] >= 0 && dims[i] <= dim, "rs_wire_pack: record %lld has dim %d outside [0, %d]", i, dims[i], dim);
   rs::WireWriter w(static_cast<int>(n));
   for (long long i = 0; i < n; ++i) w.add(static_cast<int>(i), keys[i], dims ? dims[i] : dim, values + i * dim);
   RS_REQUIRE(static_cast<long long>(w.buf.size()) <= cap, "rs_wire_pack: buffer too small (%zu > %lld)", w.buf.size(), cap);
