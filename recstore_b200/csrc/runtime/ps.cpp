@@ -220,6 +220,10 @@ class CachePS {
 constexpr uint32_t kPsMagic = 0x52535053;  // "RSPS"
 enum PsOp : uint32_t { OP_GET = 1, OP_PUT = 2, OP_UPDATE = 3, OP_CLEAR = 4, OP_FAKE = 5, OP_SAVE = 6, OP_LOAD = 7, OP_STATS = 8, OP_BYE = 9 };
 struct Frame { uint32_t magic, op; uint64_t len; };
+// A request larger than this (or naming more keys) is a protocol error: the connection is closed instead of sizing
+// buffers from a header that may be garbage.  Clients split their batches far below both (max_per_req).
+constexpr uint64_t kMaxFrameBytes = 256ull << 20;
+constexpr size_t kMaxKeysPerRequest = size_t{1} << 22;
 
 static bool send_all(int fd, const void* p, size_t n) {
   const char* c = static_cast<const char*>(p);
@@ -299,16 +303,25 @@ class PsServer {
     }
   }
   void Serve(int fd) {
+    try {
+      ServeLoop(fd);
+    } catch (const std::exception&) {
+      // e.g. std::bad_alloc on a hostile size: this connection ends, the server and its other connections go on
+    }
+    ::close(fd);
+  }
+  void ServeLoop(int fd) {
     std::vector<char> in;
     const int dim = ps_->dim();
     while (running_) {
       Frame f;
-      if (!recv_all(fd, &f, sizeof(f)) || f.magic != kPsMagic || f.len > (1ull << 32)) break;
+      if (!recv_all(fd, &f, sizeof(f)) || f.magic != kPsMagic || f.len > kMaxFrameBytes) break;
       in.resize(f.len);
       if (f.len && !recv_all(fd, in.data(), f.len)) break;
       requests_.fetch_add(1, std::memory_order_relaxed);
       if (f.op == OP_GET) {
         const size_t n = f.len / 8;
+        if (f.len % 8 != 0 || n > kMaxKeysPerRequest) break;
         const uint64_t* keys = reinterpret_cast<const uint64_t*>(in.data());
         std::vector<float> vals(n * dim);
         std::vector<uint8_t> found(n);
@@ -320,7 +333,7 @@ class PsServer {
       } else if (f.op == OP_PUT || f.op == OP_UPDATE) {
         WireReader r(in.data(), f.len);
         uint64_t done = 0;
-        if (r.ok) {
+        if (r.ok && static_cast<size_t>(r.n) <= kMaxKeysPerRequest) {
           std::vector<uint64_t> keys;
           std::vector<float> vals;
           for (int i = 0; i < r.n; ++i) {
@@ -354,7 +367,6 @@ class PsServer {
         break;
       }
     }
-    ::close(fd);
   }
   CachePS* ps_;
   int port_, lfd_ = -1;

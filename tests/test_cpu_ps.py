@@ -149,3 +149,53 @@ def test_record_parser_survives_random_and_truncated_buffers():
             pass
 
     run()
+
+
+def test_server_survives_malformed_frames():
+    """Hostile or broken clients: wrong magic, absurd lengths, truncated payloads, unknown verbs, key counts that do not
+    divide, record buffers with wild offsets.  The connection concerned is dropped; the server keeps serving others."""
+    import random
+    import socket
+    from recstore_b200.ps import ParameterClient, ParameterServer
+    srv = ParameterServer("KVEngineMap", {"capacity": 4096, "dim": 4})
+    port = srv.serve(0)
+    good = ParameterClient("127.0.0.1", port, 0, 4)
+    good.PutParameter(torch.tensor([1, 2, 3]), torch.arange(12, dtype=torch.float32).view(3, 4))
+    MAGIC = 0x52535053
+    rnd = random.Random(0)
+
+    def send(raw: bytes):
+        s = socket.create_connection(("127.0.0.1", port), timeout=5)
+        try:
+            s.sendall(raw)
+            s.settimeout(0.3)
+            try:
+                s.recv(64)
+            except (socket.timeout, ConnectionError):
+                pass
+        finally:
+            s.close()
+
+    frames = [
+        struct.pack("<IIQ", 0xDEADBEEF, 1, 8) + b"\x00" * 8,                        # wrong magic
+        struct.pack("<IIQ", MAGIC, 1, 1 << 40),                                     # absurd length
+        struct.pack("<IIQ", MAGIC, 1, (256 << 20) + 8),                             # just over the frame limit
+        struct.pack("<IIQ", MAGIC, 1, 64) + b"\x01" * 10,                           # truncated payload
+        struct.pack("<IIQ", MAGIC, 1, 12) + b"\x01" * 12,                           # GET whose length is not a multiple of 8
+        struct.pack("<IIQ", MAGIC, 77, 0),                                          # unknown verb
+        struct.pack("<IIQ", MAGIC, 2, 8) + struct.pack("<ii", 1 << 30, 0),          # PUT announcing 2^30 records
+        struct.pack("<IIQ", MAGIC, 3, 24) + struct.pack("<iiQi", 1, 1 << 28, 5, 4), # UPDATE with an end offset far outside
+        struct.pack("<IIQ", MAGIC, 2, 20) + struct.pack("<iiQi", 1, -5, 5, 4),      # negative offset
+        b"\x00" * 3,                                                                # less than a header
+    ]
+    for _ in range(40):
+        op, ln = rnd.randrange(0, 12), rnd.randrange(0, 200)
+        body = bytes(rnd.randrange(256) for _ in range(rnd.randrange(0, ln + 1)))
+        frames.append(struct.pack("<IIQ", MAGIC if rnd.random() < 0.8 else rnd.getrandbits(32), op if op not in (4, 5, 6, 7) else 1, ln) + body)
+    for fr in frames:
+        send(fr)
+        got = good.GetParameter(torch.tensor([2, 3, 99]))
+        assert got[0].tolist() == [4.0, 5.0, 6.0, 7.0] and got[1].tolist() == [8.0, 9.0, 10.0, 11.0] and float(got[2].abs().sum()) == 0.0
+    assert good.Stats()["keys_stored"] >= 3
+    good.close()
+    srv.close()
