@@ -744,8 +744,10 @@ KVConfig ParseKVConfig(const std::string& json) {
   JsonLite j(json);
   c.raw_json = json;
   c.path = j.str("path", "");
-  c.capacity = static_cast<uint64_t>(j.i64("capacity", 1 << 20));
-  c.value_size = static_cast<uint32_t>(j.i64("value_size", 128));
+  // out-of-range numbers become 0 here and are refused by CreateKV, instead of wrapping around in the casts
+  const long long cap = j.i64("capacity", 1 << 20), vs = j.i64("value_size", 128);
+  c.capacity = (cap > 0 && cap <= (1ll << 40)) ? static_cast<uint64_t>(cap) : 0;
+  c.value_size = (vs > 0 && vs <= (1ll << 24)) ? static_cast<uint32_t>(vs) : 0;
   c.num_threads = static_cast<int>(j.i64("num_threads", 8));
   c.num_shards = static_cast<int>(j.i64("num_shards", 16));
   c.prefetch = j.i64("prefetch", 0) != 0;
@@ -756,7 +758,7 @@ std::vector<std::string> ListKVEngines() { return {"KVEngineMap", "KVEngineExten
 
 std::unique_ptr<BaseKV> CreateKV(const std::string& engine, const KVConfig& cfg) {
   if (cfg.value_size == 0 || cfg.capacity == 0) {
-    set_error(RS_ERR_INVALID, "KV engine needs capacity > 0 and value_size > 0");
+    set_error(RS_ERR_INVALID, "KV engine needs 0 < capacity <= 2^40 and 0 < value_size <= 2^24");
     return nullptr;
   }
   if (engine == "KVEngineMap") {

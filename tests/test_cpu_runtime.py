@@ -273,3 +273,24 @@ def test_host_runtime_under_thread_sanitizer(tmp_path, sanitizer):
                ASAN_OPTIONS="detect_leaks=1 exitcode=67")
     p = subprocess.run([str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
     assert p.returncode == 0 and "host_stress: ok" in p.stdout and "Sanitizer" not in p.stdout, p.stdout[-3000:]
+
+
+def test_kv_factory_refuses_out_of_range_configs_and_survives_junk_json():
+    """Sizes that would wrap around in a cast are refused; arbitrary text as the JSON config never crashes the factory."""
+    import ctypes as C
+    import random
+    from recstore_b200 import _lib
+    lib = _lib.lib()
+    h = C.c_void_p()
+    for cfg in (b'{"capacity": 1e30, "value_size": 16}', b'{"capacity": -5, "value_size": 16}',
+                b'{"capacity": 1024, "value_size": 99999999999}', b'{"capacity": 1024, "value_size": 0}'):
+        assert lib.rs_kv_create(b"KVEngineChunkHash", cfg, C.byref(h)) != 0, cfg
+    assert lib.rs_kv_create(b"NoSuchEngine", b'{"capacity": 16, "value_size": 16}', C.byref(h)) != 0
+    rnd = random.Random(1)
+    alphabet = '{}[]",:0123456789.eE-+ truefalsn\\abc\n'
+    for _ in range(500):
+        s = "".join(rnd.choice(alphabet) for _ in range(rnd.randrange(0, 60)))
+        if rnd.random() < 0.5:
+            s = '{"capacity": 1024, "value_size": 16, ' + s
+        if lib.rs_kv_create(b"KVEngineMap", s.encode(), C.byref(h)) == 0:
+            lib.rs_kv_destroy(h)
