@@ -4,6 +4,8 @@
 // the message of the last failure on the calling thread is kept for
 // rs_last_error().  Nothing here throws across the ABI boundary.
 #pragma once
+#include <exception>
+#include <new>
 #include <cstdint>
 #include <cstdio>
 #include <cstdarg>
@@ -27,6 +29,17 @@ namespace rs {
 char* last_error_buf();                       // thread-local, 1024 bytes
 int set_error(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
 }  // namespace rs
+
+// Body of an extern "C" entry point that may allocate from sizes it was handed: an exception must not cross the C
+// boundary (it would terminate the process), it becomes an error code.
+#define RS_NOEXCEPT_BODY(...)                                                                          \
+  try {                                                                                                \
+    __VA_ARGS__                                                                                        \
+  } catch (const std::bad_alloc&) {                                                                    \
+    return rs::set_error(RS_ERR_CAPACITY, "%s: out of memory", __func__);                              \
+  } catch (const std::exception& e) {                                                                  \
+    return rs::set_error(RS_ERR_INVALID, "%s: %s", __func__, e.what());                                \
+  }
 
 #define RS_REQUIRE(cond, ...)                                   \
   do {                                                          \

@@ -786,10 +786,12 @@ using rs::BaseKV;
 
 RS_API int rs_kv_create(const char* engine, const char* json_config, void** out) {
   RS_REQUIRE(engine && out, "rs_kv_create: null argument");
-  auto kv = rs::CreateKV(engine, rs::ParseKVConfig(json_config ? json_config : "{}"));
-  if (!kv) return RS_ERR_INVALID;
-  *out = kv.release();
-  return RS_OK;
+  RS_NOEXCEPT_BODY(
+    auto kv = rs::CreateKV(engine, rs::ParseKVConfig(json_config ? json_config : "{}"));
+    if (!kv) return RS_ERR_INVALID;
+    *out = kv.release();
+    return RS_OK;
+  )
 }
 RS_API int rs_kv_destroy(void* h) {
   delete static_cast<BaseKV*>(h);
@@ -820,8 +822,7 @@ RS_API int rs_kv_batch_put(void* h, const unsigned long long* keys, long long n,
   return s == static_cast<size_t>(n) ? RS_OK : rs::set_error(RS_ERR_CAPACITY, "KV engine is full: stored %zu of %lld", s, n);
 }
 RS_API int rs_kv_bulk_load(void* h, unsigned long long n) {
-  static_cast<BaseKV*>(h)->BulkLoad(n);
-  return RS_OK;
+  RS_NOEXCEPT_BODY(static_cast<BaseKV*>(h)->BulkLoad(n); return RS_OK;)
 }
 RS_API int rs_kv_clear(void* h) {
   static_cast<BaseKV*>(h)->Clear();

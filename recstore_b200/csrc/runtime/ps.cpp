@@ -188,9 +188,13 @@ class CachePS {
       fclose(f);
       return set_error(RS_ERR_IO, "%s is not a parameter-server checkpoint", path.c_str());
     }
+    fseek(f, 0, SEEK_END);
+    const uint64_t file_bytes = static_cast<uint64_t>(ftell(f));
+    fseek(f, 16, SEEK_SET);
     uint64_t loaded = 0, bytes;
     std::vector<char> buf;
     while (fread(&bytes, 8, 1, f) == 1) {
+      if (bytes > file_bytes) { fclose(f); return set_error(RS_ERR_IO, "%s holds a block longer than the file", path.c_str()); }
       buf.resize(bytes);
       if (fread(buf.data(), 1, bytes, f) != bytes) { fclose(f); return set_error(RS_ERR_IO, "%s is truncated", path.c_str()); }
       WireReader r(buf.data(), bytes);
@@ -502,10 +506,12 @@ RS_API int rs_wire_unpack(const void* buf, long long len, int dim, unsigned long
 
 RS_API int rs_ps_create(const char* engine, const char* json, void** out) {
   RS_REQUIRE(engine && out, "rs_ps_create: null argument");
-  auto* ps = new CachePS(engine, json ? json : "{}");
-  if (!ps->ok()) { delete ps; return RS_ERR_INVALID; }
-  *out = ps;
-  return RS_OK;
+  RS_NOEXCEPT_BODY(
+    auto* ps = new CachePS(engine, json ? json : "{}");
+    if (!ps->ok()) { delete ps; return RS_ERR_INVALID; }
+    *out = ps;
+    return RS_OK;
+  )
 }
 RS_API int rs_ps_destroy(void* ps) { delete static_cast<CachePS*>(ps); return RS_OK; }
 RS_API int rs_ps_dim(void* ps) { return static_cast<CachePS*>(ps)->dim(); }
@@ -523,10 +529,10 @@ RS_API int rs_ps_update(void* ps, const unsigned long long* keys, long long n, c
   if (applied) *applied = static_cast<long long>(a);
   return RS_OK;
 }
-RS_API int rs_ps_load_fake(void* ps, unsigned long long n) { static_cast<CachePS*>(ps)->LoadFakeData(n); return RS_OK; }
+RS_API int rs_ps_load_fake(void* ps, unsigned long long n) { RS_NOEXCEPT_BODY(static_cast<CachePS*>(ps)->LoadFakeData(n); return RS_OK;) }
 RS_API int rs_ps_clear(void* ps) { static_cast<CachePS*>(ps)->Clear(); return RS_OK; }
-RS_API int rs_ps_save(void* ps, const char* path) { return static_cast<CachePS*>(ps)->SaveCkpt(path); }
-RS_API int rs_ps_load(void* ps, const char* path) { return static_cast<CachePS*>(ps)->LoadCkpt(path); }
+RS_API int rs_ps_save(void* ps, const char* path) { RS_NOEXCEPT_BODY(return static_cast<CachePS*>(ps)->SaveCkpt(path);) }
+RS_API int rs_ps_load(void* ps, const char* path) { RS_NOEXCEPT_BODY(return static_cast<CachePS*>(ps)->LoadCkpt(path);) }
 
 // port 0 picks a free port; *port_out receives the bound port.
 RS_API int rs_ps_server_start(void* ps, int port, void** server_out, int* port_out) {

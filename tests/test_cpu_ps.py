@@ -199,3 +199,37 @@ def test_server_survives_malformed_frames():
     assert good.Stats()["keys_stored"] >= 3
     good.close()
     srv.close()
+
+
+def test_checkpoint_loader_rejects_corrupt_files(tmp_path):
+    """Truncated or bit-flipped PS checkpoints give an error (or load the intact prefix consistently); they never take
+    the process down."""
+    import random
+    from recstore_b200 import _lib
+    from recstore_b200.ps import ParameterServer
+    ps = ParameterServer("KVEngineMap", {"capacity": 4096, "dim": 4})
+    ps.PutParameter(torch.arange(100), torch.rand(100, 4))
+    good = str(tmp_path / "c.bin")
+    ps.SaveCkpt(good)
+    raw = open(good, "rb").read()
+    rnd = random.Random(0)
+    errors = 0
+    for _ in range(150):
+        b = bytearray(raw[:rnd.randrange(0, len(raw))]) if rnd.random() < 0.5 else bytearray(raw)
+        for _ in range(rnd.randrange(0, 4)):
+            if b:
+                b[rnd.randrange(0, min(len(b), 64))] ^= 1 << rnd.randrange(8)
+        bad = str(tmp_path / "m.bin")
+        open(bad, "wb").write(bytes(b))
+        ps2 = ParameterServer("KVEngineMap", {"capacity": 4096, "dim": 4})
+        try:
+            ps2.LoadCkpt(bad)
+        except _lib.RecStoreError:
+            errors += 1
+        ps2.close()
+    assert errors > 50
+    ps3 = ParameterServer("KVEngineMap", {"capacity": 4096, "dim": 4})
+    ps3.LoadCkpt(good)
+    assert len(ps3) == 100 and torch.equal(ps3.GetParameter(torch.arange(100)), ps.GetParameter(torch.arange(100)))
+    with pytest.raises(_lib.RecStoreError):
+        ps3.LoadCkpt(str(tmp_path / "missing.bin"))
