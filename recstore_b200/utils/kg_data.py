@@ -359,3 +359,38 @@ def renumber_graph(ds: KGDataset, hot: Sequence[torch.Tensor], cache_size: int) 
     e2i = {k: int(m[v]) for k, v in ds.entity2id.items()} if ds.entity2id else None
     return KGDataset(ds.name, ds.n_entities, ds.n_relations, f(ds.train), f(ds.valid), f(ds.test), e2i, ds.relation2id,
                      ds.train_weight), d
+
+
+def _main(argv=None):
+    """``python -m recstore_b200.utils.kg_data -k 4 --out parts/ [--data_path D --data_files train.tsv --format raw_udd_hrt]``:
+    edge-cut partition of a dataset into per-part directories (the reference's ``dglke_partition`` command,
+    partition.py:35-160); without ``--data_path`` a synthetic power-law graph is partitioned."""
+    import argparse
+    import json
+    p = argparse.ArgumentParser(description="partition a knowledge graph for multi-worker training")
+    p.add_argument("-k", "--num-parts", type=int, required=True)
+    p.add_argument("--out", required=True)
+    p.add_argument("--data_path", default=None)
+    p.add_argument("--data_files", nargs="+", default=None)
+    p.add_argument("--format", default="raw_udd_hrt")
+    p.add_argument("--dataset", default="synthetic")
+    p.add_argument("--delimiter", default="\t")
+    p.add_argument("--n_entities", type=int, default=20000)
+    p.add_argument("--n_relations", type=int, default=50)
+    p.add_argument("--n_triples", type=int, default=200000)
+    p.add_argument("--balance", choices=["triples", "nodes"], default="triples")
+    p.add_argument("--seed", type=int, default=0)
+    a = p.parse_args(argv)
+    if a.data_path:
+        ds = KGDataset.load(a.data_path, a.data_files or ["train.tsv"], a.format, name=a.dataset, delimiter=a.delimiter)
+    else:
+        ds = KGDataset.synthetic(a.n_entities, a.n_relations, a.n_triples, seed=a.seed)
+    parts, node_part, st = graph_partition(ds.train[0], ds.train[2], ds.n_entities, a.num_parts, seed=a.seed, balance=a.balance)
+    dirs = write_partition_files(a.out, ds, parts, node_part)
+    out = {"parts": dirs, "triples_per_part": [int(x.size) for x in parts], **st}
+    print(json.dumps(out))
+    return out
+
+
+if __name__ == "__main__":
+    _main()

@@ -314,6 +314,8 @@ def test_partition_files_for_multi_machine_runs(tmp_path):
         assert np.isin(np.unique(tri[:, [0, 2]]), l2g).all() and np.unique(l2g).size == l2g.size
         seen += tri.shape[0]
     assert seen == ds.train[0].size
+    out = K._main(["-k", "2", "--out", str(tmp_path / "cli"), "--n_entities", "200", "--n_triples", "1500"])
+    assert len(out["parts"]) == 2 and sum(out["triples_per_part"]) > 1000 and (tmp_path / "cli" / "part_0" / "meta.json").exists()
     # without a node partition the owner is the part holding most of the entity's triples
     rp = K.random_partition(ds.train[0].size, 2, 0)
     assert len(K.write_partition_files(str(tmp_path / "r"), ds, rp)) == 2
