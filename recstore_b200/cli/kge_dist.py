@@ -50,6 +50,8 @@ def parse_args(argv=None):
     p.add_argument("--max_step", type=int, default=100)
     p.add_argument("--graph_part", action="store_true", help="edge-cut partition of the entities (else random triples)")
     p.add_argument("--partition_dir", default=None, help="also write the per-part dataset directories there")
+    p.add_argument("--from_partition_dir", default=None,
+                   help="train on existing per-part directories (part_<i>/train.txt in global ids, meta.json), one trainer per part")
     p.add_argument("--engine", default="KVEngineMap", help="KV engine of the server shards")
     p.add_argument("--test", action="store_true")
     p.add_argument("--save_path", default=None)
@@ -123,19 +125,44 @@ def trainer(rank: int, args, triples, ports, queue) -> None:
                       "triples_per_s": args.batch_size * args.max_step / max(el, 1e-9)}))
 
 
+def _load_partition_dirs(root: str, name: str):
+    """Dataset and per-part triple index lists from ``part_<i>`` directories (``utils.kg_data.write_partition_files``)."""
+    from recstore_b200.utils import kg_data as K
+    dirs = sorted((d for d in os.listdir(root) if d.startswith("part_")), key=lambda d: int(d.split("_")[1]))
+    if not dirs:
+        raise FileNotFoundError(f"{root} holds no part_<i> directories")
+    hs, rs, ts, parts, o = [], [], [], [], 0
+    meta = {}
+    for d in dirs:
+        with open(os.path.join(root, d, "meta.json")) as f:
+            meta = json.load(f)
+        tri = np.loadtxt(os.path.join(root, d, "train.txt"), dtype=np.int64, ndmin=2)
+        hs.append(tri[:, 0]); rs.append(tri[:, 1]); ts.append(tri[:, 2])
+        parts.append(np.arange(o, o + tri.shape[0], dtype=np.int64))
+        o += tri.shape[0]
+    assert meta.get("n_parts", len(dirs)) == len(dirs), "a part directory is missing"
+    train = (np.concatenate(hs), np.concatenate(rs), np.concatenate(ts))
+    return K.KGDataset(name, int(meta["n_entities"]), int(meta["n_relations"]), train), parts
+
+
 def main(argv=None) -> dict:
     args = parse_args(argv)
     from recstore_b200.baseline.kge_torch import TorchKGE
     from recstore_b200.ps.client import ParameterServer
     from recstore_b200.utils import kg_data as K
-    if args.data_path:
+    if args.from_partition_dir:
+        ds, parts = _load_partition_dirs(args.from_partition_dir, args.dataset)
+        args.num_clients = len(parts)
+    elif args.data_path:
         ds = K.KGDataset.load(args.data_path, args.data_files or ["train.tsv"], args.format, name=args.dataset)
     else:
         ds = K.KGDataset.synthetic(args.n_entities, args.n_relations, args.n_triples, seed=args.seed)
     args.n_entities, args.n_relations = ds.n_entities, ds.n_relations
     info = {"n_entities": ds.n_entities, "n_relations": ds.n_relations, "n_train": int(ds.train[0].size)}
     node_part = None
-    if args.graph_part:
+    if args.from_partition_dir:
+        pass                                         # the directories are the partition
+    elif args.graph_part:
         parts, node_part, st = K.graph_partition(ds.train[0], ds.train[2], ds.n_entities, args.num_clients, seed=args.seed)
         info["edge_cut"] = st["edge_cut"]
     else:

@@ -337,6 +337,10 @@ def test_distributed_trainer_against_ps_shards(tmp_path):
     assert np.load(tmp_path / "ck" / "synthetic_TransE_l2_entity.npy").shape == (1500, 16)
     assert np.load(tmp_path / "ck" / "synthetic_TransE_l2_relation.npy").shape == (10, 16)
     assert (tmp_path / "parts" / "part_1" / "train.txt").exists()
+    # a second run trains straight from the directories the first one wrote
+    out2 = kge_dist.main(["--model_name", "DistMult", "--num_servers", "1", "--max_step", "10", "--hidden_dim", "8", "--batch_size", "32",
+                          "--neg_sample_size", "8", "--from_partition_dir", str(tmp_path / "parts")])
+    assert len(out2["workers"]) == 2 and out2["prepared"]["n_entities"] == 1500 and sum(out2["server_keys"]) == 1510
 
 
 def test_full_filtered_ranking_matches_brute_force_and_driver_flag():
