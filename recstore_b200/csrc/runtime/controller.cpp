@@ -148,6 +148,7 @@ class Controller {
     row_locks_.resize(static_cast<size_t>(rows));
   }
   void RegisterCache(int rank, float* cache) { caches_[rank] = cache; }
+  int ranks() const { return ranks_; }
   void Start() {
     if (!async_ || running_) return;
     running_ = true;
@@ -419,8 +420,28 @@ RS_API int rs_heap_check(void* h) { return static_cast<IndexedHeap*>(h)->check()
 
 RS_API int rs_ctrl_create(const char* json, void** out) {
   RS_REQUIRE(json && out, "rs_ctrl_create: null argument");
-  *out = new Controller(json);
-  return RS_OK;
+  // sizes from the config size vectors and start threads: check them before anything is built from them
+  {
+    rs::JsonLite j(json);
+    const long long ranks = j.i64("num_gpus", 1), L = j.i64("L", 10), dim = j.i64("dim", j.i64("emb_dim", 32));
+    const long long cap = j.i64("full_emb_capacity", 0), threads = j.i64("nr_background_threads", 2);
+    const long long workers = j.i64("kUpdatePqWorkerNum", 16);
+    const double ratio = j.num("cache_ratio", 0.0);
+    RS_REQUIRE(ranks >= 1 && ranks <= 1024, "rs_ctrl_create: num_gpus = %lld outside [1, 1024]", ranks);
+    RS_REQUIRE(L >= 0, "rs_ctrl_create: L = %lld is negative", L);
+    RS_REQUIRE(dim >= 1 && dim <= (1 << 20), "rs_ctrl_create: dim = %lld outside [1, 2^20]", dim);
+    RS_REQUIRE(cap >= 0 && cap <= (1ll << 40), "rs_ctrl_create: full_emb_capacity = %lld outside [0, 2^40]", cap);
+    RS_REQUIRE(threads >= 0 && threads <= 256, "rs_ctrl_create: nr_background_threads = %lld outside [0, 256]", threads);
+    RS_REQUIRE(workers <= 4096, "rs_ctrl_create: kUpdatePqWorkerNum = %lld above 4096", workers);
+    RS_REQUIRE(ratio >= 0.0 && ratio <= 1.0, "rs_ctrl_create: cache_ratio = %g outside [0, 1]", ratio);
+    const std::string mode = j.str("backwardMode", "CppAsyncV2");
+    RS_REQUIRE(mode == "PySync" || mode == "CppSync" || mode == "CppAsync" || mode == "CppAsyncV2",
+               "rs_ctrl_create: backwardMode %s is not one of PySync, CppSync, CppAsync, CppAsyncV2", mode.c_str());
+  }
+  RS_NOEXCEPT_BODY(
+    *out = new Controller(json);
+    return RS_OK;
+  )
 }
 RS_API int rs_ctrl_destroy(void* c) { delete static_cast<Controller*>(c); return RS_OK; }
 RS_API int rs_ctrl_register_table(void* c, float* table, long long rows) {
@@ -428,15 +449,23 @@ RS_API int rs_ctrl_register_table(void* c, float* table, long long rows) {
   static_cast<Controller*>(c)->RegisterTable(table, rows);
   return RS_OK;
 }
-RS_API int rs_ctrl_register_cache(void* c, int rank, float* cache) { static_cast<Controller*>(c)->RegisterCache(rank, cache); return RS_OK; }
+RS_API int rs_ctrl_register_cache(void* c, int rank, float* cache) {
+  RS_REQUIRE(c && rank >= 0 && rank < static_cast<Controller*>(c)->ranks(), "rs_ctrl_register_cache: rank %d out of range", rank);
+  static_cast<Controller*>(c)->RegisterCache(rank, cache);
+  return RS_OK;
+}
 RS_API int rs_ctrl_start(void* c) { static_cast<Controller*>(c)->Start(); return RS_OK; }
 RS_API int rs_ctrl_stop(void* c) { static_cast<Controller*>(c)->StopThreads(); return RS_OK; }
 RS_API int rs_ctrl_drain(void* c) { static_cast<Controller*>(c)->Drain(); return RS_OK; }
 RS_API int rs_ctrl_publish_reads(void* c, int rank, long long step, const long long* ids, long long n) {
+  RS_REQUIRE(c && rank >= 0 && rank < static_cast<Controller*>(c)->ranks() && n >= 0 && (ids || n == 0) && step >= 0,
+             "rs_ctrl_publish_reads: bad argument (rank %d, step %lld, n %lld)", rank, step, n);
   static_cast<Controller*>(c)->PublishReads(rank, step, reinterpret_cast<const int64_t*>(ids), n);
   return RS_OK;
 }
 RS_API int rs_ctrl_set_step_input(void* c, int rank, const long long* keys, long long n, const float* grads) {
+  RS_REQUIRE(c && rank >= 0 && rank < static_cast<Controller*>(c)->ranks() && n >= 0 && ((keys && grads) || n == 0),
+             "rs_ctrl_set_step_input: bad argument (rank %d, n %lld)", rank, n);
   static_cast<Controller*>(c)->SetStepInput(rank, reinterpret_cast<const int64_t*>(keys), n, grads);
   return RS_OK;
 }

@@ -118,3 +118,30 @@ def test_wrapper_after_backward_protocol():
     assert torch.allclose(table, expect)
     d = KGCacheControllerWrapperBase.FactoryNew("Dummy", cfg)
     d.AfterBackward(); d.StopThreads()
+
+
+def test_controller_refuses_hostile_configs_and_ranks():
+    """Sizes from the JSON config size vectors and start threads; out-of-range values and rank arguments are errors,
+    not crashes."""
+    from recstore_b200 import _lib
+    from recstore_b200.controller import KGCacheController
+    good = {"num_gpus": 2, "L": 5, "clr": 0.1, "dim": 8, "full_emb_capacity": 100, "backwardMode": "CppSync", "cache_ratio": 0.1}
+    for bad in ({"num_gpus": 0}, {"num_gpus": -3}, {"num_gpus": 100000}, {"L": -1}, {"dim": 0}, {"full_emb_capacity": -1},
+                {"cache_ratio": 5.0}, {"backwardMode": "Nope"}, {"nr_background_threads": -4}, {"nr_background_threads": 100000}):
+        with pytest.raises(_lib.RecStoreError):
+            KGCacheController(json.dumps({**good, **bad}))
+    ctrl = KGCacheController(json.dumps(good))
+    table = torch.zeros(100, 8)
+    caches = [torch.zeros(5, 8), torch.zeros(5, 8)]
+    ctrl.RegTensorsPerProcess(table, caches)
+    ids, g = torch.arange(4), torch.ones(4, 8)
+    for rank in (-1, 2, 99):
+        with pytest.raises(_lib.RecStoreError):
+            ctrl.SetStepInput(rank, ids, g)
+        with pytest.raises(_lib.RecStoreError):
+            ctrl.PublishReads(rank, 0, ids)
+    ctrl.SetStepInput(0, ids, g); ctrl.SetStepInput(1, ids, g)
+    ctrl.ProcessOneStep(0)
+    ctrl.StopThreads()
+    # still alive after the refused calls: ids 0..3 live in rank 0's cache and took both ranks' gradients
+    assert torch.allclose(caches[0][:4], torch.full((4, 8), -0.2)) and float(caches[1].abs().sum()) == 0.0
