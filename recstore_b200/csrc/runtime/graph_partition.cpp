@@ -168,9 +168,9 @@ void refine(const Graph& g, int k, std::vector<int32_t>& part, int64_t cap, int 
 // `node_weight` (optional, [n_nodes], positive) is what the parts balance; without it every node weighs 1.
 // part_out[n_nodes] receives the part of every node; stats_out[0] = number of edges whose ends lie in different
 // parts, stats_out[1] = weight of the heaviest part, stats_out[2] = number of levels used, stats_out[3] = total weight.
-RS_API int rs_graph_partition(long long n_nodes, long long n_edges, const long long* src, const long long* dst,
-                              const long long* node_weight, int k, double imbalance, unsigned long long seed,
-                              int refine_sweeps, int* part_out, long long* stats_out) {
+static int partition_impl(long long n_nodes, long long n_edges, const long long* src, const long long* dst,
+                          const long long* node_weight, int k, double imbalance, unsigned long long seed,
+                          int refine_sweeps, int* part_out, long long* stats_out) {
   RS_REQUIRE(n_nodes > 0 && n_edges >= 0 && k > 0 && part_out, "rs_graph_partition: bad sizes");
   RS_REQUIRE(n_edges == 0 || (src && dst), "rs_graph_partition: null edge list");
   RS_REQUIRE(imbalance >= 0.0 && refine_sweeps >= 0, "rs_graph_partition: bad imbalance / sweeps");
@@ -228,4 +228,10 @@ RS_API int rs_graph_partition(long long n_nodes, long long n_edges, const long l
     stats_out[3] = total_w;
   }
   return RS_OK;
+}
+
+RS_API int rs_graph_partition(long long n_nodes, long long n_edges, const long long* src, const long long* dst,
+                              const long long* node_weight, int k, double imbalance, unsigned long long seed,
+                              int refine_sweeps, int* part_out, long long* stats_out) {
+  RS_NOEXCEPT_BODY(return partition_impl(n_nodes, n_edges, src, dst, node_weight, k, imbalance, seed, refine_sweeps, part_out, stats_out);)
 }
