@@ -242,6 +242,9 @@ RS_API int rs_devpool_destroy(void* h) {
 }
 RS_API int rs_devpool_alloc(void* h, size_t bytes, void** out) {
   RS_REQUIRE(h && out, "rs_devpool_alloc: null argument");
+  *out = nullptr;
+  if (bytes > (size_t{1} << 48))      // rounding such a size up to the block granularity would wrap around
+    return rs::set_error(RS_ERR_CAPACITY, "rs_devpool_alloc: %zu bytes do not fit (limit reached or block too large)", bytes);
   *out = static_cast<Allocator*>(h)->alloc(bytes);
   if (*out == nullptr) return rs::set_error(RS_ERR_CAPACITY, "rs_devpool_alloc: %zu bytes do not fit (limit reached or block too large)", bytes);
   return RS_OK;

@@ -26,6 +26,8 @@ def test_pool_allocator_coalesces_and_respects_limit():
     with pytest.raises(_lib.RecStoreError):
         p.free(12345 * 256)         # foreign pointer
     assert p.stats()["failures"] == 1
+    with pytest.raises(_lib.RecStoreError):
+        p.alloc((1 << 64) - 1)      # rounding this up to the block granularity would wrap to zero
     p.close()
 
 
