@@ -34,29 +34,31 @@ def write_binary_trace(path: str, requests, dim: int = 32) -> None:
 
 
 def read_binary_trace(path: str) -> List[np.ndarray]:
-    raw = np.fromfile(path, dtype=np.uint8)
-    nreq = int(raw[:4].view("<i4")[0])
-    o, out = 4, []
-    rec = np.dtype([("key", "<u8"), ("dim", "<i4")])
-    for _ in range(nreq):
-        n = int(raw[o:o + 4].view("<i4")[0]); o += 4
-        out.append(raw[o:o + n * rec.itemsize].view(rec)["key"].astype(np.int64)); o += n * rec.itemsize
-    if o != raw.size:
-        raise ValueError(f"{path}: {raw.size - o} trailing bytes after {nreq} requests")
-    return out
+    return [r["key"].astype(np.int64) for r in _read_trace_records(path)]
 
 
 VALID_TRACE_DIMS = (4, 8, 16, 32, 64)
 
 
 def _read_trace_records(path: str):
-    """Requests of a binary trace as structured arrays with ``key`` and ``dim`` fields."""
+    """Requests of a binary trace as structured arrays with ``key`` and ``dim`` fields; a truncated or over-long file
+    is a ``ValueError`` that says where it stops making sense."""
     raw = np.fromfile(path, dtype=np.uint8)
-    nreq = int(raw[:4].view("<i4")[0])
     rec = np.dtype([("key", "<u8"), ("dim", "<i4")])
+
+    def i32(o, what):
+        if o + 4 > raw.size:
+            raise ValueError(f"{path}: truncated at byte {o} (expected {what})")
+        return int(raw[o:o + 4].view("<i4")[0])
+
+    nreq = i32(0, "the request count")
+    if nreq < 0:
+        raise ValueError(f"{path}: negative request count {nreq}")
     o, out = 4, []
-    for _ in range(nreq):
-        n = int(raw[o:o + 4].view("<i4")[0]); o += 4
+    for q in range(nreq):
+        n = i32(o, f"the key count of request {q}"); o += 4
+        if n < 0 or o + n * rec.itemsize > raw.size:
+            raise ValueError(f"{path}: request {q} announces {n} keys but only {raw.size - o} bytes follow")
         out.append(raw[o:o + n * rec.itemsize].view(rec).copy()); o += n * rec.itemsize
     if o != raw.size:
         raise ValueError(f"{path}: {raw.size - o} trailing bytes after {nreq} requests")

@@ -163,6 +163,14 @@ def test_binary_trace_renumber_and_wordcount(tmp_path):
         L.renumber_trace(src, dst)
     replay = L.DatasetReplay(dst, loop=False)
     assert sum(1 for _ in replay) == 3
+    raw = open(dst, "rb").read()
+    for cut in (0, 2, 4, 6, 10, len(raw) - 1):                      # truncated files say where they stop making sense
+        (tmp_path / "t.bin").write_bytes(raw[:cut])
+        with pytest.raises(ValueError, match="truncated|announces"):
+            L.read_binary_trace(str(tmp_path / "t.bin"))
+    (tmp_path / "t.bin").write_bytes(raw + b"xx")
+    with pytest.raises(ValueError, match="trailing"):
+        L.trace_wordcount(str(tmp_path / "t.bin"))
 
 
 def test_ps_client_benchmark_with_several_processes(capsys):
