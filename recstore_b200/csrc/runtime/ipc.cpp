@@ -134,8 +134,15 @@ RS_API int rs_shm_open(const char* name, void** out_handle) {
   close(fd);
   if (base == MAP_FAILED) return rs::set_error(RS_ERR_IO, "mmap of %s failed", path.c_str());
   ShmHeader* h = static_cast<ShmHeader*>(base);
+  if (static_cast<size_t>(st.st_size) < kHeaderBytes) {
+    munmap(base, static_cast<size_t>(st.st_size));
+    return rs::set_error(RS_ERR_STATE, "shared object %s is not a recstore tensor", name);
+  }
   for (int spin = 0; h->ready.load(std::memory_order_acquire) == 0 && spin < 100000; ++spin) std::this_thread::yield();
-  if (static_cast<size_t>(st.st_size) < kHeaderBytes || h->magic != kMagic) {
+  // the header is trusted by every reader afterwards: a foreign or damaged object must not describe more than is mapped
+  const bool sane = h->magic == kMagic && h->ndim >= 0 && h->ndim <= 8 &&
+                    (h->device >= 0 || h->data_bytes <= static_cast<unsigned long long>(st.st_size) - kHeaderBytes);
+  if (!sane) {
     munmap(base, static_cast<size_t>(st.st_size));
     return rs::set_error(RS_ERR_STATE, "shared object %s is not a recstore tensor", name);
   }

@@ -294,3 +294,37 @@ def test_kv_factory_refuses_out_of_range_configs_and_survives_junk_json():
             s = '{"capacity": 1024, "value_size": 16, ' + s
         if lib.rs_kv_create(b"KVEngineMap", s.encode(), C.byref(h)) == 0:
             lib.rs_kv_destroy(h)
+
+
+def test_foreign_or_damaged_shm_objects_are_refused():
+    """A shared-memory object that is not one of ours, or whose header describes more data than is mapped, is an error
+    at open time (readers trust the header afterwards)."""
+    import os
+    import struct
+    import uuid
+    from recstore_b200 import _lib, ipc
+    ns = "t" + uuid.uuid4().hex[:8]
+    ipc.set_namespace(ns)
+    try:
+        t = ipc.IPCTensorFactory.NewIPCTensor("good", (4, 3))
+        t.fill_(2.0)
+        assert ipc.IPCTensorFactory.FindIPCTensorFromName("good").sum().item() == 24.0
+        good_path = f"/dev/shm/rsb200.{os.getuid()}.{ns}.good"
+        raw = open(good_path, "rb").read()
+        cases = {"junk": os.urandom(8192), "short": raw[:100], "empty": b""}
+        pos = raw.find(struct.pack("<Q", 48))            # data_bytes of a 4 x 3 float tensor
+        if pos >= 0:
+            cases["oversized"] = raw[:pos] + struct.pack("<Q", 1 << 40) + raw[pos + 8:]
+        for name, blob in cases.items():
+            with open(f"/dev/shm/rsb200.{os.getuid()}.{ns}.{name}", "wb") as f:
+                f.write(blob)
+            with pytest.raises(_lib.RecStoreError):
+                ipc.IPCTensorFactory.FindIPCTensorFromName(name)
+    finally:
+        ipc.IPCTensorFactory.ClearIPCMemory()
+        for name in ("junk", "short", "empty", "oversized"):
+            try:
+                os.unlink(f"/dev/shm/rsb200.{os.getuid()}.{ns}.{name}")
+            except OSError:
+                pass
+        ipc.set_namespace(f"pytest{os.getpid()}")         # what the fixture of this file set
