@@ -12,7 +12,9 @@ Recognised flags (src/executable/dlrm/dlrm_model.py:618-760): ``--arch-sparse-fe
 --loss-threshold --lr-num-warmup-steps --lr-decay-start-step --lr-num-decay-steps --mlperf-acc-threshold
 --enable-profiling --print-time``.  Flags of features this engine does not have (QR / mixed-dimension embeddings,
 quantisation, ONNX export, ``--arch-interaction-itself``, ``--weighted-pooling``) are recognised and refused with a
-message; loader / logging flags of the Criteo pipeline are accepted and have no effect on generated data.  The first number of
+message; ``--data-generation dataset`` trains on Criteo-format files (``--raw-data-file`` text or a ``--processed-data-file``
+.npz; table sizes from the category counts, ``--data-sub-sample-rate``, ``--data-randomize``, ``--max-ind-range``); the
+remaining loader / logging flags of the Criteo pipeline are accepted and have no effect.  The first number of
 ``--arch-mlp-bot`` is the count of dense features, its last must equal the sparse feature size; the first number of
 ``--arch-mlp-top`` is the interaction width and is checked, as the reference does (:914-951).
 
@@ -56,8 +58,9 @@ def parse_args(argv=None):
     p.add_argument("--emb-optimizer", choices=["rowwise_adagrad", "sgd"], default="rowwise_adagrad")
     p.add_argument("--num-indices-per-lookup", type=int, default=1)
     p.add_argument("--num-indices-per-lookup-fixed", action="store_true", default=True)
-    p.add_argument("--data-generation", choices=["random", "synthetic"], default="random",
-                   help="random: uniform ids; synthetic: Zipf ids (--zipf-alpha)")
+    p.add_argument("--data-generation", choices=["random", "synthetic", "dataset"], default="random",
+                   help="random: uniform ids; synthetic: Zipf ids (--zipf-alpha) or a trace profile (--data-trace-file); "
+                        "dataset: Criteo-format files (--raw-data-file / --processed-data-file)")
     p.add_argument("--zipf-alpha", type=float, default=1.2)
     p.add_argument("--numpy-rand-seed", type=int, default=123)
     p.add_argument("--print-freq", type=int, default=10)
@@ -252,7 +255,54 @@ class _GpuModel:
         return self.e.load_checkpoint(path)
 
 
+class _DatasetSource:
+    """``next()`` over a ``CriteoDataset`` that starts over (reshuffled when asked) at the end of an epoch."""
+
+    def __init__(self, make):
+        self.make, self.it = make, None
+
+    def next(self):
+        if self.it is None:
+            self.it = iter(self.make())
+        try:
+            return next(self.it)
+        except StopIteration:
+            self.it = iter(self.make())
+            return next(self.it)
+
+
+def _open_dataset(args):
+    """Criteo-format data (``--data-generation dataset``): a preprocessed ``.npz`` (``--processed-data-file``) or the raw
+    tab-separated text (``--raw-data-file``: label, 13 integer and 26 hexadecimal categorical columns), preprocessed on the
+    fly and cached in the processed file if one is named (dlrm_data_pytorch.py:50-323 and data_utils.py of the
+    reference).  Returns the arrays; the table sizes of the model come from the category counts, as the reference does."""
+    from recstore_b200.utils import dlrm_data as Dd
+    if args.processed_data_file and os.path.exists(args.processed_data_file):
+        d = dict(np.load(args.processed_data_file))
+    elif args.raw_data_file:
+        with open(args.raw_data_file) as f:
+            d = Dd.criteo_preprocess(f, args.processed_data_file or None, args.max_ind_range)
+    else:
+        sys.exit("ERROR: --data-generation dataset needs --raw-data-file or an existing --processed-data-file")
+    if args.data_sub_sample_rate > 0.0:                 # drop that share of the negatives (the reference's sub-sampling)
+        rng = np.random.default_rng(args.numpy_rand_seed)
+        keep = (d["y"] > 0.5) | (rng.random(d["y"].shape[0]) >= args.data_sub_sample_rate)
+        d = {"y": d["y"][keep], "X_int": d["X_int"][keep], "X_cat": d["X_cat"][keep], "counts": d["counts"]}
+    if d["y"].shape[0] < 2 * args.mini_batch_size:
+        sys.exit(f"ERROR: {d['y'].shape[0]} samples are fewer than two mini-batches of {args.mini_batch_size}")
+    return d
+
+
 def run(args) -> dict:
+    data = None
+    if args.data_generation == "dataset":
+        from recstore_b200.utils import dlrm_data as Dd
+        data = _open_dataset(args)
+        args.arch_embedding_size = [max(1, int(c)) for c in data["counts"]]
+        if args.arch_mlp_bot[0] != Dd.NUM_INT:
+            sys.exit(f"ERROR: the data has {Dd.NUM_INT} dense features; --arch-mlp-bot must start with {Dd.NUM_INT}")
+        args.num_indices_per_lookup = 1
+        args.arch_mlp_top = None if args.arch_mlp_top is None else args.arch_mlp_top
     validate(args)
     from recstore_b200.utils.data import DLRMBatchSource
     rows, D = args.arch_embedding_size, args.arch_sparse_feature_size
@@ -295,10 +345,21 @@ def run(args) -> dict:
     gauss = ((args.rand_data_mu, args.rand_data_sigma, args.rand_data_min, args.rand_data_max)
              if args.data_generation == "random" and args.rand_data_dist == "gaussian" else None)
     id_fn = _trace_id_fn(args) if (args.data_generation == "synthetic" and args.data_trace_file) else None
-    src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 1, gaussian=gauss,
-                          id_fn=id_fn)
-    test_src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 2, gaussian=gauss,
-                               id_fn=id_fn)
+    if data is not None:
+        from recstore_b200.utils.dlrm_data import CriteoDataset
+        shuffle = args.data_randomize in ("total", "day")
+        src = _DatasetSource(lambda: CriteoDataset(data, args.mini_batch_size, shuffle=shuffle, seed=args.numpy_rand_seed + 1, split="train"))
+        test_src = _DatasetSource(lambda: CriteoDataset(data, args.mini_batch_size, seed=args.numpy_rand_seed + 2, split="test"))
+        n_train = len(CriteoDataset(data, args.mini_batch_size, split="train"))
+        if args.num_batches <= 0 or args.num_batches > n_train:
+            args.num_batches = n_train                    # one epoch = one pass over the training split
+        if len(CriteoDataset(data, args.mini_batch_size, split="test")) == 0:
+            test_src = _DatasetSource(lambda: CriteoDataset(data, args.mini_batch_size, seed=args.numpy_rand_seed + 2, split="train"))
+    else:
+        src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 1, gaussian=gauss,
+                              id_fn=id_fn)
+        test_src = DLRMBatchSource(rows, hot, args.mini_batch_size, num_dense=nd, alpha=alpha, seed=args.numpy_rand_seed + 2,
+                                   gaussian=gauss, id_fn=id_fn)
     step0 = 0
     if args.load_model:
         step0 = int(model.load(args.load_model).get("step", 0))

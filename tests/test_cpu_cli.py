@@ -143,3 +143,26 @@ def test_dlrm_driver_reference_flags():
         dlrm_main.main(base + ["--qr-flag"])
     with pytest.raises(SystemExit):
         dlrm_main.main(base + ["--quantize-emb-with-bit", "8"])
+
+
+def test_dlrm_driver_trains_on_criteo_format_files(tmp_path):
+    """--data-generation dataset: raw Criteo text is preprocessed (and cached as .npz), the table sizes come from the
+    category counts, a second run reads the cache, negatives can be sub-sampled."""
+    import numpy as np
+    from recstore_b200.cli import dlrm_main
+    rng = np.random.default_rng(0)
+    raw = tmp_path / "day.txt"
+    with open(raw, "w") as f:
+        for _ in range(400):
+            cat = [format(int(rng.integers(0, 30)), "x") for _ in range(26)]
+            label = int(int(cat[0], 16) % 2 == 0)                           # learnable from the first categorical column
+            f.write("\t".join([str(label)] + [str(int(rng.integers(0, 9))) for _ in range(13)] + cat) + "\n")
+    base = ["--arch-sparse-feature-size", "8", "--arch-mlp-bot", "13-16-8", "--mini-batch-size", "40", "--print-freq", "0",
+            "--data-generation", "dataset", "--raw-data-file", str(raw), "--processed-data-file", str(tmp_path / "day.npz"),
+            "--nepochs", "6", "--num-batches", "0", "--test-freq", "9", "--learning-rate", "0.1"]
+    out = dlrm_main.main(base)
+    assert out["steps"] == 6 * 9 and out["mean_last_10"] < out["first_loss"] and (tmp_path / "day.npz").exists()
+    assert out["test_accuracy"] is not None and 0 <= out["test_auc"] <= 1
+    raw.unlink()                                                           # the cached file is enough now
+    out2 = dlrm_main.main(base + ["--data-sub-sample-rate", "0.3", "--data-randomize", "none"])
+    assert 0 < out2["steps"] <= 6 * 9
