@@ -100,7 +100,7 @@ def parse_args(argv=None):
                    help="accepted: the dense replicas are always kept identical by the all-reduce")
     p.add_argument("--weighted-pooling", default=None, choices=[None, "fixed", "learned"], help="not offered: bags are summed")
     p.add_argument("--enable-profiling", action="store_true", help="stamp the GPU timer at the phase boundaries and print the timeline")
-    p.add_argument("--tensor-board-filename", default="run_kaggle_pt")
+    p.add_argument("--tensor-board-filename", default="", help="directory that receives scalars.jsonl (step, loss, lr, test metrics)")
     p.add_argument("--data-set", default="kaggle", help="accepted; data here is generated (--data-generation)")
     for name in ("--raw-data-file", "--processed-data-file", "--data-trace-file"):
         p.add_argument(name, default="")
@@ -388,6 +388,10 @@ def run(args) -> dict:
         _teardown(args, world)
         return out
     stop = False
+    scalars = None
+    if args.tensor_board_filename and rank == 0:          # one JSON object per line: a plain-text stand-in for the event file
+        os.makedirs(args.tensor_board_filename, exist_ok=True)
+        scalars = open(os.path.join(args.tensor_board_filename, "scalars.jsonl"), "a")
     for ep in range(args.nepochs):
         if stop:
             break
@@ -401,6 +405,8 @@ def run(args) -> dict:
             loss = model.train_step(b)
             losses.append(loss)
             done += 1
+            if scalars is not None:
+                scalars.write(json.dumps({"step": step0 + done, "epoch": ep, "train_loss": float(loss)}) + "\n")
             if rank == 0 and args.print_freq and done % args.print_freq == 0:
                 el = (time.time() - t0) / done * 1e3
                 print(f"Finished training it {j + 1}/{args.num_batches} of epoch {ep}, {el:.2f} ms/it, "
@@ -409,10 +415,14 @@ def run(args) -> dict:
                 test_acc = test_once()
                 if rank == 0:
                     print(f"Testing at - {done}: accuracy {test_acc * 100:.3f} % (rank 0 share)", flush=True)
+                if scalars is not None:
+                    scalars.write(json.dumps({"step": step0 + done, "test_accuracy": test_acc, "test_auc": last_auc[0]}) + "\n")
                 reached_auc = args.mlperf_auc_threshold > 0 and last_auc[0] >= args.mlperf_auc_threshold
                 if (reached_auc or (args.mlperf_acc_threshold > 0 and test_acc >= args.mlperf_acc_threshold)) and world == 1:
                     stop = True                   # the reference's early exit once the accuracy target is met
                     break
+    if scalars is not None:
+        scalars.close()
     if args.save_model:
         model.save(args.save_model, step0 + done)
         if rank == 0:

@@ -129,11 +129,17 @@ def test_dlrm_driver_reference_flags():
     sc, yy = torch.randint(0, 10, (300,), generator=g).float(), (torch.rand(300, generator=g) < 0.4).float()
     pairs = (sc[yy > 0.5][:, None] > sc[yy < 0.5][None, :]).double() + 0.5 * (sc[yy > 0.5][:, None] == sc[yy < 0.5][None, :]).double()
     assert abs(dlrm_main.roc_auc(sc, yy) - pairs.mean().item()) < 1e-9             # AUC = P(score of a positive > score of a negative)
-    out = dlrm_main.main(base + ["--num-batches", "6", "--test-freq", "3"])
+    import os
+    import tempfile
+    tb = tempfile.mkdtemp()
+    out = dlrm_main.main(base + ["--num-batches", "6", "--test-freq", "3", "--tensor-board-filename", tb])
     assert 0.0 <= out["test_auc"] <= 1.0
+    import json as _json
+    rows = [_json.loads(ln) for ln in open(os.path.join(tb, "scalars.jsonl"))]
+    assert sum("train_loss" in r for r in rows) == 6 and sum("test_accuracy" in r for r in rows) == 2
     out = dlrm_main.main(base + ["--num-batches", "3", "--inference-only", "--loss-threshold", "0.01"])
     assert out["steps"] == 0 and out["inference_batches"] == 3 and 0 <= out["test_accuracy"] <= 1
-    import numpy as np, os, tempfile
+    import numpy as np
     tf = os.path.join(tempfile.mkdtemp(), "trace.txt")
     with open(tf, "w") as f:
         f.write(", ".join(str(int(x)) for x in np.random.default_rng(0).zipf(1.5, 400) % 40))
