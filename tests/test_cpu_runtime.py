@@ -254,7 +254,7 @@ def test_renumbering_narrow_and_zipf_filler():
     assert t.min() >= 1 and t.max() <= 1000 and (t <= 10).float().mean() > 0.2
 
 
-@pytest.mark.parametrize("sanitizer", ["thread", "address"])
+@pytest.mark.parametrize("sanitizer", ["thread", "address", "undefined"])
 def test_host_runtime_under_thread_sanitizer(tmp_path, sanitizer):
     """The host runtime (KV engines, parameter server + clients, lookahead controller with its background threads) built
     with -fsanitize=thread / address (+ leak check) and driven from several threads by the stand-alone stress driver: no
@@ -270,9 +270,9 @@ def test_host_runtime_under_thread_sanitizer(tmp_path, sanitizer):
             pytest.skip(str(e))
         raise
     env = dict(os.environ, TSAN_OPTIONS="halt_on_error=1 exitcode=66 report_signal_unsafe=0",
-               ASAN_OPTIONS="detect_leaks=1 exitcode=67")
+               ASAN_OPTIONS="detect_leaks=1 exitcode=67", UBSAN_OPTIONS="halt_on_error=1 exitcode=68 print_stacktrace=1")
     p = subprocess.run([str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
-    assert p.returncode == 0 and "host_stress: ok" in p.stdout and "Sanitizer" not in p.stdout, p.stdout[-3000:]
+    assert p.returncode == 0 and "host_stress: ok" in p.stdout and "Sanitizer" not in p.stdout and "runtime error" not in p.stdout, p.stdout[-3000:]
 
 
 def test_kv_factory_refuses_out_of_range_configs_and_survives_junk_json():
