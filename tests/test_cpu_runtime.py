@@ -255,7 +255,7 @@ def test_renumbering_narrow_and_zipf_filler():
 
 
 @pytest.mark.parametrize("sanitizer", ["thread", "address", "undefined"])
-def test_host_runtime_under_thread_sanitizer(tmp_path, sanitizer):
+def test_host_runtime_under_sanitizers(tmp_path, sanitizer):
     """The host runtime (KV engines, parameter server + clients, lookahead controller with its background threads) built
     with -fsanitize=thread / address (+ leak check) and driven from several threads by the stand-alone stress driver: no
     sanitizer report, no broken invariant."""
