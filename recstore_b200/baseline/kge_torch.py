@@ -188,12 +188,17 @@ class TorchKGE:
         return loss.item()
 
     @torch.no_grad()
-    def evaluate(self, h_ids, r_ids, t_ids, n_neg: int = 256, generator: Optional[torch.Generator] = None) -> Dict[str, float]:
-        """Rank of each positive among ``n_neg`` sampled corruptions of its head and of its tail."""
+    def evaluate(self, h_ids, r_ids, t_ids, n_neg: int = 256, generator: Optional[torch.Generator] = None,
+                 neg_prob: Optional[torch.Tensor] = None) -> Dict[str, float]:
+        """Rank of each positive among ``n_neg`` sampled corruptions of its head and of its tail; ``neg_prob``
+        (``[n_entities]``, e.g. proportional to degree: ``--neg_deg_sample_eval``) replaces the uniform draw."""
         bs = h_ids.numel()
         ranks = []
         for corrupt_head in (False, True):
-            neg_ids = torch.randint(0, self.entity.shape[0], (n_neg,), generator=generator).to(self.device)
+            if neg_prob is None:
+                neg_ids = torch.randint(0, self.entity.shape[0], (n_neg,), generator=generator).to(self.device)
+            else:
+                neg_ids = torch.multinomial(neg_prob.cpu(), n_neg, replacement=True, generator=generator).to(self.device)
             p = self.proj[r_ids] if self.proj is not None else None
             pos = edge_score(self.model, self.entity[h_ids], self.relation[r_ids], self.entity[t_ids], self.gamma, p, self.emb_init)
             neg = chunk_neg_score(self.model, self.entity[h_ids], self.relation[r_ids], self.entity[t_ids], self.entity[neg_ids],

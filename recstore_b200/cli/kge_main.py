@@ -79,7 +79,7 @@ def parse_args(argv=None):
     p.add_argument("--regularization_coef", "-rc", type=float, default=0.0)
     p.add_argument("--regularization_norm", "-rn", type=int, default=3)
     p.add_argument("--neg_deg_sample", action="store_true", help="draw negatives proportionally to entity degree")
-    p.add_argument("--neg_deg_sample_eval", action="store_true")
+    p.add_argument("--neg_deg_sample_eval", action="store_true", help="PyTorch path: evaluation negatives in proportion to entity degree")
     p.add_argument("--valid", action="store_true", help="evaluate on the validation split every --eval_interval steps")
     p.add_argument("--eval_interval", type=int, default=10000)
     p.add_argument("--eval_percent", type=float, default=1.0, help="share of the evaluation split that is scored")
@@ -231,7 +231,11 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
                 ms.append(model.evaluate(th[s0:s0 + args.batch_size], tr[s0:s0 + args.batch_size], tt[s0:s0 + args.batch_size], g))
             return {k: float(np.mean([m[k] for m in ms])) for k in ms[0]} if ms else None
         if rank == 0:
-            return model.evaluate(th, tr, tt, args.neg_sample_size_eval, g)
+            prob = None
+            if args.neg_deg_sample_eval:                 # corruptions drawn in proportion to 1 + degree in the training graph
+                deg = torch.bincount(torch.as_tensor(np.concatenate([ds.train[0], ds.train[2]])), minlength=ds.n_entities).float() + 1.0
+                prob = deg / deg.sum()
+            return model.evaluate(th, tr, tt, args.neg_sample_size_eval, g, neg_prob=prob)
         return None
 
     t0 = time.time()
