@@ -58,6 +58,7 @@ class DLRMConfig:
     projection_hidden: Tuple[Sequence[int], Sequence[int]] = ((), ())   # hidden widths of the two branch MLPs (multiples of 64)
     dcn_layers: int = 3
     dcn_rank: int = 512
+    placement: str = "round_robin"               # tables on ranks: "round_robin" (t % world) or "balanced" (greedy by ids per sample)
     trace_phases: bool = False                   # stamp the GPU timer at phase boundaries (see DLRM.phase_times)
 
     def __post_init__(self):
@@ -121,8 +122,12 @@ class DLRM:
         self.proj = cfg.interaction == "projection"
         assert cfg.interaction in ("dot", "dcn", "projection")
         assert self.dcn or self.proj or self.F <= 32, "dot interaction kernel handles up to 31 embedding features"
-        # ---- table placement: round robin by table index
-        self.owner = [t % self.world for t in range(self.T)]
+        # ---- table placement: round robin by table index unless the config asks for the load-balanced greedy
+        if cfg.placement == "round_robin":
+            self.owner = [t % self.world for t in range(self.T)]
+        else:
+            from ..parallel.placement import place_tables
+            self.owner = place_tables(list(cfg.hotness), list(cfg.table_rows), self.world, cfg.placement)
         self.local_tables = [t for t in range(self.T) if self.owner[t] == self.rank]
         self.Tl = len(self.local_tables)
         self.Tmax = max(sum(1 for t in range(self.T) if self.owner[t] == r) for r in range(self.world))

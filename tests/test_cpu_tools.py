@@ -113,3 +113,20 @@ def test_create_mini_dataset_truncates_and_recounts(tmp_path):
     assert np.all(mini["counts"] <= full["counts"]) and np.all(mini["counts"] == mini["X_cat"].max(0) + 1)
     ds = Dd.CriteoDataset(str(tmp_path / "mini.npz"), batch=5, test_frac=0.2)
     assert len(ds) == 4 and len(next(iter(ds)).ids) == Dd.NUM_CAT
+
+
+def test_table_placement_policies():
+    """Round robin by index, and the greedy by ids per sample: equal costs reproduce round robin, the multi-hot
+    configuration is levelled as far as its heaviest table allows."""
+    from recstore_b200.parallel.placement import place_tables, placement_stats
+    hot = [3, 2, 1, 2, 6, 1, 1, 1, 1, 7, 3, 8, 1, 6, 9, 5, 1, 1, 1, 12, 100, 27, 10, 3, 1, 1]
+    rows = list(range(1000, 1026))
+    for w in (1, 2, 3, 4, 8):
+        assert place_tables([1] * 26, rows, w, "balanced") == place_tables([1] * 26, rows, w) == [t % w for t in range(26)]
+        rr, bal = place_tables(hot, rows, w), place_tables(hot, rows, w, "balanced")
+        assert sorted(set(bal)) == list(range(min(w, 26))) and len(bal) == 26
+        assert placement_stats(bal, hot, w)["imbalance"] <= placement_stats(rr, hot, w)["imbalance"] + 1e-9
+    assert placement_stats(place_tables(hot, rows, 2, "balanced"), hot, 2)["lookups_per_rank"] == [107, 107]
+    assert max(placement_stats(place_tables(hot, rows, 8, "balanced"), hot, 8)["lookups_per_rank"]) == 100     # the 100-hot table alone
+    with pytest.raises(ValueError):
+        place_tables(hot, rows, 2, "nope")
