@@ -138,6 +138,11 @@ def lib():
     return _lib
 
 
+def lib_path() -> str:
+    """File the native library is (or will be) loaded from: ``RECSTORE_B200_LIB`` when set, else the in-tree build."""
+    return os.environ.get("RECSTORE_B200_LIB") or str(_LIB_PATH)
+
+
 def check(rc: int) -> None:
     if rc != 0:
         msg = lib().rs_last_error()

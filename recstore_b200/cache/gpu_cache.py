@@ -35,6 +35,7 @@ _lib.register_signatures({
     "rs_ht_insert": (i32, [C.POINTER(HashTableView), vp, i64, vp, vp, vp]),
     "rs_ht_lookup": (i32, [C.POINTER(HashTableView), vp, i64, vp, vp]),
     "rs_ht_erase": (i32, [C.POINTER(HashTableView), vp, i64, vp, vp]),
+    "rs_ht_erase_checked": (i32, [C.POINTER(HashTableView), vp, i64, vp, vp, vp]),
     "rs_ht_dump": (i32, [C.POINTER(HashTableView), vp, vp, vp, u64, vp]),
     "rs_ht_check": (i32, [C.POINTER(HashTableView), C.POINTER(u64), C.POINTER(i64), C.POINTER(u64)]),
     "rs_unique_keys": (i32, [vp, i64, vp, vp, u64, vp, vp, vp, vp, vp]),
@@ -172,7 +173,7 @@ class GpuHashTable:
     def erase(self, keys: torch.Tensor) -> torch.Tensor:
         keys = self._k(keys)
         rows = torch.empty(keys.numel(), dtype=torch.int64, device=self.device)
-        _lib.call("rs_ht_erase", C.byref(self.view), ptr(keys), keys.numel(), ptr(rows), stream_ptr())
+        _lib.call("rs_ht_erase_checked", C.byref(self.view), ptr(keys), keys.numel(), ptr(rows), ptr(self.status), stream_ptr())
         return rows
 
     def clear(self) -> None:
@@ -201,7 +202,8 @@ class GpuHashTable:
 
 def unique_keys(keys: torch.Tensor, status: Optional[torch.Tensor] = None):
     """Device-side unique: returns (unique keys [u] in arbitrary order, inverse [n] with
-    ``unique[inverse] == keys``).  Allocates its scratch (2 n slots rounded up to a power of two)."""
+    ``unique[inverse] == keys``).  Allocates its scratch (2 n slots rounded up to a power of two).
+    The reserved keys -1 and -2 are not deduplicated: their inverse is -1 and ``status`` gets ``DEV_BAD_ARG``."""
     keys = keys.contiguous()
     n = keys.numel()
     nslots = 2

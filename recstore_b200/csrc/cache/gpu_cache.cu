@@ -8,8 +8,11 @@
 // 64-thread block, a per-set mutex even on reads):
 //   * each warp walks a strided list of keys and keeps the next key's set line in flight while it
 //     copies the current row, so many keys are in flight per SM;
-//   * the hit path takes no lock: it only reads keys / values and stamps the slot's counter with a
-//     relaxed store (a stale stamp only makes LRU slightly approximate);
+//   * the hit path takes no lock: it reads keys / values and stamps the slot's counter with a relaxed store (a
+//     stale stamp only makes LRU slightly approximate).  Every slot carries a sequence number that a writer makes
+//     odd before it touches the slot's key or values and even again afterwards; Query reads it before and after
+//     the row copy and reports the key as a MISS when it was odd or changed, so a Query that overlaps a Replace /
+//     Update of the same slot on another stream never returns a torn or wrong-key row as a hit;
 //   * Replace / Update take a per-set lock with a BOUNDED spin; on give-up the key is skipped and
 //     RS_DEV_WAIT_TIMEOUT is recorded.
 // Semantics kept: Query writes hit rows in place, leaves miss rows untouched, appends (position,
@@ -28,6 +31,7 @@ constexpr int kWays = 32;
 struct CacheView {
   unsigned long long* keys;   // [nsets * 32]
   unsigned* stamps;           // [nsets * 32]
+  unsigned* vers;             // [nsets * 32] slot sequence numbers (odd while a writer is inside)
   float* values;              // [nsets * 32, dim]
   int* locks;                 // [nsets]
   unsigned* clock;            // global LRU clock
@@ -39,11 +43,18 @@ __device__ __forceinline__ void copy_row(float* __restrict__ dst, const float* _
   for (int v = lane; v < (dim >> 2); v += 32) reinterpret_cast<float4*>(dst)[v] = reinterpret_cast<const float4*>(src)[v];
 }
 
+// Same copy with the source read from L2 (never from a possibly stale L1 line): used by the lock-free hit path, whose
+// sequence-number check only vouches for what L2 holds.
+__device__ __forceinline__ void copy_row_cg(float* __restrict__ dst, const float* src, int dim, int lane) {
+  for (int v = lane; v < (dim >> 2); v += 32) reinterpret_cast<float4*>(dst)[v] = __ldcg(reinterpret_cast<const float4*>(src) + v);
+}
+
 __global__ void cache_init_kernel(CacheView c) {
   const unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < c.nsets * kWays) {
     c.keys[i] = kEmptyKey;
     c.stamps[i] = 0;
+    c.vers[i] = 0;
   }
   if (i < c.nsets) c.locks[i] = 0;
   if (i == 0) *c.clock = 0;
@@ -75,12 +86,20 @@ __global__ void __launch_bounds__(256) cache_query_kernel(CacheView c, const lon
       nline = c.keys[nset * kWays + lane];
     }
     const unsigned hit = __ballot_sync(0xffffffffu, line == key && key != kEmptyKey);
+    bool valid = false;
     if (hit) {
       const int way = __ffs(hit) - 1;
       const unsigned long long slot = set * kWays + way;
-      if (lane == 0) c.stamps[slot] = now;
-      copy_row(out + i * c.dim, c.values + slot * c.dim, c.dim, lane);
-    } else if (lane == 0) {
+      const unsigned v0 = *reinterpret_cast<volatile unsigned*>(&c.vers[slot]);
+      __threadfence();
+      const unsigned long long k0 = *reinterpret_cast<volatile unsigned long long*>(&c.keys[slot]);
+      copy_row_cg(out + i * c.dim, c.values + slot * c.dim, c.dim, lane);
+      __threadfence();
+      const unsigned v1 = *reinterpret_cast<volatile unsigned*>(&c.vers[slot]);
+      valid = __all_sync(0xffffffffu, (v0 & 1u) == 0u && v1 == v0 && k0 == key);
+      if (valid && lane == 0) c.stamps[slot] = now;
+    }
+    if (!valid && lane == 0) {
       const int pos = atomicAdd(miss_count, 1);
       miss_index[pos] = i;
       miss_keys[pos] = static_cast<long long>(key);
@@ -149,11 +168,20 @@ __global__ void __launch_bounds__(256) cache_write_kernel(CacheView c, const lon
     }
     if (way >= 0) {
       const unsigned long long slot = set * kWays + way;
-      if (write_value) copy_row(c.values + slot * c.dim, values + i * c.dim, c.dim, lane);
-      if (lane == 0) {
-        if (!hit) c.keys[slot] = key;
-        if (mode == 0) c.stamps[slot] = now;
+      if (write_value) {
+        // sequence number odd -> key and values change -> even again (readers discard what they copied meanwhile)
+        if (lane == 0) {
+          atomicAdd(&c.vers[slot], 1u);
+          __threadfence();
+        }
+        __syncwarp();
+        copy_row(c.values + slot * c.dim, values + i * c.dim, c.dim, lane);
+        if (lane == 0 && !hit) *reinterpret_cast<volatile unsigned long long*>(&c.keys[slot]) = key;
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(&c.vers[slot], 1u);
       }
+      if (lane == 0 && mode == 0) c.stamps[slot] = now;
     }
     unlock_set(&c.locks[set], lane);
   }
@@ -183,6 +211,7 @@ RS_API int rs_cache_create(unsigned long long num_items, int dim, void** handle)
   const unsigned long long slots = v.nsets * kWays;
   RS_CUDA(cudaMalloc(&v.keys, slots * sizeof(unsigned long long)));
   RS_CUDA(cudaMalloc(&v.stamps, slots * sizeof(unsigned)));
+  RS_CUDA(cudaMalloc(&v.vers, slots * sizeof(unsigned)));
   RS_CUDA(cudaMalloc(&v.values, slots * static_cast<size_t>(dim) * sizeof(float)));
   RS_CUDA(cudaMalloc(&v.locks, v.nsets * sizeof(int)));
   RS_CUDA(cudaMalloc(&v.clock, sizeof(unsigned)));
@@ -195,7 +224,7 @@ RS_API int rs_cache_create(unsigned long long num_items, int dim, void** handle)
 RS_API int rs_cache_destroy(void* handle) {
   if (!handle) return RS_OK;
   CacheOwned* h = static_cast<CacheOwned*>(handle);
-  cudaFree(h->v.keys); cudaFree(h->v.stamps); cudaFree(h->v.values); cudaFree(h->v.locks); cudaFree(h->v.clock);
+  cudaFree(h->v.keys); cudaFree(h->v.stamps); cudaFree(h->v.vers); cudaFree(h->v.values); cudaFree(h->v.locks); cudaFree(h->v.clock);
   delete h;
   return RS_OK;
 }

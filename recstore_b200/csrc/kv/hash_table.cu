@@ -42,10 +42,17 @@ __global__ void ht_lookup_kernel(HashTableView t, const long long* keys, long lo
   rows_out[i] = ht_find(t, static_cast<unsigned long long>(keys[i]));
 }
 
-__global__ void ht_erase_kernel(HashTableView t, const long long* keys, long long n, long long* rows_out) {
+__global__ void ht_erase_kernel(HashTableView t, const long long* keys, long long n, long long* rows_out,
+                                unsigned long long* status) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const int r = ht_erase(t, static_cast<unsigned long long>(keys[i]));
+  const unsigned long long k = static_cast<unsigned long long>(keys[i]);
+  if (k >= kHtTomb) {  // reserved sentinels would match an empty / erased slot: nothing is erased, nothing is freed
+    if (status) atomicOr(status, (unsigned long long)RS_DEV_BAD_ARG);
+    if (rows_out) rows_out[i] = -1;
+    return;
+  }
+  const int r = ht_erase(t, k);
   if (rows_out) rows_out[i] = r;
 }
 
@@ -91,6 +98,13 @@ __global__ void unique_kernel(const long long* keys, long long n, unsigned long 
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const unsigned long long k = static_cast<unsigned long long>(keys[i]);
+  if (k >= kHtTomb) {
+    // The two reserved keys (-1 = empty marker, -2 = tombstone) cannot be told from a free slot: they take no
+    // slot and no output position, their inverse is -1 and the status word says so.
+    if (status) atomicOr(status, (unsigned long long)RS_DEV_BAD_ARG);
+    if (inverse) inverse[i] = -1;
+    return;
+  }
   unsigned long long s = ht_hash(k) & mask;
   for (int p = 0; p < kHtMaxProbe; ++p) {
     unsigned long long cur = __ldcv(&slots_key[s]);
@@ -193,7 +207,16 @@ RS_API int rs_ht_erase(const rs::HashTableView* v, const long long* keys, long l
                        cudaStream_t stream) {
   RS_REQUIRE(v && keys, "rs_ht_erase: null argument");
   if (n == 0) return RS_OK;
-  ht_erase_kernel<<<grid_for(n), 256, 0, stream>>>(*v, keys, n, rows_out);
+  ht_erase_kernel<<<grid_for(n), 256, 0, stream>>>(*v, keys, n, rows_out, nullptr);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+// Same with a status word: the reserved keys -1 / -2 are refused with RS_DEV_BAD_ARG (and row -1).
+RS_API int rs_ht_erase_checked(const rs::HashTableView* v, const long long* keys, long long n, long long* rows_out,
+                               unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(v && keys, "rs_ht_erase_checked: null argument");
+  if (n == 0) return RS_OK;
+  ht_erase_kernel<<<grid_for(n), 256, 0, stream>>>(*v, keys, n, rows_out, status);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
@@ -225,7 +248,9 @@ RS_API int rs_ht_check(const rs::HashTableView* v, unsigned long long* live, lon
   return RS_OK;
 }
 
-// Deduplicates keys[0..n).  Scratch (caller-provided): slots_key [nslots] u64, slots_idx [nslots] i32 with
+// Deduplicates keys[0..n).  Keys are 64-bit patterns; the two reserved ones (-1 and -2 as signed values) are not
+// deduplicated: their inverse is -1, they do not appear in unique_out and RS_DEV_BAD_ARG is set in the status word.
+// Scratch (caller-provided): slots_key [nslots] u64, slots_idx [nslots] i32 with
 // nslots a power of two >= 2 n.  Outputs: unique_out [<= n], inverse [n] (optional), count (device int).
 RS_API int rs_unique_keys(const long long* keys, long long n, void* slots_key, void* slots_idx,
                           unsigned long long nslots, long long* unique_out, int* inverse, int* count,

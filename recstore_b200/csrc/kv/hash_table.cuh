@@ -9,6 +9,9 @@
 // from fmix64(key) & mask.  A slot is claimed with one 64-bit CAS on the key; the row index is
 // published afterwards, readers that see the key but not yet the row spin a bounded number of
 // times (insert and lookup of the same key inside one kernel launch is supported).
+//
+// Reserved keys: 0xFFFF...FF (-1, empty slot) and 0xFFFF...FE (-2, tombstone).  Insert, erase and unique refuse
+// them (row / inverse -1, RS_DEV_BAD_ARG in the status word); lookup of either returns -1.
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -53,6 +56,7 @@ __device__ __forceinline__ int ht_wait_row(const int* p) {
 
 // Returns the row of `key`, or -1 when absent.
 __device__ __forceinline__ int ht_find(const HashTableView& t, unsigned long long key) {
+  if (key >= kHtTomb) return -1;
   unsigned long long s = ht_hash(key) & t.mask;
   for (int p = 0; p < kHtMaxProbe; ++p) {
     const unsigned long long k = __ldcv(&t.keys[s]);

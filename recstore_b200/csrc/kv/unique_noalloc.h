@@ -26,8 +26,12 @@
 //     the caller's stream.  Two calls whose kernels can overlap on the GPU (different streams without
 //     an ordering between them, or different host threads) race on the array and give wrong results:
 //     order them.
+//   * Keys are 64-bit patterns.  Two of them are reserved for the hash slots themselves: -1 (empty) and -2
+//     (tombstone), read as signed values.  Such a key takes no output position: inverse[i] = -1, it is not
+//     counted, and RS_DEV_BAD_ARG is ORed into the status word.  Map padding ids to something else first.
 //   * The order of unique_out is arbitrary (first hash-slot claimer wins), as for rs_unique_keys;
-//     unique_out[inverse[i]] == keys[i] holds for every i.
+//     unique_out[inverse[i]] == keys[i] holds for every i
+//     whose key is not reserved.
 #pragma once
 #include <cuda_runtime.h>
 

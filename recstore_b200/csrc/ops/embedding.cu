@@ -13,9 +13,9 @@
 // 2-12, static_hash_table.cu:223-268).
 //
 // Backward (rs_emb_backward): consumes per-bag gradients (as pushed by the peers into this
-// rank's gradient window), segment-reduces duplicate rows inside each 256-occurrence group
-// with a shared-memory hash + linked lists, and applies SGD or row-wise Adagrad in place with
-// one vector atomic per (group, distinct row).  Semantics follow the reference optimizers
+// rank's gradient window), counting-sorts each 256-occurrence group by row in shared memory so
+// that equal rows are adjacent, sums every run in registers and applies SGD or row-wise Adagrad in
+// place with one vector atomic per run.  Semantics follow the reference optimizers
 // (src/python/pytorch/recstore/DistOpt.py:511-557): state[row] += sum over occurrences of
 // mean(g^2); W[row] -= lr * sum over occurrences of g / (sqrt(state[row]) + eps), with the
 // state read after all occurrences of the step were accumulated (hence two passes).

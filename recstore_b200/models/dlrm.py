@@ -99,7 +99,15 @@ class StepHandle:
     def result(self) -> float:
         """Waits for the step and returns this rank's share of the mean BCE loss (sum over ranks = loss)."""
         self._ev.synchronize()
-        return float(self._e._loss_host[self._slot].item())
+        e = self._e
+        word = int(e._status_host[self._slot].item()) & 0xFFFFFFFFFFFFFFFF
+        if word:
+            # A kernel of this step (or an earlier one) gave up a bounded wait, met an id outside its table or a full
+            # window: what the step computed from that point on is not to be trusted.
+            e.ctx.status.zero_()
+            raise _lib.DeviceStatusError(_lib.ERR_TIMEOUT if word & _lib.DEV_WAIT_TIMEOUT else _lib.ERR_INVALID,
+                                         "device status after the step: " + _lib.decode_status(word))
+        return float(e._loss_host[self._slot].item())
 
 
 class DLRM:
@@ -308,6 +316,7 @@ class DLRM:
         self.in_labels = [torch.empty(Bl, **f32) for _ in range(2)]
         self._loss_dev = [torch.zeros(1, **f32) for _ in range(2)]
         self._loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self._status_host = [torch.zeros(1, dtype=torch.int64).pin_memory() for _ in range(2)]   # the device status word, read back with the loss
         self.copy_stream = torch.cuda.Stream(device=dev)
         self.compute_stream = torch.cuda.Stream(device=dev)
         self._copied = [torch.cuda.Event() for _ in range(2)]
@@ -615,6 +624,7 @@ class DLRM:
                 self._run_step(slot)
             self._consumed[slot].record(ms)
             self._loss_host[slot].copy_(self._loss_dev[slot], non_blocking=True)
+            self._status_host[slot].copy_(self.ctx.status, non_blocking=True)
             self._done[slot].record(ms)
         return StepHandle(self, slot, self._done[slot])
 

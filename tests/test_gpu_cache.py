@@ -59,6 +59,36 @@ def test_unique_keys(dev):
     assert torch.equal(u[inv], keys)
 
 
+def test_reserved_keys_are_refused_not_miscounted(dev):
+    """-1 (empty marker) and -2 (tombstone) mixed into a batch: unique() gives them inverse -1 and does not count
+    them, erase() frees nothing for them, and both say so in the status word.  Compared with a CPU oracle."""
+    from recstore_b200 import _lib
+    from recstore_b200.cache import GpuHashTable, unique_keys
+    g = torch.Generator().manual_seed(5)
+    keys = torch.randint(0, 300, (4000,), generator=g)
+    keys[::7] = -1
+    keys[3::11] = -2
+    st = torch.zeros(1, dtype=torch.int64, device=dev)
+    u, inv = unique_keys(keys.to(dev), st)
+    u, inv = u.cpu(), inv.cpu()
+    real = keys >= 0
+    assert st.item() & _lib.DEV_BAD_ARG
+    assert torch.equal(torch.sort(u).values, torch.unique(keys[real]))          # count and contents: CPU oracle
+    assert (inv[~real] == -1).all()
+    assert torch.equal(u[inv[real]], keys[real])
+    ht = GpuHashTable(capacity=1 << 12, max_rows=1000, device=dev)
+    ht.insert(torch.arange(100))
+    assert ht.status.item() == 0
+    r = ht.erase(torch.tensor([-1, -2, 5, -1])).cpu()
+    assert r[0] == -1 and r[1] == -1 and r[3] == -1 and r[2] >= 0
+    assert ht.status.item() & _lib.DEV_BAD_ARG
+    live, size, bad = ht.check()
+    assert live == size == 99 and bad == 0                                      # only key 5 went away; free stack intact
+    assert (ht.lookup(torch.tensor([-1, -2])).cpu() == -1).all()
+    r2 = ht.insert(torch.tensor([1000, 1001])).cpu()
+    assert (r2 >= 0).all() and r2.max() < 1000 and len(set(r2.tolist())) == 2
+
+
 def test_gpu_cache_query_replace_update_dump(dev):
     from recstore_b200.cache import GpuCache, merge_op
     D = 32

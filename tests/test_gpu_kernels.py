@@ -351,6 +351,25 @@ def test_dlrm_step_matches_torch_oracle(dev, graph):
     assert losses[-1][0] < losses[0][0]
 
 
+def test_train_step_raises_on_out_of_range_ids(dev):
+    """An id outside its table is skipped by the kernels and recorded in the device status word; the step's result
+    must not be handed out as if nothing happened: ``train_step`` reads the word with the loss and raises."""
+    from recstore_b200 import _lib
+    from recstore_b200.models.dlrm import DLRM, DLRMConfig
+    from recstore_b200.utils.data import DLRMBatchSource
+    rows, B = [100, 50, 2000], 256
+    eng = DLRM(DLRMConfig(table_rows=rows, batch=B, emb_dim=64, bottom_mlp=(64, 64), top_mlp=(64, 1), seed=1))
+    src = DLRMBatchSource(rows, [1, 1, 1], B, alpha=1.1, seed=2)
+    b = src.next()
+    assert eng.train_step(eng.make_pinned_batch(b.dense, b.ids, b.labels)) > 0
+    bad = [i.clone() for i in b.ids]
+    bad[1][7] = 50                                   # one past the last row of table 1
+    with pytest.raises(_lib.DeviceStatusError) as e:
+        eng.train_step(eng.make_pinned_batch(b.dense, bad, b.labels))
+    assert "oob_row" in str(e.value)
+    assert eng.train_step(eng.make_pinned_batch(b.dense, b.ids, b.labels)) > 0     # the word was cleared, the engine goes on
+
+
 def test_bounded_wait_times_out_without_hanging(dev):
     """A flag wait that nothing satisfies returns after its time limit with an error status; the CUDA
     context stays usable (no trap, no hang)."""

@@ -9,19 +9,21 @@ checks that an oversized batch is refused with a clear error.  The file is named
 it last.
 """
 import ctypes as C
-from pathlib import Path
 
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
 
-LIB = Path(__file__).resolve().parent.parent / "recstore_b200" / "lib" / "librecstore_b200.so"
 MAX_KEYS = 1 << 17
 
 
 def _load():
-    lib = C.CDLL(str(LIB))
+    # The package's loader builds the library when it is missing and honours RECSTORE_B200_LIB; the symbols are then
+    # looked up on a plain ctypes handle of that same file, so the call goes through the exported C symbol.
+    from recstore_b200 import _lib
+    _lib.lib()
+    lib = C.CDLL(str(_lib.lib_path()))
     vp, i64, u64 = C.c_void_p, C.c_longlong, C.c_ulonglong
     lib.rs_unique_keys_noalloc.restype = C.c_int
     lib.rs_unique_keys_noalloc.argtypes = [vp, i64, vp, vp, vp, vp, vp]
