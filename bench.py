@@ -146,16 +146,21 @@ def run_native(args):
     from recstore_b200.utils.data import DLRMBatchSource
     rank, world, local = dist_setup(args.gpus)
     dcn = args.workload == "dcnv2"
+    B = args.batch
     rows = dcn_table_rows(args.seed) if dcn else table_rows(args.seed)
     hot = DCN_HOTNESS if dcn else [1] * TABLES
     ctx = PeerContext(rank, world, device=torch.device(f"cuda:{local}"))
-    extra = dict(interaction="dcn", dcn_layers=3, dcn_rank=512, hotness=hot, top_mlp=(1024, 1024, 512, 256, 1)) if dcn else {}
+    # dcnv2: the heavy multi-hot tables are spread row-wise over the ranks (--row-split none keeps every table whole on
+    # one rank), the others are placed by a greedy on their ids per sample.
+    extra = dict(interaction="dcn", dcn_layers=3, dcn_rank=512, hotness=hot, top_mlp=(1024, 1024, 512, 256, 1),
+                 row_split=(None if args.row_split == "none" else "auto" if args.row_split == "auto" else
+                            [int(t) for t in args.row_split.split(",")]), placement="balanced") if dcn else {}
     # dcnv2: with sum-of-squares row-wise Adagrad a row that occurs n times in a batch moves by ~lr * sqrt(n); the
     # 100-hot Zipf feature repeats its hottest rows ~10^5 times per batch, so the embedding step is kept small.
-    cfg = DLRMConfig(table_rows=rows, batch=BATCH, emb_dim=DIM, emb_lr=0.01 if not dcn else 1e-4, mlp_lr=0.01 if not dcn else 0.001, seed=args.seed,
+    cfg = DLRMConfig(table_rows=rows, batch=B, emb_dim=DIM, emb_lr=0.01 if not dcn else 1e-4, mlp_lr=0.01 if not dcn else 0.001, seed=args.seed,
                      use_cuda_graph=not args.no_graph, trace_phases=args.trace_phases, **extra)
     eng = DLRM(cfg, ctx)
-    src = DLRMBatchSource(rows, hot, BATCH, alpha=1.1 if dcn else ALPHA, seed=args.seed + 1)
+    src = DLRMBatchSource(rows, hot, B, alpha=1.1 if dcn else ALPHA, seed=args.seed + 1)
     nb = 4
     batches = []
     for _ in range(nb):
@@ -167,14 +172,19 @@ def run_native(args):
         last = eng.train_step(batches[i % nb])
     eng.check()
     # ---- device-timed region: exactly K steps, inputs resident on the device
+    # The K-step region is timed `repeats` times (each bracketed by barrier + synchronize, max over ranks); the median
+    # is the value, the spread is reported beside it.
     sampler = ClockSampler(local)
     barrier(world)
     if rank == 0:
         sampler.start()
-    ms_dev = eng.time_steps_on_device(args.steps)
+    samples = []
+    for _ in range(max(1, args.repeats)):
+        barrier(world)
+        samples.append(max_over_ranks(eng.time_steps_on_device(args.steps), world))
     barrier(world)
     clocks = sampler.stop() if rank == 0 else None
-    ms_dev = max_over_ranks(ms_dev, world)
+    ms_dev = statistics.median(samples)
     # ---- end to end: pinned host -> device copies and the loss read back, every step
     barrier(world)
     t0 = time.perf_counter()
@@ -201,20 +211,23 @@ def run_native(args):
     h2d = batches[0].nbytes
     if rank == 0:
         out = {
-            "metric": METRIC if not dcn else "dlrm_dcnv2_train_samples_per_s", "value": BATCH * args.steps / (ms_dev * 1e-3), "unit": "samples/s",
+            "metric": METRIC if not dcn else "dlrm_dcnv2_train_samples_per_s", "value": B * args.steps / (ms_dev * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": f"synthetic (Zipf {1.1 if dcn else 1.2} ids, random-init weights)", "impl": "native",
             "config": {"model": "DLRM dot, 26 tables x dim 128, ~34M rows, bot 13-512-256-128, top 479-1024-1024-512-256-1" if not dcn else
                        "DLRM-DCNv2 multi-hot (sum of hotness 214), 26 tables x dim 128, ~200M rows (largest 40M), bot 13-512-256-128, "
                        "3-layer rank-512 cross network, top 3456-1024-1024-512-256-1",
-                       "global_batch": BATCH, "seq_len": None,
-                       "parallelism": f"table-wise MP embeddings x{world} + DP MLP x{world}",
+                       "global_batch": B, "seq_len": None,
+                       "parallelism": (f"table-wise MP embeddings x{world} + DP MLP x{world}" if not eng.K else
+                                       f"row-wise sharded tables {eng.split_tables} + table-wise MP for the rest x{world} + DP MLP x{world}"),
                        "l2": "working set per step (>=450 MB of windows + ~17 GB of tables) exceeds the 126 MB L2",
                        "optimizer": "row-wise Adagrad (embeddings) + SGD (MLP)", "total_rows": sum(rows)},
             "clocks": clocks,
-            "e2e": {"value": BATCH * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
+            "e2e": {"value": B * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "timed_regions": {"repeats": len(samples), "ms_per_step_min": min(samples) / args.steps,
+                              "ms_per_step_max": max(samples) / args.steps, "value_is": "median"},
             "gpu_launches": eng.launches_per_step * args.steps,
             "launches_per_step": eng.launches_per_step,
             "last_loss_rank0": last,
@@ -301,6 +314,13 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--workload", default="dlrm", choices=["dlrm", "dcnv2"],
                     help="dlrm: the headline config; dcnv2: the multi-hot DLRM-DCNv2 config (native arm only)")
+    ap.add_argument("--row-split", default="auto",
+                    help="dcnv2 workload: tables spread row-wise over the GPUs: auto (those with more than 1/N of the ids per sample), "
+                         "none (every table whole on one GPU) or a comma-separated list of table indices")
+    ap.add_argument("--repeats", type=int, default=5, help="how many times the K-step timed region is measured (median reported)")
+    ap.add_argument("--batch", type=int, default=BATCH,
+                    help="global batch; the headline config is 65,536 (other values are for profiling, e.g. 8,192 on one GPU "
+                         "has the per-GPU dense shapes of the 8-GPU run)")
     ap.add_argument("--trace-phases", action="store_true",
                     help="stamp the GPU timer at phase boundaries of the step and print the timeline of every rank to stderr")
     args = ap.parse_args()

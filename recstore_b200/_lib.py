@@ -64,6 +64,16 @@ _SIGNATURES = {
     # ops/embedding.cu
     "rs_emb_forward": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i64, vp, i32, vp, vp, vp, vp, vp]),
     "rs_emb_backward": (i32, [vp, vp, i64, vp, vp, i64, vp, vp, i64, vp, i32, i32, i32, i32, vp, f32, f32, i32, vp, vp]),
+    "rs_emb_forward_ex": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i64, vp, i32, vp, vp, vp,
+                                vp, i32, i32, vp, vp, vp, u64, i32, vp, vp, i32, i32, i32, vp]),
+    "rs_emb_backward_ex": (i32, [vp, vp, i64, vp, vp, i64, vp, vp, i64, vp, i32, i32, i32, i32, f32, f32, i32, vp,
+                                 vp, vp, vp, u64, i32, i32, vp]),
+    # comm/emb_exchange.cu
+    "rs_push_rows": (i32, [vp, i64, i32, i32, i32, i32, vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i32, i32, vp]),
+    "rs_rw_push_keys": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp]),
+    "rs_rw_reduce_partials": (i32, [vp, vp, vp, i64, i32, i32, i32, i32, vp, vp, u64, i32, vp, vp]),
+    "rs_interaction_forward_ex": (i32, [vp, i32, i32, i32, vp, i32, vp, vp, u64, i32, i32, vp, vp]),
+    "rs_peer_wait_own": (i32, [vp, i32, i32, vp, u64, vp, vp]),
     "rs_rows_gather": (i32, [vp, vp, i64, i32, vp, vp]),
     "rs_rows_scatter": (i32, [vp, vp, i64, i32, vp, vp]),
     # ops/interaction.cu
@@ -80,7 +90,7 @@ _SIGNATURES = {
     "rs_mse_fwd_bwd": (i32, [vp, vp, i32, f32, vp, vp, vp]),
     "rs_cross_fwd": (i32, [vp, vp, vp, vp, i64, vp]),
     "rs_cross_bwd": (i32, [vp, vp, vp, vp, vp, i64, i32, vp]),
-    "rs_push_feature_grads": (i32, [vp, vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, i64, i64, i32, vp, i32, vp, i32, vp]),
+    "rs_push_feature_grads": (i32, [vp, vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, i64, i64, i32, vp, i32, vp, i32, i32, vp]),
     "rs_proj_inter_fwd": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp]),
     "rs_proj_inter_bwd": (i32, [vp, i32, i32, vp, vp, i32, i32, i32, i32, vp, vp, vp]),
     # comm/peer.cu

@@ -69,6 +69,31 @@ __global__ void wait_kernel(const uint32_t* my_flags, int world, int channel, ui
   }
 }
 
+// Same wait, but for this rank's OWN signal epoch on the channel (no wait counter): for channels on which every rank
+// signals exactly once per round from inside a producing kernel (comm/flags.cuh) and the consumer cannot wait in its own
+// prologue (a GEMM fed by TMA).
+__global__ void wait_own_kernel(const uint32_t* my_flags, int world, int channel, const uint32_t* sig_counters,
+                                unsigned long long timeout_ns, unsigned long long* status) {
+  const int s = threadIdx.x;
+  if (s >= world) return;
+  const uint32_t epoch = sig_counters[channel];
+  const uint32_t* f = my_flags + channel * world + s;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (true) {
+    const uint32_t v = ld_acquire_sys(f);
+    if (static_cast<int32_t>(v - epoch) >= 0) break;
+    if ((++spins & 63u) == 0u) {
+      if (globaltimer_ns() - t0 > timeout_ns) {
+        if (status) atomicOr(status, (unsigned long long)RS_DEV_WAIT_TIMEOUT | (static_cast<unsigned long long>(s) << 32) |
+                                         (static_cast<unsigned long long>(channel) << 48));
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
 // Signal then wait on one channel in ONE launch (a barrier of the ranks): lane d publishes this rank's new epoch to
 // rank d, then waits for rank d's flag to reach this rank's new wait epoch.  Same bounds as wait_kernel.
 __global__ void sync_kernel(uint32_t* const* flags_of, const uint32_t* my_flags, int world, int me, int channel,
@@ -101,7 +126,7 @@ __global__ void sync_kernel(uint32_t* const* flags_of, const uint32_t* my_flags,
 
 // grads_of[p]: peer p's gradient buffer; reduced_of[p]: peer p's output buffer; n elements (fp32),
 // slice boundaries in float4 units.
-__global__ void __launch_bounds__(512) allreduce_push_kernel(const float* const* grads_of, float* const* reduced_of,
+__global__ void __launch_bounds__(256) allreduce_push_kernel(const float* const* grads_of, float* const* reduced_of,
                                                              int world, int me, long long off4, long long n4, float scale) {
   const long long per = (n4 + world - 1) / world;
   const long long beg = off4 + per * me;
@@ -177,6 +202,14 @@ RS_API int rs_peer_wait(const void* my_flags, int world, int channel, unsigned* 
   return RS_OK;
 }
 
+RS_API int rs_peer_wait_own(const void* my_flags, int world, int channel, const unsigned* sig_counters,
+                            unsigned long long timeout_ns, unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(my_flags && sig_counters && world >= 1 && world <= 32, "rs_peer_wait_own: bad argument");
+  wait_own_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint32_t*>(my_flags), world, channel, sig_counters, timeout_ns, status);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
 RS_API int rs_peer_sync(void* const* flags_of, const void* my_flags, int world, int me, int channel, unsigned* sig_counters,
                         unsigned* wait_counters, unsigned long long timeout_ns, unsigned long long* status, cudaStream_t stream) {
   RS_REQUIRE(flags_of && my_flags && sig_counters && wait_counters && world >= 1 && world <= 32, "rs_peer_sync: bad argument");
@@ -195,10 +228,11 @@ RS_API int rs_allreduce_push(const void* const* grads_of, void* const* reduced_o
   if (n == 0) return RS_OK;
   const long long n4 = n / 4;
   const long long per = (n4 + world - 1) / world;
-  int grid = static_cast<int>((per + 511) / 512);
-  if (grid > 296) grid = 296;
+  // 256-thread CTAs: small enough in registers to sit on an SM beside a persistent GEMM CTA
+  int grid = static_cast<int>((per + 255) / 256);
+  if (grid > 592) grid = 592;
   if (grid < 1) grid = 1;
-  allreduce_push_kernel<<<grid, 512, 0, stream>>>(reinterpret_cast<const float* const*>(grads_of),
+  allreduce_push_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float* const*>(grads_of),
                                                   reinterpret_cast<float* const*>(reduced_of), world, me, off / 4, n4, scale);
   RS_LAUNCH_CHECK();
   return RS_OK;

@@ -269,6 +269,14 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
 }
 
 // ---------------------------------------------------------------- peer flags (system scope)
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may become
+// resident while the kernel before it on the stream is still draining; pdl_wait() returns once that kernel has
+// completed and its writes are visible (a no-op for a plain launch), so everything before it must touch no data the
+// predecessor produces or reads.  pdl_launch_dependents() lets the NEXT kernel's blocks be scheduled as soon as every
+// block of this grid has issued it (or exited).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

@@ -340,6 +340,7 @@ struct PushArgs {
   int relu_mask_dx;
   float* const* ndst; int nstride;
   const __nv_bfloat16* extra; int extra_ld;   // optional [B, >= D]: added to feature 0 only (a direct path of the dense feature)
+  int world;                                  // a feature whose owner is < 0 (row-sharded table) goes to ranks 0..world-1
 };
 __global__ void __launch_bounds__(256) push_feature_grads_kernel(const PushArgs a) {
   const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -373,20 +374,29 @@ __global__ void __launch_bounds__(256) push_feature_grads_kernel(const PushArgs 
       }
       dst = a.dx + static_cast<long long>(b) * a.dx_ld + d;
     } else {
-      dst = reinterpret_cast<__nv_bfloat16*>(a.gdst[a.owner[f - 1]]) + (a.sample_base + b) * a.grow_stride + a.gcol[f - 1] + d;
+      const int own = a.owner[f - 1];
+      dst = reinterpret_cast<__nv_bfloat16*>(a.gdst[own < 0 ? 0 : own]) + (a.sample_base + b) * a.grow_stride + a.gcol[f - 1] + d;
     }
     __nv_bfloat162 o0 = __floats2bfloat162_rn(v[0], v[1]), o1 = __floats2bfloat162_rn(v[2], v[3]);
     uint2 o;
     o.x = *reinterpret_cast<uint32_t*>(&o0);
     o.y = *reinterpret_cast<uint32_t*>(&o1);
     *reinterpret_cast<uint2*>(dst) = o;
+    if (f > 0 && a.owner[f - 1] < 0) {          // row-sharded table: every rank holds rows of it
+      for (int r = 1; r < a.world; ++r)
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.gdst[r]) + (a.sample_base + b) * a.grow_stride + a.gcol[f - 1] + d) = o;
+    }
     const float2 r0 = __bfloat1622float2(o0), r1 = __bfloat1622float2(o1);
     sq += r0.x * r0.x + r0.y * r0.y + r1.x * r1.x + r1.y * r1.y;
   }
   if (a.ndst && f > 0) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    if (lane == 0) a.ndst[a.owner[f - 1]][(a.sample_base + b) * a.nstride + a.gcol[f - 1] / a.D] = sq;
+    if (lane == 0) {
+      const int own = a.owner[f - 1];
+      const int r0 = own < 0 ? 0 : own, r1 = own < 0 ? a.world : own + 1;
+      for (int r = r0; r < r1; ++r) a.ndst[r][(a.sample_base + b) * a.nstride + a.gcol[f - 1] / a.D] = sq;
+    }
   }
 }
 
@@ -499,7 +509,7 @@ RS_API int rs_cross_bwd(const void* dx, const void* x0, const void* u, void* du,
 RS_API int rs_push_feature_grads(const float* acc, const void* dxb, const void* T, int B, int F, int D, void* dx, int dx_ld,
                                  void* const* gdst, const int* owner, const int* gcol, long long grow_stride,
                                  long long sample_base, int relu_mask_dx, void* const* ndst, int nstride, const void* extra,
-                                 int extra_ld, cudaStream_t stream) {
+                                 int extra_ld, int world, cudaStream_t stream) {
   RS_REQUIRE(dxb && T && dx && gdst && owner && gcol && D % 4 == 0, "rs_push_feature_grads: bad argument");
   RS_REQUIRE(!extra || (extra_ld % 4 == 0 && extra_ld >= D), "rs_push_feature_grads: bad extra gradient");
   if (B == 0) return RS_OK;
@@ -509,6 +519,7 @@ RS_API int rs_push_feature_grads(const float* acc, const void* dxb, const void* 
   a.gcol = gcol; a.grow_stride = grow_stride; a.sample_base = sample_base; a.relu_mask_dx = relu_mask_dx;
   a.ndst = reinterpret_cast<float* const*>(ndst); a.nstride = nstride;
   a.extra = reinterpret_cast<const __nv_bfloat16*>(extra); a.extra_ld = extra_ld;
+  a.world = world < 1 ? 1 : world;
   const long long warps = static_cast<long long>(B) * F;
   push_feature_grads_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(a);
   RS_LAUNCH_CHECK();

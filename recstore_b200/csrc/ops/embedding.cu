@@ -22,7 +22,9 @@
 //
 // No kernel here traps: out-of-range ids set RS_DEV_OOB_ROW in the status word and are skipped.
 #include <cuda_bf16.h>
+#include <cstdlib>
 #include "common/rs_common.h"
+#include "comm/flags.cuh"
 #include "kv/hash_table.cuh"
 
 namespace {
@@ -46,6 +48,16 @@ struct EmbFwdArgs {
   int use_hash;
   rs::HashTableView ht;
   unsigned long long* status;
+  // Row-sharded tables (a table spread cyclically over the ranks, this rank holding ids with id % id_div == id_rem at
+  // local row id / id_div): the ids of a bag arrive from the sample's rank in a fixed-capacity region of `hotness`
+  // slots, of which only counts[bag] are filled.
+  const int* counts;             // [T*B] or null
+  int id_div, id_rem;            // 1, 0 for whole tables
+  // Occurrence list for the backward pass, compacted: positions come from an atomic cursor instead of the id's index
+  // (the regions above are mostly holes).  Null = write at the id's own index.
+  int* occ_cursor;
+  rs::FlagWait wait;             // optional: wait for the source rank's keys before reading a bag
+  rs::FlagSignal sig;            // optional: publish "my pooled rows have landed" when the grid is done
 };
 
 constexpr int kMaxChunks = 4;  // D <= 512
@@ -78,7 +90,7 @@ __device__ __forceinline__ void store_pooled(const EmbFwdArgs& a, int t, int b, 
 // bag i (id range, and for single-id bags the row itself) with coalesced loads; the rows are then
 // fetched 8 bags at a time so that every warp keeps 8 independent 512-byte reads in flight.
 template <int NC>
-__global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
+__device__ __forceinline__ void emb_fwd_body(const EmbFwdArgs& a) {
   const int warps_per_block = blockDim.x >> 5;
   const long long blk = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -91,6 +103,11 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
   const long long nrows = a.table_rows[t];
   const int nvec = a.D >> 2;
 
+  if (a.wait.my_flags != nullptr) {
+    // The bags of this warp come from one source rank (two when the block of 32 straddles a boundary).
+    const int s0 = b0 / a.B_local, s1 = (b0 + nb - 1) / a.B_local;
+    for (int src = s0; src <= s1; ++src) rs::flag_wait_one_warp(a.wait, src);
+  }
   long long beg = 0, end = 0;
   if (lane < nb) {
     const long long bag = static_cast<long long>(t) * a.B + b0 + lane;
@@ -100,17 +117,26 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
     } else {
       const int h = a.hotness[t];
       beg = a.hot_base[t] + static_cast<long long>(b0 + lane) * h;
-      end = beg + h;
+      end = beg + (a.counts ? min(max(__ldcv(a.counts + bag), 0), h) : h);
     }
   }
-  const bool single = __all_sync(0xffffffffu, lane >= nb || end - beg == 1);
+  const bool sharded = a.id_div > 1;
+  auto resolve = [&](long long id) -> long long {
+    if (a.use_hash) return rs::ht_find(a.ht, static_cast<unsigned long long>(id));
+    if (!sharded) {
+      if (id >= 0 && id < nrows) return base + id;
+    } else if (id >= 0 && id % a.id_div == a.id_rem && id / a.id_div < nrows) {
+      return base + id / a.id_div;
+    }
+    if (a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
+    return -1;
+  };
+  const bool single = a.counts == nullptr && a.occ_cursor == nullptr && __all_sync(0xffffffffu, lane >= nb || end - beg == 1);
   if (single && a.psw == nullptr) {
     long long my_row = -1;
     if (lane < nb) {
       const long long id = a.indices[beg];
-      if (a.use_hash) my_row = rs::ht_find(a.ht, static_cast<unsigned long long>(id));
-      else if (id >= 0 && id < nrows) my_row = base + id;
-      else if (a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
+      my_row = resolve(id);
       if (a.row_idx) a.row_idx[beg] = my_row;
       if (a.occ2bag) a.occ2bag[beg] = static_cast<int>(static_cast<long long>(t) * a.B + b0 + lane);
     }
@@ -145,14 +171,18 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
       const int n = static_cast<int>(min(32ll, je - i0));
       long long my_row = -1;
       float my_w = 1.f;
+      long long opos = i0;                        // where this chunk's occurrences are recorded
+      if (a.occ_cursor != nullptr) {
+        int p = 0;
+        if (lane == 0) p = atomicAdd(a.occ_cursor, n);
+        opos = __shfl_sync(0xffffffffu, p, 0);
+      }
       if (lane < n) {
-        const long long id = a.indices[i0 + lane];
-        if (a.use_hash) my_row = rs::ht_find(a.ht, static_cast<unsigned long long>(id));
-        else if (id >= 0 && id < nrows) my_row = base + id;
-        else if (a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
+        const long long id = a.counts ? __ldcv(a.indices + i0 + lane) : a.indices[i0 + lane];   // pushed by a peer: not through L1
+        my_row = resolve(id);
         if (a.psw) my_w = a.psw[i0 + lane];
-        if (a.row_idx) a.row_idx[i0 + lane] = my_row;
-        if (a.occ2bag) a.occ2bag[i0 + lane] = static_cast<int>(bag);
+        if (a.row_idx) a.row_idx[opos + lane] = my_row;
+        if (a.occ2bag) a.occ2bag[opos + lane] = static_cast<int>(bag);
       }
       for (int k0 = 0; k0 < n; k0 += 4) {
         long long r[4];
@@ -185,6 +215,12 @@ __global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
   }
 }
 
+template <int NC>
+__global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
+  emb_fwd_body<NC>(a);
+  rs::flag_publish_when_grid_done(a.sig);   // (no-op without a signal) every thread arrives here: the body only returns early
+}
+
 // ------------------------------------------------------------------ backward
 struct EmbBwdArgs {
   float* weight;
@@ -203,7 +239,15 @@ struct EmbBwdArgs {
   int optimizer;                 // 0 = SGD, 1 = row-wise Adagrad
   long long total_rows;
   unsigned long long* status;
+  const int* nnz_dev;            // optional: the live number of occurrences (<= nnz) as counted on the device
+  rs::FlagWait wait;             // optional: wait for the peers' gradient pushes first
 };
+
+__device__ __forceinline__ long long live_nnz(const EmbBwdArgs& a) {
+  if (a.nnz_dev == nullptr) return a.nnz;
+  const long long n = *reinterpret_cast<const volatile int*>(a.nnz_dev);
+  return n < a.nnz ? n : a.nnz;
+}
 
 constexpr int kGroup = 256;
 constexpr int kSlots = 512;
@@ -233,7 +277,10 @@ __device__ __forceinline__ void load_grad(const EmbBwdArgs& a, long long goff, i
 template <int NC>
 __global__ void __launch_bounds__(256) emb_state_kernel(const EmbBwdArgs a) {
   const float inv_d = 1.f / static_cast<float>(a.D);
+  const long long nnz = live_nnz(a);
   if (a.gnorm) {
+    if (static_cast<long long>(blockIdx.x) * blockDim.x >= nnz) return;   // whole block past the live occurrences
+    rs::flag_wait_all(a.wait);
     // One thread per occurrence; equal rows of the block are combined in a shared-memory hash first, so a hot
     // row costs one global atomic per block instead of one per occurrence.
     __shared__ long long s_key[kSlots];
@@ -244,7 +291,7 @@ __global__ void __launch_bounds__(256) emb_state_kernel(const EmbBwdArgs a) {
     }
     __syncthreads();
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i < a.nnz) {
+    if (i < nnz) {
       const long long row = a.row_idx[i];
       if (row >= 0 && row < a.total_rows) {
         const long long bag = a.occ2bag ? a.occ2bag[i] : i;
@@ -270,8 +317,10 @@ __global__ void __launch_bounds__(256) emb_state_kernel(const EmbBwdArgs a) {
       if (s_key[s] >= 0) atomicAdd(&a.state[s_key[s]], s_val[s]);
     return;
   }
+  if (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) >= nnz) return;
+  rs::flag_wait_all(a.wait);
   const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (i >= a.nnz) return;
+  if (i >= nnz) return;
   const int lane = threadIdx.x & 31;
   const long long row = a.row_idx[i];
   if (row < 0 || row >= a.total_rows) return;
@@ -332,6 +381,9 @@ __global__ void __launch_bounds__(kGroup) emb_apply_kernel(const EmbBwdArgs a) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const long long g0 = static_cast<long long>(blockIdx.x) * kGroup;
+  const long long nnz = live_nnz(a);
+  if (g0 >= nnz) return;                       // whole group past the live occurrences
+  rs::flag_wait_all(a.wait);
   for (int s = tid; s < kSlots; s += kGroup) {
     s_key[s] = -1;
     s_cnt[s] = 0;
@@ -341,7 +393,7 @@ __global__ void __launch_bounds__(kGroup) emb_apply_kernel(const EmbBwdArgs a) {
   long long row = -1, goff = 0;
   float w = 1.f;
   int slot = -1, rank = 0;
-  if (g0 + tid < a.nnz) {
+  if (g0 + tid < nnz) {
     const long long occ = g0 + tid;
     row = a.row_idx[occ];
     if (row >= a.total_rows) {
@@ -496,6 +548,23 @@ __global__ void rows_scatter_kernel(float* __restrict__ w, const long long* __re
 
 }  // namespace
 
+namespace {
+int launch_emb_fwd(const EmbFwdArgs& a, cudaStream_t stream) {
+  if (a.T == 0 || a.B == 0) return RS_OK;
+  const long long nblocks = static_cast<long long>(a.T) * ((a.B + 31) / 32);
+  // Four warps per CTA: at 64 registers per thread such a CTA still fits on an SM beside one persistent GEMM CTA, so the
+  // lookup and its NVLink pushes really run at the same time as the MLP that is launched beside them.
+  static const int wpb = [] { const char* e = getenv("RECSTORE_EMB_FWD_WARPS"); return (e && e[0] == '8') ? 8 : 4; }();
+  const long long grid = (nblocks + wpb - 1) / wpb;
+  RS_REQUIRE(grid < (1ll << 31), "rs_emb_forward: too many bags");
+  if (a.D <= 128) emb_fwd_kernel<1><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
+  else if (a.D <= 256) emb_fwd_kernel<2><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
+  else emb_fwd_kernel<4><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+}  // namespace
+
 RS_API int rs_emb_forward(const float* weight, const long long* table_base, const long long* table_rows,
                           const long long* indices, const long long* offsets, const int* hotness,
                           const long long* hot_base, const float* psw, int T, int B, int D, int B_local,
@@ -506,34 +575,100 @@ RS_API int rs_emb_forward(const float* weight, const long long* table_base, cons
   RS_REQUIRE(offsets || (hotness && hot_base), "rs_emb_forward: need offsets or fixed hotness");
   RS_REQUIRE(D % 4 == 0 && D > 0 && D <= 128 * kMaxChunks, "rs_emb_forward: D=%d must be a multiple of 4, <= 512", D);
   RS_REQUIRE(T >= 0 && B >= 0 && B_local > 0, "rs_emb_forward: bad sizes");
-  if (T == 0 || B == 0) return RS_OK;
   EmbFwdArgs a;
+  memset(&a, 0, sizeof(a));
   a.weight = weight; a.table_base = table_base; a.table_rows = table_rows; a.indices = indices;
   a.offsets = offsets; a.hotness = hotness; a.hot_base = hot_base; a.psw = psw;
   a.T = T; a.B = B; a.D = D; a.B_local = B_local; a.dst = dst; a.dst_row_stride = dst_row_stride;
   a.dst_col = dst_col; a.out_bf16 = out_bf16; a.row_idx = row_idx; a.occ2bag = occ2bag;
   a.use_hash = ht != nullptr;
-  if (ht) a.ht = *ht; else memset(&a.ht, 0, sizeof(a.ht));
+  if (ht) a.ht = *ht;
   a.status = status;
-  const long long nblocks = static_cast<long long>(T) * ((B + 31) / 32);
-  const int wpb = 8;
-  const long long grid = (nblocks + wpb - 1) / wpb;
-  RS_REQUIRE(grid < (1ll << 31), "rs_emb_forward: too many bags");
-  if (D <= 128) emb_fwd_kernel<1><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
-  else if (D <= 256) emb_fwd_kernel<2><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
-  else emb_fwd_kernel<4><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
-  RS_LAUNCH_CHECK();
-  return RS_OK;
+  a.id_div = 1; a.id_rem = 0;
+  return launch_emb_fwd(a, stream);
+}
+
+// The same lookup with the extras of the multi-GPU engine.
+//   counts / id_div / id_rem / occ_cursor: bags of a row-sharded table (see EmbFwdArgs); occ_cursor must be zero on entry.
+//   wait_flags ... wait_channel:  each warp first waits (bounded) for the flag of the rank its bags come from.
+//   sig_flags_of ... sig_channel: when the whole grid is done its last block publishes this rank's next epoch on the
+//                                  channel to every rank (data then flag, one launch).  sig_done: a zeroed device counter.
+RS_API int rs_emb_forward_ex(const float* weight, const long long* table_base, const long long* table_rows,
+                             const long long* indices, const int* hotness, const long long* hot_base, int T, int B, int D,
+                             int B_local, void* const* dst, long long dst_row_stride, const int* dst_col, int out_bf16,
+                             long long* row_idx, int* occ2bag, unsigned long long* status,
+                             const int* counts, int id_div, int id_rem, int* occ_cursor,
+                             const void* wait_flags, const unsigned* counters, unsigned long long timeout_ns, int wait_channel,
+                             void* const* sig_flags_of, unsigned* sig_done, int sig_channel, int world, int me,
+                             cudaStream_t stream) {
+  RS_REQUIRE(weight && table_base && table_rows && indices && dst && dst_col && hotness && hot_base, "rs_emb_forward_ex: null argument");
+  RS_REQUIRE(D % 4 == 0 && D > 0 && D <= 128 * kMaxChunks, "rs_emb_forward_ex: D=%d must be a multiple of 4, <= 512", D);
+  RS_REQUIRE(T >= 0 && B >= 0 && B_local > 0 && id_div >= 1 && id_rem >= 0 && id_rem < id_div, "rs_emb_forward_ex: bad sizes");
+  RS_REQUIRE(world >= 1 && world <= 32 && me >= 0 && me < world, "rs_emb_forward_ex: bad rank / world");
+  RS_REQUIRE((!wait_flags && !sig_flags_of) || counters, "rs_emb_forward_ex: flags need the epoch counters");
+  RS_REQUIRE(!sig_flags_of || sig_done, "rs_emb_forward_ex: a signal needs its done counter");
+  EmbFwdArgs a;
+  memset(&a, 0, sizeof(a));
+  a.weight = weight; a.table_base = table_base; a.table_rows = table_rows; a.indices = indices;
+  a.hotness = hotness; a.hot_base = hot_base;
+  a.T = T; a.B = B; a.D = D; a.B_local = B_local; a.dst = dst; a.dst_row_stride = dst_row_stride;
+  a.dst_col = dst_col; a.out_bf16 = out_bf16; a.row_idx = row_idx; a.occ2bag = occ2bag;
+  a.status = status;
+  a.counts = counts; a.id_div = id_div; a.id_rem = id_rem; a.occ_cursor = occ_cursor;
+  a.wait.my_flags = reinterpret_cast<const uint32_t*>(wait_flags); a.wait.sig_counters = counters;
+  a.wait.timeout_ns = timeout_ns; a.wait.status = status; a.wait.world = world; a.wait.channel = wait_channel;
+  a.sig.flags_of = reinterpret_cast<uint32_t* const*>(sig_flags_of); a.sig.sig_counters = const_cast<unsigned*>(counters);
+  a.sig.done = sig_done; a.sig.world = world; a.sig.me = me; a.sig.channel = sig_channel;
+  if ((T == 0 || B == 0) && sig_flags_of) return rs::set_error(RS_ERR_INVALID, "rs_emb_forward_ex: an empty lookup cannot carry the signal");
+  return launch_emb_fwd(a, stream);
 }
 
 // optimizer: 0 SGD (one launch), 1 row-wise Adagrad (two launches: state pass, apply pass).
 // gnorm (optional): precomputed sum of squares of every bag gradient, [B, gnorm_stride] fp32 indexed
 // [sample, local table]; saves the state pass a full read of the gradients.
+namespace {
+int emb_backward_impl(float* weight, float* state, long long total_rows, const long long* row_idx,
+                      const int* occ2bag, long long nnz, const void* grad, const int* grad_col,
+                      long long grad_row_stride, const float* gnorm, int gnorm_stride, int B, int D,
+                      int grad_bf16, const float* psw, float lr, float eps, int optimizer,
+                      unsigned long long* status, const int* nnz_dev, const rs::FlagWait& wait, cudaStream_t stream);
+}  // namespace
+
 RS_API int rs_emb_backward(float* weight, float* state, long long total_rows, const long long* row_idx,
                            const int* occ2bag, long long nnz, const void* grad, const int* grad_col,
                            long long grad_row_stride, const float* gnorm, int gnorm_stride, int B, int D,
                            int grad_bf16, const float* psw, float lr, float eps, int optimizer,
                            unsigned long long* status, cudaStream_t stream) {
+  rs::FlagWait w;
+  memset(&w, 0, sizeof(w));
+  return emb_backward_impl(weight, state, total_rows, row_idx, occ2bag, nnz, grad, grad_col, grad_row_stride, gnorm, gnorm_stride,
+                           B, D, grad_bf16, psw, lr, eps, optimizer, status, nullptr, w, stream);
+}
+
+// The same update with the extras of the multi-GPU engine: nnz_dev (optional) is the live occurrence count on the device
+// (nnz is then the capacity of the lists and sizes the grids); wait_flags (optional) makes the first kernel wait, bounded,
+// until every rank's flag on `wait_channel` has reached this rank's own epoch (the peers' gradient pushes have landed).
+RS_API int rs_emb_backward_ex(float* weight, float* state, long long total_rows, const long long* row_idx,
+                              const int* occ2bag, long long nnz, const void* grad, const int* grad_col,
+                              long long grad_row_stride, const float* gnorm, int gnorm_stride, int B, int D,
+                              int grad_bf16, float lr, float eps, int optimizer, unsigned long long* status,
+                              const int* nnz_dev, const void* wait_flags, const unsigned* counters, unsigned long long timeout_ns,
+                              int wait_channel, int world, cudaStream_t stream) {
+  rs::FlagWait w;
+  memset(&w, 0, sizeof(w));
+  w.my_flags = reinterpret_cast<const uint32_t*>(wait_flags); w.sig_counters = counters; w.timeout_ns = timeout_ns;
+  w.status = status; w.world = world; w.channel = wait_channel;
+  RS_REQUIRE(!wait_flags || (counters && world >= 1 && world <= 32), "rs_emb_backward_ex: bad flag arguments");
+  return emb_backward_impl(weight, state, total_rows, row_idx, occ2bag, nnz, grad, grad_col, grad_row_stride, gnorm, gnorm_stride,
+                           B, D, grad_bf16, nullptr, lr, eps, optimizer, status, nnz_dev, w, stream);
+}
+
+namespace {
+int emb_backward_impl(float* weight, float* state, long long total_rows, const long long* row_idx,
+                      const int* occ2bag, long long nnz, const void* grad, const int* grad_col,
+                      long long grad_row_stride, const float* gnorm, int gnorm_stride, int B, int D,
+                      int grad_bf16, const float* psw, float lr, float eps, int optimizer,
+                      unsigned long long* status, const int* nnz_dev, const rs::FlagWait& wait, cudaStream_t stream) {
   RS_REQUIRE(weight && row_idx && grad, "rs_emb_backward: null argument");
   RS_REQUIRE(optimizer == 0 || (optimizer == 1 && state), "rs_emb_backward: row-wise Adagrad needs a state tensor");
   RS_REQUIRE(D % 4 == 0 && D > 0 && D <= 128 * kMaxChunks, "rs_emb_backward: D=%d must be a multiple of 4, <= 512", D);
@@ -544,6 +679,7 @@ RS_API int rs_emb_backward(float* weight, float* state, long long total_rows, co
   a.grad_col = grad_col; a.grad_row_stride = grad_row_stride; a.gnorm = gnorm; a.gnorm_stride = gnorm_stride;
   a.B = B; a.D = D; a.grad_bf16 = grad_bf16;
   a.psw = psw; a.lr = lr; a.eps = eps; a.optimizer = optimizer; a.total_rows = total_rows; a.status = status;
+  a.nnz_dev = nnz_dev; a.wait = wait;
   const long long grid = (nnz + kGroup - 1) / kGroup;
   RS_REQUIRE(grid < (1ll << 31), "rs_emb_backward: too many occurrences");
   const int nc = D <= 128 ? 1 : (D <= 256 ? 2 : 4);
@@ -568,6 +704,8 @@ RS_API int rs_emb_backward(float* weight, float* state, long long total_rows, co
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
+
+}  // namespace
 
 RS_API int rs_rows_gather(const float* weight, const long long* rows, long long n, int D, float* out,
                           cudaStream_t stream) {

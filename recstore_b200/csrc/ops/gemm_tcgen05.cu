@@ -175,6 +175,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   if (CG == 2) cluster_sync_all();   // the peer's barriers are initialised before anything is signalled across CTAs
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above (barriers, TMEM, descriptor prefetch) touched no tensor: with a programmatic dependent launch it
+  // ran while the previous kernel on the stream was still draining.  From here on its results are needed.
+  pdl_launch_dependents();
+  pdl_wait();
   // Releasing an accumulator: an arrival on the leader's tempty barrier (local for CG = 1).
   auto release_acc = [&](int a) {
     if (CG == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[a]), 0));
@@ -821,13 +825,28 @@ RS_API int rs_gemm_bf16(const void* A, const void* B, void* D, const float* bias
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = static_cast<unsigned>(cg);
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  // Programmatic dependent launch (RECSTORE_GEMM_PDL=0 switches it off): the prologue of this GEMM overlaps the tail
+  // of the kernel before it on the stream, which matters when a step is a chain of short GEMMs.
+  static const bool pdl = [] {
+    const char* e = getenv("RECSTORE_GEMM_PDL");
+    return !(e && e[0] == '0');
+  }();
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (cg == 2) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = static_cast<unsigned>(cg);
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = cg == 2 ? 1 : 0;
+  cfg.numAttrs = na;
   RS_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, md, g));
   RS_LAUNCH_CHECK();
   return RS_OK;

@@ -13,6 +13,7 @@
 // The per-sample products are 32x32x128 / 32x128x32, far below one tcgen05 tile, and the op is
 // bound by the bytes of T; warp-level mma.m16n8k16 keeps it at memory speed.
 #include <cuda_bf16.h>
+#include "comm/flags.cuh"
 #include "common/rs_common.h"
 
 namespace {
@@ -69,10 +70,12 @@ __device__ __forceinline__ void load_tile_async(__nv_bfloat16* sT, const __nv_bf
 // Persistent warps: every warp walks samples b = first, first + stride, ...; the positions of this lane's
 // accumulator elements inside the output row (strict lower triangle, row-major) are worked out once.
 __global__ void __launch_bounds__(kWarps * 32) interaction_fwd_kernel(const __nv_bfloat16* __restrict__ T, int B, int F,
-                                                                      int D, __nv_bfloat16* __restrict__ out, int out_ld) {
+                                                                      int D, __nv_bfloat16* __restrict__ out, int out_ld,
+                                                                      const rs::FlagWait wait) {
   __shared__ __align__(16) __nv_bfloat16 sT[kWarps][32 * kLd];
   __shared__ __align__(16) __nv_bfloat16 sO[kWarps][kMaxD + kMaxF * (kMaxF - 1) / 2 + 8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  rs::flag_wait_all(wait);   // multi-GPU: the peers' pooled rows have landed in T (no-op without flags)
   __nv_bfloat16* t = sT[warp];
   __nv_bfloat16* o = sO[warp];
   zero_tail_rows(t, F, D, lane);
@@ -394,7 +397,28 @@ RS_API int rs_interaction_dx(const void* T, const void* dout, int B, int F, int 
   return RS_OK;
 }
 
+namespace {
+int interaction_forward_impl(const void* T, int B, int F, int D, void* out, int out_ld, const rs::FlagWait& wait, cudaStream_t stream);
+}
 RS_API int rs_interaction_forward(const void* T, int B, int F, int D, void* out, int out_ld, cudaStream_t stream) {
+  rs::FlagWait w;
+  memset(&w, 0, sizeof(w));
+  return interaction_forward_impl(T, B, F, D, out, out_ld, w, stream);
+}
+// Same, but every CTA first waits (bounded) until all ranks' flags on `wait_channel` have reached this rank's own epoch:
+// the forward all-to-all has delivered the peers' rows into T.
+RS_API int rs_interaction_forward_ex(const void* T, int B, int F, int D, void* out, int out_ld, const void* wait_flags,
+                                     const unsigned* counters, unsigned long long timeout_ns, int wait_channel, int world,
+                                     unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(!wait_flags || (counters && world >= 1 && world <= 32), "rs_interaction_forward_ex: bad flag arguments");
+  rs::FlagWait w;
+  memset(&w, 0, sizeof(w));
+  w.my_flags = reinterpret_cast<const uint32_t*>(wait_flags); w.sig_counters = counters; w.timeout_ns = timeout_ns;
+  w.status = status; w.world = world; w.channel = wait_channel;
+  return interaction_forward_impl(T, B, F, D, out, out_ld, w, stream);
+}
+namespace {
+int interaction_forward_impl(const void* T, int B, int F, int D, void* out, int out_ld, const rs::FlagWait& wait, cudaStream_t stream) {
   RS_REQUIRE(T && out, "rs_interaction_forward: null argument");
   RS_REQUIRE(F >= 1 && F <= kMaxF && D % 16 == 0 && D >= 16 && D <= kMaxD, "rs_interaction_forward: F=%d D=%d unsupported", F, D);
   RS_REQUIRE(out_ld % 8 == 0 && out_ld >= D + F * (F - 1) / 2, "rs_interaction_forward: out_ld=%d too small or unaligned", out_ld);
@@ -402,10 +426,11 @@ RS_API int rs_interaction_forward(const void* T, int B, int F, int D, void* out,
   int grid = (B + kWarps - 1) / kWarps;
   if (grid > 148 * 5) grid = 148 * 5;   // persistent: 5 CTAs of 4 warps fit one SM's shared memory
   interaction_fwd_kernel<<<grid, kWarps * 32, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(T), B, F, D, reinterpret_cast<__nv_bfloat16*>(out), out_ld);
+      reinterpret_cast<const __nv_bfloat16*>(T), B, F, D, reinterpret_cast<__nv_bfloat16*>(out), out_ld, wait);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }
+}  // namespace
 
 RS_API int rs_interaction_backward(const void* T, const void* dout, int B, int F, int D, int dout_ld, void* dx,
                                    int dx_ld, void* const* gdst, const int* owner, const int* gcol,

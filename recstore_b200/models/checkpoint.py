@@ -3,6 +3,8 @@
     <dir>/meta.json          table rows, embedding width, MLP shapes, interaction, step counter, world size at save time
     <dir>/dense.pt           {"bot.0.weight": ..., "head.bias": ...}  (fp32, torch.save)
     <dir>/table_<t>.pt       {"weight": [rows, D] fp32, "state": [rows] fp32 row-wise Adagrad accumulator}
+    <dir>/table_<t>.shard<r>of<w>.pt   the same for a table that is spread row-wise over w ranks: rank r's rows
+                                        (ids r, r + w, r + 2w, ...), one file per rank
 
 Tables are keyed by table index, not by rank, so a checkpoint written by N ranks loads on M ranks (each rank reads
 the tables it owns under the new placement) and moves between the GPU engine and the PyTorch restatement: both
@@ -22,10 +24,13 @@ import torch
 def save_checkpoint(model, path: str, step: int = 0, extra: Optional[dict] = None) -> None:
     os.makedirs(path, exist_ok=True)
     rank = getattr(model, "rank", 0)
+    split = set(getattr(model, "split_tables", []))
+    world = getattr(model, "world", 1)
     for t in model.local_tables:
-        tmp = os.path.join(path, f".table_{t}.pt.tmp")
+        name = f"table_{t}.shard{rank}of{world}.pt" if t in split else f"table_{t}.pt"
+        tmp = os.path.join(path, "." + name + ".tmp")
         torch.save({"weight": model.table_weight(t).detach().cpu(), "state": model.table_state(t).detach().cpu()}, tmp)
-        os.replace(tmp, os.path.join(path, f"table_{t}.pt"))
+        os.replace(tmp, os.path.join(path, name))
     if rank == 0:
         tmp = os.path.join(path, ".dense.pt.tmp")
         torch.save({k: v.detach().cpu() for k, v in model.dense_state().items()}, tmp)
@@ -45,8 +50,36 @@ def load_checkpoint(model, path: str) -> dict:
         if k in meta and list(meta[k]) != list(mine[k]) if isinstance(mine[k], (list, tuple)) else meta.get(k, mine[k]) != mine[k]:
             raise ValueError(f"checkpoint {path} was written for {k}={meta[k]}, this model has {mine[k]}")
     model.load_dense_state(torch.load(os.path.join(path, "dense.pt"), map_location="cpu"))
+    split = set(getattr(model, "split_tables", []))
+    rank, world = getattr(model, "rank", 0), getattr(model, "world", 1)
     for t in model.local_tables:
-        d = torch.load(os.path.join(path, f"table_{t}.pt"), map_location="cpu")
+        d = _load_table(path, t, int(mine["table_rows"][t]), int(mine["emb_dim"]))
+        if t in split:       # this rank keeps ids rank, rank + world, ...
+            d = {"weight": d["weight"][rank::world], "state": d["state"][rank::world]}
         model.table_weight(t).copy_(d["weight"])
         model.table_state(t).copy_(d["state"])
     return meta
+
+
+def _load_table(path: str, t: int, rows: int, dim: int) -> dict:
+    """The whole table ``t`` from its file, or re-interleaved from the shard files of a row-wise spread save."""
+    whole = os.path.join(path, f"table_{t}.pt")
+    if os.path.exists(whole):
+        return torch.load(whole, map_location="cpu")
+    import glob
+    import re
+    shards = {}
+    for f in glob.glob(os.path.join(path, f"table_{t}.shard*of*.pt")):
+        m = re.search(r"shard(\d+)of(\d+)\.pt$", f)
+        shards[int(m.group(1))] = (int(m.group(2)), f)
+    if not shards:
+        raise FileNotFoundError(f"checkpoint {path} has no file for table {t}")
+    w = next(iter(shards.values()))[0]
+    if sorted(shards) != list(range(w)):
+        raise ValueError(f"checkpoint {path}: table {t} needs shards 0..{w - 1}, found {sorted(shards)}")
+    weight, state = torch.empty(rows, dim), torch.empty(rows)
+    for r, (_, f) in shards.items():
+        d = torch.load(f, map_location="cpu")
+        weight[r::w] = d["weight"]
+        state[r::w] = d["state"]
+    return {"weight": weight, "state": state}

@@ -20,6 +20,7 @@ copy stream while the previous step still computes.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -30,7 +31,7 @@ from .._lib import call, stream_ptr
 from ..ops import functional as F_
 from ..parallel.peer import PeerContext
 
-CH_FWD, CH_BWD, CH_GRADS, CH_REDUCED, CH_MISC, CH_GRADS_TOP = 0, 1, 2, 3, 4, 5
+CH_FWD, CH_BWD, CH_GRADS, CH_REDUCED, CH_MISC, CH_GRADS_TOP, CH_KEYS, CH_PART = 0, 1, 2, 3, 4, 5, 6, 7
 
 
 def _round_up(x: int, m: int) -> int:
@@ -60,6 +61,10 @@ class DLRMConfig:
     dcn_rank: int = 512
     placement: str = "round_robin"               # tables on ranks: "round_robin" (t % world) or "balanced" (greedy by ids per sample)
     trace_phases: bool = False                   # stamp the GPU timer at phase boundaries (see DLRM.phase_times)
+    # Tables spread ROW-WISE over all ranks (owner of id = id % world) instead of living whole on one rank: a list of
+    # table indices, or "auto" = every table whose share of the ids per sample exceeds 1 / world (one rank could
+    # never keep up with it).  Ignored on one GPU.
+    row_split: object = None
 
     def __post_init__(self):
         if self.hotness is None:
@@ -82,12 +87,14 @@ class _Layer:
 class PinnedBatch:
     """One rank's share of a global batch in pinned host memory."""
     dense: torch.Tensor     # [B_local, num_dense] fp32
-    ids: torch.Tensor       # [nnz_local] int64: for each local table, B * hotness ids, sample-major
+    ids: torch.Tensor       # [nnz_local] int64: for each whole local table, B * hotness ids, sample-major
     labels: torch.Tensor    # [B_local] fp32
+    ids_rw: Optional[torch.Tensor] = None   # row-sharded tables: for each of them, this rank's B_local * hotness ids
 
     @property
     def nbytes(self) -> int:
-        return self.dense.numel() * 4 + self.ids.numel() * 8 + self.labels.numel() * 4
+        return (self.dense.numel() * 4 + self.ids.numel() * 8 + self.labels.numel() * 4 +
+                (self.ids_rw.numel() * 8 if self.ids_rw is not None else 0))
 
 
 class StepHandle:
@@ -125,23 +132,36 @@ class DLRM:
         self.T = len(cfg.table_rows)
         self.D = cfg.emb_dim
         self.F = self.T + 1
-        import os
         self.dcn = cfg.interaction == "dcn"
         self.proj = cfg.interaction == "projection"
         assert cfg.interaction in ("dot", "dcn", "projection")
         assert self.dcn or self.proj or self.F <= 32, "dot interaction kernel handles up to 31 embedding features"
-        # ---- table placement: round robin by table index unless the config asks for the load-balanced greedy
+        # ---- table placement.  Row-sharded tables (if any) are local tables 0..K-1 of EVERY rank; the others live whole
+        # on one rank: round robin unless the config asks for the load-balanced greedy.
+        split: List[int] = []
+        if self.world > 1 and cfg.row_split:
+            if cfg.row_split == "auto":
+                tot = float(sum(cfg.hotness))
+                split = [t for t in range(self.T) if cfg.hotness[t] / tot > 1.0 / self.world]
+            else:
+                split = sorted(set(int(t) for t in cfg.row_split))
+        self.split_tables, self.K = split, len(split)
+        K = self.K
+        whole = [t for t in range(self.T) if t not in split]
         if cfg.placement == "round_robin":
-            self.owner = [t % self.world for t in range(self.T)]
+            own = {t: (t if not split else i) % self.world for i, t in enumerate(whole)}
         else:
             from ..parallel.placement import place_tables
-            self.owner = place_tables(list(cfg.hotness), list(cfg.table_rows), self.world, cfg.placement)
-        self.local_tables = [t for t in range(self.T) if self.owner[t] == self.rank]
-        self.Tl = len(self.local_tables)
-        self.Tmax = max(sum(1 for t in range(self.T) if self.owner[t] == r) for r in range(self.world))
-        local_idx = {}
-        cnt = [0] * self.world
-        for t in range(self.T):
+            placed = place_tables([cfg.hotness[t] for t in whole], [cfg.table_rows[t] for t in whole], self.world, cfg.placement)
+            own = {t: placed[i] for i, t in enumerate(whole)}
+        self.owner = [-1 if t in split else own[t] for t in range(self.T)]
+        self.whole_local = [t for t in whole if self.owner[t] == self.rank]
+        self.local_tables = split + self.whole_local
+        self.Tl, self.Tw = len(self.local_tables), len(self.whole_local)
+        self.Tmax = K + max(sum(1 for t in whole if self.owner[t] == r) for r in range(self.world))
+        local_idx = {t: k for k, t in enumerate(split)}
+        cnt = [K] * self.world
+        for t in whole:
             local_idx[t] = cnt[self.owner[t]]
             cnt[self.owner[t]] += 1
         self.local_idx = local_idx
@@ -152,8 +172,11 @@ class DLRM:
         bf = dict(dtype=torch.bfloat16, device=dev)
         f32 = dict(dtype=torch.float32, device=dev)
 
-        # ---- embedding shard
-        rows = [cfg.table_rows[t] for t in self.local_tables]
+        # ---- embedding shard: [rows of the row-sharded tables with id % world == rank | rows of the whole local tables]
+        def local_rows(t):
+            n = cfg.table_rows[t]
+            return (n - self.rank + self.world - 1) // self.world if t in split else n
+        rows = [local_rows(t) for t in self.local_tables]
         base = [0]
         for r in rows:
             base.append(base[-1] + r)
@@ -161,30 +184,64 @@ class DLRM:
         self.table_base = torch.tensor(base[:-1] or [0], **i64)
         self.table_rows = torch.tensor(rows or [0], **i64)
         self.weight = torch.empty(max(self.total_rows, 1), self.D, **f32)
-        gg = torch.Generator(device=dev).manual_seed(cfg.seed * 1000 + 17)
         for j, t in enumerate(self.local_tables):
             n = cfg.table_rows[t]
             gt = torch.Generator(device=dev).manual_seed(cfg.seed * 1000 + t)
             w = self.weight[base[j]:base[j + 1]]
-            if cfg.emb_init == "uniform":
+            if t in split:
+                # the same values as the whole table would get, of which this rank keeps every world-th row
+                full = torch.empty(n, self.D, **f32)
+                if cfg.emb_init == "uniform":
+                    full.uniform_(-math.sqrt(1.0 / n), math.sqrt(1.0 / n), generator=gt)
+                else:
+                    full.normal_(0.0, 0.01, generator=gt)
+                w.copy_(full[self.rank::self.world])
+                del full
+            elif cfg.emb_init == "uniform":
                 w.uniform_(-math.sqrt(1.0 / n), math.sqrt(1.0 / n), generator=gt)
             else:
                 w.normal_(0.0, 0.01, generator=gt)
-        del gg
         self.state = torch.zeros(max(self.total_rows, 1), **f32)
-        hot = [cfg.hotness[t] for t in self.local_tables]
+        # whole local tables: the ids of the GLOBAL batch, table after table
+        hot = [cfg.hotness[t] for t in self.whole_local]
         hb = [0]
         for h in hot:
             hb.append(hb[-1] + self.B * h)
         self.nnz = hb[-1]
         self.hotness = torch.tensor(hot or [1], **i32)
         self.hot_base = torch.tensor(hb[:-1] or [0], **i64)
-        self.dst_col = torch.tensor([(1 + t) * self.D for t in self.local_tables] or [0], **i32)
-        self.grad_col = torch.tensor([j * self.D for j in range(self.Tl)] or [0], **i32)
+        self.dst_col = torch.tensor([(1 + t) * self.D for t in self.whole_local] or [0], **i32)
+        self.grad_col = torch.tensor([(K + j) * self.D for j in range(self.Tw)] or [0], **i32)
         self.row_idx = torch.empty(max(self.nnz, 1), **i64)
         self.occ2bag = torch.empty(max(self.nnz, 1), **i32)
         self.owner_dev = torch.tensor(self.owner, **i32)
         self.gcol_dev = torch.tensor([local_idx[t] * self.D for t in range(self.T)], **i32)
+        self.table_base_w, self.table_rows_w = self.table_base[K:], self.table_rows[K:]
+        if self.Tw == 0:
+            self.table_base_w = self.table_rows_w = torch.zeros(1, **i64)
+        # row-sharded tables: this rank's B_local samples send their ids to the owners (key windows), the owners pool
+        # their share of every bag and send the partial sums back (partial windows)
+        if K:
+            hk = [cfg.hotness[t] for t in split]
+            self.hot_rw = torch.tensor(hk, **i32)
+            idb, kb = [0], [0]
+            for h in hk:
+                idb.append(idb[-1] + self.Bl * h)
+                kb.append(kb[-1] + self.B * h)
+            self.nnz_rw_local = idb[-1]                    # ids of this rank's samples
+            self.nnz_rw_cap = kb[-1]                       # key slots per owner (worst case: every id lives here)
+            self.id_base_rw = torch.tensor(idb[:-1], **i64)
+            self.key_base_rw = torch.tensor(kb[:-1], **i64)
+            self.key_win = self.ctx.alloc("dlrm_rw_keys", self.nnz_rw_cap * 8)
+            self.cnt_win = self.ctx.alloc("dlrm_rw_counts", K * self.B * 4)
+            self.part_win = self.ctx.alloc("dlrm_rw_partials", self.Bl * K * self.world * self.D * 2)
+            self.part_col = torch.tensor([(k * self.world + self.rank) * self.D for k in range(K)], **i32)
+            self.red_col = torch.tensor([(1 + t) * self.D for t in split], **i32)
+            self.grad_col_rw = torch.tensor([k * self.D for k in range(K)], **i32)
+            self.row_idx_rw = torch.empty(self.nnz_rw_cap, **i64)
+            self.occ2bag_rw = torch.empty(self.nnz_rw_cap, **i32)
+            self.occ_cursor = torch.zeros(1, **i32)
+        self._grid_done = torch.zeros(8, **i32)            # "grid done" counters of the kernels that publish their own flag
 
         # ---- peer windows
         self.grow_stride = self.Tmax * self.D
@@ -195,6 +252,13 @@ class DLRM:
         self.gnorm = self.Gwin.view(torch.float32, (self.B, self.Tmax), byte_offset=self.gn_off)
         self.ndst_table = torch.tensor([p + self.gn_off for p in self.Gwin.ptrs], dtype=torch.int64, device=dev)
         self.Tbuf = self.Twin.view(torch.bfloat16, (self.Bl, self.F * self.D))
+        if self.world > 1 and self.K and not self.dcn and not self.proj:
+            # Backward all-to-all with row-sharded tables under the dot interaction: its backward leaves the per-(sample,
+            # table) gradient rows in this local staging buffer; a thin copy kernel then fans them out to their owners.
+            self.gstage = torch.empty(self.Bl, self.T * self.D, **bf)
+            self.stage_table = torch.tensor([self.gstage.data_ptr()] * self.world, **i64)
+            self.stage_owner = torch.zeros(self.T, **i32)
+            self.stage_col = torch.tensor([t * self.D for t in range(self.T)], **i32)
 
         # ---- dense parameters (flat fp32 master / grad / reduced buffers)
         self.Kin0 = _round_up(cfg.num_dense, 64)
@@ -313,22 +377,29 @@ class DLRM:
         # ---- double-buffered inputs, loss
         self.in_dense = [torch.empty(Bl, cfg.num_dense, **f32) for _ in range(2)]
         self.in_ids = [torch.empty(max(self.nnz, 1), **i64) for _ in range(2)]
+        self.in_ids_rw = [torch.empty(self.nnz_rw_local, **i64) for _ in range(2)] if self.K else [None, None]
         self.in_labels = [torch.empty(Bl, **f32) for _ in range(2)]
         self._loss_dev = [torch.zeros(1, **f32) for _ in range(2)]
         self._loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
         self._status_host = [torch.zeros(1, dtype=torch.int64).pin_memory() for _ in range(2)]   # the device status word, read back with the loss
+        # Dot interaction without row-sharded tables: the interaction backward pushes the embedding gradients itself.  With
+        # row-sharded tables (a gradient row then goes to every rank) they are staged and a thin copy kernel fans them out.
+        self._fused_push = not self.K and not self.dcn and not self.proj
+        # Stream priorities (RECSTORE_STREAM_PRIORITIES: 0 = none, 1 = main stream first, 2 = communication stream first).
+        prio = os.environ.get("RECSTORE_STREAM_PRIORITIES", "0")
+        p_main, p_comm, p_col, p_wgrad = {"1": (-3, -2, -1, 0), "2": (-2, -3, -1, 0)}.get(prio, (0, 0, 0, 0))
         self.copy_stream = torch.cuda.Stream(device=dev)
-        self.compute_stream = torch.cuda.Stream(device=dev)
+        self.compute_stream = torch.cuda.Stream(device=dev, priority=p_main)
         self._copied = [torch.cuda.Event() for _ in range(2)]
         self._consumed = [torch.cuda.Event() for _ in range(2)]
         self._done = [torch.cuda.Event() for _ in range(2)]
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._step_no = 0
         self.launches_per_step = 0
-        self.s_wgrad = torch.cuda.Stream(device=dev)   # weight/bias gradients, then the dense all-reduce and SGD
-        self.s_comm = torch.cuda.Stream(device=dev)    # embedding lookup / gradient push: the NVLink-bound kernels
-        self.s_wgrad2 = torch.cuda.Stream(device=dev)  # weight gradients of the bottom MLP
-        self.s_col = torch.cuda.Stream(device=dev)     # bias gradients (column sums): bandwidth-bound, beside the wgrad GEMMs
+        self.s_wgrad = torch.cuda.Stream(device=dev, priority=p_wgrad)   # weight/bias gradients, then the dense all-reduce and SGD
+        self.s_comm = torch.cuda.Stream(device=dev, priority=p_comm)     # embedding lookup / gradient push: the NVLink-bound kernels
+        self.s_wgrad2 = torch.cuda.Stream(device=dev, priority=p_wgrad)  # weight gradients of the bottom MLP
+        self.s_col = torch.cuda.Stream(device=dev, priority=p_col)       # bias gradients (column sums): bandwidth-bound, beside the wgrad GEMMs
         self._phase_names: List[str] = []
         self._no_stamp = False
         self._phase_buf = torch.zeros(64, dtype=torch.int64, device=dev)
@@ -358,12 +429,16 @@ class DLRM:
         lo, hi = self.rank * self.Bl, (self.rank + 1) * self.Bl
         d = dense[lo:hi].contiguous().pin_memory()
         l = labels[lo:hi].contiguous().pin_memory()
-        if self.local_tables:
-            i = torch.cat([ids[t].reshape(-1) for t in self.local_tables]).to(torch.int64).pin_memory()
+        if self.whole_local:
+            i = torch.cat([ids[t].reshape(-1) for t in self.whole_local]).to(torch.int64).pin_memory()
         else:
             i = torch.zeros(1, dtype=torch.int64).pin_memory()
         assert i.numel() == max(self.nnz, 1)
-        return PinnedBatch(d, i, l)
+        irw = None
+        if self.K:     # row-sharded tables: the ids of this rank's own samples; the owners get them over NVLink
+            irw = torch.cat([ids[t].reshape(self.B, -1)[lo:hi].reshape(-1) for t in self.split_tables]).to(torch.int64).pin_memory()
+            assert irw.numel() == self.nnz_rw_local
+        return PinnedBatch(d, i, l, irw)
 
     def _count(self, n=1):
         self.launches_per_step += n
@@ -395,14 +470,43 @@ class DLRM:
         if overlap:
             self.s_comm.wait_stream(main)
         with torch.cuda.stream(self.s_comm if overlap else main):
-            if self.Tl:
-                F_.emb_forward(self.weight, self.table_base, self.table_rows, self.in_ids[slot], hotness=self.hotness,
-                               hot_base=self.hot_base, T=self.Tl, B=self.B, D=self.D, B_local=self.Bl,
-                               dst_table=self.Twin.table, dst_row_stride=self.F * self.D, dst_col=self.dst_col,
-                               out_bf16=True, row_idx=self.row_idx, occ2bag=self.occ2bag, status=st)
+            if self.world == 1:
+                if self.Tl:
+                    F_.emb_forward(self.weight, self.table_base, self.table_rows, self.in_ids[slot], hotness=self.hotness,
+                                   hot_base=self.hot_base, T=self.Tl, B=self.B, D=self.D, B_local=self.Bl,
+                                   dst_table=self.Twin.table, dst_row_stride=self.F * self.D, dst_col=self.dst_col,
+                                   out_bf16=True, row_idx=self.row_idx, occ2bag=self.occ2bag, status=st)
+                    self._count()
+            else:
+                gd = self._grid_done
+                if self.K:
+                    # row-sharded tables, step 1: the ids of my samples go to their owners (+ CH_KEYS)
+                    F_.rw_push_keys(self.in_ids_rw[slot], self.id_base_rw, self.hot_rw, self.key_base_rw, self.K, self.Bl,
+                                    self.B, self.key_win.table, self.cnt_win.table, self.occ_cursor, ctx=self.ctx,
+                                    sig_channel=CH_KEYS, sig_done=gd[0:1], status=st)
+                    self._count()
+                if self.Tw:
+                    # whole tables: pooled rows go straight into the samples' ranks; the kernel publishes CH_FWD itself
+                    F_.emb_forward_ex(self.weight, self.table_base_w, self.table_rows_w, self.in_ids[slot], self.hotness,
+                                      self.hot_base, T=self.Tw, B=self.B, D=self.D, B_local=self.Bl, dst_table=self.Twin.table,
+                                      dst_row_stride=self.F * self.D, dst_col=self.dst_col, row_idx=self.row_idx,
+                                      occ2bag=self.occ2bag, status=st, ctx=self.ctx, sig_channel=CH_FWD, sig_done=gd[1:2])
+                else:
+                    self.ctx.signal(CH_FWD)
                 self._count()
-            if self.world > 1:
-                self.ctx.signal(CH_FWD); self._count()
+                if self.K:
+                    # step 2 (owner side): wait for each source rank's keys, pool my share of every bag, push the partial
+                    # sums into the samples' ranks (+ CH_PART); step 3: add the partials up into the feature slots
+                    F_.emb_forward_ex(self.weight, self.table_base, self.table_rows, self.key_win.local_ptr, self.hot_rw,
+                                      self.key_base_rw, T=self.K, B=self.B, D=self.D, B_local=self.Bl,
+                                      dst_table=self.part_win.table, dst_row_stride=self.K * self.world * self.D,
+                                      dst_col=self.part_col, row_idx=self.row_idx_rw, occ2bag=self.occ2bag_rw, status=st,
+                                      counts=self.cnt_win.local_ptr, id_div=self.world, id_rem=self.rank,
+                                      occ_cursor=self.occ_cursor, ctx=self.ctx, wait_channel=CH_KEYS, sig_channel=CH_PART,
+                                      sig_done=gd[2:3])
+                    F_.rw_reduce_partials(self.part_win.local_ptr, self.Tbuf, self.red_col, self.Bl, self.K, self.D,
+                                          ctx=self.ctx, wait_channel=CH_PART, status=st)
+                    self._count(2)
         self._stamp("emb_fwd_done")
         x = self.x0p
         for i, L in enumerate(self.bot):
@@ -411,8 +515,8 @@ class DLRM:
             x = out
         self._stamp("bot_fwd_done")
         main.wait_stream(self.s_comm)
-        if self.world > 1:
-            self.ctx.wait(CH_FWD); self._count()
+        if self.world > 1 and (self.dcn or self.proj):
+            self.ctx.wait_own(CH_FWD); self._count()     # the consumer is a GEMM fed by TMA: it cannot wait in its own prologue
         self._stamp("a2a_fwd_arrived")
         if self.dcn:
             for l in range(len(self.crossV)):
@@ -428,6 +532,9 @@ class DLRM:
                     F_.gemm_bf16(x, L.wb, out, mode=0, epi=F_.EPI_RELU, bias=L.b, status=st); self._count()
                     x = out
             F_.proj_inter_forward(self.Tbuf, self.pb[0][-1], self.pb[1][-1], self.I1, self.I2, self.D, self.z)
+            self._count()
+        elif self.world > 1:
+            F_.interaction_forward_ex(self.Tbuf, self.Bl, self.F, self.D, self.z, ctx=self.ctx, wait_channel=CH_FWD, status=st)
             self._count()
         else:
             F_.interaction_forward(self.Tbuf, self.Bl, self.F, self.D, self.z); self._count()
@@ -497,7 +604,7 @@ class DLRM:
                 self._count(6)
             F_.push_feature_grads(self.c_dx0, dx, self.Tbuf, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
                                   self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl, relu_mask_dx=True,
-                                  ndst_table=self.ndst_table, nstride=self.Tmax)
+                                  ndst_table=self.ndst_table, nstride=self.Tmax, world=self.world)
             self._count()
             if self.world > 1:
                 self.ctx.signal(CH_BWD); self._count()
@@ -525,34 +632,63 @@ class DLRM:
             # features: both branches' input gradients; the dense feature also feeds the over-arch directly
             F_.push_feature_grads(None, self.p_dx[1], self.Tbuf, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
                                   self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl, relu_mask_dx=True,
-                                  ndst_table=self.ndst_table, nstride=self.Tmax, dense_extra=self.d_z)
+                                  ndst_table=self.ndst_table, nstride=self.Tmax, dense_extra=self.d_z, world=self.world)
             self._count()
             if self.world > 1:
                 self.ctx.signal(CH_BWD); self._count()
-        elif self.world > 1:
-            # The gradient all-to-all (peer stores from the kernel) is bound by NVLink, not by the SMs: a first pass
-            # produces only the bottom MLP's input gradient (a matrix-vector product per sample), then the pass that pushes the embedding gradients runs
-            # on the communication stream beside the bottom MLP's backward.
-            F_.interaction_dx(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], relu_mask_dx=True)
+        elif self.world > 1 and self._fused_push:
+            # The gradient all-to-all is done by the interaction backward itself (peer stores from the kernel that computes
+            # the rows, bound by NVLink) on the communication stream; it leads to the sparse optimizer, the longest chain
+            # of the backward, so it starts as soon as the top MLP's input gradient exists.  A small kernel of its own
+            # produces only the bottom MLP's input gradient (a matrix-vector product per sample) on the main stream.
             self.s_comm.wait_stream(main)
+            F_.interaction_dx(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], relu_mask_dx=True)
             with torch.cuda.stream(self.s_comm):
                 F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
                                         self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
                                         relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax, rows=2)
                 self.ctx.signal(CH_BWD)
             self._count(3)
+        elif self.world > 1:
+            # Dot interaction with row-sharded tables: one pass leaves dx (the bottom MLP's input gradient) and every
+            # embedding gradient row in a local staging buffer; the thin push below fans them out.
+            F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.stage_table,
+                                    self.stage_owner, self.stage_col, self.T * self.D, 0, relu_mask_dx=True)
+            self._count()
         else:
             F_.interaction_backward(self.Tbuf, self.d_z, self.Bl, self.F, self.D, self.d_act_b[-1], self.Gwin.table,
                                     self.owner_dev, self.gcol_dev, self.grow_stride, self.rank * self.Bl,
                                     relu_mask_dx=True, ndst_table=self.ndst_table, nstride=self.Tmax)
             self._count()
-        # ---- sparse optimizer on the owned rows: bound by HBM (and by the peers' pushes), so it runs on the
-        # communication stream beside the bottom MLP's backward, the dense all-reduce and the SGD step
+        # ---- sparse optimizer on the owned rows (after the staged gradient rows, if any, have been fanned out): bound by
+        # HBM and by the peers' pushes, so it runs on the communication stream beside the bottom MLP's backward, the dense
+        # all-reduce and the SGD step.  Its first kernel waits for the peers' flags itself.
         self.s_comm.wait_stream(main)
         with torch.cuda.stream(self.s_comm):
             if self.world > 1:
-                self.ctx.wait(CH_BWD); self._count()
-            if self.Tl:
+                if not (self._fused_push or self.dcn or self.proj):
+                    F_.push_rows(self.gstage, self.Bl, self.T, self.D, self.Gwin.table, self.owner_dev, self.gcol_dev,
+                                 self.grow_stride, self.rank * self.Bl, ndst_table=self.ndst_table, nstride=self.Tmax,
+                                 ctx=self.ctx, sig_channel=CH_BWD, sig_done=self._grid_done[3:4])
+                    self._count()
+                nl = 2 if c.emb_optimizer == "rowwise_adagrad" else 1
+                if self.Tw:
+                    F_.emb_backward_ex(self.weight, self.state, self.row_idx, self.occ2bag, self.nnz, self.Gwin.local,
+                                       grad_col=self.grad_col, grad_row_stride=self.grow_stride, B=self.B, D=self.D,
+                                       lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st,
+                                       gnorm=self.gnorm.data_ptr() + 4 * self.K, gnorm_stride=self.Tmax,
+                                       ctx=self.ctx, wait_channel=CH_BWD)
+                    self._count(nl)
+                if self.K:
+                    F_.emb_backward_ex(self.weight, self.state, self.row_idx_rw, self.occ2bag_rw, self.nnz_rw_cap,
+                                       self.Gwin.local, grad_col=self.grad_col_rw, grad_row_stride=self.grow_stride, B=self.B,
+                                       D=self.D, lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st,
+                                       gnorm=self.gnorm, gnorm_stride=self.Tmax, nnz_dev=self.occ_cursor,
+                                       ctx=self.ctx, wait_channel=CH_BWD)
+                    self._count(nl)
+                if not self.Tl:
+                    self.ctx.wait_own(CH_BWD); self._count()       # nothing to update here, but the step ends after the peers' pushes
+            elif self.Tl:
                 F_.emb_backward(self.weight, self.state, self.row_idx, self.occ2bag, self.nnz, self.Gwin.local,
                                 grad_col=self.grad_col, grad_row_stride=self.grow_stride, B=self.B, D=self.D,
                                 grad_bf16=True, lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st,
@@ -611,6 +747,8 @@ class DLRM:
             cs.wait_event(self._consumed[slot])       # previous user of this slot has finished
             self.in_dense[slot].copy_(batch.dense, non_blocking=True)
             self.in_ids[slot].copy_(batch.ids, non_blocking=True)
+            if self.K:
+                self.in_ids_rw[slot].copy_(batch.ids_rw, non_blocking=True)
             self.in_labels[slot].copy_(batch.labels, non_blocking=True)
             self._copied[slot].record(cs)
         with torch.cuda.stream(ms):
@@ -667,6 +805,8 @@ class DLRM:
         with torch.cuda.stream(self.compute_stream):
             self.in_dense[0].copy_(batch.dense, non_blocking=True)
             self.in_ids[0].copy_(batch.ids, non_blocking=True)
+            if self.K:
+                self.in_ids_rw[0].copy_(batch.ids_rw, non_blocking=True)
             self._no_stamp = True          # the phase stamps describe the last training step, not an inference pass
             try:
                 x = self._forward(0)
@@ -727,13 +867,47 @@ class DLRM:
         torch.cuda.synchronize(self.dev)
         return meta
 
+    def gather_table(self, t: int, what: str = "weight") -> Optional[torch.Tensor]:
+        """Collective: the whole table ``t`` (``what`` = "weight" or "state") on rank 0, wherever its rows live (``None``
+        on the other ranks).  Tests and checkpoint tools use it; rows of a row-sharded table are re-interleaved."""
+        import torch.distributed as dist
+        mine = (self.table_weight if what == "weight" else self.table_state)
+        n = self.cfg.table_rows[t]
+        shape = (n, self.D) if what == "weight" else (n,)
+        if self.world == 1:
+            return mine(t).clone()
+        if self.owner[t] >= 0:
+            if self.owner[t] == 0:
+                return mine(t).clone() if self.rank == 0 else None
+            if self.rank == self.owner[t]:
+                dist.send(mine(t).contiguous(), dst=0, group=self.ctx.group)
+                return None
+            if self.rank == 0:
+                out = torch.empty(*shape, device=self.dev)
+                dist.recv(out, src=self.owner[t], group=self.ctx.group)
+                return out
+            return None
+        out = torch.empty(*shape, device=self.dev) if self.rank == 0 else None
+        for r in range(self.world):
+            if r == 0:
+                if self.rank == 0:
+                    out[0::self.world] = mine(t)
+            elif self.rank == r:
+                dist.send(mine(t).contiguous(), dst=0, group=self.ctx.group)
+            elif self.rank == 0:
+                part = torch.empty_like(out[r::self.world]).contiguous()
+                dist.recv(part, src=r, group=self.ctx.group)
+                out[r::self.world] = part
+        return out
+
     def table_weight(self, t: int) -> torch.Tensor:
-        """View of table ``t`` if this rank owns it."""
+        """View of table ``t`` if this rank owns it (of this rank's rows, ids = rank, rank + world, ..., if the table is
+        row-sharded)."""
         j = self.local_tables.index(t)
         b0 = int(self.table_base[j].item())
-        return self.weight[b0:b0 + self.cfg.table_rows[t]]
+        return self.weight[b0:b0 + int(self.table_rows[j].item())]
 
     def table_state(self, t: int) -> torch.Tensor:
         j = self.local_tables.index(t)
         b0 = int(self.table_base[j].item())
-        return self.state[b0:b0 + self.cfg.table_rows[t]]
+        return self.state[b0:b0 + int(self.table_rows[j].item())]

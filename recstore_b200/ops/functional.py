@@ -81,6 +81,78 @@ def emb_backward(weight, state, row_idx, occ2bag, nnz: int, grad, *, grad_col=No
          ptr(status), stream_ptr())
 
 
+def emb_forward_ex(weight, table_base, table_rows, indices, hotness, hot_base, *, T: int, B: int, D: int, B_local: int,
+                   dst_table, dst_row_stride: int, dst_col, row_idx=None, occ2bag=None, status=None, counts=None,
+                   id_div: int = 1, id_rem: int = 0, occ_cursor=None, ctx=None, wait_channel: int = -1,
+                   sig_channel: int = -1, sig_done=None) -> None:
+    """:func:`emb_forward` (bf16 output, fixed-capacity bags) with the multi-GPU extras: bags shortened by ``counts`` and
+    ids mapped to the rows of a cyclic shard (``id_div``, ``id_rem``), a compacted occurrence list (``occ_cursor``), a
+    bounded in-kernel wait on ``wait_channel`` for the rank each bag comes from, and the flag of ``sig_channel``
+    published by the kernel itself when its grid is done.  ``indices`` / ``counts`` may be raw device addresses."""
+    _need_cuda(weight)
+    wait = ctx is not None and wait_channel >= 0
+    sig = ctx is not None and sig_channel >= 0
+    iptr = indices if isinstance(indices, int) else ptr(indices)
+    cptr = counts if isinstance(counts, int) or counts is None else ptr(counts)
+    call("rs_emb_forward_ex", ptr(weight), ptr(table_base), ptr(table_rows), iptr, ptr(hotness), ptr(hot_base), T, B, D,
+         B_local, ptr(dst_table), dst_row_stride, ptr(dst_col), 1, ptr(row_idx), ptr(occ2bag), ptr(status), cptr, id_div,
+         id_rem, ptr(occ_cursor), ctx.my_flags_ptr if wait else None, ctx.counters_ptr if (wait or sig) else None,
+         ctx.wait_timeout_ns if ctx is not None else 0, max(wait_channel, 0), ctx.flags_table_ptr if sig else None,
+         ptr(sig_done) if sig else None, max(sig_channel, 0), ctx.world if ctx is not None else 1,
+         ctx.rank if ctx is not None else 0, stream_ptr())
+
+
+def emb_backward_ex(weight, state, row_idx, occ2bag, nnz: int, grad, *, grad_col=None, grad_row_stride: int, B: int, D: int,
+                    lr: float, eps: float = 1e-10, optimizer: str = "rowwise_adagrad", status=None, gnorm=None,
+                    gnorm_stride: int = 0, nnz_dev=None, ctx=None, wait_channel: int = -1) -> None:
+    """:func:`emb_backward` (bf16 gradients) with a device-side occurrence count (``nnz_dev``; ``nnz`` is then the capacity
+    of the lists) and a bounded in-kernel wait on ``wait_channel`` for the peers' gradient pushes."""
+    _need_cuda(weight, row_idx, grad)
+    opt = {"sgd": 0, "rowwise_adagrad": 1}[optimizer]
+    wait = ctx is not None and wait_channel >= 0
+    call("rs_emb_backward_ex", ptr(weight), ptr(state), weight.shape[0], ptr(row_idx), ptr(occ2bag), nnz, ptr(grad),
+         ptr(grad_col), grad_row_stride, gnorm if isinstance(gnorm, int) else ptr(gnorm), gnorm_stride, B, D, 1, lr, eps, opt,
+         ptr(status), ptr(nnz_dev), ctx.my_flags_ptr if wait else None, ctx.counters_ptr if wait else None,
+         ctx.wait_timeout_ns if ctx is not None else 0, max(wait_channel, 0), ctx.world if ctx is not None else 1, stream_ptr())
+
+
+def push_rows(src, B: int, T: int, D: int, gdst_table, owner, gcol, grow_stride: int, sample_base: int, *, ndst_table=None,
+              nstride: int = 0, ctx=None, sig_channel: int = -1, sig_done=None) -> None:
+    """Thin all-to-all push: row (b, f) of ``src`` (bf16 ``[B, >= T*D]``) goes to ``gdst_table[owner[f]]`` at
+    ``(sample_base + b) * grow_stride + gcol[f]`` (to every rank when ``owner[f] < 0``), its sum of squares to
+    ``ndst_table``; optionally publishes ``sig_channel`` when done."""
+    _need_cuda(src)
+    sig = ctx is not None and sig_channel >= 0
+    call("rs_push_rows", ptr(src), src.stride(0), B, T, D, ctx.world if ctx is not None else 1, ptr(gdst_table), ptr(owner),
+         ptr(gcol), grow_stride, sample_base, ptr(ndst_table), nstride, ctx.flags_table_ptr if sig else None,
+         ctx.counters_ptr if sig else None, ptr(sig_done) if sig else None, max(sig_channel, 0),
+         ctx.rank if ctx is not None else 0, stream_ptr())
+
+
+def rw_push_keys(ids, id_base, hot, key_base, K: int, B_local: int, B: int, key_win_table, cnt_win_table, occ_cursor, *,
+                 ctx, sig_channel: int, sig_done, status=None) -> None:
+    """Row-sharded tables, forward step 1: the ids of this rank's bags go to their owners' key windows (owner = id %
+    world) with per-(bag, owner) counts; publishes ``sig_channel``."""
+    call("rs_rw_push_keys", ptr(ids), ptr(id_base), ptr(hot), ptr(key_base), K, B_local, B, ctx.world, ctx.rank,
+         ptr(key_win_table), ptr(cnt_win_table), ptr(occ_cursor), ptr(status), ctx.flags_table_ptr, ctx.counters_ptr,
+         ptr(sig_done), sig_channel, stream_ptr())
+
+
+def rw_reduce_partials(part_ptr: int, out, dst_col, B_local: int, K: int, D: int, *, ctx, wait_channel: int, status=None) -> None:
+    """Row-sharded tables, forward step 3: sums the ``world`` partial pooled rows of every (sample, table) into its slot
+    of the feature buffer, after a bounded in-kernel wait on ``wait_channel``."""
+    call("rs_rw_reduce_partials", part_ptr, ptr(out), ptr(dst_col), out.stride(0), B_local, K, ctx.world, D, ctx.my_flags_ptr,
+         ctx.counters_ptr, ctx.wait_timeout_ns, wait_channel, ptr(status), stream_ptr())
+
+
+def interaction_forward_ex(T, B: int, F: int, D: int, out, *, ctx, wait_channel: int, status=None) -> torch.Tensor:
+    """:func:`interaction_forward` whose CTAs first wait (bounded) for ``wait_channel``: the forward all-to-all."""
+    _need_cuda(T, out)
+    call("rs_interaction_forward_ex", ptr(T), B, F, D, ptr(out), out.stride(0), ctx.my_flags_ptr, ctx.counters_ptr,
+         ctx.wait_timeout_ns, wait_channel, ctx.world, ptr(status), stream_ptr())
+    return out
+
+
 def rows_gather(weight, rows, out) -> torch.Tensor:
     call("rs_rows_gather", ptr(weight), ptr(rows), rows.numel(), weight.shape[1], ptr(out), stream_ptr())
     return out
@@ -169,14 +241,15 @@ def cross_bwd(dx, x0, u, du, dx0_acc, accumulate: bool) -> None:
 
 
 def push_feature_grads(acc, dxb, T, B: int, F: int, D: int, dx, gdst_table, owner, gcol, grow_stride: int, sample_base: int,
-                       relu_mask_dx: bool = True, ndst_table=None, nstride: int = 0, dense_extra=None) -> None:
+                       relu_mask_dx: bool = True, ndst_table=None, nstride: int = 0, dense_extra=None, world: int = 1) -> None:
     """Splits the gradient of the feature matrix ``[B, F, D]`` (``acc`` fp32, optional, plus ``dxb`` bf16): feature 0 to
     ``dx``, features 1.. through the owners' peer pointers, with squared norms (see :func:`interaction_backward`).
     ``dense_extra`` (bf16 ``[B, >= D]``, optional) is added to feature 0: the gradient of a direct path of the dense
-    feature into the over-arch."""
+    feature into the over-arch.  A feature whose ``owner`` entry is negative (a row-sharded table) goes to ranks
+    ``0..world-1``."""
     call("rs_push_feature_grads", ptr(acc), ptr(dxb), ptr(T), B, F, D, ptr(dx), dx.stride(0), ptr(gdst_table), ptr(owner),
          ptr(gcol), grow_stride, sample_base, 1 if relu_mask_dx else 0, ptr(ndst_table), nstride, ptr(dense_extra),
-         dense_extra.stride(0) if dense_extra is not None else 0, stream_ptr())
+         dense_extra.stride(0) if dense_extra is not None else 0, world, stream_ptr())
 
 
 def proj_inter_forward(T, b1, b2, I1: int, I2: int, D: int, z) -> None:

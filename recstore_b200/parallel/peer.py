@@ -148,6 +148,25 @@ class PeerContext:
                   self._counters.data_ptr() + 4 * self.NUM_CHANNELS, self.wait_timeout_ns,
                   self.status.data_ptr(), _lib.stream_ptr(stream))
 
+    def wait_own(self, channel: int, stream=None) -> None:
+        """Orders the stream after every rank's flag on ``channel`` has reached THIS rank's own signal count there: for
+        channels whose signals come from inside producing kernels (one per rank and round)."""
+        _lib.call("rs_peer_wait_own", self._flags.local_ptr, self.world, channel, self._counters.data_ptr(),
+                  self.wait_timeout_ns, self.status.data_ptr(), _lib.stream_ptr(stream))
+
+    # what a kernel with a fused signal / an in-kernel wait needs
+    @property
+    def flags_table_ptr(self) -> int:
+        return self._flags.table.data_ptr()
+
+    @property
+    def my_flags_ptr(self) -> int:
+        return self._flags.local_ptr
+
+    @property
+    def counters_ptr(self) -> int:
+        return self._counters.data_ptr()
+
     def sync(self, channel: int, stream=None) -> None:
         """``signal`` + ``wait`` on one channel in a single launch (a barrier of the ranks on that channel)."""
         _lib.call("rs_peer_sync", self._flags.table.data_ptr(), self._flags.local_ptr, self.world, self.rank, channel,

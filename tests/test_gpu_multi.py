@@ -52,51 +52,79 @@ def _leave(dist, rank, out, err):
     os._exit(1)
 
 
-def _dlrm_worker(rank, world, port, graph, out, kind="dot"):
+def _dlrm_worker(rank, world, port, graph, out, kind="dot", split=None):
     dist = _init(rank, world, port)
     try:
         from recstore_b200.models.dlrm import DLRM, DLRMConfig
         from recstore_b200.parallel.peer import PeerContext
         from recstore_b200.utils.data import DLRMBatchSource
         rows = [1000, 37, 5000, 12, 300, 20000, 64]
-        hot = [1, 2, 1, 3, 1, 1, 1]
+        hot = [1, 2, 1, 3, 1, 1, 1] if split is None else [1, 2, 40, 3, 1, 1, 1]
         B = 512
-        cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=0.05, mlp_lr=0.05 if kind == "dot" else 0.002, seed=5,
-                         use_cuda_graph=graph, interaction=kind, dcn_layers=2, dcn_rank=64, projection_sizes=(3, 4))
+        # The dot model is compared under row-wise Adagrad.  The interactions with more stacked GEMMs are compared under
+        # plain SGD on the embeddings: Adagrad's normalised step (while a row's state is still tiny) would amplify the
+        # fp32 summation-order noise of the all-reduce step over step, which says nothing about the exchange itself.
+        opt = "rowwise_adagrad" if kind == "dot" else "sgd"
+        # What is compared, and how tightly.  From identical parameters the sharded and the single-GPU run do the same
+        # arithmetic per sample; only fp32 summation order differs (split reductions, the all-reduce), so the FIRST step's
+        # parameter updates must agree almost to rounding: that is the check that catches a wrong exchange, a dropped id or
+        # a misrouted gradient.  Later steps compound those last-bit differences through bf16 re-rounding of the weights
+        # and the multiplicative cross layers, so they only have to stay close.  Row-sharded tables send their pooled
+        # partial sums as bf16, one rounding more than the single-GPU run has: tolerances of the size of that rounding.
+        lr_e, lr_m = (0.05, 0.05 if kind == "dot" else 0.002) if split is None else (0.01, 0.01 if kind == "dot" else 0.002)
+        tol_pred, tol_upd, tol_loss = (2e-3, 2e-3, 5e-3) if split is None else (2e-2, 5e-2, 5e-2)
+        cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=lr_e, mlp_lr=lr_m, seed=5,
+                         use_cuda_graph=graph, interaction=kind, dcn_layers=2, dcn_rank=64, projection_sizes=(3, 4),
+                         emb_optimizer=opt, row_split=split)
         ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"))
         eng = DLRM(cfg, ctx)
         solo = DLRM(cfg) if rank == 0 else None          # same seeds -> identical initial state
+        if split is not None:
+            assert eng.split_tables == sorted(split) and eng.K == len(split)
         src = DLRMBatchSource(rows, hot, B, alpha=1.2, seed=9)
-        # The first step is bit-exact between the sharded and the single-GPU run; afterwards fp32 summation order
-        # differs and row-wise Adagrad (a normalised step while a row's state is still tiny) amplifies the difference
-        # step over step - faster for the interactions with more stacked GEMMs, which are compared over fewer steps.
-        for step in range({"dot": 4, "projection": 2, "dcn": 1}[kind]):
+
+        def rel(a, b):
+            return ((a - b).norm() / (b.norm() + 1e-20)).item()
+
+        # forward only, before any update
+        b = src.next()
+        p = eng.predict(eng.make_pinned_batch(b.dense, b.ids, b.labels))
+        if rank == 0:
+            ps = solo.predict(solo.make_pinned_batch(b.dense, b.ids, b.labels))
+            assert (p - ps[:p.numel()]).abs().max().item() < tol_pred
+        dense0 = {k: v.clone() for k, v in eng.dense_state().items()}
+        tab0 = [eng.gather_table(t) for t in range(len(rows))]
+        for step in range(4):
             b = src.next()
             l = eng.train_step(eng.make_pinned_batch(b.dense, b.ids, b.labels))
             lt = torch.tensor([l], device="cuda", dtype=torch.float64)
             dist.all_reduce(lt)
             if rank == 0:
                 ls = solo.train_step(solo.make_pinned_batch(b.dense, b.ids, b.labels))
-                assert abs(lt.item() - ls) < 2e-3 * max(1.0, abs(ls)), (step, lt.item(), ls)
+                assert abs(lt.item() - ls) < (2e-3 if step == 0 else tol_loss) * max(1.0, abs(ls)), (step, lt.item(), ls)
+            if step == 0:
+                # first-step UPDATES (parameter minus its initial value), dense and every table
+                errs = {}
+                tabs = [eng.gather_table(t) for t in range(len(rows))]
+                if rank == 0:
+                    sd, sr = eng.dense_state(), solo.dense_state()
+                    for k in sd:
+                        if (sr[k] - dense0[k]).abs().sum() > 0:
+                            errs[k] = rel(sd[k] - dense0[k], sr[k] - dense0[k])
+                    for t in range(len(rows)):
+                        errs[f"table{t}"] = rel(tabs[t] - tab0[t], solo.table_weight(t) - tab0[t])
+                    bad = {k: round(v, 5) for k, v in errs.items() if v >= tol_upd}
+                    assert not bad, (bad, {k: round(v, 5) for k, v in errs.items()})
         eng.check()
-        # tables: every rank sends its tables to rank 0 for comparison with the single-GPU run
+        # after four steps: parameters still close
         for t in range(len(rows)):
-            if eng.owner[t] == rank and rank != 0:
-                dist.send(eng.table_weight(t).contiguous(), dst=0)
+            w = eng.gather_table(t)
             if rank == 0:
-                if eng.owner[t] == 0:
-                    w = eng.table_weight(t)
-                else:
-                    w = torch.empty(rows[t], cfg.emb_dim, device="cuda")
-                    dist.recv(w, src=eng.owner[t])
-                ref = solo.table_weight(t)
-                err = ((w - ref).norm() / ref.norm()).item()
-                assert err < 5e-2, (t, err)
+                assert rel(w, solo.table_weight(t)) < 5e-2, (t, rel(w, solo.table_weight(t)))
         if rank == 0:
             sd, sr = eng.dense_state(), solo.dense_state()
             for k in sd:
-                err = ((sd[k] - sr[k]).norm() / (sr[k].norm() + 1e-12)).item()
-                assert err < 1e-3, (k, err)
+                assert rel(sd[k], sr[k]) < 5e-2, (k, rel(sd[k], sr[k]))
         # inference path agrees between the sharded and the single-GPU engine
         b = src.next()
         p = eng.predict(eng.make_pinned_batch(b.dense, b.ids, b.labels))
@@ -124,7 +152,8 @@ def test_dlrm_two_ranks_match_single(graph):
 
 @pytest.mark.parametrize("kind", ["dcn", "projection"])
 def test_dlrm_two_ranks_match_single_other_interactions(kind):
-    """The cross-network and projection interactions: sharded run == single-GPU run (losses, tables, dense weights)."""
+    """The cross-network and projection interactions: sharded run == single-GPU run (losses, tables, dense weights) over
+    four steps."""
     if _ngpus() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -132,6 +161,20 @@ def test_dlrm_two_ranks_match_single_other_interactions(kind):
     out = mgr.dict()
     _spawn(_dlrm_worker, (2, _free_port(), True, out, kind), 2)
     assert all(out.get(r) == "ok" for r in range(2)), dict(out)
+
+
+@pytest.mark.parametrize("kind", ["dot", "dcn"])
+def test_dlrm_row_sharded_tables_match_single(kind):
+    """Tables spread row-wise over the ranks (owner = id % world; a 40-hot, a 3-hot and a 1-hot one): keys travel to the
+    owners, pooled partial sums come back, gradients fan out to every owner.  Result == single-GPU run."""
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    world = 4 if _ngpus() >= 4 else 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    _spawn(_dlrm_worker, (world, _free_port(), True, out, kind, [2, 3, 5]), world)
+    assert all(out.get(r) == "ok" for r in range(world)), dict(out)
 
 
 def _timeout_worker(rank, world, port, out):
