@@ -70,9 +70,12 @@ def _dlrm_worker(rank, world, port, graph, out, kind="dot", split=None):
         # parameter updates must agree almost to rounding: that is the check that catches a wrong exchange, a dropped id or
         # a misrouted gradient.  Later steps compound those last-bit differences through bf16 re-rounding of the weights
         # and the multiplicative cross layers, so they only have to stay close.  Row-sharded tables send their pooled
-        # partial sums as bf16, one rounding more than the single-GPU run has: tolerances of the size of that rounding.
+        # partial sums as bf16, one rounding more than the single-GPU run has (the model's backward turns that 0.3 % into
+        # several per cent of gradient difference, measured); so that the first step can still be compared tightly, that
+        # test starts from table values on a coarse grid (multiples of 1/32, |v| <= 1/16) whose partial sums of up to 40
+        # rows are exact in bf16, which makes its forward pass bit-identical to the single-GPU one.
         lr_e, lr_m = (0.05, 0.05 if kind == "dot" else 0.002) if split is None else (0.01, 0.01 if kind == "dot" else 0.002)
-        tol_pred, tol_upd, tol_loss = (2e-3, 2e-3, 5e-3) if split is None else (2e-2, 5e-2, 5e-2)
+        tol_pred, tol_upd, tol_loss = (2e-3, 2e-3, 5e-3) if split is None else (2e-3, 2e-3, 5e-2)
         cfg = DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=lr_e, mlp_lr=lr_m, seed=5,
                          use_cuda_graph=graph, interaction=kind, dcn_layers=2, dcn_rank=64, projection_sizes=(3, 4),
                          emb_optimizer=opt, row_split=split)
@@ -82,6 +85,13 @@ def _dlrm_worker(rank, world, port, graph, out, kind="dot", split=None):
         if split is not None:
             assert eng.split_tables == sorted(split) and eng.K == len(split)
         src = DLRMBatchSource(rows, hot, B, alpha=1.2, seed=9)
+        if split is not None:
+            for t in range(len(rows)):
+                full = torch.randint(-2, 3, (rows[t], cfg.emb_dim), generator=torch.Generator().manual_seed(100 + t)).float() / 32
+                if rank == 0:
+                    solo.table_weight(t).copy_(full)
+                if t in eng.local_tables:
+                    eng.table_weight(t).copy_(full[rank::world] if t in split else full)
 
         def rel(a, b):
             return ((a - b).norm() / (b.norm() + 1e-20)).item()
@@ -113,14 +123,17 @@ def _dlrm_worker(rank, world, port, graph, out, kind="dot", split=None):
                             errs[k] = rel(sd[k] - dense0[k], sr[k] - dense0[k])
                     for t in range(len(rows)):
                         errs[f"table{t}"] = rel(tabs[t] - tab0[t], solo.table_weight(t) - tab0[t])
-                    bad = {k: round(v, 5) for k, v in errs.items() if v >= tol_upd}
+                    # (a table update is the difference of two fp32 numbers of the size of the weights: with weights on the
+                    # coarse grid, ~1000 x larger than the update, the subtraction alone costs a few 1e-3)
+                    bad = {k: round(v, 5) for k, v in errs.items()
+                           if v >= (1e-2 if split is not None and k.startswith("table") else tol_upd)}
                     assert not bad, (bad, {k: round(v, 5) for k, v in errs.items()})
         eng.check()
         # after four steps: parameters still close
         for t in range(len(rows)):
             w = eng.gather_table(t)
             if rank == 0:
-                assert rel(w, solo.table_weight(t)) < 5e-2, (t, rel(w, solo.table_weight(t)))
+                assert rel(w, solo.table_weight(t)) < (5e-2 if split is None else 1e-1), (t, rel(w, solo.table_weight(t)))
         if rank == 0:
             sd, sr = eng.dense_state(), solo.dense_state()
             for k in sd:
