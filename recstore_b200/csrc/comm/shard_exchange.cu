@@ -18,6 +18,7 @@
 // all2all_data_transfer (recstore/utils.py:227-310) done by three kernels and peer stores, with no
 // host staging, no pack / unpack and no collective call.
 #include <cuda_bf16.h>
+#include "comm/flags.cuh"
 #include "common/rs_common.h"
 #include "kv/hash_table.cuh"
 
@@ -281,6 +282,363 @@ RS_API int rs_expand_rows(const float* src, const int* inverse, long long n, int
   RS_REQUIRE(src && inverse && out && D % 4 == 0, "rs_expand_rows: bad argument");
   if (n == 0) return RS_OK;
   expand_rows_kernel<<<warps_grid(n), 256, 0, stream>>>(src, inverse, n, D, out);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Fused forms: three launches per lookup and two per gradient exchange, flags published and awaited inside the kernels
+// (comm/flags.cuh), no count / signal / wait launches in between.
+//   rs_shard_keys_fused     bucket + push keys (block-aggregated slot assignment), last block delivers the per-owner counts
+//                           and publishes CH_KEYS
+//   rs_shard_gather_fused   owner side: waits for each source's keys, resolves them (cyclic index, or find-or-insert in the
+//                           shard's hash table with a key-derived initial row), pushes the rows back, records a COMPACT
+//                           (row, slot) occurrence list for the optimizer, publishes CH_ROWS
+//   rs_shard_unbucket_fused waits for the rows, writes out[i] = row_window[slot[inverse[i]]] (unbucket + expand in one pass)
+//                           and clears the per-key gradient accumulators for the update that follows
+//   rs_shard_grads_fused    pushes per-key gradient sums and squared norms to the owners, publishes CH_GRADS
+namespace {
+using rs::FlagSignal;
+using rs::FlagWait;
+
+struct KeysFusedArgs {
+  const long long* keys;     // [n]; negative = padding
+  const int* n_dev;          // optional live count (<= n)
+  long long n;
+  int world, me;
+  long long cap;
+  int* cursor;               // [world], zero on entry, zero again on exit
+  long long* const* key_win;
+  int* const* count_win;
+  long long* slot;           // [n]
+  unsigned long long* status;
+  FlagSignal sig;
+};
+
+__global__ void __launch_bounds__(256) shard_keys_fused_kernel(const KeysFusedArgs a) {
+  __shared__ int s_cnt[kMaxWorld];    // keys of this block per owner
+  __shared__ int s_base[kMaxWorld];   // first slot of this block in each owner's region
+  __shared__ uint32_t s_epoch;
+  const int tid = threadIdx.x, lane = tid & 31;
+  if (tid < kMaxWorld) s_cnt[tid] = 0;
+  __syncthreads();
+  const long long n = a.n_dev ? min(static_cast<long long>(*a.n_dev), a.n) : a.n;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + tid;
+  long long k = -1;
+  if (i < n) k = a.keys[i];
+  const int d = k >= 0 ? static_cast<int>(k % a.world) : -1;
+  // rank of this key among the block's keys for the same owner: warp ballot + one shared atomic per (warp, owner)
+  int pos = 0;
+  for (int dd = 0; dd < a.world; ++dd) {
+    const unsigned m = __ballot_sync(0xffffffffu, d == dd);
+    if (m == 0u) continue;
+    int wbase = 0;
+    if (lane == __ffs(m) - 1) wbase = atomicAdd(&s_cnt[dd], __popc(m));
+    wbase = __shfl_sync(0xffffffffu, wbase, __ffs(m) - 1);
+    if (d == dd) pos = wbase + __popc(m & ((1u << lane) - 1u));
+  }
+  __syncthreads();
+  if (tid < a.world) s_base[tid] = s_cnt[tid] ? atomicAdd(&a.cursor[tid], s_cnt[tid]) : 0;
+  __syncthreads();
+  if (i < a.n) {
+    long long sl = -1;
+    if (d >= 0) {
+      const long long p = static_cast<long long>(s_base[d]) + pos;
+      if (p < a.cap) {
+        a.key_win[d][static_cast<long long>(a.me) * a.cap + p] = k;
+        sl = static_cast<long long>(d) * a.cap + p;
+      } else if (a.status) {
+        atomicOr(a.status, (unsigned long long)RS_DEV_OOB_PEER);
+      }
+    }
+    a.slot[i] = sl;
+  }
+  // last block: counts to the owners, cursors back to zero, then the flag
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(a.sig.done, 1u);
+    uint32_t e = 0;
+    if (prev == gridDim.x - 1) {
+      *a.sig.done = 0;
+      e = ++a.sig.sig_counters[a.sig.channel];
+      if (e == 0) e = ++a.sig.sig_counters[a.sig.channel];
+    }
+    s_epoch = e;
+  }
+  __syncthreads();
+  if (s_epoch != 0 && tid < a.world) {
+    __threadfence_system();
+    const int c = *reinterpret_cast<volatile int*>(&a.cursor[tid]);
+    a.count_win[tid][a.me] = c < a.cap ? c : static_cast<int>(a.cap);
+    a.cursor[tid] = 0;
+    __threadfence_system();
+    if (a.sig.flags_of) rs::ptx::st_release_sys(a.sig.flags_of[tid] + a.sig.channel * a.sig.world + a.sig.me, s_epoch);
+  }
+}
+
+// Initial value of a row that the hash-table shard sees for the first time: uniform in [-scale, scale), a function of the key
+// and the column only, so a table does not depend on the order in which its keys arrive.
+__device__ __forceinline__ float key_init_value(unsigned long long key, int col, float scale) {
+  const unsigned long long h = rs::ht_hash(key * 0x9E3779B97F4A7C15ull + static_cast<unsigned long long>(col) + 1ull);
+  return (static_cast<float>(h >> 40) * (1.0f / 16777216.0f) * 2.f - 1.f) * scale;
+}
+
+struct GatherFusedArgs {
+  float* weight;                    // local shard rows (HBM tier)
+  const float* cold_weight;         // rows [hot_rows, local_rows) in device-visible host memory, or null
+  long long hot_rows, local_rows;
+  const long long* key_win;         // my key window [world, cap]
+  const int* count_win;             // my count window [world]
+  float* const* row_win;            // peers' row windows [world, cap, D]
+  long long* rowidx;                // [world, cap] local row per received key (-1 = none), or null
+  long long* occ_row;               // compact occurrence list: local row ...
+  int* occ_slot;                    // ... and its slot (index into the [world, cap] windows)
+  int* occ_cursor;                  // zero on entry
+  int world, me, D;
+  long long cap;
+  int use_hash;
+  rs::HashTableView ht;
+  float init_scale;
+  unsigned char* row_init;          // hash mode: 1 once a row holds its initial value (readers that come earlier compute it)
+  unsigned long long* status;
+  FlagWait wait;
+  FlagSignal sig;
+};
+
+// Persistent warps: source rank s = 0..world-1 in turn (waiting for its flag first), slots p = warp, warp + nwarps, ...
+__global__ void __launch_bounds__(128) shard_gather_fused_kernel(const GatherFusedArgs a) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const int nvec = a.D >> 2;
+  for (int si = 0; si < a.world; ++si) {
+    const int s = (a.me + si) % a.world;                 // start with my own keys (already here)
+    rs::flag_wait_one_warp(a.wait, s);
+    const int cnt = __ldcv(a.count_win + s);
+    for (long long p = warp; p < cnt; p += nwarps) {
+      const long long w = static_cast<long long>(s) * a.cap + p;
+      const long long k = __ldcv(a.key_win + w);
+      long long r = -1;
+      bool fresh = false;
+      if (a.use_hash) {
+        if (lane == 0) {
+          bool ins = false, full = false;
+          r = rs::ht_insert(a.ht, static_cast<unsigned long long>(k), &ins, &full);
+          if (full && a.status) atomicOr(a.status, (unsigned long long)RS_DEV_TABLE_FULL);
+          fresh = ins;
+        }
+        r = __shfl_sync(0xffffffffu, r, 0);
+        fresh = __shfl_sync(0xffffffffu, static_cast<int>(fresh), 0) != 0;
+      } else {
+        r = k / a.world;
+      }
+      if (r < 0 || r >= a.local_rows) {
+        if (!a.use_hash && lane == 0 && a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
+        r = -1;
+      }
+      if (lane == 0) {
+        if (a.rowidx) a.rowidx[w] = r;
+        if (a.occ_cursor && r >= 0) {
+          const int q = atomicAdd(a.occ_cursor, 1);
+          a.occ_row[q] = r;
+          a.occ_slot[q] = static_cast<int>(w);
+        }
+      }
+      // A key that another warp inserted a moment ago may not hold its initial value yet: such a reader computes the same
+      // value from the key instead of reading the row.
+      bool by_formula = fresh;
+      if (a.use_hash && r >= 0 && !fresh) by_formula = *reinterpret_cast<volatile unsigned char*>(a.row_init + r) == 0;
+      float* dst = a.row_win[s] + (static_cast<long long>(a.me) * a.cap + p) * a.D;
+      for (int v = lane; v < nvec; v += 32) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r >= 0) {
+          if (by_formula) {
+            x = make_float4(key_init_value(k, v * 4, a.init_scale), key_init_value(k, v * 4 + 1, a.init_scale),
+                            key_init_value(k, v * 4 + 2, a.init_scale), key_init_value(k, v * 4 + 3, a.init_scale));
+            if (fresh) reinterpret_cast<float4*>(a.weight + r * a.D)[v] = x;   // first touch: the row keeps it
+          } else if (r < a.hot_rows) {
+            x = __ldcg(reinterpret_cast<const float4*>(a.weight + r * a.D) + v);
+          } else {
+            x = __ldcv(reinterpret_cast<const float4*>(a.cold_weight + (r - a.hot_rows) * a.D) + v);   // host tier, read in place
+          }
+        }
+        reinterpret_cast<float4*>(dst)[v] = x;
+      }
+      if (fresh) {
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          *reinterpret_cast<volatile unsigned char*>(a.row_init + r) = 1;
+        }
+      }
+    }
+  }
+  rs::flag_publish_when_grid_done(a.sig);
+}
+
+struct UnbucketFusedArgs {
+  const float* row_win;        // my row window [world, cap, D]
+  const long long* slot;       // [n_unique]
+  const int* inverse;          // [n] or null (then out[i] = row_win[slot[i]])
+  long long n;
+  int D;
+  void* out;
+  int out_bf16;
+  float* ugrad;                // optional: cleared for u < *ucount (per-key gradient accumulators of the coming update)
+  float* unorm;
+  const int* ucount;
+  FlagWait wait;
+};
+
+__global__ void __launch_bounds__(128) shard_unbucket_fused_kernel(const UnbucketFusedArgs a) {
+  rs::flag_wait_all(a.wait);
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const int nvec = a.D >> 2;
+  const long long nu = a.ucount ? *a.ucount : 0;
+  for (long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); i < a.n; i += nwarps) {
+    const long long u = a.inverse ? a.inverse[i] : i;
+    const long long s = u >= 0 ? a.slot[u] : -1;
+    for (int v = lane; v < nvec; v += 32) {
+      const float4 x = s >= 0 ? __ldcv(reinterpret_cast<const float4*>(a.row_win + s * a.D) + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (a.out_bf16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + i * a.D)[v] = o;
+      } else {
+        reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + i * a.D)[v] = x;
+      }
+    }
+    if (a.ugrad && i < nu) {
+      for (int v = lane; v < nvec; v += 32) reinterpret_cast<float4*>(a.ugrad + i * a.D)[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (lane == 0 && a.unorm) a.unorm[i] = 0.f;
+    }
+  }
+}
+
+struct GradsFusedArgs {
+  const float* grad;           // [n, D] per-key gradient sums (or per-occurrence gradients without dedup)
+  const long long* slot;       // [n]
+  const int* n_dev;            // optional live count
+  long long n;
+  int D, me;
+  long long cap;
+  float* const* grad_win;
+  const float* norm;           // optional [n]
+  float* const* norm_win;
+  FlagSignal sig;
+};
+
+__global__ void __launch_bounds__(128) shard_grads_fused_kernel(const GradsFusedArgs a) {
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const long long n = a.n_dev ? min(static_cast<long long>(*a.n_dev), a.n) : a.n;
+  const int nvec = a.D >> 2;
+  for (long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n; i += nwarps) {
+    const long long s = a.slot[i];
+    if (s < 0) continue;
+    const int d = static_cast<int>(s / a.cap);
+    const long long p = s % a.cap;
+    float* dst = a.grad_win[d] + (static_cast<long long>(a.me) * a.cap + p) * a.D;
+    for (int v = lane; v < nvec; v += 32) reinterpret_cast<float4*>(dst)[v] = __ldg(reinterpret_cast<const float4*>(a.grad + i * a.D) + v);
+    if (a.norm && lane == 0) a.norm_win[d][static_cast<long long>(a.me) * a.cap + p] = a.norm[i];
+  }
+  rs::flag_publish_when_grid_done(a.sig);
+}
+
+int persistent_grid(long long items, int warps_per_block) {
+  long long g = (items + warps_per_block - 1) / warps_per_block;
+  const long long capg = 148 * 8;
+  if (g > capg) g = capg;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+FlagSignal make_sig(void* const* flags_of, unsigned* counters, unsigned* done, int channel, int world, int me) {
+  FlagSignal s;
+  s.flags_of = reinterpret_cast<uint32_t* const*>(flags_of); s.sig_counters = counters; s.done = done;
+  s.channel = channel; s.world = world; s.me = me;
+  return s;
+}
+FlagWait make_wait(const void* my_flags, const unsigned* counters, unsigned long long timeout_ns, int channel, int world,
+                   unsigned long long* status) {
+  FlagWait w;
+  w.my_flags = reinterpret_cast<const uint32_t*>(my_flags); w.sig_counters = counters; w.timeout_ns = timeout_ns;
+  w.status = status; w.world = world; w.channel = channel;
+  return w;
+}
+}  // namespace
+
+// n_dev (optional): device count of live keys (the output count of rs_unique_keys); n is then the capacity that sizes the grid.
+RS_API int rs_shard_keys_fused(const long long* keys, const int* n_dev, long long n, int world, int me, long long cap, int* cursor,
+                               void* const* key_win, void* const* count_win, long long* slot, unsigned long long* status,
+                               void* const* flags_of, unsigned* counters, unsigned* done, int channel, cudaStream_t stream) {
+  RS_REQUIRE(keys && cursor && key_win && count_win && slot && flags_of && counters && done, "rs_shard_keys_fused: null argument");
+  RS_REQUIRE(world >= 1 && world <= kMaxWorld && n >= 0 && me >= 0 && me < world, "rs_shard_keys_fused: bad sizes");
+  KeysFusedArgs a;
+  a.keys = keys; a.n_dev = n_dev; a.n = n; a.world = world; a.me = me; a.cap = cap; a.cursor = cursor;
+  a.key_win = reinterpret_cast<long long* const*>(key_win); a.count_win = reinterpret_cast<int* const*>(count_win);
+  a.slot = slot; a.status = status; a.sig = make_sig(flags_of, counters, done, channel, world, me);
+  const long long grid = n > 0 ? (n + 255) / 256 : 1;
+  RS_REQUIRE(grid < (1ll << 31), "rs_shard_keys_fused: too many keys");
+  shard_keys_fused_kernel<<<static_cast<unsigned>(grid), 256, 0, stream>>>(a);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+// ht (optional): find-or-insert in the shard's hash table instead of the cyclic index; a key seen for the first time gets a row
+// initialised to uniform(-init_scale, init_scale) values derived from the key.  occ_* (optional): compact occurrence list.
+RS_API int rs_shard_gather_fused(float* weight, const float* cold_weight, long long hot_rows, long long local_rows,
+                                 const long long* key_win, const int* count_win, void* const* row_win, long long* rowidx,
+                                 long long* occ_row, int* occ_slot, int* occ_cursor, int world, int me, int D, long long cap,
+                                 const rs::HashTableView* ht, float init_scale, unsigned char* row_init, unsigned long long* status,
+                                 const void* my_flags,
+                                 void* const* flags_of, unsigned* counters, unsigned* done, unsigned long long timeout_ns,
+                                 int wait_channel, int sig_channel, cudaStream_t stream) {
+  RS_REQUIRE((weight || hot_rows == 0) && key_win && count_win && row_win && D % 4 == 0, "rs_shard_gather_fused: bad argument");
+  RS_REQUIRE(hot_rows >= 0 && hot_rows <= local_rows && (hot_rows == local_rows || cold_weight), "rs_shard_gather_fused: bad tiers");
+  RS_REQUIRE(!occ_cursor || (occ_row && occ_slot), "rs_shard_gather_fused: the occurrence list needs both arrays");
+  RS_REQUIRE(my_flags && flags_of && counters && done, "rs_shard_gather_fused: null flag argument");
+  GatherFusedArgs a;
+  a.weight = weight; a.cold_weight = cold_weight; a.hot_rows = hot_rows; a.local_rows = local_rows; a.key_win = key_win;
+  a.count_win = count_win; a.row_win = reinterpret_cast<float* const*>(row_win); a.rowidx = rowidx; a.occ_row = occ_row;
+  a.occ_slot = occ_slot; a.occ_cursor = occ_cursor; a.world = world; a.me = me; a.D = D; a.cap = cap;
+  a.use_hash = ht != nullptr;
+  if (ht) a.ht = *ht; else memset(&a.ht, 0, sizeof(a.ht));
+  RS_REQUIRE(!ht || row_init, "rs_shard_gather_fused: the hash-table shard needs its row_init bytes");
+  a.init_scale = init_scale; a.row_init = row_init; a.status = status;
+  a.wait = make_wait(my_flags, counters, timeout_ns, wait_channel, world, status);
+  a.sig = make_sig(flags_of, counters, done, sig_channel, world, me);
+  shard_gather_fused_kernel<<<persistent_grid(cap, 4), 128, 0, stream>>>(a);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+RS_API int rs_shard_unbucket_fused(const float* row_win, const long long* slot, const int* inverse, long long n, int D, void* out,
+                                   int out_bf16, float* ugrad, float* unorm, const int* ucount, const void* my_flags,
+                                   const unsigned* counters, unsigned long long timeout_ns, int wait_channel, int world,
+                                   unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(row_win && slot && out && D % 4 == 0 && my_flags && counters, "rs_shard_unbucket_fused: bad argument");
+  UnbucketFusedArgs a;
+  a.row_win = row_win; a.slot = slot; a.inverse = inverse; a.n = n; a.D = D; a.out = out; a.out_bf16 = out_bf16;
+  a.ugrad = ugrad; a.unorm = unorm; a.ucount = ucount;
+  a.wait = make_wait(my_flags, counters, timeout_ns, wait_channel, world, status);
+  shard_unbucket_fused_kernel<<<persistent_grid(n, 4), 128, 0, stream>>>(a);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+RS_API int rs_shard_grads_fused(const float* grad, const long long* slot, const int* n_dev, long long n, int D, int me, long long cap,
+                                void* const* grad_win, const float* norm, void* const* norm_win, void* const* flags_of,
+                                unsigned* counters, unsigned* done, int channel, int world, cudaStream_t stream) {
+  RS_REQUIRE(grad && slot && grad_win && D % 4 == 0 && flags_of && counters && done, "rs_shard_grads_fused: bad argument");
+  GradsFusedArgs a;
+  a.grad = grad; a.slot = slot; a.n_dev = n_dev; a.n = n; a.D = D; a.me = me; a.cap = cap;
+  a.grad_win = reinterpret_cast<float* const*>(grad_win); a.norm = norm; a.norm_win = reinterpret_cast<float* const*>(norm_win);
+  a.sig = make_sig(flags_of, counters, done, channel, world, me);
+  shard_grads_fused_kernel<<<persistent_grid(n, 4), 128, 0, stream>>>(a);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

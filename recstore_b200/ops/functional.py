@@ -104,14 +104,15 @@ def emb_forward_ex(weight, table_base, table_rows, indices, hotness, hot_base, *
 
 def emb_backward_ex(weight, state, row_idx, occ2bag, nnz: int, grad, *, grad_col=None, grad_row_stride: int, B: int, D: int,
                     lr: float, eps: float = 1e-10, optimizer: str = "rowwise_adagrad", status=None, gnorm=None,
-                    gnorm_stride: int = 0, nnz_dev=None, ctx=None, wait_channel: int = -1) -> None:
-    """:func:`emb_backward` (bf16 gradients) with a device-side occurrence count (``nnz_dev``; ``nnz`` is then the capacity
+                    gnorm_stride: int = 0, nnz_dev=None, ctx=None, wait_channel: int = -1, grad_bf16: bool = True) -> None:
+    """:func:`emb_backward` with a device-side occurrence count (``nnz_dev``; ``nnz`` is then the capacity
     of the lists) and a bounded in-kernel wait on ``wait_channel`` for the peers' gradient pushes."""
     _need_cuda(weight, row_idx, grad)
     opt = {"sgd": 0, "rowwise_adagrad": 1}[optimizer]
     wait = ctx is not None and wait_channel >= 0
     call("rs_emb_backward_ex", ptr(weight), ptr(state), weight.shape[0], ptr(row_idx), ptr(occ2bag), nnz, ptr(grad),
-         ptr(grad_col), grad_row_stride, gnorm if isinstance(gnorm, int) else ptr(gnorm), gnorm_stride, B, D, 1, lr, eps, opt,
+         ptr(grad_col), grad_row_stride, gnorm if isinstance(gnorm, int) else ptr(gnorm), gnorm_stride, B, D,
+         1 if grad_bf16 else 0, lr, eps, opt,
          ptr(status), ptr(nnz_dev), ctx.my_flags_ptr if wait else None, ctx.counters_ptr if wait else None,
          ctx.wait_timeout_ns if ctx is not None else 0, max(wait_channel, 0), ctx.world if ctx is not None else 1, stream_ptr())
 

@@ -1,11 +1,20 @@
-"""Row-sharded embedding table over the GPUs of one box (cyclic placement: owner(id) = id % world).
+"""Row-sharded embedding table over the GPUs of one box (owner(id) = id % world).
 
 ``lookup(ids)`` returns the rows of arbitrary global ids on the calling rank; ``update(grads)`` sends
 the gradients of the last lookup back to the owners, which segment-reduce duplicates and apply SGD
 or row-wise Adagrad in place.  Keys, rows and gradients move with peer stores into NVLink-mapped
-windows (``csrc/comm/shard_exchange.cu``), ordered by flag channels; nothing is staged through the
-host and no collective is called.  Duplicate ids are folded before they travel
-(``unique_keys`` + ``segment_sum``), which matters for Zipf / power-law id streams.
+windows (``csrc/comm/shard_exchange.cu``); every kernel publishes its own flag when its grid is
+done and the consumer waits inside its own prologue, so a lookup is five launches (clear + unique,
+bucket-and-push keys, owner-side gather-and-push rows, unbucket-and-expand) and an update four
+(segment sum, push, optimizer state, apply).  Nothing is staged through the host and no collective is
+called.  Duplicate ids are folded before they travel (``unique_keys`` + ``segment_sum``), which
+matters for Zipf / power-law id streams.
+
+Storage of a shard: a dense array indexed by ``id // world`` (ids are row numbers 0..N-1), or, with
+``hashed=True``, an HBM hash table (``csrc/kv/hash_table.cuh``) from arbitrary 64-bit keys to rows of
+a row store: a key is inserted when it is first looked up and its row starts from values derived
+from the key, so a table does not depend on the order in which keys arrive.  ``hbm_ratio < 1`` (dense
+storage only) keeps the cold part of every shard in pinned host memory.
 
 This is the storage behind the knowledge-graph entity table (86 M x 400 spread over 8 x HBM) and the
 parameter-server micro-benchmark, and the native counterpart of the reference's
@@ -35,6 +44,14 @@ _lib.register_signatures({
     "rs_segment_sum": (i32, [vp, vp, i64, i32, vp, vp, vp]),
     "rs_expand_rows": (i32, [vp, vp, i64, i32, vp, vp]),
     "rs_unique_keys": (i32, [vp, i64, vp, vp, _lib.u64, vp, vp, vp, vp, vp]),
+    "rs_shard_keys_fused": (i32, [vp, vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp]),
+    "rs_shard_gather_fused": (i32, [vp, vp, i64, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, C.POINTER(HashTableView), f32, vp,
+                                    vp, vp, vp, vp, vp, _lib.u64, i32, i32, vp]),
+    "rs_shard_unbucket_fused": (i32, [vp, vp, vp, i64, i32, vp, i32, vp, vp, vp, vp, vp, _lib.u64, i32, i32, vp, vp]),
+    "rs_shard_grads_fused": (i32, [vp, vp, vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp, i32, i32, vp]),
+    "rs_ht_create": (i32, [_lib.u64, i32, C.POINTER(vp), C.POINTER(HashTableView)]),
+    "rs_ht_destroy": (i32, [vp]),
+    "rs_ht_dump": (i32, [C.POINTER(HashTableView), vp, vp, vp, _lib.u64, vp]),
 })
 
 CH_KEYS, CH_ROWS, CH_GRADS = 8, 9, 10
@@ -43,14 +60,20 @@ CH_KEYS, CH_ROWS, CH_GRADS = 8, 9, 10
 class ShardedEmbeddingTable:
     def __init__(self, ctx: PeerContext, name: str, num_rows: int, dim: int, max_keys: int, *, lr: float = 0.01,
                  eps: float = 1e-10, optimizer: str = "rowwise_adagrad", dedup: bool = True, init: str = "uniform",
-                 init_scale: Optional[float] = None, seed: int = 0, hbm_ratio: float = 1.0):
+                 init_scale: Optional[float] = None, seed: int = 0, hbm_ratio: float = 1.0, hashed: bool = False,
+                 fused: bool = True):
         assert dim % 4 == 0
+        assert not (hashed and hbm_ratio < 1.0), "the hash-table shard lives in HBM"
         self.ctx, self.name, self.N, self.D = ctx, name, int(num_rows), int(dim)
         self.rank, self.world = ctx.rank, ctx.world
         self.cap = int(max_keys)
         self.lr, self.eps, self.optimizer, self.dedup = lr, eps, optimizer, dedup
         dev = self.dev = ctx.device
+        self.hashed, self.fused = bool(hashed), bool(fused) or bool(hashed)
+        # dense storage: rows of ids me, me + world, ...; hashed storage: room for this shard's share of N distinct keys
         self.local_rows = (self.N + self.world - 1) // self.world
+        if self.hashed:
+            self.local_rows = int(self.local_rows * 1.25) + 1024        # keys hash unevenly over the owners
         # Two tiers per shard when hbm_ratio < 1: local rows [0, hot_rows) in HBM, the rest in pinned host memory that
         # the kernels address in place.  Local row = id // world, so with ids in popularity order the hot ids of every
         # shard are its first rows.
@@ -76,6 +99,13 @@ class ShardedEmbeddingTable:
                 self.cold.copy_(full[self.hot_rows:])
         else:
             raise ValueError(init)
+        self.init_scale = float(init_scale if init_scale is not None else math.sqrt(1.0 / self.N))
+        self._ht = self._ht_view = None
+        if self.hashed:
+            self._ht, self._ht_view = vp(), HashTableView()
+            with torch.cuda.device(dev):
+                _lib.call("rs_ht_create", 2 * self.local_rows, self.local_rows, C.byref(self._ht), C.byref(self._ht_view))
+            self.row_init = torch.zeros(self.local_rows, dtype=torch.uint8, device=dev)
         adagrad = optimizer == "rowwise_adagrad"
         self.state = torch.zeros(self.hot_rows, device=dev) if adagrad else None
         self.cold_state = torch.zeros(self.local_rows - self.hot_rows, pin_memory=True) if adagrad and self.tiered else None
@@ -102,8 +132,22 @@ class ShardedEmbeddingTable:
         self._ucount = torch.zeros(1, dtype=torch.int32, device=dev)
         self._urows = torch.empty(n, D, device=dev)
         self._ugrad = torch.empty(n, D, device=dev)
+        # compact (row, slot) occurrence list written by the owner-side gather of the fused path, and the "grid done"
+        # counters of the kernels that publish their own flag
+        self._occ_row = torch.empty(n, dtype=torch.int64, device=dev)
+        self._occ_slot = torch.empty(n, dtype=torch.int32, device=dev)
+        self._occ_cursor = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._grid_done = torch.zeros(4, dtype=torch.int32, device=dev)
         self._n = 0
         self.launches = 0
+
+    def __del__(self):
+        try:
+            if self._ht:
+                _lib.lib().rs_ht_destroy(self._ht)
+                self._ht = None
+        except Exception:
+            pass
 
     # ------------------------------------------------------------------ forward
     def lookup(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -122,7 +166,7 @@ class ShardedEmbeddingTable:
             self.launches += 3
         else:
             keys = ids
-        if self.world == 1 and not self.tiered:
+        if self.world == 1 and not self.tiered and not self.hashed:
             # One rank: every row is local (local row = id), so nothing is bucketed or exchanged.
             src_keys = keys[:n]
             if out is None:
@@ -134,6 +178,8 @@ class ShardedEmbeddingTable:
             self._local_rows = src_keys
             self.launches += 2
             return out
+        if self.fused:
+            return self._lookup_fused(keys, n, out, st, sp)
         _lib.call("rs_shard_push_keys", ptr(keys), n, self.world, self.rank, self.cap, ptr(self._counts), ptr(self._cursor),
                   ptr(self.key_win.table), ptr(self.count_win.table), ptr(self._slot), ptr(st), sp)
         self.ctx.signal(CH_KEYS); self.ctx.wait(CH_KEYS)
@@ -156,6 +202,51 @@ class ShardedEmbeddingTable:
         self.launches += 9
         return out
 
+    def _lookup_fused(self, keys, n, out, st, sp):
+        c = self.ctx
+        gd = self._grid_done
+        self._occ_cursor.zero_()
+        _lib.call("rs_shard_keys_fused", ptr(keys), ptr(self._ucount) if self.dedup else None, n, self.world, self.rank, self.cap,
+                  ptr(self._cursor), ptr(self.key_win.table), ptr(self.count_win.table), ptr(self._slot), ptr(st),
+                  c.flags_table_ptr, c.counters_ptr, ptr(gd[0:1]), CH_KEYS, sp)
+        _lib.call("rs_shard_gather_fused", ptr(self.weight), ptr(self.cold), self.hot_rows, self.local_rows, self.key_win.local_ptr,
+                  self.count_win.local_ptr, ptr(self.row_win.table), ptr(self.rowidx) if self.tiered else None, ptr(self._occ_row),
+                  ptr(self._occ_slot), ptr(self._occ_cursor), self.world, self.rank, self.D, self.cap,
+                  C.byref(self._ht_view) if self.hashed else None, self.init_scale, ptr(self.row_init) if self.hashed else None,
+                  ptr(st), c.my_flags_ptr, c.flags_table_ptr, c.counters_ptr, ptr(gd[1:2]), c.wait_timeout_ns, CH_KEYS, CH_ROWS, sp)
+        if out is None:
+            out = torch.empty(n, self.D, device=self.dev)
+        _lib.call("rs_shard_unbucket_fused", self.row_win.local_ptr, ptr(self._slot), ptr(self._inv) if self.dedup else None, n, self.D,
+                  ptr(out), 0, ptr(self._ugrad) if self.dedup else None, ptr(self._unorm) if self.dedup else None,
+                  ptr(self._ucount) if self.dedup else None, c.my_flags_ptr, c.counters_ptr, c.wait_timeout_ns, CH_ROWS, self.world,
+                  ptr(st), sp)
+        self.launches += 4
+        return out
+
+    def _update_fused(self, grads, n, st, sp):
+        c = self.ctx
+        if self.dedup:      # the accumulators were cleared by the lookup's last kernel
+            _lib.call("rs_segment_sum", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), sp)
+            g, gn, nd = self._ugrad, self._unorm, self._ucount
+            self.launches += 1
+        else:
+            g, gn, nd = grads, None, None
+        _lib.call("rs_shard_grads_fused", ptr(g), ptr(self._slot), ptr(nd), n, self.D, self.rank, self.cap, ptr(self.grad_win.table),
+                  ptr(gn), ptr(self.norm_win.table) if gn is not None else None, c.flags_table_ptr, c.counters_ptr,
+                  ptr(self._grid_done[2:3]), CH_GRADS, self.world, sp)
+        nnz = self.world * self.cap
+        if self.tiered:
+            c.wait_own(CH_GRADS)
+            gnorm = self.norm_win.view(torch.float32, (nnz,)) if gn is not None else None
+            self._apply_tiered(nnz, gnorm, st, sp)
+            self.launches += 11
+            return
+        F_.emb_backward_ex(self.weight, self.state, self._occ_row, self._occ_slot, nnz, self.grad_win.local, grad_row_stride=self.D,
+                           B=nnz, D=self.D, grad_bf16=False, lr=self.lr, eps=self.eps, optimizer=self.optimizer, status=st,
+                           gnorm=self.norm_win.local if gn is not None else None, gnorm_stride=1, nnz_dev=self._occ_cursor,
+                           ctx=c, wait_channel=CH_GRADS)
+        self.launches += 3 if self.optimizer == "rowwise_adagrad" else 2
+
     # ------------------------------------------------------------------ backward
     def update(self, grads: torch.Tensor) -> None:
         """Applies the optimizer to the rows of the LAST lookup; ``grads`` [n, D] fp32, one row per looked-up id."""
@@ -163,7 +254,7 @@ class ShardedEmbeddingTable:
         assert grads.shape == (n, self.D) and grads.dtype == torch.float32
         grads = grads.contiguous()
         st, sp = self.ctx.status, stream_ptr()
-        if self.world == 1 and not self.tiered:
+        if self.world == 1 and not self.tiered and not self.hashed:
             if self.dedup:
                 self._ugrad[:n].zero_()
                 self._unorm[:n].zero_()
@@ -175,6 +266,8 @@ class ShardedEmbeddingTable:
                             grad_bf16=False, lr=self.lr, eps=self.eps, optimizer=self.optimizer, status=st, gnorm=gn, gnorm_stride=1)
             self.launches += 5
             return
+        if self.fused:
+            return self._update_fused(grads, n, st, sp)
         gnorm = None
         if self.dedup:
             self._ugrad[:n].zero_()
@@ -236,6 +329,21 @@ class ShardedEmbeddingTable:
     # ------------------------------------------------------------------ whole-table access (tests, checkpoints)
     def local_global_ids(self) -> torch.Tensor:
         return torch.arange(self.local_rows, device=self.dev) * self.world + self.rank
+
+    def dump(self):
+        """(keys, rows) of this rank's shard: every key of a hashed shard with its row values, for checkpoints and tests;
+        for dense storage the ids ``rank, rank + world, ...`` below ``num_rows`` with theirs."""
+        if not self.hashed:
+            ids = self.local_global_ids()
+            ids = ids[ids < self.N]
+            return ids, self.weight[:ids.numel()].clone()
+        cap = int(self._ht_view.mask) + 1
+        k = torch.empty(cap, dtype=torch.int64, device=self.dev)
+        r = torch.empty(cap, dtype=torch.int64, device=self.dev)
+        cnt = torch.zeros(1, dtype=torch.int64, device=self.dev)
+        _lib.call("rs_ht_dump", C.byref(self._ht_view), ptr(k), ptr(r), ptr(cnt), cap, stream_ptr())
+        m = int(cnt.item())
+        return k[:m], self.weight[r[:m]]
 
     def nvlink_bytes_per_lookup(self, n_unique_remote: int) -> int:
         return n_unique_remote * (8 + self.D * 4)

@@ -175,6 +175,61 @@ def test_sharded_table_single_gpu(dev):
         assert torch.allclose(tab.weight, W, atol=2e-3, rtol=2e-3)
 
 
+def _key_init_rows(keys, D, scale):
+    """CPU mirror of the hash-table shard's first-touch initial row (a function of key and column only)."""
+    import numpy as np
+    M = np.uint64(0xFFFFFFFFFFFFFFFF)
+    with np.errstate(over="ignore"):
+        k = np.asarray(keys, dtype=np.uint64)[:, None] * np.uint64(0x9E3779B97F4A7C15) + (np.arange(D, dtype=np.uint64)[None, :] + np.uint64(1))
+        k ^= k >> np.uint64(33); k *= np.uint64(0xff51afd7ed558ccd)
+        k ^= k >> np.uint64(33); k *= np.uint64(0xc4ceb9fe1a85ec53)
+        k ^= k >> np.uint64(33)
+    u = (k >> np.uint64(40)).astype(np.float32) * np.float32(1.0 / 16777216.0)
+    return torch.from_numpy((u * np.float32(2.0) - np.float32(1.0)) * np.float32(scale))
+
+
+@pytest.mark.parametrize("dedup", [True, False])
+def test_hashed_shard_first_touch_lookup_update_dump(dev, dedup):
+    """A shard whose storage is the HBM hash table: arbitrary 64-bit keys, inserted when first looked up with a row
+    derived from the key, updated in place by row-wise Adagrad, enumerated by dump().  Against a dict on the CPU."""
+    from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
+    from recstore_b200.parallel.peer import PeerContext
+    from recstore_b200.parallel.sharded_table import ShardedEmbeddingTable
+    ctx = PeerContext(0, 1, device=dev)
+    D, n, scale = 32, 3000, 0.05
+    tab = ShardedEmbeddingTable(ctx, f"hashed{int(dedup)}", 8000, D, max_keys=n, lr=0.1, eps=1e-8, dedup=dedup, hashed=True,
+                                init_scale=scale)
+    g = torch.Generator().manual_seed(11)
+    pool = torch.randint(1 << 40, 1 << 62, (4000,), generator=g)                # nothing like row numbers
+    oracle_w, oracle_s = {}, {}
+    for step in range(4):
+        ids = pool[torch.randint(0, pool.numel(), (n,), generator=g)]
+        ids[::7] = pool[5]                                                       # a hot key
+        new = [k for k in set(ids.tolist()) if k not in oracle_w]
+        if new:
+            init = _key_init_rows(new, D, scale)
+            for k, r in zip(new, init):
+                oracle_w[k], oracle_s[k] = r.clone(), 0.0
+        rows = tab.lookup(ids.to(dev)).cpu()
+        ref = torch.stack([oracle_w[k] for k in ids.tolist()])
+        assert torch.allclose(rows, ref, atol=1e-6), (step, (rows - ref).abs().max())
+        grads = torch.randn(n, D, generator=g)
+        tab.update(grads.to(dev))
+        # oracle update on a dense copy of the touched keys
+        uk = sorted(set(ids.tolist()))
+        pos = {k: i for i, k in enumerate(uk)}
+        W = torch.stack([oracle_w[k] for k in uk]); S = torch.tensor([oracle_s[k] for k in uk])
+        rowwise_adagrad_update(W, S, torch.tensor([pos[k] for k in ids.tolist()]), grads, 0.1, 1e-8)
+        for k, i in pos.items():
+            oracle_w[k], oracle_s[k] = W[i], float(S[i])
+    torch.cuda.synchronize()
+    ctx.check_status()
+    keys, vals = tab.dump()
+    assert sorted(keys.cpu().tolist()) == sorted(oracle_w)                       # exactly the keys that were ever looked up
+    ref = torch.stack([oracle_w[k] for k in keys.cpu().tolist()])
+    assert torch.allclose(vals.cpu(), ref, atol=2e-4, rtol=2e-4)
+
+
 def test_tiered_table_lookup_and_adagrad_on_both_tiers():
     from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
     from recstore_b200.cache.tiered_table import TieredEmbeddingTable

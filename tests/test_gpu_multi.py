@@ -237,9 +237,10 @@ def _sharded_worker(rank, world, port, out):
         from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
         ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"))
         N, D, n = 5000, 32, 3000
-        for dedup, ratio in ((True, 1.0), (False, 1.0), (True, 0.2), (False, 0.2)):   # ratio < 1: host tier behind the HBM rows
-            tab = ShardedEmbeddingTable(ctx, f"t{int(dedup)}{int(ratio * 10)}", N, D, max_keys=n, lr=0.1, eps=1e-8, dedup=dedup,
-                                        init="row_index", hbm_ratio=ratio)
+        # ratio < 1: host tier behind the HBM rows; fused = False: the exchange as separate count / signal / wait launches
+        for dedup, ratio, fused in ((True, 1.0, True), (False, 1.0, True), (True, 0.2, True), (False, 0.2, True), (True, 1.0, False)):
+            tab = ShardedEmbeddingTable(ctx, f"t{int(dedup)}{int(ratio * 10)}{int(fused)}", N, D, max_keys=n, lr=0.1, eps=1e-8,
+                                        dedup=dedup, init="row_index", hbm_ratio=ratio, fused=fused)
             # oracle: full table replicated on every rank
             W = torch.arange(N, device="cuda", dtype=torch.float32).unsqueeze(1).repeat(1, D)
             S = torch.zeros(N, device="cuda")
