@@ -416,6 +416,8 @@ __global__ void __launch_bounds__(128) shard_gather_fused_kernel(const GatherFus
     const int s = (a.me + si) % a.world;                 // start with my own keys (already here)
     rs::flag_wait_one_warp(a.wait, s);
     const int cnt = __ldcv(a.count_win + s);
+    if (a.rowidx)   // the [world, cap] view (two-tier update): slots past this step's count hold nothing
+      for (long long p = cnt + warp * 32 + lane; p < a.cap; p += nwarps * 32) a.rowidx[static_cast<long long>(s) * a.cap + p] = -1;
     for (long long p = warp; p < cnt; p += nwarps) {
       const long long w = static_cast<long long>(s) * a.cap + p;
       const long long k = __ldcv(a.key_win + w);

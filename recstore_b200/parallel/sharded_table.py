@@ -182,7 +182,7 @@ class ShardedEmbeddingTable:
             return self._lookup_fused(keys, n, out, st, sp)
         _lib.call("rs_shard_push_keys", ptr(keys), n, self.world, self.rank, self.cap, ptr(self._counts), ptr(self._cursor),
                   ptr(self.key_win.table), ptr(self.count_win.table), ptr(self._slot), ptr(st), sp)
-        self.ctx.signal(CH_KEYS); self.ctx.wait(CH_KEYS)
+        self.ctx.signal(CH_KEYS); self.ctx.wait_own(CH_KEYS)
         if self.tiered:
             _lib.call("rs_shard_gather_push_rows_tiered", ptr(self.weight), ptr(self.cold), self.hot_rows, self.local_rows,
                       self.key_win.local_ptr, self.count_win.local_ptr, ptr(self.row_win.table), ptr(self.rowidx), self.world,
@@ -190,7 +190,7 @@ class ShardedEmbeddingTable:
         else:
             _lib.call("rs_shard_gather_push_rows", ptr(self.weight), self.local_rows, self.key_win.local_ptr, self.count_win.local_ptr,
                       ptr(self.row_win.table), ptr(self.rowidx), self.world, self.rank, self.D, self.cap, None, ptr(st), sp)
-        self.ctx.signal(CH_ROWS); self.ctx.wait(CH_ROWS)
+        self.ctx.signal(CH_ROWS); self.ctx.wait_own(CH_ROWS)
         if out is None:
             out = torch.empty(n, self.D, device=self.dev)
         if self.dedup:
@@ -279,7 +279,7 @@ class ShardedEmbeddingTable:
         else:
             _lib.call("rs_shard_push_grads", ptr(grads), ptr(self._slot), n, self.D, self.rank, self.cap,
                       ptr(self.grad_win.table), None, None, sp)
-        self.ctx.signal(CH_GRADS); self.ctx.wait(CH_GRADS)
+        self.ctx.signal(CH_GRADS); self.ctx.wait_own(CH_GRADS)
         nnz = self.world * self.cap
         if self.tiered:
             self._apply_tiered(nnz, gnorm, st, sp)

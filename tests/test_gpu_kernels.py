@@ -351,6 +351,73 @@ def test_dlrm_step_matches_torch_oracle(dev, graph):
     assert losses[-1][0] < losses[0][0]
 
 
+def test_dlrm_first_step_matches_precision_faithful_oracle(dev):
+    """The engine against a restatement that rounds where the engine rounds (bf16 weights, activations and activation
+    gradients, fp32 accumulation, ReLU masks taken from the bf16 activations): unlike the fp32 oracle above it sees the
+    same masks, so every first-step dense update and every embedding gradient row has to agree to about one per cent;
+    a transposed operand, a dropped bias gradient or a wrong mask would be tens of per cent."""
+    from recstore_b200.models.dlrm import DLRM, DLRMConfig
+    from recstore_b200.utils.data import DLRMBatchSource
+    rows, hot, B, lr = [1000, 37, 5000, 12, 300, 20000], [1, 2, 1, 3, 1, 1], 512, 0.05
+    eng = DLRM(DLRMConfig(table_rows=rows, batch=B, hotness=hot, emb_lr=lr, mlp_lr=lr, seed=5, use_cuda_graph=True))
+    D, F = eng.D, eng.F
+    bf = lambda x: x.bfloat16().float()
+    P = {k: v.clone() for k, v in eng.dense_state().items()}
+    Wb = {k: bf(v) for k, v in P.items()}
+    tabs = [eng.table_weight(t).clone() for t in range(len(rows))]
+    b = DLRMBatchSource(rows, hot, B, alpha=1.2, seed=9).next()
+    loss = eng.train_step(eng.make_pinned_batch(b.dense, b.ids, b.labels))
+    # ---- forward, rounding where the engine rounds
+    nb, nt = len(eng.bot), len(eng.top)
+    h = bf(b.dense.to(dev))
+    acts_b = []
+    for i in range(nb):
+        h = bf(torch.relu(h @ Wb[f"bot.{i}.weight"].t() + P[f"bot.{i}.bias"]))
+        acts_b.append(h)
+    feats = [acts_b[-1]] + [bf(tabs[t][b.ids[t].to(dev).view(B, hot[t])].sum(1)) for t in range(len(rows))]
+    T = torch.stack(feats, 1)
+    li, lj = torch.tril_indices(F, F, offset=-1)
+    li, lj = li.to(dev), lj.to(dev)
+    z = bf(torch.cat([T[:, 0], (T @ T.transpose(1, 2))[:, li, lj]], 1))
+    a, acts_t = z, []
+    for i in range(nt):
+        a = bf(torch.relu(a @ Wb[f"top.{i}.weight"].t() + P[f"top.{i}.bias"]))
+        acts_t.append(a)
+    logit = a @ P["head.weight"] + P["head.bias"]
+    y = b.labels.to(dev)
+    ref_loss = torch.nn.functional.binary_cross_entropy_with_logits(logit, y, reduction="sum").item() / B
+    assert abs(loss - ref_loss) < 2e-3 * max(1.0, abs(ref_loss)), (loss, ref_loss)
+    # ---- backward
+    dlogit = (torch.sigmoid(logit) - y) / B
+    G = {"head.weight": (dlogit[:, None] * a).sum(0), "head.bias": dlogit.sum().view(1)}
+    d = bf(dlogit[:, None] * P["head.weight"][None, :] * (a > 0))
+    for i in range(nt - 1, -1, -1):
+        xin = acts_t[i - 1] if i > 0 else z
+        G[f"top.{i}.weight"], G[f"top.{i}.bias"] = d.t() @ xin, d.sum(0)
+        dn = d @ Wb[f"top.{i}.weight"]
+        d = bf(dn * (xin > 0)) if i > 0 else bf(dn)
+    dZ = torch.zeros(B, F, F, device=dev)
+    dZ[:, li, lj] = d[:, D:D + li.numel()]
+    dT = (dZ + dZ.transpose(1, 2)) @ T
+    dT[:, 0] += d[:, :D]
+    emb_g = bf(dT[:, 1:])
+    d = bf(dT[:, 0] * (T[:, 0] > 0))
+    x0 = bf(b.dense.to(dev))
+    for i in range(nb - 1, -1, -1):
+        xin = acts_b[i - 1] if i > 0 else x0
+        G[f"bot.{i}.weight"], G[f"bot.{i}.bias"] = d.t() @ xin, d.sum(0)
+        if i > 0:
+            d = bf((d @ Wb[f"bot.{i}.weight"]) * (xin > 0))
+    # ---- compare: dense updates (SGD: -lr * gradient) and the embedding gradient rows the engine produced
+    now = eng.dense_state()
+    errs = {k: _rel_err(now[k] - P[k], (-lr * G[k]).view_as(P[k])) for k in P}
+    Gw = eng.Gwin.view(torch.bfloat16, (B, eng.grow_stride)).view(B, eng.Tmax, D).float()
+    for t in range(len(rows)):
+        errs[f"emb_grad{t}"] = _rel_err(Gw[:, t], emb_g[:, t])
+    bad = {k: round(v, 4) for k, v in errs.items() if v > 2e-2}
+    assert not bad, (bad, {k: round(v, 4) for k, v in errs.items()})
+
+
 def test_train_step_raises_on_out_of_range_ids(dev):
     """An id outside its table is skipped by the kernels and recorded in the device status word; the step's result
     must not be handed out as if nothing happened: ``train_step`` reads the word with the loss and raises."""
