@@ -15,7 +15,15 @@ Types (``CacheEmbFactory.New``), as in src/python/pytorch/recstore/cache/cache_e
   table; backward sends (keys, grads) to the owners and the miss gradients to the host table.
 * ``KGExternelEmbedding``  host table updated directly in backward (cache_common.py:162-220).
 
-``args``: ``cache_ratio`` (per-rank fraction c = int(N * ratio)), ``backwardMode`` in {PySync, CppSync, CppAsync,
+On CUDA devices the two cached placements run on the native data plane: the per-rank hot ranges are the shards of a
+range-owned :class:`~recstore_b200.parallel.sharded_table.ShardedEmbeddingTable` (peer windows over NVLink, fused
+exchange kernels with in-kernel flags, no NCCL call and no ``torch`` masking on the path); the sharded variant asks
+the owners for rows (``lookup``), both deliver every rank's gradients to the owning rank with ``push_update`` (dedup,
+key / gradient push, segment-reduce + SGD on the owner), and rows outside the cached ranges are read from the
+device-mapped host table inside the same kernels.  The CPU path (gloo) keeps the ``torch`` implementation below.
+
+``args``: ``max_batch_keys`` (native path: most ids one rank looks up or updates per step, default 65,536),
+``cache_ratio`` (per-rank fraction c = int(N * ratio)), ``backwardMode`` in {PySync, CppSync, CppAsync,
 CppAsyncV2}, ``kForwardItersPerStep``, ``backgrad_init`` (accepted, unused: gradients stay on their device), ``clr``.
 Semantics of the update on the cached paths: plain SGD with ``clr`` on the sum over duplicates, gradients pre-divided
 by the world size (grad_base.h:456-457, local_cache.py:342-349).
@@ -144,9 +152,32 @@ class _CachedBase(AbsEmb):
         self.cache = self.full[self.start:self.end].to(self.device).clone()
         self._dummy = torch.zeros(1, requires_grad=True, device=self.device)
         self.controller = args.get("controller")          # KGCacheControllerWrapper or None
+        self.native = None
+        if self.device.type == "cuda" and self.end > self.start:
+            self._init_native(int(args.get("max_batch_keys", 65536)))
         self._step_keys: List[torch.Tensor] = []
         self._step_grads: List[torch.Tensor] = []
         self.hits = self.lookups = 0
+
+    _native_count = 0
+
+    def _init_native(self, max_keys: int) -> None:
+        """The hot ranges become the shards of a range-owned table on the peer-window transport (collective: every rank
+        constructs its embedding at the same point)."""
+        from ..kvstore import get_kvstore, kvinit
+        from ..parallel.peer import PeerContext
+        from ..parallel.sharded_table import ShardedEmbeddingTable
+        if not self.full.is_pinned():                      # the kernels read host rows in place
+            kv = get_kvstore() or kvinit()
+            rc = kv.GetUVAMap(self.full)
+            if rc not in (0, 712):
+                raise RuntimeError(f"cudaHostRegister of the host table failed with code {rc}")
+        _CachedBase._native_count += 1
+        self._ctx = PeerContext(self.rank, self.world, device=self.device)
+        self.native = ShardedEmbeddingTable(self._ctx, f"cached_emb{_CachedBase._native_count}", self.N, self.D, max_keys=max_keys,
+                                            lr=self.clr, optimizer="sgd", dedup=True, init=self.cache,
+                                            range_rows=self.end - self.start, host_table=self.full)
+        self.cache = self.native.weight                    # one copy: the shard IS the cache
 
     def forward(self, keys, trace=True):
         keys = keys.to(self.device)
@@ -217,6 +248,12 @@ class KnownLocalCachedEmbedding(_CachedBase):
         keys = torch.cat(self._step_keys) if self._step_keys else torch.empty(0, dtype=torch.int64, device=self.device)
         grads = torch.cat(self._step_grads) if self._step_grads else torch.empty(0, self.D, device=self.device)
         self._step_keys, self._step_grads = [], []
+        if self.native is not None:
+            self.native.push_update(keys, grads.float())    # (a) on the native plane: owners fold duplicates and apply SGD
+            self._host_update(keys, grads)
+            if self.controller is not None:
+                self.controller.AfterBackward()
+            return
         owner = torch.full_like(keys, -1)
         for r, (s, e) in enumerate(self.ranges):
             owner[(keys >= s) & (keys < e)] = r
@@ -240,6 +277,8 @@ class KnownLocalCachedEmbeddingSoftware(KnownLocalCachedEmbedding):
 class KnownShardedCachedEmbedding(_CachedBase):
     def _lookup(self, keys):
         self.lookups += keys.numel()
+        if self.native is not None:
+            return self.native.lookup(keys)       # keys to the owners, rows back, host rows read in place: three fused kernels
         owner = torch.full_like(keys, -1)
         for r, (s, e) in enumerate(self.ranges):
             owner[(keys >= s) & (keys < e)] = r
@@ -262,6 +301,13 @@ class KnownShardedCachedEmbedding(_CachedBase):
         keys = torch.cat(self._step_keys) if self._step_keys else torch.empty(0, dtype=torch.int64, device=self.device)
         grads = torch.cat(self._step_grads) if self._step_grads else torch.empty(0, self.D, device=self.device)
         self._step_keys, self._step_grads = [], []
+        if self.native is not None:
+            self.native.push_update(keys, grads.float())
+            miss = keys >= self.world * (self.end - self.start)
+            self._host_update(keys[miss], grads[miss])
+            if self.controller is not None:
+                self.controller.AfterBackward()
+            return
         owner = torch.full_like(keys, -1)
         for r, (s, e) in enumerate(self.ranges):
             owner[(keys >= s) & (keys < e)] = r

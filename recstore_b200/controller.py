@@ -45,6 +45,7 @@ _lib.register_signatures({
     "rs_ctrl_pending": (i64, [vp]),
     "rs_ctrl_min_priority": (i64, [vp]),
     "rs_ctrl_print_pq": (i32, [vp, C.c_char_p, i32]),
+    "rs_ctrl_stats": (i32, [vp, vp]),
 })
 
 
@@ -138,6 +139,14 @@ class KGCacheController:
     def PendingCount(self) -> int:
         return int(self._l.rs_ctrl_pending(self._h))
 
+    def Stats(self) -> dict:
+        """Counters that tell the strategies apart: rows written back, whole-bucket swaps (CppAsyncV2), announcements
+        that went through a mailbox and the detect thread (CppAsync), and how the steps' keys were upserted."""
+        out = (C.c_longlong * 6)()
+        _lib.call("rs_ctrl_stats", self._h, out)
+        return {"flushed": out[0], "bucket_swaps": out[1], "mailed_announcements": out[2], "upsert_serial": out[3],
+                "upsert_per_rank": out[4], "upsert_per_shard_group": out[5]}
+
     def PrintPq(self) -> str:
         n = self._l.rs_ctrl_print_pq(self._h, None, 0)
         buf = C.create_string_buffer(n + 1)
@@ -158,7 +167,10 @@ class CircleBuffer:
 
     def __init__(self, L: int, rank: int, controller: Optional[KGCacheController] = None):
         self.L, self.rank, self.controller = L, rank, controller
-        self.slots: List[Optional[torch.Tensor]] = [None] * max(L, 1)
+        # L batches wait in the ring and a push comes before the matching pop, so L + 1 slots: with only L the push of
+        # batch t + L would overwrite batch t before it is popped and every batch would be read L steps before the
+        # step it was announced for.
+        self.slots: List[Optional[torch.Tensor]] = [None] * (max(L, 1) + 1)
         self.start = self.end = 0
         self.step_of_next_push = 0
 

@@ -312,7 +312,8 @@ struct KeysFusedArgs {
   int* const* count_win;
   long long* slot;           // [n]
   unsigned long long* status;
-  FlagSignal sig;
+  long long range_c;         // 0: owner = key % world; > 0: owner = key / range_c for key < world * range_c, else nobody
+  FlagSignal sig;            //    (such a key gets slot -2: its row lives in the host table)
 };
 
 __global__ void __launch_bounds__(256) shard_keys_fused_kernel(const KeysFusedArgs a) {
@@ -326,7 +327,13 @@ __global__ void __launch_bounds__(256) shard_keys_fused_kernel(const KeysFusedAr
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + tid;
   long long k = -1;
   if (i < n) k = a.keys[i];
-  const int d = k >= 0 ? static_cast<int>(k % a.world) : -1;
+  int d = -1;
+  bool host_row = false;
+  if (k >= 0) {
+    if (a.range_c <= 0) d = static_cast<int>(k % a.world);
+    else if (k < a.range_c * a.world) d = static_cast<int>(k / a.range_c);
+    else host_row = true;
+  }
   // rank of this key among the block's keys for the same owner: warp ballot + one shared atomic per (warp, owner)
   int pos = 0;
   for (int dd = 0; dd < a.world; ++dd) {
@@ -341,7 +348,7 @@ __global__ void __launch_bounds__(256) shard_keys_fused_kernel(const KeysFusedAr
   if (tid < a.world) s_base[tid] = s_cnt[tid] ? atomicAdd(&a.cursor[tid], s_cnt[tid]) : 0;
   __syncthreads();
   if (i < a.n) {
-    long long sl = -1;
+    long long sl = host_row ? -2 : -1;
     if (d >= 0) {
       const long long p = static_cast<long long>(s_base[d]) + pos;
       if (p < a.cap) {
@@ -399,6 +406,8 @@ struct GatherFusedArgs {
   long long cap;
   int use_hash;
   rs::HashTableView ht;
+  long long range_c;                // > 0: this rank holds keys [me * range_c, (me + 1) * range_c), local row = key - me * range_c
+  int push_rows;                    // 0: only resolve rows and record occurrences (a gradient exchange without a lookup)
   float init_scale;
   unsigned char* row_init;          // hash mode: 1 once a row holds its initial value (readers that come earlier compute it)
   unsigned long long* status;
@@ -433,7 +442,7 @@ __global__ void __launch_bounds__(128) shard_gather_fused_kernel(const GatherFus
         r = __shfl_sync(0xffffffffu, r, 0);
         fresh = __shfl_sync(0xffffffffu, static_cast<int>(fresh), 0) != 0;
       } else {
-        r = k / a.world;
+        r = a.range_c > 0 ? k - static_cast<long long>(a.me) * a.range_c : k / a.world;
       }
       if (r < 0 || r >= a.local_rows) {
         if (!a.use_hash && lane == 0 && a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
@@ -447,6 +456,7 @@ __global__ void __launch_bounds__(128) shard_gather_fused_kernel(const GatherFus
           a.occ_slot[q] = static_cast<int>(w);
         }
       }
+      if (!a.push_rows) continue;
       // A key that another warp inserted a moment ago may not hold its initial value yet: such a reader computes the same
       // value from the key instead of reading the row.
       bool by_formula = fresh;
@@ -490,6 +500,10 @@ struct UnbucketFusedArgs {
   float* ugrad;                // optional: cleared for u < *ucount (per-key gradient accumulators of the coming update)
   float* unorm;
   const int* ucount;
+  const long long* keys;       // the (unique) keys: a slot of -2 means "row keys[u] of the host table"
+  const float* host_table;     // device-visible host memory, read in place, or null
+  long long host_rows;
+  unsigned long long* status;
   FlagWait wait;
 };
 
@@ -502,8 +516,16 @@ __global__ void __launch_bounds__(128) shard_unbucket_fused_kernel(const Unbucke
   for (long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); i < a.n; i += nwarps) {
     const long long u = a.inverse ? a.inverse[i] : i;
     const long long s = u >= 0 ? a.slot[u] : -1;
+    const float* host_src = nullptr;
+    if (s == -2 && a.host_table != nullptr) {
+      const long long k = a.keys[u];
+      if (k >= 0 && k < a.host_rows) host_src = a.host_table + k * a.D;
+      else if (lane == 0 && a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
+    }
     for (int v = lane; v < nvec; v += 32) {
-      const float4 x = s >= 0 ? __ldcv(reinterpret_cast<const float4*>(a.row_win + s * a.D) + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s >= 0) x = __ldcv(reinterpret_cast<const float4*>(a.row_win + s * a.D) + v);
+      else if (host_src) x = __ldcv(reinterpret_cast<const float4*>(host_src) + v);
       if (a.out_bf16) {
         __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
         uint2 o;
@@ -574,15 +596,18 @@ FlagWait make_wait(const void* my_flags, const unsigned* counters, unsigned long
 }  // namespace
 
 // n_dev (optional): device count of live keys (the output count of rs_unique_keys); n is then the capacity that sizes the grid.
+// range_c: 0 = cyclic ownership (key % world); > 0 = rank r owns keys [r * range_c, (r + 1) * range_c) and larger keys belong to
+// the host table (slot -2).
 RS_API int rs_shard_keys_fused(const long long* keys, const int* n_dev, long long n, int world, int me, long long cap, int* cursor,
                                void* const* key_win, void* const* count_win, long long* slot, unsigned long long* status,
-                               void* const* flags_of, unsigned* counters, unsigned* done, int channel, cudaStream_t stream) {
+                               long long range_c, void* const* flags_of, unsigned* counters, unsigned* done, int channel,
+                               cudaStream_t stream) {
   RS_REQUIRE(keys && cursor && key_win && count_win && slot && flags_of && counters && done, "rs_shard_keys_fused: null argument");
   RS_REQUIRE(world >= 1 && world <= kMaxWorld && n >= 0 && me >= 0 && me < world, "rs_shard_keys_fused: bad sizes");
   KeysFusedArgs a;
   a.keys = keys; a.n_dev = n_dev; a.n = n; a.world = world; a.me = me; a.cap = cap; a.cursor = cursor;
   a.key_win = reinterpret_cast<long long* const*>(key_win); a.count_win = reinterpret_cast<int* const*>(count_win);
-  a.slot = slot; a.status = status; a.sig = make_sig(flags_of, counters, done, channel, world, me);
+  a.slot = slot; a.status = status; a.range_c = range_c; a.sig = make_sig(flags_of, counters, done, channel, world, me);
   const long long grid = n > 0 ? (n + 255) / 256 : 1;
   RS_REQUIRE(grid < (1ll << 31), "rs_shard_keys_fused: too many keys");
   shard_keys_fused_kernel<<<static_cast<unsigned>(grid), 256, 0, stream>>>(a);
@@ -595,8 +620,8 @@ RS_API int rs_shard_keys_fused(const long long* keys, const int* n_dev, long lon
 RS_API int rs_shard_gather_fused(float* weight, const float* cold_weight, long long hot_rows, long long local_rows,
                                  const long long* key_win, const int* count_win, void* const* row_win, long long* rowidx,
                                  long long* occ_row, int* occ_slot, int* occ_cursor, int world, int me, int D, long long cap,
-                                 const rs::HashTableView* ht, float init_scale, unsigned char* row_init, unsigned long long* status,
-                                 const void* my_flags,
+                                 const rs::HashTableView* ht, float init_scale, unsigned char* row_init, long long range_c,
+                                 int push_rows, unsigned long long* status, const void* my_flags,
                                  void* const* flags_of, unsigned* counters, unsigned* done, unsigned long long timeout_ns,
                                  int wait_channel, int sig_channel, cudaStream_t stream) {
   RS_REQUIRE((weight || hot_rows == 0) && key_win && count_win && row_win && D % 4 == 0, "rs_shard_gather_fused: bad argument");
@@ -610,7 +635,7 @@ RS_API int rs_shard_gather_fused(float* weight, const float* cold_weight, long l
   a.use_hash = ht != nullptr;
   if (ht) a.ht = *ht; else memset(&a.ht, 0, sizeof(a.ht));
   RS_REQUIRE(!ht || row_init, "rs_shard_gather_fused: the hash-table shard needs its row_init bytes");
-  a.init_scale = init_scale; a.row_init = row_init; a.status = status;
+  a.init_scale = init_scale; a.row_init = row_init; a.status = status; a.range_c = range_c; a.push_rows = push_rows;
   a.wait = make_wait(my_flags, counters, timeout_ns, wait_channel, world, status);
   a.sig = make_sig(flags_of, counters, done, sig_channel, world, me);
   shard_gather_fused_kernel<<<persistent_grid(cap, 4), 128, 0, stream>>>(a);
@@ -618,14 +643,18 @@ RS_API int rs_shard_gather_fused(float* weight, const float* cold_weight, long l
   return RS_OK;
 }
 
+// keys / host_table / host_rows (optional): rows of slot -2 are read from the host table (device-visible host memory).
 RS_API int rs_shard_unbucket_fused(const float* row_win, const long long* slot, const int* inverse, long long n, int D, void* out,
-                                   int out_bf16, float* ugrad, float* unorm, const int* ucount, const void* my_flags,
+                                   int out_bf16, float* ugrad, float* unorm, const int* ucount, const long long* keys,
+                                   const float* host_table, long long host_rows, const void* my_flags,
                                    const unsigned* counters, unsigned long long timeout_ns, int wait_channel, int world,
                                    unsigned long long* status, cudaStream_t stream) {
   RS_REQUIRE(row_win && slot && out && D % 4 == 0 && my_flags && counters, "rs_shard_unbucket_fused: bad argument");
   UnbucketFusedArgs a;
   a.row_win = row_win; a.slot = slot; a.inverse = inverse; a.n = n; a.D = D; a.out = out; a.out_bf16 = out_bf16;
-  a.ugrad = ugrad; a.unorm = unorm; a.ucount = ucount;
+  a.ugrad = ugrad; a.unorm = unorm; a.ucount = ucount; a.keys = keys; a.host_table = host_table; a.host_rows = host_rows;
+  a.status = status;
+  RS_REQUIRE(!host_table || keys, "rs_shard_unbucket_fused: host rows need the keys");
   a.wait = make_wait(my_flags, counters, timeout_ns, wait_channel, world, status);
   shard_unbucket_fused_kernel<<<persistent_grid(n, 4), 128, 0, stream>>>(a);
   RS_LAUNCH_CHECK();

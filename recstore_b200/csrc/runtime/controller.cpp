@@ -8,13 +8,22 @@
 // batches (lookahead); an id with pending writes has priority = its earliest future read step,
 // +infinity when no read is registered.
 //
-// What is different: no polling "detect" thread and no shared-memory mailboxes inside the
-// controller -- the sampler calls PublishReads directly and the trainer passes (keys, grads) of the
-// step; the queue is a bucket array over steps (O(1) insert / move, like ParallelPq,
-// parallel_pq.h:164-446) sharded by id so that ranks upsert in parallel; background flusher threads
-// drain the lowest bucket first and BlockToStepN helps draining instead of spinning.  Rows cached in
-// HBM are updated by the owning GPU's kernel; here "cache" rows are the caller-registered per-rank
-// cache tensors (used on the CPU path and by the tests).
+// The queue is a bucket array over steps (O(1) insert / move, like ParallelPq, parallel_pq.h:164-446)
+// sharded by id; background flusher threads drain the lowest bucket first and BlockToStepN helps
+// draining instead of spinning.  Rows cached in HBM are updated by the owning GPU's kernel; here
+// "cache" rows are the caller-registered per-rank cache tensors (used on the CPU path and by the tests).
+//
+// Two asynchronous strategies, chosen by "backwardMode":
+//   CppAsync   (grad_async_v1.h): the samplers' read announcements go through per-rank mailboxes that a
+//              "detect" thread turns into queue priorities (use_detect_thread = 0 applies them in the
+//              caller instead); pending updates are flushed ONE ID AT A TIME, lowest priority first.
+//              The step's (keys, grads) are upserted in one of three ways ("update_pq_use_omp",
+//              grad_async_v1.h:496-541): 0 = serially on the calling thread, 1 = one task per rank,
+//              2 = one task per group of queue shards, each task scanning every rank's keys and taking
+//              only the ids of its own shards (no two tasks ever contend for a shard lock).
+//   CppAsyncV2 (grad_async_v2.h:86-163, parallel_pq_v2.h:256-290): flushers take a WHOLE BUCKET: the id
+//              list of the lowest step is swapped out under the shard lock, the pending updates of its
+//              live entries are detached, and the rows are written back after the lock is released.
 //
 // Also here: the binary-heap priority queue with an index map and an invariant checker
 // (src/base/pq.h:11-224) used as the oracle in tests.
@@ -25,6 +34,7 @@
 #include <condition_variable>
 #include <cstring>
 #include <mutex>
+#include <shared_mutex>
 #include <thread>
 #include <unordered_map>
 #include <vector>
@@ -132,10 +142,15 @@ class Controller {
     cache_size_ = static_cast<int64_t>(capacity_ * ratio);
     const std::string mode = j.str("backwardMode", "CppAsyncV2");
     async_ = mode != "CppSync" && mode != "PySync";
+    v2_ = mode == "CppAsyncV2";
+    upsert_mode_ = static_cast<int>(j.i64("update_pq_use_omp", 1));
+    detect_ = async_ && j.i64("use_detect_thread", v2_ ? 0 : 1) != 0;
+
     nthreads_ = static_cast<int>(j.i64("nr_background_threads", 2));
     nshards_ = std::max(1, static_cast<int>(j.i64("kUpdatePqWorkerNum", 16)));
     shards_ = std::vector<Shard>(nshards_);
     for (auto& s : shards_) s.buckets.resize(kHorizon);
+    mail_ = std::vector<Mailbox>(ranks_);
     caches_.assign(ranks_, nullptr);
     inputs_.assign(ranks_, Input{});
   }
@@ -153,22 +168,35 @@ class Controller {
     if (!async_ || running_) return;
     running_ = true;
     for (int t = 0; t < nthreads_; ++t) flushers_.emplace_back([this] { FlushLoop(); });
+    if (detect_) flushers_.emplace_back([this] { DetectLoop(); });
   }
   void StopThreads() {
     if (!running_.exchange(false)) return;
     for (auto& t : flushers_) t.join();
     flushers_.clear();
+    DrainMail();                       // announcements that were still in the mailboxes are not lost
   }
   // Flush everything that is still pending (end of training / before a checkpoint).
   void Drain() {
+    DrainMail();
     for (int s = 0; s < nshards_; ++s)
-      while (FlushOne(s, kInf, true)) {}
+      while (Flush(s, kInf, true)) {}
   }
 
-  // The sampler tells that `rank` will read `ids` at `step` (step > current step).
+  // The sampler tells that `rank` will read `ids` at `step` (step > current step).  With the detect thread the
+  // announcement is only dropped into the rank's mailbox here.
   void PublishReads(int rank, int64_t step, const int64_t* ids, int64_t n) {
-    (void)rank;
     if (!async_) return;
+    if (detect_ && running_) {
+      Mailbox& m = mail_[rank];
+      mail_items_.fetch_add(1);
+      std::lock_guard<SpinLock> lk(m.mu);
+      m.q.push_back(Mail{step, std::vector<int64_t>(ids, ids + n)});
+      return;
+    }
+    ApplyReads(step, ids, n);
+  }
+  void ApplyReads(int64_t step, const int64_t* ids, int64_t n) {
     for (int64_t i = 0; i < n; ++i) {
       const int64_t id = ids[i];
       if (id < 0 || id >= rows_) continue;
@@ -185,12 +213,15 @@ class Controller {
   // Consumes the registered (keys, grads) of every rank for `step`: cached rows are updated in the
   // owning rank's cache, the rest goes to the host table now (sync) or to the queue (async).
   void ProcessOneStep(int64_t step) {
-    auto body = [&](size_t rb, size_t re, int) {
+    // group = -1: every id of ranks [rb, re); group >= 0: only the ids whose queue shard belongs to that group
+    const int ngroups = std::max(1, std::min(nshards_, ThreadPool::global().size() > 0 ? ThreadPool::global().size() : 1));
+    auto body_ranks = [&](size_t rb, size_t re, int group) {
       for (size_t r = rb; r < re; ++r) {
         const Input& in = inputs_[r];
         for (int64_t i = 0; i < in.n; ++i) {
           const int64_t id = in.keys[i];
           if (id < 0 || id >= rows_) continue;
+          if (group >= 0 && static_cast<int>(hash64(static_cast<uint64_t>(id)) % nshards_) % ngroups != group) continue;
           const float* g = in.grads + i * dim_;
           const int owner = CacheOwner(id);
           if (owner >= 0 && caches_[owner]) {
@@ -221,8 +252,20 @@ class Controller {
         }
       }
     };
-    if (ranks_ > 1) ThreadPool::global().parallel_for(ranks_, body);
-    else body(0, ranks_, 0);
+    // announcements of reads up to this step must be in the queue before this step's updates are ranked
+    if (detect_) DrainMail();
+    if (async_ && upsert_mode_ == 2 && ngroups > 1) {
+      upsert_calls_[2].fetch_add(1);
+      ThreadPool::global().parallel_for(ngroups, [&](size_t gb, size_t ge, int) {
+        for (size_t g = gb; g < ge; ++g) body_ranks(0, ranks_, static_cast<int>(g));
+      });
+    } else if (ranks_ > 1 && (!async_ || upsert_mode_ != 0)) {
+      upsert_calls_[1].fetch_add(1);
+      ThreadPool::global().parallel_for(ranks_, [&](size_t rb, size_t re, int) { body_ranks(rb, re, -1); });
+    } else {
+      upsert_calls_[0].fetch_add(1);
+      body_ranks(0, ranks_, -1);
+    }
     // reads registered for this step by ranks that produced no gradient for the id are dropped lazily in Requeue
     cur_step_.store(step);
   }
@@ -234,14 +277,37 @@ class Controller {
     const auto t0 = std::chrono::steady_clock::now();
     for (;;) {
       bool busy = false;
+      if (detect_ && DrainMail()) busy = true;     // a read that is still in a mailbox has no priority yet
       for (int s = 0; s < nshards_; ++s) {
-        while (FlushOne(s, step, false)) busy = true;
+        while (Flush(s, step, false)) busy = true;
       }
-      if (!busy && MinPriority() > step && inflight_.load() == 0) return true;
+      if (!busy && inflight_.load() == 0 && mail_items_.load() == 0) {
+        // Every flusher holds flight_mu_ (shared) from the moment it detaches an update until the row is written.
+        // Taking it exclusively means: nobody is between "detached" and "written" right now, and nobody can detach
+        // anything while the queue is inspected.
+        std::unique_lock<std::shared_mutex> quiet(flight_mu_);
+        if (MinPriority() > step && inflight_.load() == 0 && mail_items_.load() == 0) {
+          return true;
+        }
+      }
       if (timeout_ms >= 0 &&
           std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > timeout_ms)
         return false;
     }
+  }
+  // out: has_pending, prio, number of registered reads, earliest read (-1 = none), queued
+  void DebugElem(int64_t id, long long* out) {
+    Shard& sh = shard_of(id);
+    std::lock_guard<SpinLock> lk(sh.mu);
+    auto it = sh.elems.find(id);
+    out[0] = out[2] = out[4] = 0; out[1] = out[3] = -1;
+    if (it == sh.elems.end()) return;
+    const Elem& e = it->second;
+    out[0] = e.pending.empty() ? 0 : 1;
+    out[1] = e.prio == kInf ? -2 : e.prio;
+    out[2] = static_cast<long long>(e.reads.size());
+    out[3] = e.reads.empty() ? -1 : e.reads.front();
+    out[4] = e.queued ? 1 : 0;
   }
   int64_t MinPriority() {
     int64_t m = kInf;
@@ -264,14 +330,50 @@ class Controller {
   }
   std::string PrintPq() {
     std::string s = "pq: min=" + (MinPriority() == kInf ? std::string("inf") : std::to_string(MinPriority())) +
-                    " pending=" + std::to_string(PendingCount()) + " flushed=" + std::to_string(flushed_.load());
+                    " pending=" + std::to_string(PendingCount()) + " flushed=" + std::to_string(flushed_.load()) +
+                    " bucket_swaps=" + std::to_string(bucket_swaps_.load()) + " mail=" + std::to_string(mail_seen_.load());
     return s;
+  }
+  // out[0] rows written back, [1] whole-bucket swaps (V2), [2] announcements that went through a mailbox,
+  // [3..5] ProcessOneStep calls that upserted serially / per rank / per shard group
+  void Stats(long long* out) const {
+    out[0] = flushed_.load(); out[1] = bucket_swaps_.load(); out[2] = mail_seen_.load();
+    for (int m = 0; m < 3; ++m) out[3 + m] = upsert_calls_[m].load();
   }
   int dim() const { return dim_; }
   bool async() const { return async_; }
 
  private:
   struct Input { const int64_t* keys = nullptr; int64_t n = 0; const float* grads = nullptr; };
+  struct Mail { int64_t step; std::vector<int64_t> ids; };
+  struct Mailbox {
+    SpinLock mu;
+    std::vector<Mail> q;
+  };
+  // Moves every announcement that sits in a mailbox into the queue; true when there was any.
+  bool DrainMail() {
+    bool any = false;
+    for (auto& m : mail_) {
+      std::vector<Mail> got;
+      {
+        std::lock_guard<SpinLock> lk(m.mu);
+        got.swap(m.q);
+      }
+      for (auto& x : got) {
+        ApplyReads(x.step, x.ids.data(), static_cast<int64_t>(x.ids.size()));
+        mail_seen_.fetch_add(1);
+        mail_items_.fetch_sub(1);
+        any = true;
+      }
+    }
+    return any;
+  }
+  void DetectLoop() {
+    while (running_) {
+      if (!DrainMail()) std::this_thread::sleep_for(std::chrono::microseconds(20));
+    }
+  }
+  bool Flush(int s, int64_t limit, bool any) { return v2_ ? FlushBucket(s, limit, any) : FlushOne(s, limit, any); }
   struct Shard {
     SpinLock mu;
     std::unordered_map<int64_t, Elem> elems;
@@ -315,6 +417,7 @@ class Controller {
   // Applies the pending update of one id of shard s whose priority is <= limit (or anything, when
   // `any`, including the infinity bucket).  Returns false when nothing qualified.
   bool FlushOne(int s, int64_t limit, bool any) {
+    std::shared_lock<std::shared_mutex> in_flight(flight_mu_);
     Shard& sh = shards_[s];
     int64_t id = -1;
     std::vector<float> upd;
@@ -353,12 +456,53 @@ class Controller {
     }
     {
       BitRow br = row_lock(id);
-            std::lock_guard<BitRow> lk(br);
+      std::lock_guard<BitRow> lk(br);
       float* row = table_ + id * dim_;
       for (int d = 0; d < dim_; ++d) row[d] += upd[d];
     }
     flushed_.fetch_add(1, std::memory_order_relaxed);
     inflight_.fetch_sub(1);
+    return true;
+  }
+  // V2: detaches a WHOLE bucket of shard s (the lowest one with priority <= limit; with `any` also the infinity
+  // bucket) under the shard lock and writes its rows back after the lock is released.
+  bool FlushBucket(int s, int64_t limit, bool any) {
+    std::shared_lock<std::shared_mutex> in_flight(flight_mu_);
+    Shard& sh = shards_[s];
+    std::vector<std::pair<int64_t, std::vector<float>>> batch;
+    {
+      std::lock_guard<SpinLock> lk(sh.mu);
+      std::vector<int64_t> ids;
+      int64_t p_found = kInf;
+      const int64_t hi = std::min<int64_t>(any ? sh.max_prio : limit, sh.max_prio);
+      for (int64_t p = sh.min_hint; p <= hi; ++p) {
+        auto& b = sh.buckets[p % kHorizon];
+        if (!b.empty()) { ids.swap(b); p_found = p; break; }
+        if (p == sh.min_hint && sh.min_hint < sh.max_prio) ++sh.min_hint;
+      }
+      if (ids.empty() && any && !sh.inf_bucket.empty()) ids.swap(sh.inf_bucket);
+      if (ids.empty()) return false;
+      bucket_swaps_.fetch_add(1, std::memory_order_relaxed);
+      for (const int64_t cand : ids) {
+        auto it = sh.elems.find(cand);
+        if (it == sh.elems.end() || !it->second.queued || it->second.prio != p_found || it->second.pending.empty()) continue;  // moved meanwhile
+        Elem& e = it->second;
+        batch.emplace_back(cand, std::vector<float>());
+        batch.back().second.swap(e.pending);
+        e.queued = false;
+        e.prio = kInf;
+        if (e.reads.empty()) sh.elems.erase(it);
+      }
+      inflight_.fetch_add(static_cast<int>(batch.size()));
+    }
+    for (auto& kv : batch) {
+      BitRow br = row_lock(kv.first);
+      std::lock_guard<BitRow> lk(br);
+      float* row = table_ + kv.first * dim_;
+      for (int d = 0; d < dim_; ++d) row[d] += kv.second[d];
+      inflight_.fetch_sub(1);
+    }
+    flushed_.fetch_add(static_cast<int64_t>(batch.size()), std::memory_order_relaxed);
     return true;
   }
   void FlushLoop() {
@@ -368,11 +512,11 @@ class Controller {
       for (int k = 0; k < nshards_ && running_; ++k) {
         s = (s + 1) % nshards_;
         // background threads stay within the lookahead window first, then take idle (infinity) work
-        if (FlushOne(s, cur_step_.load() + L_ + 1, false)) any = true;
+        if (Flush(s, cur_step_.load() + L_ + 1, false)) any = true;
       }
       if (!any) {
         for (int k = 0; k < nshards_ && running_; ++k)
-          if (FlushOne(k, kInf, true)) { any = true; break; }
+          if (Flush(k, kInf, true)) { any = true; break; }
       }
       if (!any) std::this_thread::sleep_for(std::chrono::microseconds(50));
     }
@@ -381,7 +525,11 @@ class Controller {
   int ranks_ = 1, L_ = 10, dim_ = 32, nthreads_ = 2, nshards_ = 16;
   float clr_ = 0.01f;
   int64_t capacity_ = 0, cache_size_ = 0, rows_ = 0;
-  bool async_ = true;
+  bool async_ = true, v2_ = true, detect_ = false;
+  int upsert_mode_ = 1;
+  std::vector<Mailbox> mail_;
+  std::atomic<int64_t> mail_items_{0}, mail_seen_{0}, bucket_swaps_{0};
+  std::atomic<int64_t> upsert_calls_[3] = {{0}, {0}, {0}};
   float* table_ = nullptr;
   std::vector<float*> caches_;
   std::vector<Input> inputs_;
@@ -389,6 +537,7 @@ class Controller {
   BitLockTable row_locks_;
   std::atomic<int64_t> cur_step_{-1}, max_published_{-1}, flushed_{0};
   std::atomic<int> inflight_{0};
+  std::shared_mutex flight_mu_;
   std::atomic<bool> running_{false};
   std::vector<std::thread> flushers_;
 };
@@ -434,6 +583,8 @@ RS_API int rs_ctrl_create(const char* json, void** out) {
     RS_REQUIRE(threads >= 0 && threads <= 256, "rs_ctrl_create: nr_background_threads = %lld outside [0, 256]", threads);
     RS_REQUIRE(workers <= 4096, "rs_ctrl_create: kUpdatePqWorkerNum = %lld above 4096", workers);
     RS_REQUIRE(ratio >= 0.0 && ratio <= 1.0, "rs_ctrl_create: cache_ratio = %g outside [0, 1]", ratio);
+    const long long um = j.i64("update_pq_use_omp", 1);
+    RS_REQUIRE(um >= 0 && um <= 2, "rs_ctrl_create: update_pq_use_omp = %lld is not 0 (serial), 1 (per rank) or 2 (per shard group)", um);
     const std::string mode = j.str("backwardMode", "CppAsyncV2");
     RS_REQUIRE(mode == "PySync" || mode == "CppSync" || mode == "CppAsync" || mode == "CppAsyncV2",
                "rs_ctrl_create: backwardMode %s is not one of PySync, CppSync, CppAsync, CppAsyncV2", mode.c_str());
@@ -474,6 +625,16 @@ RS_API int rs_ctrl_block_to_step(void* c, long long step, int timeout_ms) {
   return static_cast<Controller*>(c)->BlockToStepN(step, timeout_ms)
              ? RS_OK
              : rs::set_error(RS_ERR_TIMEOUT, "BlockToStepN(%lld) timed out after %d ms", step, timeout_ms);
+}
+RS_API int rs_ctrl_debug_elem(void* c, long long id, long long* out5) {
+  RS_REQUIRE(c && out5, "rs_ctrl_debug_elem: null argument");
+  static_cast<Controller*>(c)->DebugElem(id, out5);
+  return RS_OK;
+}
+RS_API int rs_ctrl_stats(void* c, long long* out6) {
+  RS_REQUIRE(c && out6, "rs_ctrl_stats: null argument");
+  static_cast<Controller*>(c)->Stats(out6);
+  return RS_OK;
 }
 RS_API long long rs_ctrl_pending(void* c) { return static_cast<Controller*>(c)->PendingCount(); }
 RS_API long long rs_ctrl_min_priority(void* c) { return static_cast<Controller*>(c)->MinPriority(); }

@@ -44,10 +44,10 @@ _lib.register_signatures({
     "rs_segment_sum": (i32, [vp, vp, i64, i32, vp, vp, vp]),
     "rs_expand_rows": (i32, [vp, vp, i64, i32, vp, vp]),
     "rs_unique_keys": (i32, [vp, i64, vp, vp, _lib.u64, vp, vp, vp, vp, vp]),
-    "rs_shard_keys_fused": (i32, [vp, vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp]),
+    "rs_shard_keys_fused": (i32, [vp, vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, vp]),
     "rs_shard_gather_fused": (i32, [vp, vp, i64, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, C.POINTER(HashTableView), f32, vp,
-                                    vp, vp, vp, vp, vp, _lib.u64, i32, i32, vp]),
-    "rs_shard_unbucket_fused": (i32, [vp, vp, vp, i64, i32, vp, i32, vp, vp, vp, vp, vp, _lib.u64, i32, i32, vp, vp]),
+                                    i64, i32, vp, vp, vp, vp, vp, _lib.u64, i32, i32, vp]),
+    "rs_shard_unbucket_fused": (i32, [vp, vp, vp, i64, i32, vp, i32, vp, vp, vp, vp, vp, i64, vp, vp, _lib.u64, i32, i32, vp, vp]),
     "rs_shard_grads_fused": (i32, [vp, vp, vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp, i32, i32, vp]),
     "rs_ht_create": (i32, [_lib.u64, i32, C.POINTER(vp), C.POINTER(HashTableView)]),
     "rs_ht_destroy": (i32, [vp]),
@@ -61,9 +61,16 @@ class ShardedEmbeddingTable:
     def __init__(self, ctx: PeerContext, name: str, num_rows: int, dim: int, max_keys: int, *, lr: float = 0.01,
                  eps: float = 1e-10, optimizer: str = "rowwise_adagrad", dedup: bool = True, init: str = "uniform",
                  init_scale: Optional[float] = None, seed: int = 0, hbm_ratio: float = 1.0, hashed: bool = False,
-                 fused: bool = True):
+                 fused: bool = True, range_rows: int = 0, host_table: Optional[torch.Tensor] = None):
+        """``range_rows = c > 0`` switches from cyclic to RANGE ownership: rank r holds ids ``[r*c, (r+1)*c)`` in HBM (a
+        range-sharded device cache) and ids ``>= world*c`` are rows of ``host_table`` (device-visible host memory), read in
+        place by ``lookup`` and left alone by ``update`` (their gradients are the caller's to deliver).  ``init`` is then the
+        tensor holding this rank's ``c`` rows."""
         assert dim % 4 == 0
         assert not (hashed and hbm_ratio < 1.0), "the hash-table shard lives in HBM"
+        self.range_c = int(range_rows)
+        self.host_table = host_table
+        assert not (self.range_c and (hashed or hbm_ratio < 1.0)), "range ownership: dense HBM rows only"
         self.ctx, self.name, self.N, self.D = ctx, name, int(num_rows), int(dim)
         self.rank, self.world = ctx.rank, ctx.world
         self.cap = int(max_keys)
@@ -72,6 +79,8 @@ class ShardedEmbeddingTable:
         self.hashed, self.fused = bool(hashed), bool(fused) or bool(hashed)
         # dense storage: rows of ids me, me + world, ...; hashed storage: room for this shard's share of N distinct keys
         self.local_rows = (self.N + self.world - 1) // self.world
+        if self.range_c:
+            self.local_rows = self.range_c
         if self.hashed:
             self.local_rows = int(self.local_rows * 1.25) + 1024        # keys hash unevenly over the owners
         # Two tiers per shard when hbm_ratio < 1: local rows [0, hot_rows) in HBM, the rest in pinned host memory that
@@ -82,7 +91,10 @@ class ShardedEmbeddingTable:
         self.cold = torch.empty(self.local_rows - self.hot_rows, self.D, pin_memory=True) if self.tiered else None
         self.weight = torch.empty(self.hot_rows, self.D, device=dev)
         g = torch.Generator(device=dev).manual_seed(seed * 131 + self.rank)
-        if init == "uniform":
+        if isinstance(init, torch.Tensor):
+            assert init.shape == (self.hot_rows, self.D)
+            self.weight.copy_(init)
+        elif init == "uniform":
             b = init_scale if init_scale is not None else math.sqrt(1.0 / self.N)
             self.weight.uniform_(-b, b, generator=g)
             if self.tiered:
@@ -166,7 +178,7 @@ class ShardedEmbeddingTable:
             self.launches += 3
         else:
             keys = ids
-        if self.world == 1 and not self.tiered and not self.hashed:
+        if self.world == 1 and not self.tiered and not self.hashed and not self.range_c:
             # One rank: every row is local (local row = id), so nothing is bucketed or exchanged.
             src_keys = keys[:n]
             if out is None:
@@ -204,24 +216,57 @@ class ShardedEmbeddingTable:
 
     def _lookup_fused(self, keys, n, out, st, sp):
         c = self.ctx
-        gd = self._grid_done
+        self._exchange_keys(keys, n, st, sp, push_rows=True)
+        if out is None:
+            out = torch.empty(n, self.D, device=self.dev)
+        ht = self.host_table
+        _lib.call("rs_shard_unbucket_fused", self.row_win.local_ptr, ptr(self._slot), ptr(self._inv) if self.dedup else None, n, self.D,
+                  ptr(out), 0, ptr(self._ugrad) if self.dedup else None, ptr(self._unorm) if self.dedup else None,
+                  ptr(self._ucount) if self.dedup else None, ptr(keys), ht.data_ptr() if ht is not None else None,
+                  ht.shape[0] if ht is not None else 0, c.my_flags_ptr, c.counters_ptr, c.wait_timeout_ns, CH_ROWS, self.world,
+                  ptr(st), sp)
+        self.launches += 4
+        return out
+
+    def _exchange_keys(self, keys, n, st, sp, push_rows: bool):
+        """Keys to their owners (+ CH_KEYS), owner-side resolution into the compact occurrence list and, for a lookup, the
+        rows back to the askers (+ CH_ROWS)."""
+        c, gd = self.ctx, self._grid_done
         self._occ_cursor.zero_()
         _lib.call("rs_shard_keys_fused", ptr(keys), ptr(self._ucount) if self.dedup else None, n, self.world, self.rank, self.cap,
-                  ptr(self._cursor), ptr(self.key_win.table), ptr(self.count_win.table), ptr(self._slot), ptr(st),
+                  ptr(self._cursor), ptr(self.key_win.table), ptr(self.count_win.table), ptr(self._slot), ptr(st), self.range_c,
                   c.flags_table_ptr, c.counters_ptr, ptr(gd[0:1]), CH_KEYS, sp)
         _lib.call("rs_shard_gather_fused", ptr(self.weight), ptr(self.cold), self.hot_rows, self.local_rows, self.key_win.local_ptr,
                   self.count_win.local_ptr, ptr(self.row_win.table), ptr(self.rowidx) if self.tiered else None, ptr(self._occ_row),
                   ptr(self._occ_slot), ptr(self._occ_cursor), self.world, self.rank, self.D, self.cap,
                   C.byref(self._ht_view) if self.hashed else None, self.init_scale, ptr(self.row_init) if self.hashed else None,
-                  ptr(st), c.my_flags_ptr, c.flags_table_ptr, c.counters_ptr, ptr(gd[1:2]), c.wait_timeout_ns, CH_KEYS, CH_ROWS, sp)
-        if out is None:
-            out = torch.empty(n, self.D, device=self.dev)
-        _lib.call("rs_shard_unbucket_fused", self.row_win.local_ptr, ptr(self._slot), ptr(self._inv) if self.dedup else None, n, self.D,
-                  ptr(out), 0, ptr(self._ugrad) if self.dedup else None, ptr(self._unorm) if self.dedup else None,
-                  ptr(self._ucount) if self.dedup else None, c.my_flags_ptr, c.counters_ptr, c.wait_timeout_ns, CH_ROWS, self.world,
-                  ptr(st), sp)
-        self.launches += 4
-        return out
+                  self.range_c, 1 if push_rows else 0, ptr(st), c.my_flags_ptr, c.flags_table_ptr, c.counters_ptr, ptr(gd[1:2]),
+                  c.wait_timeout_ns, CH_KEYS, CH_ROWS, sp)
+
+    def push_update(self, ids: torch.Tensor, grads: torch.Tensor) -> None:
+        """A gradient exchange WITHOUT a preceding lookup: ``grads[i]`` is delivered to the owner of ``ids[i]`` and applied
+        there (duplicates folded first); ids that belong to the host table are skipped.  This is how a replicated-read cache
+        (every rank reads its own hot range and the host table, nobody asks a peer) still gets every rank's updates to the
+        rank that holds the row."""
+        assert self.fused and not self.tiered
+        ids, grads = ids.contiguous(), grads.contiguous()
+        n = ids.numel()
+        assert n <= self.world * self.cap and grads.shape == (n, self.D) and grads.dtype == torch.float32
+        st, sp = self.ctx.status, stream_ptr()
+        self._n = n
+        self.launches = 0
+        if self.dedup:
+            _lib.call("rs_unique_keys", ptr(ids), n, ptr(self._sk), ptr(self._si), self._nslots, ptr(self._uniq), ptr(self._inv),
+                      ptr(self._ucount), ptr(st), sp)
+            keys = self._uniq
+            self._ugrad[:n].zero_()
+            self._unorm[:n].zero_()
+            self.launches += 4
+        else:
+            keys = ids
+        self._exchange_keys(keys, n, st, sp, push_rows=False)
+        self.launches += 3
+        self._update_fused(grads, n, st, sp)
 
     def _update_fused(self, grads, n, st, sp):
         c = self.ctx
@@ -254,7 +299,7 @@ class ShardedEmbeddingTable:
         assert grads.shape == (n, self.D) and grads.dtype == torch.float32
         grads = grads.contiguous()
         st, sp = self.ctx.status, stream_ptr()
-        if self.world == 1 and not self.tiered and not self.hashed:
+        if self.world == 1 and not self.tiered and not self.hashed and not self.range_c:
             if self.dedup:
                 self._ugrad[:n].zero_()
                 self._unorm[:n].zero_()

@@ -29,7 +29,8 @@ def test_indexed_heap_random_ops_keep_invariants():
     assert pq.CheckConsistency()
 
 
-@pytest.mark.parametrize("mode", ["CppSync", "CppAsyncV2"])
+@pytest.mark.parametrize("mode", ["CppSync", "CppAsyncV2", "CppAsync", "CppAsync/omp0", "CppAsync/omp2", "CppAsync/nodetect",
+                                  "CppAsyncV2/omp2", "CppAsyncV2/detect"])
 def test_controller_read_sees_all_previous_updates(mode):
     """4 'ranks' (threads sharing one controller, as the reference's VirtualEnvironment test does) read ids,
     produce gradients and call the AfterBackward protocol; at every read the table row must equal the
@@ -37,8 +38,15 @@ def test_controller_read_sees_all_previous_updates(mode):
     from recstore_b200.controller import KGCacheController, BasePerfSampler
     ranks, N, D, L, steps, per = 4, 2000, 8, 5, 40, 64
     clr = 0.5
+    mode, _, variant = mode.partition("/")
     cfg = {"num_gpus": ranks, "L": L, "clr": clr, "dim": D, "backwardMode": mode, "nr_background_threads": 2,
            "full_emb_capacity": N, "cache_ratio": 0.05}
+    if variant.startswith("omp"):
+        cfg["update_pq_use_omp"] = int(variant[3:])       # how a step's keys enter the queue: serial / per rank / per shard group
+    if variant == "nodetect":
+        cfg["use_detect_thread"] = 0
+    if variant == "detect":
+        cfg["use_detect_thread"] = 1
     ctrl = KGCacheController.Init(json.dumps(cfg))
     table = torch.zeros(N, D)
     c = int(N * 0.05)
@@ -91,10 +99,45 @@ def test_controller_read_sees_all_previous_updates(mode):
     ctrl.Drain()
     ctrl.StopThreads()
     assert ctrl.PendingCount() == 0
+    # the strategies really differ: the first one flushes id by id and reads announcements through mailboxes + a detect
+    # thread, the second one swaps whole buckets out; the upsert variant that was asked for is the one that ran
+    st = ctrl.Stats()
+    if mode == "CppAsync":
+        assert st["bucket_swaps"] == 0 and st["flushed"] > 0
+        assert (st["mailed_announcements"] > 0) == (variant != "nodetect")
+    elif mode == "CppAsyncV2":
+        assert st["bucket_swaps"] > 0 and (st["mailed_announcements"] > 0) == (variant == "detect")
+    if mode != "CppSync":
+        want = {"omp0": "upsert_serial", "omp2": "upsert_per_shard_group"}.get(variant, "upsert_per_rank")
+        assert st[want] == steps and sum(st[k] for k in ("upsert_serial", "upsert_per_rank", "upsert_per_shard_group")) == steps, st
     full = table.clone()
     for r in range(ranks):
         full[r * c:(r + 1) * c] = caches[r]
     assert torch.allclose(full, oracle, atol=1e-4)
+
+
+def test_sampler_ring_pops_the_batch_announced_for_the_current_step():
+    """``next()`` pushes batch t + L (announcing its reads for step t + L) and pops batch t: the ids a rank reads at step t
+    must be exactly the ones it announced for step t, L steps earlier (a ring of only L slots would hand out batch
+    t + L instead, and every read would come L steps before its announcement)."""
+    from recstore_b200.controller import BasePerfSampler
+
+    class Recorder:
+        def __init__(self):
+            self.by_step = {}
+
+        def PublishReads(self, rank, step, ids):
+            self.by_step[step] = ids.clone()
+
+    for L in (1, 2, 5):
+        rec = Recorder()
+        s = BasePerfSampler(0, L, 16, 1000, "CppAsyncV2", rec, seed=4)
+        s.Prefill()
+        assert sorted(rec.by_step) == list(range(L))
+        for step in range(12):
+            ids = next(s)
+            assert torch.equal(ids, rec.by_step[step]), (L, step)
+            assert max(rec.by_step) == step + L                 # the lookahead window stays L steps deep
 
 
 def test_wrapper_after_backward_protocol():
