@@ -58,7 +58,8 @@ def routine(rank: int, args, port: int, ns: str, out=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     if args.device == "cuda":
         torch.cuda.set_device(rank)
-    dist.init_process_group("nccl" if args.device == "cuda" else "gloo", rank=rank, world_size=args.num_workers)
+    # host-side tensors (announced ids, host-table updates) travel over gloo, device tensors over NCCL
+    dist.init_process_group("cpu:gloo,cuda:nccl" if args.device == "cuda" else "gloo", rank=rank, world_size=args.num_workers)
     import recstore_b200 as rs
     from recstore_b200 import ipc
     from recstore_b200.cache import CacheEmbFactory
@@ -121,7 +122,10 @@ def routine(rank: int, args, port: int, ns: str, out=None):
                 loss.backward()
                 if golden is not None:
                     ref = golden.forward(ids)
-                    worst = max(worst, (out_emb.detach() - ref.detach()).abs().max().item())
+                    # relative to the row's size: a hot row takes thousands of gradient occurrences per step and drifts to
+                    # magnitudes where the fp32 summation order alone (dense all-reduce there, per-occurrence adds here) shows
+                    d, r = out_emb.detach(), ref.detach()
+                    worst = max(worst, ((d - r).abs() / (1.0 + r.abs())).max().item())
                     gopt.zero_grad()
                     (ref.sum() * (rank + 1)).backward()
                     gopt.step()
@@ -143,7 +147,7 @@ def routine(rank: int, args, port: int, ns: str, out=None):
         if args.with_perf:
             print(Reporter.Report())
         if args.diff_test:
-            print(f"diff_test: worst |cached - golden| = {worst:.3e}")
+            print(f"diff_test: worst |cached - golden| / (1 + |golden|) = {worst:.3e}")
         print("Successfully xmh", flush=True)
     if out is not None:
         out[rank] = (steps_done, worst)

@@ -305,16 +305,19 @@ __global__ void range_cache_query_kernel(float* __restrict__ dst, const long lon
   const int lane = threadIdx.x & 31;
   const long long k = ids[i];
   const float* src;
+  bool host = false;
   if (k >= start && k < end) src = hbm + (k - start) * dim;
-  else if (k >= 0 && k < host_rows) src = host_table + k * dim;
+  else if (k >= 0 && k < host_rows) { src = host_table + k * dim; host = true; }
   else {
     if (lane == 0 && status) atomicOr(status, (unsigned long long)RS_DEV_OOB_ROW);
     return;
   }
+  // Host rows are written by the CPU between kernels: they are read around the GPU's caches, every time.
   if ((dim & 3) == 0) {
-    for (int v = lane; v < (dim >> 2); v += 32) reinterpret_cast<float4*>(dst + i * dim)[v] = reinterpret_cast<const float4*>(src)[v];
+    for (int v = lane; v < (dim >> 2); v += 32)
+      reinterpret_cast<float4*>(dst + i * dim)[v] = host ? __ldcv(reinterpret_cast<const float4*>(src) + v) : reinterpret_cast<const float4*>(src)[v];
   } else {
-    for (int v = lane; v < dim; v += 32) dst[i * dim + v] = src[v];
+    for (int v = lane; v < dim; v += 32) dst[i * dim + v] = host ? __ldcv(src + v) : src[v];
   }
 }
 }  // namespace

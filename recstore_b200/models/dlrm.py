@@ -252,7 +252,7 @@ class DLRM:
         self.gnorm = self.Gwin.view(torch.float32, (self.B, self.Tmax), byte_offset=self.gn_off)
         self.ndst_table = torch.tensor([p + self.gn_off for p in self.Gwin.ptrs], dtype=torch.int64, device=dev)
         self.Tbuf = self.Twin.view(torch.bfloat16, (self.Bl, self.F * self.D))
-        if self.world > 1 and self.K and not self.dcn and not self.proj:
+        if self.world > 1 and not self.dcn and not self.proj and (self.K or os.environ.get("RECSTORE_GRAD_PUSH", "") == "staged"):
             # Backward all-to-all with row-sharded tables under the dot interaction: its backward leaves the per-(sample,
             # table) gradient rows in this local staging buffer; a thin copy kernel then fans them out to their owners.
             self.gstage = torch.empty(self.Bl, self.T * self.D, **bf)
@@ -384,7 +384,8 @@ class DLRM:
         self._status_host = [torch.zeros(1, dtype=torch.int64).pin_memory() for _ in range(2)]   # the device status word, read back with the loss
         # Dot interaction without row-sharded tables: the interaction backward pushes the embedding gradients itself.  With
         # row-sharded tables (a gradient row then goes to every rank) they are staged and a thin copy kernel fans them out.
-        self._fused_push = not self.K and not self.dcn and not self.proj
+        # (RECSTORE_GRAD_PUSH=staged forces the staged form for measurements.)
+        self._fused_push = not self.K and not self.dcn and not self.proj and os.environ.get("RECSTORE_GRAD_PUSH", "") != "staged"
         # Stream priorities (RECSTORE_STREAM_PRIORITIES: 0 = none, 1 = main stream first, 2 = communication stream first).
         prio = os.environ.get("RECSTORE_STREAM_PRIORITIES", "0")
         p_main, p_comm, p_col, p_wgrad = {"1": (-3, -2, -1, 0), "2": (-2, -3, -1, 0)}.get(prio, (0, 0, 0, 0))

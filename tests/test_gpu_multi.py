@@ -283,6 +283,20 @@ def test_sharded_table_lookup_update_matches_replicated_oracle():
     assert all(out.get(r) == "ok" for r in range(world)), dict(out)
 
 
+@pytest.mark.parametrize("choice", ["KnownShardedCachedEmbedding", "KnownLocalCachedEmbedding"])
+def test_cached_embeddings_on_the_native_plane_match_replicated_embedding(choice):
+    """The reference-named cached embeddings on two GPUs (hot ranges as range-owned shards on the peer-window
+    transport, rows of other ranges from the device-mapped host table, gradients delivered by ``push_update``): every
+    step's forward output equals a replicated ``nn.Embedding`` trained with the same gradients (the driver's --diff_test)."""
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    from recstore_b200.cli import perf_emb
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    out = perf_emb.main(["--num_workers", "2", "--device", "cuda", "--run_steps", "25", "--diff_test", "--emb_choice", choice,
+                         "--backwardMode", "CppAsyncV2", "--batch_size", "3000", "--num_embs", "50000", "--log_interval", "1000"])
+    assert len(out) == 2 and all(v[0] == 25 and v[1] < 1e-3 for v in out.values()), out
+
+
 def test_kge_driver_two_gpus_native_path():
     """TransE-L2 on entity / relation tables sharded over two GPUs, through the training driver."""
     if _ngpus() < 2:
