@@ -3,3 +3,4 @@ from .gpu_cache import GpuCache, GpuHashTable, CacheQueryResult, merge_op, uva_c
 from .embeddings import (CacheShardingPolicy, AbsEmb, TorchNativeStdEmb, TorchNativeStdEmbDDP, KnownLocalCachedEmbedding,  # noqa: F401,E402
                          KnownLocalCachedEmbeddingSoftware, KnownShardedCachedEmbedding, KGExternelEmbedding, NVGPUCache,
                          CacheEmbFactory)
+from .lookahead_table import LookaheadCachedTable  # noqa: F401,E402

@@ -32,6 +32,7 @@ struct CacheView {
   unsigned long long* keys;   // [nsets * 32]
   unsigned* stamps;           // [nsets * 32]
   unsigned* vers;             // [nsets * 32] slot sequence numbers (odd while a writer is inside)
+  unsigned char* dirty;       // [nsets * 32] 1 = the row was changed in the cache and the backing store is behind
   float* values;              // [nsets * 32, dim]
   int* locks;                 // [nsets]
   unsigned* clock;            // global LRU clock
@@ -55,6 +56,7 @@ __global__ void cache_init_kernel(CacheView c) {
     c.keys[i] = kEmptyKey;
     c.stamps[i] = 0;
     c.vers[i] = 0;
+    c.dirty[i] = 0;
   }
   if (i < c.nsets) c.locks[i] = 0;
   if (i == 0) *c.clock = 0;
@@ -93,13 +95,13 @@ __global__ void __launch_bounds__(256) cache_query_kernel(CacheView c, const lon
       const unsigned v0 = *reinterpret_cast<volatile unsigned*>(&c.vers[slot]);
       __threadfence();
       const unsigned long long k0 = *reinterpret_cast<volatile unsigned long long*>(&c.keys[slot]);
-      copy_row_cg(out + i * c.dim, c.values + slot * c.dim, c.dim, lane);
+      if (out != nullptr) copy_row_cg(out + i * c.dim, c.values + slot * c.dim, c.dim, lane);
       __threadfence();
       const unsigned v1 = *reinterpret_cast<volatile unsigned*>(&c.vers[slot]);
       valid = __all_sync(0xffffffffu, (v0 & 1u) == 0u && v1 == v0 && k0 == key);
       if (valid && lane == 0) c.stamps[slot] = now;
     }
-    if (!valid && lane == 0) {
+    if (!valid && lane == 0 && key != kEmptyKey) {          // the empty marker is padding: neither a hit nor a miss
       const int pos = atomicAdd(miss_count, 1);
       miss_index[pos] = i;
       miss_keys[pos] = static_cast<long long>(key);
@@ -187,6 +189,150 @@ __global__ void __launch_bounds__(256) cache_write_kernel(CacheView c, const lon
   }
 }
 
+// Replace that hands the evicted rows back (write-back caches) and never evicts a row stamped at or after
+// `protect_from` (rows of the step in flight and of the batches already announced).  Dirty evicted rows go to
+// evict_keys / evict_values (cursor evict_count); a key that finds its set full of protected rows is not inserted and is
+// reported in refused_keys (cursor refused_count): the caller serves it from the backing store.
+__global__ void __launch_bounds__(256) cache_replace_evict_kernel(CacheView c, const long long* __restrict__ keys, const int* n_dev,
+                                                                  long long n_cap, const float* __restrict__ values, unsigned protect_from,
+                                                                  long long* __restrict__ evict_keys, float* __restrict__ evict_values,
+                                                                  int* evict_count, long long* __restrict__ refused_keys,
+                                                                  int* refused_count, unsigned long long* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const unsigned now = *c.clock;
+  const long long n = n_dev ? min(static_cast<long long>(*n_dev), n_cap) : n_cap;
+  for (long long i = warp; i < n; i += nwarps) {
+    const unsigned long long key = static_cast<unsigned long long>(keys[i]);
+    if (key == kEmptyKey) continue;
+    const unsigned long long set = ht_hash(key) % c.nsets;
+    if (!lock_set(&c.locks[set], lane)) {
+      if (lane == 0 && status) atomicOr(status, (unsigned long long)RS_DEV_WAIT_TIMEOUT);
+      if (lane == 0 && refused_keys) refused_keys[atomicAdd(refused_count, 1)] = static_cast<long long>(key);
+      continue;
+    }
+    const unsigned long long line = *reinterpret_cast<volatile unsigned long long*>(&c.keys[set * kWays + lane]);
+    const unsigned hit = __ballot_sync(0xffffffffu, line == key);
+    if (hit) {                                   // already cached (brought in by a step in between): only refresh the stamp
+      if (lane == 0) c.stamps[set * kWays + (__ffs(hit) - 1)] = now;
+      unlock_set(&c.locks[set], lane);
+      continue;
+    }
+    int way = -1;
+    bool evicting = false;
+    const unsigned empty = __ballot_sync(0xffffffffu, line == kEmptyKey);
+    if (empty) {
+      way = __ffs(empty) - 1;
+    } else {
+      const unsigned st = *reinterpret_cast<volatile unsigned*>(&c.stamps[set * kWays + lane]);
+      unsigned long long best = (static_cast<unsigned long long>(st) << 5) | lane;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other < best ? other : best;
+      }
+      if (static_cast<unsigned>(best >> 5) < protect_from) { way = static_cast<int>(best & 31); evicting = true; }
+    }
+    if (way < 0) {                               // every way holds a protected row
+      if (lane == 0 && refused_keys) refused_keys[atomicAdd(refused_count, 1)] = static_cast<long long>(key);
+      unlock_set(&c.locks[set], lane);
+      continue;
+    }
+    const unsigned long long slot = set * kWays + way;
+    if (evicting && c.dirty[slot] && evict_keys) {
+      int pos = 0;
+      if (lane == 0) pos = atomicAdd(evict_count, 1);
+      pos = __shfl_sync(0xffffffffu, pos, 0);
+      copy_row(evict_values + static_cast<long long>(pos) * c.dim, c.values + slot * c.dim, c.dim, lane);
+      const unsigned long long old = __shfl_sync(0xffffffffu, line, way);
+      if (lane == 0) evict_keys[pos] = static_cast<long long>(old);
+    }
+    if (lane == 0) {
+      atomicAdd(&c.vers[slot], 1u);
+      __threadfence();
+    }
+    __syncwarp();
+    copy_row(c.values + slot * c.dim, values + i * c.dim, c.dim, lane);
+    if (lane == 0) {
+      *reinterpret_cast<volatile unsigned long long*>(&c.keys[slot]) = key;
+      c.stamps[slot] = now;
+      c.dirty[slot] = 0;
+    }
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) atomicAdd(&c.vers[slot], 1u);
+    unlock_set(&c.locks[set], lane);
+  }
+}
+
+// Optimizer step on cached rows, in place.  A cached row is [D weights | state | padding] (dim = D + 4).  keys are distinct;
+// grad [n, D] and norm [n] (sum of squares over the key's occurrences).  optimizer 0: w -= lr * g; 1 (row-wise Adagrad):
+// state += norm / D, w -= lr * g / (sqrt(state) + eps).  A key that is not cached is appended to missing (cursor
+// missing_count) with its index, for the caller to apply on the backing store.
+__global__ void __launch_bounds__(256) cache_apply_kernel(CacheView c, const long long* __restrict__ keys, const int* n_dev, long long n_cap,
+                                                          const float* __restrict__ grad, const float* __restrict__ norm, int D, float lr,
+                                                          float eps, int optimizer, long long* __restrict__ missing_index,
+                                                          int* missing_count) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const long long n = n_dev ? min(static_cast<long long>(*n_dev), n_cap) : n_cap;
+  for (long long i = warp; i < n; i += nwarps) {
+    const unsigned long long key = static_cast<unsigned long long>(keys[i]);
+    if (key == kEmptyKey) continue;
+    const unsigned long long set = ht_hash(key) % c.nsets;
+    const unsigned long long line = c.keys[set * kWays + lane];
+    const unsigned hit = __ballot_sync(0xffffffffu, line == key);
+    if (!hit) {
+      if (lane == 0 && missing_index) missing_index[atomicAdd(missing_count, 1)] = i;
+      continue;
+    }
+    const unsigned long long slot = set * kWays + (__ffs(hit) - 1);
+    float* row = c.values + slot * c.dim;
+    if (lane == 0) {
+      atomicAdd(&c.vers[slot], 1u);
+      __threadfence();
+    }
+    __syncwarp();
+    float scale = -lr;
+    if (optimizer == 1) {
+      const float stt = row[D] + (norm ? norm[i] : 0.f) / static_cast<float>(D);
+      scale = -lr / (sqrtf(stt) + eps);
+      __syncwarp();
+      if (lane == 0) row[D] = stt;
+    }
+    for (int v = lane; v < (D >> 2); v += 32) {
+      float4 w = reinterpret_cast<float4*>(row)[v];
+      const float4 g = __ldg(reinterpret_cast<const float4*>(grad + i * D) + v);
+      w.x += scale * g.x; w.y += scale * g.y; w.z += scale * g.z; w.w += scale * g.w;
+      reinterpret_cast<float4*>(row)[v] = w;
+    }
+    if (lane == 0) c.dirty[slot] = 1;
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) atomicAdd(&c.vers[slot], 1u);
+  }
+}
+
+__global__ void cache_set_clock_kernel(unsigned* clock, unsigned v) { *clock = v; }
+
+// Every dirty row of the set range -> (keys, values), dirty bits cleared: a flush for checkpoints.
+__global__ void __launch_bounds__(256) cache_flush_dirty_kernel(CacheView c, long long* __restrict__ keys_out, float* __restrict__ values_out,
+                                                                int* count) {
+  const int lane = threadIdx.x & 31;
+  const unsigned long long warp = static_cast<unsigned long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const unsigned long long nwarps = static_cast<unsigned long long>(gridDim.x) * (blockDim.x >> 5);
+  for (unsigned long long slot = warp; slot < c.nsets * kWays; slot += nwarps) {
+    if (c.keys[slot] == kEmptyKey || !c.dirty[slot]) continue;
+    int pos = 0;
+    if (lane == 0) pos = atomicAdd(count, 1);
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (lane == 0) { keys_out[pos] = static_cast<long long>(c.keys[slot]); c.dirty[slot] = 0; }
+    copy_row(values_out + static_cast<long long>(pos) * c.dim, c.values + slot * c.dim, c.dim, lane);
+  }
+}
+
 __global__ void cache_dump_kernel(CacheView c, unsigned long long set_begin, unsigned long long set_end,
                                   long long* __restrict__ keys_out, unsigned long long* count) {
   const unsigned long long i = set_begin * kWays + static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -212,6 +358,7 @@ RS_API int rs_cache_create(unsigned long long num_items, int dim, void** handle)
   RS_CUDA(cudaMalloc(&v.keys, slots * sizeof(unsigned long long)));
   RS_CUDA(cudaMalloc(&v.stamps, slots * sizeof(unsigned)));
   RS_CUDA(cudaMalloc(&v.vers, slots * sizeof(unsigned)));
+  RS_CUDA(cudaMalloc(&v.dirty, slots));
   RS_CUDA(cudaMalloc(&v.values, slots * static_cast<size_t>(dim) * sizeof(float)));
   RS_CUDA(cudaMalloc(&v.locks, v.nsets * sizeof(int)));
   RS_CUDA(cudaMalloc(&v.clock, sizeof(unsigned)));
@@ -224,7 +371,7 @@ RS_API int rs_cache_create(unsigned long long num_items, int dim, void** handle)
 RS_API int rs_cache_destroy(void* handle) {
   if (!handle) return RS_OK;
   CacheOwned* h = static_cast<CacheOwned*>(handle);
-  cudaFree(h->v.keys); cudaFree(h->v.stamps); cudaFree(h->v.vers); cudaFree(h->v.values); cudaFree(h->v.locks); cudaFree(h->v.clock);
+  cudaFree(h->v.keys); cudaFree(h->v.stamps); cudaFree(h->v.vers); cudaFree(h->v.dirty); cudaFree(h->v.values); cudaFree(h->v.locks); cudaFree(h->v.clock);
   delete h;
   return RS_OK;
 }
@@ -234,7 +381,7 @@ RS_API unsigned long long rs_cache_num_sets(void* handle) { return static_cast<C
 // out: [n, dim] (hit rows written, miss rows untouched); miss_index / miss_keys: [n]; miss_count: device int.
 RS_API int rs_cache_query(void* handle, const long long* keys, long long n, float* out, long long* miss_index,
                           long long* miss_keys, int* miss_count, cudaStream_t stream) {
-  RS_REQUIRE(handle && keys && out && miss_index && miss_keys && miss_count, "rs_cache_query: null argument");
+  RS_REQUIRE(handle && keys && miss_index && miss_keys && miss_count, "rs_cache_query: null argument");   // out == null: probe only
   CacheView& v = static_cast<CacheOwned*>(handle)->v;
   cache_tick_kernel<<<1, 1, 0, stream>>>(v.clock, miss_count);
   RS_LAUNCH_CHECK();
@@ -276,6 +423,68 @@ RS_API int rs_cache_dump(void* handle, unsigned long long set_begin, unsigned lo
   const unsigned long long slots = (set_end - set_begin) * kWays;
   if (slots == 0) return RS_OK;
   cache_dump_kernel<<<static_cast<unsigned>((slots + 255) / 256), 256, 0, stream>>>(v, set_begin, set_end, keys_out, count);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+// ---- write-back cache verbs (the HBM tier of a table whose backing store is host memory)
+// keys may be bounded by a device count n_dev (<= n_cap).  evict_* / refused_* outputs hold up to n_cap entries; their
+// counters are NOT cleared here (one pair of counters can collect over several calls).
+RS_API int rs_cache_replace_evict(void* handle, const long long* keys, const int* n_dev, long long n_cap, const float* values,
+                                  unsigned protect_from, long long* evict_keys, float* evict_values, int* evict_count,
+                                  long long* refused_keys, int* refused_count, unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(handle && keys && values, "rs_cache_replace_evict: null argument");
+  RS_REQUIRE(!evict_keys || (evict_values && evict_count), "rs_cache_replace_evict: eviction output needs values and a counter");
+  RS_REQUIRE(!refused_keys || refused_count, "rs_cache_replace_evict: refusal output needs a counter");
+  if (n_cap == 0) return RS_OK;
+  CacheView& v = static_cast<CacheOwned*>(handle)->v;
+  long long warps = n_cap < 148 * 32 ? n_cap : 148 * 32;
+  cache_replace_evict_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(v, keys, n_dev, n_cap, values, protect_from,
+                                                                                        evict_keys, evict_values, evict_count,
+                                                                                        refused_keys, refused_count, status);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+// D: weights per row; the cache was created with dim >= D + 1 (state at column D).
+RS_API int rs_cache_apply(void* handle, const long long* keys, const int* n_dev, long long n_cap, const float* grad, const float* norm,
+                          int D, float lr, float eps, int optimizer, long long* missing_index, int* missing_count, cudaStream_t stream) {
+  RS_REQUIRE(handle && keys && grad, "rs_cache_apply: null argument");
+  CacheView& v = static_cast<CacheOwned*>(handle)->v;
+  RS_REQUIRE(D % 4 == 0 && D > 0 && D + 1 <= v.dim, "rs_cache_apply: rows of %d weights need a cache of at least %d columns (has %d)", D, D + 1, v.dim);
+  RS_REQUIRE(!missing_index || missing_count, "rs_cache_apply: the missing list needs a counter");
+  if (n_cap == 0) return RS_OK;
+  long long warps = n_cap < 148 * 32 ? n_cap : 148 * 32;
+  cache_apply_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(v, keys, n_dev, n_cap, grad, norm, D, lr, eps, optimizer,
+                                                                                missing_index, missing_count);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+RS_API int rs_cache_set_clock(void* handle, unsigned value, cudaStream_t stream) {
+  RS_REQUIRE(handle, "rs_cache_set_clock: null handle");
+  cache_set_clock_kernel<<<1, 1, 0, stream>>>(static_cast<CacheOwned*>(handle)->v.clock, value);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+// keys_out / values_out: room for the whole capacity; count: device int, cleared here.
+RS_API int rs_cache_flush_dirty(void* handle, long long* keys_out, float* values_out, int* count, cudaStream_t stream) {
+  RS_REQUIRE(handle && keys_out && values_out && count, "rs_cache_flush_dirty: null argument");
+  CacheView& v = static_cast<CacheOwned*>(handle)->v;
+  RS_CUDA(cudaMemsetAsync(count, 0, sizeof(int), stream));
+  cache_flush_dirty_kernel<<<148 * 4, 256, 0, stream>>>(v, keys_out, values_out, count);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+// Query variant that does not advance the clock (the caller sets it with rs_cache_set_clock) and may skip the row copy
+// (out == null: probe: stamps the hits, lists the misses).
+RS_API int rs_cache_query_noclock(void* handle, const long long* keys, long long n, float* out, long long* miss_index,
+                                  long long* miss_keys, int* miss_count, cudaStream_t stream) {
+  RS_REQUIRE(handle && keys && miss_index && miss_keys && miss_count, "rs_cache_query_noclock: null argument");
+  CacheView& v = static_cast<CacheOwned*>(handle)->v;
+  RS_CUDA(cudaMemsetAsync(miss_count, 0, sizeof(int), stream));
+  if (n == 0) return RS_OK;
+  long long warps = (n + 3) / 4;
+  if (warps > 148 * 32) warps = 148 * 32;
+  cache_query_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(v, keys, n, out, miss_index, miss_keys, miss_count);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

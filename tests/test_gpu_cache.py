@@ -298,3 +298,66 @@ def test_tiered_table_lookahead_prefetch_is_exact():
     st = ahead.hit_stats()
     assert st["prefetched_lookups"] == len(batches) - 1 and st["staged_rows_refreshed"] > 0
     assert ahead.status.item() == 0
+
+
+def test_lookahead_cached_table_reads_its_own_updates(dev):
+    """Host-resident table + write-back HBM cache fed by the lookahead window: batches are announced two steps ahead,
+    their missing rows are gathered on the host and copied to the device on a side stream, inserted at the step that
+    uses them (evicting and writing back dirty rows), read, and updated in the cache.  Every lookup must return what a
+    plain table updated synchronously would hold; after a flush the host table equals it."""
+    from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
+    from recstore_b200.cache import LookaheadCachedTable
+    N, D, n, L, steps = 20000, 32, 512, 2, 40
+    tab = LookaheadCachedTable(N, D, cache_rows=8192, max_keys=n, lr=0.1, eps=1e-8, device=dev, lookahead=L, init="row_index")
+    W = torch.arange(N, dtype=torch.float32, device=dev).unsqueeze(1).repeat(1, D)
+    S = torch.zeros(N, device=dev)
+    g = torch.Generator(device=dev).manual_seed(21)
+    batches = [torch.randint(0, N, (n,), device=dev, generator=g) for _ in range(steps + L)]
+    for b in batches:
+        b[::9] = 7                                       # a hot id in every batch
+    for t in range(L):
+        tab.prefetch(batches[t], t)
+    for t in range(steps):
+        tab.prefetch(batches[t + L], t + L)              # the sampler is L steps ahead
+        ids = batches[t]
+        rows = tab.lookup(ids, t)
+        assert torch.allclose(rows, W[ids], atol=1e-3, rtol=1e-5), (t, (rows - W[ids]).abs().max().item())
+        grads = torch.randn(n, D, device=dev, generator=g)
+        tab.update(grads)
+        rowwise_adagrad_update(W, S, ids, grads, 0.1, 1e-8)
+    tab.check()
+    st = tab.stats
+    assert st["late_announcements"] == 0 and st["staged_rows"] > 0 and st["written_back_rows"] > 0, st   # rows did migrate both ways
+    tab.flush()
+    assert torch.allclose(tab.weights(), W.cpu(), atol=2e-3, rtol=1e-5)
+    assert torch.allclose(tab.state(), S.cpu(), atol=1e-2, rtol=2e-3)
+    # a batch that was never announced is fetched on demand (counted), and is still right
+    extra = torch.randint(0, N, (n,), device=dev, generator=g)
+    rows = tab.lookup(extra, steps + L)
+    assert torch.allclose(rows, W[extra], atol=1e-3, rtol=1e-5) and tab.stats["late_announcements"] == 1
+    tab.close()
+
+
+def test_lookahead_cached_table_withheld_staging_and_undersized_cache(dev):
+    """Failure paths made on the host: (a) the staging of an announced batch never arrives (the worker is told to hold
+    it): the lookup gives up after its time limit with an error instead of hanging; (b) a cache too small for the window
+    refuses inserts and says so through the status word."""
+    from recstore_b200 import _lib
+    from recstore_b200.cache import LookaheadCachedTable
+    tab = LookaheadCachedTable(1000, 16, cache_rows=1024, max_keys=64, device=dev, lookahead=1, wait_timeout_s=0.3)
+    ids = torch.arange(64, device=dev)
+    tab._hold.set()
+    tab.prefetch(ids, 0)
+    with pytest.raises(_lib.RecStoreError) as e:
+        tab.lookup(ids, 0)
+    assert e.value.code == _lib.ERR_TIMEOUT
+    assert torch.ones(4, device=dev).sum().item() == 4          # the context is fine
+    tab.close()
+    small = LookaheadCachedTable(100000, 16, cache_rows=64, max_keys=2048, device=dev, lookahead=1, init="row_index")
+    ids = torch.arange(2048, device=dev) * 7
+    small.prefetch(ids, 0)
+    small.lookup(ids, 0)
+    with pytest.raises(_lib.DeviceStatusError) as e2:
+        small.check()
+    assert "table_full" in str(e2.value)
+    small.close()
