@@ -239,6 +239,90 @@ def run_native(args):
         dist.destroy_process_group()
 
 
+def run_kge(args):
+    """Knowledge-graph embedding training at the shape of the fourth benchmark config: 86 M entities x dim 400 fp32 (138 GB)
+    spread over the GPUs' HBM, 14,824 relations, 1,024 positives per GPU with 256 chunk-shared uniform negatives, log-sigmoid
+    loss, gamma 10, sparse row-wise Adagrad lr 0.1; synthetic triples (head / tail power law alpha 1.3, relations uniform)
+    drawn on the device.  Weak scaling: the per-GPU batch is fixed.  --kge-entities scales the table down for small runs."""
+    from recstore_b200.models.kge import KGEConfig, KGEModel
+    from recstore_b200.parallel.peer import PeerContext
+    from recstore_b200.utils.data import device_uniform_ids, device_zipf_ids
+    rank, world, local = dist_setup(args.gpus)
+    dev = torch.device(f"cuda:{local}")
+    ctx = PeerContext(rank, world, device=dev)
+    NE, NR, D, bs, ns = args.kge_entities, 14824, 400, 1024, 256
+    cfg = KGEConfig(NE, NR, dim=D, model=args.kge_model, gamma=10.0, batch=bs, neg_sample_size=ns, neg_chunk_size=ns, lr=0.1,
+                    seed=args.seed, use_cuda_graph=not args.no_graph)
+    model = KGEModel(cfg, ctx)
+    nneg = bs // ns * ns
+    nb = 8
+
+    def draw(k):   # one step's ids, on the device, from counter-based streams
+        c = (k * world + rank) * 4 * bs
+        return (device_zipf_ids(bs, NE, 1.3, args.seed + 11, c, device=dev, spread=True),
+                device_uniform_ids(bs, NR, args.seed + 12, c, device=dev),
+                device_zipf_ids(bs, NE, 1.3, args.seed + 13, c, device=dev, spread=True),
+                device_uniform_ids(nneg, NE, args.seed + 14, c, device=dev))
+    dev_batches = [draw(k) for k in range(nb)]
+    host_batches = [tuple(t.cpu().pin_memory() for t in b) for b in dev_batches]
+    for i in range(max(args.warmup, 3) + 2):          # both corruption sides get captured
+        loss = model.train_step(*dev_batches[i % nb])
+    ctx.check_status()
+    sampler = ClockSampler(local)
+    barrier(world)
+    if rank == 0:
+        sampler.start()
+    samples = []
+    for _ in range(max(1, args.repeats)):
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            loss = model.train_step(*dev_batches[i % nb])
+        e1.record()
+        e1.synchronize()
+        samples.append(max_over_ranks(e0.elapsed_time(e1), world))
+    barrier(world)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_dev = statistics.median(samples)
+    # end to end: ids from pinned host memory every step, loss read back every step
+    bufs = [tuple(torch.empty_like(t, device=dev) for t in host_batches[0]) for _ in range(2)]
+    barrier(world)
+    t0 = time.perf_counter()
+    last = 0.0
+    for i in range(args.steps):
+        hb, db = host_batches[i % nb], bufs[i & 1]
+        for d, h in zip(db, hb):
+            d.copy_(h, non_blocking=True)
+        last = model.train_step(*db).item()
+    torch.cuda.synchronize()
+    ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3, world)
+    ctx.check_status()
+    if rank == 0:
+        h2d = sum(t.numel() * 8 for t in host_batches[0])
+        out = {
+            "metric": "kge_train_triples_per_s", "value": bs * world * args.steps / (ms_dev * 1e-3), "unit": "triples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32 tables, bf16 score GEMMs", "impl": "native",
+            "data": "synthetic (power-law alpha 1.3 head / tail entities, uniform relations and negatives, drawn on the device)",
+            "config": {"model": f"{args.kge_model}, {NE} entities x dim {D} fp32 ({NE * D * 4 / 1e9:.0f} GB) sharded over {world} GPU(s), {NR} relations",
+                       "global_batch": bs * world, "negatives": f"{ns} chunk-shared uniform per {ns} positives", "gamma": 10.0,
+                       "optimizer": "sparse row-wise Adagrad lr 0.1", "parallelism": f"row-sharded entity / relation tables x{world}",
+                       "l2": "the entity shard (17-138 GB) exceeds the 126 MB L2; ids differ every step"},
+            "clocks": clocks,
+            "e2e": {"value": bs * world * args.steps / (ms_e2e * 1e-3), "unit": "triples/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "timed_regions": {"repeats": len(samples), "ms_per_step_min": min(samples) / args.steps,
+                              "ms_per_step_max": max(samples) / args.steps, "value_is": "median"},
+            "gpu_launches": model.launches_per_step * args.steps, "launches_per_step": model.launches_per_step, "last_loss_rank0": last,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_torch_baseline(args):
     """PyTorch + NCCL + cuBLAS restatement of the reference algorithm on the same data."""
     from recstore_b200.baseline.dlrm_torch import TorchDLRM
@@ -312,8 +396,11 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference", "torch_baseline"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--workload", default="dlrm", choices=["dlrm", "dcnv2"],
-                    help="dlrm: the headline config; dcnv2: the multi-hot DLRM-DCNv2 config (native arm only)")
+    ap.add_argument("--workload", default="dlrm", choices=["dlrm", "dcnv2", "kge"],
+                    help="dlrm: the headline config; dcnv2: the multi-hot DLRM-DCNv2 config; kge: knowledge-graph embedding training "
+                         "(native arm only for the last two)")
+    ap.add_argument("--kge-model", default="TransE_l2", choices=["TransE_l2", "DistMult", "ComplEx", "SimplE", "TransE_l1", "RotatE"])
+    ap.add_argument("--kge-entities", type=int, default=86_054_151, help="entities of the kge workload (the config's Freebase count)")
     ap.add_argument("--row-split", default="auto",
                     help="dcnv2 workload: tables spread row-wise over the GPUs: auto (those with more than 1/N of the ids per sample), "
                          "none (every table whole on one GPU) or a comma-separated list of table indices")
@@ -329,6 +416,8 @@ def main():
         run_reference(args)
     elif args.impl == "torch_baseline":
         run_torch_baseline(args)
+    elif args.workload == "kge":
+        run_kge(args)
     else:
         run_native(args)
 

@@ -103,6 +103,9 @@ def main(argv=None):
     ap.add_argument("--sharded-tiered", action="store_true",
                     help="with --sharded / several ranks: every shard keeps only --hbm-ratio of its rows in HBM, the rest in pinned host memory")
     ap.add_argument("--sharded", action="store_true", help="all-HBM table sharded over the ranks instead of the tiered table")
+    ap.add_argument("--lookahead", type=int, default=0,
+                    help="one GPU: host-resident table behind a write-back HBM cache of --hbm-ratio of the rows, batches announced this "
+                         "many steps ahead (LookaheadCachedTable) instead of the static hot range")
     ap.add_argument("--graph", action="store_true", help="sharded table: replay lookup + update from a CUDA graph")
     ap.add_argument("--legacy", action="store_true", help="sharded table: separate count / signal / wait launches instead of the fused kernels")
     ap.add_argument("--hashed", action="store_true", help="sharded table: hash-table shards (keys inserted on first touch)")
@@ -125,6 +128,9 @@ def main(argv=None):
             ctx = PeerContext(rank, world, device=dev)
             tab = ShardedEmbeddingTable(ctx, "psbench", a.rows, a.dim, max_keys=maxb, lr=0.01,
                                         hbm_ratio=a.hbm_ratio if a.sharded_tiered else 1.0, fused=not a.legacy, hashed=a.hashed)
+    elif a.lookahead > 0:
+        from recstore_b200.cache import LookaheadCachedTable
+        tab = LookaheadCachedTable(a.rows, a.dim, int(a.rows * a.hbm_ratio), maxb, lr=0.01, device=dev, lookahead=a.lookahead)
     else:
         from recstore_b200.cache.tiered_table import TieredEmbeddingTable
         tab = TieredEmbeddingTable(a.rows, a.dim, a.hbm_ratio, max_keys=maxb, lr=0.01, device=dev)
@@ -137,6 +143,41 @@ def main(argv=None):
 
             graphs = {}
             out_buf = torch.empty(B, a.dim, device=dev)
+            if a.lookahead > 0:
+                # the sampler runs `lookahead` batches ahead of the trainer (fresh ids every step, as in training)
+                L = a.lookahead
+                nsteps = a.iters + 5 + 2 * L + 2
+                stream_ids = [zipf_ids_torch(B, a.rows, alpha, generator=g, device=dev) for _ in range(nsteps)]
+                base = getattr(tab, "_bench_step", 0)
+                for t in range(L):
+                    tab.prefetch(stream_ids[t], base + t)
+                it[0] = 0
+                st0 = dict(tab.stats)
+
+                def step():
+                    t = it[0]
+                    it[0] += 1
+                    tab.prefetch(stream_ids[t + L], base + t + L)
+                    tab.lookup(stream_ids[t], base + t, out=out_buf)
+                    tab.update(grads)
+                ms = _time(step, a.iters, warmup=5)
+                # announced but unused batches are consumed so that the next configuration starts clean
+                for t in range(it[0], it[0] + L):
+                    tab.lookup(stream_ids[t], base + t, out=out_buf)
+                tab._bench_step = base + it[0] + L
+                tab.check()
+                d = {k: tab.stats[k] - st0[k] for k in st0}
+                nst = it[0] + L
+                uniq = float(torch.stack([torch.unique(p).numel() * torch.ones((), device=dev) for p in stream_ids[:8]]).mean().item())
+                rec = {"alpha": alpha, "batch_per_gpu": B, "ms": round(ms, 4), "mkeys_per_s_per_gpu": round(B / ms / 1e3, 2),
+                       "unique_fraction": round(uniq / B, 4), "mode": f"lookahead cache hbm_ratio={a.hbm_ratio} L={L}",
+                       "hit_ratio_unique": round(1.0 - d["staged_rows"] / max(uniq * nst, 1.0), 4),
+                       "staged_mb_per_step": round(d["staged_bytes"] / nst / 1e6, 3),
+                       "written_back_rows_per_step": round(d["written_back_rows"] / nst, 1), "late_announcements": d["late_announcements"],
+                       "rows": a.rows, "host_table_gb": round(a.rows * (a.dim + 4) * 4 / 1e9, 1)}
+                if rank == 0:
+                    print(json.dumps(rec), flush=True)
+                continue
 
             def step():
                 ids = pool[it[0] & 3]

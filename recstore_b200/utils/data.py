@@ -49,6 +49,54 @@ def zipf_ids_torch(n: int, n_rows: int, alpha: float, generator: Optional[torch.
     return zipf_from_uniform(u, n_rows, alpha)
 
 
+def device_uniform_ids(n: int, n_rows: int, seed: int, counter: int, out: Optional[torch.Tensor] = None, device="cuda") -> torch.Tensor:
+    """``n`` uniform ids in ``[0, n_rows)`` drawn on the device: element i comes from ``hash(seed, counter + i)``."""
+    from .. import _lib
+    _register_gen()
+    if out is None:
+        out = torch.empty(n, dtype=torch.int64, device=device)
+    _lib.call("rs_gen_uniform_ids", out.data_ptr(), n, n_rows, seed & 0xFFFFFFFFFFFFFFFF, counter, _lib.stream_ptr())
+    return out
+
+
+def device_zipf_ids(n: int, n_rows: int, alpha: float, seed: int, counter: int, out: Optional[torch.Tensor] = None, device="cuda",
+                    spread: bool = False) -> torch.Tensor:
+    """``n`` bounded Zipf-like ids drawn on the device with the closed form of :func:`zipf_from_uniform`.  ``spread``
+    applies the affine permutation of :func:`powerlaw_triples` so that the popular ids do not all sit on one shard."""
+    from .. import _lib
+    _register_gen()
+    if out is None:
+        out = torch.empty(n, dtype=torch.int64, device=device)
+    a, b = (spread_permutation(n_rows) if spread else (0, 0))
+    _lib.call("rs_gen_zipf_ids", out.data_ptr(), n, n_rows, float(alpha), seed & 0xFFFFFFFFFFFFFFFF, counter, a, b, _lib.stream_ptr())
+    return out
+
+
+def spread_permutation(n_rows: int) -> Tuple[int, int]:
+    """Multiplier (coprime to ``n_rows``) and offset of the popularity-rank -> id permutation."""
+    a = 0x9E3779B97F4A7C15 % n_rows | 1
+    while math.gcd(a, n_rows) != 1:
+        a += 2
+    return a, 12345
+
+
+_gen_registered = False
+
+
+def _register_gen():
+    global _gen_registered
+    if not _gen_registered:
+        import ctypes as C
+        from .. import _lib
+        _lib.register_signatures({
+            "rs_gen_uniform_ids": (C.c_int, [C.c_void_p, C.c_longlong, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_void_p]),
+            "rs_gen_zipf_ids": (C.c_int, [C.c_void_p, C.c_longlong, C.c_longlong, C.c_double, C.c_ulonglong, C.c_ulonglong,
+                                          C.c_ulonglong, C.c_ulonglong, C.c_void_p]),
+            "rs_gen_draw": (C.c_ulonglong, [C.c_ulonglong, C.c_ulonglong]),
+        })
+        _gen_registered = True
+
+
 def loguniform_table_rows(num_tables: int, lo: int, hi: int, total: Optional[int], seed: int,
                           pin_largest: Optional[int] = None) -> List[int]:
     """Row counts drawn log-uniform in [lo, hi] from ``seed``; rescaled (and clamped) so the sum is ~``total``."""
@@ -73,11 +121,9 @@ def powerlaw_triples(n_triples: int, n_entities: int, n_relations: int, alpha: f
     h = zipf_ids(n_triples, n_entities, alpha, rng)
     t = zipf_ids(n_triples, n_entities, alpha, rng)
     # decorrelate popularity rank from id so that hot entities are spread over all shards
-    a = 0x9E3779B97F4A7C15 % n_entities | 1
-    while math.gcd(a, n_entities) != 1:
-        a += 2
-    h = (h * a + 12345) % n_entities
-    t = (t * a + 12345) % n_entities
+    a, b = spread_permutation(n_entities)
+    h = (h * a + b) % n_entities
+    t = (t * a + b) % n_entities
     r = rng.integers(0, n_relations, size=n_triples, dtype=np.int64)
     return h, r, t
 

@@ -74,3 +74,30 @@ def test_uvm_baseline_trainer_allocates_managed_memory():
     assert r["intercepted"]["made_managed"] > 0 and r["intercepted"]["bytes"] >= 200000 * 32 * 4
     r0 = uvm_trainer.main(args + ["--no_uvm"])
     assert r0["uvm"] is False and abs(r0["first_loss"] - r["first_loss"]) < 1e-3 * max(1.0, abs(r["first_loss"]))
+
+
+def test_device_id_generators_match_the_host_formula():
+    """Uniform and Zipf ids drawn on the device: reproducible from (seed, counter), independent of how a stream is cut into
+    calls, inside the range, and equal to the host generator's closed form fed with the same uniforms."""
+    import ctypes as C
+    import numpy as np
+    from recstore_b200 import _lib
+    from recstore_b200.utils.data import device_uniform_ids, device_zipf_ids, spread_permutation, zipf_from_uniform
+    dev = torch.device("cuda:0")
+    n, N = 20000, 86_054_151
+    a = device_zipf_ids(n, N, 1.3, 7, 0, device=dev)
+    b = torch.cat([device_zipf_ids(n // 2, N, 1.3, 7, 0, device=dev), device_zipf_ids(n // 2, N, 1.3, 7, n // 2, device=dev)])
+    assert torch.equal(a, b) and int(a.min()) >= 0 and int(a.max()) < N
+    draw = _lib.lib().rs_gen_draw
+    u = np.array([draw(7, i) >> 11 for i in range(n)], dtype=np.float64) / 9007199254740992.0
+    ref = torch.from_numpy(zipf_from_uniform(u, N, 1.3))
+    assert (a.cpu() != ref).float().mean().item() < 1e-3                 # the last ulp of pow() may flip a floor
+    pa, pb = spread_permutation(N)
+    s = device_zipf_ids(n, N, 1.3, 7, 0, device=dev, spread=True).cpu()
+    assert torch.equal(s, torch.tensor([(int(k) * pa + pb) % N for k in a.cpu().tolist()]))
+    un = device_uniform_ids(200000, 1000, 3, 0, device=dev)
+    cnt = torch.bincount(un, minlength=1000).float()
+    assert int(un.min()) >= 0 and int(un.max()) < 1000 and (cnt - 200).abs().max().item() < 80      # ~5.6 sigma
+    # popularity: P(rank 0) = (2^-0.3 - 1) / ((N + 1)^-0.3 - 1) = 0.1885 for this N
+    top = (a == 0).float().mean().item()
+    assert 0.17 < top < 0.21
