@@ -192,7 +192,12 @@ class KGEModel:
         (rank of the positive among its chunk's negatives; general_models.py:464-513): MRR, MR, HITS@1/3/10."""
         ranks = []
         for corrupt_head in (False, True):
-            neg = torch.randint(0, self.cfg.n_entities, (self.nneg,), device=self.dev, generator=generator)
+            if generator is not None:
+                neg = torch.randint(0, self.cfg.n_entities, (self.nneg,), device=self.dev, generator=generator)
+            else:
+                from ..utils.data import device_uniform_ids
+                self._eval_draws = getattr(self, "_eval_draws", 0) + 1
+                neg = device_uniform_ids(self.nneg, self.cfg.n_entities, 0x5EED + self.cfg.seed, self._eval_draws * self.nneg, device=self.dev)
             pos, negs = self.score_batch(h_ids, r_ids, t_ids, neg, corrupt_head)
             ranks.append(1 + (negs >= pos.unsqueeze(1)).sum(1))
         r = torch.cat(ranks).float()
@@ -252,12 +257,17 @@ class KGSampler:
         self.h, self.r, self.t = (torch.from_numpy(x).to(device) for x in (h, r, t))
         self.cfg, self.dev, self.n = cfg, device, n_triples
         self.gen = torch.Generator(device=device).manual_seed(seed * 31 + rank)
+        self._seed = (seed * 31 + rank) * 2 + 1000003
         self.nneg = cfg.batch // cfg.neg_chunk_size * cfg.neg_sample_size
         self.step = 0
 
     def __next__(self):
-        idx = torch.randint(0, self.n, (self.cfg.batch,), device=self.dev, generator=self.gen)
-        neg = torch.randint(0, self.cfg.n_entities, (self.nneg,), device=self.dev, generator=self.gen)
+        # positives and negatives are drawn on the device from counter-based streams (csrc/ops/sampling.cu): no host
+        # generator state, the same stream whatever the launch shape
+        from ..utils.data import device_uniform_ids
+        c = self.step * (self.cfg.batch + self.nneg)
+        idx = device_uniform_ids(self.cfg.batch, self.n, self._seed, c, device=self.dev)
+        neg = device_uniform_ids(self.nneg, self.cfg.n_entities, self._seed + 1, c, device=self.dev)
         self.step += 1
         return self.h[idx], self.r[idx], self.t[idx], neg
 
