@@ -408,6 +408,7 @@ struct GatherFusedArgs {
   rs::HashTableView ht;
   long long range_c;                // > 0: this rank holds keys [me * range_c, (me + 1) * range_c), local row = key - me * range_c
   int push_rows;                    // 0: only resolve rows and record occurrences (a gradient exchange without a lookup)
+  int find_only;                    // hash mode: 1 = never insert; an absent key answers with a NaN in column 0 (then zeros)
   float init_scale;
   unsigned char* row_init;          // hash mode: 1 once a row holds its initial value (readers that come earlier compute it)
   unsigned long long* status;
@@ -434,10 +435,14 @@ __global__ void __launch_bounds__(128) shard_gather_fused_kernel(const GatherFus
       bool fresh = false;
       if (a.use_hash) {
         if (lane == 0) {
-          bool ins = false, full = false;
-          r = rs::ht_insert(a.ht, static_cast<unsigned long long>(k), &ins, &full);
-          if (full && a.status) atomicOr(a.status, (unsigned long long)RS_DEV_TABLE_FULL);
-          fresh = ins;
+          if (a.find_only) {
+            r = rs::ht_find(a.ht, static_cast<unsigned long long>(k));
+          } else {
+            bool ins = false, full = false;
+            r = rs::ht_insert(a.ht, static_cast<unsigned long long>(k), &ins, &full);
+            if (full && a.status) atomicOr(a.status, (unsigned long long)RS_DEV_TABLE_FULL);
+            fresh = ins;
+          }
         }
         r = __shfl_sync(0xffffffffu, r, 0);
         fresh = __shfl_sync(0xffffffffu, static_cast<int>(fresh), 0) != 0;
@@ -448,6 +453,7 @@ __global__ void __launch_bounds__(128) shard_gather_fused_kernel(const GatherFus
         if (!a.use_hash && lane == 0 && a.status) atomicOr(a.status, (unsigned long long)RS_DEV_OOB_ROW);
         r = -1;
       }
+      const bool absent = a.find_only && r < 0;
       if (lane == 0) {
         if (a.rowidx) a.rowidx[w] = r;
         if (a.occ_cursor && r >= 0) {
@@ -456,7 +462,7 @@ __global__ void __launch_bounds__(128) shard_gather_fused_kernel(const GatherFus
           a.occ_slot[q] = static_cast<int>(w);
         }
       }
-      if (!a.push_rows) continue;
+      if (!a.push_rows && !fresh) continue;      // (a key seen for the first time gets its initial row even when nothing is sent back)
       // A key that another warp inserted a moment ago may not hold its initial value yet: such a reader computes the same
       // value from the key instead of reading the row.
       bool by_formula = fresh;
@@ -475,7 +481,8 @@ __global__ void __launch_bounds__(128) shard_gather_fused_kernel(const GatherFus
             x = __ldcv(reinterpret_cast<const float4*>(a.cold_weight + (r - a.hot_rows) * a.D) + v);   // host tier, read in place
           }
         }
-        reinterpret_cast<float4*>(dst)[v] = x;
+        if (absent && v == 0) x.x = __int_as_float(0x7fc00000);   // "no such key"
+        if (a.push_rows) reinterpret_cast<float4*>(dst)[v] = x;
       }
       if (fresh) {
         __syncwarp();
@@ -573,6 +580,36 @@ __global__ void __launch_bounds__(128) shard_grads_fused_kernel(const GradsFused
   rs::flag_publish_when_grid_done(a.sig);
 }
 
+// Owner side of a PUT: after the value push has landed (CH wait inside), every recorded occurrence overwrites its row with
+// the value that arrived in its slot; the row counts as initialised from then on.
+struct ScatterArgs {
+  float* weight;
+  const long long* occ_row;
+  const int* occ_slot;
+  const int* occ_cursor;
+  const float* win;            // my value window [world, cap, D]
+  float* state;                // optional per-row optimizer state, reset for the rows that are put
+  unsigned char* row_init;     // optional (hash mode)
+  int D;
+  FlagWait wait;
+};
+__global__ void __launch_bounds__(128) shard_scatter_rows_kernel(const ScatterArgs a) {
+  rs::flag_wait_all(a.wait);
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const long long n = *reinterpret_cast<const volatile int*>(a.occ_cursor);
+  for (long long q = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); q < n; q += nwarps) {
+    const long long r = a.occ_row[q];
+    const long long s = a.occ_slot[q];
+    for (int v = lane; v < (a.D >> 2); v += 32)
+      reinterpret_cast<float4*>(a.weight + r * a.D)[v] = __ldcv(reinterpret_cast<const float4*>(a.win + s * a.D) + v);
+    if (lane == 0) {
+      if (a.state) a.state[r] = 0.f;
+      if (a.row_init) a.row_init[r] = 1;
+    }
+  }
+}
+
 int persistent_grid(long long items, int warps_per_block) {
   long long g = (items + warps_per_block - 1) / warps_per_block;
   const long long capg = 148 * 8;
@@ -621,7 +658,7 @@ RS_API int rs_shard_gather_fused(float* weight, const float* cold_weight, long l
                                  const long long* key_win, const int* count_win, void* const* row_win, long long* rowidx,
                                  long long* occ_row, int* occ_slot, int* occ_cursor, int world, int me, int D, long long cap,
                                  const rs::HashTableView* ht, float init_scale, unsigned char* row_init, long long range_c,
-                                 int push_rows, unsigned long long* status, const void* my_flags,
+                                 int push_rows, int find_only, unsigned long long* status, const void* my_flags,
                                  void* const* flags_of, unsigned* counters, unsigned* done, unsigned long long timeout_ns,
                                  int wait_channel, int sig_channel, cudaStream_t stream) {
   RS_REQUIRE((weight || hot_rows == 0) && key_win && count_win && row_win && D % 4 == 0, "rs_shard_gather_fused: bad argument");
@@ -635,7 +672,7 @@ RS_API int rs_shard_gather_fused(float* weight, const float* cold_weight, long l
   a.use_hash = ht != nullptr;
   if (ht) a.ht = *ht; else memset(&a.ht, 0, sizeof(a.ht));
   RS_REQUIRE(!ht || row_init, "rs_shard_gather_fused: the hash-table shard needs its row_init bytes");
-  a.init_scale = init_scale; a.row_init = row_init; a.status = status; a.range_c = range_c; a.push_rows = push_rows;
+  a.init_scale = init_scale; a.row_init = row_init; a.status = status; a.range_c = range_c; a.push_rows = push_rows; a.find_only = find_only;
   a.wait = make_wait(my_flags, counters, timeout_ns, wait_channel, world, status);
   a.sig = make_sig(flags_of, counters, done, sig_channel, world, me);
   shard_gather_fused_kernel<<<persistent_grid(cap, 4), 128, 0, stream>>>(a);
@@ -670,6 +707,20 @@ RS_API int rs_shard_grads_fused(const float* grad, const long long* slot, const 
   a.grad_win = reinterpret_cast<float* const*>(grad_win); a.norm = norm; a.norm_win = reinterpret_cast<float* const*>(norm_win);
   a.sig = make_sig(flags_of, counters, done, channel, world, me);
   shard_grads_fused_kernel<<<persistent_grid(n, 4), 128, 0, stream>>>(a);
+  RS_LAUNCH_CHECK();
+  return RS_OK;
+}
+
+RS_API int rs_shard_scatter_rows(float* weight, const long long* occ_row, const int* occ_slot, const int* occ_cursor, const float* win,
+                                 float* state, unsigned char* row_init, int D, long long cap_items, const void* my_flags,
+                                 const unsigned* counters, unsigned long long timeout_ns, int wait_channel, int world,
+                                 unsigned long long* status, cudaStream_t stream) {
+  RS_REQUIRE(weight && occ_row && occ_slot && occ_cursor && win && D % 4 == 0 && my_flags && counters, "rs_shard_scatter_rows: bad argument");
+  ScatterArgs a;
+  a.weight = weight; a.occ_row = occ_row; a.occ_slot = occ_slot; a.occ_cursor = occ_cursor; a.win = win; a.state = state;
+  a.row_init = row_init; a.D = D;
+  a.wait = make_wait(my_flags, counters, timeout_ns, wait_channel, world, status);
+  shard_scatter_rows_kernel<<<persistent_grid(cap_items, 4), 128, 0, stream>>>(a);
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

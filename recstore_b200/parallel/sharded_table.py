@@ -46,7 +46,9 @@ _lib.register_signatures({
     "rs_unique_keys": (i32, [vp, i64, vp, vp, _lib.u64, vp, vp, vp, vp, vp]),
     "rs_shard_keys_fused": (i32, [vp, vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, vp]),
     "rs_shard_gather_fused": (i32, [vp, vp, i64, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, C.POINTER(HashTableView), f32, vp,
-                                    i64, i32, vp, vp, vp, vp, vp, _lib.u64, i32, i32, vp]),
+                                    i64, i32, i32, vp, vp, vp, vp, vp, _lib.u64, i32, i32, vp]),
+    "rs_shard_scatter_rows": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i64, vp, vp, _lib.u64, i32, i32, vp, vp]),
+    "rs_ht_clear": (i32, [vp, vp]),
     "rs_shard_unbucket_fused": (i32, [vp, vp, vp, i64, i32, vp, i32, vp, vp, vp, vp, vp, i64, vp, vp, _lib.u64, i32, i32, vp, vp]),
     "rs_shard_grads_fused": (i32, [vp, vp, vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, vp, i32, i32, vp]),
     "rs_ht_create": (i32, [_lib.u64, i32, C.POINTER(vp), C.POINTER(HashTableView)]),
@@ -228,20 +230,63 @@ class ShardedEmbeddingTable:
         self.launches += 4
         return out
 
-    def _exchange_keys(self, keys, n, st, sp, push_rows: bool):
+    def _exchange_keys(self, keys, n, st, sp, push_rows: bool, find_only: bool = False, folded: Optional[bool] = None):
         """Keys to their owners (+ CH_KEYS), owner-side resolution into the compact occurrence list and, for a lookup, the
         rows back to the askers (+ CH_ROWS)."""
         c, gd = self.ctx, self._grid_done
+        folded = self.dedup if folded is None else folded
         self._occ_cursor.zero_()
-        _lib.call("rs_shard_keys_fused", ptr(keys), ptr(self._ucount) if self.dedup else None, n, self.world, self.rank, self.cap,
+        _lib.call("rs_shard_keys_fused", ptr(keys), ptr(self._ucount) if folded else None, n, self.world, self.rank, self.cap,
                   ptr(self._cursor), ptr(self.key_win.table), ptr(self.count_win.table), ptr(self._slot), ptr(st), self.range_c,
                   c.flags_table_ptr, c.counters_ptr, ptr(gd[0:1]), CH_KEYS, sp)
         _lib.call("rs_shard_gather_fused", ptr(self.weight), ptr(self.cold), self.hot_rows, self.local_rows, self.key_win.local_ptr,
                   self.count_win.local_ptr, ptr(self.row_win.table), ptr(self.rowidx) if self.tiered else None, ptr(self._occ_row),
                   ptr(self._occ_slot), ptr(self._occ_cursor), self.world, self.rank, self.D, self.cap,
                   C.byref(self._ht_view) if self.hashed else None, self.init_scale, ptr(self.row_init) if self.hashed else None,
-                  self.range_c, 1 if push_rows else 0, ptr(st), c.my_flags_ptr, c.flags_table_ptr, c.counters_ptr, ptr(gd[1:2]),
+                  self.range_c, 1 if push_rows else 0, 1 if find_only else 0, ptr(st), c.my_flags_ptr, c.flags_table_ptr,
+                  c.counters_ptr, ptr(gd[1:2]),
                   c.wait_timeout_ns, CH_KEYS, CH_ROWS, sp)
+
+    # ------------------------------------------------------------------ parameter-server verbs (hashed shards)
+    def get(self, ids: torch.Tensor):
+        """Rows of ``ids`` WITHOUT inserting: ``(rows, found)``; a key that was never put or looked up gives a zero row and
+        ``found = False``.  (The owner marks such a row with a NaN in column 0 on the wire.)"""
+        assert self.fused and not self.tiered
+        ids = ids.contiguous()
+        n = ids.numel()
+        assert n <= self.world * self.cap
+        st, sp = self.ctx.status, stream_ptr()
+        self._exchange_keys(ids, n, st, sp, push_rows=True, find_only=self.hashed, folded=False)
+        out = torch.empty(n, self.D, device=self.dev)
+        c = self.ctx
+        _lib.call("rs_shard_unbucket_fused", self.row_win.local_ptr, ptr(self._slot), None, n, self.D, ptr(out), 0, None, None, None,
+                  ptr(ids), None, 0, c.my_flags_ptr, c.counters_ptr, c.wait_timeout_ns, CH_ROWS, self.world, ptr(st), sp)
+        found = ~torch.isnan(out[:, 0])
+        out[~found] = 0
+        return out, found
+
+    def put(self, ids: torch.Tensor, values: torch.Tensor) -> None:
+        """Stores ``values[i]`` as the row of ``ids[i]`` on its owner (inserting the key if the shard is hashed); the row's
+        optimizer state starts over.  Keys of one call should be distinct (of two equal keys one wins)."""
+        assert self.fused and not self.tiered
+        ids, values = ids.contiguous(), values.contiguous()
+        n = ids.numel()
+        assert n <= self.world * self.cap and values.shape == (n, self.D) and values.dtype == torch.float32
+        st, sp, c = self.ctx.status, stream_ptr(), self.ctx
+        self._exchange_keys(ids, n, st, sp, push_rows=False, folded=False)
+        _lib.call("rs_shard_grads_fused", ptr(values), ptr(self._slot), None, n, self.D, self.rank, self.cap, ptr(self.grad_win.table),
+                  None, None, c.flags_table_ptr, c.counters_ptr, ptr(self._grid_done[2:3]), CH_GRADS, self.world, sp)
+        _lib.call("rs_shard_scatter_rows", ptr(self.weight), ptr(self._occ_row), ptr(self._occ_slot), ptr(self._occ_cursor),
+                  self.grad_win.local_ptr, ptr(self.state), ptr(self.row_init) if self.hashed else None, self.D, self.world * self.cap,
+                  c.my_flags_ptr, c.counters_ptr, c.wait_timeout_ns, CH_GRADS, self.world, ptr(st), sp)
+
+    def clear(self) -> None:
+        """Forgets every key of a hashed shard (rows and optimizer state start over)."""
+        assert self.hashed
+        _lib.call("rs_ht_clear", self._ht, stream_ptr())
+        self.row_init.zero_()
+        if self.state is not None:
+            self.state.zero_()
 
     def push_update(self, ids: torch.Tensor, grads: torch.Tensor) -> None:
         """A gradient exchange WITHOUT a preceding lookup: ``grads[i]`` is delivered to the owner of ``ids[i]`` and applied

@@ -361,3 +361,41 @@ def test_lookahead_cached_table_withheld_staging_and_undersized_cache(dev):
         small.check()
     assert "table_full" in str(e2.value)
     small.close()
+
+
+def test_nvlink_parameter_client_verbs_on_one_gpu(dev, tmp_path):
+    """The parameter-server verbs served by an HBM hash-table shard: absent keys read as zeros (and say so), put
+    overwrites, update applies SGD on the owner, stats count, a checkpoint round-trips.  Against a dict."""
+    from recstore_b200.parallel.peer import PeerContext
+    from recstore_b200.ps.gpu_client import NvlinkParameterClient
+    ctx = PeerContext(0, 1, device=dev)
+    D = 16
+    ps = NvlinkParameterClient(ctx, emb_dim=D, capacity=20000, max_batch=4096, lr=0.5, name="ps_test")
+    g = torch.Generator().manual_seed(3)
+    keys = torch.randperm(1 << 20, generator=g)[:3000] + (1 << 33)
+    vals = torch.randn(3000, D, generator=g)
+    rows, found = ps.GetParameterWithMask(keys[:100])
+    assert not found.any() and rows.abs().sum().item() == 0
+    ps.PutParameter(keys, vals)
+    rows, found = ps.GetParameterWithMask(torch.cat([keys[:500], keys[:5] + 1]))
+    assert found[:500].all() and not found[500:].any()
+    assert torch.equal(rows[:500].cpu(), vals[:500])
+    grads = torch.randn(1000, D, generator=g)
+    idx = torch.randint(0, 200, (1000,), generator=g)                      # duplicates: folded before they travel
+    ps.UpdateParameter(keys[idx], grads)
+    ref = vals.clone()
+    ref.index_add_(0, idx, -0.5 * grads)
+    got = ps.GetParameter(keys[:200]).cpu()
+    assert torch.allclose(got, ref[:200], atol=1e-5)
+    ps.PutParameter(keys[:10], torch.ones(10, D))                           # put overwrites
+    assert torch.equal(ps.GetParameter(keys[:10]).cpu(), torch.ones(10, D))
+    assert ps.Stats()["keys_stored"] == 3000
+    ps.SaveCkpt(str(tmp_path / "ps"))
+    ps.ClearPS()
+    assert ps.Stats()["keys_stored"] == 0 and not ps.GetParameterWithMask(keys[:50])[1].any()
+    ps.LoadCkpt(emb_file_path=str(tmp_path / "ps"))
+    assert ps.Stats()["keys_stored"] == 3000
+    assert torch.allclose(ps.GetParameter(keys[10:200]).cpu(), ref[10:200], atol=1e-5)
+    ps.LoadFakeData(1000)
+    assert torch.equal(ps.GetParameter(torch.tensor([5, 999]))[:, 0].cpu(), torch.tensor([5.0, 999.0]))
+    ctx.check_status()

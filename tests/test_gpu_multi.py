@@ -297,6 +297,55 @@ def test_cached_embeddings_on_the_native_plane_match_replicated_embedding(choice
     assert len(out) == 2 and all(v[0] == 25 and v[1] < 1e-3 for v in out.values()), out
 
 
+def _ps_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    try:
+        from recstore_b200.parallel.peer import PeerContext
+        from recstore_b200.ps.gpu_client import NvlinkParameterClient
+        ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"))
+        D = 16
+        ps = NvlinkParameterClient(ctx, emb_dim=D, capacity=40000, max_batch=4096, lr=0.5, name="ps_multi")
+        g = torch.Generator().manual_seed(5)
+        keys = torch.randperm(1 << 20, generator=g)[:4000] + (1 << 35)        # the same key set on every rank
+        vals = torch.randn(4000, D, generator=g)
+        mine = slice(rank, 4000, world)                                       # every rank puts ITS part; owners are key % world
+        ps.PutParameter(keys[mine], vals[mine])
+        ctx.barrier()
+        rows, found = ps.GetParameterWithMask(keys[:1500])                    # most of them put by, and stored on, other ranks
+        assert found.all() and torch.equal(rows.cpu(), vals[:1500]), rank
+        gg = torch.Generator().manual_seed(9 + rank)
+        idx = torch.randint(0, 300, (800,), generator=gg)
+        grads = torch.randn(800, D, generator=gg)
+        ps.UpdateParameter(keys[idx], grads)                                  # every rank updates overlapping keys
+        all_idx = [torch.empty_like(idx).cuda() for _ in range(world)]
+        all_g = [torch.empty_like(grads).cuda() for _ in range(world)]
+        dist.all_gather(all_idx, idx.cuda()); dist.all_gather(all_g, grads.cuda())
+        ref = vals.clone().cuda()
+        ref.index_add_(0, torch.cat(all_idx), -0.5 * torch.cat(all_g))
+        ctx.barrier()
+        got = ps.GetParameter(keys[:300])
+        assert torch.allclose(got, ref[:300], atol=1e-4), (rank, (got - ref[:300]).abs().max().item())
+        assert ps.Stats()["keys_stored"] == 4000
+        ctx.check_status()
+        dist.barrier()
+        out[rank] = "ok"
+    except BaseException as e:          # noqa: BLE001 - reported to the parent, then the process exits
+        _leave(dist, rank, out, e)
+    _leave(dist, rank, out, None)
+
+
+def test_nvlink_parameter_client_across_ranks():
+    """PS verbs served by HBM hash-table shards on two GPUs: keys put by one rank are read and updated by the other over
+    the peer windows; concurrent updates of the same keys from both ranks add up on the owner."""
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    out = mgr.dict()
+    _spawn(_ps_worker, (2, _free_port(), out), 2)
+    assert all(out.get(r) == "ok" for r in range(2)), dict(out)
+
+
 def test_kge_driver_two_gpus_native_path():
     """TransE-L2 on entity / relation tables sharded over two GPUs, through the training driver."""
     if _ngpus() < 2:
