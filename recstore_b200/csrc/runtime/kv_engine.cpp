@@ -754,7 +754,12 @@ KVConfig ParseKVConfig(const std::string& json) {
   return c;
 }
 
-std::vector<std::string> ListKVEngines() { return {"KVEngineMap", "KVEngineExtendibleHash", "KVEngineChunkHash"}; }
+std::unique_ptr<BaseKV> CreatePoolMapKV(const KVConfig& cfg);                       // kv_engine_pool.cpp
+bool PoolMapRecoveryState(BaseKV* kv, bool* recovered, uint64_t* dropped);
+
+std::vector<std::string> ListKVEngines() {
+  return {"KVEngineMap", "KVEngineExtendibleHash", "KVEngineChunkHash", "KVEnginePoolMap"};
+}
 
 std::unique_ptr<BaseKV> CreateKV(const std::string& engine, const KVConfig& cfg) {
   if (cfg.value_size == 0 || cfg.capacity == 0) {
@@ -770,6 +775,9 @@ std::unique_ptr<BaseKV> CreateKV(const std::string& engine, const KVConfig& cfg)
   } else if (engine == "KVEngineChunkHash" || engine == "KVEnginePetKV") {
     auto p = std::make_unique<KVEngineChunkHash>(cfg);
     if (p->ok()) return p;
+  } else if (engine == "KVEnginePoolMap") {
+    auto p = CreatePoolMapKV(cfg);
+    if (p) return p;
   } else {
     set_error(RS_ERR_NOTFOUND, "unknown KV engine %s", engine.c_str());
     return nullptr;
@@ -865,6 +873,13 @@ RS_API int rs_kv_recovery_state(void* h, int* recovered, int* clean) {
   if (auto* e = dynamic_cast<rs::KVEngineChunkHash*>(static_cast<BaseKV*>(h))) {
     *recovered = e->recovered() ? 1 : 0;
     *clean = e->was_clean() ? 1 : 0;
+    return RS_OK;
+  }
+  bool rec = false;
+  uint64_t dropped = 0;
+  if (rs::PoolMapRecoveryState(static_cast<BaseKV*>(h), &rec, &dropped)) {   // clean: nothing had to be dropped
+    *recovered = rec ? 1 : 0;
+    *clean = (rec && dropped == 0) ? 1 : 0;
     return RS_OK;
   }
   *recovered = 0;

@@ -8,11 +8,13 @@
 //   "KVEngineMap"            sharded unordered_map + reader/writer locks (engine_map.h:10-129)
 //   "KVEngineExtendibleHash" extendible hashing with bucket splits and directory doubling
 //                            (engine_extendiblehash.h:12-130, dram/src/extendible_hash.cpp)
+//   "KVEnginePoolMap"        sharded index over out-of-place sealed records in a crash-recoverable slab pool,
+//                            readers protected by epochs (kv_engine_pool.cpp, persist_pool.h)
 //   "KVEngineChunkHash"      14-slot tagged chunks with SSE2 tag matching and overflow counters,
 //                            16 shards, optional file-backed persistence with crash reload and
 //                            hot-key migration (role of PetHash / PetKV, nvm/pet_kv/pet_hash.h:
 //                            45-117, 154-249, 422-510)
-// All engines store values in a SlabValueStore (bump allocator + free list over an anonymous or
+// The first three engines store values in a SlabValueStore (bump allocator + free list over an anonymous or
 // file-backed mapping; role of PersistSimpleMalloc, src/memory/persist_malloc.h:26-124).
 #pragma once
 #include <cstdint>

@@ -1,0 +1,220 @@
+// "KVEnginePoolMap": a host KV engine whose values live in a PersistSlabPool and are replaced out of place.
+//
+// Every value is a sealed record {key, version, seal, bytes} in its own slab.  Put writes a NEW record, swings the
+// index entry over under the shard lock and retires the old record through the EpochManager; Get copies the value
+// outside the shard lock, inside a protected region, so readers never block writers for the length of a copy and never
+// see a torn value.  The index (64 sharded hash maps key -> slab offset) is volatile: on reopen it is rebuilt from
+// the allocated slabs of the pool, keeping the highest sealed version of each key and freeing unsealed (torn) or
+// superseded records.  The reference keeps values in its PersistMemoryPool and defers frees through its epoch manager
+// the same way in the persistent hash engines (src/memory/persist_malloc.h:126-420, src/memory/epoch_manager.h).
+#include <atomic>
+#include <cstring>
+#include <shared_mutex>
+#include <unordered_map>
+
+#include <sys/stat.h>
+
+#include "common/rs_common.h"
+#include "runtime/kv_engine.h"
+#include "runtime/persist_pool.h"
+
+namespace rs {
+
+namespace {
+
+struct Record {
+  uint64_t key;
+  uint64_t version;
+  std::atomic<uint64_t> seal;     // key ^ version ^ kSeal once the bytes are complete, 0 when unlinked
+  char bytes[1];
+};
+constexpr uint64_t kSeal = 0x9E3779B97F4A7C15ull;
+constexpr size_t kRecordHeader = 24;
+
+class KVEnginePoolMap final : public BaseKV {
+ public:
+  explicit KVEnginePoolMap(const KVConfig& c) : BaseKV(c), shards_(64) {
+    rec_bytes_ = kRecordHeader + c.value_size;
+    const uint64_t cs = PersistSlabPool::ClassSize(rec_bytes_);
+    uint64_t chunk = 2ull << 20;
+    while (chunk < cs * 4 + 4096) chunk <<= 1;
+    // room for every key plus the records that wait for their epoch, rounded up to whole chunks
+    const uint64_t per_chunk = (chunk - 4096) / cs;
+    const uint64_t chunks = (c.capacity + c.capacity / 4 + 64 + per_chunk - 1) / per_chunk + 1;
+    const std::string file = c.path.empty() ? std::string() : c.path + "/poolmap.slabs";
+    if (!c.path.empty()) mkdir(c.path.c_str(), 0755);
+    bool rec = false;
+    pool_ = PersistSlabPool::Open(file, chunks * chunk, chunk, &rec);
+    if (!pool_) return;
+    recovered_ = rec;
+    if (rec) Rebuild();
+  }
+  bool ok() const { return pool_ != nullptr; }
+  bool recovered() const { return recovered_; }
+  uint64_t dropped_on_recovery() const { return dropped_; }
+
+  bool Get(uint64_t key, void* out) override {
+    Shard& s = shard(key);
+    epoch_.Protect();
+    uint64_t off = 0;
+    {
+      std::shared_lock<std::shared_mutex> lk(s.mu);
+      auto it = s.map.find(key);
+      if (it != s.map.end()) off = it->second;
+    }
+    if (off) memcpy(out, rec(off)->bytes, cfg_.value_size);   // the record cannot be reused while we are protected
+    epoch_.Unprotect();
+    return off != 0;
+  }
+  bool Put(uint64_t key, const void* value) override {
+    uint64_t off = pool_->Malloc(rec_bytes_);
+    if (!off) {
+      epoch_.Bump();
+      epoch_.Collect();
+      off = pool_->Malloc(rec_bytes_);
+      if (!off) return false;
+    }
+    Record* r = rec(off);
+    r->key = key;
+    r->version = version_.fetch_add(1, std::memory_order_relaxed);
+    memcpy(r->bytes, value, cfg_.value_size);
+    r->seal.store(key ^ r->version ^ kSeal, std::memory_order_release);
+    Shard& s = shard(key);
+    uint64_t old = 0;
+    {
+      std::unique_lock<std::shared_mutex> lk(s.mu);
+      auto it = s.map.find(key);
+      if (it == s.map.end()) {
+        if (size_.load(std::memory_order_relaxed) >= cfg_.capacity) {
+          lk.unlock();
+          r->seal.store(0, std::memory_order_release);
+          pool_->Free(off);
+          return false;
+        }
+        s.map.emplace(key, off);
+        size_.fetch_add(1, std::memory_order_relaxed);
+      } else {
+        old = it->second;
+        it->second = off;
+      }
+    }
+    if (old) Unlink(old);
+    return true;
+  }
+  bool Erase(uint64_t key) override {
+    Shard& s = shard(key);
+    uint64_t old = 0;
+    {
+      std::unique_lock<std::shared_mutex> lk(s.mu);
+      auto it = s.map.find(key);
+      if (it == s.map.end()) return false;
+      old = it->second;
+      s.map.erase(it);
+      size_.fetch_sub(1, std::memory_order_relaxed);
+    }
+    Unlink(old);
+    return true;
+  }
+  void Clear() override {
+    for (Shard& s : shards_) s.mu.lock();
+    for (Shard& s : shards_) s.map.clear();
+    epoch_.DrainAll();
+    pool_->Reset();
+    size_.store(0);
+    for (Shard& s : shards_) s.mu.unlock();
+  }
+  uint64_t Size() const override { return size_.load(); }
+  std::string DebugInfo() const override {
+    const auto st = pool_->GetStats();
+    return "KVEnginePoolMap size=" + std::to_string(Size()) + " capacity=" + std::to_string(cfg_.capacity) +
+           " slabs=" + std::to_string(st.slabs_in_use) + " chunks=" + std::to_string(st.chunks_in_use) + "/" +
+           std::to_string(st.chunks_total) + " pending_frees=" + std::to_string(epoch_.Pending()) +
+           " epoch=" + std::to_string(epoch_.Current());
+  }
+  bool Persistent() const override { return !cfg_.path.empty(); }
+  void Flush() override {
+    epoch_.Bump();
+    epoch_.Collect();
+    pool_->Sync();
+  }
+  size_t Keys(uint64_t* out, size_t cap) const override {
+    size_t n = 0;
+    for (const Shard& s : shards_) {
+      std::shared_lock<std::shared_mutex> lk(s.mu);
+      for (auto& kv : s.map) {
+        if (n >= cap) return n;
+        out[n++] = kv.first;
+      }
+    }
+    return n;
+  }
+
+ private:
+  struct Shard {
+    mutable std::shared_mutex mu;
+    std::unordered_map<uint64_t, uint64_t> map;
+  };
+  Shard& shard(uint64_t key) { return shards_[hash64(key) & 63]; }
+  Record* rec(uint64_t off) const { return static_cast<Record*>(pool_->At(off)); }
+  // The record is out of the index: it must not come back after a crash, and its slab returns to the pool once no
+  // reader can still be copying from it.
+  void Unlink(uint64_t off) {
+    rec(off)->seal.store(0, std::memory_order_release);
+    PersistSlabPool* p = pool_.get();
+    epoch_.Retire([p, off] { p->Free(off); });
+  }
+  void Rebuild() {
+    const uint64_t want = PersistSlabPool::ClassSize(rec_bytes_);
+    std::vector<uint64_t> drop;
+    uint64_t max_version = 0;
+    pool_->ForEachAllocated([&](uint64_t off, uint64_t cs) {
+      Record* r = rec(off);
+      if (cs != want || r->seal.load(std::memory_order_acquire) != (r->key ^ r->version ^ kSeal)) {
+        drop.push_back(off);
+        return;
+      }
+      max_version = std::max(max_version, r->version);
+      auto& m = shard(r->key).map;
+      auto it = m.find(r->key);
+      if (it == m.end()) {
+        m.emplace(r->key, off);
+      } else if (rec(it->second)->version < r->version) {
+        drop.push_back(it->second);
+        it->second = off;
+      } else {
+        drop.push_back(off);
+      }
+    });
+    for (uint64_t off : drop) pool_->Free(off);
+    dropped_ = drop.size();
+    uint64_t n = 0;
+    for (Shard& s : shards_) n += s.map.size();
+    size_.store(n);
+    version_.store(max_version + 1);
+  }
+
+  std::vector<Shard> shards_;
+  std::unique_ptr<PersistSlabPool> pool_;
+  EpochManager epoch_;
+  std::atomic<uint64_t> size_{0}, version_{1};
+  uint64_t rec_bytes_ = 0, dropped_ = 0;
+  bool recovered_ = false;
+};
+
+}  // namespace
+
+std::unique_ptr<BaseKV> CreatePoolMapKV(const KVConfig& cfg) {
+  auto p = std::make_unique<KVEnginePoolMap>(cfg);
+  if (!p->ok()) return nullptr;
+  return p;
+}
+
+bool PoolMapRecoveryState(BaseKV* kv, bool* recovered, uint64_t* dropped) {
+  auto* e = dynamic_cast<KVEnginePoolMap*>(kv);
+  if (!e) return false;
+  *recovered = e->recovered();
+  *dropped = e->dropped_on_recovery();
+  return true;
+}
+
+}  // namespace rs

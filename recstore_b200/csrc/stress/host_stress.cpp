@@ -344,6 +344,7 @@ int main(int argc, char** argv) {
     stress_kv("KVEngineMap", "{\"capacity\": 65536, \"value_size\": 32}");
     stress_kv("KVEngineExtendibleHash", "{\"capacity\": 65536, \"value_size\": 32}");
     stress_kv("KVEngineChunkHash", "{\"capacity\": 65536, \"value_size\": 32}");
+    stress_kv("KVEnginePoolMap", "{\"capacity\": 65536, \"value_size\": 32}");
   }
   if (only == "all" || only == "ps") stress_ps();
   if (only == "all" || only == "alloc") {

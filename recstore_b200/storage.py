@@ -143,3 +143,136 @@ class BaseKV:
         r, c = i32(), i32()
         _lib.call("rs_kv_recovery_state", self._h, C.byref(r), C.byref(c))
         return bool(r.value), bool(c.value)
+
+
+_lib.register_signatures({
+    "rs_ppool_open": (i32, [cstr, u64, u64, C.POINTER(vp), C.POINTER(i32)]),
+    "rs_ppool_close": (i32, [vp]),
+    "rs_ppool_malloc": (u64, [vp, u64]),
+    "rs_ppool_free": (i32, [vp, u64]),
+    "rs_ppool_slab_size": (u64, [vp, u64]),
+    "rs_ppool_class_size": (u64, [u64]),
+    "rs_ppool_write": (i32, [vp, u64, vp, u64]),
+    "rs_ppool_read": (i32, [vp, u64, vp, u64]),
+    "rs_ppool_stats": (i32, [vp, vp]),
+    "rs_ppool_allocated": (i64, [vp, vp, i64]),
+    "rs_ppool_sync": (i32, [vp]),
+    "rs_epoch_new": (i32, [C.POINTER(vp)]),
+    "rs_epoch_delete": (i32, [vp]),
+    "rs_epoch_protect": (i32, [vp]),
+    "rs_epoch_unprotect": (i32, [vp]),
+    "rs_epoch_current": (u64, [vp]),
+    "rs_epoch_bump": (u64, [vp]),
+    "rs_epoch_safe": (i32, [vp, u64]),
+    "rs_epoch_retire_slab": (i32, [vp, vp, u64]),
+    "rs_epoch_collect": (i64, [vp]),
+    "rs_epoch_pending": (i64, [vp]),
+})
+
+
+class PersistSlabPool:
+    """Crash-recoverable slab allocator over one file (``path=None``: anonymous memory).  Allocations are byte offsets
+    into the mapping; after a reopen the bitmaps of the chunks say which slabs are live (``recovered`` is then True).
+    Native, see ``csrc/runtime/persist_pool.h``; role of the reference's PersistMemoryPool
+    (src/memory/persist_malloc.h:126-420)."""
+
+    def __init__(self, path: Optional[str], nbytes: int, chunk_bytes: int = 2 << 20):
+        self._l = _lib.lib()
+        h, rec = vp(), i32(0)
+        _lib.call("rs_ppool_open", (path or "").encode(), int(nbytes), int(chunk_bytes), C.byref(h), C.byref(rec))
+        self._h = h.value
+        self.recovered = bool(rec.value)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._l.rs_ppool_close(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def malloc(self, size: int) -> int:
+        """Offset of a slab of at least ``size`` bytes; 0 when the pool is exhausted."""
+        return int(self._l.rs_ppool_malloc(self._h, int(size)))
+
+    def free(self, off: int) -> None:
+        self._l.rs_ppool_free(self._h, int(off))
+
+    def slab_size(self, off: int) -> int:
+        return int(self._l.rs_ppool_slab_size(self._h, int(off)))
+
+    @staticmethod
+    def class_size(size: int) -> int:
+        return int(_lib.lib().rs_ppool_class_size(int(size)))
+
+    def write(self, off: int, data: bytes) -> None:
+        _lib.call("rs_ppool_write", self._h, int(off), C.c_char_p(data), len(data))
+
+    def read(self, off: int, n: int) -> bytes:
+        buf = C.create_string_buffer(n)
+        _lib.call("rs_ppool_read", self._h, int(off), buf, n)
+        return buf.raw
+
+    def allocated(self) -> List[int]:
+        n = int(self._l.rs_ppool_allocated(self._h, None, 0))
+        a = np.zeros(max(n, 1), dtype=np.uint64)
+        self._l.rs_ppool_allocated(self._h, a.ctypes.data, n)
+        return a[:n].tolist()
+
+    def stats(self) -> dict:
+        a = np.zeros(6, dtype=np.uint64)
+        self._l.rs_ppool_stats(self._h, a.ctypes.data)
+        names = ("chunk_bytes", "chunks_total", "chunks_in_use", "slabs_in_use", "bytes_in_use", "bytes_reserved")
+        return dict(zip(names, (int(x) for x in a)))
+
+    def sync(self) -> None:
+        self._l.rs_ppool_sync(self._h)
+
+
+class EpochManager:
+    """Epoch-based reclamation (``csrc/runtime/persist_pool.h``; role of src/memory/epoch_manager.h): readers bracket
+    their accesses with ``protect`` / ``unprotect`` (or ``with em:``), writers ``retire`` what they unlinked and it is
+    freed once no protected region that could still see it is left."""
+
+    def __init__(self):
+        self._l = _lib.lib()
+        h = vp()
+        _lib.call("rs_epoch_new", C.byref(h))
+        self._h = h.value
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._l.rs_epoch_delete(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def protect(self) -> None:
+        self._l.rs_epoch_protect(self._h)
+
+    def unprotect(self) -> None:
+        self._l.rs_epoch_unprotect(self._h)
+
+    def __enter__(self):
+        self.protect()
+        return self
+
+    def __exit__(self, *exc):
+        self.unprotect()
+
+    def current(self) -> int:
+        return int(self._l.rs_epoch_current(self._h))
+
+    def bump(self) -> int:
+        return int(self._l.rs_epoch_bump(self._h))
+
+    def safe_to_reclaim(self, epoch: int) -> bool:
+        return bool(self._l.rs_epoch_safe(self._h, int(epoch)))
+
+    def retire_slab(self, pool: PersistSlabPool, off: int) -> None:
+        _lib.call("rs_epoch_retire_slab", self._h, pool._h, int(off))
+
+    def collect(self) -> int:
+        return int(self._l.rs_epoch_collect(self._h))
+
+    def pending(self) -> int:
+        return int(self._l.rs_epoch_pending(self._h))

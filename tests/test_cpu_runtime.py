@@ -100,7 +100,7 @@ def test_zipf_native_matches_python_and_is_skewed():
     assert (ids == 1).mean() > 0.1                    # heavy head
 
 
-@pytest.mark.parametrize("engine", ["KVEngineMap", "KVEngineExtendibleHash", "KVEngineChunkHash"])
+@pytest.mark.parametrize("engine", ["KVEngineMap", "KVEngineExtendibleHash", "KVEngineChunkHash", "KVEnginePoolMap"])
 def test_kv_engine_put_get_mirror(engine):
     """Random put / get / erase against a Python dict mirror (the reference's client consistency test,
     src/grpc_ps/python_client/python_client_test.py:9-44, applied to every engine)."""
@@ -328,3 +328,153 @@ def test_foreign_or_damaged_shm_objects_are_refused():
             except OSError:
                 pass
         ipc.set_namespace(f"pytest{os.getpid()}")         # what the fixture of this file set
+
+
+def test_persist_slab_pool_allocates_frees_and_recovers(tmp_path):
+    """Slabs of mixed sizes keep their bytes, freed slabs are reused, empty chunks return to the pool, and a reopened file
+    has exactly the slabs that were live (the reference's PersistMemoryPool::Recovery, src/memory/persist_malloc.h)."""
+    from recstore_b200.storage import PersistSlabPool
+    path = str(tmp_path / "pool.bin")
+    P = PersistSlabPool(path, 64 * 65536, chunk_bytes=65536)
+    assert not P.recovered
+    assert [P.class_size(s) for s in (1, 16, 17, 256, 257, 300, 1000, 1025)] == [16, 16, 32, 256, 320, 320, 1024, 1280]
+    rng = np.random.default_rng(0)
+    live = {}
+    for i in range(3000):
+        size = int(rng.choice([8, 24, 100, 152, 700, 5000]))
+        off = P.malloc(size)
+        assert off != 0 and off not in live and P.slab_size(off) >= size
+        data = bytes([i % 251]) * size
+        P.write(off, data)
+        live[off] = data
+        if i % 3 == 0:
+            victim = list(live)[int(rng.integers(len(live)))]
+            P.free(victim)
+            assert P.slab_size(victim) == 0
+            P.free(victim)                                  # a double free is ignored
+            del live[victim]
+    st = P.stats()
+    assert st["slabs_in_use"] == len(live) and sorted(P.allocated()) == sorted(live)
+    assert st["bytes_in_use"] <= st["bytes_reserved"] <= 64 * 65536
+    for off, data in live.items():
+        assert P.read(off, len(data)) == data
+    with pytest.raises(Exception):
+        P.write(next(iter(live)), b"x" * 70000)            # larger than the slab
+    assert P.malloc(70000) == 0                            # larger than a chunk
+    # "crash": a second mapping of the file while the first is still open sees the same live set
+    Q = PersistSlabPool(path, 64 * 65536, chunk_bytes=65536)
+    assert Q.recovered and sorted(Q.allocated()) == sorted(live) and Q.stats()["slabs_in_use"] == len(live)
+    for off, data in list(live.items())[:200]:
+        assert Q.read(off, len(data)) == data
+    fresh = Q.malloc(152)
+    assert fresh != 0 and fresh not in live                 # the rebuilt free lists do not hand out a live slab
+    Q.free(fresh)
+    Q.close()
+    for off in list(live):
+        P.free(off)
+    assert P.stats()["slabs_in_use"] == 0 and P.stats()["chunks_in_use"] == 0
+    # exhaustion: 64 chunks of 65536 bytes hold fewer than 64 * 16 slabs of 5000 (class 5120) bytes
+    got = []
+    while True:
+        off = P.malloc(5000)
+        if off == 0:
+            break
+        got.append(off)
+    assert 64 * 11 <= len(got) <= 64 * 12 and len(set(got)) == len(got)
+    P.close()
+    R = PersistSlabPool(path, 64 * 65536, chunk_bytes=65536)
+    assert R.recovered and R.stats()["slabs_in_use"] == len(got)
+    R.close()
+    assert not PersistSlabPool(path, 32 * 65536, chunk_bytes=32768).recovered     # another geometry: formatted anew
+
+
+def test_epoch_manager_defers_frees_past_protected_regions():
+    """A retired slab stays allocated while a reader that could have seen it is inside a protected region, and goes back
+    to the pool afterwards (Protect / UnProtect / BumpCurrentEpoch / IsSafeToReclaim of src/memory/epoch_manager.h)."""
+    import threading
+    from recstore_b200.storage import EpochManager, PersistSlabPool
+    P, E = PersistSlabPool(None, 16 * 65536, chunk_bytes=65536), EpochManager()
+    e0 = E.current()
+    assert E.safe_to_reclaim(e0)                            # nobody is protected
+    inside, leave = threading.Event(), threading.Event()
+
+    def reader():
+        with E:
+            inside.set()
+            leave.wait(10)
+    t = threading.Thread(target=reader)
+    t.start()
+    assert inside.wait(10)
+    off = P.malloc(100)
+    E.retire_slab(P, off)                                   # unlinked at epoch e0, the reader published e0
+    assert not E.safe_to_reclaim(e0) and E.safe_to_reclaim(e0 - 1)
+    E.bump()
+    assert E.collect() == 0 and E.pending() == 1 and P.slab_size(off) != 0
+    with E:                                                 # a reader that starts after the bump does not hold it up
+        off2 = P.malloc(100)
+        E.retire_slab(P, off2)
+        assert E.collect() == 0                             # ... but protects what is unlinked during its own region
+    leave.set()
+    t.join()
+    assert E.collect() == 2 and E.pending() == 0 and P.slab_size(off) == 0 and P.slab_size(off2) == 0
+    with E:
+        with E:                                             # regions nest
+            pass
+        assert not E.safe_to_reclaim(E.current())
+    assert E.safe_to_reclaim(E.current())
+    E.close()
+    P.close()
+
+
+def test_pool_map_engine_concurrent_readers_never_see_torn_or_freed_values(tmp_path):
+    """Writers replace values out of place while readers copy them without the shard lock: every value a reader gets is
+    one complete version, superseded records return to the pool (bounded slab count), and a reopen after a 'crash' keeps
+    the newest sealed version of every key and forgets erased keys."""
+    import threading
+    from recstore_b200.storage import BaseKV
+    cfg = {"capacity": 4096, "value_size": 256, "path": str(tmp_path / "pm")}
+    kv = BaseKV("KVEnginePoolMap", cfg)
+    keys = torch.arange(2000)
+    kv.BatchPut(keys, torch.zeros(2000, 64))
+    stop, bad = threading.Event(), []
+
+    def writer(seed):
+        g = torch.Generator().manual_seed(seed)
+        v = 1
+        while not stop.is_set():
+            ks = torch.randint(0, 2000, (256,), generator=g)
+            kv.BatchPut(ks, torch.full((256, 64), float(seed * 100000 + v)))
+            v += 1
+
+    def reader(seed):
+        g = torch.Generator().manual_seed(100 + seed)
+        while not stop.is_set():
+            ks = torch.randint(0, 2000, (512,), generator=g)
+            got, found = kv.BatchGet(ks)
+            if not bool(found.all()) or not bool((got == got[:, :1]).all()):
+                bad.append((seed, got[(got != got[:, :1]).any(1)][:2]))
+                return
+    ts = [threading.Thread(target=writer, args=(i + 1,)) for i in range(2)] + [threading.Thread(target=reader, args=(i,)) for i in range(3)]
+    for t in ts:
+        t.start()
+    import time
+    time.sleep(1.5)
+    stop.set()
+    for t in ts:
+        t.join()
+    assert not bad, bad
+    info = kv.DebugInfo()
+    slabs = int(info.split("slabs=")[1].split()[0])
+    assert len(kv) == 2000 and 2000 <= slabs <= 2000 + 4096 // 4 + 64 + 300, info     # old versions were reclaimed
+    for k in range(0, 2000, 5):
+        kv.Erase(k)
+    final, _ = kv.BatchGet(keys)
+    kv2 = BaseKV("KVEnginePoolMap", cfg)                    # reopened while the first is still mapped: a crash image
+    rec, _clean = kv2.recovery_state()
+    assert rec and len(kv2) == 1600
+    got, found = kv2.BatchGet(keys)
+    exp = torch.ones(2000, dtype=torch.bool)
+    exp[::5] = False
+    assert torch.equal(found, exp) and torch.equal(got[found], final[found])
+    kv2.close()
+    kv.close()
