@@ -22,12 +22,20 @@ from ..ps import ParameterClient, ParameterServer
 from ..ps.load_generator import DatasetReplay, PoissonLoadGenerator, zipf_key_source
 
 
-def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, seconds, dataset=None, quiet=False):
+def make_client(host, port, dim, transport="tcp"):
+    """``tcp``: the native framed-socket client; ``grpc``: the reference's transport (``ps/grpc_transport.py``)."""
+    if transport == "grpc":
+        from ..ps.grpc_transport import GrpcParameterClient
+        return GrpcParameterClient(host, port, 0, dim)
+    return ParameterClient(host, port, 0, dim)
+
+
+def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, seconds, dataset=None, quiet=False, transport="tcp"):
     done = [0] * threads
     stop = threading.Event()
 
     def worker(t):
-        c = ParameterClient(host, port, 0, dim)
+        c = make_client(host, port, dim, transport)
         c.InitThread(window)
         src = iter(DatasetReplay(dataset)) if dataset else zipf_key_source(key_space, batch, alpha, seed=t + 1)
         inflight = []
@@ -103,22 +111,30 @@ def main(argv=None):
     ap.add_argument("--poisson-rate", type=float, default=0.0, help="open loop: requests per second (0 = closed loop)")
     ap.add_argument("--engine", default="KVEngineMap")
     ap.add_argument("--processes", type=int, default=1, help="closed loop: load-generator processes, each with --threads senders")
+    ap.add_argument("--transport", choices=["tcp", "grpc"], default="tcp", help="framed loopback sockets or gRPC (closed loop / poisson)")
     a = ap.parse_args(argv)
     srv = None
     host, port = a.host, a.port
     if host is None:
         srv = ParameterServer(a.engine, {"capacity": int(a.key_space * 1.5), "dim": a.dim})
         srv.LoadFakeData(a.key_space)
-        host, port = "127.0.0.1", srv.serve(0)
+        if a.transport == "grpc":
+            from ..ps.grpc_transport import GrpcParameterServer
+            gsrv = GrpcParameterServer(srv, 0, workers=max(8, a.threads * 2))
+            host, port = "127.0.0.1", gsrv.port
+        else:
+            host, port = "127.0.0.1", srv.serve(0)
     try:
         if a.poisson_rate > 0:
             src = iter(DatasetReplay(a.dataset)) if a.dataset else zipf_key_source(a.key_space, a.batch, a.alpha)
-            gen = PoissonLoadGenerator(lambda: ParameterClient(host, port, 0, a.dim), src, a.poisson_rate, senders=a.threads)
+            gen = PoissonLoadGenerator(lambda: make_client(host, port, a.dim, a.transport), src, a.poisson_rate, senders=a.threads)
             out = {"mode": "poisson", "rate": a.poisson_rate, **gen.run(a.seconds).summary()}
         elif a.processes > 1:
             out = multi_process(host, port, a.dim, a.processes, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset)
         else:
-            out = closed_loop(host, port, a.dim, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset)
+            out = closed_loop(host, port, a.dim, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset,
+                              transport=a.transport)
+        out["transport"] = a.transport
         print(json.dumps(out), flush=True)
     finally:
         if srv is not None:

@@ -128,6 +128,13 @@ class ParameterServer:
         _lib.call("rs_ps_get", self._h, k.data_ptr(), k.numel(), out.data_ptr(), None)
         return out
 
+    def GetParameterWithMask(self, keys) -> Tuple[torch.Tensor, torch.Tensor]:
+        k = _keys(keys)
+        out = torch.empty(k.numel(), self.dim)
+        found = torch.empty(k.numel(), dtype=torch.uint8)
+        _lib.call("rs_ps_get", self._h, k.data_ptr(), k.numel(), out.data_ptr(), found.data_ptr())
+        return out, found.bool()
+
     def UpdateParameter(self, keys, grads) -> int:
         k = _keys(keys); g = torch.as_tensor(grads, dtype=torch.float32).contiguous()
         a = i64()

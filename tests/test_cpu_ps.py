@@ -233,3 +233,68 @@ def test_checkpoint_loader_rejects_corrupt_files(tmp_path):
     assert len(ps3) == 100 and torch.equal(ps3.GetParameter(torch.arange(100)), ps.GetParameter(torch.arange(100)))
     with pytest.raises(_lib.RecStoreError):
         ps3.LoadCkpt(str(tmp_path / "missing.bin"))
+
+
+def test_grpc_transport_mirror_commands_and_wire_format(tmp_path):
+    """The parameter service over gRPC (the reference's transport, src/grpc_ps/proto/ps.proto): put / get / update
+    against a Python mirror over several sub-requests, the three commands, checkpoints, absent keys as zero rows with a
+    cleared mask, the asynchronous form, the sharded fan-out, and the raw wire layout of a request."""
+    import struct
+    import grpc
+    from recstore_b200.ps.client import AllShardsParameterClient, ParameterServer, unpack_records
+    from recstore_b200.ps import grpc_transport as gt
+    D = 16
+    ps = ParameterServer("KVEngineMap", {"dim": D, "capacity": 1 << 16, "optimizer": "sgd", "lr": 0.5})
+    srv = gt.GrpcParameterServer(ps)
+    cli = gt.GrpcParameterClient("127.0.0.1", srv.port, 0, D)
+    g = torch.Generator().manual_seed(0)
+    keys = torch.randperm(50000, generator=g)[:5000]                  # 3 sub-requests of MAX_PARAMETER_BATCH keys
+    vals = torch.randn(5000, D, generator=g)
+    assert cli.PutParameter(keys, vals)
+    assert torch.equal(cli.GetParameter(keys), vals) and len(ps) == 5000
+    q = torch.cat([keys[:10], torch.tensor([60001, 60002])])
+    rows, found = cli.GetParameterWithMask(q)
+    assert found.tolist() == [True] * 10 + [False] * 2 and rows[10:].abs().sum() == 0 and torch.equal(rows[:10], vals[:10])
+    grads = torch.ones(100, D)
+    assert cli.UpdateParameter(keys[:100], grads) == 100
+    assert torch.allclose(cli.GetParameter(keys[:100]), vals[:100] - 0.5)
+    rid = cli.GetParameterAsync(keys[200:2700])
+    cli.WaitRPCFinish(rid)
+    assert cli.QueryRPCFinished(rid) and torch.equal(cli.GetReceiveBuffer(rid), vals[200:2700])
+    cli.RevokeRPCResource(rid)
+    ck = str(tmp_path / "ps.ckpt")
+    assert cli.SaveCkpt(ck) and cli.ClearPS() and len(ps) == 0
+    assert cli.LoadCkpt(emb_file_path=[ck]) and len(ps) == 5000 and torch.equal(cli.GetParameter(keys[100:300]), vals[100:300])
+    assert cli.ClearPS() and cli.LoadFakeData(300)
+    assert torch.equal(cli.GetParameter(torch.arange(300))[:, 0], torch.arange(300).float())
+    st = cli.Stats()
+    assert st["keys_stored"] == 300 and st["requests"] > 10
+    # the bytes on the wire: field 1 = raw little-endian u64 keys; the answer is one packed record block
+    raw = cli._channel.unary_unary("/xmhps.ParameterService/GetParameter")(
+        b"\x0a\x10" + struct.pack("<2Q", 7, 999999), timeout=10)
+    assert raw[0] == 0x0a                                                   # GetParameterResponse.parameter_value
+    blob = gt.GetParameterResponse.FromString(raw).parameter_value
+    k, d, v = unpack_records(blob, D)
+    assert k.tolist() == [7, 999999] and d.tolist() == [D, 0] and v[0, 0] == 7.0
+    # malformed requests are refused, the server keeps serving
+    with pytest.raises(grpc.RpcError) as e:
+        cli._get(gt.GetParameterRequest(keys=b"12345"), timeout=10)
+    assert e.value.code() == grpc.StatusCode.INVALID_ARGUMENT
+    with pytest.raises(grpc.RpcError):
+        cli._put(gt.PutParameterRequest(parameter_value=b"\xff\xff\xff\x7f" + b"junk"), timeout=10)
+    with pytest.raises(grpc.RpcError):
+        cli.LoadCkpt(emb_file_path=str(tmp_path / "missing.ckpt"))
+    assert cli.GetParameter([5])[0, 0] == 5.0
+    # two shards behind the fan-out client
+    ps2 = ParameterServer("KVEngineChunkHash", {"dim": D, "capacity": 1 << 16})
+    srv2 = gt.GrpcParameterServer(ps2)
+    both = AllShardsParameterClient([cli, gt.GrpcParameterClient("127.0.0.1", srv2.port, 1, D)])
+    both.ClearPS()
+    both.PutParameter(keys, vals)
+    assert torch.equal(both.GetParameter(keys), vals) and len(ps) + len(ps2) == 5000 and min(len(ps), len(ps2)) > 2000
+    # a server that is gone is an error within the timeout, not a hang
+    srv2.stop(0)
+    dead = gt.GrpcParameterClient("127.0.0.1", srv2.port, 1, D, timeout_s=1.0)
+    with pytest.raises(grpc.RpcError):
+        dead.GetParameter([1, 2, 3])
+    srv.stop(0)

@@ -20,6 +20,12 @@ def _ngpus():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
+def _world(cap=8):
+    """Largest of 8 / 4 / 2 ranks that the box (and the test's cap) allows."""
+    n = min(_ngpus(), cap)
+    return 8 if n >= 8 else 4 if n >= 4 else 2
+
+
 def _init(rank, world, port):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -58,9 +64,9 @@ def _dlrm_worker(rank, world, port, graph, out, kind="dot", split=None):
         from recstore_b200.models.dlrm import DLRM, DLRMConfig
         from recstore_b200.parallel.peer import PeerContext
         from recstore_b200.utils.data import DLRMBatchSource
-        rows = [1000, 37, 5000, 12, 300, 20000, 64]
-        hot = [1, 2, 1, 3, 1, 1, 1] if split is None else [1, 2, 40, 3, 1, 1, 1]
-        B = 512
+        rows = [1000, 37, 5000, 12, 300, 20000, 64, 900]
+        hot = [1, 2, 1, 3, 1, 1, 1, 1] if split is None else [1, 2, 40, 3, 1, 1, 1, 1]
+        B = 512 if world <= 4 else 1024
         # The dot model is compared under row-wise Adagrad.  The interactions with more stacked GEMMs are compared under
         # plain SGD on the embeddings: Adagrad's normalised step (while a row's state is still tiny) would amplify the
         # fp32 summation-order noise of the all-reduce step over step, which says nothing about the exchange itself.
@@ -156,7 +162,7 @@ def test_dlrm_two_ranks_match_single(graph):
     if _ngpus() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
-    world = min(_ngpus(), 4) if _ngpus() in (2, 4) else 2
+    world = _world() if graph else _world(4)
     mgr = mp.Manager()
     out = mgr.dict()
     _spawn(_dlrm_worker, (world, _free_port(), graph, out), world)
@@ -183,7 +189,7 @@ def test_dlrm_row_sharded_tables_match_single(kind):
     if _ngpus() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
-    world = 4 if _ngpus() >= 4 else 2
+    world = _world() if kind == "dot" else _world(4)
     mgr = mp.Manager()
     out = mgr.dict()
     _spawn(_dlrm_worker, (world, _free_port(), True, out, kind, [2, 3, 5]), world)
@@ -276,7 +282,7 @@ def test_sharded_table_lookup_update_matches_replicated_oracle():
     if _ngpus() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
-    world = 4 if _ngpus() >= 4 else 2
+    world = _world()
     mgr = mp.Manager()
     out = mgr.dict()
     _spawn(_sharded_worker, (world, _free_port(), out), world)
