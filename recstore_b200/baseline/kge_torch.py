@@ -155,6 +155,55 @@ class TorchKGE:
         if self.proj is not None:
             self.state["proj"] = torch.zeros(n_relations, device=self.device)
         self.step_no = 0
+        self._async_q = None
+        self._async_thread = None
+        self._async_error: Optional[BaseException] = None
+
+    # Asynchronous entity update: the trainer hands (ids, gradients) of a step to a worker that applies the sparse
+    # Adagrad update while the next step already computes, so a step may read rows whose last update is still queued
+    # (the reference's --async_update: tensor_models.py:144-182 async_update, 433-447 create / finish).  Relations
+    # stay synchronous, as there.  The queue is bounded: a trainer that runs ahead of the updater blocks.
+    def create_async_update(self, max_pending: int = 4) -> None:
+        import queue
+        import threading
+        if self._async_thread is not None:
+            return
+        self._async_q = queue.Queue(maxsize=max_pending)
+
+        def run():
+            while True:
+                item = self._async_q.get()
+                if item is None:
+                    return
+                try:
+                    with torch.no_grad():
+                        ids, grads = item
+                        rowwise_adagrad_(self.entity, self.state["entity"], ids.to(self.device), grads.to(self.device), self.lr)
+                except BaseException as e:      # noqa: BLE001 - surfaces in the trainer at its next step / at finish
+                    self._async_error = e
+                    return
+                finally:
+                    self._async_q.task_done()
+        self._async_thread = threading.Thread(target=run, name="kge-async-update", daemon=True)
+        self._async_thread.start()
+
+    def wait_async_update(self) -> None:
+        """Blocks until every queued update has been applied (before evaluation or a checkpoint)."""
+        if self._async_thread is not None and self._async_error is None:
+            self._async_q.join()
+        if self._async_error is not None:
+            raise RuntimeError("asynchronous entity update failed") from self._async_error
+
+    def finish_async_update(self) -> None:
+        if self._async_thread is None:
+            return
+        try:
+            self.wait_async_update()
+        finally:
+            if self._async_thread.is_alive():
+                self._async_q.put(None)
+            self._async_thread.join(timeout=30)
+            self._async_thread, self._async_q = None, None
 
     def _rows(self, h_ids, r_ids, t_ids, neg_ids):
         rows = [self.entity[h_ids].clone().requires_grad_(True), self.relation[r_ids].clone().requires_grad_(True),
@@ -180,7 +229,12 @@ class TorchKGE:
         loss.backward()
         with torch.no_grad():
             ids = torch.cat([h_ids, t_ids, neg_ids])
-            rowwise_adagrad_(self.entity, self.state["entity"], ids, torch.cat([h.grad, t.grad, n.grad]), self.lr)
+            if self._async_thread is not None:
+                if self._async_error is not None:
+                    raise RuntimeError("asynchronous entity update failed") from self._async_error
+                self._async_q.put((ids.clone(), torch.cat([h.grad, t.grad, n.grad])))
+            else:
+                rowwise_adagrad_(self.entity, self.state["entity"], ids, torch.cat([h.grad, t.grad, n.grad]), self.lr)
             if r.grad is not None:      # RESCAL scores with the relation matrix only
                 rowwise_adagrad_(self.relation, self.state["relation"], r_ids, r.grad, self.lr)
             if p is not None:

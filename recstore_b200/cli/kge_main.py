@@ -92,7 +92,7 @@ def parse_args(argv=None):
     p.add_argument("--gpu", type=int, nargs="+", default=None, help="GPU ids: selects --device cuda and one worker per GPU")
     p.add_argument("--nr_gpus", type=int, default=None)
     p.add_argument("--mix_cpu_gpu", action="store_true", help="keep only the hot share (--cache_ratio) of the entity table in HBM")
-    p.add_argument("--async_update", action="store_true", help="accepted: the native step already overlaps the sparse update")
+    p.add_argument("--async_update", action="store_true", help="PyTorch path: a worker thread applies the entity updates behind the trainer; the native step already overlaps its sparse update")
     p.add_argument("--use_my_emb", type=lambda v: str(v).lower() in ("1", "true", "yes"), default=True,
                    help="RecStore embedding path (here: the native sharded tables); false = the PyTorch tables")
     p.add_argument("--cached_emb_type", default="KnownShardedCachedEmbedding")
@@ -208,9 +208,13 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
                          **_loss_kwargs(args))
         if shared is not None:           # one table for all CPU workers
             model.entity, model.relation, model.proj, model.state = shared["entity"], shared["relation"], shared.get("proj"), shared["state"]
+        if args.async_update:            # entity updates applied by a worker thread behind the trainer (train_pytorch.py:134-135)
+            model.create_async_update()
         step_fn = lambda h, r, t, n, ch: model.train_step(h, r, t, n, args.neg_chunk_size, ch, edge_weight=smp.last_weight)
     def run_eval(split, percent: float = 1.0):
         """Sampled-negative ranking metrics of (a share of) a split; native: every rank scores, else rank 0 only."""
+        if not native and args.async_update:
+            model.wait_async_update()
         n_eval = max(args.batch_size, int(min(split[0].size, args.batch_size_eval * 4) * percent))
         th, tr, tt = (torch.as_tensor(x[:n_eval]).to(dev) for x in split)
         g = torch.Generator(device=dev if native else "cpu").manual_seed(5)
@@ -260,6 +264,8 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
         if rank == 0 and (step + 1) % args.log_interval == 0:
             recent = [float(x) for x in losses[-args.log_interval:]]
             print(f"[{rank}] step {step + 1}: loss {np.mean(recent):.5f}, {(time.time() - t0) / (step + 1) * 1e3:.2f} ms/step", flush=True)
+    if not native and args.async_update:
+        model.finish_async_update()          # train_pytorch.py:338-339
     if args.device == "cuda":
         torch.cuda.synchronize()
     el = time.time() - t0

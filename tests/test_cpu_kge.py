@@ -390,3 +390,40 @@ def test_renumber_by_partition_aligns_ids_with_cyclic_sharding():
     skew = np.zeros(1001, dtype=np.int32); skew[:700] = 0; skew[700:] = 1          # one oversized part spills
     _, nid = K.renumber_by_partition(ds, skew, 2)
     assert np.array_equal(np.sort(nid), np.arange(1001)) and np.mean(nid[700:] % 2 == 1) == 1.0
+
+
+def test_async_entity_update_applies_every_gradient_and_reports_failures():
+    """--async_update: a worker thread applies the entity updates behind the trainer.  With batches that touch disjoint
+    rows the order of application cannot matter, so after finish_async_update() the tables equal the synchronous run's
+    bit for bit; a failing update surfaces in the trainer; the driver flag trains."""
+    from recstore_b200.baseline.kge_torch import TorchKGE
+    from recstore_b200.cli import kge_main
+    E, R, D, bs, ns = 4000, 7, 16, 32, 8
+    a = TorchKGE(E, R, D, "DistMult", seed=3)
+    b = TorchKGE(E, R, D, "DistMult", seed=3)
+    b.create_async_update(max_pending=2)
+    g = torch.Generator().manual_seed(1)
+    perm = torch.randperm(E, generator=g)
+    per = 2 * bs + ns * (bs // 8)                    # rows a step touches: heads, tails, chunked negatives
+    for s in range(20):
+        blk = perm[s * per:(s + 1) * per]
+        h, t, n = blk[:bs], blk[bs:2 * bs], blk[2 * bs:]
+        r = torch.randint(0, R, (bs,), generator=g)
+        la = a.train_step(h, r, t, n, 8, corrupt_head=bool(s & 1))
+        lb = b.train_step(h, r, t, n, 8, corrupt_head=bool(s & 1))
+        assert la == lb                               # disjoint rows: a queued update cannot change this step's inputs
+    b.finish_async_update()
+    assert torch.equal(a.entity, b.entity) and torch.equal(a.state["entity"], b.state["entity"])
+    assert torch.equal(a.relation, b.relation) and b._async_thread is None
+    b.finish_async_update()                           # idempotent
+    c = TorchKGE(E, R, D, "DistMult", seed=3)
+    c.create_async_update()
+    c.state["entity"] = torch.zeros(3)                # the worker's index_add_ goes out of range
+    blk = perm[-per:]
+    c.train_step(blk[:bs], torch.zeros(bs, dtype=torch.long), blk[bs:2 * bs], blk[2 * bs:], 8)
+    with pytest.raises(RuntimeError, match="asynchronous entity update failed"):
+        c.finish_async_update()
+    out, _ = kge_main.main(["--device", "cpu", "--model_name", "TransE_l2", "--max_step", "150", "--n_entities", "500",
+                            "--n_triples", "5000", "--hidden_dim", "32", "--batch_size", "128", "--neg_sample_size", "16",
+                            "--async_update", "--log_interval", "1000", "--gamma", "6"])
+    assert out[0]["last_loss"] < out[0]["first_loss"]
