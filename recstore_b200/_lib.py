@@ -142,7 +142,7 @@ def lib():
                 from . import build as _build
                 _build.build()
             path = str(_LIB_PATH)
-        l = C.CDLL(path, mode=C.RTLD_GLOBAL)
+        l = C.CDLL(path)       # RTLD_LOCAL: nothing of this library may interpose on other extension modules
         _apply(l, _SIGNATURES)
         _lib = l
     return _lib

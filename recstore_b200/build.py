@@ -193,9 +193,14 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False, job
     objs = [str(_obj_for(s)) for s in cu + cpp]
     relink = force or bool(tasks) or not LIB_PATH.exists()
     if relink:
+        # Only the C ABI (rs_*) is exported.  The C++ runtime may be linked in statically, and its symbols must not be
+        # visible to other extension modules of the process: a module loaded later would bind its iostream calls to
+        # this library's private copy, whose locale state that module never initialised.
+        vs = OBJ_DIR / "exports.map"
+        vs.write_text("{ global: rs_*; local: *; };\n")
         link = [cxx, "-shared", "-o", str(LIB_PATH)] + objs + [
             "-L", str(cuda / "lib64"), "-lcudart_static", "-lpthread", "-lrt", "-ldl",
-            "-Wl,-rpath," + str(cuda / "lib64")]
+            "-Wl,-rpath," + str(cuda / "lib64"), "-Wl,--version-script=" + str(vs), "-Wl,--exclude-libs,ALL"]
         if os.environ.get("RS_SANITIZE"):
             link += ["-fsanitize=" + os.environ["RS_SANITIZE"]]
         rc, out = _run(link, verbose)

@@ -17,13 +17,17 @@
 // followed by the payload.  The client splits a request into sub-requests of at most
 // max_keys_per_request keys (2000 upstream, grpc_ps_client.h:31), sends them back to back and then
 // collects the replies, which is the asynchronous window of the reference client.
+#include <algorithm>
 #include <atomic>
 #include <cerrno>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 #include <mutex>
+#include <string>
 #include <thread>
+#include <unordered_map>
 #include <vector>
 
 #include <arpa/inet.h>
@@ -36,6 +40,7 @@
 #include "runtime/base.h"
 #include "runtime/json_lite.h"
 #include "runtime/kv_engine.h"
+#include "runtime/task_provider.h"
 
 namespace rs {
 
@@ -222,7 +227,7 @@ class CachePS {
 
 // ---------------------------------------------------------------- framed TCP transport
 constexpr uint32_t kPsMagic = 0x52535053;  // "RSPS"
-enum PsOp : uint32_t { OP_GET = 1, OP_PUT = 2, OP_UPDATE = 3, OP_CLEAR = 4, OP_FAKE = 5, OP_SAVE = 6, OP_LOAD = 7, OP_STATS = 8, OP_BYE = 9 };
+enum PsOp : uint32_t { OP_GET = 1, OP_PUT = 2, OP_UPDATE = 3, OP_CLEAR = 4, OP_FAKE = 5, OP_SAVE = 6, OP_LOAD = 7, OP_STATS = 8, OP_BYE = 9, OP_PRIORITY = 10 };
 struct Frame { uint32_t magic, op; uint64_t len; };
 // A request larger than this (or naming more keys) is a protocol error: the connection is closed instead of sizing
 // buffers from a header that may be garbage.  Clients split their batches far below both (max_per_req).
@@ -252,9 +257,21 @@ static bool send_frame(int fd, uint32_t op, const void* payload, uint64_t len) {
   return send_all(fd, &f, sizeof(f)) && (len == 0 || send_all(fd, payload, len));
 }
 
+// Two serving modes.  workers == 0: every connection's thread reads a request, executes it and answers (the reference's
+// synchronous server, src/grpc_ps/grpc_ps_server.cpp:35-118).  workers > 0: the connection threads are only the front
+// end; requests go through a TaskProvider (FIFO or priority levels, keyed by connection) to a pool of worker threads,
+// and a per-connection sequencer sends the answers in request order, because clients pipeline their sub-requests
+// (the reference's asynchronous server: completion queue -> task queue -> worker coroutines,
+// src/grpc_ps/grpc_ps_server_async.cpp:56-96, 246-318).  OP_PRIORITY raises the sender's class by one level.
 class PsServer {
  public:
-  PsServer(CachePS* ps, int port) : ps_(ps), port_(port) {}
+  PsServer(CachePS* ps, int port, int workers = 0, const std::string& scheduler = "fifo", int levels = 7)
+      : ps_(ps), port_(port), n_workers_(workers < 0 ? 0 : workers) {
+    if (n_workers_ > 0) {
+      if (scheduler == "priority") provider_ = std::make_unique<PriorityProvider<Task>>(levels);
+      else provider_ = std::make_unique<FifoProvider<Task>>();
+    }
+  }
   ~PsServer() { Stop(); }
   int Start() {
     lfd_ = ::socket(AF_INET, SOCK_STREAM, 0);
@@ -274,6 +291,7 @@ class PsServer {
     getsockname(lfd_, reinterpret_cast<sockaddr*>(&a), &sl);
     port_ = ntohs(a.sin_port);
     running_ = true;
+    for (int i = 0; i < n_workers_; ++i) pool_.emplace_back([this] { WorkerLoop(); });
     acceptor_ = std::thread([this] { AcceptLoop(); });
     return RS_OK;
   }
@@ -289,13 +307,32 @@ class PsServer {
       ws.swap(workers_);
     }
     for (auto& t : ws) t.join();
+    if (provider_) provider_->Close();
+    for (auto& t : pool_) t.join();
+    pool_.clear();
   }
   int port() const { return port_; }
   uint64_t requests() const { return requests_.load(); }
   uint64_t keys_served() const { return keys_.load(); }
+  uint64_t pooled_requests() const { return pooled_.load(); }
 
  private:
+  struct Conn {
+    int fd;
+    uint64_t id;
+    std::mutex mu;                               // sequencer state and the socket's send side
+    uint64_t next_send = 0;
+    std::unordered_map<uint64_t, std::pair<uint32_t, std::vector<char>>> ready;
+    bool dead = false;
+  };
+  struct Task {
+    std::shared_ptr<Conn> conn;
+    uint64_t seq = 0;
+    Frame f{};
+    std::vector<char> in;
+  };
   void AcceptLoop() {
+    uint64_t next_id = 1;
     while (running_) {
       const int fd = ::accept(lfd_, nullptr, nullptr);
       if (fd < 0) { if (!running_) break; continue; }
@@ -303,83 +340,171 @@ class PsServer {
       setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
       std::lock_guard<std::mutex> lk(mu_);
       conns_.push_back(fd);
-      workers_.emplace_back([this, fd] { Serve(fd); });
+      const uint64_t id = next_id++;
+      workers_.emplace_back([this, fd, id] { Serve(fd, id); });
     }
   }
-  void Serve(int fd) {
+  void Serve(int fd, uint64_t id) {
+    auto conn = std::make_shared<Conn>();
+    conn->fd = fd;
+    conn->id = id;
     try {
-      ServeLoop(fd);
+      ServeLoop(conn);
     } catch (const std::exception&) {
       // e.g. std::bad_alloc on a hostile size: this connection ends, the server and its other connections go on
     }
-    ::close(fd);
+    {
+      // The descriptor leaves the server's list before it is closed (Stop() shuts down what is listed, and a closed
+      // number may already belong to somebody else's socket), and it is closed under the connection's lock so that no
+      // worker sends on a reused number.  Answers that workers still hold for this connection are dropped.
+      std::lock_guard<std::mutex> sl(mu_);
+      std::lock_guard<std::mutex> lk(conn->mu);
+      conns_.erase(std::remove(conns_.begin(), conns_.end(), fd), conns_.end());
+      conn->dead = true;
+      ::close(fd);
+    }
   }
-  void ServeLoop(int fd) {
-    std::vector<char> in;
+  // Executes one request.  False: protocol error, the connection must end.
+  bool Process(const Frame& f, std::vector<char>& in, uint32_t* rop, std::vector<char>* reply) {
     const int dim = ps_->dim();
+    *rop = f.op;
+    auto put8 = [&](uint64_t v) {
+      reply->resize(8);
+      memcpy(reply->data(), &v, 8);
+    };
+    if (f.op == OP_GET) {
+      const size_t n = f.len / 8;
+      if (f.len % 8 != 0 || n > kMaxKeysPerRequest) return false;
+      const uint64_t* keys = reinterpret_cast<const uint64_t*>(in.data());
+      std::vector<float> vals(n * dim);
+      std::vector<uint8_t> found(n);
+      ps_->Get(keys, n, vals.data(), found.data());
+      WireWriter w(static_cast<int>(n));
+      for (size_t i = 0; i < n; ++i) w.add(static_cast<int>(i), keys[i], found[i] ? dim : 0, vals.data() + i * dim);
+      keys_.fetch_add(n, std::memory_order_relaxed);
+      reply->assign(w.buf.begin(), w.buf.end());
+    } else if (f.op == OP_PUT || f.op == OP_UPDATE) {
+      WireReader r(in.data(), f.len);
+      uint64_t done = 0;
+      if (r.ok && static_cast<size_t>(r.n) <= kMaxKeysPerRequest) {
+        std::vector<uint64_t> keys;
+        std::vector<float> vals;
+        for (int i = 0; i < r.n; ++i) {
+          uint64_t key; int d; const float* emb;
+          if (!r.item(i, &key, &d, &emb) || d != dim) continue;
+          keys.push_back(key);
+          vals.insert(vals.end(), emb, emb + dim);
+        }
+        if (f.op == OP_PUT) { ps_->Put(keys.data(), keys.size(), vals.data()); done = keys.size(); }
+        else done = ps_->Update(keys.data(), keys.size(), vals.data());
+        keys_.fetch_add(keys.size(), std::memory_order_relaxed);
+      }
+      put8(done);
+    } else if (f.op == OP_CLEAR) {
+      ps_->Clear();
+      put8(1);
+    } else if (f.op == OP_FAKE) {
+      uint64_t n = 0;
+      if (f.len >= 8) memcpy(&n, in.data(), 8);
+      ps_->LoadFakeData(n);
+      put8(n);
+    } else if (f.op == OP_SAVE || f.op == OP_LOAD) {
+      const std::string path(in.data(), in.size());
+      put8(f.op == OP_SAVE ? ps_->SaveCkpt(path) : ps_->LoadCkpt(path));
+    } else if (f.op == OP_STATS) {
+      uint64_t s[4] = {ps_->kv()->Size(), requests_.load(), keys_.load(), pooled_.load()};
+      reply->resize(sizeof(s));
+      memcpy(reply->data(), s, sizeof(s));
+    } else {
+      return false;
+    }
+    return true;
+  }
+  void ServeLoop(const std::shared_ptr<Conn>& conn) {
+    const int fd = conn->fd;
+    std::vector<char> in, reply;
+    uint64_t seq = 0;
     while (running_) {
       Frame f;
       if (!recv_all(fd, &f, sizeof(f)) || f.magic != kPsMagic || f.len > kMaxFrameBytes) break;
       in.resize(f.len);
       if (f.len && !recv_all(fd, in.data(), f.len)) break;
       requests_.fetch_add(1, std::memory_order_relaxed);
-      if (f.op == OP_GET) {
-        const size_t n = f.len / 8;
-        if (f.len % 8 != 0 || n > kMaxKeysPerRequest) break;
-        const uint64_t* keys = reinterpret_cast<const uint64_t*>(in.data());
-        std::vector<float> vals(n * dim);
-        std::vector<uint8_t> found(n);
-        ps_->Get(keys, n, vals.data(), found.data());
-        WireWriter w(static_cast<int>(n));
-        for (size_t i = 0; i < n; ++i) w.add(static_cast<int>(i), keys[i], found[i] ? dim : 0, vals.data() + i * dim);
-        keys_.fetch_add(n, std::memory_order_relaxed);
-        if (!send_frame(fd, OP_GET, w.buf.data(), w.buf.size())) break;
-      } else if (f.op == OP_PUT || f.op == OP_UPDATE) {
-        WireReader r(in.data(), f.len);
-        uint64_t done = 0;
-        if (r.ok && static_cast<size_t>(r.n) <= kMaxKeysPerRequest) {
-          std::vector<uint64_t> keys;
-          std::vector<float> vals;
-          for (int i = 0; i < r.n; ++i) {
-            uint64_t key; int d; const float* emb;
-            if (!r.item(i, &key, &d, &emb) || d != dim) continue;
-            keys.push_back(key);
-            vals.insert(vals.end(), emb, emb + dim);
-          }
-          if (f.op == OP_PUT) { ps_->Put(keys.data(), keys.size(), vals.data()); done = keys.size(); }
-          else done = ps_->Update(keys.data(), keys.size(), vals.data());
-          keys_.fetch_add(keys.size(), std::memory_order_relaxed);
+      if (f.op == OP_PRIORITY) {                       // answered by the front end; travels through the sequencer
+        uint64_t level = 1;
+        if (provider_) {
+          provider_->ImprovePriority(conn->id);
+          level = static_cast<uint64_t>(provider_->LevelOf(conn->id));
         }
-        if (!send_frame(fd, f.op, &done, 8)) break;
-      } else if (f.op == OP_CLEAR) {
-        ps_->Clear();
-        uint64_t ok = 1;
-        if (!send_frame(fd, f.op, &ok, 8)) break;
-      } else if (f.op == OP_FAKE) {
-        uint64_t n = 0;
-        if (f.len >= 8) memcpy(&n, in.data(), 8);
-        ps_->LoadFakeData(n);
-        if (!send_frame(fd, f.op, &n, 8)) break;
-      } else if (f.op == OP_SAVE || f.op == OP_LOAD) {
-        const std::string path(in.data(), in.size());
-        uint64_t rc = f.op == OP_SAVE ? ps_->SaveCkpt(path) : ps_->LoadCkpt(path);
-        if (!send_frame(fd, f.op, &rc, 8)) break;
-      } else if (f.op == OP_STATS) {
-        uint64_t s[3] = {ps_->kv()->Size(), requests_.load(), keys_.load()};
-        if (!send_frame(fd, f.op, s, sizeof(s))) break;
+        std::vector<char> r(8);
+        memcpy(r.data(), &level, 8);
+        if (!Deliver(conn, seq++, f.op, std::move(r))) break;
+        continue;
+      }
+      if (!provider_) {
+        uint32_t rop;
+        reply.clear();
+        if (!Process(f, in, &rop, &reply)) break;
+        if (!send_frame(fd, rop, reply.data(), reply.size())) break;
+        continue;
+      }
+      if (f.op < OP_GET || f.op > OP_STATS) break;     // unknown verbs end the connection here, not in a worker
+      Task t;
+      t.conn = conn;
+      t.seq = seq++;
+      t.f = f;
+      t.in.swap(in);
+      provider_->Put(std::move(t), conn->id);
+    }
+  }
+  void WorkerLoop() {
+    Task t;
+    while (provider_->Get(&t)) {
+      uint32_t rop = t.f.op;
+      std::vector<char> reply;
+      bool ok = false;
+      try {
+        ok = Process(t.f, t.in, &rop, &reply);
+      } catch (const std::exception&) {
+        ok = false;
+      }
+      pooled_.fetch_add(1, std::memory_order_relaxed);
+      if (!ok) {
+        std::lock_guard<std::mutex> lk(t.conn->mu);
+        if (!t.conn->dead) ::shutdown(t.conn->fd, SHUT_RDWR);   // its reader thread sees the end and closes
       } else {
-        break;
+        Deliver(t.conn, t.seq, rop, std::move(reply));
+      }
+      t = Task();
+    }
+  }
+  // Sends the answer of request `seq` once every earlier answer of the connection has gone out.
+  bool Deliver(const std::shared_ptr<Conn>& c, uint64_t seq, uint32_t op, std::vector<char> reply) {
+    std::lock_guard<std::mutex> lk(c->mu);
+    if (c->dead) return false;
+    c->ready.emplace(seq, std::make_pair(op, std::move(reply)));
+    while (true) {
+      auto it = c->ready.find(c->next_send);
+      if (it == c->ready.end()) return true;
+      const bool sent = send_frame(c->fd, it->second.first, it->second.second.data(), it->second.second.size());
+      c->ready.erase(it);
+      ++c->next_send;
+      if (!sent) {
+        ::shutdown(c->fd, SHUT_RDWR);
+        return false;
       }
     }
   }
   CachePS* ps_;
   int port_, lfd_ = -1;
+  const int n_workers_;
+  std::unique_ptr<TaskProvider<Task>> provider_;
   std::atomic<bool> running_{false};
   std::thread acceptor_;
   std::mutex mu_;
   std::vector<int> conns_;
-  std::vector<std::thread> workers_;
-  std::atomic<uint64_t> requests_{0}, keys_{0};
+  std::vector<std::thread> workers_, pool_;
+  std::atomic<uint64_t> requests_{0}, keys_{0}, pooled_{0};
 };
 
 class PsClient {
@@ -544,6 +669,20 @@ RS_API int rs_ps_server_start(void* ps, int port, void** server_out, int* port_o
   if (port_out) *port_out = s->port();
   return RS_OK;
 }
+// workers > 0: front-end threads + a worker pool behind a "fifo" or "priority" task provider.
+RS_API int rs_ps_server_start_pool(void* ps, int port, int workers, const char* scheduler, int levels, void** server_out, int* port_out) {
+  RS_REQUIRE(ps && server_out, "rs_ps_server_start_pool: null argument");
+  const std::string sched = scheduler ? scheduler : "fifo";
+  RS_REQUIRE(sched == "fifo" || sched == "priority", "rs_ps_server_start_pool: scheduler must be fifo or priority");
+  RS_NOEXCEPT_BODY(
+    auto* s = new PsServer(static_cast<CachePS*>(ps), port, workers, sched, levels);
+    const int rc = s->Start();
+    if (rc != RS_OK) { delete s; return rc; }
+    *server_out = s;
+    if (port_out) *port_out = s->port();
+    return RS_OK;
+  )
+}
 RS_API int rs_ps_server_stop(void* server) { delete static_cast<PsServer*>(server); return RS_OK; }
 
 RS_API int rs_ps_client_connect(const char* host, int port, void** out) {
@@ -573,9 +712,36 @@ RS_API int rs_ps_client_update(void* c, const unsigned long long* keys, long lon
   return rc;
 }
 // op: 4 clear, 5 load fake data (arg = n), 6 save (path), 7 load (path), 8 stats (reply: size, requests, keys)
-RS_API int rs_ps_client_command(void* c, int op, const void* payload, long long len, unsigned long long* reply3) {
-  unsigned long long tmp[3] = {0, 0, 0};
+// reply4: up to four 64-bit words of the server's answer (unused words are zero).
+RS_API int rs_ps_client_command(void* c, int op, const void* payload, long long len, unsigned long long* reply4) {
+  unsigned long long tmp[4] = {0, 0, 0, 0};
   const int rc = static_cast<PsClient*>(c)->Command(static_cast<uint32_t>(op), payload, static_cast<size_t>(len), tmp, sizeof(tmp));
-  if (reply3) memcpy(reply3, tmp, sizeof(tmp));
+  if (reply4) memcpy(reply4, tmp, sizeof(tmp));
   return rc;
 }
+
+// Stand-alone task providers over integer task ids (the schedulers can be exercised without sockets).
+RS_API int rs_provider_new(const char* kind, int levels, unsigned long long seed, void** out) {
+  RS_REQUIRE(kind && out, "rs_provider_new: null argument");
+  RS_NOEXCEPT_BODY(
+    const std::string k = kind;
+    if (k == "fifo") *out = static_cast<rs::TaskProvider<long long>*>(new rs::FifoProvider<long long>());
+    else if (k == "priority") *out = static_cast<rs::TaskProvider<long long>*>(new rs::PriorityProvider<long long>(levels, seed));
+    else return rs::set_error(RS_ERR_INVALID, "rs_provider_new: kind must be fifo or priority");
+    return RS_OK;
+  )
+}
+RS_API int rs_provider_delete(void* p) { delete static_cast<rs::TaskProvider<long long>*>(p); return RS_OK; }
+RS_API int rs_provider_put(void* p, long long task, unsigned long long klass) {
+  RS_NOEXCEPT_BODY(static_cast<rs::TaskProvider<long long>*>(p)->Put(task, klass); return RS_OK;)
+}
+// Returns the next task id, or -1 when nothing is queued.
+RS_API long long rs_provider_try_get(void* p) {
+  long long t = -1;
+  return static_cast<rs::TaskProvider<long long>*>(p)->TryGet(&t) ? t : -1;
+}
+RS_API long long rs_provider_left(void* p) { return static_cast<long long>(static_cast<rs::TaskProvider<long long>*>(p)->Left()); }
+RS_API int rs_provider_improve(void* p, unsigned long long klass) {
+  RS_NOEXCEPT_BODY(static_cast<rs::TaskProvider<long long>*>(p)->ImprovePriority(klass); return RS_OK;)
+}
+RS_API int rs_provider_level(void* p, unsigned long long klass) { return static_cast<rs::TaskProvider<long long>*>(p)->LevelOf(klass); }

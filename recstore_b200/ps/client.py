@@ -45,6 +45,7 @@ _lib.register_signatures({
     "rs_ps_save": (i32, [vp, cstr]),
     "rs_ps_load": (i32, [vp, cstr]),
     "rs_ps_server_start": (i32, [vp, i32, C.POINTER(vp), C.POINTER(i32)]),
+    "rs_ps_server_start_pool": (i32, [vp, i32, i32, cstr, i32, C.POINTER(vp), C.POINTER(i32)]),
     "rs_ps_server_stop": (i32, [vp]),
     "rs_ps_client_connect": (i32, [cstr, i32, C.POINTER(vp)]),
     "rs_ps_client_close": (i32, [vp]),
@@ -54,8 +55,18 @@ _lib.register_signatures({
     "rs_ps_client_command": (i32, [vp, i32, vp, i64, C.POINTER(u64)]),
 })
 
+_lib.register_signatures({
+    "rs_provider_new": (i32, [cstr, i32, u64, C.POINTER(vp)]),
+    "rs_provider_delete": (i32, [vp]),
+    "rs_provider_put": (i32, [vp, i64, u64]),
+    "rs_provider_try_get": (i64, [vp]),
+    "rs_provider_left": (i64, [vp]),
+    "rs_provider_improve": (i32, [vp, u64]),
+    "rs_provider_level": (i32, [vp, u64]),
+})
+
 MAX_PARAMETER_BATCH = 2000
-OP_CLEAR, OP_FAKE, OP_SAVE, OP_LOAD, OP_STATS = 4, 5, 6, 7, 8
+OP_CLEAR, OP_FAKE, OP_SAVE, OP_LOAD, OP_STATS, OP_PRIORITY = 4, 5, 6, 7, 8, 10
 
 
 def _keys(keys) -> torch.Tensor:
@@ -87,6 +98,44 @@ def unpack_records(buf: bytes, dim: int) -> Tuple[torch.Tensor, torch.Tensor, to
     v = torch.empty(n, dim, dtype=torch.float32)
     _lib.call("rs_wire_unpack", buf, len(buf), dim, k.data_ptr(), d.data_ptr(), v.data_ptr())
     return k, d, v
+
+
+class TaskProvider:
+    """The server's task schedulers on their own (``csrc/runtime/task_provider.h``): ``"fifo"``, or ``"priority"``
+    with ``levels`` lists where the next task comes from level i with probability proportional to i x (tasks waiting
+    at level i) and ``ImprovePriority(klass)`` raises a class by one level (src/grpc_ps/provider.h:13-201)."""
+
+    def __init__(self, kind: str = "fifo", levels: int = 7, seed: int = 1):
+        self._l = _lib.lib()
+        h = vp()
+        _lib.call("rs_provider_new", kind.encode(), int(levels), int(seed), C.byref(h))
+        self._h = h.value
+
+    def PutTask(self, task: int, klass: int = 0) -> None:
+        _lib.call("rs_provider_put", self._h, int(task), int(klass))
+
+    def GetTask(self) -> Optional[int]:
+        t = int(self._l.rs_provider_try_get(self._h))
+        return None if t < 0 else t
+
+    def ExistTask(self) -> bool:
+        return self.LeftTask() > 0
+
+    def LeftTask(self) -> int:
+        return int(self._l.rs_provider_left(self._h))
+
+    def ImprovePriority(self, klass: int) -> None:
+        _lib.call("rs_provider_improve", self._h, int(klass))
+
+    def LevelOf(self, klass: int) -> int:
+        return int(self._l.rs_provider_level(self._h, int(klass)))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._l.rs_provider_delete(self._h)
+            self._h = None
+
+    __del__ = close
 
 
 class ShardManager:
@@ -157,10 +206,17 @@ class ParameterServer:
         return int(self._l.rs_ps_size(self._h))
 
     # serving ----------------------------------------------------------
-    def serve(self, port: int = 0) -> int:
-        """Starts the loopback server; returns the bound port (``port=0`` picks a free one)."""
+    def serve(self, port: int = 0, workers: int = 0, scheduler: str = "fifo", levels: int = 7) -> int:
+        """Starts the loopback server; returns the bound port (``port=0`` picks a free one).  ``workers=0``: each
+        connection's thread executes its requests (the reference's synchronous server); ``workers>0``: connection
+        threads hand requests to a pool of worker threads through a ``"fifo"`` or ``"priority"`` task provider
+        (the asynchronous server and the schedulers of src/grpc_ps/provider.h); answers keep request order per
+        connection."""
         s, p = vp(), i32()
-        _lib.call("rs_ps_server_start", self._h, int(port), C.byref(s), C.byref(p))
+        if workers > 0:
+            _lib.call("rs_ps_server_start_pool", self._h, int(port), int(workers), scheduler.encode(), int(levels), C.byref(s), C.byref(p))
+        else:
+            _lib.call("rs_ps_server_start", self._h, int(port), C.byref(s), C.byref(p))
         self._server, self.port = s.value, p.value
         return self.port
 
@@ -222,10 +278,10 @@ class ParameterClient:
         _lib.call("rs_ps_client_update", self._h, k.data_ptr(), k.numel(), self.dim, g.data_ptr(), MAX_PARAMETER_BATCH, C.byref(a))
         return int(a.value)
 
-    def _cmd(self, op: int, payload: bytes = b"") -> Tuple[int, int, int]:
-        r = (u64 * 3)()
+    def _cmd(self, op: int, payload: bytes = b"") -> Tuple[int, int, int, int]:
+        r = (u64 * 4)()
         _lib.call("rs_ps_client_command", self._h, op, payload, len(payload), r)
-        return int(r[0]), int(r[1]), int(r[2])
+        return int(r[0]), int(r[1]), int(r[2]), int(r[3])
 
     def ClearPS(self) -> bool:
         self._cmd(OP_CLEAR)
@@ -251,7 +307,12 @@ class ParameterClient:
 
     def Stats(self) -> dict:
         s = self._cmd(OP_STATS)
-        return {"keys_stored": s[0], "requests": s[1], "keys_served": s[2]}
+        return {"keys_stored": s[0], "requests": s[1], "keys_served": s[2], "pooled_requests": s[3]}
+
+    def ImprovePriority(self) -> int:
+        """Raises this connection's class by one level at a server with the priority scheduler; returns the new level
+        (always 1 at a FIFO or synchronous server).  Role of Provider::ImporvePriority, src/grpc_ps/provider.h."""
+        return self._cmd(OP_PRIORITY)[0]
 
     # asynchronous form ------------------------------------------------------------------
     def InitThread(self, n: int = 1) -> None:

@@ -298,3 +298,81 @@ def test_grpc_transport_mirror_commands_and_wire_format(tmp_path):
     with pytest.raises(grpc.RpcError):
         dead.GetParameter([1, 2, 3])
     srv.stop(0)
+
+
+def test_task_providers_fifo_and_priority_levels():
+    """FIFO order; the priority provider draws level i with probability ~ i x queue length, raises a class on
+    ImprovePriority, keeps levels relative (nobody left at level 1 -> everybody moves down) and caps at `levels`."""
+    from recstore_b200.ps.client import TaskProvider
+    f = TaskProvider("fifo")
+    for i in range(10):
+        f.PutTask(i, i % 3)
+    assert f.LeftTask() == 10 and [f.GetTask() for _ in range(10)] == list(range(10)) and f.GetTask() is None and not f.ExistTask()
+    p = TaskProvider("priority", levels=4, seed=7)
+    assert p.LevelOf(1) == 1
+    p.PutTask(0, 1); p.PutTask(0, 2)                      # both classes known at level 1
+    p.ImprovePriority(2); p.ImprovePriority(2)
+    assert (p.LevelOf(1), p.LevelOf(2)) == (1, 3)
+    for _ in range(5):
+        p.ImprovePriority(2)
+    assert p.LevelOf(2) == 4                              # capped
+    p.ImprovePriority(1)                                  # 1 -> 2: nobody at level 1 any more, so (2, 4) -> (1, 3)
+    assert (p.LevelOf(1), p.LevelOf(2)) == (1, 3)
+    while p.GetTask() is not None:
+        pass
+    # equal backlogs of class 1 (level 1, ids < 1000) and class 2 (level 3, ids >= 1000): the first draws favour class 2 by 3:1
+    for i in range(600):
+        p.PutTask(i, 1); p.PutTask(1000 + i, 2)
+    first = [p.GetTask() for _ in range(200)]
+    hi = sum(1 for t in first if t >= 1000)
+    assert 125 <= hi <= 175, hi                           # expectation 150, sigma ~ 6
+    lo_ids = [t for t in first if t < 1000]
+    assert lo_ids == sorted(lo_ids)                       # FIFO inside a level
+    rest = []
+    while p.ExistTask():
+        rest.append(p.GetTask())
+    assert sorted(first + rest) == sorted(list(range(600)) + list(range(1000, 1600)))   # nothing lost, nothing starved
+
+
+@pytest.mark.parametrize("scheduler", ["fifo", "priority"])
+def test_pooled_server_keeps_request_order_per_connection(scheduler):
+    """Front-end threads + worker pool: pipelined sub-requests of several concurrent clients come back in order (the
+    client checks every key of every answer), updates from all clients add up, and the priority verb answers."""
+    import threading
+    from recstore_b200.ps.client import ParameterClient, ParameterServer
+    D = 8
+    ps = ParameterServer("KVEngineMap", {"dim": D, "capacity": 1 << 17, "optimizer": "sgd", "lr": 1.0})
+    port = ps.serve(0, workers=4, scheduler=scheduler)
+    ps.LoadFakeData(60000)
+    errs = []
+    known = threading.Barrier(4)
+
+    def client(seed):
+        try:
+            c = ParameterClient("127.0.0.1", port, 0, D)
+            c.GetParameter([seed])                     # the server knows this connection's class from its first task on
+            known.wait(30)
+            if seed == 0:                              # levels are relative: somebody else has to be at level 1
+                assert c.ImprovePriority() == (2 if scheduler == "priority" else 1)
+            g = torch.Generator().manual_seed(seed)
+            for _ in range(6):
+                k = torch.randint(0, 50000, (9000,), generator=g)          # 5 pipelined sub-requests
+                rows, found = c.GetParameterWithMask(k)
+                assert bool(found.all()) and torch.equal(rows[:, 0], k.float())
+            c.UpdateParameter(torch.arange(50000, 50100), torch.ones(100, D))
+            c.close()
+        except BaseException as e:      # noqa: BLE001
+            errs.append(repr(e))
+    ts = [threading.Thread(target=client, args=(i,)) for i in range(4)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert not errs, errs
+    c = ParameterClient("127.0.0.1", port, 0, D)
+    base = torch.arange(50000, 50100).float().unsqueeze(1).repeat(1, D)
+    assert torch.equal(c.GetParameter(torch.arange(50000, 50100)), base - 4.0)
+    st = c.Stats()
+    assert st["pooled_requests"] >= 4 * (6 * 5 + 1) and st["requests"] > st["pooled_requests"]
+    c.close()
+    ps.close()
