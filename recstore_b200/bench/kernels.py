@@ -123,6 +123,57 @@ def bench_embedding(tm, dev, B, T, D, rows, alpha=1.2):
             extra="bytes = bf16 grad read + indices + norm; unique-row RMW estimated at 1/4 of occurrences")
 
 
+def bench_cache(tm, dev, n_keys, D, items, alpha=1.1):
+    """32-way set-associative HBM cache: Query of a Zipf batch (hits copy a row, misses are listed), Replace of the missed
+    keys, Update of resident rows.  Bytes counted: 8 B key + one 256 B tag line per probe + the rows moved."""
+    from ..cache.gpu_cache import GpuCache
+    from ..utils.data import zipf_ids_torch
+    cache = GpuCache(items, D, dev)
+    space = items * 4
+    perm = torch.randperm(space, device=dev)                 # popular ids are spread over the sets
+    warm = perm[: items * 3 // 4]                             # the cache holds the most popular keys, as a warmed-up cache would
+    cache.Replace(warm, torch.randn(warm.numel(), D, device=dev))
+    keys = perm[zipf_ids_torch(n_keys, space, alpha, device=dev)]
+    vals = torch.empty(n_keys, D, device=dev)
+    r = cache.Query(keys, vals)
+    hit = 1.0 - r.missing_keys.numel() / n_keys
+    ms = tm.run(lambda: cache.Query(keys, vals, sync=False))
+    _report(f"cache_query n={n_keys} D={D} items={items} zipf={alpha} hit={hit:.2f}", ms,
+            bytes_=n_keys * (8 + 256) + int(n_keys * hit) * D * 4 * 2,
+            extra="bytes = key + 256-B tag line per probe, row read + row write per hit")
+    resident = keys[torch.isin(keys, r.missing_keys, invert=True)]
+    upd = torch.unique(resident)
+    uv = torch.randn(upd.numel(), D, device=dev)
+    ms = tm.run(lambda: cache.Update(upd, uv))
+    _report(f"cache_update n={upd.numel()} D={D}", ms, bytes_=upd.numel() * (8 + 256 + D * 4 * 2),
+            extra="bytes = key + tag line + value read + row write")
+    fresh = torch.arange(space, space + n_keys, device=dev)   # all absent: every key evicts the LRU way of its set
+    fv = torch.randn(n_keys, D, device=dev)
+    ms = tm.run(lambda: cache.Replace(fresh, fv), iters=5)
+    _report(f"cache_replace n={n_keys} D={D} (all new keys)", ms, bytes_=n_keys * (8 + 512 + D * 4 * 2),
+            extra="bytes = key + tag and stamp lines + value read + row write")
+    cache.status.zero_()
+
+
+def bench_hash(tm, dev, n_keys, capacity):
+    """GPU hash table (open addressing, 64-bit CAS): insert of new keys, lookup of resident keys, device-side unique."""
+    from ..cache.gpu_cache import GpuHashTable, unique_keys
+    from ..utils.data import zipf_ids_torch
+    ht = GpuHashTable(capacity, device=dev)
+    base = torch.randperm(capacity * 2, device=dev)[: capacity // 2]
+    ht.insert(base)                                           # load factor 0.5 before the timed calls
+    look = base[torch.randint(0, base.numel(), (n_keys,), device=dev)]
+    ms = tm.run(lambda: ht.lookup(look))
+    _report(f"hash_lookup n={n_keys} capacity={capacity} load=0.5", ms, bytes_=n_keys * (8 + 32 + 8),
+            extra="bytes = key + one 32-B sector of the slot array per probe + row index out")
+    ms = tm.run(lambda: ht.lookup(look + capacity * 4))
+    _report(f"hash_lookup (all absent) n={n_keys}", ms, bytes_=n_keys * (8 + 32 + 8))
+    dup = zipf_ids_torch(n_keys, capacity, 1.1, device=dev)
+    ms = tm.run(lambda: unique_keys(dup))
+    _report(f"unique_keys n={n_keys} zipf=1.1", ms, bytes_=n_keys * (8 + 32 + 8 + 8),
+            extra="includes the scratch-table clear; bytes = key + slot sector + inverse + unique list")
+
+
 def bench_interaction(tm, dev, B, F, D):
     T = torch.randn(B, F, D, device=dev).bfloat16()
     n = D + F * (F - 1) // 2
@@ -145,7 +196,7 @@ def bench_interaction(tm, dev, B, F, D):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="all", choices=["all", "gemm", "wgrad", "embedding", "interaction"])
+    ap.add_argument("--kernel", default="all", choices=["all", "gemm", "wgrad", "embedding", "interaction", "cache", "hash"])
     ap.add_argument("--m", type=int, default=65536)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -172,6 +223,10 @@ def main():
         bench_embedding(tm, dev, B, 26 if not a.small else 8, 128, 1_000_000, alpha=a.alpha)
     if a.kernel in ("all", "interaction"):
         bench_interaction(tm, dev, B, 27, 128)
+    if a.kernel in ("all", "cache"):
+        bench_cache(tm, dev, 262144 if a.small else 1 << 20, 128, (1 << 20) if a.small else (1 << 22), a.alpha)
+    if a.kernel in ("all", "hash"):
+        bench_hash(tm, dev, 1 << 20 if a.small else 1 << 22, 1 << 24)
 
 
 if __name__ == "__main__":

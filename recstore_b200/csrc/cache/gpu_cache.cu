@@ -67,47 +67,79 @@ __global__ void cache_tick_kernel(unsigned* clock, int* miss_count) {
   if (miss_count) *miss_count = 0;
 }
 
+// One warp per key: the 32 lanes compare the 32 tags of the key's set (one 256-B line).  A warp takes its keys four at a
+// time so that four tag lines are in flight before the first is compared, and it collects its misses in registers
+// (lane r keeps the r-th miss) and appends them with ONE atomicAdd per 32 misses: a counter bumped once per missing key
+// serialises the whole grid on one L2 address when the hit rate is low.
 __global__ void __launch_bounds__(256) cache_query_kernel(CacheView c, const long long* __restrict__ keys, long long n,
                                                           float* __restrict__ out, long long* __restrict__ miss_index,
                                                           long long* __restrict__ miss_keys, int* __restrict__ miss_count) {
+  constexpr int kAhead = 4;
   const int lane = threadIdx.x & 31;
   const long long warp = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
   const unsigned now = *c.clock;
-  long long i = warp;
-  if (i >= n) return;
-  unsigned long long key = static_cast<unsigned long long>(keys[i]);
-  unsigned long long set = ht_hash(key) % c.nsets;
-  unsigned long long line = c.keys[set * kWays + lane];
-  while (i < n) {
-    const long long ni = i + nwarps;
-    unsigned long long nkey = 0, nset = 0, nline = 0;
-    if (ni < n) {  // next key's set line in flight while this row is copied
-      nkey = static_cast<unsigned long long>(keys[ni]);
-      nset = ht_hash(nkey) % c.nsets;
-      nline = c.keys[nset * kWays + lane];
+  int n_miss = 0;
+  long long my_miss_index = 0;
+  unsigned long long my_miss_key = 0;
+  auto flush_misses = [&]() {
+    int base = 0;
+    if (lane == 0) base = atomicAdd(miss_count, n_miss);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    if (lane < n_miss) {
+      miss_index[base + lane] = my_miss_index;
+      miss_keys[base + lane] = static_cast<long long>(my_miss_key);
     }
-    const unsigned hit = __ballot_sync(0xffffffffu, line == key && key != kEmptyKey);
-    bool valid = false;
-    if (hit) {
-      const int way = __ffs(hit) - 1;
-      const unsigned long long slot = set * kWays + way;
-      const unsigned v0 = *reinterpret_cast<volatile unsigned*>(&c.vers[slot]);
-      __threadfence();
-      const unsigned long long k0 = *reinterpret_cast<volatile unsigned long long*>(&c.keys[slot]);
-      if (out != nullptr) copy_row_cg(out + i * c.dim, c.values + slot * c.dim, c.dim, lane);
-      __threadfence();
-      const unsigned v1 = *reinterpret_cast<volatile unsigned*>(&c.vers[slot]);
-      valid = __all_sync(0xffffffffu, (v0 & 1u) == 0u && v1 == v0 && k0 == key);
-      if (valid && lane == 0) c.stamps[slot] = now;
+    n_miss = 0;
+  };
+  for (long long i0 = warp; i0 < n; i0 += nwarps * kAhead) {
+    unsigned long long key[kAhead], set[kAhead], line[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const long long i = i0 + u * nwarps;
+      key[u] = i < n ? static_cast<unsigned long long>(keys[i]) : kEmptyKey;
+      set[u] = ht_hash(key[u]) % c.nsets;
+      line[u] = key[u] != kEmptyKey ? c.keys[set[u] * kWays + lane] : kEmptyKey;
     }
-    if (!valid && lane == 0 && key != kEmptyKey) {          // the empty marker is padding: neither a hit nor a miss
-      const int pos = atomicAdd(miss_count, 1);
-      miss_index[pos] = i;
-      miss_keys[pos] = static_cast<long long>(key);
+    // Hits are validated like a seqlock reader (version, key, row, version again), in three phases over the four keys so
+    // that the warp pays three dependent round trips and two fences per FOUR keys, not per key.
+    unsigned long long slot[kAhead], k0[kAhead];
+    unsigned v0[kAhead];
+    bool hit[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const unsigned m = __ballot_sync(0xffffffffu, key[u] != kEmptyKey && line[u] == key[u]);
+      hit[u] = m != 0;
+      slot[u] = set[u] * kWays + (hit[u] ? __ffs(m) - 1 : 0);
+      v0[u] = hit[u] ? *reinterpret_cast<volatile unsigned*>(&c.vers[slot[u]]) : 1u;
     }
-    i = ni; key = nkey; set = nset; line = nline;
+    __threadfence();
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (!hit[u]) continue;
+      k0[u] = *reinterpret_cast<volatile unsigned long long*>(&c.keys[slot[u]]);
+      if (out != nullptr) copy_row_cg(out + (i0 + u * nwarps) * c.dim, c.values + slot[u] * c.dim, c.dim, lane);
+    }
+    __threadfence();
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (key[u] == kEmptyKey) continue;                     // padding (or past the end): neither a hit nor a miss
+      bool valid = false;
+      if (hit[u]) {
+        const unsigned v1 = *reinterpret_cast<volatile unsigned*>(&c.vers[slot[u]]);
+        valid = __all_sync(0xffffffffu, (v0[u] & 1u) == 0u && v1 == v0[u] && k0[u] == key[u]);
+        if (valid && lane == 0 && c.stamps[slot[u]] != now) c.stamps[slot[u]] = now;
+      }
+      if (!valid) {
+        if (lane == n_miss) {
+          my_miss_index = i0 + u * nwarps;
+          my_miss_key = key[u];
+        }
+        if (++n_miss == 32) flush_misses();
+      }
+    }
   }
+  if (n_miss > 0) flush_misses();
 }
 
 __device__ __forceinline__ bool lock_set(int* lock, int lane) {
@@ -387,7 +419,7 @@ RS_API int rs_cache_query(void* handle, const long long* keys, long long n, floa
   RS_LAUNCH_CHECK();
   if (n == 0) return RS_OK;
   long long warps = (n + 3) / 4;  // >= 4 keys per warp when there are enough keys
-  if (warps > 148 * 32) warps = 148 * 32;
+  if (warps > 148 * 24) warps = 148 * 24;    // three resident blocks of eight warps per SM (80 registers per thread)
   cache_query_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(v, keys, n, out, miss_index, miss_keys, miss_count);
   RS_LAUNCH_CHECK();
   return RS_OK;
