@@ -14,6 +14,9 @@ Types (``CacheEmbFactory.New``), as in src/python/pytorch/recstore/cache/cache_e
   bucketed by owner, exchanged, gathered on the owner, rows exchanged back, misses come from the host
   table; backward sends (keys, grads) to the owners and the miss gradients to the host table.
 * ``KGExternelEmbedding``  host table updated directly in backward (cache_common.py:162-220).
+* ``LocalCachedEmbedding`` / ``ShardedCachedEmbedding``  the hash-cache forms (local_cache.py:17-110,
+  sharded_cache.py:13-178): a set-associative ``GpuCache`` filled on demand instead of a known hot range, per rank
+  or sharded by row range; cached copies are updated in backward.
 
 On CUDA devices the two cached placements run on the native data plane: the per-rank hot ranges are the shards of a
 range-owned :class:`~recstore_b200.parallel.sharded_table.ShardedEmbeddingTable` (peer windows over NVLink, fused
@@ -323,6 +326,169 @@ class KnownShardedCachedEmbedding(_CachedBase):
             self.controller.AfterBackward()
 
 
+class _HostRowCache:
+    """Stand-in for :class:`GpuCache` on a CPU device (same Query / Replace / Update surface, LRU over a dict) so that the
+    hash-cache placements run under gloo as well."""
+
+    def __init__(self, capacity: int, dim: int):
+        from collections import OrderedDict
+        self.capacity, self.dim = max(1, capacity), dim
+        self.rows: "OrderedDict[int, torch.Tensor]" = OrderedDict()
+
+    def Query(self, keys, values=None, sync=True):
+        from .gpu_cache import CacheQueryResult
+        n = keys.numel()
+        values = torch.zeros(n, self.dim) if values is None else values
+        mi, mk = [], []
+        for i, k in enumerate(keys.tolist()):
+            r = self.rows.get(k)
+            if r is None:
+                mi.append(i)
+                mk.append(k)
+            else:
+                self.rows.move_to_end(k)
+                values[i] = r
+        return CacheQueryResult(values, torch.tensor(mi, dtype=torch.int64), torch.tensor(mk, dtype=torch.int64))
+
+    def Replace(self, keys, values):
+        for k, v in zip(keys.tolist(), values):
+            if k in self.rows:
+                self.rows.move_to_end(k)
+                continue
+            if len(self.rows) >= self.capacity:
+                self.rows.popitem(last=False)
+            self.rows[k] = v.clone()
+
+    def Update(self, keys, values):
+        for k, v in zip(keys.tolist(), values):
+            if k in self.rows:
+                self.rows[k] = v.clone()
+
+
+class _HashCachedBase(_CachedBase):
+    """Placements whose device cache is a hash cache filled on demand (no key range known in advance).  The reference
+    sketches both (local_cache.py:17-110 ``LocalCachedEmbedding``, whose constructor still raises "TODO: update cache in
+    backward", and sharded_cache.py:13-178 ``ShardedCachedEmbedding``); here the cached copies ARE updated in backward,
+    with the same SGD rule as the host table, so a cached row never goes stale."""
+
+    def __init__(self, emb, args, device="cpu"):
+        ratio = float(dict(args).get("cache_ratio", 0.1))
+        a = dict(args)
+        a["cache_ratio"] = 0.0                                 # no range-owned slice: the base only sets up the host side
+        super().__init__(emb, a, device)
+        self.ratio = ratio
+        cap = max(32, int(self.N * ratio))
+        if self.device.type == "cuda":
+            from .gpu_cache import GpuCache
+            self.gpu_cache = GpuCache(cap, self.D, self.device)
+        else:
+            self.gpu_cache = _HostRowCache(cap, self.D)
+
+    def _host_rows(self, keys: torch.Tensor) -> torch.Tensor:
+        return self.full[keys.cpu()].to(self.device)
+
+    def _query_fill(self, keys: torch.Tensor) -> torch.Tensor:
+        """Rows of ``keys``: hits from the cache, misses from the host table (and into the cache for next time)."""
+        out = torch.zeros(keys.numel(), self.D, device=self.device)
+        if keys.numel() == 0:
+            return out
+        res = self.gpu_cache.Query(keys, out)
+        self.lookups += keys.numel()
+        self.hits += keys.numel() - res.missing_keys.numel()
+        if res.missing_keys.numel():
+            rows = self._host_rows(res.missing_keys)
+            out[res.missing_index] = rows
+            mk, first = _first_occurrence(res.missing_keys)
+            self.gpu_cache.Replace(mk, rows[first])
+        return out
+
+    def _update_cached(self, keys: torch.Tensor, grads: torch.Tensor) -> None:
+        """Applies row -= clr * (sum of the key's gradients) to the rows of ``keys`` that this rank's cache holds."""
+        if keys.numel() == 0:
+            return
+        uk, inv = torch.unique(keys, return_inverse=True)
+        g = torch.zeros(uk.numel(), self.D, device=grads.device, dtype=torch.float32).index_add_(0, inv, grads.float())
+        cur = torch.zeros(uk.numel(), self.D, device=self.device)
+        res = self.gpu_cache.Query(uk, cur)
+        present = torch.ones(uk.numel(), dtype=torch.bool, device=self.device)
+        present[res.missing_index] = False
+        if present.any():
+            self.gpu_cache.Update(uk[present], cur[present] - self.clr * g[present])
+
+
+def _first_occurrence(keys: torch.Tensor):
+    """(unique keys, index of one occurrence of each) so that a batch inserts every missing key once."""
+    uk, inv = torch.unique(keys, return_inverse=True)
+    first = torch.empty(uk.numel(), dtype=torch.int64, device=keys.device)
+    first[inv] = torch.arange(keys.numel(), device=keys.device)
+    return uk, first
+
+
+class LocalCachedEmbedding(_HashCachedBase):
+    """Every rank keeps its own hash cache (``cache_ratio`` x table rows) over the shared host table: no communication
+    in forward; after backward every rank learns every rank's (keys, gradients), refreshes its cached copies, and the
+    host table is updated through the controller."""
+
+    def _lookup(self, keys):
+        return self._query_fill(keys)
+
+    def after_backward(self):
+        keys = torch.cat(self._step_keys) if self._step_keys else torch.empty(0, dtype=torch.int64, device=self.device)
+        grads = torch.cat(self._step_grads) if self._step_grads else torch.empty(0, self.D, device=self.device)
+        self._step_keys, self._step_grads = [], []
+        if self.world > 1:                                      # any rank may cache any key
+            ak = comm.all2all_data_transfer([keys] * self.world)
+            ag = comm.all2all_data_transfer([grads] * self.world)
+            self._update_cached(torch.cat(ak), torch.cat(ag))
+        else:
+            self._update_cached(keys, grads)
+        self._host_update(keys, grads)
+        if self.controller is not None:
+            self.controller.AfterBackward()
+
+
+class ShardedCachedEmbedding(_HashCachedBase):
+    """Keys are owned by row range (``linspace(0, N, world + 1)``); the owner answers from its hash cache and fills it
+    from the host table on a miss; keys travel to the owners and rows back (two all-to-alls), gradients travel to the
+    owners after backward."""
+
+    def __init__(self, emb, args, device="cpu"):
+        super().__init__(emb, args, device)
+        self.shard_range = [int(x) for x in torch.linspace(0, self.N, self.world + 1).long().tolist()]
+        self.shard_range[-1] = self.N
+
+    def _owner(self, keys):
+        bounds = torch.tensor(self.shard_range[1:-1], device=keys.device, dtype=keys.dtype)
+        return torch.bucketize(keys, bounds, right=True)
+
+    def _lookup(self, keys):
+        if self.world == 1:
+            return self._query_fill(keys)
+        owner = self._owner(keys)
+        pos = [torch.nonzero(owner == r).flatten() for r in range(self.world)]
+        asked = comm.all2all_data_transfer([keys[p] for p in pos])
+        rows = comm.all2all_data_transfer([self._query_fill(k) for k in asked])
+        out = torch.empty(keys.numel(), self.D, device=self.device)
+        for p, r in zip(pos, rows):
+            out[p] = r
+        return out
+
+    def after_backward(self):
+        keys = torch.cat(self._step_keys) if self._step_keys else torch.empty(0, dtype=torch.int64, device=self.device)
+        grads = torch.cat(self._step_grads) if self._step_grads else torch.empty(0, self.D, device=self.device)
+        self._step_keys, self._step_grads = [], []
+        if self.world > 1:
+            owner = self._owner(keys)
+            mk = comm.all2all_data_transfer([keys[owner == r] for r in range(self.world)])
+            mg = comm.all2all_data_transfer([grads[owner == r] for r in range(self.world)])
+            self._update_cached(torch.cat(mk), torch.cat(mg))
+        else:
+            self._update_cached(keys, grads)
+        self._host_update(keys, grads)
+        if self.controller is not None:
+            self.controller.AfterBackward()
+
+
 class KGExternelEmbedding(_CachedBase):
     """No device cache: rows come from the host table and the update is applied to it right after backward."""
 
@@ -362,6 +528,8 @@ class CacheEmbFactory:
         "KnownLocalCachedEmbedding": KnownLocalCachedEmbedding,
         "KnownLocalCachedEmbeddingSoftware": KnownLocalCachedEmbeddingSoftware,
         "KGExternelEmbedding": KGExternelEmbedding,
+        "LocalCachedEmbedding": LocalCachedEmbedding,
+        "ShardedCachedEmbedding": ShardedCachedEmbedding,
     }
 
     @staticmethod

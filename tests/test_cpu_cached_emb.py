@@ -78,7 +78,9 @@ def _worker(rank, world, port, ns, cache_type, mode, q):
 
 
 @pytest.mark.parametrize("cache_type,mode", [("KnownLocalCachedEmbedding", "CppSync"), ("KnownLocalCachedEmbedding", "CppAsyncV2"),
-                                             ("KnownShardedCachedEmbedding", "CppAsyncV2"), ("KGExternelEmbedding", "CppSync")])
+                                             ("KnownShardedCachedEmbedding", "CppAsyncV2"), ("KGExternelEmbedding", "CppSync"),
+                                             ("LocalCachedEmbedding", "CppAsyncV2"), ("ShardedCachedEmbedding", "CppSync"),
+                                             ("ShardedCachedEmbedding", "CppAsync")])
 def test_cached_embedding_matches_golden(cache_type, mode):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")

@@ -399,3 +399,15 @@ def test_nvlink_parameter_client_verbs_on_one_gpu(dev, tmp_path):
     ps.LoadFakeData(1000)
     assert torch.equal(ps.GetParameter(torch.tensor([5, 999]))[:, 0].cpu(), torch.tensor([5.0, 999.0]))
     ctx.check_status()
+
+
+@pytest.mark.parametrize("choice", ["LocalCachedEmbedding", "ShardedCachedEmbedding"])
+def test_hash_cache_embeddings_stay_coherent_with_the_host_table(choice):
+    """The on-demand hash-cache placements on one GPU: rows are filled from the host table on a miss, evicted under
+    pressure (the cache holds 2 % of the table) and updated in backward, so every step's forward output equals a
+    replicated ``nn.Embedding`` trained with the same gradients."""
+    from recstore_b200.cli import perf_emb
+    out = perf_emb.main(["--num_workers", "1", "--device", "cuda", "--run_steps", "30", "--diff_test", "--emb_choice", choice,
+                         "--backwardMode", "CppSync", "--batch_size", "2000", "--num_embs", "20000", "--cache_ratio", "0.02",
+                         "--log_interval", "1000"])
+    assert len(out) == 1 and out[0][0] == 30 and out[0][1] < 1e-3, out

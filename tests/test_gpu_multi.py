@@ -289,11 +289,14 @@ def test_sharded_table_lookup_update_matches_replicated_oracle():
     assert all(out.get(r) == "ok" for r in range(world)), dict(out)
 
 
-@pytest.mark.parametrize("choice", ["KnownShardedCachedEmbedding", "KnownLocalCachedEmbedding"])
+@pytest.mark.parametrize("choice", ["KnownShardedCachedEmbedding", "KnownLocalCachedEmbedding", "LocalCachedEmbedding",
+                                    "ShardedCachedEmbedding"])
 def test_cached_embeddings_on_the_native_plane_match_replicated_embedding(choice):
     """The reference-named cached embeddings on two GPUs (hot ranges as range-owned shards on the peer-window
     transport, rows of other ranges from the device-mapped host table, gradients delivered by ``push_update``): every
-    step's forward output equals a replicated ``nn.Embedding`` trained with the same gradients (the driver's --diff_test)."""
+    step's forward output equals a replicated ``nn.Embedding`` trained with the same gradients (the driver's --diff_test).
+    The two hash-cache placements run their ``GpuCache`` (query, fill on miss, update of cached copies in backward) with
+    NCCL all-to-alls around it."""
     if _ngpus() < 2:
         pytest.skip("needs 2 GPUs")
     from recstore_b200.cli import perf_emb
