@@ -67,11 +67,11 @@ class KVEnginePoolMap final : public BaseKV {
     return off != 0;
   }
   bool Put(uint64_t key, const void* value) override {
-    uint64_t off = pool_->Malloc(rec_bytes_);
+    uint64_t off = AllocRecord();
     if (!off) {
       epoch_.Bump();
       epoch_.Collect();
-      off = pool_->Malloc(rec_bytes_);
+      off = AllocRecord();
       if (!off) return false;
     }
     Record* r = rec(off);
@@ -119,6 +119,10 @@ class KVEnginePoolMap final : public BaseKV {
     for (Shard& s : shards_) s.mu.lock();
     for (Shard& s : shards_) s.map.clear();
     epoch_.DrainAll();
+    for (Stock& st : stocks_) {
+      std::lock_guard<SpinLock> lk(st.mu);
+      st.n = 0;
+    }
     pool_->Reset();
     size_.store(0);
     for (Shard& s : shards_) s.mu.unlock();
@@ -135,6 +139,10 @@ class KVEnginePoolMap final : public BaseKV {
   void Flush() override {
     epoch_.Bump();
     epoch_.Collect();
+    for (Stock& st : stocks_) {                      // unused stock goes back, so a clean reopen drops nothing
+      std::lock_guard<SpinLock> lk(st.mu);
+      while (st.n > 0) pool_->Free(st.off[--st.n]);
+    }
     pool_->Sync();
   }
   size_t Keys(uint64_t* out, size_t cap) const override {
@@ -154,14 +162,47 @@ class KVEnginePoolMap final : public BaseKV {
     mutable std::shared_mutex mu;
     std::unordered_map<uint64_t, uint64_t> map;
   };
+  // Small stocks of free slabs, one per stripe of threads, refilled 32 at a time: concurrent writers do not meet on the
+  // pool's class lock.  Slabs sitting in a stock are allocated but unsealed, so a reopen after a crash frees them.
+  static constexpr int kStockSlabs = 64;
+  struct alignas(64) Stock {
+    SpinLock mu;
+    uint64_t off[kStockSlabs];
+    int n = 0;
+  };
+  Stock& my_stock() {
+    static std::atomic<unsigned> next_stripe{0};
+    thread_local unsigned stripe = next_stripe.fetch_add(1, std::memory_order_relaxed);
+    return stocks_[stripe % kStocks];
+  }
+  uint64_t AllocRecord() {
+    Stock& st = my_stock();
+    std::lock_guard<SpinLock> lk(st.mu);
+    if (st.n == 0) st.n = static_cast<int>(pool_->MallocBatch(rec_bytes_, st.off, kStockSlabs / 2));
+    return st.n > 0 ? st.off[--st.n] : 0;
+  }
+  static constexpr int kStocks = 16;
+  Stock stocks_[kStocks];
   Shard& shard(uint64_t key) { return shards_[hash64(key) & 63]; }
   Record* rec(uint64_t off) const { return static_cast<Record*>(pool_->At(off)); }
   // The record is out of the index: it must not come back after a crash, and its slab returns to the pool once no
   // reader can still be copying from it.
   void Unlink(uint64_t off) {
     rec(off)->seal.store(0, std::memory_order_release);
-    PersistSlabPool* p = pool_.get();
-    epoch_.Retire([p, off] { p->Free(off); });
+    epoch_.Retire([this, off] { Recycle(off); });
+  }
+  // A reclaimed record goes straight into the reclaiming thread's stock when there is room (all records have one size),
+  // so in steady state writers neither free to nor allocate from the pool.
+  void Recycle(uint64_t off) {
+    Stock& st = my_stock();
+    {
+      std::lock_guard<SpinLock> lk(st.mu);
+      if (st.n < kStockSlabs) {
+        st.off[st.n++] = off;
+        return;
+      }
+    }
+    pool_->Free(off);
   }
   void Rebuild() {
     const uint64_t want = PersistSlabPool::ClassSize(rec_bytes_);

@@ -175,35 +175,41 @@ uint64_t PersistSlabPool::alloc_in_chunk(uint64_t c) {
 }
 
 uint64_t PersistSlabPool::Malloc(uint64_t size) {
+  uint64_t off = 0;
+  return MallocBatch(size, &off, 1) == 1 ? off : 0;
+}
+
+size_t PersistSlabPool::MallocBatch(uint64_t size, uint64_t* out, size_t n) {
   if (size == 0) size = 1;
   const uint64_t cs = ClassSize(size);
   if (cs + 128 > chunk_bytes_) return 0;
   ClassState& st = *classes_[class_index(cs)];
   std::lock_guard<SpinLock> lk(st.mu);
-  while (true) {
-    while (!st.partial.empty()) {
+  size_t got = 0;
+  while (got < n) {
+    while (got < n && !st.partial.empty()) {
       const uint64_t off = alloc_in_chunk(st.partial.back());
-      if (off) {
-        slabs_in_use_.fetch_add(1, std::memory_order_relaxed);
-        bytes_in_use_.fetch_add(cs, std::memory_order_relaxed);
-        return off;
-      }
-      st.partial.pop_back();                                 // full: a Free puts it back
+      if (off) out[got++] = off;
+      else st.partial.pop_back();                            // full: a Free puts it back
     }
+    if (got == n) break;
     uint32_t c;
     {
       std::lock_guard<SpinLock> fl(free_mu_);
-      if (free_chunks_.empty()) return 0;
+      if (free_chunks_.empty()) break;
       c = free_chunks_.back();
       free_chunks_.pop_back();
     }
     if (!format_chunk(c, cs)) {
       std::lock_guard<SpinLock> fl(free_mu_);
       free_chunks_.push_back(c);
-      return 0;
+      break;
     }
     st.partial.push_back(c);
   }
+  slabs_in_use_.fetch_add(got, std::memory_order_relaxed);
+  bytes_in_use_.fetch_add(got * cs, std::memory_order_relaxed);
+  return got;
 }
 
 uint64_t PersistSlabPool::SlabSize(uint64_t off) const {
@@ -312,7 +318,7 @@ struct ThreadSlots {
 thread_local ThreadSlots t_slots;
 }  // namespace
 
-EpochManager::EpochManager() : slots_(new Slot[kSlots]), id_(g_manager_ids.fetch_add(1) + 1) {}
+EpochManager::EpochManager() : slots_(new Slot[kSlots]), stripes_(new Stripe[kStripes]), id_(g_manager_ids.fetch_add(1) + 1) {}
 
 EpochManager::Slot* EpochManager::my_slot() {
   for (auto& h : t_slots.held)
@@ -361,48 +367,66 @@ uint64_t EpochManager::MinProtected() const {
 
 void EpochManager::Retire(std::function<void()> reclaim) {
   const uint64_t e = global_.load(std::memory_order_acquire);
+  Slot* s = my_slot();
+  Stripe& st = stripes_[s ? static_cast<size_t>(s - slots_.get()) % kStripes : 0];
+  bool collect;
   {
-    std::lock_guard<std::mutex> lk(mu_);
-    garbage_.push_back({e, std::move(reclaim)});
+    std::lock_guard<std::mutex> lk(st.mu);
+    st.garbage.push_back({e, std::move(reclaim)});
+    collect = (++st.retired & 63) == 0;
   }
-  if ((retired_.fetch_add(1, std::memory_order_relaxed) & 63) == 63) {
+  if (collect) {
     Bump();
-    Collect();
+    CollectStripe(st, MinProtected());
   }
+}
+
+size_t EpochManager::CollectStripe(Stripe& st, uint64_t safe_below) {
+  std::vector<Item> run;
+  {
+    std::lock_guard<std::mutex> lk(st.mu);
+    size_t keep = 0;
+    for (size_t i = 0; i < st.garbage.size(); ++i) {
+      if (st.garbage[i].epoch < safe_below) run.push_back(std::move(st.garbage[i]));
+      else {
+        if (keep != i) st.garbage[keep] = std::move(st.garbage[i]);
+        ++keep;
+      }
+    }
+    st.garbage.resize(keep);
+  }
+  for (auto& it : run) it.fn();
+  return run.size();
 }
 
 size_t EpochManager::Collect() {
   const uint64_t safe_below = MinProtected();
-  std::vector<Item> run;
-  {
-    std::lock_guard<std::mutex> lk(mu_);
-    size_t keep = 0;
-    for (size_t i = 0; i < garbage_.size(); ++i) {
-      if (garbage_[i].epoch < safe_below) run.push_back(std::move(garbage_[i]));
-      else {
-        if (keep != i) garbage_[keep] = std::move(garbage_[i]);
-        ++keep;
-      }
-    }
-    garbage_.resize(keep);
-  }
-  for (auto& it : run) it.fn();
-  return run.size();
+  size_t n = 0;
+  for (int i = 0; i < kStripes; ++i) n += CollectStripe(stripes_[i], safe_below);
+  return n;
 }
 
 size_t EpochManager::DrainAll() {
-  std::vector<Item> run;
-  {
-    std::lock_guard<std::mutex> lk(mu_);
-    run.swap(garbage_);
+  size_t n = 0;
+  for (int i = 0; i < kStripes; ++i) {
+    std::vector<Item> run;
+    {
+      std::lock_guard<std::mutex> lk(stripes_[i].mu);
+      run.swap(stripes_[i].garbage);
+    }
+    for (auto& it : run) it.fn();
+    n += run.size();
   }
-  for (auto& it : run) it.fn();
-  return run.size();
+  return n;
 }
 
 size_t EpochManager::Pending() const {
-  std::lock_guard<std::mutex> lk(mu_);
-  return garbage_.size();
+  size_t n = 0;
+  for (int i = 0; i < kStripes; ++i) {
+    std::lock_guard<std::mutex> lk(stripes_[i].mu);
+    n += stripes_[i].garbage.size();
+  }
+  return n;
 }
 
 }  // namespace rs

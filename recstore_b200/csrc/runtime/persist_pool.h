@@ -38,6 +38,9 @@ class PersistSlabPool {
 
   // Returns the offset of a slab of at least `size` bytes, 0 when the pool is exhausted or size exceeds a chunk.
   uint64_t Malloc(uint64_t size);
+  // Up to n slabs of one size under a single acquisition of the class lock (callers keep small per-thread or per-stripe
+  // stocks so that concurrent allocators do not meet on that lock); returns how many offsets were written.
+  size_t MallocBatch(uint64_t size, uint64_t* out, size_t n);
   void Free(uint64_t off);
   void* At(uint64_t off) const { return base_ + off; }
   uint64_t OffsetOf(const void* p) const { return static_cast<uint64_t>(static_cast<const char*>(p) - base_); }
@@ -120,9 +123,14 @@ class EpochManager {
   Slot* my_slot();
   std::atomic<uint64_t> global_{1};
   std::shared_ptr<Slot[]> slots_;    // shared with the threads that hold a slot, which release it when they exit
-  mutable std::mutex mu_;
-  std::vector<Item> garbage_;
-  std::atomic<uint64_t> retired_{0};
+  static constexpr int kStripes = 16;   // garbage lists, chosen by the retiring thread's slot: retirers rarely share one
+  struct alignas(64) Stripe {
+    mutable std::mutex mu;
+    std::vector<Item> garbage;
+    uint64_t retired = 0;
+  };
+  size_t CollectStripe(Stripe& st, uint64_t safe_below);
+  std::unique_ptr<Stripe[]> stripes_;
   const uint64_t id_;
 };
 
