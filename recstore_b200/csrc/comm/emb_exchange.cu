@@ -15,6 +15,8 @@
 //   rs_rw_reduce_partials   step 3: every owner has pushed the pooled partial sum of its share of each bag (step 2 is
 //                           rs_emb_forward_ex on the owner); the partials are added up into the feature slot.
 #include <cuda_bf16.h>
+#include <cstdlib>
+
 #include "comm/flags.cuh"
 #include "common/rs_common.h"
 
@@ -172,7 +174,11 @@ __global__ void __launch_bounds__(kThreads) rw_reduce_partials_kernel(const RwRe
 
 int grid_for(long long items) {
   long long g = (items + (kThreads / 32) - 1) / (kThreads / 32);
-  const long long cap = 148 * 8;   // a few CTAs per SM; warps loop over the items
+  // A few CTAs per SM; warps loop over the items.  RECSTORE_EXCHANGE_CTAS_PER_SM lowers it to a grid that is resident as
+  // a whole beside a GEMM CTA (two 128-thread CTAs fit in the registers a GEMM CTA leaves), so that the exchange does
+  // not hold back the dispatch of GEMMs launched after it on other streams.
+  static const int per_sm = [] { const char* e = getenv("RECSTORE_EXCHANGE_CTAS_PER_SM"); const int v = e ? atoi(e) : 0; return v > 0 ? v : 8; }();
+  const long long cap = 148ll * per_sm;
   if (g > cap) g = cap;
   if (g < 1) g = 1;
   return static_cast<int>(g);

@@ -90,12 +90,9 @@ __device__ __forceinline__ void store_pooled(const EmbFwdArgs& a, int t, int b, 
 // bag i (id range, and for single-id bags the row itself) with coalesced loads; the rows are then
 // fetched 8 bags at a time so that every warp keeps 8 independent 512-byte reads in flight.
 template <int NC>
-__device__ __forceinline__ void emb_fwd_body(const EmbFwdArgs& a) {
-  const int warps_per_block = blockDim.x >> 5;
-  const long long blk = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+__device__ __forceinline__ void emb_fwd_body(const EmbFwdArgs& a, long long blk) {
   const int lane = threadIdx.x & 31;
   const int blocks_per_table = (a.B + 31) >> 5;
-  if (blk >= static_cast<long long>(a.T) * blocks_per_table) return;
   const int t = static_cast<int>(blk / blocks_per_table);
   const int b0 = static_cast<int>(blk % blocks_per_table) << 5;
   const int nb = min(32, a.B - b0);
@@ -217,8 +214,13 @@ __device__ __forceinline__ void emb_fwd_body(const EmbFwdArgs& a) {
 
 template <int NC>
 __global__ void __launch_bounds__(256) emb_fwd_kernel(const EmbFwdArgs a) {
-  emb_fwd_body<NC>(a);
-  rs::flag_publish_when_grid_done(a.sig);   // (no-op without a signal) every thread arrives here: the body only returns early
+  // Warps loop over the blocks of 32 bags, so the grid can be a single resident wave (see launch_emb_fwd).
+  const int warps_per_block = blockDim.x >> 5;
+  const long long total = static_cast<long long>(a.T) * ((a.B + 31) >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * warps_per_block;
+  for (long long blk = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); blk < total; blk += stride)
+    emb_fwd_body<NC>(a, blk);
+  rs::flag_publish_when_grid_done(a.sig);   // (no-op without a signal) every thread arrives here
 }
 
 // ------------------------------------------------------------------ backward
@@ -555,7 +557,13 @@ int launch_emb_fwd(const EmbFwdArgs& a, cudaStream_t stream) {
   // Four warps per CTA: at 64 registers per thread such a CTA still fits on an SM beside one persistent GEMM CTA, so the
   // lookup and its NVLink pushes really run at the same time as the MLP that is launched beside them.
   static const int wpb = [] { const char* e = getenv("RECSTORE_EMB_FWD_WARPS"); return (e && e[0] == '8') ? 8 : 4; }();
-  const long long grid = (nblocks + wpb - 1) / wpb;
+  long long grid = (nblocks + wpb - 1) / wpb;
+  // RECSTORE_EMB_FWD_CTAS_PER_SM=c (0 = one CTA per 4 or 8 blocks of bags, the default): at most c CTAs per SM, the
+  // warps looping over the bags.  The hardware hands out the CTAs of a later kernel only once every CTA of the earlier
+  // one has been placed, so a lookup with thousands of CTAs holds back the GEMMs launched beside it on another stream
+  // until its last wave; a grid that is resident as a whole does not.
+  static const int per_sm = [] { const char* e = getenv("RECSTORE_EMB_FWD_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
+  if (per_sm > 0 && grid > 148ll * per_sm) grid = 148ll * per_sm;
   RS_REQUIRE(grid < (1ll << 31), "rs_emb_forward: too many bags");
   if (a.D <= 128) emb_fwd_kernel<1><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
   else if (a.D <= 256) emb_fwd_kernel<2><<<static_cast<unsigned>(grid), wpb * 32, 0, stream>>>(a);
