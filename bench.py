@@ -158,7 +158,8 @@ def run_native(args):
     # dcnv2: with sum-of-squares row-wise Adagrad a row that occurs n times in a batch moves by ~lr * sqrt(n); the
     # 100-hot Zipf feature repeats its hottest rows ~10^5 times per batch, so the embedding step is kept small.
     cfg = DLRMConfig(table_rows=rows, batch=B, emb_dim=DIM, emb_lr=0.01 if not dcn else 1e-4, mlp_lr=0.01 if not dcn else 0.001, seed=args.seed,
-                     use_cuda_graph=not args.no_graph, trace_phases=args.trace_phases, **extra)
+                     use_cuda_graph=not args.no_graph, trace_phases=args.trace_phases, pipeline_lookup=bool(args.pipeline),
+                     **extra)
     eng = DLRM(cfg, ctx)
     src = DLRMBatchSource(rows, hot, B, alpha=1.1 if dcn else ALPHA, seed=args.seed + 1)
     nb = 4
@@ -222,7 +223,8 @@ def run_native(args):
                        "parallelism": (f"table-wise MP embeddings x{world} + DP MLP x{world}" if not eng.K else
                                        f"row-wise sharded tables {eng.split_tables} + table-wise MP for the rest x{world} + DP MLP x{world}"),
                        "l2": "working set per step (>=450 MB of windows + ~17 GB of tables) exceeds the 126 MB L2",
-                       "optimizer": "row-wise Adagrad (embeddings) + SGD (MLP)", "total_rows": sum(rows)},
+                       "optimizer": "row-wise Adagrad (embeddings) + SGD (MLP)", "total_rows": sum(rows),
+                       "pipeline_lookup": bool(eng._pipe)},
             "clocks": clocks,
             "e2e": {"value": B * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
@@ -404,6 +406,8 @@ def main():
     ap.add_argument("--row-split", default="auto",
                     help="dcnv2 workload: tables spread row-wise over the GPUs: auto (those with more than 1/N of the ids per sample), "
                          "none (every table whole on one GPU) or a comma-separated list of table indices")
+    ap.add_argument("--pipeline", type=int, choices=[0, 1], default=int(os.environ.get("RECSTORE_PIPELINE_LOOKUP", "0")),
+                    help="dlrm workload: 1 = the lookup + forward all-to-all of batch t + 1 runs at the end of step t's graph")
     ap.add_argument("--repeats", type=int, default=5, help="how many times the K-step timed region is measured (median reported)")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="global batch; the headline config is 65,536 (other values are for profiling, e.g. 8,192 on one GPU "

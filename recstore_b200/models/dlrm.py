@@ -65,6 +65,11 @@ class DLRMConfig:
     # table indices, or "auto" = every table whose share of the ids per sample exceeds 1 / world (one rank could
     # never keep up with it).  Ignored on one GPU.
     row_split: object = None
+    # Cross-step pipelining of the sparse forward (dot interaction, tables whole on their ranks): the lookup + forward
+    # all-to-all of batch t + 1 runs at the END of step t's graph, beside the dense all-reduce and SGD, instead of at the
+    # start of step t + 1 (role of TrainPipelineSparseDist, model_zoo/golden_train.py:146-159).  `submit` then launches
+    # step t when batch t + 1 is submitted (or when the result of step t is asked for).
+    pipeline_lookup: bool = False
 
     def __post_init__(self):
         if self.hotness is None:
@@ -100,13 +105,15 @@ class PinnedBatch:
 class StepHandle:
     """Result of an asynchronously submitted step."""
 
-    def __init__(self, engine: "DLRM", slot: int, event: torch.cuda.Event):
-        self._e, self._slot, self._ev = engine, slot, event
+    def __init__(self, engine: "DLRM", slot: int, event: torch.cuda.Event, step: int = 0):
+        self._e, self._slot, self._ev, self._step = engine, slot, event, step
 
     def result(self) -> float:
         """Waits for the step and returns this rank's share of the mean BCE loss (sum over ranks = loss)."""
-        self._ev.synchronize()
         e = self._e
+        if self._step >= e._launched:                # pipelined mode: the step still waits for its successor
+            e.flush()
+        self._ev.synchronize()
         word = int(e._status_host[self._slot].item()) & 0xFFFFFFFFFFFFFFFF
         if word:
             # A kernel of this step (or an earlier one) gave up a bounded wait, met an id outside its table or a full
@@ -245,13 +252,19 @@ class DLRM:
 
         # ---- peer windows
         self.grow_stride = self.Tmax * self.D
-        self.Twin = self.ctx.alloc("dlrm_T", self.Bl * self.F * self.D * 2)
+        # Two forward windows, used alternately by the two input slots: a peer that is one step ahead writes the rows of
+        # batch t + 1 into the other window while this rank may still read those of batch t.
+        self._T = []
+        for i in range(2):
+            w = self.ctx.alloc("dlrm_T" if i == 0 else "dlrm_T1", self.Bl * self.F * self.D * 2)
+            self._T.append((w, w.view(torch.bfloat16, (self.Bl, self.F * self.D))))
+        self.Twin = self._T[0][0]
         # gradient window: [B, Tmax*D] bf16 rows pushed by the peers, then [B, Tmax] fp32 squared norms
         self.gn_off = _round_up(self.B * self.grow_stride * 2, 256)
         self.Gwin = self.ctx.alloc("dlrm_G", self.gn_off + self.B * self.Tmax * 4)
         self.gnorm = self.Gwin.view(torch.float32, (self.B, self.Tmax), byte_offset=self.gn_off)
         self.ndst_table = torch.tensor([p + self.gn_off for p in self.Gwin.ptrs], dtype=torch.int64, device=dev)
-        self.Tbuf = self.Twin.view(torch.bfloat16, (self.Bl, self.F * self.D))
+        self.Tbuf = self._T[0][1]
         if self.world > 1 and not self.dcn and not self.proj and (self.K or os.environ.get("RECSTORE_GRAD_PUSH", "") == "staged"):
             # Backward all-to-all with row-sharded tables under the dot interaction: its backward leaves the per-(sample,
             # table) gradient rows in this local staging buffer; a thin copy kernel then fans them out to their owners.
@@ -394,9 +407,14 @@ class DLRM:
         self._copied = [torch.cuda.Event() for _ in range(2)]
         self._consumed = [torch.cuda.Event() for _ in range(2)]
         self._done = [torch.cuda.Event() for _ in range(2)]
-        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._graphs: Dict[object, torch.cuda.CUDAGraph] = {}
         self._step_no = 0
         self.launches_per_step = 0
+        # Pipelined lookup: supported where the forward exchange is the one lookup kernel (dot interaction, no row-sharded
+        # tables).  `_pending` is the submitted step whose graph has not been launched yet (its lookup has been).
+        self._pipe = bool(cfg.pipeline_lookup) and not self.dcn and not self.proj and not self.K
+        self._pending: Optional[int] = None           # slot of the pending step
+        self._launched = 0                            # steps whose graph has been launched
         self.s_wgrad = torch.cuda.Stream(device=dev, priority=p_wgrad)   # weight/bias gradients, then the dense all-reduce and SGD
         self.s_comm = torch.cuda.Stream(device=dev, priority=p_comm)     # embedding lookup / gradient push: the NVLink-bound kernels
         self.s_wgrad2 = torch.cuda.Stream(device=dev, priority=p_wgrad)  # weight gradients of the bottom MLP
@@ -462,52 +480,65 @@ class DLRM:
                 for i, (a, b) in enumerate(zip(self._phase_names[:-1], self._phase_names[1:]))}
 
     # ------------------------------------------------------------------ the step as a launch sequence
-    def _forward(self, slot: int):
+    def _bind_slot(self, slot: int):
+        """The forward window of this input slot becomes the one the launch sequence below refers to."""
+        self.Twin, self.Tbuf = self._T[slot]
+        if self.dcn:
+            self.cx[0] = self.Tbuf
+
+    def _lookup(self, slot: int):
+        """Embedding lookup + forward all-to-all of the batch in input slot ``slot`` (current stream: communication)."""
+        st = self.ctx.status
+        twin = self._T[slot][0]
+        if self.world == 1:
+            if self.Tl:
+                F_.emb_forward(self.weight, self.table_base, self.table_rows, self.in_ids[slot], hotness=self.hotness,
+                               hot_base=self.hot_base, T=self.Tl, B=self.B, D=self.D, B_local=self.Bl,
+                               dst_table=twin.table, dst_row_stride=self.F * self.D, dst_col=self.dst_col,
+                               out_bf16=True, row_idx=self.row_idx, occ2bag=self.occ2bag, status=st)
+                self._count()
+            return
+        gd = self._grid_done
+        if self.K:
+            # row-sharded tables, step 1: the ids of my samples go to their owners (+ CH_KEYS)
+            F_.rw_push_keys(self.in_ids_rw[slot], self.id_base_rw, self.hot_rw, self.key_base_rw, self.K, self.Bl,
+                            self.B, self.key_win.table, self.cnt_win.table, self.occ_cursor, ctx=self.ctx,
+                            sig_channel=CH_KEYS, sig_done=gd[0:1], status=st)
+            self._count()
+        if self.Tw:
+            # whole tables: pooled rows go straight into the samples' ranks; the kernel publishes CH_FWD itself
+            F_.emb_forward_ex(self.weight, self.table_base_w, self.table_rows_w, self.in_ids[slot], self.hotness,
+                              self.hot_base, T=self.Tw, B=self.B, D=self.D, B_local=self.Bl, dst_table=twin.table,
+                              dst_row_stride=self.F * self.D, dst_col=self.dst_col, row_idx=self.row_idx,
+                              occ2bag=self.occ2bag, status=st, ctx=self.ctx, sig_channel=CH_FWD, sig_done=gd[1:2])
+        else:
+            self.ctx.signal(CH_FWD)
+        self._count()
+        if self.K:
+            # step 2 (owner side): wait for each source rank's keys, pool my share of every bag, push the partial
+            # sums into the samples' ranks (+ CH_PART); step 3: add the partials up into the feature slots
+            F_.emb_forward_ex(self.weight, self.table_base, self.table_rows, self.key_win.local_ptr, self.hot_rw,
+                              self.key_base_rw, T=self.K, B=self.B, D=self.D, B_local=self.Bl,
+                              dst_table=self.part_win.table, dst_row_stride=self.K * self.world * self.D,
+                              dst_col=self.part_col, row_idx=self.row_idx_rw, occ2bag=self.occ2bag_rw, status=st,
+                              counts=self.cnt_win.local_ptr, id_div=self.world, id_rem=self.rank,
+                              occ_cursor=self.occ_cursor, ctx=self.ctx, wait_channel=CH_KEYS, sig_channel=CH_PART,
+                              sig_done=gd[2:3])
+            F_.rw_reduce_partials(self.part_win.local_ptr, self._T[slot][1], self.red_col, self.Bl, self.K, self.D,
+                                  ctx=self.ctx, wait_channel=CH_PART, status=st)
+            self._count(2)
+
+    def _forward(self, slot: int, lookup: bool = True):
         c, st = self.cfg, self.ctx.status
+        self._bind_slot(slot)
         self._stamp("start")
         F_.pad_cast_bf16(self.in_dense[slot], self.x0p); self._count()
         main = torch.cuda.current_stream(self.dev)
-        overlap = True   # the lookup (bound by HBM, and by NVLink when multi-GPU) runs beside the bottom MLP (bound by the tensor pipe)
-        if overlap:
+        if lookup:
+            # the lookup (bound by HBM, and by NVLink when multi-GPU) runs beside the bottom MLP (bound by the tensor pipe)
             self.s_comm.wait_stream(main)
-        with torch.cuda.stream(self.s_comm if overlap else main):
-            if self.world == 1:
-                if self.Tl:
-                    F_.emb_forward(self.weight, self.table_base, self.table_rows, self.in_ids[slot], hotness=self.hotness,
-                                   hot_base=self.hot_base, T=self.Tl, B=self.B, D=self.D, B_local=self.Bl,
-                                   dst_table=self.Twin.table, dst_row_stride=self.F * self.D, dst_col=self.dst_col,
-                                   out_bf16=True, row_idx=self.row_idx, occ2bag=self.occ2bag, status=st)
-                    self._count()
-            else:
-                gd = self._grid_done
-                if self.K:
-                    # row-sharded tables, step 1: the ids of my samples go to their owners (+ CH_KEYS)
-                    F_.rw_push_keys(self.in_ids_rw[slot], self.id_base_rw, self.hot_rw, self.key_base_rw, self.K, self.Bl,
-                                    self.B, self.key_win.table, self.cnt_win.table, self.occ_cursor, ctx=self.ctx,
-                                    sig_channel=CH_KEYS, sig_done=gd[0:1], status=st)
-                    self._count()
-                if self.Tw:
-                    # whole tables: pooled rows go straight into the samples' ranks; the kernel publishes CH_FWD itself
-                    F_.emb_forward_ex(self.weight, self.table_base_w, self.table_rows_w, self.in_ids[slot], self.hotness,
-                                      self.hot_base, T=self.Tw, B=self.B, D=self.D, B_local=self.Bl, dst_table=self.Twin.table,
-                                      dst_row_stride=self.F * self.D, dst_col=self.dst_col, row_idx=self.row_idx,
-                                      occ2bag=self.occ2bag, status=st, ctx=self.ctx, sig_channel=CH_FWD, sig_done=gd[1:2])
-                else:
-                    self.ctx.signal(CH_FWD)
-                self._count()
-                if self.K:
-                    # step 2 (owner side): wait for each source rank's keys, pool my share of every bag, push the partial
-                    # sums into the samples' ranks (+ CH_PART); step 3: add the partials up into the feature slots
-                    F_.emb_forward_ex(self.weight, self.table_base, self.table_rows, self.key_win.local_ptr, self.hot_rw,
-                                      self.key_base_rw, T=self.K, B=self.B, D=self.D, B_local=self.Bl,
-                                      dst_table=self.part_win.table, dst_row_stride=self.K * self.world * self.D,
-                                      dst_col=self.part_col, row_idx=self.row_idx_rw, occ2bag=self.occ2bag_rw, status=st,
-                                      counts=self.cnt_win.local_ptr, id_div=self.world, id_rem=self.rank,
-                                      occ_cursor=self.occ_cursor, ctx=self.ctx, wait_channel=CH_KEYS, sig_channel=CH_PART,
-                                      sig_done=gd[2:3])
-                    F_.rw_reduce_partials(self.part_win.local_ptr, self.Tbuf, self.red_col, self.Bl, self.K, self.D,
-                                          ctx=self.ctx, wait_channel=CH_PART, status=st)
-                    self._count(2)
+            with torch.cuda.stream(self.s_comm):
+                self._lookup(slot)
         self._stamp("emb_fwd_done")
         x = self.x0p
         for i, L in enumerate(self.bot):
@@ -515,7 +546,8 @@ class DLRM:
             F_.gemm_bf16(x, L.wb, out, mode=0, epi=F_.EPI_RELU, bias=L.b, status=st, n=L.N); self._count()
             x = out
         self._stamp("bot_fwd_done")
-        main.wait_stream(self.s_comm)
+        if lookup:
+            main.wait_stream(self.s_comm)         # (without a lookup of its own the step started after the one it relies on)
         if self.world > 1 and (self.dcn or self.proj):
             self.ctx.wait_own(CH_FWD); self._count()     # the consumer is a GEMM fed by TMA: it cannot wait in its own prologue
         self._stamp("a2a_fwd_arrived")
@@ -546,10 +578,13 @@ class DLRM:
             x = self.act_t[i]
         return x
 
-    def _run_step(self, slot: int):
+    def _run_step(self, slot: int, mode: str = "self"):
+        """One training step on input slot ``slot``.  ``mode``: "self" = with its own lookup at the start; "none" = the
+        rows of this batch are already on their way (a previous graph looked them up); "next" = like "none", and the
+        lookup of the OTHER slot's batch runs at the end of this step, behind the sparse optimizer."""
         c, st = self.cfg, self.ctx.status
         self.launches_per_step = 0
-        x = self._forward(slot)
+        x = self._forward(slot, lookup=(mode == "self"))
         self._stamp("top_fwd_done")
         self._loss_dev[slot].zero_(); self._count()
         F_.head_bce(x, self.head_w, self.head_b, self.in_labels[slot], 1.0 / self.B, prob=self.prob,
@@ -695,6 +730,10 @@ class DLRM:
                                 grad_bf16=True, lr=c.emb_lr, eps=c.emb_eps, optimizer=c.emb_optimizer, status=st,
                                 gnorm=self.gnorm, gnorm_stride=self.Tmax)
                 self._count(2 if c.emb_optimizer == "rowwise_adagrad" else 1)
+            if mode == "next":
+                # The tables now hold this step's update: the next batch's lookup + forward all-to-all can go, beside the
+                # bottom MLP's backward, the dense all-reduce and the SGD step that are still to come.
+                self._lookup(1 - slot)
         self._stamp("interaction_bwd_done")
         # ---- bottom MLP backward
         for i in range(len(self.bot) - 1, -1, -1):
@@ -739,11 +778,8 @@ class DLRM:
         self._stamp("sgd_done")
 
     # ------------------------------------------------------------------ public API
-    def submit(self, batch: PinnedBatch) -> StepHandle:
-        """Enqueues H2D copies of ``batch`` and one training step; returns immediately."""
-        slot = self._step_no & 1
-        self._step_no += 1
-        cs, ms = self.copy_stream, self.compute_stream
+    def _copy_in(self, batch: PinnedBatch, slot: int):
+        cs = self.copy_stream
         with torch.cuda.stream(cs):
             cs.wait_event(self._consumed[slot])       # previous user of this slot has finished
             self.in_dense[slot].copy_(batch.dense, non_blocking=True)
@@ -752,57 +788,115 @@ class DLRM:
                 self.in_ids_rw[slot].copy_(batch.ids_rw, non_blocking=True)
             self.in_labels[slot].copy_(batch.labels, non_blocking=True)
             self._copied[slot].record(cs)
+
+    def _launch(self, slot: int, mode: str):
+        """Step graph (or eager launch sequence) of input slot ``slot`` on the compute stream, then the result copies."""
+        ms = self.compute_stream
         with torch.cuda.stream(ms):
-            ms.wait_event(self._copied[slot])
             if self.cfg.use_cuda_graph:
-                g = self._graphs.get(slot)
+                g = self._graphs.get((slot, mode))
                 if g is None:
-                    g = self._capture(slot)
+                    g = self._capture(slot, mode)
                 g.replay()
             else:
-                self._run_step(slot)
+                self._run_step(slot, mode)
             self._consumed[slot].record(ms)
             self._loss_host[slot].copy_(self._loss_dev[slot], non_blocking=True)
             self._status_host[slot].copy_(self.ctx.status, non_blocking=True)
             self._done[slot].record(ms)
-        return StepHandle(self, slot, self._done[slot])
+        self._launched += 1
+
+    def _launch_lookup(self, slot: int):
+        ms = self.compute_stream
+        with torch.cuda.stream(ms):
+            if self.cfg.use_cuda_graph:
+                g = self._graphs.get((slot, "lookup"))
+                if g is None:
+                    g = self._capture(slot, "lookup")
+                g.replay()
+            else:
+                self._run_lookup(slot)
+
+    def _run_lookup(self, slot: int):
+        main = torch.cuda.current_stream(self.dev)
+        self.s_comm.wait_stream(main)
+        with torch.cuda.stream(self.s_comm):
+            self._lookup(slot)
+        main.wait_stream(self.s_comm)
+
+    def flush(self) -> None:
+        """Pipelined mode: launches the step that is still waiting for its successor (without a look-ahead)."""
+        if self._pending is not None:
+            slot, self._pending = self._pending, None
+            self._launch(slot, "none")
+
+    def submit(self, batch: PinnedBatch) -> StepHandle:
+        """Enqueues H2D copies of ``batch`` and one training step; returns immediately.  With ``pipeline_lookup`` the
+        step itself is launched when the NEXT batch is submitted (its graph ends with that batch's lookup) or when its
+        result is asked for; the lookup of this batch is launched now."""
+        slot = self._step_no & 1
+        step = self._step_no
+        self._step_no += 1
+        self._copy_in(batch, slot)
+        ms = self.compute_stream
+        with torch.cuda.stream(ms):
+            ms.wait_event(self._copied[slot])
+        if not self._pipe:
+            self._launch(slot, "self")
+        elif self._pending is None:
+            self._launch_lookup(slot)                  # nothing to hide it behind: the pipeline starts here
+            self._pending = slot
+        else:
+            self._launch(self._pending, "next")        # the previous step, ending with this batch's lookup
+            self._pending = slot
+        return StepHandle(self, slot, self._done[slot], step)
 
     def train_step(self, batch: PinnedBatch) -> float:
         return self.submit(batch).result()
 
     def time_steps_on_device(self, steps: int) -> float:
         """Runs ``steps`` training steps on the batches already resident in the two input slots and
-        returns the elapsed milliseconds measured with CUDA events on the compute stream."""
+        returns the elapsed milliseconds measured with CUDA events on the compute stream.  Pipelined mode: the lookup of
+        the first batch precedes the timed region, every timed step ends with the lookup of the following batch (so the
+        region holds ``steps`` lookups and ``steps`` dense passes, like the unpipelined one)."""
+        self.flush()
         ms = self.compute_stream
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize(self.dev)
+        mode = "next" if self._pipe else "self"
         with torch.cuda.stream(ms):
             if self.cfg.use_cuda_graph:
                 for slot in (0, 1):
-                    if slot not in self._graphs:
-                        self._capture(slot)
+                    if (slot, mode) not in self._graphs:
+                        self._capture(slot, mode)
+            if self._pipe:
+                self._launch_lookup(0)
             e0.record(ms)
             for i in range(steps):
                 slot = i & 1
                 if self.cfg.use_cuda_graph:
-                    self._graphs[slot].replay()
+                    self._graphs[(slot, mode)].replay()
                 else:
-                    self._run_step(slot)
+                    self._run_step(slot, mode)
             e1.record(ms)
         e1.synchronize()
         return e0.elapsed_time(e1)
 
-    def _capture(self, slot: int) -> torch.cuda.CUDAGraph:
+    def _capture(self, slot: int, mode: str = "self") -> torch.cuda.CUDAGraph:
         torch.cuda.current_stream().synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=torch.cuda.current_stream(), capture_error_mode="relaxed"):
-            self._run_step(slot)
-        self._graphs[slot] = g
+            if mode == "lookup":
+                self._run_lookup(slot)
+            else:
+                self._run_step(slot, mode)
+        self._graphs[(slot, mode)] = g
         return g
 
     @torch.no_grad()
     def predict(self, batch: PinnedBatch) -> torch.Tensor:
         """Click probabilities of this rank's samples (inference, no parameter update)."""
+        self.flush()
         with torch.cuda.stream(self.compute_stream):
             self.in_dense[0].copy_(batch.dense, non_blocking=True)
             self.in_ids[0].copy_(batch.ids, non_blocking=True)
@@ -821,6 +915,7 @@ class DLRM:
         return out
 
     def check(self):
+        self.flush()
         self.ctx.check_status()
 
     # ------------------------------------------------------------------ state access (tests, checkpoints)
@@ -830,6 +925,8 @@ class DLRM:
                 ("proj1", self.projB[0]), ("proj2", self.projB[1]))
 
     def dense_state(self) -> Dict[str, torch.Tensor]:
+        self.flush()
+        torch.cuda.synchronize(self.dev)
         out = {}
         for name, Ls in self._named_layers():
             for i, L in enumerate(Ls):
@@ -859,6 +956,7 @@ class DLRM:
 
     def save_checkpoint(self, path: str, step: int = 0) -> None:
         from .checkpoint import save_checkpoint
+        self.flush()
         torch.cuda.synchronize(self.dev)
         save_checkpoint(self, path, step)
 
@@ -872,6 +970,8 @@ class DLRM:
         """Collective: the whole table ``t`` (``what`` = "weight" or "state") on rank 0, wherever its rows live (``None``
         on the other ranks).  Tests and checkpoint tools use it; rows of a row-sharded table are re-interleaved."""
         import torch.distributed as dist
+        self.flush()
+        torch.cuda.synchronize(self.dev)
         mine = (self.table_weight if what == "weight" else self.table_state)
         n = self.cfg.table_rows[t]
         shape = (n, self.D) if what == "weight" else (n,)

@@ -196,6 +196,70 @@ def test_dlrm_row_sharded_tables_match_single(kind):
     assert all(out.get(r) == "ok" for r in range(world)), dict(out)
 
 
+def _pipe_worker(rank, world, port, out):
+    """Pipelined lookup on several GPUs against the single-GPU engine: a chain of submits whose results are read one step
+    late (every step's graph ends with the next batch's lookup and forward all-to-all)."""
+    dist = _init(rank, world, port)
+    try:
+        from recstore_b200.models.dlrm import DLRM, DLRMConfig
+        from recstore_b200.parallel.peer import PeerContext
+        from recstore_b200.utils.data import DLRMBatchSource
+        rows = [1000, 37, 5000, 12, 300, 20000, 64, 900]
+        hot = [1, 2, 1, 3, 1, 1, 1, 1]
+        B = 512 if world <= 4 else 1024
+        kw = dict(table_rows=rows, batch=B, hotness=hot, emb_lr=0.05, mlp_lr=0.05, seed=5)
+        ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"))
+        eng = DLRM(DLRMConfig(pipeline_lookup=True, **kw), ctx)
+        assert eng._pipe
+        solo = DLRM(DLRMConfig(**kw)) if rank == 0 else None
+        src = DLRMBatchSource(rows, hot, B, alpha=1.2, seed=9)
+        batches = [src.next() for _ in range(4)]
+        got, prev = [], None
+        for b in batches:
+            h = eng.submit(eng.make_pinned_batch(b.dense, b.ids, b.labels))
+            if prev is not None:
+                got.append(prev.result())
+            prev = h
+        got.append(prev.result())
+        eng.check()
+        lt = torch.tensor(got, device="cuda", dtype=torch.float64)
+        dist.all_reduce(lt)
+        tabs = [eng.gather_table(t) for t in range(len(rows))]
+        if rank == 0:
+            ref = [solo.train_step(solo.make_pinned_batch(b.dense, b.ids, b.labels)) for b in batches]
+            for i, (a, r) in enumerate(zip(lt.tolist(), ref)):
+                assert abs(a - r) < (2e-3 if i == 0 else 5e-3) * max(1.0, abs(r)), (i, lt.tolist(), ref)
+            rel = lambda a, b: ((a - b).norm() / (b.norm() + 1e-20)).item()
+            for t in range(len(rows)):
+                assert rel(tabs[t], solo.table_weight(t)) < 5e-2, (t, rel(tabs[t], solo.table_weight(t)))
+            sd, sr = eng.dense_state(), solo.dense_state()
+            for k in sd:
+                assert rel(sd[k], sr[k]) < 5e-2, (k, rel(sd[k], sr[k]))
+        else:
+            eng.dense_state()
+        ms = eng.time_steps_on_device(4)          # look-ahead graphs back to back, then a normal step
+        assert ms > 0
+        b = src.next()
+        eng.train_step(eng.make_pinned_batch(b.dense, b.ids, b.labels))
+        eng.check()
+        dist.barrier()
+        out[rank] = "ok"
+    except BaseException as e:          # noqa: BLE001
+        _leave(dist, rank, out, e)
+    _leave(dist, rank, out, None)
+
+
+def test_dlrm_pipelined_lookup_matches_single():
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    world = _world()
+    mgr = mp.Manager()
+    out = mgr.dict()
+    _spawn(_pipe_worker, (world, _free_port(), out), world)
+    assert all(out.get(r) == "ok" for r in range(world)), dict(out)
+
+
 def _timeout_worker(rank, world, port, out):
     """A wait whose signal never comes must return an error status, not hang, and leave the context usable."""
     dist = _init(rank, world, port)
