@@ -18,6 +18,8 @@
 // all2all_data_transfer (recstore/utils.py:227-310) done by three kernels and peer stores, with no
 // host staging, no pack / unpack and no collective call.
 #include <cuda_bf16.h>
+#include <cstdlib>
+
 #include "comm/flags.cuh"
 #include "common/rs_common.h"
 #include "kv/hash_table.cuh"
@@ -177,6 +179,104 @@ __global__ void __launch_bounds__(256) segment_sum_kernel(const float* __restric
   }
 }
 
+// The same sum with duplicates combined inside the CTA first.  With skewed keys the plain kernel sends tens of
+// thousands of atomics to the hottest row (47,000 of 262,144 occurrences at Zipf 1.1: they serialise in L2 and set the
+// kernel's time).  Here a CTA takes 512 occurrences, counts its distinct keys in a shared-memory hash table, gives every
+// key that occurs more than once a row in shared memory, adds those occurrences there (shared-memory atomics) and sends
+// ONE global atomic per such key; keys that occur once in the chunk, or that found no free row, go to global memory
+// directly, so a batch without duplicates pays only the counting pass.
+constexpr int kSegChunk = 512, kSegSlots = 1024, kSegMaxRows = 64;
+__device__ __forceinline__ unsigned seg_hash(int u) { return (static_cast<unsigned>(u) * 2654435761u) >> 22; }   // 10 bits
+
+__global__ void __launch_bounds__(256) segment_sum_combine_kernel(const float* __restrict__ grad, const int* __restrict__ inverse,
+                                                                  long long n, int D, int R, float* __restrict__ ugrad,
+                                                                  float* __restrict__ unorm) {
+  extern __shared__ __align__(16) unsigned char seg_smem[];
+  int* hkey = reinterpret_cast<int*>(seg_smem);            // [kSegSlots] unique index or -1
+  int* hcnt = hkey + kSegSlots;                            // [kSegSlots] occurrences in this chunk
+  int* hrow = hcnt + kSegSlots;                            // [kSegSlots] shared row of the key or -1
+  int* rkey = hrow + kSegSlots;                            // [kSegMaxRows] unique index of a shared row
+  float* rnorm = reinterpret_cast<float*>(rkey + kSegMaxRows);   // [kSegMaxRows]
+  float* rows = rnorm + kSegMaxRows;                       // [R, D]
+  __shared__ int nrow;
+  const long long c0 = static_cast<long long>(blockIdx.x) * kSegChunk;
+  const int cn = static_cast<int>(min(static_cast<long long>(kSegChunk), n - c0));
+  for (int s = threadIdx.x; s < kSegSlots; s += blockDim.x) { hkey[s] = -1; hcnt[s] = 0; }
+  for (int v = threadIdx.x; v < R * D; v += blockDim.x) rows[v] = 0.f;
+  for (int r = threadIdx.x; r < kSegMaxRows; r += blockDim.x) rnorm[r] = 0.f;
+  if (threadIdx.x == 0) nrow = 0;
+  __syncthreads();
+  // 1: count the distinct keys of the chunk
+  for (int j = threadIdx.x; j < cn; j += blockDim.x) {
+    const int u = inverse[c0 + j];
+    if (u < 0) continue;
+    unsigned s = seg_hash(u);
+    for (int probe = 0; probe < kSegSlots; ++probe, s = (s + 1) & (kSegSlots - 1)) {
+      const int prev = atomicCAS(&hkey[s], -1, u);
+      if (prev == -1 || prev == u) { atomicAdd(&hcnt[s], 1); break; }
+    }
+  }
+  __syncthreads();
+  // 2: a shared row for every key that occurs more than once (while rows last)
+  for (int s = threadIdx.x; s < kSegSlots; s += blockDim.x) {
+    int r = -1;
+    if (hcnt[s] > 1) {
+      r = atomicAdd(&nrow, 1);
+      if (r < R) rkey[r] = hkey[s];
+      else r = -1;
+    }
+    hrow[s] = r;
+  }
+  __syncthreads();
+  // 3: add every occurrence to its shared row, or straight to global memory (four occurrences in flight per warp)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int nvec = D >> 2;                                  // D <= 128: one float4 per lane
+  for (int j0 = warp * 4; j0 < cn; j0 += nwarp * 4) {
+    int u[4], r[4];
+    float4 g[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int j = j0 + q;
+      u[q] = j < cn ? inverse[c0 + j] : -1;
+      g[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (u[q] >= 0 && lane < nvec) g[q] = __ldg(reinterpret_cast<const float4*>(grad + (c0 + j) * D) + lane);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (u[q] < 0) continue;
+      unsigned s = seg_hash(u[q]);
+      while (hkey[s] != u[q]) s = (s + 1) & (kSegSlots - 1);
+      r[q] = hrow[s];
+      float sq = g[q].x * g[q].x + g[q].y * g[q].y + g[q].z * g[q].z + g[q].w * g[q].w;
+      if (lane < nvec) {
+        if (r[q] >= 0) {
+          float* d = rows + r[q] * D + lane * 4;
+          atomicAdd(d, g[q].x); atomicAdd(d + 1, g[q].y); atomicAdd(d + 2, g[q].z); atomicAdd(d + 3, g[q].w);
+        } else {
+          atomicAdd(reinterpret_cast<float4*>(ugrad + static_cast<long long>(u[q]) * D) + lane, g[q]);
+        }
+      }
+      if (unorm) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0) {
+          if (r[q] >= 0) atomicAdd(&rnorm[r[q]], sq);
+          else atomicAdd(&unorm[u[q]], sq);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // 4: one global atomic per combined key
+  const int used = min(nrow, R);
+  for (int r = warp; r < used; r += nwarp) {
+    const int u = rkey[r];
+    for (int v = lane; v < (D >> 2); v += 32)
+      atomicAdd(reinterpret_cast<float4*>(ugrad + static_cast<long long>(u) * D) + v, *reinterpret_cast<const float4*>(rows + r * D + v * 4));
+    if (unorm && lane == 0) atomicAdd(&unorm[u], rnorm[r]);
+  }
+}
+
 // out[i] = src[inverse[i]]
 __global__ void __launch_bounds__(256) expand_rows_kernel(const float* __restrict__ src, const int* __restrict__ inverse, long long n,
                                                           int D, float* __restrict__ out) {
@@ -273,7 +373,22 @@ RS_API int rs_segment_sum(const float* grad, const int* inverse, long long n, in
                           cudaStream_t stream) {
   RS_REQUIRE(grad && inverse && ugrad && D % 4 == 0, "rs_segment_sum: bad argument");
   if (n == 0) return RS_OK;
-  segment_sum_kernel<<<warps_grid(n), 256, 0, stream>>>(grad, inverse, n, D, ugrad, unorm);
+  // RECSTORE_SEGMENT_SUM=direct keeps the one-atomic-per-occurrence kernel (A/B); rows wider than 128 floats use it too.
+  static const bool combine = [] { const char* e = getenv("RECSTORE_SEGMENT_SUM"); return !(e && e[0] == 'd'); }();
+  if (combine && D <= 128 && n >= 131072) {   // measured: below ~100 k occurrences the four passes inside a CTA cost more than the hot atomics
+    int R = (32 * 1024) / (D * 4);
+    if (R > kSegMaxRows) R = kSegMaxRows;
+    const size_t smem = static_cast<size_t>(kSegSlots) * 12 + kSegMaxRows * 8 + static_cast<size_t>(R) * D * 4;
+    static bool attr_done = false;
+    if (!attr_done) {
+      RS_CUDA(cudaFuncSetAttribute(segment_sum_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      attr_done = true;
+    }
+    const unsigned grid = static_cast<unsigned>((n + kSegChunk - 1) / kSegChunk);
+    segment_sum_combine_kernel<<<grid, 256, smem, stream>>>(grad, inverse, n, D, R, ugrad, unorm);
+  } else {
+    segment_sum_kernel<<<warps_grid(n), 256, 0, stream>>>(grad, inverse, n, D, ugrad, unorm);
+  }
   RS_LAUNCH_CHECK();
   return RS_OK;
 }

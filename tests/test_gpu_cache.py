@@ -411,3 +411,31 @@ def test_hash_cache_embeddings_stay_coherent_with_the_host_table(choice):
                          "--backwardMode", "CppSync", "--batch_size", "2000", "--num_embs", "20000", "--cache_ratio", "0.02",
                          "--log_interval", "1000"])
     assert len(out) == 1 and out[0][0] == 30 and out[0][1] < 1e-3, out
+
+
+@pytest.mark.parametrize("D,alpha", [(32, 1.2), (128, 1.05), (32, 0.0), (400, 1.2)])
+def test_segment_sum_of_duplicate_keys_matches_index_add(D, alpha):
+    """Folding the gradients of duplicate keys (sum and sum of squared norms per unique key): skewed keys go through the
+    CTA-level combine (hot keys meet in shared memory first), keys without duplicates and rows wider than 128 floats take
+    the direct path; entries marked -1 are skipped.  Oracle: torch.index_add_ in fp64."""
+    from recstore_b200 import _lib
+    from recstore_b200._lib import ptr, stream_ptr
+    from recstore_b200.parallel import sharded_table  # noqa: F401  (registers rs_segment_sum)
+    from recstore_b200.utils.data import zipf_ids_torch
+    dev = torch.device("cuda:0")
+    n, U = 150_000, 20_000
+    if alpha > 0:
+        inv = zipf_ids_torch(n, U, alpha, device=dev).to(torch.int32)
+    else:
+        inv = torch.randperm(n, device=dev)[:n].to(torch.int32) % U      # every key at most three times
+    inv[::97] = -1
+    g = torch.randn(n, D, device=dev)
+    ug = torch.zeros(U, D, device=dev)
+    un = torch.zeros(U, device=dev)
+    _lib.call("rs_segment_sum", ptr(g), ptr(inv), n, D, ptr(ug), ptr(un), stream_ptr())
+    torch.cuda.synchronize()
+    keep = inv >= 0
+    ref = torch.zeros(U, D, device=dev, dtype=torch.float64).index_add_(0, inv[keep].long(), g[keep].double())
+    refn = torch.zeros(U, device=dev, dtype=torch.float64).index_add_(0, inv[keep].long(), g[keep].double().pow(2).sum(1))
+    assert (ug.double() - ref).abs().max().item() < 1e-3 * max(1.0, ref.abs().max().item())
+    assert (un.double() - refn).abs().max().item() < 1e-4 * max(1.0, refn.abs().max().item())
