@@ -727,7 +727,9 @@ __global__ void __launch_bounds__(128) shard_scatter_rows_kernel(const ScatterAr
 
 int persistent_grid(long long items, int warps_per_block) {
   long long g = (items + warps_per_block - 1) / warps_per_block;
-  const long long capg = 148 * 8;
+  // CTAs per SM of the persistent exchange kernels (RECSTORE_SHARD_CTAS_PER_SM, default 8; 16 and 32 measured within 2 %).
+  static const int per_sm = [] { const char* e = getenv("RECSTORE_SHARD_CTAS_PER_SM"); const int v = e ? atoi(e) : 0; return v > 0 ? v : 8; }();
+  const long long capg = 148ll * per_sm;
   if (g > capg) g = capg;
   if (g < 1) g = 1;
   return static_cast<int>(g);
