@@ -401,7 +401,7 @@ def main():
     ap.add_argument("--workload", default="dlrm", choices=["dlrm", "dcnv2", "kge"],
                     help="dlrm: the headline config; dcnv2: the multi-hot DLRM-DCNv2 config; kge: knowledge-graph embedding training "
                          "(native arm only for the last two)")
-    ap.add_argument("--kge-model", default="TransE_l2", choices=["TransE_l2", "DistMult", "ComplEx", "SimplE", "TransE_l1", "RotatE"])
+    ap.add_argument("--kge-model", default="TransE_l2", choices=["TransE_l2", "DistMult", "ComplEx", "SimplE", "TransE_l1", "RotatE", "RESCAL"])
     ap.add_argument("--kge-entities", type=int, default=86_054_151, help="entities of the kge workload (the config's Freebase count)")
     ap.add_argument("--row-split", default="auto",
                     help="dcnv2 workload: tables spread row-wise over the GPUs: auto (those with more than 1/N of the ids per sample), "

@@ -11,7 +11,7 @@ that each worker's hot entities are contiguous -> one training process per worke
 
 Engines: on ``--device cuda`` TransE (L1 / L2), DistMult, ComplEx, SimplE and RotatE run on the native path (entity and
 relation tables row-sharded over the GPUs' HBM; tcgen05 scoring where the negative scores are cross products, fp32 pair
-kernels for the L1 / modulus distances); TransR and RESCAL, and ``--device cpu``, run the PyTorch implementation on
+kernels for the L1 / modulus distances; RESCAL with a row-blocked matrix table); TransR, and ``--device cpu``, run the PyTorch implementation on
 tables shared between the worker processes (lock-free updates, as the reference's stock path does).  Prints
 ``Successfully xmh`` when done.
 
@@ -32,7 +32,7 @@ import time
 import numpy as np
 import torch
 
-NATIVE_MODELS = ("TransE", "TransE_l1", "TransE_l2", "DistMult", "ComplEx", "SimplE", "RotatE")
+NATIVE_MODELS = ("TransE", "TransE_l1", "TransE_l2", "DistMult", "ComplEx", "SimplE", "RotatE", "RESCAL")
 
 
 def parse_args(argv=None):

@@ -159,8 +159,11 @@ __global__ void __launch_bounds__(256) push_grads_kernel(const float* __restrict
 // ugrad[inverse[i]] += grad[i], unorm[inverse[i]] += |grad[i]|^2   (segment-sum of duplicate keys before the
 // exchange; both outputs zeroed by the caller).  The separate sum of squares keeps row-wise Adagrad exact:
 // its state needs the sum over occurrences of mean(g^2), not the square of the summed gradient.
+// occ_norm (optional): the squared norm to account for occurrence i instead of |grad[i]|^2 (a caller whose rows are
+// slices of a wider object, e.g. the rows of a relation matrix, passes the norm of the whole object).
 __global__ void __launch_bounds__(256) segment_sum_kernel(const float* __restrict__ grad, const int* __restrict__ inverse,
-                                                          long long n, int D, float* __restrict__ ugrad, float* __restrict__ unorm) {
+                                                          long long n, int D, float* __restrict__ ugrad, float* __restrict__ unorm,
+                                                          const float* __restrict__ occ_norm) {
   const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (i >= n) return;
   const int lane = threadIdx.x & 31;
@@ -175,7 +178,7 @@ __global__ void __launch_bounds__(256) segment_sum_kernel(const float* __restric
   if (unorm) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    if (lane == 0) atomicAdd(&unorm[u], sq);
+    if (lane == 0) atomicAdd(&unorm[u], occ_norm ? occ_norm[i] : sq);
   }
 }
 
@@ -190,7 +193,7 @@ __device__ __forceinline__ unsigned seg_hash(int u) { return (static_cast<unsign
 
 __global__ void __launch_bounds__(256) segment_sum_combine_kernel(const float* __restrict__ grad, const int* __restrict__ inverse,
                                                                   long long n, int D, int R, float* __restrict__ ugrad,
-                                                                  float* __restrict__ unorm) {
+                                                                  float* __restrict__ unorm, const float* __restrict__ occ_norm) {
   extern __shared__ __align__(16) unsigned char seg_smem[];
   int* hkey = reinterpret_cast<int*>(seg_smem);            // [kSegSlots] unique index or -1
   int* hcnt = hkey + kSegSlots;                            // [kSegSlots] occurrences in this chunk
@@ -260,6 +263,7 @@ __global__ void __launch_bounds__(256) segment_sum_combine_kernel(const float* _
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
         if (lane == 0) {
+          if (occ_norm) sq = occ_norm[c0 + j0 + q];
           if (r[q] >= 0) atomicAdd(&rnorm[r[q]], sq);
           else atomicAdd(&unorm[u[q]], sq);
         }
@@ -369,9 +373,11 @@ RS_API int rs_shard_push_grads(const float* grad, const long long* slot, long lo
   return RS_OK;
 }
 
-RS_API int rs_segment_sum(const float* grad, const int* inverse, long long n, int D, float* ugrad, float* unorm,
-                          cudaStream_t stream) {
+namespace {
+int segment_sum_impl(const float* grad, const int* inverse, long long n, int D, float* ugrad, float* unorm, const float* occ_norm,
+                     cudaStream_t stream) {
   RS_REQUIRE(grad && inverse && ugrad && D % 4 == 0, "rs_segment_sum: bad argument");
+  RS_REQUIRE(!occ_norm || unorm, "rs_segment_sum: per-occurrence norms need the norm output");
   if (n == 0) return RS_OK;
   // RECSTORE_SEGMENT_SUM=direct keeps the one-atomic-per-occurrence kernel (A/B); rows wider than 128 floats use it too.
   static const bool combine = [] { const char* e = getenv("RECSTORE_SEGMENT_SUM"); return !(e && e[0] == 'd'); }();
@@ -385,12 +391,23 @@ RS_API int rs_segment_sum(const float* grad, const int* inverse, long long n, in
       attr_done = true;
     }
     const unsigned grid = static_cast<unsigned>((n + kSegChunk - 1) / kSegChunk);
-    segment_sum_combine_kernel<<<grid, 256, smem, stream>>>(grad, inverse, n, D, R, ugrad, unorm);
+    segment_sum_combine_kernel<<<grid, 256, smem, stream>>>(grad, inverse, n, D, R, ugrad, unorm, occ_norm);
   } else {
-    segment_sum_kernel<<<warps_grid(n), 256, 0, stream>>>(grad, inverse, n, D, ugrad, unorm);
+    segment_sum_kernel<<<warps_grid(n), 256, 0, stream>>>(grad, inverse, n, D, ugrad, unorm, occ_norm);
   }
   RS_LAUNCH_CHECK();
   return RS_OK;
+}
+}  // namespace
+
+RS_API int rs_segment_sum(const float* grad, const int* inverse, long long n, int D, float* ugrad, float* unorm,
+                          cudaStream_t stream) {
+  return segment_sum_impl(grad, inverse, n, D, ugrad, unorm, nullptr, stream);
+}
+// occ_norm [n]: squared norm accounted for every occurrence instead of |grad[i]|^2.
+RS_API int rs_segment_sum_ex(const float* grad, const int* inverse, long long n, int D, float* ugrad, float* unorm,
+                             const float* occ_norm, cudaStream_t stream) {
+  return segment_sum_impl(grad, inverse, n, D, ugrad, unorm, occ_norm, stream);
 }
 
 RS_API int rs_expand_rows(const float* src, const int* inverse, long long n, int D, float* out, cudaStream_t stream) {

@@ -34,7 +34,9 @@
 
 namespace {
 
-enum : int { kTransE2 = 0, kDistMult = 1, kComplEx = 2, kSimplE = 3, kTransE1 = 4, kRotatE = 5 };
+enum : int { kTransE2 = 0, kDistMult = 1, kComplEx = 2, kSimplE = 3, kTransE1 = 4, kRotatE = 5, kRescal = 6 };
+__host__ __device__ __forceinline__ bool is_pairwise(int model) { return model == kTransE1 || model == kRotatE; }
+constexpr int kRescalCols = 16;   // columns of the relation matrix per lane: D <= 512
 constexpr float kPi = 3.14159265358979323846f;
 
 struct KgeArgs {
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(256) kge_prepare_kernel(const KgeArgs k) {
   const int D = k.D, H = k.D >> 1;
   if (row >= k.bs + k.C * k.ns) return;
   if (row >= k.bs) {
-    if (k.model >= kTransE1) return;                 // the pairwise kernels read the fp32 rows themselves
+    if (is_pairwise(k.model)) return;                // the pairwise kernels read the fp32 rows themselves
     const int j = row - k.bs;
     float s = 0.f;
     for (int d = lane; d < k.Dp; d += 32) {
@@ -173,6 +175,66 @@ __global__ void __launch_bounds__(256) kge_prepare_kernel(const KgeArgs k) {
   const float* x = ch ? t : h;
   const float* y = ch ? h : t;
   float* gy = ch ? gh : gt;
+  if (k.model == kRescal) {
+    // RESCAL: score = h^T M t with one D x D matrix M per relation (row-major in r).  Tails corrupted: a = M^T h, heads
+    // corrupted: a = M t; either way pos = a . y and the negatives' scores are the cross products a . e'.
+    // (score_fun.py:378-449 of the reference's DGL-KE.)
+    float* a32 = k.A32 + static_cast<size_t>(i) * k.Dp;   // fp32 copy of a for this kernel (the GEMM overwrites it later)
+    __nv_bfloat16* A = k.A + static_cast<size_t>(i) * k.Dp;
+    if (!ch) {                                        // a_j = sum_i h_i M[i][j]: every lane owns columns j = lane + 32 c
+      float acc[kRescalCols];
+#pragma unroll
+      for (int c = 0; c < kRescalCols; ++c) acc[c] = 0.f;
+      for (int row = 0; row < D; ++row) {
+        const float hv = x[row];
+        const float* m = r + static_cast<size_t>(row) * D;
+#pragma unroll
+        for (int c = 0; c < kRescalCols; ++c) {
+          const int j = lane + 32 * c;
+          if (j < D) acc[c] += hv * m[j];
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < kRescalCols; ++c) {
+        const int j = lane + 32 * c;
+        if (j < D) a32[j] = acc[c];
+      }
+    } else {                                          // a_i = sum_j M[i][j] t_j: a row's dot product per step
+      float xv[kRescalCols];
+#pragma unroll
+      for (int c = 0; c < kRescalCols; ++c) {
+        const int j = lane + 32 * c;
+        xv[c] = j < D ? x[j] : 0.f;
+      }
+      for (int row = 0; row < D; ++row) {
+        const float* m = r + static_cast<size_t>(row) * D;
+        float p = 0.f;
+#pragma unroll
+        for (int c = 0; c < kRescalCols; ++c) {
+          const int j = lane + 32 * c;
+          if (j < D) p += m[j] * xv[c];
+        }
+        p = warp_sum(p);
+        if (lane == 0) a32[row] = p;
+      }
+    }
+    __syncwarp();
+    float pos = 0.f;
+    for (int d = lane; d < k.Dp; d += 32) {
+      const float a = d < D ? a32[d] : 0.f;
+      A[d] = __float2bfloat16(a);
+      if (d < D) pos += a * y[d];
+    }
+    pos = warp_sum(pos);
+    const float q = -sigmoid(-pos) * inv_bs;
+    if (lane == 0) {
+      k.a2[i] = q;
+      if (k.pos_score) k.pos_score[i] = pos;
+      atomicAdd(&k.loss[0], -log_sigmoid(pos) * inv_bs);
+    }
+    for (int d = lane; d < D; d += 32) gy[d] = q * a32[d];
+    return;
+  }
   if (k.model <= kSimplE) {                           // bilinear: a = bil(x, r), pos = a . y
     float pos = 0.f;
     __nv_bfloat16* A = k.A + static_cast<size_t>(i) * k.Dp;
@@ -300,6 +362,67 @@ __global__ void __launch_bounds__(256) kge_finish_kernel(const KgeArgs k) {
       const float ga = GA[d] - rs * __bfloat162float(k.A[static_cast<size_t>(i) * k.Dp + d]);
       if (k.corrupt_head) { gt[d] += ga; gr[d] -= ga; }    // a = t - r
       else { gh[d] += ga; gr[d] += ga; }                   // a = h + r
+    }
+    return;
+  }
+  if (k.model == kRescal) {
+    // g = d loss / d a = q * y + GA.  Tails corrupted (a = M^T h): dh = M g, dM[i][j] = h_i g_j.  Heads corrupted
+    // (a = M t): dt = M^T g, dM[i][j] = g_i t_j.  rowsum[i] receives |dM|^2 = |g|^2 |x|^2, the squared norm of this
+    // occurrence's whole matrix gradient: the row-blocked relation table turns it into ONE Adagrad state per relation.
+    const bool chr = k.corrupt_head != 0;
+    const float* x = (chr ? k.t : k.h) + static_cast<size_t>(i) * D;
+    const float* y = (chr ? k.h : k.t) + static_cast<size_t>(i) * D;
+    const float* M = k.r + static_cast<size_t>(i) * k.Dr;
+    float* gx = chr ? gt : gh;
+    float* g = const_cast<float*>(GA);               // this kernel is the last reader of GA: g is formed in place
+    const float q = k.a2[i];
+    float g2 = 0.f, x2 = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      const float gv = q * y[d] + GA[d];
+      g[d] = gv;
+      g2 += gv * gv;
+      x2 += x[d] * x[d];
+    }
+    g2 = warp_sum(g2);
+    x2 = warp_sum(x2);
+    if (lane == 0) k.rowsum[i] = g2 * x2;
+    __syncwarp();
+    float gv[kRescalCols], xv[kRescalCols], acc[kRescalCols];
+#pragma unroll
+    for (int c = 0; c < kRescalCols; ++c) {
+      const int j = lane + 32 * c;
+      gv[c] = j < D ? g[j] : 0.f;
+      xv[c] = j < D ? x[j] : 0.f;
+      acc[c] = 0.f;
+    }
+    for (int row = 0; row < D; ++row) {
+      const float* m = M + static_cast<size_t>(row) * D;
+      float* dm = gr + static_cast<size_t>(row) * D;
+      if (!chr) {                                     // dh_row = M[row,:] . g ; dM[row][j] = h_row g_j
+        const float hv = x[row];
+        float p = 0.f;
+#pragma unroll
+        for (int c = 0; c < kRescalCols; ++c) {
+          const int j = lane + 32 * c;
+          if (j < D) { p += m[j] * gv[c]; dm[j] = hv * gv[c]; }
+        }
+        p = warp_sum(p);
+        if (lane == 0) gx[row] = p;
+      } else {                                        // dt_j += g_row M[row][j] ; dM[row][j] = g_row t_j
+        const float gr_ = g[row];
+#pragma unroll
+        for (int c = 0; c < kRescalCols; ++c) {
+          const int j = lane + 32 * c;
+          if (j < D) { acc[c] += gr_ * m[j]; dm[j] = gr_ * xv[c]; }
+        }
+      }
+    }
+    if (chr) {
+#pragma unroll
+      for (int c = 0; c < kRescalCols; ++c) {
+        const int j = lane + 32 * c;
+        if (j < D) gx[j] = acc[c];
+      }
     }
     return;
   }
@@ -486,17 +609,19 @@ __global__ void __launch_bounds__(kPairThreads) kge_pair_grad_neg_kernel(const K
 
 // stage: 0 prepare, 1 negative loss, 2 finish.  model: 0 TransE_l2, 1 DistMult, 2 ComplEx, 3 SimplE (these four
 // have the GEMMs S = A.Bn^T between stages 0 and 1 and GA = W.Bn, GB = W^T.A between 1 and 2), 4 TransE_l1,
-// 5 RotatE (no GEMM: stage 1 and 2 walk the pairs; GA doubles as the fp32 copy of a, S as the pair weights).
+// 5 RotatE (no GEMM: stage 1 and 2 walk the pairs; GA doubles as the fp32 copy of a, S as the pair weights), 6 RESCAL
+// (GEMM family; r holds a row-major D x D matrix per positive, gr receives its gradient, rowsum the squared norm of it).
 RS_API int rs_kge_stage(int stage, const float* h, const float* r, const float* t, const float* neg, int bs, int cs, int ns,
                         int D, int Dp, int Dr, int model, int corrupt_head, float gamma, float emb_init, void* A, void* Bn,
                         float* a2, float* b2, float* loss, float* gh, float* gr, float* gt, float* gneg, float* S, void* W,
                         float* rowsum, float* colsum, float* GA, const float* GB, float* pos_score, float* neg_score,
                         cudaStream_t stream) {
   RS_REQUIRE(bs > 0 && cs > 0 && bs % cs == 0 && ns > 0 && D > 0 && Dp >= D, "rs_kge_stage: bad sizes");
-  RS_REQUIRE(model >= kTransE2 && model <= kRotatE, "rs_kge_stage: model must be 0..5");
+  RS_REQUIRE(model >= kTransE2 && model <= kRescal, "rs_kge_stage: model must be 0..6");
   RS_REQUIRE(model == kTransE2 || D % 2 == 0, "rs_kge_stage: this model splits the embedding into two halves");
-  RS_REQUIRE(Dr == (model == kRotatE ? D / 2 : D), "rs_kge_stage: relation row length");
-  const bool pairwise = model >= kTransE1;
+  RS_REQUIRE(Dr == (model == kRotatE ? D / 2 : model == kRescal ? D * D : D), "rs_kge_stage: relation row length");
+  RS_REQUIRE(model != kRescal || D <= 32 * kRescalCols, "rs_kge_stage: RESCAL needs dim <= 512");
+  const bool pairwise = is_pairwise(model);
   RS_REQUIRE(!pairwise || (cs % kPairRows == 0 && ns % kPairRows == 0 && emb_init > 0.f),
              "rs_kge_stage: TransE_l1 / RotatE need chunk and negative counts that are multiples of 8");
   KgeArgs k;

@@ -1,4 +1,4 @@
-"""Knowledge-graph embedding training (TransE L2 / L1, DistMult, ComplEx, SimplE, RotatE) on row-sharded HBM tables.
+"""Knowledge-graph embedding training (TransE L2 / L1, DistMult, ComplEx, SimplE, RotatE, RESCAL) on row-sharded HBM tables.
 
 Model, negative sampling and loss follow the reference's patched DGL-KE
 (src/kg/kg/dgl-ke/python/dglke/models/general_models.py:568-631, score_fun.py, loss.py:69-99,
@@ -12,7 +12,12 @@ host memory behind a cache; it is spread cyclically over the GPUs' HBM
 (``parallel.sharded_table.ShardedEmbeddingTable``), rows and gradients move by peer stores, and the
 scoring is three element-wise kernels around tcgen05 GEMMs for the models whose negative scores are cross
 products (TransE-L2, DistMult, ComplEx, SimplE) and three pair-walking fp32 kernels for TransE-L1 and RotatE
-(``csrc/ops/kge.cu``).  TransR and RESCAL (a matrix per relation) run on the PyTorch path only.
+(``csrc/ops/kge.cu``).  RESCAL (score h^T M_r t, score_fun.py:378-449) is in the GEMM family too: a = M_r^T h or M_r t is
+a matrix-vector product per positive, the negatives' scores are a . e'.  Its relation table is ROW-BLOCKED: relation r
+owns the D table rows r*D .. r*D+D-1 (the rows of its D x D matrix), and every row is updated with the squared norm of
+the whole matrix gradient / D, so that all D rows carry the same Adagrad accumulator: one state per relation, as the
+reference's [n_relations, D*D] embedding has.  TransR (which projects every negative with the matrix of every positive
+of its chunk) runs on the PyTorch path only.
 
 Checkpoints keep the reference layout (tensor_models.py:452-476, general_models.py:316-346):
 ``{dataset}_{model}_entity.npy``, ``{dataset}_{model}_relation.npy`` and ``config.json``.
@@ -38,7 +43,7 @@ _lib.register_signatures({
                            vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
 })
 
-MODELS = {"TransE": 0, "TransE_l2": 0, "DistMult": 1, "ComplEx": 2, "SimplE": 3, "TransE_l1": 4, "RotatE": 5}
+MODELS = {"TransE": 0, "TransE_l2": 0, "DistMult": 1, "ComplEx": 2, "SimplE": 3, "TransE_l1": 4, "RotatE": 5, "RESCAL": 6}
 PAIRWISE = (4, 5)                     # no cross-product form: scored pair by pair in fp32
 
 
@@ -75,21 +80,33 @@ class KGEModel:
         self.Dp = (self.D + 63) // 64 * 64
         self.model_id = MODELS[cfg.model]
         self.pairwise = self.model_id in PAIRWISE
+        self.rescal = cfg.model == "RESCAL"
         self.Dr = self.D // 2 if cfg.model == "RotatE" else self.D      # RotatE relations are phases
+        if self.rescal:
+            assert self.D <= 512, "RESCAL: dim <= 512"
+            self.Dr = self.D * self.D                                    # a row-major D x D matrix per relation
         if self.pairwise:
             assert self.cs % 8 == 0 and self.ns % 8 == 0, "TransE_l1 / RotatE: chunk and negative counts are multiples of 8"
         scale = self.emb_init = (cfg.gamma + 2.0) / cfg.dim
         n_ids = 2 * self.bs + self.nneg
         self.entity = ShardedEmbeddingTable(self.ctx, "kge_entity", cfg.n_entities, self.D, max_keys=n_ids, lr=cfg.lr, eps=cfg.eps,
                                             init="uniform", init_scale=scale, seed=cfg.seed, hbm_ratio=cfg.entity_hbm_ratio)
-        self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations, self.Dr, max_keys=self.bs, lr=cfg.lr,
-                                              eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 1)
+        if self.rescal:   # row-blocked: D table rows of D floats per relation
+            self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations * self.D, self.D, max_keys=self.bs * self.D,
+                                                  lr=cfg.lr, eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 1)
+            self._row_of_block = torch.arange(self.D, dtype=torch.int64, device=dev)
+        else:
+            self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations, self.Dr, max_keys=self.bs, lr=cfg.lr,
+                                                  eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 1)
         f = dict(dtype=torch.float32, device=dev)
         b = dict(dtype=torch.bfloat16, device=dev)
         self.ent_rows = torch.empty(n_ids, self.D, **f)
         self.rel_rows = torch.empty(self.bs, self.Dr, **f)
         self.ent_grad = torch.empty(n_ids, self.D, **f)
         self.rel_grad = torch.empty(self.bs, self.Dr, **f)
+        if self.rescal:
+            self._rel_keys = torch.empty(self.bs * self.D, dtype=torch.int64, device=dev)
+            self._rel_norm = torch.empty(self.bs * self.D, **f)
         self.A = torch.zeros(self.bs, self.Dp, **b)
         self.Bn = torch.zeros(self.nneg, self.Dp, **b)
         self.a2 = torch.empty(self.bs, **f)
@@ -135,7 +152,11 @@ class KGEModel:
         bs = self.bs
         self.ids[:bs].copy_(h_ids); self.ids[bs:2 * bs].copy_(t_ids); self.ids[2 * bs:].copy_(neg_ids)
         self.entity.lookup(self.ids, out=self.ent_rows)
-        self.relation.lookup(r_ids.contiguous(), out=self.rel_rows)
+        if self.rescal:
+            self._rel_keys.copy_((r_ids.view(-1, 1) * self.D + self._row_of_block).view(-1))
+            self.relation.lookup(self._rel_keys, out=self.rel_rows.view(self.bs * self.D, self.D))
+        else:
+            self.relation.lookup(r_ids.contiguous(), out=self.rel_rows)
 
     def train_step(self, h_ids: torch.Tensor, r_ids: torch.Tensor, t_ids: torch.Tensor, neg_ids: torch.Tensor,
                    corrupt_head: Optional[bool] = None) -> torch.Tensor:
@@ -175,7 +196,11 @@ class KGEModel:
             F_.gemm_bf16(self.W, self.A, self.GB, mode=1, epi=F_.EPI_F32, status=st)
         self._stage(2, corrupt_head, False)
         self.entity.update(self.ent_grad)
-        self.relation.update(self.rel_grad)
+        if self.rescal:   # rowsum holds |dM|^2 of every positive: / D makes the table's mean over a row the mean over the matrix
+            self._rel_norm.copy_((self.rowsum / self.D).view(-1, 1).expand(self.bs, self.D).reshape(-1))
+            self.relation.update(self.rel_grad.view(self.bs * self.D, self.D), norms=self._rel_norm)
+        else:
+            self.relation.update(self.rel_grad)
         self.launches_per_step = (7 if self.pairwise else 9) + self.entity.launches + self.relation.launches
         return self.loss.sum()
 
@@ -229,6 +254,8 @@ class KGEModel:
         rel = self._gather_table(self.relation)
         if self.ctx.rank == 0:
             c = self.cfg
+            if self.rescal:
+                rel = rel.reshape(c.n_relations, self.D * self.D)
             np.save(os.path.join(path, f"{c.dataset}_{c.model}_entity.npy"), ent)
             np.save(os.path.join(path, f"{c.dataset}_{c.model}_relation.npy"), rel)
             conf = asdict(c)
@@ -241,6 +268,8 @@ class KGEModel:
         c = self.cfg
         for tab, kind in ((self.entity, "entity"), (self.relation, "relation")):
             full = torch.from_numpy(np.load(os.path.join(path, f"{c.dataset}_{c.model}_{kind}.npy")))
+            if self.rescal and kind == "relation":
+                full = full.reshape(c.n_relations * self.D, self.D)
             mine = full[self.ctx.rank::self.ctx.world]
             hot = min(mine.shape[0], tab.weight.shape[0])
             tab.weight[:hot].copy_(mine[:hot])

@@ -42,6 +42,7 @@ _lib.register_signatures({
     "rs_shard_unbucket_rows": (i32, [vp, vp, i64, i32, vp, i32, vp]),
     "rs_shard_push_grads": (i32, [vp, vp, i64, i32, i32, i64, vp, vp, vp, vp]),
     "rs_segment_sum": (i32, [vp, vp, i64, i32, vp, vp, vp]),
+    "rs_segment_sum_ex": (i32, [vp, vp, i64, i32, vp, vp, vp, vp]),
     "rs_expand_rows": (i32, [vp, vp, i64, i32, vp, vp]),
     "rs_unique_keys": (i32, [vp, i64, vp, vp, _lib.u64, vp, vp, vp, vp, vp]),
     "rs_shard_keys_fused": (i32, [vp, vp, i64, i32, i32, i64, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, vp]),
@@ -313,10 +314,19 @@ class ShardedEmbeddingTable:
         self.launches += 3
         self._update_fused(grads, n, st, sp)
 
-    def _update_fused(self, grads, n, st, sp):
+    def _fold(self, grads, n, sp, norms=None):
+        """ugrad / unorm of the unique keys: sums over the occurrences (``norms``: per-occurrence squared norms that
+        replace |grad row|^2 in the Adagrad state)."""
+        if norms is None:
+            _lib.call("rs_segment_sum", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), sp)
+        else:
+            assert norms.numel() == n and norms.dtype == torch.float32 and norms.is_contiguous()
+            _lib.call("rs_segment_sum_ex", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), ptr(norms), sp)
+
+    def _update_fused(self, grads, n, st, sp, norms=None):
         c = self.ctx
         if self.dedup:      # the accumulators were cleared by the lookup's last kernel
-            _lib.call("rs_segment_sum", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), sp)
+            self._fold(grads, n, sp, norms)
             g, gn, nd = self._ugrad, self._unorm, self._ucount
             self.launches += 1
         else:
@@ -338,17 +348,21 @@ class ShardedEmbeddingTable:
         self.launches += 3 if self.optimizer == "rowwise_adagrad" else 2
 
     # ------------------------------------------------------------------ backward
-    def update(self, grads: torch.Tensor) -> None:
-        """Applies the optimizer to the rows of the LAST lookup; ``grads`` [n, D] fp32, one row per looked-up id."""
+    def update(self, grads: torch.Tensor, norms: Optional[torch.Tensor] = None) -> None:
+        """Applies the optimizer to the rows of the LAST lookup; ``grads`` [n, D] fp32, one row per looked-up id.
+        ``norms`` [n] (deduplicating tables only): the squared norm that row-wise Adagrad accounts for each occurrence
+        instead of the row's own; rows that are slices of one wider parameter (the D rows of a D x D relation matrix)
+        pass the whole parameter's norm / D here and so share ONE accumulator value."""
         n = self._n
         assert grads.shape == (n, self.D) and grads.dtype == torch.float32
+        assert norms is None or self.dedup, "per-occurrence norms need a deduplicating table"
         grads = grads.contiguous()
         st, sp = self.ctx.status, stream_ptr()
         if self.world == 1 and not self.tiered and not self.hashed and not self.range_c:
             if self.dedup:
                 self._ugrad[:n].zero_()
                 self._unorm[:n].zero_()
-                _lib.call("rs_segment_sum", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), sp)
+                self._fold(grads, n, sp, norms)
                 g, gn = self._ugrad, self._unorm
             else:
                 g, gn = grads, None
@@ -357,12 +371,12 @@ class ShardedEmbeddingTable:
             self.launches += 5
             return
         if self.fused:
-            return self._update_fused(grads, n, st, sp)
+            return self._update_fused(grads, n, st, sp, norms)
         gnorm = None
         if self.dedup:
             self._ugrad[:n].zero_()
             self._unorm[:n].zero_()
-            _lib.call("rs_segment_sum", ptr(grads), ptr(self._inv), n, self.D, ptr(self._ugrad), ptr(self._unorm), sp)
+            self._fold(grads, n, sp, norms)
             _lib.call("rs_shard_push_grads", ptr(self._ugrad), ptr(self._slot), n, self.D, self.rank, self.cap,
                       ptr(self.grad_win.table), ptr(self._unorm), ptr(self.norm_win.table), sp)
             gnorm = self.norm_win.view(torch.float32, (self.world * self.cap,))

@@ -82,3 +82,77 @@ def test_kge_training_improves_mrr_and_checkpoints(tmp_path):
     m2 = KGEModel(cfg)
     m2.load(str(tmp_path))
     assert torch.equal(m2.entity.weight, m.entity.weight)
+
+
+@pytest.mark.parametrize("corrupt_head", [False, True])
+def test_rescal_step_matches_autograd_with_one_state_per_relation(corrupt_head):
+    """RESCAL natively: scores, loss and gradients against autograd on h^T M_r t; the row-blocked relation table (D rows
+    per relation) must move exactly like a [n_relations, D*D] table under row-wise Adagrad, i.e. with ONE accumulator
+    value per relation, shared by its D rows."""
+    from recstore_b200.models.kge import KGEConfig, KGEModel
+    from recstore_b200.baseline.kge_torch import chunk_neg_score, edge_score, logsigmoid_loss
+    from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
+    dev = torch.device("cuda:0")
+    cfg = KGEConfig(n_entities=2000, n_relations=12, dim=32, model="RESCAL", gamma=10.0, batch=256, neg_sample_size=64,
+                    neg_chunk_size=64, lr=0.1, seed=3)
+    m = KGEModel(cfg)
+    bs, ns, cs, D = cfg.batch, cfg.neg_sample_size, cfg.neg_chunk_size, cfg.dim
+    g = torch.Generator(device=dev).manual_seed(1)
+    E = m.entity.weight[: cfg.n_entities].clone()
+    M = m.relation.weight[: cfg.n_relations * D].clone().view(cfg.n_relations, D * D)
+    SE = torch.zeros(cfg.n_entities, device=dev); SM = torch.zeros(cfg.n_relations, device=dev)
+    dummy_r = torch.zeros(bs, D, device=dev)
+    for step in range(2):
+        hi = torch.randint(0, 150, (bs,), device=dev, generator=g)
+        ti = torch.randint(0, cfg.n_entities, (bs,), device=dev, generator=g)
+        ri = torch.randint(0, cfg.n_relations, (bs,), device=dev, generator=g)             # 12 relations: many duplicates
+        ni = torch.randint(0, cfg.n_entities, (bs // cs * ns,), device=dev, generator=g)
+        h = E[hi].clone().requires_grad_(True); t = E[ti].clone().requires_grad_(True)
+        P = M[ri].clone().requires_grad_(True); n = E[ni].clone().requires_grad_(True)
+        pos_ref = edge_score("RESCAL", h, dummy_r, t, cfg.gamma, P)
+        neg_ref = chunk_neg_score("RESCAL", h, dummy_r, t, n, corrupt_head, cs, cfg.gamma, P)
+        loss_ref = logsigmoid_loss(pos_ref, neg_ref)
+        loss_ref.backward()
+        pos, negs = m.score_batch(hi, ri, ti, ni, corrupt_head)
+        assert torch.allclose(pos, pos_ref, atol=2e-3, rtol=1e-3)
+        assert torch.allclose(negs, neg_ref, atol=3e-2, rtol=2e-2)
+        loss = m.train_step(hi, ri, ti, ni, corrupt_head)
+        assert abs(loss.item() - loss_ref.item()) < 5e-3 * max(1.0, abs(loss_ref.item()))
+        ge = torch.cat([h.grad, t.grad, n.grad])
+        assert ((m.ent_grad - ge).norm() / ge.norm()).item() < 3e-2
+        assert ((m.rel_grad - P.grad).norm() / P.grad.norm()).item() < 3e-2
+        rowwise_adagrad_update(E, SE, torch.cat([hi, ti, ni]), m.ent_grad.clone(), cfg.lr, cfg.eps)
+        rowwise_adagrad_update(M, SM, ri, m.rel_grad.clone(), cfg.lr, cfg.eps)
+        torch.cuda.synchronize()
+        assert torch.allclose(m.entity.weight[: cfg.n_entities], E, atol=2e-3, rtol=2e-3)
+        got = m.relation.weight[: cfg.n_relations * D].view(cfg.n_relations, D * D)
+        assert torch.allclose(got, M, atol=2e-3, rtol=2e-3), (got - M).abs().max().item()
+        st = m.relation.state[: cfg.n_relations * D].view(cfg.n_relations, D)
+        assert torch.allclose(st, SM.view(-1, 1).expand_as(st), atol=1e-6, rtol=2e-3)       # one value per relation
+    m.ctx.check_status()
+
+
+def test_rescal_trains_with_graph_replay_and_keeps_the_reference_checkpoint_shape(tmp_path):
+    """RESCAL through the graph-replayed step: the loss falls, and the relation file has the reference's
+    [n_relations, D*D] shape and loads back into the row-blocked table."""
+    from recstore_b200.models.kge import KGEConfig, KGEModel, KGSampler
+    import numpy as np, os
+    dev = torch.device("cuda:0")
+    cfg = KGEConfig(n_entities=2000, n_relations=8, dim=32, model="RESCAL", gamma=10.0, batch=256, neg_sample_size=64,
+                    neg_chunk_size=64, lr=0.1, seed=1, use_cuda_graph=True)
+    m = KGEModel(cfg)
+    smp = KGSampler(cfg, n_triples=4000, alpha=1.3, device=dev, seed=2)
+    losses = []
+    for step in range(200):
+        h, r, t, neg = next(smp)
+        losses.append(m.train_step(h, r, t, neg))
+    m.ctx.check_status()
+    first, last = torch.stack(losses[:10]).mean().item(), torch.stack(losses[-10:]).mean().item()
+    assert last < 0.8 * first, (first, last)
+    m.save(str(tmp_path))
+    rel = np.load(os.path.join(tmp_path, "synthetic_RESCAL_relation.npy"))
+    assert rel.shape == (8, 32 * 32)
+    assert np.allclose(rel.reshape(8 * 32, 32), m.relation.weight[: 8 * 32].cpu().numpy())
+    m2 = KGEModel(cfg)
+    m2.load(str(tmp_path))
+    assert torch.equal(m2.relation.weight[: 8 * 32], m.relation.weight[: 8 * 32])
