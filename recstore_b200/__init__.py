@@ -17,7 +17,7 @@ from . import _lib  # noqa: F401
 from ._lib import RecStoreError, DeviceStatusError  # noqa: F401
 
 from .kvstore import kvinit, get_kvstore, AbsKVStore, ShmKVStore  # noqa: F401,E402
-from .dist_tensor import DistTensor, DistEmbedding, PartitionPolicy  # noqa: F401,E402
+from .dist_tensor import DistTensor, DistEmbedding, HbmDistEmbedding, PartitionPolicy  # noqa: F401,E402
 from . import dist_opt as DistOpt  # noqa: F401,E402
 from .dist_opt import SparseSGD, SparseAdagrad, SparseRowWiseAdaGrad  # noqa: F401,E402
 from .ipc import IPCTensorFactory, SlicedTensor, MultiProcessBarrierFactory, Mfence  # noqa: F401,E402

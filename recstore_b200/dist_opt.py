@@ -23,7 +23,7 @@ from typing import Dict, List
 import torch
 import torch.distributed as dist
 
-from .dist_tensor import DistEmbedding, DistTensor
+from .dist_tensor import DistEmbedding, DistTensor, HbmDistEmbedding
 
 EMB_STATES, PARAMS, WORLD_SIZE, IDS, STATES = "emb_states", "params", "world_size", "ids", "states"
 
@@ -51,13 +51,27 @@ class DistSparseGradOptimizer(ABC):
     def local_state_dict(self) -> dict:
         out = {EMB_STATES: {}, PARAMS: {WORLD_SIZE: self._world_size}}
         for emb in self._params:
+            if isinstance(emb, HbmDistEmbedding):       # the accumulator is the table's own: this rank's rows of it
+                t = emb.table
+                idx = t.local_global_ids()
+                keep = idx < emb.num_embeddings
+                out[EMB_STATES][emb.name] = {IDS: idx[keep].cpu(), STATES: {emb.name + "_hbm_state": t.state[: int(keep.sum())].cpu()}}
+                continue
             idx = emb.part_policy.local_ids(self._rank, self._world_size)
             out[EMB_STATES][emb.name] = {IDS: idx, STATES: {st.name: st[idx].clone() for st in self._states_of(emb.name)}}
         out[PARAMS].update(self._defaults)
         return out
 
     def load_local_state_dict(self, sd: dict) -> None:
+        hbm = {e.name: e for e in self._params if isinstance(e, HbmDistEmbedding)}
         for emb_name, emb_state in sd[EMB_STATES].items():
+            if emb_name in hbm:       # rows owned by this rank (id % world == rank) take their accumulator values
+                t = hbm[emb_name].table
+                idx = emb_state[IDS].to(torch.int64)
+                val = next(iter(emb_state[STATES].values())).to(torch.float32)
+                own = (idx % t.world) == t.rank
+                t.state[(idx[own] // t.world).to(t.dev)] = val[own].to(t.dev)
+                continue
             if emb_name not in self._state:
                 raise ValueError(f"loaded state refers to embedding {emb_name!r} unknown to this optimizer")
             states = {st.name: st for st in self._states_of(emb_name)}
@@ -106,11 +120,21 @@ class DistSparseGradOptimizer(ABC):
     def lr(self) -> float:
         return self._lr
 
+    _hbm_kind = None     # the table optimizer of an HbmDistEmbedding that this class corresponds to
+
     def step(self) -> None:
         with torch.no_grad():
             for emb in self._params:
                 for idx, grad in emb.get_grad():
-                    self.update(idx, grad, emb)
+                    if isinstance(emb, HbmDistEmbedding):
+                        # rows and state live in HBM beside each other: the gradients go to the owning GPUs, which fold
+                        # duplicates and apply the same rule there (lr / world_size as on the host path)
+                        if emb.optimizer_kind != self._hbm_kind:
+                            raise TypeError(f"{type(self).__name__} cannot drive an HBM embedding built with optimizer="
+                                            f"{emb.optimizer_kind!r}")
+                        emb.apply_grad(idx, grad, self._lr / self._world_size)
+                    else:
+                        self.update(idx, grad, emb)
 
     def zero_grad(self) -> None:
         for emb in self._params:
@@ -128,6 +152,8 @@ def _mean_over_duplicates(idx: torch.Tensor, grad: torch.Tensor):
 
 
 class SparseSGD(DistSparseGradOptimizer):
+    _hbm_kind = "sgd"        # on an HBM embedding duplicates are SUMMED (the cached-embedding convention), not averaged
+
     def __init__(self, params, lr):
         super().__init__(params, lr)
         self._defaults = {"_lr": lr}
@@ -164,13 +190,18 @@ class SparseAdagrad(DistSparseGradOptimizer):
 
 
 class SparseRowWiseAdaGrad(DistSparseGradOptimizer):
-    """One accumulator per row; state tensor ``{emb}_SparseRowWiseAdaGrad_sum`` of shape ``(N,)``."""
+    """One accumulator per row; state tensor ``{emb}_SparseRowWiseAdaGrad_sum`` of shape ``(N,)``.  For an
+    ``HbmDistEmbedding`` the accumulator is the table's own (``emb.optm_state``) and the update runs on the owning GPU."""
+    _hbm_kind = "rowwise_adagrad"
 
     def __init__(self, params, lr, eps=1e-10):
         super().__init__(params, lr)
         self._eps = eps
         self._defaults = {"_lr": lr, "_eps": eps}
         for emb in params:
+            if isinstance(emb, HbmDistEmbedding):
+                emb.table.eps = eps
+                continue
             assert isinstance(emb, DistEmbedding), "SparseRowWiseAdaGrad only supports DistEmbedding"
             assert emb.name not in self._state, f"{emb.name} already registered in the optimizer"
             self._state[emb.name] = DistTensor((emb.num_embeddings,), torch.float32,

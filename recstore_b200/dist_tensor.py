@@ -147,3 +147,104 @@ class DistEmbedding:
     optm_state = property(lambda self: self._optm_state)
     weight = property(lambda self: self._tensor.get_shm_tensor())
     part_policy = property(lambda self: self._part_policy)
+
+
+class HbmDistEmbedding:
+    """``DistEmbedding`` whose rows live in the GPUs' HBM instead of host shared memory.
+
+    Same surface as :class:`DistEmbedding` (``emb(idx, device)`` -> rows that record their gradient, ``record_grad``,
+    ``get_grad``, ``reset_trace``, ``weight``, ``set_data``, ``name``, ``shape``), so a training loop written against
+    the reference API (src/python/pytorch/recstore/DistEmb.py:10-108) runs unchanged, but the table is a row-sharded
+    :class:`~recstore_b200.parallel.sharded_table.ShardedEmbeddingTable` over the NVLink peer windows: a lookup sends the
+    keys to their owning GPUs and brings the rows back with the fused exchange kernels, and the sparse optimizers of
+    ``dist_opt`` deliver the traced gradients to the owners (``push_update``), where duplicates are folded and the
+    update is applied in place.  Lookups and optimizer steps are collective: every rank calls them the same number of
+    times per step (with any ids, up to ``max_keys`` per call).
+
+    ``optimizer`` ("rowwise_adagrad" or "sgd") is fixed at construction because the state lives beside the rows; the
+    ``dist_opt`` optimizer that is given this embedding must be the matching one (it sets the learning rate).
+    """
+
+    def __init__(self, ctx, num_embeddings: int, embedding_dim: int, name: str, init_func=None, max_keys: int = 65536,
+                 optimizer: str = "rowwise_adagrad", eps: float = 1e-10):
+        from .parallel.sharded_table import ShardedEmbeddingTable
+        self._ctx = ctx
+        self._name = name
+        self._num_embeddings, self._embedding_dim = int(num_embeddings), int(embedding_dim)
+        self._table = ShardedEmbeddingTable(ctx, "distemb_" + name, num_embeddings, embedding_dim, max_keys=max_keys, lr=0.0, eps=eps,
+                                            optimizer=optimizer, dedup=True, init="zeros")
+        self.optimizer_kind = optimizer
+        if init_func is not None:            # the reference's init_func(tensor, shape, dtype) fills the whole table
+            full = torch.empty(num_embeddings, embedding_dim)
+            init_func(full, (num_embeddings, embedding_dim), torch.float32)
+            self.set_data(full)
+        self._trace: List[Tuple[torch.Tensor, torch.Tensor]] = []
+        self._hand_grad: List[Tuple[torch.Tensor, torch.Tensor]] = []
+        self._optm_state = None
+
+    # ---- DistEmbedding surface
+    def __call__(self, idx, device=None, record_trace: bool = True) -> torch.Tensor:
+        dev = self._table.dev
+        idx = torch.as_tensor(idx, dtype=torch.int64).to(dev)
+        emb = self._table.lookup(idx).clone()
+        if device is not None and torch.device(device) != dev:
+            emb = emb.to(device)
+        emb.requires_grad_(True)
+        if record_trace:
+            self._trace.append((idx, emb))
+        return emb
+
+    def record_grad(self, idx: torch.Tensor, grad: torch.Tensor) -> None:
+        assert len(idx) == len(grad)
+        self._hand_grad.append((idx, grad))
+
+    def reset_trace(self) -> None:
+        self._trace = []
+        self._hand_grad = []
+
+    def get_grad(self) -> Iterator[Tuple[torch.Tensor, torch.Tensor]]:
+        for idx, emb in self._trace:
+            if emb.grad is not None:
+                yield idx, emb.grad.data
+        for idx, grad in self._hand_grad:
+            if grad is not None:
+                yield idx, grad
+
+    def apply_grad(self, idx: torch.Tensor, grad: torch.Tensor, lr: float) -> None:
+        """One gradient batch to the owners (collective).  Called by the ``dist_opt`` optimizers."""
+        t = self._table
+        t.lr = float(lr)
+        t.push_update(torch.as_tensor(idx, dtype=torch.int64).to(t.dev), grad.detach().to(t.dev, torch.float32))
+
+    def set_data(self, data: torch.Tensor) -> None:
+        assert tuple(data.shape) == self.shape, "shape does not match"
+        t = self._table
+        mine = data[t.rank::t.world].to(t.dev, torch.float32)
+        t.weight[: mine.shape[0]].copy_(mine)
+
+    def to_dense_tensor(self) -> Optional[torch.Tensor]:
+        """Collective: the whole table on rank 0's host (``None`` elsewhere)."""
+        t = self._table
+        torch.cuda.synchronize(t.dev)
+        local = t.weight.cpu()
+        if t.world == 1:
+            return local[: self._num_embeddings]
+        import torch.distributed as dist
+        parts = [None] * t.world if t.rank == 0 else None
+        dist.gather_object(local, parts, dst=0, group=self._ctx.group)
+        if t.rank != 0:
+            return None
+        full = torch.empty(t.local_rows * t.world, t.D)
+        for r, p in enumerate(parts):
+            full[r::t.world] = p
+        return full[: self._num_embeddings]
+
+    name = property(lambda self: self._name)
+    data_name = property(lambda self: self._name)
+    num_embeddings = property(lambda self: self._num_embeddings)
+    embedding_dim = property(lambda self: self._embedding_dim)
+    shape = property(lambda self: (self._num_embeddings, self._embedding_dim))
+    optm_state = property(lambda self: self._table.state)
+    weight = property(lambda self: self._table.weight)          # this rank's shard: rows of ids rank, rank + world, ...
+    table = property(lambda self: self._table)
+    part_policy = property(lambda self: None)

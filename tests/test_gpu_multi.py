@@ -419,6 +419,66 @@ def test_nvlink_parameter_client_across_ranks():
     assert all(out.get(r) == "ok" for r in range(2)), dict(out)
 
 
+def _hbm_emb_worker(rank, world, port, ns, out):
+    """The reference-named training API (DistEmbedding + SparseRowWiseAdaGrad) on the HBM plane against the same loop on
+    the host shared-memory table: identical ids and gradients, ranks touching disjoint rows (so the host path, where every
+    rank applies its own update, is order-free), duplicates inside a rank."""
+    dist = _init(rank, world, port)
+    try:
+        import recstore_b200 as rs
+        from recstore_b200 import ipc
+        from recstore_b200.dist_opt import SparseRowWiseAdaGrad
+        from recstore_b200.parallel.peer import PeerContext
+        ipc.set_namespace(ns)
+        rs.kvinit()
+        N, D, lr = 5000, 32, 0.1
+
+        def init(t, shape, dtype):
+            t.copy_((torch.arange(shape[0], dtype=dtype) % 97).unsqueeze(1).expand(shape) * 0.01 + 0.05)
+        host = rs.DistEmbedding(N, D, name="hbm_ref", init_func=init) if rank == 0 else None
+        dist.barrier()
+        if rank != 0:
+            host = rs.DistEmbedding(N, D, name="hbm_ref", init_func=init)
+        ctx = PeerContext(rank, world, device=torch.device(f"cuda:{rank}"))
+        hbm = rs.HbmDistEmbedding(ctx, N, D, "hbm_emb", init_func=init, max_keys=4096)
+        o_host, o_hbm = SparseRowWiseAdaGrad([host], lr), SparseRowWiseAdaGrad([hbm], lr)
+        g = torch.Generator().manual_seed(100 + rank)
+        for step in range(3):
+            ids = torch.randint(0, N // world, (600,), generator=g) * world + rank        # rows of this rank's own residue class
+            ids[::7] = ids[0]                                                              # duplicates
+            w = torch.randn(600, D, generator=g)
+            a = host(ids, torch.device("cuda"))
+            b = hbm(ids, torch.device("cuda"))
+            assert torch.allclose(a, b, atol=1e-6), (step, (a - b).abs().max().item())
+            (a * w.cuda()).sum().backward()
+            (b * w.cuda()).sum().backward()
+            o_host.step(); o_hbm.step()
+            o_host.zero_grad(); o_hbm.zero_grad()
+            torch.cuda.synchronize()
+            dist.barrier()
+        ctx.check_status()
+        full = hbm.to_dense_tensor()
+        if rank == 0:
+            assert torch.allclose(full, host.weight, atol=1e-5, rtol=1e-5), (full - host.weight).abs().max().item()
+        sd = o_hbm.local_state_dict()
+        assert len(sd["emb_states"]["hbm_emb"]["ids"]) == hbm.table.local_global_ids()[hbm.table.local_global_ids() < N].numel()
+        dist.barrier()
+        out[rank] = "ok"
+    except BaseException as e:          # noqa: BLE001
+        _leave(dist, rank, out, e)
+    _leave(dist, rank, out, None)
+
+
+def test_dist_embedding_api_on_the_hbm_plane_matches_the_host_table():
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    out = mgr.dict()
+    _spawn(_hbm_emb_worker, (2, _free_port(), f"pytest_hbm_{os.getpid()}", out), 2)
+    assert all(out.get(r) == "ok" for r in range(2)), dict(out)
+
+
 def test_kge_driver_two_gpus_native_path():
     """TransE-L2 on entity / relation tables sharded over two GPUs, through the training driver."""
     if _ngpus() < 2:
