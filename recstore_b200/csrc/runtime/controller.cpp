@@ -32,6 +32,7 @@
 #include <chrono>
 #include <climits>
 #include <condition_variable>
+#include <cstdio>
 #include <cstring>
 #include <mutex>
 #include <shared_mutex>
@@ -275,6 +276,7 @@ class Controller {
   bool BlockToStepN(int64_t step, int timeout_ms) {
     if (!async_) return true;
     const auto t0 = std::chrono::steady_clock::now();
+    long long next_warn_ms = 1000;
     for (;;) {
       bool busy = false;
       if (detect_ && DrainMail()) busy = true;     // a read that is still in a mailbox has no priority yet
@@ -290,11 +292,21 @@ class Controller {
           return true;
         }
       }
-      if (timeout_ms >= 0 &&
-          std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > timeout_ms)
-        return false;
+      const long long waited_ms =
+          std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+      if (timeout_ms >= 0 && waited_ms > timeout_ms) return false;
+      // A wait that drags on is reported once a second with what it is waiting for (the reference logs the same from
+      // its BlockToStepN and dispatch loops, grad_async_v1.h:450-452, 553-559), so a stuck trainer is not silent.
+      if (waited_ms >= next_warn_ms) {
+        next_warn_ms = waited_ms + 1000;
+        stall_warnings_.fetch_add(1, std::memory_order_relaxed);
+        fprintf(stderr, "[recstore controller] BlockToStepN(%lld) has waited %lld ms: min priority %lld, %d updates in flight, %d announcements in mailboxes\n",
+                static_cast<long long>(step), waited_ms, static_cast<long long>(MinPriority()), static_cast<int>(inflight_.load()),
+                static_cast<int>(mail_items_.load()));
+      }
     }
   }
+  uint64_t stall_warnings() const { return stall_warnings_.load(); }
   // out: has_pending, prio, number of registered reads, earliest read (-1 = none), queued
   void DebugElem(int64_t id, long long* out) {
     Shard& sh = shard_of(id);
@@ -537,6 +549,7 @@ class Controller {
   BitLockTable row_locks_;
   std::atomic<int64_t> cur_step_{-1}, max_published_{-1}, flushed_{0};
   std::atomic<int> inflight_{0};
+  std::atomic<uint64_t> stall_warnings_{0};
   std::shared_mutex flight_mu_;
   std::atomic<bool> running_{false};
   std::vector<std::thread> flushers_;

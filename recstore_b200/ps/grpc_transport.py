@@ -18,6 +18,9 @@ its client cuts a request into sub-requests of ``MAX_PARAMETER_BATCH`` keys issu
   by the server-side optimizer), because the reference's trainers update through Put of client-computed rows while the
   native shard owns the optimizer state.
 
+* the standard health-check service ``/grpc.health.v1.Health/Check`` (the reference enables gRPC's default one,
+  grpc_ps_server.cpp:131): SERVING while the shard answers, for the service names "" and "xmhps.ParameterService".
+
 ``GrpcParameterClient`` has the API of ``ps.client.ParameterClient`` and can be handed to
 ``AllShardsParameterClient``.
 """
@@ -97,13 +100,31 @@ class GrpcParameterServer:
             "UpdateParameter": un(self._update, PutParameterRequest.FromString, PutParameterResponse.SerializeToString),
             "Command": un(self._command, CommandRequest.FromString, CommandResponse.SerializeToString),
         }
-        self._server.add_generic_rpc_handlers((grpc.method_handlers_generic_handler(SERVICE, handlers),))
+        health = {"Check": un(self._health, lambda b: b, lambda b: b)}
+        self._server.add_generic_rpc_handlers((grpc.method_handlers_generic_handler(SERVICE, handlers),
+                                               grpc.method_handlers_generic_handler("grpc.health.v1.Health", health)))
         self.port = self._server.add_insecure_port(f"{host}:{int(port)}")
         if self.port == 0:
             raise OSError(f"cannot bind {host}:{port}")
         self._server.start()
 
     # handlers ---------------------------------------------------------------------------
+    def _health(self, raw: bytes, ctx):
+        """grpc.health.v1: HealthCheckRequest{string service = 1} -> HealthCheckResponse{ServingStatus status = 1}; the two
+        messages are small enough to be read and written as raw protobuf bytes."""
+        service = b""
+        if raw:
+            if raw[0] != 0x0a or len(raw) < 2 or raw[1] != len(raw) - 2:
+                ctx.abort(grpc.StatusCode.INVALID_ARGUMENT, "malformed HealthCheckRequest")
+            service = raw[2:]
+        if service not in (b"", SERVICE.encode()):
+            ctx.abort(grpc.StatusCode.NOT_FOUND, "unknown service")
+        try:
+            len(self.ps)                      # the shard still answers
+            return b"\x08\x01"                # SERVING
+        except Exception:
+            return b"\x08\x02"                # NOT_SERVING
+
     def _get(self, req, ctx):
         raw = req.keys
         if len(raw) % 8:
@@ -269,6 +290,12 @@ class GrpcParameterClient:
     def Stats(self) -> dict:
         a, b, c = (int(x) for x in self._command(STATS).split())
         return {"keys_stored": a, "requests": b, "keys_served": c}
+
+    def HealthCheck(self, service: str = "") -> bool:
+        """True when the server reports SERVING for ``service`` through the standard gRPC health protocol."""
+        req = (b"\x0a" + bytes([len(service)]) + service.encode()) if service else b""
+        rep = self._channel.unary_unary("/grpc.health.v1.Health/Check")(req, timeout=self.timeout_s)
+        return rep == b"\x08\x01"
 
     # asynchronous form (src/rdma_ps/base_client.h:6-47) -----------------------------------------
     def InitThread(self, n: int = 1) -> None:

@@ -269,6 +269,10 @@ def test_grpc_transport_mirror_commands_and_wire_format(tmp_path):
     assert torch.equal(cli.GetParameter(torch.arange(300))[:, 0], torch.arange(300).float())
     st = cli.Stats()
     assert st["keys_stored"] == 300 and st["requests"] > 10
+    assert cli.HealthCheck() and cli.HealthCheck("xmhps.ParameterService")
+    with pytest.raises(grpc.RpcError) as he:
+        cli.HealthCheck("no.such.Service")
+    assert he.value.code() == grpc.StatusCode.NOT_FOUND
     # the bytes on the wire: field 1 = raw little-endian u64 keys; the answer is one packed record block
     raw = cli._channel.unary_unary("/xmhps.ParameterService/GetParameter")(
         b"\x0a\x10" + struct.pack("<2Q", 7, 999999), timeout=10)
