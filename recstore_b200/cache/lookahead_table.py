@@ -27,6 +27,13 @@ row that was evicted after it had been announced, which the protection window (s
 steps are never evicted) rules out; a set that is full of protected rows refuses the insert instead, which is reported
 through the device status word (``DEV_TABLE_FULL``): size the cache at several times ``(lookahead + 2) * max_keys``.
 
+Hashed host tier.  With ``host_engine`` (the name of a host KV engine, e.g. ``"KVEngineExtendibleHash"``) the rows live
+in that engine instead of a dense array, so keys are arbitrary non-negative 64-bit ids and ``num_rows`` is only the
+engine's capacity: this is the two-level table of the reference (device hash block over a host hash block,
+src/storage/gpu_cache/uvm_table.h, uvm_table.cu:421-497) with the lookahead staging in front.  A key that the engine
+has never seen reads as its initial value, a pure function of the key, and enters the engine when it is first written
+back.
+
 The host side never spins on the device and the device never waits for the host: the only blocking wait is the
 training thread waiting (bounded) for the worker to have QUEUED the copy of a batch that was announced too late.
 """
@@ -100,20 +107,30 @@ class _Slot:
 class LookaheadCachedTable:
     def __init__(self, num_rows: int, dim: int, cache_rows: int, max_keys: int, *, lr: float = 0.01, eps: float = 1e-10,
                  optimizer: str = "rowwise_adagrad", device: Optional[torch.device] = None, lookahead: int = 2,
-                 init: str = "uniform", seed: int = 0, wait_timeout_s: float = 20.0):
+                 init: str = "uniform", seed: int = 0, wait_timeout_s: float = 20.0, host_engine: Optional[str] = None,
+                 host_engine_config: Optional[dict] = None):
         assert dim % 4 == 0 and lookahead >= 1
         self.N, self.D, self.Dv, self.cap, self.L = int(num_rows), int(dim), int(dim) + 4, int(max_keys), int(lookahead)
         self.dev = dev = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
         self.lr, self.eps, self.optimizer = lr, eps, optimizer
         self.timeout = wait_timeout_s
-        self.host = torch.zeros(self.N, self.Dv).pin_memory()
-        if init == "uniform":
-            b = math.sqrt(1.0 / self.N)
-            self.host[:, :self.D].uniform_(-b, b, generator=torch.Generator().manual_seed(seed))
-        elif init == "row_index":
-            self.host[:, :self.D] = torch.arange(self.N, dtype=torch.float32).unsqueeze(1)
-        elif init != "zeros":
+        self._init, self._seed = init, int(seed)
+        if init not in ("uniform", "row_index", "zeros"):
             raise ValueError(init)
+        self.kv = None
+        if host_engine is not None:
+            from ..storage import BaseKV
+            cfg = {"capacity": self.N, "value_size": self.Dv * 4}
+            cfg.update(host_engine_config or {})
+            self.kv = BaseKV(host_engine, cfg)
+            self.host = None
+        else:
+            self.host = torch.zeros(self.N, self.Dv).pin_memory()
+            if init == "uniform":
+                b = math.sqrt(1.0 / self.N)
+                self.host[:, :self.D].uniform_(-b, b, generator=torch.Generator().manual_seed(seed))
+            elif init == "row_index":
+                self.host[:, :self.D] = torch.arange(self.N, dtype=torch.float32).unsqueeze(1)
         self.cache = GpuCache(cache_rows, self.Dv, dev)
         self.status = self.cache.status
         self.side = torch.cuda.Stream(device=dev)
@@ -152,6 +169,9 @@ class LookaheadCachedTable:
     def close(self):
         self._q.put(None)
         self._worker.join(timeout=5)
+        if self.kv is not None and not self._worker.is_alive():
+            self.kv.close()
+            self.kv = None
 
     # ------------------------------------------------------------------ announce a future batch
     def prefetch(self, ids: torch.Tensor, step: int) -> None:
@@ -184,8 +204,7 @@ class LookaheadCachedTable:
             s.probed.synchronize()
             m = int(s.miss_count_host.item())
             if m:
-                _lib.call("rs_host_gather_rows", self.host.data_ptr(), self.N, self.Dv, s.miss_keys_host.data_ptr(), m,
-                          s.rows_host.data_ptr())
+                self._host_gather(s.miss_keys_host, m, s.rows_host)
             with torch.cuda.stream(self.side):
                 if m:
                     s.rows_dev[:m].copy_(s.rows_host[:m], non_blocking=True)      # one cudaMemcpyAsync for the staged block
@@ -228,8 +247,7 @@ class LookaheadCachedTable:
             m = int(s.evict_count_host.item())
             if m:
                 s.evict_rows_host[:m].copy_(s.evict_rows[:m])          # D2H of the evicted block (worker thread, blocking)
-                _lib.call("rs_host_scatter_rows", self.host.data_ptr(), self.N, self.Dv, s.evict_keys_host.data_ptr(), m,
-                          s.evict_rows_host.data_ptr())
+                self._host_scatter(s.evict_keys_host, m, s.evict_rows_host)
                 self.stats["written_back_rows"] += m
             s.writeback_done.set()
         self._q.put(write_back)
@@ -280,7 +298,48 @@ class LookaheadCachedTable:
         m = int(cnt.item())
         if m:
             k, r = keys[:m].cpu(), rows[:m].cpu()
-            _lib.call("rs_host_scatter_rows", self.host.data_ptr(), self.N, self.Dv, k.data_ptr(), m, r.data_ptr())
+            self._host_scatter(k.contiguous(), m, r.contiguous())
+
+    # ------------------------------------------------------------------ host tier (dense array or KV engine)
+    def _initial_rows(self, keys: torch.Tensor) -> torch.Tensor:
+        """Rows of keys the engine has never stored: a pure function of (seed, key, column)."""
+        n = keys.numel()
+        out = torch.zeros(n, self.Dv)
+        if self._init == "row_index":
+            out[:, :self.D] = keys.to(torch.float32).unsqueeze(1)
+        elif self._init == "uniform":
+            # splitmix64 of (key * D + column + seed), top 24 bits -> U(-b, b); int64 arithmetic wraps like uint64
+            x = keys.view(-1, 1) * self.D + torch.arange(self.D, dtype=torch.int64) + (self._seed * 0x632BE59B + 0x9E3779B9)
+            x = (x ^ (x >> 30).bitwise_and(0x3FFFFFFFF)) * -0x40A7B892E31B1A47
+            x = (x ^ (x >> 27).bitwise_and(0x1FFFFFFFFF)) * -0x6B2FB644ECCEEE15
+            x = x ^ (x >> 31).bitwise_and(0x1FFFFFFFF)
+            u = ((x >> 40).bitwise_and(0xFFFFFF)).to(torch.float32) / float(1 << 24)
+            out[:, :self.D] = (u * 2 - 1) * math.sqrt(1.0 / self.N)
+        return out
+
+    def _host_gather(self, keys_host: torch.Tensor, m: int, rows_host: torch.Tensor) -> None:
+        if self.kv is None:
+            _lib.call("rs_host_gather_rows", self.host.data_ptr(), self.N, self.Dv, keys_host.data_ptr(), m, rows_host.data_ptr())
+            return
+        k = keys_host[:m]
+        rows, found = self.kv.BatchGet(k)
+        if not bool(found.all()):
+            miss = ~found
+            rows[miss] = self._initial_rows(k[miss])
+        rows_host[:m].copy_(rows)
+
+    def _host_scatter(self, keys: torch.Tensor, m: int, rows: torch.Tensor) -> None:
+        if self.kv is None:
+            _lib.call("rs_host_scatter_rows", self.host.data_ptr(), self.N, self.Dv, keys.data_ptr(), m, rows.data_ptr())
+        else:
+            self.kv.BatchPut(keys[:m], rows[:m])
+
+    def host_rows(self, keys) -> torch.Tensor:
+        """``[n, dim + 1]``: weights and Adagrad state of ``keys`` as the host tier holds them (call :meth:`flush` first)."""
+        k = torch.as_tensor(keys, dtype=torch.int64).cpu().contiguous()
+        buf = torch.empty(k.numel(), self.Dv)
+        self._host_gather(k, k.numel(), buf)
+        return buf[:, : self.D + 1]
 
     def check(self) -> None:
         self._check_worker()
@@ -294,8 +353,10 @@ class LookaheadCachedTable:
                                          (" (a cache set was full of protected rows: enlarge the cache)" if word & _lib.DEV_TABLE_FULL else ""))
 
     def weights(self) -> torch.Tensor:
-        """Host view of the weights (call :meth:`flush` first)."""
+        """Host view of the weights (call :meth:`flush` first); dense host tier only, see :meth:`host_rows`."""
+        assert self.host is not None, "a hashed host tier has no dense view: use host_rows(keys)"
         return self.host[:, :self.D]
 
     def state(self) -> torch.Tensor:
+        assert self.host is not None, "a hashed host tier has no dense view: use host_rows(keys)"
         return self.host[:, self.D]

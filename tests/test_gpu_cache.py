@@ -439,3 +439,49 @@ def test_segment_sum_of_duplicate_keys_matches_index_add(D, alpha):
     refn = torch.zeros(U, device=dev, dtype=torch.float64).index_add_(0, inv[keep].long(), g[keep].double().pow(2).sum(1))
     assert (ug.double() - ref).abs().max().item() < 1e-3 * max(1.0, ref.abs().max().item())
     assert (un.double() - refn).abs().max().item() < 1e-4 * max(1.0, refn.abs().max().item())
+
+
+@pytest.mark.parametrize("engine", ["KVEngineExtendibleHash", "KVEnginePoolMap"])
+def test_lookahead_cached_table_over_a_hashed_host_tier(dev, engine):
+    """The two-level table: HBM cache over a host KV engine.  Keys are sparse 40-bit ids; a key the engine has never seen
+    reads as its initial value (a function of the key), updated rows reach the engine when they are evicted or flushed.
+    Oracle: a dict of rows under row-wise Adagrad."""
+    from recstore_b200.cache import LookaheadCachedTable
+    D, n, L, steps = 16, 256, 2, 30
+    tab = LookaheadCachedTable(50000, D, cache_rows=2048, max_keys=n, lr=0.1, eps=1e-8, device=dev, lookahead=L, init="uniform",
+                               seed=4, host_engine=engine)
+    g = torch.Generator().manual_seed(5)
+    universe = torch.randint(1 << 20, 1 << 40, (3000,), generator=g)
+    batches = [universe[torch.randint(0, 3000, (n,), generator=g)] for _ in range(steps + L)]
+    for b in batches:
+        b[::11] = universe[0]                            # a hot key in every batch
+    W, S = {}, {}
+
+    def row(k):
+        if k not in W:
+            W[k] = tab._initial_rows(torch.tensor([k]))[0, :D].clone()
+            S[k] = 0.0
+        return W[k]
+    for t in range(L):
+        tab.prefetch(batches[t].to(dev), t)
+    for t in range(steps):
+        tab.prefetch(batches[t + L].to(dev), t + L)
+        ids = batches[t]
+        rows = tab.lookup(ids.to(dev), t).cpu()
+        exp = torch.stack([row(int(k)) for k in ids.tolist()])
+        assert torch.allclose(rows, exp, atol=1e-4, rtol=1e-5), (t, (rows - exp).abs().max().item())
+        grads = torch.randn(n, D, generator=g)
+        tab.update(grads.to(dev))
+        for k in set(ids.tolist()):                      # every occurrence adds mean(g^2); all apply with the post-step state
+            sel = (ids == k)
+            S[k] += float(grads[sel].pow(2).mean(1).sum())
+            W[k] = W[k] - 0.1 * grads[sel].sum(0) / (S[k] ** 0.5 + 1e-8)
+    tab.check()
+    assert tab.stats["late_announcements"] == 0 and tab.stats["staged_rows"] > 0
+    tab.flush()
+    keys = torch.tensor(sorted(W)[:500])
+    got = tab.host_rows(keys)
+    assert torch.allclose(got[:, :D], torch.stack([W[int(k)] for k in keys]), atol=1e-3, rtol=1e-4)
+    assert torch.allclose(got[:, D], torch.tensor([S[int(k)] for k in keys]), atol=1e-3, rtol=2e-3)
+    assert len(tab.kv) <= len(W)                          # only keys that were written back are stored
+    tab.close()
