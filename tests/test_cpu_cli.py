@@ -172,3 +172,16 @@ def test_dlrm_driver_trains_on_criteo_format_files(tmp_path):
     raw.unlink()                                                           # the cached file is enough now
     out2 = dlrm_main.main(base + ["--data-sub-sample-rate", "0.3", "--data-randomize", "none"])
     assert 0 < out2["steps"] <= 6 * 9
+
+
+def test_perf_emb_eight_workers_smoke():
+    """Eight worker processes (the reference's 8-process multi-card start-up check, src/executable/test/test_multicard.py)
+    through the whole cached-embedding step on gloo: shared-memory table, controller on rank 0, all-to-alls among eight
+    ranks, and the differential check against the replicated embedding."""
+    from recstore_b200.cli import perf_emb
+    out = perf_emb.main(["--num_workers", "8", "--device", "cpu", "--run_steps", "4", "--num_embs", "4000", "--emb_dim", "8",
+                         "--batch_size", "64", "--L", "2", "--diff_test", "--log_interval", "100",
+                         "--emb_choice", "KnownShardedCachedEmbedding"])
+    assert len(out) == 8
+    for r, v in dict(out).items():
+        assert v[0] == 4 and v[1] < 1e-4, (r, v)

@@ -478,3 +478,16 @@ def test_pool_map_engine_concurrent_readers_never_see_torn_or_freed_values(tmp_p
     assert torch.equal(found, exp) and torch.equal(got[found], final[found])
     kv2.close()
     kv.close()
+
+
+@pytest.mark.parametrize("engine", ["KVEngineChunkHash", "KVEnginePoolMap"])
+def test_hash_api_adapter_semantics(engine):
+    """find / insert / update / remove as a hash-evaluation harness calls them (PiBenchWrapper.cc of the reference)."""
+    from recstore_b200.storage import HashAPI
+    h = HashAPI(engine, {"capacity": 1000, "value_size": 16})
+    one, two = torch.full((4,), 1.0), torch.full((4,), 2.0)
+    assert h.find(5) is None and not h.update(5, one) and not h.remove(5)
+    assert h.insert(5, one) and not h.insert(5, two) and torch.equal(h.find(5), one)
+    assert h.update(5, two) and torch.equal(h.find(5), two) and len(h) == 1
+    assert h.remove(5) and h.find(5) is None and len(h) == 0
+    h.close()
