@@ -306,6 +306,7 @@ struct ThreadSlots {
   struct Held {
     uint64_t manager;
     std::shared_ptr<void> keep;            // keeps the slot array alive past the manager
+    std::shared_ptr<std::atomic<bool>> alive;   // cleared by the manager's destructor
     std::atomic<uint64_t>* owner;
     void* slot;
   };
@@ -318,19 +319,26 @@ struct ThreadSlots {
 thread_local ThreadSlots t_slots;
 }  // namespace
 
-EpochManager::EpochManager() : slots_(new Slot[kSlots]), stripes_(new Stripe[kStripes]), id_(g_manager_ids.fetch_add(1) + 1) {}
+EpochManager::EpochManager()
+    : slots_(new Slot[kSlots]), stripes_(new Stripe[kStripes]), alive_(std::make_shared<std::atomic<bool>>(true)),
+      id_(g_manager_ids.fetch_add(1) + 1) {}
+
+EpochManager::~EpochManager() { alive_->store(false, std::memory_order_release); }
 
 EpochManager::Slot* EpochManager::my_slot() {
   for (auto& h : t_slots.held)
     if (h.manager == id_) return static_cast<Slot*>(h.slot);
-  // First use by this thread: claim a free slot.  Managers that have gone leave stale entries behind, they only cost a
-  // comparison here.
+  // First use by this thread: entries of managers that have gone are dropped (with their share of the slot arrays),
+  // then a free slot is claimed.
+  auto& held = t_slots.held;
+  held.erase(std::remove_if(held.begin(), held.end(), [](const ThreadSlots::Held& h) { return !h.alive->load(std::memory_order_acquire); }),
+             held.end());
   for (int round = 0; round < 1 << 20; ++round) {
     for (int i = 0; i < kSlots; ++i) {
       uint64_t expect = 0;
       if (slots_[i].owner.compare_exchange_strong(expect, t_slots.token, std::memory_order_acq_rel)) {
         slots_[i].depth = 0;
-        t_slots.held.push_back({id_, std::shared_ptr<void>(slots_, slots_.get()), &slots_[i].owner, &slots_[i]});
+        t_slots.held.push_back({id_, std::shared_ptr<void>(slots_, slots_.get()), alive_, &slots_[i].owner, &slots_[i]});
         return &slots_[i];
       }
     }

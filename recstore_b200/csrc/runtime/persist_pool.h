@@ -94,6 +94,7 @@ class EpochManager {
  public:
   static constexpr int kSlots = 256;
   EpochManager();
+  ~EpochManager();
   // Publishes the current epoch for the calling thread; nests (only the outermost pair publishes / clears).
   void Protect();
   void Unprotect();
@@ -131,6 +132,7 @@ class EpochManager {
   };
   size_t CollectStripe(Stripe& st, uint64_t safe_below);
   std::unique_ptr<Stripe[]> stripes_;
+  std::shared_ptr<std::atomic<bool>> alive_;   // threads drop their slot bookkeeping for a manager that is gone
   const uint64_t id_;
 };
 
