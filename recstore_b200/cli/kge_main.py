@@ -11,7 +11,8 @@ that each worker's hot entities are contiguous -> one training process per worke
 
 Engines: on ``--device cuda`` TransE (L1 / L2), DistMult, ComplEx, SimplE and RotatE run on the native path (entity and
 relation tables row-sharded over the GPUs' HBM; tcgen05 scoring where the negative scores are cross products, fp32 pair
-kernels for the L1 / modulus distances; RESCAL with a row-blocked matrix table); TransR, and ``--device cpu``, run the PyTorch implementation on
+kernels for the L1 / modulus distances; RESCAL with a row-blocked matrix table; TransR with the same tables and its
+scoring as autograd over batched cuBLAS GEMMs); ``--device cpu`` runs the PyTorch implementation on
 tables shared between the worker processes (lock-free updates, as the reference's stock path does).  Prints
 ``Successfully xmh`` when done.
 
@@ -32,7 +33,7 @@ import time
 import numpy as np
 import torch
 
-NATIVE_MODELS = ("TransE", "TransE_l1", "TransE_l2", "DistMult", "ComplEx", "SimplE", "RotatE", "RESCAL")
+NATIVE_MODELS = ("TransE", "TransE_l1", "TransE_l2", "DistMult", "ComplEx", "SimplE", "RotatE", "RESCAL", "TransR")
 
 
 def parse_args(argv=None):
@@ -199,7 +200,7 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
         hbm = (args.cache_ratio if args.cache_ratio > 0 else 0.25) if args.mix_cpu_gpu else 1.0
         model = KGEModel(KGEConfig(ds.n_entities, ds.n_relations, dim=args.dim, model=args.model_name, gamma=args.gamma,
                                    batch=args.batch_size, neg_sample_size=args.neg_sample_size, neg_chunk_size=args.neg_chunk_size,
-                                   lr=args.lr, seed=args.seed, dataset=ds.name, use_cuda_graph=not args.no_graph,
+                                   lr=args.lr, seed=args.seed, dataset=ds.name, use_cuda_graph=(not args.no_graph) and args.model_name != "TransR",
                                    entity_hbm_ratio=hbm), ctx)
         step_fn = lambda h, r, t, n, ch: model.train_step(h, r, t, n, ch)
     else:

@@ -16,8 +16,11 @@ products (TransE-L2, DistMult, ComplEx, SimplE) and three pair-walking fp32 kern
 a matrix-vector product per positive, the negatives' scores are a . e'.  Its relation table is ROW-BLOCKED: relation r
 owns the D table rows r*D .. r*D+D-1 (the rows of its D x D matrix), and every row is updated with the squared norm of
 the whole matrix gradient / D, so that all D rows carry the same Adagrad accumulator: one state per relation, as the
-reference's [n_relations, D*D] embedding has.  TransR (which projects every negative with the matrix of every positive
-of its chunk) runs on the PyTorch path only.
+reference's [n_relations, D*D] embedding has.  TransR (score gamma - |h M_r + r - t M_r|_1, score_fun.py:110-220) projects
+every negative with the matrix of every positive of its chunk, a batched [ns x D] x [D x D] product per positive: its
+tables live on the same sharded HBM plane (entities, relation vectors, a row-blocked projection table), and the scoring
+between lookup and update is PyTorch autograd over ``torch.einsum`` / cuBLAS batched GEMMs (plain library GEMMs; there is
+no fused kernel for it).
 
 Checkpoints keep the reference layout (tensor_models.py:452-476, general_models.py:316-346):
 ``{dataset}_{model}_entity.npy``, ``{dataset}_{model}_relation.npy`` and ``config.json``.
@@ -43,7 +46,8 @@ _lib.register_signatures({
                            vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
 })
 
-MODELS = {"TransE": 0, "TransE_l2": 0, "DistMult": 1, "ComplEx": 2, "SimplE": 3, "TransE_l1": 4, "RotatE": 5, "RESCAL": 6}
+MODELS = {"TransE": 0, "TransE_l2": 0, "DistMult": 1, "ComplEx": 2, "SimplE": 3, "TransE_l1": 4, "RotatE": 5, "RESCAL": 6,
+          "TransR": 7}                # 7: tables on the HBM plane, scoring by autograd over batched library GEMMs
 PAIRWISE = (4, 5)                     # no cross-product form: scored pair by pair in fp32
 
 
@@ -81,6 +85,9 @@ class KGEModel:
         self.model_id = MODELS[cfg.model]
         self.pairwise = self.model_id in PAIRWISE
         self.rescal = cfg.model == "RESCAL"
+        self.transr = cfg.model == "TransR"
+        if self.transr:
+            assert not cfg.use_cuda_graph, "TransR scores through autograd: no graph replay"
         self.Dr = self.D // 2 if cfg.model == "RotatE" else self.D      # RotatE relations are phases
         if self.rescal:
             assert self.D <= 512, "RESCAL: dim <= 512"
@@ -95,6 +102,12 @@ class KGEModel:
             self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations * self.D, self.D, max_keys=self.bs * self.D,
                                                   lr=cfg.lr, eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 1)
             self._row_of_block = torch.arange(self.D, dtype=torch.int64, device=dev)
+        elif self.transr:  # relation vectors, and a row-blocked table of D x D projection matrices (D rows per relation)
+            self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations, self.Dr, max_keys=self.bs, lr=cfg.lr,
+                                                  eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 1)
+            self.proj = ShardedEmbeddingTable(self.ctx, "kge_proj", cfg.n_relations * self.D, self.Dr, max_keys=self.bs * self.D,
+                                              lr=cfg.lr, eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 2)
+            self._row_of_block = torch.arange(self.D, dtype=torch.int64, device=dev)
         else:
             self.relation = ShardedEmbeddingTable(self.ctx, "kge_relation", cfg.n_relations, self.Dr, max_keys=self.bs, lr=cfg.lr,
                                                   eps=cfg.eps, init="uniform", init_scale=scale, seed=cfg.seed + 1)
@@ -104,9 +117,12 @@ class KGEModel:
         self.rel_rows = torch.empty(self.bs, self.Dr, **f)
         self.ent_grad = torch.empty(n_ids, self.D, **f)
         self.rel_grad = torch.empty(self.bs, self.Dr, **f)
-        if self.rescal:
+        if self.rescal or self.transr:
             self._rel_keys = torch.empty(self.bs * self.D, dtype=torch.int64, device=dev)
             self._rel_norm = torch.empty(self.bs * self.D, **f)
+        if self.transr:
+            self.proj_rows = torch.empty(self.bs * self.D, self.Dr, **f)
+            self.proj_grad = torch.empty(self.bs * self.D, self.Dr, **f)
         self.A = torch.zeros(self.bs, self.Dp, **b)
         self.Bn = torch.zeros(self.nneg, self.Dp, **b)
         self.a2 = torch.empty(self.bs, **f)
@@ -157,6 +173,44 @@ class KGEModel:
             self.relation.lookup(self._rel_keys, out=self.rel_rows.view(self.bs * self.D, self.D))
         else:
             self.relation.lookup(r_ids.contiguous(), out=self.rel_rows)
+        if self.transr:
+            self._rel_keys.copy_((r_ids.view(-1, 1) * self.D + self._row_of_block).view(-1))
+            self.proj.lookup(self._rel_keys, out=self.proj_rows)
+
+    # ------------------------------------------------------------------ TransR: autograd over batched library GEMMs
+    def _transr_scores(self, h, r, t, neg, M, corrupt_head: bool):
+        """pos [bs], neg [bs, ns]: gamma - |x M + r - y M|_1 with the negatives of a chunk projected by every positive's
+        own matrix (one batched [ns x D] x [D x Dr] product per positive)."""
+        bs, C, cs, ns, D, Dr = self.bs, self.C, self.cs, self.ns, self.D, self.Dr
+        hp = torch.einsum("nd,ndk->nk", h, M)
+        tp = torch.einsum("nd,ndk->nk", t, M)
+        pos = self.cfg.gamma - (hp + r - tp).abs().sum(-1)
+        P = torch.einsum("cjd,cidk->cijk", neg.view(C, ns, D), M.view(C, cs, D, Dr))        # projected negatives
+        if corrupt_head:
+            diff = P + (r - tp).view(C, cs, 1, Dr)
+        else:
+            diff = (hp + r).view(C, cs, 1, Dr) - P
+        return pos, (self.cfg.gamma - diff.abs().sum(-1)).view(bs, ns)
+
+    def _transr_step(self, corrupt_head: bool) -> torch.Tensor:
+        bs, D = self.bs, self.D
+        leaf = lambda x: x.detach().requires_grad_(True)
+        h, t, neg = leaf(self.ent_rows[:bs]), leaf(self.ent_rows[bs:2 * bs]), leaf(self.ent_rows[2 * bs:])
+        r, M = leaf(self.rel_rows), leaf(self.proj_rows.view(bs, D, self.Dr))
+        with torch.enable_grad():
+            pos, negs = self._transr_scores(h, r, t, neg, M, corrupt_head)
+            loss = (-torch.nn.functional.logsigmoid(pos).mean() - torch.nn.functional.logsigmoid(-negs).mean()) / 2
+            loss.backward()
+        self.ent_grad[:bs].copy_(h.grad); self.ent_grad[bs:2 * bs].copy_(t.grad); self.ent_grad[2 * bs:].copy_(neg.grad)
+        self.rel_grad.copy_(r.grad)
+        self.proj_grad.copy_(M.grad.view(bs * D, self.Dr))
+        self.entity.update(self.ent_grad)
+        self.relation.update(self.rel_grad)
+        # one Adagrad state per relation: every row of a matrix is accounted the whole matrix's squared norm / D
+        self._rel_norm.copy_((M.grad.pow(2).sum((1, 2)) / D).view(-1, 1).expand(bs, D).reshape(-1))
+        self.proj.update(self.proj_grad, norms=self._rel_norm)
+        self.launches_per_step = self.entity.launches + self.relation.launches + self.proj.launches
+        return loss.detach()
 
     def train_step(self, h_ids: torch.Tensor, r_ids: torch.Tensor, t_ids: torch.Tensor, neg_ids: torch.Tensor,
                    corrupt_head: Optional[bool] = None) -> torch.Tensor:
@@ -190,6 +244,8 @@ class KGEModel:
     def _step(self, h_ids, r_ids, t_ids, neg_ids, corrupt_head: bool) -> torch.Tensor:
         st = self.ctx.status
         self._fetch(h_ids, r_ids, t_ids, neg_ids)
+        if self.transr:
+            return self._transr_step(corrupt_head)
         self._forward(corrupt_head, False)
         if not self.pairwise:
             F_.gemm_bf16(self.W, self.Bn, self.GA, mode=2, epi=F_.EPI_F32, status=st)
@@ -208,6 +264,10 @@ class KGEModel:
     def score_batch(self, h_ids, r_ids, t_ids, neg_ids, corrupt_head: bool) -> Tuple[torch.Tensor, torch.Tensor]:
         """Scores of the positives ``[batch]`` and of every (positive, chunk negative) pair ``[batch, neg_sample_size]``."""
         self._fetch(h_ids, r_ids, t_ids, neg_ids)
+        if self.transr:
+            bs = self.bs
+            return self._transr_scores(self.ent_rows[:bs], self.rel_rows, self.ent_rows[bs:2 * bs], self.ent_rows[2 * bs:],
+                                       self.proj_rows.view(bs, self.D, self.Dr), corrupt_head)
         self._forward(corrupt_head, True)
         return self.pos_score.clone(), self.neg_score.clone()
 
@@ -252,10 +312,13 @@ class KGEModel:
         os.makedirs(path, exist_ok=True)
         ent = self._gather_table(self.entity)
         rel = self._gather_table(self.relation)
+        prj = self._gather_table(self.proj) if self.transr else None
         if self.ctx.rank == 0:
             c = self.cfg
             if self.rescal:
                 rel = rel.reshape(c.n_relations, self.D * self.D)
+            if prj is not None:      # the reference's name for the TransR matrices (score_fun.py TransRScore.save)
+                np.save(os.path.join(path, f"{c.dataset}_{c.model}projection.npy"), prj.reshape(c.n_relations, self.D * self.Dr))
             np.save(os.path.join(path, f"{c.dataset}_{c.model}_entity.npy"), ent)
             np.save(os.path.join(path, f"{c.dataset}_{c.model}_relation.npy"), rel)
             conf = asdict(c)
@@ -266,10 +329,11 @@ class KGEModel:
 
     def load(self, path: str) -> None:
         c = self.cfg
-        for tab, kind in ((self.entity, "entity"), (self.relation, "relation")):
-            full = torch.from_numpy(np.load(os.path.join(path, f"{c.dataset}_{c.model}_{kind}.npy")))
-            if self.rescal and kind == "relation":
-                full = full.reshape(c.n_relations * self.D, self.D)
+        tabs = [(self.entity, "_entity"), (self.relation, "_relation")] + ([(self.proj, "projection")] if self.transr else [])
+        for tab, kind in tabs:
+            full = torch.from_numpy(np.load(os.path.join(path, f"{c.dataset}_{c.model}{kind}.npy")))
+            if (self.rescal and kind == "_relation") or kind == "projection":
+                full = full.reshape(c.n_relations * self.D, -1)
             mine = full[self.ctx.rank::self.ctx.world]
             hot = min(mine.shape[0], tab.weight.shape[0])
             tab.weight[:hot].copy_(mine[:hot])

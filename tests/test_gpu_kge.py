@@ -156,3 +156,57 @@ def test_rescal_trains_with_graph_replay_and_keeps_the_reference_checkpoint_shap
     m2 = KGEModel(cfg)
     m2.load(str(tmp_path))
     assert torch.equal(m2.relation.weight[: 8 * 32], m.relation.weight[: 8 * 32])
+
+
+@pytest.mark.parametrize("corrupt_head", [False, True])
+def test_transr_on_the_hbm_plane_matches_the_per_pair_definition(corrupt_head, tmp_path):
+    """TransR with its tables on the sharded HBM plane (entities, relation vectors, row-blocked projection matrices) and
+    batched-GEMM scoring: scores, loss and one optimizer step against the per-pair definition under autograd, with ONE
+    Adagrad state per projection matrix; the projection checkpoint has the reference's name and shape."""
+    from recstore_b200.models.kge import KGEConfig, KGEModel
+    from recstore_b200.baseline.kge_torch import chunk_neg_score, edge_score, logsigmoid_loss
+    from recstore_b200.baseline.dlrm_torch import rowwise_adagrad_update
+    import numpy as np, os
+    dev = torch.device("cuda:0")
+    cfg = KGEConfig(n_entities=1500, n_relations=10, dim=16, model="TransR", gamma=8.0, batch=128, neg_sample_size=32,
+                    neg_chunk_size=32, lr=0.1, seed=3)
+    m = KGEModel(cfg)
+    bs, ns, cs, D = cfg.batch, cfg.neg_sample_size, cfg.neg_chunk_size, cfg.dim
+    g = torch.Generator(device=dev).manual_seed(1)
+    E = m.entity.weight[: cfg.n_entities].clone(); R = m.relation.weight[: cfg.n_relations].clone()
+    P = m.proj.weight[: cfg.n_relations * D].clone().view(cfg.n_relations, D * D)
+    SE = torch.zeros(cfg.n_entities, device=dev); SR = torch.zeros(cfg.n_relations, device=dev); SP = torch.zeros(cfg.n_relations, device=dev)
+    for step in range(2):
+        hi = torch.randint(0, 100, (bs,), device=dev, generator=g)
+        ti = torch.randint(0, cfg.n_entities, (bs,), device=dev, generator=g)
+        ri = torch.randint(0, cfg.n_relations, (bs,), device=dev, generator=g)
+        ni = torch.randint(0, cfg.n_entities, (bs // cs * ns,), device=dev, generator=g)
+        h = E[hi].clone().requires_grad_(True); t = E[ti].clone().requires_grad_(True); n = E[ni].clone().requires_grad_(True)
+        r = R[ri].clone().requires_grad_(True); M = P[ri].clone().requires_grad_(True)
+        pos_ref = edge_score("TransR", h, r, t, cfg.gamma, M)
+        neg_ref = chunk_neg_score("TransR", h, r, t, n, corrupt_head, cs, cfg.gamma, M)
+        loss_ref = logsigmoid_loss(pos_ref, neg_ref)
+        loss_ref.backward()
+        pos, negs = m.score_batch(hi, ri, ti, ni, corrupt_head)
+        assert torch.allclose(pos, pos_ref, atol=1e-4, rtol=1e-4) and torch.allclose(negs, neg_ref, atol=1e-4, rtol=1e-4)
+        loss = m.train_step(hi, ri, ti, ni, corrupt_head)
+        assert abs(loss.item() - loss_ref.item()) < 1e-4 * max(1.0, abs(loss_ref.item()))
+        ge = torch.cat([h.grad, t.grad, n.grad])
+        assert ((m.ent_grad - ge).norm() / ge.norm()).item() < 1e-3
+        assert ((m.proj_grad.view(bs, D * D) - M.grad).norm() / M.grad.norm()).item() < 1e-3
+        rowwise_adagrad_update(E, SE, torch.cat([hi, ti, ni]), ge.detach(), cfg.lr, cfg.eps)
+        rowwise_adagrad_update(R, SR, ri, r.grad.detach(), cfg.lr, cfg.eps)
+        rowwise_adagrad_update(P, SP, ri, M.grad.detach(), cfg.lr, cfg.eps)
+        torch.cuda.synchronize()
+        assert torch.allclose(m.entity.weight[: cfg.n_entities], E, atol=2e-3, rtol=2e-3)
+        assert torch.allclose(m.relation.weight[: cfg.n_relations], R, atol=2e-3, rtol=2e-3)
+        assert torch.allclose(m.proj.weight[: cfg.n_relations * D].view(cfg.n_relations, D * D), P, atol=2e-3, rtol=2e-3)
+        st = m.proj.state[: cfg.n_relations * D].view(cfg.n_relations, D)
+        assert torch.allclose(st, SP.view(-1, 1).expand_as(st), atol=1e-6, rtol=2e-3)
+    m.ctx.check_status()
+    m.save(str(tmp_path))
+    prj = np.load(os.path.join(tmp_path, "synthetic_TransRprojection.npy"))
+    assert prj.shape == (10, D * D)
+    m2 = KGEModel(cfg)
+    m2.load(str(tmp_path))
+    assert torch.equal(m2.proj.weight[: 10 * D], m.proj.weight[: 10 * D])
