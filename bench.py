@@ -254,7 +254,8 @@ def run_kge(args):
     ctx = PeerContext(rank, world, device=dev)
     NE, NR, D, bs, ns = args.kge_entities, 14824, 400, 1024, 256
     cfg = KGEConfig(NE, NR, dim=D, model=args.kge_model, gamma=10.0, batch=bs, neg_sample_size=ns, neg_chunk_size=ns, lr=0.1,
-                    seed=args.seed, use_cuda_graph=not args.no_graph)
+                    seed=args.seed, use_cuda_graph=(not args.no_graph) and args.kge_model != "TransR",   # TransR scores through autograd
+                    tf32_scoring=args.kge_model == "TransR")
     model = KGEModel(cfg, ctx)
     nneg = bs // ns * ns
     nb = 8
@@ -305,7 +306,10 @@ def run_kge(args):
         out = {
             "metric": "kge_train_triples_per_s", "value": bs * world * args.steps / (ms_dev * 1e-3), "unit": "triples/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp32 tables, bf16 score GEMMs", "impl": "native",
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": ("fp32 tables, tf32 batched score GEMMs (cuBLAS, autograd)" if args.kge_model == "TransR" else
+                      "fp32 tables, fp32 pair kernels" if args.kge_model in ("TransE_l1", "RotatE") else "fp32 tables, bf16 score GEMMs"),
+            "impl": "native",
             "data": "synthetic (power-law alpha 1.3 head / tail entities, uniform relations and negatives, drawn on the device)",
             "config": {"model": f"{args.kge_model}, {NE} entities x dim {D} fp32 ({NE * D * 4 / 1e9:.0f} GB) sharded over {world} GPU(s), {NR} relations",
                        "global_batch": bs * world, "negatives": f"{ns} chunk-shared uniform per {ns} positives", "gamma": 10.0,
@@ -401,7 +405,7 @@ def main():
     ap.add_argument("--workload", default="dlrm", choices=["dlrm", "dcnv2", "kge"],
                     help="dlrm: the headline config; dcnv2: the multi-hot DLRM-DCNv2 config; kge: knowledge-graph embedding training "
                          "(native arm only for the last two)")
-    ap.add_argument("--kge-model", default="TransE_l2", choices=["TransE_l2", "DistMult", "ComplEx", "SimplE", "TransE_l1", "RotatE", "RESCAL"])
+    ap.add_argument("--kge-model", default="TransE_l2", choices=["TransE_l2", "DistMult", "ComplEx", "SimplE", "TransE_l1", "RotatE", "RESCAL", "TransR"])
     ap.add_argument("--kge-entities", type=int, default=86_054_151, help="entities of the kge workload (the config's Freebase count)")
     ap.add_argument("--row-split", default="auto",
                     help="dcnv2 workload: tables spread row-wise over the GPUs: auto (those with more than 1/N of the ids per sample), "

@@ -67,6 +67,7 @@ class KGEConfig:
     dataset: str = "synthetic"
     entity_hbm_ratio: float = 1.0     # < 1: that share of every entity shard stays in HBM (low ids), the rest in pinned host memory
     use_cuda_graph: bool = False      # capture the step (one graph per corruption side) and replay it: ~40 launches per step
+    tf32_scoring: bool = False        # TransR: run its batched fp32 GEMMs with TF32 tensor-core math (10-bit mantissa products)
 
 
 class KGEModel:
@@ -197,10 +198,15 @@ class KGEModel:
         leaf = lambda x: x.detach().requires_grad_(True)
         h, t, neg = leaf(self.ent_rows[:bs]), leaf(self.ent_rows[bs:2 * bs]), leaf(self.ent_rows[2 * bs:])
         r, M = leaf(self.rel_rows), leaf(self.proj_rows.view(bs, D, self.Dr))
-        with torch.enable_grad():
-            pos, negs = self._transr_scores(h, r, t, neg, M, corrupt_head)
-            loss = (-torch.nn.functional.logsigmoid(pos).mean() - torch.nn.functional.logsigmoid(-negs).mean()) / 2
-            loss.backward()
+        old_tf32 = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = bool(self.cfg.tf32_scoring)
+        try:
+            with torch.enable_grad():
+                pos, negs = self._transr_scores(h, r, t, neg, M, corrupt_head)
+                loss = (-torch.nn.functional.logsigmoid(pos).mean() - torch.nn.functional.logsigmoid(-negs).mean()) / 2
+                loss.backward()
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = old_tf32
         self.ent_grad[:bs].copy_(h.grad); self.ent_grad[bs:2 * bs].copy_(t.grad); self.ent_grad[2 * bs:].copy_(neg.grad)
         self.rel_grad.copy_(r.grad)
         self.proj_grad.copy_(M.grad.view(bs * D, self.Dr))
