@@ -479,6 +479,22 @@ def test_dist_embedding_api_on_the_hbm_plane_matches_the_host_table():
     assert all(out.get(r) == "ok" for r in range(2)), dict(out)
 
 
+@pytest.mark.parametrize("model", ["RESCAL", "TransR"])
+def test_kge_matrix_models_two_gpus(model):
+    """The models with a matrix per relation on two GPUs: the D rows of a relation's matrix are spread over both ranks
+    (cyclic ownership of the row-blocked table) and still share one Adagrad accumulator value; training reduces the loss."""
+    if _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    from recstore_b200.cli import kge_main
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    out, info = kge_main.main(["--device", "cuda", "--num_proc", "2", "--model_name", model, "--max_step", "150",
+                               "--n_entities", "3000", "--n_triples", "30000", "--hidden_dim", "16", "--gamma", "8",
+                               "--batch_size", "128", "--neg_sample_size", "32", "--log_interval", "1000"])
+    assert len(out) == 2
+    for r in (0, 1):
+        assert out[r]["last_loss"] < 0.85 * out[r]["first_loss"], out[r]
+
+
 def test_kge_driver_two_gpus_native_path():
     """TransE-L2 on entity / relation tables sharded over two GPUs, through the training driver."""
     if _ngpus() < 2:
