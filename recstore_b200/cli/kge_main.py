@@ -93,7 +93,7 @@ def parse_args(argv=None):
     p.add_argument("--gpu", type=int, nargs="+", default=None, help="GPU ids: selects --device cuda and one worker per GPU")
     p.add_argument("--nr_gpus", type=int, default=None)
     p.add_argument("--mix_cpu_gpu", action="store_true", help="keep only the hot share (--cache_ratio) of the entity table in HBM")
-    p.add_argument("--async_update", action="store_true", help="PyTorch path: a worker thread applies the entity updates behind the trainer; the native step already overlaps its sparse update")
+    p.add_argument("--async_update", action="store_true", help="PyTorch path: a worker thread applies the entity updates behind the trainer; no effect on the native path (its update is a few kernels inside the step)")
     p.add_argument("--use_my_emb", type=lambda v: str(v).lower() in ("1", "true", "yes"), default=True,
                    help="RecStore embedding path (here: the native sharded tables); false = the PyTorch tables")
     p.add_argument("--cached_emb_type", default="KnownShardedCachedEmbedding")
