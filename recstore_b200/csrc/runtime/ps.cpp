@@ -147,7 +147,10 @@ class CachePS {
     }
     return applied;
   }
-  void LoadFakeData(uint64_t n) {
+  // Keys 0 .. n-1 with value = key.  A count beyond the engine's capacity (a garbled or hostile request) is cut down
+  // to the capacity instead of looping over it; returns how many keys were written.
+  uint64_t LoadFakeData(uint64_t n) {
+    n = std::min<uint64_t>(n, kv_->config().capacity);
     auto body = [&](size_t b, size_t e, int) {
       std::vector<float> rec(dim_ + 1);
       for (size_t k = b; k < e; ++k) {
@@ -157,6 +160,7 @@ class CachePS {
       }
     };
     ThreadPool::global().parallel_for(n, body);
+    return n;
   }
   void Clear() { kv_->Clear(); }
 
@@ -406,8 +410,7 @@ class PsServer {
     } else if (f.op == OP_FAKE) {
       uint64_t n = 0;
       if (f.len >= 8) memcpy(&n, in.data(), 8);
-      ps_->LoadFakeData(n);
-      put8(n);
+      put8(ps_->LoadFakeData(n));
     } else if (f.op == OP_SAVE || f.op == OP_LOAD) {
       const std::string path(in.data(), in.size());
       put8(f.op == OP_SAVE ? ps_->SaveCkpt(path) : ps_->LoadCkpt(path));

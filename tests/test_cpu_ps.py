@@ -380,3 +380,44 @@ def test_pooled_server_keeps_request_order_per_connection(scheduler):
     assert st["pooled_requests"] >= 4 * (6 * 5 + 1) and st["requests"] > st["pooled_requests"]
     c.close()
     ps.close()
+
+
+def test_grpc_server_survives_random_request_bytes():
+    """Every method fed with random and truncated byte strings: the call ends with a gRPC status (or a well-formed answer
+    when the bytes happen to parse), never with a dead server; afterwards the shard still answers and still holds its rows."""
+    import random
+    import grpc
+    from recstore_b200.ps.client import ParameterServer
+    from recstore_b200.ps import grpc_transport as gt
+    D = 8
+    ps = ParameterServer("KVEngineMap", {"dim": D, "capacity": 1 << 14})
+    ps.LoadFakeData(500)
+    srv = gt.GrpcParameterServer(ps)
+    cli = gt.GrpcParameterClient("127.0.0.1", srv.port, 0, D, timeout_s=5.0)
+    good_put = gt.PutParameterRequest(parameter_value=__import__("recstore_b200.ps.client", fromlist=["pack_records"]).pack_records(
+        torch.arange(4), torch.ones(4, D))).SerializeToString()
+    rng = random.Random(7)
+    outcomes = {"ok": 0, "status": 0}
+    for method in ("GetParameter", "PutParameter", "UpdateParameter", "Command"):
+        call = cli._channel.unary_unary(f"/xmhps.ParameterService/{method}")
+        for trial in range(40):
+            if trial % 4 == 0:
+                blob = good_put[: rng.randrange(len(good_put))]                  # a truncated valid message
+            elif trial % 4 == 1:
+                b = bytearray(good_put)
+                b[rng.randrange(len(b))] ^= 1 << rng.randrange(8)                  # one flipped bit
+                blob = bytes(b)
+            else:
+                blob = bytes(rng.randrange(256) for _ in range(rng.randrange(1, 200)))
+            try:
+                call(blob, timeout=5)
+                outcomes["ok"] += 1
+            except grpc.RpcError as e:
+                assert e.code() in (grpc.StatusCode.INVALID_ARGUMENT, grpc.StatusCode.INTERNAL, grpc.StatusCode.NOT_FOUND,
+                                    grpc.StatusCode.FAILED_PRECONDITION, grpc.StatusCode.UNKNOWN), e.code()
+                outcomes["status"] += 1
+    assert outcomes["status"] > 20, outcomes
+    assert cli.HealthCheck()
+    got = cli.GetParameter(torch.arange(100, 110))
+    assert got.shape == (10, D)
+    srv.stop(0)
