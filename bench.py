@@ -329,6 +329,61 @@ def run_kge(args):
         dist.destroy_process_group()
 
 
+def run_kge_torch(args):
+    """The KG workload on the PyTorch path (`baseline/kge_torch.py`: dense tables on one device, autograd scoring with
+    the bmm-style chunked negatives, sparse row-wise Adagrad through index_add_), same ids and shapes as `run_kge`.
+    One GPU; --kge-entities sizes the table (the PyTorch path builds it on the host first)."""
+    from recstore_b200.baseline.kge_torch import TorchKGE
+    from recstore_b200.utils.data import device_uniform_ids, device_zipf_ids
+    rank, world, local = dist_setup(args.gpus)
+    assert world == 1, "the PyTorch KG arm is single-GPU"
+    dev = torch.device(f"cuda:{local}")
+    NE, NR, D, bs, ns = args.kge_entities, 14824, 400, 1024, 256
+    m = TorchKGE(NE, NR, D, args.kge_model, gamma=10.0, lr=0.1, device=dev, seed=args.seed)
+    nneg, nb = bs // ns * ns, 8
+
+    def draw(k):
+        c = k * 4 * bs
+        return (device_zipf_ids(bs, NE, 1.3, args.seed + 11, c, device=dev, spread=True),
+                device_uniform_ids(bs, NR, args.seed + 12, c, device=dev),
+                device_zipf_ids(bs, NE, 1.3, args.seed + 13, c, device=dev, spread=True),
+                device_uniform_ids(nneg, NE, args.seed + 14, c, device=dev))
+    dev_batches = [draw(k) for k in range(nb)]
+    host_batches = [tuple(t.cpu().pin_memory() for t in b) for b in dev_batches]
+    for i in range(max(args.warmup, 3)):
+        m.train_step(*dev_batches[i % nb], ns)
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(args.steps):
+        m.train_step(*dev_batches[i % nb], ns)
+    e1.record()
+    e1.synchronize()
+    clocks = sampler.stop()
+    ms_dev = e0.elapsed_time(e1)
+    t0 = time.perf_counter()
+    last = 0.0
+    for i in range(args.steps):
+        last = m.train_step(*(t.to(dev, non_blocking=True) for t in host_batches[i % nb]), ns)
+    torch.cuda.synchronize()
+    ms_e2e = (time.perf_counter() - t0) * 1e3
+    h2d = sum(t.numel() * t.element_size() for t in host_batches[0])
+    print(json.dumps({
+        "metric": "kge_train_triples_per_s", "value": bs * args.steps / (ms_dev * 1e-3), "unit": "triples/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "impl": "torch_baseline",
+        "data": "synthetic (same device-drawn ids as the native arm)",
+        "config": {"model": f"{args.kge_model}, {NE} entities x dim {D} fp32 on one GPU (PyTorch tables, autograd scoring)",
+                   "global_batch": bs, "negatives": f"{ns} chunk-shared uniform per {ns} positives", "gamma": 10.0,
+                   "optimizer": "sparse row-wise Adagrad lr 0.1 (index_add_)"},
+        "clocks": clocks,
+        "e2e": {"value": bs * args.steps / (ms_e2e * 1e-3), "unit": "triples/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+        "gpu_launches": 0, "last_loss": last}), flush=True)
+
+
 def run_torch_baseline(args):
     """PyTorch + NCCL + cuBLAS restatement of the reference algorithm on the same data."""
     from recstore_b200.baseline.dlrm_torch import TorchDLRM
@@ -422,6 +477,8 @@ def main():
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "torch_baseline" and args.workload == "kge":
+        run_kge_torch(args)
     elif args.impl == "torch_baseline":
         run_torch_baseline(args)
     elif args.workload == "kge":
