@@ -389,10 +389,14 @@ def run_torch_baseline(args):
     from recstore_b200.baseline.dlrm_torch import TorchDLRM
     from recstore_b200.utils.data import DLRMBatchSource
     rank, world, local = dist_setup(args.gpus)
-    rows = table_rows(args.seed)
+    dcn = args.workload == "dcnv2"
+    rows = dcn_table_rows(args.seed) if dcn else table_rows(args.seed)
+    hot = DCN_HOTNESS if dcn else [1] * TABLES
     dev = torch.device(f"cuda:{local}")
-    m = TorchDLRM(rows, BATCH, emb_dim=DIM, device=dev, rank=rank, world=world, autocast_bf16=True, seed=args.seed)
-    src = DLRMBatchSource(rows, [1] * TABLES, BATCH, alpha=ALPHA, seed=args.seed + 1)
+    extra = dict(interaction="dcn", dcn_layers=3, dcn_rank=512, hotness=hot, top_mlp=(1024, 1024, 512, 256, 1), emb_lr=1e-4,
+                 mlp_lr=0.001) if dcn else {}
+    m = TorchDLRM(rows, BATCH, emb_dim=DIM, device=dev, rank=rank, world=world, autocast_bf16=True, seed=args.seed, **extra)
+    src = DLRMBatchSource(rows, hot, BATCH, alpha=1.1 if dcn else ALPHA, seed=args.seed + 1)
     nb = 4
     host = []
     for _ in range(nb):
@@ -424,10 +428,12 @@ def run_torch_baseline(args):
     ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3, world)
     if rank == 0:
         print(json.dumps({
-            "metric": METRIC, "value": BATCH * args.steps / (ms_dev * 1e-3), "unit": "samples/s", "n_gpus": world,
+            "metric": "dlrm_dcnv2_train_samples_per_s" if dcn else METRIC, "value": BATCH * args.steps / (ms_dev * 1e-3),
+            "unit": "samples/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": "torch_baseline", "config": {"model": "DLRM dot (PyTorch+NCCL+cuBLAS restatement of the reference algorithm)",
+            "impl": "torch_baseline", "config": {"model": ("DLRM-DCNv2 multi-hot" if dcn else "DLRM dot") +
+                                                          " (PyTorch+NCCL+cuBLAS restatement of the reference algorithm)",
                                                  "global_batch": BATCH, "parallelism": f"table-wise MP x{world} + DP"},
             "clocks": clocks,
             "e2e": {"value": BATCH * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
