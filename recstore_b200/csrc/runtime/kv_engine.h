@@ -29,7 +29,7 @@ struct KVConfig {
   uint64_t capacity = 1 << 20;
   uint32_t value_size = 128;
   int num_threads = 8;
-  int num_shards = 16;
+  int num_shards = 64;
   bool prefetch = false;
   std::string raw_json;
 };
