@@ -74,17 +74,17 @@ def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, secon
 
 
 def _process_entry(args, q):
-    q.put(closed_loop(*args, quiet=True))
+    q.put(closed_loop(*args))          # args end with (dataset, quiet, transport)
 
 
-def multi_process(host, port, dim, processes, threads, window, batch, alpha, key_space, seconds, dataset=None):
+def multi_process(host, port, dim, processes, threads, window, batch, alpha, key_space, seconds, dataset=None, transport="tcp"):
     """``processes`` load-generator processes (each with ``threads`` closed-loop senders) against one server: the Python
     interpreter of a single process is the limit long before the server is, as the reference's multi_client.py (8
     processes) works around (src/grpc_ps/python_client/multi_client.py)."""
     import multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_process_entry, args=((host, port, dim, threads, window, batch, alpha, key_space, seconds, dataset), q))
+    ps = [ctx.Process(target=_process_entry, args=((host, port, dim, threads, window, batch, alpha, key_space, seconds, dataset, True, transport), q))
           for _ in range(processes)]
     for p in ps:
         p.start()
@@ -130,7 +130,8 @@ def main(argv=None):
             gen = PoissonLoadGenerator(lambda: make_client(host, port, a.dim, a.transport), src, a.poisson_rate, senders=a.threads)
             out = {"mode": "poisson", "rate": a.poisson_rate, **gen.run(a.seconds).summary()}
         elif a.processes > 1:
-            out = multi_process(host, port, a.dim, a.processes, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset)
+            out = multi_process(host, port, a.dim, a.processes, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset,
+                                transport=a.transport)
         else:
             out = closed_loop(host, port, a.dim, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset,
                               transport=a.transport)
