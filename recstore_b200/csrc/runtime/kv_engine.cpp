@@ -886,6 +886,81 @@ RS_API int rs_kv_recovery_state(void* h, int* recovered, int* clean) {
   *clean = 0;
   return RS_OK;
 }
+// Warm-up of one PS shard and its check (role of LoadDBHelper, src/storage/kv_engine/load_db.h:13-165): of the keys
+// 1 ... warm_capacity, those whose partition hash(key) % num_servers equals server_id get the value float(key) repeated,
+// written by `threads` threads over contiguous key ranges (or, with shuffle, by one thread in a scattered order, which
+// is what an engine sees when keys arrive unsorted).  *inserted = keys stored; a full engine is an error.
+RS_API int rs_kv_preload(void* h, int server_id, int num_servers, unsigned long long warm_capacity, int threads, int shuffle,
+                         unsigned long long* inserted) {
+  RS_REQUIRE(h && num_servers > 0 && server_id >= 0 && server_id < num_servers && threads > 0, "rs_kv_preload: bad argument");
+  RS_NOEXCEPT_BODY(
+    auto* kv = static_cast<BaseKV*>(h);
+    const size_t nfloat = kv->value_size() / sizeof(float);
+    std::atomic<uint64_t> stored{0}, refused{0};
+    auto put_range = [&](uint64_t lo, uint64_t hi, uint64_t stride, uint64_t first) {
+      std::vector<char> value(kv->value_size(), 0);
+      float* emb = reinterpret_cast<float*>(value.data());
+      uint64_t ok = 0, bad = 0;
+      for (uint64_t j = lo + first; j < hi; j += stride) {
+        if (rs::hash64(j) % static_cast<uint64_t>(num_servers) != static_cast<uint64_t>(server_id)) continue;
+        for (size_t k = 0; k < nfloat; ++k) emb[k] = static_cast<float>(j);
+        (kv->Put(j, value.data()) ? ok : bad)++;
+      }
+      stored += ok;
+      refused += bad;
+    };
+    const uint64_t start = 1, end = warm_capacity + 1;
+    if (shuffle) {
+      // a fixed odd stride walks the range in kStride interleaved passes: deterministic, and far from sorted
+      constexpr uint64_t kStride = 9973;
+      for (uint64_t first = 0; first < kStride && first < warm_capacity; ++first) put_range(start, end, kStride, first);
+    } else {
+      const uint64_t per = (warm_capacity + threads - 1) / threads;
+      std::vector<std::thread> th;
+      for (int i = 0; i < threads; ++i)
+        th.emplace_back(put_range, start + i * per, std::min(end, start + (i + 1) * per), uint64_t{1}, uint64_t{0});
+      for (auto& t : th) t.join();
+    }
+    if (inserted) *inserted = stored.load();
+    if (refused.load())
+      return rs::set_error(RS_ERR_CAPACITY, "preload: the engine refused %llu of %llu keys",
+                           static_cast<unsigned long long>(refused.load()),
+                           static_cast<unsigned long long>(refused.load() + stored.load()));
+    return RS_OK;
+  )
+}
+// *right = keys of this shard whose every float equals the key; *expected = keys of this shard in 1 ... warm_capacity.
+RS_API int rs_kv_check_preload(void* h, int server_id, int num_servers, unsigned long long warm_capacity, int threads,
+                               unsigned long long* right, unsigned long long* expected) {
+  RS_REQUIRE(h && num_servers > 0 && server_id >= 0 && server_id < num_servers && threads > 0, "rs_kv_check_preload: bad argument");
+  RS_NOEXCEPT_BODY(
+    auto* kv = static_cast<BaseKV*>(h);
+    const size_t nfloat = kv->value_size() / sizeof(float);
+    std::atomic<uint64_t> good{0}, mine{0};
+    const uint64_t start = 1, end = warm_capacity + 1, per = (warm_capacity + threads - 1) / threads;
+    std::vector<std::thread> th;
+    for (int i = 0; i < threads; ++i)
+      th.emplace_back([&, i] {
+        std::vector<char> value(kv->value_size());
+        const float* emb = reinterpret_cast<const float*>(value.data());
+        uint64_t ok = 0, n = 0;
+        for (uint64_t j = start + i * per; j < std::min(end, start + (i + 1) * per); ++j) {
+          if (rs::hash64(j) % static_cast<uint64_t>(num_servers) != static_cast<uint64_t>(server_id)) continue;
+          ++n;
+          if (!kv->Get(j, value.data())) continue;
+          bool same = true;
+          for (size_t k = 0; k < nfloat; ++k) same &= emb[k] == static_cast<float>(j);
+          ok += same;
+        }
+        good += ok;
+        mine += n;
+      });
+    for (auto& t : th) t.join();
+    if (right) *right = good.load();
+    if (expected) *expected = mine.load();
+    return RS_OK;
+  )
+}
 RS_API int rs_kv_list_engines(char* buf, int cap) {
   std::string s;
   for (auto& e : rs::ListKVEngines()) s += e + "\n";

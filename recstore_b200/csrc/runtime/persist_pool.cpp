@@ -1,6 +1,7 @@
 #include "runtime/persist_pool.h"
 
 #include <algorithm>
+#include <chrono>
 #include <cstring>
 
 #include <fcntl.h>
@@ -437,11 +438,69 @@ size_t EpochManager::Pending() const {
   return n;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+namespace {
+uint64_t steady_ns() {
+  return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+}  // namespace
+
+SlabRecycler::SlabRecycler(PersistSlabPool* pool, Policy policy, uint64_t delay_ns, EpochManager* epochs, uint32_t bump_every)
+    : pool_(pool), policy_(policy), delay_ns_(delay_ns), epochs_(epochs), bump_every_(bump_every ? bump_every : 1) {}
+
+size_t SlabRecycler::drain_locked(uint64_t now_ns) {
+  size_t n = 0;
+  const uint64_t delay = delay_ns_.load(std::memory_order_relaxed);
+  while (head_ < q_.size()) {
+    const auto& e = q_[head_];
+    const bool due = policy_ == kDelayed ? now_ns - e.first >= delay : epochs_->SafeToReclaim(e.first);
+    if (!due) break;
+    pool_->Free(e.second);
+    ++head_;
+    ++n;
+  }
+  if (head_ == q_.size()) {
+    q_.clear();
+    head_ = 0;
+  } else if (head_ > 4096 && head_ * 2 > q_.size()) {       // drop the consumed front now and then
+    q_.erase(q_.begin(), q_.begin() + static_cast<std::ptrdiff_t>(head_));
+    head_ = 0;
+  }
+  return n;
+}
+
+size_t SlabRecycler::Recycle(uint64_t off) {
+  if (policy_ == kDirect) {
+    if (off) pool_->Free(off);
+    return off ? 1 : 0;
+  }
+  std::lock_guard<SpinLock> lk(mu_);
+  const uint64_t now = policy_ == kDelayed ? steady_ns() : 0;
+  if (off) q_.emplace_back(policy_ == kDelayed ? now : epochs_->Current(), off);
+  if (policy_ == kEpoch && ++calls_ % bump_every_ == 0) epochs_->Bump();
+  return drain_locked(now);
+}
+
+size_t SlabRecycler::Clear() {
+  std::lock_guard<SpinLock> lk(mu_);
+  size_t n = 0;
+  for (; head_ < q_.size(); ++head_, ++n) pool_->Free(q_[head_].second);
+  q_.clear();
+  head_ = 0;
+  return n;
+}
+
+size_t SlabRecycler::Pending() const {
+  std::lock_guard<SpinLock> lk(mu_);
+  return q_.size() - head_;
+}
+
 }  // namespace rs
 
 // ============================================================== C ABI
 using rs::EpochManager;
 using rs::PersistSlabPool;
+using rs::SlabRecycler;
 
 RS_API int rs_ppool_open(const char* path, unsigned long long bytes, unsigned long long chunk_bytes, void** out, int* recovered) {
   RS_REQUIRE(out, "rs_ppool_open: null argument");
@@ -520,3 +579,27 @@ RS_API int rs_epoch_retire_slab(void* h, void* pool, unsigned long long off) {
 }
 RS_API long long rs_epoch_collect(void* h) { return static_cast<long long>(static_cast<EpochManager*>(h)->Collect()); }
 RS_API long long rs_epoch_pending(void* h) { return static_cast<long long>(static_cast<EpochManager*>(h)->Pending()); }
+
+// policy: 0 direct, 1 delayed (delay_ns), 2 epoch (epochs must be an EpochManager that outlives the recycler).
+RS_API int rs_recycler_new(void* pool, int policy, unsigned long long delay_ns, void* epochs, unsigned bump_every, void** out) {
+  RS_REQUIRE(pool && out && policy >= 0 && policy <= 2, "rs_recycler_new: bad argument");
+  RS_REQUIRE(policy != 2 || epochs, "rs_recycler_new: the epoch policy needs an epoch manager");
+  RS_NOEXCEPT_BODY(
+    *out = new SlabRecycler(static_cast<PersistSlabPool*>(pool), static_cast<SlabRecycler::Policy>(policy), delay_ns,
+                            static_cast<EpochManager*>(epochs), bump_every);
+    return RS_OK;
+  )
+}
+RS_API int rs_recycler_delete(void* h) {
+  delete static_cast<SlabRecycler*>(h);
+  return RS_OK;
+}
+RS_API long long rs_recycler_recycle(void* h, unsigned long long off) {
+  return static_cast<long long>(static_cast<SlabRecycler*>(h)->Recycle(off));
+}
+RS_API long long rs_recycler_clear(void* h) { return static_cast<long long>(static_cast<SlabRecycler*>(h)->Clear()); }
+RS_API long long rs_recycler_pending(void* h) { return static_cast<long long>(static_cast<SlabRecycler*>(h)->Pending()); }
+RS_API int rs_recycler_set_delay_ns(void* h, unsigned long long ns) {
+  static_cast<SlabRecycler*>(h)->SetDelayNs(ns);
+  return RS_OK;
+}

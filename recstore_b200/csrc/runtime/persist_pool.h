@@ -20,6 +20,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "runtime/base.h"
@@ -134,6 +135,41 @@ class EpochManager {
   std::unique_ptr<Stripe[]> stripes_;
   std::shared_ptr<std::atomic<bool>> alive_;   // threads drop their slot bookkeeping for a manager that is gone
   const uint64_t id_;
+};
+
+// When a freed slab goes back to its pool.  The reference has one class per policy behind ShmBaseRecycle
+// (src/memory/malloc.h:34-152: DirectRecycle, DelayedRecycle / StdDelayedRecycle by age, ShmEpochRecycle by epoch);
+// here one class with the policy as a value, offsets instead of pointers, and a lock, so several writers may share it.
+//   kDirect   the slab is freed at once (no concurrent readers);
+//   kDelayed  it is freed once it has waited delay_ns (readers are known to finish within that time);
+//   kEpoch    it is freed once every protected region that began before the call has ended; the recycler bumps the
+//             epoch every `bump_every` calls.
+// Every call also frees what has become due; Recycle(0) only does that.
+class SlabRecycler {
+ public:
+  enum Policy { kDirect = 0, kDelayed = 1, kEpoch = 2 };
+  SlabRecycler(PersistSlabPool* pool, Policy policy, uint64_t delay_ns = 1000000000ull, EpochManager* epochs = nullptr,
+               uint32_t bump_every = 1000);
+  ~SlabRecycler() { Clear(); }
+  // Returns how many slabs went back to the pool during the call.
+  size_t Recycle(uint64_t off);
+  // Frees everything that waits, due or not (no reader is left); returns how many.
+  size_t Clear();
+  size_t Pending() const;
+  void SetDelayNs(uint64_t ns) { delay_ns_ = ns; }
+  Policy policy() const { return policy_; }
+
+ private:
+  size_t drain_locked(uint64_t now_ns);
+  PersistSlabPool* pool_;
+  Policy policy_;
+  std::atomic<uint64_t> delay_ns_;
+  EpochManager* epochs_;
+  uint32_t bump_every_;
+  mutable SpinLock mu_;
+  std::vector<std::pair<uint64_t, uint64_t>> q_;   // (stamp: ns or epoch, offset), oldest first from head_
+  size_t head_ = 0;
+  uint64_t calls_ = 0;
 };
 
 }  // namespace rs

@@ -8,11 +8,14 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <cmath>
 #include <condition_variable>
 #include <cstdio>
+#include <cstring>
 #include <map>
 #include <memory>
 #include <mutex>
+#include <new>
 #include <string>
 #include <thread>
 #include <vector>
@@ -209,4 +212,133 @@ RS_API void rs_timers_clear() {
     s->sum.store(0.0);
     s->last.store(0.0);
   }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Histogram over the whole life of a measurement (the rings above only keep the latest samples).  Same role as the
+// Histogram of the reference (src/base/timer.h:102-204: Add / Merge / Median / Percentile / ToString with bars), with
+// computed bucket bounds instead of a table: bucket 0 is [0, 1), above that every power of two is cut into 8 equal
+// parts, so a percentile is off by at most 1/16 of its value; 64 octaves cover 1 ... 1.8e19.
+namespace {
+
+class Histogram {
+ public:
+  static constexpr int kSub = 8, kOctaves = 64, kBuckets = 1 + kSub * kOctaves;
+  void Clear() { *this = Histogram(); }
+  void Add(double v) {
+    if (!(v >= 0)) v = 0;                       // negative values and NaN count as zero
+    ++buckets_[index_of(v)];
+    min_ = std::min(min_, v);
+    max_ = std::max(max_, v);
+    ++num_;
+    sum_ += v;
+    sum_sq_ += v * v;
+  }
+  void Merge(const Histogram& o) {
+    min_ = std::min(min_, o.min_);
+    max_ = std::max(max_, o.max_);
+    num_ += o.num_;
+    sum_ += o.sum_;
+    sum_sq_ += o.sum_sq_;
+    for (int b = 0; b < kBuckets; ++b) buckets_[b] += o.buckets_[b];
+  }
+  uint64_t Count() const { return num_; }
+  double Min() const { return num_ ? min_ : 0.0; }
+  double Max() const { return max_; }
+  double Average() const { return num_ ? sum_ / num_ : 0.0; }
+  double StdDev() const {
+    if (!num_) return 0.0;
+    const double n = static_cast<double>(num_), var = (sum_sq_ * n - sum_ * sum_) / (n * n);
+    return var > 0 ? std::sqrt(var) : 0.0;
+  }
+  // Linear interpolation inside the bucket that holds the p-th percentile, clamped to the observed range.
+  double Percentile(double p) const {
+    if (!num_) return 0.0;
+    const double want = static_cast<double>(num_) * std::min(100.0, std::max(0.0, p)) / 100.0;
+    double seen = 0;
+    for (int b = 0; b < kBuckets; ++b) {
+      if (!buckets_[b]) continue;
+      const double next = seen + static_cast<double>(buckets_[b]);
+      if (next >= want) {
+        const double lo = lower(b), hi = upper(b);
+        const double r = lo + (hi - lo) * (want - seen) / static_cast<double>(buckets_[b]);
+        return std::min(max_, std::max(min_, r));
+      }
+      seen = next;
+    }
+    return max_;
+  }
+  std::string ToString() const {
+    char buf[256];
+    std::string r;
+    snprintf(buf, sizeof buf, "Count: %llu  Average: %.4f  StdDev: %.2f\nMin: %.4f  Median: %.4f  P99: %.4f  Max: %.4f\n",
+             static_cast<unsigned long long>(num_), Average(), StdDev(), Min(), Percentile(50), Percentile(99), Max());
+    r += buf;
+    if (!num_) return r;
+    double cum = 0;
+    for (int b = 0; b < kBuckets; ++b) {
+      if (!buckets_[b]) continue;
+      cum += static_cast<double>(buckets_[b]);
+      snprintf(buf, sizeof buf, "[ %12.6g, %12.6g ) %10llu %7.3f%% %7.3f%% ", lower(b), upper(b),
+               static_cast<unsigned long long>(buckets_[b]), 100.0 * buckets_[b] / num_, 100.0 * cum / num_);
+      r += buf;
+      r.append(static_cast<size_t>(20.0 * buckets_[b] / num_ + 0.5), '#');
+      r += '\n';
+    }
+    return r;
+  }
+
+ private:
+  static int index_of(double v) {
+    if (v < 1.0) return 0;
+    int e;
+    const double m = std::frexp(v, &e);          // v = m * 2^e, m in [0.5, 1)
+    const int oct = e - 1;                       // v in [2^oct, 2^(oct+1))
+    if (oct >= kOctaves) return kBuckets - 1;
+    return 1 + oct * kSub + std::min(kSub - 1, static_cast<int>((m * 2.0 - 1.0) * kSub));
+  }
+  static double lower(int b) {
+    if (b == 0) return 0.0;
+    const int oct = (b - 1) / kSub, sub = (b - 1) % kSub;
+    return std::ldexp(1.0 + static_cast<double>(sub) / kSub, oct);
+  }
+  static double upper(int b) {
+    if (b == 0) return 1.0;
+    const int oct = (b - 1) / kSub, sub = (b - 1) % kSub;
+    return std::ldexp(1.0 + static_cast<double>(sub + 1) / kSub, oct);
+  }
+  uint64_t buckets_[kBuckets] = {};
+  uint64_t num_ = 0;
+  double min_ = 1e300, max_ = 0, sum_ = 0, sum_sq_ = 0;
+};
+
+}  // namespace
+
+RS_API void* rs_hist_new() { return new (std::nothrow) Histogram(); }
+RS_API void rs_hist_delete(void* h) { delete static_cast<Histogram*>(h); }
+RS_API void rs_hist_clear(void* h) { static_cast<Histogram*>(h)->Clear(); }
+RS_API void rs_hist_add(void* h, double v) { static_cast<Histogram*>(h)->Add(v); }
+RS_API void rs_hist_add_many(void* h, const double* v, long long n) {
+  auto* hist = static_cast<Histogram*>(h);
+  for (long long i = 0; i < n; ++i) hist->Add(v[i]);
+}
+RS_API void rs_hist_merge(void* h, const void* other) { static_cast<Histogram*>(h)->Merge(*static_cast<const Histogram*>(other)); }
+RS_API double rs_hist_percentile(void* h, double p) { return static_cast<Histogram*>(h)->Percentile(p); }
+// count, min, max, average, standard deviation
+RS_API void rs_hist_summary(void* h, double* out5) {
+  auto* hist = static_cast<Histogram*>(h);
+  out5[0] = static_cast<double>(hist->Count());
+  out5[1] = hist->Min();
+  out5[2] = hist->Max();
+  out5[3] = hist->Average();
+  out5[4] = hist->StdDev();
+}
+RS_API int rs_hist_to_string(void* h, char* buf, int cap) {
+  const std::string s = static_cast<Histogram*>(h)->ToString();
+  if (buf && cap > 0) {
+    const int n = std::min<int>(cap - 1, static_cast<int>(s.size()));
+    memcpy(buf, s.data(), n);
+    buf[n] = 0;
+  }
+  return static_cast<int>(s.size());
 }

@@ -36,6 +36,8 @@ _lib.register_signatures({
     "rs_kv_migrate_hot": (i32, [vp, vp, i64, C.POINTER(i64)]),
     "rs_kv_recovery_state": (i32, [vp, C.POINTER(i32), C.POINTER(i32)]),
     "rs_kv_list_engines": (i32, [C.c_char_p, i32]),
+    "rs_kv_preload": (i32, [vp, i32, i32, u64, i32, i32, C.POINTER(u64)]),
+    "rs_kv_check_preload": (i32, [vp, i32, i32, u64, i32, C.POINTER(u64), C.POINTER(u64)]),
 })
 
 
@@ -167,6 +169,12 @@ _lib.register_signatures({
     "rs_epoch_retire_slab": (i32, [vp, vp, u64]),
     "rs_epoch_collect": (i64, [vp]),
     "rs_epoch_pending": (i64, [vp]),
+    "rs_recycler_new": (i32, [vp, i32, u64, vp, C.c_uint, C.POINTER(vp)]),
+    "rs_recycler_delete": (i32, [vp]),
+    "rs_recycler_recycle": (i64, [vp, u64]),
+    "rs_recycler_clear": (i64, [vp]),
+    "rs_recycler_pending": (i64, [vp]),
+    "rs_recycler_set_delay_ns": (i32, [vp, u64]),
 })
 
 
@@ -278,6 +286,72 @@ class EpochManager:
         return int(self._l.rs_epoch_pending(self._h))
 
 
+class SlabRecycler:
+    """When a freed slab goes back to its pool: ``"direct"`` (at once), ``"delayed"`` (after ``delay_s``) or
+    ``"epoch"`` (once every region protected before the call has ended; needs ``epochs``).  Every ``recycle`` also
+    frees what has become due.  Role of DirectRecycle / DelayedRecycle / ShmEpochRecycle, src/memory/malloc.h:34-152."""
+
+    POLICIES = {"direct": 0, "delayed": 1, "epoch": 2}
+
+    def __init__(self, pool: PersistSlabPool, policy: str = "direct", delay_s: float = 1.0,
+                 epochs: Optional[EpochManager] = None, bump_every: int = 1000):
+        if policy not in self.POLICIES:
+            raise ValueError(f"unknown recycle policy {policy!r}; known: {sorted(self.POLICIES)}")
+        self._l = _lib.lib()
+        self._pool, self._epochs = pool, epochs       # keep both alive for as long as the recycler
+        h = vp()
+        _lib.call("rs_recycler_new", pool._h, self.POLICIES[policy], int(delay_s * 1e9),
+                  epochs._h if epochs is not None else None, int(bump_every), C.byref(h))
+        self._h = h.value
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._l.rs_recycler_delete(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def recycle(self, off: int = 0) -> int:
+        """Hands over the slab at ``off`` (0: nothing, just free what is due); returns how many slabs were freed."""
+        return int(self._l.rs_recycler_recycle(self._h, int(off)))
+
+    def clear(self) -> int:
+        return int(self._l.rs_recycler_clear(self._h))
+
+    def pending(self) -> int:
+        return int(self._l.rs_recycler_pending(self._h))
+
+    def set_delay(self, delay_s: float) -> None:
+        self._l.rs_recycler_set_delay_ns(self._h, int(delay_s * 1e9))
+
+
+class LoadDBHelper:
+    """Warm-up of one PS shard's engine and its check: of the keys ``1 ... warm_capacity`` those that
+    ``ShardManager.KeyPartition`` gives to ``server_id`` are stored with the value ``float(key)`` repeated, by
+    ``warm_thread_count`` native threads (``shuffle_load``: one thread, scattered key order).  Role of LoadDBHelper,
+    src/storage/kv_engine/load_db.h:13-165."""
+
+    def __init__(self, kv: "BaseKV", server_id: int = 0, num_servers: int = 1, warm_thread_count: int = 8,
+                 warm_capacity: int = 0):
+        self.kv, self.server_id, self.num_servers = kv, int(server_id), int(num_servers)
+        self.warm_thread_count, self.warm_capacity = int(warm_thread_count), int(warm_capacity)
+        self.inserted = 0
+
+    def PreLoadDB(self, shuffle_load: bool = False) -> int:
+        n = u64()
+        _lib.call("rs_kv_preload", self.kv._h, self.server_id, self.num_servers, self.warm_capacity,
+                  1 if shuffle_load else self.warm_thread_count, int(shuffle_load), C.byref(n))
+        self.inserted = int(n.value)
+        return self.inserted
+
+    def CheckDBLoad(self) -> Tuple[int, int]:
+        """(keys of this shard that hold their warm-up value, keys of this shard): equal after a complete warm-up."""
+        right, expected = u64(), u64()
+        _lib.call("rs_kv_check_preload", self.kv._h, self.server_id, self.num_servers, self.warm_capacity,
+                  self.warm_thread_count, C.byref(right), C.byref(expected))
+        return int(right.value), int(expected.value)
+
+
 class HashAPI:
     """``find / insert / update / remove`` over any engine: the call surface that hash-table evaluation harnesses expect
     (the reference adapts its chunked hash to one in src/storage/nvm/pet_kv/PiBenchWrapper.cc).  ``insert`` refuses a key
@@ -309,3 +383,38 @@ class HashAPI:
 
     def close(self) -> None:
         self.kv.close()
+
+
+def reinit(path: str) -> List[str]:
+    """Removes the files that the persistent engines keep in ``path`` (``values.slab``, ``shard_*.dict``,
+    ``poolmap.slabs``), so the next engine opened there starts empty; other files are left alone.  Returns the names
+    removed.  The reference's tool for this wipes its persistent-memory mount points (src/memory/pm_command.cc:9-21)."""
+    import glob
+    import os
+    gone = []
+    for pat in ("values.slab", "shard_*.dict", "poolmap.slabs"):
+        for f in sorted(glob.glob(os.path.join(path, pat))):
+            os.remove(f)
+            gone.append(os.path.basename(f))
+    return gone
+
+
+def _main(argv=None) -> int:
+    import argparse
+    ap = argparse.ArgumentParser(prog="python -m recstore_b200.storage",
+                                 description="maintenance of the persistent engines' directories")
+    ap.add_argument("--command", required=True, choices=["reinit", "engines"])
+    ap.add_argument("--path", default=None, help="directory of a persistent engine (reinit)")
+    a = ap.parse_args(argv)
+    if a.command == "engines":
+        print("\n".join(list_engines()))
+        return 0
+    if not a.path:
+        ap.error("--command reinit needs --path")
+    for f in reinit(a.path):
+        print("removed", f)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(_main())

@@ -28,6 +28,15 @@ _lib.register_signatures({
     "rs_report_thread_start": (i32, [i32]),
     "rs_report_thread_stop": (i32, []),
     "rs_timers_clear": (None, []),
+    "rs_hist_new": (vp, []),
+    "rs_hist_delete": (None, [vp]),
+    "rs_hist_clear": (None, [vp]),
+    "rs_hist_add": (None, [vp, f64]),
+    "rs_hist_add_many": (None, [vp, C.POINTER(f64), C.c_longlong]),
+    "rs_hist_merge": (None, [vp, vp]),
+    "rs_hist_percentile": (f64, [vp, f64]),
+    "rs_hist_summary": (None, [vp, C.POINTER(f64)]),
+    "rs_hist_to_string": (i32, [vp, C.c_char_p, i32]),
 })
 
 
@@ -130,6 +139,58 @@ class Reporter:
     @staticmethod
     def Clear():
         _lib.lib().rs_timers_clear()
+
+
+class Histogram:
+    """Distribution of a measurement over its whole life: count, min / max, mean, standard deviation and percentiles
+    from log-linear buckets (8 per power of two, so a percentile is within 1/16 of the true value), mergeable across
+    threads or ranks, printable with bars (role of the reference's ``Histogram``, src/base/timer.h:102-204)."""
+
+    def __init__(self):
+        self._l = _lib.lib()
+        self._h = self._l.rs_hist_new()
+        if not self._h:
+            raise MemoryError("Histogram")
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._l.rs_hist_delete(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def Clear(self) -> None:
+        self._l.rs_hist_clear(self._h)
+
+    def Add(self, value) -> None:
+        """One value, or a sequence / tensor of values."""
+        if isinstance(value, (int, float)):
+            self._l.rs_hist_add(self._h, float(value))
+            return
+        v = torch.as_tensor(value, dtype=torch.float64).reshape(-1).contiguous().cpu()
+        self._l.rs_hist_add_many(self._h, C.cast(v.data_ptr(), C.POINTER(f64)), v.numel())
+
+    def Merge(self, other: "Histogram") -> None:
+        self._l.rs_hist_merge(self._h, other._h)
+
+    def Percentile(self, p: float) -> float:
+        return float(self._l.rs_hist_percentile(self._h, float(p)))
+
+    def Median(self) -> float:
+        return self.Percentile(50.0)
+
+    def summary(self) -> dict:
+        out = (f64 * 5)()
+        self._l.rs_hist_summary(self._h, out)
+        return {"count": int(out[0]), "min": out[1], "max": out[2], "mean": out[3], "stddev": out[4]}
+
+    def ToString(self) -> str:
+        n = self._l.rs_hist_to_string(self._h, None, 0)
+        buf = C.create_string_buffer(n + 1)
+        self._l.rs_hist_to_string(self._h, buf, n + 1)
+        return buf.value.decode()
+
+    __str__ = ToString
 
 
 def stats(name: str) -> dict:

@@ -491,3 +491,129 @@ def test_hash_api_adapter_semantics(engine):
     assert h.update(5, two) and torch.equal(h.find(5), two) and len(h) == 1
     assert h.remove(5) and h.find(5) is None and len(h) == 0
     h.close()
+
+
+def test_slab_recyclers_direct_delayed_and_epoch():
+    """The three policies for returning a freed slab to its pool (DirectRecycle / DelayedRecycle / ShmEpochRecycle of
+    src/memory/malloc.h:34-152)."""
+    import time
+    from recstore_b200.storage import EpochManager, PersistSlabPool, SlabRecycler
+    P, E = PersistSlabPool(None, 16 * 65536, chunk_bytes=65536), EpochManager()
+    with pytest.raises(ValueError):
+        SlabRecycler(P, "sometimes")
+    with pytest.raises(Exception):
+        SlabRecycler(P, "epoch")                            # no epoch manager
+
+    R = SlabRecycler(P, "direct")
+    off = P.malloc(64)
+    assert R.recycle(off) == 1 and P.slab_size(off) == 0 and R.pending() == 0 and R.recycle(0) == 0
+
+    R = SlabRecycler(P, "delayed", delay_s=0.2)
+    offs = [P.malloc(64) for _ in range(5)]
+    assert sum(R.recycle(o) for o in offs) == 0 and R.pending() == 5 and all(P.slab_size(o) for o in offs)
+    time.sleep(0.3)
+    late = P.malloc(64)
+    assert R.recycle(late) == 5 and R.pending() == 1          # the five are due, the new one waits
+    assert all(P.slab_size(o) == 0 for o in offs) and P.slab_size(late) != 0
+    R.set_delay(0.0)
+    assert R.recycle(0) == 1 and R.pending() == 0
+    R.set_delay(60.0)
+    o = P.malloc(64)
+    R.recycle(o)
+    assert R.clear() == 1 and P.slab_size(o) == 0              # clear frees what is not due yet
+
+    R = SlabRecycler(P, "epoch", epochs=E, bump_every=4)
+    E.protect()                                             # this thread may still read what is unlinked from now on
+    offs = [P.malloc(64) for _ in range(8)]
+    assert sum(R.recycle(o) for o in offs) == 0 and R.pending() == 8
+    E.unprotect()
+    assert R.recycle(0) == 8 and R.pending() == 0 and all(P.slab_size(o) == 0 for o in offs)
+    o = P.malloc(64)
+    R.recycle(o)
+    R.close()                                               # closing frees what is left
+    assert P.slab_size(o) == 0 and P.stats()["slabs_in_use"] == 0
+    E.close()
+    P.close()
+
+
+@pytest.mark.parametrize("engine", ["KVEngineMap", "KVEngineExtendibleHash", "KVEngineChunkHash", "KVEnginePoolMap"])
+def test_load_db_helper_warms_one_shard_and_checks_it(engine):
+    """Warm-up of a PS shard: the keys that the partition function gives this server, value = float(key) repeated, then
+    the check that counts them (LoadDBHelper::PreLoadDB / CheckDBLoad, src/storage/kv_engine/load_db.h:13-165)."""
+    from recstore_b200.ps.client import ShardManager
+    from recstore_b200.storage import BaseKV, LoadDBHelper
+    N, S = 20000, 3
+    owner = ShardManager.KeyPartition(torch.arange(1, N + 1), S)
+    total = 0
+    for sid in range(S):
+        kv = BaseKV(engine, {"capacity": N, "value_size": 32})
+        h = LoadDBHelper(kv, sid, S, warm_thread_count=4, warm_capacity=N)
+        mine = int((owner == sid).sum())
+        assert h.PreLoadDB(shuffle_load=(sid == 1)) == mine and len(kv) == mine
+        assert h.CheckDBLoad() == (mine, mine)
+        k = int((owner == sid).nonzero()[0]) + 1
+        assert torch.equal(kv.Get(k), torch.full((8,), float(k)))
+        other = int((owner != sid).nonzero()[0]) + 1
+        assert kv.Get(other) is None
+        kv.Put(k, torch.zeros(8))                           # a damaged row is counted as wrong, not as missing
+        assert h.CheckDBLoad() == (mine - 1, mine)
+        total += mine
+        kv.close()
+    assert total == N
+    small = BaseKV("KVEngineMap", {"capacity": 100, "value_size": 32})
+    with pytest.raises(Exception):
+        LoadDBHelper(small, 0, 1, 2, 1000).PreLoadDB()      # more keys than the engine holds: an error, not a silent cut
+    small.close()
+
+
+def test_histogram_percentiles_merge_and_report():
+    """Whole-run distribution of a measurement (Histogram of src/base/timer.h:102-204)."""
+    from recstore_b200.utils.timer import Histogram
+    h = Histogram()
+    assert h.summary()["count"] == 0 and h.Percentile(50) == 0.0
+    v = torch.arange(1, 10001, dtype=torch.float64)
+    h.Add(v)
+    s = h.summary()
+    assert s["count"] == 10000 and s["min"] == 1.0 and s["max"] == 10000.0 and abs(s["mean"] - 5000.5) < 1e-6
+    assert abs(s["stddev"] - float(v.std(unbiased=False))) < 1e-3
+    for p in (1, 25, 50, 90, 99, 99.9):
+        exact = float(torch.quantile(v, p / 100.0))
+        assert abs(h.Percentile(p) - exact) <= exact / 16 + 1, (p, h.Percentile(p), exact)
+    assert h.Percentile(0) >= 1.0 and h.Percentile(100) == 10000.0 and h.Median() == h.Percentile(50)
+    g = Histogram()
+    g.Add(0.25)
+    g.Add(3e6)
+    g.Add(-5.0)                                             # counted as zero
+    h.Merge(g)
+    s = h.summary()
+    assert s["count"] == 10003 and s["min"] == 0.0 and s["max"] == 3e6
+    text = h.ToString()
+    assert text.startswith("Count: 10003") and "Median" in text and "#" in text and text.count("\n") > 10
+    h.Clear()
+    assert h.summary()["count"] == 0
+    h.close()
+    g.close()
+
+
+@pytest.mark.parametrize("engine", ["KVEngineChunkHash", "KVEnginePoolMap"])
+def test_reinit_tool_wipes_a_persistent_engine_directory(tmp_path, engine):
+    """`python -m recstore_b200.storage --command reinit --path DIR` (role of src/memory/pm_command.cc)."""
+    import subprocess, sys
+    from recstore_b200.storage import BaseKV
+    d = tmp_path / "kv"
+    cfg = {"capacity": 1000, "value_size": 16, "path": str(d), "num_shards": 2}
+    kv = BaseKV(engine, cfg)
+    kv.Put(7, torch.ones(4))
+    kv.Flush()
+    kv.close()
+    (d / "notes.txt").write_text("keep me")
+    kv = BaseKV(engine, cfg)
+    assert len(kv) == 1                                      # the directory brings the data back
+    kv.close()
+    r = subprocess.run([sys.executable, "-m", "recstore_b200.storage", "--command", "reinit", "--path", str(d)],
+                       capture_output=True, text=True, timeout=300, cwd=os.path.dirname(os.path.dirname(__file__)))
+    assert r.returncode == 0 and "removed" in r.stdout, r.stderr
+    assert (d / "notes.txt").exists()
+    kv = BaseKV(engine, cfg)
+    assert len(kv) == 0 and kv.Get(7) is None
+    kv.close()
