@@ -96,9 +96,52 @@ std::vector<int> numa_node_cores(int node) {
   return out;
 }
 
+uint64_t CoarseClock::SteadyNs() {
+  return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+CoarseClock::CoarseClock(int interval_ms) : interval_ms_(interval_ms < 1 ? 1 : interval_ms), now_(SteadyNs()) {
+  thread_ = std::thread([this] { run(); });
+}
+CoarseClock::~CoarseClock() {
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    stop_ = true;
+  }
+  cv_.notify_all();
+  if (thread_.joinable()) thread_.join();
+}
+void CoarseClock::run() {
+  std::unique_lock<std::mutex> lk(mu_);
+  while (!stop_) {
+    now_.store(SteadyNs(), std::memory_order_relaxed);
+    cv_.wait_for(lk, std::chrono::milliseconds(interval_ms_), [this] { return stop_; });
+  }
+}
+CoarseClock& CoarseClock::Global() {
+  static CoarseClock clock(10);
+  return clock;
+}
+
 }  // namespace rs
 
 // ---------------------------------------------------------------- C ABI
+RS_API unsigned long long rs_coarse_now_ns() { return rs::CoarseClock::Global().NowNs(); }
+RS_API unsigned long long rs_steady_now_ns() { return rs::CoarseClock::SteadyNs(); }
+
+RS_API int rs_ring_new(unsigned capacity, void** out) {
+  RS_REQUIRE(out && capacity > 0, "rs_ring_new: bad argument");
+  RS_NOEXCEPT_BODY(*out = new rs::IndexRing(capacity); return RS_OK;)
+}
+RS_API int rs_ring_delete(void* h) {
+  delete static_cast<rs::IndexRing*>(h);
+  return RS_OK;
+}
+// 1: appended, 0: the batch does not fit (nothing appended).
+RS_API int rs_ring_push(void* h, const int* v, unsigned n) { return static_cast<rs::IndexRing*>(h)->Push(v, n) ? 1 : 0; }
+RS_API unsigned rs_ring_pop(void* h, int* out, unsigned want) { return static_cast<rs::IndexRing*>(h)->TryPop(out, want); }
+RS_API unsigned rs_ring_size(void* h) { return static_cast<rs::IndexRing*>(h)->Size(); }
+RS_API void rs_ring_clear(void* h) { static_cast<rs::IndexRing*>(h)->Clear(); }
+
 RS_API int rs_bind_core(int core) { return rs::bind_core(core) == 0 ? RS_OK : rs::set_error(RS_ERR_INVALID, "cannot bind to core %d", core); }
 
 RS_API int rs_numa_node_cores(int node, int* out, int cap) {

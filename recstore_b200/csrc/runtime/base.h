@@ -1,9 +1,10 @@
 // Small host-side building blocks of the runtime: spin locks (with an optional deadlock
 // detector), a per-row bit-lock table, a sense-reversing thread barrier, a bounded SPSC queue,
-// a bitmap, a thread pool and a bounded Zipf generator that also supports exponents >= 1.
+// a ring of free indices with lock-free range pops, a bitmap, a thread pool, a bounded Zipf generator that also
+// supports exponents >= 1, and a coarse clock refreshed by a background thread.
 //
-// They cover the roles of src/base/{lock.h:14-209, queue.h:19-189, bitmap.h, zipf.h:78-175,
-// bind_core.cc:14-70} of the reference without folly/glog.
+// They cover the roles of src/base/{lock.h:14-209, queue.h:19-189, lf_list.h, bitmap.h, zipf.h:78-175,
+// async_time.h, bind_core.cc:14-70} of the reference without folly/glog.
 #pragma once
 #include <atomic>
 #include <chrono>
@@ -152,6 +153,74 @@ class SpscQueue {
   std::vector<T> buf_;
   alignas(64) std::atomic<size_t> head_{0};
   alignas(64) std::atomic<size_t> tail_{0};
+};
+
+// Ring of free indices (slots, row numbers): producers append batches, any number of consumers claim runs of
+// consecutive entries with one compare-and-swap.  Role of LFList (src/base/lf_list.h), with 64-bit positions that only
+// grow (no ABA when the ring wraps), entries copied out before the claim is made (a successful claim proves that the
+// producer has not touched them) and a refusal instead of an abort when a batch does not fit.
+class IndexRing {
+ public:
+  explicit IndexRing(uint32_t capacity) : cap_(capacity ? capacity : 1), slots_(new std::atomic<int32_t>[cap_]) {}
+  uint32_t Capacity() const { return cap_; }
+  uint32_t Size() const {
+    const uint64_t h = head_.load(std::memory_order_acquire);
+    const uint64_t t = tail_.load(std::memory_order_acquire);
+    return static_cast<uint32_t>(t > h ? t - h : 0);
+  }
+  // Appends n entries; false (nothing appended) when they do not fit.
+  bool Push(const int32_t* v, uint32_t n) {
+    std::lock_guard<SpinLock> lk(push_mu_);
+    const uint64_t t = tail_.load(std::memory_order_relaxed);
+    if (t - head_.load(std::memory_order_acquire) + n > cap_) return false;
+    for (uint32_t i = 0; i < n; ++i) slots_[(t + i) % cap_].store(v[i], std::memory_order_relaxed);
+    tail_.store(t + n, std::memory_order_release);
+    return true;
+  }
+  // Takes up to `want` entries in ring order; returns how many were written to out (0: the ring is empty).
+  uint32_t TryPop(int32_t* out, uint32_t want) {
+    uint64_t h = head_.load(std::memory_order_acquire);
+    while (true) {
+      const uint64_t t = tail_.load(std::memory_order_acquire);
+      const uint32_t n = static_cast<uint32_t>(std::min<uint64_t>(want, t > h ? t - h : 0));
+      if (n == 0) return 0;
+      for (uint32_t i = 0; i < n; ++i) out[i] = slots_[(h + i) % cap_].load(std::memory_order_relaxed);
+      if (head_.compare_exchange_weak(h, h + n, std::memory_order_acq_rel, std::memory_order_acquire)) return n;
+    }
+  }
+  void Clear() {
+    std::lock_guard<SpinLock> lk(push_mu_);
+    head_.store(tail_.load(std::memory_order_acquire), std::memory_order_release);
+  }
+
+ private:
+  const uint32_t cap_;
+  std::unique_ptr<std::atomic<int32_t>[]> slots_;
+  SpinLock push_mu_;
+  alignas(64) std::atomic<uint64_t> head_{0};
+  alignas(64) std::atomic<uint64_t> tail_{0};
+};
+
+// A clock for hot paths that stamp many items and do not need better than a few milliseconds: one relaxed load of a
+// value that a background thread refreshes every `interval_ms` (role of AsyncTimeHelper, src/base/async_time.h).  The
+// process-wide instance starts on first use and is stopped when the library is unloaded.
+class CoarseClock {
+ public:
+  explicit CoarseClock(int interval_ms);
+  ~CoarseClock();
+  uint64_t NowNs() const { return now_.load(std::memory_order_relaxed); }
+  int interval_ms() const { return interval_ms_; }
+  static CoarseClock& Global();       // 10 ms
+  static uint64_t SteadyNs();         // the exact clock it samples
+
+ private:
+  void run();
+  const int interval_ms_;
+  std::atomic<uint64_t> now_;
+  std::mutex mu_;
+  std::condition_variable cv_;
+  bool stop_ = false;
+  std::thread thread_;
 };
 
 class Bitmap {

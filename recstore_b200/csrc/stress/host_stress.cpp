@@ -7,13 +7,16 @@
 //   2. Parameter server: a loopback server and several client threads putting, getting and updating overlapping keys.
 //   3. Allocators (pool / binning / fixed length on pageable host memory), the timer registry with its report thread,
 //      and the shared-memory barrier, each hit from several threads.
+//   3b. The ring of free indices (producers against consumers that claim runs) and the coarse clock.
 //   4. Lookahead controller: "ranks" as threads sharing one controller (the layout of the reference's
 //      VirtualEnvironment test, src/framework_test), background flush threads on, the read-your-updates contract
 //      checked at every step against a synchronous oracle.
 //
 // Exit code 0 and a final "host_stress: ok" line mean that no invariant broke; a sanitizer report makes the process
 // exit non-zero by itself (TSAN_OPTIONS=halt_on_error=1 exitcode=66 is set by the test that runs it).
+#include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cmath>
 #include <condition_variable>
 #include <cstdio>
@@ -65,6 +68,13 @@ int rs_series_stats(const char* name, double* out5);
 int rs_report_thread_start(int period_ms);
 int rs_report_thread_stop();
 void rs_timers_clear();
+int rs_ring_new(unsigned capacity, void** out);
+int rs_ring_delete(void* h);
+int rs_ring_push(void* h, const int* v, unsigned n);
+unsigned rs_ring_pop(void* h, int* out, unsigned want);
+unsigned rs_ring_size(void* h);
+unsigned long long rs_coarse_now_ns();
+unsigned long long rs_steady_now_ns();
 int rs_shm_set_namespace(const char* ns);
 int rs_barrier_create(const char* name, int parties, void** out_handle);
 int rs_barrier_wait(void* handle, int timeout_ms);
@@ -265,6 +275,61 @@ void stress_timers_and_barrier() {
   std::printf("host_stress: timers + barrier, %d threads x %d rounds\n", kThreads, kRounds);
 }
 
+// Two producers append batches of distinct numbers to a small ring while four consumers claim runs of them: every
+// number must come out exactly once, whatever the interleaving and however often the ring wraps.
+void stress_index_ring() {
+  constexpr int kProducers = 2, kConsumers = 4, kPerProducer = 60000, kCap = 257;
+  void* ring = nullptr;
+  EXPECT_OK(rs_ring_new(kCap, &ring));
+  std::vector<std::atomic<unsigned char>> seen(kProducers * kPerProducer);
+  for (auto& s : seen) s.store(0);
+  std::atomic<int> taken{0}, producers_left{kProducers}, dup{0};
+  std::vector<std::thread> ts;
+  for (int p = 0; p < kProducers; ++p)
+    ts.emplace_back([&, p] {
+      int next = p * kPerProducer;
+      const int end = next + kPerProducer;
+      int batch[7];
+      while (next < end) {
+        const int n = std::min(1 + next % 7, end - next);
+        for (int i = 0; i < n; ++i) batch[i] = next + i;
+        if (rs_ring_push(ring, batch, static_cast<unsigned>(n))) next += n;
+        else std::this_thread::yield();
+      }
+      producers_left.fetch_sub(1);
+    });
+  for (int c = 0; c < kConsumers; ++c)
+    ts.emplace_back([&, c] {
+      int got[16];
+      while (true) {
+        const unsigned n = rs_ring_pop(ring, got, 1 + (c * 5) % 16);
+        for (unsigned i = 0; i < n; ++i)
+          if (seen[got[i]].fetch_add(1) != 0) dup.fetch_add(1);
+        taken.fetch_add(static_cast<int>(n));
+        if (n == 0) {
+          if (producers_left.load() == 0 && rs_ring_size(ring) == 0) break;
+          std::this_thread::yield();
+        }
+      }
+    });
+  for (auto& t : ts) t.join();
+  if (taken.load() != kProducers * kPerProducer) fail("index ring lost or invented entries");
+  if (dup.load() != 0) fail("index ring handed an entry out twice");
+  EXPECT_OK(rs_ring_delete(ring));
+  // the coarse clock trails the exact one by about its refresh interval, never leads it, never runs backwards
+  unsigned long long prev = rs_coarse_now_ns();
+  for (int i = 0; i < 50; ++i) {
+    std::this_thread::sleep_for(std::chrono::milliseconds(2));
+    const unsigned long long c = rs_coarse_now_ns(), exact = rs_steady_now_ns();
+    if (c < prev) fail("coarse clock ran backwards");
+    if (c > exact) fail("coarse clock leads the exact clock");
+    if (exact - c > 2000000000ull) fail("coarse clock is stale by more than two seconds");
+    prev = c;
+  }
+  std::printf("host_stress: index ring, %d producers / %d consumers, %d entries; coarse clock\n", kProducers, kConsumers,
+              kProducers * kPerProducer);
+}
+
 void stress_controller(const char* mode) {
   constexpr int kRanks = 4, kRows = 2000, kDim = 8, kL = 5, kSteps = 30, kPer = 64;
   const float clr = 0.5f;
@@ -353,6 +418,7 @@ int main(int argc, char** argv) {
     stress_allocator(2, "fixed");
   }
   if (only == "all" || only == "misc") stress_timers_and_barrier();
+  if (only == "all" || only == "ring") stress_index_ring();
   if (only == "all" || only == "controller") {
     stress_controller("CppSync");
     stress_controller("CppAsyncV2");

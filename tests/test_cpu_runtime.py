@@ -617,3 +617,49 @@ def test_reinit_tool_wipes_a_persistent_engine_directory(tmp_path, engine):
     kv = BaseKV(engine, cfg)
     assert len(kv) == 0 and kv.Get(7) is None
     kv.close()
+
+
+def test_index_ring_coarse_clock_and_core_binding():
+    """Ring of free indices (src/base/lf_list.h), coarse clock (src/base/async_time.h), thread pinning
+    (src/base/bind_core.cc)."""
+    import threading, time
+    from recstore_b200.utils.host import IndexRing, bind_core, coarse_now_ns, numa_node_cores, steady_now_ns
+    r = IndexRing(8)
+    assert len(r) == 0 and r.pop(4).size == 0
+    assert r.push([1, 2, 3, 4, 5]) and not r.push([6, 7, 8, 9]) and len(r) == 5      # a batch that does not fit is refused whole
+    assert r.pop(2).tolist() == [1, 2] and r.push([6, 7, 8, 9]) and len(r) == 7       # ... and fits once there is room (wraps)
+    assert r.pop(100).tolist() == [3, 4, 5, 6, 7, 8, 9] and len(r) == 0
+    r.push([1, 2])
+    r.clear()
+    assert len(r) == 0
+    big, got, lock = IndexRing(1 << 12), [], threading.Lock()
+    done = threading.Event()
+
+    def consumer():
+        mine = []
+        while not (done.is_set() and len(big) == 0):
+            mine.extend(big.pop(7).tolist())
+        with lock:
+            got.extend(mine)
+    ts = [threading.Thread(target=consumer) for _ in range(3)]
+    [t.start() for t in ts]
+    nxt = 0
+    while nxt < 30000:
+        if big.push(range(nxt, nxt + 100)):
+            nxt += 100
+    done.set()
+    [t.join() for t in ts]
+    assert sorted(got) == list(range(30000))
+    a = coarse_now_ns()
+    time.sleep(0.05)
+    b, exact = coarse_now_ns(), steady_now_ns()
+    assert a < b <= exact and exact - b < 1_000_000_000
+    cores = sorted(os.sched_getaffinity(0))
+    t = threading.Thread(target=lambda: (bind_core(cores[-1]), got.append(os.sched_getaffinity(0))))
+    t.start()
+    t.join()
+    assert got[-1] == {cores[-1]}
+    n0 = numa_node_cores(0)
+    assert isinstance(n0, list) and all(isinstance(c, int) for c in n0)
+    with pytest.raises(Exception):
+        bind_core(1 << 20)
