@@ -508,6 +508,22 @@ class KGExternelEmbedding(_CachedBase):
             self.controller.AfterBackward()
 
 
+class ShmTensorStore:
+    """Process-wide registry of named zero-filled tensors in shared memory, so that forked workers see one copy
+    (src/python/pytorch/recstore/cache/cache_common.py:244-260)."""
+
+    _tensor_store: dict = {}
+
+    @classmethod
+    def GetTensor(cls, name: str):
+        return cls._tensor_store.get(name)
+
+    @classmethod
+    def RegTensor(cls, name: str, shape, dtype=torch.float32):
+        cls._tensor_store[name] = torch.zeros(shape, dtype=dtype).share_memory_()
+        return cls._tensor_store[name]
+
+
 class NVGPUCache:
     """Thin wrapper with the reference's name (cache_common.py:223-241) over :class:`GpuCache`."""
 

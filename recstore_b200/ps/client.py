@@ -330,6 +330,33 @@ class ParameterClient:
         self._rpcs[rid] = (fut, out)
         return rid
 
+    def PutParameterAsync(self, keys, values) -> int:
+        """Issues the put and returns at once with an rpc id for ``QueryRPCFinished`` / ``WaitRPCFinish``; the rows are
+        copied first, so the caller may reuse its buffer."""
+        if self._pool is None:
+            self.InitThread()
+        k = _keys(keys).clone()
+        v = torch.as_tensor(values, dtype=torch.float32).contiguous().clone()
+        assert v.shape == (k.numel(), self.dim)
+        fut = self._pool.submit(lambda: _lib.call("rs_ps_client_put", self._h, k.data_ptr(), k.numel(), self.dim, v.data_ptr(),
+                                                  MAX_PARAMETER_BATCH))
+        rid = self._next_rpc
+        self._next_rpc += 1
+        self._rpcs[rid] = (fut, v)
+        return rid
+
+    # The asynchronous put of the reference's client interface (src/rdma_ps/base_client.h:37-40,
+    # src/rdma_ps/petps_client.cc:147-174: the request names the keys and the caller's value buffer, the id is polled).
+    FakePutParameter = PutParameterAsync
+
+    def Barrier(self, name: str, count: int, postoffice=None) -> None:
+        """Waits until ``count`` participants have called it with this name (src/rdma_ps/base_client.h:17-19).  The
+        rendezvous is the process group's store: pass the ``Postoffice`` that the participants share."""
+        if postoffice is None:
+            raise ValueError("Barrier needs the Postoffice that the participants share")
+        assert count == postoffice.num_members, "every member of the postoffice takes part in its barriers"
+        postoffice.barrier(name)
+
     def QueryRPCFinished(self, rpc_id: int) -> bool:
         return self._rpcs[rpc_id][0].done()
 

@@ -427,3 +427,131 @@ def test_async_entity_update_applies_every_gradient_and_reports_failures():
                             "--n_triples", "5000", "--hidden_dim", "32", "--batch_size", "128", "--neg_sample_size", "16",
                             "--async_update", "--log_interval", "1000", "--gamma", "6"])
     assert out[0]["last_loss"] < out[0]["first_loss"]
+
+
+def test_link_predict_blocks_exclusion_and_model_objects(tmp_path):
+    """Blocked top-k equals the one-shot ranking; `mask` / `exclude` treat triples of the attached graph as the
+    reference's link_predict does (ke_model.py:205-455, 457-640); model objects load the trainers' checkpoints."""
+    import json
+    import numpy as np
+    from recstore_b200.models import kge_infer as I
+    g = torch.Generator().manual_seed(1)
+    ent, rel = torch.randn(40, 8, generator=g), torch.randn(5, 8, generator=g)
+    inf = I.ScoreInfer("TransE_l2", ent, rel, gamma=10.0)
+    hs, ts = torch.arange(20), torch.arange(20, 40)          # disjoint, so no two candidates tie
+    H, R, T = torch.meshgrid(hs, torch.arange(5), ts, indexing="ij")
+    H, R, T = H.reshape(-1), R.reshape(-1), T.reshape(-1)
+    full = 10.0 - (ent[H] + rel[R] - ent[T]).norm(dim=1)
+    want = torch.topk(full, 25)
+    for batch in (7, 1000, 1 << 16):                         # the block size does not change the answer
+        (h, r, t, s), = inf.topk(hs, None, ts, k=25, exec_mode="all", batch_size=batch)
+        assert torch.allclose(s, want.values, atol=1e-5)
+        assert torch.equal(h, H[want.indices]) and torch.equal(r, R[want.indices]) and torch.equal(t, T[want.indices])
+    # logsigmoid output keeps the order and changes the values
+    (h2, r2, t2, s2), = I.ScoreInfer("TransE_l2", ent, rel, gamma=10.0, sfunc="logsigmoid").topk(hs, None, ts, k=25)
+    assert torch.equal(h2, h) and torch.equal(t2, t) and torch.allclose(s2, torch.nn.functional.logsigmoid(want.values), atol=1e-5)
+    # the ten best triples "exist": mask marks them, exclude returns the next ones
+    inf.attach_graph(h[:10], r[:10], t[:10])
+    (mh, mr, mt, ms, mask), = inf.topk(hs, None, ts, k=25, exclude_mode="mask")
+    assert mask[:10].all() and not mask[10:].any() and torch.equal(mh, h)
+    (eh, er, et, es), = inf.topk(hs, None, ts, k=12, exclude_mode="exclude")
+    assert torch.equal(eh, h[10:22]) and torch.equal(er, r[10:22]) and torch.equal(et, t[10:22]) and torch.allclose(es, want.values[10:22], atol=1e-5)
+    inf.attach_graph(H[:1990], R[:1990], T[:1990])           # nearly everything exists
+    (eh, er, et, es), = inf.topk(hs, None, ts, k=25, exclude_mode="exclude")
+    assert es.numel() == 10 and bool(((eh * 5 + er) * 20 + (et - 20) >= 1990).all())
+    per_tail = inf.topk(head=[1, 2, 3], rel=[0, 1], tail=[7, 8], k=4, exec_mode="batch_tail", exclude_mode="mask")
+    assert len(per_tail) == 2 and all(len(x) == 5 and x[2].unique().numel() == 1 for x in per_tail)
+    with pytest.raises(AssertionError):
+        I.ScoreInfer("TransE_l2", ent, rel).topk(k=3, exclude_mode="exclude")      # no graph attached
+    with pytest.raises(ValueError):
+        inf.topk(k=3, exec_mode="sideways")
+    # model objects
+    np.save(tmp_path / "d_DistMult_entity.npy", ent.numpy()); np.save(tmp_path / "d_DistMult_relation.npy", rel.numpy())
+    (tmp_path / "config.json").write_text(json.dumps({"model_name": "DistMult", "gamma": 5.0, "emp_file": "d_DistMult_entity.npy",
+                                                       "rmap_file": "d_DistMult_relation.npy"}))
+    m = I.DistMultModel().load(str(tmp_path))
+    assert m.model_name == "DistMult" and m.num_entity == 40 and m.num_rel == 5 and m.graph is None
+    (h, r, t, s), = m.link_predict(head=[0, 1], rel=None, tail=None, topk=6)
+    assert torch.allclose(s, (ent[h] * rel[r] * ent[t]).sum(1), atol=1e-6) and bool((s[:-1] >= s[1:]).all())
+    m.attach_graph(h[:2], r[:2], t[:2])
+    (h3, r3, t3, s3), = m.link_predict(head=[0, 1], topk=4, exclude_mode="exclude")
+    assert torch.equal(h3, h[2:6]) and torch.equal(t3, t[2:6])
+    (l, rr, v), = m.embed_sim(left=[0, 1, 2], embed_type="entity", topk=3)
+    assert torch.allclose(v, torch.ones(3), atol=1e-6)
+    lists = m.embed_sim(left=[0, 4], right=None, embed_type="relation", sfunc="l2", bcast=True, topk=2)
+    assert len(lists) == 2 and lists[1][1][0].item() == 4
+    np.save(tmp_path / "entity.npy", ent.numpy()); np.save(tmp_path / "relation.npy", rel.numpy())
+    (tmp_path / "config.json").unlink()
+    assert I.TransE_l1Model(gamma=3.0).load(str(tmp_path)).model_name == "TransE_l1"      # default file names, no config
+    # RESCAL checkpoints that keep the matrices in the relation file
+    mats = torch.randn(5, 64, generator=g)
+    ri = I.ScoreInfer("RESCAL", ent, mats)
+    got = ri._score(torch.tensor([1]), torch.tensor([2]), torch.tensor([3]))
+    assert torch.allclose(got, ent[1] @ mats[2].view(8, 8) @ ent[3], atol=1e-5)
+    # big pairwise similarity goes through blocks too
+    big = torch.randn(3000, 4, generator=g)
+    (l, rr, v), = I.EmbSimInfer(big, "dot").topk(k=5, batch_size=512)
+    ref = torch.topk((big @ big.t()).reshape(-1), 5)
+    assert torch.allclose(v, ref.values, atol=1e-5) and torch.equal(l * 3000 + rr, ref.indices)
+
+
+def test_kge_infer_cli_score_emb_sim_eval_convert(tmp_path):
+    """The four tools around a saved model (infer_score.py, infer_emb_sim.py, eval.py, convert.py of the reference)."""
+    import json
+    from recstore_b200.cli import kge_infer, kge_main
+    ck = tmp_path / "ck"
+    data = ["--n_entities", "200", "--n_relations", "5", "--n_triples", "4000"]
+    kge_main.main(["--model_name", "DistMult", "--max_step", "60", "--hidden_dim", "16", "--batch_size", "64", "--neg_sample_size", "16",
+                   "--save_path", str(ck), "--log_interval", "1000"] + data)
+    # eval: one process and three processes rank the same triples, so the averages agree
+    one = kge_infer.main(["eval", "--model_path", str(ck), "--json_out", str(tmp_path / "m.json")] + data, return_result=True)
+    three = kge_infer.main(["eval", "--model_path", str(ck), "--num_proc", "3"] + data, return_result=True)
+    assert one["filtered"] and one["processes"] == 1 and three["processes"] == 3 and one["triples"] == three["triples"] == 80
+    for k in ("MRR", "MR", "HITS@10"):
+        assert abs(one[k] - three[k]) < 1e-5, (k, one[k], three[k])
+    assert 1.0 <= one["MR"] <= 200 and 0 < one["MRR"] <= 1 and json.load(open(tmp_path / "m.json"))["MRR"] == one["MRR"]
+    raw = kge_infer.main(["eval", "--model_path", str(ck), "--no_eval_filter"] + data, return_result=True)
+    assert not raw["filtered"] and raw["MR"] >= one["MR"]                       # filtering can only improve a rank
+    sampled = kge_infer.main(["eval", "--model_path", str(ck), "--neg_sample_size_eval", "32"] + data, return_result=True)
+    assert 1.0 <= sampled["MR"] <= 33
+    # score: heads and relations listed, every tail a candidate
+    (tmp_path / "h.list").write_text("3\n7\n")
+    (tmp_path / "r.list").write_text("1\n")
+    out = tmp_path / "res.tsv"
+    assert kge_infer.main(["score", "--model_path", str(ck), "--format", "h_r_*", "--data_files", str(tmp_path / "h.list"), str(tmp_path / "r.list"),
+                           "--exec_mode", "batch_head", "--topK", "4", "--output", str(out)]) == 0
+    rows = [l.split("\t") for l in out.read_text().strip().split("\n")]
+    assert rows[0] == ["head", "rel", "tail", "score"] and len(rows) == 1 + 2 * 4
+    assert [r[0] for r in rows[1:]] == ["3"] * 4 + ["7"] * 4 and all(r[1] == "1" for r in rows[1:])
+    ent, rel = np.load(ck / "synthetic_DistMult_entity.npy"), np.load(ck / "synthetic_DistMult_relation.npy")
+    best = np.argsort(-(ent[3] * rel[1] * ent).sum(1))[:4]
+    assert [int(r[2]) for r in rows[1:5]] == best.tolist()
+    # ... by name, with the best candidate declared known and excluded
+    (tmp_path / "e.map").write_text("".join(f"{i}\tent{i}\n" for i in range(200)))
+    (tmp_path / "r.map").write_text("".join(f"{i}\trel{i}\n" for i in range(5)))
+    (tmp_path / "hn.list").write_text("ent3\n")
+    (tmp_path / "rn.list").write_text("rel1\n")
+    (tmp_path / "known.tsv").write_text(f"3\t1\t{best[0]}\n")
+    assert kge_infer.main(["score", "--model_path", str(ck), "--format", "h_r_*", "--data_files", str(tmp_path / "hn.list"), str(tmp_path / "rn.list"),
+                           "--raw_data", "--entity_mfile", str(tmp_path / "e.map"), "--rel_mfile", str(tmp_path / "r.map"), "--topK", "3",
+                           "--exclude_mode", "exclude", "--known_files", str(tmp_path / "known.tsv"), "--output", str(out)]) == 0
+    rows = [l.split("\t") for l in out.read_text().strip().split("\n")][1:]
+    assert [r[2] for r in rows] == [f"ent{i}" for i in best[1:4]] and rows[0][0] == "ent3" and rows[0][1] == "rel1"
+    with pytest.raises(SystemExit):
+        kge_infer.main(["score", "--model_path", str(ck), "--format", "h_r_t", "--data_files", str(tmp_path / "h.list")])
+    # emb_sim: each listed id against everything; itself comes first
+    assert kge_infer.main(["emb_sim", "--emb_file", str(ck / "synthetic_DistMult_entity.npy"), "--format", "l_*", "--data_files", str(tmp_path / "h.list"),
+                           "--exec_mode", "batch_left", "--topK", "2", "--output", str(out)]) == 0
+    rows = [l.split("\t") for l in out.read_text().strip().split("\n")]
+    assert rows[0] == ["left", "right", "score"] and rows[1][:2] == ["3", "3"] and rows[3][:2] == ["7", "7"] and abs(float(rows[1][2]) - 1) < 1e-5
+    # convert: names -> ids + dictionaries, column order as asked
+    d = tmp_path / "raw"
+    d.mkdir()
+    (d / "train.tsv").write_text("a\tlikes\tb\nb\tlikes\tc\nc\tknows\ta\n")
+    (d / "valid.tsv").write_text("a\tknows\tc\n")
+    assert kge_infer.main(["convert", "--data_path", str(d), "--data_files", "train.tsv", "valid.tsv", "--output_format", "udd_htr",
+                           "--output_path", str(tmp_path / "udd")]) == 0
+    assert (tmp_path / "udd" / "train_output.txt").read_text() == "0\t1\t0\n1\t2\t0\n2\t0\t1\n"
+    assert (tmp_path / "udd" / "valid_output.txt").read_text() == "0\t2\t1\n" and not (tmp_path / "udd" / "test_output.txt").exists()
+    back = K.KGDataset.load(str(tmp_path / "udd"), ["entities.tsv", "relations.tsv", "train_output.txt", "valid_output.txt"], "udd_htr")
+    assert back.n_entities == 3 and back.n_relations == 2 and back.train[1].tolist() == [0, 0, 1] and back.valid[2].tolist() == [2]

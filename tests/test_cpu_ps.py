@@ -64,6 +64,14 @@ def test_ps_client_server_mirror(engine, tmp_path):
     assert cli.QueryRPCFinished(rid)
     assert torch.equal(cli.GetReceiveBuffer(rid), (mirror * present.unsqueeze(1))[:3000])
     cli.RevokeRPCResource(rid)
+    # asynchronous put: the caller's buffer may be reused at once, the rows land when the rpc has finished
+    buf = torch.full((3, dim), 7.0)
+    rid = cli.FakePutParameter(torch.tensor([11, 12, 13]), buf)
+    buf.zero_()
+    cli.WaitRPCFinish(rid)
+    assert cli.QueryRPCFinished(rid) and torch.equal(cli.GetParameter(torch.tensor([11, 12, 13])), torch.full((3, dim), 7.0))
+    cli.RevokeRPCResource(rid)
+    mirror[11:14] = 7.0; present[11:14] = True
     # checkpoint round trip through the server
     ck = str(tmp_path / "ps.ckpt")
     cli.SaveCkpt(ck)
