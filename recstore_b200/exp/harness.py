@@ -6,6 +6,15 @@
 "timeout_s": 3600, "grid": {"num_workers": [2, 4], "cache_ratio": [0.05, 0.1], "backwardMode": ["CppSync",
 "CppAsyncV2"]}, "fixed": {"run_steps": 200}, "exclude": [{"num_workers": 4, "backwardMode": "CppSync"}]}``.
 
+Optional keys: ``"bindings"``: options that vary TOGETHER -- a list of groups, each group a list of sub-grids whose
+expansions are concatenated, e.g. ``[[{"model": ["TransE_l2"], "gamma": [12.0]}, {"model": ["DistMult"], "gamma":
+[100.0, 140.0]}]]`` gives three (model, gamma) pairs, multiplied with the grid (bench_util.py ``GenBinding`` /
+``PreprocessConfig``); ``"servers"``: commands started before every run and stopped after it (client / server
+experiments such as PS benchmarks: ``[{"command": "...", "ready_marker": "listening", "ready_timeout_s": 60}]``; their
+options may use ``{key}`` placeholders of the run's configuration); ``"pre_run"`` / ``"post_run"``: shell commands
+around every run; ``"hosts"``: run the command on these machines over ``ssh`` at once (one log per host) instead of
+locally.
+
 What it keeps from the reference's harness (src/kg/scripts/exp_config.py, bench_base.py, bench_util.py): the grid
 expansion, a log directory per run named after its options, the rule that a run counts as finished only if its log
 contains the completion marker ``Successfully xmh`` (exp_config.py:119-139; anything else after the time limit is
@@ -30,15 +39,43 @@ from typing import Callable, Dict, Iterator, List, Optional, Sequence
 MARKER = "Successfully xmh"
 
 
-def expand_grid(grid: Dict[str, Sequence], fixed: Optional[dict] = None, exclude: Optional[Sequence[dict]] = None,
-                keep: Optional[Callable[[dict], bool]] = None) -> List[dict]:
-    """Cartesian product of ``grid`` (insertion order, last key fastest) merged over ``fixed``; drops every
-    configuration that contains all key/value pairs of an ``exclude`` entry or fails ``keep``."""
-    keys = list(grid)
+def expand_bindings(groups: Optional[Sequence[Sequence[Dict[str, Sequence]]]]) -> List[dict]:
+    """Every combination of one entry per group, where a group's entries are the concatenated expansions of its
+    sub-grids: options that only make sense together vary together instead of being multiplied out."""
+    per_group = []
+    for group in groups or []:
+        entries: List[dict] = []
+        for sub in group:
+            keys = list(sub)
+            entries += [dict(zip(keys, vals)) for vals in itertools.product(*(sub[k] for k in keys))]
+        per_group.append(entries)
     out = []
-    for vals in itertools.product(*(grid[k] for k in keys)):
+    for combo in itertools.product(*per_group):
+        merged: dict = {}
+        for c in combo:
+            clash = set(merged) & set(c)
+            if clash:
+                raise ValueError(f"option(s) {sorted(clash)} appear in two binding groups")
+            merged.update(c)
+        out.append(merged)
+    return out
+
+
+def expand_grid(grid: Dict[str, Sequence], fixed: Optional[dict] = None, exclude: Optional[Sequence[dict]] = None,
+                keep: Optional[Callable[[dict], bool]] = None,
+                bindings: Optional[Sequence[Sequence[Dict[str, Sequence]]]] = None) -> List[dict]:
+    """Cartesian product of ``grid`` (insertion order, last key fastest), times the bound option sets of ``bindings``,
+    merged over ``fixed``; drops every configuration that contains all key/value pairs of an ``exclude`` entry or
+    fails ``keep``."""
+    keys = list(grid)
+    bound = expand_bindings(bindings)
+    if any(set(b) & set(keys) for b in bound):
+        raise ValueError("an option is both in the grid and in a binding")
+    out = []
+    for vals, b in itertools.product(itertools.product(*(grid[k] for k in keys)), bound):
         cfg = dict(fixed or {})
         cfg.update(zip(keys, vals))
+        cfg.update(b)
         if any(all(cfg.get(k) == v for k, v in ex.items()) for ex in (exclude or [])):
             continue
         if keep is not None and not keep(cfg):
@@ -112,14 +149,77 @@ class RunResult:
     returncode: Optional[int]
 
 
+def ssh_argv(host: str, command: Sequence[str], cwd: Optional[str] = None) -> List[str]:
+    """The ``ssh`` command line that runs ``command`` on ``host`` (in ``cwd``), every word quoted for the remote shell."""
+    remote = " ".join(shlex.quote(c) for c in command)
+    if cwd:
+        remote = f"cd {shlex.quote(cwd)} && {remote}"
+    return ["ssh", "-o", "StrictHostKeyChecking=no", "-o", "BatchMode=yes", host, remote]
+
+
+def _stop_group(p: subprocess.Popen, grace_s: float = 10.0) -> Optional[int]:
+    """Ends the process group that ``p`` leads (only what this harness started)."""
+    if p.poll() is None:
+        try:
+            os.killpg(p.pid, 15)
+        except ProcessLookupError:
+            pass
+        try:
+            return p.wait(timeout=grace_s)
+        except subprocess.TimeoutExpired:
+            try:
+                os.killpg(p.pid, 9)
+            except ProcessLookupError:
+                pass
+            return p.wait()
+    return p.returncode
+
+
 class Experiment:
     def __init__(self, name: str, command: str, grid: Dict[str, Sequence], fixed: Optional[dict] = None,
                  exclude: Optional[Sequence[dict]] = None, log_root: str = "runs", timeout_s: float = 3600.0,
-                 marker: str = MARKER, env: Optional[dict] = None):
+                 marker: str = MARKER, env: Optional[dict] = None,
+                 bindings: Optional[Sequence[Sequence[Dict[str, Sequence]]]] = None, servers: Optional[Sequence[dict]] = None,
+                 pre_run: Optional[str] = None, post_run: Optional[str] = None, hosts: Optional[Sequence[str]] = None,
+                 remote_cwd: Optional[str] = None):
         self.name, self.command, self.grid, self.fixed = name, command, grid, dict(fixed or {})
-        self.configs = expand_grid(grid, fixed, exclude)
+        self.configs = expand_grid(grid, fixed, exclude, bindings=bindings)
+        self.varying = list(grid) + [k for k in (expand_bindings(bindings)[0] if bindings else {})]
         self.root = os.path.join(log_root, name)
         self.timeout_s, self.marker, self.env = timeout_s, marker, env
+        self.servers, self.pre_run, self.post_run = list(servers or []), pre_run, post_run
+        self.hosts, self.remote_cwd = list(hosts or []), remote_cwd
+
+    # ---- client / server runs (bench_base.py CSExperiment: servers first, clients once they are up) ----
+    def _start_servers(self, cfg: dict, d: str, env: dict) -> List[subprocess.Popen]:
+        procs = []
+        for i, spec in enumerate(self.servers):
+            argv = [a.format(**cfg) for a in shlex.split(spec["command"])]
+            log = os.path.join(d, f"server_{i}.log")
+            lf = open(log, "w")
+            p = subprocess.Popen(argv, stdout=lf, stderr=subprocess.STDOUT, env=env, start_new_session=True)
+            lf.close()
+            procs.append(p)
+            marker, limit = spec.get("ready_marker"), float(spec.get("ready_timeout_s", 60.0))
+            t0 = time.time()
+            while marker:
+                if log_succeeded(log, marker):
+                    break
+                if p.poll() is not None or time.time() - t0 > limit:
+                    for q in procs:
+                        _stop_group(q)
+                    raise RuntimeError(f"server {i} ({argv[0]} ...) did not print {marker!r}: see {log}")
+                time.sleep(0.05)
+            if not marker:
+                time.sleep(float(spec.get("settle_s", 0.5)))
+        return procs
+
+    def _hook(self, command: Optional[str], cfg: dict, d: str, env: dict, tag: str) -> None:
+        if not command:
+            return
+        with open(os.path.join(d, f"{tag}.log"), "w") as lf:
+            subprocess.run(command.format(run_dir=d, **cfg), shell=True, stdout=lf, stderr=subprocess.STDOUT, env=env,
+                           timeout=self.timeout_s, check=False)
 
     def argv(self, cfg: dict) -> List[str]:
         args = shlex.split(self.command)
@@ -134,7 +234,7 @@ class Experiment:
     def run(self, rerun: bool = False, dry: bool = False) -> List[RunResult]:
         os.makedirs(self.root, exist_ok=True)
         results = []
-        varying = list(self.grid)             # every grid key names the directory, so a narrower re-run finds its runs
+        varying = self.varying                # every grid / bound key names the directory, so a narrower re-run finds its runs
         for i, cfg in enumerate(self.configs):
             d = os.path.join(self.root, run_dir_name(i, cfg, varying))
             log = os.path.join(d, "log")
@@ -150,25 +250,56 @@ class Experiment:
             t0 = time.time()
             env = dict(os.environ)
             env.update(self.env or {})
-            with open(log, "w") as lf:
-                p = subprocess.Popen(self.argv(cfg), stdout=lf, stderr=subprocess.STDOUT, env=env, start_new_session=True)
-                try:
-                    rc = p.wait(timeout=self.timeout_s)
-                    timed_out = False
-                except subprocess.TimeoutExpired:
-                    timed_out = True
-                    os.killpg(p.pid, 15)            # the run's own process group, nobody else's
-                    try:
-                        rc = p.wait(timeout=10)
-                    except subprocess.TimeoutExpired:
-                        os.killpg(p.pid, 9)
-                        rc = p.wait()
+            self._hook(self.pre_run, cfg, d, env, "pre_run")
+            try:
+                servers = self._start_servers(cfg, d, env)
+            except RuntimeError as e:
+                with open(log, "w") as lf:
+                    lf.write(f"{e}\n")
+                results.append(RunResult(i, cfg, d, "failed", time.time() - t0, None))
+                continue
+            try:
+                rc, timed_out = self._run_clients(cfg, d, log, env)
+            finally:
+                for sp in servers:
+                    _stop_group(sp)
+                self._hook(self.post_run, cfg, d, env, "post_run")
             ok = log_succeeded(log, self.marker)
             status = "ok" if ok else ("deadlock?" if timed_out else "failed")
             results.append(RunResult(i, cfg, d, status, time.time() - t0, rc))
         with open(os.path.join(self.root, "summary.json"), "w") as f:
             json.dump([asdict(r) for r in results], f, indent=1)
         return results
+
+    def _run_clients(self, cfg: dict, d: str, log: str, env: dict):
+        """The run's command, locally or on every host at once; (return code, timed out).  With hosts the per-host
+        outputs go to ``log.<host>`` and are joined into ``log`` at the end, so the marker rule reads one file; the
+        run succeeds only if every host printed the marker."""
+        targets = [(None, self.argv(cfg), log)] if not self.hosts else \
+            [(h, ssh_argv(h, self.argv(cfg), self.remote_cwd), f"{log}.{h}") for h in self.hosts]
+        procs = []
+        for _, argv, path in targets:
+            lf = open(path, "w")
+            procs.append(subprocess.Popen(argv, stdout=lf, stderr=subprocess.STDOUT, env=env, start_new_session=True))
+            lf.close()
+        deadline = time.time() + self.timeout_s
+        rcs, timed_out = [], False
+        for p in procs:
+            try:
+                rcs.append(p.wait(timeout=max(0.0, deadline - time.time())))
+            except subprocess.TimeoutExpired:
+                timed_out = True
+                rcs.append(_stop_group(p))          # the run's own process group, nobody else's
+        if self.hosts:
+            all_ok = all(log_succeeded(path, self.marker) for _, _, path in targets)
+            with open(log, "w") as out:
+                for h, _, path in targets:
+                    out.write(f"===== {h} =====\n")
+                    with open(path, errors="replace") as f:
+                        text = f.read()
+                    out.write(text if all_ok else text.replace(self.marker, "(marker of one host)"))
+        rc = next((r for r in rcs if r not in (0, None)), rcs[0] if rcs else None)
+        return rc, timed_out
 
 
 def main(argv=None):
@@ -183,7 +314,9 @@ def main(argv=None):
     with open(a.spec) as f:
         spec = json.load(f)
     exp = Experiment(spec["name"], spec["command"], spec.get("grid", {}), spec.get("fixed"), spec.get("exclude"),
-                     spec.get("log_root", "runs"), spec.get("timeout_s", 3600.0), spec.get("marker", MARKER), spec.get("env"))
+                     spec.get("log_root", "runs"), spec.get("timeout_s", 3600.0), spec.get("marker", MARKER), spec.get("env"),
+                     bindings=spec.get("bindings"), servers=spec.get("servers"), pre_run=spec.get("pre_run"),
+                     post_run=spec.get("post_run"), hosts=spec.get("hosts"), remote_cwd=spec.get("remote_cwd"))
     if a.clean:
         for d in clean_unsuccessful(exp.root, exp.marker, dry=a.dry):
             print(("would remove " if a.dry else "removed ") + d)

@@ -82,3 +82,81 @@ def test_determinism_recorder_and_driver_flag(tmp_path):
     kge_main.main(base)
     with pytest.raises(DeterminismError):
         kge_main.main(base + ["--seed", "7"])
+
+
+def test_bindings_vary_options_together():
+    """Sub-grids of a binding group are expanded one by one and concatenated, groups are multiplied with each other and
+    with the grid (GenBinding / PreprocessConfig of src/kg/scripts/bench_util.py)."""
+    from recstore_b200.exp.harness import expand_bindings
+    groups = [[{"model": ["TransE_l2"], "gamma": [12.0]}, {"model": ["DistMult"], "gamma": [100.0, 140.0]}],
+              [{"bs": [256], "lr": [0.1]}, {"bs": [1024], "lr": [0.4]}]]
+    b = expand_bindings(groups)
+    assert len(b) == 3 * 2 and b[0] == {"model": "TransE_l2", "gamma": 12.0, "bs": 256, "lr": 0.1}
+    assert {"model": "DistMult", "gamma": 140.0, "bs": 1024, "lr": 0.4} in b
+    assert not any(c["model"] == "TransE_l2" and c["gamma"] != 12.0 for c in b)
+    g = expand_grid({"gpus": [1, 2]}, fixed={"steps": 5}, bindings=groups, exclude=[{"gpus": 2, "bs": 256}])
+    assert len(g) == 2 * 6 - 3 and all(c["steps"] == 5 for c in g)
+    assert expand_bindings(None) == [{}] and expand_grid({"a": [1]}, bindings=[]) == [{"a": 1}]
+    with pytest.raises(ValueError):
+        expand_grid({"bs": [1]}, bindings=groups)                       # an option cannot be in both
+    with pytest.raises(ValueError):
+        expand_bindings([[{"x": [1]}], [{"x": [2]}]])                   # nor in two groups
+
+
+def test_client_server_runs_hooks_and_server_failure(tmp_path):
+    """Servers come up first (ready marker), the client talks to them, they are stopped after the run; hooks run around
+    it; a server that never gets ready fails the run without starting the client (bench_base.py CSExperiment)."""
+    server = tmp_path / "server.py"
+    server.write_text(
+        "import socket, sys, time\n"
+        "port, mode = int(sys.argv[1]), sys.argv[2]\n"
+        "if mode == 'broken': sys.exit(5)\n"
+        "s = socket.socket(); s.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)\n"
+        "s.bind(('127.0.0.1', port)); s.listen(4)\n"
+        "print('listening', port, flush=True)\n"
+        "while True:\n"
+        "    c, _ = s.accept(); c.sendall(b'pong'); c.close()\n")
+    client = tmp_path / "client.py"
+    client.write_text(
+        "import socket, sys\n"
+        "a = dict(zip(sys.argv[1::2], sys.argv[2::2]))\n"
+        "c = socket.create_connection(('127.0.0.1', int(a['--port'])), timeout=10)\n"
+        "assert c.recv(4) == b'pong'\n"
+        "print('Successfully xmh')\n")
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    exp = Experiment("cs", f"{sys.executable} {client}", {"mode": ["fine", "broken"]}, fixed={"port": port},
+                     log_root=str(tmp_path / "runs"), timeout_s=30,
+                     servers=[{"command": f"{sys.executable} {server} {{port}} {{mode}}", "ready_marker": "listening", "ready_timeout_s": 20}],
+                     pre_run="echo before {mode} > {run_dir}/pre.txt", post_run="echo after {mode} > {run_dir}/post.txt")
+    res = exp.run()
+    assert [r.status for r in res] == ["ok", "failed"]
+    d0, d1 = res[0].directory, res[1].directory
+    assert "listening" in open(os.path.join(d0, "server_0.log")).read()
+    assert open(os.path.join(d0, "pre.txt")).read().strip() == "before fine" and open(os.path.join(d0, "post.txt")).read().strip() == "after fine"
+    assert "did not print" in open(os.path.join(d1, "log")).read()
+    with pytest.raises(OSError):                                       # the first run's server is gone: nobody listens any more
+        socket.create_connection(("127.0.0.1", port), timeout=2)
+
+
+def test_runs_on_hosts_go_through_ssh_and_need_every_marker(tmp_path, monkeypatch):
+    """With `hosts` the command runs once per host through `ssh` (here a stand-in on PATH that runs it locally and can
+    fail one host); the run counts only if every host printed the marker."""
+    from recstore_b200.exp.harness import ssh_argv
+    assert ssh_argv("box7", ["python", "-c", "print('a b')"], cwd="/w d")[-2:] == ["box7", "cd '/w d' && python -c 'print('\"'\"'a b'\"'\"')'"]
+    fake = tmp_path / "bin"
+    fake.mkdir()
+    (fake / "ssh").write_text("#!/bin/sh\n# stand-in: drop the options, note the host, run the command here\n"
+                              "while [ \"$1\" = \"-o\" ]; do shift 2; done\nhost=$1; shift\n"
+                              "if [ \"$host\" = \"bad\" ]; then echo no route; exit 255; fi\necho on $host; exec sh -c \"$1\"\n")
+    (fake / "ssh").chmod(0o755)
+    monkeypatch.setenv("PATH", f"{fake}:{os.environ['PATH']}")
+    job = tmp_path / "job.py"
+    job.write_text("print('Successfully xmh')\n")
+    ok = Experiment("h", f"{sys.executable} {job}", {"x": [1]}, log_root=str(tmp_path / "runs"), hosts=["n1", "n2"], timeout_s=30).run()
+    assert [r.status for r in ok] == ["ok"]
+    text = open(os.path.join(ok[0].directory, "log")).read()
+    assert "===== n1 =====" in text and "on n2" in text and text.count("Successfully xmh") == 2
+    bad = Experiment("h2", f"{sys.executable} {job}", {"x": [1]}, log_root=str(tmp_path / "runs"), hosts=["n1", "bad"], timeout_s=30).run()
+    assert [r.status for r in bad] == ["failed"] and bad[0].returncode == 255
+    assert "no route" in open(os.path.join(bad[0].directory, "log")).read()
