@@ -131,13 +131,12 @@ def kg_loss(pos: torch.Tensor, neg: torch.Tensor, genre: str = "Logsigmoid", mar
 
 
 def rowwise_adagrad_(weight: torch.Tensor, state: torch.Tensor, ids: torch.Tensor, grad: torch.Tensor, lr: float, eps: float = 1e-10):
-    """state[u] += mean_d((sum of the row's gradients / count)^2); w[u] -= lr * g / (sqrt(state[u]) + eps), with the
-    duplicate gradients of a row averaged as the reference's sparse Adagrad does (tensor_models.py:380-415)."""
-    u, inv, cnt = torch.unique(ids, return_inverse=True, return_counts=True)
-    g = torch.zeros(u.numel(), grad.shape[1], dtype=grad.dtype, device=grad.device).index_add_(0, inv, grad)
-    g = g / cnt.unsqueeze(1).to(g.dtype)
-    state[u] += (g * g).mean(1)
-    weight[u] -= lr * g / (state[u].sqrt().unsqueeze(1) + eps)
+    """The reference's sparse row-wise Adagrad (tensor_models.py:398-430 ``ExternalEmbedding.update``), duplicates
+    allowed: ``state[id] += mean_d(g^2)`` for every occurrence, then every occurrence moves its row by
+    ``-lr * g / (sqrt(state[id]) + eps)`` with the state AFTER all of the step's occurrences were added."""
+    state.index_add_(0, ids, (grad * grad).mean(1))
+    std = state[ids].sqrt().add_(eps).unsqueeze(1)
+    weight.index_add_(0, ids, -lr * grad / std)
 
 
 class TorchKGE:

@@ -555,3 +555,95 @@ def test_kge_infer_cli_score_emb_sim_eval_convert(tmp_path):
     assert (tmp_path / "udd" / "valid_output.txt").read_text() == "0\t2\t1\n" and not (tmp_path / "udd" / "test_output.txt").exists()
     back = K.KGDataset.load(str(tmp_path / "udd"), ["entities.tsv", "relations.tsv", "train_output.txt", "valid_output.txt"], "udd_htr")
     assert back.n_entities == 3 and back.n_relations == 2 and back.train[1].tolist() == [0, 0, 1] and back.valid[2].tolist() == [2]
+
+
+def test_external_embedding_trace_update_async_and_cross_relations(tmp_path):
+    """The trainer's table object (tensor_models.py:217-476): traced lookups, row-wise Adagrad with duplicates,
+    asynchronous update, relations shared across partitions, .npy round trip."""
+    from recstore_b200.models.kg_embedding import ExternalEmbedding
+    torch.manual_seed(0)
+    e = ExternalEmbedding(50, 4, lr=0.5)
+    e.init(0.3)
+    assert float(e.emb.abs().max()) <= 0.3 and float(e.state_sum.abs().sum()) == 0
+    w0 = e.emb.clone()
+    idx = torch.tensor([3, 7, 3])
+    rows = e(idx)
+    assert rows.requires_grad and torch.equal(rows.detach(), w0[idx]) and torch.equal(e.curr_emb(), rows)
+    assert not e(idx, trace=False).requires_grad and len(e.trace) == 1
+    (rows * torch.tensor([[1.0], [2.0], [3.0]])).sum().backward()
+    e.update()
+    g = torch.tensor([[1.0] * 4, [2.0] * 4, [3.0] * 4])
+    state = torch.zeros(50).index_add_(0, idx, (g * g).mean(1))
+    want = w0.clone().index_add_(0, idx, -0.5 * g / (state[idx].sqrt() + 1e-10).unsqueeze(1))
+    assert torch.allclose(e.emb, want, atol=1e-6) and torch.allclose(e.state_sum, state) and e.trace == [] and e.state_step == 1
+    # asynchronous: the same updates, applied by the worker; after finish the table equals the synchronous one
+    a, b = ExternalEmbedding(50, 4, lr=0.5), ExternalEmbedding(50, 4, lr=0.5)
+    a.emb.copy_(w0); b.emb.copy_(w0)
+    b.create_async_update()
+    gen = torch.Generator().manual_seed(1)
+    for _ in range(20):
+        ids = torch.randint(0, 50, (16,), generator=gen)
+        coef = torch.randn(16, 1, generator=gen)
+        for t in (a, b):
+            if t is b:
+                t.wait_async_update()                # keep the two in lockstep so the results are comparable
+            (t(ids) * coef).sum().backward()
+            t.update()
+    b.finish_async_update()
+    assert torch.allclose(a.emb, b.emb, atol=1e-6) and torch.allclose(a.state_sum, b.state_sum, atol=1e-6)
+    # relations 1 and 4 are shared by several partitions: their updates land in the global table, reads refresh from it
+    glob, loc = ExternalEmbedding(6, 4, lr=0.5), ExternalEmbedding(6, 4, lr=0.5)
+    glob.emb.fill_(1.0); loc.emb.fill_(2.0)
+    loc.setup_cross_rels([1, 4], glob)
+    assert loc.get_noncross_idx(torch.tensor([0, 1, 2, 4])).tolist() == [0, 2]
+    r = loc(torch.tensor([1, 2]))
+    assert torch.equal(r.detach(), torch.tensor([[1.0] * 4, [2.0] * 4]))          # row 1 came from the global table
+    r.sum().backward()
+    loc.update()
+    assert float(glob.emb[1, 0]) == pytest.approx(1.0 - 0.5 / 1.0, abs=1e-6) and float(glob.emb[2, 0]) == 1.0
+    assert float(loc.emb[2, 0]) == pytest.approx(2.0 - 0.5, abs=1e-6)
+    e.save(str(tmp_path), "ent")
+    f = ExternalEmbedding(50, 4)
+    f.load(str(tmp_path), "ent")
+    assert torch.equal(f.emb, e.emb)
+    with pytest.raises(AssertionError):
+        ExternalEmbedding(49, 4).load(str(tmp_path), "ent")
+
+
+def test_custom_external_embedding_over_a_shared_table(tmp_path):
+    """The RecStore-backed table object (cus_external_emb.py:20-215): DistEmbedding + cached embedding; update goes to
+    the shared table; save / load work."""
+    import os
+    import recstore_b200 as rs
+    from recstore_b200 import ipc
+    from recstore_b200.models.kg_embedding import CustomExternalEmbedding
+    ipc.set_namespace(f"pytest_cee_{os.getpid()}")
+    rs.kvinit()
+    c = CustomExternalEmbedding(40, 4, "cee_entity", lr=0.25, cached_emb_type="KGExternelEmbedding")
+    c.init(0.0)
+    assert float(c.emb.weight.abs().sum()) == 0
+    c.init(0.2)
+    w0 = c.emb.weight.clone()
+    with pytest.raises(AssertionError):
+        c(torch.tensor([1]))
+    c.prepare_per_worker_process()
+    idx = torch.tensor([5, 9, 5])
+    rows = c(idx)
+    assert torch.allclose(rows.detach(), w0[idx]) and torch.equal(c.curr_emb(), rows)
+    rows.sum().backward()
+    c.update()
+    want = w0.clone().index_add_(0, idx, torch.full((3, 4), -0.25))
+    assert torch.allclose(c.emb.weight, want, atol=1e-6) and c.trace == []
+    c.save(str(tmp_path), "cee")
+    c.emb.weight.zero_()
+    c.load(str(tmp_path), "cee")
+    assert torch.allclose(c.emb.weight, want, atol=1e-6)
+    # the plain torch table as the "cache type": rows updated by a torch optimizer
+    t = CustomExternalEmbedding(40, 4, "cee_entity2", lr=0.5, cached_emb_type="TorchNativeStdEmb")
+    t.init(0.1)
+    t.prepare_per_worker_process()
+    before = t.cached_emb.weight.detach().clone()
+    t(torch.tensor([2, 2, 3])).sum().backward()
+    t.update()
+    assert torch.allclose(t.cached_emb.weight.detach()[2], before[2] - 0.5 * 2, atol=1e-6)
+    assert torch.allclose(t.cached_emb.weight.detach()[3], before[3] - 0.5, atol=1e-6)
