@@ -46,6 +46,20 @@ class KGDataset:
         return KGDataset("synthetic", n_entities, n_relations, cut(2 * n_test, n_triples), cut(0, n_test), cut(n_test, 2 * n_test))
 
     @staticmethod
+    def planted_grid(width: int = 20, height: int = 15, shifts: Sequence[Tuple[int, int]] = ((1, 0), (0, 1), (2, 1), (-1, 3)),
+                     test_frac: float = 0.1, seed: int = 0) -> "KGDataset":
+        """A graph with structure to find: the entities are the cells of a ``width x height`` grid, relation k links a
+        cell to the cell ``shifts[k]`` away (where that is still on the grid).  A share of the triples is held out:
+        a model that has learnt the geometry ranks them high without having seen them, one that memorises does not."""
+        trip = [(x * height + y, k, (x + dx) * height + (y + dy)) for x in range(width) for y in range(height)
+                for k, (dx, dy) in enumerate(shifts) if 0 <= x + dx < width and 0 <= y + dy < height]
+        trip = np.array(trip, dtype=np.int64)
+        np.random.default_rng(seed).shuffle(trip)
+        n_test = max(1, int(len(trip) * test_frac))
+        cut = lambda a, b: tuple(np.ascontiguousarray(trip[a:b, i]) for i in range(3))
+        return KGDataset("planted_grid", width * height, len(shifts), cut(n_test, len(trip)), None, cut(0, n_test))
+
+    @staticmethod
     def load(path: str, files: Sequence[str], fmt: str = "raw_udd_hrt", name: Optional[str] = None, delimiter: str = "\t",
              has_edge_importance: bool = False):
         """``files``: train [valid test] for ``raw_udd_*``; entities, relations, train [valid test] for ``udd_*``.

@@ -647,3 +647,24 @@ def test_custom_external_embedding_over_a_shared_table(tmp_path):
     t.update()
     assert torch.allclose(t.cached_emb.weight.detach()[2], before[2] - 0.5 * 2, atol=1e-6)
     assert torch.allclose(t.cached_emb.weight.detach()[3], before[3] - 0.5, atol=1e-6)
+
+
+@pytest.mark.parametrize("model,floor", [("RotatE", 0.6), ("ComplEx", 0.5)])
+def test_training_generalises_to_held_out_triples_of_a_planted_graph(model, floor):
+    """Sampler -> scores -> loss -> sparse Adagrad -> filtered full ranking, end to end: on a graph whose relations are
+    fixed shifts on a grid, held-out triples rank far above chance (MRR of a random table: ~0.02) after training."""
+    from recstore_b200.baseline.kge_torch import known_triple_index
+    ds = K.KGDataset.planted_grid(seed=0)
+    assert ds.n_entities == 300 and ds.n_relations == 4 and ds.test[0].size == 104 and ds.train[0].size == 941
+    m = TorchKGE(ds.n_entities, ds.n_relations, 16, model, gamma=6.0, lr=0.1, seed=0)
+    known = known_triple_index(ds.train, ds.test)
+    test = tuple(torch.from_numpy(x) for x in ds.test)
+    before = m.evaluate_full(*test, known)["MRR"]
+    train = tuple(torch.from_numpy(x) for x in ds.train)
+    g = torch.Generator().manual_seed(1)
+    for step in range(1500):
+        b = torch.randint(0, train[0].numel(), (128,), generator=g)
+        neg = torch.randint(0, ds.n_entities, (128,), generator=g)
+        m.train_step(train[0][b], train[1][b], train[2][b], neg, 32, step % 2 == 1)
+    after = m.evaluate_full(*test, known)
+    assert before < 0.06 and after["MRR"] > floor and after["HITS@10"] > 0.8, (before, after)
