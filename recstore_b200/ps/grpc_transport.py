@@ -21,6 +21,11 @@ its client cuts a request into sub-requests of ``MAX_PARAMETER_BATCH`` keys issu
 * the standard health-check service ``/grpc.health.v1.Health/Check`` (the reference enables gRPC's default one,
   grpc_ps_server.cpp:131): SERVING while the shard answers, for the service names "" and "xmhps.ParameterService".
 
+* server reflection ``/grpc.reflection.v1alpha.ServerReflection/ServerReflectionInfo`` (and the same under ``v1``), which
+  the reference switches on beside the health service (grpc_ps_server.cpp:131-146): ``list_services``,
+  ``file_containing_symbol`` and ``file_by_filename`` answer with the descriptor written here, so generic tools can
+  list the service and call it without a ``.proto`` file.
+
 ``GrpcParameterClient`` has the API of ``ps.client.ParameterClient`` and can be handed to
 ``AllShardsParameterClient``.
 """
@@ -70,14 +75,74 @@ def _build_messages():
     msg("CommandResponse", [("reply", 1, T.TYPE_STRING, opt, "")])
     msg("PutParameterRequest", [("parameter_value", 2, T.TYPE_BYTES, opt, "")])
     msg("PutParameterResponse", [("sucess", 1, T.TYPE_BOOL, opt, "")])
+    svc = f.service.add()
+    svc.name = "ParameterService"
+    for name, req, resp in (("GetParameter", "GetParameterRequest", "GetParameterResponse"),
+                            ("Command", "CommandRequest", "CommandResponse"),
+                            ("PutParameter", "PutParameterRequest", "PutParameterResponse"),
+                            ("UpdateParameter", "PutParameterRequest", "PutParameterResponse")):
+        m = svc.method.add()
+        m.name, m.input_type, m.output_type = name, ".xmhps." + req, ".xmhps." + resp
     pool = descriptor_pool.DescriptorPool()
     pool.Add(f)
-    return {n: message_factory.GetMessageClass(pool.FindMessageTypeByName("xmhps." + n))
-            for n in ("GetParameterRequest", "GetParameterResponse", "CommandRequest", "CommandResponse",
-                      "PutParameterRequest", "PutParameterResponse")}
+    out = {n: message_factory.GetMessageClass(pool.FindMessageTypeByName("xmhps." + n))
+           for n in ("GetParameterRequest", "GetParameterResponse", "CommandRequest", "CommandResponse",
+                     "PutParameterRequest", "PutParameterResponse")}
+    out["__file__"] = f
+    return out
+
+
+def _build_reflection_messages():
+    """grpc.reflection.v1alpha (reflection.proto): the request / response pair of ServerReflectionInfo and their parts."""
+    f = descriptor_pb2.FileDescriptorProto()
+    f.name = "recstore_b200/reflection.proto"
+    f.package = "grpc.reflection.v1alpha"
+    f.syntax = "proto3"
+    T = descriptor_pb2.FieldDescriptorProto
+    opt, rep = T.LABEL_OPTIONAL, T.LABEL_REPEATED
+    P = ".grpc.reflection.v1alpha."
+
+    def msg(name, fields, oneof=None):
+        m = f.message_type.add()
+        m.name = name
+        if oneof:
+            m.oneof_decl.add().name = oneof
+        for fname, num, ftype, label, tname, in_oneof in fields:
+            fd = m.field.add()
+            fd.name, fd.number, fd.type, fd.label = fname, num, ftype, label
+            if tname:
+                fd.type_name = tname
+            if in_oneof:
+                fd.oneof_index = 0
+    msg("ExtensionRequest", [("containing_type", 1, T.TYPE_STRING, opt, "", False), ("extension_number", 2, T.TYPE_INT32, opt, "", False)])
+    msg("ServerReflectionRequest", [("host", 1, T.TYPE_STRING, opt, "", False),
+                                    ("file_by_filename", 3, T.TYPE_STRING, opt, "", True),
+                                    ("file_containing_symbol", 4, T.TYPE_STRING, opt, "", True),
+                                    ("file_containing_extension", 5, T.TYPE_MESSAGE, opt, P + "ExtensionRequest", True),
+                                    ("all_extension_numbers_of_type", 6, T.TYPE_STRING, opt, "", True),
+                                    ("list_services", 7, T.TYPE_STRING, opt, "", True)], oneof="message_request")
+    msg("FileDescriptorResponse", [("file_descriptor_proto", 1, T.TYPE_BYTES, rep, "", False)])
+    msg("ExtensionNumberResponse", [("base_type_name", 1, T.TYPE_STRING, opt, "", False), ("extension_number", 2, T.TYPE_INT32, rep, "", False)])
+    msg("ServiceResponse", [("name", 1, T.TYPE_STRING, opt, "", False)])
+    msg("ListServiceResponse", [("service", 1, T.TYPE_MESSAGE, rep, P + "ServiceResponse", False)])
+    msg("ErrorResponse", [("error_code", 1, T.TYPE_INT32, opt, "", False), ("error_message", 2, T.TYPE_STRING, opt, "", False)])
+    msg("ServerReflectionResponse", [("valid_host", 1, T.TYPE_STRING, opt, "", False),
+                                     ("original_request", 2, T.TYPE_MESSAGE, opt, P + "ServerReflectionRequest", False),
+                                     ("file_descriptor_response", 4, T.TYPE_MESSAGE, opt, P + "FileDescriptorResponse", True),
+                                     ("all_extension_numbers_response", 5, T.TYPE_MESSAGE, opt, P + "ExtensionNumberResponse", True),
+                                     ("list_services_response", 6, T.TYPE_MESSAGE, opt, P + "ListServiceResponse", True),
+                                     ("error_response", 7, T.TYPE_MESSAGE, opt, P + "ErrorResponse", True)], oneof="message_response")
+    pool = descriptor_pool.DescriptorPool()
+    pool.Add(f)
+    return {n: message_factory.GetMessageClass(pool.FindMessageTypeByName("grpc.reflection.v1alpha." + n))
+            for n in ("ServerReflectionRequest", "ServerReflectionResponse")}
 
 
 _M = _build_messages()
+_PS_FILE = _M.pop("__file__")
+_R = _build_reflection_messages()
+ServerReflectionRequest, ServerReflectionResponse = _R["ServerReflectionRequest"], _R["ServerReflectionResponse"]
+REFLECTION_SERVICES = ("grpc.reflection.v1alpha.ServerReflection", "grpc.reflection.v1.ServerReflection")
 GetParameterRequest, GetParameterResponse = _M["GetParameterRequest"], _M["GetParameterResponse"]
 CommandRequest, CommandResponse = _M["CommandRequest"], _M["CommandResponse"]
 PutParameterRequest, PutParameterResponse = _M["PutParameterRequest"], _M["PutParameterResponse"]
@@ -101,8 +166,12 @@ class GrpcParameterServer:
             "Command": un(self._command, CommandRequest.FromString, CommandResponse.SerializeToString),
         }
         health = {"Check": un(self._health, lambda b: b, lambda b: b)}
-        self._server.add_generic_rpc_handlers((grpc.method_handlers_generic_handler(SERVICE, handlers),
-                                               grpc.method_handlers_generic_handler("grpc.health.v1.Health", health)))
+        reflect = {"ServerReflectionInfo": grpc.stream_stream_rpc_method_handler(
+            self._reflect, ServerReflectionRequest.FromString, ServerReflectionResponse.SerializeToString)}
+        self._server.add_generic_rpc_handlers(
+            (grpc.method_handlers_generic_handler(SERVICE, handlers),
+             grpc.method_handlers_generic_handler("grpc.health.v1.Health", health))
+            + tuple(grpc.method_handlers_generic_handler(name, reflect) for name in REFLECTION_SERVICES))
         self.port = self._server.add_insecure_port(f"{host}:{int(port)}")
         if self.port == 0:
             raise OSError(f"cannot bind {host}:{port}")
@@ -124,6 +193,31 @@ class GrpcParameterServer:
             return b"\x08\x01"                # SERVING
         except Exception:
             return b"\x08\x02"                # NOT_SERVING
+
+    def _reflect(self, requests, ctx):
+        """One answer per request of the stream.  Symbols of the parameter service resolve to the descriptor this module
+        built; the health and reflection services are listed but carry no descriptor here."""
+        symbols = {SERVICE} | {f"xmhps.{m.name}" for m in _PS_FILE.message_type} | {f"xmhps.{e.name}" for e in _PS_FILE.enum_type} \
+            | {f"{SERVICE}.{m.name}" for m in _PS_FILE.service[0].method}
+        for req in requests:
+            rep = ServerReflectionResponse(valid_host=req.host, original_request=req)
+            which = req.WhichOneof("message_request")
+            if which == "list_services":
+                for name in (SERVICE, "grpc.health.v1.Health") + REFLECTION_SERVICES:
+                    rep.list_services_response.service.add().name = name
+            elif which == "file_containing_symbol" and req.file_containing_symbol in symbols:
+                rep.file_descriptor_response.file_descriptor_proto.append(_PS_FILE.SerializeToString())
+            elif which == "file_by_filename" and req.file_by_filename == _PS_FILE.name:
+                rep.file_descriptor_response.file_descriptor_proto.append(_PS_FILE.SerializeToString())
+            elif which == "all_extension_numbers_of_type" and req.all_extension_numbers_of_type in symbols:
+                rep.all_extension_numbers_response.base_type_name = req.all_extension_numbers_of_type     # proto3: none
+            elif which is None:
+                rep.error_response.error_code = grpc.StatusCode.INVALID_ARGUMENT.value[0]
+                rep.error_response.error_message = "empty reflection request"
+            else:
+                rep.error_response.error_code = grpc.StatusCode.NOT_FOUND.value[0]
+                rep.error_response.error_message = f"{which}: not known to this server"
+            yield rep
 
     def _get(self, req, ctx):
         raw = req.keys
@@ -296,6 +390,17 @@ class GrpcParameterClient:
         req = (b"\x0a" + bytes([len(service)]) + service.encode()) if service else b""
         rep = self._channel.unary_unary("/grpc.health.v1.Health/Check")(req, timeout=self.timeout_s)
         return rep == b"\x08\x01"
+
+    def Reflect(self, **request) -> "ServerReflectionResponse":
+        """One server-reflection exchange, e.g. ``Reflect(list_services="")`` or
+        ``Reflect(file_containing_symbol="xmhps.ParameterService")``."""
+        call = self._channel.stream_stream(f"/{REFLECTION_SERVICES[0]}/ServerReflectionInfo",
+                                           request_serializer=ServerReflectionRequest.SerializeToString,
+                                           response_deserializer=ServerReflectionResponse.FromString)
+        return next(iter(call(iter([ServerReflectionRequest(**request)]), timeout=self.timeout_s)))
+
+    def ListServices(self) -> List[str]:
+        return [s.name for s in self.Reflect(list_services="").list_services_response.service]
 
     # asynchronous form (src/rdma_ps/base_client.h:6-47) -----------------------------------------
     def InitThread(self, n: int = 1) -> None:

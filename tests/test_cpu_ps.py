@@ -281,6 +281,23 @@ def test_grpc_transport_mirror_commands_and_wire_format(tmp_path):
     with pytest.raises(grpc.RpcError) as he:
         cli.HealthCheck("no.such.Service")
     assert he.value.code() == grpc.StatusCode.NOT_FOUND
+    # server reflection: the services are listed, the service's symbol resolves to a descriptor that names its methods
+    assert set(cli.ListServices()) >= {"xmhps.ParameterService", "grpc.health.v1.Health", "grpc.reflection.v1alpha.ServerReflection"}
+    from google.protobuf import descriptor_pb2
+    rep = cli.Reflect(file_containing_symbol="xmhps.ParameterService", host="h")
+    assert rep.valid_host == "h" and rep.original_request.file_containing_symbol == "xmhps.ParameterService"
+    fd = descriptor_pb2.FileDescriptorProto.FromString(rep.file_descriptor_response.file_descriptor_proto[0])
+    assert fd.package == "xmhps" and [m.name for m in fd.service[0].method] == ["GetParameter", "Command", "PutParameter", "UpdateParameter"]
+    assert {m.name for m in fd.message_type} >= {"GetParameterRequest", "PutParameterResponse"}
+    assert cli.Reflect(file_by_filename=fd.name).file_descriptor_response.file_descriptor_proto[0] == fd.SerializeToString()
+    assert cli.Reflect(file_containing_symbol="xmhps.GetParameterRequest").WhichOneof("message_response") == "file_descriptor_response"
+    miss = cli.Reflect(file_containing_symbol="no.such.Symbol")
+    assert miss.WhichOneof("message_response") == "error_response" and miss.error_response.error_code == grpc.StatusCode.NOT_FOUND.value[0]
+    assert cli.Reflect().error_response.error_code == grpc.StatusCode.INVALID_ARGUMENT.value[0]
+    v1 = cli._channel.stream_stream("/grpc.reflection.v1.ServerReflection/ServerReflectionInfo",
+                                    request_serializer=gt.ServerReflectionRequest.SerializeToString,
+                                    response_deserializer=gt.ServerReflectionResponse.FromString)
+    assert len(next(iter(v1(iter([gt.ServerReflectionRequest(list_services="")]), timeout=10))).list_services_response.service) == 4
     # the bytes on the wire: field 1 = raw little-endian u64 keys; the answer is one packed record block
     raw = cli._channel.unary_unary("/xmhps.ParameterService/GetParameter")(
         b"\x0a\x10" + struct.pack("<2Q", 7, 999999), timeout=10)
