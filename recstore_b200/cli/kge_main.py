@@ -105,6 +105,9 @@ def parse_args(argv=None):
     p.add_argument("--determinism_dir", default=os.environ.get("RECSTORE_DETERMINISM_DIR"),
                    help="record the sampled batches of the first --determinism_steps steps there; later runs must reproduce them")
     p.add_argument("--determinism_steps", type=int, default=20)
+    p.add_argument("--heartbeat_timeout", type=float, default=0.0,
+                   help="seconds without a sign of life after which a worker counts as lost (0: no liveness check); the "
+                        "others then stop before their next step instead of waiting inside a collective")
     a = p.parse_args(argv)
     if a.pairwise:
         p.error("--pairwise is closed in the reference (its loss generator asserts) and is not offered here")
@@ -189,6 +192,11 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
         if args.device == "cuda":
             torch.cuda.set_device(rank)
         dist.init_process_group("nccl" if args.device == "cuda" else "gloo", rank=rank, world_size=W)
+    hb = None
+    if W > 1 and args.heartbeat_timeout > 0:
+        from recstore_b200.utils.liveness import Heartbeat
+        hb = Heartbeat(rank, W, name=f"kge_heartbeat_{port}", period_s=min(0.2, args.heartbeat_timeout / 5)).start()
+        hb.wait_all_alive(max(60.0, args.heartbeat_timeout))
     mine = tuple(x[parts[rank]] for x in ds.train)
     w_mine = ds.train_weight[parts[rank]] if (args.has_edge_importance and ds.train_weight is not None) else None
     smp = ChunkedNegativeSampler(mine, ds.n_entities, args.batch_size, args.neg_sample_size, args.neg_chunk_size,
@@ -250,6 +258,8 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
     recorder = RunRecorder(args.determinism_dir)
     for step in range(args.max_step):
         h, r, t, n, ch = next(smp)
+        if hb is not None:
+            hb.check(args.heartbeat_timeout)
         if step < args.determinism_steps:
             recorder.diff_presampling(h, r, t, n, rank, step, ch)
         losses.append(step_fn(h, r, t, n, ch))
@@ -296,6 +306,12 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
     if W > 1 or native:
         import torch.distributed as dist
         dist.barrier()
+        if hb is not None:
+            hb.stop(leaving=True)            # only now: a worker that finishes early keeps beating until all are done
+            dist.barrier()
+            if rank == 0:
+                from recstore_b200.ipc import IPCTensorFactory
+                IPCTensorFactory.Delete(hb.name)
         dist.destroy_process_group()
 
 

@@ -188,6 +188,9 @@ def routine(rank: int, args, port: int, ns: str, out=None):
         print("Successfully xmh", flush=True)
     if out is not None:
         out[rank] = (steps_done, worst, last_loss)
+    dist.barrier()                       # nobody opens a shared object by name after this point
+    if rank == 0:
+        ipc.IPCTensorFactory.ClearIPCMemory()        # the run's shared-memory objects do not outlive it
     dist.destroy_process_group()
 
 

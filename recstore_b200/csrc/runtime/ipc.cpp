@@ -62,6 +62,19 @@ std::string obj_name(const char* name) {
 }
 std::string prefix() { return "rsb200." + std::to_string(getuid()) + "." + g_namespace + "."; }
 
+// An attaching process can open an object between its creator's shm_open and ftruncate: the file then still has size
+// zero, mapping it fails, and touching a mapping beyond its end would raise SIGBUS.  So whoever attaches first waits
+// (bounded) until the file has reached the size that every object of this kind has at least.
+bool wait_for_size(int fd, size_t min_bytes, struct stat* st, int timeout_ms = 5000) {
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  while (true) {
+    if (fstat(fd, st) != 0) return false;
+    if (static_cast<size_t>(st->st_size) >= min_bytes) return true;
+    if (std::chrono::steady_clock::now() > deadline) return false;
+    std::this_thread::sleep_for(std::chrono::microseconds(200));
+  }
+}
+
 struct BarrierState {
   uint64_t magic;
   int32_t parties;
@@ -95,7 +108,10 @@ RS_API int rs_shm_create(const char* name, int dtype, int ndim, const long long*
     return rs::set_error(RS_ERR_CAPACITY, "cannot size shared tensor %s to %zu bytes (is /dev/shm large enough?)", name, bytes);
   }
   struct stat st;
-  fstat(fd, &st);
+  if (!wait_for_size(fd, kHeaderBytes, &st)) {
+    close(fd);
+    return rs::set_error(RS_ERR_STATE, "shared object %s never reached the size of a tensor header (creator gone, or a foreign object)", name);
+  }
   void* base = mmap(nullptr, static_cast<size_t>(st.st_size), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
   close(fd);
   if (base == MAP_FAILED) return rs::set_error(RS_ERR_IO, "mmap of %s failed", path.c_str());
@@ -129,15 +145,14 @@ RS_API int rs_shm_open(const char* name, void** out_handle) {
   int fd = shm_open(path.c_str(), O_RDWR, 0600);
   if (fd < 0) return rs::set_error(RS_ERR_NOTFOUND, "no shared tensor named %s", name);
   struct stat st;
-  fstat(fd, &st);
+  if (!wait_for_size(fd, kHeaderBytes, &st, 1000)) {      // smaller than a header for a second: not one of ours
+    close(fd);
+    return rs::set_error(RS_ERR_STATE, "shared object %s is not a recstore tensor", name);
+  }
   void* base = mmap(nullptr, static_cast<size_t>(st.st_size), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
   close(fd);
   if (base == MAP_FAILED) return rs::set_error(RS_ERR_IO, "mmap of %s failed", path.c_str());
   ShmHeader* h = static_cast<ShmHeader*>(base);
-  if (static_cast<size_t>(st.st_size) < kHeaderBytes) {
-    munmap(base, static_cast<size_t>(st.st_size));
-    return rs::set_error(RS_ERR_STATE, "shared object %s is not a recstore tensor", name);
-  }
   for (int spin = 0; h->ready.load(std::memory_order_acquire) == 0 && spin < 100000; ++spin) std::this_thread::yield();
   // the header is trusted by every reader afterwards: a foreign or damaged object must not describe more than is mapped
   const bool sane = h->magic == kMagic && h->ndim >= 0 && h->ndim <= 8 &&
@@ -234,6 +249,11 @@ RS_API int rs_barrier_create(const char* name, int parties, void** out_handle) {
   if (made && ftruncate(fd, 4096) != 0) {
     close(fd);
     return rs::set_error(RS_ERR_IO, "ftruncate(%s) failed", path.c_str());
+  }
+  struct stat bst;
+  if (!made && !wait_for_size(fd, 4096, &bst)) {
+    close(fd);
+    return rs::set_error(RS_ERR_STATE, "barrier %s was never sized by its creator", name);
   }
   void* base = mmap(nullptr, 4096, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
   close(fd);

@@ -409,6 +409,10 @@ class DLRM:
         self._done = [torch.cuda.Event() for _ in range(2)]
         self._graphs: Dict[object, torch.cuda.CUDAGraph] = {}
         self._step_no = 0
+        # Optional liveness check before every launch (utils/liveness.Heartbeat): set both to have `submit` raise
+        # RankLostError when another rank has died or left, instead of launching a step whose peers never answer.
+        self.heartbeat = None
+        self.heartbeat_timeout_s = 2.0
         self.launches_per_step = 0
         # Pipelined lookup: supported where the forward exchange is the one lookup kernel (dot interaction, no row-sharded
         # tables).  `_pending` is the submitted step whose graph has not been launched yet (its lookup has been).
@@ -834,6 +838,8 @@ class DLRM:
         """Enqueues H2D copies of ``batch`` and one training step; returns immediately.  With ``pipeline_lookup`` the
         step itself is launched when the NEXT batch is submitted (its graph ends with that batch's lookup) or when its
         result is asked for; the lookup of this batch is launched now."""
+        if self.heartbeat is not None:       # a peer that is gone must be noticed here, on the host, not inside a peer wait
+            self.heartbeat.check(self.heartbeat_timeout_s)
         slot = self._step_no & 1
         step = self._step_no
         self._step_no += 1

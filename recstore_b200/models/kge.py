@@ -139,6 +139,8 @@ class KGEModel:
         self.neg_score = torch.empty(self.bs, self.ns, **f)
         self.ids = torch.empty(n_ids, dtype=torch.int64, device=dev)
         self.step_no = 0
+        self.heartbeat = None                # utils/liveness.Heartbeat: checked on the host before every step when set
+        self.heartbeat_timeout_s = 2.0
         self.launches_per_step = 0
         self._graphs: Dict[bool, torch.cuda.CUDAGraph] = {}
         self._g_ids = (torch.zeros(self.bs, dtype=torch.int64, device=dev), torch.zeros(self.bs, dtype=torch.int64, device=dev),
@@ -223,6 +225,8 @@ class KGEModel:
         """One step on device id tensors (``neg_ids``: ``[batch / chunk * neg_sample_size]`` entity ids); returns the
         loss as a 0-d device tensor (no host synchronisation).  With ``use_cuda_graph`` the ids are copied into fixed
         buffers and the captured launch sequence of that corruption side is replayed."""
+        if self.heartbeat is not None:
+            self.heartbeat.check(self.heartbeat_timeout_s)
         if corrupt_head is None:
             corrupt_head = bool(self.step_no & 1)            # head / tail corruption alternate
         self.step_no += 1

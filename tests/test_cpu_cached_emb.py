@@ -73,6 +73,9 @@ def _worker(rank, world, port, ns, cache_type, mode, q):
         ctrl.GraceFullyStopThreads()
         dist.barrier()
         q.put((rank, worst))
+        dist.barrier()
+        if rank == 0:
+            ipc.IPCTensorFactory.ClearIPCMemory()          # leave nothing in shared memory
     finally:
         dist.destroy_process_group()
 

@@ -647,6 +647,7 @@ def test_custom_external_embedding_over_a_shared_table(tmp_path):
     t.update()
     assert torch.allclose(t.cached_emb.weight.detach()[2], before[2] - 0.5 * 2, atol=1e-6)
     assert torch.allclose(t.cached_emb.weight.detach()[3], before[3] - 0.5, atol=1e-6)
+    ipc.IPCTensorFactory.ClearIPCMemory()                    # leave nothing in shared memory
 
 
 @pytest.mark.parametrize("model,floor", [("RotatE", 0.6), ("ComplEx", 0.5)])
