@@ -30,16 +30,22 @@ def make_client(host, port, dim, transport="tcp"):
     return ParameterClient(host, port, 0, dim)
 
 
-def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, seconds, dataset=None, quiet=False, transport="tcp"):
+def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, seconds, dataset=None, quiet=False, transport="tcp",
+                cut_off_period=0.0, cut_off_stride=2):
+    """``cut_off_period > 0``: the thread cut-off mode of the reference's client benchmark
+    (src/benchmark/benchmark_client_common.h:156-184): every period ``cut_off_stride`` sender threads are stopped, the
+    run ends when none is left (``seconds`` is ignored), and the result lists the throughput seen at every thread
+    count -- one run gives the whole load curve."""
     done = [0] * threads
     stop = threading.Event()
+    stop_one = [threading.Event() for _ in range(threads)]
 
     def worker(t):
         c = make_client(host, port, dim, transport)
         c.InitThread(window)
         src = iter(DatasetReplay(dataset)) if dataset else zipf_key_source(key_space, batch, alpha, seed=t + 1)
         inflight = []
-        while not stop.is_set():
+        while not stop.is_set() and not stop_one[t].is_set():
             while len(inflight) < window:
                 k = next(src)
                 inflight.append((c.GetParameterAsync(k), k.numel()))
@@ -57,6 +63,22 @@ def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, secon
         th.start()
     last, last_t = 0, t0
     per_sec = []
+    if cut_off_period > 0:
+        curve, alive = [], threads
+        while alive > 0:
+            a0, n0 = time.perf_counter(), sum(done)
+            time.sleep(cut_off_period)
+            rate = (sum(done) - n0) / (time.perf_counter() - a0)
+            curve.append({"threads": alive, "keys_per_s": rate})
+            if not quiet:
+                print(f"[ps_client] {alive:3d} threads {rate / 1e6:8.3f} M keys/s", flush=True)
+            for _ in range(min(cut_off_stride, alive)):
+                alive -= 1
+                stop_one[alive].set()
+                ths[alive].join()
+        el = time.perf_counter() - t0
+        return {"mode": "closed_cut_off", "threads": threads, "window": window, "batch": batch, "keys_per_s": sum(done) / el,
+                "by_threads": curve, "seconds": el}
     while time.perf_counter() - t0 < seconds:
         time.sleep(min(1.0, max(0.05, seconds - (time.perf_counter() - t0))))
         now, tot = time.perf_counter(), sum(done)
@@ -112,6 +134,9 @@ def main(argv=None):
     ap.add_argument("--engine", default="KVEngineMap")
     ap.add_argument("--processes", type=int, default=1, help="closed loop: load-generator processes, each with --threads senders")
     ap.add_argument("--transport", choices=["tcp", "grpc"], default="tcp", help="framed loopback sockets or gRPC (closed loop / poisson)")
+    ap.add_argument("--thread-cut-off", type=float, default=0.0, metavar="SECONDS",
+                    help="closed loop: stop --cut-off-stride sender threads every SECONDS and report the throughput per thread count")
+    ap.add_argument("--cut-off-stride", type=int, default=2)
     a = ap.parse_args(argv)
     srv = None
     host, port = a.host, a.port
@@ -134,7 +159,7 @@ def main(argv=None):
                                 transport=a.transport)
         else:
             out = closed_loop(host, port, a.dim, a.threads, a.window, a.batch, a.alpha, a.key_space, a.seconds, a.dataset,
-                              transport=a.transport)
+                              transport=a.transport, cut_off_period=a.thread_cut_off, cut_off_stride=a.cut_off_stride)
         out["transport"] = a.transport
         print(json.dumps(out), flush=True)
     finally:

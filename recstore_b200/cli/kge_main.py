@@ -105,6 +105,8 @@ def parse_args(argv=None):
     p.add_argument("--determinism_dir", default=os.environ.get("RECSTORE_DETERMINISM_DIR"),
                    help="record the sampled batches of the first --determinism_steps steps there; later runs must reproduce them")
     p.add_argument("--determinism_steps", type=int, default=20)
+    p.add_argument("--profile_dir", default=None,
+                   help="record three steps (after three warm-up steps) with torch.profiler: trace_rank{r}.json + ops_rank{r}.txt")
     p.add_argument("--heartbeat_timeout", type=float, default=0.0,
                    help="seconds without a sign of life after which a worker counts as lost (0: no liveness check); the "
                         "others then stop before their next step instead of waiting inside a collective")
@@ -256,6 +258,8 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
     valid_log = []
     from recstore_b200.utils.determinism import RunRecorder
     recorder = RunRecorder(args.determinism_dir)
+    from recstore_b200.utils.profiling import StepProfiler
+    prof = StepProfiler(args.profile_dir, rank)
     for step in range(args.max_step):
         h, r, t, n, ch = next(smp)
         if hb is not None:
@@ -263,6 +267,7 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
         if step < args.determinism_steps:
             recorder.diff_presampling(h, r, t, n, rank, step, ch)
         losses.append(step_fn(h, r, t, n, ch))
+        prof.step()
         if args.force_sync_interval > 0 and W > 1 and (step + 1) % args.force_sync_interval == 0:
             import torch.distributed as dist
             dist.barrier()                   # keeps the workers within one interval of each other (train_pytorch.py:292-294)
@@ -277,6 +282,7 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
             print(f"[{rank}] step {step + 1}: loss {np.mean(recent):.5f}, {(time.time() - t0) / (step + 1) * 1e3:.2f} ms/step", flush=True)
     if not native and args.async_update:
         model.finish_async_update()          # train_pytorch.py:338-339
+    prof.finish()
     if args.device == "cuda":
         torch.cuda.synchronize()
     el = time.time() - t0

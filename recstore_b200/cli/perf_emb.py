@@ -29,6 +29,8 @@ def parse_args(argv=None):
     p.add_argument("--emb_dim", type=int, default=32)
     p.add_argument("--L", type=int, default=10)
     p.add_argument("--with_perf", action="store_true")
+    p.add_argument("--profile_dir", default=None,
+                   help="record three steps (after three warm-up steps) with torch.profiler and write trace_rank{r}.json + ops_rank{r}.txt there")
     p.add_argument("--batch_size", type=int, default=5000)
     p.add_argument("--cache_ratio", type=float, default=0.1)
     p.add_argument("--log_interval", type=int, default=50)
@@ -107,6 +109,8 @@ def routine(rank: int, args, port: int, ns: str, out=None):
     for s, ids in enumerate(future):
         publish(s, ids)
     t_step = Timer("OneStep")
+    from recstore_b200.utils.profiling import StepProfiler
+    prof = StepProfiler(args.profile_dir, rank)
     t0 = time.time()
     worst = 0.0
     steps_done = 0
@@ -130,6 +134,7 @@ def routine(rank: int, args, port: int, ns: str, out=None):
                     (ref.sum() * (rank + 1)).backward()
                     gopt.step()
             abs_emb.after_backward()
+        prof.step()
         steps_done += 1
         if rank == 0 and (step + 1) % args.log_interval == 0:
             el = time.time() - t0
@@ -141,6 +146,7 @@ def routine(rank: int, args, port: int, ns: str, out=None):
         dist.all_reduce(stop)
         if int(stop.item()) > 0:
             break
+    prof.finish()
     ctrl.GraceFullyStopThreads()
     dist.barrier()
     if rank == 0:

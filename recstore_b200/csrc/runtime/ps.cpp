@@ -299,7 +299,47 @@ class PsServer {
     acceptor_ = std::thread([this] { AcceptLoop(); });
     return RS_OK;
   }
+  // Once per period: requests, keys and reply payload served since the last line, to stderr (only while there is
+  // traffic) and into `out` for callers that want the last reading.  The reference's asynchronous server prints its
+  // MB/s once a second from such a thread (src/grpc_ps/grpc_ps_server_async.cpp:109-117).
+  void StartMonitor(int period_ms, bool print) {
+    std::lock_guard<std::mutex> lk(mon_mu_);
+    if (monitor_.joinable()) return;
+    mon_stop_ = false;
+    monitor_ = std::thread([this, period_ms, print] {
+      uint64_t r0 = requests_.load(), k0 = keys_.load();
+      auto t0 = std::chrono::steady_clock::now();
+      std::unique_lock<std::mutex> lk(mon_mu_);
+      while (!mon_stop_) {
+        if (mon_cv_.wait_for(lk, std::chrono::milliseconds(period_ms), [this] { return mon_stop_; })) break;
+        const uint64_t r1 = requests_.load(), k1 = keys_.load();
+        const auto t1 = std::chrono::steady_clock::now();
+        const double sec = std::chrono::duration<double>(t1 - t0).count();
+        const double kreq = (r1 - r0) / sec / 1e3, mkeys = (k1 - k0) / sec / 1e6;
+        const double mbs = (k1 - k0) * (12.0 + 4.0 * ps_->dim()) / sec / 1e6;       // record bytes per served key
+        mon_last_[0] = kreq; mon_last_[1] = mkeys; mon_last_[2] = mbs;
+        mon_lines_.fetch_add(1, std::memory_order_relaxed);
+        if (print && r1 != r0) fprintf(stderr, "PS throughput: %.3f Kreq/s %.3f Mkeys/s %.1f MB/s\n", kreq, mkeys, mbs);
+        r0 = r1; k0 = k1; t0 = t1;
+      }
+    });
+  }
+  void StopMonitor() {
+    {
+      std::lock_guard<std::mutex> lk(mon_mu_);
+      mon_stop_ = true;
+    }
+    mon_cv_.notify_all();
+    if (monitor_.joinable()) monitor_.join();
+  }
+  // out[0..2] = Kreq/s, Mkeys/s, MB/s of the last period; returns how many periods have been measured.
+  uint64_t MonitorLast(double* out) {
+    std::lock_guard<std::mutex> lk(mon_mu_);
+    for (int i = 0; i < 3; ++i) out[i] = mon_last_[i];
+    return mon_lines_.load();
+  }
   void Stop() {
+    StopMonitor();
     if (!running_.exchange(false)) return;
     ::shutdown(lfd_, SHUT_RDWR);
     ::close(lfd_);
@@ -508,6 +548,12 @@ class PsServer {
   std::vector<int> conns_;
   std::vector<std::thread> workers_, pool_;
   std::atomic<uint64_t> requests_{0}, keys_{0}, pooled_{0};
+  std::mutex mon_mu_;
+  std::condition_variable mon_cv_;
+  std::thread monitor_;
+  bool mon_stop_ = false;
+  double mon_last_[3] = {0, 0, 0};
+  std::atomic<uint64_t> mon_lines_{0};
 };
 
 class PsClient {
@@ -687,6 +733,17 @@ RS_API int rs_ps_server_start_pool(void* ps, int port, int workers, const char* 
   )
 }
 RS_API int rs_ps_server_stop(void* server) { delete static_cast<PsServer*>(server); return RS_OK; }
+RS_API int rs_ps_server_monitor_start(void* server, int period_ms, int print) {
+  RS_REQUIRE(server && period_ms > 0, "rs_ps_server_monitor_start: bad argument");
+  RS_NOEXCEPT_BODY(static_cast<PsServer*>(server)->StartMonitor(period_ms, print != 0); return RS_OK;)
+}
+RS_API int rs_ps_server_monitor_stop(void* server) {
+  static_cast<PsServer*>(server)->StopMonitor();
+  return RS_OK;
+}
+RS_API unsigned long long rs_ps_server_monitor_last(void* server, double* out3) {
+  return static_cast<PsServer*>(server)->MonitorLast(out3);
+}
 
 RS_API int rs_ps_client_connect(const char* host, int port, void** out) {
   RS_REQUIRE(host && out, "rs_ps_client_connect: null argument");

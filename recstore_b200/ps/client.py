@@ -47,6 +47,9 @@ _lib.register_signatures({
     "rs_ps_server_start": (i32, [vp, i32, C.POINTER(vp), C.POINTER(i32)]),
     "rs_ps_server_start_pool": (i32, [vp, i32, i32, cstr, i32, C.POINTER(vp), C.POINTER(i32)]),
     "rs_ps_server_stop": (i32, [vp]),
+    "rs_ps_server_monitor_start": (i32, [vp, i32, i32]),
+    "rs_ps_server_monitor_stop": (i32, [vp]),
+    "rs_ps_server_monitor_last": (u64, [vp, C.POINTER(C.c_double)]),
     "rs_ps_client_connect": (i32, [cstr, i32, C.POINTER(vp)]),
     "rs_ps_client_close": (i32, [vp]),
     "rs_ps_client_get": (i32, [vp, vp, i64, i32, vp, vp, i32]),
@@ -219,6 +222,23 @@ class ParameterServer:
             _lib.call("rs_ps_server_start", self._h, int(port), C.byref(s), C.byref(p))
         self._server, self.port = s.value, p.value
         return self.port
+
+    def start_monitor(self, period_s: float = 1.0, print_lines: bool = True) -> None:
+        """A server thread measures requests, keys and payload served per period and (``print_lines``) writes
+        ``PS throughput: ... Kreq/s ... Mkeys/s ... MB/s`` to stderr while there is traffic (the once-a-second line of
+        the reference's asynchronous server, src/grpc_ps/grpc_ps_server_async.cpp:109-117)."""
+        assert self._server, "serve() first"
+        _lib.call("rs_ps_server_monitor_start", self._server, max(1, int(period_s * 1000)), int(print_lines))
+
+    def stop_monitor(self) -> None:
+        if self._server:
+            self._l.rs_ps_server_monitor_stop(self._server)
+
+    def monitor_last(self) -> dict:
+        """The last period's reading: ``{"periods", "kreq_per_s", "mkeys_per_s", "mb_per_s"}``."""
+        out = (C.c_double * 3)()
+        n = int(self._l.rs_ps_server_monitor_last(self._server, out))
+        return {"periods": n, "kreq_per_s": out[0], "mkeys_per_s": out[1], "mb_per_s": out[2]}
 
     def stop(self) -> None:
         if self._server:

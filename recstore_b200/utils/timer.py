@@ -61,6 +61,19 @@ class Timer:
 
     start, stop = Start, End
 
+    # Cumulative form: several separate intervals add up to ONE sample (e.g. the pieces of a phase that is interleaved
+    # with others inside a step): CumStart / CumEnd around every piece, CumReport once per step
+    # (src/base/timer.h:426-450).
+    def CumStart(self):
+        self._t0 = self._l.rs_now_ns()
+
+    def CumEnd(self):
+        self._cum = getattr(self, "_cum", 0) + (self._l.rs_now_ns() - self._t0)
+
+    def CumReport(self):
+        self._l.rs_series_record(self._h, float(getattr(self, "_cum", 0)))
+        self._cum = 0
+
     def __enter__(self):
         self.Start()
         return self

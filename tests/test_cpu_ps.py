@@ -446,3 +446,48 @@ def test_grpc_server_survives_random_request_bytes():
     got = cli.GetParameter(torch.arange(100, 110))
     assert got.shape == (10, D)
     srv.stop(0)
+
+
+def test_server_throughput_monitor_reports_traffic_per_period(capfd):
+    """The server's monitor thread (role of the MB/s line of src/grpc_ps/grpc_ps_server_async.cpp:109-117)."""
+    import time
+    from recstore_b200.ps import ParameterClient, ParameterServer
+    D = 8
+    srv = ParameterServer("KVEngineMap", {"dim": D, "capacity": 10000})
+    port = srv.serve(0)
+    srv.start_monitor(0.1)
+    srv.start_monitor(0.1)                                   # a second start is a no-op
+    cli = ParameterClient("127.0.0.1", port, 0, D)
+    cli.LoadFakeData(5000)
+    t0, best = time.time(), 0.0
+    while time.time() - t0 < 0.6:
+        cli.GetParameter(torch.arange(2000))
+        best = max(best, srv.monitor_last()["mkeys_per_s"])
+    m = srv.monitor_last()
+    assert m["periods"] >= 3 and best > 0.01 and m["mb_per_s"] == pytest.approx(m["mkeys_per_s"] * (12 + 4 * D), rel=1e-6)
+    time.sleep(0.35)                                          # idle periods read zero and print nothing
+    assert srv.monitor_last()["mkeys_per_s"] == 0.0
+    srv.stop_monitor()
+    n = srv.monitor_last()["periods"]
+    time.sleep(0.25)
+    assert srv.monitor_last()["periods"] == n
+    cli.close()
+    srv.close()                                               # closing with or without a running monitor is fine
+    err = capfd.readouterr().err
+    lines = [l for l in err.splitlines() if l.startswith("PS throughput:")]
+    assert 2 <= len(lines) <= 9 and "Mkeys/s" in lines[0] and "MB/s" in lines[0]
+
+
+def test_client_benchmark_thread_cut_off_reports_every_thread_count():
+    """One run, the whole load curve: sender threads are stopped a few at a time
+    (src/benchmark/benchmark_client_common.h:156-184 `thread_cut_off`)."""
+    from recstore_b200.bench.ps_client import closed_loop
+    from recstore_b200.ps import ParameterServer
+    srv = ParameterServer("KVEngineMap", {"dim": 8, "capacity": 20000})
+    srv.LoadFakeData(10000)
+    port = srv.serve(0)
+    out = closed_loop("127.0.0.1", port, 8, threads=5, window=2, batch=100, alpha=0.9, key_space=10000, seconds=999, quiet=True,
+                      cut_off_period=0.15, cut_off_stride=2)
+    assert out["mode"] == "closed_cut_off" and [c["threads"] for c in out["by_threads"]] == [5, 3, 1]
+    assert all(c["keys_per_s"] > 0 for c in out["by_threads"]) and out["seconds"] < 5
+    srv.close()
