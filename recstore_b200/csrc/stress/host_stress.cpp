@@ -41,6 +41,8 @@ int rs_ps_create(const char* engine, const char* json, void** out);
 int rs_ps_destroy(void* ps);
 int rs_ps_server_start(void* ps, int port, void** server_out, int* port_out);
 int rs_ps_server_stop(void* server);
+int rs_ps_server_monitor_start(void* server, int period_ms, int print);
+unsigned long long rs_ps_server_monitor_last(void* server, double* out3);
 int rs_ps_client_connect(const char* host, int port, void** out);
 int rs_ps_client_close(void* c);
 int rs_ps_client_get(void* c, const unsigned long long* keys, long long n, int dim, float* out, unsigned char* found, int max_per_req);
@@ -162,6 +164,7 @@ void stress_ps() {
   int port = 0;
   if (rs_ps_create("KVEngineMap", "{\"capacity\": 65536, \"dim\": 8}", &ps) != 0) { fail("rs_ps_create"); return; }
   if (rs_ps_server_start(ps, 0, &server, &port) != 0) { fail("rs_ps_server_start"); rs_ps_destroy(ps); return; }
+  EXPECT_OK(rs_ps_server_monitor_start(server, 5, 0));        // the monitor reads the counters the connection threads bump
   std::vector<std::thread> ts;
   for (int c = 0; c < kClients; ++c) {
     ts.emplace_back([&, c] {
@@ -191,7 +194,9 @@ void stress_ps() {
     });
   }
   for (auto& t : ts) t.join();
-  EXPECT_OK(rs_ps_server_stop(server));
+  double mon[3];
+  if (rs_ps_server_monitor_last(server, mon) == 0) fail("the throughput monitor never measured a period");
+  EXPECT_OK(rs_ps_server_stop(server));                        // stops the monitor too
   EXPECT_OK(rs_ps_destroy(ps));
   std::printf("host_stress: ps %d clients x %d rounds\n", kClients, kRounds);
 }
