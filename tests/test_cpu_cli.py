@@ -223,3 +223,75 @@ def test_cumulative_timer_adds_pieces_into_one_sample():
         t.CumReport()
     s = stats("cum.phase")
     assert s["count"] == 3 and 15e6 < s["mean"] < 80e6       # one sample per step, ~20 ms each (in ns)
+
+
+def test_checkpoint_loader_refuses_torn_damaged_and_misfitting_saves(tmp_path):
+    """A save interrupted half way (files of two steps), a truncated or bit-flipped file, a file that is not tensors,
+    and a model of another shape are all refused with a message, and the model is left as it was."""
+    import os
+    import shutil
+    import torch
+    from recstore_b200.baseline.dlrm_torch import TorchDLRM
+    from recstore_b200.models.checkpoint import load_checkpoint, save_checkpoint
+    from recstore_b200.utils.data import DLRMBatchSource
+    rows = [30, 200, 17]
+    kw = dict(emb_dim=8, bottom_mlp=(16, 8), top_mlp=(16, 1), num_dense=4, seed=1)
+    m = TorchDLRM(rows, 32, **kw)
+    src = DLRMBatchSource(rows, [1, 1, 1], 32, num_dense=4, seed=2)
+    step = lambda: (lambda b: m.train_step(b.dense, b.ids, b.labels))(src.next())
+    step()
+    old, new = str(tmp_path / "old"), str(tmp_path / "new")
+    save_checkpoint(m, old, step=1)
+    step()
+    save_checkpoint(m, new, step=2)
+    fresh = lambda: TorchDLRM(rows, 32, **dict(kw, seed=7))
+    assert load_checkpoint(fresh(), new)["step"] == 2 and not (tmp_path / "new" / ".meta.json.tmp").exists()
+    # torn: the save of step 2 was interrupted after table 1 -- meta.json and the rest are still those of step 1
+    torn = str(tmp_path / "torn")
+    shutil.copytree(old, torn)
+    shutil.copy(tmp_path / "new" / "table_1.pt", tmp_path / "torn" / "table_1.pt")
+    victim = fresh()
+    before = [victim.table_weight(t).clone() for t in range(3)] + [v.clone() for v in victim.dense_state().values()]
+    with pytest.raises(ValueError, match="torn checkpoint"):
+        load_checkpoint(victim, torn)
+    after = [victim.table_weight(t) for t in range(3)] + list(victim.dense_state().values())
+    assert all(torch.equal(a, b) for a, b in zip(before, after))            # nothing was restored half way
+    # damaged files
+    for name, damage in (("table_0.pt", lambda b: b[: len(b) // 2]), ("dense.pt", lambda b: b[:100] + bytes([b[100] ^ 0xFF]) + b[101:len(b) // 3]),
+                         ("table_2.pt", lambda b: b"this is not a tensor file")):
+        d = tmp_path / ("bad_" + name)
+        shutil.copytree(new, d)
+        (d / name).write_bytes(damage((d / name).read_bytes()))
+        with pytest.raises(ValueError, match="damaged|not a tensor"):
+            load_checkpoint(fresh(), str(d))
+    # pickled code is not executed: a file that would run something on load is refused
+    import pickle
+
+    class Boom:
+        def __reduce__(self):
+            return (os.system, ("true",))
+    d = tmp_path / "evil"
+    shutil.copytree(new, d)
+    with open(d / "table_0.pt", "wb") as f:
+        pickle.dump({"weight": Boom()}, f)
+    with pytest.raises(ValueError):
+        load_checkpoint(fresh(), str(d))
+    # a model of another shape
+    with pytest.raises(ValueError):
+        load_checkpoint(TorchDLRM([30, 200, 18], 32, **kw), new)
+    with pytest.raises(ValueError, match="dense.pt does not fit|written for"):
+        load_checkpoint(TorchDLRM(rows, 32, **dict(kw, top_mlp=(32, 1))), new)
+    d = tmp_path / "short_table"
+    shutil.copytree(new, d)
+    t = torch.load(d / "table_1.pt")
+    torch.save({"weight": t["weight"][:100], "state": t["state"][:100], "save_step": t["save_step"]}, d / "table_1.pt")
+    with pytest.raises(ValueError, match="table 1 holds"):
+        load_checkpoint(fresh(), str(d))
+    # a checkpoint of the older layout (no step stamps in the files) still loads
+    d = tmp_path / "v1"
+    shutil.copytree(new, d)
+    for f in ("table_0.pt", "table_1.pt", "table_2.pt"):
+        t = torch.load(d / f)
+        t.pop("save_step")
+        torch.save(t, d / f)
+    assert load_checkpoint(fresh(), str(d))["step"] == 2
