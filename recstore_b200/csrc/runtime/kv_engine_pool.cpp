@@ -8,8 +8,10 @@
 // superseded records.  The reference keeps values in its PersistMemoryPool and defers frees through its epoch manager
 // the same way in the persistent hash engines (src/memory/persist_malloc.h:126-420, src/memory/epoch_manager.h).
 #include <atomic>
+#include <chrono>
 #include <cstring>
 #include <shared_mutex>
+#include <thread>
 #include <unordered_map>
 
 #include <sys/stat.h>
@@ -68,12 +70,19 @@ class KVEnginePoolMap final : public BaseKV {
   }
   bool Put(uint64_t key, const void* value) override {
     uint64_t off = AllocRecord();
-    if (!off) {
+    // An empty pool usually means that superseded records are waiting for a reader that was descheduled inside its
+    // protected region, not that the engine is full: advance the epoch, collect, and give such readers a moment (bounded)
+    // before refusing the write.
+    for (int attempt = 0; !off && attempt < 400; ++attempt) {
       epoch_.Bump();
       epoch_.Collect();
       off = AllocRecord();
-      if (!off) return false;
+      if (!off) {
+        if (epoch_.Pending() == 0) break;              // nothing left to wait for: the pool really is exhausted
+        std::this_thread::sleep_for(std::chrono::microseconds(attempt < 20 ? 50 : 500));
+      }
     }
+    if (!off) return false;
     Record* r = rec(off);
     r->key = key;
     r->version = version_.fetch_add(1, std::memory_order_relaxed);

@@ -441,10 +441,13 @@ def test_pool_map_engine_concurrent_readers_never_see_torn_or_freed_values(tmp_p
     def writer(seed):
         g = torch.Generator().manual_seed(seed)
         v = 1
-        while not stop.is_set():
-            ks = torch.randint(0, 2000, (256,), generator=g)
-            kv.BatchPut(ks, torch.full((256, 64), float(seed * 100000 + v)))
-            v += 1
+        try:
+            while not stop.is_set():
+                ks = torch.randint(0, 2000, (256,), generator=g)
+                kv.BatchPut(ks, torch.full((256, 64), float(seed * 100000 + v)))
+                v += 1
+        except Exception as e:                              # a refused write (engine "full" of unreclaimed records) is a failure
+            bad.append((seed, repr(e)))
 
     def reader(seed):
         g = torch.Generator().manual_seed(100 + seed)
@@ -463,6 +466,7 @@ def test_pool_map_engine_concurrent_readers_never_see_torn_or_freed_values(tmp_p
     for t in ts:
         t.join()
     assert not bad, bad
+    kv.Flush()                                              # what still waited for a reader's epoch is reclaimed now
     info = kv.DebugInfo()
     slabs = int(info.split("slabs=")[1].split()[0])
     assert len(kv) == 2000 and 2000 <= slabs <= 2000 + 4096 // 4 + 64 + 300, info     # old versions were reclaimed
