@@ -73,7 +73,7 @@ class KVEnginePoolMap final : public BaseKV {
     // An empty pool usually means that superseded records are waiting for a reader that was descheduled inside its
     // protected region, not that the engine is full: advance the epoch, collect, and give such readers a moment (bounded)
     // before refusing the write.
-    for (int attempt = 0; !off && attempt < 400; ++attempt) {
+    for (int attempt = 0; !off && attempt < 4000; ++attempt) {     // up to ~2 s
       epoch_.Bump();
       epoch_.Collect();
       off = AllocRecord();

@@ -385,8 +385,8 @@ void EpochManager::Retire(std::function<void()> reclaim) {
     collect = (++st.retired & 63) == 0;
   }
   if (collect) {
-    Bump();
-    CollectStripe(st, MinProtected());
+    const uint64_t g = Bump();
+    CollectStripe(st, std::min(MinProtected(), g));
   }
 }
 
@@ -408,8 +408,13 @@ size_t EpochManager::CollectStripe(Stripe& st, uint64_t safe_below) {
   return run.size();
 }
 
+// The scan of the readers' slots says nothing about an object that is retired AFTER the scan: a reader may publish its
+// epoch, find the object and start copying it between the scan and the retirement.  Objects retired after the bump
+// below carry an epoch >= g, so the bound min(oldest reader, g) leaves them for a later pass; everything retired
+// before the bump is judged by a scan that came after its retirement.
 size_t EpochManager::Collect() {
-  const uint64_t safe_below = MinProtected();
+  const uint64_t g = Bump();
+  const uint64_t safe_below = std::min(MinProtected(), g);
   size_t n = 0;
   for (int i = 0; i < kStripes; ++i) n += CollectStripe(stripes_[i], safe_below);
   return n;

@@ -106,7 +106,8 @@ class EpochManager {
   uint64_t MinProtected() const;
   // Hands over an unlinked object; `reclaim` runs (on some later caller's thread) once it is safe.
   void Retire(std::function<void()> reclaim);
-  // Runs the callbacks that have become safe; returns how many ran.  Retire calls it every few dozen items.
+  // Advances the epoch, then runs the callbacks of everything retired before that whose readers have all left; returns
+  // how many ran.  Retire does the same for its own stripe every few dozen items.
   size_t Collect();
   // Runs everything regardless of epochs (shutdown, no readers left).
   size_t DrainAll();
