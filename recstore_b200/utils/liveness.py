@@ -85,7 +85,10 @@ class Heartbeat:
 
             def run():
                 while not self._stop.wait(self.period_s):
-                    self.beat()
+                    try:
+                        self.beat()
+                    except Exception:            # the carrier is gone (the rank that hosted the store has exited):
+                        return                   # nothing left to tell anybody
             self._thread = threading.Thread(target=run, name=f"heartbeat-{self.rank}", daemon=True)
             self._thread.start()
         return self
