@@ -27,6 +27,8 @@
 #include <thread>
 #include <vector>
 
+#include <unistd.h>
+
 extern "C" {
 int rs_kv_create(const char* engine, const char* json_config, void** out);
 int rs_kv_destroy(void* h);
@@ -253,7 +255,7 @@ void stress_timers_and_barrier() {
   rs_timers_clear();
   EXPECT_OK(rs_report_thread_start(5));
   char ns[64];
-  std::snprintf(ns, sizeof(ns), "rs_stress_%d", static_cast<int>(std::rand()));
+  std::snprintf(ns, sizeof(ns), "rs_stress_%d", static_cast<int>(getpid()));       // several drivers may run at once
   EXPECT_OK(rs_shm_set_namespace(ns));
   std::vector<void*> handles(kThreads, nullptr);
   for (int t = 0; t < kThreads; ++t) EXPECT_OK(rs_barrier_create("stress_barrier", kThreads, &handles[t]));
