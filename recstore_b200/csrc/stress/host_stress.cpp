@@ -159,6 +159,53 @@ void stress_kv(const char* engine, const char* json) {
   EXPECT_OK(rs_kv_destroy(kv));
 }
 
+// Writers replace the values of a small key set out of place as fast as they can while readers copy them: in a tight
+// pool every superseded record is recycled within microseconds, so a reader that were handed a record too early would
+// copy a mix of two versions (and ThreadSanitizer would see the two memcpy collide).
+void stress_shared_keys(const char* engine, const char* json, int kDim) {
+  constexpr int kKeys = 64, kWriters = 2, kReaders = 3;
+  void* kv = nullptr;
+  if (rs_kv_create(engine, json, &kv) != 0) { fail("rs_kv_create", engine); return; }
+  const std::vector<float> zero(kDim, 0.f);
+  for (int k = 0; k < kKeys; ++k) EXPECT_OK(rs_kv_put(kv, 1000 + k, zero.data()));
+  std::atomic<bool> stop{false};
+  std::atomic<int> torn{0}, missing{0}, refused{0};
+  std::atomic<unsigned long long> reads{0}, writes{0};
+  std::vector<std::thread> ts;
+  for (int w = 0; w < kWriters; ++w)
+    ts.emplace_back([&, w] {
+      Lcg rng(50 + w);
+      std::vector<float> val(kDim);
+      unsigned version = 1;
+      while (!stop.load(std::memory_order_relaxed)) {
+        for (int d = 0; d < kDim; ++d) val[d] = static_cast<float>(w * 1000000 + version);
+        ++version;
+        if (rs_kv_put(kv, 1000 + rng.next() % kKeys, val.data()) != 0) refused.fetch_add(1);
+        writes.fetch_add(1, std::memory_order_relaxed);
+      }
+    });
+  for (int r = 0; r < kReaders; ++r)
+    ts.emplace_back([&, r] {
+      Lcg rng(70 + r);
+      std::vector<float> got(kDim);
+      while (!stop.load(std::memory_order_relaxed)) {
+        int found = 0;
+        if (rs_kv_get(kv, 1000 + rng.next() % kKeys, got.data(), &found) != 0 || !found) { missing.fetch_add(1); continue; }
+        for (int d = 1; d < kDim; ++d)
+          if (got[d] != got[0]) { torn.fetch_add(1); break; }
+        reads.fetch_add(1, std::memory_order_relaxed);
+      }
+    });
+  std::this_thread::sleep_for(std::chrono::milliseconds(400));
+  stop.store(true);
+  for (auto& t : ts) t.join();
+  if (torn.load()) fail("a reader copied a mix of two versions", std::string(engine) + ": " + std::to_string(torn.load()));
+  if (missing.load()) fail("a key that is only ever replaced was reported absent", engine);
+  if (refused.load()) fail("a replacement was refused although the key set never grows", engine);
+  std::printf("host_stress: kv %-12s shared keys: %llu reads, %llu writes\n", engine, reads.load(), writes.load());
+  EXPECT_OK(rs_kv_destroy(kv));
+}
+
 void stress_ps() {
   constexpr int kDim = 8, kClients = 4, kRounds = 60, kKeys = 48;
   void* ps = nullptr;
@@ -417,6 +464,11 @@ int main(int argc, char** argv) {
     stress_kv("KVEngineExtendibleHash", "{\"capacity\": 65536, \"value_size\": 32}");
     stress_kv("KVEngineChunkHash", "{\"capacity\": 65536, \"value_size\": 32}");
     stress_kv("KVEnginePoolMap", "{\"capacity\": 65536, \"value_size\": 32}");
+    for (const char* e : {"KVEngineMap", "KVEngineExtendibleHash", "KVEngineChunkHash", "KVEnginePoolMap"})
+      stress_shared_keys(e, "{\"capacity\": 256, \"value_size\": 32}", 8);
+    // 4 KB values: the pool map's pool holds a few hundred records, so writers run it dry every few milliseconds and
+    // reclamation (epoch bump, scan of the readers, collection) runs all the time beside the readers
+    stress_shared_keys("KVEnginePoolMap", "{\"capacity\": 128, \"value_size\": 4096}", 1024);
   }
   if (only == "all" || only == "ps") stress_ps();
   if (only == "all" || only == "alloc") {
