@@ -97,3 +97,23 @@ def all2all_sparse_tensor(keys_per_dst: Sequence[torch.Tensor], values_per_dst: 
     ks = all2all_data_transfer(keys_per_dst, group)
     vs = all2all_data_transfer(values_per_dst, group)
     return sum_sparse_tensor(ks, vs)
+
+
+@torch.no_grad()
+def kv_to_sparse_tensor(keys: torch.Tensor, values: torch.Tensor, shape) -> torch.Tensor:
+    """(row ids ``[n]``, rows ``[n, D]``) as a sparse COO matrix of ``shape`` (duplicates stay uncoalesced)."""
+    idx = keys if keys.dim() == 2 else keys.unsqueeze(0)
+    return torch.sparse_coo_tensor(idx, values, size=tuple(shape), check_invariants=True)
+
+
+def reduce_sparse_tensor(sparse_tensor: torch.Tensor, dst: int = 0, group=None) -> Optional[torch.Tensor]:
+    """Sum of every rank's sparse COO matrix (row-sparse: one index row, values ``[nnz, D]``) on ``dst`` as one
+    coalesced sparse matrix; ``None`` elsewhere (src/python/pytorch/recstore/utils.py:352-380)."""
+    rank, _ = _world(group)
+    st = sparse_tensor if sparse_tensor.is_coalesced() else sparse_tensor.coalesce()
+    keys, values = st.indices(), st.values()
+    assert keys.shape[0] == 1 and values.dim() == 2, "row-sparse matrices only: indices [1, nnz], values [nnz, D]"
+    uniq, rows = reduce_sparse_kv_tensor(keys[0].contiguous(), values.contiguous(), dst, group)
+    if rank != dst:
+        return None
+    return torch.sparse_coo_tensor(uniq.unsqueeze(0), rows, size=tuple(st.shape), check_invariants=True).coalesce()

@@ -295,3 +295,35 @@ def test_checkpoint_loader_refuses_torn_damaged_and_misfitting_saves(tmp_path):
         t.pop("save_step")
         torch.save(t, d / f)
     assert load_checkpoint(fresh(), str(d))["step"] == 2
+
+
+def test_sparse_reduce_helpers_and_rank_logging(capsys):
+    """kv_to_sparse_tensor / reduce_sparse_tensor on one rank (the multi-rank gather is covered by the cached-embedding
+    tests), and the logging helpers (src/python/pytorch/recstore/utils.py:183-219, 352-402)."""
+    import logging
+    import torch
+    from recstore_b200.utils import comm
+    from recstore_b200.utils.log import XLOG, cdebug, get_logger, print_rank0
+    keys, vals = torch.tensor([5, 2, 5]), torch.tensor([[1.0, 1.0], [2.0, 2.0], [3.0, 3.0]])
+    st = comm.kv_to_sparse_tensor(keys, vals, (8, 2))
+    assert st.shape == (8, 2) and not st.is_coalesced()
+    red = comm.reduce_sparse_tensor(st)
+    assert red.is_coalesced() and red.indices().tolist() == [[2, 5]] and red.values().tolist() == [[2.0, 2.0], [4.0, 4.0]]
+    assert torch.equal(red.to_dense()[5], torch.tensor([4.0, 4.0]))
+    lg = get_logger()
+    lg.setLevel(logging.DEBUG)
+    records = []
+    h = logging.Handler()
+    h.emit = records.append
+    lg.addHandler(h)
+    try:
+        cdebug("hello")
+        XLOG.cdebug("again", colour=False)
+        XLOG.info("plain")
+    finally:
+        lg.removeHandler(h)
+        lg.setLevel(logging.INFO)
+    assert [r.getMessage() for r in records] == ["\033[31mhello\033[0m", "again", "plain"]
+    assert records[0].filename == "test_cpu_cli.py" and records[0].levelno == logging.DEBUG      # the caller's file, not log.py
+    print_rank0("only once")
+    assert capsys.readouterr().out == "only once\n"
