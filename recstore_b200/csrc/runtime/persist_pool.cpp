@@ -582,6 +582,9 @@ RS_API int rs_epoch_retire_slab(void* h, void* pool, unsigned long long off) {
     return RS_OK;
   )
 }
+// Runs every pending callback whatever its epoch (the owner of the retired objects is about to go away and no reader
+// is left); returns how many ran.
+RS_API long long rs_epoch_drain(void* h) { return static_cast<long long>(static_cast<EpochManager*>(h)->DrainAll()); }
 RS_API long long rs_epoch_collect(void* h) { return static_cast<long long>(static_cast<EpochManager*>(h)->Collect()); }
 RS_API long long rs_epoch_pending(void* h) { return static_cast<long long>(static_cast<EpochManager*>(h)->Pending()); }
 

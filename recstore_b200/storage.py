@@ -168,6 +168,7 @@ _lib.register_signatures({
     "rs_epoch_safe": (i32, [vp, u64]),
     "rs_epoch_retire_slab": (i32, [vp, vp, u64]),
     "rs_epoch_collect": (i64, [vp]),
+    "rs_epoch_drain": (i64, [vp]),
     "rs_epoch_pending": (i64, [vp]),
     "rs_recycler_new": (i32, [vp, i32, u64, vp, C.c_uint, C.POINTER(vp)]),
     "rs_recycler_delete": (i32, [vp]),
@@ -191,7 +192,21 @@ class PersistSlabPool:
         self._h = h.value
         self.recovered = bool(rec.value)
 
+    def _depends_on_me(self, obj) -> None:
+        """Recyclers and epoch managers hold slabs of this pool that they will free later: they are settled before the
+        mapping goes away."""
+        import weakref
+        if not hasattr(self, "_dependents"):
+            self._dependents = []
+        if not any(r() is obj for r in self._dependents):
+            self._dependents.append(weakref.ref(obj))
+
     def close(self):
+        for ref in getattr(self, "_dependents", []):
+            dep = ref()
+            if dep is not None and getattr(dep, "_h", None):
+                dep._settle()
+        self._dependents = []
         if getattr(self, "_h", None):
             self._l.rs_ppool_close(self._h)
             self._h = None
@@ -248,6 +263,11 @@ class EpochManager:
         self._h = h.value
 
     def close(self):
+        for ref in getattr(self, "_recyclers", []):          # recyclers with the epoch policy consult this manager
+            rec = ref()
+            if rec is not None and getattr(rec, "_h", None):
+                rec.close()
+        self._recyclers = []
         if getattr(self, "_h", None):
             self._l.rs_epoch_delete(self._h)
             self._h = None
@@ -277,7 +297,14 @@ class EpochManager:
         return bool(self._l.rs_epoch_safe(self._h, int(epoch)))
 
     def retire_slab(self, pool: PersistSlabPool, off: int) -> None:
+        pool._depends_on_me(self)
         _lib.call("rs_epoch_retire_slab", self._h, pool._h, int(off))
+
+    def drain(self) -> int:
+        """Frees everything that waits, whatever its epoch: for shutdown, when no reader is left."""
+        return int(self._l.rs_epoch_drain(self._h))
+
+    _settle = drain
 
     def collect(self) -> int:
         return int(self._l.rs_epoch_collect(self._h))
@@ -303,6 +330,12 @@ class SlabRecycler:
         _lib.call("rs_recycler_new", pool._h, self.POLICIES[policy], int(delay_s * 1e9),
                   epochs._h if epochs is not None else None, int(bump_every), C.byref(h))
         self._h = h.value
+        pool._depends_on_me(self)
+        if epochs is not None:
+            import weakref
+            if not hasattr(epochs, "_recyclers"):
+                epochs._recyclers = []
+            epochs._recyclers.append(weakref.ref(self))
 
     def close(self) -> None:
         if getattr(self, "_h", None):
@@ -317,6 +350,8 @@ class SlabRecycler:
 
     def clear(self) -> int:
         return int(self._l.rs_recycler_clear(self._h))
+
+    _settle = close
 
     def pending(self) -> int:
         return int(self._l.rs_recycler_pending(self._h))

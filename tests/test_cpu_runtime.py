@@ -667,3 +667,31 @@ def test_index_ring_coarse_clock_and_core_binding():
     assert isinstance(n0, list) and all(isinstance(c, int) for c in n0)
     with pytest.raises(Exception):
         bind_core(1 << 20)
+
+
+def test_closing_a_pool_or_an_epoch_manager_first_settles_what_depends_on_it():
+    """Shutdown in any order: a pool that closes first has its recyclers closed and its epoch managers drained (their
+    pending frees would otherwise touch an unmapped pool); an epoch manager that closes first closes the recyclers that
+    consult it."""
+    from recstore_b200.storage import EpochManager, PersistSlabPool, SlabRecycler
+    P, E = PersistSlabPool(None, 16 * 65536, chunk_bytes=65536), EpochManager()
+    R1 = SlabRecycler(P, "delayed", delay_s=60.0)
+    R2 = SlabRecycler(P, "epoch", epochs=E)
+    offs = [P.malloc(64) for _ in range(6)]
+    R1.recycle(offs[0]); R1.recycle(offs[1])
+    E.protect()
+    R2.recycle(offs[2]); R2.recycle(offs[3])
+    E.retire_slab(P, offs[4]); E.retire_slab(P, offs[5])
+    E.unprotect()
+    assert R1.pending() == 2 and R2.pending() == 2 and E.pending() == 2
+    P.close()                                               # recyclers closed, manager drained, then the pool unmapped
+    assert R1._h is None and R2._h is None and E.pending() == 0
+    assert E.collect() == 0                                 # nothing left that could touch the pool
+    R1.close(); R2.close()                                  # closing again is harmless
+    P2 = PersistSlabPool(None, 16 * 65536, chunk_bytes=65536)
+    R3 = SlabRecycler(P2, "epoch", epochs=E)
+    o = P2.malloc(64)
+    E.protect(); R3.recycle(o); E.unprotect()
+    E.close()                                               # the manager goes first: its recycler is closed (and frees o)
+    assert R3._h is None and P2.slab_size(o) == 0
+    P2.close()
