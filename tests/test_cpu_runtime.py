@@ -695,3 +695,49 @@ def test_closing_a_pool_or_an_epoch_manager_first_settles_what_depends_on_it():
     E.close()                                               # the manager goes first: its recycler is closed (and frees o)
     assert R3._h is None and P2.slab_size(o) == 0
     P2.close()
+
+
+def test_symmetric_allocator_is_deterministic_reuses_and_merges():
+    """The offset allocator of the peer heap: same calls, same layout (that is what lets every rank run it alone);
+    freed blocks are reused lowest-address first and merge with free neighbours."""
+    import random
+    from recstore_b200.parallel.peer import SymmetricAllocator
+    a = SymmetricAllocator(10 * 256 + 100)                  # rounded down to whole alignment units
+    assert a.nbytes == 2560 and a.largest_free == 2560
+    x, y, z = a.alloc(1), a.alloc(512), a.alloc(300)
+    assert (x, y, z) == (0, 256, 768) and a.bytes_in_use == 256 + 512 + 512
+    assert a.alloc(4096) is None and a.alloc(1281) is None and a.bytes_in_use == 1280
+    a.free(y)
+    assert a.alloc(600) == 1280                             # 600 -> 768 bytes: too big for the 512-byte hole, placed in the tail
+    a2 = SymmetricAllocator(2560)
+    for n in (1, 512, 300):
+        a2.alloc(n)
+    a2.free(256)
+    assert a2.alloc(512) == 256                             # exact hole reused
+    a2.free(0); a2.free(256)
+    assert (0, 768, "free") in a2.layout()                  # neighbours merged into one block
+    a2.free(768)
+    assert a2.layout() == [(0, 2560, "free")] and a2.bytes_in_use == 0
+    with pytest.raises(ValueError):
+        a2.free(768)
+    # two "ranks" replay one random script: identical offsets throughout, no overlap, everything inside the heap
+    script, rng, live = [], random.Random(5), []
+    for i in range(2000):
+        if live and rng.random() < 0.45:
+            script.append(("free", live.pop(rng.randrange(len(live)))))
+        else:
+            script.append(("alloc", rng.randrange(1, 40000)))
+            live.append(len(script) - 1)
+    def replay():
+        h, got, out = SymmetricAllocator(1 << 20), {}, []
+        for i, (op, v) in enumerate(script):
+            if op == "alloc":
+                got[i] = h.alloc(v)
+                out.append(got[i])
+            elif got.get(v) is not None:
+                h.free(got.pop(v))
+            used = sorted((o, s) for o, s, k in h.layout() if k == "used")
+            assert all(o1 + s1 <= o2 for (o1, s1), (o2, _) in zip(used, used[1:])) and (not used or used[-1][0] + used[-1][1] <= 1 << 20)
+        return out
+    r0, r1 = replay(), replay()
+    assert r0 == r1 and sum(o is not None for o in r0) > 500

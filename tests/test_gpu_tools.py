@@ -101,3 +101,40 @@ def test_device_id_generators_match_the_host_formula():
     # popularity: P(rank 0) = (2^-0.3 - 1) / ((N + 1)^-0.3 - 1) = 0.1885 for this N
     top = (a == 0).float().mean().item()
     assert 0.17 < top < 0.21
+
+
+def test_peer_context_symmetric_heap_slices_reuse_and_fallback():
+    """Windows carved out of one pre-exchanged heap: addresses follow from the heap's base, freed bytes are reused,
+    a request that does not fit gets a window of its own, and tearing down frees only what owns memory."""
+    from recstore_b200.parallel.peer import PeerContext
+    ctx = PeerContext(0, 1, heap_bytes=1 << 20)
+    heap = ctx.windows["__heap__"]
+    a = ctx.alloc("a", 1000)                                # rounded to 1024
+    b = ctx.alloc("b", 4096)
+    assert a.heap_offset == 0 and b.heap_offset == 1024 and a.ptrs[0] == heap.ptrs[0] and b.ptrs[0] == heap.ptrs[0] + 1024
+    assert int(b.table[0].item()) == b.local_ptr
+    a.view(torch.float32, (256,)).fill_(3.0)
+    b.view(torch.int32, (1024,)).copy_(torch.arange(1024, dtype=torch.int32, device="cuda:0"))
+    raw = heap.view(torch.float32, (256,))
+    assert torch.equal(raw, torch.full((256,), 3.0, device="cuda:0"))              # the slice IS heap memory
+    assert torch.equal(b.peer_view(0, torch.int32, (1024,)).cpu(), torch.arange(1024, dtype=torch.int32))
+    st = ctx.heap_stats()
+    assert st["in_use"] == 1024 + 4096 and st["windows_in_heap"] == 2
+    ctx.free("a")
+    c = ctx.alloc("c", 512)
+    assert c.heap_offset == 0 and "a" not in ctx.windows                           # the freed bytes are reused
+    big = ctx.alloc("big", 2 << 20)                                                # larger than the heap: its own window
+    assert big.heap_offset is None and big.nbytes == 2 << 20
+    big.view(torch.uint8, (16,)).fill_(7)
+    ctx.free("big")
+    with pytest.raises(ValueError):
+        ctx.free("__heap__")
+    with pytest.raises(KeyError):
+        ctx.free("a")
+    ctx.free_all()
+    assert ctx.windows == {}
+    plain = PeerContext(0, 1)                                                      # without a heap nothing changes
+    w = plain.alloc("w", 4096)
+    assert w.heap_offset is None and plain.heap_stats()["heap_bytes"] == 0
+    plain.free("w")
+    plain.free_all()
