@@ -59,12 +59,68 @@ class KGDataset:
         cut = lambda a, b: tuple(np.ascontiguousarray(trip[a:b, i]) for i in range(3))
         return KGDataset("planted_grid", width * height, len(shifts), cut(n_test, len(trip)), None, cut(0, n_test))
 
+    BUILT_IN = ("FB15k", "FB15k-237", "wn18", "wn18rr", "wikikg2", "biokg", "Freebase")
+
+    @staticmethod
+    def load_built_in(data_path: str, name: str, delimiter: str = "\t") -> "KGDataset":
+        """The directory layouts of the reference's named datasets (``--format built_in``; KGDataset.py:186-470), read
+        from ``data_path/name``; nothing is downloaded.  FB15k, FB15k-237, wn18, wn18rr, wikikg2, biokg:
+        ``entities.dict`` / ``relations.dict`` (``id<TAB>name``) and ``train.txt`` / ``valid.txt`` / ``test.txt`` with
+        ``head<TAB>relation<TAB>tail`` names.  Freebase: ``entity2id.txt`` / ``relation2id.txt`` whose first line is
+        the count, and triple files of integer ids in the order ``head<TAB>tail<TAB>relation``."""
+        if name not in KGDataset.BUILT_IN:
+            raise ValueError(f"unknown built-in dataset {name!r}; known: {', '.join(KGDataset.BUILT_IN)}")
+        d = os.path.join(data_path, name)
+        if not os.path.isdir(d):
+            raise FileNotFoundError(f"{d} does not exist: put the extracted dataset there (this build downloads nothing)")
+
+        def triples(fn, parse):
+            path = os.path.join(d, fn)
+            if not os.path.exists(path):
+                return None
+            hs, rs, ts = [], [], []
+            with open(path) as f:
+                for ln, line in enumerate(f):
+                    p = line.strip().split(delimiter)
+                    if len(p) < 3:
+                        if line.strip():
+                            raise ValueError(f"{path}:{ln + 1}: expected 3 columns")
+                        continue
+                    try:
+                        h, r, t = parse(p)
+                    except KeyError as e:
+                        raise ValueError(f"{path}:{ln + 1}: {e.args[0]!r} is not in the dictionaries") from None
+                    hs.append(h); rs.append(r); ts.append(t)
+            return (np.array(hs, dtype=np.int64), np.array(rs, dtype=np.int64), np.array(ts, dtype=np.int64))
+        if name == "Freebase":
+            with open(os.path.join(d, "entity2id.txt")) as f:
+                ne = int(f.readline())
+            with open(os.path.join(d, "relation2id.txt")) as f:
+                nr = int(f.readline())
+            e2i = r2i = None
+            parse = lambda p: (int(p[0]), int(p[2]), int(p[1]))
+        else:
+            e2i = _read_dict(os.path.join(d, "entities.dict"), delimiter)
+            r2i = _read_dict(os.path.join(d, "relations.dict"), delimiter)
+            ne, nr = len(e2i), len(r2i)
+            parse = lambda p: (e2i[p[0]], r2i[p[1]], e2i[p[2]])
+        train = triples("train.txt", parse)
+        if train is None:
+            raise FileNotFoundError(f"{d} has no train.txt")
+        valid, test = triples("valid.txt", parse), triples("test.txt", parse)
+        for sp in (train, valid, test):
+            if sp is not None and sp[0].size and (max(sp[0].max(), sp[2].max()) >= ne or sp[1].max() >= nr or min(sp[0].min(), sp[1].min(), sp[2].min()) < 0):
+                raise ValueError(f"{d}: a triple id lies outside the {ne} entities / {nr} relations")
+        return KGDataset(name, ne, nr, train, valid, test, e2i, r2i)
+
     @staticmethod
     def load(path: str, files: Sequence[str], fmt: str = "raw_udd_hrt", name: Optional[str] = None, delimiter: str = "\t",
              has_edge_importance: bool = False):
         """``files``: train [valid test] for ``raw_udd_*``; entities, relations, train [valid test] for ``udd_*``.
         With ``has_edge_importance`` the training file has a fourth column, the weight of the triple in the loss
         (KGDataset.py of the reference: ``has_importance``)."""
+        if fmt == "built_in":
+            return KGDataset.load_built_in(path, name or "FB15k", delimiter)
         raw = fmt.startswith("raw_udd_")
         order = fmt.split("_")[-1]
         assert sorted(order) == ["h", "r", "t"], f"bad format {fmt}"

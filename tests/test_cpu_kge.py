@@ -691,3 +691,44 @@ def test_dataset_files_to_kvstore_trainers_to_checkpoint_to_eval_tool_generalise
     res = kge_infer.main(["eval", "--model_path", str(tmp_path / "ck"), "--num_proc", "2"] + data, return_result=True)
     assert res["filtered"] and res["triples"] == 104 and res["model"] == "ComplEx"
     assert res["MRR"] > 0.4 and res["HITS@10"] > 0.7, res
+
+
+def test_built_in_dataset_layouts_from_fake_files(tmp_path):
+    """`--format built_in`: the directory layouts of the reference's named datasets, on hand-made files (its own tests
+    use fake data files the same way: dgl-ke/tests/fake_data)."""
+    d = tmp_path / "FB15k"
+    d.mkdir()
+    (d / "entities.dict").write_text("0\t/m/a\n1\t/m/b\n2\t/m/c\n")
+    (d / "relations.dict").write_text("0\tlikes\n1\tknows\n")
+    (d / "train.txt").write_text("/m/a\tlikes\t/m/b\n/m/b\tknows\t/m/c\n\n/m/c\tlikes\t/m/a\n")
+    (d / "valid.txt").write_text("/m/a\tknows\t/m/c\n")
+    ds = K.KGDataset.load_built_in(str(tmp_path), "FB15k")
+    assert (ds.name, ds.n_entities, ds.n_relations) == ("FB15k", 3, 2) and ds.test is None
+    assert [x.tolist() for x in ds.train] == [[0, 1, 2], [0, 1, 0], [1, 2, 0]] and [x.tolist() for x in ds.valid] == [[0], [1], [2]]
+    assert ds.entity2id["/m/c"] == 2
+    assert K.KGDataset.load(str(tmp_path), [], "built_in", name="FB15k").n_entities == 3      # through the general loader
+    f = tmp_path / "Freebase"
+    f.mkdir()
+    (f / "entity2id.txt").write_text("5\n")
+    (f / "relation2id.txt").write_text("3\n")
+    (f / "train.txt").write_text("0\t4\t2\n3\t1\t0\n")                    # head, tail, relation
+    (f / "test.txt").write_text("4\t0\t1\n")
+    fb = K.KGDataset.load_built_in(str(tmp_path), "Freebase")
+    assert (fb.n_entities, fb.n_relations) == (5, 3) and [x.tolist() for x in fb.train] == [[0, 3], [2, 0], [4, 1]]
+    assert [x.tolist() for x in fb.test] == [[4], [1], [0]] and fb.valid is None
+    (d / "test.txt").write_text("/m/a\tlikes\t/m/zzz\n")
+    with pytest.raises(ValueError, match="not in the dictionaries"):
+        K.KGDataset.load_built_in(str(tmp_path), "FB15k")
+    (f / "train.txt").write_text("0\t9\t2\n")
+    with pytest.raises(ValueError, match="outside"):
+        K.KGDataset.load_built_in(str(tmp_path), "Freebase")
+    with pytest.raises(FileNotFoundError, match="downloads nothing"):
+        K.KGDataset.load_built_in(str(tmp_path), "wn18")
+    with pytest.raises(ValueError, match="unknown built-in"):
+        K.KGDataset.load_built_in(str(tmp_path), "imagenet")
+    # the trainer's command line takes it
+    (d / "test.txt").write_text("/m/b\tlikes\t/m/c\n")
+    from recstore_b200.cli import kge_main
+    out, info = kge_main.main(["--dataset", "FB15k", "--data_path", str(tmp_path), "--format", "built_in", "--max_step", "4", "--hidden_dim", "8",
+                               "--batch_size", "2", "--neg_sample_size", "2", "--log_interval", "1000"])
+    assert info["n_entities"] == 3 and out[0]["steps"] == 4
