@@ -512,10 +512,10 @@ def test_slab_recyclers_direct_delayed_and_epoch():
     off = P.malloc(64)
     assert R.recycle(off) == 1 and P.slab_size(off) == 0 and R.pending() == 0 and R.recycle(0) == 0
 
-    R = SlabRecycler(P, "delayed", delay_s=0.2)
+    R = SlabRecycler(P, "delayed", delay_s=1.0)
     offs = [P.malloc(64) for _ in range(5)]
     assert sum(R.recycle(o) for o in offs) == 0 and R.pending() == 5 and all(P.slab_size(o) for o in offs)
-    time.sleep(0.3)
+    time.sleep(1.2)
     late = P.malloc(64)
     assert R.recycle(late) == 5 and R.pending() == 1          # the five are due, the new one waits
     assert all(P.slab_size(o) == 0 for o in offs) and P.slab_size(late) != 0
