@@ -277,6 +277,8 @@ def worker(rank: int, args, ds, parts, port: int, shared, out):
                 valid_log.append({"step": step + 1, **m})
                 if rank == 0:
                     print(f"[{rank}] valid @ {step + 1}: " + ", ".join(f"{k} {v:.4f}" for k, v in m.items()), flush=True)
+        if native and (step + 1) % args.log_interval == 0:
+            model.ctx.check_status()         # an id out of range or a peer wait that ran out must not train on silently
         if rank == 0 and (step + 1) % args.log_interval == 0:
             recent = [float(x) for x in losses[-args.log_interval:]]
             print(f"[{rank}] step {step + 1}: loss {np.mean(recent):.5f}, {(time.time() - t0) / (step + 1) * 1e3:.2f} ms/step", flush=True)

@@ -319,6 +319,7 @@ class KGEModel:
         return full[: tab.N].numpy()
 
     def save(self, path: str) -> None:
+        self.ctx.check_status()              # tables written after a device-side error would be a wrong checkpoint
         os.makedirs(path, exist_ok=True)
         ent = self._gather_table(self.entity)
         rel = self._gather_table(self.relation)
