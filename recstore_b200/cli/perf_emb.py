@@ -136,6 +136,8 @@ def routine(rank: int, args, port: int, ns: str, out=None):
             abs_emb.after_backward()
         prof.step()
         steps_done += 1
+        if (step + 1) % args.log_interval == 0 and getattr(abs_emb, "_ctx", None) is not None:
+            abs_emb._ctx.check_status()      # native exchange: a bounded wait that ran out or an id out of range raises here
         if rank == 0 and (step + 1) % args.log_interval == 0:
             el = time.time() - t0
             print(f"step {step + 1}: {el / (step + 1) * 1e3:.2f} ms/step, "
