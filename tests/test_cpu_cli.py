@@ -327,3 +327,16 @@ def test_sparse_reduce_helpers_and_rank_logging(capsys):
     assert records[0].filename == "test_cpu_cli.py" and records[0].levelno == logging.DEBUG      # the caller's file, not log.py
     print_rank0("only once")
     assert capsys.readouterr().out == "only once\n"
+
+
+def test_packaging_metadata_names_real_entry_points():
+    """pyproject.toml: every console script points at a callable that exists."""
+    import importlib
+    import os
+    import tomllib
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = tomllib.load(open(os.path.join(root, "pyproject.toml"), "rb"))
+    assert cfg["project"]["name"] == "recstore_b200" and len(cfg["project"]["scripts"]) >= 8
+    for name, target in cfg["project"]["scripts"].items():
+        mod, fn = target.split(":")
+        assert callable(getattr(importlib.import_module(mod), fn)), (name, target)
