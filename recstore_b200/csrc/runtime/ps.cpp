@@ -269,8 +269,9 @@ static bool send_frame(int fd, uint32_t op, const void* payload, uint64_t len) {
 // src/grpc_ps/grpc_ps_server_async.cpp:56-96, 246-318).  OP_PRIORITY raises the sender's class by one level.
 class PsServer {
  public:
-  PsServer(CachePS* ps, int port, int workers = 0, const std::string& scheduler = "fifo", int levels = 7)
-      : ps_(ps), port_(port), n_workers_(workers < 0 ? 0 : workers) {
+  PsServer(CachePS* ps, int port, int workers = 0, const std::string& scheduler = "fifo", int levels = 7,
+           const std::string& bind_host = "127.0.0.1")
+      : ps_(ps), port_(port), n_workers_(workers < 0 ? 0 : workers), bind_host_(bind_host == "localhost" ? "127.0.0.1" : bind_host) {
     if (n_workers_ > 0) {
       if (scheduler == "priority") provider_ = std::make_unique<PriorityProvider<Task>>(levels);
       else provider_ = std::make_unique<FifoProvider<Task>>();
@@ -284,12 +285,16 @@ class PsServer {
     setsockopt(lfd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
     sockaddr_in a{};
     a.sin_family = AF_INET;
-    a.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+    if (inet_pton(AF_INET, bind_host_.c_str(), &a.sin_addr) != 1) {      // loopback by default; "0.0.0.0" serves every interface
+      ::close(lfd_);
+      lfd_ = -1;
+      return set_error(RS_ERR_INVALID, "%s is not an IPv4 address to listen on", bind_host_.c_str());
+    }
     a.sin_port = htons(static_cast<uint16_t>(port_));
     if (::bind(lfd_, reinterpret_cast<sockaddr*>(&a), sizeof(a)) != 0 || ::listen(lfd_, 64) != 0) {
       ::close(lfd_);
       lfd_ = -1;
-      return set_error(RS_ERR_IO, "cannot listen on 127.0.0.1:%d", port_);
+      return set_error(RS_ERR_IO, "cannot listen on %s:%d", bind_host_.c_str(), port_);
     }
     socklen_t sl = sizeof(a);
     getsockname(lfd_, reinterpret_cast<sockaddr*>(&a), &sl);
@@ -541,6 +546,7 @@ class PsServer {
   CachePS* ps_;
   int port_, lfd_ = -1;
   const int n_workers_;
+  const std::string bind_host_;
   std::unique_ptr<TaskProvider<Task>> provider_;
   std::atomic<bool> running_{false};
   std::thread acceptor_;
@@ -725,6 +731,22 @@ RS_API int rs_ps_server_start_pool(void* ps, int port, int workers, const char* 
   RS_REQUIRE(sched == "fifo" || sched == "priority", "rs_ps_server_start_pool: scheduler must be fifo or priority");
   RS_NOEXCEPT_BODY(
     auto* s = new PsServer(static_cast<CachePS*>(ps), port, workers, sched, levels);
+    const int rc = s->Start();
+    if (rc != RS_OK) { delete s; return rc; }
+    *server_out = s;
+    if (port_out) *port_out = s->port();
+    return RS_OK;
+  )
+}
+// The general form: listens on `host` (an IPv4 address; the two entry points above listen on 127.0.0.1, the reference's
+// server on 0.0.0.0:15000, src/grpc_ps/grpc_ps_server.cpp:129); workers == 0 is the synchronous mode.
+RS_API int rs_ps_server_start_on(void* ps, const char* host, int port, int workers, const char* scheduler, int levels,
+                                 void** server_out, int* port_out) {
+  RS_REQUIRE(ps && server_out && host, "rs_ps_server_start_on: null argument");
+  const std::string sched = scheduler ? scheduler : "fifo";
+  RS_REQUIRE(sched == "fifo" || sched == "priority", "rs_ps_server_start_on: scheduler must be fifo or priority");
+  RS_NOEXCEPT_BODY(
+    auto* s = new PsServer(static_cast<CachePS*>(ps), port, workers, sched, levels, host);
     const int rc = s->Start();
     if (rc != RS_OK) { delete s; return rc; }
     *server_out = s;

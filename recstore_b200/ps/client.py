@@ -46,6 +46,7 @@ _lib.register_signatures({
     "rs_ps_load": (i32, [vp, cstr]),
     "rs_ps_server_start": (i32, [vp, i32, C.POINTER(vp), C.POINTER(i32)]),
     "rs_ps_server_start_pool": (i32, [vp, i32, i32, cstr, i32, C.POINTER(vp), C.POINTER(i32)]),
+    "rs_ps_server_start_on": (i32, [vp, cstr, i32, i32, cstr, i32, C.POINTER(vp), C.POINTER(i32)]),
     "rs_ps_server_stop": (i32, [vp]),
     "rs_ps_server_monitor_start": (i32, [vp, i32, i32]),
     "rs_ps_server_monitor_stop": (i32, [vp]),
@@ -209,14 +210,18 @@ class ParameterServer:
         return int(self._l.rs_ps_size(self._h))
 
     # serving ----------------------------------------------------------
-    def serve(self, port: int = 0, workers: int = 0, scheduler: str = "fifo", levels: int = 7) -> int:
+    def serve(self, port: int = 0, workers: int = 0, scheduler: str = "fifo", levels: int = 7, host: str = "127.0.0.1") -> int:
         """Starts the loopback server; returns the bound port (``port=0`` picks a free one).  ``workers=0``: each
         connection's thread executes its requests (the reference's synchronous server); ``workers>0``: connection
         threads hand requests to a pool of worker threads through a ``"fifo"`` or ``"priority"`` task provider
         (the asynchronous server and the schedulers of src/grpc_ps/provider.h); answers keep request order per
-        connection."""
+        connection.  ``host``: the IPv4 address to listen on (loopback by default; ``"0.0.0.0"`` for every interface,
+        which is what the reference's server does)."""
         s, p = vp(), i32()
-        if workers > 0:
+        if host not in ("127.0.0.1", "localhost"):
+            _lib.call("rs_ps_server_start_on", self._h, host.encode(), int(port), int(workers), scheduler.encode(), int(levels),
+                      C.byref(s), C.byref(p))
+        elif workers > 0:
             _lib.call("rs_ps_server_start_pool", self._h, int(port), int(workers), scheduler.encode(), int(levels), C.byref(s), C.byref(p))
         else:
             _lib.call("rs_ps_server_start", self._h, int(port), C.byref(s), C.byref(p))

@@ -491,3 +491,22 @@ def test_client_benchmark_thread_cut_off_reports_every_thread_count():
     assert out["mode"] == "closed_cut_off" and [c["threads"] for c in out["by_threads"]] == [5, 3, 1]
     assert all(c["keys_per_s"] > 0 for c in out["by_threads"]) and out["seconds"] < 60
     srv.close()
+
+
+def test_server_listens_on_the_address_it_is_given():
+    """Loopback by default; any IPv4 address on request (the reference's server listens on 0.0.0.0)."""
+    from recstore_b200.ps import ParameterClient, ParameterServer
+    srv = ParameterServer("KVEngineMap", {"dim": 4, "capacity": 1000})
+    port = srv.serve(0, host="0.0.0.0", workers=2)
+    cli = ParameterClient("127.0.0.1", port, 0, 4)
+    cli.PutParameter(torch.tensor([3]), torch.ones(1, 4))
+    assert torch.equal(cli.GetParameter(torch.tensor([3])), torch.ones(1, 4)) and cli.Stats()["pooled_requests"] >= 2
+    cli.close()
+    srv.close()
+    bad = ParameterServer("KVEngineMap", {"dim": 4, "capacity": 1000})
+    with pytest.raises(Exception, match="not an IPv4 address"):
+        bad.serve(0, host="not-an-address")
+    with pytest.raises(Exception, match="cannot listen"):
+        bad.serve(0, host="203.0.113.7")                      # a documentation address: not on this machine
+    assert bad.serve(0) > 0                                   # the shard is still usable
+    bad.close()
