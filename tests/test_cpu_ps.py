@@ -510,3 +510,62 @@ def test_server_listens_on_the_address_it_is_given():
         bad.serve(0, host="203.0.113.7")                      # a documentation address: not on this machine
     assert bad.serve(0) > 0                                   # the shard is still usable
     bad.close()
+
+
+@pytest.mark.parametrize("transport", ["tcp", "grpc"])
+def test_stand_alone_server_process_serves_until_sigterm_and_saves(tmp_path, transport):
+    """`python -m recstore_b200.ps.server`: a shard as a process of its own (the reference's grpc_ps_server binary):
+    ready line, warm-up of its partition, requests from a client, SIGTERM -> checkpoint -> a second server restores it."""
+    import os, re, signal, subprocess, sys, time
+    from recstore_b200.ps import ParameterClient
+    from recstore_b200.ps.client import ShardManager
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ck = str(tmp_path / "shard.ckpt")
+
+    def start(*extra):
+        import queue, threading
+        p = subprocess.Popen([sys.executable, "-m", "recstore_b200.ps.server", "--port", "0", "--dim", "8", "--capacity", "20000",
+                              "--transport", transport, "--workers", "2", *extra],
+                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=root)
+        q = queue.Queue()
+        threading.Thread(target=lambda: [q.put(l) for l in iter(p.stdout.readline, "")], daemon=True).start()
+        lines, t0 = [], time.time()
+        while time.time() - t0 < 120 and p.poll() is None:
+            try:
+                line = q.get(timeout=0.5)
+            except queue.Empty:
+                continue
+            lines.append(line)
+            m = re.search(r"listening on [0-9.]+:([0-9]+)", line)
+            if m:
+                p._lines = q                               # what it prints later is read from here
+                return p, int(m.group(1)), lines
+        p.kill()
+        raise AssertionError("the server never got ready: " + "".join(lines))
+
+    def client(port):
+        if transport == "grpc":
+            from recstore_b200.ps.grpc_transport import GrpcParameterClient
+            return GrpcParameterClient("127.0.0.1", port, 0, 8)
+        return ParameterClient("127.0.0.1", port, 0, 8)
+    p, port, lines = start("--warm", "3000", "--shard_id", "1", "--num_shards", "2", "--save_on_exit", ck)
+    mine = int((ShardManager.KeyPartition(torch.arange(1, 3001), 2) == 1).sum())
+    assert any(f"warmed {mine} keys of shard 1/2" in l for l in lines)
+    c = client(port)
+    k = torch.arange(1, 3001)
+    own = ShardManager.KeyPartition(k, 2) == 1
+    got = c.GetParameter(k)
+    assert torch.equal(got[own][:, 0], k[own].float()) and float(got[~own].abs().sum()) == 0      # only this shard's keys are here
+    c.PutParameter(torch.tensor([777777]), torch.full((1, 8), 5.0))
+    c.close()
+    p.send_signal(signal.SIGTERM)
+    assert p.wait(timeout=60) == 0
+    time.sleep(0.2)
+    out = "".join(p._lines.get() for _ in range(p._lines.qsize()))
+    assert '"stopped"' in out and os.path.exists(ck)
+    p2, port2, _ = start("--load_ckpt", ck)
+    c2 = client(port2)
+    assert torch.equal(c2.GetParameter(torch.tensor([777777])), torch.full((1, 8), 5.0)) and c2.Stats()["keys_stored"] == mine + 1
+    c2.close()
+    p2.send_signal(signal.SIGINT)
+    assert p2.wait(timeout=60) == 0
