@@ -160,3 +160,22 @@ def test_runs_on_hosts_go_through_ssh_and_need_every_marker(tmp_path, monkeypatc
     bad = Experiment("h2", f"{sys.executable} {job}", {"x": [1]}, log_root=str(tmp_path / "runs"), hosts=["n1", "bad"], timeout_s=30).run()
     assert [r.status for r in bad] == ["failed"] and bad[0].returncode == 255
     assert "no route" in open(os.path.join(bad[0].directory, "log")).read()
+
+
+def test_sweep_of_the_ps_client_benchmark_against_stand_alone_servers(tmp_path):
+    """The pieces together, as the reference's PS experiments run them: for every configuration the harness starts a
+    server process, waits for its ready line, runs the client benchmark against it and stops the server."""
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    py = sys.executable
+    exp = Experiment("ps_sweep", f"{py} -m recstore_b200.bench.ps_client --host 127.0.0.1 --seconds 0.4 --key-space 5000 --batch 64",
+                     {"threads": [1, 2]}, fixed={"port": port, "dim": 8}, log_root=str(tmp_path / "runs"), timeout_s=120,
+                     marker='"keys_per_s"',
+                     servers=[{"command": f"{py} -m recstore_b200.ps.server --port {{port}} --dim {{dim}} --capacity 20000 --load_fake 5000 --workers 2",
+                               "ready_marker": "listening on", "ready_timeout_s": 60}],
+                     env={"PYTHONPATH": os.path.dirname(os.path.dirname(os.path.abspath(__file__)))})
+    res = exp.run()
+    assert [r.status for r in res] == ["ok", "ok"], [open(os.path.join(r.directory, "log")).read()[-500:] for r in res]
+    out = json.loads(open(os.path.join(res[1].directory, "log")).read().strip().splitlines()[-1])
+    assert out["threads"] == 2 and out["keys_per_s"] > 1000
+    assert "listening on" in open(os.path.join(res[0].directory, "server_0.log")).read()
