@@ -53,6 +53,10 @@ def parse_args(argv=None):
     p.add_argument("--from_partition_dir", default=None,
                    help="train on existing per-part directories (part_<i>/train.txt in global ids, meta.json), one trainer per part")
     p.add_argument("--engine", default="KVEngineMap", help="KV engine of the server shards")
+    p.add_argument("--servers", nargs="+", default=None, metavar="HOST:PORT",
+                   help="shards that are running already (python -m recstore_b200.ps.server, possibly on other machines; they must "
+                        "have been started with --dim = --hidden_dim, --optimizer rowwise_adagrad and the --lr of this run): "
+                        "none is started here and --num_servers is their count")
     p.add_argument("--test", action="store_true")
     p.add_argument("--save_path", default=None)
     p.add_argument("--seed", type=int, default=0)
@@ -66,9 +70,11 @@ def parse_args(argv=None):
 class ShardedClient:
     """The trainers' view of the servers: keys are routed by ``ShardManager.KeyPartition`` and answers put back in order."""
 
-    def __init__(self, ports: Sequence[int], dim: int):
+    def __init__(self, ports: Sequence, dim: int):
+        """``ports``: one entry per shard, a port on this machine or a ``(host, port)`` pair."""
         from recstore_b200.ps.client import ParameterClient
-        self.clients = [ParameterClient("127.0.0.1", p, shard=i, emb_dim=dim) for i, p in enumerate(ports)]
+        addrs = [("127.0.0.1", p) if isinstance(p, int) else (p[0], int(p[1])) for p in ports]
+        self.clients = [ParameterClient(h, p, shard=i, emb_dim=dim) for i, (h, p) in enumerate(addrs)]
         self.dim = dim
 
     def _route(self, keys: torch.Tensor) -> List[torch.Tensor]:
@@ -169,11 +175,16 @@ def main(argv=None) -> dict:
         parts = K.random_partition(ds.train[0].size, args.num_clients, args.seed)
     if args.partition_dir:
         info["partition_dirs"] = K.write_partition_files(args.partition_dir, ds, parts, node_part)
-    # ---- servers: one shard each, server-side row-wise Adagrad
-    cap = 1 << max(16, int(np.ceil(np.log2((ds.n_entities + ds.n_relations) * 2 / args.num_servers + 1))))
-    servers = [ParameterServer(args.engine, {"dim": args.hidden_dim, "capacity": cap, "optimizer": "rowwise_adagrad", "lr": args.lr})
-               for _ in range(args.num_servers)]
-    ports = [s.serve(0) for s in servers]
+    # ---- servers: one shard each, server-side row-wise Adagrad (started here, or running already)
+    servers = []
+    if args.servers:
+        ports = [(a.rsplit(":", 1)[0], int(a.rsplit(":", 1)[1])) for a in args.servers]
+        args.num_servers = len(ports)
+    else:
+        cap = 1 << max(16, int(np.ceil(np.log2((ds.n_entities + ds.n_relations) * 2 / args.num_servers + 1))))
+        servers = [ParameterServer(args.engine, {"dim": args.hidden_dim, "capacity": cap, "optimizer": "rowwise_adagrad", "lr": args.lr})
+                   for _ in range(args.num_servers)]
+        ports = [s.serve(0) for s in servers]
     boot = ShardedClient(ports, args.hidden_dim)
     g = torch.Generator().manual_seed(args.seed)
     emb_init = (args.gamma + 2.0) / args.hidden_dim
@@ -193,7 +204,8 @@ def main(argv=None) -> dict:
     for p in procs:
         p.join(60)
     out = {"prepared": info, "seconds": time.time() - t0, "workers": [results[r] for r in range(args.num_clients)],
-           "triples_per_s": sum(results[r]["triples_per_s"] for r in results), "server_keys": [len(s) for s in servers]}
+           "triples_per_s": sum(results[r]["triples_per_s"] for r in results),
+           "server_keys": [len(s) for s in servers] if servers else [c.Stats()["keys_stored"] for c in boot.clients]}
     # ---- the trained tables come back for evaluation and the checkpoint
     if args.test or args.save_path:
         ent = boot.pull(torch.arange(ds.n_entities, dtype=torch.int64))

@@ -47,7 +47,9 @@ def build_parser() -> argparse.ArgumentParser:
     return p
 
 
-def main(argv=None, stop_event: "threading.Event | None" = None) -> int:
+def main(argv=None, stop_event: "threading.Event | None" = None, on_ready=None) -> int:
+    """As a process: serves until SIGINT / SIGTERM.  Embedded (a thread of another program): pass ``stop_event`` to end
+    it and ``on_ready(port)`` to learn the bound port."""
     a = build_parser().parse_args(argv)
     from .client import ParameterServer
     cfg = {"dim": a.dim, "capacity": a.capacity, "optimizer": a.optimizer, "lr": a.lr, "eps": a.eps}
@@ -83,6 +85,8 @@ def main(argv=None, stop_event: "threading.Event | None" = None) -> int:
         for sig in (signal.SIGINT, signal.SIGTERM):
             signal.signal(sig, lambda *_: stop.set())
     print(f"listening on {a.host}:{port} ({a.transport}, engine {a.engine}, {len(ps)} keys)", flush=True)
+    if on_ready is not None:
+        on_ready(port)
     while not stop.wait(0.2):
         pass
     if gsrv is not None:

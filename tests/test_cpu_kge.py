@@ -732,3 +732,31 @@ def test_built_in_dataset_layouts_from_fake_files(tmp_path):
     out, info = kge_main.main(["--dataset", "FB15k", "--data_path", str(tmp_path), "--format", "built_in", "--max_step", "4", "--hidden_dim", "8",
                                "--batch_size", "2", "--neg_sample_size", "2", "--log_interval", "1000"])
     assert info["n_entities"] == 3 and out[0]["steps"] == 4
+
+
+def test_kvstore_trainers_against_shards_that_run_already(tmp_path):
+    """`--servers host:port ...`: the trainers use parameter-server processes started elsewhere (here: two stand-alone
+    servers in threads) instead of starting their own -- the multi-machine form of the distributed trainer
+    (dist_train.py / kvserver.py of the reference start servers and clients on the machines of an ip list)."""
+    import queue, threading
+    from recstore_b200.cli import kge_dist
+    from recstore_b200.ps import server as ps_server
+    stops, threads, ports = [], [], []
+    for i in range(2):
+        ev, ready = threading.Event(), queue.Queue()
+        t = threading.Thread(target=ps_server.main, args=(["--port", "0", "--dim", "8", "--capacity", "65536", "--optimizer", "rowwise_adagrad",
+                                                          "--lr", "0.1", "--workers", "2"], ev, ready.put))
+        t.start()
+        ports.append(ready.get(timeout=60))
+        stops.append(ev); threads.append(t)
+    assert len(ports) == 2
+    out = kge_dist.main(["--model_name", "DistMult", "--servers", f"127.0.0.1:{ports[0]}", f"localhost:{ports[1]}", "--num_clients", "2",
+                         "--max_step", "30", "--n_entities", "800", "--n_relations", "6", "--n_triples", "6000", "--hidden_dim", "8",
+                         "--batch_size", "32", "--neg_sample_size", "8", "--lr", "0.1", "--test"])
+    assert sum(out["server_keys"]) == 806 and min(out["server_keys"]) > 200
+    assert all(w["last_loss"] < w["first_loss"] for w in out["workers"]) and 0 < out["test"]["MRR"] <= 1
+    for ev in stops:
+        ev.set()
+    for t in threads:
+        t.join(30)
+    assert not any(t.is_alive() for t in threads)
