@@ -52,6 +52,12 @@ def parse_args(argv=None):
     p.add_argument("--partition_dir", default=None, help="also write the per-part dataset directories there")
     p.add_argument("--from_partition_dir", default=None,
                    help="train on existing per-part directories (part_<i>/train.txt in global ids, meta.json), one trainer per part")
+    p.add_argument("--loss_genre", "-lg", default="Logsigmoid", choices=["Hinge", "Logistic", "Logsigmoid", "BCE"])
+    p.add_argument("--margin", "-m", type=float, default=1.0, help="margin of the hinge loss")
+    p.add_argument("--neg_adversarial_sampling", "-adv", action="store_true", help="weigh a positive's negatives by softmax(score * temperature)")
+    p.add_argument("--adversarial_temperature", "-a", type=float, default=1.0)
+    p.add_argument("--regularization_coef", "-rc", type=float, default=0.0, help="Lp penalty on the rows a step touches")
+    p.add_argument("--regularization_norm", "-rn", type=int, default=3)
     p.add_argument("--engine", default="KVEngineMap", help="KV engine of the server shards")
     p.add_argument("--servers", nargs="+", default=None, metavar="HOST:PORT",
                    help="shards that are running already (python -m recstore_b200.ps.server, possibly on other machines; they must "
@@ -120,7 +126,10 @@ def trainer(rank: int, args, triples, ports, queue) -> None:
         re = rel[rel_inv]
         pos = edge_score(args.model_name, he, re, te, args.gamma, None, emb_init)
         negs = chunk_neg_score(args.model_name, he, re, te, ne, corrupt_head, args.neg_chunk_size, args.gamma, None, emb_init)
-        loss = kg_loss(pos, negs)
+        loss = kg_loss(pos, negs, args.loss_genre, args.margin, args.neg_adversarial_sampling, args.adversarial_temperature)
+        if args.regularization_coef > 0:         # on the distinct rows of the step (general_models.py:623-629)
+            loss = loss + args.regularization_coef * (ent.norm(p=args.regularization_norm) ** args.regularization_norm +
+                                                      rel.norm(p=args.regularization_norm) ** args.regularization_norm)
         loss.backward()
         ps.push(ent_ids, ent.grad, update=True)
         ps.push(rel_ids + REL_BASE, rel.grad, update=True)

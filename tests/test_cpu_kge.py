@@ -760,3 +760,15 @@ def test_kvstore_trainers_against_shards_that_run_already(tmp_path):
     for t in threads:
         t.join(30)
     assert not any(t.is_alive() for t in threads)
+
+
+def test_distributed_trainer_takes_the_loss_options():
+    """Self-adversarial negatives, the other loss genres and the Lp penalty in the KVStore trainer (the reference's
+    distributed mode takes the same CommonArgParser flags as its single-box trainer)."""
+    from recstore_b200.cli import kge_dist
+    base = ["--num_servers", "1", "--num_clients", "1", "--max_step", "40", "--n_entities", "400", "--n_relations", "5", "--n_triples", "4000",
+            "--hidden_dim", "8", "--batch_size", "32", "--neg_sample_size", "8", "--gamma", "6"]
+    for extra in (["-adv", "-a", "0.5"], ["--loss_genre", "Hinge", "--margin", "2.0"], ["-lg", "Logistic", "-rc", "1e-4", "-rn", "2"], ["-lg", "BCE"]):
+        out = kge_dist.main(base + extra)
+        w = out["workers"][0]
+        assert w["last_loss"] < w["first_loss"] and w["last_loss"] == w["last_loss"], (extra, w)
