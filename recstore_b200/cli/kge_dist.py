@@ -26,7 +26,7 @@ import numpy as np
 import torch
 
 REL_BASE = 1 << 40          # relation r is key REL_BASE + r: one key space for both tables
-DIST_MODELS = ("TransE", "TransE_l1", "TransE_l2", "DistMult", "ComplEx", "SimplE")
+DIST_MODELS = ("TransE", "TransE_l1", "TransE_l2", "DistMult", "ComplEx", "SimplE", "RotatE")
 
 
 def parse_args(argv=None):
@@ -114,6 +114,8 @@ def trainer(rank: int, args, triples, ports, queue) -> None:
     smp = ChunkedNegativeSampler(triples, args.n_entities, args.batch_size, args.neg_sample_size, args.neg_chunk_size,
                                  seed=args.seed * 100 + rank)
     emb_init = (args.gamma + 2.0) / args.hidden_dim
+    from recstore_b200.baseline.kge_torch import relation_dim
+    rel_dim = relation_dim(args.model_name, args.hidden_dim)
     losses, t0 = [], time.time()
     for step in range(args.max_step):
         h, r, t, neg, corrupt_head = next(smp)
@@ -123,7 +125,7 @@ def trainer(rank: int, args, triples, ports, queue) -> None:
         rel = ps.pull(rel_ids + REL_BASE).requires_grad_(True)
         bs = h.numel()
         he, te, ne = ent[ent_inv[:bs]], ent[ent_inv[bs:2 * bs]], ent[ent_inv[2 * bs:]]
-        re = rel[rel_inv]
+        re = rel[rel_inv][:, :rel_dim]               # RotatE: a relation is hidden_dim / 2 phases; the shard's rows are hidden_dim wide
         pos = edge_score(args.model_name, he, re, te, args.gamma, None, emb_init)
         negs = chunk_neg_score(args.model_name, he, re, te, ne, corrupt_head, args.neg_chunk_size, args.gamma, None, emb_init)
         loss = kg_loss(pos, negs, args.loss_genre, args.margin, args.neg_adversarial_sampling, args.adversarial_temperature)
@@ -218,7 +220,8 @@ def main(argv=None) -> dict:
     # ---- the trained tables come back for evaluation and the checkpoint
     if args.test or args.save_path:
         ent = boot.pull(torch.arange(ds.n_entities, dtype=torch.int64))
-        rel = boot.pull(torch.arange(ds.n_relations, dtype=torch.int64) + REL_BASE)
+        from recstore_b200.baseline.kge_torch import relation_dim
+        rel = boot.pull(torch.arange(ds.n_relations, dtype=torch.int64) + REL_BASE)[:, :relation_dim(args.model_name, args.hidden_dim)].contiguous()
         if args.test and ds.test is not None:
             m = TorchKGE(ds.n_entities, ds.n_relations, args.hidden_dim, args.model_name, args.gamma, args.lr, seed=args.seed)
             m.entity, m.relation = ent, rel

@@ -772,3 +772,23 @@ def test_distributed_trainer_takes_the_loss_options():
         out = kge_dist.main(base + extra)
         w = out["workers"][0]
         assert w["last_loss"] < w["first_loss"] and w["last_loss"] == w["last_loss"], (extra, w)
+
+
+def test_distributed_trainer_rotate_generalises_on_the_planted_graph(tmp_path):
+    """RotatE through the KVStore trainer (relations use half of a shard row): held-out triples of the planted graph."""
+    from recstore_b200.cli import kge_dist, kge_infer
+    ds = K.KGDataset.planted_grid(seed=0)
+    d = tmp_path / "grid"
+    d.mkdir()
+    (d / "entities.tsv").write_text("".join(f"{i}\te{i}\n" for i in range(ds.n_entities)))
+    (d / "relations.tsv").write_text("".join(f"{i}\tr{i}\n" for i in range(ds.n_relations)))
+    for name, split in (("train.txt", ds.train), ("valid.txt", ds.test), ("test.txt", ds.test)):
+        (d / name).write_text("".join(f"{h}\t{r}\t{t}\n" for h, r, t in zip(*(x.tolist() for x in split))))
+    data = ["--dataset", "grid", "--data_path", str(d), "--data_files", "entities.tsv", "relations.tsv", "train.txt", "valid.txt", "test.txt",
+            "--format", "udd_hrt"]
+    kge_dist.main(["--model_name", "RotatE", "--num_servers", "2", "--num_clients", "1", "--max_step", "1500", "--hidden_dim", "16",
+                   "--batch_size", "128", "--neg_sample_size", "32", "--gamma", "6", "--lr", "0.1", "--save_path", str(tmp_path / "ck")] + data)
+    import numpy as np
+    assert np.load(tmp_path / "ck" / "grid_RotatE_relation.npy").shape == (4, 8)
+    res = kge_infer.main(["eval", "--model_path", str(tmp_path / "ck")] + data, return_result=True)
+    assert res["MRR"] > 0.5 and res["HITS@10"] > 0.8, res
