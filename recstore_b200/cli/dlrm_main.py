@@ -100,6 +100,9 @@ def parse_args(argv=None):
                    help="accepted: the dense replicas are always kept identical by the all-reduce")
     p.add_argument("--weighted-pooling", default=None, choices=[None, "fixed", "learned"], help="not offered: bags are summed")
     p.add_argument("--enable-profiling", action="store_true", help="stamp the GPU timer at the phase boundaries and print the timeline")
+    p.add_argument("--heartbeat-timeout", type=float, default=0.0,
+                   help="multi-GPU: seconds without a sign of life after which a rank counts as lost (0: off); the others then "
+                        "raise before their next step instead of waiting for it inside a kernel")
     p.add_argument("--tensor-board-filename", default="", help="directory that receives scalars.jsonl (step, loss, lr, test metrics)")
     p.add_argument("--data-set", default="kaggle", help="accepted; data here is generated (--data-generation)")
     for name in ("--raw-data-file", "--processed-data-file", "--data-trace-file"):
@@ -334,6 +337,12 @@ def run(args) -> dict:
                                           projection_sizes=tuple(args.interaction_branch_sizes),
                                           projection_hidden=(tuple(args.interaction_branch1_hidden),
                                                              tuple(args.interaction_branch2_hidden)), **kw), ctx))
+        if world > 1 and args.heartbeat_timeout > 0:      # liveness word per rank, checked on the host before every launch
+            from recstore_b200.utils.liveness import Heartbeat
+            hb = Heartbeat(rank, world, name=f"dlrm_heartbeat_{os.environ.get('MASTER_PORT', '0')}",
+                           period_s=min(0.2, args.heartbeat_timeout / 5)).start()
+            hb.wait_all_alive(max(60.0, args.heartbeat_timeout))
+            model.e.heartbeat, model.e.heartbeat_timeout_s = hb, args.heartbeat_timeout
     else:
         from recstore_b200.baseline.dlrm_torch import TorchDLRM
         model = _CpuModel(TorchDLRM(rows, args.mini_batch_size, device="cpu", rank=0, world=1,
@@ -385,7 +394,7 @@ def run(args) -> dict:
                "ms_per_batch": (time.time() - t0) / len(accs) * 1e3}
         if rank == 0:
             print(json.dumps(out), flush=True)
-        _teardown(args, world)
+        _teardown(args, world, model)
         return out
     stop = False
     scalars = None
@@ -436,14 +445,17 @@ def run(args) -> dict:
         out["phases_us"] = {k: round(v, 1) for k, v in model.e.phase_times().items()}
     if rank == 0:
         print(json.dumps(out), flush=True)
-    _teardown(args, world)
+    _teardown(args, world, model)
     return out
 
 
-def _teardown(args, world):
+def _teardown(args, world, model=None):
     if args.use_gpu and world > 1:
         import torch.distributed as dist
         dist.barrier()
+        hb = getattr(getattr(model, "e", None), "heartbeat", None)
+        if hb is not None:                   # after the barrier: a rank that finishes early keeps beating until all are done
+            hb.stop(leaving=True)
         dist.destroy_process_group()
 
 
