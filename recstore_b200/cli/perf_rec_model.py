@@ -24,6 +24,8 @@ def parse_args(argv=None):
     p.add_argument("--emb_dim", type=int, default=32)
     p.add_argument("--L", type=int, default=10)
     p.add_argument("--with_perf", action="store_true")
+    p.add_argument("--profile_dir", default=None,
+                   help="record three steps (after three warm-up steps) with torch.profiler: trace_rank{r}.json + ops_rank{r}.txt")
     p.add_argument("--batch_size", type=int, default=1024)
     p.add_argument("--cache_ratio", type=float, default=0.1)
     p.add_argument("--log_interval", type=int, default=50)
@@ -131,6 +133,8 @@ def routine(rank: int, args, port: int, ns: str, out=None):
     for s, b in enumerate(future):
         publish(s, b.reshape(-1))
     t_step = Timer("OneStep")
+    from recstore_b200.utils.profiling import StepProfiler
+    prof = StepProfiler(args.profile_dir, rank)
     t0 = time.time()
     worst = 0.0
     last_loss = float("nan")
@@ -167,6 +171,7 @@ def routine(rank: int, args, port: int, ns: str, out=None):
                     if gopt_nn is not None:
                         gopt_nn.step()
             abs_emb.after_backward()
+        prof.step()
         steps_done += 1
         if rank == 0 and (step + 1) % args.log_interval == 0:
             el = time.time() - t0
@@ -178,6 +183,7 @@ def routine(rank: int, args, port: int, ns: str, out=None):
         dist.all_reduce(stop)
         if int(stop.item()) > 0:
             break
+    prof.finish()
     ctrl.GraceFullyStopThreads()
     dist.barrier()
     if rank == 0:
