@@ -11,7 +11,7 @@ Sub-packages
 
 The native library is built in-tree (``python -m recstore_b200.build``) and bound with ctypes.
 """
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 from . import _lib  # noqa: F401
 from ._lib import RecStoreError, DeviceStatusError  # noqa: F401
