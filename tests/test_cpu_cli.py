@@ -340,3 +340,30 @@ def test_packaging_metadata_names_real_entry_points():
     for name, target in cfg["project"]["scripts"].items():
         mod, fn = target.split(":")
         assert callable(getattr(importlib.import_module(mod), fn)), (name, target)
+
+
+def test_migration_guide_names_things_that_exist():
+    """Every `recstore_b200....` name and every `python -m recstore_b200....` module of the migration guide resolves."""
+    import importlib
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "MIGRATION.md")).read()
+    names = set(re.findall(r"`(recstore_b200(?:\.\w+)+)", text)) | set(re.findall(r"python -m (recstore_b200(?:\.\w+)+)", text))
+    assert len(names) > 25
+    for dotted in sorted(names):
+        parts = dotted.split(".")
+        obj = None
+        for cut in range(len(parts), 0, -1):
+            try:
+                obj = importlib.import_module(".".join(parts[:cut]))
+            except ModuleNotFoundError:
+                continue
+            for attr in parts[cut:]:
+                assert hasattr(obj, attr), f"{dotted}: {'.'.join(parts[:cut])} has no {attr}"
+                obj = getattr(obj, attr)
+            break
+        assert obj is not None, dotted
+    for fn in re.findall(r"`(rs\.\w+)`?", text):
+        import recstore_b200 as rs
+        assert hasattr(rs, fn.split(".")[1]), fn
