@@ -156,6 +156,15 @@ class ShardedEmbeddingTable:
         self._n = 0
         self.launches = 0
 
+    def close(self) -> None:
+        """Collective: gives the five exchange windows back to the context (with a symmetric heap their bytes are reused
+        by the next table; otherwise they are unmapped and freed).  The table must not be used afterwards."""
+        for w in ("key_win", "count_win", "row_win", "grad_win", "norm_win"):
+            win = getattr(self, w, None)
+            if win is not None and win.name in self.ctx.windows:
+                self.ctx.free(win.name)
+            setattr(self, w, None)
+
     def __del__(self):
         try:
             if self._ht:
