@@ -26,7 +26,10 @@ import numpy as np
 import torch
 
 REL_BASE = 1 << 40          # relation r is key REL_BASE + r: one key space for both tables
-DIST_MODELS = ("TransE", "TransE_l1", "TransE_l2", "DistMult", "ComplEx", "SimplE", "RotatE")
+PROJ_BASE = 1 << 41         # TransR / RESCAL: row i of relation r's hidden_dim x hidden_dim matrix is key PROJ_BASE + r * hidden_dim + i
+                            # (a matrix is hidden_dim shard rows; the server keeps one Adagrad state per ROW of it, where the
+                            # single-box trainers keep one per matrix)
+DIST_MODELS = ("TransE", "TransE_l1", "TransE_l2", "DistMult", "ComplEx", "SimplE", "RotatE", "TransR", "RESCAL")
 
 
 def parse_args(argv=None):
@@ -116,6 +119,7 @@ def trainer(rank: int, args, triples, ports, queue) -> None:
     emb_init = (args.gamma + 2.0) / args.hidden_dim
     from recstore_b200.baseline.kge_torch import relation_dim
     rel_dim = relation_dim(args.model_name, args.hidden_dim)
+    matrix_model = args.model_name in ("TransR", "RESCAL")
     losses, t0 = [], time.time()
     for step in range(args.max_step):
         h, r, t, neg, corrupt_head = next(smp)
@@ -126,15 +130,24 @@ def trainer(rank: int, args, triples, ports, queue) -> None:
         bs = h.numel()
         he, te, ne = ent[ent_inv[:bs]], ent[ent_inv[bs:2 * bs]], ent[ent_inv[2 * bs:]]
         re = rel[rel_inv][:, :rel_dim]               # RotatE: a relation is hidden_dim / 2 phases; the shard's rows are hidden_dim wide
-        pos = edge_score(args.model_name, he, re, te, args.gamma, None, emb_init)
-        negs = chunk_neg_score(args.model_name, he, re, te, ne, corrupt_head, args.neg_chunk_size, args.gamma, None, emb_init)
+        proj = mat = None
+        if matrix_model:
+            D = args.hidden_dim
+            mat_keys = (rel_ids.unsqueeze(1) * D + torch.arange(D)).reshape(-1) + PROJ_BASE
+            mat = ps.pull(mat_keys).requires_grad_(True)            # [distinct relations * D, D]
+            proj = mat.view(rel_ids.numel(), D * D)[rel_inv]
+        pos = edge_score(args.model_name, he, re, te, args.gamma, proj, emb_init)
+        negs = chunk_neg_score(args.model_name, he, re, te, ne, corrupt_head, args.neg_chunk_size, args.gamma, proj, emb_init)
         loss = kg_loss(pos, negs, args.loss_genre, args.margin, args.neg_adversarial_sampling, args.adversarial_temperature)
         if args.regularization_coef > 0:         # on the distinct rows of the step (general_models.py:623-629)
             loss = loss + args.regularization_coef * (ent.norm(p=args.regularization_norm) ** args.regularization_norm +
                                                       rel.norm(p=args.regularization_norm) ** args.regularization_norm)
         loss.backward()
         ps.push(ent_ids, ent.grad, update=True)
-        ps.push(rel_ids + REL_BASE, rel.grad, update=True)
+        if rel.grad is not None:                     # RESCAL scores with the matrix only
+            ps.push(rel_ids + REL_BASE, rel.grad, update=True)
+        if mat is not None:
+            ps.push(mat_keys, mat.grad, update=True)
         losses.append(loss.item())
     el = time.time() - t0
     ps.close()
@@ -192,14 +205,18 @@ def main(argv=None) -> dict:
         ports = [(a.rsplit(":", 1)[0], int(a.rsplit(":", 1)[1])) for a in args.servers]
         args.num_servers = len(ports)
     else:
-        cap = 1 << max(16, int(np.ceil(np.log2((ds.n_entities + ds.n_relations) * 2 / args.num_servers + 1))))
+        n_keys = ds.n_entities + ds.n_relations * (1 + (args.hidden_dim if args.model_name in ("TransR", "RESCAL") else 0))
+        cap = 1 << max(16, int(np.ceil(np.log2(n_keys * 2 / args.num_servers + 1))))
         servers = [ParameterServer(args.engine, {"dim": args.hidden_dim, "capacity": cap, "optimizer": "rowwise_adagrad", "lr": args.lr})
                    for _ in range(args.num_servers)]
         ports = [s.serve(0) for s in servers]
     boot = ShardedClient(ports, args.hidden_dim)
     g = torch.Generator().manual_seed(args.seed)
     emb_init = (args.gamma + 2.0) / args.hidden_dim
-    for base, n in ((0, ds.n_entities), (REL_BASE, ds.n_relations)):      # U(+-emb_init), as the single-box trainers start
+    tables = [(0, ds.n_entities), (REL_BASE, ds.n_relations)]
+    if args.model_name in ("TransR", "RESCAL"):
+        tables.append((PROJ_BASE, ds.n_relations * args.hidden_dim))
+    for base, n in tables:                                                # U(+-emb_init), as the single-box trainers start
         for lo in range(0, n, 65536):
             k = torch.arange(lo, min(n, lo + 65536), dtype=torch.int64)
             boot.push(k + base, (torch.rand(k.numel(), args.hidden_dim, generator=g) * 2 - 1) * emb_init, update=False)
@@ -225,12 +242,17 @@ def main(argv=None) -> dict:
         if args.test and ds.test is not None:
             m = TorchKGE(ds.n_entities, ds.n_relations, args.hidden_dim, args.model_name, args.gamma, args.lr, seed=args.seed)
             m.entity, m.relation = ent, rel
+            if args.model_name in ("TransR", "RESCAL"):
+                m.proj = boot.pull(torch.arange(ds.n_relations * args.hidden_dim, dtype=torch.int64) + PROJ_BASE).view(ds.n_relations, -1)
             th, tr, tt = (torch.as_tensor(x[:1024]) for x in ds.test)
             out["test"] = m.evaluate(th, tr, tt, 256, torch.Generator().manual_seed(5))
         if args.save_path:
             os.makedirs(args.save_path, exist_ok=True)
             np.save(os.path.join(args.save_path, f"{ds.name}_{args.model_name}_entity.npy"), ent.numpy())
             np.save(os.path.join(args.save_path, f"{ds.name}_{args.model_name}_relation.npy"), rel.numpy())
+            if args.model_name in ("TransR", "RESCAL"):
+                prj = boot.pull(torch.arange(ds.n_relations * args.hidden_dim, dtype=torch.int64) + PROJ_BASE)
+                np.save(os.path.join(args.save_path, f"{ds.name}_{args.model_name}projection.npy"), prj.view(ds.n_relations, -1).numpy())
             with open(os.path.join(args.save_path, "config.json"), "w") as f:
                 json.dump({"dataset": ds.name, "model_name": args.model_name, "hidden_dim": args.hidden_dim, "gamma": args.gamma,
                            "emp_file": f"{ds.name}_{args.model_name}_entity.npy",

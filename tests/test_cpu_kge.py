@@ -792,3 +792,20 @@ def test_distributed_trainer_rotate_generalises_on_the_planted_graph(tmp_path):
     assert np.load(tmp_path / "ck" / "grid_RotatE_relation.npy").shape == (4, 8)
     res = kge_infer.main(["eval", "--model_path", str(tmp_path / "ck")] + data, return_result=True)
     assert res["MRR"] > 0.5 and res["HITS@10"] > 0.8, res
+
+
+@pytest.mark.parametrize("model", ["TransR", "RESCAL"])
+def test_distributed_trainer_matrix_models(model, tmp_path):
+    """TransR and RESCAL through the KVStore trainer: every relation's matrix is hidden_dim rows of the shards; the
+    checkpoint has the projection file and the evaluation tool scores with it."""
+    import numpy as np
+    from recstore_b200.cli import kge_dist, kge_infer
+    data = ["--n_entities", "300", "--n_relations", "4", "--n_triples", "3000"]
+    out = kge_dist.main(["--model_name", model, "--num_servers", "2", "--num_clients", "2", "--max_step", "60", "--hidden_dim", "8",
+                         "--batch_size", "32", "--neg_sample_size", "8", "--gamma", "6", "--lr", "0.1", "--test", "--save_path", str(tmp_path / "ck")] + data)
+    assert sum(out["server_keys"]) == 300 + 4 + 4 * 8                       # entities, relation vectors, matrix rows
+    assert all(w["last_loss"] < w["first_loss"] for w in out["workers"]) and 0 < out["test"]["MRR"] <= 1
+    prj = np.load(tmp_path / "ck" / f"synthetic_{model}projection.npy")
+    assert prj.shape == (4, 64) and np.abs(prj).sum() > 0
+    res = kge_infer.main(["eval", "--model_path", str(tmp_path / "ck"), "--neg_sample_size_eval", "64"] + data, return_result=True)
+    assert res["model"] == model and 1.0 <= res["MR"] <= 65
