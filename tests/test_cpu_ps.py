@@ -569,3 +569,32 @@ def test_stand_alone_server_process_serves_until_sigterm_and_saves(tmp_path, tra
     c2.close()
     p2.send_signal(signal.SIGINT)
     assert p2.wait(timeout=60) == 0
+
+
+@pytest.mark.parametrize("engine", ["KVEngineChunkHash", "KVEnginePoolMap"])
+def test_server_on_a_persistent_engine_restarts_with_rows_and_optimizer_state(tmp_path, engine):
+    """A shard whose engine lives in files needs no checkpoint to restart: the rows are there, and so is the row-wise
+    Adagrad state (the second update of a row after the restart is smaller than the first by 1 / sqrt(2))."""
+    import queue, threading
+    from recstore_b200.ps import ParameterClient, server
+    argv = ["--port", "0", "--dim", "8", "--capacity", "5000", "--engine", engine, "--path", str(tmp_path / "shard"), "--lr", "0.01"]
+
+    def start():
+        ev, ready = threading.Event(), queue.Queue()
+        t = threading.Thread(target=server.main, args=(argv, ev, ready.put))
+        t.start()
+        return ev, t, ParameterClient("127.0.0.1", ready.get(timeout=60), 0, 8)
+    ev, t, c = start()
+    c.PutParameter(torch.arange(100), torch.arange(100).float().unsqueeze(1).expand(-1, 8).contiguous())
+    c.UpdateParameter(torch.tensor([5]), torch.ones(1, 8))
+    v5 = c.GetParameter(torch.tensor([5]))
+    assert torch.allclose(v5, torch.full((1, 8), 5.0 - 0.01), atol=1e-6)
+    c.close(); ev.set(); t.join(30)
+    ev, t, c = start()
+    got = c.GetParameter(torch.arange(100))
+    assert c.Stats()["keys_stored"] == 100 and torch.equal(got[7], torch.full((8,), 7.0)) and torch.equal(got[5:6], v5)
+    c.UpdateParameter(torch.tensor([5]), torch.ones(1, 8))
+    step2 = float((v5 - c.GetParameter(torch.tensor([5]))).abs().max())
+    assert step2 == pytest.approx(0.01 / 2 ** 0.5, rel=1e-3)
+    c.close(); ev.set(); t.join(30)
+    assert not t.is_alive()
