@@ -598,3 +598,44 @@ def test_server_on_a_persistent_engine_restarts_with_rows_and_optimizer_state(tm
     assert step2 == pytest.approx(0.01 / 2 ** 0.5, rel=1e-3)
     c.close(); ev.set(); t.join(30)
     assert not t.is_alive()
+
+
+@pytest.mark.parametrize("engine", ["KVEngineChunkHash", "KVEnginePoolMap"])
+def test_server_process_killed_without_warning_recovers_its_rows(tmp_path, engine):
+    """Crash recovery at the level a user sees: the shard process is killed (SIGKILL: no flush, no goodbye), a new one on
+    the same directory serves every row that had been acknowledged."""
+    import os, queue, re, signal, subprocess, sys, threading, time
+    from recstore_b200.ps import ParameterClient
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "recstore_b200.ps.server", "--port", "0", "--dim", "8", "--capacity", "20000", "--engine", engine,
+           "--path", str(tmp_path / "shard")]
+
+    def start():
+        p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=root)
+        q = queue.Queue()
+        threading.Thread(target=lambda: [q.put(l) for l in iter(p.stdout.readline, "")], daemon=True).start()
+        t0 = time.time()
+        while time.time() - t0 < 120 and p.poll() is None:
+            try:
+                m = re.search(r"listening on [0-9.]+:([0-9]+)", q.get(timeout=0.5))
+            except queue.Empty:
+                continue
+            if m:
+                return p, int(m.group(1))
+        p.kill()
+        raise AssertionError("the server never got ready")
+    p, port = start()
+    c = ParameterClient("127.0.0.1", port, 0, 8)
+    keys = torch.arange(1, 5001)
+    c.PutParameter(keys, keys.float().unsqueeze(1).expand(-1, 8).contiguous())
+    assert c.Stats()["keys_stored"] == 5000                  # every put above has been answered
+    c.close()
+    os.kill(p.pid, signal.SIGKILL)                           # this test's own child, by its pid
+    assert p.wait(timeout=30) == -signal.SIGKILL
+    p2, port2 = start()
+    c2 = ParameterClient("127.0.0.1", port2, 0, 8)
+    got, found = c2.GetParameterWithMask(keys)
+    assert bool(found.all()) and torch.equal(got[:, 0], keys.float()) and torch.equal(got[:, 7], keys.float())
+    c2.close()
+    p2.send_signal(signal.SIGTERM)
+    assert p2.wait(timeout=60) == 0
