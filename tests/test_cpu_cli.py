@@ -367,3 +367,33 @@ def test_migration_guide_names_things_that_exist():
     for fn in re.findall(r"`(rs\.\w+)`?", text):
         import recstore_b200 as rs
         assert hasattr(rs, fn.split(".")[1]), fn
+
+
+def test_checkpoint_written_by_three_ranks_loads_on_one_and_on_two(tmp_path):
+    """Tables are filed by table index, not by rank: a save of three ranks restores on one rank and on two (each rank
+    reads the tables it owns under the new placement)."""
+    import torch
+    from recstore_b200.baseline.dlrm_torch import TorchDLRM
+    from recstore_b200.models.checkpoint import load_checkpoint, save_checkpoint
+    rows = [30, 200, 17, 64, 9]
+    kw = dict(emb_dim=8, bottom_mlp=(16, 8), top_mlp=(16, 1), num_dense=4)
+    savers = [TorchDLRM(rows, 30, rank=r, world=3, seed=1, **kw) for r in range(3)]
+    assert sorted(t for m in savers for t in m.local_tables) == list(range(5))
+    for m in savers:
+        for t in m.local_tables:
+            m.table_weight(t).add_(t + 1.0)                  # make every table recognisable
+            m.table_state(t).fill_(0.5 + t)
+    for m in reversed(savers):                               # rank 0 (dense + meta.json) last, as after a barrier
+        save_checkpoint(m, str(tmp_path / "ck"), step=9)
+    truth = {t: (m.table_weight(t).clone(), m.table_state(t).clone()) for m in savers for t in m.local_tables}
+    one = TorchDLRM(rows, 30, rank=0, world=1, seed=5, **kw)
+    meta = load_checkpoint(one, str(tmp_path / "ck"))
+    assert meta["step"] == 9 and meta["world_at_save"] == 3
+    for t in range(5):
+        assert torch.equal(one.table_weight(t), truth[t][0]) and torch.equal(one.table_state(t), truth[t][1])
+    for k, v in savers[0].dense_state().items():
+        assert torch.equal(one.dense_state()[k], v)
+    for r in range(2):
+        two = TorchDLRM(rows, 30, rank=r, world=2, seed=7, **kw)
+        load_checkpoint(two, str(tmp_path / "ck"))
+        assert all(torch.equal(two.table_weight(t), truth[t][0]) for t in two.local_tables) and len(two.local_tables) in (2, 3)
