@@ -6,7 +6,10 @@ Sub-packages
 ``ops``       native kernels (tcgen05 GEMM, fused embedding forward/backward, interaction, losses)
 ``parallel``  in-box NVLink transport: peer windows, flags, all-reduce, sharding policies
 ``models``    DLRM (dot / DCNv2), SimpleDLRM, knowledge-graph embedding models
-``utils``     synthetic data, timers, logging
+``utils``     synthetic data, timers, logging, liveness (heartbeat), profiler windows
+``cache``     cached embeddings, GPU cache, tiered and lookahead tables
+``ps``        parameter server: shard process, clients (TCP, gRPC, NVLink), load generation
+``cli``       drivers (DLRM, KG training / inference / distributed, micro-benchmarks)
 ``baseline``  PyTorch + NCCL restatements of the reference algorithms (oracle and measured baseline)
 
 The native library is built in-tree (``python -m recstore_b200.build``) and bound with ctypes.
@@ -21,3 +24,4 @@ from .dist_tensor import DistTensor, DistEmbedding, HbmDistEmbedding, PartitionP
 from . import dist_opt as DistOpt  # noqa: F401,E402
 from .dist_opt import SparseSGD, SparseAdagrad, SparseRowWiseAdaGrad  # noqa: F401,E402
 from .ipc import IPCTensorFactory, SlicedTensor, MultiProcessBarrierFactory, Mfence  # noqa: F401,E402
+from .utils.liveness import Heartbeat, RankLostError  # noqa: F401,E402
