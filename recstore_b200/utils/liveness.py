@@ -57,8 +57,10 @@ class Heartbeat:
             self._table = None
         else:
             from ..ipc import IPCTensorFactory
-            # [rank] = (beat counter, state)
-            self._table = IPCTensorFactory.NewOrGetIPCTensor(name, (world, 2), torch.int64)
+            # [rank] = (beat counter, state, barrier generation)
+            self._table = IPCTensorFactory.NewOrGetIPCTensor(name, (world, 3), torch.int64)
+        self._gen = 0
+        self._write_gen(0)
         self._write(0, 0)                            # nothing of an earlier owner of this row survives
         self._seen: Dict[int, tuple] = {}            # rank -> (last counter value, local time it changed)
         self._stop = threading.Event()
@@ -72,6 +74,21 @@ class Heartbeat:
             self._table[self.rank, 0] = beats
         else:
             self._store.set(f"{self.name}/{self.rank}", f"{beats} {state}")
+
+    def _write_gen(self, gen: int) -> None:
+        if self._table is not None:
+            self._table[self.rank, 2] = gen
+        else:
+            self._store.set(f"{self.name}/{self.rank}/gen", str(gen))
+
+    def _read_gen(self, r: int) -> int:
+        if self._table is not None:
+            return int(self._table[r, 2])
+        try:
+            k = f"{self.name}/{r}/gen"
+            return int(self._store.get(k).decode()) if self._store.check([k]) else 0
+        except Exception:
+            return -1
 
     def beat(self) -> None:
         """One sign of life (the background thread calls this; a caller without the thread may call it per step)."""
@@ -155,6 +172,18 @@ class Heartbeat:
             if time.monotonic() - t0 > timeout_s:
                 raise RankLostError(st["unseen"], [], timeout_s)
             time.sleep(min(0.02, self.period_s))
+
+    def barrier(self, timeout_s: float = 2.0, poll_s: float = 0.005) -> None:
+        """A host barrier of all ranks that cannot hang on a dead rank: returns when every rank has entered its
+        barrier of the same count (or a later one), raises ``RankLostError`` as soon as one of them is found gone."""
+        self._gen += 1
+        self._write_gen(self._gen)
+        others = [r for r in range(self.world) if r != self.rank]
+        while True:
+            if all(self._read_gen(r) >= self._gen for r in others):
+                return
+            self.check(timeout_s)
+            time.sleep(poll_s)
 
     def __enter__(self):
         return self.start()

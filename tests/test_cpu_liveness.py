@@ -119,3 +119,46 @@ def test_heartbeat_status_unseen_left_and_context_manager():
     time.sleep(0.15)
     assert 1 in a.status(0.1)["lost"]                        # silent for longer than the limit
     ipc.IPCTensorFactory.ClearIPCMemory()
+
+
+def _barrier_worker(rank, world, ns, dies, q):
+    from recstore_b200 import ipc
+    from recstore_b200.utils.liveness import Heartbeat, RankLostError
+    ipc.set_namespace(ns)
+    hb = Heartbeat(rank, world, name="hb_barrier", period_s=0.05).start()
+    hb.wait_all_alive(30.0)
+    done = 0
+    try:
+        for i in range(6):
+            if dies and rank == world - 1 and i == 3:
+                os._exit(0)                                  # gone between barriers, without a word
+            time.sleep(0.01 * rank)                          # ranks arrive at different times
+            hb.barrier(timeout_s=1.5)
+            done += 1
+        hb.stop(leaving=False)
+        q.put((rank, done, None))
+    except RankLostError as e:
+        hb.stop(leaving=False)
+        q.put((rank, done, sorted(e.lost)))
+
+
+@pytest.mark.parametrize("dies", [False, True])
+def test_heartbeat_barrier_releases_together_and_cannot_hang_on_a_dead_rank(dies):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    world, ns = 3, f"pytest_hbb_{os.getpid()}_{int(dies)}"
+    ps = [ctx.Process(target=_barrier_worker, args=(r, world, ns, dies, q)) for r in range(world)]
+    [p.start() for p in ps]
+    expect = world - 1 if dies else world
+    res = dict((r[0], r[1:]) for r in (q.get(timeout=120) for _ in range(expect)))
+    [p.join(30) for p in ps]
+    from recstore_b200 import ipc
+    ipc.set_namespace(ns)
+    ipc.IPCTensorFactory.ClearIPCMemory()
+    if not dies:
+        assert all(res[r] == (6, None) for r in range(world)), res
+    else:
+        for r in range(world - 1):
+            done, lost = res[r]
+            assert done == 3 and lost is not None and world - 1 in lost, res   # three common barriers, then the loss is reported
