@@ -12,6 +12,8 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
+import sys
 import threading
 import time
 
@@ -30,6 +32,17 @@ def make_client(host, port, dim, transport="tcp"):
     return ParameterClient(host, port, 0, dim)
 
 
+def _latency(hists, quiet) -> dict:
+    """The threads' latency histograms merged: percentiles for the JSON line, the bucket table on stderr."""
+    total = hists[0]
+    for h in hists[1:]:
+        total.Merge(h)
+    if not quiet and os.environ.get("RECSTORE_PS_CLIENT_HISTOGRAM"):
+        print(total.ToString(), file=sys.stderr)
+    s = total.summary()
+    return {"lat_us_mean": s["mean"], "lat_us_p50": total.Percentile(50), "lat_us_p99": total.Percentile(99), "lat_us_max": s["max"]}
+
+
 def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, seconds, dataset=None, quiet=False, transport="tcp",
                 cut_off_period=0.0, cut_off_stride=2):
     """``cut_off_period > 0``: the thread cut-off mode of the reference's client benchmark
@@ -39,6 +52,8 @@ def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, secon
     done = [0] * threads
     stop = threading.Event()
     stop_one = [threading.Event() for _ in range(threads)]
+    from ..utils.timer import Histogram
+    hists = [Histogram() for _ in range(threads)]        # request latency in microseconds, issue to completion
 
     def worker(t):
         c = make_client(host, port, dim, transport)
@@ -48,12 +63,13 @@ def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, secon
         while not stop.is_set() and not stop_one[t].is_set():
             while len(inflight) < window:
                 k = next(src)
-                inflight.append((c.GetParameterAsync(k), k.numel()))
-            rid, n = inflight.pop(0)
+                inflight.append((c.GetParameterAsync(k), k.numel(), time.perf_counter()))
+            rid, n, t_issue = inflight.pop(0)
             c.WaitRPCFinish(rid)
+            hists[t].Add((time.perf_counter() - t_issue) * 1e6)
             c.RevokeRPCResource(rid)
             done[t] += n
-        for rid, _ in inflight:
+        for rid, _, _ in inflight:
             c.WaitRPCFinish(rid)
         c.close()
 
@@ -78,7 +94,7 @@ def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, secon
                 ths[alive].join()
         el = time.perf_counter() - t0
         return {"mode": "closed_cut_off", "threads": threads, "window": window, "batch": batch, "keys_per_s": sum(done) / el,
-                "by_threads": curve, "seconds": el}
+                "by_threads": curve, "seconds": el, **_latency(hists, quiet)}
     while time.perf_counter() - t0 < seconds:
         time.sleep(min(1.0, max(0.05, seconds - (time.perf_counter() - t0))))
         now, tot = time.perf_counter(), sum(done)
@@ -92,7 +108,7 @@ def closed_loop(host, port, dim, threads, window, batch, alpha, key_space, secon
         th.join()
     el = time.perf_counter() - t0
     return {"mode": "closed", "threads": threads, "window": window, "batch": batch, "keys_per_s": sum(done) / el,
-            "per_second": per_sec, "seconds": el}
+            "per_second": per_sec, "seconds": el, **_latency(hists, quiet)}
 
 
 def _process_entry(args, q):
@@ -137,7 +153,10 @@ def main(argv=None):
     ap.add_argument("--thread-cut-off", type=float, default=0.0, metavar="SECONDS",
                     help="closed loop: stop --cut-off-stride sender threads every SECONDS and report the throughput per thread count")
     ap.add_argument("--cut-off-stride", type=int, default=2)
+    ap.add_argument("--histogram", action="store_true", help="closed loop: print the request-latency histogram (microseconds) to stderr")
     a = ap.parse_args(argv)
+    if a.histogram:
+        os.environ["RECSTORE_PS_CLIENT_HISTOGRAM"] = "1"
     srv = None
     host, port = a.host, a.port
     if host is None:
