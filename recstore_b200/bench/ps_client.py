@@ -131,7 +131,9 @@ def multi_process(host, port, dim, processes, threads, window, batch, alpha, key
         p.join(30)
     return {"mode": "closed", "processes": processes, "threads": threads, "window": window, "batch": batch,
             "keys_per_s": sum(r["keys_per_s"] for r in res), "per_process": [r["keys_per_s"] for r in res],
-            "seconds": max(r["seconds"] for r in res)}
+            "seconds": max(r["seconds"] for r in res),
+            "lat_us_p50": float(np.median([r["lat_us_p50"] for r in res])), "lat_us_p99": max(r["lat_us_p99"] for r in res),
+            "lat_us_max": max(r["lat_us_max"] for r in res)}
 
 
 def main(argv=None):
