@@ -183,6 +183,8 @@ def main(argv=None) -> dict:
     if args.from_partition_dir:
         ds, parts = _load_partition_dirs(args.from_partition_dir, args.dataset)
         args.num_clients = len(parts)
+    elif args.dataset == "planted_grid":
+        ds = K.KGDataset.planted_grid(seed=args.seed)
     elif args.data_path:
         ds = K.KGDataset.load(args.data_path, args.data_files or ["train.tsv"], args.format, name=args.dataset)
     else:

@@ -188,7 +188,9 @@ def cmd_eval(a) -> int:
         raise SystemExit(f"no saved model in {a.model_path}")
     if a.neg_deg_sample_eval and not a.no_eval_filter and a.neg_sample_size_eval < 0:
         raise SystemExit("degree-based evaluation negatives cannot be combined with the filtered full ranking")
-    if a.dataset == "synthetic" or a.data_path is None:
+    if a.dataset == "planted_grid":
+        ds = K.KGDataset.planted_grid(seed=a.seed)
+    elif a.dataset == "synthetic" or a.data_path is None:
         ds = K.KGDataset.synthetic(a.n_entities, a.n_relations, a.n_triples, seed=a.seed)
     else:
         ds = K.KGDataset.load(a.data_path, a.data_files or ["train.tsv"], a.format, name=a.dataset, delimiter=a.delimiter)

@@ -146,7 +146,9 @@ def _free_port():
 def prepare(args):
     """Dataset -> partitions (-> renumbering).  Returns (dataset, parts, info)."""
     from recstore_b200.utils import kg_data as K
-    if args.dataset == "synthetic" or args.data_path is None:
+    if args.dataset == "planted_grid":            # a small graph with structure to find: quality is visible on it
+        ds = K.KGDataset.planted_grid(seed=args.seed)
+    elif args.dataset == "synthetic" or args.data_path is None:
         ds = K.KGDataset.synthetic(args.n_entities, args.n_relations, args.n_triples, seed=args.seed)
     else:
         ds = K.KGDataset.load(args.data_path, args.data_files or ["train.tsv"], args.format, name=args.dataset,

@@ -809,3 +809,14 @@ def test_distributed_trainer_matrix_models(model, tmp_path):
     assert prj.shape == (4, 64) and np.abs(prj).sum() > 0
     res = kge_infer.main(["eval", "--model_path", str(tmp_path / "ck"), "--neg_sample_size_eval", "64"] + data, return_result=True)
     assert res["model"] == model and 1.0 <= res["MR"] <= 65
+
+
+def test_planted_grid_by_name_through_trainer_and_eval_tool(tmp_path):
+    """`--dataset planted_grid`: the demonstration graph straight from the command lines."""
+    from recstore_b200.cli import kge_infer, kge_main
+    out, info = kge_main.main(["--dataset", "planted_grid", "--model_name", "RotatE", "--hidden_dim", "16", "--gamma", "6", "--lr", "0.1",
+                               "--batch_size", "128", "--neg_sample_size", "32", "--max_step", "1500", "--log_interval", "100000",
+                               "--save_path", str(tmp_path / "ck")])
+    assert info["n_entities"] == 300 and info["n_train"] == 941
+    res = kge_infer.main(["eval", "--model_path", str(tmp_path / "ck"), "--dataset", "planted_grid"], return_result=True)
+    assert res["triples"] == 104 and res["MRR"] > 0.5, res
